@@ -1,0 +1,68 @@
+"""Builds the in-tree CUDA library ``pear_b200/ops/_pear_kernels.so`` for sm_100a with nvcc.
+
+Every ``csrc/*.cu`` is compiled to an object in parallel (``-gencode arch=compute_100a,code=sm_100a -lineinfo``) and
+linked into one shared library with plain C entry points (loaded through ctypes by :mod:`pear_b200.ops.lib`), so a
+build needs neither the torch headers nor a GPU. Objects are rebuilt only when a source or header is newer.
+"""
+
+from __future__ import annotations
+
+import os
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+HERE = Path(__file__).resolve().parent
+CSRC = HERE / "csrc"
+BUILD = HERE / "build"
+LIB = HERE / "_pear_kernels.so"
+NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--expt-relaxed-constexpr",
+    "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
+]
+
+
+def _newest_header() -> float:
+    return max((p.stat().st_mtime for p in CSRC.glob("*.cuh")), default=0.0)
+
+
+def build(verbose: bool = False, ptxas_info: bool = False) -> Path:
+    BUILD.mkdir(exist_ok=True)
+    sources = sorted(CSRC.glob("*.cu"))
+    header_time = _newest_header()
+    jobs = []
+    for src in sources:
+        obj = BUILD / (src.stem + ".o")
+        if obj.exists() and obj.stat().st_mtime > max(src.stat().st_mtime, header_time):
+            continue
+        cmd = [NVCC, *FLAGS, "-c", str(src), "-o", str(obj)]
+        if ptxas_info:
+            cmd[1:1] = ["-Xptxas", "-v"]
+        jobs.append((src, cmd))
+
+    def run(job):
+        src, cmd = job
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        return src, r
+
+    failed = False
+    with ThreadPoolExecutor(max_workers=min(8, max(1, len(jobs)))) as pool:
+        for src, r in pool.map(run, jobs):
+            if verbose or r.returncode != 0 or ptxas_info:
+                sys.stderr.write(f"[nvcc] {src.name}\n{r.stdout}{r.stderr}\n")
+            failed |= r.returncode != 0
+    if failed:
+        raise RuntimeError("nvcc failed; see messages above")
+    objs = [str(BUILD / (s.stem + ".o")) for s in sources]
+    if jobs or not LIB.exists():
+        cmd = [NVCC, "-shared", "-o", str(LIB), *objs, "-lcudart"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"link failed:\n{r.stdout}{r.stderr}")
+    return LIB
+
+
+if __name__ == "__main__":
+    print(build(verbose="-v" in sys.argv, ptxas_info="--ptxas" in sys.argv))
