@@ -29,7 +29,7 @@ class _Params(ctypes.Structure):
         ("barrier", ctypes.c_void_p), ("status", ctypes.c_void_p),
         ("max_instrs", ctypes.c_int32), ("ring", ctypes.c_int32), ("step_parity", ctypes.c_int32),
         ("seed", ctypes.c_uint32), ("temperature", ctypes.c_float), ("vocab", ctypes.c_int32),
-        ("barrier_base", ctypes.c_uint32), ("pad", ctypes.c_int32),
+        ("barrier_base", ctypes.c_uint32), ("pad", ctypes.c_int32), ("ctrl", ctypes.c_void_p),
     ]
 
 
@@ -90,8 +90,9 @@ class MegakernelEngine:
     """One sequence, one GPU. ``prefill`` then ``decode_steps``/``generate``."""
 
     RING = 64
-    NS = 8       # weight ring stages
-    MAXT = 8     # activation rows in shared memory
+    # (weight ring stages, rows of the activation operand) per program: decode steps have <= 4 rows (4 FP4 terms per row in
+    # a 16-row operand); prefill blocks have 8 rows (4 terms in a 32-row operand and a shorter ring)
+    LAUNCH_SHAPE = {"decode": (8, 16), "prefill": (5, 32)}
     CHUNK = 1024  # vocab entries per sampler partial
 
     def __init__(self, cfg: HybridConfig, draft_cfg: Optional[HybridConfig], weights, device="cuda", max_len: int = 8192,
@@ -110,6 +111,7 @@ class MegakernelEngine:
         self.weight_bytes = 0
         self._build(weights)
         self.launches = 0
+        self._use_ctrl = True
         self.barrier_base = 0
         self.reset()
 
@@ -155,6 +157,9 @@ class MegakernelEngine:
         self.out_host = torch.zeros(self.RING, S.STEPOUT_DTYPE.itemsize // 4, dtype=torch.int32).pin_memory()
         self.barrier = torch.zeros(4, dtype=torch.int32, device=self.device)
         self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
+        # per-step control records: pinned host ring -> device ring, one 32-byte record copied before every launch
+        self.ctrl_dev = torch.zeros(self.RING, 8, dtype=torch.int32, device=self.device)
+        self.ctrl_host = torch.zeros(self.RING, 8, dtype=torch.int32).pin_memory()
         self.prompt_dev = torch.zeros(self.max_len + 16, dtype=torch.int32, device=self.device)
         self.prompt_host = torch.zeros(self.max_len + 16, dtype=torch.int32).pin_memory()
         inv_freq = cfg.rope_theta ** (-torch.arange(cfg.rotary_dim // 2, dtype=torch.float64) * 2.0 / cfg.rotary_dim)
@@ -404,7 +409,7 @@ class MegakernelEngine:
                                     max_len, p.stats())
         self._descs_np = descs
         self.descs_dev = torch.from_numpy(descs.view(np.uint8).reshape(-1).copy()).to(self.device)
-        self.smem_bytes = _lib.lib().pear_mk_smem_bytes(self.NS, self.MAXT)
+        self.smem_bytes = {k: _lib.lib().pear_mk_smem_bytes(*v) for k, v in self.LAUNCH_SHAPE.items()}
 
     # -- descriptor patching (prompt length lives in the sampler/bookkeeping descriptors) -------------------------------
     def _set_prompt_len(self, n: int) -> None:
@@ -452,8 +457,10 @@ class MegakernelEngine:
             instrs=instrs.data_ptr(), descs=self.descs_dev.data_ptr(), rec=self.rec.data_ptr(), out_ring=self.out_ring.data_ptr(),
             barrier=self.barrier.data_ptr(), status=self.status.data_ptr(), max_instrs=max_len, ring=self.RING,
             step_parity=self.step & 1, seed=self.seed, temperature=self.temperature, vocab=self.cfg.vocab_size,
-            barrier_base=self.barrier_base & 0xFFFFFFFF, pad=0)
-        code = _lib.lib().pear_mk_launch(ctypes.byref(prm), self.num_ctas, self.NS, self.MAXT, _lib.stream())
+            barrier_base=self.barrier_base & 0xFFFFFFFF, pad=0,
+            ctrl=self.ctrl_dev[self.step % self.RING].data_ptr() if self._use_ctrl else 0)
+        ns, nb = self.LAUNCH_SHAPE[program]
+        code = _lib.lib().pear_mk_launch(ctypes.byref(prm), self.num_ctas, ns, nb, _lib.stream())
         _lib.check(code, "megakernel launch")
         _lib.count_launch()
         self.barrier_base += stats["barriers"] * self.num_ctas
@@ -464,9 +471,16 @@ class MegakernelEngine:
         for _ in range(self.prefill_steps):
             self._launch("prefill")
 
-    def decode_step(self, copy_out: bool = True) -> int:
-        """Launch one decode/verify step; returns the ring slot its output lands in."""
+    def decode_step(self, copy_out: bool = True, temperature: Optional[float] = None, seed: Optional[int] = None) -> int:
+        """Launch one decode/verify step; returns the ring slot its output lands in. The step's sampling controls
+        travel host -> device in a 32-byte record copied from pinned memory ahead of the launch."""
         slot = (self.step) % self.RING
+        if self._use_ctrl:
+            rec = self.ctrl_host[slot]
+            rec[0] = int(np.float32(self.temperature if temperature is None else temperature).view(np.int32))
+            rec[1] = int(np.uint32(self.seed if seed is None else seed).view(np.int32))
+            rec[2] = -1
+            self.ctrl_dev[slot].copy_(rec, non_blocking=True)
         self._launch("decode")
         if copy_out:
             self.out_host[slot].copy_(self.out_ring[slot], non_blocking=True)
@@ -487,17 +501,25 @@ class MegakernelEngine:
         each step's output from pinned memory, ``lookahead`` launches behind the device."""
         self.start(prompt)
         self.prefill()
+        budget = self.max_len - 16 * (1 + self.n_draft) - self.prompt_len
+        res = self.decode(min(max_new_tokens, budget), lookahead=lookahead)
+        self.check_status()
+        return res
+
+    def decode(self, count: int, by_steps: bool = False, lookahead: int = 2) -> GenerationResult:
+        """Continue the current sequence until ``count`` tokens were emitted (or for exactly ``count`` launches with
+        ``by_steps``). Per step: a control record goes pinned host -> device, the step is launched, its output slot
+        is copied device -> pinned host, and the host reads the emitted tokens ``lookahead`` launches behind."""
         tokens: list[int] = []
         pending: list[tuple[int, torch.cuda.Event]] = []
-        steps = accepted = 0
-        budget = self.max_len - 16 * (1 + self.n_draft) - self.prompt_len
-        max_new_tokens = min(max_new_tokens, budget)
-        while len(tokens) < max_new_tokens:
-            while len(pending) < lookahead and steps + len(pending) < max_new_tokens:
+        steps = launched = accepted = 0
+        while (steps < count) if by_steps else (len(tokens) < count):
+            while len(pending) < lookahead and launched < count:
                 slot = self.decode_step()
                 ev = torch.cuda.Event()
                 ev.record()
                 pending.append((slot, ev))
+                launched += 1
             slot, ev = pending.pop(0)
             ev.synchronize()
             out = self.read_slot(slot)
@@ -506,5 +528,4 @@ class MegakernelEngine:
             steps += 1
         for slot, ev in pending:
             ev.synchronize()
-        self.check_status()
-        return GenerationResult(tokens[:max_new_tokens], steps, accepted, self.prefill_steps)
+        return GenerationResult(tokens if by_steps else tokens[:count], steps, accepted, getattr(self, "prefill_steps", 0))

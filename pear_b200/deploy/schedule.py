@@ -97,11 +97,15 @@ class Program:
                 lo, hi = total * i // n, total * (i + 1) // n
             prev = None
             pos = lo
+            whole = ks <= MAX_SEG_STAGES  # the whole activation row fits in shared memory: built once per CTA and op
             while pos < hi:
                 tile, ks0 = divmod(pos, ks)
                 cnt = min(ks - ks0, hi - pos, MAX_SEG_STAGES)
-                load = 0 if prev == (ks0, cnt) else 1
-                self.emit(cta, OP_GEMV, desc, tile, ks0, cnt, load)
+                if whole:
+                    flags = 2 | (1 if pos == lo else 0)
+                else:
+                    flags = 0 if prev == (ks0, cnt) else 1
+                self.emit(cta, OP_GEMV, desc, tile, ks0, cnt, flags)
                 prev = (ks0, cnt)
                 pos += cnt
 

@@ -93,9 +93,11 @@ def dequantize(codes: torch.Tensor, scales: torch.Tensor, global_scale: float) -
 def pack_stages(q: NVFP4Tensor) -> torch.Tensor:
     """Megakernel streaming layout: uint8 [tiles, kstages, STAGE_BYTES]; rows are zero-padded to a multiple of 128.
 
-    Codes of a stage: ``((warp*4 + quad)*32 + g*4 + t)*16 + j*4 + b`` holds the byte of row ``16 warp + g + 8 (b & 1)``
-    and K pair ``64 quad + 16 j + 4 t + 2 (b >> 1)``; scales: ``16384 + (warp*4 + quad)*64 + g*8 + j*2 + half`` holds
-    the scale of row ``16 warp + g + 8 half`` and block ``4 quad + j``.
+    A stage is the shared-memory image the tensor core reads in place. Codes: the K-major operand without swizzle, i.e.
+    8-row x 16-byte core matrices, ``(chunk * 16 + row // 8) * 128 + (row % 8) * 16 + byte`` with ``chunk`` the 16-byte
+    (32-element) K chunk 0..7. Scales: four 512-byte atoms, one per 64 K elements,
+    ``16384 + j * 512 + (row % 32) * 16 + (row // 32) * 4 + block`` (the layout ``tcgen05.cp.32x128b.warpx4`` spreads
+    over tensor memory for a 128-row block-scaled MMA).
     """
     n, k = q.shape
     if k % STAGE_K:
@@ -106,24 +108,26 @@ def pack_stages(q: NVFP4Tensor) -> torch.Tensor:
         pad = tiles * TILE_ROWS - n
         codes = torch.cat([codes, codes.new_zeros(pad, codes.shape[1])])
         scales = torch.cat([scales, scales.new_zeros(pad, scales.shape[1])])
-    # rows -> (tile, warp, hi, g); code bytes -> (kstage, quad, j, t, pair)
-    c = codes.view(tiles, 8, 2, 8, ks, 4, 4, 4, 2)
-    #            0      1  2  3  4   5  6  7  8   -> (tile, ks, warp, quad, g, t, j, pair, hi)
-    c = c.permute(0, 4, 1, 5, 3, 7, 6, 8, 2).reshape(tiles, ks, STAGE_CODE_BYTES)
-    s = scales.view(tiles, 8, 2, 8, ks, 4, 4)
-    #             0     1  2  3  4   5  6      -> (tile, ks, warp, quad, g, j, hi)
-    s = s.permute(0, 4, 1, 5, 3, 6, 2).reshape(tiles, ks, STAGE_SCALE_BYTES)
+    # rows -> (tile, row // 8, row % 8); code bytes -> (kstage, chunk, byte)
+    c = codes.view(tiles, 16, 8, ks, 8, 16)
+    #            0      1   2  3   4  5    -> (tile, ks, chunk, row // 8, row % 8, byte)
+    c = c.permute(0, 3, 4, 1, 2, 5).reshape(tiles, ks, STAGE_CODE_BYTES)
+    # rows -> (tile, row // 32, row % 32); scales -> (kstage, j, block)
+    s = scales.view(tiles, 4, 32, ks, 4, 4)
+    #             0     1  2   3   4  5    -> (tile, ks, j, row % 32, row // 32, block)
+    s = s.permute(0, 3, 4, 2, 1, 5).reshape(tiles, ks, STAGE_SCALE_BYTES)
     return torch.cat([c, s], dim=-1).contiguous()
 
 
 def unpack_stages(packed: torch.Tensor, n: int, k: int) -> tuple[torch.Tensor, torch.Tensor]:
     """Inverse of :func:`pack_stages` (tests)."""
     tiles, ks = packed.shape[0], packed.shape[1]
-    c = packed[..., :STAGE_CODE_BYTES].reshape(tiles, ks, 8, 4, 8, 4, 4, 2, 2)
-    #   (tile, ks, warp, quad, g, t, j, pair, hi) -> (tile, warp, hi, g, ks, quad, j, t, pair)
-    c = c.permute(0, 2, 8, 4, 1, 3, 6, 5, 7).reshape(tiles * TILE_ROWS, k // 2)
-    s = packed[..., STAGE_CODE_BYTES:].reshape(tiles, ks, 8, 4, 8, 4, 2)
-    s = s.permute(0, 2, 6, 4, 1, 3, 5).reshape(tiles * TILE_ROWS, k // BLOCK)
+    c = packed[..., :STAGE_CODE_BYTES].reshape(tiles, ks, 8, 16, 8, 16)
+    #   (tile, ks, chunk, row // 8, row % 8, byte) -> (tile, row // 8, row % 8, ks, chunk, byte)
+    c = c.permute(0, 3, 4, 1, 2, 5).reshape(tiles * TILE_ROWS, k // 2)
+    s = packed[..., STAGE_CODE_BYTES:].reshape(tiles, ks, 4, 32, 4, 4)
+    #   (tile, ks, j, row % 32, row // 32, block) -> (tile, row // 32, row % 32, ks, j, block)
+    s = s.permute(0, 4, 3, 1, 2, 5).reshape(tiles * TILE_ROWS, k // BLOCK)
     return c[:n].contiguous(), s[:n].contiguous()
 
 

@@ -2,17 +2,21 @@
 // the whole NVFP4-quantised hybrid model. One CTA per SM walks its own instruction list (megakernel.cuh).
 //
 // Design (re-derived for B200; the counterpart of upstream deploy/blackwell/nvfp4/csrc/megakernel.cu):
-//  * Weights are pre-packed into 18 KB "stages" (128 rows x 256 K: e2m1 codes in mma-fragment order + e4m3 block
-//    scales). A producer warp streams stages with 1-D bulk copies (TMA engine, mbarrier completion) into a shared
-//    memory ring, following the same instruction list as the consumers but never waiting on activations: weights of
-//    the NEXT op keep streaming while the consumers sit in a grid barrier, so HBM never idles across op boundaries.
-//  * GEMV ops are stream-K: the (row tile, k-stage) space of an op is cut into contiguous per-CTA ranges; partial sums
-//    are added to the fp32 output with red.global.add (the residual add comes for free).
-//  * Prologues build the f16 activation rows in shared memory straight from the fp32 buffers in L2: plain, (1+w)
-//    RMSNorm, SwiGLU, or the GDN gated RMSNorm.
-//  * Dequantisation is exact: e2m1 -> f16 (cvt), times the e4m3 block scale in f16 (<= 6 significant bits), then
-//    mma.sync m16n8k16 with fp32 accumulation; activations stay f16 (not re-quantised to 4 bits).
-//  * All waits are bounded (common.cuh); on expiry the CTA records a status and drains.
+//  * Weights are pre-packed into 18 KB "stages" (128 rows x 256 K): the e2m1 codes as the tensor core's K-major
+//    shared-memory image (8-row x 16-byte core matrices) and the e4m3 block scales as the 32 x 16-byte atoms that
+//    tcgen05.cp spreads over tensor memory. A producer warp streams stages with 1-D bulk copies (TMA engine, mbarrier
+//    completion) into a shared-memory ring, following the same instruction list as the consumers but never waiting on
+//    activations: weights of the NEXT op keep streaming while the consumers sit in a grid barrier.
+//  * GEMV ops are stream-K: the (row tile, k-stage) space of an op is cut into contiguous per-CTA ranges; one thread
+//    issues tcgen05.mma.kind::mxf4nvf4.block_scale (M 128 x N 16|32 x K 64, hardware dequantisation, fp32 accumulators
+//    in tensor memory); four warps drain the accumulator with tcgen05.ld and add the partial sums to the fp32 output
+//    with red.global.add (the residual add comes for free). Two accumulators alternate between segments.
+//  * The weights stay exactly NVFP4. Activations are expanded on the fly into a sum of FP4 terms, each the NVFP4
+//    quantisation of the previous term's residual (scale rounded up, x4 gain per term), laid out as extra rows of the
+//    B operand: 4 terms for T <= 4 reach ~10 bits, so activations are better than bf16 although the MMA is 4-bit.
+//  * Prologues build that operand straight from the fp32 buffers in L2: plain, (1+w) RMSNorm, SwiGLU, or the GDN gated
+//    RMSNorm; a per-row power-of-two pre-scale keeps every block scale inside e4m3's range.
+//  * All waits are bounded (common.cuh); on expiry the CTA records a status, drains and frees its tensor memory.
 #include "common.cuh"
 #include "megakernel.cuh"
 
@@ -23,25 +27,39 @@
 namespace mk {
 using namespace pear;
 
+constexpr int kTmemCols = 512;
+constexpr int kAccCol = 0;        // 2 accumulators x 32 columns
+constexpr int kSfaCol = 64;       // ring slots x 16 columns
+constexpr int kSfbCol = 64 + 16 * 8;  // 320 columns: a 4-column group per K-64 block of a 5120-wide activation row
+constexpr int kMaxMmas = kMaxSegStages * 4;
+// shared-memory image of the activation scales: per K-64 block nb rows x 16 bytes (bytes 0..3 = the 4 block scales);
+// tcgen05.cp always reads 32 rows, so with nb = 16 it also reads the next image (lanes the MMA never looks at)
+__host__ __device__ constexpr int sfb_bytes(int nb) { return kMaxMmas * nb * 16 + 512; }
+constexpr int kStatBytes = 3072;
+
 struct Smem {
   uint64_t full[16];
   uint64_t empty[16];
-  float red[64];
-  float rstd[8];
-  int rstd_tag;
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint32_t tmem_base;
   int abort_flag;
+  float red[64];
+  float gscale[8];   // 1 / g_t: the epilogue's undo of the row pre-scale
 };
 
 struct Ctx {
   const Params* p;
-  uint8_t* ring;       // NS * kStageBytes
-  __half* xs;          // activation rows [MAXT][kXStride] (also scratch of the non-GEMV ops)
+  uint8_t* ring;       // ns * kStageBytes
+  uint8_t* xs;         // scratch: B operand image | activation scale image | statistics (other ops use it freely)
   Smem* sm;
   const StepRec* rec;  // current step record
   StepRec* rec_next;
   int ns;              // ring stages
-  int maxt;            // activation rows kept in smem (power of two)
-  int stage, phase;    // consumer ring cursor
+  int nb;              // rows of the B operand (16 or 32)
+  int stage, phase;    // ring cursor (meaningful in the issuing thread)
+  int seg;             // GEMV segments executed so far (accumulator alternation)
+  uint32_t tmem;
   uint32_t barrier_target;
 };
 
@@ -54,18 +72,17 @@ __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;"
 // ---------------------------------------------------------------------------------------------------------------------
 // grid barrier for the consumer warps: release-add by one thread per CTA, acquire-poll with a budget
 // ---------------------------------------------------------------------------------------------------------------------
-constexpr uint32_t kGridPolls = 1u << 21;
+constexpr uint32_t kGridPolls = 1u << 22;
 __device__ __forceinline__ void grid_barrier(Ctx& c) {
   consumer_sync();
   c.barrier_target += gridDim.x;
   if (threadIdx.x == 0) {
-    __threadfence();
     red_release_gpu_add(c.p->barrier, 1u);
     bool ok = false;
     for (uint32_t i = 0; i < kGridPolls; ++i) {
       if ((int32_t)(ld_acquire_gpu(c.p->barrier) - c.barrier_target) >= 0) { ok = true; break; }
-      if (i > 32) __nanosleep(32);
-      if ((i & 4095u) == 4095u && *(volatile int*)c.p->status != 0) break;
+      if (i > 256) __nanosleep(20);
+      if ((i & 16383u) == 16383u && *(volatile int*)c.p->status != 0) break;
     }
     if (!ok) { set_status(c.p->status, PEAR_ERR_GRID_BARRIER); c.sm->abort_flag = 1; }
   }
@@ -75,144 +92,186 @@ __device__ __forceinline__ void grid_barrier(Ctx& c) {
 // ---------------------------------------------------------------------------------------------------------------------
 // GEMV
 // ---------------------------------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t h2_as_u32(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
-__device__ __forceinline__ __half2 u32_as_h2(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
-
-__device__ __forceinline__ __half2 e2m1x2_to_h2(uint32_t byte) {
-  __half2_raw r = __nv_cvt_fp4x2_to_halfraw2((__nv_fp4x2_storage_t)byte, __NV_E2M1);
-  return *reinterpret_cast<__half2*>(&r);
-}
-__device__ __forceinline__ __half2 e4m3x2_to_h2(uint32_t two_bytes) {
-  __half2_raw r = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)two_bytes, __NV_E4M3);
-  return *reinterpret_cast<__half2*>(&r);
+__device__ __forceinline__ float e4m3_to_f32(uint32_t code) {
+  __half_raw h = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)code, __NV_E4M3);
+  return __half2float(*reinterpret_cast<__half*>(&h));
 }
 
-__device__ __forceinline__ void mma_f16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-
-__device__ __forceinline__ float clamp_h(float v) { return fminf(fmaxf(v, -65504.f), 65504.f); }
-
-// Build the f16 activation rows for K range [k0, k0 + kn) of the op's input into c.xs.
-__device__ void gemv_prologue(Ctx& c, const Desc& d, int k0, int kn) {
-  const StepRec* rec = c.rec;
-  const int T = step_rows(c, d);
-  const int tid = threadIdx.x;
-  const float* in = (const float*)d.p1;
-  if ((d.i7 & 1) && d.i5 != PRO_GDN_NORM) in += (size_t)rec->parity * d.i8;
-  const int istride = d.i3;
-  const int pro = d.i5;
-  if (pro == PRO_NORM) {
-    // rstd per row over the whole K; cached per descriptor
-    if (c.sm->rstd_tag != (int)(&d - c.p->descs)) {
-      for (int t = 0; t < T; ++t) {
-        float s = 0.f;
-        const float4* row = (const float4*)(in + (size_t)t * istride);
-        for (int i = tid; i < d.i0 / 4; i += kConsumerThreads) {
-          float4 v = __ldcg(row + i);
-          s += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-        }
-        s = warp_sum(s);
-        consumer_sync();
-        if ((tid & 31) == 0) c.sm->red[tid >> 5] = s;
-        consumer_sync();
-        if (tid == 0) {
-          float tot = 0.f;
-          for (int w = 0; w < kConsumerWarps; ++w) tot += c.sm->red[w];
-          c.sm->rstd[t] = rsqrtf(tot / (float)d.i0 + d.f1);
-        }
-      }
-      if (tid == 0) c.sm->rstd_tag = (int)(&d - c.p->descs);
-      consumer_sync();
+// Quantise 16 pre-scaled values into `terms` NVFP4 blocks (term i encodes the residual of terms < i, with a gain of
+// 4^i folded into its scale) and store codes + scales into the B operand image.
+//   codes : B + (chunk * (nb/8) + n/8) * 128 + (n%8) * 16 + half * 8     (chunk = block/2, half = block%2, 8 bytes)
+//   scales: SFB + (block/4) * nb * 16 + n * 16 + block%4                    (n = term * tpad + row)
+__device__ __forceinline__ void quantize_block(float (&r)[16], int terms, int tpad, int row, int blk, int nb, uint8_t* B,
+                                               uint8_t* SFB) {
+  float gain = 1.f;
+  for (int term = 0; term < terms; ++term) {
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(r[i]));
+    const float target = amax * (1.f / 6.f) * gain;
+    uint32_t code = (uint32_t)__nv_cvt_float_to_fp8(target, __NV_SATFINITE, __NV_E4M3);
+    float sv = e4m3_to_f32(code);
+    if (sv < target && code < 0x7Eu) { ++code; sv = e4m3_to_f32(code); }  // round the scale up: no code saturates
+    const float inv = sv > 0.f ? gain / sv : 0.f;
+    const float back = sv / gain;
+    uint32_t words[2] = {0u, 0u};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t byte = (uint32_t)__nv_cvt_float2_to_fp4x2(make_float2(r[2 * i] * inv, r[2 * i + 1] * inv), __NV_E2M1,
+                                                               cudaRoundNearest) & 0xffu;
+      words[i >> 2] |= byte << (8 * (i & 3));
+      __half2_raw hr = __nv_cvt_fp4x2_to_halfraw2((__nv_fp4x2_storage_t)byte, __NV_E2M1);
+      const float2 dq = __half22float2(*reinterpret_cast<__half2*>(&hr));
+      r[2 * i] -= dq.x * back;
+      r[2 * i + 1] -= dq.y * back;
     }
-    const float* w = (const float*)d.p2;
-    for (int t = 0; t < T; ++t) {
-      const float rs = c.sm->rstd[t];
-      const float* row = in + (size_t)t * istride + k0;
-      __half* xr = c.xs + (size_t)(t & (c.maxt - 1)) * kXStride;
-      for (int i = tid * 4; i < kn; i += kConsumerThreads * 4) {
-        float4 v = __ldcg((const float4*)(row + i));
-        float4 g = *(const float4*)(w + k0 + i);
-        __half2 a = __floats2half2_rn(clamp_h(v.x * rs * (1.f + g.x)), clamp_h(v.y * rs * (1.f + g.y)));
-        __half2 b = __floats2half2_rn(clamp_h(v.z * rs * (1.f + g.z)), clamp_h(v.w * rs * (1.f + g.w)));
-        *(uint2*)(xr + i) = make_uint2(h2_as_u32(a), h2_as_u32(b));
-      }
-    }
-  } else if (pro == PRO_PLAIN) {
-    for (int t = 0; t < T; ++t) {
-      const float* row = in + (size_t)t * istride + k0;
-      __half* xr = c.xs + (size_t)(t & (c.maxt - 1)) * kXStride;
-      for (int i = tid * 4; i < kn; i += kConsumerThreads * 4) {
-        float4 v = __ldcg((const float4*)(row + i));
-        __half2 a = __floats2half2_rn(clamp_h(v.x), clamp_h(v.y));
-        __half2 b = __floats2half2_rn(clamp_h(v.z), clamp_h(v.w));
-        *(uint2*)(xr + i) = make_uint2(h2_as_u32(a), h2_as_u32(b));
-      }
-    }
-  } else if (pro == PRO_SWIGLU) {
-    // input rows hold [gate (K) | up (K)]
-    for (int t = 0; t < T; ++t) {
-      const float* row = in + (size_t)t * istride + k0;
-      const float* up = row + d.i0;
-      __half* xr = c.xs + (size_t)(t & (c.maxt - 1)) * kXStride;
-      for (int i = tid * 4; i < kn; i += kConsumerThreads * 4) {
-        float4 g = __ldcg((const float4*)(row + i));
-        float4 u = __ldcg((const float4*)(up + i));
-        __half2 a = __floats2half2_rn(clamp_h(silu_f(g.x) * u.x), clamp_h(silu_f(g.y) * u.y));
-        __half2 b = __floats2half2_rn(clamp_h(silu_f(g.z) * u.z), clamp_h(silu_f(g.w) * u.w));
-        *(uint2*)(xr + i) = make_uint2(h2_as_u32(a), h2_as_u32(b));
-      }
-    }
-  } else {  // PRO_GDN_NORM: per (row, head of 128): o * rsqrt(mean(o^2) + eps) * w * silu(z); k0, kn multiples of 128
-    const float* zbase = (const float*)d.p2;  // z rows: same row stride as the record (d.i8 reused as z stride)
-    if (d.i7 & 1) zbase += (size_t)rec->parity * d.i8;
-    const int zstride = d.i9;
-    const float* nw = (const float*)d.p3;
-    const int warp = tid >> 5, lane = tid & 31;
-    const int heads = kn / 128;
-    for (int item = warp; item < T * heads; item += kConsumerWarps) {
-      const int t = item / heads, h = item % heads;
-      const float* o = (const float*)d.p1 + (size_t)t * istride + k0 + h * 128;
-      const float* z = zbase + (size_t)t * zstride + k0 + h * 128;
-      float4 v = __ldcg((const float4*)(o + lane * 4));
-      float s = warp_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w);
-      const float rs = rsqrtf(s * (1.f / 128.f) + d.f1);
-      float4 zz = __ldcg((const float4*)(z + lane * 4));
-      float4 ww = *(const float4*)(nw + lane * 4);
-      __half* xr = c.xs + (size_t)(t & (c.maxt - 1)) * kXStride + h * 128 + lane * 4;
-      __half2 a = __floats2half2_rn(clamp_h(v.x * rs * ww.x * silu_f(zz.x)), clamp_h(v.y * rs * ww.y * silu_f(zz.y)));
-      __half2 b = __floats2half2_rn(clamp_h(v.z * rs * ww.z * silu_f(zz.z)), clamp_h(v.w * rs * ww.w * silu_f(zz.w)));
-      *(uint2*)xr = make_uint2(h2_as_u32(a), h2_as_u32(b));
-    }
+    const int n = term * tpad + row;
+    *(uint2*)(B + ((size_t)(blk >> 1) * (nb >> 3) + (n >> 3)) * 128 + (n & 7) * 16 + (blk & 1) * 8) = make_uint2(words[0], words[1]);
+    SFB[(blk >> 2) * nb * 16 + n * 16 + (blk & 3)] = (uint8_t)code;
+    gain *= 4.f;
   }
 }
 
-// One stage for one warp: 16 rows x 256 K. Packed layout (see pear_b200/models/nvfp4.py: pack_stages):
-//   codes : ((warp*4 + quad)*32 + lane)*16 + j*4 + byte ; byte0 (row g, k 4t,4t+1) byte1 (row g+8, same k)
-//           byte2 (row g, k 4t+2,4t+3) byte3 (row g+8, same k), k relative to block quad*64 + j*16
-//   scales: 16384 + (warp*4 + quad)*64 + g*8 + j*2 + half   (half 0: row g, 1: row g+8)
-__device__ __forceinline__ void gemv_stage(const uint8_t* stage, const __half* xrow, int warp, int lane, float (&acc)[4]) {
-  const int g = lane >> 2, t = lane & 3;
+// Build the B operand (FP4 terms of the activation rows) for K range [k0, k0 + kn) of the op's input.
+//
+// Register-resident single pass per group of 4 rows: thread `tid` owns K block `tid` (16 elements) of all four rows,
+// and one block of the left-over columns 256.. (block 256 + tid/4 of row tid%4), i.e. 5 blocks = 80 values. Every
+// global load is issued before the first use, the row statistics (RMS, maximum) are reduced with shuffles and one
+// shared-memory exchange, and the blocks are quantised straight from registers. PRO_NORM always covers the whole row.
+__device__ void gemv_prologue(Ctx& c, const Desc& d, int k0, int kn, int T, int tpad, int terms) {
+  const StepRec* rec = c.rec;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const float* in = (const float*)d.p1;
+  if ((d.i7 & 1) && d.i5 != PRO_GDN_NORM) in += (size_t)rec->parity * d.i8;
+  const int istride = d.i3, pro = d.i5, nb = c.nb;
+  uint8_t* B = c.xs;
+  uint8_t* SFB = c.xs + (size_t)(kMaxSegStages * kStageK / 32) * (nb >> 3) * 128;
+  float* stat = (float*)(SFB + sfb_bytes(nb));  // [warp][row][2] partial (sum of squares, maximum), then [64 + row] gains
+  const float* zbase = (const float*)d.p2;
+  if (pro == PRO_GDN_NORM && (d.i7 & 1)) zbase += (size_t)rec->parity * d.i8;
+  const int nblk = kn >> 4;
+
+  for (int t0 = 0; t0 < tpad; t0 += 4) {
+    // ---- the 5 (block, row) items of this thread
+    int ib[5], it[5];
+    bool valid[5];
 #pragma unroll
-  for (int q = 0; q < 4; ++q) {
-    const uint4 codes = *(const uint4*)(stage + ((warp * 4 + q) * 32 + lane) * 16);
-    const uint2 sc = *(const uint2*)(stage + kStageCodeBytes + (warp * 4 + q) * 64 + g * 8);
-    const uint32_t cw[4] = {codes.x, codes.y, codes.z, codes.w};
-    const uint32_t sw[4] = {sc.x & 0xffffu, sc.x >> 16, sc.y & 0xffffu, sc.y >> 16};
+    for (int e = 0; e < 4; ++e) { ib[e] = tid; it[e] = t0 + e; valid[e] = tid < nblk && it[e] < T; }
+    ib[4] = 256 + (tid >> 2); it[4] = t0 + (tid & 3); valid[4] = ib[4] < nblk && it[4] < T;
+
+    // ---- loads (all issued before use)
+    float4 x[5][4], y[5][4], w[2][4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const __half2 s2 = e4m3x2_to_h2(sw[j]);
-      const __half2 s_lo = __low2half2(s2), s_hi = __high2half2(s2);
-      uint32_t a[4];
-      a[0] = h2_as_u32(__hmul2(e2m1x2_to_h2(cw[j] & 0xffu), s_lo));
-      a[1] = h2_as_u32(__hmul2(e2m1x2_to_h2((cw[j] >> 8) & 0xffu), s_hi));
-      a[2] = h2_as_u32(__hmul2(e2m1x2_to_h2((cw[j] >> 16) & 0xffu), s_lo));
-      a[3] = h2_as_u32(__hmul2(e2m1x2_to_h2(cw[j] >> 24), s_hi));
-      const uint2 b = *(const uint2*)(xrow + q * 64 + j * 16 + t * 4);
-      mma_f16(acc, a, b.x, b.y);
+    for (int e = 0; e < 5; ++e) {
+      const int k = k0 + ib[e] * 16;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        x[e][i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        y[e][i] = x[e][i];
+        if (valid[e]) {
+          if (pro == PRO_GDN_NORM) {
+            x[e][i] = __ldcg((const float4*)((const float*)d.p1 + (size_t)it[e] * istride + k) + i);
+            y[e][i] = __ldcg((const float4*)(zbase + (size_t)it[e] * d.i9 + k) + i);
+          } else {
+            x[e][i] = __ldcg((const float4*)(in + (size_t)it[e] * istride + k) + i);
+            if (pro == PRO_SWIGLU) y[e][i] = __ldcg((const float4*)(in + (size_t)it[e] * istride + k + d.i0) + i);
+          }
+        }
+      }
+    }
+    if (pro == PRO_NORM || pro == PRO_GDN_NORM) {
+      // weight of block column `tid` (shared by the four rows) and of the left-over column
+      const float* wp = pro == PRO_NORM ? (const float*)d.p2 : (const float*)d.p3;
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int b = e == 0 ? tid : ib[4];
+        const int kw = pro == PRO_NORM ? (k0 + b * 16) : ((k0 + b * 16) & 127);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) w[e][i] = b < nblk ? __ldg((const float4*)(wp + kw) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    }
+    // ---- elementwise part and per-item statistics
+    float ss[5], mx[5];
+#pragma unroll
+    for (int e = 0; e < 5; ++e) {
+      ss[e] = 0.f; mx[e] = 0.f;
+      const int we = e == 4 ? 1 : 0;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float4 v = x[e][i];
+        if (pro == PRO_NORM) {
+          ss[e] += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+          v.x *= 1.f + w[we][i].x; v.y *= 1.f + w[we][i].y; v.z *= 1.f + w[we][i].z; v.w *= 1.f + w[we][i].w;
+        } else if (pro == PRO_SWIGLU) {
+          v.x = silu_f(v.x) * y[e][i].x; v.y = silu_f(v.y) * y[e][i].y; v.z = silu_f(v.z) * y[e][i].z; v.w = silu_f(v.w) * y[e][i].w;
+        } else if (pro == PRO_GDN_NORM) {
+          ss[e] += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+          v.x *= w[we][i].x * silu_f(y[e][i].x); v.y *= w[we][i].y * silu_f(y[e][i].y);
+          v.z *= w[we][i].z * silu_f(y[e][i].z); v.w *= w[we][i].w * silu_f(y[e][i].w);
+        }
+        mx[e] = fmaxf(mx[e], fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+        x[e][i] = v;
+      }
+    }
+    if (pro == PRO_GDN_NORM) {
+      // a head is 8 consecutive blocks: lanes 8h..8h+7 for items 0-3, lanes of equal row (stride 4) for item 4
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        ss[e] += __shfl_xor_sync(0xffffffffu, ss[e], 1); ss[e] += __shfl_xor_sync(0xffffffffu, ss[e], 2);
+        ss[e] += __shfl_xor_sync(0xffffffffu, ss[e], 4);
+      }
+      ss[4] += __shfl_xor_sync(0xffffffffu, ss[4], 4); ss[4] += __shfl_xor_sync(0xffffffffu, ss[4], 8);
+      ss[4] += __shfl_xor_sync(0xffffffffu, ss[4], 16);
+#pragma unroll
+      for (int e = 0; e < 5; ++e) {
+        const float rs = rsqrtf(ss[e] * (1.f / 128.f) + d.f1);
+        mx[e] *= rs;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { x[e][i].x *= rs; x[e][i].y *= rs; x[e][i].z *= rs; x[e][i].w *= rs; }
+      }
+    }
+    // ---- per-row reduction over the CTA: sum of squares (PRO_NORM) and maximum
+    float rss[4], rmx[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      rss[r] = ss[r] + ((tid & 3) == r ? ss[4] : 0.f);
+      rmx[r] = fmaxf(mx[r], (tid & 3) == r ? mx[4] : 0.f);
+      rss[r] = warp_sum(rss[r]);
+      rmx[r] = warp_max(rmx[r]);
+    }
+    consumer_sync();  // the previous group's gains have been consumed
+    if (lane == 0) {
+#pragma unroll
+      for (int r = 0; r < 4; ++r) { stat[(warp * 4 + r) * 2] = rss[r]; stat[(warp * 4 + r) * 2 + 1] = rmx[r]; }
+    }
+    consumer_sync();
+    float gain[4], rstd[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      float s2 = 0.f, m = 0.f;
+#pragma unroll
+      for (int wq = 0; wq < kConsumerWarps; ++wq) { s2 += stat[(wq * 4 + r) * 2]; m = fmaxf(m, stat[(wq * 4 + r) * 2 + 1]); }
+      rstd[r] = 1.f;
+      if (pro == PRO_NORM) { rstd[r] = rsqrtf(s2 / (float)d.i0 + d.f1); m *= rstd[r]; }
+      // power-of-two row gain: the largest block scale lands at or below 2048 / 6
+      float g = 1.f;
+      if (m > 0.f && m < 3.0e38f) g = exp2f(floorf(log2f(2048.f / m)));
+      gain[r] = fminf(fmaxf(g, 1.0e-30f), 1.0e30f);
+      if (tid == 0 && t0 + r < 8) c.sm->gscale[t0 + r] = 1.f / gain[r];
+    }
+    // ---- quantise from registers
+#pragma unroll
+    for (int e = 0; e < 5; ++e) {
+      const int row = e == 4 ? (tid & 3) : e;
+      if (ib[e] < nblk) {
+        float r16[16];
+        const float f = gain[row] * rstd[row];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          r16[4 * i] = x[e][i].x * f; r16[4 * i + 1] = x[e][i].y * f; r16[4 * i + 2] = x[e][i].z * f; r16[4 * i + 3] = x[e][i].w * f;
+        }
+        quantize_block(r16, terms, tpad, t0 + row, ib[e], nb, B, SFB);
+      }
     }
   }
 }
@@ -221,37 +280,98 @@ __device__ void op_gemv(Ctx& c, const Instr& ins) {
   const Desc& d = c.p->descs[ins.desc];
   const int tile = ins.a, ks0 = ins.b, nks = ins.c;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  if (ins.d & 1) {
-    consumer_sync();  // previous users of xs are done
-    gemv_prologue(c, d, ks0 * kStageK, nks * kStageK);
-    consumer_sync();
-  }
-  float acc[4] = {0.f, 0.f, 0.f, 0.f};
-  const int g = lane >> 2, t = lane & 3;
-  const __half* xrow = c.xs + (size_t)(g & (c.maxt - 1)) * kXStride;
-  bool ok = true;
-  for (int s = 0; s < nks; ++s) {
-    if (ok) ok = mbar_wait_bounded(&c.sm->full[c.stage], c.phase, c.p->status);
-    if (ok) gemv_stage(c.ring + (size_t)c.stage * kStageBytes, xrow + s * kStageK, warp, lane, acc);
-    __syncwarp();
-    if (lane == 0) mbar_arrive(&c.sm->empty[c.stage]);
-    if (++c.stage == c.ns) { c.stage = 0; c.phase ^= 1; }
-  }
-  // epilogue: c0 (row g, token 2t) c1 (row g, token 2t+1) c2 (row g+8, token 2t) c3 (row g+8, token 2t+1)
   const int T = step_rows(c, d);
-  float* out = (float*)d.p4;
-  if (d.i7 & 2) out += (size_t)c.rec->parity * d.i8;
-  const int ostride = d.i4;
-  const int r0 = tile * kTileRows + warp * 16 + g;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int row = r0 + (i >> 1) * 8, tok = 2 * t + (i & 1);
-    if (tok < T && row < d.i2) {
-      float v = acc[i] * d.f0;
-      if (d.i6 == EPI_RED) red_add_f32(out + (size_t)tok * ostride + row, v);
-      else out[(size_t)tok * ostride + row] = v;
+  const int tpad = T <= 4 ? 4 : 8, nb = c.nb, terms = min(4, nb / tpad);
+  // flags: bit0 build the B operand; bit1 the whole row sits in smem (K <= 5120) and k-stages index it absolutely
+  const bool whole = ins.d & 2;
+  const int ab = c.seg & 1;
+  const uint32_t use = (uint32_t)(c.seg >> 1) & 1u;  // parity of this use of accumulator `ab`
+  uint8_t* B = c.xs;
+  uint8_t* SFB = c.xs + (size_t)(kMaxSegStages * kStageK / 32) * (nb >> 3) * 128;
+  const bool issuer = tid == 4 * 32;  // lane 0 of warp 4: warps 0-3 own the four tensor-memory lane quarters
+  if (ins.d & 1) {
+    // every MMA that reads the old B operand has completed once the previous segment's accumulator is full
+    if (c.seg > 0) mbar_wait_bounded(&c.sm->acc_full[(c.seg - 1) & 1], (uint32_t)((c.seg - 1) >> 1) & 1u, c.p->status);
+    consumer_sync();
+    if (whole) gemv_prologue(c, d, 0, d.i0, T, tpad, terms);
+    else gemv_prologue(c, d, ks0 * kStageK, nks * kStageK, T, tpad, terms);
+    fence_proxy_async();  // generic-proxy stores to the operand images -> visible to the tensor core / tcgen05.cp
+    consumer_sync();
+    if (issuer) {
+      const int nmma = (whole ? d.i1 : nks) * 4;
+      tcgen05_fence_after();
+      for (int m = 0; m < nmma; ++m)
+        tmem_cp_32x128b_warpx4(c.tmem + kSfbCol + m * 4, umma_desc_interleaved(smem_u32(SFB + m * nb * 16), 128, 128));
     }
   }
+  if (issuer) {
+    bool ok = mbar_wait_bounded(&c.sm->acc_empty[ab], use ^ 1u, c.p->status);
+    tcgen05_fence_after();
+    const uint32_t idesc = umma_idesc_nvfp4(128, nb);
+    const uint32_t chunk_b = (uint32_t)(nb >> 3) * 128u;
+    const uint32_t b_addr = smem_u32(B);
+    for (int s = 0; s < nks; ++s) {
+      if (ok) ok = mbar_wait_bounded(&c.sm->full[c.stage], c.phase, c.p->status);
+      if (ok) {
+        tcgen05_fence_after();
+        const uint32_t a_addr = smem_u32(c.ring + (size_t)c.stage * kStageBytes);
+        const int kst = whole ? ks0 + s : s;  // stage index inside the B operand
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          tmem_cp_32x128b_warpx4(c.tmem + kSfaCol + c.stage * 16 + j * 4,
+                                 umma_desc_interleaved(a_addr + kStageCodeBytes + j * 512, 128, 128));
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint64_t da = umma_desc_interleaved(a_addr + j * 4096, 2048, 128);
+          const uint64_t db = umma_desc_interleaved(b_addr + (uint32_t)(kst * 4 + j) * 2u * chunk_b, chunk_b, 128);
+          umma_nvfp4(c.tmem + kAccCol + ab * 32, da, db, idesc, (s | j) != 0 ? 1u : 0u, c.tmem + kSfaCol + c.stage * 16 + j * 4,
+                     c.tmem + kSfbCol + (kst * 4 + j) * 4);
+        }
+      }
+      tcgen05_commit(&c.sm->empty[c.stage]);  // frees the ring slot once these MMAs (and copies) have read it
+      if (++c.stage == c.ns) { c.stage = 0; c.phase ^= 1; }
+    }
+    tcgen05_commit(&c.sm->acc_full[ab]);
+  }
+  if (warp < 4) {
+    // ---- epilogue: lane quarter `warp`; row = tile * 128 + warp * 32 + lane; column n = term * tpad + token
+    const bool ok = mbar_wait_bounded(&c.sm->acc_full[ab], use, c.p->status);
+    tcgen05_fence_after();
+    uint32_t r[32];
+    if (ok) {
+      if (nb == 16) {
+        uint32_t q[16];
+        tmem_ld_32x32b_x16(c.tmem + ((uint32_t)(warp * 32) << 16) + kAccCol + ab * 32, q);
+        tcgen05_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 16; ++i) r[i] = q[i];
+      } else {
+        tmem_ld_32x32b_x32(c.tmem + ((uint32_t)(warp * 32) << 16) + kAccCol + ab * 32, r);
+        tcgen05_wait_ld();
+      }
+    }
+    tcgen05_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&c.sm->acc_empty[ab]);
+    if (ok) {
+      float* out = (float*)d.p4;
+      if (d.i7 & 2) out += (size_t)c.rec->parity * d.i8;
+      const int row = tile * kTileRows + warp * 32 + lane;
+      if (row < d.i2) {
+        for (int t = 0; t < T; ++t) {
+          float v = 0.f, w = 1.f;
+          for (int term = 0; term < terms; ++term) {
+            v += __uint_as_float(r[term * tpad + t]) * w;
+            w *= 0.25f;
+          }
+          v *= c.sm->gscale[t] * d.f0;
+          if (d.i6 == EPI_RED) red_add_f32(out + (size_t)t * d.i4 + row, v);
+          else out[(size_t)t * d.i4 + row] = v;
+        }
+      }
+    }
+  }
+  ++c.seg;
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -300,19 +420,25 @@ namespace mk {
 // ---------------------------------------------------------------------------------------------------------------------
 // the kernel
 // ---------------------------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(kThreads, 1) mk_main(const __grid_constant__ Params p, int ns, int maxt) {
+__global__ void __maxnreg__(224) mk_main(const __grid_constant__ Params p, int ns, int nb) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   Smem* sm = (Smem*)smem_raw;
   uint8_t* ring = smem_raw + 1024;
-  __half* xs = (__half*)(ring + (size_t)ns * kStageBytes);
-  const int tid = threadIdx.x;
+  uint8_t* xs = ring + (size_t)ns * kStageBytes;
+  const int tid = threadIdx.x, warp = tid >> 5;
   if (tid == 0) {
-    for (int i = 0; i < ns; ++i) { mbar_init(&sm->full[i], 1); mbar_init(&sm->empty[i], kConsumerWarps); }
-    sm->rstd_tag = -1;
+    for (int i = 0; i < ns; ++i) { mbar_init(&sm->full[i], 1); mbar_init(&sm->empty[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&sm->acc_full[i], 1); mbar_init(&sm->acc_empty[i], 4); }
     sm->abort_flag = 0;
     mbar_fence_init();
   }
+  if (warp == 0) {  // the whole tensor memory of the SM: this kernel is the only resident CTA (one per SM)
+    tmem_alloc(&sm->tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before();
   __syncthreads();
+  tcgen05_fence_after();
   const Instr* list = p.instrs + (size_t)blockIdx.x * p.max_instrs;
 
   if (tid >= kConsumerThreads) {
@@ -320,9 +446,11 @@ __global__ void __launch_bounds__(kThreads, 1) mk_main(const __grid_constant__ P
     if (tid == kConsumerThreads) {
       int stage = 0, phase = 0;
       bool ok = true;
+      Instr next = list[0];
       for (int ip = 0; ip < p.max_instrs && ok; ++ip) {
-        const Instr ins = list[ip];
+        const Instr ins = next;
         if (ins.op == OP_END) break;
+        if (ip + 1 < p.max_instrs) next = list[ip + 1];  // in flight while this instruction's stages are issued
         if (ins.op != OP_GEMV) continue;
         const Desc& d = p.descs[ins.desc];
         const uint8_t* src = (const uint8_t*)d.p0 + ((size_t)ins.a * d.i1 + ins.b) * kStageBytes;
@@ -340,17 +468,20 @@ __global__ void __launch_bounds__(kThreads, 1) mk_main(const __grid_constant__ P
     Ctx c;
     c.p = &p; c.ring = ring; c.xs = xs; c.sm = sm;
     c.rec = p.rec + p.step_parity; c.rec_next = p.rec + (p.step_parity ^ 1);
-    c.ns = ns; c.maxt = maxt; c.stage = 0; c.phase = 0; c.barrier_target = p.barrier_base;
+    c.ns = ns; c.nb = nb; c.stage = 0; c.phase = 0; c.seg = 0; c.tmem = sm->tmem_base; c.barrier_target = p.barrier_base;
+    // instruction fetch is software-pipelined: the next instruction (and its descriptor's cache line) is requested
+    // while the current one executes, so no op starts with a dependent chain of L2 round trips
+    Instr next = list[0];
     for (int ip = 0; ip < p.max_instrs; ++ip) {
-      const Instr ins = list[ip];
+      const Instr ins = next;
       if (ins.op == OP_END) break;
+      if (ip + 1 < p.max_instrs) next = list[ip + 1];
       if (*(volatile int*)&sm->abort_flag) {
         // drain: keep the ring protocol alive so the producer is never left waiting on a full ring
-        if (ins.op == OP_GEMV) {
+        if (ins.op == OP_GEMV && tid == 4 * 32) {
           for (int s = 0; s < ins.c; ++s) {
             mbar_wait_bounded(&sm->full[c.stage], c.phase, p.status);
-            __syncwarp();
-            if ((tid & 31) == 0) mbar_arrive(&sm->empty[c.stage]);
+            mbar_arrive(&sm->empty[c.stage]);
             if (++c.stage == c.ns) { c.stage = 0; c.phase ^= 1; }
           }
         }
@@ -372,7 +503,17 @@ __global__ void __launch_bounds__(kThreads, 1) mk_main(const __grid_constant__ P
         case OP_ARGMAX_FIN: op_argmax_fin(c, ins); break;
         default: set_status(p.status, PEAR_ERR_BAD_INSTR); break;
       }
+      if (next.op != OP_END && next.op != OP_BARRIER)
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(p.descs + next.desc));
     }
+    // every issued MMA has completed before tensor memory is released
+    if (c.seg > 0) mbar_wait_bounded(&sm->acc_full[(c.seg - 1) & 1], (uint32_t)((c.seg - 1) >> 1) & 1u, p.status);
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tcgen05_fence_after();
+    tmem_dealloc(sm->tmem_base, kTmemCols);
   }
 }
 
@@ -381,21 +522,26 @@ __global__ void __launch_bounds__(kThreads, 1) mk_main(const __grid_constant__ P
 // ---------------------------------------------------------------------------------------------------------------------
 // host entry points
 // ---------------------------------------------------------------------------------------------------------------------
-PEAR_API int pear_mk_smem_bytes(int ns, int maxt) {
-  return 1024 + ns * mk::kStageBytes + maxt * mk::kXStride * 2;
+static int mk_scratch_bytes(int nb) {
+  const int need = (mk::kMaxSegStages * mk::kStageK / 32) * (nb / 8) * 128 + mk::sfb_bytes(nb) + mk::kStatBytes;
+  return need > 82176 ? need : 82176;  // the attention op's tiles need 80.4 KB of the same region
 }
+PEAR_API int pear_mk_smem_bytes(int ns, int nb) { return 1024 + ns * mk::kStageBytes + mk_scratch_bytes(nb); }
 
-// Launch one step. `params` is a host copy of mk::Params. Cooperative launch: all CTAs are co-resident or the launch
-// fails (never a deadlocked grid barrier).
-PEAR_API int pear_mk_launch(const void* params, int num_ctas, int ns, int maxt, void* stream) {
+// Launch one step. `params` is a host copy of mk::Params; `nb` = rows of the activation operand (16: up to 4 rows x 4
+// terms or 8 rows x 2 terms; 32: 8 rows x 4 terms). Cooperative launch: all CTAs are co-resident or the launch fails
+// (never a deadlocked grid barrier).
+PEAR_API int pear_mk_launch(const void* params, int num_ctas, int ns, int nb, void* stream) {
   static int configured_smem = -1;
-  const int smem = pear_mk_smem_bytes(ns, maxt);
+  if ((nb != 16 && nb != 32) || ns < 2 || ns > 8) return (int)cudaErrorInvalidValue;
+  const int smem = pear_mk_smem_bytes(ns, nb);
+  if (smem > 232448) return (int)cudaErrorInvalidValue;
   if (configured_smem < smem) {
     PEAR_CUDA_CHECK(cudaFuncSetAttribute(mk::mk_main, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured_smem = smem;
   }
   mk::Params p = *(const mk::Params*)params;
-  void* args[] = {(void*)&p, (void*)&ns, (void*)&maxt};
+  void* args[] = {(void*)&p, (void*)&ns, (void*)&nb};
   PEAR_CUDA_CHECK(cudaLaunchCooperativeKernel((const void*)mk::mk_main, dim3(num_ctas), dim3(mk::kThreads), args,
                                               (size_t)smem, (cudaStream_t)stream));
   return 0;

@@ -1,0 +1,222 @@
+// bf16 GEMM for sm_100a on the 5th-generation tensor cores: C[M,N] = A[M,K] * B[N,K]^T, fp32 accumulation in tensor
+// memory. Persistent, warp-specialised: warp 0 feeds a 4-stage shared-memory ring with 2-D TMA loads (128-byte swizzle),
+// warp 1 issues tcgen05.mma (128 x BN x 16 per instruction) into one of two TMEM accumulators, warps 2-5 drain the
+// other accumulator with tcgen05.ld and write C, so the epilogue of tile i overlaps the main loop of tile i+1.
+// (The building block of the fused paths; upstream calls cuBLAS/cuBLASLt here: pear/models/qwen3_5/trainer/operands.py:204,
+// rollout/blackwell/csrc/gemm_lt.cpp.) No cluster multicast anywhere: operands come through plain per-CTA TMA loads.
+#include "common.cuh"
+
+#include <cudaTypedefs.h>
+
+namespace pear {
+
+constexpr int kBM = 128, kBK = 64, kStages = 4;
+constexpr int kGemmThreads = 192;
+
+struct GemmSmem {
+  uint64_t full[kStages], empty[kStages];
+  uint64_t tmem_full[2], tmem_empty[2];
+  uint32_t tmem_base;
+};
+
+template <int BN, bool OUT_BF16>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, void* __restrict__ c,
+                 int M, int N, int K, int ldc, int* status) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  constexpr uint32_t kABytes = kBM * kBK * 2, kBBytes = BN * kBK * 2, kStageBytes = kABytes + kBBytes;
+  uint8_t* tiles = smem;  // [stage][A | B], 1024-byte aligned
+  GemmSmem* sm = (GemmSmem*)(smem + kStages * kStageBytes);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (M + kBM - 1) / kBM, tiles_n = (N + BN - 1) / BN, ntiles = tiles_m * tiles_n;
+  const int kblocks = (K + kBK - 1) / kBK;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kStages; ++i) { mbar_init(&sm->full[i], 1); mbar_init(&sm->empty[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&sm->tmem_full[i], 1); mbar_init(&sm->tmem_empty[i], 4); }
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&sm->tmem_base, 2 * BN);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = sm->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      prefetch_tensormap(&map_a);
+      prefetch_tensormap(&map_b);
+      int st = 0, ph = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % tiles_m) * kBM, n0 = (tile / tiles_m) * BN;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          ok = mbar_wait_bounded(&sm->empty[st], ph ^ 1, status);
+          if (!ok) break;
+          uint8_t* a = tiles + st * kStageBytes;
+          mbar_expect_tx(&sm->full[st], kStageBytes);
+          tma_load_2d(a, &map_a, kb * kBK, m0, &sm->full[st]);
+          tma_load_2d(a + kABytes, &map_b, kb * kBK, n0, &sm->full[st]);
+          if (++st == kStages) { st = 0; ph ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_f16(kBM, BN, 1);
+      int st = 0, ph = 0, it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++it) {
+        const int ab = it & 1;
+        ok = mbar_wait_bounded(&sm->tmem_empty[ab], ((it >> 1) & 1) ^ 1, status);
+        if (!ok) break;
+        tcgen05_fence_after();
+        const uint32_t d_tmem = tmem_base + ab * BN;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          ok = mbar_wait_bounded(&sm->full[st], ph, status);
+          if (!ok) break;
+          tcgen05_fence_after();
+          const uint32_t a_addr = smem_u32(tiles + st * kStageBytes);
+          const uint64_t da = umma_desc_sw128(a_addr), db = umma_desc_sw128(a_addr + kABytes);
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k)
+            umma_f16(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) != 0 ? 1u : 0u);
+          tcgen05_commit(&sm->empty[st]);  // the stage is free once these MMAs have read it
+          if (++st == kStages) { st = 0; ph ^= 1; }
+        }
+        tcgen05_commit(&sm->tmem_full[ab]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------------------------------------ epilogue
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    int it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++it) {
+      const int ab = it & 1;
+      const int m0 = (tile % tiles_m) * kBM, n0 = (tile / tiles_m) * BN;
+      if (ok) ok = mbar_wait_bounded(&sm->tmem_full[ab], (it >> 1) & 1, status);
+      if (!ok) break;
+      tcgen05_fence_after();
+      const int row = m0 + q * 32 + lane;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + ab * BN + c0, r);
+        tcgen05_wait_ld();
+        if (row < M) {
+          const int col = n0 + c0;
+          if (OUT_BF16) {
+            __nv_bfloat16* dst = (__nv_bfloat16*)c + (size_t)row * ldc + col;
+            if (col + 32 <= N && (ldc % 8) == 0) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                uint4 v;
+                __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+                __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
+                __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
+                v.x = *(uint32_t*)&p0; v.y = *(uint32_t*)&p1; v.z = *(uint32_t*)&p2; v.w = *(uint32_t*)&p3;
+                *(uint4*)(dst + j) = v;
+              }
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (col + j < N) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+            }
+          } else {
+            float* dst = (float*)c + (size_t)row * ldc + col;
+            if (col + 32 <= N && (ldc % 4) == 0) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4)
+                *(float4*)(dst + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
+                                                  __uint_as_float(r[j + 3]));
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (col + j < N) dst[j] = __uint_as_float(r[j]);
+            }
+          }
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sm->tmem_empty[ab]);
+    }
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, 2 * BN);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ host side
+static PFN_cuTensorMapEncodeTiled_v12000 get_encode() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  if (!fn) {
+    cudaDriverEntryPointQueryResult q;
+    void* p = nullptr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (PFN_cuTensorMapEncodeTiled_v12000)p;
+  }
+  return fn;
+}
+
+// Row-major [rows, cols] bf16 matrix with leading dimension ld (elements); box = [box_rows, 64 cols], 128-byte swizzle.
+static int make_map_bf16(CUtensorMap* map, const void* base, int rows, int cols, int ld, int box_rows) {
+  auto enc = get_encode();
+  if (!enc) return (int)cudaErrorNotSupported;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : 1000 + (int)r;
+}
+
+template <int BN, bool OUT_BF16>
+static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, void* c, int M, int N, int K, int ldc, int* status,
+                       int num_sms, cudaStream_t stream) {
+  constexpr int smem = kStages * (kBM * kBK * 2 + BN * kBK * 2) + 1024;
+  static bool configured = false;
+  if (!configured) {
+    PEAR_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_kernel<BN, OUT_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    configured = true;
+  }
+  const int ntiles = ((M + kBM - 1) / kBM) * ((N + BN - 1) / BN);
+  const int grid = ntiles < num_sms ? ntiles : num_sms;
+  gemm_bf16_kernel<BN, OUT_BF16><<<grid, kGemmThreads, smem, stream>>>(ma, mb, c, M, N, K, ldc, status);
+  PEAR_LAUNCH_CHECK();
+  return 0;
+}
+
+}  // namespace pear
+
+// C[M,N] (fp32 or bf16, leading dimension ldc) = A[M,K] (bf16, lda) * B[N,K]^T (bf16, ldb).
+// Requirements: A, B 16-byte aligned, lda and ldb multiples of 8. `status` is a device int (0 = ok) that a bounded wait
+// sets on expiry.
+PEAR_API int pear_gemm_bf16_nt(const void* a, const void* b, void* c, int M, int N, int K, int lda, int ldb, int ldc,
+                               int out_bf16, int* status, int num_sms, void* stream) {
+  using namespace pear;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda % 8) || (ldb % 8) || ((uintptr_t)a % 16) || ((uintptr_t)b % 16)) return (int)cudaErrorInvalidValue;
+  const bool wide = N > 128;
+  CUtensorMap ma, mb;
+  int r = make_map_bf16(&ma, a, M, K, lda, kBM);
+  if (r) return r;
+  r = make_map_bf16(&mb, b, N, K, ldb, wide ? 256 : 128);
+  if (r) return r;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (wide) return out_bf16 ? launch_gemm<256, true>(ma, mb, c, M, N, K, ldc, status, num_sms, s)
+                            : launch_gemm<256, false>(ma, mb, c, M, N, K, ldc, status, num_sms, s);
+  return out_bf16 ? launch_gemm<128, true>(ma, mb, c, M, N, K, ldc, status, num_sms, s)
+                  : launch_gemm<128, false>(ma, mb, c, M, N, K, ldc, status, num_sms, s);
+}

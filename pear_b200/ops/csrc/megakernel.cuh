@@ -96,6 +96,15 @@ struct StepOut {
   float logprobs[4];
 };
 
+// Per-step control record the host copies from pinned memory before every launch: sampling parameters may change
+// between steps of a session without rebuilding anything.
+struct StepCtrl {
+  float temperature;
+  uint32_t seed;
+  int32_t stop_token;   // -1: none (recorded in the output slot when emitted)
+  int32_t reserved[5];
+};
+
 struct Params {
   const Instr* instrs;     // [num_ctas][max_instrs]
   const Desc* descs;
@@ -111,6 +120,7 @@ struct Params {
   int32_t vocab;
   uint32_t barrier_base;   // value of the barrier counter when the launch starts (the counter is never reset)
   int32_t pad;
+  const StepCtrl* ctrl;    // null: temperature/seed above
 };
 
 }  // namespace mk

@@ -40,27 +40,57 @@ __device__ void op_gdn(Ctx& c, const Instr& ins) {
   float* dec = u + 16 * kGdnCh;                    // [16] exp(g)
   float* beta = dec + 16;                          // [16]
 
-  // ---- stage the conv inputs of this item's channels: q(128) k(128) v(nrows)
+  // ---- stage the conv inputs of this item's channels, q(128) k(128) v(nrows), the conv weights and the gates:
+  // every global load is issued before the first use (one L2 round trip for the whole staging)
   const int nch = 2 * kGdnD + nrows;
-  for (int idx = tid; idx < (3 + nseq) * nch; idx += kConsumerThreads) {
-    const int r = idx / nch, ch = idx % nch;
-    const int gch = ch < kGdnD ? hk * kGdnD + ch
-                  : ch < 2 * kGdnD ? Hk * kGdnD + hk * kGdnD + (ch - kGdnD)
-                                   : 2 * Hk * kGdnD + hv * kGdnD + row0 + (ch - 2 * kGdnD);
-    float v;
-    if (r < 3) v = __ldcg(conv_rd + (size_t)r * C + gch);
-    else if (r < 3 + R) v = __ldcg(rec_prev + (size_t)(r - 3) * rstride + gch);
-    else v = __ldcg(rec_cur + (size_t)(r - 3 - R) * rstride + gch);
-    xin[r * kGdnCh + ch] = v;
-  }
-  // gates
-  if (tid < nseq) {
-    const float* row = tid < R ? rec_prev + (size_t)tid * rstride : rec_cur + (size_t)(tid - R) * rstride;
-    const float b = __ldcg(row + C + Hv * kGdnD + hv);
-    const float a = __ldcg(row + C + Hv * kGdnD + Hv + hv);
-    const float A_log = ((const float*)d.p3)[hv], dt_bias = ((const float*)d.p3)[Hv + hv];
-    dec[tid] = __expf(-__expf(A_log) * softplus_f(a + dt_bias));
-    beta[tid] = sigmoid_f(b);
+  auto gch_of = [&](int ch) {
+    return ch < kGdnD ? hk * kGdnD + ch
+         : ch < 2 * kGdnD ? Hk * kGdnD + hk * kGdnD + (ch - kGdnD)
+                          : 2 * Hk * kGdnD + hv * kGdnD + row0 + (ch - 2 * kGdnD);
+  };
+  float* cw = beta + 16;                           // [kGdnCh][4] conv weights of the staged channels
+  {
+    constexpr int kMaxPer = (kGdnMaxRows * kGdnCh + kConsumerThreads - 1) / kConsumerThreads;  // 24
+    const int total = (3 + nseq) * nch;
+    float tmp[kMaxPer];
+#pragma unroll
+    for (int e = 0; e < kMaxPer; ++e) {
+      const int idx = tid + e * kConsumerThreads;
+      if (idx < total) {
+        const int r = idx / nch, gch = gch_of(idx % nch);
+        const float* src = r < 3 ? conv_rd + (size_t)r * C + gch
+                         : r < 3 + R ? rec_prev + (size_t)(r - 3) * rstride + gch
+                                     : rec_cur + (size_t)(r - 3 - R) * rstride + gch;
+        tmp[e] = __ldcg(src);
+      }
+    }
+    float4 wv[2];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int ch = tid + e * kConsumerThreads;
+      if (ch < nch) wv[e] = __ldg((const float4*)(conv_w + (size_t)gch_of(ch) * 4));
+    }
+    float gb = 0.f, ga = 0.f;
+    if (tid < nseq) {
+      const float* row = tid < R ? rec_prev + (size_t)tid * rstride : rec_cur + (size_t)(tid - R) * rstride;
+      gb = __ldcg(row + C + Hv * kGdnD + hv);
+      ga = __ldcg(row + C + Hv * kGdnD + Hv + hv);
+    }
+#pragma unroll
+    for (int e = 0; e < kMaxPer; ++e) {
+      const int idx = tid + e * kConsumerThreads;
+      if (idx < total) xin[(idx / nch) * kGdnCh + idx % nch] = tmp[e];
+    }
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int ch = tid + e * kConsumerThreads;
+      if (ch < nch) *(float4*)(cw + ch * 4) = wv[e];
+    }
+    if (tid < nseq) {
+      const float A_log = ((const float*)d.p3)[hv], dt_bias = ((const float*)d.p3)[Hv + hv];
+      dec[tid] = __expf(-__expf(A_log) * softplus_f(ga + dt_bias));
+      beta[tid] = sigmoid_f(gb);
+    }
   }
   consumer_sync();
 
@@ -70,19 +100,13 @@ __device__ void op_gdn(Ctx& c, const Instr& ins) {
     for (int idx = tid; idx < 3 * nch; idx += kConsumerThreads) {
       const int r = idx / nch, ch = idx % nch;
       if (ch < 2 * kGdnD && !qk_writer) continue;
-      const int gch = ch < kGdnD ? hk * kGdnD + ch
-                    : ch < 2 * kGdnD ? Hk * kGdnD + hk * kGdnD + (ch - kGdnD)
-                                     : 2 * Hk * kGdnD + hv * kGdnD + row0 + (ch - 2 * kGdnD);
-      conv_wr[(size_t)r * C + gch] = xin[(R + r) * kGdnCh + ch];
+      conv_wr[(size_t)r * C + gch_of(ch)] = xin[(R + r) * kGdnCh + ch];
     }
   }
   // ---- conv + SiLU
   for (int idx = tid; idx < nseq * nch; idx += kConsumerThreads) {
     const int r = idx / nch, ch = idx % nch;
-    const int gch = ch < kGdnD ? hk * kGdnD + ch
-                  : ch < 2 * kGdnD ? Hk * kGdnD + hk * kGdnD + (ch - kGdnD)
-                                   : 2 * Hk * kGdnD + hv * kGdnD + row0 + (ch - 2 * kGdnD);
-    const float4 w = *(const float4*)(conv_w + (size_t)gch * 4);
+    const float4 w = *(const float4*)(cw + ch * 4);
     const float acc = w.x * xin[r * kGdnCh + ch] + w.y * xin[(r + 1) * kGdnCh + ch] + w.z * xin[(r + 2) * kGdnCh + ch] +
                       w.w * xin[(r + 3) * kGdnCh + ch];
     u[r * kGdnCh + ch] = silu_f(acc);

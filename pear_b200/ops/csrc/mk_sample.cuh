@@ -18,6 +18,9 @@
 namespace mk {
 using namespace pear;
 
+__device__ __forceinline__ float step_temperature(const Ctx& c) { return c.p->ctrl ? c.p->ctrl->temperature : c.p->temperature; }
+__device__ __forceinline__ uint32_t step_seed(const Ctx& c) { return c.p->ctrl ? c.p->ctrl->seed : c.p->seed; }
+
 __device__ __forceinline__ uint4 philox4x32_10(uint4 ctr, uint2 key) {
   constexpr uint32_t M0 = 0xD2511F53u, M1 = 0xCD9E8D57u, W0 = 0x9E3779B9u, W1 = 0xBB67AE85u;
 #pragma unroll
@@ -44,7 +47,7 @@ __device__ void op_sample_part(Ctx& c, const Instr& ins) {
   const Desc& d = c.p->descs[ins.desc];
   const StepRec* rec = c.rec;
   const int T = rec->T, V = d.i1, chunk = d.i2, nchunks = d.i3;
-  const float inv_t = 1.f / c.p->temperature;
+  const float inv_t = 1.f / step_temperature(c);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   float* part = (float*)d.p4;
   for (int ch = ins.a; ch < ins.a + ins.b; ++ch) {
@@ -56,7 +59,7 @@ __device__ void op_sample_part(Ctx& c, const Instr& ins) {
       for (int i = ch * chunk + tid * 4; i < min(V, (ch + 1) * chunk); i += kConsumerThreads * 4) {
         const float4 z4 = __ldcg((const float4*)(row + i));
         const uint4 rnd = philox4x32_10(make_uint4((uint32_t)(i >> 2), (uint32_t)r, (uint32_t)rec->step, 0u),
-                                        make_uint2(c.p->seed, 0x5eedu));
+                                        make_uint2(step_seed(c), 0x5eedu));
         const float z[4] = {z4.x * inv_t, z4.y * inv_t, z4.z * inv_t, z4.w * inv_t};
         const uint32_t rr[4] = {rnd.x, rnd.y, rnd.z, rnd.w};
 #pragma unroll
@@ -125,7 +128,7 @@ __device__ void op_sample_fin(Ctx& c, const Instr& ins) {
     return;
   }
   const int T = rec->T, nchunks = d.i3;
-  const float inv_t = 1.f / c.p->temperature;
+  const float inv_t = 1.f / step_temperature(c);
   const float* part = (const float*)d.p4;
   float* lse_s = c.sm->red;        // [8]
   float* best_s = c.sm->red + 8;   // [8] (int bits)
@@ -157,7 +160,7 @@ __device__ void op_sample_fin(Ctx& c, const Instr& ins) {
       const int dtok = rec->tokens[r + 1];
       const float lp = __ldcg(logits + (size_t)r * d.i0 + dtok) * inv_t - lse_s[r];
       const uint4 rnd = philox4x32_10(make_uint4(0xffffffffu, (uint32_t)r, (uint32_t)rec->step, 1u),
-                                      make_uint2(c.p->seed, 0x5eedu));
+                                      make_uint2(step_seed(c), 0x5eedu));
       if (__logf(u01(rnd.x)) < lp) ++n_acc; else break;
     }
     const int y = __float_as_int(best_s[n_acc]);

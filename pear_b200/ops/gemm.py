@@ -1,0 +1,77 @@
+"""bf16 GEMM bindings: ``C = A @ B^T`` on the tcgen05/TMEM/TMA kernel (``csrc/gemm_tcgen05.cu``).
+
+``linear_bf16`` is the forward of every bf16 linear layer of the trainer model; its backward (dX = dY @ W,
+dW = dY^T @ X) is a plain library GEMM (cuBLAS through torch), which needs the MN-major operand forms the kernel does
+not take.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from .lib import check, count_launch, lib, ptr, stream
+
+_status = {}
+_sms = {}
+
+
+def _dev_state(device: torch.device):
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    if key not in _status:
+        _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
+        _sms[key] = torch.cuda.get_device_properties(device).multi_processor_count
+    return _status[key], _sms[key]
+
+
+def gemm_nt(a: torch.Tensor, b: torch.Tensor, out_dtype=torch.float32, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``a`` [M, K] bf16, ``b`` [N, K] bf16 (row-major, K contiguous) -> [M, N] in fp32 or bf16."""
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.shape[1] == b.shape[1]
+    if a.stride(1) != 1 or a.stride(0) % 8 or a.data_ptr() % 16:
+        a = a.contiguous()
+    if b.stride(1) != 1 or b.stride(0) % 8 or b.data_ptr() % 16:
+        b = b.contiguous()
+    m, k = a.shape
+    n = b.shape[0]
+    if k % 8:
+        raise ValueError("K must be a multiple of 8 (16-byte rows for TMA)")
+    c = out if out is not None else torch.empty(m, n, dtype=out_dtype, device=a.device)
+    status, sms = _dev_state(a.device)
+    check(lib().pear_gemm_bf16_nt(ptr(a), ptr(b), ptr(c), m, n, k, a.stride(0), b.stride(0), c.stride(0),
+                                  1 if c.dtype == torch.bfloat16 else 0, ptr(status), sms, stream()), "gemm_bf16_nt")
+    count_launch()
+    return c
+
+
+def gemm_status(device=None) -> int:
+    status, _ = _dev_state(torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device))
+    return int(status.item())
+
+
+class _LinearBF16(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight):
+        shape = x.shape
+        x2 = x.reshape(-1, shape[-1]).to(torch.bfloat16)
+        ctx.save_for_backward(x2, weight)
+        ctx.in_dtype, ctx.shape = x.dtype, shape
+        y = gemm_nt(x2, weight, torch.float32)
+        return y.view(*shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, weight = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1]).to(torch.bfloat16)
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = (dy2 @ weight).to(ctx.in_dtype).view(ctx.shape)
+        if ctx.needs_input_grad[1]:
+            dw = (dy2.t() @ x2).to(weight.dtype)
+        return dx, dw
+
+
+def linear_bf16(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    if weight.shape[1] % 8 or x.numel() == 0:
+        return torch.nn.functional.linear(x.to(weight.dtype), weight).float()
+    return _LinearBF16.apply(x, weight)

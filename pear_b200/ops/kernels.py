@@ -1,0 +1,217 @@
+"""Autograd bindings of the sm_100a kernels in ``csrc/`` (library loaded by :mod:`pear_b200.ops.lib`).
+
+Each op is a :class:`torch.autograd.Function` whose forward and backward launch the hand-written kernels on the current
+stream. Ops that do not have a kernel yet run the torch statement on the device (cuBLAS / SDPA library calls) and are
+listed in ``LIBRARY_FALLBACKS`` so reports can say so.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.nn.functional as F
+
+from . import reference as ref
+from .lib import check, count_launch, lib, ptr, stream
+
+DT_F32, DT_BF16 = 0, 1
+LIBRARY_FALLBACKS = {"causal_attention": "torch SDPA", "causal_conv_silu": "torch", "gdn_scan": "torch chunked scan",
+                     "logprob_entropy": "torch chunked (cuBLAS)"}
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return DT_F32
+    if t.dtype == torch.bfloat16:
+        return DT_BF16
+    raise TypeError(f"unsupported dtype {t.dtype}")
+
+
+def _f32c(t: torch.Tensor) -> torch.Tensor:
+    return t.float().contiguous()
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+class _RMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, eps, one_plus, residual):
+        shape = x.shape
+        dim = shape[-1]
+        xc = x.contiguous()
+        if xc.dtype not in (torch.float32, torch.bfloat16):
+            xc = xc.float()
+        rows = xc.numel() // dim
+        w = _f32c(weight)
+        y = torch.empty(shape, dtype=torch.float32, device=x.device)
+        rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+        res_in = _f32c(residual) if residual is not None else None
+        res_out = torch.empty(shape, dtype=torch.float32, device=x.device) if residual is not None else None
+        check(lib().pear_rms_norm_fwd(ptr(xc), _dt(xc), ptr(res_in), ptr(w), ptr(y), DT_F32, ptr(res_out), ptr(rstd),
+                                      rows, dim, ctypes.c_float(eps), int(one_plus), stream()), "rms_norm_fwd")
+        count_launch()
+        normed_in = res_out if residual is not None else (xc if xc.dtype == torch.float32 else xc.float())
+        ctx.save_for_backward(normed_in, w, rstd)
+        ctx.one_plus, ctx.has_res, ctx.wdtype, ctx.xdtype = one_plus, residual is not None, weight.dtype, x.dtype
+        if residual is not None:
+            return y, res_out
+        return y
+
+    @staticmethod
+    def backward(ctx, dy, dres=None):
+        r, w, rstd = ctx.saved_tensors
+        dim = r.shape[-1]
+        rows = r.numel() // dim
+        dyc = _f32c(dy) if dy is not None else torch.zeros_like(r)
+        dresc = _f32c(dres) if (ctx.has_res and dres is not None) else None
+        dx = torch.empty_like(r)
+        dw = torch.zeros(dim, dtype=torch.float32, device=r.device)
+        check(lib().pear_rms_norm_bwd(ptr(dyc), ptr(r), ptr(w), ptr(rstd), ptr(dresc), ptr(dx), ptr(dw), rows, dim,
+                                      int(ctx.one_plus), stream()), "rms_norm_bwd")
+        count_launch()
+        dxo = dx.to(ctx.xdtype)
+        return dxo, dw.to(ctx.wdtype), None, None, (dx if ctx.has_res else None)
+
+
+def rms_norm(x, weight, eps=1e-6, one_plus=True):
+    return _RMSNorm.apply(x, weight, eps, one_plus, None)
+
+
+def add_rms_norm(x, residual, weight, eps=1e-6):
+    return _RMSNorm.apply(x, weight, eps, True, residual)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+class _GatedRMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, o, z, weight, eps):
+        oc, zc, w = _f32c(o), _f32c(z), _f32c(weight)
+        dim = oc.shape[-1]
+        rows = oc.numel() // dim
+        y = torch.empty_like(oc)
+        rstd = torch.empty(rows, dtype=torch.float32, device=o.device)
+        check(lib().pear_gated_rms_norm_fwd(ptr(oc), ptr(zc), ptr(w), ptr(y), DT_F32, ptr(rstd), rows, dim,
+                                            ctypes.c_float(eps), stream()), "gated_rms_norm_fwd")
+        count_launch()
+        ctx.save_for_backward(oc, zc, w, rstd)
+        ctx.wdtype = weight.dtype
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        oc, zc, w, rstd = ctx.saved_tensors
+        dim = oc.shape[-1]
+        rows = oc.numel() // dim
+        d_o, d_z = torch.empty_like(oc), torch.empty_like(zc)
+        dw = torch.zeros(dim, dtype=torch.float32, device=oc.device)
+        check(lib().pear_gated_rms_norm_bwd(ptr(_f32c(dy)), ptr(oc), ptr(zc), ptr(w), ptr(rstd), ptr(d_o), ptr(d_z), ptr(dw),
+                                            rows, dim, stream()), "gated_rms_norm_bwd")
+        count_launch()
+        return d_o, d_z, dw.to(ctx.wdtype), None
+
+
+def gated_rms_norm(o, z, weight, eps=1e-6):
+    return _GatedRMSNorm.apply(o, z, weight, eps)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+class _SwiGLU(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gate, up):
+        g, u = _f32c(gate), _f32c(up)
+        y = torch.empty_like(g)
+        check(lib().pear_swiglu_fwd(ptr(g), ptr(u), ptr(y), DT_F32, ctypes.c_longlong(g.numel()), stream()), "swiglu_fwd")
+        count_launch()
+        ctx.save_for_backward(g, u)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        g, u = ctx.saved_tensors
+        dg, du = torch.empty_like(g), torch.empty_like(u)
+        check(lib().pear_swiglu_bwd(ptr(_f32c(dy)), ptr(g), ptr(u), ptr(dg), ptr(du), ctypes.c_longlong(g.numel()), stream()),
+              "swiglu_bwd")
+        count_launch()
+        return dg, du
+
+
+def swiglu(gate, up):
+    return _SwiGLU.apply(gate, up)
+
+
+class _SigmoidGate(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, gate):
+        xc, g = _f32c(x), _f32c(gate)
+        y = torch.empty_like(xc)
+        check(lib().pear_sigmoid_gate_fwd(ptr(xc), ptr(g), ptr(y), DT_F32, ctypes.c_longlong(xc.numel()), stream()), "gate_fwd")
+        count_launch()
+        ctx.save_for_backward(xc, g)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        xc, g = ctx.saved_tensors
+        dx, dg = torch.empty_like(xc), torch.empty_like(g)
+        check(lib().pear_sigmoid_gate_bwd(ptr(_f32c(dy)), ptr(xc), ptr(g), ptr(dx), ptr(dg), ctypes.c_longlong(xc.numel()),
+                                          stream()), "gate_bwd")
+        count_launch()
+        return dx, dg
+
+
+def sigmoid_gate(x, gate):
+    return _SigmoidGate.apply(x, gate)
+
+
+class _Rope(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, cos, sin):
+        xc, c, s = _f32c(x), _f32c(cos), _f32c(sin)
+        t, h, d = xc.shape
+        y = torch.empty_like(xc)
+        check(lib().pear_rope(ptr(xc), ptr(c), ptr(s), ptr(y), t, h, d, c.shape[-1], ctypes.c_float(1.0), stream()), "rope")
+        count_launch()
+        ctx.save_for_backward(c, s)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        c, s = ctx.saved_tensors
+        dyc = _f32c(dy)
+        t, h, d = dyc.shape
+        dx = torch.empty_like(dyc)
+        check(lib().pear_rope(ptr(dyc), ptr(c), ptr(s), ptr(dx), t, h, d, c.shape[-1], ctypes.c_float(-1.0), stream()), "rope_bwd")
+        count_launch()
+        return dx, None, None
+
+
+def apply_rope(x, cos, sin):
+    return _Rope.apply(x, cos, sin)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# GEMM: tcgen05 kernel when the shape qualifies, cuBLAS otherwise
+# ---------------------------------------------------------------------------------------------------------------------
+def linear_bf16(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    from . import gemm
+
+    return gemm.linear_bf16(x, weight)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# ops still on library kernels
+# ---------------------------------------------------------------------------------------------------------------------
+def causal_attention(q, k, v, cu_seqlens, scale=None):
+    return ref.causal_attention(q, k, v, cu_seqlens, scale)
+
+
+def causal_conv_silu(x, weight, bounds, init_state=None):
+    return ref.causal_conv_silu(x, weight, bounds, init_state)
+
+
+def gdn_scan(q, k, v, g, beta, state=None):
+    return ref.gdn_chunked(q, k, v, g, beta, state)
+
+
+def logprob_entropy(hidden, weight, ids, temperature=1.0, chunk=4096):
+    return ref.logprob_entropy(hidden, weight, ids, temperature, chunk)

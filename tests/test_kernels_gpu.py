@@ -1,0 +1,104 @@
+"""Elementwise / norm / rope kernels and the tcgen05 GEMM against the plain fp32 torch statements (forward + backward)."""
+
+import pytest
+import torch
+
+from pear_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+
+
+def _grads(fn, inputs, gout_seed=0):
+    ins = [i.clone().requires_grad_(True) if i.is_floating_point() else i for i in inputs]
+    out = fn(*ins)
+    outs = out if isinstance(out, tuple) else (out,)
+    g = torch.Generator(device=outs[0].device).manual_seed(gout_seed)
+    loss = sum((o * torch.randn(o.shape, device=o.device, generator=g)).sum() for o in outs)
+    loss.backward()
+    return outs, [i.grad for i in ins if i.is_floating_point()]
+
+
+def _cmp(a, b, tol=2e-5):
+    for x, y in zip(a, b):
+        scale = y.abs().max().item() + 1e-6
+        assert (x.float() - y.float()).abs().max().item() <= tol * scale + 1e-6
+
+
+@pytest.mark.parametrize("rows,dim,one_plus", [(37, 5120, True), (300, 256, True), (129, 128, False)])
+def test_rms_norm(rows, dim, one_plus):
+    from pear_b200.ops import kernels as K
+
+    torch.manual_seed(0)
+    x = torch.randn(rows, dim, device="cuda") * 3
+    w = torch.randn(dim, device="cuda") * 0.2
+    o1, g1 = _grads(lambda a, b: K.rms_norm(a, b, 1e-6, one_plus), [x, w])
+    o2, g2 = _grads(lambda a, b: ref.rms_norm(a, b, 1e-6, one_plus), [x, w])
+    _cmp(o1, o2)
+    _cmp(g1, g2, 1e-4)
+
+
+def test_add_rms_norm():
+    from pear_b200.ops import kernels as K
+
+    torch.manual_seed(1)
+    x, r = torch.randn(65, 5120, device="cuda"), torch.randn(65, 5120, device="cuda") * 4
+    w = torch.randn(5120, device="cuda") * 0.1
+    o1, g1 = _grads(lambda a, b, c: K.add_rms_norm(a, b, c, 1e-6), [x, r, w])
+    o2, g2 = _grads(lambda a, b, c: ref.add_rms_norm(a, b, c, 1e-6), [x, r, w])
+    _cmp(o1, o2)
+    _cmp(g1, g2, 1e-4)
+
+
+def test_gated_rms_norm_swiglu_gate_rope():
+    from pear_b200.ops import kernels as K
+
+    torch.manual_seed(2)
+    o, z = torch.randn(50, 48, 128, device="cuda"), torch.randn(50, 48, 128, device="cuda")
+    w = torch.rand(128, device="cuda") + 0.5
+    _o1, _g1 = _grads(lambda a, b, c: K.gated_rms_norm(a, b, c, 1e-6), [o, z, w])
+    _o2, _g2 = _grads(lambda a, b, c: ref.gated_rms_norm(a, b, c, 1e-6), [o, z, w])
+    _cmp(_o1, _o2); _cmp(_g1, _g2, 1e-4)
+    g, u = torch.randn(33, 17408, device="cuda"), torch.randn(33, 17408, device="cuda")
+    a1, b1 = _grads(K.swiglu, [g, u]); a2, b2 = _grads(ref.swiglu, [g, u])
+    _cmp(a1, a2); _cmp(b1, b2)
+    a1, b1 = _grads(K.sigmoid_gate, [g, u]); a2, b2 = _grads(ref.sigmoid_gate, [g, u])
+    _cmp(a1, a2); _cmp(b1, b2)
+    x = torch.randn(77, 24, 256, device="cuda")
+    pos = torch.stack([torch.arange(77), torch.arange(77) // 2, torch.arange(77) // 3]).cuda()
+    cos, sin = ref.mrope_cos_sin(pos, 64, 1e7, (11, 11, 10))
+    a1, b1 = _grads(lambda t: K.apply_rope(t, cos, sin), [x]); a2, b2 = _grads(lambda t: ref.apply_rope(t, cos, sin), [x])
+    _cmp(a1, a2); _cmp(b1, b2)
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (300, 520, 200), (4096, 5120, 5120), (77, 100, 136), (1024, 34816, 5120)])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_gemm_tcgen05(m, n, k, out_dtype):
+    from pear_b200.ops import gemm
+
+    torch.manual_seed(3)
+    a = (torch.randn(m, k, device="cuda") * 0.5).bfloat16()
+    b = (torch.randn(n, k, device="cuda") * 0.5).bfloat16()
+    c = gemm.gemm_nt(a, b, out_dtype)
+    torch.cuda.synchronize()
+    assert gemm.gemm_status() == 0
+    refc = a.float() @ b.float().t()
+    err = (c.float() - refc).abs().max().item()
+    tol = (2e-5 if out_dtype == torch.float32 else 8e-3) * refc.abs().max().item() + 1e-4
+    assert err <= tol, f"max err {err} tol {tol}"
+
+
+def test_linear_bf16_autograd():
+    from pear_b200.ops import gemm
+
+    torch.manual_seed(4)
+    x = torch.randn(200, 512, device="cuda", requires_grad=True)
+    w = (torch.randn(768, 512, device="cuda") * 0.05).bfloat16().requires_grad_(True)
+    y = gemm.linear_bf16(x, w)
+    y.square().sum().backward()
+    xr = x.detach().clone().requires_grad_(True)
+    wr = w.detach().float().requires_grad_(True)
+    yr = xr.bfloat16().float() @ wr.t()
+    yr.square().sum().backward()
+    assert (y - yr).abs().max() <= 1e-3 * yr.abs().max()
+    assert (x.grad - xr.grad).abs().max() <= 2e-2 * xr.grad.abs().max()
+    assert (w.grad.float() - wr.grad).abs().max() <= 2e-2 * wr.grad.abs().max()

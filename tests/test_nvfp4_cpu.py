@@ -36,9 +36,10 @@ def test_pack_unpack_roundtrip():
     assert torch.equal(c, q.codes) and torch.equal(s, q.scales)
 
 
-def test_stage_layout_matches_kernel_fragment_indexing():
-    """Emulates gemv_stage of decode_megakernel.cu: lane (g, t) of warp w reads 16 code bytes per quad and 8 scale bytes,
-    and feeds mma.m16n8k16 whose A rows are (g, g+8) and K slots (2t, 2t+1, 2t+8, 2t+9) <-> original k 4t..4t+3."""
+def test_stage_layout_matches_tensor_core_operand_addressing():
+    """Emulates what the block-scaled MMA of decode_megakernel.cu reads: for the j-th K-64 step of a stage, element
+    (row, k) sits at ``j*4096 + (k // 32) * LBO(2048) + (row // 8) * SBO(128) + (row % 8) * 16 + (k % 32) // 2`` (low
+    nibble = even k), and its scale at ``16384 + j*512 + (row % 32) * 16 + (row // 32) * 4 + (k // 16)``."""
     torch.manual_seed(2)
     n, k = 128, 256
     w = torch.randn(n, k)
@@ -54,20 +55,12 @@ def test_stage_layout_matches_kernel_fragment_indexing():
 
     e4m3 = torch.arange(256, dtype=torch.uint8).view(torch.float8_e4m3fn).float().numpy()
     out = np.zeros(n, dtype=np.float64)
-    for warp in range(8):
-        for lane in range(32):
-            g, t = lane >> 2, lane & 3
-            for quad in range(4):
-                cbase = ((warp * 4 + quad) * 32 + lane) * 16
-                sbase = nvfp4.STAGE_CODE_BYTES + (warp * 4 + quad) * 64 + g * 8
-                for j in range(4):
-                    s_lo, s_hi = e4m3[stage[sbase + j * 2]], e4m3[stage[sbase + j * 2 + 1]]
-                    kk = quad * 64 + j * 16 + 4 * t
-                    for b in range(4):
-                        byte = int(stage[cbase + j * 4 + b])
-                        row = warp * 16 + g + 8 * (b & 1)
-                        k0 = kk + 2 * (b >> 1)
-                        sc = s_hi if (b & 1) else s_lo
-                        out[row] += sc * (dec(byte & 15) * x[k0] + dec(byte >> 4) * x[k0 + 1])
+    for j in range(4):
+        for row in range(n):
+            for kk in range(64):
+                byte = int(stage[j * 4096 + (kk // 32) * 2048 + (row // 8) * 128 + (row % 8) * 16 + (kk % 32) // 2])
+                nib = (byte >> 4) if (kk & 1) else (byte & 15)
+                sc = e4m3[stage[nvfp4.STAGE_CODE_BYTES + j * 512 + (row % 32) * 16 + (row // 32) * 4 + kk // 16]]
+                out[row] += sc * dec(nib) * x[j * 64 + kk]
     ref = deq.astype(np.float64) @ x
     assert np.allclose(out, ref, rtol=1e-5, atol=1e-5)
