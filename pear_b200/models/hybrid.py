@@ -265,13 +265,9 @@ class HybridForCausalLM(nn.Module):
         return r
 
     def run_layers(self, r: torch.Tensor, meta: SeqMeta) -> torch.Tensor:
+        runner = getattr(self, "layer_runner", None)
         for i, layer in enumerate(self.model.layers):
-            if self.gradient_checkpointing and torch.is_grad_enabled():
-                from ..train.checkpointing import checkpoint_layer
-
-                r = checkpoint_layer(layer, r, meta, self.activation_offload, i)
-            else:
-                r = layer(r, meta)
+            r = runner(i, layer, r, meta) if runner is not None else layer(r, meta)
         return r
 
     def forward(self, input_ids: torch.Tensor, position_ids: Optional[torch.Tensor] = None, cu_seqlens=None,

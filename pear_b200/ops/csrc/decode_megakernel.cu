@@ -420,7 +420,7 @@ namespace mk {
 // ---------------------------------------------------------------------------------------------------------------------
 // the kernel
 // ---------------------------------------------------------------------------------------------------------------------
-__global__ void __maxnreg__(224) mk_main(const __grid_constant__ Params p, int ns, int nb) {
+__global__ void __launch_bounds__(kThreads, 1) mk_main(const __grid_constant__ Params p, int ns, int nb) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   Smem* sm = (Smem*)smem_raw;
   uint8_t* ring = smem_raw + 1024;

@@ -1,0 +1,194 @@
+"""ZeRO-3 style parameter sharding owned by the trainer (no wrapper framework).
+
+Each unit (one decoder layer, or the root: embedding + final norm + head + MTP) flattens its parameters into one
+buffer, keeps an fp32 master SHARD of it as the optimizer's parameter, all-gathers the compute-dtype copy right before
+the unit runs and frees it right after, and reduce-scatters the unit's gradients as soon as its backward finishes.
+Units are driven explicitly by the layer runner (:mod:`pear_b200.train.checkpointing`), which also recomputes the layer
+in backward, so gather / recompute / reduce-scatter / release happen in one place per layer.
+
+Behaviours kept from the upstream FSDP2 setup (``3rdparty/verl/patches``): named ``fp32_modules`` become their own fp32
+units (0027); with a replicate group (HSDP) the replica all-reduce runs on the last micro-batch only while the
+reduce-scatter runs on every micro-batch (0019); the replicate communicator is warmed right after sharding (0020).
+"""
+
+from __future__ import annotations
+
+from typing import Iterable, Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from . import collectives as C
+
+
+class FlatUnit:
+    def __init__(self, name: str, params: list[tuple[str, nn.Parameter]], shard_group=None, replicate_group=None,
+                 compute_dtype: torch.dtype = torch.bfloat16, device=None, average: bool = False):
+        self.name = name
+        self.average = average  # False: gradients are SUMMED over ranks (the loss is already normalised globally)
+        self.names = [n for n, _ in params]
+        self.params = [p for _, p in params]
+        self.group, self.replicate_group = shard_group, replicate_group
+        self.world = dist.get_world_size(shard_group) if shard_group is not None else 1
+        self.rank = dist.get_rank(shard_group) if shard_group is not None else 0
+        self.compute_dtype = compute_dtype
+        self.shapes = [tuple(p.shape) for p in self.params]
+        self.numels = [p.numel() for p in self.params]
+        total = sum(self.numels)
+        align = 8 * self.world  # 16-byte aligned bf16 shards
+        self.padded = (total + align - 1) // align * align
+        self.shard_numel = self.padded // self.world
+        device = device or self.params[0].device
+        flat = torch.zeros(self.padded, dtype=torch.float32, device=device)
+        o = 0
+        for p, n in zip(self.params, self.numels):
+            flat[o : o + n] = p.detach().reshape(-1).float().to(device)
+            o += n
+        # the optimizer's parameter: this rank's fp32 master shard
+        self.shard = nn.Parameter(flat[self.rank * self.shard_numel : (self.rank + 1) * self.shard_numel].clone())
+        self.full: Optional[torch.Tensor] = None
+        self._empty = torch.empty(0, dtype=compute_dtype, device=device)
+        for p in self.params:
+            p.data = self._empty
+        self.gathered = False
+
+    # -- parameter lifetime -----------------------------------------------------------------------------------------
+    def gather(self, stream=None) -> None:
+        if self.gathered:
+            return
+        local = self.shard.detach().to(self.compute_dtype)
+        if self.world > 1:
+            full = torch.empty(self.padded, dtype=self.compute_dtype, device=local.device)
+            dist.all_gather_into_tensor(full, local.contiguous(), group=self.group)
+        else:
+            full = local if local.data_ptr() != self.shard.data_ptr() else local.clone()
+        self.full = full
+        o = 0
+        for p, n, shp in zip(self.params, self.numels, self.shapes):
+            p.data = full[o : o + n].view(shp)
+            o += n
+        self.gathered = True
+
+    def release(self) -> None:
+        for p in self.params:
+            p.data = self._empty
+        self.full = None
+        self.gathered = False
+
+    # -- gradients ----------------------------------------------------------------------------------------------------
+    def reduce_grads(self, last_micro_batch: bool = True) -> None:
+        """Flatten the unit's full gradients, reduce-scatter over the shard group into the master shard's ``.grad``
+        (accumulating over micro-batches), and all-reduce over the replicate group on the last micro-batch."""
+        average = self.average
+        flat = torch.zeros(self.padded, dtype=torch.float32, device=self.shard.device)
+        o = 0
+        for p, n in zip(self.params, self.numels):
+            if p.grad is not None:
+                flat[o : o + n] = p.grad.reshape(-1).float()
+                p.grad = None
+            o += n
+        if self.world > 1:
+            piece = C.reduce_scatter_sum(flat, self.group)
+            if average:
+                piece = piece / self.world
+        else:
+            piece = flat
+        if self.shard.grad is None:
+            self.shard.grad = piece.clone()
+        else:
+            self.shard.grad.add_(piece)
+        if last_micro_batch and self.replicate_group is not None and dist.get_world_size(self.replicate_group) > 1:
+            dist.all_reduce(self.shard.grad, group=self.replicate_group)
+            if average:
+                self.shard.grad.div_(dist.get_world_size(self.replicate_group))
+
+    # -- full state (checkpoint export, weight sync) ------------------------------------------------------------------
+    def full_state(self, dtype=torch.float32) -> dict[str, torch.Tensor]:
+        local = self.shard.detach().to(dtype)
+        if self.world > 1:
+            full = torch.empty(self.padded, dtype=dtype, device=local.device)
+            dist.all_gather_into_tensor(full, local.contiguous(), group=self.group)
+        else:
+            full = local
+        out, o = {}, 0
+        for name, n, shp in zip(self.names, self.numels, self.shapes):
+            out[name] = full[o : o + n].view(shp).clone()
+            o += n
+        return out
+
+    def load_full_state(self, state: dict[str, torch.Tensor]) -> None:
+        flat = torch.zeros(self.padded, dtype=torch.float32, device=self.shard.device)
+        o = 0
+        for name, n in zip(self.names, self.numels):
+            flat[o : o + n] = state[name].reshape(-1).float().to(flat.device)
+            o += n
+        with torch.no_grad():
+            self.shard.copy_(flat[self.rank * self.shard_numel : (self.rank + 1) * self.shard_numel])
+
+
+class ShardedModel:
+    """The model's parameters as flat sharded units: one per decoder layer, fp32 units for ``fp32_modules``, one root."""
+
+    def __init__(self, model: nn.Module, shard_group=None, replicate_group=None, compute_dtype=torch.bfloat16,
+                 fp32_modules: Iterable[str] = (), device=None):
+        self.model = model
+        self.units: dict[str, FlatUnit] = {}
+        taken: set[int] = set()
+        named = dict(model.named_parameters())
+        fp32_modules = tuple(fp32_modules)
+
+        def make(name: str, items: list[tuple[str, nn.Parameter]], dtype) -> None:
+            items = [(n, p) for n, p in items if id(p) not in taken]
+            if not items:
+                return
+            taken.update(id(p) for _, p in items)
+            self.units[name] = FlatUnit(name, items, shard_group, replicate_group, dtype, device)
+
+        for pat in fp32_modules:
+            make(f"fp32:{pat}", [(n, p) for n, p in named.items() if pat in n], torch.float32)
+        self.layer_units: list[FlatUnit] = []
+        for i, layer in enumerate(model.model.layers):
+            make(f"layer{i}", [(f"model.layers.{i}.{n}", p) for n, p in layer.named_parameters()], compute_dtype)
+            self.layer_units.append(self.units[f"layer{i}"])
+        make("root", [(n, p) for n, p in named.items()], compute_dtype)
+        self.root = self.units.get("root")
+        if replicate_group is not None and dist.get_world_size(replicate_group) > 1:
+            # warm the replicate communicator while memory is still free
+            dist.all_reduce(torch.zeros(1, device=self.root.shard.device), group=replicate_group)
+
+    def parameters(self) -> list[nn.Parameter]:
+        return [u.shard for u in self.units.values()]
+
+    def gather_static(self) -> None:
+        for name, u in self.units.items():
+            if not name.startswith("layer"):
+                u.gather()
+
+    def release_static(self) -> None:
+        for name, u in self.units.items():
+            if not name.startswith("layer"):
+                u.release()
+
+    def reduce_static_grads(self, last_micro_batch: bool = True) -> None:
+        for name, u in self.units.items():
+            if not name.startswith("layer"):
+                u.reduce_grads(last_micro_batch)
+
+    def full_state_dict(self, dtype=torch.float32) -> dict[str, torch.Tensor]:
+        out: dict[str, torch.Tensor] = {}
+        for u in self.units.values():
+            out.update(u.full_state(dtype))
+        return out
+
+    def load_full_state_dict(self, state: dict[str, torch.Tensor]) -> None:
+        for u in self.units.values():
+            u.load_full_state(state)
+
+    def shard_state(self) -> dict[str, torch.Tensor]:
+        return {name: u.shard.detach().clone() for name, u in self.units.items()}
+
+    def load_shard_state(self, state: dict[str, torch.Tensor]) -> None:
+        with torch.no_grad():
+            for name, u in self.units.items():
+                u.shard.copy_(state[name])

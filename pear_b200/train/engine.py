@@ -1,0 +1,306 @@
+"""Trainer engine: sharded hybrid model + GRPO forward/backward over packed micro-batches + optimizer step.
+
+The role of upstream ``pear/trainer/engine.py`` (``PearFSDPEngine``): kernels are installed in a fixed order before the
+model is sharded (``kernels.install`` -> ``check_model`` -> ``install_gpu_backend`` -> ``install_checkpointing``,
+``engine.py:71-98``), garbage collection is frozen after init (``:55-62``), a batch whose fast path reports an overflow
+is re-run on the safe path (``forward_backward_batch`` ``:100-112``), and the sampler's top-k head ids are passed into
+the fused head whose log-probs become the score-centering term (``:114-137``). The optimizer update is clip -> skip on a
+non-finite norm -> step (``3rdparty/verl/patches/0017-*``); a resumed run trains at the CONFIGURED learning rate at the
+restored schedule position (``0003-*``).
+"""
+
+from __future__ import annotations
+
+import gc
+import math
+from dataclasses import dataclass, field
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from ..models.config import HybridConfig
+from ..models.hybrid import HybridForCausalLM
+from ..models.kernels import TrainingKernels
+from ..ops import api as ops
+from ..parallel.fsdp import ShardedModel
+from ..parallel.ulysses import SequenceParallel
+from . import grpo
+from .checkpointing import LayerRunner, install as install_runner
+from .offload import CheckpointInputOffload
+from .streamed_adamw import StreamedAdamW
+
+
+@dataclass
+class PackedBatch:
+    """Packed (padding-free) trajectories. All per-token tensors have T entries; ``labels[t]`` is the token following
+    ``input_ids[t]`` inside its sequence (anything where ``loss_mask`` is 0)."""
+
+    input_ids: torch.Tensor
+    position_ids: torch.Tensor
+    cu_seqlens: list[int]
+    labels: torch.Tensor
+    loss_mask: torch.Tensor
+    advantages: torch.Tensor
+    sampler_log_probs: Optional[torch.Tensor] = None
+    head_ids: Optional[torch.Tensor] = None
+    head_log_probs: Optional[torch.Tensor] = None
+    inputs_embeds: Optional[torch.Tensor] = None
+    embeds_mask: Optional[torch.Tensor] = None
+
+    @property
+    def num_tokens(self) -> int:
+        return int(self.input_ids.shape[0])
+
+    def to(self, device) -> "PackedBatch":
+        kw = {}
+        for k, v in self.__dict__.items():
+            kw[k] = v.to(device, non_blocking=True) if torch.is_tensor(v) else v
+        return PackedBatch(**kw)
+
+    def pad_to_multiple(self, m: int) -> "PackedBatch":
+        """Append a dummy masked sequence so that T is a multiple of ``m`` (equal sequence-parallel slices)."""
+        pad = (-self.num_tokens) % m
+        if pad == 0:
+            return self
+        def ext(t, fill=0):
+            if t is None:
+                return None
+            shape = (pad,) + tuple(t.shape[1:])
+            return torch.cat([t, torch.full(shape, fill, dtype=t.dtype, device=t.device)], dim=0)
+        pos = self.position_ids
+        if pos.dim() == 2:
+            pos = torch.cat([pos, torch.arange(pad, device=pos.device).expand(pos.shape[0], pad)], dim=1)
+        else:
+            pos = torch.cat([pos, torch.arange(pad, device=pos.device)])
+        return PackedBatch(
+            input_ids=ext(self.input_ids), position_ids=pos, cu_seqlens=self.cu_seqlens + [self.cu_seqlens[-1] + pad],
+            labels=ext(self.labels), loss_mask=ext(self.loss_mask), advantages=ext(self.advantages),
+            sampler_log_probs=ext(self.sampler_log_probs), head_ids=ext(self.head_ids),
+            head_log_probs=ext(self.head_log_probs, -math.log(max(1, self.head_ids.shape[1])) if self.head_ids is not None else 0),
+            inputs_embeds=ext(self.inputs_embeds), embeds_mask=ext(self.embeds_mask, False) if self.embeds_mask is not None else None)
+
+    def slice(self, lo: int, hi: int) -> "PackedBatch":
+        def cut(t):
+            return None if t is None else t[lo:hi]
+        pos = self.position_ids[..., lo:hi]
+        return PackedBatch(cut(self.input_ids), pos, self.cu_seqlens, cut(self.labels), cut(self.loss_mask), cut(self.advantages),
+                           cut(self.sampler_log_probs), cut(self.head_ids), cut(self.head_log_probs), cut(self.inputs_embeds),
+                           cut(self.embeds_mask))
+
+
+@dataclass
+class EngineConfig:
+    lr: float = 1e-6
+    betas: tuple = (0.9, 0.999)
+    eps: float = 1e-8
+    weight_decay: float = 0.01
+    clip_grad: float = 1.0
+    lr_warmup_steps: int = 0
+    param_dtype: str = "bf16"
+    fp32_modules: list = field(default_factory=list)
+    ulysses_sequence_parallel_size: int = 1
+    enable_gradient_checkpointing: bool = True
+    enable_activation_offload: bool = False
+    streamed_adamw: bool = False
+    streamed_chunk_bytes: int = 2 << 30
+    temperature: float = 1.0
+    topk_log_probs: int = 0
+    head_chunk: int = 4096
+    loss: grpo.LossConfig = field(default_factory=grpo.LossConfig)
+    kernels: Optional[str] = None
+    use_gpu_backend: bool = False
+    hsdp_all_reduce_on_last_micro_batch: bool = True
+
+    @classmethod
+    def from_config(cls, cfg) -> "EngineConfig":
+        """From a composed recipe (``actor_rollout_ref`` / ``algorithm`` sections with the upstream key names)."""
+        actor, model, rollout = cfg.actor_rollout_ref.actor, cfg.actor_rollout_ref.model, cfg.actor_rollout_ref.rollout
+        fs = actor.fsdp_config
+        rc = cfg.algorithm.rollout_correction
+        return cls(
+            lr=float(actor.optim.lr), betas=tuple(actor.optim.get("betas", (0.9, 0.999))), eps=float(actor.optim.get("eps", 1e-8)),
+            weight_decay=float(actor.optim.get("weight_decay", 0.01)), clip_grad=float(actor.get("clip_grad", 1.0)),
+            lr_warmup_steps=int(actor.optim.get("lr_warmup_steps", 0)), param_dtype=fs.mixed_precision.get("param_dtype", "bf16"),
+            fp32_modules=list(fs.mixed_precision.get("fp32_modules", [])),
+            ulysses_sequence_parallel_size=int(fs.ulysses_sequence_parallel_size),
+            enable_gradient_checkpointing=bool(model.enable_gradient_checkpointing),
+            enable_activation_offload=bool(model.get("enable_activation_offload", False)),
+            streamed_adamw=bool(fs.get("streamed_adamw", False) or fs.get("optimizer_offload", False)),
+            temperature=float(rollout.temperature), topk_log_probs=int(rollout.get("topk_log_probs", 0)),
+            loss=grpo.LossConfig(loss_agg_mode=actor.loss_agg_mode, score_centering=bool(rc.score_centering),
+                                 rollout_is=rc.get("rollout_is"), rollout_is_threshold=rc.get("rollout_is_threshold", 2.0),
+                                 entropy_coeff=float(actor.entropy_coeff)),
+            kernels=fs.get("kernels"), use_gpu_backend=bool(fs.get("use_gpu_backend", False)),
+            hsdp_all_reduce_on_last_micro_batch=bool(fs.get("hsdp_all_reduce_on_last_micro_batch", True)))
+
+
+class TrainEngine:
+    def __init__(self, model_cfg: HybridConfig, cfg: EngineConfig, device="cpu", world_group=None, replicate_group=None,
+                 kernels: Optional[type[TrainingKernels]] = None, seed: int = 0, state_dict: Optional[dict] = None,
+                 with_mtp: bool = False):
+        self.model_cfg, self.cfg, self.device = model_cfg, cfg, torch.device(device)
+        self.group = world_group
+        self.world = dist.get_world_size(world_group) if world_group is not None else 1
+        self.rank = dist.get_rank(world_group) if world_group is not None else 0
+        sp = cfg.ulysses_sequence_parallel_size
+        if self.world % sp:
+            raise ValueError(f"world size {self.world} is not a multiple of the sequence-parallel size {sp}")
+        self.sp_size, self.dp_size = sp, self.world // sp
+        self.dp_rank, self.sp_rank = self.rank // sp, self.rank % sp
+        self.sp_group = None
+        if sp > 1:
+            for d in range(self.dp_size):  # every rank creates every group (collective call)
+                g = dist.new_group(list(range(d * sp, (d + 1) * sp)))
+                if d == self.dp_rank:
+                    self.sp_group = g
+        self.sp = SequenceParallel(self.sp_group) if sp > 1 else None
+        self.kernels = kernels
+        if kernels is not None:
+            kernels.check_config(cfg)
+
+        # ---- build: every rank builds the same seeded model, or takes the given weights (rank 0's in a real run)
+        model = HybridForCausalLM(model_cfg, with_mtp=with_mtp)
+        if state_dict is not None:
+            model.load_state_dict(state_dict, strict=False)
+        else:
+            model.init_weights(seed)
+        if kernels is not None:  # the install order the GPU backend relies on
+            kernels.install(model, fp32_residual=True, use_fused_kernels=True, fused_kernels_backend=None)
+            kernels.check_model(model, use_remove_padding=True, use_fused_kernels=True, fused_kernels_backend=None)
+            if cfg.use_gpu_backend:
+                kernels.install_gpu_backend(model)
+            kernels.install_checkpointing(model)
+        model.to(self.device)
+        dtype = {"bf16": torch.bfloat16, "fp32": torch.float32, "fp16": torch.float16}[cfg.param_dtype]
+        if self.device.type == "cpu" and dtype != torch.float32:
+            dtype = torch.float32  # CPU plumbing runs in fp32
+        self.model = model
+        self.sharded = ShardedModel(model, world_group if self.world > 1 else None, replicate_group, dtype, cfg.fp32_modules,
+                                    self.device)
+        self.offload = CheckpointInputOffload(True) if cfg.enable_activation_offload else None
+        self.runner = LayerRunner(self.sharded, self.offload, cfg.enable_gradient_checkpointing)
+        install_runner(model, self.runner)
+        opt_cls = StreamedAdamW if cfg.streamed_adamw else torch.optim.AdamW
+        kw = dict(lr=cfg.lr, betas=cfg.betas, eps=cfg.eps, weight_decay=cfg.weight_decay)
+        if cfg.streamed_adamw:
+            kw["chunk_bytes"] = cfg.streamed_chunk_bytes
+        else:
+            kw.update(foreach=False, fused=False)
+        self.optimizer = opt_cls(self.sharded.parameters(), **kw)
+        self.step_count = 0
+        self.policy_version = 0
+        gc.collect()
+        gc.freeze()  # the long-lived model objects leave the collector's working set
+
+    # -- learning rate ------------------------------------------------------------------------------------------------
+    def _lr_at(self, step: int) -> float:
+        w = self.cfg.lr_warmup_steps
+        return self.cfg.lr * min(1.0, (step + 1) / w) if w > 0 else self.cfg.lr
+
+    # -- micro-batch forward/backward -----------------------------------------------------------------------------------
+    def _forward_loss(self, mb: PackedBatch, denom: torch.Tensor):
+        """Loss of this rank's slice of one packed micro-batch."""
+        cfg = self.cfg
+        mb = mb.pad_to_multiple(self.sp_size)
+        t = mb.num_tokens
+        t_local = t // self.sp_size
+        lo = self.sp_rank * t_local
+        loc = mb.slice(lo, lo + t_local) if self.sp_size > 1 else mb
+        hidden = self.model(loc.input_ids, loc.position_ids, mb.cu_seqlens, inputs_embeds=loc.inputs_embeds,
+                            embeds_mask=loc.embeds_mask, sp=self.sp, offset=lo)
+        ids = loc.labels[:, None].long()
+        use_sc = cfg.loss.score_centering and loc.head_ids is not None
+        if use_sc:
+            ids = torch.cat([ids, loc.head_ids.long()], dim=1)
+        lp, ent = ops.logprob_entropy(hidden, self.model.lm_head.weight, ids, cfg.temperature, cfg.head_chunk)
+        loss, metrics = grpo.policy_loss(
+            lp[:, 0], loc.advantages, loc.loss_mask, cfg.loss, head_log_probs=lp[:, 1:] if use_sc else None,
+            sampler_head_log_probs=loc.head_log_probs if use_sc else None, sampler_log_probs=loc.sampler_log_probs,
+            entropy=ent, denominator=denom)
+        return loss, metrics
+
+    def forward_backward_batch(self, micro_batches: list[PackedBatch], total_loss_tokens: Optional[int] = None) -> dict:
+        """Accumulate gradients over this DP rank's micro-batches. ``total_loss_tokens``: loss tokens of the GLOBAL
+        batch (token-mean over everything the step trains on); computed by an all-reduce when omitted."""
+        local = sum(int(mb.loss_mask.sum()) for mb in micro_batches)
+        if total_loss_tokens is None:
+            tot = torch.tensor([float(local)], device=self.device)
+            if self.world > 1:
+                if self.sp_rank != 0:
+                    tot.zero_()
+                dist.all_reduce(tot, group=self.group)
+            total_loss_tokens = int(tot.item())
+        denom = torch.tensor(float(max(1, total_loss_tokens)), device=self.device)
+
+        def run():
+            agg: dict[str, float] = {}
+            self.sharded.gather_static()
+            for i, mb in enumerate(micro_batches):
+                self.runner.last_micro_batch = (i == len(micro_batches) - 1) or not self.cfg.hsdp_all_reduce_on_last_micro_batch
+                loss, metrics = self._forward_loss(mb.to(self.device), denom)
+                loss.backward()
+                w = float(mb.loss_mask.sum()) / max(1, local)
+                for k, v in metrics.items():
+                    agg[k] = agg.get(k, 0.0) + (v if k == "actor/pg_loss" else v * w)
+                if self.offload is not None:
+                    self.offload.clear()
+            self.sharded.reduce_static_grads(True)
+            self.sharded.release_static()
+            return agg
+
+        def before_rerun():
+            self.optimizer.zero_grad(set_to_none=True)
+
+        if self.kernels is not None:
+            return self.kernels.run_checked(run, before_rerun)
+        return run()
+
+    # -- optimizer ----------------------------------------------------------------------------------------------------
+    def _grad_norm(self) -> torch.Tensor:
+        sq = torch.zeros((), device=self.device)
+        for p in self.sharded.parameters():
+            if p.grad is not None:
+                sq = sq + p.grad.float().pow(2).sum()
+        if self.world > 1:
+            dist.all_reduce(sq, group=self.group)
+        return sq.sqrt()
+
+    def optimizer_step(self) -> dict:
+        """Clip by the global norm, skip the update when the norm is not finite, step."""
+        for g in self.optimizer.param_groups:
+            g["lr"] = self._lr_at(self.step_count)
+        norm = self._grad_norm()
+        metrics = {"actor/grad_norm": float(norm), "actor/lr": self.optimizer.param_groups[0]["lr"]}
+        if not torch.isfinite(norm):
+            self.optimizer.zero_grad(set_to_none=True)
+            metrics["actor/skipped_update"] = 1.0
+            return metrics
+        if self.cfg.clip_grad > 0:
+            scale = min(1.0, self.cfg.clip_grad / (float(norm) + 1e-6))
+            if scale < 1.0:
+                for p in self.sharded.parameters():
+                    if p.grad is not None:
+                        p.grad.mul_(scale)
+        self.optimizer.step()
+        self.optimizer.zero_grad(set_to_none=True)
+        self.step_count += 1
+        self.policy_version += 1
+        return metrics
+
+    # -- state --------------------------------------------------------------------------------------------------------
+    def full_state_dict(self, dtype=torch.float32) -> dict[str, torch.Tensor]:
+        return self.sharded.full_state_dict(dtype)
+
+    def train_state(self) -> dict:
+        return {"shards": self.sharded.shard_state(), "optimizer": self.optimizer.state_dict(), "step": self.step_count,
+                "policy_version": self.policy_version, "world_size": self.world}
+
+    def load_train_state(self, st: dict) -> None:
+        if st["world_size"] != self.world:
+            raise ValueError(f"checkpoint was written by world size {st['world_size']}, this run has {self.world}")
+        self.sharded.load_shard_state(st["shards"])
+        self.optimizer.load_state_dict(st["optimizer"])
+        self.step_count, self.policy_version = st["step"], st["policy_version"]
+        for g in self.optimizer.param_groups:  # the configured LR, at the restored schedule position
+            g["lr"] = self._lr_at(self.step_count)
