@@ -11,6 +11,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 from dataclasses import dataclass
 from typing import Optional
 
@@ -457,7 +458,7 @@ class MegakernelEngine:
             instrs=instrs.data_ptr(), descs=self.descs_dev.data_ptr(), rec=self.rec.data_ptr(), out_ring=self.out_ring.data_ptr(),
             barrier=self.barrier.data_ptr(), status=self.status.data_ptr(), max_instrs=max_len, ring=self.RING,
             step_parity=self.step & 1, seed=self.seed, temperature=self.temperature, vocab=self.cfg.vocab_size,
-            barrier_base=self.barrier_base & 0xFFFFFFFF, pad=0,
+            barrier_base=self.barrier_base & 0xFFFFFFFF, pad=int(os.environ.get("PEAR_MK_DEBUG", "0")),
             ctrl=self.ctrl_dev[self.step % self.RING].data_ptr() if self._use_ctrl else 0)
         ns, nb = self.LAUNCH_SHAPE[program]
         code = _lib.lib().pear_mk_launch(ctypes.byref(prm), self.num_ctas, ns, nb, _lib.stream())

@@ -289,15 +289,18 @@ __device__ void op_gemv(Ctx& c, const Instr& ins) {
   uint8_t* B = c.xs;
   uint8_t* SFB = c.xs + (size_t)(kMaxSegStages * kStageK / 32) * (nb >> 3) * 128;
   const bool issuer = tid == 4 * 32;  // lane 0 of warp 4: warps 0-3 own the four tensor-memory lane quarters
+  const int dbg = c.p->pad;  // timing experiments only: 1 skip the prologue, 2 skip UTCCP/MMA issue, 4 skip the epilogue math
   if (ins.d & 1) {
     // every MMA that reads the old B operand has completed once the previous segment's accumulator is full
     if (c.seg > 0) mbar_wait_bounded(&c.sm->acc_full[(c.seg - 1) & 1], (uint32_t)((c.seg - 1) >> 1) & 1u, c.p->status);
     consumer_sync();
-    if (whole) gemv_prologue(c, d, 0, d.i0, T, tpad, terms);
-    else gemv_prologue(c, d, ks0 * kStageK, nks * kStageK, T, tpad, terms);
+    if (!(dbg & 1)) {
+      if (whole) gemv_prologue(c, d, 0, d.i0, T, tpad, terms);
+      else gemv_prologue(c, d, ks0 * kStageK, nks * kStageK, T, tpad, terms);
+    }
     fence_proxy_async();  // generic-proxy stores to the operand images -> visible to the tensor core / tcgen05.cp
     consumer_sync();
-    if (issuer) {
+    if (issuer && !(dbg & 2)) {
       const int nmma = (whole ? d.i1 : nks) * 4;
       tcgen05_fence_after();
       for (int m = 0; m < nmma; ++m)
@@ -312,7 +315,7 @@ __device__ void op_gemv(Ctx& c, const Instr& ins) {
     const uint32_t b_addr = smem_u32(B);
     for (int s = 0; s < nks; ++s) {
       if (ok) ok = mbar_wait_bounded(&c.sm->full[c.stage], c.phase, c.p->status);
-      if (ok) {
+      if (ok && !(dbg & 2)) {
         tcgen05_fence_after();
         const uint32_t a_addr = smem_u32(c.ring + (size_t)c.stage * kStageBytes);
         const int kst = whole ? ks0 + s : s;  // stage index inside the B operand
@@ -338,7 +341,7 @@ __device__ void op_gemv(Ctx& c, const Instr& ins) {
     const bool ok = mbar_wait_bounded(&c.sm->acc_full[ab], use, c.p->status);
     tcgen05_fence_after();
     uint32_t r[32];
-    if (ok) {
+    if (ok && !(dbg & 4)) {
       if (nb == 16) {
         uint32_t q[16];
         tmem_ld_32x32b_x16(c.tmem + ((uint32_t)(warp * 32) << 16) + kAccCol + ab * 32, q);
@@ -353,7 +356,7 @@ __device__ void op_gemv(Ctx& c, const Instr& ins) {
     tcgen05_fence_before();
     __syncwarp();
     if (lane == 0) mbar_arrive(&c.sm->acc_empty[ab]);
-    if (ok) {
+    if (ok && !(dbg & 4)) {
       float* out = (float*)d.p4;
       if (d.i7 & 2) out += (size_t)c.rec->parity * d.i8;
       const int row = tile * kTileRows + warp * 32 + lane;
@@ -384,7 +387,7 @@ __device__ void op_embed(Ctx& c, const Instr& ins) {
   float* out = (float*)d.p4;
   const int T = c.rec->T;
   for (int t = 0; t < T; ++t) {
-    const int tok = c.rec->tokens[t];
+    const int tok = min(max(c.rec->tokens[t], 0), c.p->vocab - 1);  // a corrupted record must never turn into a wild read
     const __nv_bfloat16* src = table + (size_t)tok * d.i0 + ins.a;
     float* dst = out + (size_t)t * d.i4 + ins.a;
     for (int i = threadIdx.x; i < ins.b; i += kConsumerThreads) dst[i] = __bfloat162float(src[i]);
@@ -493,9 +496,9 @@ __global__ void __launch_bounds__(kThreads, 1) mk_main(const __grid_constant__ P
         case OP_EMBED: op_embed(c, ins); break;
         case OP_ZERO: op_zero(c, ins); break;
         case OP_COPY: op_copy(c, ins); break;
-        case OP_GDN: op_gdn(c, ins); break;
-        case OP_ATTN: op_attn(c, ins); break;
-        case OP_ATTN_COMBINE: op_attn_combine(c, ins); break;
+        case OP_GDN: if (!(p.pad & 16)) op_gdn(c, ins); break;
+        case OP_ATTN: if (!(p.pad & 32)) op_attn(c, ins); break;
+        case OP_ATTN_COMBINE: if (!(p.pad & 32)) op_attn_combine(c, ins); break;
         case OP_SAMPLE_PART: op_sample_part(c, ins); break;
         case OP_SAMPLE_FIN: op_sample_fin(c, ins); break;
         case OP_DRAFT_IN: op_draft_in(c, ins); break;

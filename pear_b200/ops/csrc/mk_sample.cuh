@@ -157,7 +157,7 @@ __device__ void op_sample_fin(Ctx& c, const Instr& ins) {
     const float* logits = (const float*)d.p0;
     int n_acc = 0;
     for (int r = 0; r < T - 1; ++r) {
-      const int dtok = rec->tokens[r + 1];
+      const int dtok = min(max(rec->tokens[r + 1], 0), c.p->vocab - 1);
       const float lp = __ldcg(logits + (size_t)r * d.i0 + dtok) * inv_t - lse_s[r];
       const uint4 rnd = philox4x32_10(make_uint4(0xffffffffu, (uint32_t)r, (uint32_t)rec->step, 1u),
                                       make_uint2(step_seed(c), 0x5eedu));
@@ -194,6 +194,7 @@ __device__ void op_draft_in(Ctx& c, const Instr& ins) {
     if (row <= n_acc) { tok = row < n_acc ? rec->tokens[row + 1] : nx->tokens[0]; src = row; }
     else { tok = d.i5; src = n_acc; }
   }
+  tok = min(max(tok, 0), c.p->vocab - 1);
   const __nv_bfloat16* e = (const __nv_bfloat16*)d.p0 + (size_t)tok * H;
   const float* hrow = (const float*)d.p1 + (size_t)src * d.i3;
   const float* w = (const float*)d.p2;

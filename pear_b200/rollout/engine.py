@@ -1,0 +1,449 @@
+"""Rollout engine: continuous batching over paged KV with prefix caching across rounds, host-DRAM offload of evicted
+prefixes, chunked prefill, MTP speculative decoding and pause/abort/resume for weight sync.
+
+It replaces the serving runtime the upstream builds on (vLLM V2 runner + scheduler + LMCache connector, wrapped by
+``pear/rollout/server.py``) with the framework's own pieces:
+
+* requests carry a ``session`` so a multi-turn episode hits the prefix its previous turn left behind (sticky routing,
+  ``examples/.../run_stage1.sh:102-104``); every finished request publishes its full blocks, and the recurrent-state
+  snapshot of its last full block, so the next turn resumes right after the previous answer;
+* a step schedules decode/verify rows first, then prefill chunks up to ``max_num_batched_tokens`` (chunked prefill);
+  when blocks run out the youngest running request is preempted (its blocks are released, it re-enters the queue and
+  re-hits its own prefix);
+* ``pause(abort=True)`` stops scheduling and returns every in-flight request as ABORTED with the tokens it has so far
+  (the client resubmits, upstream patches 0044/0048); requests submitted while paused are rejected as aborted;
+* ``update_weights`` loads new tensors in place, bumps the policy version, and invalidates the prefix cache and the
+  host tier (``pear/rollout/lmcache.py:263-274``);
+* per-request MTP acceptance counts and the counters the monitor scrapes are kept (patches 0051/0053,
+  ``pear/monitor/metrics.py:88-97``).
+"""
+
+from __future__ import annotations
+
+import itertools
+import time
+from collections import deque
+from dataclasses import dataclass, field
+from enum import Enum
+from typing import Optional
+
+import torch
+
+from ..models.hybrid import HybridForCausalLM
+from . import sampler as S
+from .block_manager import NULL_BLOCK, BlockManager
+from .host_tier import HostTier
+from .model_runner import ModelRunner, SeqState, StepRow
+
+
+class FinishReason(str, Enum):
+    LENGTH = "length"
+    STOP = "stop"
+    ABORTED = "aborted"
+
+
+@dataclass
+class SamplingParams:
+    max_tokens: int = 64
+    temperature: float = 1.0
+    top_p: float = 1.0
+    top_k: int = -1
+    topk_logprobs: int = 0
+    stop_token_ids: tuple = ()
+    seed: Optional[int] = None
+
+
+@dataclass
+class Request:
+    request_id: str
+    prompt: list[int]
+    params: SamplingParams
+    session: Optional[str] = None
+    embeds: Optional[torch.Tensor] = None  # [len(prompt), H] placeholder rows (vision embeddings)
+    embeds_mask: Optional[torch.Tensor] = None
+    arrival: float = field(default_factory=time.time)
+    # -- runtime
+    output: list[int] = field(default_factory=list)
+    logprobs: list[float] = field(default_factory=list)
+    topk_ids: list[list[int]] = field(default_factory=list)
+    topk_logprobs: list[list[float]] = field(default_factory=list)
+    block_table: list[int] = field(default_factory=list)
+    computed: int = 0  # tokens whose KV / state are in the caches
+    cached_prefix: int = 0
+    seq: Optional[SeqState] = None
+    drafts: list[int] = field(default_factory=list)
+    spec_drafted: int = 0
+    spec_accepted: int = 0
+    finish: Optional[FinishReason] = None
+    policy_version: int = 0
+    preemptions: int = 0
+
+    @property
+    def tokens(self) -> list[int]:
+        return self.prompt + self.output
+
+
+@dataclass
+class EngineConfig:
+    num_blocks: int = 512
+    block_size: int = 16
+    max_num_seqs: int = 64
+    max_num_batched_tokens: int = 8192
+    enable_prefix_caching: bool = True
+    num_speculative_tokens: int = 0
+    host_blocks: int = 0  # capacity of the host-DRAM tier in blocks (0: disabled)
+    state_interval_blocks: int = 0  # extra recurrent-state snapshots every N blocks during prefill (0: turn ends only)
+    seed: int = 0
+
+
+class RolloutEngine:
+    def __init__(self, model: HybridForCausalLM, cfg: EngineConfig, device="cpu"):
+        self.model, self.cfg = model.eval(), cfg
+        self.device = torch.device(device)
+        n_slots = 2 * cfg.max_num_seqs + 64
+        self.runner = ModelRunner(model, cfg.num_blocks, cfg.block_size, n_slots, device)
+        self.host = None
+        has_state = len(model.config.gdn_layers) > 0
+        self.blocks = BlockManager(cfg.num_blocks, cfg.block_size, n_slots, cfg.enable_prefix_caching, needs_state=has_state)
+        if cfg.host_blocks > 0:
+            self.host = HostTier(cfg.host_blocks, self.runner.kv_tensors(), self.runner.state_tensors())
+            self.blocks.host_tier = self.host
+        self.waiting: deque[Request] = deque()
+        self.running: list[Request] = []
+        self.finished: dict[str, Request] = {}
+        self.paused = False
+        self.policy_version = 0
+        self.step_count = 0
+        self.gen = torch.Generator(device="cpu").manual_seed(cfg.seed)
+        self._ids = itertools.count()
+        self.metrics = {"prompt_tokens": 0, "generation_tokens": 0, "preemptions": 0, "aborted": 0, "spec_drafted": 0,
+                        "spec_accepted": 0, "steps": 0}
+        self.spec = cfg.num_speculative_tokens if model.mtp is not None else 0
+
+    # -- public API ---------------------------------------------------------------------------------------------------
+    def add_request(self, prompt: list[int], params: Optional[SamplingParams] = None, session: Optional[str] = None,
+                    request_id: Optional[str] = None, embeds=None, embeds_mask=None) -> Request:
+        req = Request(request_id or f"req-{next(self._ids)}", list(prompt), params or SamplingParams(), session, embeds, embeds_mask)
+        req.policy_version = self.policy_version
+        if self.paused:  # the submission gate closes before the pause: the client resubmits later
+            req.finish = FinishReason.ABORTED
+            self.finished[req.request_id] = req
+            self.metrics["aborted"] += 1
+            return req
+        self.waiting.append(req)
+        return req
+
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    def generate(self, prompts: list[list[int]], params: Optional[SamplingParams] = None, sessions=None) -> list[Request]:
+        reqs = [self.add_request(p, params, sessions[i] if sessions else None) for i, p in enumerate(prompts)]
+        while self.has_work():
+            self.step()
+        return reqs
+
+    def pause(self, abort: bool = True) -> list[Request]:
+        """Stop scheduling. ``abort``: in-flight requests end as ABORTED right away (not drained)."""
+        self.paused = True
+        out = []
+        if abort:
+            for req in list(self.running) + list(self.waiting):
+                self._finish(req, FinishReason.ABORTED)
+                out.append(req)
+            self.waiting.clear()
+            self.metrics["aborted"] += len(out)
+        return out
+
+    def resume(self) -> None:
+        self.paused = False
+
+    def update_weights(self, state: dict[str, torch.Tensor], version: Optional[int] = None) -> None:
+        """In-place load (kernels reference the weights where they are), then invalidate every cached prefix."""
+        assert not self.running, "pause(abort=True) before a weight update"
+        own = dict(self.model.named_parameters())
+        with torch.no_grad():
+            for name, t in state.items():
+                if name in own:
+                    own[name].copy_(t.to(own[name].dtype))
+        self.policy_version = version if version is not None else self.policy_version + 1
+        self.clear_kv_cache()
+
+    def clear_kv_cache(self) -> int:
+        return self.blocks.reset_prefix_cache(new_salt=f"v{self.policy_version}".encode())
+
+    # -- sequence lifecycle -------------------------------------------------------------------------------------------
+    def _admit(self, req: Request) -> bool:
+        """Prefix lookup + state slot for a waiting request. False when resources are missing."""
+        slot = self.blocks.allocate_slot()
+        if slot is None:
+            return False
+        toks = req.tokens
+        # the last token must be recomputed (its logits are needed), so look up at most len - 1 tokens
+        hit = self.blocks.lookup(toks[: len(toks) - 1], extra_fn=self._extra_fn(req))
+        req.block_table = list(hit.blocks)
+        req.computed = req.cached_prefix = hit.tokens
+        req.seq = SeqState(seq_id=id(req), slot=slot)
+        if hit.state_slot is not None:
+            self.runner.copy_state(hit.state_slot, slot)
+        else:
+            self.runner.zero_state(slot)
+        if req.preemptions == 0:
+            self.metrics["prompt_tokens"] += len(req.prompt)
+        return True
+
+    def _extra_fn(self, req: Request):
+        if req.embeds is None:
+            return None
+        bs = self.cfg.block_size
+
+        def extra(i: int) -> bytes:  # placeholder rows are content too: hash their bytes with the block
+            m = req.embeds_mask[i * bs : (i + 1) * bs]
+            if not bool(m.any()):
+                return b""
+            return req.embeds[i * bs : (i + 1) * bs][m].float().numpy().tobytes()
+
+        return extra
+
+    def _ensure_blocks(self, req: Request, upto_tokens: int) -> bool:
+        need = (upto_tokens + self.cfg.block_size - 1) // self.cfg.block_size - len(req.block_table)
+        if need <= 0:
+            return True
+        if not self.blocks.can_allocate(need):
+            return False
+        for _ in range(need):
+            req.block_table.append(self.blocks.allocate())
+        return True
+
+    def _publish(self, req: Request, final: bool) -> None:
+        """Publish the full blocks of the committed prefix; the last one (at a turn end, or every
+        ``state_interval_blocks``) carries a snapshot of the recurrent state."""
+        bs = self.cfg.block_size
+        toks = req.tokens
+        full = req.computed // bs
+        if full == 0 or not self.cfg.enable_prefix_caching:
+            return
+        extra = self._extra_fn(req)
+        parent = None
+        for i in range(full):
+            blk = req.block_table[i]
+            b = self.blocks.blocks[blk]
+            snap = None
+            is_last = i == full - 1
+            # the snapshot is valid only when the committed prefix ends exactly at this block's end
+            at_boundary = is_last and req.computed == full * bs
+            if at_boundary and self.blocks.needs_state and b.state_slot is None and (final or self._interval_hit(full)):
+                snap = self.blocks.allocate_slot()
+                if snap is not None:
+                    self.runner.flush(req.seq)
+                    self.runner.copy_state(req.seq.slot, snap)
+            if b.hash is None or snap is not None:
+                parent = self.blocks.publish(blk, parent, toks[i * bs : (i + 1) * bs], snap, extra(i) if extra else b"")
+            else:
+                parent = b.hash
+
+    def _interval_hit(self, full_blocks: int) -> bool:
+        n = self.cfg.state_interval_blocks
+        return n > 0 and full_blocks % n == 0
+
+    def _finish(self, req: Request, reason: FinishReason) -> None:
+        req.finish = reason
+        if req.seq is not None:
+            if reason != FinishReason.ABORTED:
+                self.runner.flush(req.seq)
+                # a turn end: commit the tail so the block boundary (if any) carries a snapshot
+                self._publish(req, final=True)
+            if self.host is not None and reason != FinishReason.ABORTED:
+                hashes = [self.blocks.blocks[b].hash for b in req.block_table]
+                slots = [self.blocks.blocks[b].state_slot for b in req.block_table]
+                self.host.run_store(self.host.schedule_store(req.block_table, hashes, slots, session=req.session))
+            for b in req.block_table:
+                self.blocks.release(b)
+            self.blocks.release_slot(req.seq.slot)
+            req.block_table, req.seq = [], None
+        if req in self.running:
+            self.running.remove(req)
+        self.finished[req.request_id] = req
+        self.metrics["spec_drafted"] += req.spec_drafted
+        self.metrics["spec_accepted"] += req.spec_accepted
+
+    def _preempt(self, req: Request) -> None:
+        for b in req.block_table:
+            self.blocks.release(b)
+        self.blocks.release_slot(req.seq.slot)
+        req.block_table, req.seq, req.computed, req.drafts = [], None, 0, []
+        req.preemptions += 1
+        self.running.remove(req)
+        self.waiting.appendleft(req)
+        self.metrics["preemptions"] += 1
+
+    # -- one step -----------------------------------------------------------------------------------------------------
+    def step(self) -> list[Request]:
+        """Schedule and run one step; returns the requests that finished in it."""
+        if self.paused:
+            return []
+        cfg = self.cfg
+        budget = cfg.max_num_batched_tokens
+        rows: list[StepRow] = []
+        plan: list[tuple[Request, int, bool]] = []  # (request, rows scheduled, is decode/verify)
+        # 1. decode / verify rows of running requests whose prompt is fully computed
+        for req in list(self.running):
+            total = len(req.tokens)
+            if req.computed < total - 1:
+                continue
+            if req.seq is None:  # preempted earlier in this loop
+                continue
+            n = 1 + len(req.drafts)
+            planned = {id(p[0]) for p in plan}
+            while not self._ensure_blocks(req, req.computed + n):
+                # the youngest request that has no row in this step yet gives its blocks back (possibly `req` itself)
+                victim = next((r for r in reversed(self.running) if id(r) not in planned and r.seq is not None), None)
+                if victim is None:
+                    break
+                self._preempt(victim)
+                if victim is req:
+                    break
+            if req.seq is None or not self._ensure_blocks(req, req.computed + n) or budget < n:
+                continue
+            toks = torch.tensor([req.tokens[-1]] + req.drafts, dtype=torch.long)
+            rows.append(StepRow(req.seq, toks, req.computed, req.block_table, n))
+            plan.append((req, n, True))
+            budget -= n
+        # 2. prefill chunks: running requests still in prefill, then newly admitted ones
+        def add_prefill(req: Request) -> None:
+            nonlocal budget
+            total = len(req.tokens)
+            remaining = (total - 1) - req.computed
+            n = min(remaining, budget)
+            if n <= 0:
+                return
+            last_chunk = n == remaining
+            n_rows = n + (1 if last_chunk else 0)  # the final chunk also runs the last token to get its logits
+            if last_chunk and budget < n_rows:
+                n_rows, last_chunk = n, False
+            if not self._ensure_blocks(req, req.computed + n_rows):
+                return
+            s = req.computed
+            toks = torch.tensor(req.tokens[s : s + n_rows], dtype=torch.long)
+            emb = msk = None
+            if req.embeds is not None and s < len(req.prompt):
+                e = min(s + n_rows, len(req.prompt))
+                emb = torch.zeros(n_rows, req.embeds.shape[1])
+                msk = torch.zeros(n_rows, dtype=torch.bool)
+                emb[: e - s], msk[: e - s] = req.embeds[s:e], req.embeds_mask[s:e]
+            rows.append(StepRow(req.seq, toks, s, req.block_table, 1 if last_chunk else 0, emb, msk))
+            plan.append((req, n_rows, False))
+            budget -= n_rows
+
+        for req in self.running:
+            if req.computed < len(req.tokens) - 1 and all(req is not p[0] for p in plan):
+                add_prefill(req)
+        while self.waiting and budget > 0 and len(self.running) < cfg.max_num_seqs:
+            req = self.waiting[0]
+            if not self._admit(req):
+                break
+            self.waiting.popleft()
+            self.running.append(req)
+            if len(req.tokens) == 1:  # nothing to prefill: decode right away next step
+                continue
+            add_prefill(req)
+        if not rows:
+            if self.running and not any(True for _ in rows):
+                # every running request is blocked on memory: preempt the youngest to make progress
+                if len(self.running) > 1:
+                    self._preempt(self.running[-1])
+            return []
+        speculative = any(is_dec and n > 1 for _, n, is_dec in plan)
+        logits, resid, x_all, bounds = self.runner.forward(rows, speculative=speculative)
+        self.step_count += 1
+        self.metrics["steps"] += 1
+        done: list[Request] = []
+        lo = 0
+        for i, (req, n, is_dec) in enumerate(plan):
+            row = rows[i]
+            if not is_dec:
+                # prefill chunk: rows are committed; the final chunk's last row yields the first sampled token
+                if row.need_logits:
+                    req.computed += n - 1
+                    self._sample_rows(req, logits[lo : lo + 1], resid[lo : lo + 1], [], row)
+                    lo += 1
+                    if req.finish is None:
+                        self._publish(req, final=False)
+                else:
+                    req.computed += n
+                    if self._interval_hit(req.computed // cfg.block_size) and req.computed % cfg.block_size == 0:
+                        self._publish(req, final=False)
+            else:
+                self._sample_rows(req, logits[lo : lo + n], resid[lo : lo + n], req.drafts, row)
+                lo += n
+            if req.finish is not None:
+                done.append(req)
+        return done
+
+    # -- sampling / verification / drafting -----------------------------------------------------------------------------
+    def _sample_rows(self, req: Request, logits: torch.Tensor, resid: torch.Tensor, drafts: list[int], row: StepRow) -> None:
+        p = req.params
+        bad = S.count_nonfinite(logits)
+        if bool((bad > 0).any()):
+            raise S.NonFiniteLogits(self.step_count, torch.nonzero(bad).flatten().tolist(), [req.request_id])
+        logits = logits.cpu()
+        if drafts:
+            out = S.verify_greedy_drafts(logits[None], torch.tensor([drafts]), p.temperature, p.topk_logprobs, self.gen)
+            acc = int(out.accepted[0])
+            new = [int(t) for t in out.tokens[0, : acc + 1]]
+            lps = [float(v) for v in out.logprobs[0, : acc + 1]]
+            tk_i = [out.topk_ids[0, j].tolist() for j in range(acc + 1)] if out.topk_ids is not None else []
+            tk_l = [out.topk_logprobs[0, j].tolist() for j in range(acc + 1)] if out.topk_logprobs is not None else []
+            req.spec_drafted += len(drafts)
+            req.spec_accepted += acc
+        else:
+            so = S.sample(logits[-1:], p.temperature, p.top_p, p.top_k, p.topk_logprobs, self.gen)
+            acc, new, lps = 0, [int(so.tokens[0])], [float(so.logprobs[0])]
+            tk_i = [so.topk_ids[0].tolist()] if so.topk_ids is not None else []
+            tk_l = [so.topk_logprobs[0].tolist()] if so.topk_logprobs is not None else []
+        committed = acc + 1  # rows [x0, accepted drafts] enter the state
+        if row.need_logits > 1 or drafts:
+            self.runner.commit(req.seq, committed)
+        req.computed += committed if (drafts or row.tokens.shape[0] == 1) else 1
+        req.seq.mtp_hidden = resid[acc]
+        for j, t in enumerate(new):
+            req.output.append(t)
+            req.logprobs.append(lps[j])
+            if tk_i:
+                req.topk_ids.append(tk_i[j])
+                req.topk_logprobs.append(tk_l[j])
+            self.metrics["generation_tokens"] += 1
+            if t in p.stop_token_ids:
+                self._finish(req, FinishReason.STOP)
+                return
+            if len(req.output) >= p.max_tokens:
+                self._finish(req, FinishReason.LENGTH)
+                return
+        req.drafts = self._draft(req, row, resid, acc, new) if self.spec > 0 else []
+
+    def _draft(self, req: Request, row: StepRow, resid: torch.Tensor, acc: int, new: list[int]) -> list[int]:
+        """MTP drafts for the next step: first a pass over the rows committed in this step (it fills the drafter's KV
+        pages and predicts the token after ``new[-1]``), then greedy chained passes on the drafter's own output."""
+        toks = req.tokens
+        n_commit = acc + 1
+        first = req.computed - n_commit  # position of the first committed row
+        nxt = torch.tensor(toks[first + 1 : first + 1 + n_commit], dtype=torch.long)
+        sub = StepRow(req.seq, nxt, first, req.block_table, 0)
+        if not self._ensure_blocks(req, req.computed + self.spec + 1):
+            return []
+        logits, r = self.runner.mtp_forward(sub, nxt, resid[:n_commit] if resid.shape[0] >= n_commit else resid[-1:].expand(n_commit, -1))
+        drafts = [int(logits[-1].argmax())]
+        hidden = r[-1:]
+        for j in range(1, self.spec):
+            pos = req.computed + j - 1
+            sub = StepRow(req.seq, torch.tensor(drafts[-1:]), pos, req.block_table, 0)
+            logits, hidden = self.runner.mtp_forward(sub, torch.tensor(drafts[-1:]), hidden)
+            drafts.append(int(logits[-1].argmax()))
+        return drafts
+
+    def stats(self) -> dict:
+        out = dict(self.metrics)
+        out.update(self.blocks.stats())
+        if self.host is not None:
+            out.update(self.host.stats())
+        out.update(num_running=len(self.running), num_waiting=len(self.waiting), policy_version=self.policy_version)
+        return out
