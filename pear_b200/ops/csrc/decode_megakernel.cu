@@ -134,149 +134,179 @@ __device__ __forceinline__ void quantize_block(float (&r)[16], int terms, int tp
 
 // Build the B operand (FP4 terms of the activation rows) for K range [k0, k0 + kn) of the op's input.
 //
-// Register-resident single pass per group of 4 rows: thread `tid` owns K block `tid` (16 elements) of all four rows,
-// and one block of the left-over columns 256.. (block 256 + tid/4 of row tid%4), i.e. 5 blocks = 80 values. Every
-// global load is issued before the first use, the row statistics (RMS, maximum) are reduced with shuffles and one
-// shared-memory exchange, and the blocks are quantised straight from registers. PRO_NORM always covers the whole row.
-__device__ void gemv_prologue(Ctx& c, const Desc& d, int k0, int kn, int T, int tpad, int terms) {
+// Register-resident rounds over PAIRS of rows (no stack, no spills: the L1 left beside 227 KB of shared memory is too
+// small to absorb any): thread `tid` owns K block `tid` (16 elements) of both rows and, for tid < 128, one block of
+// the left-over columns 256.. (block 256 + tid/2 of row tid%2), i.e. 3 blocks = 48 values. All global loads of a round
+// are issued before the first use; the row statistics (RMS, maximum) are reduced with shuffles and one shared-memory
+// exchange; the blocks are quantised straight from registers. PRO_NORM always covers the whole row.
+template <int PRO>
+__device__ __forceinline__ void gemv_prologue_t(Ctx& c, const Desc& d, int k0, int kn, int T, int tpad, int terms) {
   const StepRec* rec = c.rec;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const float* in = (const float*)d.p1;
-  if ((d.i7 & 1) && d.i5 != PRO_GDN_NORM) in += (size_t)rec->parity * d.i8;
-  const int istride = d.i3, pro = d.i5, nb = c.nb;
+  if ((d.i7 & 1) && PRO != PRO_GDN_NORM) in += (size_t)rec->parity * d.i8;
+  const int istride = d.i3, nb = c.nb;
   uint8_t* B = c.xs;
   uint8_t* SFB = c.xs + (size_t)(kMaxSegStages * kStageK / 32) * (nb >> 3) * 128;
-  float* stat = (float*)(SFB + sfb_bytes(nb));  // [warp][row][2] partial (sum of squares, maximum), then [64 + row] gains
+  float* stat = (float*)(SFB + sfb_bytes(nb));  // [warp][row of the pair][2]: partial (sum of squares, maximum)
   const float* zbase = (const float*)d.p2;
-  if (pro == PRO_GDN_NORM && (d.i7 & 1)) zbase += (size_t)rec->parity * d.i8;
+  if (PRO == PRO_GDN_NORM && (d.i7 & 1)) zbase += (size_t)rec->parity * d.i8;
   const int nblk = kn >> 4;
+  const float* wp = PRO == PRO_NORM ? (const float*)d.p2 : (const float*)d.p3;
 
-  for (int t0 = 0; t0 < tpad; t0 += 4) {
-    // ---- the 5 (block, row) items of this thread
-    int ib[5], it[5];
-    bool valid[5];
-#pragma unroll
-    for (int e = 0; e < 4; ++e) { ib[e] = tid; it[e] = t0 + e; valid[e] = tid < nblk && it[e] < T; }
-    ib[4] = 256 + (tid >> 2); it[4] = t0 + (tid & 3); valid[4] = ib[4] < nblk && it[4] < T;
-
+  for (int t0 = 0; t0 < tpad; t0 += 2) {
+    // ---- items: e = 0, 1: (block tid, row t0 + e); e = 2: (block 256 + tid/2, row t0 + tid%2) for tid < 128
+    const int b2 = 256 + (tid >> 1), r2 = tid & 1;
+    float4 x[3][4];
     // ---- loads (all issued before use)
-    float4 x[5][4], y[5][4], w[2][4];
 #pragma unroll
-    for (int e = 0; e < 5; ++e) {
-      const int k = k0 + ib[e] * 16;
+    for (int e = 0; e < 3; ++e) {
+      const int b = e < 2 ? tid : b2, t = t0 + (e < 2 ? e : r2);
+      const bool valid = b < nblk && t < T && (e < 2 || tid < 128);
+      const int k = k0 + b * 16;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         x[e][i] = make_float4(0.f, 0.f, 0.f, 0.f);
-        y[e][i] = x[e][i];
-        if (valid[e]) {
-          if (pro == PRO_GDN_NORM) {
-            x[e][i] = __ldcg((const float4*)((const float*)d.p1 + (size_t)it[e] * istride + k) + i);
-            y[e][i] = __ldcg((const float4*)(zbase + (size_t)it[e] * d.i9 + k) + i);
+        if (valid) {
+          if (PRO == PRO_GDN_NORM) x[e][i] = __ldcg((const float4*)((const float*)d.p1 + (size_t)t * istride + k) + i);
+          else x[e][i] = __ldcg((const float4*)(in + (size_t)t * istride + k) + i);
+        }
+      }
+    }
+    if (PRO == PRO_SWIGLU || PRO == PRO_GDN_NORM) {
+      // second operand: loaded while the first is in flight, folded in as it arrives
+#pragma unroll
+      for (int e = 0; e < 3; ++e) {
+        const int b = e < 2 ? tid : b2, t = t0 + (e < 2 ? e : r2);
+        const bool valid = b < nblk && t < T && (e < 2 || tid < 128);
+        const int k = k0 + b * 16;
+        float4 y[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          y[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (valid) {
+            if (PRO == PRO_GDN_NORM) y[i] = __ldcg((const float4*)(zbase + (size_t)t * d.i9 + k) + i);
+            else y[i] = __ldcg((const float4*)(in + (size_t)t * istride + k + d.i0) + i);
+          }
+        }
+        if (PRO == PRO_SWIGLU) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            x[e][i].x = silu_f(x[e][i].x) * y[i].x; x[e][i].y = silu_f(x[e][i].y) * y[i].y;
+            x[e][i].z = silu_f(x[e][i].z) * y[i].z; x[e][i].w = silu_f(x[e][i].w) * y[i].w;
+          }
+        } else {
+          // the head statistic needs the raw o: keep sum(o^2) in .. a scalar, fold silu(z) now
+          float ssq = 0.f;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            ssq += x[e][i].x * x[e][i].x + x[e][i].y * x[e][i].y + x[e][i].z * x[e][i].z + x[e][i].w * x[e][i].w;
+            x[e][i].x *= silu_f(y[i].x); x[e][i].y *= silu_f(y[i].y); x[e][i].z *= silu_f(y[i].z); x[e][i].w *= silu_f(y[i].w);
+          }
+          // a head is 8 consecutive blocks: lanes 8h..8h+7 (items 0, 1); lanes of equal row, stride 2 (item 2)
+          if (e < 2) {
+            ssq += __shfl_xor_sync(0xffffffffu, ssq, 1); ssq += __shfl_xor_sync(0xffffffffu, ssq, 2);
+            ssq += __shfl_xor_sync(0xffffffffu, ssq, 4);
           } else {
-            x[e][i] = __ldcg((const float4*)(in + (size_t)it[e] * istride + k) + i);
-            if (pro == PRO_SWIGLU) y[e][i] = __ldcg((const float4*)(in + (size_t)it[e] * istride + k + d.i0) + i);
+            ssq += __shfl_xor_sync(0xffffffffu, ssq, 2); ssq += __shfl_xor_sync(0xffffffffu, ssq, 4);
+            ssq += __shfl_xor_sync(0xffffffffu, ssq, 8);
+          }
+          const float rs = rsqrtf(ssq * (1.f / 128.f) + d.f1);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) { x[e][i].x *= rs; x[e][i].y *= rs; x[e][i].z *= rs; x[e][i].w *= rs; }
+        }
+      }
+    }
+    // ---- weights and per-item statistics
+    float ss[3], mx[3];
+#pragma unroll
+    for (int e = 0; e < 3; ++e) {
+      ss[e] = 0.f; mx[e] = 0.f;
+      if (e == 1) continue;  // item 1 shares item 0's weight block: handled together below
+    }
+    if (PRO == PRO_NORM || PRO == PRO_GDN_NORM) {
+#pragma unroll
+      for (int wsel = 0; wsel < 2; ++wsel) {
+        const int b = wsel == 0 ? tid : b2;
+        const int kw = PRO == PRO_NORM ? (k0 + b * 16) : ((k0 + b * 16) & 127);
+        float4 w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) w[i] = b < nblk ? __ldg((const float4*)(wp + kw) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int e = (wsel == 0 ? 0 : 2); e < (wsel == 0 ? 2 : 3); ++e) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            float4 v = x[e][i];
+            if (PRO == PRO_NORM) {
+              ss[e] += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+              v.x *= 1.f + w[i].x; v.y *= 1.f + w[i].y; v.z *= 1.f + w[i].z; v.w *= 1.f + w[i].w;
+            } else {
+              v.x *= w[i].x; v.y *= w[i].y; v.z *= w[i].z; v.w *= w[i].w;
+            }
+            x[e][i] = v;
           }
         }
       }
     }
-    if (pro == PRO_NORM || pro == PRO_GDN_NORM) {
-      // weight of block column `tid` (shared by the four rows) and of the left-over column
-      const float* wp = pro == PRO_NORM ? (const float*)d.p2 : (const float*)d.p3;
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int b = e == 0 ? tid : ib[4];
-        const int kw = pro == PRO_NORM ? (k0 + b * 16) : ((k0 + b * 16) & 127);
+    for (int e = 0; e < 3; ++e)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) w[e][i] = b < nblk ? __ldg((const float4*)(wp + kw) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
-      }
+      for (int i = 0; i < 4; ++i)
+        mx[e] = fmaxf(mx[e], fmaxf(fmaxf(fabsf(x[e][i].x), fabsf(x[e][i].y)), fmaxf(fabsf(x[e][i].z), fabsf(x[e][i].w))));
+    // ---- per-row reduction over the CTA
+    float rss[2], rmx[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      rss[r] = warp_sum(ss[r] + (r2 == r ? ss[2] : 0.f));
+      rmx[r] = warp_max(fmaxf(mx[r], r2 == r ? mx[2] : 0.f));
     }
-    // ---- elementwise part and per-item statistics
-    float ss[5], mx[5];
-#pragma unroll
-    for (int e = 0; e < 5; ++e) {
-      ss[e] = 0.f; mx[e] = 0.f;
-      const int we = e == 4 ? 1 : 0;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        float4 v = x[e][i];
-        if (pro == PRO_NORM) {
-          ss[e] += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-          v.x *= 1.f + w[we][i].x; v.y *= 1.f + w[we][i].y; v.z *= 1.f + w[we][i].z; v.w *= 1.f + w[we][i].w;
-        } else if (pro == PRO_SWIGLU) {
-          v.x = silu_f(v.x) * y[e][i].x; v.y = silu_f(v.y) * y[e][i].y; v.z = silu_f(v.z) * y[e][i].z; v.w = silu_f(v.w) * y[e][i].w;
-        } else if (pro == PRO_GDN_NORM) {
-          ss[e] += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-          v.x *= w[we][i].x * silu_f(y[e][i].x); v.y *= w[we][i].y * silu_f(y[e][i].y);
-          v.z *= w[we][i].z * silu_f(y[e][i].z); v.w *= w[we][i].w * silu_f(y[e][i].w);
-        }
-        mx[e] = fmaxf(mx[e], fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
-        x[e][i] = v;
-      }
-    }
-    if (pro == PRO_GDN_NORM) {
-      // a head is 8 consecutive blocks: lanes 8h..8h+7 for items 0-3, lanes of equal row (stride 4) for item 4
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        ss[e] += __shfl_xor_sync(0xffffffffu, ss[e], 1); ss[e] += __shfl_xor_sync(0xffffffffu, ss[e], 2);
-        ss[e] += __shfl_xor_sync(0xffffffffu, ss[e], 4);
-      }
-      ss[4] += __shfl_xor_sync(0xffffffffu, ss[4], 4); ss[4] += __shfl_xor_sync(0xffffffffu, ss[4], 8);
-      ss[4] += __shfl_xor_sync(0xffffffffu, ss[4], 16);
-#pragma unroll
-      for (int e = 0; e < 5; ++e) {
-        const float rs = rsqrtf(ss[e] * (1.f / 128.f) + d.f1);
-        mx[e] *= rs;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) { x[e][i].x *= rs; x[e][i].y *= rs; x[e][i].z *= rs; x[e][i].w *= rs; }
-      }
-    }
-    // ---- per-row reduction over the CTA: sum of squares (PRO_NORM) and maximum
-    float rss[4], rmx[4];
-#pragma unroll
-    for (int r = 0; r < 4; ++r) {
-      rss[r] = ss[r] + ((tid & 3) == r ? ss[4] : 0.f);
-      rmx[r] = fmaxf(mx[r], (tid & 3) == r ? mx[4] : 0.f);
-      rss[r] = warp_sum(rss[r]);
-      rmx[r] = warp_max(rmx[r]);
-    }
-    consumer_sync();  // the previous group's gains have been consumed
+    consumer_sync();  // the previous round's partials have been consumed
     if (lane == 0) {
-#pragma unroll
-      for (int r = 0; r < 4; ++r) { stat[(warp * 4 + r) * 2] = rss[r]; stat[(warp * 4 + r) * 2 + 1] = rmx[r]; }
+      stat[warp * 4 + 0] = rss[0]; stat[warp * 4 + 1] = rmx[0]; stat[warp * 4 + 2] = rss[1]; stat[warp * 4 + 3] = rmx[1];
     }
     consumer_sync();
-    float gain[4], rstd[4];
+    float f[2];
 #pragma unroll
-    for (int r = 0; r < 4; ++r) {
+    for (int r = 0; r < 2; ++r) {
       float s2 = 0.f, m = 0.f;
 #pragma unroll
-      for (int wq = 0; wq < kConsumerWarps; ++wq) { s2 += stat[(wq * 4 + r) * 2]; m = fmaxf(m, stat[(wq * 4 + r) * 2 + 1]); }
-      rstd[r] = 1.f;
-      if (pro == PRO_NORM) { rstd[r] = rsqrtf(s2 / (float)d.i0 + d.f1); m *= rstd[r]; }
+      for (int wq = 0; wq < kConsumerWarps; ++wq) { s2 += stat[wq * 4 + 2 * r]; m = fmaxf(m, stat[wq * 4 + 2 * r + 1]); }
+      float rstd = 1.f;
+      if (PRO == PRO_NORM) { rstd = rsqrtf(s2 / (float)d.i0 + d.f1); m *= rstd; }
       // power-of-two row gain: the largest block scale lands at or below 2048 / 6
       float g = 1.f;
       if (m > 0.f && m < 3.0e38f) g = exp2f(floorf(log2f(2048.f / m)));
-      gain[r] = fminf(fmaxf(g, 1.0e-30f), 1.0e30f);
-      if (tid == 0 && t0 + r < 8) c.sm->gscale[t0 + r] = 1.f / gain[r];
+      g = fminf(fmaxf(g, 1.0e-30f), 1.0e30f);
+      if (tid == 0 && t0 + r < 8) c.sm->gscale[t0 + r] = 1.f / g;
+      f[r] = g * rstd;
     }
     // ---- quantise from registers
 #pragma unroll
-    for (int e = 0; e < 5; ++e) {
-      const int row = e == 4 ? (tid & 3) : e;
-      if (ib[e] < nblk) {
+    for (int e = 0; e < 3; ++e) {
+      const int b = e < 2 ? tid : b2, row = e < 2 ? e : r2;
+      if (b < nblk && (e < 2 || tid < 128)) {
         float r16[16];
-        const float f = gain[row] * rstd[row];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          r16[4 * i] = x[e][i].x * f; r16[4 * i + 1] = x[e][i].y * f; r16[4 * i + 2] = x[e][i].z * f; r16[4 * i + 3] = x[e][i].w * f;
+          r16[4 * i] = x[e][i].x * f[row]; r16[4 * i + 1] = x[e][i].y * f[row];
+          r16[4 * i + 2] = x[e][i].z * f[row]; r16[4 * i + 3] = x[e][i].w * f[row];
         }
-        quantize_block(r16, terms, tpad, t0 + row, ib[e], nb, B, SFB);
+        quantize_block(r16, terms, tpad, t0 + row, b, nb, B, SFB);
       }
     }
   }
 }
 
-__device__ void op_gemv(Ctx& c, const Instr& ins) {
+__device__ __noinline__ void gemv_prologue(Ctx& c, const Desc& d, int k0, int kn, int T, int tpad, int terms) {
+  switch (d.i5) {
+    case PRO_NORM: gemv_prologue_t<PRO_NORM>(c, d, k0, kn, T, tpad, terms); break;
+    case PRO_SWIGLU: gemv_prologue_t<PRO_SWIGLU>(c, d, k0, kn, T, tpad, terms); break;
+    case PRO_GDN_NORM: gemv_prologue_t<PRO_GDN_NORM>(c, d, k0, kn, T, tpad, terms); break;
+    default: gemv_prologue_t<PRO_PLAIN>(c, d, k0, kn, T, tpad, terms); break;
+  }
+}
+
+__device__ __noinline__ void op_gemv(Ctx& c, const Instr& ins) {
   const Desc& d = c.p->descs[ins.desc];
   const int tile = ins.a, ks0 = ins.b, nks = ins.c;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -340,17 +370,38 @@ __device__ void op_gemv(Ctx& c, const Instr& ins) {
     // ---- epilogue: lane quarter `warp`; row = tile * 128 + warp * 32 + lane; column n = term * tpad + token
     const bool ok = mbar_wait_bounded(&c.sm->acc_full[ab], use, c.p->status);
     tcgen05_fence_after();
-    uint32_t r[32];
+    float v[8];  // per token: sum over terms of D[term * tpad + token] * 4^-term
+#pragma unroll
+    for (int t = 0; t < 8; ++t) v[t] = 0.f;
     if (ok && !(dbg & 4)) {
       if (nb == 16) {
         uint32_t q[16];
         tmem_ld_32x32b_x16(c.tmem + ((uint32_t)(warp * 32) << 16) + kAccCol + ab * 32, q);
         tcgen05_wait_ld();
+        if (tpad == 4) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) r[i] = q[i];
+          for (int t = 0; t < 4; ++t)
+            v[t] = __uint_as_float(q[t]) + 0.25f * __uint_as_float(q[4 + t]) + 0.0625f * __uint_as_float(q[8 + t]) +
+                   0.015625f * __uint_as_float(q[12 + t]);
+        } else {
+#pragma unroll
+          for (int t = 0; t < 8; ++t) v[t] = __uint_as_float(q[t]) + 0.25f * __uint_as_float(q[8 + t]);
+        }
       } else {
-        tmem_ld_32x32b_x32(c.tmem + ((uint32_t)(warp * 32) << 16) + kAccCol + ab * 32, r);
+        uint32_t q[32];
+        tmem_ld_32x32b_x32(c.tmem + ((uint32_t)(warp * 32) << 16) + kAccCol + ab * 32, q);
         tcgen05_wait_ld();
+        if (tpad == 4) {
+#pragma unroll
+          for (int t = 0; t < 4; ++t)
+            v[t] = __uint_as_float(q[t]) + 0.25f * __uint_as_float(q[4 + t]) + 0.0625f * __uint_as_float(q[8 + t]) +
+                   0.015625f * __uint_as_float(q[12 + t]);
+        } else {
+#pragma unroll
+          for (int t = 0; t < 8; ++t)
+            v[t] = __uint_as_float(q[t]) + 0.25f * __uint_as_float(q[8 + t]) + 0.0625f * __uint_as_float(q[16 + t]) +
+                   0.015625f * __uint_as_float(q[24 + t]);
+        }
       }
     }
     tcgen05_fence_before();
@@ -361,15 +412,13 @@ __device__ void op_gemv(Ctx& c, const Instr& ins) {
       if (d.i7 & 2) out += (size_t)c.rec->parity * d.i8;
       const int row = tile * kTileRows + warp * 32 + lane;
       if (row < d.i2) {
-        for (int t = 0; t < T; ++t) {
-          float v = 0.f, w = 1.f;
-          for (int term = 0; term < terms; ++term) {
-            v += __uint_as_float(r[term * tpad + t]) * w;
-            w *= 0.25f;
+#pragma unroll
+        for (int t = 0; t < 8; ++t) {
+          if (t < T) {
+            const float val = v[t] * c.sm->gscale[t] * d.f0;
+            if (d.i6 == EPI_RED) red_add_f32(out + (size_t)t * d.i4 + row, val);
+            else out[(size_t)t * d.i4 + row] = val;
           }
-          v *= c.sm->gscale[t] * d.f0;
-          if (d.i6 == EPI_RED) red_add_f32(out + (size_t)t * d.i4 + row, v);
-          else out[(size_t)t * d.i4 + row] = v;
         }
       }
     }

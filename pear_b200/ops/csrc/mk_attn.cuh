@@ -58,15 +58,18 @@ __device__ __forceinline__ void norm_rope_warp(const float* src, const float* w,
 #pragma unroll
   for (int i = 0; i < D / 32; ++i) x[i] = x[i] * rs * (1.f + w[lane + 32 * i]);
   // rotary_dim 64: pair (lane, lane + 32) lives in x[0], x[1]
+  // the angle is reduced modulo 2 pi in double so that sincosf stays on its fast, stack-free path at long contexts
+  double ang = (double)pos * (double)inv_freq[lane];
+  ang -= 6.283185307179586 * rint(ang * 0.15915494309189535);
   float sn, cs;
-  sincosf((float)pos * inv_freq[lane], &sn, &cs);
+  sincosf((float)ang, &sn, &cs);
   const float a = x[0], b = x[1];
   x[0] = a * cs - b * sn;
   x[1] = b * cs + a * sn;
 }
 
 template <int D>
-__device__ void attn_item(Ctx& c, const Desc& d, int h, int split, int nsplit) {
+__device__ __noinline__ void attn_item(Ctx& c, const Desc& d, int h, int split, int nsplit) {
   constexpr int QS = D + 16;     // Q row stride (halves): bytes = D*2 + 32
   constexpr int VS = D + 8;      // V row stride (halves)
   constexpr int SS = 68;         // S row stride (floats)
@@ -270,7 +273,7 @@ __device__ void op_attn(Ctx& c, const Instr& ins) {
 }
 
 // Combine: item = (row tq, q head) pair; one warp per pair. Output = softmax-merged o, times sigmoid(gate) if gated.
-__device__ void op_attn_combine(Ctx& c, const Instr& ins) {
+__device__ __noinline__ void op_attn_combine(Ctx& c, const Instr& ins) {
   const Desc& d = c.p->descs[ins.desc];
   const int T = step_rows(c, d);
   const int Hq = d.i2, D = d.i3, nsmax = d.i4, nsplit = ins.c;

@@ -19,7 +19,7 @@ constexpr int kGdnD = 128;          // key dim == value dim per head
 constexpr int kGdnMaxRows = 19;     // 3 window rows + up to 8 replayed + up to 8 current
 constexpr int kGdnCh = 2 * kGdnD + 64;  // q, k and up to 64 v channels staged per item
 
-__device__ void op_gdn(Ctx& c, const Instr& ins) {
+__device__ __noinline__ void op_gdn(Ctx& c, const Instr& ins) {
   const Desc& d = c.p->descs[ins.desc];
   const StepRec* rec = c.rec;
   const int T = rec->T, R = rec->n_replay, par = rec->parity;

@@ -43,7 +43,7 @@ __device__ __forceinline__ void ms_merge(float& m, float& s, float m2, float s2)
   m = mn;
 }
 
-__device__ void op_sample_part(Ctx& c, const Instr& ins) {
+__device__ __noinline__ void op_sample_part(Ctx& c, const Instr& ins) {
   const Desc& d = c.p->descs[ins.desc];
   const StepRec* rec = c.rec;
   const int T = rec->T, V = d.i1, chunk = d.i2, nchunks = d.i3;
@@ -118,7 +118,7 @@ __device__ __forceinline__ void book_prefill(Ctx& c, const Desc& d) {
   }
 }
 
-__device__ void op_sample_fin(Ctx& c, const Instr& ins) {
+__device__ __noinline__ void op_sample_fin(Ctx& c, const Instr& ins) {
   const Desc& d = c.p->descs[ins.desc];
   const StepRec* rec = c.rec;
   StepRec* nx = c.rec_next;
@@ -179,7 +179,7 @@ __device__ void op_sample_fin(Ctx& c, const Instr& ins) {
 }
 
 // Drafter input row `a`: [norm_e(embed(next token)) | norm_h(target residual row)]
-__device__ void op_draft_in(Ctx& c, const Instr& ins) {
+__device__ __noinline__ void op_draft_in(Ctx& c, const Instr& ins) {
   const Desc& d = c.p->descs[ins.desc];
   const StepRec* rec = c.rec;
   const StepRec* nx = c.rec_next;
@@ -218,7 +218,7 @@ __device__ void op_draft_in(Ctx& c, const Instr& ins) {
   consumer_sync();
 }
 
-__device__ void op_argmax_part(Ctx& c, const Instr& ins) {
+__device__ __noinline__ void op_argmax_part(Ctx& c, const Instr& ins) {
   const Desc& d = c.p->descs[ins.desc];
   const StepRec* nx = c.rec_next;
   const int V = d.i1, chunk = d.i2, nchunks = d.i3, nd = d.i4;
@@ -258,7 +258,7 @@ __device__ void op_argmax_part(Ctx& c, const Instr& ins) {
   }
 }
 
-__device__ void op_argmax_fin(Ctx& c, const Instr& ins) {
+__device__ __noinline__ void op_argmax_fin(Ctx& c, const Instr& ins) {
   const Desc& d = c.p->descs[ins.desc];
   StepRec* nx = c.rec_next;
   const int nchunks = d.i3, nd = d.i4;
