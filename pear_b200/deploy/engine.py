@@ -31,6 +31,7 @@ class _Params(ctypes.Structure):
         ("max_instrs", ctypes.c_int32), ("ring", ctypes.c_int32), ("step_parity", ctypes.c_int32),
         ("seed", ctypes.c_uint32), ("temperature", ctypes.c_float), ("vocab", ctypes.c_int32),
         ("barrier_base", ctypes.c_uint32), ("pad", ctypes.c_int32), ("ctrl", ctypes.c_void_p),
+        ("trace", ctypes.c_void_p), ("trace_ctas", ctypes.c_int32), ("trace_cap", ctypes.c_int32),
     ]
 
 
@@ -113,6 +114,7 @@ class MegakernelEngine:
         self._build(weights)
         self.launches = 0
         self._use_ctrl = True
+        self._trace, self._trace_ctas, self._trace_cap = None, 0, 0
         self.barrier_base = 0
         self.reset()
 
@@ -169,6 +171,12 @@ class MegakernelEngine:
         self.attn_part = self._zeros(T8 * cfg.num_attention_heads, nsplit_max, cfg.head_dim + 2)
         self.embed = self._dev(W.matrix("model.embed_tokens.weight", V, H), torch.bfloat16)
 
+        # activation-operand images built by the QUANT phases (largest K = the FFN width, 32-row operand) and the per-GEMV
+        # row statistics (sum of squares for the deferred RMS), zeroed at the start of every step
+        kmax = max(I, 2 * H, VD, cfg.q_size, *((dc.intermediate_size, dc.q_size) if dc is not None else ()))
+        self.b_image = self._zeros((kmax // 32) * 4 * 128 + 1024, dtype=torch.uint8)
+        self.sfb_image = self._zeros((kmax // 64) * 32 * 16 + 1024, dtype=torch.uint8)
+        self.gemv_stats = self._zeros(4096 * 8)
         progs = {"decode": S.Program(self.num_ctas), "prefill": S.Program(self.num_ctas)}
         self.programs = progs
         self._descs: list[dict] = []
@@ -187,7 +195,8 @@ class MegakernelEngine:
 
         def gemv_desc(packed, gs, K, rows, inp, in_stride, out, out_stride, pro, epi, flags=0, p2=0, p3=0, i8=0, i9=0,
                       eps=cfg.rms_eps):
-            return desc(p0=P(packed), p1=inp, p2=p2, p3=p3, p4=out, i0=K, i1=K // S.STAGE_K, i2=rows, i3=in_stride,
+            return desc(p0=P(packed), p1=inp, p2=p2, p3=p3, p4=out, p5=P(self.b_image), p6=P(self.sfb_image),
+                        p7=P(self.gemv_stats, 8 * len(self._descs)), i0=K, i1=K // S.STAGE_K, i2=rows, i3=in_stride,
                         i4=out_stride, i5=pro, i6=epi, i7=flags, i8=i8, i9=i9, f0=1.0 / gs, f1=eps)
 
         def zero_desc(t: torch.Tensor, flags=0, i8=0) -> int:
@@ -200,7 +209,14 @@ class MegakernelEngine:
         d_embed = desc(p0=P(self.embed), p4=P(self.r), i0=H, i4=H)
         z_gu = zero_desc(self.gu)
         z_qkv = zero_desc(self.qkv)
-        both(lambda p: p.ranged(S.OP_EMBED, d_embed, H, granule=256))
+        z_stats = zero_desc(self.gemv_stats)
+        both(lambda p: (p.ranged(S.OP_EMBED, d_embed, H, granule=256), add_zero(p, z_stats, 4096 * 8)))
+
+        def G(p: S.Program, d: int, rows: int, K: int, aligned: bool = False) -> None:
+            """A GEMV op: the phase that builds its activation operand, a grid barrier, then the streamed GEMV."""
+            p.quant(d, K)
+            p.barrier()
+            p.gemv(d, rows, K, aligned)
 
         # drafter buffers (zeroed during the target's first phase)
         if dc is not None:
@@ -263,7 +279,7 @@ class MegakernelEngine:
             nsplit = self.attn_splits or max(1, self.num_ctas // Hkv)
             if pre is not None:
                 pre(p)
-            p.gemv(d_in, rows, icfg.hidden_size)
+            G(p, d_in, rows, icfg.hidden_size)
             p.barrier()
             p.spread(S.OP_ATTN, d_at, [(h, s, nsplit) for s in range(nsplit) for h in range(Hkv)])
             p.barrier()
@@ -271,14 +287,14 @@ class MegakernelEngine:
             per = max(1, (npairs + p.num_ctas - 1) // p.num_ctas)
             p.spread(S.OP_ATTN_COMBINE, d_at, [(a, min(per, npairs - a), nsplit) for a in range(0, npairs, per)])
             p.barrier()
-            p.gemv(d_out, icfg.hidden_size, icfg.q_size)
+            G(p, d_out, icfg.hidden_size, icfg.q_size)
             add_zero(p, z_qkv_desc, qkv_elems)
             p.barrier()
 
         def emit_mlp(p: S.Program, d_gu, d_dn, gu_rows, ii, hh):
-            p.gemv(d_gu, gu_rows, hh)
+            G(p, d_gu, gu_rows, hh)
             p.barrier()
-            p.gemv(d_dn, hh, ii)
+            G(p, d_dn, hh, ii)
             p.barrier()
 
         for li, lt in enumerate(cfg.layer_types):
@@ -320,12 +336,12 @@ class MegakernelEngine:
 
                 def emit(p: S.Program, d_in=d_in, d_core=d_core, d_out=d_out, z_rec=z_rec, items=items, d_gu=d_gu, d_dn=d_dn,
                          gu_rows=gu_rows, ii=ii):
-                    p.gemv(d_in, C + VD + 2 * HV, H)
+                    G(p, d_in, C + VD + 2 * HV, H)
                     add_zero(p, z_gu, T8 * 2 * I)
                     p.barrier()
                     p.spread(S.OP_GDN, d_core, items)
                     p.barrier()
-                    p.gemv(d_out, H, VD)
+                    G(p, d_out, H, VD)
                     add_zero(p, z_rec, T8 * self.rec_stride)
                     p.barrier()
                     emit_mlp(p, d_gu, d_dn, gu_rows, ii, H)
@@ -353,7 +369,7 @@ class MegakernelEngine:
         d_book = desc(p1=P(self.prompt_dev), i4=self.n_draft, i5=0, i6=1, i9=self.mask_token_id)
         self._d_samp, self._d_book = d_samp, d_book
         dp, pp = progs["decode"], progs["prefill"]
-        dp.gemv(d_head, V, H, aligned=True)
+        G(dp, d_head, V, H, aligned=True)
         dp.barrier()
         dp.ranged(S.OP_SAMPLE_PART, d_samp, nchunks)
         dp.barrier()
@@ -374,7 +390,7 @@ class MegakernelEngine:
             dp.spread(S.OP_DRAFT_IN, d_din, [(j,) for j in range(T8)])
             pp.spread(S.OP_DRAFT_IN, d_din_pre, [(j,) for j in range(T8)])
             both(lambda p: p.barrier())
-            both(lambda p: (p.gemv(d_fc, H, 2 * H), p.barrier()))
+            both(lambda p: (G(p, d_fc, H, 2 * H), p.barrier()))
             for li in range(dc.num_layers):
                 prefix = f"draft.layers.{li}"
                 d_in, rows, d_at, d_out = attn_block(prefix, ("draft", li), dc, self.rd, self.dqkv, self.d_qkv_stride,
@@ -395,7 +411,7 @@ class MegakernelEngine:
                                 p2=P(dfin_w))
             d_arg = desc(p0=P(self.dlogits), p4=P(self.argmax_part), i0=V, i1=V, i2=self.CHUNK, i3=nchunks, i4=self.n_draft)
             if self.n_draft > 0:
-                dp.gemv(d_dhead, V, H, aligned=True)
+                G(dp, d_dhead, V, H, aligned=True)
                 dp.barrier()
                 dp.ranged(S.OP_ARGMAX_PART, d_arg, nchunks)
                 dp.barrier()
@@ -459,7 +475,8 @@ class MegakernelEngine:
             barrier=self.barrier.data_ptr(), status=self.status.data_ptr(), max_instrs=max_len, ring=self.RING,
             step_parity=self.step & 1, seed=self.seed, temperature=self.temperature, vocab=self.cfg.vocab_size,
             barrier_base=self.barrier_base & 0xFFFFFFFF, pad=int(os.environ.get("PEAR_MK_DEBUG", "0")),
-            ctrl=self.ctrl_dev[self.step % self.RING].data_ptr() if self._use_ctrl else 0)
+            ctrl=self.ctrl_dev[self.step % self.RING].data_ptr() if self._use_ctrl else 0,
+            trace=self._trace.data_ptr() if self._trace is not None else 0, trace_ctas=self._trace_ctas, trace_cap=self._trace_cap)
         ns, nb = self.LAUNCH_SHAPE[program]
         code = _lib.lib().pear_mk_launch(ctypes.byref(prm), self.num_ctas, ns, nb, _lib.stream())
         _lib.check(code, "megakernel launch")
@@ -467,6 +484,29 @@ class MegakernelEngine:
         self.barrier_base += stats["barriers"] * self.num_ctas
         self.step += 1
         self.launches += 1
+
+    # -- in-kernel tracing ------------------------------------------------------------------------------------------------
+    def enable_trace(self, ctas: int = 2, cap: int = 8192) -> None:
+        """Timeline of the next launches: thread 0 of the first ``ctas`` CTAs records (mark, instruction, globaltimer)."""
+        self._trace = torch.zeros(ctas * cap * 2, dtype=torch.int64, device=self.device)
+        self._trace_ctas, self._trace_cap = ctas, cap
+
+    def read_trace(self, program: str = "decode") -> list[list[tuple[int, int, int, int]]]:
+        """Per traced CTA: (mark id, instruction index, opcode, nanoseconds since the CTA's first record)."""
+        t = self._trace.cpu().numpy().reshape(self._trace_ctas, self._trace_cap, 2)
+        instrs = self._prog_dev[program][0].cpu().numpy().reshape(self.num_ctas, -1, 8)
+        out = []
+        for c in range(self._trace_ctas):
+            n = int(t[c, 0, 0])
+            recs = []
+            for i in range(1, n + 1):
+                word, ts = int(t[c, i, 0]), int(t[c, i, 1])
+                ip = word & 0xFFFFFFFF
+                op = int(instrs[c, ip, 0]) if ip < instrs.shape[1] else -1
+                recs.append((word >> 32, ip, op, ts - int(t[c, 1, 1])))
+            out.append(recs)
+        self._trace.zero_()
+        return out
 
     def prefill(self) -> None:
         for _ in range(self.prefill_steps):

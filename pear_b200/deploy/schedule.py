@@ -16,7 +16,7 @@ import numpy as np
 
 # opcodes / enums (megakernel.cuh)
 OP_END, OP_GEMV, OP_BARRIER, OP_EMBED, OP_ZERO, OP_GDN, OP_ATTN, OP_ATTN_COMBINE = range(8)
-OP_SAMPLE_PART, OP_SAMPLE_FIN, OP_DRAFT_IN, OP_ARGMAX_PART, OP_ARGMAX_FIN, OP_COPY = range(8, 14)
+OP_SAMPLE_PART, OP_SAMPLE_FIN, OP_DRAFT_IN, OP_ARGMAX_PART, OP_ARGMAX_FIN, OP_COPY, OP_QUANT = range(8, 15)
 PRO_PLAIN, PRO_NORM, PRO_SWIGLU, PRO_GDN_NORM = range(4)
 EPI_RED, EPI_STORE = range(2)
 F_IN_PARITY, F_OUT_PARITY, F_OUT_OTHER_PARITY, F_DRAFT_ROWS = 1, 2, 4, 8
@@ -81,6 +81,10 @@ class Program:
             lo, hi = units * i // n, units * (i + 1) // n
             if hi > lo:
                 self.emit((r + i) % self.num_ctas, op, desc, lo * granule, min(total, hi * granule) - lo * granule)
+
+    def quant(self, desc: int, k: int) -> None:
+        """Phase that builds the activation operand of GEMV ``desc``: one unit per 128 K elements, dealt over the CTAs."""
+        self.spread(OP_QUANT, desc, [(u, 1) for u in range(k // 128)])
 
     def gemv(self, desc: int, rows: int, k: int, aligned: bool = False) -> None:
         """Stream-K split of a [rows x k] GEMV. ``aligned``: cuts only at tile boundaries (plain-store epilogues)."""

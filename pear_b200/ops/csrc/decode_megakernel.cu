@@ -42,6 +42,7 @@ struct Smem {
   uint64_t empty[16];
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
+  uint64_t bload;      // completion of the activation-operand bulk copies
   uint32_t tmem_base;
   int abort_flag;
   float red[64];
@@ -59,12 +60,27 @@ struct Ctx {
   int nb;              // rows of the B operand (16 or 32)
   int stage, phase;    // ring cursor (meaningful in the issuing thread)
   int seg;             // GEMV segments executed so far (accumulator alternation)
+  int nload;           // operand loads so far (parity of the bload barrier)
   uint32_t tmem;
   uint32_t barrier_target;
+  int ip;              // index of the instruction being executed (tracing)
 };
 
 __device__ __forceinline__ int step_rows(const Ctx& c, const Desc& d) {
   return (d.i7 & 8) ? *(volatile const int*)&c.rec_next->rows_draft : c.rec->T;
+}
+
+// Timeline record (thread 0 of the traced CTAs only): mark ids are small integers documented beside their call sites.
+__device__ __forceinline__ void trace_mark(const Ctx& c, int id) {
+  if (c.p->trace == nullptr || threadIdx.x != 0 || (int)blockIdx.x >= c.p->trace_ctas) return;
+  unsigned long long* base = c.p->trace + (size_t)blockIdx.x * c.p->trace_cap * 2;
+  const unsigned long long n = base[0];
+  if ((int)n + 1 >= c.p->trace_cap) return;
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  base[2 * (n + 1)] = ((unsigned long long)id << 32) | (unsigned)c.ip;
+  base[2 * (n + 1) + 1] = t;
+  base[0] = n + 1;
 }
 
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory"); }
@@ -92,219 +108,11 @@ __device__ __forceinline__ void grid_barrier(Ctx& c) {
 // ---------------------------------------------------------------------------------------------------------------------
 // GEMV
 // ---------------------------------------------------------------------------------------------------------------------
-__device__ __forceinline__ float e4m3_to_f32(uint32_t code) {
-  __half_raw h = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)code, __NV_E4M3);
-  return __half2float(*reinterpret_cast<__half*>(&h));
-}
+}  // namespace mk
 
-// Quantise 16 pre-scaled values into `terms` NVFP4 blocks (term i encodes the residual of terms < i, with a gain of
-// 4^i folded into its scale) and store codes + scales into the B operand image.
-//   codes : B + (chunk * (nb/8) + n/8) * 128 + (n%8) * 16 + half * 8     (chunk = block/2, half = block%2, 8 bytes)
-//   scales: SFB + (block/4) * nb * 16 + n * 16 + block%4                    (n = term * tpad + row)
-__device__ __forceinline__ void quantize_block(float (&r)[16], int terms, int tpad, int row, int blk, int nb, uint8_t* B,
-                                               uint8_t* SFB) {
-  float gain = 1.f;
-  for (int term = 0; term < terms; ++term) {
-    float amax = 0.f;
-#pragma unroll
-    for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(r[i]));
-    const float target = amax * (1.f / 6.f) * gain;
-    uint32_t code = (uint32_t)__nv_cvt_float_to_fp8(target, __NV_SATFINITE, __NV_E4M3);
-    float sv = e4m3_to_f32(code);
-    if (sv < target && code < 0x7Eu) { ++code; sv = e4m3_to_f32(code); }  // round the scale up: no code saturates
-    const float inv = sv > 0.f ? gain / sv : 0.f;
-    const float back = sv / gain;
-    uint32_t words[2] = {0u, 0u};
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const uint32_t byte = (uint32_t)__nv_cvt_float2_to_fp4x2(make_float2(r[2 * i] * inv, r[2 * i + 1] * inv), __NV_E2M1,
-                                                               cudaRoundNearest) & 0xffu;
-      words[i >> 2] |= byte << (8 * (i & 3));
-      __half2_raw hr = __nv_cvt_fp4x2_to_halfraw2((__nv_fp4x2_storage_t)byte, __NV_E2M1);
-      const float2 dq = __half22float2(*reinterpret_cast<__half2*>(&hr));
-      r[2 * i] -= dq.x * back;
-      r[2 * i + 1] -= dq.y * back;
-    }
-    const int n = term * tpad + row;
-    *(uint2*)(B + ((size_t)(blk >> 1) * (nb >> 3) + (n >> 3)) * 128 + (n & 7) * 16 + (blk & 1) * 8) = make_uint2(words[0], words[1]);
-    SFB[(blk >> 2) * nb * 16 + n * 16 + (blk & 3)] = (uint8_t)code;
-    gain *= 4.f;
-  }
-}
+#include "mk_quant.cuh"
 
-// Build the B operand (FP4 terms of the activation rows) for K range [k0, k0 + kn) of the op's input.
-//
-// Register-resident rounds over PAIRS of rows (no stack, no spills: the L1 left beside 227 KB of shared memory is too
-// small to absorb any): thread `tid` owns K block `tid` (16 elements) of both rows and, for tid < 128, one block of
-// the left-over columns 256.. (block 256 + tid/2 of row tid%2), i.e. 3 blocks = 48 values. All global loads of a round
-// are issued before the first use; the row statistics (RMS, maximum) are reduced with shuffles and one shared-memory
-// exchange; the blocks are quantised straight from registers. PRO_NORM always covers the whole row.
-template <int PRO>
-__device__ __forceinline__ void gemv_prologue_t(Ctx& c, const Desc& d, int k0, int kn, int T, int tpad, int terms) {
-  const StepRec* rec = c.rec;
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const float* in = (const float*)d.p1;
-  if ((d.i7 & 1) && PRO != PRO_GDN_NORM) in += (size_t)rec->parity * d.i8;
-  const int istride = d.i3, nb = c.nb;
-  uint8_t* B = c.xs;
-  uint8_t* SFB = c.xs + (size_t)(kMaxSegStages * kStageK / 32) * (nb >> 3) * 128;
-  float* stat = (float*)(SFB + sfb_bytes(nb));  // [warp][row of the pair][2]: partial (sum of squares, maximum)
-  const float* zbase = (const float*)d.p2;
-  if (PRO == PRO_GDN_NORM && (d.i7 & 1)) zbase += (size_t)rec->parity * d.i8;
-  const int nblk = kn >> 4;
-  const float* wp = PRO == PRO_NORM ? (const float*)d.p2 : (const float*)d.p3;
-
-  for (int t0 = 0; t0 < tpad; t0 += 2) {
-    // ---- items: e = 0, 1: (block tid, row t0 + e); e = 2: (block 256 + tid/2, row t0 + tid%2) for tid < 128
-    const int b2 = 256 + (tid >> 1), r2 = tid & 1;
-    float4 x[3][4];
-    // ---- loads (all issued before use)
-#pragma unroll
-    for (int e = 0; e < 3; ++e) {
-      const int b = e < 2 ? tid : b2, t = t0 + (e < 2 ? e : r2);
-      const bool valid = b < nblk && t < T && (e < 2 || tid < 128);
-      const int k = k0 + b * 16;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        x[e][i] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (valid) {
-          if (PRO == PRO_GDN_NORM) x[e][i] = __ldcg((const float4*)((const float*)d.p1 + (size_t)t * istride + k) + i);
-          else x[e][i] = __ldcg((const float4*)(in + (size_t)t * istride + k) + i);
-        }
-      }
-    }
-    if (PRO == PRO_SWIGLU || PRO == PRO_GDN_NORM) {
-      // second operand: loaded while the first is in flight, folded in as it arrives
-#pragma unroll
-      for (int e = 0; e < 3; ++e) {
-        const int b = e < 2 ? tid : b2, t = t0 + (e < 2 ? e : r2);
-        const bool valid = b < nblk && t < T && (e < 2 || tid < 128);
-        const int k = k0 + b * 16;
-        float4 y[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          y[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-          if (valid) {
-            if (PRO == PRO_GDN_NORM) y[i] = __ldcg((const float4*)(zbase + (size_t)t * d.i9 + k) + i);
-            else y[i] = __ldcg((const float4*)(in + (size_t)t * istride + k + d.i0) + i);
-          }
-        }
-        if (PRO == PRO_SWIGLU) {
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            x[e][i].x = silu_f(x[e][i].x) * y[i].x; x[e][i].y = silu_f(x[e][i].y) * y[i].y;
-            x[e][i].z = silu_f(x[e][i].z) * y[i].z; x[e][i].w = silu_f(x[e][i].w) * y[i].w;
-          }
-        } else {
-          // the head statistic needs the raw o: keep sum(o^2) in .. a scalar, fold silu(z) now
-          float ssq = 0.f;
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            ssq += x[e][i].x * x[e][i].x + x[e][i].y * x[e][i].y + x[e][i].z * x[e][i].z + x[e][i].w * x[e][i].w;
-            x[e][i].x *= silu_f(y[i].x); x[e][i].y *= silu_f(y[i].y); x[e][i].z *= silu_f(y[i].z); x[e][i].w *= silu_f(y[i].w);
-          }
-          // a head is 8 consecutive blocks: lanes 8h..8h+7 (items 0, 1); lanes of equal row, stride 2 (item 2)
-          if (e < 2) {
-            ssq += __shfl_xor_sync(0xffffffffu, ssq, 1); ssq += __shfl_xor_sync(0xffffffffu, ssq, 2);
-            ssq += __shfl_xor_sync(0xffffffffu, ssq, 4);
-          } else {
-            ssq += __shfl_xor_sync(0xffffffffu, ssq, 2); ssq += __shfl_xor_sync(0xffffffffu, ssq, 4);
-            ssq += __shfl_xor_sync(0xffffffffu, ssq, 8);
-          }
-          const float rs = rsqrtf(ssq * (1.f / 128.f) + d.f1);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) { x[e][i].x *= rs; x[e][i].y *= rs; x[e][i].z *= rs; x[e][i].w *= rs; }
-        }
-      }
-    }
-    // ---- weights and per-item statistics
-    float ss[3], mx[3];
-#pragma unroll
-    for (int e = 0; e < 3; ++e) {
-      ss[e] = 0.f; mx[e] = 0.f;
-      if (e == 1) continue;  // item 1 shares item 0's weight block: handled together below
-    }
-    if (PRO == PRO_NORM || PRO == PRO_GDN_NORM) {
-#pragma unroll
-      for (int wsel = 0; wsel < 2; ++wsel) {
-        const int b = wsel == 0 ? tid : b2;
-        const int kw = PRO == PRO_NORM ? (k0 + b * 16) : ((k0 + b * 16) & 127);
-        float4 w[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) w[i] = b < nblk ? __ldg((const float4*)(wp + kw) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-        for (int e = (wsel == 0 ? 0 : 2); e < (wsel == 0 ? 2 : 3); ++e) {
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            float4 v = x[e][i];
-            if (PRO == PRO_NORM) {
-              ss[e] += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-              v.x *= 1.f + w[i].x; v.y *= 1.f + w[i].y; v.z *= 1.f + w[i].z; v.w *= 1.f + w[i].w;
-            } else {
-              v.x *= w[i].x; v.y *= w[i].y; v.z *= w[i].z; v.w *= w[i].w;
-            }
-            x[e][i] = v;
-          }
-        }
-      }
-    }
-#pragma unroll
-    for (int e = 0; e < 3; ++e)
-#pragma unroll
-      for (int i = 0; i < 4; ++i)
-        mx[e] = fmaxf(mx[e], fmaxf(fmaxf(fabsf(x[e][i].x), fabsf(x[e][i].y)), fmaxf(fabsf(x[e][i].z), fabsf(x[e][i].w))));
-    // ---- per-row reduction over the CTA
-    float rss[2], rmx[2];
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      rss[r] = warp_sum(ss[r] + (r2 == r ? ss[2] : 0.f));
-      rmx[r] = warp_max(fmaxf(mx[r], r2 == r ? mx[2] : 0.f));
-    }
-    consumer_sync();  // the previous round's partials have been consumed
-    if (lane == 0) {
-      stat[warp * 4 + 0] = rss[0]; stat[warp * 4 + 1] = rmx[0]; stat[warp * 4 + 2] = rss[1]; stat[warp * 4 + 3] = rmx[1];
-    }
-    consumer_sync();
-    float f[2];
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      float s2 = 0.f, m = 0.f;
-#pragma unroll
-      for (int wq = 0; wq < kConsumerWarps; ++wq) { s2 += stat[wq * 4 + 2 * r]; m = fmaxf(m, stat[wq * 4 + 2 * r + 1]); }
-      float rstd = 1.f;
-      if (PRO == PRO_NORM) { rstd = rsqrtf(s2 / (float)d.i0 + d.f1); m *= rstd; }
-      // power-of-two row gain: the largest block scale lands at or below 2048 / 6
-      float g = 1.f;
-      if (m > 0.f && m < 3.0e38f) g = exp2f(floorf(log2f(2048.f / m)));
-      g = fminf(fmaxf(g, 1.0e-30f), 1.0e30f);
-      if (tid == 0 && t0 + r < 8) c.sm->gscale[t0 + r] = 1.f / g;
-      f[r] = g * rstd;
-    }
-    // ---- quantise from registers
-#pragma unroll
-    for (int e = 0; e < 3; ++e) {
-      const int b = e < 2 ? tid : b2, row = e < 2 ? e : r2;
-      if (b < nblk && (e < 2 || tid < 128)) {
-        float r16[16];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          r16[4 * i] = x[e][i].x * f[row]; r16[4 * i + 1] = x[e][i].y * f[row];
-          r16[4 * i + 2] = x[e][i].z * f[row]; r16[4 * i + 3] = x[e][i].w * f[row];
-        }
-        quantize_block(r16, terms, tpad, t0 + row, b, nb, B, SFB);
-      }
-    }
-  }
-}
-
-__device__ __noinline__ void gemv_prologue(Ctx& c, const Desc& d, int k0, int kn, int T, int tpad, int terms) {
-  switch (d.i5) {
-    case PRO_NORM: gemv_prologue_t<PRO_NORM>(c, d, k0, kn, T, tpad, terms); break;
-    case PRO_SWIGLU: gemv_prologue_t<PRO_SWIGLU>(c, d, k0, kn, T, tpad, terms); break;
-    case PRO_GDN_NORM: gemv_prologue_t<PRO_GDN_NORM>(c, d, k0, kn, T, tpad, terms); break;
-    default: gemv_prologue_t<PRO_PLAIN>(c, d, k0, kn, T, tpad, terms); break;
-  }
-}
+namespace mk {
 
 __device__ __noinline__ void op_gemv(Ctx& c, const Instr& ins) {
   const Desc& d = c.p->descs[ins.desc];
@@ -320,16 +128,33 @@ __device__ __noinline__ void op_gemv(Ctx& c, const Instr& ins) {
   uint8_t* SFB = c.xs + (size_t)(kMaxSegStages * kStageK / 32) * (nb >> 3) * 128;
   const bool issuer = tid == 4 * 32;  // lane 0 of warp 4: warps 0-3 own the four tensor-memory lane quarters
   const int dbg = c.p->pad;  // timing experiments only: 1 skip the prologue, 2 skip UTCCP/MMA issue, 4 skip the epilogue math
+  trace_mark(c, 10);  // gemv: entered
   if (ins.d & 1) {
     // every MMA that reads the old B operand has completed once the previous segment's accumulator is full
     if (c.seg > 0) mbar_wait_bounded(&c.sm->acc_full[(c.seg - 1) & 1], (uint32_t)((c.seg - 1) >> 1) & 1u, c.p->status);
     consumer_sync();
-    if (!(dbg & 1)) {
-      if (whole) gemv_prologue(c, d, 0, d.i0, T, tpad, terms);
-      else gemv_prologue(c, d, ks0 * kStageK, nks * kStageK, T, tpad, terms);
+    trace_mark(c, 11);  // gemv: previous MMAs drained, operand load starts
+    // the operand images of this op were built by OP_QUANT in the previous phase: pull this segment's K range
+    const int k0 = whole ? 0 : ks0 * kStageK, kn = whole ? d.i0 : nks * kStageK;
+    const uint32_t chunk_bytes = (uint32_t)(nb >> 3) * 128u;
+    const uint32_t b_bytes = (uint32_t)(kn >> 5) * chunk_bytes;
+    const uint32_t sf_bytes = (uint32_t)(kn >> 6) * nb * 16u + (nb == 16 ? 256u : 0u);  // tcgen05.cp reads 32 rows
+    if (tid == 0 && !(dbg & 1)) {
+      asm volatile("fence.proxy.async;" ::: "memory");
+      mbar_expect_tx(&c.sm->bload, b_bytes + sf_bytes);
+      bulk_load_1d(B, (const uint8_t*)d.p5 + (size_t)(k0 >> 5) * chunk_bytes, b_bytes, &c.sm->bload);
+      bulk_load_1d(SFB, (const uint8_t*)d.p6 + (size_t)(k0 >> 6) * nb * 16, sf_bytes, &c.sm->bload);
     }
-    fence_proxy_async();  // generic-proxy stores to the operand images -> visible to the tensor core / tcgen05.cp
+    if (!(dbg & 1)) mbar_wait_bounded(&c.sm->bload, (uint32_t)c.nload & 1u, c.p->status);
+    ++c.nload;
+    if (tid < 8) {
+      // epilogue factor per row: undo the pre-gain, apply the deferred RMS of PRO_NORM
+      float f = 1.f / kPreGain;
+      if (d.i5 == PRO_NORM) f *= rsqrtf(__ldcg((const float*)d.p7 + tid) / (float)d.i0 + d.f1);
+      c.sm->gscale[tid] = f;
+    }
     consumer_sync();
+    trace_mark(c, 12);  // gemv: operand in shared memory
     if (issuer && !(dbg & 2)) {
       const int nmma = (whole ? d.i1 : nks) * 4;
       tcgen05_fence_after();
@@ -369,6 +194,7 @@ __device__ __noinline__ void op_gemv(Ctx& c, const Instr& ins) {
   if (warp < 4) {
     // ---- epilogue: lane quarter `warp`; row = tile * 128 + warp * 32 + lane; column n = term * tpad + token
     const bool ok = mbar_wait_bounded(&c.sm->acc_full[ab], use, c.p->status);
+    trace_mark(c, 13);  // gemv: accumulator full
     tcgen05_fence_after();
     float v[8];  // per token: sum over terms of D[term * tpad + token] * 4^-term
 #pragma unroll
@@ -423,6 +249,7 @@ __device__ __noinline__ void op_gemv(Ctx& c, const Instr& ins) {
       }
     }
   }
+  trace_mark(c, 14);  // gemv: epilogue issued
   ++c.seg;
 }
 
@@ -481,6 +308,7 @@ __global__ void __launch_bounds__(kThreads, 1) mk_main(const __grid_constant__ P
   if (tid == 0) {
     for (int i = 0; i < ns; ++i) { mbar_init(&sm->full[i], 1); mbar_init(&sm->empty[i], 1); }
     for (int i = 0; i < 2; ++i) { mbar_init(&sm->acc_full[i], 1); mbar_init(&sm->acc_empty[i], 4); }
+    mbar_init(&sm->bload, 1);
     sm->abort_flag = 0;
     mbar_fence_init();
   }
@@ -520,7 +348,7 @@ __global__ void __launch_bounds__(kThreads, 1) mk_main(const __grid_constant__ P
     Ctx c;
     c.p = &p; c.ring = ring; c.xs = xs; c.sm = sm;
     c.rec = p.rec + p.step_parity; c.rec_next = p.rec + (p.step_parity ^ 1);
-    c.ns = ns; c.nb = nb; c.stage = 0; c.phase = 0; c.seg = 0; c.tmem = sm->tmem_base; c.barrier_target = p.barrier_base;
+    c.ns = ns; c.nb = nb; c.stage = 0; c.phase = 0; c.seg = 0; c.nload = 0; c.tmem = sm->tmem_base; c.barrier_target = p.barrier_base; c.ip = 0;
     // instruction fetch is software-pipelined: the next instruction (and its descriptor's cache line) is requested
     // while the current one executes, so no op starts with a dependent chain of L2 round trips
     Instr next = list[0];
@@ -539,12 +367,15 @@ __global__ void __launch_bounds__(kThreads, 1) mk_main(const __grid_constant__ P
         }
         continue;
       }
+      c.ip = ip;
+      trace_mark(c, 1);  // instruction start (op code = instrs[ip].op)
       switch (ins.op) {
         case OP_GEMV: op_gemv(c, ins); break;
         case OP_BARRIER: grid_barrier(c); break;
         case OP_EMBED: op_embed(c, ins); break;
         case OP_ZERO: op_zero(c, ins); break;
         case OP_COPY: op_copy(c, ins); break;
+        case OP_QUANT: op_quant(c, ins); break;
         case OP_GDN: if (!(p.pad & 16)) op_gdn(c, ins); break;
         case OP_ATTN: if (!(p.pad & 32)) op_attn(c, ins); break;
         case OP_ATTN_COMBINE: if (!(p.pad & 32)) op_attn_combine(c, ins); break;
@@ -558,6 +389,8 @@ __global__ void __launch_bounds__(kThreads, 1) mk_main(const __grid_constant__ P
       if (next.op != OP_END && next.op != OP_BARRIER)
         asm volatile("prefetch.global.L2 [%0];" ::"l"(p.descs + next.desc));
     }
+    c.ip = p.max_instrs;
+    trace_mark(c, 2);  // list finished
     // every issued MMA has completed before tensor memory is released
     if (c.seg > 0) mbar_wait_bounded(&sm->acc_full[(c.seg - 1) & 1], (uint32_t)((c.seg - 1) >> 1) & 1u, p.status);
   }

@@ -35,6 +35,7 @@ enum Op : int {
   OP_ARGMAX_PART = 11,  // a: first vocab chunk, b: chunk count
   OP_ARGMAX_FIN = 12,   // run by one CTA: draft tokens into the next step record
   OP_COPY = 13,         // a: first float, b: float count: dst[i] = src[i]
+  OP_QUANT = 14,        // a: first unit of 128 K elements, b: unit count: builds the next GEMV's activation operand
 };
 
 struct __align__(16) Instr {
@@ -121,6 +122,11 @@ struct Params {
   uint32_t barrier_base;   // value of the barrier counter when the launch starts (the counter is never reset)
   int32_t pad;
   const StepCtrl* ctrl;    // null: temperature/seed above
+  // in-kernel tracing: CTAs below trace_ctas append (mark id, instruction index, globaltimer ns) records;
+  // trace[cta * trace_cap] holds the record count, records follow (2 x uint64 each). Null: tracing off.
+  unsigned long long* trace;
+  int32_t trace_ctas;
+  int32_t trace_cap;
 };
 
 }  // namespace mk

@@ -1,0 +1,216 @@
+"""Simulator servers: supervised environment subprocesses lent to episodes by a pool.
+
+The role of upstream ``pear/sim/server.py`` (Ray-actor ``ServerPool`` on the head lending ``Server`` actors that
+supervise simulator subprocesses over pipes), ``process.py`` and ``client.py``, without Ray: a ``Server`` owns one
+subprocess per slot and talks to it over a pipe; a watchdog restarts ended processes; a call that exceeds its timeout
+kills the process and raises ``EpisodeLost`` (``server.py:169-182``, ``process.py:122-134``); a stateless call is
+retried once on another process (``:80-94``); a process that fails its first start three times fails the run
+(``:37, :146-154``). ``ServerPool.acquire / release`` hands processes to episodes (``:262, :266``).
+
+All failure paths are host-side: nothing here touches a GPU.
+"""
+
+from __future__ import annotations
+
+import importlib
+import multiprocessing as mp
+import threading
+import time
+import traceback
+from dataclasses import dataclass
+from typing import Any, Optional
+
+from ..utils.process import die_with_parent
+from .env import EpisodeLost, StatefulEnv, StatelessEnv
+
+MAX_FIRST_START_FAILURES = 3
+
+
+def _load(path: str):
+    module, _, name = path.rpartition(".")
+    return getattr(importlib.import_module(module), name)
+
+
+def _worker(conn, env_path: str, mode: str, kwargs: dict) -> None:
+    """Child process: serve calls from the pipe until it closes."""
+    die_with_parent()
+    try:
+        env_cls = _load(env_path)
+        host = StatelessEnv(env_cls, **kwargs) if mode == "stateless" else StatefulEnv(env_cls, **kwargs)
+        conn.send(("ready", None))
+    except Exception:  # noqa: BLE001
+        conn.send(("error", traceback.format_exc()))
+        return
+    while True:
+        try:
+            msg = conn.recv()
+        except (EOFError, OSError):
+            return
+        if msg is None:
+            return
+        method, args = msg
+        try:
+            conn.send(("ok", getattr(host, method)(*args)))
+        except EpisodeLost as e:
+            conn.send(("lost", str(e)))
+        except Exception:  # noqa: BLE001
+            conn.send(("error", traceback.format_exc()))
+
+
+@dataclass
+class _Slot:
+    index: int
+    proc: Optional[mp.Process] = None
+    conn: Any = None
+    busy: bool = False
+    starts: int = 0
+    ever_ready: bool = False
+    episode: Optional[str] = None
+
+
+class StartFailure(RuntimeError):
+    pass
+
+
+class Server:
+    """Supervises ``num_processes`` environment subprocesses of one family."""
+
+    def __init__(self, env_path: str, mode: str = "stateless", num_processes: int = 2, call_timeout_s: float = 30.0,
+                 start_timeout_s: float = 60.0, env_kwargs: Optional[dict] = None, name: str = "server"):
+        self.env_path, self.mode, self.name = env_path, mode, name
+        self.call_timeout_s, self.start_timeout_s = call_timeout_s, start_timeout_s
+        self.env_kwargs = env_kwargs or {}
+        self.ctx = mp.get_context("spawn")
+        self.lock = threading.Condition()
+        self.slots = [_Slot(i) for i in range(num_processes)]
+        self.failed: Optional[str] = None
+        self.restarts = 0
+        self.closed = False
+        for s in self.slots:
+            self._start(s)
+        self.watchdog = threading.Thread(target=self._watch, daemon=True, name=f"{name}-watchdog")
+        self.watchdog.start()
+
+    # -- process lifecycle --------------------------------------------------------------------------------------------
+    def _start(self, s: _Slot) -> None:
+        parent, child = self.ctx.Pipe()
+        s.proc = self.ctx.Process(target=_worker, args=(child, self.env_path, self.mode, self.env_kwargs), daemon=True)
+        s.proc.start()
+        child.close()
+        s.conn, s.starts = parent, s.starts + 1
+        ok = parent.poll(self.start_timeout_s)
+        status = parent.recv() if ok else ("error", "start timed out")
+        if status[0] != "ready":
+            self._kill(s)
+            if not s.ever_ready and s.starts >= MAX_FIRST_START_FAILURES:
+                self.failed = f"{self.name}: process {s.index} failed its first start {s.starts} times: {status[1]}"
+                raise StartFailure(self.failed)
+            return self._start(s)
+        s.ever_ready = True
+
+    def _kill(self, s: _Slot) -> None:
+        try:
+            if s.conn is not None:
+                s.conn.close()
+        except OSError:
+            pass
+        if s.proc is not None and s.proc.is_alive():
+            s.proc.kill()
+            s.proc.join(5)
+        s.proc, s.conn, s.episode = None, None, None
+
+    def _watch(self) -> None:
+        while not self.closed:
+            time.sleep(0.2)
+            with self.lock:
+                for s in self.slots:
+                    if not s.busy and (s.proc is None or not s.proc.is_alive()) and not self.closed and self.failed is None:
+                        try:
+                            self._kill(s)
+                            self._start(s)
+                            self.restarts += 1
+                        except StartFailure:
+                            pass
+                self.lock.notify_all()
+
+    # -- calls --------------------------------------------------------------------------------------------------------
+    def _call(self, s: _Slot, method: str, args: tuple, timeout_s: Optional[float] = None):
+        try:
+            s.conn.send((method, args))
+            if not s.conn.poll(timeout_s or self.call_timeout_s):
+                raise TimeoutError(f"{self.name}: {method} exceeded {timeout_s or self.call_timeout_s}s")
+            status, payload = s.conn.recv()
+        except (TimeoutError, EOFError, OSError, BrokenPipeError) as e:
+            with self.lock:
+                self._kill(s)  # the watchdog starts a fresh process
+            raise EpisodeLost(str(e)) from e
+        if status == "ok":
+            return payload
+        if status == "lost":
+            raise EpisodeLost(payload)
+        raise RuntimeError(f"{self.name}: environment raised\n{payload}")
+
+    def acquire(self, episode: Optional[str] = None, timeout_s: float = 60.0) -> _Slot:
+        deadline = time.time() + timeout_s
+        with self.lock:
+            while True:
+                if self.failed:
+                    raise StartFailure(self.failed)
+                for s in self.slots:
+                    if not s.busy and s.proc is not None and s.proc.is_alive():
+                        s.busy, s.episode = True, episode
+                        return s
+                if not self.lock.wait(max(0.0, min(0.5, deadline - time.time()))) and time.time() > deadline:
+                    raise TimeoutError(f"{self.name}: no free environment process")
+
+    def release(self, s: _Slot) -> None:
+        with self.lock:
+            s.busy, s.episode = False, None
+            self.lock.notify_all()
+
+    def rollout(self, args: dict, actions: list[dict]) -> dict:
+        """Stateless call, retried once on another process when the first one is lost."""
+        last: Optional[Exception] = None
+        for _ in range(2):
+            s = self.acquire()
+            try:
+                return self._call(s, "rollout", (args, actions))
+            except EpisodeLost as e:
+                last = e
+            finally:
+                self.release(s)
+        raise EpisodeLost(f"{self.name}: stateless call lost twice: {last}")
+
+    def close(self) -> None:
+        self.closed = True
+        with self.lock:
+            for s in self.slots:
+                try:
+                    if s.conn is not None:
+                        s.conn.send(None)
+                except OSError:
+                    pass
+                self._kill(s)
+
+
+class ServerPool:
+    """Servers per environment family; episodes borrow a process through it."""
+
+    def __init__(self) -> None:
+        self.servers: dict[str, Server] = {}
+
+    def start(self, family: str, env_path: str, mode: str = "stateless", **kwargs) -> Server:
+        if family not in self.servers:
+            self.servers[family] = Server(env_path, mode, name=family, **kwargs)
+        return self.servers[family]
+
+    def get(self, family: str) -> Server:
+        return self.servers[family]
+
+    def capacity(self, family: str) -> int:
+        return len(self.servers[family].slots)
+
+    def close(self) -> None:
+        for s in self.servers.values():
+            s.close()
+        self.servers.clear()
