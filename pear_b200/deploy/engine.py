@@ -32,6 +32,7 @@ class _Params(ctypes.Structure):
         ("seed", ctypes.c_uint32), ("temperature", ctypes.c_float), ("vocab", ctypes.c_int32),
         ("barrier_base", ctypes.c_uint32), ("pad", ctypes.c_int32), ("ctrl", ctypes.c_void_p),
         ("trace", ctypes.c_void_p), ("trace_ctas", ctypes.c_int32), ("trace_cap", ctypes.c_int32),
+        ("l2_ahead", ctypes.c_int32), ("pad2", ctypes.c_int32),
     ]
 
 
@@ -95,6 +96,7 @@ class MegakernelEngine:
     # (weight ring stages, rows of the activation operand) per program: decode steps have <= 4 rows (4 FP4 terms per row in
     # a 16-row operand); prefill blocks have 8 rows (4 terms in a 32-row operand and a shorter ring)
     LAUNCH_SHAPE = {"decode": (8, 16), "prefill": (5, 32)}
+    L2_AHEAD = 0  # weight stages per CTA requested into L2 beyond the ring (148 x 16 x 18 KB = 44 MB of the 126 MB L2)
     CHUNK = 1024  # vocab entries per sampler partial
 
     def __init__(self, cfg: HybridConfig, draft_cfg: Optional[HybridConfig], weights, device="cuda", max_len: int = 8192,
@@ -114,6 +116,7 @@ class MegakernelEngine:
         self._build(weights)
         self.launches = 0
         self._use_ctrl = True
+        self.l2_ahead = int(os.environ.get("PEAR_MK_L2_AHEAD", self.L2_AHEAD))
         self._trace, self._trace_ctas, self._trace_cap = None, 0, 0
         self.barrier_base = 0
         self.reset()
@@ -474,7 +477,7 @@ class MegakernelEngine:
             instrs=instrs.data_ptr(), descs=self.descs_dev.data_ptr(), rec=self.rec.data_ptr(), out_ring=self.out_ring.data_ptr(),
             barrier=self.barrier.data_ptr(), status=self.status.data_ptr(), max_instrs=max_len, ring=self.RING,
             step_parity=self.step & 1, seed=self.seed, temperature=self.temperature, vocab=self.cfg.vocab_size,
-            barrier_base=self.barrier_base & 0xFFFFFFFF, pad=int(os.environ.get("PEAR_MK_DEBUG", "0")),
+            barrier_base=self.barrier_base & 0xFFFFFFFF, pad=int(os.environ.get("PEAR_MK_DEBUG", "0")), l2_ahead=self.l2_ahead,
             ctrl=self.ctrl_dev[self.step % self.RING].data_ptr() if self._use_ctrl else 0,
             trace=self._trace.data_ptr() if self._trace is not None else 0, trace_ctas=self._trace_ctas, trace_cap=self._trace_cap)
         ns, nb = self.LAUNCH_SHAPE[program]
@@ -488,12 +491,14 @@ class MegakernelEngine:
     # -- in-kernel tracing ------------------------------------------------------------------------------------------------
     def enable_trace(self, ctas: int = 2, cap: int = 8192) -> None:
         """Timeline of the next launches: thread 0 of the first ``ctas`` CTAs records (mark, instruction, globaltimer)."""
-        self._trace = torch.zeros(ctas * cap * 2, dtype=torch.int64, device=self.device)
+        self._trace = torch.zeros(3 * ctas * cap * 2, dtype=torch.int64, device=self.device)
         self._trace_ctas, self._trace_cap = ctas, cap
 
-    def read_trace(self, program: str = "decode") -> list[list[tuple[int, int, int, int]]]:
-        """Per traced CTA: (mark id, instruction index, opcode, nanoseconds since the CTA's first record)."""
-        t = self._trace.cpu().numpy().reshape(self._trace_ctas, self._trace_cap, 2)
+    def read_trace(self, program: str = "decode", issuer: int = 0, clear: bool = True) -> list[list[tuple[int, int, int, int]]]:
+        """Per traced CTA: (mark id, instruction index, opcode, nanoseconds since the earliest record of any CTA)."""
+        full = self._trace.cpu().numpy().reshape(self._trace_ctas, 3, self._trace_cap, 2)
+        t0 = min(int(full[c, w, 1, 1]) for c in range(self._trace_ctas) for w in range(3) if int(full[c, w, 0, 0]) > 0)
+        t = full[:, int(issuer)]
         instrs = self._prog_dev[program][0].cpu().numpy().reshape(self.num_ctas, -1, 8)
         out = []
         for c in range(self._trace_ctas):
@@ -503,9 +508,10 @@ class MegakernelEngine:
                 word, ts = int(t[c, i, 0]), int(t[c, i, 1])
                 ip = word & 0xFFFFFFFF
                 op = int(instrs[c, ip, 0]) if ip < instrs.shape[1] else -1
-                recs.append((word >> 32, ip, op, ts - int(t[c, 1, 1])))
+                recs.append((word >> 32, ip, op, ts - t0))
             out.append(recs)
-        self._trace.zero_()
+        if clear:
+            self._trace.zero_()
         return out
 
     def prefill(self) -> None:

@@ -115,6 +115,39 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
   return false;
 }
 
+// Non-suspending variant for the single threads on a pipeline's critical path (weight producer, MMA issuer): test_wait
+// returns at once, so the thread reacts to a completed phase within a few cycles instead of after try_wait's
+// suspension slice.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_spin_bounded(uint64_t* bar, uint32_t parity, int* status) {
+  for (uint32_t i = 0; i < (1u << 26); ++i) {
+    if (mbar_test_wait(bar, parity)) return true;
+    if (status && (i & 65535u) == 65535u && *(volatile int*)status != 0) return false;  // someone else gave up
+  }
+  set_status(status, PEAR_ERR_MBAR_TIMEOUT);
+  return false;
+}
+
+// Same wait with a sleep between polls: for threads whose wake-up latency does not matter but whose polling would
+// compete with the tensor core's and the copy engine's own shared-memory traffic.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, int* status, unsigned ns = 100) {
+  for (uint32_t i = 0; i < kMbarPolls; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    __nanosleep(ns);
+    if (status && (i & 1023u) == 1023u && *(volatile int*)status != 0) return false;
+  }
+  set_status(status, PEAR_ERR_MBAR_TIMEOUT);
+  return false;
+}
+
 // ------------------------------------------------------------------------------------------------ bulk copies (TMA)
 // 1-D bulk copy global -> shared, completion counted on an mbarrier. Both addresses 16-byte aligned, bytes % 16 == 0.
 __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {

@@ -72,8 +72,10 @@ __device__ __forceinline__ int step_rows(const Ctx& c, const Desc& d) {
 
 // Timeline record (thread 0 of the traced CTAs only): mark ids are small integers documented beside their call sites.
 __device__ __forceinline__ void trace_mark(const Ctx& c, int id) {
-  if (c.p->trace == nullptr || threadIdx.x != 0 || (int)blockIdx.x >= c.p->trace_ctas) return;
-  unsigned long long* base = c.p->trace + (size_t)blockIdx.x * c.p->trace_cap * 2;
+  // three timelines per traced CTA: thread 0, the MMA-issuing thread, the weight producer thread
+  const int who = threadIdx.x == 0 ? 0 : (threadIdx.x == 4 * 32 ? 1 : (threadIdx.x == kConsumerThreads ? 2 : -1));
+  if (c.p->trace == nullptr || who < 0 || (int)blockIdx.x >= c.p->trace_ctas) return;
+  unsigned long long* base = c.p->trace + ((size_t)blockIdx.x * 3 + who) * c.p->trace_cap * 2;
   const unsigned long long n = base[0];
   if ((int)n + 1 >= c.p->trace_cap) return;
   unsigned long long t;
@@ -131,7 +133,8 @@ __device__ __noinline__ void op_gemv(Ctx& c, const Instr& ins) {
   trace_mark(c, 10);  // gemv: entered
   if (ins.d & 1) {
     // every MMA that reads the old B operand has completed once the previous segment's accumulator is full
-    if (c.seg > 0) mbar_wait_bounded(&c.sm->acc_full[(c.seg - 1) & 1], (uint32_t)((c.seg - 1) >> 1) & 1u, c.p->status);
+    // (one polling thread per wait: hundreds of threads polling an mbarrier slow the tensor core's own operand reads)
+    if (c.seg > 0 && tid == 0) mbar_wait_bounded(&c.sm->acc_full[(c.seg - 1) & 1], (uint32_t)((c.seg - 1) >> 1) & 1u, c.p->status);
     consumer_sync();
     trace_mark(c, 11);  // gemv: previous MMAs drained, operand load starts
     // the operand images of this op were built by OP_QUANT in the previous phase: pull this segment's K range
@@ -145,7 +148,7 @@ __device__ __noinline__ void op_gemv(Ctx& c, const Instr& ins) {
       bulk_load_1d(B, (const uint8_t*)d.p5 + (size_t)(k0 >> 5) * chunk_bytes, b_bytes, &c.sm->bload);
       bulk_load_1d(SFB, (const uint8_t*)d.p6 + (size_t)(k0 >> 6) * nb * 16, sf_bytes, &c.sm->bload);
     }
-    if (!(dbg & 1)) mbar_wait_bounded(&c.sm->bload, (uint32_t)c.nload & 1u, c.p->status);
+    if (tid == 0 && !(dbg & 1)) mbar_wait_bounded(&c.sm->bload, (uint32_t)c.nload & 1u, c.p->status);
     ++c.nload;
     if (tid < 8) {
       // epilogue factor per row: undo the pre-gain, apply the deferred RMS of PRO_NORM
@@ -158,42 +161,84 @@ __device__ __noinline__ void op_gemv(Ctx& c, const Instr& ins) {
     if (issuer && !(dbg & 2)) {
       const int nmma = (whole ? d.i1 : nks) * 4;
       tcgen05_fence_after();
-      for (int m = 0; m < nmma; ++m)
-        tmem_cp_32x128b_warpx4(c.tmem + kSfbCol + m * 4, umma_desc_interleaved(smem_u32(SFB + m * nb * 16), 128, 128));
+      // descriptors differ only in their 14-bit address field: one add per instruction (the issuing thread's own
+      // instruction stream is what bounds the issue rate, so nothing is rebuilt inside these loops)
+      const uint64_t sf_desc = umma_desc_interleaved(smem_u32(SFB), 128, 128);
+      const uint32_t sf_step = (uint32_t)(nb * 16) >> 4;
+      uint32_t lo = (uint32_t)sf_desc, taddr = c.tmem + kSfbCol;
+      const uint32_t hi = (uint32_t)(sf_desc >> 32);
+      for (int m = 0; m < nmma; ++m, lo += sf_step, taddr += 4) tmem_cp_32x128b_warpx4(taddr, ((uint64_t)hi << 32) | lo);
+      trace_mark(c, 20);  // issuer: operand scale factors queued
     }
   }
   if (issuer) {
-    bool ok = mbar_wait_bounded(&c.sm->acc_empty[ab], use ^ 1u, c.p->status);
+    bool ok = mbar_spin_bounded(&c.sm->acc_empty[ab], use ^ 1u, c.p->status);
+    trace_mark(c, 21);  // issuer: accumulator free
     tcgen05_fence_after();
     const uint32_t idesc = umma_idesc_nvfp4(128, nb);
     const uint32_t chunk_b = (uint32_t)(nb >> 3) * 128u;
-    const uint32_t b_addr = smem_u32(B);
-    for (int s = 0; s < nks; ++s) {
-      if (ok) ok = mbar_wait_bounded(&c.sm->full[c.stage], c.phase, c.p->status);
-      if (ok && !(dbg & 2)) {
-        tcgen05_fence_after();
-        const uint32_t a_addr = smem_u32(c.ring + (size_t)c.stage * kStageBytes);
-        const int kst = whole ? ks0 + s : s;  // stage index inside the B operand
+    const uint64_t a_desc0 = umma_desc_interleaved(smem_u32(c.ring), 2048, 128);
+    const uint64_t sfa_desc0 = umma_desc_interleaved(smem_u32(c.ring) + kStageCodeBytes, 128, 128);
+    const uint64_t b_desc0 = umma_desc_interleaved(smem_u32(B), chunk_b, 128);
+    const uint32_t a_hi = (uint32_t)(a_desc0 >> 32), sfa_hi = (uint32_t)(sfa_desc0 >> 32), b_hi = (uint32_t)(b_desc0 >> 32);
+    const uint32_t b_mma = (2u * chunk_b) >> 4;  // address-field step of the B operand per MMA (64 K elements)
+    const uint32_t acc_addr = c.tmem + kAccCol + ab * 32;
+    const int kst0 = whole ? ks0 : 0;            // stage index inside the B operand
+    uint32_t b_lo = (uint32_t)b_desc0 + (uint32_t)kst0 * 4u * b_mma;
+    uint32_t sfb_addr = c.tmem + kSfbCol + (uint32_t)kst0 * 16u;
+    uint32_t accumulate = 0;
+    // Two stages per iteration: what bounds this loop is the issuing thread's own chain of latencies (barrier poll,
+    // issue, commit), so both polls go out back to back and eight MMAs follow; each scale-factor copy sits directly
+    // in front of its MMA, where the tensor pipe overlaps it with the previous MMA.
+    constexpr int kGroup = 4;
+    for (int s = 0; s < nks; s += kGroup) {
+      const int n = min(kGroup, nks - s);
+      int st[kGroup];
+      uint32_t ph[kGroup];
+      bool ready[kGroup];
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-          tmem_cp_32x128b_warpx4(c.tmem + kSfaCol + c.stage * 16 + j * 4,
-                                 umma_desc_interleaved(a_addr + kStageCodeBytes + j * 512, 128, 128));
+      for (int g = 0; g < kGroup; ++g) {
+        int x = c.stage + g;
+        ph[g] = c.phase;
+        if (x >= c.ns) { x -= c.ns; ph[g] ^= 1u; }
+        st[g] = x;
+        ready[g] = g >= n || mbar_test_wait(&c.sm->full[x], ph[g]);
+      }
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const uint64_t da = umma_desc_interleaved(a_addr + j * 4096, 2048, 128);
-          const uint64_t db = umma_desc_interleaved(b_addr + (uint32_t)(kst * 4 + j) * 2u * chunk_b, chunk_b, 128);
-          umma_nvfp4(c.tmem + kAccCol + ab * 32, da, db, idesc, (s | j) != 0 ? 1u : 0u, c.tmem + kSfaCol + c.stage * 16 + j * 4,
-                     c.tmem + kSfbCol + (kst * 4 + j) * 4);
+      for (int g = 0; g < kGroup; ++g)
+        if (ok && !ready[g]) ok = mbar_spin_bounded(&c.sm->full[st[g]], ph[g], c.p->status);
+      tcgen05_fence_after();
+#pragma unroll
+      for (int g = 0; g < kGroup; ++g) {
+        if (g < n) {
+          if (ok && !(dbg & 2)) {
+            const uint32_t a_lo = (uint32_t)a_desc0 + (uint32_t)st[g] * (kStageBytes >> 4);
+            const uint32_t sfa_lo = (uint32_t)sfa_desc0 + (uint32_t)st[g] * (kStageBytes >> 4);
+            const uint32_t sfa_addr = c.tmem + kSfaCol + st[g] * 16;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              tmem_cp_32x128b_warpx4(sfa_addr + j * 4, ((uint64_t)sfa_hi << 32) | (sfa_lo + j * 32));
+              umma_nvfp4(acc_addr, ((uint64_t)a_hi << 32) | (a_lo + j * 256), ((uint64_t)b_hi << 32) | (b_lo + j * b_mma), idesc,
+                         accumulate, sfa_addr + j * 4, sfb_addr + j * 4);
+              accumulate = 1;
+            }
+          }
+          b_lo += 4u * b_mma;
+          sfb_addr += 16;
+          tcgen05_commit(&c.sm->empty[st[g]]);  // frees the ring slot once these MMAs (and copies) have read it
         }
       }
-      tcgen05_commit(&c.sm->empty[c.stage]);  // frees the ring slot once these MMAs (and copies) have read it
-      if (++c.stage == c.ns) { c.stage = 0; c.phase ^= 1; }
+      c.stage += n;
+      if (c.stage >= c.ns) { c.stage -= c.ns; c.phase ^= 1; }
     }
     tcgen05_commit(&c.sm->acc_full[ab]);
+    trace_mark(c, 22);  // issuer: segment issued
   }
   if (warp < 4) {
     // ---- epilogue: lane quarter `warp`; row = tile * 128 + warp * 32 + lane; column n = term * tpad + token
-    const bool ok = mbar_wait_bounded(&c.sm->acc_full[ab], use, c.p->status);
+    bool ok = true;
+    if (lane == 0) ok = mbar_wait_relaxed(&c.sm->acc_full[ab], use, c.p->status);
+    ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
     trace_mark(c, 13);  // gemv: accumulator full
     tcgen05_fence_after();
     float v[8];  // per token: sum over terms of D[term * tpad + token] * 4^-term
@@ -326,6 +371,32 @@ __global__ void __launch_bounds__(kThreads, 1) mk_main(const __grid_constant__ P
     if (tid == kConsumerThreads) {
       int stage = 0, phase = 0;
       bool ok = true;
+      // L2 look-ahead: a second cursor walks the same instruction list `l2_ahead` stages in front of the ring and asks
+      // the TMA engine to pull those stages into L2, so HBM keeps streaming through phases in which the ring is full
+      // (grid barriers, recurrent/attention ops); the ring then refills from L2 faster than HBM could deliver.
+      // (requested in chunks of up to 8 stages per bulk-prefetch instruction: every bulk instruction costs this
+      // thread a few hundred cycles whatever its size.)
+      int pf_ip = 0, pf_s = 0, pf_left = 0, pf_issued = 0, main_issued = 0;
+      const uint8_t* pf_src = nullptr;
+      bool pf_end = p.l2_ahead <= 0;
+      auto pf_step = [&]() {
+        while (!pf_end && pf_issued < main_issued + p.l2_ahead) {
+          while (!pf_end && pf_s >= pf_left) {
+            if (pf_ip >= p.max_instrs) { pf_end = true; break; }
+            const Instr pi = list[pf_ip++];
+            if (pi.op == OP_END) { pf_end = true; break; }
+            if (pi.op != OP_GEMV) continue;
+            const Desc& pd = p.descs[pi.desc];
+            pf_src = (const uint8_t*)pd.p0 + ((size_t)pi.a * pd.i1 + pi.b) * kStageBytes;
+            pf_s = 0; pf_left = pi.c;
+          }
+          if (pf_end) return;
+          const int n = min(8, pf_left - pf_s);
+          asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(pf_src + (size_t)pf_s * kStageBytes), "r"(n * kStageBytes) : "memory");
+          pf_s += n; pf_issued += n;
+        }
+      };
+      pf_step();
       Instr next = list[0];
       for (int ip = 0; ip < p.max_instrs && ok; ++ip) {
         const Instr ins = next;
@@ -334,13 +405,19 @@ __global__ void __launch_bounds__(kThreads, 1) mk_main(const __grid_constant__ P
         if (ins.op != OP_GEMV) continue;
         const Desc& d = p.descs[ins.desc];
         const uint8_t* src = (const uint8_t*)d.p0 + ((size_t)ins.a * d.i1 + ins.b) * kStageBytes;
+        Ctx tc; tc.p = &p; tc.ip = ip;
+        trace_mark(tc, 40);  // producer: first stage of this instruction about to be requested
         for (int s = 0; s < ins.c; ++s) {
-          ok = mbar_wait_bounded(&sm->empty[stage], phase ^ 1, p.status);
+          if (s == 8) trace_mark(tc, 41);  // producer: 8 stages requested
+          ok = mbar_spin_bounded(&sm->empty[stage], phase ^ 1, p.status);
           if (!ok) break;
           mbar_expect_tx(&sm->full[stage], kStageBytes);
           bulk_load_1d(ring + (size_t)stage * kStageBytes, src + (size_t)s * kStageBytes, kStageBytes, &sm->full[stage]);
           if (++stage == ns) { stage = 0; phase ^= 1; }
+          ++main_issued;
+          if ((main_issued & 3) == 0) pf_step();
         }
+        trace_mark(tc, 42);  // producer: all stages of this instruction requested
       }
     }
   } else {

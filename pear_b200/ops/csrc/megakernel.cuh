@@ -127,6 +127,8 @@ struct Params {
   unsigned long long* trace;
   int32_t trace_ctas;
   int32_t trace_cap;
+  int32_t l2_ahead;        // weight stages the producer keeps requested into L2 beyond the shared-memory ring (0: off)
+  int32_t pad2;
 };
 
 }  // namespace mk
