@@ -33,6 +33,7 @@ class _Params(ctypes.Structure):
         ("barrier_base", ctypes.c_uint32), ("pad", ctypes.c_int32), ("ctrl", ctypes.c_void_p),
         ("trace", ctypes.c_void_p), ("trace_ctas", ctypes.c_int32), ("trace_cap", ctypes.c_int32),
         ("l2_ahead", ctypes.c_int32), ("pad2", ctypes.c_int32),
+        ("tile_cnt", ctypes.c_void_p), ("tile_expect", ctypes.c_void_p),
     ]
 
 
@@ -177,8 +178,14 @@ class MegakernelEngine:
         # activation-operand images built by the QUANT phases (largest K = the FFN width, 32-row operand) and the per-GEMV
         # row statistics (sum of squares for the deferred RMS), zeroed at the start of every step
         kmax = max(I, 2 * H, VD, cfg.q_size, *((dc.intermediate_size, dc.q_size) if dc is not None else ()))
-        self.b_image = self._zeros((kmax // 32) * 4 * 128 + 1024, dtype=torch.uint8)
-        self.sfb_image = self._zeros((kmax // 64) * 32 * 16 + 1024, dtype=torch.uint8)
+        # (two of each: the finishers of GEMV n build GEMV n + 1's operand while other CTAs still read GEMV n's)
+        self._b_bytes, self._sfb_bytes = (kmax // 32) * 4 * 128 + 1024, (kmax // 64) * 32 * 16 + 1024
+        self.b_image = self._zeros(2 * self._b_bytes, dtype=torch.uint8)
+        self.sfb_image = self._zeros(2 * self._sfb_bytes, dtype=torch.uint8)
+        self._gemv_count = 0
+        self.link_gemvs = os.environ.get("PEAR_MK_LINK", "0") != "0"  # finishers build the next operand (measured: no faster)
+        self._links: dict[int, int] = {}  # producer GEMV descriptor -> first tile counter
+        self._num_counters = 0
         self.gemv_stats = self._zeros(4096 * 8)
         progs = {"decode": S.Program(self.num_ctas), "prefill": S.Program(self.num_ctas)}
         self.programs = progs
@@ -198,8 +205,10 @@ class MegakernelEngine:
 
         def gemv_desc(packed, gs, K, rows, inp, in_stride, out, out_stride, pro, epi, flags=0, p2=0, p3=0, i8=0, i9=0,
                       eps=cfg.rms_eps):
-            return desc(p0=P(packed), p1=inp, p2=p2, p3=p3, p4=out, p5=P(self.b_image), p6=P(self.sfb_image),
-                        p7=P(self.gemv_stats, 8 * len(self._descs)), i0=K, i1=K // S.STAGE_K, i2=rows, i3=in_stride,
+            img = self._gemv_count & 1
+            self._gemv_count += 1
+            return desc(p0=P(packed), p1=inp, p2=p2, p3=p3, p4=out, p5=P(self.b_image, img * self._b_bytes),
+                        p6=P(self.sfb_image, img * self._sfb_bytes), p7=P(self.gemv_stats, 8 * len(self._descs)), i0=K, i1=K // S.STAGE_K, i2=rows, i3=in_stride,
                         i4=out_stride, i5=pro, i6=epi, i7=flags, i8=i8, i9=i9, f0=1.0 / gs, f1=eps)
 
         def zero_desc(t: torch.Tensor, flags=0, i8=0) -> int:
@@ -215,10 +224,29 @@ class MegakernelEngine:
         z_stats = zero_desc(self.gemv_stats)
         both(lambda p: (p.ranged(S.OP_EMBED, d_embed, H, granule=256), add_zero(p, z_stats, 4096 * 8)))
 
-        def G(p: S.Program, d: int, rows: int, K: int, aligned: bool = False) -> None:
-            """A GEMV op: the phase that builds its activation operand, a grid barrier, then the streamed GEMV."""
-            p.quant(d, K)
-            p.barrier()
+        def G(p: S.Program, d: int, rows: int, K: int, aligned: bool = False, producer: Optional[int] = None) -> None:
+            """A GEMV op. Its activation operand is built either by a phase of its own (followed by a grid barrier) or,
+            when the input is the output of GEMV ``producer`` (the previous GEMV op), by that op's finishers: the warps
+            that deliver the last stream-K contribution to a row tile quantise it in place of a separate phase."""
+            if producer is None or not self.link_gemvs:
+                p.quant(d, K)
+                p.barrier()
+            else:
+                units = K // 128
+                if producer not in self._links:
+                    self._links[producer] = self._num_counters
+                    self._num_counters += units
+                    assert self._descs[d]["p5"] != self._descs[producer]["p5"], "linked GEMVs must use different images"
+                    self._descs[producer]["pad"] = (d + 1, self._links[producer])
+                base = self._links[producer]
+                counts = [0] * units
+                for l in p.lists:
+                    for ins in l:
+                        if ins[0] == S.OP_GEMV and ins[1] == producer:
+                            counts[ins[2] % units] += 1
+                assert min(counts) > 0
+                p.expect.extend([0] * (base + units - len(p.expect)))
+                p.expect[base:base + units] = counts
             p.gemv(d, rows, K, aligned)
 
         # drafter buffers (zeroed during the target's first phase)
@@ -277,12 +305,12 @@ class MegakernelEngine:
             d_out = gemv_desc(pk2, gs2, icfg.q_size, Hh, P(aout_buf), icfg.q_size, P(r_buf), Hh, S.PRO_PLAIN, S.EPI_RED, flags)
             return d_in, rows, d_at, d_out
 
-        def emit_attn(p: S.Program, icfg, d_in, rows, d_at, d_out, z_qkv_desc, qkv_elems, pre=None):
+        def emit_attn(p: S.Program, icfg, d_in, rows, d_at, d_out, z_qkv_desc, qkv_elems, pre=None, producer=None):
             Hq, Hkv = icfg.num_attention_heads, icfg.num_kv_heads
             nsplit = self.attn_splits or max(1, self.num_ctas // Hkv)
             if pre is not None:
                 pre(p)
-            G(p, d_in, rows, icfg.hidden_size)
+            G(p, d_in, rows, icfg.hidden_size, producer=producer)
             p.barrier()
             p.spread(S.OP_ATTN, d_at, [(h, s, nsplit) for s in range(nsplit) for h in range(Hkv)])
             p.barrier()
@@ -294,12 +322,13 @@ class MegakernelEngine:
             add_zero(p, z_qkv_desc, qkv_elems)
             p.barrier()
 
-        def emit_mlp(p: S.Program, d_gu, d_dn, gu_rows, ii, hh):
-            G(p, d_gu, gu_rows, hh)
+        def emit_mlp(p: S.Program, d_out, d_gu, d_dn, gu_rows, ii, hh):
+            G(p, d_gu, gu_rows, hh, producer=d_out)
             p.barrier()
-            G(p, d_dn, hh, ii)
+            G(p, d_dn, hh, ii, producer=d_gu)
             p.barrier()
 
+        prev_dn = None  # the previous layer's down projection: its finishers build this layer's first operand
         for li, lt in enumerate(cfg.layer_types):
             prefix = f"model.layers.{li}"
             if lt == "linear_attention":
@@ -338,8 +367,8 @@ class MegakernelEngine:
                 d_gu, d_dn, gu_rows, ii = mlp_block(prefix, self.r, self.gu, z_gu, cfg, 0, lt)
 
                 def emit(p: S.Program, d_in=d_in, d_core=d_core, d_out=d_out, z_rec=z_rec, items=items, d_gu=d_gu, d_dn=d_dn,
-                         gu_rows=gu_rows, ii=ii):
-                    G(p, d_in, C + VD + 2 * HV, H)
+                         gu_rows=gu_rows, ii=ii, prev_dn=prev_dn):
+                    G(p, d_in, C + VD + 2 * HV, H, producer=prev_dn)
                     add_zero(p, z_gu, T8 * 2 * I)
                     p.barrier()
                     p.spread(S.OP_GDN, d_core, items)
@@ -347,7 +376,7 @@ class MegakernelEngine:
                     G(p, d_out, H, VD)
                     add_zero(p, z_rec, T8 * self.rec_stride)
                     p.barrier()
-                    emit_mlp(p, d_gu, d_dn, gu_rows, ii, H)
+                    emit_mlp(p, d_out, d_gu, d_dn, gu_rows, ii, H)
 
                 both(emit)
             else:
@@ -355,12 +384,14 @@ class MegakernelEngine:
                                                      self.attn_part, 0)
                 d_gu, d_dn, gu_rows, ii = mlp_block(prefix, self.r, self.gu, z_gu, cfg, 0, lt)
 
-                def emit(p: S.Program, d_in=d_in, rows=rows, d_at=d_at, d_out=d_out, d_gu=d_gu, d_dn=d_dn, gu_rows=gu_rows, ii=ii):
+                def emit(p: S.Program, d_in=d_in, rows=rows, d_at=d_at, d_out=d_out, d_gu=d_gu, d_dn=d_dn, gu_rows=gu_rows, ii=ii,
+                         prev_dn=prev_dn):
                     emit_attn(p, cfg, d_in, rows, d_at, d_out, z_qkv, T8 * self.qkv_stride,
-                              pre=lambda q: add_zero(q, z_gu, T8 * 2 * I))
-                    emit_mlp(p, d_gu, d_dn, gu_rows, ii, H)
+                              pre=lambda q: add_zero(q, z_gu, T8 * 2 * I), producer=prev_dn)
+                    emit_mlp(p, d_out, d_gu, d_dn, gu_rows, ii, H)
 
                 both(emit)
+            prev_dn = d_dn
 
         # ---- head + sampler (decode) / bookkeeping (prefill)
         fin_w = self._dev(W.vector("model.norm.weight", H))
@@ -372,7 +403,7 @@ class MegakernelEngine:
         d_book = desc(p1=P(self.prompt_dev), i4=self.n_draft, i5=0, i6=1, i9=self.mask_token_id)
         self._d_samp, self._d_book = d_samp, d_book
         dp, pp = progs["decode"], progs["prefill"]
-        G(dp, d_head, V, H, aligned=True)
+        G(dp, d_head, V, H, aligned=True, producer=prev_dn)
         dp.barrier()
         dp.ranged(S.OP_SAMPLE_PART, d_samp, nchunks)
         dp.barrier()
@@ -394,6 +425,7 @@ class MegakernelEngine:
             pp.spread(S.OP_DRAFT_IN, d_din_pre, [(j,) for j in range(T8)])
             both(lambda p: p.barrier())
             both(lambda p: (G(p, d_fc, H, 2 * H), p.barrier()))
+            prev_dn = d_fc
             for li in range(dc.num_layers):
                 prefix = f"draft.layers.{li}"
                 d_in, rows, d_at, d_out = attn_block(prefix, ("draft", li), dc, self.rd, self.dqkv, self.d_qkv_stride,
@@ -402,19 +434,21 @@ class MegakernelEngine:
                 z_dgu2 = zero_desc(self.dgu)
 
                 def emit(p: S.Program, d_in=d_in, rows=rows, d_at=d_at, d_out=d_out, d_gu=d_gu, d_dn=d_dn, gu_rows=gu_rows,
-                         ii=ii, li=li, z_dgu2=z_dgu2):
+                         ii=ii, li=li, z_dgu2=z_dgu2, prev_dn=prev_dn):
                     emit_attn(p, dc, d_in, rows, d_at, d_out, z_dqkv, T8 * self.d_qkv_stride,
-                              pre=(lambda q: add_zero(q, z_dgu2, T8 * 2 * dc.intermediate_size)) if li > 0 else None)
-                    emit_mlp(p, d_gu, d_dn, gu_rows, ii, dc.hidden_size)
+                              pre=(lambda q: add_zero(q, z_dgu2, T8 * 2 * dc.intermediate_size)) if li > 0 else None,
+                              producer=prev_dn)
+                    emit_mlp(p, d_out, d_gu, d_dn, gu_rows, ii, dc.hidden_size)
 
                 both(emit)
+                prev_dn = d_dn
             dfin_w = self._dev(W.vector("draft.norm.weight", H))
             pk, gs = self._lm_head
             d_dhead = gemv_desc(pk, gs, H, V, P(self.rd), H, P(self.dlogits), V, S.PRO_NORM, S.EPI_STORE, S.F_DRAFT_ROWS,
                                 p2=P(dfin_w))
             d_arg = desc(p0=P(self.dlogits), p4=P(self.argmax_part), i0=V, i1=V, i2=self.CHUNK, i3=nchunks, i4=self.n_draft)
             if self.n_draft > 0:
-                G(dp, d_dhead, V, H, aligned=True)
+                G(dp, d_dhead, V, H, aligned=True, producer=prev_dn)
                 dp.barrier()
                 dp.ranged(S.OP_ARGMAX_PART, d_arg, nchunks)
                 dp.barrier()
@@ -427,6 +461,11 @@ class MegakernelEngine:
             instrs, descs, max_len = p.finalize()
             self._prog_dev[name] = (torch.from_numpy(instrs.view(np.int32).reshape(self.num_ctas, max_len * 8).copy()).to(self.device),
                                     max_len, p.stats())
+        self.tile_cnt = torch.zeros(max(1, self._num_counters), dtype=torch.int32, device=self.device)
+        self._expect_dev = {}
+        for name, p in progs.items():
+            e = list(p.expect) + [0] * (max(1, self._num_counters) - len(p.expect))
+            self._expect_dev[name] = torch.tensor(e, dtype=torch.int32, device=self.device)
         self._descs_np = descs
         self.descs_dev = torch.from_numpy(descs.view(np.uint8).reshape(-1).copy()).to(self.device)
         self.smem_bytes = {k: _lib.lib().pear_mk_smem_bytes(*v) for k, v in self.LAUNCH_SHAPE.items()}
@@ -477,7 +516,8 @@ class MegakernelEngine:
             instrs=instrs.data_ptr(), descs=self.descs_dev.data_ptr(), rec=self.rec.data_ptr(), out_ring=self.out_ring.data_ptr(),
             barrier=self.barrier.data_ptr(), status=self.status.data_ptr(), max_instrs=max_len, ring=self.RING,
             step_parity=self.step & 1, seed=self.seed, temperature=self.temperature, vocab=self.cfg.vocab_size,
-            barrier_base=self.barrier_base & 0xFFFFFFFF, pad=int(os.environ.get("PEAR_MK_DEBUG", "0")), l2_ahead=self.l2_ahead,
+            barrier_base=self.barrier_base & 0xFFFFFFFF, pad=int(os.environ.get("PEAR_MK_DEBUG", "0")), l2_ahead=self.l2_ahead, tile_cnt=self.tile_cnt.data_ptr(),
+            tile_expect=self._expect_dev[program].data_ptr(),
             ctrl=self.ctrl_dev[self.step % self.RING].data_ptr() if self._use_ctrl else 0,
             trace=self._trace.data_ptr() if self._trace is not None else 0, trace_ctas=self._trace_ctas, trace_cap=self._trace_cap)
         ns, nb = self.LAUNCH_SHAPE[program]

@@ -44,6 +44,7 @@ class Program:
     descs: list[dict] = field(default_factory=list)
     rotate: int = 0
     gemv_stages: int = 0  # total weight stages streamed per launch (bytes = stages * STAGE_BYTES)
+    expect: list[int] = field(default_factory=list)  # contributions per tile counter of the linked GEMVs
 
     def __post_init__(self) -> None:
         self.lists = [[] for _ in range(self.num_ctas)]

@@ -47,6 +47,7 @@ struct Smem {
   int abort_flag;
   float red[64];
   float gscale[8];   // 1 / g_t: the epilogue's undo of the row pre-scale
+  int fin_unit;      // unit of the next GEMV's operand this CTA's epilogue warps build (-1: none)
 };
 
 struct Ctx {
@@ -158,18 +159,6 @@ __device__ __noinline__ void op_gemv(Ctx& c, const Instr& ins) {
     }
     consumer_sync();
     trace_mark(c, 12);  // gemv: operand in shared memory
-    if (issuer && !(dbg & 2)) {
-      const int nmma = (whole ? d.i1 : nks) * 4;
-      tcgen05_fence_after();
-      // descriptors differ only in their 14-bit address field: one add per instruction (the issuing thread's own
-      // instruction stream is what bounds the issue rate, so nothing is rebuilt inside these loops)
-      const uint64_t sf_desc = umma_desc_interleaved(smem_u32(SFB), 128, 128);
-      const uint32_t sf_step = (uint32_t)(nb * 16) >> 4;
-      uint32_t lo = (uint32_t)sf_desc, taddr = c.tmem + kSfbCol;
-      const uint32_t hi = (uint32_t)(sf_desc >> 32);
-      for (int m = 0; m < nmma; ++m, lo += sf_step, taddr += 4) tmem_cp_32x128b_warpx4(taddr, ((uint64_t)hi << 32) | lo);
-      trace_mark(c, 20);  // issuer: operand scale factors queued
-    }
   }
   if (issuer) {
     bool ok = mbar_spin_bounded(&c.sm->acc_empty[ab], use ^ 1u, c.p->status);
@@ -185,7 +174,12 @@ __device__ __noinline__ void op_gemv(Ctx& c, const Instr& ins) {
     const uint32_t acc_addr = c.tmem + kAccCol + ab * 32;
     const int kst0 = whole ? ks0 : 0;            // stage index inside the B operand
     uint32_t b_lo = (uint32_t)b_desc0 + (uint32_t)kst0 * 4u * b_mma;
-    uint32_t sfb_addr = c.tmem + kSfbCol + (uint32_t)kst0 * 16u;
+    // the operand's scale factors (one 4-column group per MMA) are copied into tensor memory right before the MMA that
+    // reads them, like the weights' own: the tensor pipe overlaps such a copy with the previous MMA, whereas copying
+    // the whole row's groups up front would sit on the critical path of every GEMV op
+    const uint64_t sfb_desc0 = umma_desc_interleaved(smem_u32(SFB), 128, 128);
+    const uint32_t sfb_hi = (uint32_t)(sfb_desc0 >> 32), sfb_mma = (uint32_t)(nb * 16) >> 4;
+    uint32_t sfb_lo = (uint32_t)sfb_desc0 + (uint32_t)kst0 * 4u * sfb_mma;
     uint32_t accumulate = 0;
     // Two stages per iteration: what bounds this loop is the issuing thread's own chain of latencies (barrier poll,
     // issue, commit), so both polls go out back to back and eight MMAs follow; each scale-factor copy sits directly
@@ -214,17 +208,18 @@ __device__ __noinline__ void op_gemv(Ctx& c, const Instr& ins) {
           if (ok && !(dbg & 2)) {
             const uint32_t a_lo = (uint32_t)a_desc0 + (uint32_t)st[g] * (kStageBytes >> 4);
             const uint32_t sfa_lo = (uint32_t)sfa_desc0 + (uint32_t)st[g] * (kStageBytes >> 4);
-            const uint32_t sfa_addr = c.tmem + kSfaCol + st[g] * 16;
+            const uint32_t sfa_addr = c.tmem + kSfaCol + st[g] * 16, sfb_addr = c.tmem + kSfbCol + st[g] * 16;
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               tmem_cp_32x128b_warpx4(sfa_addr + j * 4, ((uint64_t)sfa_hi << 32) | (sfa_lo + j * 32));
+              tmem_cp_32x128b_warpx4(sfb_addr + j * 4, ((uint64_t)sfb_hi << 32) | (sfb_lo + j * sfb_mma));
               umma_nvfp4(acc_addr, ((uint64_t)a_hi << 32) | (a_lo + j * 256), ((uint64_t)b_hi << 32) | (b_lo + j * b_mma), idesc,
                          accumulate, sfa_addr + j * 4, sfb_addr + j * 4);
               accumulate = 1;
             }
           }
           b_lo += 4u * b_mma;
-          sfb_addr += 16;
+          sfb_lo += 4u * sfb_mma;
           tcgen05_commit(&c.sm->empty[st[g]]);  // frees the ring slot once these MMAs (and copies) have read it
         }
       }
@@ -291,6 +286,26 @@ __device__ __noinline__ void op_gemv(Ctx& c, const Instr& ins) {
             else out[(size_t)t * d.i4 + row] = val;
           }
         }
+      }
+    }
+    if (d.pad[0] > 0) {
+      // This GEMV feeds another one: count this contribution to the row tile; the warps that delivered the last one
+      // ("finishers") turn the now complete 128 outputs into one unit of the next GEMV's operand.
+      const Desc& cd = c.p->descs[d.pad[0] - 1];
+      __threadfence();
+      asm volatile("bar.sync 2, 128;" ::: "memory");
+      if (tid == 0) {
+        const int slot = d.pad[1] + tile % (cd.i0 >> 7);
+        const int expect = __ldg(c.p->tile_expect + slot);  // 0: this program does not run the consumer
+        const bool last = expect > 0 && atomicAdd(c.p->tile_cnt + slot, 1) + 1 == expect;
+        if (last) c.p->tile_cnt[slot] = 0;  // nobody touches the counter again before the next step
+        c.sm->fin_unit = last ? tile % (cd.i0 >> 7) : -1;
+      }
+      asm volatile("bar.sync 2, 128;" ::: "memory");
+      const int unit = *(volatile int*)&c.sm->fin_unit;
+      if (unit >= 0) {
+        __threadfence();
+        quant_units(c, cd, unit, 1, 128);
       }
     }
   }

@@ -71,7 +71,8 @@ struct __align__(16) Desc {
   float f1;        // eps
   float f2;
   float f3;
-  int32_t pad[2];
+  int32_t pad[2];  // GEMV: [0] = 1 + descriptor of the GEMV whose operand this op's finishers build (0: none),
+                   //       [1] = first of that link's tile counters
 };
 static_assert(sizeof(Desc) == 128, "Desc is 128 bytes");
 
@@ -129,6 +130,8 @@ struct Params {
   int32_t trace_cap;
   int32_t l2_ahead;        // weight stages the producer keeps requested into L2 beyond the shared-memory ring (0: off)
   int32_t pad2;
+  int32_t* tile_cnt;           // arrival counters of the linked GEMVs' row tiles (zero between steps)
+  const int32_t* tile_expect;  // instructions that contribute to each counter (per program)
 };
 
 }  // namespace mk

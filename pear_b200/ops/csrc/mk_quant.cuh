@@ -85,11 +85,14 @@ __device__ __forceinline__ void pack_pairs(const float4 (&v)[4], float f, __half
   h[6] = __floats2half2_rn(v[2].z * f, v[3].z * f); h[7] = __floats2half2_rn(v[2].w * f, v[3].w * f);
 }
 
+// Two callers: the OP_QUANT phase (inputs produced by a non-GEMV op), and the epilogue warps of a GEMV whose row tile
+// just received its last stream-K contribution ("finishers": a row tile of 128 outputs is exactly one unit of the next
+// GEMV's K, so that GEMV needs no phase of its own for its operand).
 // Instr: a = first unit (128 K elements each), b = unit count; desc = the GEMV descriptor whose operand is built.
 // Desc fields used: p1 input rows, p2 norm weight | z rows, p3 gated-norm weight, p5 B image, p6 SFB image, p7 stats,
 //                   i0 K, i3 input row stride, i5 prologue, i7 flags, i8 parity stride, i9 z row stride, f1 eps.
-__device__ __noinline__ void op_quant(Ctx& c, const Instr& ins) {
-  const Desc& d = c.p->descs[ins.desc];
+// `nthreads` threads (whole warps, numbered from threadIdx 0) build units [first, first + count) of descriptor d's operand.
+__device__ __noinline__ void quant_units(Ctx& c, const Desc& d, int first, int count, int nthreads) {
   const StepRec* rec = c.rec;
   const int T = step_rows(c, d);
   const int tpad = T <= 4 ? 4 : 8, nb = c.nb, terms = min(4, nb / tpad);
@@ -102,10 +105,10 @@ __device__ __noinline__ void op_quant(Ctx& c, const Instr& ins) {
   uint8_t* B = (uint8_t*)d.p5;
   uint8_t* SFB = (uint8_t*)d.p6;
   float* stats = (float*)d.p7;
-  const int items = ins.b * tpad * 8;  // (unit, row, block of the unit): 8 consecutive lanes share (unit, row)
-  for (int idx = tid; idx < ((items + 31) & ~31); idx += kConsumerThreads) {
+  const int items = count * tpad * 8;  // (unit, row, block of the unit): 8 consecutive lanes share (unit, row)
+  for (int idx = tid; idx < ((items + 31) & ~31); idx += nthreads) {
     const bool live = idx < items;
-    const int unit = ins.a + idx / (tpad * 8), row = (idx >> 3) % tpad, blk = unit * 8 + (idx & 7);
+    const int unit = first + idx / (tpad * 8), row = (idx >> 3) % tpad, blk = unit * 8 + (idx & 7);
     const int k = blk * 16;
     const bool valid = live && row < T;
     float4 x[4];
@@ -158,6 +161,10 @@ __device__ __noinline__ void op_quant(Ctx& c, const Instr& ins) {
   // the images are read by bulk copies (async proxy) of other CTAs after the next grid barrier
   asm volatile("fence.proxy.async;" ::: "memory");
   __threadfence();
+}
+
+__device__ __forceinline__ void op_quant(Ctx& c, const Instr& ins) {
+  quant_units(c, c.p->descs[ins.desc], ins.a, ins.b, kConsumerThreads);
 }
 
 }  // namespace mk
