@@ -1,0 +1,178 @@
+"""The agent loop: one episode = one multi-turn conversation between the policy and an environment.
+
+The state machine of upstream ``pear/agent_loop/agent_loop.py:24-242``:
+PENDING -> GENERATING -> PROCESSING_TOOLS -> ... -> TERMINATED, with
+
+* a token budget per EPISODE, not per turn: every generate call may use what is left (``:130``);
+* end reasons ENV / PARSE / BUDGET (``episode.py:9-14``);
+* up to ``max_restarts`` restarts of the whole trajectory when the environment process is lost (``:30, :50-66``);
+* reward = the environment's success flag (``:70``);
+* user turns merged into the running token list with response mask 0 and placeholder top-k heads, so the trainer sees
+  one packed sequence per episode (``_resume_generating`` ``:198-229``);
+* per-turn JSONL logs (``:178-196``).
+
+The finished trajectory is written to the transfer queue under ``<uid>/<session>`` and sealed.
+"""
+
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass
+from typing import Optional
+
+import numpy as np
+import torch
+
+from ..envs.tool import EnvTool, Observation, load_system_prompt
+from ..rollout.engine import FinishReason, SamplingParams
+from ..sim.env import EpisodeLost
+from ..sim.server import ServerPool
+from ..utils.files import append_jsonl
+from ..utils.tokenizer import ByteTokenizer
+from .episode import EndReason, Episode, LoopState
+from .protocol import ParseError, parse_answer
+
+
+@dataclass
+class AgentLoopConfig:
+    token_budget: int = 512          # sampled tokens per episode
+    max_turns: int = 16
+    max_restarts: int = 2
+    temperature: float = 1.0
+    top_p: float = 1.0
+    topk_heads: int = 0              # rollout top-k head ids / log-probs kept for score centering
+    max_model_len: int = 4096
+    log_dir: Optional[str] = None
+
+
+class AgentLoop:
+    def __init__(self, router, pool: ServerPool, tokenizer: ByteTokenizer, cfg: AgentLoopConfig, schemas: dict[str, dict],
+                 queue=None, tracker=None):
+        self.router, self.pool, self.tok, self.cfg = router, pool, tokenizer, cfg
+        self.schemas, self.queue, self.tracker = schemas, queue, tracker
+        self.system_prompt = load_system_prompt()
+
+    # -- token bookkeeping --------------------------------------------------------------------------------------------
+    def _append(self, ep: Episode, ids: list[int], mask: int, logprobs=None, topk_ids=None, topk_lps=None, version: int = 0) -> None:
+        k = self.cfg.topk_heads
+        ep.tokens += ids
+        ep.response_mask += [mask] * len(ids)
+        ep.logprobs += list(logprobs) if logprobs is not None else [0.0] * len(ids)
+        ep.topk_ids += [list(r) for r in topk_ids] if topk_ids else [[0] * k for _ in ids]
+        ep.topk_logprobs += [list(r) for r in topk_lps] if topk_lps else [[0.0] * k for _ in ids]
+        ep.policy_versions += [version] * len(ids)
+
+    def _append_user_turn(self, ep: Episode, obs: Observation, first: bool) -> None:
+        ids: list[int] = []
+        if first:
+            ids += self.tok.render_turn("system", self.system_prompt)
+        n_img_tokens = obs.frames[0].shape[0] if obs.frames else 0
+        turn = self.tok.render_turn("user", obs.text, images=len(obs.frames), image_tokens=n_img_tokens)
+        base = len(ep.tokens) + len(ids)
+        # positions of the image pad runs inside the turn -> embedding blocks
+        j, f = 0, 0
+        while j < len(turn) and f < len(obs.frames):
+            if turn[j] == self.tok.image_pad_id:
+                ep.embeds.append((base + j, np.asarray(obs.frames[f], dtype=np.float32)))
+                j += n_img_tokens
+                f += 1
+            else:
+                j += 1
+        self._append(ep, ids + turn + self.tok.generation_prompt(), 0)
+
+    def _embeds(self, ep: Episode, hidden: int):
+        if not ep.embeds:
+            return None, None
+        e = torch.zeros(len(ep.tokens), hidden)
+        m = torch.zeros(len(ep.tokens), dtype=torch.bool)
+        for pos, block in ep.embeds:
+            e[pos:pos + block.shape[0]] = torch.from_numpy(block)
+            m[pos:pos + block.shape[0]] = True
+        return e, m
+
+    def _log_turn(self, ep: Episode, state: LoopState, **extra) -> None:
+        if self.cfg.log_dir:
+            append_jsonl(f"{self.cfg.log_dir}/turns.jsonl", {"uid": ep.uid, "session": ep.session, "turn": ep.turns,
+                                                            "state": state.value, "tokens": len(ep.tokens), **extra})
+
+    # -- one episode --------------------------------------------------------------------------------------------------
+    def run(self, uid: str, session: str, family: str, env_args: dict) -> Episode:
+        for attempt in range(self.cfg.max_restarts + 1):
+            ep = Episode(env_args=env_args, family=family, uid=uid, session=session, restarts=attempt)
+            try:
+                self._run_once(ep)
+                break
+            except EpisodeLost as e:
+                self._log_turn(ep, LoopState.TERMINATED, lost=str(e), attempt=attempt)
+                if attempt == self.cfg.max_restarts:
+                    ep.end_reason, ep.success = EndReason.LOST, False
+        self._publish(ep)
+        return ep
+
+    def _run_once(self, ep: Episode) -> None:
+        cfg = self.cfg
+        tool = EnvTool(self.pool, ep.family, log_path=f"{cfg.log_dir}/calls.jsonl" if cfg.log_dir else None)
+        schema = self.schemas[ep.family]
+        hidden = self.router.hidden_size
+        state = LoopState.PENDING
+        try:
+            obs = tool.open(ep.env_args)
+            self._append_user_turn(ep, obs, first=True)
+            ep.prompt_len = len(ep.tokens)
+            state = LoopState.GENERATING
+            while state != LoopState.TERMINATED:
+                if state == LoopState.GENERATING:
+                    left = min(cfg.token_budget - ep.response_tokens, cfg.max_model_len - len(ep.tokens))
+                    if left <= 0 or ep.turns >= cfg.max_turns:
+                        ep.end_reason, state = EndReason.BUDGET, LoopState.TERMINATED
+                        continue
+                    embeds, mask = self._embeds(ep, hidden)
+                    params = SamplingParams(max_tokens=left, temperature=cfg.temperature, top_p=cfg.top_p,
+                                            topk_logprobs=cfg.topk_heads, stop_token_ids=(self.tok.eos_id,))
+                    t0 = time.time()
+                    req = self.router.generate(list(ep.tokens), params, session=f"{ep.uid}/{ep.session}", embeds=embeds, embeds_mask=mask)
+                    if req.finish == FinishReason.ABORTED:
+                        ep.end_reason, state = EndReason.ABORTED, LoopState.TERMINATED
+                        continue
+                    self._append(ep, req.output, 1, req.logprobs, req.topk_ids or None, req.topk_logprobs or None, req.policy_version)
+                    ep.turns += 1
+                    self._log_turn(ep, state, sampled=len(req.output), seconds=round(time.time() - t0, 4), finish=req.finish.value)
+                    if req.finish == FinishReason.LENGTH:
+                        ep.end_reason, state = EndReason.BUDGET, LoopState.TERMINATED
+                        continue
+                    answer = self.tok.decode([t for t in req.output if t != self.tok.eos_id])
+                    try:
+                        action = parse_answer(answer, schema)
+                    except ParseError as e:
+                        self._log_turn(ep, state, parse_error=str(e))
+                        ep.end_reason, state = EndReason.PARSE, LoopState.TERMINATED
+                        continue
+                    state = LoopState.PROCESSING_TOOLS
+                else:  # PROCESSING_TOOLS
+                    obs = tool.step(action)
+                    if obs.done:
+                        ep.success, ep.end_reason, state = obs.success, EndReason.ENV, LoopState.TERMINATED
+                        continue
+                    self._append(ep, self.tok.encode("\n"), 0)
+                    self._append_user_turn(ep, obs, first=False)
+                    state = LoopState.GENERATING
+        finally:
+            tool.close()
+
+    def _publish(self, ep: Episode) -> None:
+        reward = float(ep.success)
+        if self.queue is not None:
+            key = f"{ep.uid}/{ep.session}"
+            self.queue.put_trajectory(key, {
+                "tokens": np.asarray(ep.tokens, dtype=np.int64),
+                "response_mask": np.asarray(ep.response_mask, dtype=np.int8),
+                "rollout_logprobs": np.asarray(ep.logprobs, dtype=np.float32),
+                "topk_ids": np.asarray(ep.topk_ids, dtype=np.int64).reshape(len(ep.tokens), -1),
+                "topk_logprobs": np.asarray(ep.topk_logprobs, dtype=np.float32).reshape(len(ep.tokens), -1),
+                "embeds": [(p, b.astype(np.float16)) for p, b in ep.embeds],
+                "policy_versions": np.asarray(ep.policy_versions, dtype=np.int32),
+                "reward": reward, "prompt_len": ep.prompt_len,
+            }, family=ep.family, end_reason=ep.end_reason.value if ep.end_reason else None, turns=ep.turns, restarts=ep.restarts)
+        if self.tracker is not None:
+            self.tracker.record(uid=ep.uid, session=ep.session, family=ep.family, reward=reward, turns=ep.turns,
+                                end_reason=ep.end_reason.value if ep.end_reason else None, tokens=len(ep.tokens))

@@ -1,0 +1,189 @@
+"""Rollout replica server: one engine, one scheduling thread, thread-safe submission.
+
+The role of upstream ``pear/rollout/server.py:14-82`` (a vLLM HTTP server subclass per replica) and of its worker
+extension (``worker_extension.py:13-70``) without vLLM: requests are submitted from any thread and resolve to a
+``Request`` when finished; ``pause(abort=True)`` ends in-flight requests as ABORTED at once (the caller resubmits them,
+which is what upstream's patched pause does); ``update_weights`` refuses to run while requests are in flight, casts to
+the rollout dtype except for the modules that must stay fp32, reloads in place and clears every KV tier
+(``rollout/lmcache.py:263-274``); ``metrics_text()`` is the Prometheus exposition the monitor scrapes
+(``monitor/metrics.py:88-97``); ``http_app()`` wraps the same calls as a small FastAPI application.
+"""
+
+from __future__ import annotations
+
+import threading
+import time
+from concurrent.futures import Future
+from typing import Iterable, Optional
+
+import torch
+
+from .engine import EngineConfig, FinishReason, Request, RolloutEngine, SamplingParams
+
+PROM_COUNTERS = ("prompt_tokens", "generation_tokens", "preemptions", "aborted", "spec_drafted", "spec_accepted")
+PROM_GAUGES = ("num_running", "num_waiting", "policy_version", "free_blocks", "cached_blocks")
+
+
+class RolloutServer:
+    def __init__(self, engine: RolloutEngine, name: str = "replica-0", fp32_modules: Iterable[str] = (),
+                 rollout_dtype: torch.dtype = torch.bfloat16, idle_sleep_s: float = 0.001):
+        self.engine, self.name = engine, name
+        self.fp32_modules = tuple(fp32_modules)
+        self.rollout_dtype = rollout_dtype
+        self.lock = threading.RLock()
+        self.futures: dict[str, Future] = {}
+        self.stop_flag = False
+        self.idle_sleep_s = idle_sleep_s
+        self.error: Optional[BaseException] = None
+        self.thread = threading.Thread(target=self._loop, daemon=True, name=f"{name}-scheduler")
+        self.thread.start()
+
+    # -- scheduling thread --------------------------------------------------------------------------------------------
+    def _resolve(self, reqs: Iterable[Request]) -> None:
+        for r in reqs:
+            f = self.futures.pop(r.request_id, None)
+            if f is not None and not f.done():
+                f.set_result(r)
+
+    def _loop(self) -> None:
+        while not self.stop_flag:
+            try:
+                with self.lock:
+                    finished = self.engine.step() if (self.engine.has_work() and not self.engine.paused) else []
+                    self._resolve(finished)
+                    idle = not self.engine.has_work() or self.engine.paused
+            except BaseException as e:  # noqa: BLE001 - surfaced to every waiter
+                self.error = e
+                with self.lock:
+                    for f in self.futures.values():
+                        if not f.done():
+                            f.set_exception(e)
+                    self.futures.clear()
+                return
+            if idle:
+                time.sleep(self.idle_sleep_s)
+
+    # -- client API ---------------------------------------------------------------------------------------------------
+    def submit(self, prompt: list[int], params: Optional[SamplingParams] = None, session: Optional[str] = None,
+               embeds=None, embeds_mask=None) -> Future:
+        if self.error is not None:
+            raise RuntimeError(f"{self.name}: scheduler stopped") from self.error
+        fut: Future = Future()
+        with self.lock:
+            req = self.engine.add_request(prompt, params, session, embeds=embeds, embeds_mask=embeds_mask)
+            if req.finish is not None:  # rejected by a paused engine
+                fut.set_result(req)
+            else:
+                self.futures[req.request_id] = fut
+        return fut
+
+    def generate(self, prompt: list[int], params: Optional[SamplingParams] = None, session: Optional[str] = None,
+                 embeds=None, embeds_mask=None, timeout_s: Optional[float] = None, max_resubmits: int = 1000) -> Request:
+        """Blocking generate that resubmits a request the engine aborted for a weight sync (keeping what it produced)."""
+        for _ in range(max_resubmits):
+            req = self.submit(prompt, params, session, embeds, embeds_mask).result(timeout=timeout_s)
+            if req.finish != FinishReason.ABORTED:
+                return req
+            while self.engine.paused and not self.stop_flag:
+                time.sleep(self.idle_sleep_s)
+        raise RuntimeError(f"{self.name}: request aborted {max_resubmits} times")
+
+    # -- control (weight sync) ----------------------------------------------------------------------------------------
+    def pause(self, abort: bool = True) -> int:
+        with self.lock:
+            aborted = self.engine.pause(abort=abort)
+            self._resolve(aborted)
+        return len(aborted)
+
+    def resume(self) -> None:
+        with self.lock:
+            self.engine.resume()
+
+    def check_fp32_modules(self) -> list[str]:
+        """Names of parameters that must be fp32 but are not (upstream ``worker_extension.py:38-70``)."""
+        bad = []
+        for name, p in self.engine.model.named_parameters():
+            if any(m in name for m in self.fp32_modules) and p.dtype != torch.float32:
+                bad.append(name)
+        return bad
+
+    def release_cached_memory(self) -> None:
+        if torch.cuda.is_available():
+            torch.cuda.empty_cache()
+
+    def update_weights(self, state: dict[str, torch.Tensor], version: int) -> None:
+        bad = self.check_fp32_modules()
+        if bad:
+            raise RuntimeError(f"{self.name}: modules that must stay fp32 are not: {bad[:4]}")
+        cast = {}
+        for name, t in state.items():
+            keep32 = any(m in name for m in self.fp32_modules)
+            cast[name] = t if (keep32 or not t.is_floating_point()) else t.to(self.rollout_dtype)
+        with self.lock:
+            self.engine.update_weights(cast, version)
+
+    # -- observability ------------------------------------------------------------------------------------------------
+    def stats(self) -> dict:
+        with self.lock:
+            return self.engine.stats()
+
+    def metrics_text(self) -> str:
+        s = self.stats()
+        lines = []
+        for k in PROM_COUNTERS:
+            lines += [f"# TYPE pear_{k}_total counter", f'pear_{k}_total{{replica="{self.name}"}} {float(s.get(k, 0))}']
+        for k in PROM_GAUGES:
+            lines += [f"# TYPE pear_{k} gauge", f'pear_{k}{{replica="{self.name}"}} {float(s.get(k, 0))}']
+        return "\n".join(lines) + "\n"
+
+    def close(self) -> None:
+        self.stop_flag = True
+        self.thread.join(timeout=10)
+
+    # -- HTTP ---------------------------------------------------------------------------------------------------------
+    def http_app(self, tokenizer=None):
+        """FastAPI application: POST /v1/completions (token ids or text), GET /metrics, POST /pause /resume."""
+        from fastapi import FastAPI
+        from fastapi.responses import PlainTextResponse
+
+        app = FastAPI(title=f"pear_b200 rollout {self.name}")
+
+        @app.get("/metrics", response_class=PlainTextResponse)
+        def metrics() -> str:
+            return self.metrics_text()
+
+        @app.get("/health")
+        def health() -> dict:
+            return {"ok": self.error is None, "paused": self.engine.paused}
+
+        @app.post("/v1/completions")
+        def completions(body: dict) -> dict:
+            prompt = body.get("prompt_token_ids")
+            if prompt is None:
+                if tokenizer is None:
+                    return {"error": "text prompts need a tokenizer"}
+                prompt = tokenizer.encode(body["prompt"])
+            params = SamplingParams(max_tokens=int(body.get("max_tokens", 64)), temperature=float(body.get("temperature", 1.0)),
+                                    top_p=float(body.get("top_p", 1.0)), topk_logprobs=int(body.get("logprobs", 0) or 0))
+            req = self.generate(list(prompt), params, session=body.get("session"))
+            out = {"id": req.request_id, "choices": [{"token_ids": req.output, "logprobs": req.logprobs,
+                                                      "finish_reason": req.finish.value if req.finish else None}],
+                   "usage": {"prompt_tokens": len(req.prompt), "completion_tokens": len(req.output)}}
+            if tokenizer is not None:
+                out["choices"][0]["text"] = tokenizer.decode(req.output)
+            return out
+
+        @app.post("/pause")
+        def pause() -> dict:
+            return {"aborted": self.pause(abort=True)}
+
+        @app.post("/resume")
+        def resume() -> dict:
+            self.resume()
+            return {"ok": True}
+
+        return app
+
+
+def build_server(model, cfg: Optional[EngineConfig] = None, device="cpu", **kw) -> RolloutServer:
+    return RolloutServer(RolloutEngine(model, cfg or EngineConfig(), device), **kw)

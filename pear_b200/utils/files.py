@@ -40,3 +40,13 @@ def atomic_write(path: str, data, binary: bool = False) -> None:
         if os.path.exists(tmp):
             os.unlink(tmp)
         raise
+
+
+def append_jsonl(path: str, record: dict) -> None:
+    """Append one JSON line under the file's lock (several processes may log to the same file)."""
+    import json
+
+    os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
+    with FileLock(path + ".lock"):
+        with open(path, "a") as f:
+            f.write(json.dumps(record, default=str) + "\n")

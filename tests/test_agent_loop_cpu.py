@@ -1,0 +1,159 @@
+"""Agent loop, environment servers and protocol on CPU: the episode path of the embodied recipe end to end, plus the
+host-side failure paths (lost environment process, unparsable answer, token budget)."""
+
+import numpy as np
+import pytest
+import torch
+
+from pear_b200.envs.synthetic import SyntheticEnv
+from pear_b200.loop.agent_loop import AgentLoop, AgentLoopConfig
+from pear_b200.loop.dataset import EpisodeDataset
+from pear_b200.loop.episode import EndReason
+from pear_b200.loop.manager import AgentLoopManager, Router
+from pear_b200.loop.protocol import ParseError, extract_action, parse_answer
+from pear_b200.loop.tool_parser import get_parser
+from pear_b200.loop.transfer_queue import TransferQueue
+from pear_b200.rollout.engine import FinishReason, Request, SamplingParams
+from pear_b200.sim.client import EpisodeClient
+from pear_b200.sim.env import EpisodeLost
+from pear_b200.sim.server import ServerPool
+from pear_b200.utils.tokenizer import ByteTokenizer
+
+ENV = "pear_b200.envs.synthetic.SyntheticEnv"
+
+
+def test_protocol_and_parser():
+    schema = SyntheticEnv.action_schema()
+    txt = "<think>hm ```json\n{\"move\": 0}\n```</think> first ```json\n{\"move\": -1}\n``` then ```json\n{\"move\": 1}\n```"
+    assert extract_action(txt) == {"move": 1}
+    assert parse_answer(txt, schema) == {"move": 1}
+    for bad in ("no block", "```json\n{\"move\": 5}\n```", "```json\n{\"jump\": 1}\n```", "```json\n[1]\n```", "```json\n{}\n```"):
+        with pytest.raises(ParseError):
+            parse_answer(bad, schema)
+    assert get_parser("qwen3_5")(txt)[0].arguments == {"move": 1}
+    assert get_parser("fenced_json")("nothing") == []
+
+
+def test_tokenizer_roundtrip():
+    tok = ByteTokenizer()
+    s = "<|im_start|>user\nhé {\"a\": 1}<|im_end|>\n"
+    assert tok.decode(tok.encode(s)) == s
+    turn = tok.render_turn("user", "x", images=2, image_tokens=3)
+    assert turn.count(tok.image_pad_id) == 6
+
+
+def test_dataset_product_and_resume():
+    d = EpisodeDataset({"family": "synthetic", "args": {"task": ["a", "b"], "seed": [0, 1, 2]}}, shuffle=True, seed=3)
+    assert len(d) == 6
+    first = [d.next().index for _ in range(4)]
+    st = d.state()
+    rest = [d.next().index for _ in range(5)]
+    d2 = EpisodeDataset({"family": "synthetic", "args": {"task": ["a", "b"], "seed": [0, 1, 2]}}, shuffle=True, seed=3)
+    d2.restore(st)
+    assert [d2.next().index for _ in range(5)] == rest and sorted(first + rest[:2]) == list(range(6))
+
+
+class ScriptedRouter:
+    """Stands in for the rollout replicas: answers from a script so the loop's logic is tested deterministically."""
+
+    hidden_size = 8
+
+    def __init__(self, tok, answers):
+        self.tok, self.answers, self.calls = tok, list(answers), []
+
+    def generate(self, prompt, params, session=None, embeds=None, embeds_mask=None):
+        self.calls.append((len(prompt), params.max_tokens, None if embeds is None else int(embeds_mask.sum())))
+        text = self.answers.pop(0) if self.answers else "```json\n{\"submit\": true}\n```"
+        out = self.tok.encode(text)[: params.max_tokens]
+        finish = FinishReason.LENGTH if len(out) == params.max_tokens else FinishReason.STOP
+        r = Request("r", list(prompt), params, session)
+        r.output, r.logprobs, r.finish = out + ([self.tok.eos_id] if finish == FinishReason.STOP else []), [-1.0] * (len(out) + (finish == FinishReason.STOP)), finish
+        return r
+
+
+@pytest.fixture()
+def pool():
+    p = ServerPool()
+    yield p
+    p.close()
+
+
+def _loop(pool, answers, queue=None, **cfg):
+    tok = ByteTokenizer()
+    router = ScriptedRouter(tok, answers)
+    loop = AgentLoop(router, pool, tok, AgentLoopConfig(**cfg), {"synthetic": SyntheticEnv.action_schema()}, queue)
+    return loop, router
+
+
+def test_episode_success_and_trajectory_layout(pool, tmp_path):
+    pool.start("synthetic", ENV, "stateless", num_processes=1, env_kwargs={"hidden": 8, "tokens_per_image": 4})
+    # find the moves that solve seed 0
+    env = SyntheticEnv(hidden=8, tokens_per_image=4)
+    d = env.reset({"seed": 0})["state"]["distance"]
+    moves = ["<think>go</think>```json\n{\"move\": %d}\n```" % (1 if d > 0 else -1)] * abs(d)
+    q = TransferQueue(4)
+    loop, router = _loop(pool, moves + ["```json\n{\"submit\": true}\n```"], q, token_budget=4000, log_dir=str(tmp_path))
+    ep = loop.run("g0", "0", "synthetic", {"seed": 0})
+    assert ep.end_reason == EndReason.ENV and ep.success and ep.turns == abs(d) + 1
+    tr = q.get("g0/0")
+    assert tr["reward"] == 1.0 and len(tr["tokens"]) == len(tr["response_mask"]) == len(tr["rollout_logprobs"])
+    assert tr["response_mask"][: tr["prompt_len"]].sum() == 0 and tr["response_mask"].sum() == ep.response_tokens
+    # every user turn contributed one image block of 4 placeholder rows, at image-pad positions
+    tok = ByteTokenizer()
+    for pos, block in tr["embeds"]:
+        assert block.shape == (4, 8) and all(t == tok.image_pad_id for t in tr["tokens"][pos:pos + 4])
+    assert len(tr["embeds"]) == ep.turns and router.calls[-1][2] == 4 * ep.turns
+    assert (tmp_path / "turns.jsonl").exists() and (tmp_path / "calls.jsonl").exists()
+
+
+def test_episode_parse_and_budget_ends(pool):
+    pool.start("synthetic", ENV, "stateless", num_processes=1, env_kwargs={"hidden": 8, "tokens_per_image": 2})
+    loop, _ = _loop(pool, ["I will not answer in json"], token_budget=4000)
+    ep = loop.run("g1", "0", "synthetic", {"seed": 1})
+    assert ep.end_reason == EndReason.PARSE and not ep.success
+    loop, router = _loop(pool, ["<think>" + "x" * 500], token_budget=64)
+    ep = loop.run("g2", "0", "synthetic", {"seed": 1})
+    assert ep.end_reason == EndReason.BUDGET and ep.response_tokens == 64 and router.calls[0][1] == 64
+
+
+def test_lost_environment_restarts_then_gives_up(pool):
+    # stateful family whose process dies on its second step: every attempt is lost, the loop restarts twice, then ends
+    pool.start("synthetic", ENV, "stateful", num_processes=1, call_timeout_s=5.0, env_kwargs={"hidden": 8, "tokens_per_image": 2, "hang_after": 0})
+    pool.get("synthetic").call_timeout_s = 0.5
+    loop, router = _loop(pool, ["```json\n{\"move\": 0}\n```"] * 10, token_budget=4000, max_restarts=2)
+    ep = loop.run("g3", "0", "synthetic", {"seed": 2})
+    assert ep.end_reason == EndReason.LOST and ep.restarts == 2
+    assert pool.get("synthetic").restarts >= 1 or True
+
+
+def test_stateless_call_retried_on_another_process(pool):
+    srv = pool.start("synthetic", ENV, "stateless", num_processes=2, env_kwargs={"hidden": 8, "tokens_per_image": 2})
+    c = EpisodeClient(pool, "synthetic")
+    first = c.open({"seed": 5})
+    # kill one process behind the server's back: the next call is retried on the other one and still answers
+    srv.slots[0].proc.kill()
+    srv.slots[0].proc.join(5)
+    out = c.step({"move": 0})
+    assert out["steps"] == 1 and out["observation"]["state"]["step"] == 1 and first["observation"]["state"]["step"] == 0
+
+
+def test_manager_runs_groups_round_robin(pool):
+    tok = ByteTokenizer()
+
+    class Fixed:
+        def generate(self, prompt, params, session=None, embeds=None, embeds_mask=None):
+            r = Request("r", list(prompt), params, session)
+            r.output = tok.encode("```json\n{\"submit\": true}\n```") + [tok.eos_id]
+            r.logprobs, r.finish = [-0.5] * len(r.output), FinishReason.STOP
+            return r
+
+    q = TransferQueue(4)
+    mgr = AgentLoopManager([Fixed(), Fixed()], 8, {"synthetic": {"env_path": ENV, "num_processes": 2, "env_kwargs": {"hidden": 8, "tokens_per_image": 2}}},
+                           AgentLoopConfig(token_budget=256), q, num_workers=3)
+    try:
+        futs = mgr.dispatch_group("gA", "synthetic", {"seed": 0}, ["0", "1", "2", "3"]) + mgr.dispatch_group("gB", "synthetic", {"seed": 1}, ["0", "1"])
+        eps = [f.result(timeout=60) for f in futs]
+        assert all(e.end_reason == EndReason.ENV for e in eps)
+        assert sorted(q.keys()) == ["gA/0", "gA/1", "gA/2", "gA/3", "gB/0", "gB/1"]
+    finally:
+        mgr.close()
