@@ -1,0 +1,168 @@
+"""Training entry point: ``python -m pear_b200.train.main <recipe> key=value ...``.
+
+The order of upstream ``pear/trainer/main.py:12-32`` and ``runner.py:22-88``: compose the recipe, derive the run sizes
+(``RunConfig.prepare``), open the transfer queue, build the trainer engine and the rollout replicas, start the
+environment server pools and the agent-loop manager, ``fit``; on the way out (also on error) cancel in-flight prompt
+groups, stop the servers and close the queue.
+
+One process hosts one trainer rank. With ``WORLD_SIZE > 1`` (torchrun) the ranks form the FSDP / sequence-parallel
+group; rank 0 additionally hosts the rollout replicas and environment pools of the single-node recipes.
+"""
+
+from __future__ import annotations
+
+import json
+import os
+import sys
+import time
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from ..config.loader import compose
+from ..loop.agent_loop import AgentLoopConfig
+from ..loop.dataset import EpisodeDataset
+from ..loop.manager import AgentLoopManager
+from ..loop.transfer_queue import TransferQueue
+from ..loop.weight_sync import InProcessTransport, SyncConfig, WeightSync
+from ..models.config import HybridConfig
+from ..models.hybrid import HybridForCausalLM
+from ..models import io as model_io
+from ..rollout.engine import EngineConfig as RolloutConfig
+from ..rollout.server import build_server
+from ..utils.logging_utils import get_logger
+from .checkpoint import CheckpointManager
+from .engine import EngineConfig, TrainEngine
+from .replay_buffer import ReplayBuffer
+from .trainer import Trainer, TrainerConfig
+
+log = get_logger("pear_b200.train")
+
+
+@dataclass
+class RunConfig:
+    """Derived sizes (upstream ``pear/trainer/config.py:37-63``): with ``run_sizes.sessions_per_replica`` set,
+    ``max_num_seqs = seqs_per_session * sessions_per_replica``, the agent workers cover those slots, and the trainer
+    caps in-flight sessions at ``replicas * sessions_per_replica``."""
+
+    cfg: object
+    replicas: int = 1
+
+    def prepare(self):
+        cfg = self.cfg
+        rs = cfg.run_sizes
+        ro = cfg.actor_rollout_ref.rollout
+        if rs.sessions_per_replica is not None:
+            spr = int(rs.sessions_per_replica)
+            ro.max_num_seqs = int(rs.seqs_per_session) * spr
+            ro.agent.num_workers = max(1, (ro.max_num_seqs * self.replicas + int(rs.seqs_per_agent_worker) - 1) // int(rs.seqs_per_agent_worker))
+            cfg.trainer.v1.sampler.max_inflight_sessions = self.replicas * spr
+        for k, v in cfg.get("env_vars", {}).items():
+            os.environ.setdefault(str(k), str(v))
+        os.makedirs(cfg.run_dir, exist_ok=True)
+        return cfg
+
+
+def _model_config(path: str) -> HybridConfig:
+    if path.startswith("preset:"):
+        return getattr(HybridConfig, path.split(":", 1)[1])()
+    return model_io.load_config(path)
+
+
+class MetricsLog:
+    def __init__(self, run_dir: str, backends=("console", "file")):
+        self.path = os.path.join(run_dir, "metrics.jsonl")
+        self.train_log = os.path.join(run_dir, "train.log")
+        self.backends = backends
+
+    def __call__(self, step: int, m: dict) -> None:
+        rec = {"step": step, "time": time.time(), **{k: (float(v) if isinstance(v, (int, float)) else v) for k, v in m.items()}}
+        if "file" in self.backends:
+            with open(self.path, "a") as f:
+                f.write(json.dumps(rec) + "\n")
+            with open(self.train_log, "a") as f:
+                f.write(f"step:{step} - " + " - ".join(f"{k}:{v:.6g}" for k, v in sorted(m.items()) if isinstance(v, (int, float))) + "\n")
+        if "console" in self.backends:
+            keys = ("data/reward_mean", "actor/pg_loss", "actor/grad_norm", "timing/step_s", "train/staleness_mean")
+            log.info("step %d | %s", step, " | ".join(f"{k.split('/')[-1]} {m[k]:.4g}" for k in keys if k in m))
+
+
+def build_stack(cfg, replicas: int = 1, device: str = "cpu", env_families: Optional[dict] = None, world_group=None):
+    """Everything a single-node run needs, wired together. Returns (trainer, closers)."""
+    mcfg = _model_config(str(cfg.actor_rollout_ref.model.path))
+    ecfg = EngineConfig.from_config(cfg)
+    init = None
+    mpath = str(cfg.actor_rollout_ref.model.path)
+    if not mpath.startswith("preset:"):
+        m = HybridForCausalLM(mcfg, with_mtp=False)
+        model_io.load_model_dir(mpath, m)
+        init = m.state_dict()
+    engine = TrainEngine(mcfg, ecfg, device=device, world_group=world_group, seed=int(cfg.trainer.seed), state_dict=init)
+    rank = engine.rank
+    queue = TransferQueue(int(cfg.transfer_queue.num_data_storage_units))
+    ro = cfg.actor_rollout_ref.rollout
+    servers, manager = [], None
+    tcfg = TrainerConfig.from_config(cfg)
+    if rank == 0:
+        full = engine.full_state_dict(torch.float32)
+        for i in range(replicas):
+            rm = HybridForCausalLM(mcfg, with_mtp=bool(cfg.actor_rollout_ref.model.mtp.enable_rollout))
+            rm.load_state_dict(full, strict=False)
+            rc = RolloutConfig(num_blocks=int(ro.get("num_blocks", 2048)), block_size=int(ro.block_size), max_num_seqs=int(ro.max_num_seqs),
+                               max_num_batched_tokens=int(ro.max_num_batched_tokens), enable_prefix_caching=bool(ro.enable_prefix_caching),
+                               num_speculative_tokens=int(cfg.actor_rollout_ref.model.mtp.num_speculative_tokens) if cfg.actor_rollout_ref.model.mtp.enable_rollout else 0,
+                               host_blocks=int(ro.get("host_blocks", 0)), seed=int(cfg.trainer.seed) + i)
+            servers.append(build_server(rm, rc, device, name=f"replica-{i}", fp32_modules=tuple(ro.fp32_modules)))
+        families = env_families or {"synthetic": {"env_path": "pear_b200.envs.synthetic.SyntheticEnv", "num_processes": 2,
+                                                  "env_kwargs": {"hidden": mcfg.hidden_size, "tokens_per_image": 4}}}
+        acfg = AgentLoopConfig(token_budget=int(cfg.data.max_response_length), temperature=float(ro.temperature), top_p=float(ro.top_p),
+                               topk_heads=tcfg.topk_heads, max_model_len=int(ro.max_model_len), log_dir=os.environ.get("PEAR_LOG_DIR"))
+        manager = AgentLoopManager(servers, mcfg.hidden_size, families, acfg, queue, num_workers=int(ro.agent.num_workers))
+    else:
+        full = engine.full_state_dict(torch.float32)  # collective: every rank takes part
+    sam = cfg.trainer.v1.sampler
+    replay = ReplayBuffer(queue, tcfg.n, int(sam.max_off_policy_threshold), str(sam.max_off_policy_strategy),
+                          bool(cfg.algorithm.filter_groups.enable), sam.max_inflight_sessions)
+    files = cfg.data.train_files
+    dataset = EpisodeDataset(files if files is not None else {"family": "synthetic", "args": {"task": ["reach"], "seed": list(range(64))}},
+                             seed=int(cfg.trainer.seed))
+    ce = ro.checkpoint_engine
+    sync = WeightSync(SyncConfig(int(ce.update_weights_bucket_megabytes), getattr(torch, str(ro.dtype)), tuple(ro.fp32_modules)),
+                      InProcessTransport(servers), servers) if rank == 0 else None
+    ckpt = CheckpointManager(str(cfg.run_dir), rank, engine.world, cfg.trainer.max_actor_ckpt_to_keep,
+                             barrier=(lambda: dist.barrier(world_group)) if engine.world > 1 else None)
+    trainer = Trainer(tcfg, engine, dataset, manager, replay, queue, sync, ckpt, MetricsLog(str(cfg.run_dir), tuple(cfg.trainer.logger)))
+
+    def close():
+        if manager is not None:
+            manager.close()
+        for s in servers:
+            s.close()
+        queue.close()
+
+    return trainer, close
+
+
+def main(argv: Optional[list[str]] = None) -> int:
+    argv = list(sys.argv[1:] if argv is None else argv)
+    recipe = argv.pop(0) if argv and "=" not in argv[0] else "training"
+    cfg = RunConfig(compose(recipe, argv)).prepare()
+    world_group = None
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        dist.init_process_group("nccl" if torch.cuda.is_available() else "gloo")
+        world_group = dist.group.WORLD
+    device = f"cuda:{os.environ.get('LOCAL_RANK', 0)}" if torch.cuda.is_available() else "cpu"
+    trainer, close = build_stack(cfg, device=device, world_group=world_group)
+    try:
+        trainer.fit()
+    finally:
+        close()
+        if world_group is not None:
+            dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
