@@ -1,0 +1,85 @@
+"""Monitor (metrics scraper, tracker, driver log, panel) and evaluation helpers on CPU."""
+
+import json
+import os
+
+import torch
+
+from pear_b200.eval.general import Item, LeastInFlightRouter, paired_bootstrap, run_benchmark
+from pear_b200.models.config import HybridConfig
+from pear_b200.models.hybrid import HybridForCausalLM
+from pear_b200.monitor.driver_log import DriverLog
+from pear_b200.monitor.metrics import MetricsScraper, parse_prometheus
+from pear_b200.monitor.progress_panel import ProgressPanel
+from pear_b200.monitor.progress_tracker import ProgressTracker
+from pear_b200.rollout.engine import EngineConfig, SamplingParams
+from pear_b200.rollout.server import build_server
+from pear_b200.utils.tokenizer import ByteTokenizer
+
+
+def test_prometheus_parse_and_rates():
+    text = '# TYPE x counter\npear_generation_tokens_total{replica="a"} 10\npear_num_running{replica="a"} 2\n'
+    assert parse_prometheus(text) == {"pear_generation_tokens_total": 10.0, "pear_num_running": 2.0}
+    vals = {"n": 0}
+
+    def src():
+        vals["n"] += 100
+        return f'pear_generation_tokens_total{{replica="a"}} {vals["n"]}\npear_num_running{{replica="a"}} 1\n'
+
+    def dead():
+        raise ConnectionError("down")
+
+    s = MetricsScraper({"a": src, "b": dead})
+    s.scrape()
+    s.last["a"].t -= 2.0  # two seconds ago
+    s.scrape()
+    assert 40 < s.rates()["a"]["pear_generation_tokens_per_s"] < 60
+    assert "b" in s.errors and s.summary()["pear_num_running"] == 1.0
+
+
+def test_tracker_driver_log_and_panel(tmp_path):
+    tr = ProgressTracker()
+    tr.record("g", "0", "synthetic", 1.0, 3, "env", 100)
+    tr.record("g", "1", "synthetic", 0.0, 5, "parse", 50)
+    snap = tr.snapshot()
+    assert snap["families"]["synthetic"]["success_rate"] == 0.5 and snap["end_reasons"] == {"env": 1, "parse": 1}
+    log = tmp_path / "train.log"
+    log.write_text("noise\nstep:1 - timing/train_s:2.5 - data/reward_mean:0.25 - timing/wait_rollout_s:1\nstep:2 - timing/train_s:3")
+    d = DriverLog(str(log))
+    assert [r.step for r in d.poll()] == [1] and d.latest().phases == {"train_s": 2.5, "wait_rollout_s": 1.0}
+    with open(log, "a") as f:
+        f.write(".5\n")
+    assert [r.step for r in d.poll()] == [2] and d.latest().phases["train_s"] == 3.5
+    panel = ProgressPanel(str(tmp_path), MetricsScraper({"a": lambda: "pear_num_running 1\n"}), tr)
+    state = panel.tick()
+    assert state["trainer"]["step"] == 2 and json.load(open(tmp_path / "progress.json"))["trajectories"]["episodes"] == 2
+    assert "episodes 2" in open(tmp_path / "progress.log").read()
+
+
+def test_paired_bootstrap():
+    a = {str(i): [0.0] for i in range(40)}
+    b = {str(i): [1.0 if i % 2 else 0.0] for i in range(40)}
+    r = paired_bootstrap(a, b, samples=500, seed=1)
+    assert r["items"] == 40 and abs(r["diff"] - 0.5) < 1e-9 and r["p_b_better"] == 1.0 and r["ci95"][0] > 0.2
+
+
+def test_server_metrics_pause_resubmit_and_benchmark():
+    cfg = HybridConfig.tiny()
+    model = HybridForCausalLM(cfg, with_mtp=False).init_weights(0)
+    srv = build_server(model, EngineConfig(num_blocks=256, max_num_seqs=4))
+    try:
+        tok = ByteTokenizer()
+        router = LeastInFlightRouter([srv])
+        scores = run_benchmark(router, tok, [Item("0", "2+2?", "4"), Item("1", "3+3?", "6")], n=2, max_tokens=8, workers=2)
+        assert set(scores) == {"0", "1"} and all(len(v) == 2 for v in scores.values())
+        assert "pear_generation_tokens_total" in srv.metrics_text()
+        # a paused replica rejects new requests as aborted; generate() resubmits after the resume
+        srv.pause(abort=True)
+        fut = srv.submit([1, 2, 3], SamplingParams(max_tokens=4))
+        assert fut.result(timeout=5).finish.value == "aborted"
+        srv.update_weights({k: v.detach().clone() for k, v in model.state_dict().items()}, version=7)
+        srv.resume()
+        req = srv.generate([1, 2, 3], SamplingParams(max_tokens=4), timeout_s=60)
+        assert len(req.output) == 4 and req.policy_version == 7
+    finally:
+        srv.close()
