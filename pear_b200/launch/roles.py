@@ -1,0 +1,76 @@
+"""Cluster roles and per-process environment (upstream ``scripts/start_ray_node.sh:58-61`` starts Ray nodes with the
+custom resources trainer / rollout / robodojo / robolab; ``scripts/gpu_process_variables.sh:17-59`` sets the JIT-cache
+and thread environment of GPU processes).
+
+Without Ray a "role" is a set of processes started by ``launch.py``: trainer ranks under ``torch.distributed.run``,
+rollout replicas (one process group per replica of ``tensor_model_parallel_size`` GPUs), environment server hosts and
+the monitor. Roles map to GPU index ranges of a node; the plan is pure data so it can be checked without a cluster.
+"""
+
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass, field
+
+
+@dataclass
+class RolePlan:
+    role: str
+    processes: int
+    gpus_per_process: int = 0
+    gpu_offset: int = 0
+    module: str = ""
+    args: list[str] = field(default_factory=list)
+
+    def gpu_ids(self, index: int) -> list[int]:
+        lo = self.gpu_offset + index * self.gpus_per_process
+        return list(range(lo, lo + self.gpus_per_process))
+
+
+def plan_node(n_gpus: int, trainer_gpus: int, rollout_tp: int, recipe: str, overrides: list[str], env_hosts: int = 1) -> list[RolePlan]:
+    """Split one node: the first ``trainer_gpus`` GPUs train, the rest serve rollouts in groups of ``rollout_tp``."""
+    if trainer_gpus > n_gpus or (n_gpus - trainer_gpus) % max(1, rollout_tp):
+        raise ValueError(f"{n_gpus} GPUs cannot hold {trainer_gpus} trainer GPUs plus rollout replicas of {rollout_tp}")
+    replicas = (n_gpus - trainer_gpus) // max(1, rollout_tp)
+    return [
+        RolePlan("trainer", trainer_gpus, 1, 0, "pear_b200.train.main", [recipe] + overrides),
+        RolePlan("rollout", replicas, rollout_tp, trainer_gpus, "pear_b200.rollout.server", overrides),
+        RolePlan("env", env_hosts, 0, 0, "pear_b200.sim.server", []),
+        RolePlan("monitor", 1, 0, 0, "pear_b200.monitor.progress_panel", []),
+    ]
+
+
+def gpu_process_env(gpu_ids: list[int], threads: int = 8, cache_dir: str = "") -> dict[str, str]:
+    """Environment of one GPU process: visible devices, bounded host thread pools (many processes share a host),
+    several NCCL communicators per GPU ordered by host issue order, build cache kept inside the tree."""
+    env = {
+        "CUDA_VISIBLE_DEVICES": ",".join(map(str, gpu_ids)),
+        "OMP_NUM_THREADS": str(threads), "MKL_NUM_THREADS": str(threads), "TOKENIZERS_PARALLELISM": "false",
+        "NCCL_LAUNCH_ORDER_IMPLICIT": "1", "NCCL_MNNVL_ENABLE": "0", "CUDA_DEVICE_MAX_CONNECTIONS": "32",
+        "PYTORCH_CUDA_ALLOC_CONF": "expandable_segments:True",
+    }
+    if cache_dir:
+        env["PEAR_BUILD_DIR"] = cache_dir
+    return env
+
+
+def command(plan: RolePlan, index: int, master_port: int = 29500) -> tuple[list[str], dict[str, str]]:
+    env = gpu_process_env(plan.gpu_ids(index)) if plan.gpus_per_process else {}
+    if plan.role == "trainer":
+        cmd = ["python", "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={plan.processes}", "--master-addr", "127.0.0.1",
+               "--master-port", str(master_port), "-m", plan.module] + plan.args
+        env = gpu_process_env(list(range(plan.gpu_offset, plan.gpu_offset + plan.processes)))
+    else:
+        cmd = ["python", "-m", plan.module] + plan.args
+    return cmd, env
+
+
+def raise_fd_limit(target: int = 65536) -> int:
+    """Servers hold one pipe pair per environment process and one socket per session: lift the soft FD limit early
+    (upstream presizes the FD table in a ``sitecustomize``)."""
+    import resource
+    soft, hard = resource.getrlimit(resource.RLIMIT_NOFILE)
+    new = min(target, hard) if hard != resource.RLIM_INFINITY else target
+    if new > soft:
+        resource.setrlimit(resource.RLIMIT_NOFILE, (new, hard))
+    return max(new, soft)

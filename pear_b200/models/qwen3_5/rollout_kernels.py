@@ -1,0 +1,30 @@
+"""Rollout kernel façade of the family (upstream ``rollout/rollout_kernels.py:9-72``, ``gpu_backend.py:10-65``)."""
+
+from __future__ import annotations
+
+from ..hybrid import HybridForCausalLM
+from ..kernels import RolloutKernels
+from .gpu_backend import REQUIREMENTS, GpuGeneration, detect
+
+
+class Qwen3_5RolloutKernels(RolloutKernels):
+    @classmethod
+    def configure_server(cls, engine_config: dict, max_num_seqs: int, max_num_batched_tokens: int) -> None:
+        REQUIREMENTS.check_rollout(engine_config)
+        engine_config.setdefault("block_size", 16)
+        # decode steps replay CUDA graphs captured at these token counts; larger (prefill) steps launch eagerly
+        sizes = [s for s in (1, 2, 4, 8, 16, 32, 64, 128, 256) if s <= max(1, max_num_seqs * 8)]
+        engine_config.setdefault("cudagraph_capture_sizes", sizes)
+        engine_config["max_num_batched_tokens"] = max_num_batched_tokens
+
+    @classmethod
+    def install_worker(cls, engine) -> None:
+        if detect() is GpuGeneration.NONE:
+            return
+        from ...ops import lib
+        lib.lib()
+
+    @classmethod
+    def check_model(cls, model, engine_config) -> None:
+        if not isinstance(model, HybridForCausalLM):
+            raise TypeError(f"expected the hybrid GDN + attention model, got {type(model).__name__}")

@@ -26,6 +26,7 @@ def _cuda(*tensors) -> bool:
 
 # when set (tests, baseline arm of a benchmark) CUDA tensors also take the torch statement
 FORCE_REFERENCE = False
+PRECISE_OPERANDS = False  # set during an overflow rerun: GEMM operands stay fp32 instead of bf16
 
 
 def _use_kernels(*tensors) -> bool:

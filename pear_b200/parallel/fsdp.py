@@ -185,8 +185,19 @@ class ShardedModel:
         for u in self.units.values():
             u.load_full_state(state)
 
-    def shard_state(self) -> dict[str, torch.Tensor]:
-        return {name: u.shard.detach().clone() for name, u in self.units.items()}
+    def shard_state(self) -> dict:
+        """This rank's flat shards plus the layout (unit -> parameter name -> (offset, shape) in the unit's full flat
+        buffer) an offline merger needs to rebuild the tensors from all ranks' files."""
+        out: dict = {name: u.shard.detach().clone() for name, u in self.units.items()}
+        layout = {}
+        for uname, u in self.units.items():
+            o, meta = 0, {}
+            for name, n, shp in zip(u.names, u.numels, u.shapes):
+                meta[name] = (o, tuple(shp))
+                o += n
+            layout[uname] = meta
+        out["__layout__"] = layout
+        return out
 
     def load_shard_state(self, state: dict[str, torch.Tensor]) -> None:
         with torch.no_grad():

@@ -101,6 +101,8 @@ def build_stack(cfg, replicas: int = 1, device: str = "cpu", env_families: Optio
         init = m.state_dict()
     engine = TrainEngine(mcfg, ecfg, device=device, world_group=world_group, seed=int(cfg.trainer.seed), state_dict=init)
     rank = engine.rank
+    if rank == 0:
+        mcfg.save(os.path.join(str(cfg.run_dir), "model_config.json"))  # the offline merger reads it
     queue = TransferQueue(int(cfg.transfer_queue.num_data_storage_units))
     ro = cfg.actor_rollout_ref.rollout
     servers, manager = [], None

@@ -81,6 +81,13 @@ def test_two_steps_checkpoint_and_resume(tmp_path):
         m = HybridForCausalLM(model_io.load_config(out), with_mtp=False)
         missing, unexpected = model_io.load_model_dir(out, m)
         assert not unexpected and all(k.startswith("mtp.") for k in missing)
+        # the offline merger rebuilds the same tensors from the shard files of the run directory
+        from pear_b200.utils import model_merger
+        merged_dir = str(tmp_path / "merged")
+        trainer2.checkpoints.save(3, trainer2.engine, trainer2.dataset, trainer2.replay, trainer2.queue)
+        assert model_merger.main([run, merged_dir]) == 0
+        a, b = model_io.load_safetensors(os.path.join(out, "model.safetensors")), model_io.load_safetensors(os.path.join(merged_dir, "model.safetensors"))
+        assert a.keys() == b.keys() and all(torch.equal(a[k], b[k]) for k in a)
     finally:
         close2()
 
