@@ -1,0 +1,307 @@
+// bf16 GEMMs on tcgen05 fused with the collective that precedes or follows them, over peer memory (NVLink / NVSwitch):
+//
+//   all-gather -> GEMM   C[M, N] = gather_r(A_r)[M, K] * B[N, K]^T,  A row-sharded: rank r holds rows [r M/W, (r+1) M/W)
+//       There is no gather pass: the TMA producer reads each 128-row tile of A straight from the memory of the rank
+//       that owns it (one tensor map per rank; plain, non-multicast TMA loads). Tiles of the local shard come first,
+//       remote shards are touched only once their owner has signalled that the shard is written (bounded wait).
+//
+//   GEMM -> reduce-scatter   C_r[M/W, N] = sum_s A_s[M, K_s] * B_s[N, K_s]^T restricted to the rows rank r owns
+//       There is no reduce pass: the epilogue adds each finished fp32 tile into the OWNER's accumulation buffer with
+//       vectorised `red.global.add` over NVLink while the tensor cores work on the next tile. Tiles are visited owner by
+//       owner starting after the own rank, so at any moment the ranks write to different owners.
+//
+// Upstream runs these as separate steps (FSDP2 NCCL all-gather then cuBLAS, `operands.py:204`; split-K partials then
+// `ar_norm.cu` at TP2). The main loop is the one of gemm_tcgen05.cu: 4-stage TMA ring, one MMA-issuing thread, two TMEM
+// accumulators, four epilogue warps. No cluster multicast anywhere.
+#include "common.cuh"
+
+#include <cudaTypedefs.h>
+
+namespace pear {
+
+constexpr int kCBM = 128, kCBK = 64, kCStages = 4, kCThreads = 192, kCMaxRanks = 8;
+
+struct CollSmem {
+  uint64_t full[kCStages], empty[kCStages];
+  uint64_t tmem_full[2], tmem_empty[2];
+  uint32_t tmem_base;
+};
+
+struct MapSet {
+  CUtensorMap a[kCMaxRanks];
+};
+struct OutPtrs {
+  float* p[kCMaxRanks];
+};
+
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ bool wait_epoch(const uint32_t* flag, uint32_t epoch, uint32_t budget) {
+  for (uint32_t i = 0; i < budget; ++i) {
+    if ((int32_t)(ld_acquire_sys_u32(flag) - epoch) >= 0) return true;
+    if (i > 32) __nanosleep(100);
+  }
+  return false;
+}
+__device__ __forceinline__ void red_add_v4_f32_sys(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+// MODE 0: all-gather -> GEMM (A from maps.a[owner], C local, plain stores, fp32 or bf16)
+// MODE 1: GEMM -> reduce-scatter (A, B local = maps.a[0], C tiles red-added into outs.p[owner])
+template <int BN, int MODE, bool OUT_BF16>
+__global__ void __launch_bounds__(kCThreads, 1)
+gemm_coll_kernel(const __grid_constant__ MapSet maps, const __grid_constant__ CUtensorMap map_b, void* __restrict__ c,
+                 const __grid_constant__ OutPtrs outs, int M, int N, int K, int ldc, int rank, int world,
+                 const uint32_t* __restrict__ my_flags, int slot, uint32_t epoch, uint32_t budget, int* status) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  constexpr uint32_t kABytes = kCBM * kCBK * 2, kBBytes = BN * kCBK * 2, kStageBytes = kABytes + kBBytes;
+  uint8_t* tiles = smem;
+  CollSmem* sm = (CollSmem*)(smem + kCStages * kStageBytes);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = M / kCBM, tiles_n = (N + BN - 1) / BN, ntiles = tiles_m * tiles_n;
+  const int kblocks = (K + kCBK - 1) / kCBK;
+  const int m_local = M / world, tiles_m_local = m_local / kCBM;
+  // tile order: owner-major starting at the own rank (MODE 0) or at the next rank (MODE 1); within an owner n varies fastest
+  auto tile_coords = [&](int t, int& owner, int& m0, int& n0) {
+    const int per_owner = tiles_m_local * tiles_n;
+    const int o = t / per_owner, rest = t % per_owner;
+    owner = (rank + (MODE == 1 ? 1 : 0) + o) % world;
+    m0 = (owner * tiles_m_local + rest / tiles_n) * kCBM;
+    n0 = (rest % tiles_n) * BN;
+  };
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kCStages; ++i) { mbar_init(&sm->full[i], 1); mbar_init(&sm->empty[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&sm->tmem_full[i], 1); mbar_init(&sm->tmem_empty[i], 4); }
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&sm->tmem_base, 2 * BN);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = sm->tmem_base;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      prefetch_tensormap(&map_b);
+      int st = 0, ph = 0;
+      bool ok = true;
+      uint32_t ready = 1u << rank;  // owners whose shard is known to be written
+      for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+        int owner, m0, n0;
+        tile_coords(tile, owner, m0, n0);
+        if (MODE == 0 && !((ready >> owner) & 1u)) {
+          if (!wait_epoch(my_flags + slot * kCMaxRanks + owner, epoch, budget)) {
+            set_status(status, PEAR_ERR_FLAG_TIMEOUT);
+            // keep the pipeline protocol alive with local data so the other warps drain and the kernel returns
+            owner = rank;
+            m0 = rank * m_local;
+          } else {
+            ready |= 1u << owner;
+          }
+        }
+        const CUtensorMap* ma = MODE == 0 ? &maps.a[owner] : &maps.a[0];
+        const int am0 = MODE == 0 ? m0 - owner * m_local : m0;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          ok = mbar_wait_bounded(&sm->empty[st], ph ^ 1, status);
+          if (!ok) break;
+          uint8_t* a = tiles + st * kStageBytes;
+          mbar_expect_tx(&sm->full[st], kStageBytes);
+          tma_load_2d(a, ma, kb * kCBK, am0, &sm->full[st]);
+          tma_load_2d(a + kABytes, &map_b, kb * kCBK, n0, &sm->full[st]);
+          if (++st == kCStages) { st = 0; ph ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_f16(kCBM, BN, 1);
+      int st = 0, ph = 0, it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++it) {
+        const int ab = it & 1;
+        ok = mbar_wait_bounded(&sm->tmem_empty[ab], ((it >> 1) & 1) ^ 1, status);
+        if (!ok) break;
+        tcgen05_fence_after();
+        const uint32_t d_tmem = tmem_base + ab * BN;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          ok = mbar_wait_bounded(&sm->full[st], ph, status);
+          if (!ok) break;
+          tcgen05_fence_after();
+          const uint32_t a_addr = smem_u32(tiles + st * kStageBytes);
+          const uint64_t da = umma_desc_sw128(a_addr), db = umma_desc_sw128(a_addr + kABytes);
+#pragma unroll
+          for (int k = 0; k < kCBK / 16; ++k)
+            umma_f16(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) != 0 ? 1u : 0u);
+          tcgen05_commit(&sm->empty[st]);
+          if (++st == kCStages) { st = 0; ph ^= 1; }
+        }
+        tcgen05_commit(&sm->tmem_full[ab]);
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    int it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++it) {
+      const int ab = it & 1;
+      int owner, m0, n0;
+      tile_coords(tile, owner, m0, n0);
+      if (ok) ok = mbar_wait_bounded(&sm->tmem_full[ab], (it >> 1) & 1, status);
+      if (!ok) break;
+      tcgen05_fence_after();
+      const int row = m0 + q * 32 + lane;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + ab * BN + c0, r);
+        tcgen05_wait_ld();
+        const int col = n0 + c0;
+        if (MODE == 1) {
+          // the owner's accumulation buffer holds ITS rows only: [M / world, ldc] fp32
+          float* dst = outs.p[owner] + (size_t)(row - owner * m_local) * ldc + col;
+          if (col + 32 <= N) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+              red_add_v4_f32_sys(dst + j, __uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
+                                 __uint_as_float(r[j + 3]));
+          } else {
+            for (int j = 0; j < 32; ++j)
+              if (col + j < N) atomicAdd_system(dst + j, __uint_as_float(r[j]));
+          }
+        } else if (OUT_BF16) {
+          __nv_bfloat16* dst = (__nv_bfloat16*)c + (size_t)row * ldc + col;
+          if (col + 32 <= N) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              uint4 v;
+              __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+              __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+              __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
+              __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
+              v.x = *(uint32_t*)&p0; v.y = *(uint32_t*)&p1; v.z = *(uint32_t*)&p2; v.w = *(uint32_t*)&p3;
+              *(uint4*)(dst + j) = v;
+            }
+          } else {
+            for (int j = 0; j < 32; ++j)
+              if (col + j < N) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+          }
+        } else {
+          float* dst = (float*)c + (size_t)row * ldc + col;
+          if (col + 32 <= N) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+              *(float4*)(dst + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
+                                                __uint_as_float(r[j + 3]));
+          } else {
+            for (int j = 0; j < 32; ++j)
+              if (col + j < N) dst[j] = __uint_as_float(r[j]);
+          }
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sm->tmem_empty[ab]);
+    }
+    if (MODE == 1) __threadfence_system();  // the adds are performed before the host-ordered "done" signal that follows the kernel
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, 2 * BN);
+  }
+}
+
+static PFN_cuTensorMapEncodeTiled_v12000 coll_encode() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  if (!fn) {
+    cudaDriverEntryPointQueryResult q;
+    void* p = nullptr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = (PFN_cuTensorMapEncodeTiled_v12000)p;
+  }
+  return fn;
+}
+
+static int coll_map_bf16(CUtensorMap* map, const void* base, int rows, int cols, int ld, int box_rows) {
+  auto enc = coll_encode();
+  if (!enc) return (int)cudaErrorNotSupported;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)kCBK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : 1000 + (int)r;
+}
+
+template <int BN, int MODE, bool OUT_BF16>
+static int launch_coll(const MapSet& maps, const CUtensorMap& mb, void* c, const OutPtrs& outs, int M, int N, int K, int ldc, int rank,
+                       int world, const uint32_t* flags, int slot, uint32_t epoch, uint32_t budget, int* status, int num_sms,
+                       cudaStream_t stream) {
+  constexpr int smem = kCStages * (kCBM * kCBK * 2 + BN * kCBK * 2) + 1024;
+  static bool configured = false;
+  if (!configured) {
+    PEAR_CUDA_CHECK(cudaFuncSetAttribute(gemm_coll_kernel<BN, MODE, OUT_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    configured = true;
+  }
+  const int ntiles = (M / kCBM) * ((N + BN - 1) / BN);
+  const int grid = ntiles < num_sms ? ntiles : num_sms;
+  gemm_coll_kernel<BN, MODE, OUT_BF16><<<grid, kCThreads, smem, stream>>>(maps, mb, c, outs, M, N, K, ldc, rank, world, flags, slot, epoch,
+                                                                          budget, status);
+  PEAR_LAUNCH_CHECK();
+  return 0;
+}
+
+}  // namespace pear
+
+using namespace pear;
+
+// all-gather -> GEMM. a_shards[r]: rank r's [M / world, K] bf16 shard (symmetric memory, leading dimension lda);
+// my_flags: this rank's signal region; the owner of shard r must have signalled `epoch` in `slot` (pear_symm_signal)
+// after writing it. C [M, N] is local (fp32 or bf16). M / world must be a multiple of 128.
+PEAR_API int pear_ag_gemm_bf16(const void* const* a_shards, const void* b, void* c, int M, int N, int K, int lda, int ldb, int ldc,
+                               int out_bf16, int rank, int world, const void* my_flags, int slot, unsigned epoch, unsigned budget,
+                               int* status, int num_sms, void* stream) {
+  if (world < 1 || world > kCMaxRanks || M % (world * kCBM) || (lda % 8) || (ldb % 8)) return (int)cudaErrorInvalidValue;
+  MapSet maps;
+  for (int r = 0; r < world; ++r) {
+    int e = coll_map_bf16(&maps.a[r], a_shards[r], M / world, K, lda, kCBM);
+    if (e) return e;
+  }
+  for (int r = world; r < kCMaxRanks; ++r) maps.a[r] = maps.a[0];
+  CUtensorMap mb;
+  int e = coll_map_bf16(&mb, b, N, K, ldb, 256);
+  if (e) return e;
+  OutPtrs outs{};
+  cudaStream_t s = (cudaStream_t)stream;
+  return out_bf16 ? launch_coll<256, 0, true>(maps, mb, c, outs, M, N, K, ldc, rank, world, (const uint32_t*)my_flags, slot, epoch, budget, status, num_sms, s)
+                  : launch_coll<256, 0, false>(maps, mb, c, outs, M, N, K, ldc, rank, world, (const uint32_t*)my_flags, slot, epoch, budget, status, num_sms, s);
+}
+
+// GEMM -> reduce-scatter. A [M, K_local], B [N, K_local] local bf16; acc[r]: rank r's fp32 [M / world, ldc] accumulation
+// buffer in symmetric memory, zeroed by its owner before any rank launches (order that with pear_symm_signal / wait).
+// After the kernel, signal completion; the owner waits for every rank's signal before reading its buffer.
+PEAR_API int pear_gemm_rs_bf16(const void* a, const void* b, void* const* acc, int M, int N, int K, int lda, int ldb, int ldc, int rank,
+                               int world, int* status, int num_sms, void* stream) {
+  if (world < 1 || world > kCMaxRanks || M % (world * kCBM) || (lda % 8) || (ldb % 8) || (ldc % 4) || N % 4) return (int)cudaErrorInvalidValue;
+  MapSet maps;
+  int e = coll_map_bf16(&maps.a[0], a, M, K, lda, kCBM);
+  if (e) return e;
+  for (int r = 1; r < kCMaxRanks; ++r) maps.a[r] = maps.a[0];
+  CUtensorMap mb;
+  e = coll_map_bf16(&mb, b, N, K, ldb, 256);
+  if (e) return e;
+  OutPtrs outs{};
+  for (int r = 0; r < world; ++r) outs.p[r] = (float*)acc[r];
+  return launch_coll<256, 1, false>(maps, mb, nullptr, outs, M, N, K, ldc, rank, world, nullptr, 0, 0, 0, status, num_sms, (cudaStream_t)stream);
+}

@@ -1,0 +1,170 @@
+"""Symmetric memory over NVLink / NVSwitch and the kernels that use it.
+
+Every rank of a process group allocates the same buffers (``torch.distributed._symmetric_memory``) and learns every
+peer's address; the kernels of ``ops/csrc/comm_kernels.cu`` and ``ops/csrc/gemm_collective.cu`` then read or write peer
+memory directly. This module owns the buffers, the flag protocol (slots x source ranks of monotonically growing
+epochs) and the Python entry points:
+
+* ``all_reduce_add_rmsnorm``: tensor-parallel partial rows -> all-reduce + fp32 residual add + (1 + w) RMSNorm, one
+  kernel (upstream ``rollout/blackwell/csrc/ar_norm.cu`` at TP2; here any power of two up to 8);
+* ``ag_gemm``: all-gather -> GEMM with the A tiles pulled from their owners by the GEMM's own TMA producer;
+* ``gemm_rs``: GEMM -> reduce-scatter with the epilogue adding tiles into the owner's buffer;
+* ``pull_quantize_nvfp4``: weight broadcast fused with bf16 -> NVFP4 requantisation on the receiver (the NVSwitch
+  transport of the trainer -> rollout weight sync; upstream broadcasts with NCCL and casts afterwards,
+  ``rollout/checkpoint_engine.py:36-43``).
+
+Every device-side wait is bounded; ``check()`` raises if a kernel recorded a timeout.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import lib as _lib
+
+SLOTS = 32
+SLOT_AR, SLOT_AG, SLOT_RS_ZERO, SLOT_RS_DONE, SLOT_SYNC = 0, 1, 2, 3, 4
+DEFAULT_BUDGET = 1 << 22  # polls of >= 100 ns: a few hundred milliseconds, then the kernel gives up
+
+
+class SymmBuffer:
+    def __init__(self, tensor: torch.Tensor, ptrs: list[int]):
+        self.tensor, self.ptrs = tensor, ptrs
+        self.c_ptrs = (ctypes.c_void_p * len(ptrs))(*ptrs)
+
+
+class SymmWorld:
+    def __init__(self, group=None, device: Optional[torch.device] = None):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self._symm = symm_mem
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
+        if self.world > 8 or self.world & (self.world - 1):
+            raise ValueError(f"world size {self.world}: the NVSwitch kernels take a power of two up to 8")
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        self.flags = self.alloc((SLOTS * 8,), torch.int32)
+        self.flags.tensor.zero_()
+        self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
+        self.epochs = [0] * SLOTS
+        self.num_sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)
+
+    # -- memory -------------------------------------------------------------------------------------------------------
+    def alloc(self, shape, dtype) -> SymmBuffer:
+        t = self._symm.empty(shape, dtype=dtype, device=self.device)
+        h = self._symm.rendezvous(t, self.group.group_name)
+        buf = SymmBuffer(t, [int(p) for p in h.buffer_ptrs])
+        buf.handle = h
+        return buf
+
+    def check(self) -> None:
+        code = int(self.status[0].item())
+        if code != 0:
+            self.status.zero_()
+            raise RuntimeError(f"rank {self.rank}: a device-side wait on a peer gave up (status {code})")
+
+    # -- flags --------------------------------------------------------------------------------------------------------
+    def next_epoch(self, slot: int) -> int:
+        self.epochs[slot] += 1
+        return self.epochs[slot]
+
+    def signal(self, slot: int, epoch: int) -> None:
+        _lib.check(_lib.lib().pear_symm_signal(self.flags.c_ptrs, self.rank, self.world, slot, epoch, _lib.stream()), "symm_signal")
+
+    def wait(self, slot: int, epoch: int, budget: int = DEFAULT_BUDGET) -> None:
+        _lib.check(_lib.lib().pear_symm_wait(_lib.ptr(self.flags.tensor), self.world, slot, epoch, budget, _lib.ptr(self.status),
+                                              _lib.stream()), "symm_wait")
+
+    def device_barrier(self, slot: int = SLOT_SYNC) -> None:
+        """All ranks' streams meet: everything issued before on any rank is visible to everything issued after."""
+        e = self.next_epoch(slot)
+        self.signal(slot, e)
+        self.wait(slot, e)
+
+    # -- all-reduce + residual add + RMSNorm --------------------------------------------------------------------------
+    def make_ar_workspace(self, max_rows: int, hidden: int) -> SymmBuffer:
+        return self.alloc((2, max_rows, hidden), torch.bfloat16)
+
+    def all_reduce_add_rmsnorm(self, ws: SymmBuffer, partial: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor,
+                               eps: float = 1e-6, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``residual += sum_ranks(partial)`` (fp32, in place); returns ``rmsnorm(residual) * (1 + weight)`` in bf16."""
+        t, h = partial.shape
+        e = self.next_epoch(SLOT_AR)
+        ws.tensor[e & 1, :t].copy_(partial)
+        out = out if out is not None else torch.empty(t, h, dtype=torch.bfloat16, device=self.device)
+        buf_elems = ws.tensor.shape[1] * ws.tensor.shape[2]
+        if ws.tensor.shape[2] != h:
+            raise ValueError("workspace hidden size mismatch")
+        _lib.check(_lib.lib().pear_ar_add_rmsnorm(ws.c_ptrs, self.flags.c_ptrs, self.rank, self.world, SLOT_AR, e, _lib.ptr(residual),
+                                                   _lib.ptr(weight), _lib.ptr(out), t, h, ctypes.c_size_t(buf_elems), ctypes.c_float(eps),
+                                                   DEFAULT_BUDGET, _lib.ptr(self.status), 2 * self.num_sms, _lib.stream()), "ar_add_rmsnorm")
+        _lib.LAUNCH_COUNT += 1
+        return out
+
+    # -- all-gather -> GEMM -------------------------------------------------------------------------------------------
+    def ag_gemm(self, a_shard: SymmBuffer, b: torch.Tensor, out_dtype=torch.float32) -> torch.Tensor:
+        """``C = concat_ranks(A_shard) @ B^T``. ``a_shard.tensor`` [M / world, K] bf16 must be written on this stream
+        before the call; the call publishes it and the kernel pulls the other shards from their owners."""
+        ml, k = a_shard.tensor.shape
+        n = b.shape[0]
+        m = ml * self.world
+        c = torch.empty(m, n, dtype=out_dtype, device=self.device)
+        e = self.next_epoch(SLOT_AG)
+        self.signal(SLOT_AG, e)
+        _lib.check(_lib.lib().pear_ag_gemm_bf16(a_shard.c_ptrs, _lib.ptr(b), _lib.ptr(c), m, n, k, a_shard.tensor.stride(0), b.stride(0),
+                                                 c.stride(0), 1 if out_dtype == torch.bfloat16 else 0, self.rank, self.world,
+                                                 _lib.ptr(self.flags.tensor), SLOT_AG, e, DEFAULT_BUDGET, _lib.ptr(self.status), self.num_sms,
+                                                 _lib.stream()), "ag_gemm")
+        _lib.LAUNCH_COUNT += 1
+        return c
+
+    def ag_gemm_done(self) -> None:
+        """Call before overwriting the A shard again: every rank has finished pulling it."""
+        self.device_barrier()
+
+    # -- GEMM -> reduce-scatter ---------------------------------------------------------------------------------------
+    def make_rs_accumulator(self, rows_local: int, n: int) -> SymmBuffer:
+        return self.alloc((rows_local, n), torch.float32)
+
+    def gemm_rs(self, a: torch.Tensor, b: torch.Tensor, acc: SymmBuffer) -> torch.Tensor:
+        """``sum_ranks(A_r @ B_r^T)`` restricted to this rank's rows; returns ``acc.tensor`` (fp32 [M / world, N])."""
+        m, k = a.shape
+        n = b.shape[0]
+        acc.tensor.zero_()
+        e = self.next_epoch(SLOT_RS_ZERO)
+        self.signal(SLOT_RS_ZERO, e)
+        self.wait(SLOT_RS_ZERO, e)  # every owner's buffer is zero before anyone adds into it
+        ptrs = (ctypes.c_void_p * self.world)(*acc.ptrs)
+        _lib.check(_lib.lib().pear_gemm_rs_bf16(_lib.ptr(a), _lib.ptr(b), ptrs, m, n, k, a.stride(0), b.stride(0), acc.tensor.stride(0),
+                                                 self.rank, self.world, _lib.ptr(self.status), self.num_sms, _lib.stream()), "gemm_rs")
+        _lib.LAUNCH_COUNT += 1
+        e = self.next_epoch(SLOT_RS_DONE)
+        self.signal(SLOT_RS_DONE, e)
+        self.wait(SLOT_RS_DONE, e)  # every rank's adds have landed in my buffer
+        return acc.tensor
+
+    # -- weight sync: pull bf16 from the sender, write NVFP4 ----------------------------------------------------------
+    def pull_quantize_nvfp4(self, staging: SymmBuffer, src_rank: int, rows: int, k: int) -> tuple[torch.Tensor, float]:
+        """Receiver side: read ``[rows, k]`` bf16 from ``src_rank``'s staging buffer over NVLink and return the weight in
+        the decode megakernel's NVFP4 stage layout plus its power-of-two tensor scale. The sender must have published
+        the buffer (``device_barrier`` after writing it)."""
+        import math
+
+        src = staging.ptrs[src_rank]
+        bits = torch.zeros(1, dtype=torch.int32, device=self.device)
+        lib = _lib.lib()
+        _lib.check(lib.pear_amax_bf16(ctypes.c_void_p(src), ctypes.c_size_t(rows * k), _lib.ptr(bits), _lib.stream()), "amax_bf16")
+        amax = float(bits.view(torch.float32).item())
+        gs = 1.0 if (amax <= 0.0 or not math.isfinite(amax)) else 2.0 ** math.floor(math.log2(448.0 * 6.0 / amax))
+        tiles = (rows + 127) // 128
+        packed = torch.zeros(tiles, k // 256, 18432, dtype=torch.uint8, device=self.device)
+        _lib.check(lib.pear_bcast_quant_nvfp4(ctypes.c_void_p(src), rows, k, k, ctypes.c_float(gs), _lib.ptr(packed), _lib.stream()),
+                   "bcast_quant_nvfp4")
+        _lib.LAUNCH_COUNT += 2
+        return packed, gs

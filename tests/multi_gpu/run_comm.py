@@ -1,0 +1,135 @@
+"""Worker of the multi-GPU kernel tests (one process per GPU under ``torch.distributed.run``): each fused
+compute+collective kernel is compared with a plain fp32 PyTorch / NCCL reference of the same op. Prints one ``PASS`` line
+per check; any exception fails the run. Timings (CUDA events, max over ranks) are printed for the bench notes."""
+
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+
+from pear_b200.models import nvfp4  # noqa: E402
+from pear_b200.parallel.symm import SymmWorld  # noqa: E402
+
+
+def timed(fn, iters=10, warmup=3):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / iters], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def main() -> int:
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ["LOCAL_RANK"])))
+    sw = SymmWorld()
+    g = torch.Generator(device="cuda").manual_seed(1234)  # same stream of numbers on every rank
+    big = len(sys.argv) > 1 and sys.argv[1] == "big"
+
+    # ---- all-reduce + residual add + RMSNorm
+    T, H = 8, 5120
+    parts = torch.randn(world, T, H, device="cuda", generator=g) * 0.5
+    resid0 = torch.randn(T, H, device="cuda", generator=g)
+    w = torch.randn(H, device="cuda", generator=g) * 0.1
+    ws = sw.make_ar_workspace(64, H)
+    for it in range(3):  # several epochs: both parities of the double buffer
+        resid = resid0.clone()
+        out = sw.all_reduce_add_rmsnorm(ws, parts[rank].to(torch.bfloat16), resid, w, 1e-6)
+        torch.cuda.synchronize()
+        sw.check()
+        ref_r = resid0 + parts.to(torch.bfloat16).float().sum(0)
+        ref = ref_r * torch.rsqrt(ref_r.pow(2).mean(-1, keepdim=True) + 1e-6) * (1 + w)
+        assert torch.allclose(resid, ref_r, atol=1e-5, rtol=1e-5), (resid - ref_r).abs().max()
+        assert torch.allclose(out.float(), ref, atol=2e-2, rtol=2e-2), (out.float() - ref).abs().max()
+    if rank == 0:
+        print("PASS all_reduce_add_rmsnorm", flush=True)
+
+    # ---- all-gather -> GEMM
+    M, N, K = (world * 1024, 4096, 4096) if big else (world * 256, 512, 512)
+    a_full = (torch.randn(M, K, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
+    b = (torch.randn(N, K, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
+    shard = sw.alloc((M // world, K), torch.bfloat16)
+    shard.tensor.copy_(a_full[rank * (M // world):(rank + 1) * (M // world)])
+    c = sw.ag_gemm(shard, b, torch.float32)
+    torch.cuda.synchronize()
+    sw.check()
+    ref = a_full.float() @ b.float().t()
+    err = (c - ref).abs().max().item()
+    assert err <= 2e-2 * ref.abs().max().item() + 1e-3, err
+    sw.ag_gemm_done()
+    if rank == 0:
+        print("PASS ag_gemm", flush=True)
+
+    # ---- GEMM -> reduce-scatter
+    Kl = K // world
+    a_loc = a_full[:, rank * Kl:(rank + 1) * Kl].contiguous()
+    b_loc = b[:, rank * Kl:(rank + 1) * Kl].contiguous()
+    acc = sw.make_rs_accumulator(M // world, N)
+    out = sw.gemm_rs(a_loc, b_loc, acc)
+    torch.cuda.synchronize()
+    sw.check()
+    mine = ref[rank * (M // world):(rank + 1) * (M // world)]
+    err = (out - mine).abs().max().item()
+    assert err <= 2e-2 * ref.abs().max().item() + 1e-3, err
+    if rank == 0:
+        print("PASS gemm_rs", flush=True)
+
+    # ---- weight broadcast fused with NVFP4 requantisation (rank 0 is the trainer)
+    rows, k = 384, 1024
+    wsrc = (torch.randn(rows, k, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+    staging = sw.alloc((rows, k), torch.bfloat16)
+    if rank == 0:
+        staging.tensor.copy_(wsrc)
+    sw.device_barrier()
+    packed, gs = sw.pull_quantize_nvfp4(staging, 0, rows, k)
+    torch.cuda.synchronize()
+    ref_packed, ref_gs = nvfp4.quantize_packed(wsrc.float())
+    assert gs == ref_gs, (gs, ref_gs)
+    assert torch.equal(packed.cpu(), ref_packed.cpu()), (packed.cpu() != ref_packed.cpu()).sum()
+    sw.device_barrier()
+    if rank == 0:
+        print("PASS pull_quantize_nvfp4", flush=True)
+
+    # ---- timings against the unfused NCCL + cuBLAS sequence
+    if big:
+        gathered = torch.empty(M, K, dtype=torch.bfloat16, device="cuda")
+
+        def unfused_ag():
+            dist.all_gather_into_tensor(gathered, shard.tensor)
+            return gathered @ b.t()
+
+        def fused_ag():
+            r = sw.ag_gemm(shard, b, torch.bfloat16)
+            sw.ag_gemm_done()
+            return r
+
+        t_ref, t_own = timed(unfused_ag), timed(fused_ag)
+        rs_out = torch.empty(M // world, N, dtype=torch.bfloat16, device="cuda")
+
+        def unfused_rs():
+            dist.reduce_scatter_tensor(rs_out, a_loc @ b_loc.t())
+
+        t_ref2, t_own2 = timed(unfused_rs), timed(lambda: sw.gemm_rs(a_loc, b_loc, acc))
+        sw.check()
+        if rank == 0:
+            print(f"TIMING world {world} M {M} N {N} K {K}: ag_gemm fused {t_own:.3f} ms vs nccl+cublas {t_ref:.3f} ms; "
+                  f"gemm_rs fused {t_own2:.3f} ms vs cublas+nccl {t_ref2:.3f} ms", flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

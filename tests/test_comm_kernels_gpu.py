@@ -1,0 +1,26 @@
+"""Fused compute+collective kernels over NVLink peer memory: needs at least two GPUs (skipped otherwise). The ranks run
+as child processes, one per GPU, with NVLS off and every device-side wait bounded."""
+
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.timeout(600)
+def test_fused_collective_kernels_two_ranks():
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=root)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29533", os.path.join(root, "tests", "multi_gpu", "run_comm.py")]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=540)
+    out = r.stdout + r.stderr
+    assert r.returncode == 0, out[-4000:]
+    for name in ("all_reduce_add_rmsnorm", "ag_gemm", "gemm_rs", "pull_quantize_nvfp4"):
+        assert f"PASS {name}" in out, out[-4000:]
