@@ -1,0 +1,99 @@
+"""Python bindings of the stand-alone rollout kernels (``csrc/rollout_kernels.cu``): fused sampler, rejection sampler of
+greedy drafts, GDN decode step, split-KV paged attention, embedding merge, paged-KV block gather/scatter."""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import lib as _lib
+
+_f = ctypes.c_float
+
+
+def fused_sample(logits: torch.Tensor, temperature: float, noise_u: torch.Tensor, topk: int = 32, chunks: int = 0):
+    """Returns (token, logprob, topk ids, topk log-probs, rank, nonfinite count) per row; see ``reference.sample_exponential_race``."""
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and noise_u.is_contiguous()
+    rows, v = logits.shape
+    if chunks <= 0:
+        chunks = max(1, min(64, (2 * 148 + rows - 1) // rows))
+    dev = logits.device
+    ws = torch.empty(_lib.lib().pear_sample_workspace_bytes(rows, chunks), dtype=torch.uint8, device=dev)
+    tok = torch.empty(rows, dtype=torch.int32, device=dev)
+    lp = torch.empty(rows, dtype=torch.float32, device=dev)
+    tid = torch.empty(rows, topk, dtype=torch.int32, device=dev)
+    tlp = torch.empty(rows, topk, dtype=torch.float32, device=dev)
+    rank = torch.empty(rows, dtype=torch.int32, device=dev)
+    nf = torch.empty(rows, dtype=torch.int32, device=dev)
+    _lib.check(_lib.lib().pear_fused_sample(_lib.ptr(logits), rows, v, logits.stride(0), _f(temperature), _lib.ptr(noise_u), chunks, topk,
+                                            _lib.ptr(ws), _lib.ptr(tok), _lib.ptr(lp), _lib.ptr(tid), _lib.ptr(tlp), _lib.ptr(rank), _lib.ptr(nf),
+                                            _lib.stream()), "fused_sample")
+    _lib.count_launch(2)
+    return tok.long(), lp, tid.long(), tlp, rank.long(), nf.long()
+
+
+def verify_greedy(logits: torch.Tensor, drafts: torch.Tensor, temperature: float, accept_u: torch.Tensor, noise_u: torch.Tensor):
+    """logits [requests, n_draft + 1, V]; drafts [requests, n_draft]. Returns (tokens [requests, n_draft + 1] with -1 after the
+    stop, accepted count per request, log-probs)."""
+    r, rows, v = logits.shape
+    n = rows - 1
+    logits = logits.contiguous()
+    dev = logits.device
+    out = torch.empty(r, rows, dtype=torch.int32, device=dev)
+    acc = torch.empty(r, dtype=torch.int32, device=dev)
+    lp = torch.zeros(r, rows, dtype=torch.float32, device=dev)
+    _lib.check(_lib.lib().pear_verify_greedy(_lib.ptr(logits), r, n, v, v, _f(temperature), _lib.ptr(drafts.int().contiguous()),
+                                             _lib.ptr(accept_u.contiguous()), _lib.ptr(noise_u.contiguous()), _lib.ptr(out), _lib.ptr(acc),
+                                             _lib.ptr(lp), _lib.stream()), "verify_greedy")
+    _lib.count_launch(1)
+    return out.long(), acc.long(), lp
+
+
+def gdn_decode(x, z, a, b, conv_w, A_log, dt_bias, norm_w, conv_state, state, slots, hk: int, hv: int, l2_eps=1e-6, rms_eps=1e-6):
+    """One decode token per sequence; updates ``conv_state`` [slots, 3, C] and ``state`` [slots, Hv, 128, 128] in place."""
+    batch = x.shape[0]
+    out = torch.empty(batch, hv * 128, dtype=torch.float32, device=x.device)
+    _lib.check(_lib.lib().pear_gdn_decode(_lib.ptr(x), _lib.ptr(z), _lib.ptr(a), _lib.ptr(b), _lib.ptr(conv_w), _lib.ptr(A_log), _lib.ptr(dt_bias),
+                                          _lib.ptr(norm_w), _lib.ptr(conv_state), _lib.ptr(state), _lib.ptr(slots.int()), _lib.ptr(out), batch, hk, hv,
+                                          _f(l2_eps), _f(rms_eps), _lib.stream()), "gdn_decode")
+    _lib.count_launch(2)
+    return out
+
+
+def paged_attention(q, k_cache, v_cache, block_table, ctx_len, scale: float, nsplit: int = 0):
+    """q [rows, Hq, D] fp32; caches [blocks, 16, Hkv, D] bf16; block_table [rows, max_blocks] int32; ctx_len [rows] int32."""
+    rows, hq, d = q.shape
+    hkv = k_cache.shape[2]
+    if nsplit <= 0:
+        nsplit = max(1, min(32, (2 * 148) // max(1, rows * hkv)))
+    dev = q.device
+    part_o = torch.empty(rows * hq * nsplit * d, dtype=torch.float32, device=dev)
+    part_ml = torch.empty(rows * hq * nsplit * 2, dtype=torch.float32, device=dev)
+    out = torch.empty(rows, hq, d, dtype=torch.float32, device=dev)
+    _lib.check(_lib.lib().pear_paged_attention(_lib.ptr(q.contiguous()), _lib.ptr(k_cache), _lib.ptr(v_cache), _lib.ptr(block_table.int().contiguous()),
+                                               block_table.shape[1], _lib.ptr(ctx_len.int().contiguous()), rows, hq, hkv, d, _f(scale), nsplit,
+                                               _lib.ptr(part_o), _lib.ptr(part_ml), _lib.ptr(out), _lib.stream()), "paged_attention")
+    _lib.count_launch(2)
+    return out
+
+
+def embed_merge(ids: torch.Tensor, table: torch.Tensor, embeds: Optional[torch.Tensor] = None, mask: Optional[torch.Tensor] = None):
+    t, (v, h) = ids.shape[0], table.shape
+    out = torch.empty(t, h, dtype=torch.float32, device=ids.device)
+    m = mask.to(torch.uint8).contiguous() if mask is not None else None
+    _lib.check(_lib.lib().pear_embed_merge(_lib.ptr(ids.int().contiguous()), _lib.ptr(table), _lib.ptr(embeds.float().contiguous() if embeds is not None else None),
+                                           _lib.ptr(m), _lib.ptr(out), t, h, v, _lib.stream()), "embed_merge")
+    _lib.count_launch(1)
+    return out
+
+
+def kv_blocks_copy(cache: torch.Tensor, staging: torch.Tensor, block_ids: torch.Tensor, to_staging: bool) -> None:
+    """cache [blocks, ...] and staging [n, ...] with equal per-block byte size (a multiple of 16)."""
+    n = block_ids.numel()
+    bb = cache[0].numel() * cache.element_size()
+    assert staging[0].numel() * staging.element_size() == bb and staging.shape[0] >= n
+    _lib.check(_lib.lib().pear_kv_blocks_copy(_lib.ptr(cache), _lib.ptr(staging), _lib.ptr(block_ids.int().contiguous()), n, bb, 1 if to_staging else 0,
+                                              _lib.stream()), "kv_blocks_copy")
+    _lib.count_launch(1)

@@ -1,0 +1,128 @@
+"""Stand-alone rollout kernels against plain PyTorch fp32 references of the same ops."""
+
+import math
+
+import pytest
+import torch
+
+from pear_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    from pear_b200.ops import rollout_ops
+    return rollout_ops
+
+
+def test_fused_sampler(ops):
+    g = torch.Generator(device="cuda").manual_seed(0)
+    for rows, v, k in ((4, 248320, 32), (3, 5000, 8), (1, 1024, 32)):
+        logits = torch.randn(rows, v, device="cuda", generator=g) * 3
+        u = torch.rand(rows, v, device="cuda", generator=g)
+        tok, lp, tid, tlp, rank, nf = ops.fused_sample(logits, 0.7, u, k)
+        rt, rlp, rid, rtlp, rrank, rnf = ref.sample_exponential_race(logits, 0.7, u, k)
+        assert torch.equal(tok, rt) and torch.equal(rank, rrank) and torch.equal(nf, rnf)
+        assert torch.allclose(lp, rlp, atol=1e-3) and torch.allclose(tlp, rtlp, atol=1e-3) and torch.equal(tid, rid)
+    bad = torch.randn(2, 4096, device="cuda", generator=g)
+    bad[0, 5], bad[1, 7], bad[1, 9] = float("nan"), float("inf"), float("-inf")
+    nf = ops.fused_sample(bad, 1.0, torch.rand(2, 4096, device="cuda", generator=g), 4)[5]
+    assert nf.tolist() == [1, 1]
+
+
+def test_verify_greedy(ops):
+    g = torch.Generator(device="cuda").manual_seed(1)
+    r, n, v = 6, 3, 4096
+    logits = torch.randn(r, n + 1, v, device="cuda", generator=g) * 2
+    logp = torch.log_softmax(logits.float() / 0.9, -1)
+    drafts = logits[:, :n].argmax(-1)  # greedy drafts of the same distribution: high acceptance
+    drafts[1, 0] = 17  # an unlikely draft: rejected at row 0
+    au = torch.rand(r, n, device="cuda", generator=g)
+    u = torch.rand(r, n + 1, v, device="cuda", generator=g)
+    tok, acc, lp = ops.verify_greedy(logits, drafts, 0.9, au, u)
+    for i in range(r):
+        a = 0
+        while a < n and logp[i, a, drafts[i, a]] > math.log(max(float(au[i, a]), 1e-30)):
+            a += 1
+        assert int(acc[i]) == a
+        assert tok[i, :a].tolist() == drafts[i, :a].tolist()
+        z = logits[i, a].float() / 0.9
+        key = z - torch.log(-torch.log(u[i, a].clamp(1e-20, 1 - 1e-7)))
+        if a < n:
+            key[drafts[i, a]] = float("-inf")
+        assert int(tok[i, a]) == int(key.argmax()) and abs(float(lp[i, a]) - float(logp[i, a, tok[i, a]])) < 1e-3
+        assert (tok[i, a + 1:] == -1).all()
+
+
+def test_gdn_decode_step(ops):
+    g = torch.Generator(device="cuda").manual_seed(2)
+    B, Hk, Hv, D = 3, 4, 8, 128
+    C = 2 * Hk * D + Hv * D
+    rn = lambda *s: torch.randn(*s, device="cuda", generator=g)  # noqa: E731
+    conv_w, A_log, dt_bias, norm_w = rn(C, 4) * 0.5, rn(Hv) * 0.1, rn(Hv) * 0.1, rn(D) * 0.1 + 1
+    slots = torch.tensor([4, 0, 2], device="cuda")
+    conv_state, state = rn(6, 3, C) * 0.5, rn(6, Hv, D, D) * 0.1
+    cs_ref, st_ref = conv_state.clone(), state.clone()
+    for step in range(3):
+        x, z, a, b = rn(B, C), rn(B, Hv * D), rn(B, Hv), rn(B, Hv)
+        out = ops.gdn_decode(x, z, a, b, conv_w, A_log, dt_bias, norm_w, conv_state, state, slots, Hk, Hv)
+        for i in range(B):
+            s = int(slots[i])
+            y, fin = ref.causal_conv_silu(x[i:i + 1], conv_w, None, cs_ref[s][None])
+            cs_ref[s] = fin[0]
+            q = ref.l2norm(y[:, : Hk * D].view(1, Hk, D)) * D ** -0.5
+            k = ref.l2norm(y[:, Hk * D: 2 * Hk * D].view(1, Hk, D))
+            v = y[:, 2 * Hk * D:].view(1, Hv, D)
+            gg, beta = ref.gdn_gates(a[i:i + 1], b[i:i + 1], A_log, dt_bias)
+            o, st_ref[s] = ref.gdn_recurrent(q, k, v, gg, beta, st_ref[s])
+            want = ref.gated_rms_norm(o[0], z[i].view(Hv, D), norm_w).reshape(-1)
+            assert torch.allclose(out[i], want, atol=2e-4, rtol=2e-3), (out[i] - want).abs().max()
+        assert torch.allclose(conv_state, cs_ref) and torch.allclose(state, st_ref, atol=1e-4, rtol=1e-3)
+
+
+def test_paged_attention(ops):
+    g = torch.Generator(device="cuda").manual_seed(3)
+    Hq, Hkv, D, nblocks = 12, 2, 256, 64
+    kc = (torch.randn(nblocks, 16, Hkv, D, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+    vc = (torch.randn(nblocks, 16, Hkv, D, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+    lens = [37, 160, 1, 203]
+    perm = torch.randperm(nblocks, device="cuda", generator=g)
+    table = torch.zeros(len(lens), 16, dtype=torch.int32, device="cuda")
+    off = 0
+    for i, n in enumerate(lens):
+        nb = (n + 15) // 16
+        table[i, :nb] = perm[off: off + nb]
+        off += nb
+    q = torch.randn(len(lens), Hq, D, device="cuda", generator=g)
+    out = ops.paged_attention(q, kc, vc, table, torch.tensor(lens, device="cuda"), D ** -0.5)
+    for i, n in enumerate(lens):
+        nb = (n + 15) // 16
+        k = kc[table[i, :nb].long()].reshape(-1, Hkv, D)[:n]
+        v = vc[table[i, :nb].long()].reshape(-1, Hkv, D)[:n]
+        want = ref.attention_with_cache(q[i:i + 1], k, v, n - 1, D ** -0.5)[0]
+        assert torch.allclose(out[i], want, atol=2e-3, rtol=2e-3), (out[i] - want).abs().max()
+
+
+def test_embed_merge_and_kv_block_copy(ops):
+    g = torch.Generator(device="cuda").manual_seed(4)
+    table = torch.randn(1000, 512, device="cuda", generator=g).to(torch.bfloat16)
+    ids = torch.randint(0, 1000, (33,), device="cuda", generator=g)
+    emb = torch.randn(33, 512, device="cuda", generator=g)
+    mask = torch.rand(33, device="cuda", generator=g) < 0.3
+    out = ops.embed_merge(ids, table, emb, mask)
+    want = torch.where(mask[:, None], emb, table[ids].float())
+    assert torch.equal(out, want)
+    assert torch.equal(ops.embed_merge(ids, table), table[ids].float())
+    cache = torch.randn(40, 16, 4, 64, device="cuda", generator=g).to(torch.bfloat16)
+    staging = torch.zeros(8, 16, 4, 64, dtype=torch.bfloat16, device="cuda")
+    bid = torch.tensor([3, 39, 0, 17, 5], device="cuda")
+    ops.kv_blocks_copy(cache, staging, bid, True)
+    assert torch.equal(staging[:5], cache[bid])
+    cache2 = torch.zeros_like(cache)
+    ops.kv_blocks_copy(cache2, staging, bid, False)
+    others = torch.ones(40, dtype=torch.bool, device="cuda")
+    others[bid] = False
+    assert torch.equal(cache2[bid], cache[bid]) and not cache2[others].any()
