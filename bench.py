@@ -25,11 +25,28 @@ BASELINE_TOK_S = 921.0  # upstream README.md:52, 1 x GB300, NVFP4 batch-1 decode
 
 
 def reference_arm() -> None:
-    print(json.dumps({
-        "impl": "reference",
-        "unavailable": "reference cannot be installed offline: it needs verl, vLLM 0.34, LMCache and FlashInfer fetched "
-                       "by scripts/install.sh, and its decode megakernels refuse sm_100 (they require compute capability 10.3)",
-    }))
+    """The reference's own path for this metric is its sm_103a decode megakernel under a patched vLLM server. The
+    reference package itself installs offline (pure Python, into baseline/_ref); what decides is its own GPU check."""
+    here = os.path.dirname(os.path.abspath(__file__))
+    ref = os.path.join(here, "baseline", "_ref")
+    why = None
+    if not os.path.isdir(os.path.join(ref, "pear")):
+        why = "baseline/_ref is missing: python -m pip install --no-index --no-build-isolation --target baseline/_ref <reference> was not run"
+    else:
+        sys.path.insert(0, ref)
+        try:
+            import torch
+            from pear.models.qwen3_5.gpu_generation import GpuGeneration  # the reference's own module, unmodified
+            cap = torch.cuda.get_device_capability() if torch.cuda.is_available() else None
+            if not GpuGeneration.BLACKWELL_ULTRA.includes(cap):
+                why = (f"the reference's decode megakernel backend requires its GpuGeneration.BLACKWELL_ULTRA (compute capability 10.3, "
+                       f"built for sm_103a); this GPU is {cap}: pear/models/qwen3_5/deploy/blackwell/gpu_backend.py selects no backend here")
+            else:
+                why = ("the reference's deploy path needs its patched vLLM server and a ModelOpt NVFP4 checkpoint of the 27B model, "
+                       "neither of which exists offline")
+        except Exception as e:  # noqa: BLE001
+            why = f"reference import failed: {type(e).__name__}: {e}"
+    print(json.dumps({"impl": "reference", "unavailable": why}))
 
 
 class ClockSampler:
