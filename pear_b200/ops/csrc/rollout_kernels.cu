@@ -468,3 +468,38 @@ PEAR_API int pear_kv_blocks_copy(void* cache, void* staging, const int* block_id
   PEAR_LAUNCH_CHECK();
   return 0;
 }
+
+// ------------------------------------------------------------------------------------------------ no-allocation variant
+// pear_fused_sample with its workspace inside the library's own device image (declaration and contract:
+// pear_no_alloc.h). The array exists once per device; its address is looked up on the first call on each device.
+#include "pear_no_alloc.h"
+
+static __device__ __align__(256) unsigned char g_sample_scratch[PEAR_SAMPLE_STATIC_MAX_RECORDS * sizeof(pear::ChunkRec)];
+
+extern "C" __attribute__((visibility("default"))) int pear_fused_sample_static(
+    const float* logits, int rows, int V, int ld, float temperature, const float* noise, int chunks, int topk, int* tok, float* tok_lp,
+    int* top_id, float* top_lp, int* rank, int* nonfinite, void* stream) {
+  static void* scratch_of_device[64] = {nullptr};
+  if (topk < 1 || topk > kSampK || chunks < 1 || chunks > 64 || temperature <= 0.f || rows < 1 || V < 1) return PEAR_NOALLOC_BAD_ARGUMENT;
+  if (rows > PEAR_SAMPLE_STATIC_MAX_ROWS || (long long)rows * chunks > PEAR_SAMPLE_STATIC_MAX_RECORDS) return PEAR_NOALLOC_TOO_LARGE;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= 64) return (int)cudaErrorInvalidDevice;
+  if (scratch_of_device[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_sample_scratch);
+    if (e != cudaSuccess) return (int)e;
+    scratch_of_device[dev] = p;
+  }
+  ChunkRec* ws = (ChunkRec*)scratch_of_device[dev];
+  cudaStream_t s = (cudaStream_t)stream;
+  const size_t sh1 = (size_t)(2048 + kSampK) * 8 + kSampK * 8;
+  sample_chunks_kernel<<<dim3(chunks, rows), 256, sh1, s>>>(logits, V, ld, 1.f / temperature, noise, chunks, topk, ws);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return (int)e;
+  const size_t sh2 = (size_t)chunks * kSampK * 8 + kSampK * 8;
+  sample_rows_kernel<<<rows, 256, sh2, s>>>(logits, V, ld, 1.f / temperature, chunks, topk, ws, tok, tok_lp, top_id, top_lp, rank, nonfinite);
+  e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : (int)e;
+}
