@@ -75,3 +75,51 @@ def linear_bf16(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     if weight.shape[1] % 8 or x.numel() == 0:
         return torch.nn.functional.linear(x.to(weight.dtype), weight).float()
     return _LinearBF16.apply(x, weight)
+
+
+def _main() -> None:
+    """``python -m pear_b200.ops.gemm M N K [--iters I]``: time the tcgen05 GEMM against cuBLAS (CUDA events, L2 flushed
+    between iterations) and print one JSON line; the command profiles of this kernel are taken with."""
+    import argparse
+    import json
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("m", type=int)
+    ap.add_argument("n", type=int)
+    ap.add_argument("k", type=int)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    a = ap.parse_args()
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = (torch.randn(a.m, a.k, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
+    w = (torch.randn(a.n, a.k, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")  # larger than the 126 MB L2
+
+    def timed(fn) -> float:
+        for _ in range(a.warmup):
+            fn()
+        total = 0.0
+        for _ in range(a.iters):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            total += e0.elapsed_time(e1)
+        return total / a.iters
+
+    out = torch.empty(a.m, a.n, dtype=torch.bfloat16, device="cuda")
+    t_own = timed(lambda: gemm_nt(x, w, torch.bfloat16, out=out))
+    t_lib = timed(lambda: torch.matmul(x, w.t(), out=out))
+    ref = x.float() @ w.float().t()
+    err = float((gemm_nt(x, w, torch.float32) - ref).abs().max() / ref.abs().max())
+    fl = 2.0 * a.m * a.n * a.k
+    print(json.dumps({"m": a.m, "n": a.n, "k": a.k, "tcgen05_ms": round(t_own, 4), "cublas_ms": round(t_lib, 4),
+                      "tcgen05_tflops": round(fl / t_own / 1e9, 1), "cublas_tflops": round(fl / t_lib / 1e9, 1),
+                      "rel_err": err, "status": gemm_status()}))
+
+
+if __name__ == "__main__":
+    _main()
