@@ -201,7 +201,7 @@ def main() -> None:
         out = {
             "metric": "NVFP4 batch-1 decode tok/s", "value": round(value, 2), "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": warmup, "ms_per_step": round(step_ms, 4), "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": round(value / world / BASELINE_TOK_S, 4) if not args.small else None,
+            "scaling": "weak", "vs_baseline": round(value / BASELINE_TOK_S, 4) if not args.small else None,
             "dtype": "nvfp4 weights (e2m1 + e4m3 block scales), f16 activations, fp32 accumulate", "data": "synthetic",
             "config": {
                 "model": "27B-shape hybrid GDN+gated-attention (64 layers, hidden 5120), random init" if not args.small
