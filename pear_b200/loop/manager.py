@@ -65,6 +65,7 @@ class AgentLoopManager:
         self.loop = AgentLoop(self.router, self.pool, tokenizer or ByteTokenizer(), cfg, schemas, queue_, tracker)
         self.jobs: "queue.Queue" = queue.Queue()
         self.cancelled: set[str] = set()
+        self.errors: list[str] = []
         self.stop_flag = False
         self._rr = itertools.count()
         self.worker_queues = [queue.Queue() for _ in range(num_workers)]
@@ -85,7 +86,9 @@ class AgentLoopManager:
                 continue
             try:
                 fut.set_result(self.loop.run(uid, session, family, env_args))
-            except BaseException as e:  # noqa: BLE001
+            except BaseException as e:  # noqa: BLE001 - recorded so that the trainer fails fast instead of waiting for a group forever
+                import traceback
+                self.errors.append(f"{uid}/{session}: {type(e).__name__}: {e}\n{traceback.format_exc()}")
                 fut.set_exception(e)
             finally:
                 self.router.forget(f"{uid}/{session}")

@@ -98,8 +98,8 @@ class EngineConfig:
 
 class RolloutEngine:
     def __init__(self, model: HybridForCausalLM, cfg: EngineConfig, device="cpu"):
-        self.model, self.cfg = model.eval(), cfg
         self.device = torch.device(device)
+        self.model, self.cfg = model.eval().to(self.device), cfg
         n_slots = 2 * cfg.max_num_seqs + 64
         self.runner = ModelRunner(model, cfg.num_blocks, cfg.block_size, n_slots, device)
         self.host = None

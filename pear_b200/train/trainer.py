@@ -160,6 +160,16 @@ class Trainer:
             issued += 1
         return issued
 
+    def _while_waiting(self) -> None:
+        """Called by the replay buffer while it waits for groups: surface a failed episode worker at once."""
+        errs = getattr(self.manager, "errors", None)
+        if errs:
+            raise RuntimeError("an agent-loop worker failed:\n" + errs[0])
+        if self.progress is not None:
+            self.progress()
+        else:
+            time.sleep(0.01)
+
     # -- one step -----------------------------------------------------------------------------------------------------
     def _build(self, groups: list[PromptGroup]) -> tuple[list[PackedBatch], dict]:
         rows, rewards_all, lengths = [], [], []
@@ -184,7 +194,7 @@ class Trainer:
         t0 = time.time()
         cap = None if self.cfg.trainer_mode == "sync" else self.replay.max_inflight_sessions
         groups = self.replay.sample(self.engine.policy_version, self.cfg.train_batch_size, refill=self._refill,
-                                    timeout_s=self.cfg.sample_timeout_s, progress=self.progress)
+                                    timeout_s=self.cfg.sample_timeout_s, progress=self._while_waiting)
         t_gen = time.time() - t0
         mbs, stats = self._build(groups)
         total = stats.pop("_total_loss_tokens")
