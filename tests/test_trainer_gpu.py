@@ -12,7 +12,7 @@ def test_one_training_step_on_gpu(tmp_path):
     if not torch.cuda.is_available():
         pytest.skip("needs a GPU")
     from pear_b200.ops import lib as kl
-    from tests.test_trainer_e2e_cpu import _cfg
+    from test_trainer_e2e_cpu import _cfg
     from pear_b200.train.main import build_stack
 
     kl.lib()  # the CUDA library must be present on a GPU box
