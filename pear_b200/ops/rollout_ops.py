@@ -97,3 +97,53 @@ def kv_blocks_copy(cache: torch.Tensor, staging: torch.Tensor, block_ids: torch.
     _lib.check(_lib.lib().pear_kv_blocks_copy(_lib.ptr(cache), _lib.ptr(staging), _lib.ptr(block_ids.int().contiguous()), n, bb, 1 if to_staging else 0,
                                               _lib.stream()), "kv_blocks_copy")
     _lib.count_launch(1)
+
+
+def logprob_entropy_fused(hidden: torch.Tensor, weight: torch.Tensor, ids: torch.Tensor, temperature: float = 1.0,
+                          row_chunk: int = 1024, vocab_chunk: int = 16384):
+    """Forward of the fused head: log-probs at ``ids`` [T, J] and the entropy per row, with the logits produced chunk by
+    chunk by the tcgen05 GEMM ([row_chunk, vocab_chunk] fp32, sized to stay in L2) and folded into running softmax
+    statistics; the full [T, V] logits never exist. ``hidden`` [T, H], ``weight`` [V, H] (cast to bf16 operands)."""
+    from .gemm import gemm_nt
+
+    t, h = hidden.shape
+    v = weight.shape[0]
+    j = ids.shape[1]
+    dev = hidden.device
+    hb = hidden.to(torch.bfloat16).contiguous()
+    wb = weight.to(torch.bfloat16).contiguous()
+    ids32 = ids.int().contiguous()
+    lp = torch.empty(t, j, dtype=torch.float32, device=dev)
+    ent = torch.empty(t, dtype=torch.float32, device=dev)
+    lib = _lib.lib()
+    buf = torch.empty(min(row_chunk, t), min(vocab_chunk, v), dtype=torch.float32, device=dev)
+    for r0 in range(0, t, row_chunk):
+        r1 = min(t, r0 + row_chunk)
+        n = r1 - r0
+        run = torch.zeros(n, 4, dtype=torch.float32, device=dev)
+        run[:, 0] = -3.4028234663852886e38
+        idz = torch.zeros(n, j, dtype=torch.float32, device=dev)
+        for v0 in range(0, v, vocab_chunk):
+            v1 = min(v, v0 + vocab_chunk)
+            out = buf[:n, : v1 - v0]
+            gemm_nt(hb[r0:r1], wb[v0:v1], torch.float32, out=out)
+            _lib.check(lib.pear_head_stats_update(_lib.ptr(out), n, out.stride(0), v1 - v0, v0, _f(temperature), _lib.ptr(run),
+                                                  _lib.ptr(ids32[r0:r1]), j, _lib.ptr(idz), _lib.stream()), "head_stats_update")
+            _lib.count_launch(2)
+        _lib.check(lib.pear_head_stats_finish(_lib.ptr(run), _lib.ptr(idz), j, _lib.ptr(lp[r0:r1]), _lib.ptr(ent[r0:r1]), n, _lib.stream()),
+                   "head_stats_finish")
+        _lib.count_launch(1)
+    return lp, ent
+
+
+def gdn_front(x: torch.Tensor, conv_w: torch.Tensor, cu_seqlens: list[int], qk_channels: int, eps: float = 1e-6) -> torch.Tensor:
+    """conv(4) + SiLU over packed sequences, q / k heads L2-normalised (q scaled by 128^-0.5). x [T, C] fp32."""
+    t, c = x.shape
+    starts = torch.empty(t, dtype=torch.int32)
+    for s, e in zip(cu_seqlens[:-1], cu_seqlens[1:]):
+        starts[s:e] = s
+    y = torch.empty_like(x)
+    _lib.check(_lib.lib().pear_gdn_front(_lib.ptr(x.contiguous()), _lib.ptr(conv_w.float().contiguous()), _lib.ptr(starts.to(x.device)), _lib.ptr(y), t, c,
+                                         qk_channels, _f(eps), _lib.stream()), "gdn_front")
+    _lib.count_launch(1)
+    return y

@@ -64,6 +64,10 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor | float = 1.0, top_p:
     """Exponential-race sampling ``argmax(log p - log(-log u))`` from the processed distribution (temperature, then
     top-k / top-p). ``temperature`` 0 means greedy. Log-probs are those of the processed distribution."""
     n, v = logits.shape
+    if logits.is_cuda and n > 0:
+        fast = _fused_sample_cuda(logits, temperature, top_p, top_k, topk_logprobs, generator, noise)
+        if fast is not None:
+            return fast
     nonfinite = count_nonfinite(logits)
     t = torch.as_tensor(temperature, dtype=torch.float32, device=logits.device).expand(n).reshape(n, 1)
     greedy = t <= 0
@@ -85,6 +89,33 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor | float = 1.0, top_p:
     if topk_logprobs > 0:
         top_lp, top_id = torch.topk(logp, min(topk_logprobs, v), dim=-1)
     return SampleOutput(tok, tok_lp, top_id, top_lp, ranks, nonfinite)
+
+
+def _scalar(x) -> Optional[float]:
+    if isinstance(x, (int, float)):
+        return float(x)
+    if torch.is_tensor(x) and x.numel() == 1:
+        return float(x.item())
+    return None
+
+
+def _fused_sample_cuda(logits, temperature, top_p, top_k, topk_logprobs, generator, noise) -> Optional[SampleOutput]:
+    """Temperature-only rows on a GPU go through the fused CUDA sampler (two launches instead of a dozen torch ops over
+    the vocabulary); anything else (greedy, top-k / top-p, per-row temperatures) takes the general path."""
+    t, tp = _scalar(temperature), _scalar(top_p)
+    if t is None or t <= 0 or tp is None or tp < 1.0 or (top_k and top_k > 0) or topk_logprobs > 32:
+        return None
+    from ..ops import rollout_ops
+
+    n, v = logits.shape
+    if noise is None:
+        noise = torch.rand(n, v, device=logits.device, generator=generator)
+    x = logits.float()
+    if x.stride(1) != 1:
+        x = x.contiguous()
+    k = max(1, topk_logprobs)
+    tok, lp, tid, tlp, rank, nf = rollout_ops.fused_sample(x, t, noise.contiguous(), k)
+    return SampleOutput(tok, lp, tid if topk_logprobs > 0 else None, tlp if topk_logprobs > 0 else None, rank, nf)
 
 
 @dataclass

@@ -126,3 +126,49 @@ def test_embed_merge_and_kv_block_copy(ops):
     others = torch.ones(40, dtype=torch.bool, device="cuda")
     others[bid] = False
     assert torch.equal(cache2[bid], cache[bid]) and not cache2[others].any()
+
+
+def test_rollout_sampler_uses_the_fused_kernel_on_gpu(ops):
+    from pear_b200.ops import lib as kl
+    from pear_b200.rollout import sampler
+    g = torch.Generator(device="cuda").manual_seed(5)
+    logits = torch.randn(3, 9000, device="cuda", generator=g)
+    noise = torch.rand(3, 9000, device="cuda", generator=g)
+    before = kl.LAUNCH_COUNT
+    out = sampler.sample(logits, 0.8, 1.0, -1, topk_logprobs=8, noise=noise)
+    assert kl.LAUNCH_COUNT == before + 2
+    want = sampler.sample(logits.cpu(), 0.8, 1.0, -1, topk_logprobs=8, noise=noise.cpu())
+    assert torch.equal(out.tokens.cpu(), want.tokens) and torch.allclose(out.logprobs.cpu(), want.logprobs, atol=1e-3)
+    assert torch.equal(out.topk_ids.cpu(), want.topk_ids) and torch.equal(out.ranks.cpu(), want.ranks)
+    # top-p rows take the general path
+    before = kl.LAUNCH_COUNT
+    sampler.sample(logits, 0.8, 0.9, -1, noise=noise)
+    assert kl.LAUNCH_COUNT == before
+
+
+def test_fused_head_forward(ops):
+    g = torch.Generator(device="cuda").manual_seed(6)
+    t, h, v, j = 300, 512, 40000, 5
+    hidden = torch.randn(t, h, device="cuda", generator=g)
+    w = torch.randn(v, h, device="cuda", generator=g) * 0.05
+    ids = torch.randint(0, v, (t, j), device="cuda", generator=g)
+    lp, ent = ops.logprob_entropy_fused(hidden, w, ids, 0.9, row_chunk=128, vocab_chunk=8192)
+    logits = hidden.to(torch.bfloat16).float() @ w.to(torch.bfloat16).float().t() / 0.9
+    logp = torch.log_softmax(logits, -1)
+    assert torch.allclose(lp, logp.gather(1, ids), atol=2e-3, rtol=1e-3)
+    assert torch.allclose(ent, -(logp.exp() * logp).sum(-1), atol=2e-3, rtol=1e-3)
+
+
+def test_gdn_front_end(ops):
+    g = torch.Generator(device="cuda").manual_seed(7)
+    hk, hv, d = 2, 4, 128
+    c = 2 * hk * d + hv * d
+    cu = [0, 5, 6, 40]
+    x = torch.randn(cu[-1], c, device="cuda", generator=g)
+    w = torch.randn(c, 4, device="cuda", generator=g) * 0.5
+    y = ops.gdn_front(x, w, cu, 2 * hk * d)
+    want, _ = ref.causal_conv_silu(x, w, cu)
+    q = ref.l2norm(want[:, : hk * d].view(-1, hk, d)).reshape(-1, hk * d) * d ** -0.5
+    k = ref.l2norm(want[:, hk * d: 2 * hk * d].view(-1, hk, d)).reshape(-1, hk * d)
+    want = torch.cat([q, k, want[:, 2 * hk * d:]], dim=1)
+    assert torch.allclose(y, want, atol=1e-5, rtol=1e-4), (y - want).abs().max()
