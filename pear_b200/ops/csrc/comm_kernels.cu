@@ -198,6 +198,24 @@ __global__ void bcast_quant_nvfp4_kernel(const __nv_bfloat16* __restrict__ src, 
   }
 }
 
+// ------------------------------------------------------------------------------------------------ logits all-gather
+// Vocab-parallel lm_head: every rank holds fp32 logits [T, Vs] of its vocabulary shard and writes them into the full
+// [T, V] buffer of EVERY rank at column offset rank * Vs with 16-byte stores over NVLink (upstream sg_logits / lg_gather,
+// rollout/blackwell/csrc/logits_gather.cu:32-68, for two ranks). Grid-stride over (peer, row, 4-float vector), peers
+// visited starting after the own rank so the ranks write to different targets at any moment. Completion is published by
+// pear_symm_signal after the kernel; readers wait with pear_symm_wait.
+__global__ void __launch_bounds__(256) logits_allgather_kernel(const float4* __restrict__ shard, PeerPtrs full, int rank, int world, int T, int Vs4,
+                                                                int ld4) {
+  const size_t per_peer = (size_t)T * Vs4;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < per_peer * world; i += (size_t)gridDim.x * blockDim.x) {
+    const int p = (rank + 1 + (int)(i / per_peer)) % world;
+    const size_t e = i % per_peer;
+    const int t = (int)(e / Vs4), c = (int)(e % Vs4);
+    ((float4*)full.p[p])[(size_t)t * ld4 + (size_t)rank * Vs4 + c] = shard[e];
+  }
+  __threadfence_system();
+}
+
 }  // namespace pear
 
 using namespace pear;
@@ -248,6 +266,14 @@ PEAR_API int pear_amax_bf16(const void* src, size_t n, void* out_bits, void* str
 PEAR_API int pear_bcast_quant_nvfp4(const void* src, int rows, int K, int ld, float gscale, void* packed, void* stream) {
   if ((K % 256) != 0 || (ld % 8) != 0) return (int)cudaErrorInvalidValue;
   bcast_quant_nvfp4_kernel<<<592, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)src, rows, K, ld, gscale, (uint8_t*)packed);
+  PEAR_LAUNCH_CHECK();
+  return 0;
+}
+
+// shard: fp32 [T, Vs] contiguous; full[r]: rank r's fp32 [T, ld] buffer (ld >= world * Vs); Vs and ld multiples of 4.
+PEAR_API int pear_logits_allgather(const void* shard, const void* const* full, int rank, int world, int T, int Vs, int ld, void* stream) {
+  if (world < 1 || world > kMaxRanks || (Vs % 4) || (ld % 4)) return (int)cudaErrorInvalidValue;
+  logits_allgather_kernel<<<296, 256, 0, (cudaStream_t)stream>>>((const float4*)shard, to_ptrs(full, world), rank, world, T, Vs / 4, ld / 4);
   PEAR_LAUNCH_CHECK();
   return 0;
 }

@@ -27,7 +27,7 @@ import torch.distributed as dist
 from ..ops import lib as _lib
 
 SLOTS = 32
-SLOT_AR, SLOT_AG, SLOT_RS_ZERO, SLOT_RS_DONE, SLOT_SYNC = 0, 1, 2, 3, 4
+SLOT_AR, SLOT_AG, SLOT_RS_ZERO, SLOT_RS_DONE, SLOT_SYNC, SLOT_LOGITS = 0, 1, 2, 3, 4, 5
 DEFAULT_BUDGET = 1 << 22  # polls of >= 100 ns: a few hundred milliseconds, then the kernel gives up
 
 
@@ -148,6 +148,19 @@ class SymmWorld:
         self.signal(SLOT_RS_DONE, e)
         self.wait(SLOT_RS_DONE, e)  # every rank's adds have landed in my buffer
         return acc.tensor
+
+    # -- vocab-parallel logits all-gather -----------------------------------------------------------------------------
+    def all_gather_logits(self, shard: torch.Tensor, full: SymmBuffer) -> torch.Tensor:
+        """Write this rank's fp32 logits shard [T, V / world] into every rank's ``full`` [T, V]; returns the local full
+        buffer once every rank's shard has landed in it."""
+        t, vs = shard.shape
+        _lib.check(_lib.lib().pear_logits_allgather(_lib.ptr(shard.contiguous()), full.c_ptrs, self.rank, self.world, t, vs,
+                                                     full.tensor.stride(0), _lib.stream()), "logits_allgather")
+        _lib.LAUNCH_COUNT += 1
+        e = self.next_epoch(SLOT_LOGITS)
+        self.signal(SLOT_LOGITS, e)
+        self.wait(SLOT_LOGITS, e)
+        return full.tensor[:t]
 
     # -- weight sync: pull bf16 from the sender, write NVFP4 ----------------------------------------------------------
     def pull_quantize_nvfp4(self, staging: SymmBuffer, src_rank: int, rows: int, k: int) -> tuple[torch.Tensor, float]:

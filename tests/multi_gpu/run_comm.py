@@ -102,6 +102,20 @@ def main() -> int:
     if rank == 0:
         print("PASS pull_quantize_nvfp4", flush=True)
 
+    # ---- vocab-parallel logits all-gather by P2P stores
+    Tl, Vs = 8, 4096
+    shards = torch.randn(world, Tl, Vs, device="cuda", generator=g)
+    full = sw.alloc((16, world * Vs), torch.float32)
+    for it in range(2):
+        got = sw.all_gather_logits(shards[rank] + it, full)
+        torch.cuda.synchronize()
+        sw.check()
+        want = torch.cat([shards[r] + it for r in range(world)], dim=1)
+        assert torch.equal(got, want)
+        sw.device_barrier()  # nobody overwrites a buffer a peer is still reading
+    if rank == 0:
+        print("PASS all_gather_logits", flush=True)
+
     # ---- timings against the unfused NCCL + cuBLAS sequence
     if big:
         gathered = torch.empty(M, K, dtype=torch.bfloat16, device="cuda")
