@@ -37,6 +37,26 @@ class RMSNorm(nn.Module):
         return ops.rms_norm(x, self.weight, self.eps, self.one_plus)
 
 
+_TP: dict = {"group": None}
+
+
+def set_tensor_parallel_group(group) -> None:
+    """Tensor-parallel mode: the modules hold 1 / world of the heads and of the FFN width
+    (``pear_b200/parallel/tensor_parallel.py`` shards the weights); the outputs of the row-parallel projections
+    (o_proj, out_proj, down_proj) are partial sums that ``row_linear`` all-reduces over this group."""
+    _TP["group"] = group
+
+
+def row_linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    y = linear_fp32(x, weight)
+    g = _TP["group"]
+    if g is not None:
+        import torch.distributed as dist
+
+        dist.all_reduce(y, group=g)
+    return y
+
+
 class SwiGLUMLP(nn.Module):
     def __init__(self, cfg: HybridConfig):
         super().__init__()
@@ -46,7 +66,7 @@ class SwiGLUMLP(nn.Module):
 
     def forward(self, y: torch.Tensor) -> torch.Tensor:
         act = ops.swiglu(linear_fp32(y, self.gate_proj.weight), linear_fp32(y, self.up_proj.weight))
-        return linear_fp32(act, self.down_proj.weight)
+        return row_linear(act, self.down_proj.weight)
 
 
 @dataclass
@@ -107,7 +127,7 @@ class GatedAttention(nn.Module):
         else:
             attn = ops.causal_attention(q, k, v, meta.cu_seqlens, cfg.head_dim ** -0.5)
         gated = (ops.sigmoid_gate(attn, gate) if gate is not None else attn).reshape(t, cfg.q_size)
-        return linear_fp32(gated, self.o_proj.weight)
+        return row_linear(gated, self.o_proj.weight)
 
 
 class GatedDeltaNet(nn.Module):
@@ -158,7 +178,7 @@ class GatedDeltaNet(nn.Module):
             q, k, v, _ = self.front(mixed, bounds, None)
             o = ops.gdn_scan_packed(q, k, v, g, beta, bounds)
         y = ops.gated_rms_norm(o, z, self.norm.weight, cfg.rms_eps).reshape(t, cfg.gdn_value_dim)
-        return linear_fp32(y, self.out_proj.weight)
+        return row_linear(y, self.out_proj.weight)
 
 
 class DecoderLayer(nn.Module):
@@ -352,7 +372,7 @@ def forward_cached(model: HybridForCausalLM, input_ids: torch.Tensor, cache: Den
             from ..ops import reference as ref
 
             o = ref.attention_with_cache(q, kc, vc, kc.shape[0] - t, cfg.head_dim ** -0.5)
-            mixed = linear_fp32((ops.sigmoid_gate(o, gate) if gate is not None else o).reshape(t, cfg.q_size), att.o_proj.weight)
+            mixed = row_linear((ops.sigmoid_gate(o, gate) if gate is not None else o).reshape(t, cfg.q_size), att.o_proj.weight)
         else:
             gdn = layer.linear_attn
             x = linear_fp32(h, gdn.in_proj_qkv.weight)
@@ -367,7 +387,7 @@ def forward_cached(model: HybridForCausalLM, input_ids: torch.Tensor, cache: Den
             o, s = ref.gdn_recurrent(q, k, v, g, beta, cache.state.get(li))
             cache.state[li] = s
             y = ops.gated_rms_norm(o, z, gdn.norm.weight, cfg.rms_eps).reshape(t, cfg.gdn_value_dim)
-            mixed = linear_fp32(y, gdn.out_proj.weight)
+            mixed = row_linear(y, gdn.out_proj.weight)
         y, r = ops.add_rms_norm(mixed, r, layer.post_attention_layernorm.weight, layer.post_attention_layernorm.eps)
         r = r + layer.mlp(y)
     if layers is None:

@@ -19,7 +19,7 @@ from typing import Optional
 import torch
 
 from ..models.config import HybridConfig
-from ..models.hybrid import HybridForCausalLM, linear_fp32
+from ..models.hybrid import HybridForCausalLM, linear_fp32, row_linear
 from ..ops import api as ops
 from ..ops import reference as ref
 
@@ -126,7 +126,7 @@ class ModelRunner:
             outs.append(ref.attention_with_cache(q[s:e], kk, vv, row.start, cfg.head_dim ** -0.5))
         o = torch.cat(outs, dim=0)
         o = (ops.sigmoid_gate(o, gate) if gate is not None else o).reshape(hidden.shape[0], cfg.q_size)
-        return linear_fp32(o, att.o_proj.weight)
+        return row_linear(o, att.o_proj.weight)
 
     def _gdn(self, li: int, gdn, hidden: torch.Tensor, rows: list[StepRow], bounds: list[int], speculative: bool) -> torch.Tensor:
         cfg = self.cfg
@@ -157,7 +157,7 @@ class ModelRunner:
             outs.append(o)
         o = torch.cat(outs, dim=0)
         y = ops.gated_rms_norm(o, z, gdn.norm.weight, cfg.rms_eps).reshape(t, cfg.gdn_value_dim)
-        return linear_fp32(y, gdn.out_proj.weight)
+        return row_linear(y, gdn.out_proj.weight)
 
     def _advance(self, gdn, mixed, a, b, conv, rec):
         """Run conv + gates + delta rule over rows from (conv, rec); returns (outputs, new conv rows, new state)."""
