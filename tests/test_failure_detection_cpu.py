@@ -73,6 +73,8 @@ def _silent_worker(rank, world, path, results):
         results.put("no error")
     except Exception as e:  # noqa: BLE001
         results.put(f"error after {time.time() - t0:.0f}s: {type(e).__name__}")
+    results.close()
+    results.join_thread()  # the message is on its way before the process goes (no process-group teardown with a dead peer)
     os._exit(0)
 
 
