@@ -102,3 +102,21 @@ def test_linear_bf16_autograd():
     assert (y - yr).abs().max() <= 1e-3 * yr.abs().max()
     assert (x.grad - xr.grad).abs().max() <= 2e-2 * xr.grad.abs().max()
     assert (w.grad.float() - wr.grad).abs().max() <= 2e-2 * wr.grad.abs().max()
+
+
+def test_cuda_graph_runner_replays_kernel_sequences():
+    from pear_b200.ops import api
+    from pear_b200.utils.cuda_graph import GraphRunner
+
+    w = torch.randn(512, device="cuda") * 0.1
+
+    def step(x, r):
+        y, r2 = api.add_rms_norm(x, r, w, 1e-6)
+        return api.swiglu(y, r2)
+
+    runner = GraphRunner(step)
+    for i in range(3):
+        x, r = torch.randn(8, 512, device="cuda"), torch.randn(8, 512, device="cuda")
+        got = runner(8, x, r).clone()
+        assert torch.allclose(got, step(x, r), atol=1e-5)
+    assert runner.replays == 3 and len(runner.graphs) == 1
