@@ -35,6 +35,7 @@ __device__ __noinline__ void op_gdn(Ctx& c, const Instr& ins) {
   const int nseq = R + T;  // rows of the extended sequence that get a conv output
 
   consumer_sync();
+  trace_mark(c, 55);  // gdn: op entered, scratch free
   float* xin = (float*)c.xs;                       // [3 + nseq][kGdnCh]
   float* u = xin + kGdnMaxRows * kGdnCh;           // [nseq][kGdnCh]
   float* dec = u + 16 * kGdnCh;                    // [16] exp(g)
@@ -48,71 +49,70 @@ __device__ __noinline__ void op_gdn(Ctx& c, const Instr& ins) {
          : ch < 2 * kGdnD ? Hk * kGdnD + hk * kGdnD + (ch - kGdnD)
                           : 2 * Hk * kGdnD + hv * kGdnD + row0 + (ch - 2 * kGdnD);
   };
-  float* cw = beta + 16;                           // [kGdnCh][4] conv weights of the staged channels
+  // Compact code on purpose: the megakernel's code is far larger than the instruction caches, so every op starts cold
+  // and its cost is the number of instruction-cache lines it touches, not its arithmetic. All loops over rows are rolled;
+  // the input columns go global -> shared with 4-byte asynchronous copies (all in flight at once without unrolling),
+  // and no index is divided: a thread owns up to two channels of the item.
   {
-    constexpr int kMaxPer = (kGdnMaxRows * kGdnCh + kConsumerThreads - 1) / kConsumerThreads;  // 24
-    const int total = (3 + nseq) * nch;
-    float tmp[kMaxPer];
-#pragma unroll
-    for (int e = 0; e < kMaxPer; ++e) {
-      const int idx = tid + e * kConsumerThreads;
-      if (idx < total) {
-        const int r = idx / nch, gch = gch_of(idx % nch);
-        const float* src = r < 3 ? conv_rd + (size_t)r * C + gch
-                         : r < 3 + R ? rec_prev + (size_t)(r - 3) * rstride + gch
-                                     : rec_cur + (size_t)(r - 3 - R) * rstride + gch;
-        tmp[e] = __ldcg(src);
-      }
-    }
-    float4 wv[2];
+    int gchs[2];
+    bool okc[2];
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
       const int ch = tid + e * kConsumerThreads;
-      if (ch < nch) wv[e] = __ldg((const float4*)(conv_w + (size_t)gch_of(ch) * 4));
+      okc[e] = ch < nch;
+      gchs[e] = okc[e] ? gch_of(ch) : 0;
     }
-    float gb = 0.f, ga = 0.f;
+#pragma unroll 1
+    for (int r = 0; r < 3 + nseq; ++r) {
+      const float* row = r < 3 ? conv_rd + (size_t)r * C : r < 3 + R ? rec_prev + (size_t)(r - 3) * rstride : rec_cur + (size_t)(r - 3 - R) * rstride;
+#pragma unroll
+      for (int e = 0; e < 2; ++e)
+        if (okc[e])
+          asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(xin + r * kGdnCh + tid + e * kConsumerThreads)), "l"(row + gchs[e]) : "memory");
+    }
+    float4 wv[2];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) wv[e] = okc[e] ? __ldg((const float4*)(conv_w + (size_t)gchs[e] * 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    float gb = 0.f, ga = 0.f, A_log = 0.f, dt_bias = 0.f;
     if (tid < nseq) {
       const float* row = tid < R ? rec_prev + (size_t)tid * rstride : rec_cur + (size_t)(tid - R) * rstride;
       gb = __ldcg(row + C + Hv * kGdnD + hv);
       ga = __ldcg(row + C + Hv * kGdnD + Hv + hv);
+      A_log = __ldg((const float*)d.p3 + hv);
+      dt_bias = __ldg((const float*)d.p3 + Hv + hv);
     }
+    asm volatile("cp.async.wait_all;" ::: "memory");
+    trace_mark(c, 56);  // gdn: input columns in shared memory (this thread's)
+    const bool qk_writer = (hv % (Hv / Hk) == 0) && row0 == 0;
+    // a thread reads back only what it copied itself: no barrier needed before the convolution
+#pragma unroll 1
+    for (int r = 0; r < nseq; ++r) {
 #pragma unroll
-    for (int e = 0; e < kMaxPer; ++e) {
-      const int idx = tid + e * kConsumerThreads;
-      if (idx < total) xin[(idx / nch) * kGdnCh + idx % nch] = tmp[e];
+      for (int e = 0; e < 2; ++e) {
+        if (!okc[e]) continue;
+        const float* x = xin + r * kGdnCh + tid + e * kConsumerThreads;
+        const float acc = wv[e].x * x[0] + wv[e].y * x[kGdnCh] + wv[e].z * x[2 * kGdnCh] + wv[e].w * x[3 * kGdnCh];
+        u[r * kGdnCh + tid + e * kConsumerThreads] = silu_f(acc);
+      }
     }
+    // conv window for the next step: rows [R, R + 3) of the extended sequence
+#pragma unroll 1
+    for (int w = 0; w < 3; ++w) {
 #pragma unroll
-    for (int e = 0; e < 2; ++e) {
-      const int ch = tid + e * kConsumerThreads;
-      if (ch < nch) *(float4*)(cw + ch * 4) = wv[e];
+      for (int e = 0; e < 2; ++e) {
+        const int ch = tid + e * kConsumerThreads;
+        if (okc[e] && (ch >= 2 * kGdnD || qk_writer)) conv_wr[(size_t)w * C + gchs[e]] = xin[(R + w) * kGdnCh + ch];
+      }
     }
     if (tid < nseq) {
-      const float A_log = ((const float*)d.p3)[hv], dt_bias = ((const float*)d.p3)[Hv + hv];
       dec[tid] = __expf(-__expf(A_log) * softplus_f(ga + dt_bias));
       beta[tid] = sigmoid_f(gb);
     }
   }
   consumer_sync();
-
-  // ---- conv window for the next step: rows [R, R+3) of the extended sequence
-  {
-    const bool qk_writer = (hv % (Hv / Hk) == 0) && row0 == 0;
-    for (int idx = tid; idx < 3 * nch; idx += kConsumerThreads) {
-      const int r = idx / nch, ch = idx % nch;
-      if (ch < 2 * kGdnD && !qk_writer) continue;
-      conv_wr[(size_t)r * C + gch_of(ch)] = xin[(R + r) * kGdnCh + ch];
-    }
-  }
-  // ---- conv + SiLU
-  for (int idx = tid; idx < nseq * nch; idx += kConsumerThreads) {
-    const int r = idx / nch, ch = idx % nch;
-    const float4 w = *(const float4*)(cw + ch * 4);
-    const float acc = w.x * xin[r * kGdnCh + ch] + w.y * xin[(r + 1) * kGdnCh + ch] + w.z * xin[(r + 2) * kGdnCh + ch] +
-                      w.w * xin[(r + 3) * kGdnCh + ch];
-    u[r * kGdnCh + ch] = silu_f(acc);
-  }
-  consumer_sync();
+  trace_mark(c, 51);  // gdn: conv done
   // ---- L2 norm of q (scaled by D^-0.5) and k per row: one warp per (row, q|k)
+#pragma unroll 1
   for (int item = warp; item < 2 * nseq; item += kConsumerWarps) {
     float* v = u + (item >> 1) * kGdnCh + (item & 1) * kGdnD;
     float4 x = *(float4*)(v + lane * 4);
@@ -122,6 +122,7 @@ __device__ __noinline__ void op_gdn(Ctx& c, const Instr& ins) {
     *(float4*)(v + lane * 4) = x;
   }
   consumer_sync();
+  trace_mark(c, 52);  // gdn: q, k normalised
 
   // ---- recurrence: thread (row = tid / 4, kq = tid % 4) owns columns {16 i + 4 kq .. + 3 : i = 0..7} of its row
   const int r = tid >> 2, kq = tid & 3;
@@ -134,6 +135,8 @@ __device__ __noinline__ void op_gdn(Ctx& c, const Instr& ins) {
     S[4 * i] = v.x; S[4 * i + 1] = v.y; S[4 * i + 2] = v.z; S[4 * i + 3] = v.w;
   }
   float* out = (float*)d.p6;
+  trace_mark(c, 53);  // gdn: state rows loaded (issued)
+#pragma unroll 1
   for (int s = 0; s < nseq; ++s) {
     if (s == R && active) {
 #pragma unroll
@@ -171,6 +174,7 @@ __device__ __noinline__ void op_gdn(Ctx& c, const Instr& ins) {
       if (active && kq == 0) out[(size_t)(s - R) * d.i4 + hv * kGdnD + row0 + r] = o;
     }
   }
+  trace_mark(c, 54);  // gdn: recurrence done
   if (R == nseq && active) {  // T == 0 never happens; kept for completeness when a block is replay-only
 #pragma unroll
     for (int i = 0; i < 8; ++i)
