@@ -293,14 +293,31 @@ __device__ __noinline__ void op_attn_combine(Ctx& c, const Instr& ins) {
     for (int i = 0; i < 8; ++i) acc[i] = 0.f;
     float l = 0.f;
     const int per = D / 32;  // dims per lane (8 or 4), contiguous
-    for (int s = 0; s < nsplit; ++s) {
-      const float* p = base + (size_t)s * (D + 2);
-      const float ms = __ldcg(p + D);
-      if (ms == -INFINITY) continue;
-      const float w = __expf(ms - mx);
-      l += w * __ldcg(p + D + 1);
-      for (int i = 0; i < per; ++i) acc[i] += w * __ldcg(p + lane * per + i);
+    // Lanes first take one split each (its max and sum), then the partial outputs are accumulated split by split with the
+    // weight broadcast by shuffle: no load depends on a loaded flag, so the unrolled loop keeps eight splits in flight
+    // (the split-by-split version with an early `continue` paid one L2 round trip per split: ~20 us at 37 splits).
+    for (int s0 = 0; s0 < nsplit; s0 += 32) {
+      const int sl = s0 + lane;
+      const float ms = sl < nsplit ? __ldcg(base + (size_t)sl * (D + 2) + D) : -INFINITY;
+      const float ls = sl < nsplit ? __ldcg(base + (size_t)sl * (D + 2) + D + 1) : 0.f;
+      const float w = ms == -INFINITY ? 0.f : __expf(ms - mx);
+      l += w * ls;
+      const int cnt = min(32, nsplit - s0);
+#pragma unroll 8
+      for (int j = 0; j < cnt; ++j) {
+        const float wj = __shfl_sync(0xffffffffu, w, j);
+        const float2* p = (const float2*)(base + (size_t)(s0 + j) * (D + 2) + lane * per);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          if (2 * i < per) {
+            const float2 v = __ldcg(p + i);
+            acc[2 * i] += wj > 0.f ? wj * v.x : 0.f;       // an empty split's slot may hold anything
+            acc[2 * i + 1] += wj > 0.f ? wj * v.y : 0.f;
+          }
+        }
+      }
     }
+    l = warp_sum(l);
     const float inv = l > 0.f ? 1.f / l : 0.f;
     for (int i = 0; i < per; ++i) {
       float v = acc[i] * inv;
