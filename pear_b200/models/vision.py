@@ -69,9 +69,13 @@ class VisionTower(nn.Module):
     def init_weights(self, seed: int = 0) -> "VisionTower":
         g = torch.Generator().manual_seed(seed)
         with torch.no_grad():
-            for p in self.parameters():
+            for name, p in self.named_parameters():
                 if p.dim() >= 2:
                     p.copy_(torch.randn(p.shape, generator=g) * 0.02)
+                elif "norm" in name and name.endswith("weight"):
+                    p.fill_(1.0)
+                else:
+                    p.zero_()  # biases: nn.Linear draws them from the global generator otherwise
         return self
 
     def tokens_per_image(self, height: int, width: int) -> int:

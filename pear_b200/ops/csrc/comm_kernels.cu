@@ -216,6 +216,52 @@ __global__ void __launch_bounds__(256) logits_allgather_kernel(const float4* __r
   __threadfence_system();
 }
 
+// ------------------------------------------------------------------------------------------------ sharded argmax exchange
+// The drafter's greedy token under vocabulary parallelism (upstream draft_argmax.cu: one tagged 64-bit word per row
+// swapped with the peer): every rank reduces its logits shard [rows, Vs] to (max value, global token id) per row, packs
+// them as an ORDERED 64-bit key (monotone float bits << 32 | ~token, so ties go to the lower id) and stores the key into
+// slot `rank` of EVERY rank's exchange buffer [rows][world]. After signal / wait, arg_finish takes the maximum key per row.
+__global__ void __launch_bounds__(256) argmax_shard_kernel(const float* __restrict__ logits, int Vs, int ld, int v0, PeerPtrs xbuf, int rank, int world) {
+  __shared__ unsigned long long red[8];
+  const int row = blockIdx.x, tid = threadIdx.x;
+  const float* x = logits + (size_t)row * ld;
+  unsigned long long best = 0ull;
+  for (int i = tid; i < Vs; i += blockDim.x) {
+    uint32_t b = __float_as_uint(x[i]);
+    b = (b & 0x80000000u) ? ~b : (b | 0x80000000u);  // monotone map of IEEE floats to unsigned
+    const unsigned long long key = ((unsigned long long)b << 32) | (uint32_t)~(uint32_t)(v0 + i);
+    best = key > best ? key : best;
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+    best = other > best ? other : best;
+  }
+  if ((tid & 31) == 0) red[tid >> 5] = best;
+  __syncthreads();
+  if (tid == 0) {
+    for (int w = 1; w < 8; ++w) best = red[w] > best ? red[w] : best;
+    for (int p = 0; p < world; ++p) {
+      const int peer = (rank + p) % world;
+      ((volatile unsigned long long*)xbuf.p[peer])[(size_t)row * kMaxRanks + rank] = best;
+    }
+    __threadfence_system();
+  }
+}
+
+__global__ void argmax_finish_kernel(const unsigned long long* __restrict__ my_xbuf, int rows, int world, int* __restrict__ token, float* __restrict__ value) {
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= rows) return;
+  unsigned long long best = 0ull;
+  for (int r = 0; r < world; ++r) {
+    const unsigned long long k = ((const volatile unsigned long long*)my_xbuf)[(size_t)row * kMaxRanks + r];
+    best = k > best ? k : best;
+  }
+  uint32_t b = (uint32_t)(best >> 32);
+  b = (b & 0x80000000u) ? (b & 0x7FFFFFFFu) : ~b;
+  token[row] = (int)~(uint32_t)best;
+  value[row] = __uint_as_float(b);
+}
+
 }  // namespace pear
 
 using namespace pear;
@@ -274,6 +320,21 @@ PEAR_API int pear_bcast_quant_nvfp4(const void* src, int rows, int K, int ld, fl
 PEAR_API int pear_logits_allgather(const void* shard, const void* const* full, int rank, int world, int T, int Vs, int ld, void* stream) {
   if (world < 1 || world > kMaxRanks || (Vs % 4) || (ld % 4)) return (int)cudaErrorInvalidValue;
   logits_allgather_kernel<<<296, 256, 0, (cudaStream_t)stream>>>((const float4*)shard, to_ptrs(full, world), rank, world, T, Vs / 4, ld / 4);
+  PEAR_LAUNCH_CHECK();
+  return 0;
+}
+
+// logits: this rank's fp32 shard [rows, Vs] (columns v0 .. v0 + Vs of the vocabulary); xbuf[r]: rank r's exchange buffer
+// of rows * 8 uint64. Order with pear_symm_signal / pear_symm_wait, then pear_argmax_finish.
+PEAR_API int pear_argmax_shard(const float* logits, int rows, int Vs, int ld, int v0, const void* const* xbuf, int rank, int world, void* stream) {
+  if (world < 1 || world > kMaxRanks) return (int)cudaErrorInvalidValue;
+  argmax_shard_kernel<<<rows, 256, 0, (cudaStream_t)stream>>>(logits, Vs, ld, v0, to_ptrs(xbuf, world), rank, world);
+  PEAR_LAUNCH_CHECK();
+  return 0;
+}
+
+PEAR_API int pear_argmax_finish(const void* my_xbuf, int rows, int world, int* token, float* value, void* stream) {
+  argmax_finish_kernel<<<(rows + 127) / 128, 128, 0, (cudaStream_t)stream>>>((const unsigned long long*)my_xbuf, rows, world, token, value);
   PEAR_LAUNCH_CHECK();
   return 0;
 }

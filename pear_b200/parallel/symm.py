@@ -27,7 +27,7 @@ import torch.distributed as dist
 from ..ops import lib as _lib
 
 SLOTS = 32
-SLOT_AR, SLOT_AG, SLOT_RS_ZERO, SLOT_RS_DONE, SLOT_SYNC, SLOT_LOGITS = 0, 1, 2, 3, 4, 5
+SLOT_AR, SLOT_AG, SLOT_RS_ZERO, SLOT_RS_DONE, SLOT_SYNC, SLOT_LOGITS, SLOT_ARGMAX = 0, 1, 2, 3, 4, 5, 6
 DEFAULT_BUDGET = 1 << 22  # polls of >= 100 ns: a few hundred milliseconds, then the kernel gives up
 
 
@@ -161,6 +161,26 @@ class SymmWorld:
         self.signal(SLOT_LOGITS, e)
         self.wait(SLOT_LOGITS, e)
         return full.tensor[:t]
+
+    # -- sharded argmax (drafter's greedy token under vocabulary parallelism) -------------------------------------------
+    def make_argmax_buffer(self, max_rows: int) -> SymmBuffer:
+        return self.alloc((max_rows, 8), torch.int64)
+
+    def sharded_argmax(self, logits_shard: torch.Tensor, xbuf: SymmBuffer) -> tuple[torch.Tensor, torch.Tensor]:
+        """Global (token, value) of the row-wise maximum over the vocabulary, each rank holding columns
+        ``[rank * Vs, (rank + 1) * Vs)``; ties go to the lower token id."""
+        rows, vs = logits_shard.shape
+        lib = _lib.lib()
+        _lib.check(lib.pear_argmax_shard(_lib.ptr(logits_shard), rows, vs, logits_shard.stride(0), self.rank * vs, xbuf.c_ptrs, self.rank,
+                                         self.world, _lib.stream()), "argmax_shard")
+        e = self.next_epoch(SLOT_ARGMAX)
+        self.signal(SLOT_ARGMAX, e)
+        self.wait(SLOT_ARGMAX, e)
+        tok = torch.empty(rows, dtype=torch.int32, device=self.device)
+        val = torch.empty(rows, dtype=torch.float32, device=self.device)
+        _lib.check(lib.pear_argmax_finish(_lib.ptr(xbuf.tensor), rows, self.world, _lib.ptr(tok), _lib.ptr(val), _lib.stream()), "argmax_finish")
+        _lib.LAUNCH_COUNT += 2
+        return tok.long(), val
 
     # -- weight sync: pull bf16 from the sender, write NVFP4 ----------------------------------------------------------
     def pull_quantize_nvfp4(self, staging: SymmBuffer, src_rank: int, rows: int, k: int) -> tuple[torch.Tensor, float]:

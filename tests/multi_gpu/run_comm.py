@@ -116,6 +116,19 @@ def main() -> int:
     if rank == 0:
         print("PASS all_gather_logits", flush=True)
 
+    # ---- sharded argmax exchange
+    xbuf = sw.make_argmax_buffer(16)
+    for it in range(2):
+        sh = shards + it  # [world, Tl, Vs]
+        tok, val = sw.sharded_argmax(sh[rank].contiguous(), xbuf)
+        torch.cuda.synchronize()
+        sw.check()
+        full_l = torch.cat([sh[r] for r in range(world)], dim=1)
+        assert torch.equal(tok, full_l.argmax(-1)) and torch.equal(val, full_l.max(-1).values)
+        sw.device_barrier()
+    if rank == 0:
+        print("PASS sharded_argmax", flush=True)
+
     # ---- timings against the unfused NCCL + cuBLAS sequence
     if big:
         gathered = torch.empty(M, K, dtype=torch.bfloat16, device="cuda")

@@ -59,3 +59,39 @@ def test_tp2_matches_single_rank():
 def test_tp_config_refuses_uneven_splits():
     with pytest.raises(ValueError, match="num_kv_heads=2"):
         tp_config(_cfg(), 4)
+
+
+def _vision_worker(rank, world, path, q):
+    from pear_b200.models.vision import VisionConfig, VisionTower
+    from pear_b200.parallel.vision_sp import encode_sharded, reduce_tower_grads
+
+    dist.init_process_group("gloo", init_method=f"file://{path}", rank=rank, world_size=world)
+    g = torch.Generator().manual_seed(0)
+    images = [torch.randn(3, 16, 16, generator=g), torch.randn(3, 32, 16, generator=g), torch.randn(3, 16, 16, generator=g)]
+    tower = VisionTower(VisionConfig.tiny(out_hidden=32)).init_weights(1)
+    ref_tower = VisionTower(VisionConfig.tiny(out_hidden=32)).init_weights(1)
+    want = ref_tower(images)
+    torch.cat(want).pow(2).sum().backward()
+    got = encode_sharded(tower, images, dist.group.WORLD)
+    # every rank consumes every image's rows; the loss is counted once per rank, so scale by 1 / world
+    (torch.cat(got).pow(2).sum() / world).backward()
+    reduce_tower_grads(tower, dist.group.WORLD)
+    err_f = max(float((a - b).abs().max()) for a, b in zip(got, want))
+    err_g = max(float((p.grad - r.grad).abs().max()) for p, r in zip(tower.parameters(), ref_tower.parameters()))
+    q.put((rank, err_f, err_g))
+    dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+def test_vision_tower_sharded_over_ranks_matches_single_rank():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    with tempfile.TemporaryDirectory() as d:
+        procs = [ctx.Process(target=_vision_worker, args=(r, 2, os.path.join(d, "rdzv"), q)) for r in range(2)]
+        for p in procs:
+            p.start()
+        res = [q.get(timeout=240) for _ in range(2)]
+        for p in procs:
+            p.join(30)
+    for rank, err_f, err_g in res:
+        assert err_f < 1e-5 and err_g < 1e-4, (rank, err_f, err_g)
