@@ -57,7 +57,7 @@ def main() -> int:
         print("PASS all_reduce_add_rmsnorm", flush=True)
 
     # ---- all-gather -> GEMM
-    M, N, K = (world * 1024, 4096, 4096) if big else (world * 256, 512, 512)
+    M, N, K = (world * 4096, 8192, 8192) if big else (world * 256, 512, 512)  # big: ~1 ms of GEMM, launch overheads negligible
     a_full = (torch.randn(M, K, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
     b = (torch.randn(N, K, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
     shard = sw.alloc((M // world, K), torch.bfloat16)
