@@ -1,9 +1,12 @@
 // bf16 GEMMs on tcgen05 fused with the collective that precedes or follows them, over peer memory (NVLink / NVSwitch):
 //
 //   all-gather -> GEMM   C[M, N] = gather_r(A_r)[M, K] * B[N, K]^T,  A row-sharded: rank r holds rows [r M/W, (r+1) M/W)
-//       There is no gather pass: the TMA producer reads each 128-row tile of A straight from the memory of the rank
-//       that owns it (one tensor map per rank; plain, non-multicast TMA loads). Tiles of the local shard come first,
-//       remote shards are touched only once their owner has signalled that the shard is written (bounded wait).
+//       There is no separate gather launch: two copier warps per CTA pull the remote shards over NVLink, 128-row block by
+//       block in the order the tiles will need them, into a local full-A buffer and publish each block with a release
+//       flag; the TMA producer computes the tiles of the local shard first and takes a remote block as soon as its flag
+//       is up (bounded waits on both sides). Every remote byte crosses NVLink exactly once: reading remote tiles straight
+//       from peer memory re-fetched each A block once per N tile (measured 3.7 ms against 0.8 ms for NCCL + cuBLAS at
+//       M = N = K = 8192 on two GPUs).
 //
 //   GEMM -> reduce-scatter   C_r[M/W, N] = sum_s A_s[M, K_s] * B_s[N, K_s]^T restricted to the rows rank r owns
 //       There is no reduce pass: the epilogue adds each finished fp32 tile into the OWNER's accumulation buffer with
@@ -19,7 +22,7 @@
 
 namespace pear {
 
-constexpr int kCBM = 128, kCBK = 64, kCStages = 4, kCThreads = 192, kCMaxRanks = 8;
+constexpr int kCBM = 128, kCBK = 64, kCStages = 4, kCThreads = 256, kCMaxRanks = 8;  // warps: TMA, MMA, 4 epilogue, 2 copier
 
 struct CollSmem {
   uint64_t full[kCStages], empty[kCStages];
@@ -46,6 +49,18 @@ __device__ __forceinline__ bool wait_epoch(const uint32_t* flag, uint32_t epoch,
   }
   return false;
 }
+__device__ __forceinline__ uint32_t ld_acquire_gpu_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ bool wait_epoch_gpu(const uint32_t* flag, uint32_t epoch, uint32_t budget) {
+  for (uint32_t i = 0; i < budget; ++i) {
+    if ((int32_t)(ld_acquire_gpu_u32(flag) - epoch) >= 0) return true;
+    if (i > 32) __nanosleep(100);
+  }
+  return false;
+}
 __device__ __forceinline__ void red_add_v4_f32_sys(float* addr, float a, float b, float c, float d) {
   asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
@@ -56,8 +71,10 @@ template <int BN, int MODE, bool OUT_BF16>
 __global__ void __launch_bounds__(kCThreads, 1)
 gemm_coll_kernel(const __grid_constant__ MapSet maps, const __grid_constant__ CUtensorMap map_b, void* __restrict__ c,
                  const __grid_constant__ OutPtrs outs, int M, int N, int K, int ldc, int rank, int world,
-                 const uint32_t* __restrict__ my_flags, int slot, uint32_t epoch, uint32_t budget, int* status) {
+                 const uint32_t* __restrict__ my_flags, int slot, uint32_t epoch, uint32_t budget, int* status,
+                 uint4* __restrict__ a_full, uint32_t* __restrict__ chunk_flags) {
   extern __shared__ __align__(1024) uint8_t smem[];
+  __shared__ int copier_ok;
   constexpr uint32_t kABytes = kCBM * kCBK * 2, kBBytes = BN * kCBK * 2, kStageBytes = kABytes + kBBytes;
   uint8_t* tiles = smem;
   CollSmem* sm = (CollSmem*)(smem + kCStages * kStageBytes);
@@ -97,18 +114,14 @@ gemm_coll_kernel(const __grid_constant__ MapSet maps, const __grid_constant__ CU
       for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
         int owner, m0, n0;
         tile_coords(tile, owner, m0, n0);
-        if (MODE == 0 && !((ready >> owner) & 1u)) {
-          if (!wait_epoch(my_flags + slot * kCMaxRanks + owner, epoch, budget)) {
-            set_status(status, PEAR_ERR_FLAG_TIMEOUT);
-            // keep the pipeline protocol alive with local data so the other warps drain and the kernel returns
-            owner = rank;
-            m0 = rank * m_local;
-          } else {
-            ready |= 1u << owner;
-          }
+        if (MODE == 0 && owner != rank) {
+          // the copier warps publish every remote 128-row block of A in the local full buffer
+          if (!wait_epoch_gpu(chunk_flags + m0 / kCBM, epoch, budget)) set_status(status, PEAR_ERR_FLAG_TIMEOUT);
         }
-        const CUtensorMap* ma = MODE == 0 ? &maps.a[owner] : &maps.a[0];
-        const int am0 = MODE == 0 ? m0 - owner * m_local : m0;
+        (void)ready;
+        // MODE 0: maps.a[0] = the local shard (rows relative to it), maps.a[1] = the local full-A buffer (global rows)
+        const CUtensorMap* ma = MODE == 0 ? (owner == rank ? &maps.a[0] : &maps.a[1]) : &maps.a[0];
+        const int am0 = (MODE == 0 && owner == rank) ? m0 - owner * m_local : m0;
         for (int kb = 0; kb < kblocks; ++kb) {
           ok = mbar_wait_bounded(&sm->empty[st], ph ^ 1, status);
           if (!ok) break;
@@ -146,7 +159,7 @@ gemm_coll_kernel(const __grid_constant__ MapSet maps, const __grid_constant__ CU
         tcgen05_commit(&sm->tmem_full[ab]);
       }
     }
-  } else {
+  } else if (warp < 6) {
     const int q = warp & 3;
     int it = 0;
     bool ok = true;
@@ -212,6 +225,40 @@ gemm_coll_kernel(const __grid_constant__ MapSet maps, const __grid_constant__ CU
     }
     if (MODE == 1) __threadfence_system();  // the adds are performed before the host-ordered "done" signal that follows the kernel
   }
+  if (MODE == 0 && warp >= 6 && world > 1) {
+    // ------------------------------------------------------------------------------------------------ copier warps
+    const int ct = threadIdx.x - 192;  // 0..63
+    const int remote_tiles = tiles_m - tiles_m_local;
+    const size_t vec_per_block = (size_t)kCBM * K / 8;  // 16-byte vectors of a 128-row block (rows are contiguous: lda == K)
+    for (int cidx = blockIdx.x; cidx < remote_tiles; cidx += gridDim.x) {
+      const int owner = (rank + 1 + cidx / tiles_m_local) % world, mt = cidx % tiles_m_local;
+      if (ct == 0) {
+        copier_ok = wait_epoch(my_flags + slot * kCMaxRanks + owner, epoch, budget) ? 1 : 0;
+        if (!copier_ok) set_status(status, PEAR_ERR_FLAG_TIMEOUT);
+      }
+      asm volatile("bar.sync 3, 64;" ::: "memory");
+      if (copier_ok) {
+        const uint4* src = (const uint4*)outs.p[owner] + (size_t)mt * vec_per_block;
+        uint4* dst = a_full + (size_t)(owner * tiles_m_local + mt) * vec_per_block;
+        for (size_t i = ct; i < vec_per_block; i += 64 * 8) {
+          uint4 v[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            if (i + (size_t)u * 64 < vec_per_block)
+              asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w) : "l"(src + i + (size_t)u * 64) : "memory");
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            if (i + (size_t)u * 64 < vec_per_block) dst[i + (size_t)u * 64] = v[u];
+        }
+        // the block is read by TMA (async proxy) of other CTAs: make the generic-proxy stores visible to it
+        asm volatile("fence.proxy.async;" ::: "memory");
+        __threadfence();
+      }
+      asm volatile("bar.sync 3, 64;" ::: "memory");
+      // publish also after a timeout (the status word already says so): nobody is left waiting for this block
+      if (ct == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(chunk_flags + owner * tiles_m_local + mt), "r"(epoch) : "memory");
+    }
+  }
   tcgen05_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -247,7 +294,7 @@ static int coll_map_bf16(CUtensorMap* map, const void* base, int rows, int cols,
 template <int BN, int MODE, bool OUT_BF16>
 static int launch_coll(const MapSet& maps, const CUtensorMap& mb, void* c, const OutPtrs& outs, int M, int N, int K, int ldc, int rank,
                        int world, const uint32_t* flags, int slot, uint32_t epoch, uint32_t budget, int* status, int num_sms,
-                       cudaStream_t stream) {
+                       cudaStream_t stream, void* a_full = nullptr, void* chunk_flags = nullptr) {
   constexpr int smem = kCStages * (kCBM * kCBK * 2 + BN * kCBK * 2) + 1024;
   static bool configured = false;
   if (!configured) {
@@ -257,7 +304,7 @@ static int launch_coll(const MapSet& maps, const CUtensorMap& mb, void* c, const
   const int ntiles = (M / kCBM) * ((N + BN - 1) / BN);
   const int grid = ntiles < num_sms ? ntiles : num_sms;
   gemm_coll_kernel<BN, MODE, OUT_BF16><<<grid, kCThreads, smem, stream>>>(maps, mb, c, outs, M, N, K, ldc, rank, world, flags, slot, epoch,
-                                                                          budget, status);
+                                                                          budget, status, (uint4*)a_full, (uint32_t*)chunk_flags);
   PEAR_LAUNCH_CHECK();
   return 0;
 }
@@ -266,26 +313,28 @@ static int launch_coll(const MapSet& maps, const CUtensorMap& mb, void* c, const
 
 using namespace pear;
 
-// all-gather -> GEMM. a_shards[r]: rank r's [M / world, K] bf16 shard (symmetric memory, leading dimension lda);
+// all-gather -> GEMM. a_shards[r]: rank r's [M / world, K] bf16 shard (symmetric memory, rows contiguous: lda == K);
 // my_flags: this rank's signal region; the owner of shard r must have signalled `epoch` in `slot` (pear_symm_signal)
-// after writing it. C [M, N] is local (fp32 or bf16). M / world must be a multiple of 128.
+// after writing it. a_full: local [M, K] bf16 buffer the remote shards are copied into; chunk_flags: local uint32 per
+// 128-row block of A (any values below `epoch`). C [M, N] is local (fp32 or bf16). M / world must be a multiple of 128.
 PEAR_API int pear_ag_gemm_bf16(const void* const* a_shards, const void* b, void* c, int M, int N, int K, int lda, int ldb, int ldc,
                                int out_bf16, int rank, int world, const void* my_flags, int slot, unsigned epoch, unsigned budget,
-                               int* status, int num_sms, void* stream) {
-  if (world < 1 || world > kCMaxRanks || M % (world * kCBM) || (lda % 8) || (ldb % 8)) return (int)cudaErrorInvalidValue;
+                               int* status, int num_sms, void* a_full, void* chunk_flags, void* stream) {
+  if (world < 1 || world > kCMaxRanks || M % (world * kCBM) || lda != K || (K % 8) || (ldb % 8)) return (int)cudaErrorInvalidValue;
   MapSet maps;
-  for (int r = 0; r < world; ++r) {
-    int e = coll_map_bf16(&maps.a[r], a_shards[r], M / world, K, lda, kCBM);
-    if (e) return e;
-  }
-  for (int r = world; r < kCMaxRanks; ++r) maps.a[r] = maps.a[0];
-  CUtensorMap mb;
-  int e = coll_map_bf16(&mb, b, N, K, ldb, 256);
+  int e = coll_map_bf16(&maps.a[0], a_shards[rank], M / world, K, lda, kCBM);
   if (e) return e;
-  OutPtrs outs{};
+  e = coll_map_bf16(&maps.a[1], a_full, M, K, K, kCBM);
+  if (e) return e;
+  for (int r = 2; r < kCMaxRanks; ++r) maps.a[r] = maps.a[0];
+  CUtensorMap mb;
+  e = coll_map_bf16(&mb, b, N, K, ldb, 256);
+  if (e) return e;
+  OutPtrs shards{};
+  for (int r = 0; r < world; ++r) shards.p[r] = (float*)const_cast<void*>(a_shards[r]);
   cudaStream_t s = (cudaStream_t)stream;
-  return out_bf16 ? launch_coll<256, 0, true>(maps, mb, c, outs, M, N, K, ldc, rank, world, (const uint32_t*)my_flags, slot, epoch, budget, status, num_sms, s)
-                  : launch_coll<256, 0, false>(maps, mb, c, outs, M, N, K, ldc, rank, world, (const uint32_t*)my_flags, slot, epoch, budget, status, num_sms, s);
+  return out_bf16 ? launch_coll<256, 0, true>(maps, mb, c, shards, M, N, K, ldc, rank, world, (const uint32_t*)my_flags, slot, epoch, budget, status, num_sms, s, a_full, chunk_flags)
+                  : launch_coll<256, 0, false>(maps, mb, c, shards, M, N, K, ldc, rank, world, (const uint32_t*)my_flags, slot, epoch, budget, status, num_sms, s, a_full, chunk_flags);
 }
 
 // GEMM -> reduce-scatter. A [M, K_local], B [N, K_local] local bf16; acc[r]: rank r's fp32 [M / world, ldc] accumulation

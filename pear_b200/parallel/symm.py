@@ -51,6 +51,7 @@ class SymmWorld:
         self.flags.tensor.zero_()
         self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
         self.epochs = [0] * SLOTS
+        self._ag_bufs: dict = {}
         self.num_sms = torch.cuda.get_device_properties(self.device).multi_processor_count
         torch.cuda.synchronize(self.device)
         dist.barrier(self.group)
@@ -115,12 +116,17 @@ class SymmWorld:
         n = b.shape[0]
         m = ml * self.world
         c = torch.empty(m, n, dtype=out_dtype, device=self.device)
+        key = (m, k)
+        if key not in self._ag_bufs:  # local full-A buffer + one flag per 128-row block, kept across calls
+            self._ag_bufs[key] = (torch.empty(m, k, dtype=torch.bfloat16, device=self.device),
+                                  torch.zeros(m // 128, dtype=torch.int32, device=self.device))
+        a_full, chunk_flags = self._ag_bufs[key]
         e = self.next_epoch(SLOT_AG)
         self.signal(SLOT_AG, e)
         _lib.check(_lib.lib().pear_ag_gemm_bf16(a_shard.c_ptrs, _lib.ptr(b), _lib.ptr(c), m, n, k, a_shard.tensor.stride(0), b.stride(0),
                                                  c.stride(0), 1 if out_dtype == torch.bfloat16 else 0, self.rank, self.world,
                                                  _lib.ptr(self.flags.tensor), SLOT_AG, e, DEFAULT_BUDGET, _lib.ptr(self.status), self.num_sms,
-                                                 _lib.stream()), "ag_gemm")
+                                                 _lib.ptr(a_full), _lib.ptr(chunk_flags), _lib.stream()), "ag_gemm")
         _lib.LAUNCH_COUNT += 1
         return c
 
