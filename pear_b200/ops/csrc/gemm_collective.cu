@@ -9,9 +9,12 @@
 //       M = N = K = 8192 on two GPUs).
 //
 //   GEMM -> reduce-scatter   C_r[M/W, N] = sum_s A_s[M, K_s] * B_s[N, K_s]^T restricted to the rows rank r owns
-//       There is no reduce pass: the epilogue adds each finished fp32 tile into the OWNER's accumulation buffer with
-//       vectorised `red.global.add` over NVLink while the tensor cores work on the next tile. Tiles are visited owner by
-//       owner starting after the own rank, so at any moment the ranks write to different owners.
+//       There is no reduce pass: tiles are visited owner by owner starting after the own rank (at any moment the ranks
+//       write to different owners) and the own tiles come last. The epilogue of a tile owned by a peer PUSHES the fp32
+//       partial into that peer's staging slot for this source with plain 16-byte stores over NVLink and raises a per-tile
+//       flag; the epilogue of an own tile waits (bounded) for the flags of the other sources, adds their staged partials
+//       (local reads) to its accumulator and writes the final rows. No atomics, no zeroing; a first version that used
+//       `red.add` packets over NVLink ran at 0.90 ms against 0.51 ms for cuBLAS + NCCL at 8192^3 on two GPUs.
 //
 // Upstream runs these as separate steps (FSDP2 NCCL all-gather then cuBLAS, `operands.py:204`; split-K partials then
 // `ar_norm.cu` at TP2). The main loop is the one of gemm_tcgen05.cu: 4-stage TMA ring, one MMA-issuing thread, two TMEM
@@ -35,6 +38,9 @@ struct MapSet {
 };
 struct OutPtrs {
   float* p[kCMaxRanks];
+};
+struct FlagPtrs {
+  uint32_t* p[kCMaxRanks];
 };
 
 __device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
@@ -72,12 +78,13 @@ __global__ void __launch_bounds__(kCThreads, 1)
 gemm_coll_kernel(const __grid_constant__ MapSet maps, const __grid_constant__ CUtensorMap map_b, void* __restrict__ c,
                  const __grid_constant__ OutPtrs outs, int M, int N, int K, int ldc, int rank, int world,
                  const uint32_t* __restrict__ my_flags, int slot, uint32_t epoch, uint32_t budget, int* status,
-                 uint4* __restrict__ a_full, uint32_t* __restrict__ chunk_flags) {
+                 uint4* __restrict__ a_full, uint32_t* __restrict__ chunk_flags, const __grid_constant__ FlagPtrs rs_flags) {
   extern __shared__ __align__(1024) uint8_t smem[];
   __shared__ int copier_ok;
   constexpr uint32_t kABytes = kCBM * kCBK * 2, kBBytes = BN * kCBK * 2, kStageBytes = kABytes + kBBytes;
   uint8_t* tiles = smem;
   CollSmem* sm = (CollSmem*)(smem + kCStages * kStageBytes);
+  float* epi_tile = (float*)(smem + kCStages * kStageBytes + 1024);  // 4 warps x 32 x 33 floats (reduce-scatter push)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_m = M / kCBM, tiles_n = (N + BN - 1) / BN, ntiles = tiles_m * tiles_n;
   const int kblocks = (K + kCBK - 1) / kCBK;
@@ -171,6 +178,17 @@ gemm_coll_kernel(const __grid_constant__ MapSet maps, const __grid_constant__ CU
       if (!ok) break;
       tcgen05_fence_after();
       const int row = m0 + q * 32 + lane;
+      // index of this tile among the owner's tiles: (m tile inside the owner's rows) * tiles_n + n tile
+      const int tile_in_owner = ((m0 - owner * m_local) / kCBM) * tiles_n + n0 / BN;
+      if (MODE == 1 && owner == rank && world > 1) {
+        if (warp == 2 && lane == 0) {
+          for (int s2 = 1; s2 < world; ++s2) {
+            const int src = (rank + s2) % world;
+            if (!wait_epoch(rs_flags.p[rank] + (size_t)src * tiles_m_local * tiles_n + tile_in_owner, epoch, budget)) set_status(status, PEAR_ERR_FLAG_TIMEOUT);
+          }
+        }
+        asm volatile("bar.sync 4, 128;" ::: "memory");
+      }
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t r[32];
@@ -178,16 +196,50 @@ gemm_coll_kernel(const __grid_constant__ MapSet maps, const __grid_constant__ CU
         tcgen05_wait_ld();
         const int col = n0 + c0;
         if (MODE == 1) {
-          // the owner's accumulation buffer holds ITS rows only: [M / world, ldc] fp32
-          float* dst = outs.p[owner] + (size_t)(row - owner * m_local) * ldc + col;
-          if (col + 32 <= N) {
+          const int lrow = row - owner * m_local;
+          if (owner != rank) {
+            // push the partial into the owner's staging slot of this source: stage[owner][rank][lrow][col]. The accumulator
+            // arrives one ROW per lane; over NVLink a warp store should cover contiguous bytes, so the 32 x 32 block is
+            // transposed through shared memory and written one 128-byte row segment per warp instruction.
+            float* tb = epi_tile + (warp - 2) * (32 * 33);
 #pragma unroll
-            for (int j = 0; j < 32; j += 4)
-              red_add_v4_f32_sys(dst + j, __uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
-                                 __uint_as_float(r[j + 3]));
+            for (int j = 0; j < 32; ++j) tb[lane * 33 + j] = __uint_as_float(r[j]);
+            __syncwarp();
+            const int lrow0 = (m0 - owner * m_local) + q * 32;
+            float* dst0 = outs.p[owner] + ((size_t)rank * m_local + lrow0) * ldc + col;
+            if (col + lane < N) {
+#pragma unroll 4
+              for (int rr = 0; rr < 32; ++rr) dst0[(size_t)rr * ldc + lane] = tb[rr * 33 + lane];
+            }
+            __syncwarp();
           } else {
-            for (int j = 0; j < 32; ++j)
-              if (col + j < N) atomicAdd_system(dst + j, __uint_as_float(r[j]));
+            // own tile: add what the other sources pushed (their flags were awaited before this loop) and write the result
+            float* dst = (float*)c + (size_t)lrow * ldc + col;
+            for (int s2 = 1; s2 < world; ++s2) {
+              const int src = (rank + s2) % world;
+              const float* ps = outs.p[rank] + ((size_t)src * m_local + lrow) * ldc + col;
+              if (col + 32 <= N) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 4) {
+                  const float4 v = __ldcg((const float4*)(ps + j));
+                  r[j] = __float_as_uint(__uint_as_float(r[j]) + v.x);
+                  r[j + 1] = __float_as_uint(__uint_as_float(r[j + 1]) + v.y);
+                  r[j + 2] = __float_as_uint(__uint_as_float(r[j + 2]) + v.z);
+                  r[j + 3] = __float_as_uint(__uint_as_float(r[j + 3]) + v.w);
+                }
+              } else {
+                for (int j = 0; j < 32; ++j)
+                  if (col + j < N) r[j] = __float_as_uint(__uint_as_float(r[j]) + __ldcg(ps + j));
+              }
+            }
+            if (col + 32 <= N) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4)
+                *(float4*)(dst + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (col + j < N) dst[j] = __uint_as_float(r[j]);
+            }
           }
         } else if (OUT_BF16) {
           __nv_bfloat16* dst = (__nv_bfloat16*)c + (size_t)row * ldc + col;
@@ -222,6 +274,13 @@ gemm_coll_kernel(const __grid_constant__ MapSet maps, const __grid_constant__ CU
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&sm->tmem_empty[ab]);
+      if (MODE == 1 && owner != rank) {
+        // the whole tile is stored: publish it to the owner (release after every epilogue thread's stores)
+        __threadfence_system();
+        asm volatile("bar.sync 4, 128;" ::: "memory");
+        if (warp == 2 && lane == 0)
+          asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(rs_flags.p[owner] + (size_t)rank * tiles_m_local * tiles_n + tile_in_owner), "r"(epoch) : "memory");
+      }
     }
     if (MODE == 1) __threadfence_system();  // the adds are performed before the host-ordered "done" signal that follows the kernel
   }
@@ -294,8 +353,8 @@ static int coll_map_bf16(CUtensorMap* map, const void* base, int rows, int cols,
 template <int BN, int MODE, bool OUT_BF16>
 static int launch_coll(const MapSet& maps, const CUtensorMap& mb, void* c, const OutPtrs& outs, int M, int N, int K, int ldc, int rank,
                        int world, const uint32_t* flags, int slot, uint32_t epoch, uint32_t budget, int* status, int num_sms,
-                       cudaStream_t stream, void* a_full = nullptr, void* chunk_flags = nullptr) {
-  constexpr int smem = kCStages * (kCBM * kCBK * 2 + BN * kCBK * 2) + 1024;
+                       cudaStream_t stream, void* a_full = nullptr, void* chunk_flags = nullptr, const FlagPtrs* rs_flags = nullptr) {
+  constexpr int smem = kCStages * (kCBM * kCBK * 2 + BN * kCBK * 2) + 1024 + 4 * 32 * 33 * 4;
   static bool configured = false;
   if (!configured) {
     PEAR_CUDA_CHECK(cudaFuncSetAttribute(gemm_coll_kernel<BN, MODE, OUT_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -304,7 +363,7 @@ static int launch_coll(const MapSet& maps, const CUtensorMap& mb, void* c, const
   const int ntiles = (M / kCBM) * ((N + BN - 1) / BN);
   const int grid = ntiles < num_sms ? ntiles : num_sms;
   gemm_coll_kernel<BN, MODE, OUT_BF16><<<grid, kCThreads, smem, stream>>>(maps, mb, c, outs, M, N, K, ldc, rank, world, flags, slot, epoch,
-                                                                          budget, status, (uint4*)a_full, (uint32_t*)chunk_flags);
+                                                                          budget, status, (uint4*)a_full, (uint32_t*)chunk_flags, rs_flags ? *rs_flags : FlagPtrs{});
   PEAR_LAUNCH_CHECK();
   return 0;
 }
@@ -337,11 +396,13 @@ PEAR_API int pear_ag_gemm_bf16(const void* const* a_shards, const void* b, void*
                   : launch_coll<256, 0, false>(maps, mb, c, shards, M, N, K, ldc, rank, world, (const uint32_t*)my_flags, slot, epoch, budget, status, num_sms, s, a_full, chunk_flags);
 }
 
-// GEMM -> reduce-scatter. A [M, K_local], B [N, K_local] local bf16; acc[r]: rank r's fp32 [M / world, ldc] accumulation
-// buffer in symmetric memory, zeroed by its owner before any rank launches (order that with pear_symm_signal / wait).
-// After the kernel, signal completion; the owner waits for every rank's signal before reading its buffer.
-PEAR_API int pear_gemm_rs_bf16(const void* a, const void* b, void* const* acc, int M, int N, int K, int lda, int ldb, int ldc, int rank,
-                               int world, int* status, int num_sms, void* stream) {
+// GEMM -> reduce-scatter. A [M, K_local], B [N, K_local] local bf16. stage[r]: rank r's staging buffer in symmetric memory,
+// fp32 [world sources][M / world][ldc]; flags[r]: rank r's uint32 [world sources][tiles of an owner] in symmetric memory
+// (any values below `epoch`); out: local fp32 [M / world, ldc] result. Before the call every rank must have finished
+// reading its staging buffer of the previous call (one pear_symm_signal / wait round). The result is complete when the
+// kernel ends.
+PEAR_API int pear_gemm_rs_bf16(const void* a, const void* b, void* const* stage, void* const* flags, void* out, int M, int N, int K, int lda,
+                               int ldb, int ldc, int rank, int world, unsigned epoch, unsigned budget, int* status, int num_sms, void* stream) {
   if (world < 1 || world > kCMaxRanks || M % (world * kCBM) || (lda % 8) || (ldb % 8) || (ldc % 4) || N % 4) return (int)cudaErrorInvalidValue;
   MapSet maps;
   int e = coll_map_bf16(&maps.a[0], a, M, K, lda, kCBM);
@@ -351,6 +412,8 @@ PEAR_API int pear_gemm_rs_bf16(const void* a, const void* b, void* const* acc, i
   e = coll_map_bf16(&mb, b, N, K, ldb, 256);
   if (e) return e;
   OutPtrs outs{};
-  for (int r = 0; r < world; ++r) outs.p[r] = (float*)acc[r];
-  return launch_coll<256, 1, false>(maps, mb, nullptr, outs, M, N, K, ldc, rank, world, nullptr, 0, 0, 0, status, num_sms, (cudaStream_t)stream);
+  FlagPtrs fl{};
+  for (int r = 0; r < world; ++r) { outs.p[r] = (float*)stage[r]; fl.p[r] = (uint32_t*)flags[r]; }
+  return launch_coll<256, 1, false>(maps, mb, out, outs, M, N, K, ldc, rank, world, nullptr, 0, epoch, budget, status, num_sms, (cudaStream_t)stream,
+                                    nullptr, nullptr, &fl);
 }

@@ -136,24 +136,28 @@ class SymmWorld:
 
     # -- GEMM -> reduce-scatter ---------------------------------------------------------------------------------------
     def make_rs_accumulator(self, rows_local: int, n: int) -> SymmBuffer:
-        return self.alloc((rows_local, n), torch.float32)
+        """Staging for ``gemm_rs``: one fp32 slot of this rank's rows per source rank, plus per-tile flags."""
+        buf = self.alloc((self.world, rows_local, n), torch.float32)
+        tiles = (rows_local // 128) * ((n + 255) // 256)
+        buf.flags = self.alloc((self.world, tiles), torch.int32)
+        buf.flags.tensor.zero_()
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)
+        return buf
 
     def gemm_rs(self, a: torch.Tensor, b: torch.Tensor, acc: SymmBuffer) -> torch.Tensor:
-        """``sum_ranks(A_r @ B_r^T)`` restricted to this rank's rows; returns ``acc.tensor`` (fp32 [M / world, N])."""
+        """``sum_ranks(A_r @ B_r^T)`` restricted to this rank's rows, fp32 [M / world, N]."""
         m, k = a.shape
         n = b.shape[0]
-        acc.tensor.zero_()
-        e = self.next_epoch(SLOT_RS_ZERO)
-        self.signal(SLOT_RS_ZERO, e)
-        self.wait(SLOT_RS_ZERO, e)  # every owner's buffer is zero before anyone adds into it
-        ptrs = (ctypes.c_void_p * self.world)(*acc.ptrs)
-        _lib.check(_lib.lib().pear_gemm_rs_bf16(_lib.ptr(a), _lib.ptr(b), ptrs, m, n, k, a.stride(0), b.stride(0), acc.tensor.stride(0),
-                                                 self.rank, self.world, _lib.ptr(self.status), self.num_sms, _lib.stream()), "gemm_rs")
-        _lib.LAUNCH_COUNT += 1
+        out = torch.empty(m // self.world, n, dtype=torch.float32, device=self.device)
+        self.device_barrier()  # every rank has finished reading what the previous call pushed into its staging buffer
         e = self.next_epoch(SLOT_RS_DONE)
-        self.signal(SLOT_RS_DONE, e)
-        self.wait(SLOT_RS_DONE, e)  # every rank's adds have landed in my buffer
-        return acc.tensor
+        stage = (ctypes.c_void_p * self.world)(*acc.ptrs)
+        flags = (ctypes.c_void_p * self.world)(*acc.flags.ptrs)
+        _lib.check(_lib.lib().pear_gemm_rs_bf16(_lib.ptr(a), _lib.ptr(b), stage, flags, _lib.ptr(out), m, n, k, a.stride(0), b.stride(0), out.stride(0),
+                                                 self.rank, self.world, e, DEFAULT_BUDGET, _lib.ptr(self.status), self.num_sms, _lib.stream()), "gemm_rs")
+        _lib.LAUNCH_COUNT += 1
+        return out
 
     # -- vocab-parallel logits all-gather -----------------------------------------------------------------------------
     def all_gather_logits(self, shard: torch.Tensor, full: SymmBuffer) -> torch.Tensor:
