@@ -123,7 +123,7 @@ gemm_coll_kernel(const __grid_constant__ MapSet maps, const __grid_constant__ CU
         tile_coords(tile, owner, m0, n0);
         if (MODE == 0 && owner != rank) {
           // the copier warps publish every remote 128-row block of A in the local full buffer
-          if (!wait_epoch_gpu(chunk_flags + m0 / kCBM, epoch, budget)) set_status(status, PEAR_ERR_FLAG_TIMEOUT);
+          if (!wait_epoch_gpu(chunk_flags + m0 / kCBM, 8u, budget)) set_status(status, PEAR_ERR_FLAG_TIMEOUT);  // all 8 pieces of the block
         }
         (void)ready;
         // MODE 0: maps.a[0] = the local shard (rows relative to it), maps.a[1] = the local full-A buffer (global rows)
@@ -287,35 +287,39 @@ gemm_coll_kernel(const __grid_constant__ MapSet maps, const __grid_constant__ CU
   if (MODE == 0 && warp >= 6 && world > 1) {
     // ------------------------------------------------------------------------------------------------ copier warps
     const int ct = threadIdx.x - 192;  // 0..63
+    // A 128-row block is copied as kSub pieces of 16 rows by (up to) kSub different CTAs, so that all SMs' copier warps
+    // share the gather; the block's counter (zero at launch) counts its pieces, the consumer waits for kSub.
+    constexpr int kSub = 8;
     const int remote_tiles = tiles_m - tiles_m_local;
-    const size_t vec_per_block = (size_t)kCBM * K / 8;  // 16-byte vectors of a 128-row block (rows are contiguous: lda == K)
-    for (int cidx = blockIdx.x; cidx < remote_tiles; cidx += gridDim.x) {
-      const int owner = (rank + 1 + cidx / tiles_m_local) % world, mt = cidx % tiles_m_local;
+    const size_t vec_per_piece = (size_t)(kCBM / kSub) * K / 8;  // 16-byte vectors of 16 rows (rows are contiguous: lda == K)
+    for (int cidx = blockIdx.x; cidx < remote_tiles * kSub; cidx += gridDim.x) {
+      const int t = cidx / kSub, piece = cidx % kSub;
+      const int owner = (rank + 1 + t / tiles_m_local) % world, mt = t % tiles_m_local;
       if (ct == 0) {
         copier_ok = wait_epoch(my_flags + slot * kCMaxRanks + owner, epoch, budget) ? 1 : 0;
         if (!copier_ok) set_status(status, PEAR_ERR_FLAG_TIMEOUT);
       }
       asm volatile("bar.sync 3, 64;" ::: "memory");
       if (copier_ok) {
-        const uint4* src = (const uint4*)outs.p[owner] + (size_t)mt * vec_per_block;
-        uint4* dst = a_full + (size_t)(owner * tiles_m_local + mt) * vec_per_block;
-        for (size_t i = ct; i < vec_per_block; i += 64 * 8) {
+        const uint4* src = (const uint4*)outs.p[owner] + ((size_t)mt * kSub + piece) * vec_per_piece;
+        uint4* dst = a_full + ((size_t)(owner * tiles_m_local + mt) * kSub + piece) * vec_per_piece;
+        for (size_t i = ct; i < vec_per_piece; i += 64 * 8) {
           uint4 v[8];
 #pragma unroll
           for (int u = 0; u < 8; ++u)
-            if (i + (size_t)u * 64 < vec_per_block)
+            if (i + (size_t)u * 64 < vec_per_piece)
               asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w) : "l"(src + i + (size_t)u * 64) : "memory");
 #pragma unroll
           for (int u = 0; u < 8; ++u)
-            if (i + (size_t)u * 64 < vec_per_block) dst[i + (size_t)u * 64] = v[u];
+            if (i + (size_t)u * 64 < vec_per_piece) dst[i + (size_t)u * 64] = v[u];
         }
         // the block is read by TMA (async proxy) of other CTAs: make the generic-proxy stores visible to it
         asm volatile("fence.proxy.async;" ::: "memory");
         __threadfence();
       }
       asm volatile("bar.sync 3, 64;" ::: "memory");
-      // publish also after a timeout (the status word already says so): nobody is left waiting for this block
-      if (ct == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(chunk_flags + owner * tiles_m_local + mt), "r"(epoch) : "memory");
+      // counted also after a timeout (the status word already says so): nobody is left waiting for this block
+      if (ct == 0) asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(chunk_flags + owner * tiles_m_local + mt), "r"(1u) : "memory");
     }
   }
   tcgen05_fence_before();
@@ -375,7 +379,7 @@ using namespace pear;
 // all-gather -> GEMM. a_shards[r]: rank r's [M / world, K] bf16 shard (symmetric memory, rows contiguous: lda == K);
 // my_flags: this rank's signal region; the owner of shard r must have signalled `epoch` in `slot` (pear_symm_signal)
 // after writing it. a_full: local [M, K] bf16 buffer the remote shards are copied into; chunk_flags: local uint32 per
-// 128-row block of A (any values below `epoch`). C [M, N] is local (fp32 or bf16). M / world must be a multiple of 128.
+// 128-row block of A, ZERO at launch (the 8 pieces of a block each add one). C [M, N] is local (fp32 or bf16). M / world must be a multiple of 128.
 PEAR_API int pear_ag_gemm_bf16(const void* const* a_shards, const void* b, void* c, int M, int N, int K, int lda, int ldb, int ldc,
                                int out_bf16, int rank, int world, const void* my_flags, int slot, unsigned epoch, unsigned budget,
                                int* status, int num_sms, void* a_full, void* chunk_flags, void* stream) {

@@ -121,6 +121,7 @@ class SymmWorld:
             self._ag_bufs[key] = (torch.empty(m, k, dtype=torch.bfloat16, device=self.device),
                                   torch.zeros(m // 128, dtype=torch.int32, device=self.device))
         a_full, chunk_flags = self._ag_bufs[key]
+        chunk_flags.zero_()  # piece counters of the remote blocks
         e = self.next_epoch(SLOT_AG)
         self.signal(SLOT_AG, e)
         _lib.check(_lib.lib().pear_ag_gemm_bf16(a_shard.c_ptrs, _lib.ptr(b), _lib.ptr(c), m, n, k, a_shard.tensor.stride(0), b.stride(0),
