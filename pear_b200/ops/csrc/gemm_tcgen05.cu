@@ -30,6 +30,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_m = (M + kBM - 1) / kBM, tiles_n = (N + BN - 1) / BN, ntiles = tiles_m * tiles_n;
   const int kblocks = (K + kBK - 1) / kBK;
+  // Tile order: bands of kBand row tiles; inside a band the row tile varies fastest, so the ~148 tiles in flight at any time cover about kBand x (148 / kBand) tiles: kBand A panels and ~9 B panels
+  // (~70 MB at K = 8192) stay in the 126 MB L2 instead of 148 different A panels streaming from HBM for every wave.
+  constexpr int kBand = 16;
+  auto tile_origin = [&](int t, int& m0, int& n0) {
+    const int band = t / (kBand * tiles_n), in_band = t % (kBand * tiles_n);
+    const int rows_here = min(kBand, tiles_m - band * kBand);
+    m0 = (band * kBand + in_band % rows_here) * kBM;
+    n0 = (in_band / rows_here) * BN;
+  };
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < kStages; ++i) { mbar_init(&sm->full[i], 1); mbar_init(&sm->empty[i], 1); }
@@ -53,7 +62,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       int st = 0, ph = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % tiles_m) * kBM, n0 = (tile / tiles_m) * BN;
+        int m0, n0;
+        tile_origin(tile, m0, n0);
         for (int kb = 0; kb < kblocks; ++kb) {
           ok = mbar_wait_bounded(&sm->empty[st], ph ^ 1, status);
           if (!ok) break;
@@ -99,7 +109,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     bool ok = true;
     for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++it) {
       const int ab = it & 1;
-      const int m0 = (tile % tiles_m) * kBM, n0 = (tile / tiles_m) * BN;
+      int m0, n0;
+      tile_origin(tile, m0, n0);
       if (ok) ok = mbar_wait_bounded(&sm->tmem_full[ab], (it >> 1) & 1, status);
       if (!ok) break;
       tcgen05_fence_after();
