@@ -89,13 +89,17 @@ gemm_coll_kernel(const __grid_constant__ MapSet maps, const __grid_constant__ CU
   const int tiles_m = M / kCBM, tiles_n = (N + BN - 1) / BN, ntiles = tiles_m * tiles_n;
   const int kblocks = (K + kCBK - 1) / kCBK;
   const int m_local = M / world, tiles_m_local = m_local / kCBM;
-  // tile order: owner-major starting at the own rank (MODE 0) or at the next rank (MODE 1); within an owner n varies fastest
+  // tile order: owner-major starting at the own rank (MODE 0) or at the next rank (MODE 1)
   auto tile_coords = [&](int t, int& owner, int& m0, int& n0) {
     const int per_owner = tiles_m_local * tiles_n;
     const int o = t / per_owner, rest = t % per_owner;
     owner = (rank + (MODE == 1 ? 1 : 0) + o) % world;
-    m0 = (owner * tiles_m_local + rest / tiles_n) * kCBM;
-    n0 = (rest % tiles_n) * BN;
+    // inside an owner's rows: bands of 16 row tiles, the row tile varying fastest (a wave's A and B panels stay in L2)
+    constexpr int kBand = 16;
+    const int band = rest / (kBand * tiles_n), in_band = rest % (kBand * tiles_n);
+    const int rows_here = min(kBand, tiles_m_local - band * kBand);
+    m0 = (owner * tiles_m_local + band * kBand + in_band % rows_here) * kCBM;
+    n0 = (in_band / rows_here) * BN;
   };
 
   if (threadIdx.x == 0) {
