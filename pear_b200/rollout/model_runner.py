@@ -72,6 +72,13 @@ class ModelRunner:
                            for l in self.gdn_layers}
         self.rec_state = {l: torch.zeros(num_state_slots, cfg.gdn_v_heads, cfg.gdn_head_dim, cfg.gdn_head_dim, dtype=torch.float32,
                                          device=self.device) for l in self.gdn_layers}
+        # On a GPU the decode / verify rows go through the CUDA kernels of ops/csrc/rollout_kernels.cu (split-KV paged
+        # attention straight from the block table, the fused GDN decode step); long prefill chunks and shapes the kernels
+        # are not built for take the PyTorch statements.
+        group = cfg.num_attention_heads // max(1, cfg.num_kv_heads)
+        self.use_kernels = self.device.type == "cuda"
+        self._attn_kernel_ok = cfg.head_dim in (128, 256) and group <= 8 and block_size == 16 and kv_dtype == torch.bfloat16
+        self._gdn_kernel_ok = cfg.gdn_head_dim == 128 and cfg.conv_kernel == 4
 
     # -- cache plumbing for the block manager / host tier -----------------------------------------------------------------
     def kv_tensors(self) -> list[torch.Tensor]:
@@ -118,12 +125,35 @@ class ModelRunner:
 
         meta = SeqMeta(cu_seqlens=bounds, cos=cos, sin=sin)
         q, k, v, gate = att.project(hidden, meta)
-        outs = []
+        outs: list = [None] * len(rows)
+        short = []  # rows of at most 8 query tokens: decode and verify blocks
         for i, row in enumerate(rows):
             s, e = bounds[i], bounds[i + 1]
             self._write_kv(kc, vc, row, k[s:e], v[s:e])
+            if self.use_kernels and self._attn_kernel_ok and e - s <= 8:
+                short.append(i)
+                continue
             kk, vv = self._read_kv(kc, vc, row, row.start + (e - s))
-            outs.append(ref.attention_with_cache(q[s:e], kk, vv, row.start, cfg.head_dim ** -0.5))
+            outs[i] = ref.attention_with_cache(q[s:e], kk, vv, row.start, cfg.head_dim ** -0.5)
+        if short:
+            from ..ops import rollout_ops
+
+            idx, ctx, tabs = [], [], []
+            maxb = max(len(rows[i].block_table) for i in short)
+            for i in short:
+                s, e = bounds[i], bounds[i + 1]
+                for j in range(e - s):
+                    idx.append(s + j)
+                    ctx.append(rows[i].start + j + 1)  # causal inside the block: row j sees the context up to itself
+                    tabs.append(rows[i].block_table + [0] * (maxb - len(rows[i].block_table)))
+            sel = torch.tensor(idx, device=self.device)
+            o_short = rollout_ops.paged_attention(q[sel].float().contiguous(), kc, vc, torch.tensor(tabs, dtype=torch.int32, device=self.device),
+                                                  torch.tensor(ctx, dtype=torch.int32, device=self.device), cfg.head_dim ** -0.5)
+            off = 0
+            for i in short:
+                n = bounds[i + 1] - bounds[i]
+                outs[i] = o_short[off:off + n]
+                off += n
         o = torch.cat(outs, dim=0)
         o = (ops.sigmoid_gate(o, gate) if gate is not None else o).reshape(hidden.shape[0], cfg.q_size)
         return row_linear(o, att.o_proj.weight)
@@ -135,6 +165,18 @@ class ModelRunner:
         z = linear_fp32(hidden, gdn.in_proj_z.weight).view(t, cfg.gdn_v_heads, cfg.gdn_head_dim)
         b = linear_fp32(hidden, gdn.in_proj_b.weight)
         a = linear_fp32(hidden, gdn.in_proj_a.weight)
+        if (self.use_kernels and self._gdn_kernel_ok and not speculative and all(bounds[i + 1] - bounds[i] == 1 for i in range(len(rows)))
+                and all(not (r.seq.commit_rows > 0 and li in r.seq.pending) for r in rows)):
+            # plain decode step: one token per sequence -> the fused kernel (conv update, gates, L2 norm, delta rule, gated norm)
+            from ..ops import rollout_ops
+
+            slots = torch.tensor([r.seq.slot for r in rows], dtype=torch.int32, device=self.device)
+            y = rollout_ops.gdn_decode(mixed.float().contiguous(), z.reshape(t, -1).float().contiguous(), a.float().contiguous(), b.float().contiguous(),
+                                       gdn.conv_weight().float().contiguous(), gdn.A_log.float(), gdn.dt_bias.float(), gdn.norm.weight.float(),
+                                       self.conv_state[li], self.rec_state[li], slots, cfg.gdn_qk_heads, cfg.gdn_v_heads, cfg.l2_eps, cfg.rms_eps)
+            for r in rows:
+                r.seq.pending.pop(li, None)
+            return row_linear(y, gdn.out_proj.weight)
         outs = []
         for i, row in enumerate(rows):
             s, e = bounds[i], bounds[i + 1]

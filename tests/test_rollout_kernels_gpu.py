@@ -172,3 +172,25 @@ def test_gdn_front_end(ops):
     k = ref.l2norm(want[:, hk * d: 2 * hk * d].view(-1, hk, d)).reshape(-1, hk * d)
     want = torch.cat([q, k, want[:, 2 * hk * d:]], dim=1)
     assert torch.allclose(y, want, atol=1e-5, rtol=1e-4), (y - want).abs().max()
+
+
+def test_rollout_engine_decodes_through_the_kernels(ops):
+    """The engine's decode steps on a GPU use the paged-attention and GDN-decode kernels; tokens equal the PyTorch path."""
+    from pear_b200.models.config import HybridConfig
+    from pear_b200.models.hybrid import HybridForCausalLM
+    from pear_b200.ops import lib as kl
+    from pear_b200.rollout.engine import EngineConfig, RolloutEngine, SamplingParams
+
+    cfg = HybridConfig(vocab_size=4096, hidden_size=512, num_layers=4, num_attention_heads=8, num_kv_heads=2, head_dim=128, rotary_dim=64,
+                       gdn_qk_heads=2, gdn_v_heads=4, gdn_head_dim=128, intermediate_size=1024, num_mtp_layers=0)
+    prompts = [list(range(3, 40)), list(range(100, 117)), [5, 6, 7]]
+    outs = {}
+    for use in (True, False):
+        model = HybridForCausalLM(cfg, with_mtp=False).init_weights(4)
+        eng = RolloutEngine(model, EngineConfig(num_blocks=128, max_num_seqs=4), device="cuda")
+        eng.runner.use_kernels = use
+        before = kl.LAUNCH_COUNT
+        reqs = eng.generate(prompts, SamplingParams(max_tokens=12, temperature=0.0))
+        outs[use] = ([r.output for r in reqs], kl.LAUNCH_COUNT - before)
+    assert outs[True][0] == outs[False][0]
+    assert outs[True][1] > outs[False][1] + 50  # the decode steps launched the attention and GDN kernels
