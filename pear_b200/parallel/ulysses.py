@@ -53,9 +53,14 @@ class SequenceParallel:
                 raise ValueError(f"{hkv} kv heads cannot be spread over {sp} ranks")
             k = k.repeat_interleave(rep, dim=1)
             v = v.repeat_interleave(rep, dim=1)
-        qh, kh, vh = self._seq_to_heads(q), self._seq_to_heads(k), self._seq_to_heads(v)
-        o = ops.causal_attention(qh, kh, vh, cu_seqlens, scale)
-        return self._heads_to_seq(o, t_local)
+        # ONE all-to-all in: q, k and v are packed rank-major, [sp, T_local, hq/sp + 2 hkv/sp, D], so that rank j receives
+        # its query heads together with their KV heads from every sequence slice in a single message per peer
+        hq_l, hk_l, d = hq // sp, k.shape[1] // sp, q.shape[2]
+        packed = torch.cat([q.reshape(t_local, sp, hq_l, d), k.reshape(t_local, sp, hk_l, d), v.reshape(t_local, sp, hk_l, d)], dim=2)
+        got = C.all_to_all(packed.permute(1, 0, 2, 3).contiguous(), self.group).reshape(sp * t_local, hq_l + 2 * hk_l, d)
+        qh, kh, vh = got[:, :hq_l], got[:, hq_l:hq_l + hk_l], got[:, hq_l + hk_l:]
+        o = ops.causal_attention(qh.contiguous(), kh.contiguous(), vh.contiguous(), cu_seqlens, scale)
+        return self._heads_to_seq(o, t_local)  # ONE all-to-all out
 
     # -----------------------------------------------------------------------------------------------------------------
     # gated delta net: local scan with an incoming state chained across ranks
