@@ -67,12 +67,8 @@ __device__ __forceinline__ bool wait_epoch_gpu(const uint32_t* flag, uint32_t ep
   }
   return false;
 }
-__device__ __forceinline__ void red_add_v4_f32_sys(float* addr, float a, float b, float c, float d) {
-  asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
-}
-
-// MODE 0: all-gather -> GEMM (A from maps.a[owner], C local, plain stores, fp32 or bf16)
-// MODE 1: GEMM -> reduce-scatter (A, B local = maps.a[0], C tiles red-added into outs.p[owner])
+// MODE 0: all-gather -> GEMM (outs.p[r] = rank r's A shard; A tiles from the local shard or the local full buffer; C local)
+// MODE 1: GEMM -> reduce-scatter (A, B local; outs.p[r] = rank r's staging buffer; c = this rank's result rows)
 template <int BN, int MODE, bool OUT_BF16>
 __global__ void __launch_bounds__(kCThreads, 1)
 gemm_coll_kernel(const __grid_constant__ MapSet maps, const __grid_constant__ CUtensorMap map_b, void* __restrict__ c,
@@ -121,7 +117,6 @@ gemm_coll_kernel(const __grid_constant__ MapSet maps, const __grid_constant__ CU
       prefetch_tensormap(&map_b);
       int st = 0, ph = 0;
       bool ok = true;
-      uint32_t ready = 1u << rank;  // owners whose shard is known to be written
       for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
         int owner, m0, n0;
         tile_coords(tile, owner, m0, n0);
@@ -129,7 +124,6 @@ gemm_coll_kernel(const __grid_constant__ MapSet maps, const __grid_constant__ CU
           // the copier warps publish every remote 128-row block of A in the local full buffer
           if (!wait_epoch_gpu(chunk_flags + m0 / kCBM, 8u, budget)) set_status(status, PEAR_ERR_FLAG_TIMEOUT);  // all 8 pieces of the block
         }
-        (void)ready;
         // MODE 0: maps.a[0] = the local shard (rows relative to it), maps.a[1] = the local full-A buffer (global rows)
         const CUtensorMap* ma = MODE == 0 ? (owner == rank ? &maps.a[0] : &maps.a[1]) : &maps.a[0];
         const int am0 = (MODE == 0 && owner == rank) ? m0 - owner * m_local : m0;

@@ -58,14 +58,13 @@ __device__ void block_topk(float* vals, int* ids, int n, float* out_v, int* out_
 
 __global__ void __launch_bounds__(256) sample_chunks_kernel(const float* __restrict__ logits, int V, int ld, float inv_temp,
                                                             const float* __restrict__ noise, int chunks, int topk, ChunkRec* __restrict__ recs) {
-  extern __shared__ float sh[];  // candidate values [cap] | ids [cap] | reduction scratch
+  extern __shared__ float sh[];  // top-K pass: candidate values [2048 + K] | ids [2048 + K] | running best values [K] | ids [K]
   const int row = blockIdx.y, chunk = blockIdx.x, tid = threadIdx.x;
   const int per = (V + chunks - 1) / chunks, lo = chunk * per, hi = min(V, lo + per);
   const float* x = logits + (size_t)row * ld;
   const float* u = noise + (size_t)row * V;
   float m = -FLT_MAX, bk = -FLT_MAX, bz = 0.f;
   int bid = -1, nf = 0;
-  // per-thread top-2 candidates feed the block top-K (K <= 32 of up to 512 candidates: exact for K <= 2 * 256 / ... see below)
   for (int i = lo + tid; i < hi; i += blockDim.x) {
     const float z = x[i] * inv_temp;
     if (isnan(z) || z == INFINITY) ++nf;

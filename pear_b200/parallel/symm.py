@@ -27,7 +27,7 @@ import torch.distributed as dist
 from ..ops import lib as _lib
 
 SLOTS = 32
-SLOT_AR, SLOT_AG, SLOT_RS_ZERO, SLOT_RS_DONE, SLOT_SYNC, SLOT_LOGITS, SLOT_ARGMAX = 0, 1, 2, 3, 4, 5, 6
+SLOT_AR, SLOT_AG, SLOT_RS_DONE, SLOT_SYNC, SLOT_LOGITS, SLOT_ARGMAX = 0, 1, 3, 4, 5, 6
 DEFAULT_BUDGET = 1 << 22  # polls of >= 100 ns: a few hundred milliseconds, then the kernel gives up
 
 
