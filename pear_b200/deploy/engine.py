@@ -183,6 +183,7 @@ class MegakernelEngine:
         self.b_image = self._zeros(2 * self._b_bytes, dtype=torch.uint8)
         self.sfb_image = self._zeros(2 * self._sfb_bytes, dtype=torch.uint8)
         self._gemv_count = 0
+        self.link_gdn = os.environ.get("PEAR_MK_LINK_GDN", "1") != "0"  # GDN items build the out_proj operand
         self.link_gemvs = os.environ.get("PEAR_MK_LINK", "0") != "0"  # finishers build the next operand (measured: no faster)
         self._links: dict[int, int] = {}  # producer GEMV descriptor -> first tile counter
         self._num_counters = 0
@@ -373,7 +374,18 @@ class MegakernelEngine:
                     p.barrier()
                     p.spread(S.OP_GDN, d_core, items)
                     p.barrier()
-                    G(p, d_out, H, VD)
+                    if self.link_gdn:
+                        # the GDN item that completes a value head builds that head's unit of the out_proj operand
+                        if d_core not in self._links:
+                            self._links[d_core] = self._num_counters
+                            self._num_counters += HV
+                            self._descs[d_core]["pad"] = (d_out + 1, self._links[d_core])
+                        base = self._links[d_core]
+                        p.expect.extend([0] * (base + HV - len(p.expect)))
+                        p.expect[base:base + HV] = [sum(1 for it in items if it[0] == hv) for hv in range(HV)]
+                        p.gemv(d_out, H, VD)
+                    else:
+                        G(p, d_out, H, VD)
                     add_zero(p, z_rec, T8 * self.rec_stride)
                     p.barrier()
                     emit_mlp(p, d_out, d_gu, d_dn, gu_rows, ii, H)

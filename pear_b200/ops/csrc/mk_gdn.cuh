@@ -180,6 +180,27 @@ __device__ __noinline__ void op_gdn(Ctx& c, const Instr& ins) {
     for (int i = 0; i < 8; ++i)
       *(float4*)(srow + 16 * i + 4 * kq) = make_float4(S[4 * i], S[4 * i + 1], S[4 * i + 2], S[4 * i + 3]);
   }
+  if (d.pad[0] > 0) {
+    // The head's outputs feed the output projection: the item that completes the head (its last row part) builds that
+    // GEMV's operand unit (one head of 128 values = one unit) instead of a quantisation phase of its own.
+    const Desc& cd = c.p->descs[d.pad[0] - 1];
+    __threadfence();
+    consumer_sync();
+    if (tid == 0) {
+      const int slot = d.pad[1] + hv;
+      const int expect = __ldg(c.p->tile_expect + slot);
+      const bool last = expect > 0 && atomicAdd(c.p->tile_cnt + slot, 1) + 1 == expect;
+      if (last) c.p->tile_cnt[slot] = 0;
+      c.sm->fin_unit = last ? hv : -1;
+    }
+    consumer_sync();
+    const int unit = *(volatile int*)&c.sm->fin_unit;
+    if (unit >= 0) {
+      __threadfence();
+      quant_units(c, cd, unit, 1, kConsumerThreads);
+    }
+    consumer_sync();  // fin_unit is rewritten by the next item
+  }
 }
 
 }  // namespace mk
