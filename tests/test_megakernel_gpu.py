@@ -102,3 +102,24 @@ def test_generate_runs_and_is_deterministic():
     # fp32 atomics make the last logit bits order dependent, so only a prefix is required to repeat
     assert len(a.tokens) == 24 and a.tokens[:4] == b.tokens[:4]
     assert all(0 <= t < model.config.vocab_size for t in a.tokens)
+
+
+def test_deploy_server_completes_through_the_engine():
+    """The one-session server in front of the megakernel engine: a completion returns the requested number of tokens and
+    the counters of its metrics text move."""
+    import torch
+    from pear_b200.deploy.engine import MegakernelEngine, RandomWeights
+    from pear_b200.deploy.server import DeployServer
+    from pear_b200.models.config import HybridConfig
+
+    cfg = HybridConfig(vocab_size=4096, hidden_size=1024, num_layers=4, num_attention_heads=8, num_kv_heads=2, head_dim=256,
+                       gdn_qk_heads=4, gdn_v_heads=8, gdn_head_dim=128, intermediate_size=2048, num_mtp_layers=0)
+    dcfg = HybridConfig(vocab_size=4096, hidden_size=1024, num_layers=2, full_attention_interval=1, num_attention_heads=8,
+                        num_kv_heads=2, head_dim=128, intermediate_size=2048, num_mtp_layers=0, attn_output_gate=False)
+    eng = MegakernelEngine(cfg, dcfg, RandomWeights("cuda", seed=0), max_len=256, n_draft=3, seed=0)
+    srv = DeployServer(eng, name="test")
+    out = srv.complete(list(range(1, 30)), max_tokens=6, temperature=0.8, seed=3)
+    assert len(out["token_ids"]) == 6 and all(0 <= t < 4096 for t in out["token_ids"])
+    again = srv.complete(list(range(1, 30)), max_tokens=6, temperature=0.8, seed=3)
+    assert again["token_ids"] == out["token_ids"]  # same prompt, temperature and seed: same tokens
+    assert "pear_deploy_requests_total{model=\"test\"} 2" in srv.metrics_text()
