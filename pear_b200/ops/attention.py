@@ -100,6 +100,7 @@ def _main() -> None:
     ap.add_argument("--kv-heads", type=int, default=4)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--check", action="store_true")
+    ap.add_argument("--compare", action="store_true")
     a = ap.parse_args()
     dev = torch.device("cuda", 0)
     torch.manual_seed(0)
@@ -122,6 +123,24 @@ def _main() -> None:
     flops = 4.0 * a.heads * HEAD_DIM * a.seqs * per * (per + 1) / 2
     rec = {"op": "attn_varlen_fwd_hd256", "tokens": t, "seqs": a.seqs, "heads": a.heads, "kv_heads": a.kv_heads, "ms": round(ms, 4),
            "tflops_causal": round(flops / ms / 1e9, 1), "status": attention_status()}
+    if a.compare:  # the library call this kernel replaces: torch SDPA on the same bf16 operands, one call per sequence
+        import torch.nn.functional as F
+
+        def lib_call():
+            for b in range(a.seqs):
+                sl = slice(b * per, (b + 1) * per)
+                F.scaled_dot_product_attention(q[sl].transpose(0, 1)[None], k[sl].transpose(0, 1)[None], v[sl].transpose(0, 1)[None],
+                                               is_causal=True, enable_gqa=True)
+
+        for _ in range(3):
+            lib_call()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(a.iters):
+            lib_call()
+        e1.record()
+        torch.cuda.synchronize()
+        rec["sdpa_ms"] = round(e0.elapsed_time(e1) / a.iters, 4)
     if a.check:
         ro, rl = attention_varlen_reference(q, k, v, cu, cu)
         rec["max_abs_err_o"] = float((o.float() - ro).abs().max())

@@ -201,8 +201,34 @@ def linear_bf16(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
 # ---------------------------------------------------------------------------------------------------------------------
 # ops still on library kernels
 # ---------------------------------------------------------------------------------------------------------------------
+USE_TCGEN05_ATTENTION = True  # forward passes without gradients on a GPU, head dimension 256
+
+
 def causal_attention(q, k, v, cu_seqlens, scale=None):
+    """Packed causal attention; fp32 [T, Hq, D]. Without gradients on a GPU (the first pass of a checkpointed layer, the
+    old-policy log-prob pass, rollout prefill) the tcgen05 kernel of ``ops/attention.py`` runs on bf16 operands; with
+    gradients the library path keeps its own backward."""
+    if (USE_TCGEN05_ATTENTION and q.is_cuda and q.shape[-1] == 256 and not torch.is_grad_enabled()):
+        from . import attention as A
+
+        cu = cu_seqlens if torch.is_tensor(cu_seqlens) else torch.tensor(list(cu_seqlens), dtype=torch.int32)
+        cu = cu.to(device=q.device, dtype=torch.int32)
+        o = A.attention_varlen_fwd(q.to(torch.bfloat16).contiguous(), k.to(torch.bfloat16).contiguous(),
+                                   v.to(torch.bfloat16).contiguous(), cu, cu, causal=True, scale=scale, return_lse=False)
+        return o.float()
     return ref.causal_attention(q, k, v, cu_seqlens, scale)
+
+
+def prefill_attention(q, k_all, v_all, scale=None):
+    """One sequence's chunk of queries (its last positions) over all its keys so far: q [Tq, Hq, 256], k_all / v_all
+    [Tk, Hkv, 256] -> fp32 [Tq, Hq, 256], through the tcgen05 kernel."""
+    from . import attention as A
+
+    cu_q = torch.tensor([0, q.shape[0]], dtype=torch.int32, device=q.device)
+    cu_k = torch.tensor([0, k_all.shape[0]], dtype=torch.int32, device=q.device)
+    o = A.attention_varlen_fwd(q.to(torch.bfloat16).contiguous(), k_all.to(torch.bfloat16).contiguous(),
+                               v_all.to(torch.bfloat16).contiguous(), cu_q, cu_k, causal=True, scale=scale, return_lse=False)
+    return o.float()
 
 
 def causal_conv_silu(x, weight, bounds, init_state=None):

@@ -134,6 +134,11 @@ class ModelRunner:
                 short.append(i)
                 continue
             kk, vv = self._read_kv(kc, vc, row, row.start + (e - s))
+            if self.use_kernels and self._attn_kernel_ok and cfg.head_dim == 256:  # prefill chunk: tcgen05 kernel
+                from ..ops import kernels as ops_k
+
+                outs[i] = ops_k.prefill_attention(q[s:e], kk, vv, cfg.head_dim ** -0.5)
+                continue
             outs[i] = ref.attention_with_cache(q[s:e], kk, vv, row.start, cfg.head_dim ** -0.5)
         if short:
             from ..ops import rollout_ops

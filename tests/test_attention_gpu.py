@@ -53,3 +53,48 @@ def test_non_causal():
 
 def test_operands_sliced_from_a_fused_projection():
     _case([257, 640], [257, 640], hq=6, hkv=1, fused=True)
+
+
+def test_model_attention_without_gradients_runs_the_kernel():
+    from pear_b200.ops import kernels as K
+    from pear_b200.ops import lib as kl
+    from pear_b200.ops import reference as ref
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(3)
+    q = torch.randn(400, 8, 256, device=dev, generator=g)
+    k = torch.randn(400, 2, 256, device=dev, generator=g)
+    v = torch.randn(400, 2, 256, device=dev, generator=g)
+    bounds = [0, 150, 400]
+    before = kl.LAUNCH_COUNT
+    with torch.no_grad():
+        o = K.causal_attention(q, k, v, bounds)
+    assert kl.LAUNCH_COUNT == before + 1
+    want = ref.causal_attention(q, k, v, bounds)
+    assert o.dtype == torch.float32 and ((o - want).norm() / want.norm()).item() < 1e-2
+    # with gradients the library path (and its backward) is used
+    q.requires_grad_(True)
+    before = kl.LAUNCH_COUNT
+    K.causal_attention(q, k, v, bounds).sum().backward()
+    assert kl.LAUNCH_COUNT == before and q.grad is not None
+
+
+def test_rollout_prefill_at_head_dim_256_goes_through_the_kernel():
+    from pear_b200.models.config import HybridConfig
+    from pear_b200.models.hybrid import HybridForCausalLM
+    from pear_b200.ops import lib as kl
+    from pear_b200.rollout.engine import EngineConfig, RolloutEngine, SamplingParams
+
+    cfg = HybridConfig(vocab_size=4096, hidden_size=512, num_layers=4, num_attention_heads=4, num_kv_heads=1, head_dim=256, rotary_dim=64,
+                       gdn_qk_heads=2, gdn_v_heads=4, gdn_head_dim=128, intermediate_size=1024, num_mtp_layers=0)
+    prompts = [list(range(3, 300)), list(range(100, 117))]
+    counts = {}
+    for use in (True, False):
+        model = HybridForCausalLM(cfg, with_mtp=False).init_weights(4)
+        eng = RolloutEngine(model, EngineConfig(num_blocks=128, max_num_seqs=4), device="cuda")
+        eng.runner.use_kernels = use
+        before = kl.LAUNCH_COUNT
+        reqs = eng.generate(prompts, SamplingParams(max_tokens=4, temperature=0.0))
+        counts[use] = kl.LAUNCH_COUNT - before
+        assert all(len(r.output) == 4 and all(0 <= t < cfg.vocab_size for t in r.output) for r in reqs)
+    assert counts[True] > counts[False]
