@@ -18,9 +18,10 @@
 namespace pear {
 
 constexpr int kHd = 256, kQT = 128, kKT = 128;
-constexpr int kAttnThreads = 224;
+constexpr int kAttnThreads = 352;
 constexpr uint32_t kPanel = 128 * 128;  // bytes of one [128 rows x 64 bf16] swizzled panel
-constexpr uint32_t kQOff = 0, kKOff = 4 * kPanel, kVOff = 8 * kPanel, kPOff = 12 * kPanel, kBarOff = 14 * kPanel;
+constexpr uint32_t kQOff = 0, kKOff = 4 * kPanel, kVOff = 8 * kPanel, kPOff = 12 * kPanel, kBarOff = 14 * kPanel, kXchOff = kBarOff + 256;
+constexpr uint32_t kAlignSlack = 768;  // what is left of 227 KB for rounding the dynamic shared memory base up to 1024 bytes
 constexpr uint32_t kTmemCols = 512, kTmemS = 0, kTmemO = 128;
 
 struct AttnBars {
@@ -38,6 +39,11 @@ __device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_
       "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
       "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 __device__ __forceinline__ void tcgen05_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
@@ -70,6 +76,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
                 int total_q, float scale, int causal, int* status) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  if ((uint32_t)(smem - smem_raw) > kAlignSlack) {  // never seen: the base of dynamic shared memory is 1024-byte aligned
+    if (threadIdx.x == 0) set_status(status, PEAR_ERR_SMEM_ALIGN);
+    return;
+  }
   AttnBars* bars = (AttnBars*)(smem + kBarOff);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -92,11 +102,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     mbar_init(&bars->q_full, 1);
     mbar_init(&bars->k_full, 1); mbar_init(&bars->k_empty, 1);
     mbar_init(&bars->v_full, 1); mbar_init(&bars->v_empty, 1);
-    mbar_init(&bars->s_full, 1); mbar_init(&bars->s_empty, 4);
-    mbar_init(&bars->p_full, 4); mbar_init(&bars->o_done, 1);
+    mbar_init(&bars->s_full, 1); mbar_init(&bars->s_empty, 8);
+    mbar_init(&bars->p_full, 8); mbar_init(&bars->o_done, 1);
     mbar_fence_init();
   }
-  if (warp == 1) {
+  if (warp == 9) {
     tmem_alloc(&bars->tmem_base, kTmemCols);
     tmem_relinquish();
   }
@@ -105,7 +115,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   tcgen05_fence_after();
   const uint32_t tmem = bars->tmem_base;
 
-  if (warp == 0) {
+  if (warp == 8) {
     // ---------------------------------------------------------------------------------------- Q and K producer
     if (lane == 0 && ntiles > 0) {
       prefetch_tensormap(&map_q);
@@ -119,7 +129,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           tma_load_2d(smem + kKOff + p * kPanel, &map_k, hk * kHd + p * 64, k_row0 + j * kKT, &bars->k_full);
       }
     }
-  } else if (warp == 6) {
+  } else if (warp == 10) {
     // ---------------------------------------------------------------------------------------- V producer
     if (lane == 0) {
       prefetch_tensormap(&map_v);
@@ -130,7 +140,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           tma_load_2d(smem + kVOff + p * kPanel, &map_v, hk * kHd + p * 64, k_row0 + j * kKT, &bars->v_full);
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 9) {
     // ---------------------------------------------------------------------------------------- MMA issuer
     if (lane == 0 && ntiles > 0) {
       constexpr uint32_t idesc_s = umma_idesc_f16(kQT, kKT, 1);
@@ -175,93 +185,125 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     }
   } else {
     // ---------------------------------------------------------------------------------------- softmax + epilogue
-    const int quarter = warp & 3;            // TMEM lane quarter this warp may touch
+    // Two warps per TMEM lane quarter: both own the same 32 query rows, `half` 0 takes keys 0..63 of the tile and O
+    // columns 0..127, `half` 1 the rest. They exchange the tile's row maximum through shared memory (one 64-thread
+    // named barrier per tile), keep separate partial sums, and take identical rescale decisions.
+    const int quarter = warp & 3, half = warp >> 2;
     const int row = quarter * 32 + lane;     // query row of the tile = TMEM lane
     const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
+    const uint32_t s_cols = lane_base + kTmemS + half * 64, o_cols = lane_base + kTmemO + half * 128;
     const float sl2 = scale * 1.4426950408889634f;
     const int qi = q0 + row;                 // position inside the sequence
     const int last_key = causal ? min(lk - 1, qi + off) : lk - 1;
-    float m_run = -INFINITY, l_run = 0.f;
-    uint8_t* p_row = smem + kPOff + row * 128;
+    float m_ref = -INFINITY, l_run = 0.f;    // m_ref: the (possibly stale) maximum the exponents refer to
+    uint8_t* p_row = smem + kPOff + half * kPanel + row * 128;
+    float* xch = (float*)(smem + kXchOff);   // [2 tiles][2 halves][128 rows]
     bool ok = true;
     for (int j = 0; j < ntiles && ok; ++j) {
       ok = warp_wait(&bars->s_full, j & 1, lane, status);
       if (!ok) break;
       tcgen05_fence_after();
-      const int k0 = j * kKT;
+      const int k0 = j * kKT + half * 64;
+      // rows of this tile whose last visible key lies before the tile's end need the mask (the diagonal and the tail)
+      const bool masked = j * kKT + kKT - 1 > (causal ? min(lk - 1, q0 + off) : lk - 1);
       uint32_t r[32];
-      float m_tile = -INFINITY;
+      float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        tmem_ld_32x32b_x32(lane_base + kTmemS + c * 32, r);
+      for (int c = 0; c < 2; ++c) {
+        tmem_ld_32x32b_x32(s_cols + c * 32, r);
         tcgen05_wait_ld();
+        if (masked) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (k0 + c * 32 + i <= last_key) m_tile = fmaxf(m_tile, __uint_as_float(r[i]));
+          for (int i = 0; i < 32; ++i)
+            if (k0 + c * 32 + i <= last_key) m0 = fmaxf(m0, __uint_as_float(r[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            m0 = fmaxf(m0, __uint_as_float(r[i]));     m1 = fmaxf(m1, __uint_as_float(r[i + 1]));
+            m2 = fmaxf(m2, __uint_as_float(r[i + 2])); m3 = fmaxf(m3, __uint_as_float(r[i + 3]));
+          }
+        }
       }
-      const float m_new = fmaxf(m_run, m_tile);
-      const float m_ref = m_new == -INFINITY ? 0.f : m_new * sl2;
-      uint32_t pk[64];
-      float sum = 0.f;
+      float m_tile = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+      float* x = xch + (j & 1) * 256;
+      x[half * 128 + row] = m_tile;
+      asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
+      m_tile = fmaxf(m_tile, x[(half ^ 1) * 128 + row]);
+      const float m_new = fmaxf(m_ref, m_tile);
+      // lazy rescale: the reference moves only when some row's maximum grew by more than 2^8 (exponents stay small)
+      const bool grow = (m_new - m_ref) * sl2 > 8.f;
+      const bool any = __any_sync(0xffffffffu, grow);
+      const float m_use = any ? m_new : m_ref;
+      const float e_ref = m_use == -INFINITY ? 0.f : m_use * sl2;
+      uint32_t pk[32];
+      float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        tmem_ld_32x32b_x32(lane_base + kTmemS + c * 32, r);
+      for (int c = 0; c < 2; ++c) {
+        tmem_ld_32x32b_x32(s_cols + c * 32, r);
         tcgen05_wait_ld();
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          const float p0 = k0 + c * 32 + i <= last_key ? exp2f(__uint_as_float(r[i]) * sl2 - m_ref) : 0.f;
-          const float p1 = k0 + c * 32 + i + 1 <= last_key ? exp2f(__uint_as_float(r[i + 1]) * sl2 - m_ref) : 0.f;
+          float p0 = ex2_approx(fmaf(__uint_as_float(r[i]), sl2, -e_ref));
+          float p1 = ex2_approx(fmaf(__uint_as_float(r[i + 1]), sl2, -e_ref));
+          if (masked) {
+            if (k0 + c * 32 + i > last_key) p0 = 0.f;
+            if (k0 + c * 32 + i + 1 > last_key) p1 = 0.f;
+          }
+          sum0 += p0;
+          sum1 += p1;
           const __nv_bfloat162 pp = __floats2bfloat162_rn(p0, p1);
-          // the sum uses the rounded values the MMA will multiply with, so that the rows of P / l sum to one
-          sum += __bfloat162float(pp.x) + __bfloat162float(pp.y);
           pk[c * 16 + (i >> 1)] = *(const uint32_t*)&pp;
         }
       }
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->s_empty);
-      const float alpha = m_run == -INFINITY ? 0.f : exp2f(m_run * sl2 - m_ref);
-      l_run = l_run * alpha + sum;
+      const float alpha = !any ? 1.f : (m_ref == -INFINITY ? 0.f : ex2_approx(m_ref * sl2 - e_ref));
+      l_run = l_run * alpha + (sum0 + sum1);
       if (j > 0) {
         ok = warp_wait(&bars->o_done, (j - 1) & 1, lane, status);
         if (!ok) break;
         tcgen05_fence_after();
-        if (__any_sync(0xffffffffu, m_new > m_run)) {
+        if (any) {
 #pragma unroll 1
-          for (int c = 0; c < kHd / 32; ++c) {
-            tmem_ld_32x32b_x32(lane_base + kTmemO + c * 32, r);
+          for (int c = 0; c < 4; ++c) {
+            tmem_ld_32x32b_x32(o_cols + c * 32, r);
             tcgen05_wait_ld();
 #pragma unroll
             for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st_32x32b_x32(lane_base + kTmemO + c * 32, r);
+            tmem_st_32x32b_x32(o_cols + c * 32, r);
           }
           tcgen05_wait_st();
         }
       }
-      m_run = m_new;
-      // P row: 128 keys = 2 panels x 8 chunks of 16 bytes, chunk index xor (row % 8) inside each 128-byte line
+      m_ref = m_use;
+      // P row: this half's 64 keys = one panel, 8 chunks of 16 bytes, chunk index xor (row % 8) inside the 128-byte line
 #pragma unroll
-      for (int ch = 0; ch < 16; ++ch) {
+      for (int ch = 0; ch < 8; ++ch) {
         const uint4 v = make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
-        *(uint4*)(p_row + (ch >> 3) * kPanel + (((ch & 7) ^ (row & 7)) << 4)) = v;
+        *(uint4*)(p_row + ((ch ^ (row & 7)) << 4)) = v;
       }
       fence_proxy_async();
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->p_full);
     }
-    // epilogue: O / l as bf16, log-sum-exp in natural units
+    // epilogue: O / l as bf16, log-sum-exp in natural units; the two halves add their partial sums first
     const bool valid = qi < lq;
     if (ntiles > 0 && ok) ok = warp_wait(&bars->o_done, (ntiles - 1) & 1, lane, status);
+    float* xl = xch + (ntiles & 1) * 256;  // the slot the last tile did not use
+    xl[half * 128 + row] = l_run;
+    asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
+    l_run += xl[(half ^ 1) * 128 + row];
     if (ok) {
       tcgen05_fence_after();
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      __nv_bfloat16* dst = out + (size_t)(q_row0 + row) * ldo + h * kHd;
+      __nv_bfloat16* dst = out + (size_t)(q_row0 + row) * ldo + h * kHd + half * 128;
 #pragma unroll 1
-      for (int c = 0; c < kHd / 32; ++c) {
+      for (int c = 0; c < 4; ++c) {
         uint32_t r[32];
         if (ntiles > 0) {
-          tmem_ld_32x32b_x32(lane_base + kTmemO + c * 32, r);
+          tmem_ld_32x32b_x32(o_cols + c * 32, r);
           tcgen05_wait_ld();
         } else {
 #pragma unroll
@@ -280,12 +322,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           }
         }
       }
-      if (valid && lse) lse[(size_t)h * total_q + q_row0 + row] = l_run > 0.f ? m_run * scale + logf(l_run) : -INFINITY;
+      if (valid && lse && half == 0) lse[(size_t)h * total_q + q_row0 + row] = l_run > 0.f ? m_ref * scale + logf(l_run) : -INFINITY;
     }
   }
   tcgen05_fence_before();
   __syncthreads();
-  if (warp == 1) {
+  if (warp == 9) {
     tcgen05_fence_after();
     tmem_dealloc(tmem, kTmemCols);
   }
@@ -342,7 +384,7 @@ PEAR_API int pear_attn_varlen_fwd_hd256(const void* q, const void* k, const void
   if (r) return r;
   r = attn_make_map(&mv, v, total_k, heads_kv * kHd, ldv);
   if (r) return r;
-  constexpr int smem = (int)kBarOff + 256 + 1024;
+  constexpr int smem = (int)kXchOff + 2048 + (int)kAlignSlack;  // = 227 KB, the most one CTA can have
   static bool configured = false;
   if (!configured) {
     PEAR_CUDA_CHECK(cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));

@@ -23,6 +23,7 @@ enum PearStatus : int {
   PEAR_ERR_FLAG_TIMEOUT = 3,     // a peer/flag word never took the awaited value
   PEAR_ERR_BAD_INSTR = 4,        // the instruction interpreter met an unknown opcode
   PEAR_ERR_TMEM = 5,             // tensor-memory allocation did not return
+  PEAR_ERR_SMEM_ALIGN = 6,       // the dynamic shared memory base was not aligned as the kernel's layout needs
 };
 
 #define PEAR_CUDA_CHECK(expr)                                                                  \
