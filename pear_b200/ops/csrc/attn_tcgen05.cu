@@ -2,13 +2,14 @@
 // (training forward without gradients, rollout prefill; upstream calls FlashAttention-4 / TensorRT-LLM context FMHA
 // here: pear/models/qwen3_5/trainer/blackwell/ulysses_attention.py:144, rollout/blackwell/attention.py).
 //
-// One CTA per (sequence, 128 query rows, query head). S = Q K^T (128 x 128 per KV tile, 16 tcgen05.mma of K = 16) and
-// O += P V (128 x 256, 8 MMAs with V read MN-major straight from its row-major tile) accumulate in tensor memory
-// (S: columns 0..127, O: columns 128..383). Warps: 0 = TMA producer of Q and K, 1 = MMA issuer, 2..5 = softmax (one
-// query row per thread, its TMEM lane), 6 = TMA producer of V. The softmax warps read S with tcgen05.ld, keep the
-// running maximum and sum, rescale O in tensor memory when a row maximum grows, and write P as bf16 into shared memory
-// in the 128-byte-swizzled K-major layout the MMA reads. S of tile j+1 is issued before P V of tile j, so the
-// exponentials of one tile overlap the MMAs of its neighbours. All waits are bounded and report through `status`.
+// One CTA per (sequence, 128 query rows, query head), 11 warps. S = Q K^T (128 x 128 per KV tile, 16 tcgen05.mma of
+// K = 16) and O += P V (128 x 256, 8 MMAs with V read MN-major straight from its row-major tile) accumulate in tensor
+// memory (S: two buffers in columns 0..255, O: columns 256..511). Warps 0..7 = softmax, two per TMEM lane quarter
+// (same 32 query rows, each half of the tile's keys and half of O's columns); 8 = TMA producer of Q and K; 9 = MMA
+// issuer; 10 = TMA producer of V. The softmax warps read S with tcgen05.ld, keep the running maximum and sum, rescale O
+// in tensor memory only when a row maximum grew by more than 2^8, and write P as bf16 into shared memory in the
+// 128-byte-swizzled K-major layout the MMA reads. The tensor pipe runs S0, S1, PV0, S2, PV1, ...: the scores of tile
+// j+1 are ready before the softmax warps finish tile j. All waits are bounded and report through `status`.
 #include "common.cuh"
 
 #include <cudaTypedefs.h>
@@ -22,10 +23,10 @@ constexpr int kAttnThreads = 352;
 constexpr uint32_t kPanel = 128 * 128;  // bytes of one [128 rows x 64 bf16] swizzled panel
 constexpr uint32_t kQOff = 0, kKOff = 4 * kPanel, kVOff = 8 * kPanel, kPOff = 12 * kPanel, kBarOff = 14 * kPanel, kXchOff = kBarOff + 256;
 constexpr uint32_t kAlignSlack = 768;  // what is left of 227 KB for rounding the dynamic shared memory base up to 1024 bytes
-constexpr uint32_t kTmemCols = 512, kTmemS = 0, kTmemO = 128;
+constexpr uint32_t kTmemCols = 512, kTmemS = 0, kTmemO = 256;  // S: two buffers of 128 columns, O: 256 columns
 
 struct AttnBars {
-  uint64_t q_full, k_full, k_empty, v_full, v_empty, s_full, s_empty, p_full, o_done;
+  uint64_t q_full, k_full, k_empty, v_full, v_empty, s_full[2], p_full, o_done;
   uint32_t tmem_base;
 };
 
@@ -102,7 +103,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     mbar_init(&bars->q_full, 1);
     mbar_init(&bars->k_full, 1); mbar_init(&bars->k_empty, 1);
     mbar_init(&bars->v_full, 1); mbar_init(&bars->v_empty, 1);
-    mbar_init(&bars->s_full, 1); mbar_init(&bars->s_empty, 8);
+    mbar_init(&bars->s_full[0], 1); mbar_init(&bars->s_full[1], 1);
     mbar_init(&bars->p_full, 8); mbar_init(&bars->o_done, 1);
     mbar_fence_init();
   }
@@ -154,22 +155,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         for (int kk = 0; kk < kHd / 16; ++kk) {
           const uint64_t da = umma_desc_sw128(q_addr + (kk >> 2) * kPanel) + (uint64_t)((kk & 3) * 2);
           const uint64_t db = umma_desc_sw128(k_addr + (kk >> 2) * kPanel) + (uint64_t)((kk & 3) * 2);
-          umma_f16(tmem + kTmemS, da, db, idesc_s, kk != 0 ? 1u : 0u);
+          umma_f16(tmem + kTmemS + (j & 1) * kKT, da, db, idesc_s, kk != 0 ? 1u : 0u);
         }
         tcgen05_commit(&bars->k_empty);
-        tcgen05_commit(&bars->s_full);
+        tcgen05_commit(&bars->s_full[j & 1]);
         return true;
       };
+      // order on the tensor pipe: S0, S1, PV0, S2, PV1, S3, ... so that the softmax of tile j+1 always finds its S ready
       bool ok = mbar_wait_bounded(&bars->q_full, 0, status);
       if (ok) { tcgen05_fence_after(); ok = issue_s(0); }
+      if (ok && ntiles > 1) ok = issue_s(1);
       for (int j = 0; j < ntiles && ok; ++j) {
-        if (j + 1 < ntiles) {
-          ok = mbar_wait_bounded(&bars->s_empty, j & 1, status);
-          if (!ok) break;
-          tcgen05_fence_after();
-          ok = issue_s(j + 1);
-          if (!ok) break;
-        }
         ok = mbar_wait_bounded(&bars->p_full, j & 1, status) && mbar_wait_bounded(&bars->v_full, j & 1, status);
         if (!ok) break;
         tcgen05_fence_after();
@@ -181,6 +177,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         }
         tcgen05_commit(&bars->v_empty);
         tcgen05_commit(&bars->o_done);
+        // P of tile j has arrived, so the softmax warps have finished reading S buffer j & 1
+        if (j + 2 < ntiles) ok = issue_s(j + 2);
       }
     }
   } else {
@@ -191,7 +189,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     const int quarter = warp & 3, half = warp >> 2;
     const int row = quarter * 32 + lane;     // query row of the tile = TMEM lane
     const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
-    const uint32_t s_cols = lane_base + kTmemS + half * 64, o_cols = lane_base + kTmemO + half * 128;
+    const uint32_t s_base = lane_base + kTmemS + half * 64, o_cols = lane_base + kTmemO + half * 128;
     const float sl2 = scale * 1.4426950408889634f;
     const int qi = q0 + row;                 // position inside the sequence
     const int last_key = causal ? min(lk - 1, qi + off) : lk - 1;
@@ -200,28 +198,29 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     float* xch = (float*)(smem + kXchOff);   // [2 tiles][2 halves][128 rows]
     bool ok = true;
     for (int j = 0; j < ntiles && ok; ++j) {
-      ok = warp_wait(&bars->s_full, j & 1, lane, status);
+      ok = warp_wait(&bars->s_full[j & 1], (j >> 1) & 1, lane, status);
       if (!ok) break;
       tcgen05_fence_after();
       const int k0 = j * kKT + half * 64;
       // rows of this tile whose last visible key lies before the tile's end need the mask (the diagonal and the tail)
       const bool masked = j * kKT + kKT - 1 > (causal ? min(lk - 1, q0 + off) : lk - 1);
-      uint32_t r[32];
+      const uint32_t s_cols = s_base + (j & 1) * kKT;
+      uint32_t ra[32], rb[32];  // this thread's 64 scores stay in registers for both passes
+      tmem_ld_32x32b_x32(s_cols, ra);
+      tmem_ld_32x32b_x32(s_cols + 32, rb);
+      tcgen05_wait_ld();
       float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        tmem_ld_32x32b_x32(s_cols + c * 32, r);
-        tcgen05_wait_ld();
-        if (masked) {
+      if (masked) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (k0 + c * 32 + i <= last_key) m0 = fmaxf(m0, __uint_as_float(r[i]));
-        } else {
+        for (int i = 0; i < 32; ++i) {
+          if (k0 + i <= last_key) m0 = fmaxf(m0, __uint_as_float(ra[i]));
+          if (k0 + 32 + i <= last_key) m1 = fmaxf(m1, __uint_as_float(rb[i]));
+        }
+      } else {
 #pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            m0 = fmaxf(m0, __uint_as_float(r[i]));     m1 = fmaxf(m1, __uint_as_float(r[i + 1]));
-            m2 = fmaxf(m2, __uint_as_float(r[i + 2])); m3 = fmaxf(m3, __uint_as_float(r[i + 3]));
-          }
+        for (int i = 0; i < 32; i += 2) {
+          m0 = fmaxf(m0, __uint_as_float(ra[i])); m1 = fmaxf(m1, __uint_as_float(ra[i + 1]));
+          m2 = fmaxf(m2, __uint_as_float(rb[i])); m3 = fmaxf(m3, __uint_as_float(rb[i + 1]));
         }
       }
       float m_tile = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
@@ -239,8 +238,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
-        tmem_ld_32x32b_x32(s_cols + c * 32, r);
-        tcgen05_wait_ld();
+        const uint32_t(&r)[32] = c == 0 ? ra : rb;
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
           float p0 = ex2_approx(fmaf(__uint_as_float(r[i]), sl2, -e_ref));
@@ -255,9 +253,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           pk[c * 16 + (i >> 1)] = *(const uint32_t*)&pp;
         }
       }
-      tcgen05_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->s_empty);
       const float alpha = !any ? 1.f : (m_ref == -INFINITY ? 0.f : ex2_approx(m_ref * sl2 - e_ref));
       l_run = l_run * alpha + (sum0 + sum1);
       if (j > 0) {
@@ -267,11 +262,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         if (any) {
 #pragma unroll 1
           for (int c = 0; c < 4; ++c) {
-            tmem_ld_32x32b_x32(o_cols + c * 32, r);
+            tmem_ld_32x32b_x32(o_cols + c * 32, ra);
             tcgen05_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st_32x32b_x32(o_cols + c * 32, r);
+            for (int i = 0; i < 32; ++i) ra[i] = __float_as_uint(__uint_as_float(ra[i]) * alpha);
+            tmem_st_32x32b_x32(o_cols + c * 32, ra);
           }
           tcgen05_wait_st();
         }
