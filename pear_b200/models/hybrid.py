@@ -37,7 +37,7 @@ class RMSNorm(nn.Module):
         return ops.rms_norm(x, self.weight, self.eps, self.one_plus)
 
 
-_TP: dict = {"group": None}
+_TP: dict = {"group": None, "fused": None, "defer": False}
 
 
 def set_tensor_parallel_group(group) -> None:
@@ -45,16 +45,54 @@ def set_tensor_parallel_group(group) -> None:
     (``pear_b200/parallel/tensor_parallel.py`` shards the weights); the outputs of the row-parallel projections
     (o_proj, out_proj, down_proj) are partial sums that ``row_linear`` all-reduces over this group."""
     _TP["group"] = group
+    if group is None:
+        _TP["fused"] = None
 
 
-def row_linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
-    y = linear_fp32(x, weight)
+def set_tensor_parallel_fused(symm_world, max_rows: int, hidden: int) -> None:
+    """Route the reductions that are followed by a residual add and an RMSNorm (every one inside the rollout step)
+    through the NVSwitch kernel ``SymmWorld.all_reduce_add_rmsnorm`` instead of an NCCL all-reduce plus a norm kernel
+    (upstream ``rollout/blackwell/csrc/ar_norm.cu``). Steps with more than ``max_rows`` rows keep the NCCL path."""
+    _TP["fused"] = (symm_world, symm_world.make_ar_workspace(max_rows, hidden), max_rows)
+
+
+def tensor_parallel_active() -> bool:
+    return _TP["group"] is not None
+
+
+class defer_row_reduce:
+    """Inside this context ``row_linear`` returns the rank's partial sum; the caller reduces it with
+    ``reduce_add_rms_norm`` / ``reduce_partial``."""
+
+    def __enter__(self):
+        self.prev, _TP["defer"] = _TP["defer"], True
+
+    def __exit__(self, *exc):
+        _TP["defer"] = self.prev
+
+
+def reduce_partial(y: torch.Tensor) -> torch.Tensor:
     g = _TP["group"]
     if g is not None:
         import torch.distributed as dist
 
         dist.all_reduce(y, group=g)
     return y
+
+
+def reduce_add_rms_norm(partial: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, eps: float):
+    """``residual + sum over ranks(partial)`` and its (1 + w) RMSNorm: returns (normed, new residual), both fp32."""
+    fused = _TP["fused"]
+    if fused is not None and partial.is_cuda and partial.shape[0] <= fused[2] and residual.dtype == torch.float32 and residual.is_contiguous():
+        symm, ws, _ = fused
+        y = symm.all_reduce_add_rmsnorm(ws, partial.to(torch.bfloat16), residual, weight.detach().float(), eps)  # residual in place
+        return y.float(), residual
+    return ops.add_rms_norm(reduce_partial(partial), residual, weight, eps)
+
+
+def row_linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    y = linear_fp32(x, weight)
+    return y if _TP["defer"] else reduce_partial(y)
 
 
 class SwiGLUMLP(nn.Module):

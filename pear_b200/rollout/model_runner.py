@@ -19,6 +19,7 @@ from typing import Optional
 import torch
 
 from ..models.config import HybridConfig
+from ..models import hybrid
 from ..models.hybrid import HybridForCausalLM, linear_fp32, row_linear
 from ..ops import api as ops
 from ..ops import reference as ref
@@ -234,14 +235,34 @@ class ModelRunner:
             if r.embeds is not None:
                 s, e = bounds[i], bounds[i + 1]
                 x[s:e] = torch.where(r.embeds_mask.to(self.device)[:, None], r.embeds.to(self.device).float(), x[s:e])
-        for li, layer in enumerate(model.model.layers):
-            h = layer.input_layernorm(x)
-            if layer.layer_type == "full_attention":
-                mixed = self._attention(layer.self_attn, h, rows, bounds, cos, sin, self.k_cache[li], self.v_cache[li])
-            else:
-                mixed = self._gdn(li, layer.linear_attn, h, rows, bounds, speculative)
-            y, x = ops.add_rms_norm(mixed, x, layer.post_attention_layernorm.weight, layer.post_attention_layernorm.eps)
-            x = x + layer.mlp(y)
+        layers = list(model.model.layers)
+        if not hybrid.tensor_parallel_active():
+            for li, layer in enumerate(layers):
+                h = layer.input_layernorm(x)
+                if layer.layer_type == "full_attention":
+                    mixed = self._attention(layer.self_attn, h, rows, bounds, cos, sin, self.k_cache[li], self.v_cache[li])
+                else:
+                    mixed = self._gdn(li, layer.linear_attn, h, rows, bounds, speculative)
+                y, x = ops.add_rms_norm(mixed, x, layer.post_attention_layernorm.weight, layer.post_attention_layernorm.eps)
+                x = x + layer.mlp(y)
+        else:
+            # tensor parallel: every row-parallel projection hands back its partial sum and the reduction runs together
+            # with the residual add and the norm that follow it (one NVSwitch kernel when the fused transport is set)
+            with hybrid.defer_row_reduce():
+                h = layers[0].input_layernorm(x)
+                for li, layer in enumerate(layers):
+                    if layer.layer_type == "full_attention":
+                        mixed = self._attention(layer.self_attn, h, rows, bounds, cos, sin, self.k_cache[li], self.v_cache[li])
+                    else:
+                        mixed = self._gdn(li, layer.linear_attn, h, rows, bounds, speculative)
+                    ln = layer.post_attention_layernorm
+                    y, x = hybrid.reduce_add_rms_norm(mixed, x, ln.weight, ln.eps)
+                    part = layer.mlp(y)
+                    if li + 1 < len(layers):
+                        nxt = layers[li + 1].input_layernorm
+                        h, x = hybrid.reduce_add_rms_norm(part, x, nxt.weight, nxt.eps)
+                    else:
+                        x = x + hybrid.reduce_partial(part)
         for r in rows:  # the replay (if any) has been applied by every GDN layer
             if not speculative:
                 r.seq.commit_rows = 0

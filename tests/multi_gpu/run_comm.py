@@ -153,6 +153,49 @@ def main() -> int:
         if rank == 0:
             print(f"TIMING world {world} M {M} N {N} K {K}: ag_gemm fused {t_own:.3f} ms vs nccl+cublas {t_ref:.3f} ms; "
                   f"gemm_rs fused {t_own2:.3f} ms vs cublas+nccl {t_ref2:.3f} ms", flush=True)
+    # ---- tensor-parallel rollout engine: every reduction of the step through the fused all-reduce + add + RMSNorm kernel
+    from pear_b200.models import hybrid
+    from pear_b200.models.config import HybridConfig
+    from pear_b200.ops import lib as kl
+    from pear_b200.parallel.tensor_parallel import shard_state, tp_config
+    from pear_b200.rollout.engine import EngineConfig, RolloutEngine, SamplingParams
+
+    cfg = HybridConfig(vocab_size=4096, hidden_size=512, num_layers=4, num_attention_heads=8, num_kv_heads=2, head_dim=128, rotary_dim=64,
+                       gdn_qk_heads=2, gdn_v_heads=4, gdn_head_dim=128, intermediate_size=1024, num_mtp_layers=0)
+    full = hybrid.HybridForCausalLM(cfg, with_mtp=False).init_weights(5)
+    prompts = [list(range(3, 40)), list(range(100, 117)), [5, 6, 7]]
+    tp = hybrid.HybridForCausalLM(tp_config(cfg, world), with_mtp=False)
+    tp.load_state_dict(shard_state(full.state_dict(), cfg, rank, world), strict=True)
+    outs = {}
+    fused_calls = [0]
+    plain_ar = sw.all_reduce_add_rmsnorm
+
+    def counting_ar(*a, **k):
+        fused_calls[0] += 1
+        return plain_ar(*a, **k)
+
+    sw.all_reduce_add_rmsnorm = counting_ar
+    for mode in ("nccl", "fused"):
+        hybrid.set_tensor_parallel_group(dist.group.WORLD)
+        if mode == "fused":
+            hybrid.set_tensor_parallel_fused(sw, 256, cfg.hidden_size)
+        try:
+            eng = RolloutEngine(tp, EngineConfig(num_blocks=128, max_num_seqs=4), device="cuda")
+            before = kl.LAUNCH_COUNT
+            outs[mode] = ([r.output for r in eng.generate(prompts, SamplingParams(max_tokens=8, temperature=0.0))], kl.LAUNCH_COUNT - before)
+            torch.cuda.synchronize()
+            sw.check()
+        finally:
+            hybrid.set_tensor_parallel_group(None)
+    same = sum(a == b for x, y in zip(outs["nccl"][0], outs["fused"][0]) for a, b in zip(x, y))
+    total = sum(len(x) for x in outs["nccl"][0])
+    # the fused path rounds the partial sums to bf16 before adding them, so a near-tie of a random-weight model may flip
+    # and the sequence then diverges; a wrong reduction would agree on no token at all (vocabulary 4096)
+    assert same >= total // 3, (same, total, outs["nccl"][0], outs["fused"][0])
+    assert fused_calls[0] >= (2 * cfg.num_layers - 1) * 8, fused_calls  # every step reduced through the NVSwitch kernel
+    if rank == 0:
+        print(f"PASS tp_rollout_fused ({same}/{total} tokens equal to the NCCL transport)", flush=True)
+
     dist.barrier()
     dist.destroy_process_group()
     return 0
