@@ -44,6 +44,27 @@ def gemm_nt(a: torch.Tensor, b: torch.Tensor, out_dtype=torch.float32, out: torc
     return c
 
 
+def split_operand(x: torch.Tensor, role: str) -> torch.Tensor:
+    """fp32 [R, K] -> bf16 [R, 3K] for :func:`matmul_split3`: ``x = hi + lo`` with ``hi = bf16(x)``, ``lo = bf16(x - hi)``;
+    role "a" lays out [hi | hi | lo], role "b" [hi | lo | hi], so that one K-concatenated GEMM sums hi.hi + hi.lo + lo.hi."""
+    xf = x.float()
+    hi = xf.to(torch.bfloat16)
+    lo = (xf - hi.float()).to(torch.bfloat16)
+    return torch.cat([hi, hi, lo] if role == "a" else [hi, lo, hi], dim=1)
+
+
+def matmul_split3(a: torch.Tensor, b: torch.Tensor, b_split: torch.Tensor | None = None) -> torch.Tensor:
+    """``a @ b^T`` for fp32 ``a`` [M, K], ``b`` [N, K] on the bf16 tensor cores with close to fp32 accuracy: both operands are
+    split into two bf16 terms and the three leading products are accumulated in fp32 by ONE GEMM over 3K (the lo.lo term,
+    2^-16 of the result, is dropped). The fp32 head of the trainer uses it (upstream keeps the head in fp32 through a
+    two-term fp16 operand scheme: pear/models/qwen3_5/trainer/operands.py). ``b_split`` = ``split_operand(b, "b")`` when
+    the caller reuses it over several calls."""
+    if a.shape[1] % 8:
+        return a.float() @ b.float().t()
+    bs = b_split if b_split is not None else split_operand(b, "b")
+    return gemm_nt(split_operand(a, "a"), bs, torch.float32)
+
+
 def gemm_status(device=None) -> int:
     status, _ = _dev_state(torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device))
     return int(status.item())

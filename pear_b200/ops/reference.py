@@ -263,17 +263,30 @@ class _LogProbEntropy(torch.autograd.Function):
     """Rows are processed in chunks; only lse per row is saved, logits are recomputed per chunk in backward."""
 
     @staticmethod
+    def _kernels(hidden, weight):
+        """On a GPU the three GEMMs of the head run on the tcgen05 kernel: logits with split operands (close to fp32),
+        the two gradient products with bf16 operands and fp32 accumulation."""
+        if not hidden.is_cuda or weight.shape[1] % 8:
+            return None
+        from . import gemm, lib
+
+        return gemm if lib.available() else None
+
+    @staticmethod
     def forward(ctx, hidden, weight, ids, inv_temperature, chunk):
         n = hidden.shape[0]
         lp = torch.empty(ids.shape, dtype=torch.float32, device=hidden.device)
         ent = torch.empty(n, dtype=torch.float32, device=hidden.device)
         lse = torch.empty(n, dtype=torch.float32, device=hidden.device)
-        wf = weight.float()
+        g = _LogProbEntropy._kernels(hidden, weight)
+        wf = weight.float() if g is None else None
+        ws = g.split_operand(weight, "b") if g is not None else None
         for s in range(0, n, chunk):
             e = min(s + chunk, n)
-            logits = (hidden[s:e].float() @ wf.t()) * inv_temperature
+            logits = (hidden[s:e].float() @ wf.t()) if g is None else g.matmul_split3(hidden[s:e], weight, ws)
+            logits = logits.mul_(inv_temperature)
             l = torch.logsumexp(logits, dim=-1)
-            logp = logits - l[:, None]
+            logp = logits.sub_(l[:, None])
             lp[s:e] = logp.gather(-1, ids[s:e])
             ent[s:e] = -(logp.exp() * logp).sum(-1)
             lse[s:e] = l
@@ -285,14 +298,18 @@ class _LogProbEntropy(torch.autograd.Function):
     def backward(ctx, g_lp, g_ent):
         hidden, weight, ids, lse, ent = ctx.saved_tensors
         n = hidden.shape[0]
-        wf = weight.float()
+        g = _LogProbEntropy._kernels(hidden, weight)
+        wf = weight.float() if g is None else None
         g_hidden = torch.zeros(hidden.shape, dtype=torch.float32, device=hidden.device)
         g_weight = torch.zeros(weight.shape, dtype=torch.float32, device=hidden.device)
+        if g is not None:
+            ws = g.split_operand(weight, "b")
+            wt = weight.to(torch.bfloat16).t().contiguous()  # [K, V]: the contraction of d @ W runs over V
         for s in range(0, n, ctx.chunk):
             e = min(s + ctx.chunk, n)
             hf = hidden[s:e].float()
-            logits = (hf @ wf.t()) * ctx.inv_temperature
-            logp = logits - lse[s:e, None]
+            logits = (hf @ wf.t()) if g is None else g.matmul_split3(hf, weight, ws)
+            logp = logits.mul_(ctx.inv_temperature).sub_(lse[s:e, None])
             p = logp.exp()
             glp = g_lp[s:e].float()
             d = -p * glp.sum(-1, keepdim=True)
@@ -300,8 +317,13 @@ class _LogProbEntropy(torch.autograd.Function):
             if g_ent is not None:
                 d = d - g_ent[s:e, None].float() * p * (logp + ent[s:e, None])
             d = d * ctx.inv_temperature
-            g_hidden[s:e] = d @ wf
-            g_weight += d.t() @ hf
+            if g is None or (e - s) % 8:
+                g_hidden[s:e] = d @ (wf if wf is not None else weight.float())
+                g_weight += d.t() @ hf
+            else:
+                db = d.to(torch.bfloat16)
+                g.gemm_nt(db, wt, torch.float32, out=g_hidden[s:e])
+                g_weight += g.gemm_nt(db.t().contiguous(), hf.to(torch.bfloat16).t().contiguous(), torch.float32)
         return g_hidden.to(hidden.dtype), g_weight.to(weight.dtype), None, None, None
 
 

@@ -40,6 +40,8 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--vocab", type=int, default=32768)
+    ap.add_argument("--breakdown", type=int, default=0, help="after the timed steps, run one step under the torch profiler and "
+                    "print the N kernels with the most device time (stderr)")
     a = ap.parse_args()
     cfg = HybridConfig(num_layers=a.layers, vocab_size=a.vocab)  # the 27B per-layer shape
     ecfg = EngineConfig(lr=1e-6, param_dtype="bf16", enable_gradient_checkpointing=True, topk_log_probs=0)
@@ -69,6 +71,14 @@ def main() -> None:
     if os.path.exists(peaks):
         out["frac_of_measured_bf16_sustained"] = round(out["model_tflops"] / json.load(open(peaks))["bf16_tflops_sustained"], 3)
     print(json.dumps(out))
+    if a.breakdown:
+        import sys
+        from torch.profiler import ProfilerActivity, profile
+
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            step(0)
+            torch.cuda.synchronize()
+        print(prof.key_averages().table(sort_by="cuda_time_total", row_limit=a.breakdown, max_name_column_width=70), file=sys.stderr)
 
 
 if __name__ == "__main__":

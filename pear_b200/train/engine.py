@@ -111,6 +111,9 @@ class EngineConfig:
     kernels: Optional[str] = None
     use_gpu_backend: bool = False
     hsdp_all_reduce_on_last_micro_batch: bool = True
+    # fp32 matrix products left to the library on a GPU (the chunked delta-rule scan, attention with gradients) run on
+    # the TF32 tensor cores instead of SIMT fp32; the head's logits do not (split-bf16 GEMM, close to fp32)
+    tf32_matmul: bool = True
 
     @classmethod
     def from_config(cls, cfg) -> "EngineConfig":
@@ -158,6 +161,8 @@ class TrainEngine:
         self.kernels = kernels
         if kernels is not None:
             kernels.check_config(cfg)
+        if self.device.type == "cuda" and cfg.tf32_matmul:
+            torch.backends.cuda.matmul.allow_tf32 = True
 
         # ---- build: every rank builds the same seeded model, or takes the given weights (rank 0's in a real run)
         model = HybridForCausalLM(model_cfg, with_mtp=with_mtp)

@@ -120,3 +120,36 @@ def test_cuda_graph_runner_replays_kernel_sequences():
         got = runner(8, x, r).clone()
         assert torch.allclose(got, step(x, r), atol=1e-5)
     assert runner.replays == 3 and len(runner.graphs) == 1
+
+
+def test_split_bf16_gemm_is_close_to_fp32():
+    """The head's logits GEMM: three bf16 products in one tcgen05 GEMM over 3K against an fp64 product."""
+    from pear_b200.ops import gemm
+
+    g = torch.Generator(device="cuda").manual_seed(0)
+    a = torch.randn(300, 512, device="cuda", generator=g)
+    b = torch.randn(1000, 512, device="cuda", generator=g)
+    want = (a.double() @ b.double().t())
+    got = gemm.matmul_split3(a, b)
+    plain = gemm.gemm_nt(a.to(torch.bfloat16), b.to(torch.bfloat16))
+    err = ((got.double() - want).norm() / want.norm()).item()
+    err_bf16 = ((plain.double() - want).norm() / want.norm()).item()
+    assert err < 2e-5 and err < err_bf16 / 50, (err, err_bf16)
+
+
+def test_chunked_head_on_gpu_matches_the_dense_statement():
+    from pear_b200.ops import reference as ref
+
+    g = torch.Generator(device="cuda").manual_seed(1)
+    h = (torch.randn(200, 256, device="cuda", generator=g) * 0.5).requires_grad_(True)
+    w = (torch.randn(1024, 256, device="cuda", generator=g) * 0.1).requires_grad_(True)
+    ids = torch.randint(0, 1024, (200, 1), device="cuda", generator=g)
+    lp, ent = ref.logprob_entropy(h, w, ids, temperature=0.7, chunk=64)
+    (lp.sum() + 0.1 * ent.sum()).backward()
+    gh, gw = h.grad.clone(), w.grad.clone()
+    h.grad = w.grad = None
+    lp2, ent2 = ref.logprob_entropy_dense(h.double(), w.double(), ids, temperature=0.7)
+    (lp2.sum() + 0.1 * ent2.sum()).backward()
+    assert (lp - lp2).abs().max().item() < 1e-4 and (ent - ent2).abs().max().item() < 1e-4
+    assert ((gh - h.grad).norm() / h.grad.norm()).item() < 2e-2  # bf16 operands in the gradient products
+    assert ((gw - w.grad).norm() / w.grad.norm()).item() < 2e-2
