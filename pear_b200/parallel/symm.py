@@ -212,3 +212,68 @@ class SymmWorld:
                    "bcast_quant_nvfp4")
         _lib.LAUNCH_COUNT += 2
         return packed, gs
+
+
+class FusedShardedAdamW:
+    """ZeRO-style optimizer step over NVSwitch in two kernels (``ops/csrc/optim_collective.cu``): gradient reduce-scatter +
+    scale + norm, then clip + AdamW on the owned shard + all-gather of the new bf16 parameters by peer stores.
+
+    Every rank writes its full flat gradient into ``grads.tensor`` (symmetric memory) and reads the current parameters
+    from ``params.tensor``; the fp32 master weights and moments exist only for the owned range. Upstream does the same
+    work as an NCCL reduce-scatter, ``_multi_tensor_adam`` on the shards and an NCCL all-gather
+    (pear/trainer/engine.py:155-236)."""
+
+    def __init__(self, symm: SymmWorld, numel: int, grads_dtype=torch.bfloat16, lr: float = 1e-6, betas=(0.9, 0.999), eps: float = 1e-8,
+                 weight_decay: float = 0.01, max_norm: float = 1.0):
+        self.symm = symm
+        unit = 8 * symm.world
+        self.numel = numel
+        self.padded = (numel + unit - 1) // unit * unit
+        self.shard = self.padded // symm.world
+        self.lo = symm.rank * self.shard
+        self.grads = symm.alloc((self.padded,), grads_dtype)
+        self.params = symm.alloc((self.padded,), torch.bfloat16)
+        self.norms = symm.alloc((8,), torch.float32)
+        self.grads.tensor.zero_()
+        self.params.tensor.zero_()
+        self.norms.tensor.zero_()
+        dev = symm.device
+        self.master = torch.zeros(self.shard, dtype=torch.float32, device=dev)
+        self.m = torch.zeros_like(self.master)
+        self.v = torch.zeros_like(self.master)
+        self.reduced = torch.zeros_like(self.master)
+        self.block_sums = torch.zeros(592, dtype=torch.float32, device=dev)
+        self.norm_out = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.lr, self.betas, self.eps, self.weight_decay, self.max_norm = lr, betas, eps, weight_decay, max_norm
+        self.t = 0
+        torch.cuda.synchronize(dev)
+        dist.barrier(symm.group)
+
+    def load_parameters(self, flat: torch.Tensor) -> None:
+        """``flat``: the full fp32 parameter vector (same on every rank)."""
+        self.master.zero_()
+        hi = min(self.lo + self.shard, self.numel)
+        if hi > self.lo:
+            self.master[: hi - self.lo].copy_(flat[self.lo:hi])
+        self.params.tensor[: self.numel].copy_(flat)
+        self.symm.device_barrier()
+
+    def step(self, grad_scale: float = 1.0) -> torch.Tensor:
+        """One optimizer step over the gradients currently in ``grads.tensor`` on every rank; returns the global gradient
+        norm before clipping (device scalar)."""
+        s, lib = self.symm, _lib.lib()
+        self.t += 1
+        b1, b2 = self.betas
+        s.device_barrier()  # every rank's gradient bucket is complete
+        _lib.check(lib.pear_rs_sumsq(self.grads.c_ptrs, 1 if self.grads.tensor.dtype == torch.bfloat16 else 0, s.rank, s.world,
+                                     ctypes.c_size_t(self.lo), ctypes.c_size_t(self.shard), ctypes.c_float(grad_scale), _lib.ptr(self.reduced),
+                                     _lib.ptr(self.block_sums), self.norms.c_ptrs, _lib.stream()), "rs_sumsq")
+        s.device_barrier()  # every rank's partial norm has landed here; every rank is done reading this rank's gradients
+        _lib.check(lib.pear_adamw_bcast(_lib.ptr(self.reduced), _lib.ptr(self.master), _lib.ptr(self.m), _lib.ptr(self.v), _lib.ptr(self.norms.tensor),
+                                        self.params.c_ptrs, s.world, ctypes.c_size_t(self.lo), ctypes.c_size_t(self.shard), ctypes.c_float(self.lr),
+                                        ctypes.c_float(b1), ctypes.c_float(b2), ctypes.c_float(self.eps), ctypes.c_float(self.weight_decay),
+                                        ctypes.c_float(1.0 - b1 ** self.t), ctypes.c_float(1.0 - b2 ** self.t), ctypes.c_float(self.max_norm),
+                                        _lib.ptr(self.norm_out), _lib.stream()), "adamw_bcast")
+        s.device_barrier()  # the new parameters are visible in every rank's bucket
+        _lib.LAUNCH_COUNT += 3
+        return self.norm_out

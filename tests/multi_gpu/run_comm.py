@@ -153,6 +153,58 @@ def main() -> int:
         if rank == 0:
             print(f"TIMING world {world} M {M} N {N} K {K}: ag_gemm fused {t_own:.3f} ms vs nccl+cublas {t_ref:.3f} ms; "
                   f"gemm_rs fused {t_own2:.3f} ms vs cublas+nccl {t_ref2:.3f} ms", flush=True)
+    # ---- gradient reduce-scatter + clip + sharded AdamW + parameter all-gather in two kernels
+    from pear_b200.parallel.symm import FusedShardedAdamW
+
+    n_par = 3 * 1000 * 1000 + 13
+    for gdt in (torch.bfloat16, torch.float32):
+        opt = FusedShardedAdamW(sw, n_par, grads_dtype=gdt, lr=1e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, max_norm=1.0)
+        p0 = torch.randn(n_par, device="cuda", generator=g)
+        opt.load_parameters(p0)
+        ref_p, ref_m, ref_v = p0.clone(), torch.zeros_like(p0), torch.zeros_like(p0)
+        for t in (1, 2, 3):
+            all_g = (torch.randn(world, n_par, device="cuda", generator=g) * (0.02 if t < 3 else 1e-5)).to(gdt)  # step 3: below the clip
+            opt.grads.tensor[:n_par].copy_(all_g[rank])
+            norm = opt.step(grad_scale=1.0 / world)
+            torch.cuda.synchronize()
+            sw.check()
+            gsum = all_g.float().sum(0) / world
+            ref_norm = gsum.norm()
+            gc = gsum * min(1.0, 1.0 / (float(ref_norm) + 1e-6))
+            ref_m = 0.9 * ref_m + 0.1 * gc
+            ref_v = 0.95 * ref_v + 0.05 * gc * gc
+            ref_p = ref_p * (1 - 1e-3 * 0.1) - (1e-3 / (1 - 0.9 ** t)) * ref_m / (ref_v.sqrt() / (1 - 0.95 ** t) ** 0.5 + 1e-8)
+            assert abs(float(norm) - float(ref_norm)) <= 1e-4 * float(ref_norm), (float(norm), float(ref_norm))
+            got = opt.params.tensor[:n_par].float()
+            assert torch.equal(got, ref_p.to(torch.bfloat16).float()) or (got - ref_p).abs().max() <= 1e-2 * ref_p.abs().max(), (got - ref_p).abs().max()
+            lo, hi = opt.lo, min(opt.lo + opt.shard, n_par)
+            assert torch.allclose(opt.master[: hi - lo], ref_p[lo:hi], atol=1e-5, rtol=1e-5), (opt.master[: hi - lo] - ref_p[lo:hi]).abs().max()
+    if rank == 0:
+        print("PASS reduce_scatter_adamw", flush=True)
+    if big:
+        n_big = 1 << 30  # 1 Gi parameters: 2 GiB of bf16 gradients per rank
+        opt = FusedShardedAdamW(sw, n_big, grads_dtype=torch.bfloat16)
+        opt.grads.tensor.normal_(generator=g)
+        rs_in, rs_out = opt.grads.tensor, torch.empty(n_big // world, dtype=torch.bfloat16, device="cuda")
+        pm, m1, v1 = (torch.zeros(n_big // world, device="cuda") for _ in range(3))
+        full = torch.empty(n_big, dtype=torch.bfloat16, device="cuda")
+
+        def unfused_opt():
+            dist.reduce_scatter_tensor(rs_out, rs_in)
+            gf = rs_out.float()
+            nrm = gf.pow(2).sum()
+            dist.all_reduce(nrm)
+            gf.mul_(torch.clamp(1.0 / (nrm.sqrt() + 1e-6), max=1.0))
+            torch._foreach_lerp_([m1], [gf], 0.1)
+            v1.mul_(0.999).addcmul_(gf, gf, value=0.001)
+            pm.mul_(1 - 1e-8).addcdiv_(m1, v1.sqrt().add_(1e-8), value=-1e-6)
+            dist.all_gather_into_tensor(full, pm.to(torch.bfloat16))
+
+        t_ref3, t_own3 = timed(unfused_opt, iters=5), timed(lambda: opt.step(1.0 / world), iters=5)
+        if rank == 0:
+            print(f"TIMING world {world} optimizer step over {n_big} parameters: fused {t_own3:.3f} ms vs nccl + torch {t_ref3:.3f} ms", flush=True)
+        del opt, full, pm, m1, v1, rs_out
+
     # ---- tensor-parallel rollout engine: every reduction of the step through the fused all-reduce + add + RMSNorm kernel
     from pear_b200.models import hybrid
     from pear_b200.models.config import HybridConfig
