@@ -69,6 +69,8 @@ __device__ __forceinline__ bool wait_epoch_gpu(const uint32_t* flag, uint32_t ep
 }
 // MODE 0: all-gather -> GEMM (outs.p[r] = rank r's A shard; A tiles from the local shard or the local full buffer; C local)
 // MODE 1: GEMM -> reduce-scatter (A, B local; outs.p[r] = rank r's staging buffer; c = this rank's result rows)
+// MODE 2: GEMM -> all-to-all (A [M local tokens, K], B local; column group p of width N / world goes to rank p: outs.p[p] =
+//         rank p's bf16 buffer [world * M, ldc], this rank's rows at rank * M)
 template <int BN, int MODE, bool OUT_BF16>
 __global__ void __launch_bounds__(kCThreads, 1)
 gemm_coll_kernel(const __grid_constant__ MapSet maps, const __grid_constant__ CUtensorMap map_b, void* __restrict__ c,
@@ -87,11 +89,22 @@ gemm_coll_kernel(const __grid_constant__ MapSet maps, const __grid_constant__ CU
   const int m_local = M / world, tiles_m_local = m_local / kCBM;
   // tile order: owner-major starting at the own rank (MODE 0) or at the next rank (MODE 1)
   auto tile_coords = [&](int t, int& owner, int& m0, int& n0) {
+    constexpr int kBand = 16;
+    if (MODE == 2) {
+      // destination-major starting after the own rank (at any moment the ranks store to different peers), own columns last
+      const int tiles_n_dest = tiles_n / world, per_dest = tiles_m * tiles_n_dest;
+      const int o = t / per_dest, rest = t % per_dest;
+      owner = (rank + 1 + o) % world;
+      const int band = rest / (kBand * tiles_n_dest), in_band = rest % (kBand * tiles_n_dest);
+      const int rows_here = min(kBand, tiles_m - band * kBand);
+      m0 = (band * kBand + in_band % rows_here) * kCBM;
+      n0 = (owner * tiles_n_dest + in_band / rows_here) * BN;
+      return;
+    }
     const int per_owner = tiles_m_local * tiles_n;
     const int o = t / per_owner, rest = t % per_owner;
     owner = (rank + (MODE == 1 ? 1 : 0) + o) % world;
     // inside an owner's rows: bands of 16 row tiles, the row tile varying fastest (a wave's A and B panels stay in L2)
-    constexpr int kBand = 16;
     const int band = rest / (kBand * tiles_n), in_band = rest % (kBand * tiles_n);
     const int rows_here = min(kBand, tiles_m_local - band * kBand);
     m0 = (owner * tiles_m_local + band * kBand + in_band % rows_here) * kCBM;
@@ -239,6 +252,22 @@ gemm_coll_kernel(const __grid_constant__ MapSet maps, const __grid_constant__ CU
                 if (col + j < N) dst[j] = __uint_as_float(r[j]);
             }
           }
+        } else if (MODE == 2) {
+          // the 32 x 32 block goes to the owner of its column group as bf16: transposed through shared memory so that one
+          // warp store covers two 64-byte row segments instead of 32 scattered 4-byte words
+          float* tb = epi_tile + (warp - 2) * (32 * 33);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) tb[lane * 33 + j] = __uint_as_float(r[j]);
+          __syncwarp();
+          const int group = N / world;
+          __nv_bfloat16* dst0 = (__nv_bfloat16*)outs.p[owner] + ((size_t)rank * M + m0 + q * 32) * ldc + (col - owner * group);
+          const int hr = lane >> 4, cc = (lane & 15) * 2;
+#pragma unroll 4
+          for (int rr = 0; rr < 32; rr += 2) {
+            const __nv_bfloat162 v = __floats2bfloat162_rn(tb[(rr + hr) * 33 + cc], tb[(rr + hr) * 33 + cc + 1]);
+            *(__nv_bfloat162*)(dst0 + (size_t)(rr + hr) * ldc + cc) = v;
+          }
+          __syncwarp();
         } else if (OUT_BF16) {
           __nv_bfloat16* dst = (__nv_bfloat16*)c + (size_t)row * ldc + col;
           if (col + 32 <= N) {
@@ -280,7 +309,7 @@ gemm_coll_kernel(const __grid_constant__ MapSet maps, const __grid_constant__ CU
           asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(rs_flags.p[owner] + (size_t)rank * tiles_m_local * tiles_n + tile_in_owner), "r"(epoch) : "memory");
       }
     }
-    if (MODE == 1) __threadfence_system();  // the adds are performed before the host-ordered "done" signal that follows the kernel
+    if (MODE != 0) __threadfence_system();  // the adds / peer stores are performed before the host-ordered "done" signal that follows the kernel
   }
   if (MODE == 0 && warp >= 6 && world > 1) {
     // ------------------------------------------------------------------------------------------------ copier warps
@@ -418,4 +447,27 @@ PEAR_API int pear_gemm_rs_bf16(const void* a, const void* b, void* const* stage,
   for (int r = 0; r < world; ++r) { outs.p[r] = (float*)stage[r]; fl.p[r] = (uint32_t*)flags[r]; }
   return launch_coll<256, 1, false>(maps, mb, out, outs, M, N, K, ldc, rank, world, nullptr, 0, epoch, budget, status, num_sms, (cudaStream_t)stream,
                                     nullptr, nullptr, &fl);
+}
+
+// Projection GEMM -> all-to-all (Ulysses: tokens sharded before, heads sharded after). A [M, K] (this rank's tokens), B
+// [N, K] local bf16; the columns are `world` groups of N / world (a multiple of 128) and group p is stored as bf16 into
+// outs[p] (rank p's [world * M, ldo] buffer in symmetric memory) at rows [rank * M, (rank + 1) * M). M a multiple of 128.
+// The stores are visible to the peers after a pear_symm_signal / pear_symm_wait round that follows the kernel.
+PEAR_API int pear_gemm_a2a_bf16(const void* a, const void* b, void* const* outs_, int M, int N, int K, int lda, int ldb, int ldo, int rank,
+                                int world, int* status, int num_sms, void* stream) {
+  if (world < 1 || world > kCMaxRanks || M % kCBM || N % world || (N / world) % 128 || (lda % 8) || (ldb % 8) || (ldo % 2))
+    return (int)cudaErrorInvalidValue;
+  MapSet maps;
+  int e = coll_map_bf16(&maps.a[0], a, M, K, lda, kCBM);
+  if (e) return e;
+  for (int r = 1; r < kCMaxRanks; ++r) maps.a[r] = maps.a[0];
+  const bool wide = (N / world) % 256 == 0;
+  CUtensorMap mb;
+  e = coll_map_bf16(&mb, b, N, K, ldb, wide ? 256 : 128);
+  if (e) return e;
+  OutPtrs outs{};
+  for (int r = 0; r < world; ++r) outs.p[r] = (float*)outs_[r];
+  cudaStream_t s = (cudaStream_t)stream;
+  return wide ? launch_coll<256, 2, true>(maps, mb, nullptr, outs, M, N, K, ldo, rank, world, nullptr, 0, 0, 1u << 22, status, num_sms, s)
+              : launch_coll<128, 2, true>(maps, mb, nullptr, outs, M, N, K, ldo, rank, world, nullptr, 0, 0, 1u << 22, status, num_sms, s);
 }

@@ -160,6 +160,23 @@ class SymmWorld:
         _lib.LAUNCH_COUNT += 1
         return out
 
+    # -- projection GEMM -> all-to-all (Ulysses: token-sharded in, head-sharded out) -----------------------------------
+    def make_a2a_buffer(self, rows_local: int, cols_per_rank: int) -> SymmBuffer:
+        return self.alloc((self.world * rows_local, cols_per_rank), torch.bfloat16)
+
+    def gemm_a2a(self, a: torch.Tensor, b: torch.Tensor, out: SymmBuffer) -> torch.Tensor:
+        """``a`` [M, K]: this rank's tokens, ``b`` [N, K]: the full projection weight. Column group p of ``a @ b^T`` (width
+        N / world: the heads of rank p) is stored by the GEMM's epilogue into rank p's ``out`` at rows [rank * M, ...):
+        after the call ``out.tensor`` [world * M, N / world] holds every rank's tokens for this rank's heads."""
+        m, k = a.shape
+        n = b.shape[0]
+        self.device_barrier()  # every rank has finished reading what the previous call stored into its buffer
+        _lib.check(_lib.lib().pear_gemm_a2a_bf16(_lib.ptr(a), _lib.ptr(b), out.c_ptrs, m, n, k, a.stride(0), b.stride(0), out.tensor.stride(0),
+                                                  self.rank, self.world, _lib.ptr(self.status), self.num_sms, _lib.stream()), "gemm_a2a")
+        _lib.LAUNCH_COUNT += 1
+        self.device_barrier()  # every rank's stores have landed here
+        return out.tensor
+
     # -- vocab-parallel logits all-gather -----------------------------------------------------------------------------
     def all_gather_logits(self, shard: torch.Tensor, full: SymmBuffer) -> torch.Tensor:
         """Write this rank's fp32 logits shard [T, V / world] into every rank's ``full`` [T, V]; returns the local full
