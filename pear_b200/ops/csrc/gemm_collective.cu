@@ -71,6 +71,8 @@ __device__ __forceinline__ bool wait_epoch_gpu(const uint32_t* flag, uint32_t ep
 // MODE 1: GEMM -> reduce-scatter (A, B local; outs.p[r] = rank r's staging buffer; c = this rank's result rows)
 // MODE 2: GEMM -> all-to-all (A [M local tokens, K], B local; column group p of width N / world goes to rank p: outs.p[p] =
 //         rank p's bf16 buffer [world * M, ldc], this rank's rows at rank * M)
+// MODE 3: all-to-all -> GEMM (outs.p[p] = rank p's bf16 buffer [world * M, K / world]: all tokens, rank p's K columns; this
+//         rank multiplies ITS M tokens over the whole K; copier warps stage the peers' column groups into a_full [M, K])
 template <int BN, int MODE, bool OUT_BF16>
 __global__ void __launch_bounds__(kCThreads, 1)
 gemm_coll_kernel(const __grid_constant__ MapSet maps, const __grid_constant__ CUtensorMap map_b, void* __restrict__ c,
@@ -90,6 +92,14 @@ gemm_coll_kernel(const __grid_constant__ MapSet maps, const __grid_constant__ CU
   // tile order: owner-major starting at the own rank (MODE 0) or at the next rank (MODE 1)
   auto tile_coords = [&](int t, int& owner, int& m0, int& n0) {
     constexpr int kBand = 16;
+    if (MODE == 3) {
+      owner = rank;
+      const int band = t / (kBand * tiles_n), in_band = t % (kBand * tiles_n);
+      const int rows_here = min(kBand, tiles_m - band * kBand);
+      m0 = (band * kBand + in_band % rows_here) * kCBM;
+      n0 = (in_band / rows_here) * BN;
+      return;
+    }
     if (MODE == 2) {
       // destination-major starting after the own rank (at any moment the ranks store to different peers), own columns last
       const int tiles_n_dest = tiles_n / world, per_dest = tiles_m * tiles_n_dest;
@@ -140,13 +150,23 @@ gemm_coll_kernel(const __grid_constant__ MapSet maps, const __grid_constant__ CU
         // MODE 0: maps.a[0] = the local shard (rows relative to it), maps.a[1] = the local full-A buffer (global rows)
         const CUtensorMap* ma = MODE == 0 ? (owner == rank ? &maps.a[0] : &maps.a[1]) : &maps.a[0];
         const int am0 = (MODE == 0 && owner == rank) ? m0 - owner * m_local : m0;
+        const int kbg = kblocks / world;  // MODE 3: K blocks per column group
+        int group_ready = rank;
         for (int kb = 0; kb < kblocks; ++kb) {
+          // MODE 3: the own column group first (local data), then the groups in the order the copier warps fetch them
+          const int kb2 = MODE == 3 ? (kb + rank * kbg) % kblocks : kb;
+          const int grp = MODE == 3 ? kb2 / kbg : 0;
+          if (MODE == 3 && grp != rank && grp != group_ready) {
+            if (!wait_epoch_gpu(chunk_flags + (m0 / kCBM) * world + grp, 8u, budget)) set_status(status, PEAR_ERR_FLAG_TIMEOUT);
+            group_ready = grp;
+          }
           ok = mbar_wait_bounded(&sm->empty[st], ph ^ 1, status);
           if (!ok) break;
           uint8_t* a = tiles + st * kStageBytes;
           mbar_expect_tx(&sm->full[st], kStageBytes);
-          tma_load_2d(a, ma, kb * kCBK, am0, &sm->full[st]);
-          tma_load_2d(a + kABytes, &map_b, kb * kCBK, n0, &sm->full[st]);
+          if (MODE == 3) tma_load_2d(a, grp == rank ? &maps.a[0] : &maps.a[1], grp == rank ? (kb2 - grp * kbg) * kCBK : kb2 * kCBK, m0, &sm->full[st]);
+          else tma_load_2d(a, ma, kb * kCBK, am0, &sm->full[st]);
+          tma_load_2d(a + kABytes, &map_b, kb2 * kCBK, n0, &sm->full[st]);
           if (++st == kCStages) { st = 0; ph ^= 1; }
         }
       }
@@ -349,6 +369,46 @@ gemm_coll_kernel(const __grid_constant__ MapSet maps, const __grid_constant__ CU
       if (ct == 0) asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(chunk_flags + owner * tiles_m_local + mt), "r"(1u) : "memory");
     }
   }
+  if (MODE == 3 && warp >= 6 && world > 1) {
+    // ------------------------------------------------------------------------------------------------ copier warps (all-to-all)
+    // Peer p holds [all tokens][its K / world columns]; this rank needs its own M tokens of every column group. A
+    // (128-row block, group) is copied as 8 pieces of 16 rows (contiguous at the source, strided by K here), group by
+    // group starting after the own rank, and counted in chunk_flags[block * world + group] (zero at launch).
+    const int ct = threadIdx.x - 192;
+    constexpr int kSub = 8;
+    const int kg8 = K / world / 8;  // 16-byte vectors per source row
+    const size_t vec_per_piece = (size_t)(kCBM / kSub) * kg8;
+    for (int cidx = blockIdx.x; cidx < (world - 1) * tiles_m * kSub; cidx += gridDim.x) {
+      const int t = cidx / kSub, piece = cidx % kSub;
+      const int p = (rank + 1 + t / tiles_m) % world, mt = t % tiles_m;
+      if (ct == 0) {
+        copier_ok = wait_epoch(my_flags + slot * kCMaxRanks + p, epoch, budget) ? 1 : 0;
+        if (!copier_ok) set_status(status, PEAR_ERR_FLAG_TIMEOUT);
+      }
+      asm volatile("bar.sync 3, 64;" ::: "memory");
+      if (copier_ok) {
+        const int row0 = mt * kCBM + piece * (kCBM / kSub);
+        const uint4* src = (const uint4*)outs.p[p] + ((size_t)rank * M + row0) * kg8;
+        uint4* dst = a_full + ((size_t)row0 * K + (size_t)p * (K / world)) / 8;
+        for (size_t i = ct; i < vec_per_piece; i += 64 * 8) {
+          uint4 v[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            if (i + (size_t)u * 64 < vec_per_piece)
+              asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w) : "l"(src + i + (size_t)u * 64) : "memory");
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const size_t e = i + (size_t)u * 64;
+            if (e < vec_per_piece) dst[(e / kg8) * (size_t)(K / 8) + e % kg8] = v[u];
+          }
+        }
+        asm volatile("fence.proxy.async;" ::: "memory");
+        __threadfence();
+      }
+      asm volatile("bar.sync 3, 64;" ::: "memory");
+      if (ct == 0) asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(chunk_flags + mt * world + p), "r"(1u) : "memory");
+    }
+  }
   tcgen05_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -470,4 +530,30 @@ PEAR_API int pear_gemm_a2a_bf16(const void* a, const void* b, void* const* outs_
   cudaStream_t s = (cudaStream_t)stream;
   return wide ? launch_coll<256, 2, true>(maps, mb, nullptr, outs, M, N, K, ldo, rank, world, nullptr, 0, 0, 1u << 22, status, num_sms, s)
               : launch_coll<128, 2, true>(maps, mb, nullptr, outs, M, N, K, ldo, rank, world, nullptr, 0, 0, 1u << 22, status, num_sms, s);
+}
+
+// All-to-all -> GEMM (Ulysses: head-sharded attention output in, token-sharded o_proj out). srcs[p]: rank p's bf16 buffer
+// [world * M, K / world] in symmetric memory (all tokens, rank p's columns, rows contiguous), published by pear_symm_signal
+// (`slot`, `epoch`) after it was written. b [N, K] local. C [M, N] = this rank's tokens (rows [rank * M, ...) of every
+// source) times b^T. a_full: local bf16 [M, K] staging; chunk_flags: uint32 [M / 128 * world], ZERO at launch.
+// M a multiple of 128, K / world a multiple of 64.
+PEAR_API int pear_a2a_gemm_bf16(const void* const* srcs, const void* b, void* c, int M, int N, int K, int ldb, int ldc, int out_bf16,
+                                int rank, int world, const void* my_flags, int slot, unsigned epoch, unsigned budget, int* status,
+                                int num_sms, void* a_full, void* chunk_flags, void* stream) {
+  if (world < 1 || world > kCMaxRanks || M % kCBM || K % world || (K / world) % kCBK || (ldb % 8)) return (int)cudaErrorInvalidValue;
+  const int kg = K / world;
+  MapSet maps;
+  int e = coll_map_bf16(&maps.a[0], (const __nv_bfloat16*)srcs[rank] + (size_t)rank * M * kg, M, kg, kg, kCBM);
+  if (e) return e;
+  e = coll_map_bf16(&maps.a[1], a_full, M, K, K, kCBM);
+  if (e) return e;
+  for (int r = 2; r < kCMaxRanks; ++r) maps.a[r] = maps.a[0];
+  CUtensorMap mb;
+  e = coll_map_bf16(&mb, b, N, K, ldb, 256);
+  if (e) return e;
+  OutPtrs src{};
+  for (int r = 0; r < world; ++r) src.p[r] = (float*)const_cast<void*>(srcs[r]);
+  cudaStream_t s = (cudaStream_t)stream;
+  return out_bf16 ? launch_coll<256, 3, true>(maps, mb, c, src, M, N, K, ldc, rank, world, (const uint32_t*)my_flags, slot, epoch, budget, status, num_sms, s, a_full, chunk_flags)
+                  : launch_coll<256, 3, false>(maps, mb, c, src, M, N, K, ldc, rank, world, (const uint32_t*)my_flags, slot, epoch, budget, status, num_sms, s, a_full, chunk_flags);
 }

@@ -177,6 +177,33 @@ class SymmWorld:
         self.device_barrier()  # every rank's stores have landed here
         return out.tensor
 
+    # -- all-to-all -> GEMM (Ulysses: head-sharded attention output in, token-sharded output projection out) -----------
+    def a2a_gemm(self, src: SymmBuffer, b: torch.Tensor, out_dtype=torch.float32) -> torch.Tensor:
+        """``src.tensor`` [world * M, K / world] (all tokens, this rank's columns: written on this stream before the call).
+        Returns ``C`` [M, N] = this rank's tokens over the whole K times ``b^T``; the peers' column groups are pulled by
+        the GEMM's copier warps while it already multiplies the local group."""
+        rows, kg = src.tensor.shape
+        m, k, n = rows // self.world, kg * self.world, b.shape[0]
+        c = torch.empty(m, n, dtype=out_dtype, device=self.device)
+        key = ("a2a", m, k)
+        if key not in self._ag_bufs:
+            self._ag_bufs[key] = (torch.empty(m, k, dtype=torch.bfloat16, device=self.device),
+                                  torch.zeros(m // 128 * self.world, dtype=torch.int32, device=self.device))
+        a_full, chunk_flags = self._ag_bufs[key]
+        chunk_flags.zero_()
+        e = self.next_epoch(SLOT_AG)
+        self.signal(SLOT_AG, e)
+        _lib.check(_lib.lib().pear_a2a_gemm_bf16(src.c_ptrs, _lib.ptr(b), _lib.ptr(c), m, n, k, b.stride(0), c.stride(0),
+                                                  1 if out_dtype == torch.bfloat16 else 0, self.rank, self.world, _lib.ptr(self.flags.tensor),
+                                                  SLOT_AG, e, DEFAULT_BUDGET, _lib.ptr(self.status), self.num_sms, _lib.ptr(a_full),
+                                                  _lib.ptr(chunk_flags), _lib.stream()), "a2a_gemm")
+        _lib.LAUNCH_COUNT += 1
+        return c
+
+    def a2a_gemm_done(self) -> None:
+        """Call before overwriting ``src`` again: every rank has finished pulling from it."""
+        self.device_barrier()
+
     # -- vocab-parallel logits all-gather -----------------------------------------------------------------------------
     def all_gather_logits(self, shard: torch.Tensor, full: SymmBuffer) -> torch.Tensor:
         """Write this rank's fp32 logits shard [T, V / world] into every rank's ``full`` [T, V]; returns the local full

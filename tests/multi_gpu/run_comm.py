@@ -185,6 +185,44 @@ def main() -> int:
             print(f"TIMING world {world} M {Mq} N {Nq} K {Kq}: gemm_a2a fused {t_own4:.3f} ms vs cublas + pack + nccl all-to-all {t_ref4:.3f} ms", flush=True)
         del obuf, recv
 
+    # ---- all-to-all -> GEMM (head-sharded columns in, token-sharded rows out)
+    for (Mo, No, Ko) in ((256, 384, world * 128), (128, 640, world * 320)):
+        src_all = (torch.randn(world, world * Mo, Ko // world, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+        wo = (torch.randn(No, Ko, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
+        sbuf = sw.alloc((world * Mo, Ko // world), torch.bfloat16)
+        for _ in range(2):
+            sbuf.tensor.copy_(src_all[rank])
+            got = sw.a2a_gemm(sbuf, wo)
+            sw.a2a_gemm_done()
+            torch.cuda.synchronize()
+            sw.check()
+            a_mine = torch.cat([src_all[p2][rank * Mo:(rank + 1) * Mo] for p2 in range(world)], dim=1).float()
+            want = a_mine @ wo.float().t()
+            assert torch.allclose(got, want, atol=3e-2, rtol=2e-2), (got - want).abs().max()
+    if rank == 0:
+        print("PASS a2a_gemm", flush=True)
+    if big:
+        Mo, No, Ko = 8192, 5120, 6144  # o_proj of the 27B shape over 8192 tokens per rank
+        sbuf = sw.alloc((world * Mo, Ko // world), torch.bfloat16)
+        sbuf.tensor.normal_(generator=g)
+        wo = (torch.randn(No, Ko, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
+        recv2 = torch.empty(world, Mo, Ko // world, dtype=torch.bfloat16, device="cuda")
+
+        def unfused_a2a_gemm():
+            dist.all_to_all_single(recv2.view(world * Mo, Ko // world), sbuf.tensor)
+            return recv2.permute(1, 0, 2).reshape(Mo, Ko) @ wo.t()
+
+        def fused_a2a_gemm():
+            r = sw.a2a_gemm(sbuf, wo, torch.bfloat16)
+            sw.a2a_gemm_done()
+            return r
+
+        t_ref5, t_own5 = timed(unfused_a2a_gemm), timed(fused_a2a_gemm)
+        sw.check()
+        if rank == 0:
+            print(f"TIMING world {world} M {Mo} N {No} K {Ko}: a2a_gemm fused {t_own5:.3f} ms vs nccl all-to-all + unpack + cublas {t_ref5:.3f} ms", flush=True)
+        del sbuf, recv2
+
     # ---- gradient reduce-scatter + clip + sharded AdamW + parameter all-gather in two kernels
     from pear_b200.parallel.symm import FusedShardedAdamW
 
