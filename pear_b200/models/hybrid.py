@@ -38,6 +38,7 @@ class RMSNorm(nn.Module):
 
 
 _TP: dict = {"group": None, "fused": None, "defer": False}
+FRONT_KERNEL: dict = {"on": True}  # GDN front end of the training forward through the fused kernel pair on a GPU
 
 
 def set_tensor_parallel_group(group) -> None:
@@ -188,10 +189,21 @@ class GatedDeltaNet(nn.Module):
     def conv_weight(self) -> torch.Tensor:
         return self.conv1d.weight.view(self.cfg.gdn_conv_dim, self.cfg.conv_kernel)
 
-    def front(self, mixed: torch.Tensor, bounds: list[int], init_conv: Optional[torch.Tensor]):
+    def front(self, mixed: torch.Tensor, bounds: list[int], init_conv: Optional[torch.Tensor], need_conv_state: bool = True):
         """conv + SiLU + split + L2 norms. Returns q [T,Hk,K], k, v [T,Hv,V] and the final conv rows."""
         cfg = self.cfg
         t = mixed.shape[0]
+        if (not need_conv_state and mixed.is_cuda and init_conv is None and mixed.dtype == torch.float32 and cfg.gdn_head_dim == 128 and cfg.conv_kernel == 4
+                and FRONT_KERNEL["on"]):
+            # one kernel forward (conv + SiLU + both L2 norms), two backward; the final conv rows are the last raw rows
+            from ..ops import rollout_ops
+
+            u = rollout_ops.gdn_front_autograd(mixed, self.conv_weight(), bounds, 2 * cfg.gdn_key_dim, cfg.l2_eps)
+            kd = cfg.gdn_key_dim
+            q = u[:, :kd].reshape(t, cfg.gdn_qk_heads, cfg.gdn_head_dim)
+            k = u[:, kd : 2 * kd].reshape(t, cfg.gdn_qk_heads, cfg.gdn_head_dim)
+            v = u[:, 2 * kd :].reshape(t, cfg.gdn_v_heads, cfg.gdn_head_dim)
+            return q, k, v, None
         u, conv_final = ops.causal_conv_silu(mixed, self.conv_weight(), bounds, init_conv)
         kd = cfg.gdn_key_dim
         q = u[:, :kd].reshape(t, cfg.gdn_qk_heads, cfg.gdn_head_dim)
@@ -213,7 +225,7 @@ class GatedDeltaNet(nn.Module):
         if meta.sp is not None and meta.sp.size > 1:
             o = meta.sp.gdn(self, mixed, g, beta, meta, bounds)
         else:
-            q, k, v, _ = self.front(mixed, bounds, None)
+            q, k, v, _ = self.front(mixed, bounds, None, need_conv_state=False)
             o = ops.gdn_scan_packed(q, k, v, g, beta, bounds)
         y = ops.gated_rms_norm(o, z, self.norm.weight, cfg.rms_eps).reshape(t, cfg.gdn_value_dim)
         return row_linear(y, self.out_proj.weight)

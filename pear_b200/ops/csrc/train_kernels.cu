@@ -88,9 +88,79 @@ __global__ void __launch_bounds__(128) gdn_front_kernel(const float* __restrict_
   y[(size_t)t * C + ch] = v;
 }
 
+// Backward of the front end, step 1: gradient at the convolution output. Same grid as the forward; the convolution and
+// SiLU are recomputed (4 loads), the L2 norm's Jacobian needs one more block reduction (y_hat . dy).
+__global__ void __launch_bounds__(128) gdn_front_bwd_act_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                                                const int* __restrict__ seq_start, const float* __restrict__ dy,
+                                                                float* __restrict__ dacc, int C, int qk_channels, float eps) {
+  __shared__ float red[8];
+  const int t = blockIdx.y, ch = blockIdx.x * 128 + threadIdx.x;
+  const int s0 = seq_start[t];
+  float acc = 0.f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int tt = t - 3 + j;
+    if (tt >= s0) acc += w[(size_t)ch * 4 + j] * x[(size_t)tt * C + ch];
+  }
+  const float sig = 1.f / (1.f + __expf(-acc));
+  const float v = acc * sig;
+  float dv = dy[(size_t)t * C + ch];
+  if (blockIdx.x * 128 < qk_channels) {
+    float ss = warp_sum(v * v);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    ss = red[0] + red[1] + red[2] + red[3];
+    const float n = rsqrtf(ss + eps), yhat = v * n;
+    float dot = warp_sum(yhat * dv);
+    if ((threadIdx.x & 31) == 0) red[4 + (threadIdx.x >> 5)] = dot;
+    __syncthreads();
+    dot = red[4] + red[5] + red[6] + red[7];
+    const float scale = blockIdx.x * 128 < qk_channels / 2 ? 0.08838834764831845f : 1.f;
+    dv = scale * n * (dv - yhat * dot);
+  }
+  dacc[(size_t)t * C + ch] = dv * (sig + acc * sig * (1.f - sig));
+}
+
+// Step 2: dx[t] = sum_j w[j] dacc[t + 3 - j] over the rows of the same sequence, and dw[c, j] += sum_t dacc[t] x[t - 3 + j].
+// Grid (channel group of 128, chunk of 64 tokens); one thread per channel, coalesced over channels.
+__global__ void __launch_bounds__(128) gdn_front_bwd_conv_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                                                 const int* __restrict__ seq_start, const float* __restrict__ dacc,
+                                                                 float* __restrict__ dx, float* __restrict__ dw, int T, int C) {
+  const int ch = blockIdx.x * 128 + threadIdx.x, t0 = blockIdx.y * 64, t1 = min(T, t0 + 64);
+  float wj[4], dwj[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) wj[j] = w[(size_t)ch * 4 + j];
+  for (int t = t0; t < t1; ++t) {
+    const int s0 = seq_start[t];
+    const float d = dacc[(size_t)t * C + ch];
+    float g = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int tu = t + 3 - j;  // the output row that read x[t] through tap j
+      if (tu < T && seq_start[tu] <= t) g += wj[j] * dacc[(size_t)tu * C + ch];
+      const int ti = t - 3 + j;  // the input row that output row t read through tap j
+      if (ti >= s0) dwj[j] += d * x[(size_t)ti * C + ch];
+    }
+    dx[(size_t)t * C + ch] = g;
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) atomicAdd(dw + (size_t)ch * 4 + j, dwj[j]);
+}
+
 }  // namespace pear
 
 using namespace pear;
+
+// dy [T, C] -> dx [T, C] and dw [C, 4] (ZERO at launch; accumulated with atomics). dacc: fp32 [T, C] scratch.
+PEAR_API int pear_gdn_front_bwd(const float* x, const float* w, const int* seq_start, const float* dy, float* dacc, float* dx, float* dw,
+                                int T, int C, int qk_channels, float eps, void* stream) {
+  if (C % 128 || qk_channels % 256) return (int)cudaErrorInvalidValue;
+  gdn_front_bwd_act_kernel<<<dim3(C / 128, T), 128, 0, (cudaStream_t)stream>>>(x, w, seq_start, dy, dacc, C, qk_channels, eps);
+  PEAR_LAUNCH_CHECK();
+  gdn_front_bwd_conv_kernel<<<dim3(C / 128, (T + 63) / 64), 128, 0, (cudaStream_t)stream>>>(x, w, seq_start, dacc, dx, dw, T, C);
+  PEAR_LAUNCH_CHECK();
+  return 0;
+}
 
 // run: float[rows][4] = (m, s1, s2, unused); the caller initialises it to (-FLT_MAX, 0, 0, 0) before the first chunk.
 PEAR_API int pear_head_stats_update(const float* logits, int rows, int ld, int Vc, int v0, float temperature, float* run, const int* ids, int J,

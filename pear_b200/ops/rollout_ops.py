@@ -136,14 +136,70 @@ def logprob_entropy_fused(hidden: torch.Tensor, weight: torch.Tensor, ids: torch
     return lp, ent
 
 
+_STARTS_CACHE: dict = {}
+
+
+def _seq_starts(cu_seqlens, t: int, device) -> torch.Tensor:
+    """First row of its sequence for every packed row, on the device. The same boundaries come back for every layer and
+    pass of a micro-batch, so the last few results are kept (a host-to-device copy from pageable memory would otherwise
+    drain the stream each time)."""
+    key = (tuple(cu_seqlens), t, str(device))
+    hit = _STARTS_CACHE.get(key)
+    if hit is not None:
+        return hit
+    b = torch.tensor(list(cu_seqlens[:-1]), dtype=torch.int64)
+    lens = torch.tensor([e - s for s, e in zip(cu_seqlens[:-1], cu_seqlens[1:])], dtype=torch.int64)
+    starts = torch.repeat_interleave(b, lens).to(torch.int32)
+    if starts.numel() != t:
+        raise ValueError("sequence boundaries do not cover the rows")
+    if torch.cuda.is_available():
+        starts = starts.pin_memory()
+    out = starts.to(device, non_blocking=True)
+    if len(_STARTS_CACHE) >= 16:
+        _STARTS_CACHE.pop(next(iter(_STARTS_CACHE)))
+    _STARTS_CACHE[key] = out
+    return out
+
+
+class _GdnFront(torch.autograd.Function):
+    """Forward and backward of the GDN front end on the kernels of ``csrc/train_kernels.cu``."""
+
+    @staticmethod
+    def forward(ctx, x, conv_w, starts, qk_channels, eps):
+        xc, wc = x.contiguous(), conv_w.float().contiguous()
+        t, c = xc.shape
+        y = torch.empty_like(xc)
+        _lib.check(_lib.lib().pear_gdn_front(_lib.ptr(xc), _lib.ptr(wc), _lib.ptr(starts), _lib.ptr(y), t, c, qk_channels, _f(eps), _lib.stream()),
+                   "gdn_front")
+        _lib.count_launch(1)
+        ctx.save_for_backward(xc, wc, starts)
+        ctx.qk_channels, ctx.eps, ctx.w_dtype = qk_channels, eps, conv_w.dtype
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        xc, wc, starts = ctx.saved_tensors
+        t, c = xc.shape
+        dyc = dy.contiguous().float()
+        dacc, dx = torch.empty_like(xc), torch.empty_like(xc)
+        dw = torch.zeros_like(wc)
+        _lib.check(_lib.lib().pear_gdn_front_bwd(_lib.ptr(xc), _lib.ptr(wc), _lib.ptr(starts), _lib.ptr(dyc), _lib.ptr(dacc), _lib.ptr(dx), _lib.ptr(dw),
+                                                 t, c, ctx.qk_channels, _f(ctx.eps), _lib.stream()), "gdn_front_bwd")
+        _lib.count_launch(2)
+        return dx, dw.to(ctx.w_dtype), None, None, None
+
+
+def gdn_front_autograd(x: torch.Tensor, conv_w: torch.Tensor, cu_seqlens, qk_channels: int, eps: float = 1e-6) -> torch.Tensor:
+    """:func:`gdn_front` with a backward (the trainer's path): x [T, C] fp32, conv_w [C, 4]."""
+    return _GdnFront.apply(x, conv_w, _seq_starts(list(cu_seqlens), x.shape[0], x.device), qk_channels, eps)
+
+
 def gdn_front(x: torch.Tensor, conv_w: torch.Tensor, cu_seqlens: list[int], qk_channels: int, eps: float = 1e-6) -> torch.Tensor:
     """conv(4) + SiLU over packed sequences, q / k heads L2-normalised (q scaled by 128^-0.5). x [T, C] fp32."""
     t, c = x.shape
-    starts = torch.empty(t, dtype=torch.int32)
-    for s, e in zip(cu_seqlens[:-1], cu_seqlens[1:]):
-        starts[s:e] = s
+    starts = _seq_starts(list(cu_seqlens), t, x.device)
     y = torch.empty_like(x)
-    _lib.check(_lib.lib().pear_gdn_front(_lib.ptr(x.contiguous()), _lib.ptr(conv_w.float().contiguous()), _lib.ptr(starts.to(x.device)), _lib.ptr(y), t, c,
+    _lib.check(_lib.lib().pear_gdn_front(_lib.ptr(x.contiguous()), _lib.ptr(conv_w.float().contiguous()), _lib.ptr(starts), _lib.ptr(y), t, c,
                                          qk_channels, _f(eps), _lib.stream()), "gdn_front")
     _lib.count_launch(1)
     return y

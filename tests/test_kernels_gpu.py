@@ -153,3 +153,28 @@ def test_chunked_head_on_gpu_matches_the_dense_statement():
     assert (lp - lp2).abs().max().item() < 1e-4 and (ent - ent2).abs().max().item() < 1e-4
     assert ((gh - h.grad).norm() / h.grad.norm()).item() < 2e-2  # bf16 operands in the gradient products
     assert ((gw - w.grad).norm() / w.grad.norm()).item() < 2e-2
+
+
+def test_gdn_front_end_backward_matches_autograd_of_the_torch_statement():
+    from pear_b200.ops import rollout_ops
+
+    g = torch.Generator(device="cuda").manual_seed(2)
+    hk, hv, d = 2, 4, 128
+    c = (2 * hk + hv) * d
+    bounds = [0, 37, 38, 150]
+    x = torch.randn(150, c, device="cuda", generator=g).requires_grad_(True)
+    w = (torch.randn(c, 4, device="cuda", generator=g) * 0.5).requires_grad_(True)
+    dy = torch.randn(150, c, device="cuda", generator=g)
+    y = rollout_ops.gdn_front_autograd(x, w, bounds, 2 * hk * d, 1e-6)
+    y.backward(dy)
+    gx, gw = x.grad.clone(), w.grad.clone()
+    x.grad = w.grad = None
+    u, _ = ref.causal_conv_silu(x, w, bounds, None)
+    kd = hk * d
+    q = ref.l2norm(u[:, :kd].reshape(150, hk, d), 1e-6) * d ** -0.5
+    k = ref.l2norm(u[:, kd:2 * kd].reshape(150, hk, d), 1e-6)
+    want = torch.cat([q.reshape(150, kd), k.reshape(150, kd), u[:, 2 * kd:]], dim=1)
+    assert (y - want).abs().max().item() < 1e-5
+    want.backward(dy)
+    assert (gx - x.grad).abs().max().item() < 1e-4 * max(1.0, x.grad.abs().max().item())
+    assert (gw - w.grad).abs().max().item() < 1e-3 * max(1.0, w.grad.abs().max().item())
