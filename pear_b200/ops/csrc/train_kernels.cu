@@ -182,3 +182,125 @@ PEAR_API int pear_gdn_front(const float* x, const float* w, const int* seq_start
   PEAR_LAUNCH_CHECK();
   return 0;
 }
+
+// ------------------------------------------------------------------------------------------------ delta-rule chunk loop
+// The sequential part of the chunked (WY) Gated-DeltaNet scan for one sequence: per value head and chunk c of 64 tokens,
+// with the chunk-local operands prepared in parallel beforehand (W = T (beta k e^G), U = T (beta v), Qe = q e^G,
+// A = tril(q k^T * decay), Kt = k e^(G_C - G), gamma = e^(G_C)):
+//     v' = U - W S^T;   o = Qe S^T + A v';   S <- gamma S + v'^T Kt
+// Grid (value head, 32-wide slice of the value dimension): the rows of S (one per value channel) are independent, so
+// four CTAs share a head without talking. fp32 SIMT throughout; S lives in shared memory as St[k][v]. Operands are
+// staged transposed with padded rows so that a warp reads consecutive words (upstream: cuDNN / FlashInfer sm100 GDN
+// kernels, pear/models/qwen3_5/trainer/blackwell/delta_rule.py:91-161).
+namespace pear {
+constexpr int kScC = 64, kScK = 128, kScVs = 32, kScPad = 65;
+
+__global__ void __launch_bounds__(256, 1)
+gdn_chunk_loop_kernel(const float* __restrict__ W, const float* __restrict__ U, const float* __restrict__ Qe, const float* __restrict__ A,
+                      const float* __restrict__ Kt, const float* __restrict__ gamma, const float* __restrict__ S0, float* __restrict__ O,
+                      float* __restrict__ S_out, float* __restrict__ S_hist, int n_chunks, int V) {
+  extern __shared__ float sh[];
+  float* Wt = sh;                        // [128 k][65]  (i < 64)
+  float* Qt = Wt + kScK * kScPad;        // [128 k][65]
+  float* Ks = Qt + kScK * kScPad;        // [64 i][128 k]
+  float* At = Ks + kScC * kScK;          // [64 j][65]   At[j][i] = A[i][j]
+  float* St = At + kScC * kScPad;        // [128 k][32 v]
+  float* vps = St + kScK * kScVs;        // [64 j][32 v]
+  const int h = blockIdx.x, vs = blockIdx.y * kScVs, tid = threadIdx.x;
+  // state slice: S[h][vs + v][k] -> St[k][v]
+  for (int e = tid; e < kScVs * kScK; e += 256) {
+    const int v = e / kScK, k = e % kScK;
+    St[k * kScVs + v] = S0 ? S0[((size_t)h * V + vs + v) * kScK + k] : 0.f;
+  }
+  __syncthreads();
+  const int i = tid & 63, vq = tid >> 6;      // steps 1-2: row i of the chunk, 8 value channels vq * 8 ..
+  const int kk = tid & 127, vh = tid >> 7;    // step 3: key channel kk, 16 value channels vh * 16 ..
+  for (int c = 0; c < n_chunks; ++c) {
+    const size_t hc = (size_t)h * n_chunks + c;
+    const float* Wc = W + hc * kScC * kScK;
+    const float* Qc = Qe + hc * kScC * kScK;
+    const float* Kc = Kt + hc * kScC * kScK;
+    const float* Ac = A + hc * kScC * kScC;
+    for (int e = tid; e < kScC * kScK; e += 256) {  // coalesced along k; transposed into padded rows
+      const int r = e / kScK, k = e % kScK;
+      Wt[k * kScPad + r] = Wc[e];
+      Qt[k * kScPad + r] = Qc[e];
+      Ks[e] = Kc[e];
+    }
+    for (int e = tid; e < kScC * kScC; e += 256) At[(e % kScC) * kScPad + e / kScC] = Ac[e];
+    if (S_hist) {  // the state BEFORE this chunk, for a backward pass
+      float* dst = S_hist + (hc * V + vs) * kScK;
+      for (int e = tid; e < kScVs * kScK; e += 256) dst[e] = St[(e % kScK) * kScVs + e / kScK];
+    }
+    __syncthreads();
+    // 1. v' = U - W S^T and the state part of the output, Qe S^T
+    float wv[8], ov[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) wv[j] = ov[j] = 0.f;
+#pragma unroll 4
+    for (int k = 0; k < kScK; ++k) {
+      const float w = Wt[k * kScPad + i], q = Qt[k * kScPad + i];
+      const float4 s0 = *(const float4*)(St + k * kScVs + vq * 8), s1 = *(const float4*)(St + k * kScVs + vq * 8 + 4);
+      const float s[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { wv[j] += w * s[j]; ov[j] += q * s[j]; }
+    }
+    const float* Uc = U + (hc * kScC + i) * V + vs + vq * 8;
+    const float4 u0 = *(const float4*)Uc, u1 = *(const float4*)(Uc + 4);
+    const float u[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) vps[i * kScVs + vq * 8 + j] = u[j] - wv[j];
+    __syncthreads();
+    // 2. o = Qe S^T + A v'
+#pragma unroll 4
+    for (int j = 0; j < kScC; ++j) {
+      const float a = At[j * kScPad + i];
+      const float4 p0 = *(const float4*)(vps + j * kScVs + vq * 8), p1 = *(const float4*)(vps + j * kScVs + vq * 8 + 4);
+      ov[0] += a * p0.x; ov[1] += a * p0.y; ov[2] += a * p0.z; ov[3] += a * p0.w;
+      ov[4] += a * p1.x; ov[5] += a * p1.y; ov[6] += a * p1.z; ov[7] += a * p1.w;
+    }
+    float* Oc = O + (hc * kScC + i) * V + vs + vq * 8;
+    *(float4*)Oc = make_float4(ov[0], ov[1], ov[2], ov[3]);
+    *(float4*)(Oc + 4) = make_float4(ov[4], ov[5], ov[6], ov[7]);
+    // 3. S <- gamma S + v'^T Kt (every thread owns St[kk][vh * 16 .. + 15]; nobody reads St before the next barrier pair)
+    const float gm = gamma[hc];
+    float acc[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) acc[j] = 0.f;
+#pragma unroll 2
+    for (int r = 0; r < kScC; ++r) {
+      const float kt = Ks[r * kScK + kk];
+#pragma unroll
+      for (int j4 = 0; j4 < 4; ++j4) {
+        const float4 p = *(const float4*)(vps + r * kScVs + vh * 16 + j4 * 4);
+        acc[j4 * 4] += kt * p.x; acc[j4 * 4 + 1] += kt * p.y; acc[j4 * 4 + 2] += kt * p.z; acc[j4 * 4 + 3] += kt * p.w;
+      }
+    }
+    __syncthreads();  // every thread has finished reading St (step 1) and vps before they change
+#pragma unroll
+    for (int j = 0; j < 16; ++j) St[kk * kScVs + vh * 16 + j] = gm * St[kk * kScVs + vh * 16 + j] + acc[j];
+    __syncthreads();
+  }
+  for (int e = tid; e < kScVs * kScK; e += 256) {
+    const int v = e / kScK, k = e % kScK;
+    S_out[((size_t)h * V + vs + v) * kScK + k] = St[k * kScVs + v];
+  }
+}
+}  // namespace pear
+
+// W, Qe, Kt: fp32 [H, n, 64, 128]; U, O: fp32 [H, n, 64, V]; A: fp32 [H, n, 64, 64]; gamma: fp32 [H, n]; S0 (may be null),
+// S_out: fp32 [H, V, 128]; S_hist (may be null): fp32 [H, n, V, 128]. V a multiple of 32.
+PEAR_API int pear_gdn_chunk_loop(const float* W, const float* U, const float* Qe, const float* A, const float* Kt, const float* gamma,
+                                 const float* S0, float* O, float* S_out, float* S_hist, int H, int n_chunks, int V, void* stream) {
+  using namespace pear;
+  if (V % kScVs || H <= 0 || n_chunks <= 0) return (int)cudaErrorInvalidValue;
+  constexpr int smem = (2 * kScK * kScPad + kScC * kScK + kScC * kScPad + kScK * kScVs + kScC * kScVs) * 4;
+  static bool configured = false;
+  if (!configured) {
+    PEAR_CUDA_CHECK(cudaFuncSetAttribute(gdn_chunk_loop_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    configured = true;
+  }
+  gdn_chunk_loop_kernel<<<dim3(H, V / kScVs), 256, smem, (cudaStream_t)stream>>>(W, U, Qe, A, Kt, gamma, S0, O, S_out, S_hist, n_chunks, V);
+  PEAR_LAUNCH_CHECK();
+  return 0;
+}

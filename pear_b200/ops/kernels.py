@@ -235,7 +235,25 @@ def causal_conv_silu(x, weight, bounds, init_state=None):
     return ref.causal_conv_silu(x, weight, bounds, init_state)
 
 
+USE_SCAN_KERNEL = True  # gradient-free scans on a GPU (rollout prefill, the first pass of a checkpointed layer)
+
+
 def gdn_scan(q, k, v, g, beta, state=None):
+    """Chunked delta-rule scan of one sequence. Without gradients on a GPU the chunk-by-chunk loop (64 dependent steps of
+    small products for 4096 tokens) is ONE launch of ``gdn_chunk_loop_kernel``; the chunk-local operands stay batched
+    torch statements."""
+    if (USE_SCAN_KERNEL and q.is_cuda and not torch.is_grad_enabled() and q.shape[2] == 128 and v.shape[2] % 32 == 0
+            and ref.GDN_CHUNK == 64 and q.shape[0] > 0):
+        op = ref.gdn_chunk_operands(q, k, v, g, beta)
+        hv, vd, n, t = v.shape[1], v.shape[2], op["n"], op["t"]
+        o = torch.empty(hv, n, 64, vd, dtype=torch.float32, device=q.device)
+        s_out = torch.empty(hv, vd, 128, dtype=torch.float32, device=q.device)
+        s0 = state.float().contiguous() if state is not None else None
+        c = lambda x: x.contiguous()
+        check(lib().pear_gdn_chunk_loop(ptr(c(op["W"])), ptr(c(op["U"])), ptr(c(op["Qe"])), ptr(c(op["A"])), ptr(c(op["Kt"])),
+                                        ptr(c(op["gamma"])), ptr(s0), ptr(o), ptr(s_out), ptr(None), hv, n, vd, stream()), "gdn_chunk_loop")
+        count_launch()
+        return o.permute(1, 2, 0, 3).reshape(n * 64, hv, vd)[:t], s_out
     return ref.gdn_chunked(q, k, v, g, beta, state)
 
 

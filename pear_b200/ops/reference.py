@@ -178,13 +178,11 @@ def gdn_recurrent(q, k, v, g, beta, state: torch.Tensor | None = None):
     return torch.stack(outs, dim=0) if outs else vf.new_zeros(0, hv, vd), s
 
 
-def gdn_chunked(q, k, v, g, beta, state: torch.Tensor | None = None, chunk: int = GDN_CHUNK):
-    """Chunked (WY) form of :func:`gdn_recurrent` for ONE sequence; same shapes, same result up to rounding.
-
-    Per chunk with in-chunk cumulative log decay G: ``L_ij = beta_i (k_i.k_j) exp(G_i - G_j)`` for i > j,
-    ``T = (I + L)^-1``, ``W = T (beta k e^G)``, ``U = T (beta v)``, ``v' = U - W S0^T``,
-    ``o = (q e^G) S0^T + tril((q k^T) * e^(G_i - G_j)) v'``, ``S1 = e^(G_C) S0 + v'^T (k e^(G_C - G))``.
-    """
+def gdn_chunk_operands(q, k, v, g, beta, chunk: int = GDN_CHUNK):
+    """The chunk-local operands of the chunked (WY) form, computed for all chunks in parallel: per chunk with in-chunk
+    cumulative log decay G: ``L_ij = beta_i (k_i.k_j) exp(G_i - G_j)`` for i > j, ``T = (I + L)^-1``,
+    ``W = T (beta k e^G)``, ``U = T (beta v)``, ``Qe = q e^G``, ``A = tril((q k^T) * e^(G_i - G_j))``,
+    ``Kt = k e^(G_C - G)``, ``gamma = e^(G_C)``. All fp32, shapes [Hv, n, C, *] (gamma [Hv, n])."""
     t, hk, kd = q.shape
     hv, vd = v.shape[1], v.shape[2]
     rep = hv // hk
@@ -223,12 +221,24 @@ def gdn_chunked(q, k, v, g, beta, state: torch.Tensor | None = None, chunk: int 
     qk = torch.einsum("hnik,hnjk->hnij", qc, kc) * decay
     G_last = G[..., -1]
     k_tail = kc * torch.exp(G_last[..., None] - G)[..., None]  # k e^(G_C - G)
-    s = state.float() if state is not None else qf.new_zeros(hv, vd, kd)
+    return {"W": W, "U": U, "Qe": qc * eG[..., None], "A": qk, "Kt": k_tail, "gamma": torch.exp(G_last), "n": n, "t": t}
+
+
+def gdn_chunked(q, k, v, g, beta, state: torch.Tensor | None = None, chunk: int = GDN_CHUNK):
+    """Chunked (WY) form of :func:`gdn_recurrent` for ONE sequence; same shapes, same result up to rounding.
+
+    With the operands of :func:`gdn_chunk_operands`, chunk by chunk: ``v' = U - W S0^T``,
+    ``o = Qe S0^T + A v'``, ``S1 = gamma S0 + v'^T Kt``.
+    """
+    hv, vd, kd = v.shape[1], v.shape[2], q.shape[2]
+    op = gdn_chunk_operands(q, k, v, g, beta, chunk)
+    n, t = op["n"], op["t"]
+    s = state.float() if state is not None else q.new_zeros(hv, vd, kd, dtype=torch.float32)
     outs = []
     for c in range(n):
-        v_new = U[:, c] - torch.einsum("hik,hvk->hiv", W[:, c], s)
-        o = torch.einsum("hik,hvk->hiv", qc[:, c] * eG[:, c, :, None], s) + torch.einsum("hij,hjv->hiv", qk[:, c], v_new)
-        s = s * torch.exp(G_last[:, c])[:, None, None] + torch.einsum("hiv,hik->hvk", v_new, k_tail[:, c])
+        v_new = op["U"][:, c] - torch.einsum("hik,hvk->hiv", op["W"][:, c], s)
+        o = torch.einsum("hik,hvk->hiv", op["Qe"][:, c], s) + torch.einsum("hij,hjv->hiv", op["A"][:, c], v_new)
+        s = s * op["gamma"][:, c][:, None, None] + torch.einsum("hiv,hik->hvk", v_new, op["Kt"][:, c])
         outs.append(o)
     o = torch.stack(outs, dim=1).permute(1, 2, 0, 3).reshape(n * chunk, hv, vd)[:t]
     return o, s

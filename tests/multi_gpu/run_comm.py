@@ -282,8 +282,9 @@ def main() -> int:
     from pear_b200.parallel.tensor_parallel import shard_state, tp_config
     from pear_b200.rollout.engine import EngineConfig, RolloutEngine, SamplingParams
 
-    cfg = HybridConfig(vocab_size=4096, hidden_size=512, num_layers=4, num_attention_heads=8, num_kv_heads=2, head_dim=128, rotary_dim=64,
-                       gdn_qk_heads=2, gdn_v_heads=4, gdn_head_dim=128, intermediate_size=1024, num_mtp_layers=0)
+    hd = max(2, world)  # every sharded head count divisible by the world size
+    cfg = HybridConfig(vocab_size=4096, hidden_size=512, num_layers=4, num_attention_heads=4 * hd, num_kv_heads=hd, head_dim=128, rotary_dim=64,
+                       gdn_qk_heads=hd, gdn_v_heads=2 * hd, gdn_head_dim=128, intermediate_size=1024, num_mtp_layers=0)
     full = hybrid.HybridForCausalLM(cfg, with_mtp=False).init_weights(5)
     prompts = [list(range(3, 40)), list(range(100, 117)), [5, 6, 7]]
     tp = hybrid.HybridForCausalLM(tp_config(cfg, world), with_mtp=False)

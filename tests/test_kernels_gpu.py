@@ -178,3 +178,30 @@ def test_gdn_front_end_backward_matches_autograd_of_the_torch_statement():
     want.backward(dy)
     assert (gx - x.grad).abs().max().item() < 1e-4 * max(1.0, x.grad.abs().max().item())
     assert (gw - w.grad).abs().max().item() < 1e-3 * max(1.0, w.grad.abs().max().item())
+
+
+def test_gdn_chunk_loop_kernel_matches_the_torch_loop_and_the_recurrence():
+    from pear_b200.ops import kernels as K
+    from pear_b200.ops import lib as kl
+
+    g = torch.Generator(device="cuda").manual_seed(4)
+    t, hk, hv, d = 333, 2, 4, 128  # 333 tokens: five full chunks and a padded tail
+    q = ref.l2norm(torch.randn(t, hk, d, device="cuda", generator=g)) * d ** -0.5
+    k = ref.l2norm(torch.randn(t, hk, d, device="cuda", generator=g))
+    v = torch.randn(t, hv, d, device="cuda", generator=g)
+    gate = -torch.rand(t, hv, device="cuda", generator=g) * 0.2
+    beta = torch.rand(t, hv, device="cuda", generator=g)
+    s0 = torch.randn(hv, d, d, device="cuda", generator=g) * 0.1
+    before = kl.LAUNCH_COUNT
+    with torch.no_grad():
+        o, s = K.gdn_scan(q, k, v, gate, beta, s0)
+    assert kl.LAUNCH_COUNT == before + 1
+    o_ref, s_ref = ref.gdn_chunked(q, k, v, gate, beta, s0)
+    assert (o - o_ref).abs().max().item() < 1e-4 and (s - s_ref).abs().max().item() < 1e-4
+    o_rec, s_rec = ref.gdn_recurrent(q, k, v, gate, beta, s0)
+    assert (o - o_rec).abs().max().item() < 2e-3 and (s - s_rec).abs().max().item() < 2e-3
+    # with gradients the torch loop keeps its autograd graph
+    q.requires_grad_(True)
+    before = kl.LAUNCH_COUNT
+    K.gdn_scan(q, k, v, gate, beta, s0)[0].sum().backward()
+    assert kl.LAUNCH_COUNT == before and q.grad is not None
