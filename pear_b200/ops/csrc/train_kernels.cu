@@ -187,7 +187,10 @@ PEAR_API int pear_gdn_front(const float* x, const float* w, const int* seq_start
 // The sequential part of the chunked (WY) Gated-DeltaNet scan for one sequence: per value head and chunk c of 64 tokens,
 // with the chunk-local operands prepared in parallel beforehand (W = T (beta k e^G), U = T (beta v), Qe = q e^G,
 // A = tril(q k^T * decay), Kt = k e^(G_C - G), gamma = e^(G_C)):
-//     v' = U - W S^T;   o = Qe S^T + A v';   S <- gamma S + v'^T Kt
+//     v' = U - W S^T;   o = Qe S^T + A v';   S <- gamma S + v'^T Kt (+ E)
+// The backward of this loop is the SAME linear recurrence run over the chunks in reverse with the roles of W and Kt
+// swapped (dS_c = gamma dS_{c+1} + (U' - Kt dS_{c+1}^T)^T W + dO^T Qe with U' = -A^T dO), so one kernel serves both:
+// the optional additive term E, the optional v' output and the optional state history exist for that use.
 // Grid (value head, 32-wide slice of the value dimension): the rows of S (one per value channel) are independent, so
 // four CTAs share a head without talking. fp32 SIMT throughout; S lives in shared memory as St[k][v]. Operands are
 // staged transposed with padded rows so that a warp reads consecutive words (upstream: cuDNN / FlashInfer sm100 GDN
@@ -197,8 +200,8 @@ constexpr int kScC = 64, kScK = 128, kScVs = 32, kScPad = 65;
 
 __global__ void __launch_bounds__(256, 1)
 gdn_chunk_loop_kernel(const float* __restrict__ W, const float* __restrict__ U, const float* __restrict__ Qe, const float* __restrict__ A,
-                      const float* __restrict__ Kt, const float* __restrict__ gamma, const float* __restrict__ S0, float* __restrict__ O,
-                      float* __restrict__ S_out, float* __restrict__ S_hist, int n_chunks, int V) {
+                      const float* __restrict__ Kt, const float* __restrict__ gamma, const float* __restrict__ S0, const float* __restrict__ E,
+                      float* __restrict__ O, float* __restrict__ S_out, float* __restrict__ S_hist, float* __restrict__ VP, int n_chunks, int V) {
   extern __shared__ float sh[];
   float* Wt = sh;                        // [128 k][65]  (i < 64)
   float* Qt = Wt + kScK * kScPad;        // [128 k][65]
@@ -250,18 +253,25 @@ gdn_chunk_loop_kernel(const float* __restrict__ W, const float* __restrict__ U, 
     const float u[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
 #pragma unroll
     for (int j = 0; j < 8; ++j) vps[i * kScVs + vq * 8 + j] = u[j] - wv[j];
-    __syncthreads();
-    // 2. o = Qe S^T + A v'
-#pragma unroll 4
-    for (int j = 0; j < kScC; ++j) {
-      const float a = At[j * kScPad + i];
-      const float4 p0 = *(const float4*)(vps + j * kScVs + vq * 8), p1 = *(const float4*)(vps + j * kScVs + vq * 8 + 4);
-      ov[0] += a * p0.x; ov[1] += a * p0.y; ov[2] += a * p0.z; ov[3] += a * p0.w;
-      ov[4] += a * p1.x; ov[5] += a * p1.y; ov[6] += a * p1.z; ov[7] += a * p1.w;
+    if (VP) {
+      float* Vc = VP + (hc * kScC + i) * V + vs + vq * 8;
+      *(float4*)Vc = make_float4(u[0] - wv[0], u[1] - wv[1], u[2] - wv[2], u[3] - wv[3]);
+      *(float4*)(Vc + 4) = make_float4(u[4] - wv[4], u[5] - wv[5], u[6] - wv[6], u[7] - wv[7]);
     }
-    float* Oc = O + (hc * kScC + i) * V + vs + vq * 8;
-    *(float4*)Oc = make_float4(ov[0], ov[1], ov[2], ov[3]);
-    *(float4*)(Oc + 4) = make_float4(ov[4], ov[5], ov[6], ov[7]);
+    __syncthreads();
+    // 2. o = Qe S^T + A v' (skipped when the caller wants the states only)
+    if (O) {
+#pragma unroll 4
+      for (int j = 0; j < kScC; ++j) {
+        const float a = At[j * kScPad + i];
+        const float4 p0 = *(const float4*)(vps + j * kScVs + vq * 8), p1 = *(const float4*)(vps + j * kScVs + vq * 8 + 4);
+        ov[0] += a * p0.x; ov[1] += a * p0.y; ov[2] += a * p0.z; ov[3] += a * p0.w;
+        ov[4] += a * p1.x; ov[5] += a * p1.y; ov[6] += a * p1.z; ov[7] += a * p1.w;
+      }
+      float* Oc = O + (hc * kScC + i) * V + vs + vq * 8;
+      *(float4*)Oc = make_float4(ov[0], ov[1], ov[2], ov[3]);
+      *(float4*)(Oc + 4) = make_float4(ov[4], ov[5], ov[6], ov[7]);
+    }
     // 3. S <- gamma S + v'^T Kt (every thread owns St[kk][vh * 16 .. + 15]; nobody reads St before the next barrier pair)
     const float gm = gamma[hc];
     float acc[16];
@@ -276,6 +286,11 @@ gdn_chunk_loop_kernel(const float* __restrict__ W, const float* __restrict__ U, 
         acc[j4 * 4] += kt * p.x; acc[j4 * 4 + 1] += kt * p.y; acc[j4 * 4 + 2] += kt * p.z; acc[j4 * 4 + 3] += kt * p.w;
       }
     }
+    if (E) {  // additive term of the state update (the reversed scan of the backward pass: dO^T Qe)
+      const float* Ec = E + (hc * V + vs + vh * 16) * kScK + kk;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) acc[j] += Ec[(size_t)j * kScK];
+    }
     __syncthreads();  // every thread has finished reading St (step 1) and vps before they change
 #pragma unroll
     for (int j = 0; j < 16; ++j) St[kk * kScVs + vh * 16 + j] = gm * St[kk * kScVs + vh * 16 + j] + acc[j];
@@ -288,10 +303,12 @@ gdn_chunk_loop_kernel(const float* __restrict__ W, const float* __restrict__ U, 
 }
 }  // namespace pear
 
-// W, Qe, Kt: fp32 [H, n, 64, 128]; U, O: fp32 [H, n, 64, V]; A: fp32 [H, n, 64, 64]; gamma: fp32 [H, n]; S0 (may be null),
-// S_out: fp32 [H, V, 128]; S_hist (may be null): fp32 [H, n, V, 128]. V a multiple of 32.
+// W, Qe, Kt: fp32 [H, n, 64, 128]; U, O, VP: fp32 [H, n, 64, V]; A: fp32 [H, n, 64, 64]; gamma: fp32 [H, n]; S0 (may be
+// null), S_out: fp32 [H, V, 128]; E (may be null), S_hist (may be null): fp32 [H, n, V, 128]; O and VP may be null.
+// V a multiple of 32.
 PEAR_API int pear_gdn_chunk_loop(const float* W, const float* U, const float* Qe, const float* A, const float* Kt, const float* gamma,
-                                 const float* S0, float* O, float* S_out, float* S_hist, int H, int n_chunks, int V, void* stream) {
+                                 const float* S0, const float* E, float* O, float* S_out, float* S_hist, float* VP, int H, int n_chunks,
+                                 int V, void* stream) {
   using namespace pear;
   if (V % kScVs || H <= 0 || n_chunks <= 0) return (int)cudaErrorInvalidValue;
   constexpr int smem = (2 * kScK * kScPad + kScC * kScK + kScC * kScPad + kScK * kScVs + kScC * kScVs) * 4;
@@ -300,7 +317,7 @@ PEAR_API int pear_gdn_chunk_loop(const float* W, const float* U, const float* Qe
     PEAR_CUDA_CHECK(cudaFuncSetAttribute(gdn_chunk_loop_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured = true;
   }
-  gdn_chunk_loop_kernel<<<dim3(H, V / kScVs), 256, smem, (cudaStream_t)stream>>>(W, U, Qe, A, Kt, gamma, S0, O, S_out, S_hist, n_chunks, V);
+  gdn_chunk_loop_kernel<<<dim3(H, V / kScVs), 256, smem, (cudaStream_t)stream>>>(W, U, Qe, A, Kt, gamma, S0, E, O, S_out, S_hist, VP, n_chunks, V);
   PEAR_LAUNCH_CHECK();
   return 0;
 }

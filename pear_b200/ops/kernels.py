@@ -235,24 +235,83 @@ def causal_conv_silu(x, weight, bounds, init_state=None):
     return ref.causal_conv_silu(x, weight, bounds, init_state)
 
 
-USE_SCAN_KERNEL = True  # gradient-free scans on a GPU (rollout prefill, the first pass of a checkpointed layer)
+USE_SCAN_KERNEL = True  # the chunk-by-chunk loop of the delta-rule scan as one kernel launch on a GPU
+
+
+def _chunk_loop(W, U, Qe, A, Kt, gamma, S0, E=None, want_o=True, want_hist=False, want_vp=False):
+    """One launch of ``gdn_chunk_loop_kernel`` over [H, n, 64, *] operands; returns (O, S_out, S_hist, VP)."""
+    hv, n, _, vd = U.shape
+    dev = U.device
+    c = lambda x: None if x is None else x.contiguous().float()
+    W, U, Qe, A, Kt, gamma, S0, E = (c(x) for x in (W, U, Qe, A, Kt, gamma, S0, E))
+    if not U.is_cuda:  # the kernel's statement in torch (CPU tests of the backward derivation)
+        s = S0 if S0 is not None else U.new_zeros(hv, vd, W.shape[-1])
+        outs, hists, vps = [], [], []
+        for i in range(n):
+            hists.append(s)
+            vpi = U[:, i] - torch.einsum("hik,hvk->hiv", W[:, i], s)
+            outs.append(torch.einsum("hik,hvk->hiv", Qe[:, i], s) + torch.einsum("hij,hjv->hiv", A[:, i], vpi))
+            vps.append(vpi)
+            s = s * gamma[:, i][:, None, None] + torch.einsum("hiv,hik->hvk", vpi, Kt[:, i])
+            if E is not None:
+                s = s + E[:, i]
+        return (torch.stack(outs, 1) if want_o else None, s, torch.stack(hists, 1) if want_hist else None,
+                torch.stack(vps, 1) if want_vp else None)
+    o = torch.empty(hv, n, 64, vd, dtype=torch.float32, device=dev) if want_o else None
+    s_out = torch.empty(hv, vd, 128, dtype=torch.float32, device=dev)
+    hist = torch.empty(hv, n, vd, 128, dtype=torch.float32, device=dev) if want_hist else None
+    vp = torch.empty(hv, n, 64, vd, dtype=torch.float32, device=dev) if want_vp else None
+    check(lib().pear_gdn_chunk_loop(ptr(W), ptr(U), ptr(Qe), ptr(A), ptr(Kt), ptr(gamma), ptr(S0), ptr(E), ptr(o), ptr(s_out), ptr(hist),
+                                    ptr(vp), hv, n, vd, stream()), "gdn_chunk_loop")
+    count_launch()
+    return o, s_out, hist, vp
+
+
+class _ScanLoop(torch.autograd.Function):
+    """``v' = U - W S^T; o = Qe S^T + A v'; S <- gamma S + v'^T Kt`` over the chunks of one sequence.
+
+    Backward: with dS the gradient of the state after a chunk, ``dv' = A^T dO + Kt dS^T`` and
+    ``dS_before = gamma dS + dO^T Qe - dv'^T W``: the same recurrence as the forward with W and Kt swapped,
+    ``U' = -A^T dO`` and the additive term ``dO^T Qe``, run over the chunks in reverse by the same kernel; every other
+    gradient is a batched product over all chunks at once of the saved states, v', dS and dv'."""
+
+    @staticmethod
+    def forward(ctx, W, U, Qe, A, Kt, gamma, S0):
+        need = any(ctx.needs_input_grad)
+        o, s_out, hist, vp = _chunk_loop(W, U, Qe, A, Kt, gamma, S0, want_hist=need, want_vp=need)
+        if need:
+            ctx.save_for_backward(W, Qe, A, Kt, gamma, hist, vp)
+        ctx.has_s0 = S0 is not None
+        return o, s_out
+
+    @staticmethod
+    def backward(ctx, dO, dS_out):
+        W, Qe, A, Kt, gamma, hist, vp = ctx.saved_tensors
+        dO = dO.contiguous().float()
+        up = -torch.einsum("hnij,hniv->hnjv", A.float(), dO)
+        e = torch.einsum("hniv,hnik->hnvk", dO, Qe.float())
+        f = lambda x: x.flip(1)
+        _, ds0, dhist_r, vp_r = _chunk_loop(f(Kt), f(up), f(Kt), f(A), f(W), f(gamma), dS_out, E=f(e), want_o=False, want_hist=True,
+                                            want_vp=True)
+        ds_next = f(dhist_r)      # gradient of the state AFTER chunk c
+        dvp = -f(vp_r)
+        dA = torch.einsum("hniv,hnjv->hnij", dO, vp)
+        dQe = torch.einsum("hniv,hnvk->hnik", dO, hist)
+        dKt = torch.einsum("hnjv,hnvk->hnjk", vp, ds_next)
+        dW = -torch.einsum("hnjv,hnvk->hnjk", dvp, hist)
+        dgamma = (ds_next * hist).sum((-1, -2))
+        return dW, dvp, dQe, dA, dKt, dgamma, (ds0 if ctx.has_s0 else None)
 
 
 def gdn_scan(q, k, v, g, beta, state=None):
-    """Chunked delta-rule scan of one sequence. Without gradients on a GPU the chunk-by-chunk loop (64 dependent steps of
-    small products for 4096 tokens) is ONE launch of ``gdn_chunk_loop_kernel``; the chunk-local operands stay batched
-    torch statements."""
-    if (USE_SCAN_KERNEL and q.is_cuda and not torch.is_grad_enabled() and q.shape[2] == 128 and v.shape[2] % 32 == 0
-            and ref.GDN_CHUNK == 64 and q.shape[0] > 0):
+    """Chunked delta-rule scan of one sequence. On a GPU the chunk-by-chunk loop (64 dependent steps of small products
+    for 4096 tokens) is ONE launch of ``gdn_chunk_loop_kernel``, and its backward one more launch of the same kernel
+    plus batched products; the chunk-local operands stay batched torch statements under autograd."""
+    if (USE_SCAN_KERNEL and q.is_cuda and q.shape[2] == 128 and v.shape[2] % 32 == 0 and ref.GDN_CHUNK == 64 and q.shape[0] > 0):
         op = ref.gdn_chunk_operands(q, k, v, g, beta)
         hv, vd, n, t = v.shape[1], v.shape[2], op["n"], op["t"]
-        o = torch.empty(hv, n, 64, vd, dtype=torch.float32, device=q.device)
-        s_out = torch.empty(hv, vd, 128, dtype=torch.float32, device=q.device)
-        s0 = state.float().contiguous() if state is not None else None
-        c = lambda x: x.contiguous()
-        check(lib().pear_gdn_chunk_loop(ptr(c(op["W"])), ptr(c(op["U"])), ptr(c(op["Qe"])), ptr(c(op["A"])), ptr(c(op["Kt"])),
-                                        ptr(c(op["gamma"])), ptr(s0), ptr(o), ptr(s_out), ptr(None), hv, n, vd, stream()), "gdn_chunk_loop")
-        count_launch()
+        s0 = state.float() if state is not None else None
+        o, s_out = _ScanLoop.apply(op["W"], op["U"], op["Qe"], op["A"], op["Kt"], op["gamma"], s0)
         return o.permute(1, 2, 0, 3).reshape(n * 64, hv, vd)[:t], s_out
     return ref.gdn_chunked(q, k, v, g, beta, state)
 

@@ -161,8 +161,6 @@ class TrainEngine:
         self.kernels = kernels
         if kernels is not None:
             kernels.check_config(cfg)
-        if self.device.type == "cuda" and cfg.tf32_matmul:
-            torch.backends.cuda.matmul.allow_tf32 = True
 
         # ---- build: every rank builds the same seeded model, or takes the given weights (rank 0's in a real run)
         model = HybridForCausalLM(model_cfg, with_mtp=with_mtp)
@@ -257,9 +255,19 @@ class TrainEngine:
         def before_rerun():
             self.optimizer.zero_grad(set_to_none=True)
 
-        if self.kernels is not None:
-            return self.kernels.run_checked(run, before_rerun)
-        return run()
+        # fp32 library products of the step (delta-rule scan, attention with gradients) on the TF32 tensor cores; the
+        # process-wide switch is put back afterwards so that nothing else in the process changes precision
+        tf32 = self.device.type == "cuda" and self.cfg.tf32_matmul
+        prev = torch.backends.cuda.matmul.allow_tf32
+        if tf32:
+            torch.backends.cuda.matmul.allow_tf32 = True
+        try:
+            if self.kernels is not None:
+                return self.kernels.run_checked(run, before_rerun)
+            return run()
+        finally:
+            if tf32:
+                torch.backends.cuda.matmul.allow_tf32 = prev
 
     # -- optimizer ----------------------------------------------------------------------------------------------------
     def _grad_norm(self) -> torch.Tensor:

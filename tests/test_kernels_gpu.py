@@ -200,8 +200,17 @@ def test_gdn_chunk_loop_kernel_matches_the_torch_loop_and_the_recurrence():
     assert (o - o_ref).abs().max().item() < 1e-4 and (s - s_ref).abs().max().item() < 1e-4
     o_rec, s_rec = ref.gdn_recurrent(q, k, v, gate, beta, s0)
     assert (o - o_rec).abs().max().item() < 2e-3 and (s - s_rec).abs().max().item() < 2e-3
-    # with gradients the torch loop keeps its autograd graph
-    q.requires_grad_(True)
+    # with gradients: the same kernel run in reverse gives the state gradients; compare with autograd of the torch loop
+    leaves = [x.clone().requires_grad_(True) for x in (q, k, v, gate, beta, s0)]
+    w_o = torch.randn(t, hv, d, device="cuda", generator=g)
+    w_s = torch.randn(hv, d, d, device="cuda", generator=g)
     before = kl.LAUNCH_COUNT
-    K.gdn_scan(q, k, v, gate, beta, s0)[0].sum().backward()
-    assert kl.LAUNCH_COUNT == before and q.grad is not None
+    o1, s1 = K.gdn_scan(*leaves)
+    ((o1 * w_o).sum() + (s1 * w_s).sum()).backward()
+    assert kl.LAUNCH_COUNT == before + 2  # forward loop + reversed loop
+    got = [x.grad.clone() for x in leaves]
+    leaves2 = [x.clone().requires_grad_(True) for x in (q, k, v, gate, beta, s0)]
+    o2, s2 = ref.gdn_chunked(*leaves2)
+    ((o2 * w_o).sum() + (s2 * w_s).sum()).backward()
+    for name, a_, b_ in zip(("q", "k", "v", "g", "beta", "s0"), got, [x.grad for x in leaves2]):
+        assert ((a_ - b_).norm() / (b_.norm() + 1e-12)).item() < 1e-4, name
