@@ -224,15 +224,31 @@ gdn_chunk_loop_kernel(const float* __restrict__ W, const float* __restrict__ U, 
     const float* Qc = Qe + hc * kScC * kScK;
     const float* Kc = Kt + hc * kScC * kScK;
     const float* Ac = A + hc * kScC * kScC;
-    for (int e = tid; e < kScC * kScK; e += 256) {  // coalesced along k; transposed into padded rows
-      const int r = e / kScK, k = e % kScK;
-      Wt[k * kScPad + r] = Wc[e];
-      Qt[k * kScPad + r] = Qc[e];
-      Ks[e] = Kc[e];
+    // coalesced along k, transposed into padded rows; 8 loads of each operand in flight per thread (a dependent
+    // load-store loop would expose the global latency 32 times per chunk)
+#pragma unroll 1
+    for (int e0 = tid; e0 < kScC * kScK; e0 += 256 * 8) {
+      float w8[8], q8[8], k8[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) { w8[u] = Wc[e0 + u * 256]; q8[u] = Qc[e0 + u * 256]; k8[u] = Kc[e0 + u * 256]; }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int e = e0 + u * 256, r = e / kScK, k = e % kScK;
+        Wt[k * kScPad + r] = w8[u];
+        Qt[k * kScPad + r] = q8[u];
+        Ks[e] = k8[u];
+      }
     }
-    for (int e = tid; e < kScC * kScC; e += 256) At[(e % kScC) * kScPad + e / kScC] = Ac[e];
+    {
+      float a8[16];
+#pragma unroll
+      for (int u = 0; u < 16; ++u) a8[u] = Ac[tid + u * 256];
+#pragma unroll
+      for (int u = 0; u < 16; ++u) { const int e = tid + u * 256; At[(e % kScC) * kScPad + e / kScC] = a8[u]; }
+    }
     if (S_hist) {  // the state BEFORE this chunk, for a backward pass
       float* dst = S_hist + (hc * V + vs) * kScK;
+#pragma unroll 8
       for (int e = tid; e < kScVs * kScK; e += 256) dst[e] = St[(e % kScK) * kScVs + e / kScK];
     }
     __syncthreads();
