@@ -65,6 +65,45 @@ def attention_varlen_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_q
     return (out, lse) if return_lse else out
 
 
+class _AttnVarlen(torch.autograd.Function):
+    """Forward on the tcgen05 kernel; backward through the FlashAttention-2 library kernel of the ``flash_attn`` package,
+    fed with this forward's output and log-sum-exp (no own backward kernel yet)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, cu_q, cu_k, max_q, max_k, causal, scale):
+        qb, kb, vb = (x.to(torch.bfloat16).contiguous() for x in (q, k, v))
+        o, lse = attention_varlen_fwd(qb, kb, vb, cu_q, cu_k, causal=causal, scale=scale)
+        ctx.save_for_backward(qb, kb, vb, o, lse, cu_q, cu_k)
+        ctx.args = (max_q, max_k, causal, scale, q.dtype, k.dtype, v.dtype)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        from flash_attn.flash_attn_interface import _flash_attn_varlen_backward
+
+        qb, kb, vb, o, lse, cu_q, cu_k = ctx.saved_tensors
+        max_q, max_k, causal, scale, dq_t, dk_t, dv_t = ctx.args
+        dq, dk, dv = torch.empty_like(qb), torch.empty_like(kb), torch.empty_like(vb)
+        _flash_attn_varlen_backward(do.to(torch.bfloat16).contiguous(), qb, kb, vb, o, lse, dq, dk, dv, cu_q, cu_k, max_q, max_k, 0.0,
+                                    scale, causal, -1, -1, 0.0, None, False)
+        return dq.to(dq_t), dk.to(dk_t), dv.to(dv_t), None, None, None, None, None, None
+
+
+def flash_attn_backward_available() -> bool:
+    try:
+        from flash_attn.flash_attn_interface import _flash_attn_varlen_backward  # noqa: F401
+
+        return True
+    except Exception:
+        return False
+
+
+def attention_varlen(q, k, v, cu_q, cu_k, max_q: int, max_k: int, causal: bool = True, scale: float | None = None) -> torch.Tensor:
+    """Differentiable packed attention, head dimension 256: bf16 output [Tq, Hq, 256]."""
+    scale = 1.0 / math.sqrt(HEAD_DIM) if scale is None else float(scale)
+    return _AttnVarlen.apply(q, k, v, cu_q, cu_k, int(max_q), int(max_k), bool(causal), scale)
+
+
 def attention_varlen_reference(q, k, v, cu_q, cu_k, causal: bool = True, scale: float | None = None):
     """fp32 PyTorch oracle: per sequence, per head, masked softmax(q k^T * scale) v; returns (o fp32, lse fp32 [Hq, Tq])."""
     tq, hq, d = q.shape

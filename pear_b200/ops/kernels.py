@@ -201,18 +201,39 @@ def linear_bf16(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
 # ---------------------------------------------------------------------------------------------------------------------
 # ops still on library kernels
 # ---------------------------------------------------------------------------------------------------------------------
+_CU_CACHE: dict = {}
+
+
+def _cu_tensor(bounds: tuple, device) -> torch.Tensor:
+    """Sequence boundaries as an int32 device tensor; the same boundaries recur for every layer and pass of a batch."""
+    key = (bounds, str(device))
+    t = _CU_CACHE.get(key)
+    if t is None:
+        if len(_CU_CACHE) >= 32:
+            _CU_CACHE.pop(next(iter(_CU_CACHE)))
+        host = torch.tensor(bounds, dtype=torch.int32)
+        t = (host.pin_memory() if torch.cuda.is_available() else host).to(device, non_blocking=True)
+        _CU_CACHE[key] = t
+    return t
+
+
 USE_TCGEN05_ATTENTION = True  # forward passes without gradients on a GPU, head dimension 256
 
 
 def causal_attention(q, k, v, cu_seqlens, scale=None):
-    """Packed causal attention; fp32 [T, Hq, D]. Without gradients on a GPU (the first pass of a checkpointed layer, the
-    old-policy log-prob pass, rollout prefill) the tcgen05 kernel of ``ops/attention.py`` runs on bf16 operands; with
-    gradients the library path keeps its own backward."""
-    if (USE_TCGEN05_ATTENTION and q.is_cuda and q.shape[-1] == 256 and not torch.is_grad_enabled()):
+    """Packed causal attention; fp32 [T, Hq, D]. On a GPU at head dimension 256 the forward is the tcgen05 kernel of
+    ``ops/attention.py`` on bf16 operands; with gradients the backward is the FlashAttention-2 library kernel fed with
+    that forward's output and log-sum-exp (torch SDPA when the package is missing)."""
+    if USE_TCGEN05_ATTENTION and q.is_cuda and q.shape[-1] == 256:
         from . import attention as A
 
-        cu = cu_seqlens if torch.is_tensor(cu_seqlens) else torch.tensor(list(cu_seqlens), dtype=torch.int32)
-        cu = cu.to(device=q.device, dtype=torch.int32)
+        bounds = cu_seqlens.tolist() if torch.is_tensor(cu_seqlens) else list(cu_seqlens)
+        cu = _cu_tensor(tuple(bounds), q.device)
+        if torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad):
+            if A.flash_attn_backward_available():  # own forward, library backward on its output and log-sum-exp
+                longest = max(e - s for s, e in zip(bounds[:-1], bounds[1:]))
+                return A.attention_varlen(q, k, v, cu, cu, longest, longest, True, scale).float()
+            return ref.causal_attention(q, k, v, cu_seqlens, scale)
         o = A.attention_varlen_fwd(q.to(torch.bfloat16).contiguous(), k.to(torch.bfloat16).contiguous(),
                                    v.to(torch.bfloat16).contiguous(), cu, cu, causal=True, scale=scale, return_lse=False)
         return o.float()

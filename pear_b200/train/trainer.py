@@ -16,6 +16,8 @@ The run end cancels background groups (``runner.py:44-53``).
 from __future__ import annotations
 
 import itertools
+import logging
+import os
 import time
 import uuid
 from dataclasses import dataclass
@@ -124,6 +126,30 @@ def micro_batches(rows: list[dict], max_tokens: int) -> list[list[dict]]:
     return [mb for mb in out if mb]
 
 
+_log = logging.getLogger("pear_b200.trainer")
+
+# dense bf16 peak FLOP/s per device name (nominal; a measured peak file beside the package overrides the entry of the GPU
+# the process runs on). Upstream keeps such a table in verl's flops counter (patch 0016: GB300 = 2.5e15).
+DEVICE_PEAK_FLOPS = {"B200": 2.25e15, "GB200": 2.5e15, "GB300": 2.5e15, "H100": 0.989e15, "H200": 0.989e15, "A100": 0.312e15}
+
+
+def device_peak_flops(name: Optional[str] = None) -> float:
+    if name is None:
+        name = torch.cuda.get_device_name(0) if torch.cuda.is_available() else "cpu"
+    measured = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "MEASURED_PEAKS.json")
+    if "B200" in name and os.path.exists(measured):
+        try:
+            import json
+
+            return float(json.load(open(measured))["bf16_tflops_sustained"]) * 1e12
+        except (OSError, KeyError, ValueError):
+            pass
+    for key, val in DEVICE_PEAK_FLOPS.items():
+        if key in name:
+            return val
+    return 1e12  # unknown device (CPU tests): the ratio is then only a scaled throughput
+
+
 class Trainer:
     def __init__(self, cfg: TrainerConfig, engine: TrainEngine, dataset, manager, replay: ReplayBuffer, queue, weight_sync=None,
                  checkpoints=None, log: Optional[Callable[[int, dict], None]] = None, progress: Optional[Callable[[], None]] = None):
@@ -187,7 +213,9 @@ class Trainer:
         mbs = [pack_rows(mb) for mb in micro_batches([rows[i] for i in mine], self.cfg.max_token_len_per_gpu)]
         total_loss_tokens = int(sum(float(r["loss_mask"].sum()) for r in rows))
         stats = {"data/reward_mean": float(np.mean(rewards_all)), "data/sessions": float(len(rows)), "data/tokens": float(sum(lengths)),
-                 "data/response_tokens": float(total_loss_tokens), "data/max_len": float(max(lengths))}
+                 "data/response_tokens": float(total_loss_tokens), "data/max_len": float(max(lengths)),
+                 # whole-context lengths of the trained sessions (prompt + every turn): upstream verl patch 0012
+                 "ctx_total_length/mean": float(np.mean(lengths)), "ctx_total_length/max": float(max(lengths))}
         return mbs, dict(stats, _total_loss_tokens=total_loss_tokens)
 
     def train_step(self) -> dict:
@@ -209,6 +237,15 @@ class Trainer:
             metrics.update(self.weight_sync.sync(self.engine.full_state_dict(torch.float32), self.engine.policy_version))
         metrics.update(stats)
         metrics.update(self.replay.metrics)
+        # model FLOPs utilisation of the trainer ranks against the device table (upstream verl patch 0016 adds its GPU there)
+        tokens = stats.get("data/tokens", 0.0)
+        if t_train > 0 and tokens:
+            ctx = stats["ctx_total_length/mean"] / 2.0
+            flops = 3.0 * self.engine.model_cfg.flops_per_token(context=int(ctx)) * tokens
+            metrics["perf/mfu"] = flops / t_train / (device_peak_flops() * max(1, self.engine.world))
+            metrics["perf/tokens_per_s"] = tokens / t_train
+        for name, secs in (("wait_rollout", t_gen), ("train", t_train)):
+            _log.info("phase %s %.3fs (step %d)", name, secs, self.step)  # one line per timed phase (upstream verl patch 0013)
         metrics.update({"timing/wait_rollout_s": t_gen, "timing/train_s": t_train, "timing/step_s": time.time() - t0,
                         "train/staleness_mean": float(np.mean(stale)) if stale else 0.0, "train/policy_version": float(self.engine.policy_version),
                         "train/inflight_sessions": float(self.replay.inflight_sessions()), "train/session_cap": float(cap or 0)})

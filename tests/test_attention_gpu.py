@@ -72,11 +72,16 @@ def test_model_attention_without_gradients_runs_the_kernel():
     assert kl.LAUNCH_COUNT == before + 1
     want = ref.causal_attention(q, k, v, bounds)
     assert o.dtype == torch.float32 and ((o - want).norm() / want.norm()).item() < 1e-2
-    # with gradients the library path (and its backward) is used
-    q.requires_grad_(True)
+    # with gradients: the same forward kernel, the backward by the FlashAttention-2 library kernel on its output and lse
+    leaves = [x.clone().requires_grad_(True) for x in (q, k, v)]
+    w = torch.randn(400, 8, 256, device=dev, generator=g)
     before = kl.LAUNCH_COUNT
-    K.causal_attention(q, k, v, bounds).sum().backward()
-    assert kl.LAUNCH_COUNT == before and q.grad is not None
+    (K.causal_attention(*leaves, bounds) * w).sum().backward()
+    assert kl.LAUNCH_COUNT == before + 1
+    leaves2 = [x.clone().requires_grad_(True) for x in (q, k, v)]
+    (ref.causal_attention(*leaves2, bounds) * w).sum().backward()
+    for a, b in zip(leaves, leaves2):
+        assert ((a.grad - b.grad).norm() / b.grad.norm()).item() < 2e-2
 
 
 def test_rollout_prefill_at_head_dim_256_goes_through_the_kernel():

@@ -54,6 +54,7 @@ def test_two_steps_checkpoint_and_resume(tmp_path):
         hist = trainer.fit()
         assert len(hist) == 2 and trainer.engine.policy_version == 2
         assert all(np.isfinite(h["actor/grad_norm"]) for h in hist) and "weight_sync/bytes" in hist[0]
+        assert all(h["ctx_total_length/max"] >= h["ctx_total_length/mean"] > 0 and h["perf/mfu"] > 0 and h["perf/tokens_per_s"] > 0 for h in hist)
         # the rollout replica serves the trained policy
         srv = trainer.manager.router.servers[0]
         assert srv.engine.policy_version == 2
