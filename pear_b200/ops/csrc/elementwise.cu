@@ -108,6 +108,46 @@ __global__ void rms_norm_bwd_kernel(const float* __restrict__ dy, const float* _
   }
 }
 
+// Short rows (dim <= 1024: per-head q / k norms): one warp per row, rows strided over a grid of a few CTAs per SM. The
+// weight gradient is summed per CTA in shared memory and flushed with one global atomic per element and CTA (per-row
+// global atomics onto the same few hundred addresses serialise: 2.2 ms for 115 k rows of 256 against ~0.1 ms of traffic).
+__global__ void __launch_bounds__(256) rms_norm_bwd_rows_kernel(const float* __restrict__ dy, const float* __restrict__ r,
+                                                                const float* __restrict__ w, const float* __restrict__ rstd_in,
+                                                                const float* __restrict__ dres, float* __restrict__ dx,
+                                                                float* __restrict__ dw, int rows, int dim, float w_offset) {
+  __shared__ float sdw[1024];
+  const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) sdw[i] = 0.f;
+  __syncthreads();
+  for (int row = blockIdx.x * wpb + (threadIdx.x >> 5); row < rows; row += gridDim.x * wpb) {
+    const size_t base = (size_t)row * dim;
+    const float rstd = rstd_in[row];
+    float dot = 0.f;
+    for (int i = lane * 4; i < dim; i += 128) {
+      const float4 g = *(const float4*)(dy + base + i), v = *(const float4*)(r + base + i), ww = *(const float4*)(w + i);
+      dot += g.x * (ww.x + w_offset) * v.x + g.y * (ww.y + w_offset) * v.y + g.z * (ww.z + w_offset) * v.z +
+             g.w * (ww.w + w_offset) * v.w;
+    }
+    dot = warp_sum(dot);
+    const float c = dot * rstd * rstd / (float)dim;
+    for (int i = lane * 4; i < dim; i += 128) {
+      const float4 g = *(const float4*)(dy + base + i), v = *(const float4*)(r + base + i), ww = *(const float4*)(w + i);
+      float4 o;
+      o.x = rstd * (g.x * (ww.x + w_offset) - v.x * c); o.y = rstd * (g.y * (ww.y + w_offset) - v.y * c);
+      o.z = rstd * (g.z * (ww.z + w_offset) - v.z * c); o.w = rstd * (g.w * (ww.w + w_offset) - v.w * c);
+      if (dres) { const float4 e = *(const float4*)(dres + base + i); o.x += e.x; o.y += e.y; o.z += e.z; o.w += e.w; }
+      *(float4*)(dx + base + i) = o;
+      if (dw) {
+        atomicAdd(sdw + i, g.x * v.x * rstd); atomicAdd(sdw + i + 1, g.y * v.y * rstd);
+        atomicAdd(sdw + i + 2, g.z * v.z * rstd); atomicAdd(sdw + i + 3, g.w * v.w * rstd);
+      }
+    }
+  }
+  __syncthreads();
+  if (dw)
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) atomicAdd(dw + i, sdw[i]);
+}
+
 // ---------------------------------------------------------------------------------------------------------------------
 // Gated RMSNorm over head vectors (dim 128 typical): y = o * rstd * w * silu(z); one warp per row.
 // ---------------------------------------------------------------------------------------------------------------------
@@ -142,21 +182,27 @@ __global__ void gated_rms_norm_bwd_kernel(const float* __restrict__ dy, const fl
                                           const float* __restrict__ z, const float* __restrict__ w,
                                           const float* __restrict__ rstd_in, float* __restrict__ d_o,
                                           float* __restrict__ d_z, float* __restrict__ dw, int rows, int dim) {
-  const int lane = threadIdx.x & 31;
-  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (row >= rows) return;
-  const size_t base = (size_t)row * dim;
-  const float rstd = rstd_in[row];
-  float dot = 0.f;
-  for (int i = lane; i < dim; i += 32) dot += dy[base + i] * w[i] * silu_f(z[base + i]) * o[base + i];
-  dot = warp_sum(dot);
-  const float c = dot * rstd * rstd / (float)dim;
-  for (int i = lane; i < dim; i += 32) {
-    const float g = dy[base + i], ov = o[base + i], zv = z[base + i], sz = silu_f(zv);
-    d_o[base + i] = rstd * (g * w[i] * sz - ov * c);
-    d_z[base + i] = g * ov * rstd * w[i] * dsilu_f(zv);
-    atomicAdd(dw + i, g * ov * rstd * sz);
+  // rows strided over the grid; the weight gradient is summed per CTA in shared memory first (dim <= 1024)
+  __shared__ float sdw[1024];
+  const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) sdw[i] = 0.f;
+  __syncthreads();
+  for (int row = blockIdx.x * wpb + (threadIdx.x >> 5); row < rows; row += gridDim.x * wpb) {
+    const size_t base = (size_t)row * dim;
+    const float rstd = rstd_in[row];
+    float dot = 0.f;
+    for (int i = lane; i < dim; i += 32) dot += dy[base + i] * w[i] * silu_f(z[base + i]) * o[base + i];
+    dot = warp_sum(dot);
+    const float c = dot * rstd * rstd / (float)dim;
+    for (int i = lane; i < dim; i += 32) {
+      const float g = dy[base + i], ov = o[base + i], zv = z[base + i], sz = silu_f(zv);
+      d_o[base + i] = rstd * (g * w[i] * sz - ov * c);
+      d_z[base + i] = g * ov * rstd * w[i] * dsilu_f(zv);
+      atomicAdd(sdw + i, g * ov * rstd * sz);
+    }
   }
+  __syncthreads();
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) atomicAdd(dw + i, sdw[i]);
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -246,8 +292,8 @@ PEAR_API int pear_rms_norm_bwd(const float* dy, const float* r, const float* w, 
   if (dim % 4) return (int)cudaErrorInvalidValue;
   const float off = one_plus ? 1.f : 0.f;
   if (dim <= 1024) {
-    const int wpb = 8;
-    rms_norm_bwd_kernel<true><<<(rows + wpb - 1) / wpb, wpb * 32, 0, (cudaStream_t)stream>>>(dy, r, w, rstd, dres, dx, dw, rows, dim, off);
+    const int wpb = 8, want = (rows + wpb - 1) / wpb, cap = 148 * 8;
+    rms_norm_bwd_rows_kernel<<<want < cap ? want : cap, wpb * 32, 0, (cudaStream_t)stream>>>(dy, r, w, rstd, dres, dx, dw, rows, dim, off);
   } else {
     rms_norm_bwd_kernel<false><<<rows, 256, 0, (cudaStream_t)stream>>>(dy, r, w, rstd, dres, dx, dw, rows, dim, off);
   }
@@ -264,7 +310,9 @@ PEAR_API int pear_gated_rms_norm_fwd(const float* o, const float* z, const float
 }
 PEAR_API int pear_gated_rms_norm_bwd(const float* dy, const float* o, const float* z, const float* w, const float* rstd,
                                      float* d_o, float* d_z, float* dw, int rows, int dim, void* stream) {
-  gated_rms_norm_bwd_kernel<<<(rows + 7) / 8, 256, 0, (cudaStream_t)stream>>>(dy, o, z, w, rstd, d_o, d_z, dw, rows, dim);
+  if (dim > 1024) return (int)cudaErrorInvalidValue;
+  const int want = (rows + 7) / 8, cap = 148 * 8;
+  gated_rms_norm_bwd_kernel<<<want < cap ? want : cap, 256, 0, (cudaStream_t)stream>>>(dy, o, z, w, rstd, d_o, d_z, dw, rows, dim);
   PEAR_LAUNCH_CHECK();
   return 0;
 }

@@ -191,14 +191,18 @@ PEAR_API int pear_gdn_front(const float* x, const float* w, const int* seq_start
 // The backward of this loop is the SAME linear recurrence run over the chunks in reverse with the roles of W and Kt
 // swapped (dS_c = gamma dS_{c+1} + (U' - Kt dS_{c+1}^T)^T W + dO^T Qe with U' = -A^T dO), so one kernel serves both:
 // the optional additive term E, the optional v' output and the optional state history exist for that use.
-// Grid (value head, 32-wide slice of the value dimension): the rows of S (one per value channel) are independent, so
-// four CTAs share a head without talking. fp32 SIMT throughout; S lives in shared memory as St[k][v]. Operands are
+// Grid (value head, 32-wide slice of the value dimension), 512 threads: the rows of S (one per value channel) are
+// independent, so four CTAs share a head without talking. fp32 SIMT throughout; S lives in shared memory as St[k][v]. Operands are
 // staged transposed with padded rows so that a warp reads consecutive words (upstream: cuDNN / FlashInfer sm100 GDN
 // kernels, pear/models/qwen3_5/trainer/blackwell/delta_rule.py:91-161).
 namespace pear {
 constexpr int kScC = 64, kScK = 128, kScVs = 32, kScPad = 65;
 
-__global__ void __launch_bounds__(256, 1)
+constexpr int kScT = 512;                       // threads: 16 warps, four per scheduler, to cover the shared-memory latency
+constexpr int kScV1 = kScVs / (kScT / kScC);    // value channels per thread in steps 1-2 (4)
+constexpr int kScV3 = kScVs / (kScT / kScK);    // value channels per thread in step 3 (8)
+
+__global__ void __launch_bounds__(kScT, 1)
 gdn_chunk_loop_kernel(const float* __restrict__ W, const float* __restrict__ U, const float* __restrict__ Qe, const float* __restrict__ A,
                       const float* __restrict__ Kt, const float* __restrict__ gamma, const float* __restrict__ S0, const float* __restrict__ E,
                       float* __restrict__ O, float* __restrict__ S_out, float* __restrict__ S_hist, float* __restrict__ VP, int n_chunks, int V) {
@@ -211,112 +215,115 @@ gdn_chunk_loop_kernel(const float* __restrict__ W, const float* __restrict__ U, 
   float* vps = St + kScK * kScVs;        // [64 j][32 v]
   const int h = blockIdx.x, vs = blockIdx.y * kScVs, tid = threadIdx.x;
   // state slice: S[h][vs + v][k] -> St[k][v]
-  for (int e = tid; e < kScVs * kScK; e += 256) {
+  for (int e = tid; e < kScVs * kScK; e += kScT) {
     const int v = e / kScK, k = e % kScK;
     St[k * kScVs + v] = S0 ? S0[((size_t)h * V + vs + v) * kScK + k] : 0.f;
   }
   __syncthreads();
-  const int i = tid & 63, vq = tid >> 6;      // steps 1-2: row i of the chunk, 8 value channels vq * 8 ..
-  const int kk = tid & 127, vh = tid >> 7;    // step 3: key channel kk, 16 value channels vh * 16 ..
+  const int i = tid & 63, vq = tid >> 6;      // steps 1-2: row i of the chunk, value channels vq * kScV1 ..
+  const int kk = tid & 127, vh = tid >> 7;    // step 3: key channel kk, value channels vh * kScV3 ..
   for (int c = 0; c < n_chunks; ++c) {
     const size_t hc = (size_t)h * n_chunks + c;
     const float* Wc = W + hc * kScC * kScK;
     const float* Qc = Qe + hc * kScC * kScK;
     const float* Kc = Kt + hc * kScC * kScK;
     const float* Ac = A + hc * kScC * kScC;
+    // small operands of the later steps are requested now, and the next chunk's operands are pulled into L2, so that
+    // their latency hides under this chunk's staging and arithmetic
+    const float4 u0 = *(const float4*)(U + (hc * kScC + i) * V + vs + vq * kScV1);
+    const float gm = gamma[hc];
+    float e8[kScV3];
+#pragma unroll
+    for (int j = 0; j < kScV3; ++j) e8[j] = E ? E[(hc * V + vs + vh * kScV3 + j) * kScK + kk] : 0.f;
+    if (c + 1 < n_chunks) {
+      const size_t nx = hc + 1;
+      if (tid < 256) {  // 3 x 32 KB in 128-byte lines
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(W + nx * kScC * kScK + tid * 32));
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(Qe + nx * kScC * kScK + tid * 32));
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(Kt + nx * kScC * kScK + tid * 32));
+      } else if (tid < 384) {
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(A + nx * kScC * kScC + (tid - 256) * 32));
+      } else if (tid < 448) {
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(U + (nx * kScC + (tid - 384)) * V + vs));
+      }
+    }
     // coalesced along k, transposed into padded rows; 8 loads of each operand in flight per thread (a dependent
-    // load-store loop would expose the global latency 32 times per chunk)
+    // load-store loop would expose the global latency once per iteration)
 #pragma unroll 1
-    for (int e0 = tid; e0 < kScC * kScK; e0 += 256 * 8) {
+    for (int e0 = tid; e0 < kScC * kScK; e0 += kScT * 8) {
       float w8[8], q8[8], k8[8];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) { w8[u] = Wc[e0 + u * 256]; q8[u] = Qc[e0 + u * 256]; k8[u] = Kc[e0 + u * 256]; }
+      for (int u = 0; u < 8; ++u) { w8[u] = Wc[e0 + u * kScT]; q8[u] = Qc[e0 + u * kScT]; k8[u] = Kc[e0 + u * kScT]; }
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
-        const int e = e0 + u * 256, r = e / kScK, k = e % kScK;
+        const int e = e0 + u * kScT, r = e / kScK, k = e % kScK;
         Wt[k * kScPad + r] = w8[u];
         Qt[k * kScPad + r] = q8[u];
         Ks[e] = k8[u];
       }
     }
     {
-      float a8[16];
+      float a8[kScC * kScC / kScT];
 #pragma unroll
-      for (int u = 0; u < 16; ++u) a8[u] = Ac[tid + u * 256];
+      for (int u = 0; u < kScC * kScC / kScT; ++u) a8[u] = Ac[tid + u * kScT];
 #pragma unroll
-      for (int u = 0; u < 16; ++u) { const int e = tid + u * 256; At[(e % kScC) * kScPad + e / kScC] = a8[u]; }
+      for (int u = 0; u < kScC * kScC / kScT; ++u) { const int e = tid + u * kScT; At[(e % kScC) * kScPad + e / kScC] = a8[u]; }
     }
     if (S_hist) {  // the state BEFORE this chunk, for a backward pass
       float* dst = S_hist + (hc * V + vs) * kScK;
 #pragma unroll 8
-      for (int e = tid; e < kScVs * kScK; e += 256) dst[e] = St[(e % kScK) * kScVs + e / kScK];
+      for (int e = tid; e < kScVs * kScK; e += kScT) dst[e] = St[(e % kScK) * kScVs + e / kScK];
     }
     __syncthreads();
     // 1. v' = U - W S^T and the state part of the output, Qe S^T
-    float wv[8], ov[8];
+    float wv[kScV1], ov[kScV1];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) wv[j] = ov[j] = 0.f;
-#pragma unroll 4
+    for (int j = 0; j < kScV1; ++j) wv[j] = ov[j] = 0.f;
+#pragma unroll 8
     for (int k = 0; k < kScK; ++k) {
       const float w = Wt[k * kScPad + i], q = Qt[k * kScPad + i];
-      const float4 s0 = *(const float4*)(St + k * kScVs + vq * 8), s1 = *(const float4*)(St + k * kScVs + vq * 8 + 4);
-      const float s[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
-#pragma unroll
-      for (int j = 0; j < 8; ++j) { wv[j] += w * s[j]; ov[j] += q * s[j]; }
+      const float4 s0 = *(const float4*)(St + k * kScVs + vq * kScV1);
+      wv[0] += w * s0.x; wv[1] += w * s0.y; wv[2] += w * s0.z; wv[3] += w * s0.w;
+      ov[0] += q * s0.x; ov[1] += q * s0.y; ov[2] += q * s0.z; ov[3] += q * s0.w;
     }
-    const float* Uc = U + (hc * kScC + i) * V + vs + vq * 8;
-    const float4 u0 = *(const float4*)Uc, u1 = *(const float4*)(Uc + 4);
-    const float u[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
-#pragma unroll
-    for (int j = 0; j < 8; ++j) vps[i * kScVs + vq * 8 + j] = u[j] - wv[j];
-    if (VP) {
-      float* Vc = VP + (hc * kScC + i) * V + vs + vq * 8;
-      *(float4*)Vc = make_float4(u[0] - wv[0], u[1] - wv[1], u[2] - wv[2], u[3] - wv[3]);
-      *(float4*)(Vc + 4) = make_float4(u[4] - wv[4], u[5] - wv[5], u[6] - wv[6], u[7] - wv[7]);
-    }
+    const float4 vp4 = make_float4(u0.x - wv[0], u0.y - wv[1], u0.z - wv[2], u0.w - wv[3]);
+    *(float4*)(vps + i * kScVs + vq * kScV1) = vp4;
+    if (VP) *(float4*)(VP + (hc * kScC + i) * V + vs + vq * kScV1) = vp4;
     __syncthreads();
     // 2. o = Qe S^T + A v' (skipped when the caller wants the states only)
     if (O) {
-#pragma unroll 4
+#pragma unroll 8
       for (int j = 0; j < kScC; ++j) {
         const float a = At[j * kScPad + i];
-        const float4 p0 = *(const float4*)(vps + j * kScVs + vq * 8), p1 = *(const float4*)(vps + j * kScVs + vq * 8 + 4);
+        const float4 p0 = *(const float4*)(vps + j * kScVs + vq * kScV1);
         ov[0] += a * p0.x; ov[1] += a * p0.y; ov[2] += a * p0.z; ov[3] += a * p0.w;
-        ov[4] += a * p1.x; ov[5] += a * p1.y; ov[6] += a * p1.z; ov[7] += a * p1.w;
       }
-      float* Oc = O + (hc * kScC + i) * V + vs + vq * 8;
-      *(float4*)Oc = make_float4(ov[0], ov[1], ov[2], ov[3]);
-      *(float4*)(Oc + 4) = make_float4(ov[4], ov[5], ov[6], ov[7]);
+      *(float4*)(O + (hc * kScC + i) * V + vs + vq * kScV1) = make_float4(ov[0], ov[1], ov[2], ov[3]);
     }
-    // 3. S <- gamma S + v'^T Kt (every thread owns St[kk][vh * 16 .. + 15]; nobody reads St before the next barrier pair)
-    const float gm = gamma[hc];
-    float acc[16];
+    // 3. S <- gamma S + v'^T Kt (every thread owns St[kk][vh * 8 .. + 7]; nobody reads St before the next barrier pair)
+    float acc[kScV3];
 #pragma unroll
-    for (int j = 0; j < 16; ++j) acc[j] = 0.f;
-#pragma unroll 2
+    for (int j = 0; j < kScV3; ++j) acc[j] = 0.f;
+#pragma unroll 4
     for (int r = 0; r < kScC; ++r) {
       const float kt = Ks[r * kScK + kk];
-#pragma unroll
-      for (int j4 = 0; j4 < 4; ++j4) {
-        const float4 p = *(const float4*)(vps + r * kScVs + vh * 16 + j4 * 4);
-        acc[j4 * 4] += kt * p.x; acc[j4 * 4 + 1] += kt * p.y; acc[j4 * 4 + 2] += kt * p.z; acc[j4 * 4 + 3] += kt * p.w;
-      }
+      const float4 p = *(const float4*)(vps + r * kScVs + vh * kScV3), p2 = *(const float4*)(vps + r * kScVs + vh * kScV3 + 4);
+      acc[0] += kt * p.x; acc[1] += kt * p.y; acc[2] += kt * p.z; acc[3] += kt * p.w;
+      acc[4] += kt * p2.x; acc[5] += kt * p2.y; acc[6] += kt * p2.z; acc[7] += kt * p2.w;
     }
-    if (E) {  // additive term of the state update (the reversed scan of the backward pass: dO^T Qe)
-      const float* Ec = E + (hc * V + vs + vh * 16) * kScK + kk;
 #pragma unroll
-      for (int j = 0; j < 16; ++j) acc[j] += Ec[(size_t)j * kScK];
-    }
+    for (int j = 0; j < kScV3; ++j) acc[j] += e8[j];  // additive term of the state update (reversed scan of the backward: dO^T Qe)
     __syncthreads();  // every thread has finished reading St (step 1) and vps before they change
 #pragma unroll
-    for (int j = 0; j < 16; ++j) St[kk * kScVs + vh * 16 + j] = gm * St[kk * kScVs + vh * 16 + j] + acc[j];
+    for (int j = 0; j < kScV3; ++j) St[kk * kScVs + vh * kScV3 + j] = gm * St[kk * kScVs + vh * kScV3 + j] + acc[j];
     __syncthreads();
   }
-  for (int e = tid; e < kScVs * kScK; e += 256) {
+  for (int e = tid; e < kScVs * kScK; e += kScT) {
     const int v = e / kScK, k = e % kScK;
     S_out[((size_t)h * V + vs + v) * kScK + k] = St[k * kScVs + v];
   }
 }
+static_assert(kScV1 == 4 && kScV3 == 8, "the unrolled accumulators above are written for 512 threads");
 }  // namespace pear
 
 // W, Qe, Kt: fp32 [H, n, 64, 128]; U, O, VP: fp32 [H, n, 64, V]; A: fp32 [H, n, 64, 64]; gamma: fp32 [H, n]; S0 (may be
@@ -333,7 +340,7 @@ PEAR_API int pear_gdn_chunk_loop(const float* W, const float* U, const float* Qe
     PEAR_CUDA_CHECK(cudaFuncSetAttribute(gdn_chunk_loop_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured = true;
   }
-  gdn_chunk_loop_kernel<<<dim3(H, V / kScVs), 256, smem, (cudaStream_t)stream>>>(W, U, Qe, A, Kt, gamma, S0, E, O, S_out, S_hist, VP, n_chunks, V);
+  gdn_chunk_loop_kernel<<<dim3(H, V / kScVs), kScT, smem, (cudaStream_t)stream>>>(W, U, Qe, A, Kt, gamma, S0, E, O, S_out, S_hist, VP, n_chunks, V);
   PEAR_LAUNCH_CHECK();
   return 0;
 }
