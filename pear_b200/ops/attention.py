@@ -65,6 +65,28 @@ def attention_varlen_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_q
     return (out, lse) if return_lse else out
 
 
+# Retained attention outputs of a checkpointed layer (upstream verl patch 0026): the graph-free first pass RECORDS the
+# output and log-sum-exp of every attention call of the layer, the recompute pass of the backward REPLAYS them instead of
+# running the forward kernel again (q, k, v are recomputed by the projections either way).
+_RETAIN: dict = {"mode": None, "store": None}
+
+
+class retain_attention:
+    """``with retain_attention("record", box)`` / ``with retain_attention("replay", box)``; ``box`` is a list owned by
+    the caller (one per checkpointed layer call)."""
+
+    def __init__(self, mode: str, box: list):
+        self.mode, self.box = mode, box
+
+    def __enter__(self):
+        self.prev = dict(_RETAIN)
+        _RETAIN["mode"], _RETAIN["store"] = self.mode, self.box
+        return self.box
+
+    def __exit__(self, *exc):
+        _RETAIN.update(self.prev)
+
+
 class _AttnVarlen(torch.autograd.Function):
     """Forward on the tcgen05 kernel; backward through the FlashAttention-2 library kernel of the ``flash_attn`` package,
     fed with this forward's output and log-sum-exp (no own backward kernel yet)."""
@@ -72,7 +94,10 @@ class _AttnVarlen(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, cu_q, cu_k, max_q, max_k, causal, scale):
         qb, kb, vb = (x.to(torch.bfloat16).contiguous() for x in (q, k, v))
-        o, lse = attention_varlen_fwd(qb, kb, vb, cu_q, cu_k, causal=causal, scale=scale)
+        if _RETAIN["mode"] == "replay" and _RETAIN["store"]:
+            o, lse = _RETAIN["store"].pop(0)
+        else:
+            o, lse = attention_varlen_fwd(qb, kb, vb, cu_q, cu_k, causal=causal, scale=scale)
         ctx.save_for_backward(qb, kb, vb, o, lse, cu_q, cu_k)
         ctx.args = (max_q, max_k, causal, scale, q.dtype, k.dtype, v.dtype)
         return o

@@ -234,9 +234,13 @@ def causal_attention(q, k, v, cu_seqlens, scale=None):
                 longest = max(e - s for s, e in zip(bounds[:-1], bounds[1:]))
                 return A.attention_varlen(q, k, v, cu, cu, longest, longest, True, scale).float()
             return ref.causal_attention(q, k, v, cu_seqlens, scale)
-        o = A.attention_varlen_fwd(q.to(torch.bfloat16).contiguous(), k.to(torch.bfloat16).contiguous(),
-                                   v.to(torch.bfloat16).contiguous(), cu, cu, causal=True, scale=scale, return_lse=False)
-        return o.float()
+        record = A._RETAIN["mode"] == "record" and A.flash_attn_backward_available()
+        res = A.attention_varlen_fwd(q.to(torch.bfloat16).contiguous(), k.to(torch.bfloat16).contiguous(),
+                                     v.to(torch.bfloat16).contiguous(), cu, cu, causal=True, scale=scale, return_lse=record)
+        if record:  # first pass of a checkpointed layer: keep output and log-sum-exp for the recompute pass
+            A._RETAIN["store"].append(res)
+            return res[0].float()
+        return res.float()
     return ref.causal_attention(q, k, v, cu_seqlens, scale)
 
 

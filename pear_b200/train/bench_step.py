@@ -40,11 +40,13 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--vocab", type=int, default=32768)
+    ap.add_argument("--retain-attention", action="store_true", help="keep attention outputs from the first pass of a checkpointed layer")
     ap.add_argument("--breakdown", type=int, default=0, help="after the timed steps, run one step under the torch profiler and "
                     "print the N kernels with the most device time (stderr)")
     a = ap.parse_args()
     cfg = HybridConfig(num_layers=a.layers, vocab_size=a.vocab)  # the 27B per-layer shape
-    ecfg = EngineConfig(lr=1e-6, param_dtype="bf16", enable_gradient_checkpointing=True, topk_log_probs=0)
+    ecfg = EngineConfig(lr=1e-6, param_dtype="bf16", enable_gradient_checkpointing=True, topk_log_probs=0,
+                        gradient_checkpointing_retain_attention=a.retain_attention)
     eng = TrainEngine(cfg, ecfg, device="cuda", seed=0)
     batches = [synthetic_batch(cfg, a.tokens, a.seqs, 0, s).to("cuda") for s in range(2)]
 

@@ -17,10 +17,12 @@ import torch
 class LayerRunner:
     """Callable ``(index, layer, residual, meta) -> residual`` installed on the model as ``layer_runner``."""
 
-    def __init__(self, sharded=None, offload=None, checkpoint: bool = True):
+    def __init__(self, sharded=None, offload=None, checkpoint: bool = True, retain_attention: bool = False):
         self.sharded = sharded
         self.offload = offload
         self.checkpoint = checkpoint
+        # keep the attention outputs of the graph-free pass for the recompute pass (GPU attention kernel only)
+        self.retain_attention = retain_attention
         self.last_micro_batch = True
 
     def unit(self, i: int):
@@ -46,8 +48,15 @@ class _CheckpointedLayer(torch.autograd.Function):
         u = runner.unit(i)
         if u is not None:
             u.gather()
+        ctx.attn_box = [] if runner.retain_attention else None
         with torch.no_grad():
-            out = layer(r, meta)
+            if ctx.attn_box is not None:
+                from ..ops.attention import retain_attention
+
+                with retain_attention("record", ctx.attn_box):
+                    out = layer(r, meta)
+            else:
+                out = layer(r, meta)
         if u is not None:
             u.release()
         ctx.runner, ctx.i, ctx.layer, ctx.meta = runner, i, layer, meta
@@ -72,7 +81,13 @@ class _CheckpointedLayer(torch.autograd.Function):
             r = ctx.saved
         r = r.detach().requires_grad_(True)
         with torch.enable_grad():
-            out = layer(r, meta)
+            if ctx.attn_box:
+                from ..ops.attention import retain_attention
+
+                with retain_attention("replay", ctx.attn_box):
+                    out = layer(r, meta)
+            else:
+                out = layer(r, meta)
         torch.autograd.backward(out, grad_out)
         if u is not None:
             u.reduce_grads(runner.last_micro_batch)

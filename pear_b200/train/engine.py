@@ -101,6 +101,7 @@ class EngineConfig:
     fp32_modules: list = field(default_factory=list)
     ulysses_sequence_parallel_size: int = 1
     enable_gradient_checkpointing: bool = True
+    gradient_checkpointing_retain_attention: bool = False
     enable_activation_offload: bool = False
     streamed_adamw: bool = False
     streamed_chunk_bytes: int = 2 << 30
@@ -129,6 +130,7 @@ class EngineConfig:
             ulysses_sequence_parallel_size=int(fs.ulysses_sequence_parallel_size),
             enable_gradient_checkpointing=bool(model.enable_gradient_checkpointing),
             enable_activation_offload=bool(model.get("enable_activation_offload", False)),
+            gradient_checkpointing_retain_attention=bool(model.get("gradient_checkpointing_retain_attention", False)),
             streamed_adamw=bool(fs.get("streamed_adamw", False) or fs.get("optimizer_offload", False)),
             temperature=float(rollout.temperature), topk_log_probs=int(rollout.get("topk_log_probs", 0)),
             loss=grpo.LossConfig(loss_agg_mode=actor.loss_agg_mode, score_centering=bool(rc.score_centering),
@@ -182,7 +184,8 @@ class TrainEngine:
         self.sharded = ShardedModel(model, world_group if self.world > 1 else None, replicate_group, dtype, cfg.fp32_modules,
                                     self.device)
         self.offload = CheckpointInputOffload(True) if cfg.enable_activation_offload else None
-        self.runner = LayerRunner(self.sharded, self.offload, cfg.enable_gradient_checkpointing)
+        self.runner = LayerRunner(self.sharded, self.offload, cfg.enable_gradient_checkpointing,
+                                  retain_attention=cfg.gradient_checkpointing_retain_attention)
         install_runner(model, self.runner)
         opt_cls = StreamedAdamW if cfg.streamed_adamw else torch.optim.AdamW
         kw = dict(lr=cfg.lr, betas=cfg.betas, eps=cfg.eps, weight_decay=cfg.weight_decay)

@@ -25,3 +25,28 @@ def test_one_training_step_on_gpu(tmp_path):
         assert kl.LAUNCH_COUNT > before, "the step must run this library's kernels, not a fallback"
     finally:
         close()
+
+
+def test_retained_attention_outputs_give_the_same_gradients():
+    """A checkpointed attention layer that replays the first pass's attention output in its recompute pass has the
+    gradients of one that recomputes it, and launches one attention kernel less."""
+    import torch
+
+    from pear_b200.models.config import HybridConfig
+    from pear_b200.ops import lib as kl
+    from pear_b200.train.bench_step import synthetic_batch
+    from pear_b200.train.engine import EngineConfig, TrainEngine
+
+    cfg = HybridConfig(vocab_size=2048, hidden_size=512, num_layers=4, num_attention_heads=4, num_kv_heads=1, head_dim=256, rotary_dim=64,
+                       gdn_qk_heads=2, gdn_v_heads=4, gdn_head_dim=128, intermediate_size=1024, num_mtp_layers=0)
+    grads, launches = {}, {}
+    for retain in (False, True):
+        eng = TrainEngine(cfg, EngineConfig(lr=1e-6, param_dtype="bf16", enable_gradient_checkpointing=True, topk_log_probs=0,
+                                            gradient_checkpointing_retain_attention=retain), device="cuda", seed=0)
+        batch = synthetic_batch(cfg, 512, 2, 0, 0).to("cuda")
+        before = kl.LAUNCH_COUNT
+        eng.forward_backward_batch([batch])
+        launches[retain] = kl.LAUNCH_COUNT - before
+        grads[retain] = torch.cat([p.grad.float().flatten() for p in eng.sharded.parameters() if p.grad is not None])
+    assert launches[True] == launches[False] - 1  # one attention layer: its recompute pass skipped the forward kernel
+    assert ((grads[True] - grads[False]).norm() / grads[False].norm()).item() < 1e-5
