@@ -162,3 +162,35 @@ PEAR_API int pear_adamw_bcast(const float* reduced, float* master, float* m, flo
   PEAR_LAUNCH_CHECK();
   return 0;
 }
+
+// ------------------------------------------------------------------------------------------------ local fused AdamW
+// One pass over a parameter tensor: p, m, v read and written once, the gradient read once (torch's AdamW statements make
+// about a dozen passes). The gradient may be fp32 or bf16; `grad_scale` carries the clip coefficient.
+namespace pear {
+template <bool G_BF16>
+__global__ void __launch_bounds__(256) adamw_local_kernel(float* __restrict__ p, const void* __restrict__ g, float* __restrict__ m,
+                                                          float* __restrict__ v, size_t n, float lr, float beta1, float beta2, float eps,
+                                                          float weight_decay, float bias1, float bias2, float grad_scale) {
+  const float step = lr / bias1, inv_sqrt_b2 = rsqrtf(bias2), decay = 1.f - lr * weight_decay;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const float gi = (G_BF16 ? __bfloat162float(((const __nv_bfloat16*)g)[i]) : ((const float*)g)[i]) * grad_scale;
+    const float mi = beta1 * m[i] + (1.f - beta1) * gi;
+    const float vi = beta2 * v[i] + (1.f - beta2) * gi * gi;
+    m[i] = mi;
+    v[i] = vi;
+    p[i] = p[i] * decay - step * mi / (sqrtf(vi) * inv_sqrt_b2 + eps);
+  }
+}
+}  // namespace pear
+
+PEAR_API int pear_adamw_local(float* p, const void* g, int grad_bf16, float* m, float* v, size_t n, float lr, float beta1, float beta2,
+                              float eps, float weight_decay, float bias1, float bias2, float grad_scale, void* stream) {
+  using namespace pear;
+  if (n == 0) return 0;
+  const size_t want = (n + 255) / 256;
+  const int grid = (int)(want < 148 * 16 ? want : 148 * 16);
+  if (grad_bf16) adamw_local_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>(p, g, m, v, n, lr, beta1, beta2, eps, weight_decay, bias1, bias2, grad_scale);
+  else adamw_local_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>(p, g, m, v, n, lr, beta1, beta2, eps, weight_decay, bias1, bias2, grad_scale);
+  PEAR_LAUNCH_CHECK();
+  return 0;
+}

@@ -28,6 +28,7 @@ from ..parallel.ulysses import SequenceParallel
 from . import grpo
 from .checkpointing import LayerRunner, install as install_runner
 from .offload import CheckpointInputOffload
+from .fused_adamw import FusedAdamW
 from .streamed_adamw import StreamedAdamW
 
 
@@ -115,6 +116,7 @@ class EngineConfig:
     # fp32 matrix products left to the library on a GPU (the chunked delta-rule scan, attention with gradients) run on
     # the TF32 tensor cores instead of SIMT fp32; the head's logits do not (split-bf16 GEMM, close to fp32)
     tf32_matmul: bool = True
+    fused_adamw: bool = True  # on a GPU: one kernel pass per parameter tensor instead of torch's AdamW statements
 
     @classmethod
     def from_config(cls, cfg) -> "EngineConfig":
@@ -187,11 +189,12 @@ class TrainEngine:
         self.runner = LayerRunner(self.sharded, self.offload, cfg.enable_gradient_checkpointing,
                                   retain_attention=cfg.gradient_checkpointing_retain_attention)
         install_runner(model, self.runner)
-        opt_cls = StreamedAdamW if cfg.streamed_adamw else torch.optim.AdamW
+        self.fused_adamw = (not cfg.streamed_adamw) and self.device.type == "cuda" and cfg.fused_adamw
+        opt_cls = StreamedAdamW if cfg.streamed_adamw else (FusedAdamW if self.fused_adamw else torch.optim.AdamW)
         kw = dict(lr=cfg.lr, betas=cfg.betas, eps=cfg.eps, weight_decay=cfg.weight_decay)
         if cfg.streamed_adamw:
             kw["chunk_bytes"] = cfg.streamed_chunk_bytes
-        else:
+        elif not self.fused_adamw:
             kw.update(foreach=False, fused=False)
         self.optimizer = opt_cls(self.sharded.parameters(), **kw)
         self.step_count = 0
@@ -292,13 +295,15 @@ class TrainEngine:
             self.optimizer.zero_grad(set_to_none=True)
             metrics["actor/skipped_update"] = 1.0
             return metrics
-        if self.cfg.clip_grad > 0:
-            scale = min(1.0, self.cfg.clip_grad / (float(norm) + 1e-6))
+        scale = min(1.0, self.cfg.clip_grad / (float(norm) + 1e-6)) if self.cfg.clip_grad > 0 else 1.0
+        if self.fused_adamw:
+            self.optimizer.step(grad_scale=scale)  # the clip coefficient rides in the update's single pass
+        else:
             if scale < 1.0:
                 for p in self.sharded.parameters():
                     if p.grad is not None:
                         p.grad.mul_(scale)
-        self.optimizer.step()
+            self.optimizer.step()
         self.optimizer.zero_grad(set_to_none=True)
         self.step_count += 1
         self.policy_version += 1

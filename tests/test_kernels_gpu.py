@@ -214,3 +214,30 @@ def test_gdn_chunk_loop_kernel_matches_the_torch_loop_and_the_recurrence():
     ((o2 * w_o).sum() + (s2 * w_s).sum()).backward()
     for name, a_, b_ in zip(("q", "k", "v", "g", "beta", "s0"), got, [x.grad for x in leaves2]):
         assert ((a_ - b_).norm() / (b_.norm() + 1e-12)).item() < 1e-4, name
+
+
+def test_fused_adamw_kernel_matches_torch_adamw():
+    from pear_b200.ops import lib as kl
+    from pear_b200.train.fused_adamw import FusedAdamW
+
+    def run(opt_cls, grad_dtype, **kw):
+        g = torch.Generator(device="cuda").manual_seed(0)
+        ps = [torch.nn.Parameter(torch.randn(1000, 37, device="cuda", generator=g)), torch.nn.Parameter(torch.randn(13, device="cuda", generator=g))]
+        opt = opt_cls(ps, lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, **kw)
+        for _ in range(3):
+            for x in ps:
+                gr = torch.randn(x.shape, device="cuda", generator=g).to(grad_dtype)
+                x.grad = gr if opt_cls is FusedAdamW else gr.float() * 0.5
+            if opt_cls is FusedAdamW:
+                opt.step(grad_scale=0.5)
+            else:
+                opt.step()
+        return [x.detach().clone() for x in ps]
+
+    for gd in (torch.float32,):  # torch keeps a parameter's gradient in the parameter's dtype
+        before = kl.LAUNCH_COUNT
+        a = run(FusedAdamW, gd)
+        assert kl.LAUNCH_COUNT == before + 6
+        b = run(torch.optim.AdamW, gd, foreach=False, fused=False)
+        for x, y in zip(a, b):
+            assert torch.allclose(x, y, atol=1e-6, rtol=1e-5), (x - y).abs().max()
