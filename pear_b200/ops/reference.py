@@ -189,20 +189,19 @@ def gdn_chunk_operands(q, k, v, g, beta, chunk: int = GDN_CHUNK):
     pad = (-t) % chunk
     n = (t + pad) // chunk
 
-    def prep(x, heads_first_rep=False):
+    def prep(x):
         x = x.float()
-        if heads_first_rep:
-            x = x.repeat_interleave(rep, dim=1)
         if pad:
             x = torch.cat([x, x.new_zeros((pad,) + x.shape[1:])], dim=0)
         return x
 
-    qf, kf = prep(q, True), prep(k, True)  # [Tp, Hv, K]
+    # q and k stay at their own head count: the value heads of a group share them, so the products over the key
+    # dimension are taken once per q/k head and every per-value-head factor is applied by broadcasting
+    qf, kf = prep(q), prep(k)  # [Tp, Hk, K]
     vf, gf, bf = prep(v), prep(g), prep(beta)  # padding: g = 0, beta = 0, k = 0 -> no state change
-    # -> [Hv, n, C, *]
-    qc = qf.view(n, chunk, hv, kd).permute(2, 0, 1, 3)
-    kc = kf.view(n, chunk, hv, kd).permute(2, 0, 1, 3)
-    vc = vf.view(n, chunk, hv, vd).permute(2, 0, 1, 3)
+    qc = qf.view(n, chunk, hk, kd).permute(2, 0, 1, 3)  # [Hk, n, C, K]
+    kc = kf.view(n, chunk, hk, kd).permute(2, 0, 1, 3)
+    vc = vf.view(n, chunk, hv, vd).permute(2, 0, 1, 3)  # [Hv, n, C, V]
     gc = gf.view(n, chunk, hv).permute(2, 0, 1)
     bc = bf.view(n, chunk, hv).permute(2, 0, 1)
     G = gc.cumsum(-1)  # [Hv, n, C]
@@ -211,17 +210,27 @@ def gdn_chunk_operands(q, k, v, g, beta, chunk: int = GDN_CHUNK):
     lower_strict = (idx[:, None] > idx[None, :])
     lower = (idx[:, None] >= idx[None, :])
     decay = torch.exp(diff.masked_fill(~lower, 0.0)) * lower  # exp only where i >= j
-    kk = torch.einsum("hnik,hnjk->hnij", kc, kc)
+
+    def per_value_head(x_hk, scale_hv):
+        """x_hk [Hk, n, C, D] times a per-value-head factor [Hv, n, C] -> [Hv, n, C, D] without a repeated copy of x."""
+        return (x_hk[:, None] * scale_hv.reshape(hk, rep, n, chunk, 1)).reshape(hv, n, chunk, x_hk.shape[-1])
+
+    def spread(m_hk):
+        """[Hk, n, C, C] -> a [Hv, n, C, C] view-like expansion (small: C x C per chunk)."""
+        return m_hk[:, None].expand(hk, rep, n, chunk, chunk).reshape(hv, n, chunk, chunk)
+
+    kk = spread(torch.einsum("hnik,hnjk->hnij", kc, kc))
     L = bc[..., :, None] * kk * decay * lower_strict
     eye = torch.eye(chunk, device=q.device, dtype=torch.float32)
     eG = torch.exp(G)
-    rhs = torch.cat([bc[..., None] * kc * eG[..., None], bc[..., None] * vc], dim=-1)  # [Hv, n, C, K+V]
+    rhs = torch.cat([per_value_head(kc, bc * eG), bc[..., None] * vc], dim=-1)  # [Hv, n, C, K+V]
     WU = torch.linalg.solve_triangular(eye + L, rhs, upper=False, unitriangular=True)
     W, U = WU[..., :kd], WU[..., kd:]
-    qk = torch.einsum("hnik,hnjk->hnij", qc, kc) * decay
+    qk = spread(torch.einsum("hnik,hnjk->hnij", qc, kc)) * decay
     G_last = G[..., -1]
-    k_tail = kc * torch.exp(G_last[..., None] - G)[..., None]  # k e^(G_C - G)
-    return {"W": W, "U": U, "Qe": qc * eG[..., None], "A": qk, "Kt": k_tail, "gamma": torch.exp(G_last), "n": n, "t": t}
+    k_tail = per_value_head(kc, torch.exp(G_last[..., None] - G))  # k e^(G_C - G)
+    Qe = per_value_head(qc, eG)
+    return {"W": W, "U": U, "Qe": Qe, "A": qk, "Kt": k_tail, "gamma": torch.exp(G_last), "n": n, "t": t}
 
 
 def gdn_chunked(q, k, v, g, beta, state: torch.Tensor | None = None, chunk: int = GDN_CHUNK):
