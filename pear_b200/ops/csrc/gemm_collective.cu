@@ -236,11 +236,14 @@ gemm_coll_kernel(const __grid_constant__ MapSet maps, const __grid_constant__ CU
 #pragma unroll
             for (int j = 0; j < 32; ++j) tb[lane * 33 + j] = __uint_as_float(r[j]);
             __syncwarp();
+            // the staged partials are bf16 (half the NVLink bytes and half the owner's re-read; the sum itself stays fp32)
             const int lrow0 = (m0 - owner * m_local) + q * 32;
-            float* dst0 = outs.p[owner] + ((size_t)rank * m_local + lrow0) * ldc + col;
-            if (col + lane < N) {
+            __nv_bfloat16* dst0 = (__nv_bfloat16*)outs.p[owner] + ((size_t)rank * m_local + lrow0) * ldc + col;
+            const int hr = lane >> 4, cc = (lane & 15) * 2;
+            if (col + cc + 1 < N) {
 #pragma unroll 4
-              for (int rr = 0; rr < 32; ++rr) dst0[(size_t)rr * ldc + lane] = tb[rr * 33 + lane];
+              for (int rr = 0; rr < 32; rr += 2)
+                *(__nv_bfloat162*)(dst0 + (size_t)(rr + hr) * ldc + cc) = __floats2bfloat162_rn(tb[(rr + hr) * 33 + cc], tb[(rr + hr) * 33 + cc + 1]);
             }
             __syncwarp();
           } else {
@@ -248,19 +251,22 @@ gemm_coll_kernel(const __grid_constant__ MapSet maps, const __grid_constant__ CU
             float* dst = (float*)c + (size_t)lrow * ldc + col;
             for (int s2 = 1; s2 < world; ++s2) {
               const int src = (rank + s2) % world;
-              const float* ps = outs.p[rank] + ((size_t)src * m_local + lrow) * ldc + col;
+              const __nv_bfloat16* ps = (const __nv_bfloat16*)outs.p[rank] + ((size_t)src * m_local + lrow) * ldc + col;
               if (col + 32 <= N) {
 #pragma unroll
-                for (int j = 0; j < 32; j += 4) {
-                  const float4 v = __ldcg((const float4*)(ps + j));
-                  r[j] = __float_as_uint(__uint_as_float(r[j]) + v.x);
-                  r[j + 1] = __float_as_uint(__uint_as_float(r[j + 1]) + v.y);
-                  r[j + 2] = __float_as_uint(__uint_as_float(r[j + 2]) + v.z);
-                  r[j + 3] = __float_as_uint(__uint_as_float(r[j + 3]) + v.w);
+                for (int j = 0; j < 32; j += 8) {
+                  const uint4 v = __ldcg((const uint4*)(ps + j));
+                  const __nv_bfloat162* h2 = (const __nv_bfloat162*)&v;
+#pragma unroll
+                  for (int u = 0; u < 4; ++u) {
+                    const float2 f = __bfloat1622float2(h2[u]);
+                    r[j + 2 * u] = __float_as_uint(__uint_as_float(r[j + 2 * u]) + f.x);
+                    r[j + 2 * u + 1] = __float_as_uint(__uint_as_float(r[j + 2 * u + 1]) + f.y);
+                  }
                 }
               } else {
                 for (int j = 0; j < 32; ++j)
-                  if (col + j < N) r[j] = __float_as_uint(__uint_as_float(r[j]) + __ldcg(ps + j));
+                  if (col + j < N) r[j] = __float_as_uint(__uint_as_float(r[j]) + __bfloat162float(ps[j]));
               }
             }
             if (col + 32 <= N) {
@@ -488,13 +494,13 @@ PEAR_API int pear_ag_gemm_bf16(const void* const* a_shards, const void* b, void*
 }
 
 // GEMM -> reduce-scatter. A [M, K_local], B [N, K_local] local bf16. stage[r]: rank r's staging buffer in symmetric memory,
-// fp32 [world sources][M / world][ldc]; flags[r]: rank r's uint32 [world sources][tiles of an owner] in symmetric memory
+// bf16 [world sources][M / world][ldc] (ldc a multiple of 8); flags[r]: rank r's uint32 [world sources][tiles of an owner] in symmetric memory
 // (any values below `epoch`); out: local fp32 [M / world, ldc] result. Before the call every rank must have finished
 // reading its staging buffer of the previous call (one pear_symm_signal / wait round). The result is complete when the
 // kernel ends.
 PEAR_API int pear_gemm_rs_bf16(const void* a, const void* b, void* const* stage, void* const* flags, void* out, int M, int N, int K, int lda,
                                int ldb, int ldc, int rank, int world, unsigned epoch, unsigned budget, int* status, int num_sms, void* stream) {
-  if (world < 1 || world > kCMaxRanks || M % (world * kCBM) || (lda % 8) || (ldb % 8) || (ldc % 4) || N % 4) return (int)cudaErrorInvalidValue;
+  if (world < 1 || world > kCMaxRanks || M % (world * kCBM) || (lda % 8) || (ldb % 8) || (ldc % 8) || N % 4) return (int)cudaErrorInvalidValue;
   MapSet maps;
   int e = coll_map_bf16(&maps.a[0], a, M, K, lda, kCBM);
   if (e) return e;

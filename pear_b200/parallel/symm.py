@@ -137,8 +137,8 @@ class SymmWorld:
 
     # -- GEMM -> reduce-scatter ---------------------------------------------------------------------------------------
     def make_rs_accumulator(self, rows_local: int, n: int) -> SymmBuffer:
-        """Staging for ``gemm_rs``: one fp32 slot of this rank's rows per source rank, plus per-tile flags."""
-        buf = self.alloc((self.world, rows_local, n), torch.float32)
+        """Staging for ``gemm_rs``: one bf16 slot of this rank's rows per source rank, plus per-tile flags."""
+        buf = self.alloc((self.world, rows_local, n), torch.bfloat16)
         tiles = (rows_local // 128) * ((n + 255) // 256)
         buf.flags = self.alloc((self.world, tiles), torch.int32)
         buf.flags.tensor.zero_()
