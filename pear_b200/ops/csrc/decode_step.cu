@@ -1,0 +1,852 @@
+// Kernels of the batched, GPU-resident rollout step (decode and speculative-verify rows of many sequences at once).
+// Every per-sequence quantity a step needs lives in device arrays that the step's own kernels update (context length,
+// replay count, record parity, next input tokens), so a step is a fixed sequence of launches with fixed arguments and
+// can be replayed as a CUDA graph without the host in the loop (upstream gets there through vLLM's runner buffers and
+// per-size graphs: rollout/blackwell/cudagraph.py:4-34, rollout/hopper/gdn.py:58-171).
+//
+// Row layout of a step: B sequences x T rows (row = b * T + t); t = 0 is the last committed token, t >= 1 the drafts.
+// A sequence with ctx[b] < 0 is an empty batch slot: every kernel skips it.
+//
+//   ds_add_rmsnorm        residual (+)= sum of split-K planes; (1 + w) RMSNorm -> bf16 activations for the next GEMM
+//   ds_reduce_parts_bf16  sum of split-K planes -> bf16 rows in the tensor-parallel all-reduce workspace
+//   ds_attn_prep          per-head q/k RMSNorm + RoPE + gate split + K/V written into the paged cache (one kernel;
+//                         upstream rollout/attention.py:5-71 `_qk_norm_rope_gate_kernel` + the cache write)
+//   ds_paged_attn_simt    reference / small-shape paged verify attention with the sigmoid gate fused
+//   ds_gdn_verify         Gated-DeltaNet core of a verify step under the replay scheme (upstream gdn_verify.cu:643-1395):
+//                         replay the rows committed by the previous step, write the state once, then the block's outputs
+//   ds_verify_chunks / ds_verify_finish   vocabulary-sharded rejection sampler of greedy drafts with in-kernel Philox
+//   ds_mtp_input          drafter input rows [norm_e(embed(token)) | norm_h(hidden)] (upstream rollout/blackwell/mtp.py:16)
+//   ds_argmax_chunks / ds_argmax_finish   drafter's greedy token over a vocabulary shard
+#include "common.cuh"
+
+#include <cuda_bf16.h>
+#include <cfloat>
+
+namespace pear {
+
+constexpr int kDsMaxRanks = 8;
+struct DsPeers {
+  void* p[kDsMaxRanks];
+};
+
+// ------------------------------------------------------------------------------------------------ Philox noise
+__device__ __forceinline__ uint4 ds_philox4x32_10(uint4 ctr, uint2 key) {
+  constexpr uint32_t M0 = 0xD2511F53u, M1 = 0xCD9E8D57u, W0 = 0x9E3779B9u, W1 = 0xBB67AE85u;
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const uint32_t hi0 = __umulhi(M0, ctr.x), lo0 = M0 * ctr.x;
+    const uint32_t hi1 = __umulhi(M1, ctr.z), lo1 = M1 * ctr.z;
+    ctr = make_uint4(hi1 ^ ctr.y ^ key.x, lo1, hi0 ^ ctr.w ^ key.y, lo0);
+    key.x += W0; key.y += W1;
+  }
+  return ctr;
+}
+__device__ __forceinline__ float ds_u01(uint32_t x) { return ((float)(x >> 8) + 0.5f) * (1.0f / 16777216.0f); }
+// uniforms of vocabulary ids 4*q .. 4*q+3 of (row, step): the same numbers whatever the sharding or the chunking
+__device__ __forceinline__ uint4 ds_noise4(uint32_t seed, uint32_t step, uint32_t row, uint32_t quad) {
+  return ds_philox4x32_10(make_uint4(quad, row, step, 0u), make_uint2(seed, 0x5eedu));
+}
+__device__ __forceinline__ float ds_accept_u(uint32_t seed, uint32_t step, uint32_t row) {
+  return ds_u01(ds_philox4x32_10(make_uint4(0xffffffffu, row, step, 1u), make_uint2(seed, 0x5eedu)).x);
+}
+
+__global__ void ds_philox_uniform_kernel(float* out, int rows, int V, uint32_t seed, uint32_t step) {
+  const int row = blockIdx.y;
+  for (int q = blockIdx.x * blockDim.x + threadIdx.x; q * 4 < V; q += gridDim.x * blockDim.x) {
+    const uint4 r = ds_noise4(seed, step, row, q);
+    const uint32_t rr[4] = {r.x, r.y, r.z, r.w};
+    for (int e = 0; e < 4; ++e)
+      if (q * 4 + e < V) out[(size_t)row * V + q * 4 + e] = ds_u01(rr[e]);
+  }
+}
+__global__ void ds_accept_uniform_kernel(float* out, int rows, uint32_t seed, uint32_t step) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r < rows) out[r] = ds_accept_u(seed, step, r);
+}
+
+// ------------------------------------------------------------------------------------------------ add + RMSNorm
+// mode 0: residual += sum(planes); mode 1: residual = sum(planes); then out = bf16(residual * rstd * (1 + w)).
+__global__ void __launch_bounds__(256) ds_add_rmsnorm_kernel(const float* __restrict__ parts, int nsplit, long long split_stride, int ldp,
+                                                             float* __restrict__ residual, int mode, const float* __restrict__ w,
+                                                             __nv_bfloat16* __restrict__ out, int H, float eps, int one_plus) {
+  __shared__ float red[8];
+  const int row = blockIdx.x, tid = threadIdx.x;
+  float* res = residual + (size_t)row * H;
+  float ssq = 0.f;
+  for (int i = tid * 4; i < H; i += 1024) {
+    float4 v = mode == 0 ? *(const float4*)(res + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < nsplit; ++s) {
+      const float4 p = *(const float4*)(parts + (size_t)s * split_stride + (size_t)row * ldp + i);
+      v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
+    }
+    if (nsplit > 0 || mode == 1) *(float4*)(res + i) = v;
+    ssq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+  }
+  ssq = warp_sum(ssq);
+  if ((tid & 31) == 0) red[tid >> 5] = ssq;
+  __syncthreads();
+  float tot = 0.f;
+  for (int k = 0; k < 8; ++k) tot += red[k];
+  const float rstd = rsqrtf(tot / (float)H + eps);
+  for (int i = tid * 4; i < H; i += 1024) {
+    const float4 v = *(const float4*)(res + i);
+    const float4 g = *(const float4*)(w + i);
+    const float a = one_plus ? 1.f : 0.f;
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x * rstd * (a + g.x), v.y * rstd * (a + g.y));
+    __nv_bfloat162 hi = __floats2bfloat162_rn(v.z * rstd * (a + g.z), v.w * rstd * (a + g.w));
+    uint2 pk;
+    pk.x = *(uint32_t*)&lo; pk.y = *(uint32_t*)&hi;
+    *(uint2*)(out + (size_t)row * H + i) = pk;
+  }
+}
+
+// sum of split-K planes -> bf16 rows (the rank's partial of a row-parallel projection, staged for the all-reduce).
+// `epoch_ctr` (may be null): the workspace has two [rows, H] buffers; the one of epoch *epoch_ctr + 1 is written.
+__global__ void __launch_bounds__(256) ds_reduce_parts_bf16_kernel(const float* __restrict__ parts, int nsplit, long long split_stride, int ldp,
+                                                                   __nv_bfloat16* __restrict__ out, size_t buf_elems,
+                                                                   const uint32_t* __restrict__ epoch_ctr, int H) {
+  const int row = blockIdx.x;
+  __nv_bfloat16* o = out + (epoch_ctr ? (size_t)((*epoch_ctr + 1u) & 1u) * buf_elems : 0) + (size_t)row * H;
+  for (int i = threadIdx.x * 4; i < H; i += 1024) {
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < nsplit; ++s) {
+      const float4 p = *(const float4*)(parts + (size_t)s * split_stride + (size_t)row * ldp + i);
+      v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
+    }
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 pk;
+    pk.x = *(uint32_t*)&lo; pk.y = *(uint32_t*)&hi;
+    *(uint2*)(o + i) = pk;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ attention prep
+// qkv fp32 row: Hq x [q(D) | gate(D)] (or Hq x q(D) when ungated), then Hkv x k(D), then Hkv x v(D).
+// One CTA per row, a warp per head: (1 + w) RMSNorm over the head, RoPE on the first `rot` channels pairing channel i
+// with i + rot/2 (all three M-RoPE axes carry the same position for generated text), q -> bf16 [row][Hq][D],
+// k and v -> bf16 into the paged cache at position ctx[b] + t. The gate stays in the projection output.
+template <int D>
+__global__ void __launch_bounds__(256) ds_attn_prep_kernel(const float* __restrict__ qkv, int ld, const float* __restrict__ qn_w,
+                                                           const float* __restrict__ kn_w, const double* __restrict__ inv_freq, int rot,
+                                                           const int* __restrict__ ctx, const int* __restrict__ rope_off,
+                                                           const int* __restrict__ block_table, int max_blocks, int T, int Hq, int Hkv, int gated,
+                                                           float eps, __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ kc,
+                                                           __nv_bfloat16* __restrict__ vc) {
+  __shared__ float cs[64], sn[64];
+  __shared__ float head[8][D];
+  const int row = blockIdx.x, b = row / T, t = row % T;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int c = ctx[b];
+  if (c < 0) return;
+  const int pos = c + t;
+  const int half = rot >> 1;
+  if (threadIdx.x < half) {
+    const double ang = (double)(pos + rope_off[b]) * inv_freq[threadIdx.x];
+    double sv, cv;
+    sincos(ang, &sv, &cv);
+    cs[threadIdx.x] = (float)cv; sn[threadIdx.x] = (float)sv;
+  }
+  __syncthreads();
+  const float* x = qkv + (size_t)row * ld;
+  const int qstride = gated ? 2 * D : D;
+  const size_t cache_row = ((size_t)block_table[(size_t)b * max_blocks + (pos >> 4)] * 16 + (pos & 15)) * Hkv;
+  for (int h = warp; h < Hq + 2 * Hkv; h += 8) {
+    const float* src;
+    const float* nw = nullptr;
+    __nv_bfloat16* dst;
+    if (h < Hq) { src = x + (size_t)h * qstride; nw = qn_w; dst = q_out + ((size_t)row * Hq + h) * D; }
+    else if (h < Hq + Hkv) { src = x + (size_t)Hq * qstride + (size_t)(h - Hq) * D; nw = kn_w; dst = kc + (cache_row + (h - Hq)) * D; }
+    else { src = x + (size_t)Hq * qstride + (size_t)Hkv * D + (size_t)(h - Hq - Hkv) * D; dst = vc + (cache_row + (h - Hq - Hkv)) * D; }
+    float v[D / 32];
+    float ssq = 0.f;
+#pragma unroll
+    for (int i = 0; i < D / 32; ++i) { v[i] = src[lane + 32 * i]; ssq += v[i] * v[i]; }
+    if (nw) {
+      ssq = warp_sum(ssq);
+      const float rstd = rsqrtf(ssq / (float)D + eps);
+#pragma unroll
+      for (int i = 0; i < D / 32; ++i) head[warp][lane + 32 * i] = v[i] * rstd * (1.f + nw[lane + 32 * i]);
+      __syncwarp();
+#pragma unroll
+      for (int i = 0; i < D / 32; ++i) {
+        const int ch = lane + 32 * i;
+        float y = head[warp][ch];
+        if (ch < half) y = y * cs[ch] - head[warp][ch + half] * sn[ch];
+        else if (ch < rot) y = y * cs[ch - half] + head[warp][ch - half] * sn[ch - half];
+        v[i] = y;
+      }
+      __syncwarp();
+    }
+#pragma unroll
+    for (int i = 0; i < D / 32; ++i) dst[lane + 32 * i] = __float2bfloat16_rn(v[i]);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ paged attention (SIMT)
+// Row (b, t) attends to keys 0 .. ctx[b] + t of its sequence. Grid (rows, kv heads); a warp per query head of the group.
+// out bf16 [row][Hq * D] = softmax(q k^T * scale) v * sigmoid(gate). The plain statement of the op: the tensor-core
+// kernel (paged_attn_tc.cu) is checked against it, and it serves head sizes that kernel is not built for.
+template <int D>
+__global__ void __launch_bounds__(256) ds_paged_attn_simt_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kc,
+                                                                 const __nv_bfloat16* __restrict__ vc, const int* __restrict__ block_table,
+                                                                 int max_blocks, const int* __restrict__ ctx, int T, int Hq, int Hkv, float scale,
+                                                                 const float* __restrict__ gate_src, int gate_ld, int gated,
+                                                                 __nv_bfloat16* __restrict__ out) {
+  const int row = blockIdx.x, kvh = blockIdx.y, b = row / T, t = row % T;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int group = Hq / Hkv;
+  const int c = ctx[b];
+  if (warp >= group || c < 0) return;
+  const int h = kvh * group + warp;
+  const int len = c + t + 1;
+  constexpr int PER = D / 32;
+  float qv[PER], acc[PER];
+#pragma unroll
+  for (int i = 0; i < PER; ++i) { qv[i] = __bfloat162float(q[((size_t)row * Hq + h) * D + lane + 32 * i]) * scale; acc[i] = 0.f; }
+  float m = -FLT_MAX, l = 0.f;
+  for (int k = 0; k < len; ++k) {
+    const int blk = block_table[(size_t)b * max_blocks + (k >> 4)];
+    const size_t base = (((size_t)blk * 16 + (k & 15)) * Hkv + kvh) * D;
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) s += qv[i] * __bfloat162float(kc[base + lane + 32 * i]);
+    s = warp_sum(s);
+    const float mn = fmaxf(m, s), corr = __expf(m - mn), p = __expf(s - mn);
+    l = l * corr + p;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) acc[i] = acc[i] * corr + p * __bfloat162float(vc[base + lane + 32 * i]);
+    m = mn;
+  }
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    float o = acc[i] * inv;
+    if (gated) {
+      const float g = gate_src[(size_t)row * gate_ld + (size_t)h * 2 * D + D + lane + 32 * i];
+      o *= 1.f / (1.f + __expf(-g));
+    }
+    out[(size_t)row * Hq * D + (size_t)h * D + lane + 32 * i] = __float2bfloat16_rn(o);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ GDN verify core
+// proj fp32 row: [q (Hk*128) | k (Hk*128) | v (Hv*128) | z (Hv*128) | b (Hv) | a (Hv)].
+// Per sequence and GDN layer the cache holds the recurrent state at the START of the sequence's last block (fp32
+// [Hv][128][128], one slot) and a two-copy record of that block: conv_rec [slot][2][3 + Tmax][C] = the three conv inputs
+// before the block followed by the block's conv inputs, ab_rec [slot][2][Tmax][2 * Hv] = its (a, b) rows. A step reads copy
+// `parity[b]`, replays the first ncommit[b] rows of the old block into the state (those were accepted), stores the state,
+// then runs this step's T rows on a private copy to produce their outputs and writes the new block into the other copy.
+// Nothing of the rejected rows ever reaches the stored state. CTA per (value head, sequence), thread = one state row.
+// T = 0 only replays (flush before a snapshot or when the sequence leaves the batch).
+constexpr int kGdnD = 128;
+__global__ void __launch_bounds__(128) ds_gdn_verify_kernel(const float* __restrict__ proj, int ld, const float* __restrict__ conv_w,
+                                                            const float* __restrict__ A_log, const float* __restrict__ dt_bias,
+                                                            const float* __restrict__ norm_w, float* __restrict__ state,
+                                                            float* __restrict__ conv_rec, float* __restrict__ ab_rec, const int* __restrict__ slots,
+                                                            const int* __restrict__ ctx, const int* __restrict__ parity,
+                                                            const int* __restrict__ ncommit, int T, int Tmax, int Hk, int Hv, float l2_eps,
+                                                            float rms_eps, __nv_bfloat16* __restrict__ out) {
+  constexpr int D = kGdnD;
+  __shared__ float qs[D], ks[D], red[12];
+  const int hv = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
+  if (ctx[b] < 0) return;
+  const int slot = slots[b], par = parity[b] & 1, nc = ncommit[b];
+  const int rep = Hv / Hk, hk = hv / rep;
+  const int C = 2 * Hk * D + Hv * D;
+  const int ch_q = hk * D + tid, ch_k = Hk * D + hk * D + tid, ch_v = 2 * Hk * D + hv * D + tid;
+  const size_t rec_rows = 3 + Tmax;
+  const float* rin = conv_rec + ((size_t)slot * 2 + par) * rec_rows * C;
+  float* rout = conv_rec + ((size_t)slot * 2 + (par ^ 1)) * rec_rows * C;
+  const float* abin = ab_rec + ((size_t)slot * 2 + par) * Tmax * 2 * Hv;
+  float* about = ab_rec + ((size_t)slot * 2 + (par ^ 1)) * Tmax * 2 * Hv;
+  const float4 wq = *(const float4*)(conv_w + (size_t)ch_q * 4), wk = *(const float4*)(conv_w + (size_t)ch_k * 4),
+               wv = *(const float4*)(conv_w + (size_t)ch_v * 4);
+  const float neg_a = -__expf(A_log[hv]), dtb = dt_bias[hv];
+  // this thread's state row
+  float S[D];
+  float4* Sg = (float4*)(state + (((size_t)slot * Hv + hv) * D + tid) * D);
+#pragma unroll
+  for (int i = 0; i < D / 4; ++i) {
+    const float4 s4 = Sg[i];
+    S[4 * i] = s4.x; S[4 * i + 1] = s4.y; S[4 * i + 2] = s4.z; S[4 * i + 3] = s4.w;
+  }
+  // sliding conv windows of the three channels: rows j, j+1, j+2 of the old record
+  float xq[3], xk[3], xv[3];
+#pragma unroll
+  for (int j = 0; j < 3; ++j) { xq[j] = rin[(size_t)j * C + ch_q]; xk[j] = rin[(size_t)j * C + ch_k]; xv[j] = rin[(size_t)j * C + ch_v]; }
+  const int total = nc + T;
+  for (int r = 0; r < total; ++r) {
+    const bool replay = r < nc;
+    const int t = r - nc;
+    float nq, nk, nv, av, bv;
+    if (replay) {
+      nq = rin[(size_t)(3 + r) * C + ch_q]; nk = rin[(size_t)(3 + r) * C + ch_k]; nv = rin[(size_t)(3 + r) * C + ch_v];
+      av = abin[(size_t)r * 2 * Hv + hv]; bv = abin[(size_t)r * 2 * Hv + Hv + hv];
+    } else {
+      const float* x = proj + (size_t)(b * T + t) * ld;
+      nq = x[ch_q]; nk = x[ch_k]; nv = x[ch_v];
+      bv = x[C + Hv * D + hv]; av = x[C + Hv * D + Hv + hv];
+      if (t == 0) {  // the new record starts with the window that precedes this block
+#pragma unroll
+        for (int j = 0; j < 3; ++j) {
+          rout[(size_t)j * C + ch_v] = xv[j];
+          if (hv % rep == 0) { rout[(size_t)j * C + ch_q] = xq[j]; rout[(size_t)j * C + ch_k] = xk[j]; }
+        }
+      }
+      rout[(size_t)(3 + t) * C + ch_v] = nv;
+      if (hv % rep == 0) { rout[(size_t)(3 + t) * C + ch_q] = nq; rout[(size_t)(3 + t) * C + ch_k] = nk; }
+      if (tid == 0) { about[(size_t)t * 2 * Hv + hv] = av; about[(size_t)t * 2 * Hv + Hv + hv] = bv; }
+    }
+    float cq = xq[0] * wq.x + xq[1] * wq.y + xq[2] * wq.z + nq * wq.w;
+    float ck = xk[0] * wk.x + xk[1] * wk.y + xk[2] * wk.z + nk * wk.w;
+    float cv = xv[0] * wv.x + xv[1] * wv.y + xv[2] * wv.z + nv * wv.w;
+    xq[0] = xq[1]; xq[1] = xq[2]; xq[2] = nq;
+    xk[0] = xk[1]; xk[1] = xk[2]; xk[2] = nk;
+    xv[0] = xv[1]; xv[1] = xv[2]; xv[2] = nv;
+    cq = cq / (1.f + __expf(-cq)); ck = ck / (1.f + __expf(-ck)); cv = cv / (1.f + __expf(-cv));
+    float sq = warp_sum(cq * cq), sk = warp_sum(ck * ck);
+    __syncthreads();
+    if ((tid & 31) == 0) { red[tid >> 5] = sq; red[4 + (tid >> 5)] = sk; }
+    __syncthreads();
+    sq = red[0] + red[1] + red[2] + red[3];
+    sk = red[4] + red[5] + red[6] + red[7];
+    qs[tid] = cq * rsqrtf(sq + l2_eps) * rsqrtf((float)D);
+    ks[tid] = ck * rsqrtf(sk + l2_eps);
+    __syncthreads();
+    const float ax = av + dtb;
+    const float sp = ax > 20.f ? ax : log1pf(__expf(ax));
+    const float decay = __expf(neg_a * sp);
+    const float beta = 1.f / (1.f + __expf(-bv));
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < D; ++i) { S[i] *= decay; dot += S[i] * ks[i]; }
+    const float uu = (cv - dot) * beta;
+    float o = 0.f;
+#pragma unroll
+    for (int i = 0; i < D; ++i) { S[i] += uu * ks[i]; o += S[i] * qs[i]; }
+    if (replay) {
+      if (r == nc - 1) {  // the state at the start of the new block: the only state write of the step
+#pragma unroll
+        for (int i = 0; i < D / 4; ++i) Sg[i] = make_float4(S[4 * i], S[4 * i + 1], S[4 * i + 2], S[4 * i + 3]);
+      }
+    } else {
+      float so = warp_sum(o * o);
+      if ((tid & 31) == 0) red[8 + (tid >> 5)] = so;
+      __syncthreads();
+      so = red[8] + red[9] + red[10] + red[11];
+      const float zz = proj[(size_t)(b * T + t) * ld + C + hv * D + tid];
+      out[(size_t)(b * T + t) * Hv * D + hv * D + tid] =
+          __float2bfloat16_rn(o * rsqrtf(so / (float)D + rms_eps) * norm_w[tid] * (zz / (1.f + __expf(-zz))));
+    }
+  }
+  if (T == 0) {  // flush: the other copy becomes the record of an empty block after the replayed rows
+#pragma unroll
+    for (int j = 0; j < 3; ++j) {
+      rout[(size_t)j * C + ch_v] = xv[j];
+      if (hv % rep == 0) { rout[(size_t)j * C + ch_q] = xq[j]; rout[(size_t)j * C + ch_k] = xk[j]; }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ sharded verify sampler
+// Rejection sampling of greedy drafts over a vocabulary that may be sharded over ranks (upstream verify_sampler.cu runs
+// on gathered logits; here every rank reduces its own shard to small records and only the records travel).
+// Row (b, t) holds the logits after input token t; its draft is the step's input token t + 1 (none for the last row).
+// Per (row, chunk of the local shard): max, sum exp, the best exponential-race key with the draft excluded, the draft's
+// own logit if it lives in the chunk, NaN / +inf count. The records are stored into slot [rank] of every rank's record
+// buffer (plain peer stores); after the flag barrier one CTA per sequence merges ranks x chunks in a fixed order, walks
+// the rows (accept while log p(draft) > log u), takes the first rejected row's winner (or the bonus row's) and writes the
+// step's results AND the next step's inputs.
+struct DsRec {
+  float max, sumexp, best_key, best_z;
+  int best_id, nonfinite;
+  float draft_z;
+  int pad;
+};
+
+__global__ void __launch_bounds__(256) ds_verify_chunks_kernel(const float* __restrict__ logits, int ld, int Vs, int v0, float inv_temp,
+                                                               const int* __restrict__ tok_in, const int* __restrict__ ctx, int T, int chunks,
+                                                               uint32_t seed, const uint32_t* __restrict__ step_ctr, DsPeers recs, int rank, int world,
+                                                               const uint32_t* __restrict__ epoch_ctr, size_t rec_buf_elems) {
+  __shared__ float red[8 * 5];
+  __shared__ int redi[8 * 2];
+  const int chunk = blockIdx.x, row = blockIdx.y, b = row / T, t = row % T, tid = threadIdx.x;
+  if (ctx[b] < 0) return;
+  const int per = (((Vs + chunks - 1) / chunks) + 3) & ~3;
+  const int lo = chunk * per, hi = min(Vs, lo + per);
+  const int draft = (t + 1 < T) ? tok_in[b * T + t + 1] : -1;
+  const uint32_t step = *step_ctr;
+  const float* x = logits + (size_t)row * ld;
+  float m = -FLT_MAX, bk = -FLT_MAX, bz = 0.f, dz = -FLT_MAX;
+  int bid = -1, nf = 0;
+  for (int i = lo + tid * 4; i < hi; i += 1024) {
+    const uint4 rnd = ds_noise4(seed, step, (uint32_t)row, (uint32_t)((v0 + i) >> 2));
+    const uint32_t rr[4] = {rnd.x, rnd.y, rnd.z, rnd.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      if (i + e < hi) {
+        const float z = x[i + e] * inv_temp;
+        if (isnan(z) || z == INFINITY) ++nf;
+        m = fmaxf(m, z);
+        const int id = v0 + i + e;
+        if (id == draft) { dz = z; continue; }
+        const float key = z - __logf(-__logf(ds_u01(rr[e])));
+        if (key > bk) { bk = key; bid = id; bz = z; }
+      }
+    }
+  }
+  float wm = warp_max(m);
+  if ((tid & 31) == 0) red[tid >> 5] = wm;
+  __syncthreads();
+  float cmax = -FLT_MAX;
+  for (int k = 0; k < 8; ++k) cmax = fmaxf(cmax, red[k]);
+  __syncthreads();
+  float s = 0.f;
+  for (int i = lo + tid; i < hi; i += 256) s += __expf(x[i] * inv_temp - cmax);
+  s = warp_sum(s);
+  nf = (int)warp_sum((float)nf);
+  dz = warp_max(dz);
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ok = __shfl_xor_sync(0xffffffffu, bk, o), oz = __shfl_xor_sync(0xffffffffu, bz, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bid, o);
+    if (ok > bk || (ok == bk && oi >= 0 && (bid < 0 || oi < bid))) { bk = ok; bid = oi; bz = oz; }
+  }
+  if ((tid & 31) == 0) {
+    const int w8 = tid >> 5;
+    red[w8] = s; red[8 + w8] = bk; red[16 + w8] = bz; red[24 + w8] = (float)nf; red[32 + w8] = dz; redi[w8] = bid;
+  }
+  __syncthreads();
+  if (tid == 0) {
+    DsRec r;
+    float ts = 0.f, k = -FLT_MAX, z = 0.f, d = -FLT_MAX;
+    int id = -1, tn = 0;
+    for (int w8 = 0; w8 < 8; ++w8) {
+      ts += red[w8]; tn += (int)red[24 + w8]; d = fmaxf(d, red[32 + w8]);
+      if (red[8 + w8] > k || (red[8 + w8] == k && redi[w8] >= 0 && (id < 0 || redi[w8] < id))) { k = red[8 + w8]; id = redi[w8]; z = red[16 + w8]; }
+    }
+    r.max = cmax; r.sumexp = ts; r.best_key = k; r.best_z = z; r.best_id = id; r.nonfinite = tn; r.draft_z = d; r.pad = 0;
+    const size_t buf = epoch_ctr ? (size_t)((*epoch_ctr + 1u) & 1u) * rec_buf_elems : 0;
+    const size_t idx = buf + ((size_t)rank * gridDim.y + row) * chunks + chunk;
+    for (int p = 0; p < world; ++p) {
+      const int peer = (rank + p) % world;
+      uint4* dst = (uint4*)((DsRec*)recs.p[peer] + idx);
+      const uint4* srcv = (const uint4*)&r;
+      dst[0] = srcv[0]; dst[1] = srcv[1];
+    }
+    if (world > 1) __threadfence_system();
+  }
+}
+
+// One CTA (32 threads) per sequence. Outputs of the step: out_tok [B][T] (-1 after the last emitted token), out_lp,
+// n_accept [B], nonfinite [B]. Next step's inputs: tok_in[b][0] = the emitted token that follows the accepted drafts
+// (the drafter fills tok_in[b][1..]), ctx += accepted + 1, ncommit = accepted + 1, parity ^= 1, sel_row[b] = the row
+// whose hidden state feeds the drafter, mtp_tok [B][T] = the token after each row (drafter input of its first pass),
+// mtp_ctx [T][B] = the context length of drafter pass k (pass 0 runs over the step's rows, pass k >= 1 over one new row).
+__global__ void ds_verify_finish_kernel(const DsRec* __restrict__ recs, size_t rec_buf_elems, const uint32_t* __restrict__ epoch_ctr, int world,
+                                        int chunks, int rows_total, int T, uint32_t seed, uint32_t* __restrict__ step_ctr, int* __restrict__ tok_in,
+                                        int* __restrict__ ctx, int* __restrict__ ncommit, int* __restrict__ parity, int* __restrict__ out_tok,
+                                        float* __restrict__ out_lp, int* __restrict__ n_accept, int* __restrict__ nonfinite,
+                                        int* __restrict__ sel_row, int* __restrict__ mtp_tok, int* __restrict__ mtp_ctx, int B) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  const uint32_t step = *step_ctr;
+  if (b < B && ctx[b] >= 0) {
+    const DsRec* base = recs + (epoch_ctr ? (size_t)((*epoch_ctr) & 1u) * rec_buf_elems : 0);
+    int acc = 0, nf = 0;
+    bool stopped = false;
+    for (int t = 0; t < T; ++t) {
+      const int row = b * T + t;
+      float m = -FLT_MAX;
+      for (int r = 0; r < world; ++r)
+        for (int c = 0; c < chunks; ++c) m = fmaxf(m, base[((size_t)r * rows_total + row) * chunks + c].max);
+      float s = 0.f, bk = -FLT_MAX, bz = 0.f, dz = -FLT_MAX;
+      int bid = -1;
+      for (int r = 0; r < world; ++r)
+        for (int c = 0; c < chunks; ++c) {
+          const DsRec& e = base[((size_t)r * rows_total + row) * chunks + c];
+          s += e.sumexp * __expf(e.max - m);
+          nf += e.nonfinite;
+          dz = fmaxf(dz, e.draft_z);
+          if (e.best_key > bk || (e.best_key == bk && e.best_id >= 0 && (bid < 0 || e.best_id < bid))) { bk = e.best_key; bid = e.best_id; bz = e.best_z; }
+        }
+      const float lse = m + __logf(s);
+      if (stopped) { out_tok[row] = -1; out_lp[row] = 0.f; mtp_tok[row] = 0; continue; }
+      const int draft = (t + 1 < T) ? tok_in[row + 1] : -1;
+      bool accept = false;
+      if (draft >= 0) {
+        const float lp = dz - lse;
+        accept = lp > __logf(fmaxf(ds_accept_u(seed, step, (uint32_t)row), 1e-30f));
+        if (accept) { out_tok[row] = draft; out_lp[row] = lp; mtp_tok[row] = draft; ++acc; }
+      }
+      if (!accept) {
+        out_tok[row] = bid; out_lp[row] = bz - lse; mtp_tok[row] = bid;
+        stopped = true;
+      }
+    }
+    const int c0 = ctx[b];
+    mtp_ctx[b] = c0;
+    for (int k = 1; k < T; ++k) mtp_ctx[(size_t)k * B + b] = c0 + acc + k;
+    n_accept[b] = acc; nonfinite[b] = nf;
+    sel_row[b] = b * T + acc;
+    tok_in[b * T] = out_tok[b * T + acc];
+    ctx[b] = c0 + acc + 1;
+    ncommit[b] = acc + 1;
+    parity[b] ^= 1;
+  } else if (b < B) {
+    n_accept[b] = 0; nonfinite[b] = 0; sel_row[b] = b * T;
+    for (int k = 0; k < T; ++k) mtp_ctx[(size_t)k * B + b] = -1;
+    for (int t = 0; t < T; ++t) { out_tok[b * T + t] = -1; out_lp[b * T + t] = 0.f; mtp_tok[b * T + t] = 0; }
+  }
+}
+
+// the step counter moves in a launch of its own: every CTA of the finish kernel has read it by then
+__global__ void ds_bump_kernel(uint32_t* ctr) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) *ctr += 1u;
+}
+
+// ------------------------------------------------------------------------------------------------ drafter input rows
+// out bf16 [row][2H] = [ rmsnorm_e(embed[token[row]]) | rmsnorm_h(hidden[src_row(row)]) ], both (1 + w).
+// src_row: sel (may be null -> identity) maps the output row to the row of `hidden`.
+__global__ void __launch_bounds__(256) ds_mtp_input_kernel(const int* __restrict__ tokens, const __nv_bfloat16* __restrict__ table, int V,
+                                                           const float* __restrict__ hidden, const int* __restrict__ sel,
+                                                           const float* __restrict__ we, const float* __restrict__ wh, int H, float eps,
+                                                           __nv_bfloat16* __restrict__ out) {
+  __shared__ float red[16];
+  const int row = blockIdx.x, tid = threadIdx.x;
+  const int id = min(max(tokens[row], 0), V - 1);
+  const __nv_bfloat16* e = table + (size_t)id * H;
+  const float* h = hidden + (size_t)(sel ? sel[row] : row) * H;
+  float se = 0.f, sh = 0.f;
+  for (int i = tid; i < H; i += 256) {
+    const float a = __bfloat162float(e[i]), c = h[i];
+    se += a * a; sh += c * c;
+  }
+  se = warp_sum(se); sh = warp_sum(sh);
+  if ((tid & 31) == 0) { red[tid >> 5] = se; red[8 + (tid >> 5)] = sh; }
+  __syncthreads();
+  se = 0.f; sh = 0.f;
+  for (int k = 0; k < 8; ++k) { se += red[k]; sh += red[8 + k]; }
+  const float re = rsqrtf(se / (float)H + eps), rh = rsqrtf(sh / (float)H + eps);
+  __nv_bfloat16* o = out + (size_t)row * 2 * H;
+  for (int i = tid; i < H; i += 256) {
+    o[i] = __float2bfloat16_rn(__bfloat162float(e[i]) * re * (1.f + we[i]));
+    o[H + i] = __float2bfloat16_rn(h[i] * rh * (1.f + wh[i]));
+  }
+}
+
+// rows of fp32 [*, H] gathered through `sel` (the drafter's hidden state of the accepted row)
+__global__ void ds_gather_rows_kernel(const float* __restrict__ src, const int* __restrict__ sel, float* __restrict__ dst, int H) {
+  const int row = blockIdx.x;
+  const float4* s = (const float4*)(src + (size_t)sel[row] * H);
+  float4* d = (float4*)(dst + (size_t)row * H);
+  for (int i = threadIdx.x; i < H / 4; i += blockDim.x) d[i] = s[i];
+}
+
+// ------------------------------------------------------------------------------------------------ draft argmax
+// Greedy token of the drafter over a vocabulary shard: chunk records (ordered 64-bit key: monotone float bits << 32 |
+// ~token id, so ties go to the lower id) stored into every rank's buffer, then a per-row maximum over ranks x chunks.
+__global__ void __launch_bounds__(256) ds_argmax_chunks_kernel(const float* __restrict__ logits, int ld, int Vs, int v0, int chunks, DsPeers keys,
+                                                               int rank, int world, const uint32_t* __restrict__ epoch_ctr, size_t buf_elems) {
+  __shared__ unsigned long long red[8];
+  const int chunk = blockIdx.x, row = blockIdx.y, tid = threadIdx.x;
+  const int per = (Vs + chunks - 1) / chunks, lo = chunk * per, hi = min(Vs, lo + per);
+  const float* x = logits + (size_t)row * ld;
+  unsigned long long best = 0ull;
+  for (int i = lo + tid; i < hi; i += 256) {
+    uint32_t bits = __float_as_uint(x[i]);
+    bits = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
+    const unsigned long long key = ((unsigned long long)bits << 32) | (uint32_t)~(uint32_t)(v0 + i);
+    best = key > best ? key : best;
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+    best = other > best ? other : best;
+  }
+  if ((tid & 31) == 0) red[tid >> 5] = best;
+  __syncthreads();
+  if (tid == 0) {
+    for (int k = 1; k < 8; ++k) best = red[k] > best ? red[k] : best;
+    const size_t buf = epoch_ctr ? (size_t)((*epoch_ctr + 1u) & 1u) * buf_elems : 0;
+    const size_t idx = buf + ((size_t)rank * gridDim.y + row) * chunks + chunk;
+    for (int p = 0; p < world; ++p) ((unsigned long long*)keys.p[(rank + p) % world])[idx] = best;
+    if (world > 1) __threadfence_system();
+  }
+}
+
+// token of each row -> dst[row * dst_stride + dst_off] (the next draft slot of the step's input tokens) and `tok_out`
+__global__ void ds_argmax_finish_kernel(const unsigned long long* __restrict__ keys, size_t buf_elems, const uint32_t* __restrict__ epoch_ctr,
+                                        int world, int chunks, int rows, int* __restrict__ dst, int dst_stride, int dst_off,
+                                        int* __restrict__ tok_out) {
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= rows) return;
+  const unsigned long long* base = keys + (epoch_ctr ? (size_t)((*epoch_ctr) & 1u) * buf_elems : 0);
+  unsigned long long best = 0ull;
+  for (int r = 0; r < world; ++r)
+    for (int c = 0; c < chunks; ++c) {
+      const unsigned long long k = base[((size_t)r * rows + row) * chunks + c];
+      best = k > best ? k : best;
+    }
+  const int tok = (int)~(uint32_t)best;
+  dst[(size_t)row * dst_stride + dst_off] = tok;
+  if (tok_out) tok_out[row] = tok;
+}
+
+// ------------------------------------------------------------------------------------------------ device-epoch barrier
+// All ranks' streams meet. The epoch lives in a device counter (so a captured graph can replay it): flag value
+// *ctr + 1 is released to every peer, every peer's flag is awaited with a bounded poll, then the counter takes the
+// new value. One CTA. Buffers exchanged under this barrier alternate by the epoch's parity.
+__global__ void ds_symm_barrier_kernel(DsPeers flags, int rank, int world, int slot, uint32_t* ctr, uint32_t budget, int* status) {
+  const int r = threadIdx.x;
+  const uint32_t e = *ctr + 1u;
+  if (r < world) {
+    __threadfence_system();
+    st_release_sys((uint32_t*)flags.p[r] + slot * 8 + rank, e);
+    bool ok = false;
+    for (uint32_t i = 0; i < budget; ++i) {
+      if ((int32_t)(ld_acquire_sys((const uint32_t*)flags.p[rank] + slot * 8 + r) - e) >= 0) { ok = true; break; }
+      if (i > 32) __nanosleep(100);
+    }
+    if (!ok) set_status(status, PEAR_ERR_FLAG_TIMEOUT);
+  }
+  __syncthreads();
+  if (r == 0) *ctr = e;
+}
+
+// ------------------------------------------------------------------------------------------------ all-reduce + add + norm
+// The tensor-parallel reduction of a row-parallel projection fused with the fp32 residual add and the (1 + w) RMSNorm,
+// with the epoch in a device counter (graph replay). Every rank has staged its bf16 partial rows in buffer
+// (*ctr + 1) & 1 of its workspace; the kernel releases that epoch to the peers, waits for theirs, sums all partials in
+// rank order in fp32 straight from peer memory, adds the residual and normalises. The last CTA to finish stores the new
+// epoch. (Upstream ar_norm.cu:61-208 at two ranks.)
+__global__ void __launch_bounds__(256) ds_ar_add_rmsnorm_kernel(DsPeers partials, DsPeers flags, int rank, int world, int slot, uint32_t* ctr,
+                                                                uint32_t* ticket, float* __restrict__ residual, int mode,
+                                                                const float* __restrict__ weight, __nv_bfloat16* __restrict__ out, int T, int H,
+                                                                size_t buf_elems, float eps, uint32_t budget, int* status) {
+  __shared__ float red[8];
+  __shared__ int ok_flag;
+  const int tid = threadIdx.x;
+  const uint32_t epoch = *ctr + 1u;
+  if (blockIdx.x == 0 && tid < world) {
+    __threadfence_system();
+    st_release_sys((uint32_t*)flags.p[tid] + slot * 8 + rank, epoch);
+  }
+  if (tid == 0) ok_flag = 1;
+  __syncthreads();
+  if (tid < world) {
+    bool ok = false;
+    for (uint32_t i = 0; i < budget; ++i) {
+      if ((int32_t)(ld_acquire_sys((const uint32_t*)flags.p[rank] + slot * 8 + tid) - epoch) >= 0) { ok = true; break; }
+      if (i > 32) __nanosleep(100);
+    }
+    if (!ok) { set_status(status, PEAR_ERR_FLAG_TIMEOUT); ok_flag = 0; }
+  }
+  __syncthreads();
+  if (ok_flag) {
+    const size_t boff = (size_t)(epoch & 1u) * buf_elems;
+    for (int t = blockIdx.x; t < T; t += gridDim.x) {
+      float ssq = 0.f;
+      for (int i = tid * 8; i < H; i += 2048) {
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+        for (int r = 0; r < world; ++r) {
+          const __nv_bfloat16* src = (const __nv_bfloat16*)partials.p[r] + boff + (size_t)t * H + i;
+          uint4 v;
+          asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(src) : "memory");
+          const __nv_bfloat162* h2 = (const __nv_bfloat162*)&v;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(h2[j]);
+            acc[2 * j] += f.x; acc[2 * j + 1] += f.y;
+          }
+        }
+        float* res = residual + (size_t)t * H + i;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (mode == 0) acc[j] += res[j];
+          res[j] = acc[j];
+          ssq += acc[j] * acc[j];
+        }
+      }
+      ssq = warp_sum(ssq);
+      __syncthreads();
+      if ((tid & 31) == 0) red[tid >> 5] = ssq;
+      __syncthreads();
+      float tot = 0.f;
+      for (int k = 0; k < 8; ++k) tot += red[k];
+      const float rstd = rsqrtf(tot / (float)H + eps);
+      for (int i = tid * 8; i < H; i += 2048) {
+        const float* res = residual + (size_t)t * H + i;
+        __nv_bfloat16* o = out + (size_t)t * H + i;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = __float2bfloat16_rn(res[j] * rstd * (1.f + weight[i + j]));
+      }
+    }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence();
+    if (atomicAdd(ticket, 1u) == gridDim.x - 1) { *ticket = 0u; *ctr = epoch; }
+  }
+}
+
+}  // namespace pear
+
+using namespace pear;
+
+static DsPeers ds_ptrs(const void* const* host_ptrs, int world) {
+  DsPeers p;
+  for (int i = 0; i < kDsMaxRanks; ++i) p.p[i] = (host_ptrs && i < world) ? const_cast<void*>(host_ptrs[i]) : nullptr;
+  return p;
+}
+
+PEAR_API int pear_ds_philox_uniform(float* out, int rows, int V, unsigned seed, unsigned step, void* stream) {
+  ds_philox_uniform_kernel<<<dim3(64, rows), 256, 0, (cudaStream_t)stream>>>(out, rows, V, seed, step);
+  PEAR_LAUNCH_CHECK();
+  return 0;
+}
+PEAR_API int pear_ds_accept_uniform(float* out, int rows, unsigned seed, unsigned step, void* stream) {
+  ds_accept_uniform_kernel<<<(rows + 127) / 128, 128, 0, (cudaStream_t)stream>>>(out, rows, seed, step);
+  PEAR_LAUNCH_CHECK();
+  return 0;
+}
+
+PEAR_API int pear_ds_add_rmsnorm(const float* parts, int nsplit, long long split_stride, int ldp, float* residual, int mode, const float* w,
+                                 void* out_bf16, int rows, int H, float eps, int one_plus, void* stream) {
+  if (H % 4 || (nsplit > 0 && ldp % 4)) return (int)cudaErrorInvalidValue;
+  if (rows <= 0) return 0;
+  ds_add_rmsnorm_kernel<<<rows, 256, 0, (cudaStream_t)stream>>>(parts, nsplit, split_stride, ldp, residual, mode, w, (__nv_bfloat16*)out_bf16, H, eps,
+                                                                one_plus);
+  PEAR_LAUNCH_CHECK();
+  return 0;
+}
+
+PEAR_API int pear_ds_reduce_parts_bf16(const float* parts, int nsplit, long long split_stride, int ldp, void* out_bf16, size_t buf_elems,
+                                       const unsigned* epoch_ctr, int rows, int H, void* stream) {
+  if (H % 4 || ldp % 4) return (int)cudaErrorInvalidValue;
+  if (rows <= 0) return 0;
+  ds_reduce_parts_bf16_kernel<<<rows, 256, 0, (cudaStream_t)stream>>>(parts, nsplit, split_stride, ldp, (__nv_bfloat16*)out_bf16, buf_elems, epoch_ctr, H);
+  PEAR_LAUNCH_CHECK();
+  return 0;
+}
+
+PEAR_API int pear_ds_attn_prep(const float* qkv, int ld, const float* qn_w, const float* kn_w, const double* inv_freq, int rot, const int* ctx,
+                               const int* rope_off, const int* block_table, int max_blocks, int rows, int T, int Hq, int Hkv, int D, int gated,
+                               float eps, void* q_out, void* kc, void* vc, void* stream) {
+  if (rot > 128 || rot > D || (rot & 1)) return (int)cudaErrorInvalidValue;
+  cudaStream_t s = (cudaStream_t)stream;
+#define PEAR_PREP(DD)                                                                                                                       \
+  ds_attn_prep_kernel<DD><<<rows, 256, 0, s>>>(qkv, ld, qn_w, kn_w, inv_freq, rot, ctx, rope_off, block_table, max_blocks, T, Hq, Hkv, gated, eps, \
+                                               (__nv_bfloat16*)q_out, (__nv_bfloat16*)kc, (__nv_bfloat16*)vc)
+  if (D == 256) PEAR_PREP(256);
+  else if (D == 128) PEAR_PREP(128);
+  else if (D == 64) PEAR_PREP(64);
+  else return (int)cudaErrorInvalidValue;
+#undef PEAR_PREP
+  PEAR_LAUNCH_CHECK();
+  return 0;
+}
+
+PEAR_API int pear_ds_paged_attn_simt(const void* q, const void* kc, const void* vc, const int* block_table, int max_blocks, const int* ctx, int rows,
+                                     int T, int Hq, int Hkv, int D, float scale, const float* gate_src, int gate_ld, int gated, void* out,
+                                     void* stream) {
+  if (Hq % Hkv || Hq / Hkv > 8) return (int)cudaErrorInvalidValue;
+  cudaStream_t s = (cudaStream_t)stream;
+  const dim3 grid(rows, Hkv);
+#define PEAR_PA(DD)                                                                                                                          \
+  ds_paged_attn_simt_kernel<DD><<<grid, 256, 0, s>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, block_table, \
+                                                     max_blocks, ctx, T, Hq, Hkv, scale, gate_src, gate_ld, gated, (__nv_bfloat16*)out)
+  if (D == 256) PEAR_PA(256);
+  else if (D == 128) PEAR_PA(128);
+  else if (D == 64) PEAR_PA(64);
+  else return (int)cudaErrorInvalidValue;
+#undef PEAR_PA
+  PEAR_LAUNCH_CHECK();
+  return 0;
+}
+
+PEAR_API int pear_ds_gdn_verify(const float* proj, int ld, const float* conv_w, const float* A_log, const float* dt_bias, const float* norm_w,
+                                float* state, float* conv_rec, float* ab_rec, const int* slots, const int* ctx, const int* parity,
+                                const int* ncommit, int B, int T, int Tmax, int Hk, int Hv, float l2_eps, float rms_eps, void* out, void* stream) {
+  if (Hv % Hk || T > Tmax || B <= 0) return (int)cudaErrorInvalidValue;
+  ds_gdn_verify_kernel<<<dim3(Hv, B), 128, 0, (cudaStream_t)stream>>>(proj, ld, conv_w, A_log, dt_bias, norm_w, state, conv_rec, ab_rec, slots, ctx,
+                                                                      parity, ncommit, T, Tmax, Hk, Hv, l2_eps, rms_eps, (__nv_bfloat16*)out);
+  PEAR_LAUNCH_CHECK();
+  return 0;
+}
+
+PEAR_API int pear_ds_rec_bytes() { return (int)sizeof(DsRec); }
+
+// recs: host array of `world` device pointers (each rank's record buffer: 2 x world x rows x chunks records); null for one rank
+// together with `local_recs`.
+PEAR_API int pear_ds_verify_chunks(const float* logits, int ld, int Vs, int v0, float temperature, const int* tok_in, const int* ctx, int B, int T,
+                                   int chunks, unsigned seed, const unsigned* step_ctr, const void* const* recs, int rank, int world,
+                                   const unsigned* epoch_ctr, size_t rec_buf_elems, void* stream) {
+  if (temperature <= 0.f || chunks < 1 || world < 1 || world > kDsMaxRanks) return (int)cudaErrorInvalidValue;
+  ds_verify_chunks_kernel<<<dim3(chunks, B * T), 256, 0, (cudaStream_t)stream>>>(logits, ld, Vs, v0, 1.f / temperature, tok_in, ctx, T, chunks, seed,
+                                                                                 step_ctr, ds_ptrs(recs, world), rank, world, epoch_ctr, rec_buf_elems);
+  PEAR_LAUNCH_CHECK();
+  return 0;
+}
+
+PEAR_API int pear_ds_verify_finish(const void* my_recs, size_t rec_buf_elems, const unsigned* epoch_ctr, int world, int chunks, int B, int T,
+                                   unsigned seed, unsigned* step_ctr, int* tok_in, int* ctx, int* ncommit, int* parity, int* out_tok, float* out_lp,
+                                   int* n_accept, int* nonfinite, int* sel_row, int* mtp_tok, int* mtp_ctx, void* stream) {
+  cudaStream_t s = (cudaStream_t)stream;
+  ds_verify_finish_kernel<<<(B + 31) / 32, 32, 0, s>>>((const DsRec*)my_recs, rec_buf_elems, epoch_ctr, world, chunks, B * T, T, seed, step_ctr, tok_in,
+                                                       ctx, ncommit, parity, out_tok, out_lp, n_accept, nonfinite, sel_row, mtp_tok, mtp_ctx, B);
+  PEAR_LAUNCH_CHECK();
+  ds_bump_kernel<<<1, 32, 0, s>>>(step_ctr);
+  PEAR_LAUNCH_CHECK();
+  return 0;
+}
+
+PEAR_API int pear_ds_mtp_input(const int* tokens, const void* table, int V, const float* hidden, const int* sel, const float* we, const float* wh,
+                               int rows, int H, float eps, void* out, void* stream) {
+  if (rows <= 0) return 0;
+  ds_mtp_input_kernel<<<rows, 256, 0, (cudaStream_t)stream>>>(tokens, (const __nv_bfloat16*)table, V, hidden, sel, we, wh, H, eps, (__nv_bfloat16*)out);
+  PEAR_LAUNCH_CHECK();
+  return 0;
+}
+
+PEAR_API int pear_ds_gather_rows(const float* src, const int* sel, float* dst, int rows, int H, void* stream) {
+  if (H % 4) return (int)cudaErrorInvalidValue;
+  ds_gather_rows_kernel<<<rows, 256, 0, (cudaStream_t)stream>>>(src, sel, dst, H);
+  PEAR_LAUNCH_CHECK();
+  return 0;
+}
+
+PEAR_API int pear_ds_argmax_chunks(const float* logits, int ld, int Vs, int v0, int rows, int chunks, const void* const* keys, int rank, int world,
+                                   const unsigned* epoch_ctr, size_t buf_elems, void* stream) {
+  if (chunks < 1 || world < 1 || world > kDsMaxRanks) return (int)cudaErrorInvalidValue;
+  ds_argmax_chunks_kernel<<<dim3(chunks, rows), 256, 0, (cudaStream_t)stream>>>(logits, ld, Vs, v0, chunks, ds_ptrs(keys, world), rank, world, epoch_ctr,
+                                                                                buf_elems);
+  PEAR_LAUNCH_CHECK();
+  return 0;
+}
+
+PEAR_API int pear_ds_argmax_finish(const void* my_keys, size_t buf_elems, const unsigned* epoch_ctr, int world, int chunks, int rows, int* dst,
+                                   int dst_stride, int dst_off, int* tok_out, void* stream) {
+  ds_argmax_finish_kernel<<<(rows + 127) / 128, 128, 0, (cudaStream_t)stream>>>((const unsigned long long*)my_keys, buf_elems, epoch_ctr, world, chunks,
+                                                                                rows, dst, dst_stride, dst_off, tok_out);
+  PEAR_LAUNCH_CHECK();
+  return 0;
+}
+
+PEAR_API int pear_ds_symm_barrier(const void* const* flags, int rank, int world, int slot, unsigned* ctr, unsigned budget, int* status, void* stream) {
+  if (world < 1 || world > kDsMaxRanks) return (int)cudaErrorInvalidValue;
+  ds_symm_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(ds_ptrs(flags, world), rank, world, slot, ctr, budget, status);
+  PEAR_LAUNCH_CHECK();
+  return 0;
+}
+
+// partials[r]: rank r's workspace of 2 x buf_elems bf16; ctr / ticket: device words of this rank (ticket zero-initialised).
+PEAR_API int pear_ds_ar_add_rmsnorm(const void* const* partials, const void* const* flags, int rank, int world, int slot, unsigned* ctr,
+                                    unsigned* ticket, float* residual, int mode, const float* weight, void* out_bf16, int T, int H, size_t buf_elems,
+                                    float eps, unsigned budget, int* status, int num_ctas, void* stream) {
+  if (world < 1 || world > kDsMaxRanks || (H % 8) != 0 || T <= 0) return (int)cudaErrorInvalidValue;
+  const int grid = T < num_ctas ? T : num_ctas;
+  ds_ar_add_rmsnorm_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(ds_ptrs(partials, world), ds_ptrs(flags, world), rank, world, slot, ctr, ticket,
+                                                                   residual, mode, weight, (__nv_bfloat16*)out_bf16, T, H, buf_elems, eps, budget, status);
+  PEAR_LAUNCH_CHECK();
+  return 0;
+}

@@ -1,0 +1,268 @@
+// Weight-streaming bf16 GEMM for the rollout step (decode / verify rows): Y[m, n] = sum_k X[m, k] * W[n, k] where the
+// step has few token rows (M up to a few hundred) and the weight matrix is what has to come from HBM. The roles of the
+// operands are swapped relative to the training GEMM: the WEIGHTS are the tensor core's A operand (128 output features
+// per CTA = the 128 TMEM lanes), the TOKENS are the B operand (N = a block of BT tokens), so every CTA streams its own
+// 16 KB weight panels through a deep TMA ring and the accumulator is Y^T in tensor memory. Work items are
+// (128-row weight tile, K split, token block); K is split when there are fewer weight tiles than SMs so that all 148 SMs
+// stream (the partial sums go to separate fp32 planes that the consumer adds: no atomics, fixed summation order).
+// (Upstream: rollout/blackwell/csrc/stream_gemm.cu:105-316 — weights as A, tokens as N, split-K partials.)
+// Warp roles as in the training GEMM: warp 0 TMA producer, warp 1 MMA issuer, warps 2-5 epilogue over the four TMEM
+// lane quarters; two accumulators so that the epilogue of one item overlaps the main loop of the next.
+// The epilogue writes Y un-transposed: a thread holds one output feature and 32 tokens, so for each token the 32 lanes
+// of a warp store 32 consecutive features (coalesced). No cluster multicast; every wait is bounded.
+#include "common.cuh"
+
+#include <cudaTypedefs.h>
+
+namespace pear {
+
+constexpr int kSgBM = 128, kSgBK = 64;
+constexpr int kSgThreads = 192;
+
+template <int BT>
+struct SgCfg {
+  static constexpr int kStageBytes = kSgBM * kSgBK * 2 + BT * kSgBK * 2;
+  static constexpr int kStages = BT >= 256 ? 4 : (BT >= 128 ? 6 : (BT >= 64 ? 8 : 10));
+};
+
+struct SgSmem {
+  uint64_t full[10], empty[10];
+  uint64_t tmem_full[2], tmem_empty[2];
+  uint32_t tmem_base;
+};
+
+// EPI 0: fp32 planes out[split][m][n]; EPI 1: bf16 out[m][n] (one split); EPI 2: SwiGLU — the item multiplies TWO weight
+// tiles (gate rows n0.. and up rows up_row0 + n0..) into two accumulators and writes silu(gate) * up as bf16.
+template <int BT, int EPI>
+__global__ void __launch_bounds__(kSgThreads, 1)
+stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, void* __restrict__ out,
+                   int M, int N, int K, int ldo, long long split_stride, int nsplit, int up_row0, int* status) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  constexpr int kDual = EPI == 2 ? 2 : 1;
+  constexpr uint32_t kABytes = kSgBM * kSgBK * 2, kXBytes = BT * kSgBK * 2;
+  constexpr uint32_t kStageBytes = kDual * kABytes + kXBytes;
+  constexpr int kStages = EPI == 2 ? (BT >= 256 ? 3 : (BT >= 128 ? 4 : 5)) : SgCfg<BT>::kStages;
+  constexpr int kAccBufs = (kDual * 2 * BT <= 512) ? 2 : 1;
+  constexpr uint32_t kTmemCols = kDual * kAccBufs * BT < 32 ? 32 : kDual * kAccBufs * BT;
+  uint8_t* tiles = smem;
+  SgSmem* sm = (SgSmem*)(smem + kStages * kStageBytes);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_n = (N + kSgBM - 1) / kSgBM, tblocks = (M + BT - 1) / BT;
+  const int nitems = tiles_n * nsplit * tblocks;
+  const int kblocks = (K + kSgBK - 1) / kSgBK;
+  auto item = [&](int it, int& n0, int& m0, int& s, int& kb0, int& kb1) {
+    const int tb = it % tblocks, rest = it / tblocks;
+    s = rest % nsplit;
+    n0 = (rest / nsplit) * kSgBM;
+    m0 = tb * BT;
+    kb0 = (int)((long long)kblocks * s / nsplit);
+    kb1 = (int)((long long)kblocks * (s + 1) / nsplit);
+  };
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kStages; ++i) { mbar_init(&sm->full[i], 1); mbar_init(&sm->empty[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&sm->tmem_full[i], 1); mbar_init(&sm->tmem_empty[i], 4); }
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&sm->tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = sm->tmem_base;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      prefetch_tensormap(&map_w);
+      prefetch_tensormap(&map_x);
+      int st = 0, ph = 0;
+      bool ok = true;
+      for (int it = blockIdx.x; it < nitems && ok; it += gridDim.x) {
+        int n0, m0, s, kb0, kb1;
+        item(it, n0, m0, s, kb0, kb1);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          ok = mbar_wait_bounded(&sm->empty[st], ph ^ 1, status);
+          if (!ok) break;
+          uint8_t* a = tiles + st * kStageBytes;
+          mbar_expect_tx(&sm->full[st], kStageBytes);
+          tma_load_2d(a, &map_w, kb * kSgBK, n0, &sm->full[st]);
+          if (kDual == 2) tma_load_2d(a + kABytes, &map_w, kb * kSgBK, up_row0 + n0, &sm->full[st]);
+          tma_load_2d(a + kDual * kABytes, &map_x, kb * kSgBK, m0, &sm->full[st]);
+          if (++st == kStages) { st = 0; ph ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_f16(kSgBM, BT, 1);
+      int st = 0, ph = 0, n_it = 0;
+      bool ok = true;
+      for (int it = blockIdx.x; it < nitems && ok; it += gridDim.x, ++n_it) {
+        int n0, m0, s, kb0, kb1;
+        item(it, n0, m0, s, kb0, kb1);
+        const int ab = kAccBufs == 2 ? (n_it & 1) : 0;
+        const uint32_t par = kAccBufs == 2 ? ((n_it >> 1) & 1) : (n_it & 1);
+        ok = mbar_wait_bounded(&sm->tmem_empty[ab], par ^ 1, status);
+        if (!ok) break;
+        tcgen05_fence_after();
+        const uint32_t d_tmem = tmem_base + ab * kDual * BT;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          ok = mbar_wait_bounded(&sm->full[st], ph, status);
+          if (!ok) break;
+          tcgen05_fence_after();
+          const uint32_t a_addr = smem_u32(tiles + st * kStageBytes);
+          const uint64_t da = umma_desc_sw128(a_addr), dx = umma_desc_sw128(a_addr + kDual * kABytes);
+#pragma unroll
+          for (int k = 0; k < kSgBK / 16; ++k)
+            umma_f16(d_tmem, da + (uint64_t)(k * 2), dx + (uint64_t)(k * 2), idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          if (kDual == 2) {
+            const uint64_t du = umma_desc_sw128(a_addr + kABytes);
+#pragma unroll
+            for (int k = 0; k < kSgBK / 16; ++k)
+              umma_f16(d_tmem + BT, du + (uint64_t)(k * 2), dx + (uint64_t)(k * 2), idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          tcgen05_commit(&sm->empty[st]);
+          if (++st == kStages) { st = 0; ph ^= 1; }
+        }
+        tcgen05_commit(&sm->tmem_full[ab]);
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    int n_it = 0;
+    bool ok = true;
+    for (int it = blockIdx.x; it < nitems; it += gridDim.x, ++n_it) {
+      int n0, m0, s, kb0, kb1;
+      item(it, n0, m0, s, kb0, kb1);
+      const int ab = kAccBufs == 2 ? (n_it & 1) : 0;
+      const uint32_t par = kAccBufs == 2 ? ((n_it >> 1) & 1) : (n_it & 1);
+      if (ok) ok = mbar_wait_bounded(&sm->tmem_full[ab], par, status);
+      ok = __all_sync(0xffffffffu, ok);  // the warp leaves together: the arrive below is per warp
+      if (!ok) break;
+      tcgen05_fence_after();
+      const int n = n0 + q * 32 + lane;
+      const uint32_t acc = tmem_base + ((uint32_t)(q * 32) << 16) + ab * kDual * BT;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BT; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(acc + c0, r);
+        if (EPI == 2) {
+          uint32_t u[32];
+          tmem_ld_32x32b_x32(acc + BT + c0, u);
+          tcgen05_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float g = __uint_as_float(r[j]);
+            r[j] = __float_as_uint(g / (1.f + __expf(-g)) * __uint_as_float(u[j]));
+          }
+        } else {
+          tcgen05_wait_ld();
+        }
+        if (n < N && kb1 > kb0) {
+          if (EPI == 0) {
+            float* dst = (float*)out + (size_t)s * split_stride + (size_t)(m0 + c0) * ldo + n;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (m0 + c0 + j < M) dst[(size_t)j * ldo] = __uint_as_float(r[j]);
+          } else {
+            __nv_bfloat16* dst = (__nv_bfloat16*)out + (size_t)(m0 + c0) * ldo + n;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (m0 + c0 + j < M) dst[(size_t)j * ldo] = __float2bfloat16_rn(__uint_as_float(r[j]));
+          }
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sm->tmem_empty[ab]);
+    }
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+static PFN_cuTensorMapEncodeTiled_v12000 sg_get_encode() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  if (!fn) {
+    cudaDriverEntryPointQueryResult q;
+    void* p = nullptr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = (PFN_cuTensorMapEncodeTiled_v12000)p;
+  }
+  return fn;
+}
+
+static int sg_make_map(CUtensorMap* map, const void* base, int rows, int cols, int ld, int box_rows) {
+  auto enc = sg_get_encode();
+  if (!enc) return (int)cudaErrorNotSupported;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)kSgBK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : 1000 + (int)r;
+}
+
+template <int BT, int EPI>
+static int sg_launch(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int M, int N, int K, int ldo, long long split_stride, int nsplit,
+                     int up_row0, int* status, int num_sms, cudaStream_t stream) {
+  constexpr int kDual = EPI == 2 ? 2 : 1;
+  constexpr int kStages = EPI == 2 ? (BT >= 256 ? 3 : (BT >= 128 ? 4 : 5)) : SgCfg<BT>::kStages;
+  constexpr int smem = kStages * (kDual * kSgBM * kSgBK * 2 + BT * kSgBK * 2) + 1024;
+  static bool configured = false;
+  if (!configured) {
+    PEAR_CUDA_CHECK(cudaFuncSetAttribute(stream_gemm_kernel<BT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    configured = true;
+  }
+  const int nitems = ((N + kSgBM - 1) / kSgBM) * nsplit * ((M + BT - 1) / BT);
+  const int grid = nitems < num_sms ? nitems : num_sms;
+  stream_gemm_kernel<BT, EPI><<<grid, kSgThreads, smem, stream>>>(mw, mx, out, M, N, K, ldo, split_stride, nsplit, up_row0, status);
+  PEAR_LAUNCH_CHECK();
+  return 0;
+}
+
+template <int EPI>
+static int sg_dispatch(int bt, const CUtensorMap& mw, const CUtensorMap& mx, void* out, int M, int N, int K, int ldo, long long split_stride,
+                       int nsplit, int up_row0, int* status, int num_sms, cudaStream_t s) {
+  switch (bt) {
+    case 32: return sg_launch<32, EPI>(mw, mx, out, M, N, K, ldo, split_stride, nsplit, up_row0, status, num_sms, s);
+    case 64: return sg_launch<64, EPI>(mw, mx, out, M, N, K, ldo, split_stride, nsplit, up_row0, status, num_sms, s);
+    case 128: return sg_launch<128, EPI>(mw, mx, out, M, N, K, ldo, split_stride, nsplit, up_row0, status, num_sms, s);
+    default: return sg_launch<256, EPI>(mw, mx, out, M, N, K, ldo, split_stride, nsplit, up_row0, status, num_sms, s);
+  }
+}
+
+}  // namespace pear
+
+// Y = X W^T for a step of M token rows. x [M, K] bf16 (ldx), w [N, K] bf16 (ldw); both 16-byte aligned, ldx / ldw multiples of 8.
+//   epi 0: out fp32, `nsplit` planes of [M, ldo] that are `split_stride` elements apart (the consumer adds the planes);
+//   epi 1: out bf16 [M, ldo] (nsplit must be 1);
+//   epi 2: w holds [gate rows | up rows] with the up rows starting at row `up_row0`; N = number of gate rows; out bf16
+//          [M, ldo] = silu(x gate^T) * (x up^T) (nsplit must be 1).
+// Planes whose K range is empty are not written (cannot happen while nsplit <= ceil(K / 64)).
+PEAR_API int pear_stream_gemm_bf16(const void* x, const void* w, void* out, int M, int N, int K, int ldx, int ldw, int ldo, long long split_stride,
+                                   int nsplit, int epi, int up_row0, int* status, int num_sms, void* stream) {
+  using namespace pear;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((ldx % 8) || (ldw % 8) || ((uintptr_t)x % 16) || ((uintptr_t)w % 16) || nsplit < 1 || epi < 0 || epi > 2) return (int)cudaErrorInvalidValue;
+  if (epi != 0 && nsplit != 1) return (int)cudaErrorInvalidValue;
+  if (nsplit > (K + kSgBK - 1) / kSgBK) return (int)cudaErrorInvalidValue;
+  const int bt = M <= 32 ? 32 : (M <= 64 ? 64 : (M <= 128 ? 128 : 256));
+  CUtensorMap mw, mx;
+  const int w_rows = epi == 2 ? up_row0 + N : N;
+  int r = sg_make_map(&mw, w, w_rows, K, ldw, kSgBM);
+  if (r) return r;
+  r = sg_make_map(&mx, x, M, K, ldx, bt);
+  if (r) return r;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (epi == 0) return sg_dispatch<0>(bt, mw, mx, out, M, N, K, ldo, split_stride, nsplit, up_row0, status, num_sms, s);
+  if (epi == 1) return sg_dispatch<1>(bt, mw, mx, out, M, N, K, ldo, split_stride, nsplit, up_row0, status, num_sms, s);
+  return sg_dispatch<2>(bt, mw, mx, out, M, N, K, ldo, split_stride, nsplit, up_row0, status, num_sms, s);
+}
