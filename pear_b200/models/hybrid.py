@@ -11,6 +11,7 @@ weights, ops routed to the sm_100a kernels by :mod:`pear_b200.ops.api`).
 
 from __future__ import annotations
 
+import math
 from dataclasses import dataclass, field
 from typing import Optional
 
@@ -309,6 +310,28 @@ class HybridForCausalLM(nn.Module):
                     p.copy_(dt + torch.log(-torch.expm1(-dt)))
                 elif p.dim() >= 2:
                     p.copy_((torch.randn(p.shape, generator=gen) * std).to(p.dtype))
+                elif "linear_attn.norm" in name:
+                    p.fill_(1.0)
+                else:
+                    p.zero_()
+        return self
+
+    def init_weights_device(self, seed: int = 0) -> "HybridForCausalLM":
+        """The rule of :meth:`init_weights` drawn on the parameters' own device (a 27B-shape model is initialised on the
+        GPU in seconds; the CPU generator of ``init_weights`` would take minutes and the host memory of the whole model)."""
+        std = self.config.init_std
+        dev = next(self.parameters()).device
+        gen = torch.Generator(device=dev).manual_seed(seed)
+        with torch.no_grad():
+            for name, p in self.named_parameters():
+                if name.endswith("A_log"):
+                    p.copy_(torch.log(torch.empty(p.shape, device=dev, dtype=torch.float32).uniform_(1.0, 16.0, generator=gen)))
+                elif name.endswith("dt_bias"):
+                    u = torch.empty(p.shape, device=dev, dtype=torch.float32).uniform_(0.0, 1.0, generator=gen)
+                    dt = torch.exp(u * (math.log(0.1) - math.log(0.001)) + math.log(0.001))
+                    p.copy_(dt + torch.log(-torch.expm1(-dt)))
+                elif p.dim() >= 2:
+                    p.normal_(0.0, std, generator=gen)
                 elif "linear_attn.norm" in name:
                     p.fill_(1.0)
                 else:

@@ -57,8 +57,22 @@ def test_tp2_matches_single_rank():
 
 
 def test_tp_config_refuses_uneven_splits():
-    with pytest.raises(ValueError, match="num_kv_heads=2"):
-        tp_config(_cfg(), 4)
+    with pytest.raises(ValueError, match="num_attention_heads=4"):
+        tp_config(_cfg(), 3)
+
+
+def test_kv_heads_are_replicated_when_ranks_outnumber_them():
+    """4 ranks over 2 KV heads: ranks 0, 1 hold KV head 0 and ranks 2, 3 hold head 1; each rank keeps one query head."""
+    cfg = _cfg()
+    full = HybridForCausalLM(cfg, with_mtp=False).init_weights(1).state_dict()
+    local = tp_config(cfg, 4)
+    assert (local.num_attention_heads, local.num_kv_heads) == (1, 1)
+    name = "model.layers.3.self_attn.k_proj.weight"
+    d = cfg.head_dim
+    for rank in range(4):
+        part = shard_state(full, cfg, rank, 4)
+        assert torch.equal(part[name], full[name][(rank // 2) * d:(rank // 2 + 1) * d])
+        HybridForCausalLM(local, with_mtp=False).load_state_dict(part, strict=True)
 
 
 def _vision_worker(rank, world, path, q):
