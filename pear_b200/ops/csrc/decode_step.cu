@@ -239,15 +239,24 @@ __global__ void __launch_bounds__(256) ds_paged_attn_simt_kernel(const __nv_bflo
 // Nothing of the rejected rows ever reaches the stored state. CTA per (value head, sequence), thread = one state row.
 // T = 0 only replays (flush before a snapshot or when the sequence leaves the batch).
 constexpr int kGdnD = 128;
+// Shared-memory image of one state head: 128 rows of 128 fp32 padded to 132 (no bank conflicts when every thread walks its
+// own row in 16-byte steps), moved by one 512-byte bulk copy per row each way (coalesced, asynchronous). Thread t owns state
+// row t and keeps it in registers for the whole step.
+constexpr int kGdnLd = 132;
 __global__ void __launch_bounds__(128) ds_gdn_verify_kernel(const float* __restrict__ proj, int ld, const float* __restrict__ conv_w,
                                                             const float* __restrict__ A_log, const float* __restrict__ dt_bias,
                                                             const float* __restrict__ norm_w, float* __restrict__ state,
                                                             float* __restrict__ conv_rec, float* __restrict__ ab_rec, const int* __restrict__ slots,
                                                             const int* __restrict__ ctx, const int* __restrict__ parity,
                                                             const int* __restrict__ ncommit, int T, int Tmax, int Hk, int Hv, float l2_eps,
-                                                            float rms_eps, __nv_bfloat16* __restrict__ out) {
+                                                            float rms_eps, __nv_bfloat16* __restrict__ out, int* status) {
   constexpr int D = kGdnD;
-  __shared__ float qs[D], ks[D], red[12];
+  extern __shared__ __align__(128) uint8_t gdn_smem[];
+  float* Ssm = (float*)gdn_smem;                    // [128][132]
+  float4* qs4 = (float4*)(gdn_smem + D * kGdnLd * 4);  // [32]
+  float4* ks4 = qs4 + D / 4;                        // [32]
+  float* red = (float*)(ks4 + D / 4);               // [12]
+  uint64_t* bar = (uint64_t*)(red + 12);
   const int hv = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
   if (ctx[b] < 0) return;
   const int slot = slots[b], par = parity[b] & 1, nc = ncommit[b];
@@ -259,21 +268,31 @@ __global__ void __launch_bounds__(128) ds_gdn_verify_kernel(const float* __restr
   float* rout = conv_rec + ((size_t)slot * 2 + (par ^ 1)) * rec_rows * C;
   const float* abin = ab_rec + ((size_t)slot * 2 + par) * Tmax * 2 * Hv;
   float* about = ab_rec + ((size_t)slot * 2 + (par ^ 1)) * Tmax * 2 * Hv;
+  float* Sg = state + ((size_t)slot * Hv + hv) * D * D;
+  if (tid == 0) {
+    mbar_init(bar, 1);
+    mbar_fence_init();
+    mbar_expect_tx(bar, D * D * 4);
+  }
+  __syncthreads();  // the barrier is initialised and armed before any copy can complete on it
+  bulk_load_1d(Ssm + (size_t)tid * kGdnLd, Sg + (size_t)tid * D, D * 4, bar);
   const float4 wq = *(const float4*)(conv_w + (size_t)ch_q * 4), wk = *(const float4*)(conv_w + (size_t)ch_k * 4),
                wv = *(const float4*)(conv_w + (size_t)ch_v * 4);
   const float neg_a = -__expf(A_log[hv]), dtb = dt_bias[hv];
-  // this thread's state row
-  float S[D];
-  float4* Sg = (float4*)(state + (((size_t)slot * Hv + hv) * D + tid) * D);
-#pragma unroll
-  for (int i = 0; i < D / 4; ++i) {
-    const float4 s4 = Sg[i];
-    S[4 * i] = s4.x; S[4 * i + 1] = s4.y; S[4 * i + 2] = s4.z; S[4 * i + 3] = s4.w;
-  }
-  // sliding conv windows of the three channels: rows j, j+1, j+2 of the old record
   float xq[3], xk[3], xv[3];
 #pragma unroll
   for (int j = 0; j < 3; ++j) { xq[j] = rin[(size_t)j * C + ch_q]; xk[j] = rin[(size_t)j * C + ch_k]; xv[j] = rin[(size_t)j * C + ch_v]; }
+  bool ok = mbar_wait_bounded(bar, 0, nullptr);
+  if (!ok) set_status(status, PEAR_ERR_MBAR_TIMEOUT);
+  ok = __syncthreads_and(ok ? 1 : 0) != 0;
+  if (!ok) return;  // the whole CTA leaves together; nothing has been written yet
+  float S[D];
+  const float4* Srow = (const float4*)(Ssm + (size_t)tid * kGdnLd);
+#pragma unroll
+  for (int j = 0; j < D / 4; ++j) {
+    const float4 v = Srow[j];
+    S[4 * j] = v.x; S[4 * j + 1] = v.y; S[4 * j + 2] = v.z; S[4 * j + 3] = v.w;
+  }
   const int total = nc + T;
   for (int r = 0; r < total; ++r) {
     const bool replay = r < nc;
@@ -310,24 +329,37 @@ __global__ void __launch_bounds__(128) ds_gdn_verify_kernel(const float* __restr
     __syncthreads();
     sq = red[0] + red[1] + red[2] + red[3];
     sk = red[4] + red[5] + red[6] + red[7];
-    qs[tid] = cq * rsqrtf(sq + l2_eps) * rsqrtf((float)D);
-    ks[tid] = ck * rsqrtf(sk + l2_eps);
+    ((float*)qs4)[tid] = cq * rsqrtf(sq + l2_eps) * rsqrtf((float)D);
+    ((float*)ks4)[tid] = ck * rsqrtf(sk + l2_eps);
     __syncthreads();
     const float ax = av + dtb;
     const float sp = ax > 20.f ? ax : log1pf(__expf(ax));
     const float decay = __expf(neg_a * sp);
     const float beta = 1.f / (1.f + __expf(-bv));
-    float dot = 0.f;
+    float4 d4 = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-    for (int i = 0; i < D; ++i) { S[i] *= decay; dot += S[i] * ks[i]; }
-    const float uu = (cv - dot) * beta;
-    float o = 0.f;
+    for (int j = 0; j < D / 4; ++j) {
+      const float4 kk = ks4[j];
+      S[4 * j] *= decay; S[4 * j + 1] *= decay; S[4 * j + 2] *= decay; S[4 * j + 3] *= decay;
+      d4.x += S[4 * j] * kk.x; d4.y += S[4 * j + 1] * kk.y; d4.z += S[4 * j + 2] * kk.z; d4.w += S[4 * j + 3] * kk.w;
+    }
+    const float uu = (cv - ((d4.x + d4.y) + (d4.z + d4.w))) * beta;
+    float4 o4 = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-    for (int i = 0; i < D; ++i) { S[i] += uu * ks[i]; o += S[i] * qs[i]; }
+    for (int j = 0; j < D / 4; ++j) {
+      const float4 kk = ks4[j], qq = qs4[j];
+      S[4 * j] += uu * kk.x; S[4 * j + 1] += uu * kk.y; S[4 * j + 2] += uu * kk.z; S[4 * j + 3] += uu * kk.w;
+      o4.x += S[4 * j] * qq.x; o4.y += S[4 * j + 1] * qq.y; o4.z += S[4 * j + 2] * qq.z; o4.w += S[4 * j + 3] * qq.w;
+    }
+    const float o = (o4.x + o4.y) + (o4.z + o4.w);
     if (replay) {
-      if (r == nc - 1) {  // the state at the start of the new block: the only state write of the step
+      if (r == nc - 1) {  // the state at the start of the new block: the only state write of the step, one bulk copy
+        float4* Sw = (float4*)(Ssm + (size_t)tid * kGdnLd);
 #pragma unroll
-        for (int i = 0; i < D / 4; ++i) Sg[i] = make_float4(S[4 * i], S[4 * i + 1], S[4 * i + 2], S[4 * i + 3]);
+        for (int j = 0; j < D / 4; ++j) Sw[j] = make_float4(S[4 * j], S[4 * j + 1], S[4 * j + 2], S[4 * j + 3]);
+        fence_proxy_async();  // this thread's row is visible to the copy engine; it stores its own row
+        asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(Sg + (size_t)tid * D), "r"(smem_u32(Sw)), "r"(D * 4) : "memory");
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
       }
     } else {
       float so = warp_sum(o * o);
@@ -346,6 +378,8 @@ __global__ void __launch_bounds__(128) ds_gdn_verify_kernel(const float* __restr
       if (hv % rep == 0) { rout[(size_t)j * C + ch_q] = xq[j]; rout[(size_t)j * C + ch_k] = xk[j]; }
     }
   }
+  // the bulk store reads shared memory asynchronously: it must have finished reading before the CTA's memory goes away
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
 
 // ------------------------------------------------------------------------------------------------ sharded verify sampler
@@ -766,10 +800,17 @@ PEAR_API int pear_ds_paged_attn_simt(const void* q, const void* kc, const void* 
 
 PEAR_API int pear_ds_gdn_verify(const float* proj, int ld, const float* conv_w, const float* A_log, const float* dt_bias, const float* norm_w,
                                 float* state, float* conv_rec, float* ab_rec, const int* slots, const int* ctx, const int* parity,
-                                const int* ncommit, int B, int T, int Tmax, int Hk, int Hv, float l2_eps, float rms_eps, void* out, void* stream) {
+                                const int* ncommit, int B, int T, int Tmax, int Hk, int Hv, float l2_eps, float rms_eps, void* out, int* status,
+                                void* stream) {
   if (Hv % Hk || T > Tmax || B <= 0) return (int)cudaErrorInvalidValue;
-  ds_gdn_verify_kernel<<<dim3(Hv, B), 128, 0, (cudaStream_t)stream>>>(proj, ld, conv_w, A_log, dt_bias, norm_w, state, conv_rec, ab_rec, slots, ctx,
-                                                                      parity, ncommit, T, Tmax, Hk, Hv, l2_eps, rms_eps, (__nv_bfloat16*)out);
+  constexpr int smem = kGdnD * kGdnLd * 4 + 2 * kGdnD * 4 + 12 * 4 + 16;
+  static bool configured = false;
+  if (!configured) {
+    PEAR_CUDA_CHECK(cudaFuncSetAttribute(ds_gdn_verify_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    configured = true;
+  }
+  ds_gdn_verify_kernel<<<dim3(Hv, B), 128, smem, (cudaStream_t)stream>>>(proj, ld, conv_w, A_log, dt_bias, norm_w, state, conv_rec, ab_rec, slots, ctx,
+                                                                         parity, ncommit, T, Tmax, Hk, Hv, l2_eps, rms_eps, (__nv_bfloat16*)out, status);
   PEAR_LAUNCH_CHECK();
   return 0;
 }

@@ -122,22 +122,23 @@ paged_attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
 
   if (warp == 8 || warp == 10) {
     // ---------------------------------------------------------------------------------------- K (warp 8) / V (warp 10) pages
-    if (lane == 0) {
-      const bool is_k = warp == 8;
-      const CUtensorMap* map = is_k ? &map_k : &map_v;
-      uint64_t* full = is_k ? &bars->k_full : &bars->v_full;
-      uint64_t* empty = is_k ? &bars->k_empty : &bars->v_empty;
-      uint8_t* dst = smem + (is_k ? kPaKOff : kPaVOff);
-      prefetch_tensormap(map);
-      for (int j = 0; j < ntiles; ++j) {
-        if (j > 0 && !pa_wait(empty, (j - 1) & 1, status)) break;
-        const int npages = min(8, (kv_end - j * kPaKT + 15) >> 4);
-        mbar_expect_tx(full, (uint32_t)npages * 4u * 2048u);
-        for (int pg = 0; pg < npages; ++pg) {
-          const int blk = table[j * 8 + pg];
-          for (int p = 0; p < 4; ++p) tma_load_2d(dst + p * kPaPanel + pg * 2048, map, kvh * kPaHd + p * 64, blk * 16, full);
-        }
-      }
+    // lane l fetches box (page l / 4, 64-column panel l % 4) of the tile: the 32 boxes of a tile are issued at once
+    const bool is_k = warp == 8;
+    const CUtensorMap* map = is_k ? &map_k : &map_v;
+    uint64_t* full = is_k ? &bars->k_full : &bars->v_full;
+    uint64_t* empty = is_k ? &bars->k_empty : &bars->v_empty;
+    uint8_t* dst = smem + (is_k ? kPaKOff : kPaVOff);
+    const int pg = lane >> 2, p = lane & 3;
+    if (lane == 0) prefetch_tensormap(map);
+    for (int j = 0; j < ntiles; ++j) {
+      bool ok = true;
+      if (j > 0 && lane == 0) ok = pa_wait(empty, (j - 1) & 1, status);
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) break;
+      const int npages = min(8, (kv_end - j * kPaKT + 15) >> 4);
+      if (lane == 0) mbar_expect_tx(full, (uint32_t)npages * 4u * 2048u);
+      __syncwarp();
+      if (pg < npages) tma_load_2d(dst + p * kPaPanel + pg * 2048, map, kvh * kPaHd + p * 64, table[j * 8 + pg] * 16, full);
     }
   } else if (warp == 9) {
     // ---------------------------------------------------------------------------------------- MMA issuer

@@ -131,7 +131,7 @@ def gdn_verify(proj, conv_w, a_log, dt_bias, norm_w, state, conv_rec, ab_rec, sl
     _lib.check(_lib.lib().pear_ds_gdn_verify(_lib.ptr(proj), proj.stride(0) if proj is not None else 0, _lib.ptr(conv_w), _lib.ptr(a_log),
                                              _lib.ptr(dt_bias), _lib.ptr(norm_w), _lib.ptr(state), _lib.ptr(conv_rec), _lib.ptr(ab_rec), _lib.ptr(slots),
                                              _lib.ptr(ctx), _lib.ptr(parity), _lib.ptr(ncommit), batch, t, tmax, hk, hv, _f(l2_eps), _f(rms_eps),
-                                             _lib.ptr(out), _lib.stream()), "ds_gdn_verify")
+                                             _lib.ptr(out), _lib.ptr(status_word(state.device)), _lib.stream()), "ds_gdn_verify")
     _lib.count_launch()
 
 
