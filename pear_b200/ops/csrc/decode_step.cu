@@ -19,6 +19,7 @@
 //   ds_argmax_chunks / ds_argmax_finish   drafter's greedy token over a vocabulary shard
 #include "common.cuh"
 
+#include <cudaTypedefs.h>
 #include <cuda_bf16.h>
 #include <cfloat>
 
@@ -239,147 +240,216 @@ __global__ void __launch_bounds__(256) ds_paged_attn_simt_kernel(const __nv_bflo
 // Nothing of the rejected rows ever reaches the stored state. CTA per (value head, sequence), thread = one state row.
 // T = 0 only replays (flush before a snapshot or when the sequence leaves the batch).
 constexpr int kGdnD = 128;
-// Shared-memory image of one state head: 128 rows of 128 fp32 padded to 132 (no bank conflicts when every thread walks its
-// own row in 16-byte steps), moved by one 512-byte bulk copy per row each way (coalesced, asynchronous). Thread t owns state
-// row t and keeps it in registers for the whole step.
-constexpr int kGdnLd = 132;
-__global__ void __launch_bounds__(128) ds_gdn_verify_kernel(const float* __restrict__ proj, int ld, const float* __restrict__ conv_w,
-                                                            const float* __restrict__ A_log, const float* __restrict__ dt_bias,
-                                                            const float* __restrict__ norm_w, float* __restrict__ state,
-                                                            float* __restrict__ conv_rec, float* __restrict__ ab_rec, const int* __restrict__ slots,
-                                                            const int* __restrict__ ctx, const int* __restrict__ parity,
-                                                            const int* __restrict__ ncommit, int T, int Tmax, int Hk, int Hv, float l2_eps,
-                                                            float rms_eps, __nv_bfloat16* __restrict__ out, int* status) {
-  constexpr int D = kGdnD;
-  extern __shared__ __align__(128) uint8_t gdn_smem[];
-  float* Ssm = (float*)gdn_smem;                    // [128][132]
-  float4* qs4 = (float4*)(gdn_smem + D * kGdnLd * 4);  // [32]
-  float4* ks4 = qs4 + D / 4;                        // [32]
-  float* red = (float*)(ks4 + D / 4);               // [12]
-  uint64_t* bar = (uint64_t*)(red + 12);
-  const int hv = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
+constexpr int kGdnRows = 8;    // most rows one CTA walks: replayed (<= Tmax) + new (<= Tmax), Tmax <= 4
+// Structure of the kernel: (1) the state head [128][128] fp32 starts moving into shared memory as four TMA boxes of
+// 128 rows x 32 columns with the 128-byte swizzle (threads walking their own rows hit different bank groups: no
+// conflicts, no padding, four copies per head instead of one per row); (2) meanwhile every input of every row (replayed
+// and new) is loaded, run through the conv + SiLU, and the L2 norms, the gates and k.q of ALL rows are reduced with two
+// block barriers in total; (3) TWO threads share a state row (each keeps 64 of its 128 columns in registers: 16 warps per
+// SM instead of 8 to cover the shared-memory latency of the k / q reads) and walk the rows without any barrier:
+//        a = S_t . k,  c = S_t . q   (one pass over the registers, one shuffle to add the pair's halves)
+//        u = (v_t - decay * a) * beta,   o_t = decay * c + u * (k . q),   S_t <- decay * S_t + u * k
+//     (algebraically the recurrence S <- S decay; u = (v - S k) beta; S <- S + u k^T; o = S q). The decay is carried as a
+//     running scalar (stored state = scale * registers), so the update is one FMA per element; the scalar is folded in
+//     before it can underflow;
+// (4) after the last replayed row the state goes back by TMA while the new rows continue on the registers;
+// (5) the gated RMSNorm of the new rows' outputs is one more reduction for all of them.
+constexpr int kGdnThreads = 256;
+__global__ void __launch_bounds__(kGdnThreads) ds_gdn_verify_kernel(const __grid_constant__ CUtensorMap map_s, const float* __restrict__ proj, int ld,
+                                                                    const float* __restrict__ conv_w, const float* __restrict__ A_log,
+                                                                    const float* __restrict__ dt_bias, const float* __restrict__ norm_w,
+                                                                    float* __restrict__ state, float* __restrict__ conv_rec,
+                                                                    float* __restrict__ ab_rec, const int* __restrict__ slots,
+                                                                    const int* __restrict__ ctx, const int* __restrict__ parity,
+                                                                    const int* __restrict__ ncommit, int T, int Tmax, int Hk, int Hv, float l2_eps,
+                                                                    float rms_eps, __nv_bfloat16* __restrict__ out, int* status) {
+  constexpr int D = kGdnD, RM = kGdnRows, NW = kGdnThreads / 32;
+  extern __shared__ __align__(1024) uint8_t gdn_smem_raw[];
+  uint8_t* gdn_smem = (uint8_t*)(((uintptr_t)gdn_smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* Ssm = gdn_smem;                                    // 4 boxes of [128 rows][128 bytes], swizzled
+  float* qs = (float*)(gdn_smem + D * D * 4);                 // [RM][128]
+  float* ks = qs + RM * D;                                    // [RM][128]
+  float* cvs = ks + RM * D;                                   // [RM][128]: conv outputs of the v channel, later the row outputs
+  float* red = cvs + RM * D;                                  // [RM][NW][4]: sum q^2, sum k^2, sum q k | sum o^2
+  float* rowc = red + RM * NW * 4;                            // [RM][4]: decay, beta, k.q, -
+  float* rown = rowc + RM * 4;                                // [RM][2]: normalisers of q and k
+  uint64_t* bar = (uint64_t*)(rown + RM * 2);
+  const int hv = blockIdx.x, b = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int row = tid >> 1, half = tid & 1;  // state row of this thread and which columns of it: chunks 4 * half .. + 3 of every box
   if (ctx[b] < 0) return;
-  const int slot = slots[b], par = parity[b] & 1, nc = ncommit[b];
+  const int slot = slots[b], par = parity[b] & 1, nc = min(ncommit[b], Tmax);
   const int rep = Hv / Hk, hk = hv / rep;
   const int C = 2 * Hk * D + Hv * D;
-  const int ch_q = hk * D + tid, ch_k = Hk * D + hk * D + tid, ch_v = 2 * Hk * D + hv * D + tid;
+  const int ch_q = hk * D + row, ch_k = Hk * D + hk * D + row, ch_v = 2 * Hk * D + hv * D + row;
   const size_t rec_rows = 3 + Tmax;
   const float* rin = conv_rec + ((size_t)slot * 2 + par) * rec_rows * C;
   float* rout = conv_rec + ((size_t)slot * 2 + (par ^ 1)) * rec_rows * C;
   const float* abin = ab_rec + ((size_t)slot * 2 + par) * Tmax * 2 * Hv;
   float* about = ab_rec + ((size_t)slot * 2 + (par ^ 1)) * Tmax * 2 * Hv;
-  float* Sg = state + ((size_t)slot * Hv + hv) * D * D;
+  const int total = min(nc + T, RM);
+  const int srow0 = (slot * Hv + hv) * D;  // first row of this head in the [slots * Hv * 128, 128] view of the state
   if (tid == 0) {
     mbar_init(bar, 1);
     mbar_fence_init();
     mbar_expect_tx(bar, D * D * 4);
+    for (int p = 0; p < 4; ++p) tma_load_2d(Ssm + p * 16384, &map_s, p * 32, srow0, bar);
   }
-  __syncthreads();  // the barrier is initialised and armed before any copy can complete on it
-  bulk_load_1d(Ssm + (size_t)tid * kGdnLd, Sg + (size_t)tid * D, D * 4, bar);
+
+  // ---- (2) inputs of all rows: conv + SiLU on channel `row` of q, k, v (both threads of a pair compute it, one publishes)
   const float4 wq = *(const float4*)(conv_w + (size_t)ch_q * 4), wk = *(const float4*)(conv_w + (size_t)ch_k * 4),
                wv = *(const float4*)(conv_w + (size_t)ch_v * 4);
-  const float neg_a = -__expf(A_log[hv]), dtb = dt_bias[hv];
-  float xq[3], xk[3], xv[3];
+  float iq[3 + RM], ik[3 + RM], iv[3 + RM];  // the window followed by the rows' raw conv inputs
 #pragma unroll
-  for (int j = 0; j < 3; ++j) { xq[j] = rin[(size_t)j * C + ch_q]; xk[j] = rin[(size_t)j * C + ch_k]; xv[j] = rin[(size_t)j * C + ch_v]; }
+  for (int j = 0; j < 3 + RM; ++j) {
+    const int r = j - 3;  // row index, < 0: window
+    float a = 0.f, c = 0.f, e = 0.f;
+    if (j < 3 + total) {
+      if (r < nc) {
+        a = rin[(size_t)j * C + ch_q]; c = rin[(size_t)j * C + ch_k]; e = rin[(size_t)j * C + ch_v];
+      } else {
+        const float* x = proj + (size_t)(b * T + (r - nc)) * ld;
+        a = x[ch_q]; c = x[ch_k]; e = x[ch_v];
+      }
+    }
+    iq[j] = a; ik[j] = c; iv[j] = e;
+  }
+  const float mine = half == 0 ? 1.f : 0.f;  // a pair holds the same channel: only one of the two enters the sums
+#pragma unroll
+  for (int r = 0; r < RM; ++r) {
+    float cq = iq[r] * wq.x + iq[r + 1] * wq.y + iq[r + 2] * wq.z + iq[r + 3] * wq.w;
+    float ck = ik[r] * wk.x + ik[r + 1] * wk.y + ik[r + 2] * wk.z + ik[r + 3] * wk.w;
+    float cv = iv[r] * wv.x + iv[r + 1] * wv.y + iv[r + 2] * wv.z + iv[r + 3] * wv.w;
+    cq = cq / (1.f + __expf(-cq)); ck = ck / (1.f + __expf(-ck)); cv = cv / (1.f + __expf(-cv));
+    if (half == 0) cvs[r * D + row] = cv;
+    iq[r] = cq; ik[r] = ck;  // raw input r is not read again: row r is its last user (rows use inputs r .. r + 3)
+    const float sq = warp_sum(cq * cq * mine), sk = warp_sum(ck * ck * mine), skq = warp_sum(cq * ck * mine);
+    if (lane == 0 && r < total) { red[(r * NW + warp) * 4] = sq; red[(r * NW + warp) * 4 + 1] = sk; red[(r * NW + warp) * 4 + 2] = skq; }
+  }
+  __syncthreads();
+  if (tid < total) {  // one thread per row finishes the row's scalars
+    const int r = tid;
+    float sq = 0.f, sk = 0.f, skq = 0.f;
+    for (int w8 = 0; w8 < NW; ++w8) { sq += red[(r * NW + w8) * 4]; sk += red[(r * NW + w8) * 4 + 1]; skq += red[(r * NW + w8) * 4 + 2]; }
+    const float nq = rsqrtf(sq + l2_eps) * rsqrtf((float)D), nk = rsqrtf(sk + l2_eps);
+    float av, bv;
+    if (r < nc) { av = abin[(size_t)r * 2 * Hv + hv]; bv = abin[(size_t)r * 2 * Hv + Hv + hv]; }
+    else {
+      const float* x = proj + (size_t)(b * T + (r - nc)) * ld;
+      bv = x[C + Hv * D + hv]; av = x[C + Hv * D + Hv + hv];
+      about[(size_t)(r - nc) * 2 * Hv + hv] = av; about[(size_t)(r - nc) * 2 * Hv + Hv + hv] = bv;
+    }
+    const float ax = av + dt_bias[hv];
+    const float sp = ax > 20.f ? ax : log1pf(__expf(ax));
+    rowc[r * 4] = __expf(-__expf(A_log[hv]) * sp);
+    rowc[r * 4 + 1] = 1.f / (1.f + __expf(-bv));
+    rowc[r * 4 + 2] = skq * nq * nk;
+    rown[r * 2] = nq;
+    rown[r * 2 + 1] = nk;
+  }
+  __syncthreads();
+  if (half == 0) {
+#pragma unroll
+    for (int r = 0; r < RM; ++r)
+      if (r < total) { qs[r * D + row] = iq[r] * rown[r * 2]; ks[r * D + row] = ik[r] * rown[r * 2 + 1]; }
+  }
+  __syncthreads();
+
+  // ---- (3) half a state row in registers, rows without barriers
+  // (the barriers above also made the mbarrier's initialisation visible to every waiter)
   bool ok = mbar_wait_bounded(bar, 0, nullptr);
   if (!ok) set_status(status, PEAR_ERR_MBAR_TIMEOUT);
   ok = __syncthreads_and(ok ? 1 : 0) != 0;
-  if (!ok) return;  // the whole CTA leaves together; nothing has been written yet
-  float S[D];
-  const float4* Srow = (const float4*)(Ssm + (size_t)tid * kGdnLd);
+  if (!ok) return;  // the whole CTA leaves together
+  // register block (p, i), p = 0..3 boxes, i = 0..3: columns p * 32 + (4 * half + i) * 4 .. + 3; in shared memory the 16-byte
+  // chunk c = 4 * half + i of row `row` in box p sits at slot c ^ (row % 8) of the row's 128-byte line
+  float S[D / 2];
+  uint8_t* Srow = Ssm + row * 128;
+  const int sx = row & 7, c0 = 4 * half;
 #pragma unroll
-  for (int j = 0; j < D / 4; ++j) {
-    const float4 v = Srow[j];
+  for (int j = 0; j < 16; ++j) {
+    const float4 v = *(const float4*)(Srow + (j >> 2) * 16384 + (((c0 + (j & 3)) ^ sx) << 4));
     S[4 * j] = v.x; S[4 * j + 1] = v.y; S[4 * j + 2] = v.z; S[4 * j + 3] = v.w;
   }
-  const int total = nc + T;
+  float scale = 1.f;  // true state = scale * S
+#pragma unroll 1
   for (int r = 0; r < total; ++r) {
-    const bool replay = r < nc;
-    const int t = r - nc;
-    float nq, nk, nv, av, bv;
-    if (replay) {
-      nq = rin[(size_t)(3 + r) * C + ch_q]; nk = rin[(size_t)(3 + r) * C + ch_k]; nv = rin[(size_t)(3 + r) * C + ch_v];
-      av = abin[(size_t)r * 2 * Hv + hv]; bv = abin[(size_t)r * 2 * Hv + Hv + hv];
-    } else {
-      const float* x = proj + (size_t)(b * T + t) * ld;
-      nq = x[ch_q]; nk = x[ch_k]; nv = x[ch_v];
-      bv = x[C + Hv * D + hv]; av = x[C + Hv * D + Hv + hv];
-      if (t == 0) {  // the new record starts with the window that precedes this block
+    const float4* k4 = (const float4*)(ks + r * D) + c0;
+    const float4* q4 = (const float4*)(qs + r * D) + c0;
+    const float decay = rowc[r * 4], beta = rowc[r * 4 + 1], kq = rowc[r * 4 + 2];
+    float4 a4 = make_float4(0.f, 0.f, 0.f, 0.f), c4 = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-        for (int j = 0; j < 3; ++j) {
-          rout[(size_t)j * C + ch_v] = xv[j];
-          if (hv % rep == 0) { rout[(size_t)j * C + ch_q] = xq[j]; rout[(size_t)j * C + ch_k] = xk[j]; }
-        }
-      }
-      rout[(size_t)(3 + t) * C + ch_v] = nv;
-      if (hv % rep == 0) { rout[(size_t)(3 + t) * C + ch_q] = nq; rout[(size_t)(3 + t) * C + ch_k] = nk; }
-      if (tid == 0) { about[(size_t)t * 2 * Hv + hv] = av; about[(size_t)t * 2 * Hv + Hv + hv] = bv; }
+    for (int j = 0; j < 16; ++j) {
+      const float4 kk = k4[(j >> 2) * 8 + (j & 3)], qq = q4[(j >> 2) * 8 + (j & 3)];
+      a4.x += S[4 * j] * kk.x; a4.y += S[4 * j + 1] * kk.y; a4.z += S[4 * j + 2] * kk.z; a4.w += S[4 * j + 3] * kk.w;
+      c4.x += S[4 * j] * qq.x; c4.y += S[4 * j + 1] * qq.y; c4.z += S[4 * j + 2] * qq.z; c4.w += S[4 * j + 3] * qq.w;
     }
-    float cq = xq[0] * wq.x + xq[1] * wq.y + xq[2] * wq.z + nq * wq.w;
-    float ck = xk[0] * wk.x + xk[1] * wk.y + xk[2] * wk.z + nk * wk.w;
-    float cv = xv[0] * wv.x + xv[1] * wv.y + xv[2] * wv.z + nv * wv.w;
-    xq[0] = xq[1]; xq[1] = xq[2]; xq[2] = nq;
-    xk[0] = xk[1]; xk[1] = xk[2]; xk[2] = nk;
-    xv[0] = xv[1]; xv[1] = xv[2]; xv[2] = nv;
-    cq = cq / (1.f + __expf(-cq)); ck = ck / (1.f + __expf(-ck)); cv = cv / (1.f + __expf(-cv));
-    float sq = warp_sum(cq * cq), sk = warp_sum(ck * ck);
-    __syncthreads();
-    if ((tid & 31) == 0) { red[tid >> 5] = sq; red[4 + (tid >> 5)] = sk; }
-    __syncthreads();
-    sq = red[0] + red[1] + red[2] + red[3];
-    sk = red[4] + red[5] + red[6] + red[7];
-    ((float*)qs4)[tid] = cq * rsqrtf(sq + l2_eps) * rsqrtf((float)D);
-    ((float*)ks4)[tid] = ck * rsqrtf(sk + l2_eps);
-    __syncthreads();
-    const float ax = av + dtb;
-    const float sp = ax > 20.f ? ax : log1pf(__expf(ax));
-    const float decay = __expf(neg_a * sp);
-    const float beta = 1.f / (1.f + __expf(-bv));
-    float4 d4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    float a = (a4.x + a4.y) + (a4.z + a4.w), c = (c4.x + c4.y) + (c4.z + c4.w);
+    a += __shfl_xor_sync(0xffffffffu, a, 1);
+    c += __shfl_xor_sync(0xffffffffu, c, 1);
+    a *= scale; c *= scale;
+    const float uu = (cvs[r * D + row] - decay * a) * beta;
+    __syncwarp();  // both threads of the pair have read the row's v before it is replaced by the output
+    if (half == 0) cvs[r * D + row] = decay * c + uu * kq;  // the row's output
+    scale *= decay;
+    if (scale < 1e-12f) {  // the same decision in the whole CTA (the decay is a per-head scalar)
 #pragma unroll
-    for (int j = 0; j < D / 4; ++j) {
-      const float4 kk = ks4[j];
-      S[4 * j] *= decay; S[4 * j + 1] *= decay; S[4 * j + 2] *= decay; S[4 * j + 3] *= decay;
-      d4.x += S[4 * j] * kk.x; d4.y += S[4 * j + 1] * kk.y; d4.z += S[4 * j + 2] * kk.z; d4.w += S[4 * j + 3] * kk.w;
+      for (int j = 0; j < D / 2; ++j) S[j] *= scale;
+      scale = 1.f;
     }
-    const float uu = (cv - ((d4.x + d4.y) + (d4.z + d4.w))) * beta;
-    float4 o4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float us = uu / scale;
 #pragma unroll
-    for (int j = 0; j < D / 4; ++j) {
-      const float4 kk = ks4[j], qq = qs4[j];
-      S[4 * j] += uu * kk.x; S[4 * j + 1] += uu * kk.y; S[4 * j + 2] += uu * kk.z; S[4 * j + 3] += uu * kk.w;
-      o4.x += S[4 * j] * qq.x; o4.y += S[4 * j + 1] * qq.y; o4.z += S[4 * j + 2] * qq.z; o4.w += S[4 * j + 3] * qq.w;
+    for (int j = 0; j < 16; ++j) {
+      const float4 kk = k4[(j >> 2) * 8 + (j & 3)];
+      S[4 * j] += us * kk.x; S[4 * j + 1] += us * kk.y; S[4 * j + 2] += us * kk.z; S[4 * j + 3] += us * kk.w;
     }
-    const float o = (o4.x + o4.y) + (o4.z + o4.w);
-    if (replay) {
-      if (r == nc - 1) {  // the state at the start of the new block: the only state write of the step, one bulk copy
-        float4* Sw = (float4*)(Ssm + (size_t)tid * kGdnLd);
+    if (r == nc - 1) {  // the state at the start of the new block: the only state write of the step
 #pragma unroll
-        for (int j = 0; j < D / 4; ++j) Sw[j] = make_float4(S[4 * j], S[4 * j + 1], S[4 * j + 2], S[4 * j + 3]);
-        fence_proxy_async();  // this thread's row is visible to the copy engine; it stores its own row
-        asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(Sg + (size_t)tid * D), "r"(smem_u32(Sw)), "r"(D * 4) : "memory");
+      for (int j = 0; j < 16; ++j)
+        *(float4*)(Srow + (j >> 2) * 16384 + (((c0 + (j & 3)) ^ sx) << 4)) =
+            make_float4(S[4 * j] * scale, S[4 * j + 1] * scale, S[4 * j + 2] * scale, S[4 * j + 3] * scale);
+      fence_proxy_async();
+      __syncthreads();  // nc is the same for the whole CTA: every thread passes here in the same row
+      if (tid == 0) {
+        for (int p = 0; p < 4; ++p)
+          asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(&map_s), "r"(p * 32), "r"(srow0),
+                       "r"(smem_u32(Ssm + p * 16384))
+                       : "memory");
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
       }
-    } else {
-      float so = warp_sum(o * o);
-      if ((tid & 31) == 0) red[8 + (tid >> 5)] = so;
-      __syncthreads();
-      so = red[8] + red[9] + red[10] + red[11];
-      const float zz = proj[(size_t)(b * T + t) * ld + C + hv * D + tid];
-      out[(size_t)(b * T + t) * Hv * D + hv * D + tid] =
-          __float2bfloat16_rn(o * rsqrtf(so / (float)D + rms_eps) * norm_w[tid] * (zz / (1.f + __expf(-zz))));
     }
   }
-  if (T == 0) {  // flush: the other copy becomes the record of an empty block after the replayed rows
-#pragma unroll
-    for (int j = 0; j < 3; ++j) {
-      rout[(size_t)j * C + ch_v] = xv[j];
-      if (hv % rep == 0) { rout[(size_t)j * C + ch_q] = xq[j]; rout[(size_t)j * C + ch_k] = xk[j]; }
+  // ---- (5) gated RMSNorm of the new rows' outputs, the new block's record
+  __syncthreads();
+  for (int r = nc; r < total; ++r) {
+    const float o = cvs[r * D + row] * mine;
+    const float so = warp_sum(o * o);
+    if (lane == 0) red[(r * NW + warp) * 4 + 3] = so;
+  }
+  __syncthreads();
+  if (half == 0) {
+    for (int r = nc; r < total; ++r) {
+      const int t = r - nc;
+      float so = 0.f;
+      for (int w8 = 0; w8 < NW; ++w8) so += red[(r * NW + w8) * 4 + 3];
+      const float zz = proj[(size_t)(b * T + t) * ld + C + hv * D + row];
+      out[(size_t)(b * T + t) * Hv * D + hv * D + row] =
+          __float2bfloat16_rn(cvs[r * D + row] * rsqrtf(so / (float)D + rms_eps) * norm_w[row] * (zz / (1.f + __expf(-zz))));
+    }
+    // record of the new block: [the three conv inputs before it | its own conv inputs], read back from where they came
+    for (int j = 0; j < 3 + T; ++j) {
+      const int src = nc + j;  // index into [old window | old rows] followed by the new rows
+      float a, c, e;
+      if (src < 3 + nc) { a = rin[(size_t)src * C + ch_q]; c = rin[(size_t)src * C + ch_k]; e = rin[(size_t)src * C + ch_v]; }
+      else {
+        const float* x = proj + (size_t)(b * T + (src - 3 - nc)) * ld;
+        a = x[ch_q]; c = x[ch_k]; e = x[ch_v];
+      }
+      rout[(size_t)j * C + ch_v] = e;
+      if (hv % rep == 0) { rout[(size_t)j * C + ch_q] = a; rout[(size_t)j * C + ch_k] = c; }
     }
   }
-  // the bulk store reads shared memory asynchronously: it must have finished reading before the CTA's memory goes away
-  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+  // the stores read shared memory asynchronously: they must have finished reading before the CTA's memory goes away
+  if (tid == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
 
 // ------------------------------------------------------------------------------------------------ sharded verify sampler
@@ -799,17 +869,35 @@ PEAR_API int pear_ds_paged_attn_simt(const void* q, const void* kc, const void* 
 }
 
 PEAR_API int pear_ds_gdn_verify(const float* proj, int ld, const float* conv_w, const float* A_log, const float* dt_bias, const float* norm_w,
-                                float* state, float* conv_rec, float* ab_rec, const int* slots, const int* ctx, const int* parity,
+                                float* state, int num_slots, float* conv_rec, float* ab_rec, const int* slots, const int* ctx, const int* parity,
                                 const int* ncommit, int B, int T, int Tmax, int Hk, int Hv, float l2_eps, float rms_eps, void* out, int* status,
                                 void* stream) {
-  if (Hv % Hk || T > Tmax || B <= 0) return (int)cudaErrorInvalidValue;
-  constexpr int smem = kGdnD * kGdnLd * 4 + 2 * kGdnD * 4 + 12 * 4 + 16;
+  if (Hv % Hk || T > Tmax || B <= 0 || 2 * Tmax > kGdnRows || num_slots <= 0 || ((uintptr_t)state % 16)) return (int)cudaErrorInvalidValue;
+  constexpr int smem = kGdnD * kGdnD * 4 + 3 * kGdnRows * kGdnD * 4 + kGdnRows * (kGdnThreads / 32) * 16 + kGdnRows * 24 + 16 + 1024;
+  static PFN_cuTensorMapEncodeTiled_v12000 enc = nullptr;
+  if (!enc) {
+    cudaDriverEntryPointQueryResult q;
+    void* p = nullptr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+      return (int)cudaErrorNotSupported;
+    enc = (PFN_cuTensorMapEncodeTiled_v12000)p;
+  }
+  CUtensorMap map_s;  // the state as a matrix [slots * Hv * 128 rows, 128 fp32]: boxes of 128 rows x 32 columns, 128-byte swizzle
+  {
+    cuuint64_t dims[2] = {128u, (cuuint64_t)num_slots * Hv * 128u};
+    cuuint64_t strides[1] = {512u};
+    cuuint32_t box[2] = {32u, 128u};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(&map_s, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, state, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return 1000 + (int)r;
+  }
   static bool configured = false;
   if (!configured) {
     PEAR_CUDA_CHECK(cudaFuncSetAttribute(ds_gdn_verify_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured = true;
   }
-  ds_gdn_verify_kernel<<<dim3(Hv, B), 128, smem, (cudaStream_t)stream>>>(proj, ld, conv_w, A_log, dt_bias, norm_w, state, conv_rec, ab_rec, slots, ctx,
+  ds_gdn_verify_kernel<<<dim3(Hv, B), kGdnThreads, smem, (cudaStream_t)stream>>>(map_s, proj, ld, conv_w, A_log, dt_bias, norm_w, state, conv_rec, ab_rec, slots, ctx,
                                                                          parity, ncommit, T, Tmax, Hk, Hv, l2_eps, rms_eps, (__nv_bfloat16*)out, status);
   PEAR_LAUNCH_CHECK();
   return 0;

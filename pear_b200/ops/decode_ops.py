@@ -129,7 +129,7 @@ def paged_attention(q, kc, vc, block_table, ctx, batch: int, t: int, hq: int, hk
 def gdn_verify(proj, conv_w, a_log, dt_bias, norm_w, state, conv_rec, ab_rec, slots, ctx, parity, ncommit, batch: int, t: int, tmax: int, hk: int,
                hv: int, l2_eps: float, rms_eps: float, out) -> None:
     _lib.check(_lib.lib().pear_ds_gdn_verify(_lib.ptr(proj), proj.stride(0) if proj is not None else 0, _lib.ptr(conv_w), _lib.ptr(a_log),
-                                             _lib.ptr(dt_bias), _lib.ptr(norm_w), _lib.ptr(state), _lib.ptr(conv_rec), _lib.ptr(ab_rec), _lib.ptr(slots),
+                                             _lib.ptr(dt_bias), _lib.ptr(norm_w), _lib.ptr(state), state.shape[0], _lib.ptr(conv_rec), _lib.ptr(ab_rec), _lib.ptr(slots),
                                              _lib.ptr(ctx), _lib.ptr(parity), _lib.ptr(ncommit), batch, t, tmax, hk, hv, _f(l2_eps), _f(rms_eps),
                                              _lib.ptr(out), _lib.ptr(status_word(state.device)), _lib.stream()), "ds_gdn_verify")
     _lib.count_launch()
