@@ -150,7 +150,7 @@ def build_rollout(args, rank: int, world: int, symm):
     rs = {li: torch.empty(B, cfg.gdn_v_heads, cfg.gdn_head_dim, cfg.gdn_head_dim, dtype=torch.float32, device=dev).normal_(0.0, 0.02, generator=g)
           for li in cfg.gdn_layers}
     dec = FastDecoder(model, kc, vc, rs, mk, mv, num_slots=B, max_batch=B, n_draft=args.drafts, max_blocks_per_seq=prefix // bs + per_seq,
-                      temperature=1.0, seed=1234, symm=symm, use_graph=not args.no_graph)
+                      temperature=1.0, seed=1234, symm=symm, use_graph=not args.no_graph, ar_mode=args.ar_mode)
     tok = torch.Generator().manual_seed(7)
     shared = list(range(1, 1 + prefix // bs))
     tables = []
@@ -346,6 +346,7 @@ def main() -> None:
     ap.add_argument("--mk-steps", type=int, default=128)
     ap.add_argument("--mk-prompt-len", type=int, default=4096)
     ap.add_argument("--no-megakernel", action="store_true")
+    ap.add_argument("--ar-mode", default="auto", choices=["auto", "one", "two"], help="form of the fused all-reduce + add + RMSNorm (N > 1)")
     ap.add_argument("--no-graph", action="store_true", help="launch every step eagerly (kernel-by-kernel profiling); the headline uses graph replay")
     ap.add_argument("--small", action="store_true", help="4-layer model of the 27B layer shape (smoke runs only; not the headline)")
     args = ap.parse_args()

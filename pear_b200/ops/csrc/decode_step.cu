@@ -793,6 +793,120 @@ __global__ void __launch_bounds__(256) ds_ar_add_rmsnorm_kernel(DsPeers partials
   }
 }
 
+// Two-shot form for many rows (the one-shot kernel moves (W - 1) x T rows into every rank; this one moves (W - 1) / W x T
+// rows in and as many out): row t belongs to rank t % W. After every rank has staged its partial rows, the owner sums the
+// W partials of its rows from peer memory in rank order, adds ITS copy of the fp32 residual (a row's residual is only kept
+// current on its owner), normalises, and stores the bf16 row into the `out` buffer of EVERY rank with 16-byte peer stores
+// (with `bcast_residual` also the fp32 residual row, for the consumers that read the residual itself). The last CTA of a
+// rank to finish releases a second flag to every peer and waits for theirs, so the kernel ends only when every rank's rows
+// have landed here. `out` (and `residual` when broadcast) are symmetric buffers. (Upstream's four-rank form: rollout/hopper/
+// csrc/ar_norm.cu:138-227, with the multicast store replaced by unicast peer stores.)
+__global__ void __launch_bounds__(256) ds_ar2_add_rmsnorm_kernel(DsPeers partials, DsPeers flags, DsPeers outs, DsPeers residuals, int rank, int world,
+                                                                 int slot, uint32_t* ctr, uint32_t* ticket, int mode, int bcast_residual,
+                                                                 const float* __restrict__ weight, int T, int H, size_t buf_elems, float eps,
+                                                                 uint32_t budget, int* status) {
+  __shared__ float red[8];
+  __shared__ int ok_flag;
+  const int tid = threadIdx.x;
+  const uint32_t epoch = *ctr + 1u;
+  if (blockIdx.x == 0 && tid < world) {
+    __threadfence_system();
+    st_release_sys((uint32_t*)flags.p[tid] + slot * 8 + rank, epoch);
+  }
+  if (tid == 0) ok_flag = 1;
+  __syncthreads();
+  if (tid < world) {
+    bool ok = false;
+    for (uint32_t i = 0; i < budget; ++i) {
+      if ((int32_t)(ld_acquire_sys((const uint32_t*)flags.p[rank] + slot * 8 + tid) - epoch) >= 0) { ok = true; break; }
+      if (i > 32) __nanosleep(100);
+    }
+    if (!ok) { set_status(status, PEAR_ERR_FLAG_TIMEOUT); ok_flag = 0; }
+  }
+  __syncthreads();
+  float* residual = (float*)residuals.p[rank];
+  if (ok_flag) {
+    const size_t boff = (size_t)(epoch & 1u) * buf_elems;
+    for (int t = rank + world * (int)blockIdx.x; t < T; t += world * (int)gridDim.x) {
+      float ssq = 0.f;
+      for (int i = tid * 8; i < H; i += 2048) {
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+        for (int r = 0; r < world; ++r) {
+          const __nv_bfloat16* src = (const __nv_bfloat16*)partials.p[r] + boff + (size_t)t * H + i;
+          uint4 v;
+          asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(src) : "memory");
+          const __nv_bfloat162* h2 = (const __nv_bfloat162*)&v;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(h2[j]);
+            acc[2 * j] += f.x; acc[2 * j + 1] += f.y;
+          }
+        }
+        float* res = residual + (size_t)t * H + i;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (mode == 0) acc[j] += res[j];
+          res[j] = acc[j];
+          ssq += acc[j] * acc[j];
+        }
+      }
+      ssq = warp_sum(ssq);
+      __syncthreads();
+      if ((tid & 31) == 0) red[tid >> 5] = ssq;
+      __syncthreads();
+      float tot = 0.f;
+      for (int k = 0; k < 8; ++k) tot += red[k];
+      const float rstd = rsqrtf(tot / (float)H + eps);
+      for (int i = tid * 8; i < H; i += 2048) {
+        const float* res = residual + (size_t)t * H + i;
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = res[j];
+        uint4 pk;
+        __nv_bfloat162 p0 = __floats2bfloat162_rn(v[0] * rstd * (1.f + weight[i]), v[1] * rstd * (1.f + weight[i + 1]));
+        __nv_bfloat162 p1 = __floats2bfloat162_rn(v[2] * rstd * (1.f + weight[i + 2]), v[3] * rstd * (1.f + weight[i + 3]));
+        __nv_bfloat162 p2 = __floats2bfloat162_rn(v[4] * rstd * (1.f + weight[i + 4]), v[5] * rstd * (1.f + weight[i + 5]));
+        __nv_bfloat162 p3 = __floats2bfloat162_rn(v[6] * rstd * (1.f + weight[i + 6]), v[7] * rstd * (1.f + weight[i + 7]));
+        pk.x = *(uint32_t*)&p0; pk.y = *(uint32_t*)&p1; pk.z = *(uint32_t*)&p2; pk.w = *(uint32_t*)&p3;
+        for (int p = 0; p < world; ++p) {
+          const int peer = (rank + p) % world;
+          *(uint4*)((__nv_bfloat16*)outs.p[peer] + (size_t)t * H + i) = pk;
+          if (bcast_residual && peer != rank) {
+            float4* rd = (float4*)((float*)residuals.p[peer] + (size_t)t * H + i);
+            rd[0] = make_float4(v[0], v[1], v[2], v[3]);
+            rd[1] = make_float4(v[4], v[5], v[6], v[7]);
+          }
+        }
+      }
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (atomicAdd_block((unsigned*)&ok_flag, 0u) == 0u) { /* a failed wait was already reported */ }
+  __shared__ int last;
+  if (tid == 0) {
+    __threadfence();
+    last = atomicAdd(ticket, 1u) == gridDim.x - 1 ? 1 : 0;
+  }
+  __syncthreads();
+  if (last) {  // every CTA of this rank has stored its rows: tell the peers, wait for theirs, then move the epoch
+    if (tid < world) {
+      __threadfence_system();
+      st_release_sys((uint32_t*)flags.p[tid] + (slot + 1) * 8 + rank, epoch);
+      bool ok = false;
+      for (uint32_t i = 0; i < budget; ++i) {
+        if ((int32_t)(ld_acquire_sys((const uint32_t*)flags.p[rank] + (slot + 1) * 8 + tid) - epoch) >= 0) { ok = true; break; }
+        if (i > 32) __nanosleep(100);
+      }
+      if (!ok) set_status(status, PEAR_ERR_FLAG_TIMEOUT);
+    }
+    __syncthreads();
+    if (tid == 0) { *ticket = 0u; *ctr = epoch; }
+  }
+}
+
 }  // namespace pear
 
 using namespace pear;
@@ -976,6 +1090,22 @@ PEAR_API int pear_ds_ar_add_rmsnorm(const void* const* partials, const void* con
   const int grid = T < num_ctas ? T : num_ctas;
   ds_ar_add_rmsnorm_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(ds_ptrs(partials, world), ds_ptrs(flags, world), rank, world, slot, ctr, ticket,
                                                                    residual, mode, weight, (__nv_bfloat16*)out_bf16, T, H, buf_elems, eps, budget, status);
+  PEAR_LAUNCH_CHECK();
+  return 0;
+}
+
+// Two-shot form: outs[r] / residuals[r] are rank r's symmetric `out` (bf16 [T, H]) and residual (fp32 [T, H]) buffers; uses flag
+// slots `slot` and `slot + 1`.
+PEAR_API int pear_ds_ar2_add_rmsnorm(const void* const* partials, const void* const* flags, const void* const* outs, const void* const* residuals,
+                                     int rank, int world, int slot, unsigned* ctr, unsigned* ticket, int mode, int bcast_residual, const float* weight,
+                                     int T, int H, size_t buf_elems, float eps, unsigned budget, int* status, int num_ctas, void* stream) {
+  if (world < 1 || world > kDsMaxRanks || (H % 8) != 0 || T <= 0) return (int)cudaErrorInvalidValue;
+  const int mine = (T - rank + world - 1) / world;  // rows this rank owns
+  int grid = mine < num_ctas ? mine : num_ctas;
+  if (grid < 1) grid = 1;
+  ds_ar2_add_rmsnorm_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(ds_ptrs(partials, world), ds_ptrs(flags, world), ds_ptrs(outs, world),
+                                                                    ds_ptrs(residuals, world), rank, world, slot, ctr, ticket, mode, bcast_residual, weight,
+                                                                    T, H, buf_elems, eps, budget, status);
   PEAR_LAUNCH_CHECK();
   return 0;
 }

@@ -196,3 +196,12 @@ def ar_add_rmsnorm(partial_ptrs, flag_ptrs, rank: int, world: int, slot: int, ct
                                                  _lib.ptr(weight), _lib.ptr(out), rows, h, _sz(buf_elems), _f(eps), _u(budget), _lib.ptr(status), num_ctas,
                                                  _lib.stream()), "ds_ar_add_rmsnorm")
     _lib.count_launch()
+
+
+def ar2_add_rmsnorm(partial_ptrs, flag_ptrs, out_ptrs, residual_ptrs, rank: int, world: int, slot: int, ctr, ticket, mode: int, bcast_residual: bool,
+                    weight, rows: int, h: int, buf_elems: int, eps: float, budget: int, status, num_ctas: int) -> None:
+    """Two-shot all-reduce + add + RMSNorm over symmetric ``out`` / ``residual`` buffers (row t is reduced by rank t % world)."""
+    _lib.check(_lib.lib().pear_ds_ar2_add_rmsnorm(partial_ptrs, flag_ptrs, out_ptrs, residual_ptrs, rank, world, slot, _lib.ptr(ctr), _lib.ptr(ticket), mode,
+                                                  1 if bcast_residual else 0, _lib.ptr(weight), rows, h, _sz(buf_elems), _f(eps), _u(budget),
+                                                  _lib.ptr(status), num_ctas, _lib.stream()), "ds_ar2_add_rmsnorm")
+    _lib.count_launch()

@@ -30,7 +30,7 @@ from ..ops import decode_ops as K
 from ..ops import lib as _lib
 from ..ops import rollout_ops
 
-SLOT_STEP_AR, SLOT_STEP_SYNC = 8, 9  # flag slots of the SymmWorld signal region used by the step
+SLOT_STEP_AR, SLOT_STEP_SYNC = 8, 10  # flag slots of the SymmWorld signal region used by the step (the two-shot reduction also uses 9)
 
 
 @dataclass
@@ -60,7 +60,7 @@ class FastDecoder:
 
     def __init__(self, model: HybridForCausalLM, k_cache: dict, v_cache: dict, rec_state: dict, mtp_k: list, mtp_v: list, num_slots: int,
                  max_batch: int, n_draft: int, max_blocks_per_seq: int, temperature: float = 1.0, seed: int = 0, symm=None,
-                 share_weights: bool = True, use_graph: bool = True, tensor_core_attention: Optional[bool] = None):
+                 share_weights: bool = True, use_graph: bool = True, tensor_core_attention: Optional[bool] = None, ar_mode: str = "auto"):
         cfg = model.config
         self.model, self.cfg = model, cfg
         dev = next(model.parameters()).device
@@ -73,6 +73,7 @@ class FastDecoder:
         self.temperature, self.seed = float(temperature), int(seed) & 0xFFFFFFFF
         self.use_graph, self.graph, self._warm = use_graph, None, 0
         self.tc_attn = tensor_core_attention
+        self.ar_mode = ar_mode  # "one": one-shot pull, "two": two-shot (reduce-scatter + all-gather), "auto": by rows and ranks
         if cfg.gdn_head_dim != 128 and cfg.gdn_layers:
             raise ValueError("the GDN verify kernel is built for head dimension 128")
         if model.mtp is None and n_draft > 0:
@@ -115,8 +116,14 @@ class FastDecoder:
             self.ab_rec[li] = torch.zeros(num_slots, 2, T, 2 * cfg.gdn_v_heads, dtype=torch.float32, device=dev)
         # ---- workspaces
         f32, b16 = dict(dtype=torch.float32, device=dev), dict(dtype=torch.bfloat16, device=dev)
-        self.x_res = torch.zeros(M, H, **f32)
-        self.h = torch.zeros(M, H, **b16)
+        if self.world > 1:  # symmetric: the two-shot reduction stores rows into every rank's copies
+            self.h_sym, self.x_sym = symm.alloc((M, H), torch.bfloat16), symm.alloc((M, H), torch.float32)
+            self.h, self.x_res = self.h_sym.tensor, self.x_sym.tensor
+            self.h.zero_()
+            self.x_res.zero_()
+        else:
+            self.x_res = torch.zeros(M, H, **f32)
+            self.h = torch.zeros(M, H, **b16)
         n_in = 0
         for lw in self.layers + (self.mtp.layers if self.mtp else []):
             n_in = max(n_in, lw.w_in.shape[0])
@@ -134,7 +141,12 @@ class FastDecoder:
         self.rec_buf_elems, self.key_buf_elems = rec_elems, key_elems
         if self.mtp:
             self.xcat = torch.zeros(M, 2 * H, **b16)
-            self.r_mtp = torch.zeros(M, H, **f32)
+            if self.world > 1:
+                self.r_sym = symm.alloc((M, H), torch.float32)
+                self.r_mtp = self.r_sym.tensor
+                self.r_mtp.zero_()
+            else:
+                self.r_mtp = torch.zeros(M, H, **f32)
             self.r_sel = torch.zeros(B, H, **f32)
             self.r_sel2 = torch.zeros(B, H, **f32)
             self.h_sel = torch.zeros(B, H, **b16)
@@ -293,12 +305,24 @@ class FastDecoder:
         K.stream_gemm(x[:rows], w, out[:rows], 1, epi, up_row0, n)
         return out, 1
 
-    def _reduce_norm(self, parts, ns, residual, weight, out, rows, eps, mode=0):
+    def _two_shot(self, rows: int) -> bool:
+        if self.ar_mode != "auto":
+            return self.ar_mode == "two"
+        return rows * (self.world - 1) >= 256  # rows every rank would pull in the one-shot form
+
+    def _reduce_norm(self, parts, ns, residual, weight, out, rows, eps, mode=0, bcast=False):
+        """residual (+)= sum over splits and ranks of the partial rows; out = RMSNorm(residual). Under the two-shot form a
+        row's residual is current only on its owner unless ``bcast`` (the callers that read the residual itself ask for it)."""
         if self.world == 1:
             K.add_rmsnorm(parts, ns, residual, weight, out, eps, mode, True, rows)
             return
         buf = self.ar_ws.tensor.shape[1] * self.ar_ws.tensor.shape[2]
         K.reduce_parts_bf16(parts, ns, self.ar_ws.tensor, rows, self.H, buf, self.ar_ctr)
+        if self._two_shot(rows):
+            res_sym = self.x_sym if residual is self.x_res else self.r_sym
+            K.ar2_add_rmsnorm(self.ar_ws.c_ptrs, self.symm.flags.c_ptrs, self.h_sym.c_ptrs, res_sym.c_ptrs, self.rank, self.world, SLOT_STEP_AR,
+                              self.ar_ctr, self.ar_ticket, mode, bcast, weight, rows, self.H, buf, eps, 1 << 22, self.status, 2 * self.sms)
+            return
         K.ar_add_rmsnorm(self.ar_ws.c_ptrs, self.symm.flags.c_ptrs, self.rank, self.world, SLOT_STEP_AR, self.ar_ctr, self.ar_ticket, residual, mode,
                          weight, out, rows, self.H, buf, eps, 1 << 22, self.status, 2 * self.sms)
 
@@ -312,7 +336,7 @@ class FastDecoder:
                           self.tc_attn)
         return self._gemm(self.mix_out.view(-1)[: self.M * lw.hq * lw.d].view(self.M, lw.hq * lw.d), lw.w_out, rows)
 
-    def _layer(self, li, lw, rows, batch, t, ctx, kc, vc, next_norm, residual):
+    def _layer(self, li, lw, rows, batch, t, ctx, kc, vc, next_norm, residual, bcast_last=False):
         cfg = self.cfg
         if lw.kind == "full_attention":
             parts, ns = self._attention(lw, kc, vc, ctx, batch, t)
@@ -327,7 +351,7 @@ class FastDecoder:
         act = self.act.view(-1)[: self.M * lw.ffn].view(self.M, lw.ffn)
         K.stream_gemm(self.h[:rows], lw.w_gu, act[:rows], 1, 2, lw.ffn, lw.ffn)
         parts, ns = self._gemm(act, lw.w_down, rows)
-        self._reduce_norm(parts, ns, residual, next_norm, self.h, rows, lw.eps)
+        self._reduce_norm(parts, ns, residual, next_norm, self.h, rows, lw.eps, bcast=bcast_last)
 
     def _sync(self):
         if self.world > 1:
@@ -342,7 +366,8 @@ class FastDecoder:
         K.add_rmsnorm(None, 0, self.x_res, self.layers[0].ln_in, self.h, cfg.rms_eps, 0, True, M)
         for li, lw in enumerate(self.layers):
             nxt = self.layers[li + 1].ln_in if li + 1 < len(self.layers) else self.final_norm
-            self._layer(li, lw, M, B, T, self.ctx, self.k_cache.get(li), self.v_cache.get(li), nxt, self.x_res)
+            self._layer(li, lw, M, B, T, self.ctx, self.k_cache.get(li), self.v_cache.get(li), nxt, self.x_res,
+                        bcast_last=(li + 1 == len(self.layers) and self.mtp is not None))
         K.stream_gemm(self.h, self.lm_head, self.logits, 1, 0)
         K.verify_chunks(self.logits, self.Vs, self.v0, self.temperature, self.tok_in, self.ctx, B, T, self.chunks, self.seed, self.step_ctr,
                         self.recs_ptrs, self.rank, self.world, self.sync_ctr, self.rec_buf_elems)
@@ -375,7 +400,7 @@ class FastDecoder:
             ctx = self.mtp_ctx[p]
             for j, lw in enumerate(mtp.layers):
                 nxt = mtp.layers[j + 1].ln_in if j + 1 < len(mtp.layers) else mtp.norm
-                self._layer(-1, lw, rows, batch, t, ctx, self.mtp_k[j], self.mtp_v[j], nxt, self.r_mtp)
+                self._layer(-1, lw, rows, batch, t, ctx, self.mtp_k[j], self.mtp_v[j], nxt, self.r_mtp, bcast_last=(j + 1 == len(mtp.layers)))
             nxt_r = self.r_sel if p % 2 == 0 else self.r_sel2
             if p == 0:
                 K.gather_rows(self.h, self.sel_row, self.h_sel, B)

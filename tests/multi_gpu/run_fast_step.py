@@ -19,7 +19,7 @@ from pear_b200.parallel.tensor_parallel import shard_state, tp_config  # noqa: E
 from pear_b200.rollout.fast_step import FastDecoder  # noqa: E402
 
 
-def build(cfg, full_state, rank, world, symm, B, n_draft, pages, seed):
+def build(cfg, full_state, rank, world, symm, B, n_draft, pages, seed, ar_mode="auto"):
     local = tp_config(cfg, world) if world > 1 else cfg
     model = HybridForCausalLM(local)
     model.load_state_dict(shard_state(full_state, cfg, rank, world) if world > 1 else full_state, strict=True)
@@ -49,7 +49,7 @@ def build(cfg, full_state, rank, world, symm, B, n_draft, pages, seed):
     for li in cfg.gdn_layers:
         full_rs = torch.randn(B, hv, 128, 128, device="cuda", generator=g) * 0.05
         rs[li] = full_rs[:, rank * (hv // world):(rank + 1) * (hv // world)].contiguous() if world > 1 else full_rs
-    dec = FastDecoder(model, kc, vc, rs, mk, mv, num_slots=B, max_batch=B, n_draft=n_draft, max_blocks_per_seq=16, temperature=0.8, seed=77, symm=symm)
+    dec = FastDecoder(model, kc, vc, rs, mk, mv, num_slots=B, max_batch=B, n_draft=n_draft, max_blocks_per_seq=16, temperature=0.8, seed=77, symm=symm, ar_mode=ar_mode)
     dec.debug_logits = torch.zeros_like(dec.logits)
     kd, vd = cfg.gdn_key_dim, cfg.gdn_value_dim
     for b in range(B):
@@ -74,39 +74,41 @@ def main() -> int:
     full = HybridForCausalLM(cfg).init_weights(9)
     state = {k: v.to(torch.bfloat16).float() if v.dim() >= 2 else v for k, v in full.state_dict().items()}
     B, n_draft, pages = 3, 3, 64
-    one = build(cfg, state, 0, 1, None, B, n_draft, pages, seed=5)
-    tp = build(cfg, state, rank, world, sw, B, n_draft, pages, seed=5)
     Vs = cfg.vocab_size // world
-    steps, T = 6, 1 + n_draft
-    same_hist = torch.ones(B, dtype=torch.bool)  # sequences whose committed tokens agree so far
-    compared = 0
-    for step in range(steps):
-        in1, in2 = one.tok_in.view(B, T).cpu(), tp.tok_in.view(B, T).cpu()
-        one.step()
-        tp.step()
-        r1, r2 = one.results(), tp.results()
-        one.check()
-        tp.check()
-        # row t of a sequence depends on its input rows 0 .. t (the drafts are the drafter's near-tie-prone argmax and may
-        # differ between the two runs): compare the rows whose inputs agree; there the sharded logits are the full logits'
-        # columns up to the bf16 staging of the partial sums
-        want, got = one.debug_logits[:, rank * Vs:(rank + 1) * Vs], tp.debug_logits[:, :Vs]
-        for b in range(B):
-            for t in range(T):
-                if not same_hist[b] or not torch.equal(in1[b, :t + 1], in2[b, :t + 1]):
-                    break
-                err, scale = float((got[b * T + t] - want[b * T + t]).abs().max()), float(want[b * T + t].abs().max())
-                assert err < 0.05 * max(1.0, scale), (step, b, t, err, scale)
-                compared += 1
-        toks = r2.tokens.cuda()
-        gathered = [torch.zeros_like(toks) for _ in range(world)]
-        dist.all_gather(gathered, toks)
-        assert all(torch.equal(gathered[0], t) for t in gathered), "ranks emitted different tokens"
-        same_hist &= (r1.tokens == r2.tokens).all(dim=1)
-    assert compared >= steps, compared  # at the very least the first row of one sequence at every step
-    agree = bool(same_hist.all())
-    if rank == 0:
-        print(f"PASS tp_fast_step world {world} (tokens equal to the single-rank step through all {steps} steps: {agree})", flush=True)
+    tp = None
+    for ar_mode in ("one", "two"):  # one-shot pull and two-shot (reduce-scatter + all-gather) forms of the fused reduction
+        one = build(cfg, state, 0, 1, None, B, n_draft, pages, seed=5)
+        tp = build(cfg, state, rank, world, sw, B, n_draft, pages, seed=5, ar_mode=ar_mode)
+        steps, T = 6, 1 + n_draft
+        same_hist = torch.ones(B, dtype=torch.bool)  # sequences whose committed tokens agree so far
+        compared = 0
+        for step in range(steps):
+            in1, in2 = one.tok_in.view(B, T).cpu(), tp.tok_in.view(B, T).cpu()
+            one.step()
+            tp.step()
+            r1, r2 = one.results(), tp.results()
+            one.check()
+            tp.check()
+            # row t of a sequence depends on its input rows 0 .. t (the drafts are the drafter's near-tie-prone argmax and may
+            # differ between the two runs): compare the rows whose inputs agree; there the sharded logits are the full logits'
+            # columns up to the bf16 staging of the partial sums
+            want, got = one.debug_logits[:, rank * Vs:(rank + 1) * Vs], tp.debug_logits[:, :Vs]
+            for b in range(B):
+                for t in range(T):
+                    if not same_hist[b] or not torch.equal(in1[b, :t + 1], in2[b, :t + 1]):
+                        break
+                    err, scale = float((got[b * T + t] - want[b * T + t]).abs().max()), float(want[b * T + t].abs().max())
+                    assert err < 0.05 * max(1.0, scale), (ar_mode, step, b, t, err, scale)
+                    compared += 1
+            toks = r2.tokens.cuda()
+            gathered = [torch.zeros_like(toks) for _ in range(world)]
+            dist.all_gather(gathered, toks)
+            assert all(torch.equal(gathered[0], t) for t in gathered), "ranks emitted different tokens"
+            same_hist &= (r1.tokens == r2.tokens).all(dim=1)
+        assert compared >= steps, compared  # at the very least the first row of one sequence at every step
+        agree = bool(same_hist.all())
+        if rank == 0:
+            print(f"PASS tp_fast_step world {world} reduction {ar_mode} (tokens equal to the single-rank step through all {steps} steps: {agree})", flush=True)
     # timing of the sharded step under graph replay (max over ranks)
     torch.cuda.synchronize()
     dist.barrier()

@@ -38,4 +38,4 @@ def test_tensor_parallel_fast_step_two_ranks():
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=540)
     out = r.stdout + r.stderr
     assert r.returncode == 0, out[-4000:]
-    assert "PASS tp_fast_step world 2" in out and "PASS tp_fast_step_graph" in out, out[-4000:]
+    assert "PASS tp_fast_step world 2 reduction one" in out and "PASS tp_fast_step world 2 reduction two" in out and "PASS tp_fast_step_graph" in out, out[-4000:]
