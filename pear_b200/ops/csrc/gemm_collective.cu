@@ -81,6 +81,7 @@ gemm_coll_kernel(const __grid_constant__ MapSet maps, const __grid_constant__ CU
                  uint4* __restrict__ a_full, uint32_t* __restrict__ chunk_flags, const __grid_constant__ FlagPtrs rs_flags) {
   extern __shared__ __align__(1024) uint8_t smem[];
   __shared__ int copier_ok;
+  __shared__ int epi_ok;  // decision of the epilogue's elected waiter, read by all four epilogue warps after a barrier
   constexpr uint32_t kABytes = kCBM * kCBK * 2, kBBytes = BN * kCBK * 2, kStageBytes = kABytes + kBBytes;
   uint8_t* tiles = smem;
   CollSmem* sm = (CollSmem*)(smem + kCStages * kStageBytes);
@@ -205,21 +206,29 @@ gemm_coll_kernel(const __grid_constant__ MapSet maps, const __grid_constant__ CU
       const int ab = it & 1;
       int owner, m0, n0;
       tile_coords(tile, owner, m0, n0);
-      if (ok) ok = mbar_wait_bounded(&sm->tmem_full[ab], (it >> 1) & 1, status);
-      if (!ok) break;
-      tcgen05_fence_after();
-      const int row = m0 + q * 32 + lane;
       // index of this tile among the owner's tiles: (m tile inside the owner's rows) * tiles_n + n tile
       const int tile_in_owner = ((m0 - owner * m_local) / kCBM) * tiles_n + n0 / BN;
-      if (MODE == 1 && owner == rank && world > 1) {
-        if (warp == 2 && lane == 0) {
+      // The four epilogue warps meet at named barriers inside a tile, so they must take the SAME decision to go on or to
+      // leave: one elected thread waits (it gives up only on its own poll budget, never because another CTA reported a
+      // problem) and publishes the result; every warp reads it after a barrier that all of them always reach. A late
+      // peer flag is recorded in the status word but does not end the tile: its rows are wrong, the kernel still returns.
+      if (warp == 2 && lane == 0) {
+        bool w = ok && mbar_wait_bounded(&sm->tmem_full[ab], (it >> 1) & 1, nullptr);
+        if (ok && !w) set_status(status, PEAR_ERR_MBAR_TIMEOUT);
+        if (w && MODE == 1 && owner == rank && world > 1) {
           for (int s2 = 1; s2 < world; ++s2) {
             const int src = (rank + s2) % world;
             if (!wait_epoch(rs_flags.p[rank] + (size_t)src * tiles_m_local * tiles_n + tile_in_owner, epoch, budget)) set_status(status, PEAR_ERR_FLAG_TIMEOUT);
           }
         }
-        asm volatile("bar.sync 4, 128;" ::: "memory");
+        *(volatile int*)&epi_ok = w ? 1 : 0;
       }
+      asm volatile("bar.sync 4, 128;" ::: "memory");
+      ok = *(volatile int*)&epi_ok != 0;
+      if (!ok) break;  // all 128 epilogue threads leave together
+      tcgen05_fence_after();
+      const int row = m0 + q * 32 + lane;
+      asm volatile("bar.sync 4, 128;" ::: "memory");  // everyone has read the decision before the next tile overwrites it
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t r[32];

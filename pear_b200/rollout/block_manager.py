@@ -191,14 +191,17 @@ class BlockManager:
                     hit.host_blocks += 1
             if idx is None:
                 break
+            # retained as soon as it is matched: a later promotion in this loop allocates device blocks and state slots, and
+            # neither the LRU eviction nor the snapshot stealing of those may take a block that is already part of the chain
+            self.retain(idx)
             chain.append(idx)
             parent = h
         usable = len(chain)
         if self.needs_state:
             while usable > 0 and self.blocks[chain[usable - 1]].state_slot is None:
                 usable -= 1
-        for idx in chain[:usable]:
-            self.retain(idx)
+        for idx in chain[usable:]:  # the tail past the last state snapshot is not used
+            self.release(idx)
         hit.blocks = chain[:usable]
         hit.tokens = usable * bs
         hit.state_slot = self.blocks[chain[usable - 1]].state_slot if (usable and self.needs_state) else None
@@ -216,7 +219,10 @@ class BlockManager:
             return None
         idx = self.allocate()
         slot = self.allocate_slot() if entry.has_state else None
-        if entry.has_state and slot is None:
+        # the allocation may have evicted a device block into the host tier, whose own eviction round may have dropped `h`
+        if (entry.has_state and slot is None) or self.host_tier.find(h) is None:
+            if slot is not None:
+                self.release_slot(slot)
             self.release(idx)
             return None
         self.host_tier.load(h, idx, slot)

@@ -94,6 +94,8 @@ class EngineConfig:
     host_blocks: int = 0  # capacity of the host-DRAM tier in blocks (0: disabled)
     state_interval_blocks: int = 0  # extra recurrent-state snapshots every N blocks during prefill (0: turn ends only)
     seed: int = 0
+    fast_decode: bool = True  # on a GPU: decode / verify rows go through the batched GPU-resident step (rollout/fast_step.py)
+    max_blocks_per_seq: int = 0  # width of the device block table of the fast step (0: num_blocks)
 
 
 class RolloutEngine:
@@ -119,6 +121,15 @@ class RolloutEngine:
         self.metrics = {"prompt_tokens": 0, "generation_tokens": 0, "preemptions": 0, "aborted": 0, "spec_drafted": 0,
                         "spec_accepted": 0, "steps": 0}
         self.spec = cfg.num_speculative_tokens if model.mtp is not None else 0
+        # the batched GPU-resident step for decode / verify rows (prefill chunks stay on the packed runner)
+        self.fast = None
+        self.symm = None  # set_symm_world(): tensor-parallel replicas hand their SymmWorld over before the first step
+        self._fast_slot: dict[int, int] = {}  # id(request) -> batch slot of the fast step
+        self._fast_free: list[int] = []
+        self._fast_tables: dict[int, int] = {}  # id(request) -> block-table length already on the device
+        self._fast_ok = (self.device.type == "cuda" and cfg.fast_decode and cfg.block_size == 16
+                         and (not model.config.gdn_layers or (model.config.gdn_head_dim == 128 and model.config.conv_kernel == 4))
+                         and model.config.head_dim in (64, 128, 256))
 
     # -- public API ---------------------------------------------------------------------------------------------------
     def add_request(self, prompt: list[int], params: Optional[SamplingParams] = None, session: Optional[str] = None,
@@ -166,6 +177,8 @@ class RolloutEngine:
                 if name in own:
                     own[name].copy_(t.to(own[name].dtype))
         self.policy_version = version if version is not None else self.policy_version + 1
+        if self.fast is not None:
+            self.fast.repack()  # a no-op copy-wise when the parameters are views of the merged weights
         self.clear_kv_cache()
 
     def clear_kv_cache(self) -> int:
@@ -247,6 +260,7 @@ class RolloutEngine:
 
     def _finish(self, req: Request, reason: FinishReason) -> None:
         req.finish = reason
+        self._fast_release(req)
         if req.seq is not None:
             if reason != FinishReason.ABORTED:
                 self.runner.flush(req.seq)
@@ -267,6 +281,7 @@ class RolloutEngine:
         self.metrics["spec_accepted"] += req.spec_accepted
 
     def _preempt(self, req: Request) -> None:
+        self._fast_release(req)
         for b in req.block_table:
             self.blocks.release(b)
         self.blocks.release_slot(req.seq.slot)
@@ -286,11 +301,14 @@ class RolloutEngine:
         rows: list[StepRow] = []
         plan: list[tuple[Request, int, bool]] = []  # (request, rows scheduled, is decode/verify)
         # 1. decode / verify rows of running requests whose prompt is fully computed
+        fast_reqs = self._fast_candidates()
         for req in list(self.running):
             total = len(req.tokens)
             if req.computed < total - 1:
                 continue
             if req.seq is None:  # preempted earlier in this loop
+                continue
+            if fast_reqs is not None:  # stepped by the batched GPU-resident step below
                 continue
             n = 1 + len(req.drafts)
             planned = {id(p[0]) for p in plan}
@@ -347,6 +365,8 @@ class RolloutEngine:
                 continue
             add_prefill(req)
         if not rows:
+            if fast_reqs:
+                return self._fast_step(fast_reqs)
             if self.running and not any(True for _ in rows):
                 # every running request is blocked on memory: preempt the youngest to make progress
                 if len(self.running) > 1:
@@ -377,6 +397,120 @@ class RolloutEngine:
                 lo += n
             if req.finish is not None:
                 done.append(req)
+        if fast_reqs:
+            done += self._fast_step([r for r in fast_reqs if r.finish is None and r.seq is not None])
+        return done
+
+    # -- the batched GPU-resident step --------------------------------------------------------------------------------------
+    def set_symm_world(self, symm) -> None:
+        """Tensor-parallel replica: the fast step reduces its row-parallel partials through this ``SymmWorld``."""
+        self.symm = symm
+
+    def _fast_candidates(self):
+        """Decode-phase requests when ALL of them can take the fast step (one temperature > 0, plain sampling, no top-k
+        log-probs); None when the step has to stay on the packed runner."""
+        from ..models import hybrid
+
+        if not self._fast_ok or (hybrid.tensor_parallel_active() and self.symm is None):
+            return None
+        reqs = [r for r in self.running if r.seq is not None and r.output and r.computed >= len(r.tokens) - 1]
+        if not reqs:
+            return []
+        p0 = reqs[0].params
+        if p0.temperature <= 0.0 or any(r.params.temperature != p0.temperature or r.params.top_p < 1.0 or r.params.top_k > 0 or r.params.topk_logprobs > 0
+                                        for r in reqs):
+            for r in list(self.running):
+                self._fast_release(r)
+            return None
+        return reqs
+
+    def _fast_init(self, temperature: float) -> None:
+        from .fast_step import FastDecoder
+
+        cfg, rn = self.cfg, self.runner
+        width = cfg.max_blocks_per_seq or cfg.num_blocks
+        self.fast = FastDecoder(self.model, rn.k_cache, rn.v_cache, rn.rec_state, rn.mtp_k if rn.has_mtp else [], rn.mtp_v if rn.has_mtp else [],
+                                num_slots=2 * cfg.max_num_seqs + 64, max_batch=cfg.max_num_seqs, n_draft=self.spec, max_blocks_per_seq=width,
+                                temperature=temperature, seed=cfg.seed, symm=self.symm)
+        self._fast_free = list(range(cfg.max_num_seqs - 1, -1, -1))
+
+    def _fast_release(self, req: Request, commit: Optional[int] = None) -> None:
+        """Take a request out of the fast batch: its committed rows (``commit`` of the last block when the sequence was
+        cut short of what the device accepted) are replayed into the recurrent state and the conv window goes back to
+        the runner's state slot (a snapshot or the packed runner continues from there)."""
+        b = self._fast_slot.pop(id(req), None)
+        if b is None:
+            return
+        self._fast_tables.pop(id(req), None)
+        conv = self.fast.release(b, commit)
+        if req.seq is not None:
+            for li, rows in conv.items():
+                self.runner.conv_state[li][req.seq.slot].copy_(rows)
+        self._fast_free.append(b)
+
+    def _fast_step(self, reqs: list[Request]) -> list[Request]:
+        if not reqs:
+            return []
+        temp = reqs[0].params.temperature
+        if self.fast is None:
+            self._fast_init(temp)
+        elif self.fast.temperature != temp:
+            self.fast.set_temperature(temp)
+        fast, T = self.fast, 1 + self.spec
+        active: list[Request] = []
+        for req in reqs:
+            if not self._ensure_blocks(req, req.computed + 2 * T):
+                if id(req) not in self._fast_slot:
+                    continue  # joins when pages are free again
+                if not self._ensure_blocks(req, req.computed + T):
+                    self._fast_release(req)
+                    self._preempt(req)
+                    continue
+            if id(req) not in self._fast_slot:
+                if not self._fast_free:
+                    continue
+                b = self._fast_free.pop()
+                self.runner.flush(req.seq)
+                conv = {li: self.runner.conv_state[li][req.seq.slot] for li in self.runner.gdn_layers}
+                fast.assign(b, req.seq.slot, req.computed, req.block_table, req.tokens[-1], conv, drafts=req.drafts)
+                req.drafts = []
+                self._fast_slot[id(req)] = b
+                self._fast_tables[id(req)] = len(req.block_table)
+            elif self._fast_tables[id(req)] != len(req.block_table):
+                fast.graph_sync()
+                fast.set_block_table(self._fast_slot[id(req)], req.block_table)
+                self._fast_tables[id(req)] = len(req.block_table)
+            active.append(req)
+        if not active:
+            return []
+        fast.step()
+        res = fast.results()
+        fast.check()
+        self.step_count += 1
+        self.metrics["steps"] += 1
+        done: list[Request] = []
+        for req in active:
+            b = self._fast_slot[id(req)]
+            if int(res.nonfinite[b]) > 0:
+                raise S.NonFiniteLogits(self.step_count, [b], [req.request_id])
+            acc = int(res.accepted[b])
+            req.computed += acc + 1
+            req.spec_drafted += self.spec
+            req.spec_accepted += acc
+            p = req.params
+            for j in range(acc + 1):
+                t = int(res.tokens[b, j])
+                req.output.append(t)
+                req.logprobs.append(float(res.logprobs[b, j]))
+                self.metrics["generation_tokens"] += 1
+                reason = FinishReason.STOP if t in p.stop_token_ids else (FinishReason.LENGTH if len(req.output) >= p.max_tokens else None)
+                if reason is not None:
+                    # tokens the device committed past this one are not part of the sequence: the caches are cut back to here
+                    req.computed -= acc - j
+                    self._fast_release(req, commit=j + 1)
+                    self._finish(req, reason)
+                    done.append(req)
+                    break
         return done
 
     # -- sampling / verification / drafting -----------------------------------------------------------------------------

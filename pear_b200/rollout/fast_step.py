@@ -270,10 +270,13 @@ class FastDecoder:
             raise ValueError("sequence needs more pages than max_blocks_per_seq")
         self.block_table[b, :n] = torch.tensor(block_table, dtype=torch.int32)
 
-    def release(self, b: int) -> dict:
-        """Take the sequence out of the batch: replay its committed rows into the recurrent state and return its conv
-        windows (layer -> [3, C]) so the prefill runner / a state snapshot can continue from them."""
+    def release(self, b: int, commit: Optional[int] = None) -> dict:
+        """Take the sequence out of the batch: replay its committed rows (``commit`` overrides how many rows of the last
+        block count) into the recurrent state and return its conv windows (layer -> [3, C]) so the prefill runner / a
+        state snapshot can continue from them."""
         self.graph_sync()
+        if commit is not None:
+            self.ncommit[b] = commit
         keep = self.ctx.clone()
         only = torch.full_like(self.ctx, -1)
         only[b] = keep[b]
@@ -291,6 +294,12 @@ class FastDecoder:
         self.ctx[b] = -1
         self.ncommit[b] = 0
         return out
+
+    def set_temperature(self, temperature: float) -> None:
+        """The temperature is a launch argument: a captured graph is dropped and re-captured."""
+        self.graph_sync()
+        self.temperature = float(temperature)
+        self.graph, self._warm = None, 0
 
     def graph_sync(self) -> None:
         torch.cuda.current_stream().synchronize()

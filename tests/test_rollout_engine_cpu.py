@@ -111,3 +111,32 @@ def test_mtp_speculative_decoding_is_lossless_for_greedy(model):
     want = greedy_oracle(model, p, 24)
     assert r.output == want
     assert r.spec_drafted > 0
+
+
+def test_lookup_keeps_matched_chain_blocks_out_of_eviction():
+    """A prefix whose head sits on the device (oldest LRU entry) and whose tail sits in the host tier: promoting the tail
+    needs a device block while the free list is empty, and must not evict (and overwrite) the matched head."""
+    from pear_b200.rollout.block_manager import BlockManager
+    from pear_b200.rollout.host_tier import HostTier
+
+    bs = 4
+    kv = [torch.zeros(4, bs, 2)]
+    mgr = BlockManager(4, bs, 4, True, needs_state=False)  # block 0 is the null block: three usable blocks
+    mgr.host_tier = HostTier(8, kv, [], pin=False)
+    toks = list(range(12))
+    blocks = [mgr.allocate() for _ in range(3)]
+    parent = None
+    for i, blk in enumerate(blocks):
+        kv[0][blk] = float(i + 1)  # block i holds the payload i + 1
+        parent = mgr.publish(blk, parent, toks[i * bs:(i + 1) * bs])
+    # tail blocks 1 and 2 leave the device first (into the host tier), then the head is released: it is the only LRU entry
+    mgr.release(blocks[1]); mgr.release(blocks[2])
+    x, y = mgr.allocate(), mgr.allocate()  # evicts blocks 1 and 2 into the host tier
+    mgr.release(blocks[0])
+    mgr.release(x)  # one unpublished free block: enough for ONE promotion; the second has only the LRU to take from
+    hit = mgr.lookup(toks)
+    assert hit.blocks[0] == blocks[0] and len(set(hit.blocks)) == len(hit.blocks), hit.blocks
+    for i, blk in enumerate(hit.blocks):
+        assert float(kv[0][blk].mean()) == float(i + 1), "a chain block was overwritten by a promotion"
+    assert hit.tokens in (4, 8)  # the head always; the tail as far as free blocks allowed
+    mgr.release(y)
