@@ -152,11 +152,73 @@ class HybridConfig:
         names = {f.name for f in dataclasses.fields(cls)}
         return cls(**{k: v for k, v in d.items() if k in names})
 
-    def save(self, path: str) -> None:
+    # Hugging Face layout of the family's config.json: the decoder's fields sit under "text_config" with the transformers
+    # names (num_hidden_layers, num_key_value_heads, linear_* for the Gated-DeltaNet mixer, partial_rotary_factor,
+    # rope_parameters with the M-RoPE sections, mtp_num_hidden_layers).
+    def to_hf_dict(self) -> dict:
+        text = {
+            "model_type": "qwen3_5_text", "vocab_size": self.vocab_size, "hidden_size": self.hidden_size, "num_hidden_layers": self.num_layers,
+            "num_attention_heads": self.num_attention_heads, "num_key_value_heads": self.num_kv_heads, "head_dim": self.head_dim,
+            "intermediate_size": self.intermediate_size, "rms_norm_eps": self.rms_eps, "hidden_act": "silu",
+            "partial_rotary_factor": self.rotary_dim / self.head_dim, "full_attention_interval": self.full_attention_interval,
+            "layer_types": list(self.layer_types), "attn_output_gate": self.attn_output_gate,
+            "rope_parameters": {"rope_type": "default", "rope_theta": self.rope_theta, "mrope_interleaved": True,
+                                "mrope_section": list(self.mrope_sections), "partial_rotary_factor": self.rotary_dim / self.head_dim},
+            "linear_num_key_heads": self.gdn_qk_heads, "linear_num_value_heads": self.gdn_v_heads, "linear_key_head_dim": self.gdn_head_dim,
+            "linear_value_head_dim": self.gdn_head_dim, "linear_conv_kernel_dim": self.conv_kernel, "mtp_num_hidden_layers": self.num_mtp_layers,
+            "initializer_range": self.init_std, "l2_norm_eps": self.l2_eps, "dtype": "bfloat16", "tie_word_embeddings": False,
+        }
+        return {"architectures": ["Qwen3_5ForConditionalGeneration"], "model_type": "qwen3_5", "text_config": text, "tie_word_embeddings": False}
+
+    @classmethod
+    def from_hf_dict(cls, d: dict) -> "HybridConfig":
+        t = d.get("text_config", d)
+        need = ("hidden_size", "num_hidden_layers", "num_attention_heads", "num_key_value_heads", "vocab_size", "intermediate_size")
+        lost = [k for k in need if k not in t]
+        if lost:
+            raise KeyError(f"config.json lacks {lost}: neither this framework's field names nor the Hugging Face text_config names were found")
+        rope = t.get("rope_parameters") or t.get("rope_scaling") or {}
+        head_dim = int(t.get("head_dim", t["hidden_size"] // t["num_attention_heads"]))
+        factor = float(rope.get("partial_rotary_factor", t.get("partial_rotary_factor", 0.25)))
+        rotary = int(round(head_dim * factor))
+        sections = tuple(rope.get("mrope_section", ())) or None
+        if sections is None or 2 * sum(sections) != rotary:
+            half = rotary // 2
+            sections = (half - 2 * (half // 3), half // 3, half // 3)
+        kd, vd = int(t.get("linear_key_head_dim", 128)), int(t.get("linear_value_head_dim", 128))
+        if kd != vd:
+            raise ValueError("Gated-DeltaNet key and value head dimensions differ: not supported")
+        kw = dict(
+            vocab_size=int(t["vocab_size"]), hidden_size=int(t["hidden_size"]), num_layers=int(t["num_hidden_layers"]),
+            num_attention_heads=int(t["num_attention_heads"]), num_kv_heads=int(t["num_key_value_heads"]), head_dim=head_dim, rotary_dim=rotary,
+            rope_theta=float(rope.get("rope_theta", t.get("rope_theta", 10_000_000.0))), mrope_sections=sections,
+            gdn_qk_heads=int(t.get("linear_num_key_heads", 16)), gdn_v_heads=int(t.get("linear_num_value_heads", 48)), gdn_head_dim=kd,
+            conv_kernel=int(t.get("linear_conv_kernel_dim", 4)), intermediate_size=int(t["intermediate_size"]), rms_eps=float(t.get("rms_norm_eps", 1e-6)),
+            l2_eps=float(t.get("l2_norm_eps", 1e-6)), num_mtp_layers=int(t.get("mtp_num_hidden_layers", 0)),
+            attn_output_gate=bool(t.get("attn_output_gate", True)), init_std=float(t.get("initializer_range", 0.02)),
+            full_attention_interval=int(t.get("full_attention_interval", 4)),
+        )
+        if t.get("layer_types"):
+            kw["layer_types"] = list(t["layer_types"])
+        return cls(**kw)
+
+    def save(self, path: str, hf: bool = True) -> None:
+        """``hf``: the Hugging Face layout (loadable by transformers-style tools); this framework's own flat field names are
+        added under "pear_b200" so nothing is lost in a round trip."""
+        d = self.to_hf_dict() if hf else self.to_dict()
+        if hf:
+            d["pear_b200"] = self.to_dict()
         with open(path, "w") as f:
-            json.dump(self.to_dict(), f, indent=1)
+            json.dump(d, f, indent=1)
 
     @classmethod
     def load(cls, path: str) -> "HybridConfig":
         with open(path) as f:
-            return cls.from_dict(json.load(f))
+            d = json.load(f)
+        if "pear_b200" in d:
+            return cls.from_dict(d["pear_b200"])
+        if "text_config" in d or "num_hidden_layers" in d:
+            return cls.from_hf_dict(d)
+        if "num_layers" not in d:
+            raise KeyError(f"{path}: not a model config of this framework nor a Hugging Face config (no num_layers / num_hidden_layers)")
+        return cls.from_dict(d)

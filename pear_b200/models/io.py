@@ -106,8 +106,31 @@ def iter_model_tensors(directory: str) -> Iterator[tuple[str, torch.Tensor]]:
             f.close()
 
 
+HF_TEXT_PREFIX = "model.language_model."  # the decoder of the family's Hugging Face checkpoints (the reference model is
+#                                            model.model.language_model.layers; its vision tower is model.visual.*, the drafter mtp.*)
+
+
+def to_hf_name(name: str) -> str:
+    """This framework's parameter name -> the Hugging Face checkpoint key."""
+    if name.startswith("model.") and not name.startswith(HF_TEXT_PREFIX) and not name.startswith("model.visual."):
+        return HF_TEXT_PREFIX + name[len("model."):]
+    if name.startswith("visual."):
+        return "model." + name
+    return name  # lm_head.weight, mtp.*
+
+
+def from_hf_name(key: str) -> str:
+    """A Hugging Face checkpoint key (or already one of this framework's names) -> this framework's parameter name."""
+    if key.startswith(HF_TEXT_PREFIX):
+        return "model." + key[len(HF_TEXT_PREFIX):]
+    if key.startswith("model.visual."):
+        return key[len("model."):]
+    return key
+
+
 def save_model_dir(directory: str, config: HybridConfig, state: dict[str, torch.Tensor], fp32_modules: Iterable[str] = (),
-                   dtype: torch.dtype = torch.bfloat16, drop_mtp: bool = True, max_shard_bytes: int = 4 << 30) -> list[str]:
+                   dtype: torch.dtype = torch.bfloat16, drop_mtp: bool = True, max_shard_bytes: int = 4 << 30, hf_names: bool = True) -> list[str]:
+    """Write a model directory: tensors under the Hugging Face key names (``hf_names``) and a Hugging Face config.json."""
     os.makedirs(directory, exist_ok=True)
     fp32_modules = tuple(fp32_modules)
     out: dict[str, torch.Tensor] = {}
@@ -115,7 +138,8 @@ def save_model_dir(directory: str, config: HybridConfig, state: dict[str, torch.
         if drop_mtp and name.startswith("mtp."):
             continue
         keep32 = any(m in name for m in fp32_modules)
-        out[name] = t.detach().to(torch.float32 if keep32 else dtype) if t.is_floating_point() else t.detach()
+        key = to_hf_name(name) if hf_names else name
+        out[key] = t.detach().to(torch.float32 if keep32 else dtype) if t.is_floating_point() else t.detach()
     shards: list[dict[str, torch.Tensor]] = [{}]
     size = 0
     for name in sorted(out):
@@ -138,25 +162,39 @@ def save_model_dir(directory: str, config: HybridConfig, state: dict[str, torch.
             weight_map.update({k: fn for k in sh})
         with open(os.path.join(directory, "model.safetensors.index.json"), "w") as fh:
             json.dump({"metadata": {"total_size": sum(t.numel() * t.element_size() for t in out.values())}, "weight_map": weight_map}, fh)
-    config.save(os.path.join(directory, "config.json"))
+    config.save(os.path.join(directory, "config.json"), hf=hf_names)
     return files
 
 
-def load_model_dir(directory: str, model: torch.nn.Module, strict: bool = False) -> tuple[list[str], list[str]]:
-    """Copy a model directory's tensors into ``model`` in place. Returns (missing, unexpected) names."""
+def load_model_dir(directory: str, model: torch.nn.Module, strict: bool = True, allow_missing: Iterable[str] = (),
+                   ignore_unexpected: Iterable[str] = ("visual.", "mtp.")) -> tuple[list[str], list[str]]:
+    """Copy a model directory's tensors into ``model`` in place; keys may be Hugging Face names or this framework's own.
+    Returns (missing, unexpected) names. With ``strict`` (the default) a parameter of the model that the directory does not
+    provide raises unless its name starts with one of ``allow_missing``, and so does a tensor of the directory the model has
+    no place for unless it starts with one of ``ignore_unexpected`` (a text-only model reading a checkpoint that also
+    carries the vision tower or the drafter): a model must never come up partly random without anybody noticing. A shape
+    mismatch always raises."""
     own = dict(model.state_dict())
     seen = set()
     unexpected = []
     with torch.no_grad():
-        for name, t in iter_model_tensors(directory):
+        for key, t in iter_model_tensors(directory):
+            name = from_hf_name(key)
             if name in own:
+                if tuple(own[name].shape) != tuple(t.shape):
+                    raise ValueError(f"{directory}: tensor {key} has shape {tuple(t.shape)}, the model expects {tuple(own[name].shape)}")
                 own[name].copy_(t.to(own[name].dtype))
                 seen.add(name)
             else:
                 unexpected.append(name)
     missing = [k for k in own if k not in seen]
-    if strict and (missing or unexpected):
-        raise KeyError(f"missing {missing[:5]}, unexpected {unexpected[:5]}")
+    if strict:
+        allow_missing, ignore_unexpected = tuple(allow_missing), tuple(ignore_unexpected)
+        bad_missing = [k for k in missing if not k.startswith(allow_missing)] if allow_missing else missing
+        bad_unexpected = [k for k in unexpected if not k.startswith(ignore_unexpected)] if ignore_unexpected else unexpected
+        if bad_missing or bad_unexpected:
+            raise KeyError(f"{directory} does not match the model: {len(bad_missing)} parameters missing (first: {bad_missing[:4]}), "
+                           f"{len(bad_unexpected)} tensors unexpected (first: {bad_unexpected[:4]})")
     return missing, unexpected
 
 

@@ -1,0 +1,63 @@
+"""Model directories in the Hugging Face layout: key names, config translation, strict loading."""
+
+import json
+import os
+
+import pytest
+import torch
+
+from pear_b200.models import io as model_io
+from pear_b200.models.config import HybridConfig
+from pear_b200.models.hybrid import HybridForCausalLM
+
+
+def test_export_uses_hf_names_and_round_trips(tmp_path):
+    cfg = HybridConfig.tiny()
+    model = HybridForCausalLM(cfg).init_weights(2)
+    out = str(tmp_path / "export")
+    model_io.save_model_dir(out, cfg, model.state_dict(), dtype=torch.float32, drop_mtp=False)
+    keys = set(model_io.load_safetensors(os.path.join(out, "model.safetensors")))
+    assert "model.language_model.layers.0.linear_attn.in_proj_qkv.weight" in keys
+    assert "model.language_model.embed_tokens.weight" in keys and "lm_head.weight" in keys and "mtp.fc.weight" in keys
+    assert not any(k.startswith("model.layers.") for k in keys)
+    hf = json.load(open(os.path.join(out, "config.json")))
+    t = hf["text_config"]
+    assert (t["num_hidden_layers"], t["num_key_value_heads"], t["linear_num_value_heads"]) == (cfg.num_layers, cfg.num_kv_heads, cfg.gdn_v_heads)
+    back = HybridForCausalLM(model_io.load_config(out))
+    missing, unexpected = model_io.load_model_dir(out, back)
+    assert not missing and not unexpected
+    assert all(torch.equal(a, b) for a, b in zip(model.state_dict().values(), back.state_dict().values()))
+
+
+def test_plain_hf_config_is_translated(tmp_path):
+    """A config.json with only the transformers field names (no field of this framework) yields the same model shape."""
+    cfg = HybridConfig.tiny()
+    d = cfg.to_hf_dict()
+    path = str(tmp_path / "config.json")
+    json.dump(d, open(path, "w"))
+    got = HybridConfig.load(path)
+    assert got.to_dict() == cfg.to_dict()
+    with pytest.raises(KeyError):
+        json.dump({"hidden_size": 8}, open(path, "w"))
+        HybridConfig.load(path)
+
+
+def test_loading_a_directory_that_does_not_match_raises(tmp_path):
+    cfg = HybridConfig.tiny()
+    model = HybridForCausalLM(cfg, with_mtp=False).init_weights(2)
+    state = model.state_dict()
+    out = str(tmp_path / "partial")
+    model_io.save_model_dir(out, cfg, {k: v for k, v in state.items() if "layers.2." not in k}, dtype=torch.float32)
+    fresh = HybridForCausalLM(cfg, with_mtp=False)
+    with pytest.raises(KeyError, match="parameters missing"):
+        model_io.load_model_dir(out, fresh)
+    missing, _ = model_io.load_model_dir(out, fresh, strict=False)
+    assert missing and all("layers.2." in k for k in missing)
+    # a checkpoint that also carries the drafter and a vision tower loads into a text-only model without complaint
+    full = HybridForCausalLM(cfg).init_weights(2).state_dict()
+    full["visual.patch_embed.weight"] = torch.zeros(4, 4)
+    out2 = str(tmp_path / "full")
+    model_io.save_model_dir(out2, cfg, full, dtype=torch.float32, drop_mtp=False)
+    assert "model.visual.patch_embed.weight" in model_io.load_safetensors(os.path.join(out2, "model.safetensors"))
+    missing, unexpected = model_io.load_model_dir(out2, fresh)
+    assert not missing and all(k.startswith(("mtp.", "visual.")) for k in unexpected)
