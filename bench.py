@@ -333,6 +333,97 @@ def run_megakernel(args, local_rank: int) -> dict:
             "frac_of_copy_bw": round(stats["weight_bytes"] / 1e9 / (ms / steps / 1e3) / hbm, 3), "clocks": clocks}
 
 
+# ---------------------------------------------------------------------------------------------------------------------
+# component timings (not the headline): trainer step on one GPU, Gated-DeltaNet scan
+# ---------------------------------------------------------------------------------------------------------------------
+def run_trainer_step(args) -> dict:
+    """Forward + backward + optimizer step of the trainer engine on one GPU for ``--layers`` layers of the 27B shape over a
+    packed batch of ``--tokens`` tokens (synthetic tokens, random init), CUDA events; ``--breakdown N`` adds the N kernels
+    with the most device time of one more step under the torch profiler (after the timed region, on stderr)."""
+    import torch
+
+    from pear_b200.models.config import HybridConfig
+    from pear_b200.train.engine import EngineConfig, TrainEngine, synthetic_batch
+
+    cfg = HybridConfig(num_layers=args.layers, vocab_size=args.vocab)  # the 27B per-layer shape
+    ecfg = EngineConfig(lr=1e-6, param_dtype="bf16", enable_gradient_checkpointing=True, topk_log_probs=0,
+                        gradient_checkpointing_retain_attention=args.retain_attention)
+    eng = TrainEngine(cfg, ecfg, device="cuda", seed=0)
+    batches = [synthetic_batch(cfg, args.tokens, args.seqs, 0, s).to("cuda") for s in range(2)]
+
+    def step(i: int) -> dict:
+        m = eng.forward_backward_batch([batches[i % 2]])
+        m.update(eng.optimizer_step())
+        return m
+
+    for i in range(max(3, args.warmup)):
+        step(i)
+    torch.cuda.synchronize()
+    sampler = ClockSampler(0)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        m = step(i)
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1) / args.steps
+    flops = 3.0 * cfg.flops_per_token(context=args.tokens // args.seqs // 2) * args.tokens  # fwd + 2x bwd (recompute not counted)
+    out = {"metric": "trainer step tokens/s (1 GPU)", "layers": args.layers, "tokens": args.tokens, "seqs": args.seqs, "ms_per_step": round(ms, 2),
+           "tokens_per_s": round(args.tokens / ms * 1e3, 1), "model_tflops": round(flops / ms / 1e9, 1), "grad_norm": float(m.get("actor/grad_norm", 0.0)),
+           "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2**30, 2), "data": "synthetic", "dtype": "bf16 operands, fp32 residual and head",
+           "clocks": clocks}
+    peaks = load_peaks()
+    if peaks:
+        out["frac_of_measured_bf16_sustained"] = round(out["model_tflops"] / peaks["bf16_tflops_sustained"], 3)
+    if args.breakdown:
+        from torch.profiler import ProfilerActivity, profile
+
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            step(0)
+            torch.cuda.synchronize()
+        print(prof.key_averages().table(sort_by="cuda_time_total", row_limit=args.breakdown, max_name_column_width=70), file=sys.stderr)
+    return out
+
+
+def run_gdn_scan(args) -> dict:
+    """The Gated-DeltaNet scan of one sequence without gradients: the chunk-loop kernel path against the torch loop."""
+    import torch
+
+    from pear_b200.ops import kernels as K
+    from pear_b200.ops import reference as ref
+
+    g = torch.Generator(device="cuda").manual_seed(0)
+    t, hk, hv, d = args.tokens, 16, 48, 128
+    q = ref.l2norm(torch.randn(t, hk, d, device="cuda", generator=g)) * d ** -0.5
+    k = ref.l2norm(torch.randn(t, hk, d, device="cuda", generator=g))
+    v = torch.randn(t, hv, d, device="cuda", generator=g)
+    gate = -torch.rand(t, hv, device="cuda", generator=g) * 0.2
+    beta = torch.rand(t, hv, device="cuda", generator=g)
+
+    def timed(fn, n=5):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    with torch.no_grad():
+        kernel_ms = timed(lambda: K.gdn_scan(q, k, v, gate, beta))
+        torch_ms = timed(lambda: ref.gdn_chunked(q, k, v, gate, beta))
+        operands_ms = timed(lambda: ref.gdn_chunk_operands(q, k, v, gate, beta))
+        o1, _ = K.gdn_scan(q, k, v, gate, beta)
+        o2, _ = ref.gdn_chunked(q, k, v, gate, beta)
+    return {"op": "gdn_scan", "tokens": t, "value_heads": hv, "kernel_path_ms": round(kernel_ms, 3), "torch_loop_ms": round(torch_ms, 3),
+            "operands_ms": round(operands_ms, 3), "max_abs_diff": float((o1 - o2).abs().max())}
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -349,9 +440,20 @@ def main() -> None:
     ap.add_argument("--ar-mode", default="auto", choices=["auto", "one", "two"], help="form of the fused all-reduce + add + RMSNorm (N > 1)")
     ap.add_argument("--no-graph", action="store_true", help="launch every step eagerly (kernel-by-kernel profiling); the headline uses graph replay")
     ap.add_argument("--small", action="store_true", help="4-layer model of the 27B layer shape (smoke runs only; not the headline)")
+    ap.add_argument("--trainer-step", action="store_true", help="component timing: trainer engine step on one GPU (prints its own JSON line)")
+    ap.add_argument("--gdn-scan", action="store_true", help="component timing: Gated-DeltaNet scan of one sequence (prints its own JSON line)")
+    ap.add_argument("--layers", type=int, default=4)
+    ap.add_argument("--tokens", type=int, default=4096)
+    ap.add_argument("--seqs", type=int, default=2)
+    ap.add_argument("--vocab", type=int, default=32768)
+    ap.add_argument("--retain-attention", action="store_true")
+    ap.add_argument("--breakdown", type=int, default=0)
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm()
+        return
+    if args.trainer_step or args.gdn_scan:
+        print(json.dumps(run_trainer_step(args) if args.trainer_step else run_gdn_scan(args)))
         return
 
     import torch

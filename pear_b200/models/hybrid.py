@@ -23,9 +23,14 @@ from ..ops import api as ops
 from .config import HybridConfig
 
 
-def linear_fp32(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+def linear_fp32(x: torch.Tensor, weight: torch.Tensor, output_unused: bool = False) -> torch.Tensor:
     """``x @ weight^T`` with the operands in the weight's dtype and an fp32 result."""
-    return ops.linear(x, weight)
+    return ops.linear(x, weight, output_unused)
+
+
+# Set by the layer runner around the recompute pass of a checkpointed layer: the value of the layer's LAST GEMM (the MLP's
+# down projection) is never read there (only its backward runs), so its forward is skipped (upstream trainer/mlp.py:132-134).
+RECOMPUTE: dict = {"skip_down_proj": False}
 
 
 class RMSNorm(nn.Module):
@@ -92,8 +97,8 @@ def reduce_add_rms_norm(partial: torch.Tensor, residual: torch.Tensor, weight: t
     return ops.add_rms_norm(reduce_partial(partial), residual, weight, eps)
 
 
-def row_linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
-    y = linear_fp32(x, weight)
+def row_linear(x: torch.Tensor, weight: torch.Tensor, output_unused: bool = False) -> torch.Tensor:
+    y = linear_fp32(x, weight, output_unused)
     return y if _TP["defer"] else reduce_partial(y)
 
 
@@ -106,7 +111,7 @@ class SwiGLUMLP(nn.Module):
 
     def forward(self, y: torch.Tensor) -> torch.Tensor:
         act = ops.swiglu(linear_fp32(y, self.gate_proj.weight), linear_fp32(y, self.up_proj.weight))
-        return row_linear(act, self.down_proj.weight)
+        return row_linear(act, self.down_proj.weight, output_unused=RECOMPUTE["skip_down_proj"] and torch.is_grad_enabled())
 
 
 @dataclass

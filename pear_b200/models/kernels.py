@@ -28,32 +28,32 @@ class TrainingKernels(ABC):
     @classmethod
     @abstractmethod
     def check_config(cls, engine_config) -> None:
-        """Raise unless the engine config is one the GPU backend computes under, before the module is built."""
+        """Called first, with the trainer engine's config and no module yet: refuse (raise) settings the family's GPU code cannot honour."""
 
     @classmethod
     @abstractmethod
     def install(cls, module, fp32_residual: bool, use_fused_kernels: bool, fused_kernels_backend) -> None:
-        """Apply what the family installs on any device, before the module is sharded."""
+        """Device-independent changes to the freshly built, still unsharded module (precision of the residual stream, which head it uses)."""
 
     @classmethod
     @abstractmethod
     def check_model(cls, module, use_remove_padding: bool, use_fused_kernels: bool, fused_kernels_backend) -> None:
-        """Raise unless the module runs the paths the GPU backend replaces."""
+        """Second check, now with the module: the options chosen must be the ones whose code paths the family's kernels stand in for."""
 
     @classmethod
     @abstractmethod
     def install_gpu_backend(cls, module) -> None:
-        """Patch the module with the backend of the process's GPU after install(), before sharding."""
+        """Select the kernels for the GPU this process sees; runs after ``install`` and before the parameters are sharded."""
 
     @classmethod
     @abstractmethod
     def install_checkpointing(cls, module) -> None:
-        """Extend the module's gradient checkpoints with what the GPU backend needs in a recompute."""
+        """Tell the gradient-checkpointing layer runner what this family's recompute pass may leave out or must keep."""
 
     @classmethod
     @abstractmethod
     def run_checked(cls, run: Callable[[], Any], before_rerun: Callable[[], None]) -> Any:
-        """The result of run() on the fast path, or after before_rerun() of a second run() off it."""
+        """Call ``run``; if its result shows the fast numeric path failed (non-finite loss), call ``before_rerun`` and run once more on the safe path."""
 
 
 class _Exported(ABC):
@@ -81,17 +81,17 @@ class RolloutKernels(_Exported):
     @classmethod
     @abstractmethod
     def configure_server(cls, engine_config: dict, max_num_seqs: int, max_num_batched_tokens: int) -> None:
-        """Settings of the process that builds the engine config (graph capture sizes, block size ...)."""
+        """Fill in the engine settings this family needs (KV page size, batched-step switch, token budget) in the launcher's process."""
 
     @classmethod
     @abstractmethod
     def install_worker(cls, engine) -> None:
-        """Install the family's kernels in a worker before it builds its model."""
+        """Runs inside a replica before its model exists: load the kernel library so a missing build fails here, not mid-step."""
 
     @classmethod
     @abstractmethod
     def check_model(cls, model, engine_config) -> None:
-        """Raise unless a worker built the family's model."""
+        """Refuse a replica whose model is not the architecture these kernels were written for."""
 
 
 class DeployKernels(_Exported):

@@ -12,9 +12,11 @@ class Qwen3_5RolloutKernels(RolloutKernels):
     def configure_server(cls, engine_config: dict, max_num_seqs: int, max_num_batched_tokens: int) -> None:
         REQUIREMENTS.check_rollout(engine_config)
         engine_config.setdefault("block_size", 16)
-        # decode steps replay CUDA graphs captured at these token counts; larger (prefill) steps launch eagerly
-        sizes = [s for s in (1, 2, 4, 8, 16, 32, 64, 128, 256) if s <= max(1, max_num_seqs * 8)]
-        engine_config.setdefault("cudagraph_capture_sizes", sizes)
+        # decode / verify rows run the batched GPU-resident step (rollout/fast_step.py). It has ONE shape, max_num_seqs x
+        # (1 + drafts) rows with empty batch slots skipped inside every kernel, so a single captured CUDA graph serves every
+        # batch size (upstream captures one graph per token-count bucket: rollout/blackwell/cudagraph.py:4-34)
+        engine_config.setdefault("fast_decode", True)
+        engine_config["max_num_seqs"] = max_num_seqs
         engine_config["max_num_batched_tokens"] = max_num_batched_tokens
 
     @classmethod

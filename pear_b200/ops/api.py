@@ -26,17 +26,21 @@ def _cuda(*tensors) -> bool:
 
 # when set (tests, baseline arm of a benchmark) CUDA tensors also take the torch statement
 FORCE_REFERENCE = False
-PRECISE_OPERANDS = False  # set during an overflow rerun: GEMM operands stay fp32 instead of bf16
+PRECISE_OPERANDS = False  # set during an overflow rerun: GEMM operands stay fp32 (IEEE fp32 library GEMM) instead of bf16
 
 
 def _use_kernels(*tensors) -> bool:
     return _cuda(*tensors) and not FORCE_REFERENCE
 
 
-def linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
-    """``x @ weight^T`` with operands in the weight's dtype, fp32 result."""
+def linear(x: torch.Tensor, weight: torch.Tensor, output_unused: bool = False) -> torch.Tensor:
+    """``x @ weight^T`` with operands in the weight's dtype, fp32 result. While ``PRECISE_OPERANDS`` is set (the rerun of
+    a batch whose fast pass produced a non-finite loss) both operands are taken to fp32 and multiplied without any
+    reduced-precision tensor-core mode: slower, with the full fp32 range and mantissa."""
+    if PRECISE_OPERANDS:
+        return F.linear(x.float(), weight.float())
     if _use_kernels(x, weight) and weight.dtype == torch.bfloat16:
-        return _k().linear_bf16(x, weight)
+        return _k().linear_bf16(x, weight, output_unused)
     return F.linear(x.to(weight.dtype), weight).float()
 
 

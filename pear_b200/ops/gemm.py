@@ -72,12 +72,15 @@ def gemm_status(device=None) -> int:
 
 class _LinearBF16(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, weight):
+    def forward(ctx, x, weight, output_unused=False):
         shape = x.shape
         x2 = x.reshape(-1, shape[-1]).to(torch.bfloat16)
         ctx.save_for_backward(x2, weight)
         ctx.in_dtype, ctx.shape = x.dtype, shape
-        y = gemm_nt(x2, weight, torch.float32)
+        if output_unused:  # a checkpoint recompute whose caller only backpropagates through this node: no GEMM
+            y = torch.empty(x2.shape[0], weight.shape[0], dtype=torch.float32, device=x.device)
+        else:
+            y = gemm_nt(x2, weight, torch.float32)
         return y.view(*shape[:-1], weight.shape[0])
 
     @staticmethod
@@ -89,13 +92,15 @@ class _LinearBF16(torch.autograd.Function):
             dx = (dy2 @ weight).to(ctx.in_dtype).view(ctx.shape)
         if ctx.needs_input_grad[1]:
             dw = (dy2.t() @ x2).to(weight.dtype)
-        return dx, dw
+        return dx, dw, None
 
 
-def linear_bf16(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+def linear_bf16(x: torch.Tensor, weight: torch.Tensor, output_unused: bool = False) -> torch.Tensor:
+    """``output_unused``: the forward value is never read (the last GEMM of a layer inside a checkpoint recompute, upstream
+    ``trainer/mlp.py:132-134``): the node is built for the backward, the forward GEMM is skipped."""
     if weight.shape[1] % 8 or x.numel() == 0:
         return torch.nn.functional.linear(x.to(weight.dtype), weight).float()
-    return _LinearBF16.apply(x, weight)
+    return _LinearBF16.apply(x, weight, output_unused)
 
 
 def _main() -> None:

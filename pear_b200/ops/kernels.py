@@ -1,8 +1,8 @@
 """Autograd bindings of the sm_100a kernels in ``csrc/`` (library loaded by :mod:`pear_b200.ops.lib`).
 
 Each op is a :class:`torch.autograd.Function` whose forward and backward launch the hand-written kernels on the current
-stream. Ops that do not have a kernel yet run the torch statement on the device (cuBLAS / SDPA library calls) and are
-listed in ``LIBRARY_FALLBACKS`` so reports can say so.
+stream. What still runs a library kernel is named where it happens: the backward GEMM forms of ``ops/gemm.py`` (cuBLAS),
+the attention backward of ``ops/attention.py`` (FlashAttention-2), the chunk-local operands of the delta-rule scan (torch).
 """
 
 from __future__ import annotations
@@ -16,8 +16,6 @@ from . import reference as ref
 from .lib import check, count_launch, lib, ptr, stream
 
 DT_F32, DT_BF16 = 0, 1
-LIBRARY_FALLBACKS = {"causal_attention": "torch SDPA", "causal_conv_silu": "torch", "gdn_scan": "torch chunked scan",
-                     "logprob_entropy": "torch chunked (cuBLAS)"}
 
 
 def _dt(t: torch.Tensor) -> int:
@@ -192,10 +190,10 @@ def apply_rope(x, cos, sin):
 # ---------------------------------------------------------------------------------------------------------------------
 # GEMM: tcgen05 kernel when the shape qualifies, cuBLAS otherwise
 # ---------------------------------------------------------------------------------------------------------------------
-def linear_bf16(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+def linear_bf16(x: torch.Tensor, weight: torch.Tensor, output_unused: bool = False) -> torch.Tensor:
     from . import gemm
 
-    return gemm.linear_bf16(x, weight)
+    return gemm.linear_bf16(x, weight, output_unused)
 
 
 # ---------------------------------------------------------------------------------------------------------------------

@@ -17,12 +17,14 @@ import torch
 class LayerRunner:
     """Callable ``(index, layer, residual, meta) -> residual`` installed on the model as ``layer_runner``."""
 
-    def __init__(self, sharded=None, offload=None, checkpoint: bool = True, retain_attention: bool = False):
+    def __init__(self, sharded=None, offload=None, checkpoint: bool = True, retain_attention: bool = False, skip_down_proj: bool = False):
         self.sharded = sharded
         self.offload = offload
         self.checkpoint = checkpoint
         # keep the attention outputs of the graph-free pass for the recompute pass (GPU attention kernel only)
         self.retain_attention = retain_attention
+        # the recompute pass skips the forward of the layer's last GEMM (its value is never read there)
+        self.skip_down_proj = skip_down_proj
         self.last_micro_batch = True
 
     def unit(self, i: int):
@@ -80,6 +82,9 @@ class _CheckpointedLayer(torch.autograd.Function):
         else:
             r = ctx.saved
         r = r.detach().requires_grad_(True)
+        from ..models import hybrid
+
+        prev_skip, hybrid.RECOMPUTE["skip_down_proj"] = hybrid.RECOMPUTE["skip_down_proj"], runner.skip_down_proj
         with torch.enable_grad():
             if ctx.attn_box:
                 from ..ops.attention import retain_attention
@@ -88,6 +93,7 @@ class _CheckpointedLayer(torch.autograd.Function):
                     out = layer(r, meta)
             else:
                 out = layer(r, meta)
+        hybrid.RECOMPUTE["skip_down_proj"] = prev_skip
         torch.autograd.backward(out, grad_out)
         if u is not None:
             u.reduce_grads(runner.last_micro_batch)

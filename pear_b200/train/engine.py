@@ -187,7 +187,8 @@ class TrainEngine:
                                     self.device)
         self.offload = CheckpointInputOffload(True) if cfg.enable_activation_offload else None
         self.runner = LayerRunner(self.sharded, self.offload, cfg.enable_gradient_checkpointing,
-                                  retain_attention=cfg.gradient_checkpointing_retain_attention)
+                                  retain_attention=cfg.gradient_checkpointing_retain_attention,
+                                  skip_down_proj=bool(getattr(model, "recompute_skips_down_proj", False)))
         install_runner(model, self.runner)
         self.fused_adamw = (not cfg.streamed_adamw) and self.device.type == "cuda" and cfg.fused_adamw
         opt_cls = StreamedAdamW if cfg.streamed_adamw else (FusedAdamW if self.fused_adamw else torch.optim.AdamW)
@@ -222,7 +223,10 @@ class TrainEngine:
         use_sc = cfg.loss.score_centering and loc.head_ids is not None
         if use_sc:
             ids = torch.cat([ids, loc.head_ids.long()], dim=1)
-        lp, ent = ops.logprob_entropy(hidden, self.model.lm_head.weight, ids, cfg.temperature, cfg.head_chunk)
+        if getattr(self.model, "use_fused_head", True):  # chunked: the [tokens, vocabulary] logits never exist whole
+            lp, ent = ops.logprob_entropy(hidden, self.model.lm_head.weight, ids, cfg.temperature, cfg.head_chunk)
+        else:
+            lp, ent = ops.ref.logprob_entropy_dense(hidden, self.model.lm_head.weight, ids, cfg.temperature)
         loss, metrics = grpo.policy_loss(
             lp[:, 0], loc.advantages, loc.loss_mask, cfg.loss, head_log_probs=lp[:, 1:] if use_sc else None,
             sampler_head_log_probs=loc.head_log_probs if use_sc else None, sampler_log_probs=loc.sampler_log_probs,
@@ -325,3 +329,21 @@ class TrainEngine:
         self.step_count, self.policy_version = st["step"], st["policy_version"]
         for g in self.optimizer.param_groups:  # the configured LR, at the restored schedule position
             g["lr"] = self._lr_at(self.step_count)
+
+
+def synthetic_batch(cfg: HybridConfig, tokens: int, seqs: int, topk: int, seed: int) -> PackedBatch:
+    """A packed micro-batch of uniform-random token ids in ``seqs`` equal sequences, N(0, 1) advantages on the second half of
+    each sequence (the "response"): the synthetic data of the trainer benchmarks and GPU tests."""
+    g = torch.Generator().manual_seed(seed)
+    per = tokens // seqs
+    cu = [i * per for i in range(seqs)] + [tokens]
+    ids = torch.randint(0, cfg.vocab_size, (tokens,), generator=g)
+    pos = torch.cat([torch.arange(e - s) for s, e in zip(cu[:-1], cu[1:])])
+    mask = torch.ones(tokens)
+    for s, e in zip(cu[:-1], cu[1:]):
+        mask[s: s + (e - s) // 2] = 0
+        mask[e - 1] = 0
+    return PackedBatch(ids, pos, cu, torch.roll(ids, -1), mask, torch.randn(tokens, generator=g) * mask,
+                       sampler_log_probs=-torch.rand(tokens, generator=g) * 3,
+                       head_ids=torch.randint(0, cfg.vocab_size, (tokens, topk), generator=g, dtype=torch.int32) if topk else None,
+                       head_log_probs=torch.log_softmax(torch.randn(tokens, topk + 2, generator=g), -1)[:, :topk] if topk else None)

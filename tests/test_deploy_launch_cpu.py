@@ -29,7 +29,7 @@ def test_deploy_and_rollout_kernel_facades_check_their_configs():
         Qwen3_5DeployKernels.configure_server({}, 4, 8192)
     rcfg = {"tensor_parallel_size": 2}
     Qwen3_5RolloutKernels.configure_server(rcfg, 64, 8192)
-    assert rcfg["block_size"] == 16 and rcfg["cudagraph_capture_sizes"][0] == 1
+    assert rcfg["block_size"] == 16 and rcfg["fast_decode"] is True and rcfg["max_num_seqs"] == 64
     with pytest.raises(ValueError, match="power of two"):
         REQUIREMENTS.check_rollout({"tensor_parallel_size": 3})
     with pytest.raises(ValueError, match="16-token blocks"):

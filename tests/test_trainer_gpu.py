@@ -34,7 +34,7 @@ def test_retained_attention_outputs_give_the_same_gradients():
 
     from pear_b200.models.config import HybridConfig
     from pear_b200.ops import lib as kl
-    from pear_b200.train.bench_step import synthetic_batch
+    from pear_b200.train.engine import synthetic_batch
     from pear_b200.train.engine import EngineConfig, TrainEngine
 
     cfg = HybridConfig(vocab_size=2048, hidden_size=512, num_layers=4, num_attention_heads=4, num_kv_heads=1, head_dim=256, rotary_dim=64,
