@@ -13,6 +13,9 @@ import os
 from dataclasses import dataclass, field
 
 
+ROLLOUT_PORT, ENV_PORT = 8100, 8200  # replica i serves on ROLLOUT_PORT + i, environment host j on ENV_PORT + j
+
+
 @dataclass
 class RolePlan:
     role: str
@@ -36,7 +39,8 @@ def plan_node(n_gpus: int, trainer_gpus: int, rollout_tp: int, recipe: str, over
         RolePlan("trainer", trainer_gpus, 1, 0, "pear_b200.train.main", [recipe] + overrides),
         RolePlan("rollout", replicas, rollout_tp, trainer_gpus, "pear_b200.rollout.server", overrides),
         RolePlan("env", env_hosts, 0, 0, "pear_b200.sim.server", []),
-        RolePlan("monitor", 1, 0, 0, "pear_b200.monitor.progress_panel", []),
+        RolePlan("monitor", 1, 0, 0, "pear_b200.monitor.progress_panel",
+                 overrides + [a for i in range(replicas) for a in ("--replica", f"replica-{i}=http://127.0.0.1:{ROLLOUT_PORT + i}/metrics")]),
     ]
 
 
@@ -62,6 +66,10 @@ def command(plan: RolePlan, index: int, master_port: int = 29500) -> tuple[list[
         env = gpu_process_env(list(range(plan.gpu_offset, plan.gpu_offset + plan.processes)))
     else:
         cmd = ["python", "-m", plan.module] + plan.args
+        if plan.role == "rollout":
+            cmd += ["--port", str(ROLLOUT_PORT + index), "--name", f"replica-{index}"]
+        elif plan.role == "env":
+            cmd += ["--port", str(ENV_PORT + index)]
     return cmd, env
 
 

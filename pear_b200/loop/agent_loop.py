@@ -43,6 +43,12 @@ class AgentLoopConfig:
     topk_heads: int = 0              # rollout top-k head ids / log-probs kept for score centering
     max_model_len: int = 4096
     log_dir: Optional[str] = None
+    # synthetic benchmarks with a random-init policy: play `synthetic_turns` turns with a no-op action whatever the answer
+    # says, at most `turn_max_tokens` sampled tokens per turn (0: the episode budget), and draw the reward ("hash": a seeded
+    # hash of the sampled tokens mapped to {0, 1}; "bernoulli:p": a seeded coin per trajectory) instead of the env's success
+    synthetic_turns: int = 0
+    turn_max_tokens: int = 0
+    synthetic_reward: Optional[str] = None
 
 
 class AgentLoop:
@@ -123,6 +129,11 @@ class AgentLoop:
             while state != LoopState.TERMINATED:
                 if state == LoopState.GENERATING:
                     left = min(cfg.token_budget - ep.response_tokens, cfg.max_model_len - len(ep.tokens))
+                    if cfg.turn_max_tokens > 0:
+                        left = min(left, cfg.turn_max_tokens)
+                    if cfg.synthetic_turns > 0 and ep.turns >= cfg.synthetic_turns:
+                        ep.end_reason, state = EndReason.ENV, LoopState.TERMINATED
+                        continue
                     if left <= 0 or ep.turns >= cfg.max_turns:
                         ep.end_reason, state = EndReason.BUDGET, LoopState.TERMINATED
                         continue
@@ -137,6 +148,9 @@ class AgentLoop:
                     self._append(ep, req.output, 1, req.logprobs, req.topk_ids or None, req.topk_logprobs or None, req.policy_version)
                     ep.turns += 1
                     self._log_turn(ep, state, sampled=len(req.output), seconds=round(time.time() - t0, 4), finish=req.finish.value)
+                    if cfg.synthetic_turns > 0:  # the answer is not parsed: a no-op action keeps the episode going
+                        action, state = {"move": 0}, LoopState.PROCESSING_TOOLS
+                        continue
                     if req.finish == FinishReason.LENGTH:
                         ep.end_reason, state = EndReason.BUDGET, LoopState.TERMINATED
                         continue
@@ -159,8 +173,23 @@ class AgentLoop:
         finally:
             tool.close()
 
+    def _reward(self, ep: Episode) -> float:
+        mode = self.cfg.synthetic_reward
+        if not mode:
+            return float(ep.success)
+        import hashlib
+
+        if mode == "hash":
+            sampled = np.asarray([t for t, m in zip(ep.tokens, ep.response_mask) if m], dtype=np.int64)
+            return float(hashlib.blake2b(sampled.tobytes(), digest_size=8, key=b"pear-reward").digest()[0] & 1)
+        if mode.startswith("bernoulli:"):
+            p = float(mode.split(":", 1)[1])
+            h = int.from_bytes(hashlib.blake2b(f"{ep.uid}/{ep.session}".encode(), digest_size=8, key=b"pear-reward").digest(), "little")
+            return float((h >> 11) / float(1 << 53) < p)
+        raise ValueError(f"unknown synthetic_reward {mode!r}")
+
     def _publish(self, ep: Episode) -> None:
-        reward = float(ep.success)
+        reward = self._reward(ep)
         if self.queue is not None:
             key = f"{ep.uid}/{ep.session}"
             self.queue.put_trajectory(key, {

@@ -74,3 +74,34 @@ class ProgressPanel:
         self.stop_flag.set()
         if self.thread is not None:
             self.thread.join(timeout=5)
+
+
+def main(argv=None) -> int:
+    """``python -m pear_b200.monitor.progress_panel --run-dir runs/x --replica replica-0=http://127.0.0.1:8100/metrics``: the
+    monitor role as a process of its own: scrape the replicas, follow ``train.log`` and write ``progress.json`` /
+    ``progress.log`` every ``--interval`` seconds until terminated (``--ticks N``: stop after N ticks)."""
+    import argparse
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--run-dir", default=None)
+    ap.add_argument("--replica", action="append", default=[], help="name=URL of a replica's /metrics (repeatable)")
+    ap.add_argument("--interval", type=float, default=10.0)
+    ap.add_argument("--ticks", type=int, default=0)
+    args, overrides = ap.parse_known_args(argv)
+    kv = dict(o.split("=", 1) for o in overrides if "=" in o and not o.startswith("-"))
+    run_dir = args.run_dir or kv.get("run_dir", "runs/default")
+    os.makedirs(run_dir, exist_ok=True)
+    sources = dict(r.split("=", 1) for r in args.replica)
+    panel = ProgressPanel(run_dir, MetricsScraper(sources) if sources else None, None, args.interval)
+    n = 0
+    while args.ticks <= 0 or n < args.ticks:
+        panel.tick()
+        n += 1
+        if args.ticks > 0 and n >= args.ticks:
+            break
+        time.sleep(args.interval)
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

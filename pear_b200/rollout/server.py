@@ -187,3 +187,65 @@ class RolloutServer:
 
 def build_server(model, cfg: Optional[EngineConfig] = None, device="cpu", **kw) -> RolloutServer:
     return RolloutServer(RolloutEngine(model, cfg or EngineConfig(), device), **kw)
+
+
+def load_rollout_model(path: str, dtype: torch.dtype = torch.bfloat16, device: str = "cpu", with_mtp: bool = True, seed: int = 0):
+    """``preset:<name>`` (random init of a ``HybridConfig`` preset) or a model directory in the Hugging Face layout."""
+    from ..models import io as model_io
+    from ..models.config import HybridConfig
+    from ..models.hybrid import HybridForCausalLM
+
+    if path.startswith("preset:"):
+        cfg = getattr(HybridConfig, path.split(":", 1)[1])()
+        model = HybridForCausalLM(cfg, with_mtp=with_mtp and cfg.num_mtp_layers > 0).init_weights(seed)
+    else:
+        cfg = model_io.load_config(path)
+        model = HybridForCausalLM(cfg, with_mtp=False)
+        model_io.load_model_dir(path, model)
+    if device != "cpu":
+        model = model.to(device)
+        for name, p in model.named_parameters():
+            if p.dim() >= 2 and "conv1d" not in name:
+                p.data = p.data.to(dtype)
+    return model.eval()
+
+
+def main(argv=None) -> int:
+    """``python -m pear_b200.rollout.server --model preset:tiny --port 8100``: one rollout replica as a process of its own
+    (the rollout role of ``launch/roles.py``): builds the model and the engine on this process's GPU (CPU without one) and
+    serves ``http_app`` until it is terminated. ``key=value`` arguments the launcher passes on to every role are ignored
+    except ``actor_rollout_ref.model.path=`` and ``actor_rollout_ref.rollout.max_num_seqs=``."""
+    import argparse
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", default=None)
+    ap.add_argument("--host", default="127.0.0.1")
+    ap.add_argument("--port", type=int, default=8100)
+    ap.add_argument("--name", default="replica-0")
+    ap.add_argument("--num-blocks", type=int, default=2048)
+    ap.add_argument("--max-num-seqs", type=int, default=64)
+    ap.add_argument("--speculative-tokens", type=int, default=0)
+    ap.add_argument("--check", action="store_true", help="build the replica, answer one request and exit (no HTTP server)")
+    args, overrides = ap.parse_known_args(argv)
+    kv = dict(o.split("=", 1) for o in overrides if "=" in o and not o.startswith("-"))
+    path = args.model or kv.get("actor_rollout_ref.model.path", "preset:tiny")
+    max_seqs = int(kv.get("actor_rollout_ref.rollout.max_num_seqs", args.max_num_seqs))
+    device = "cuda" if torch.cuda.is_available() else "cpu"
+    model = load_rollout_model(path, device=device)
+    server = build_server(model, EngineConfig(num_blocks=args.num_blocks, max_num_seqs=max_seqs, num_speculative_tokens=args.speculative_tokens),
+                          device=device, name=args.name)
+    try:
+        if args.check:
+            r = server.generate(list(range(1, 20)), SamplingParams(max_tokens=4, temperature=1.0))
+            print(f"{args.name}: {len(r.output)} tokens on {device}, finish {r.finish.value}")
+            return 0
+        import uvicorn
+
+        uvicorn.run(server.http_app(), host=args.host, port=args.port, log_level="warning")
+        return 0
+    finally:
+        server.close()
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

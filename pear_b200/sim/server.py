@@ -214,3 +214,60 @@ class ServerPool:
         for s in self.servers.values():
             s.close()
         self.servers.clear()
+
+
+def http_app(pool: ServerPool):
+    """The environment host's API: POST /rollout {family, args, actions} replays an action history in a borrowed process
+    (the stateless contract of ``sim/env.py``), GET /capacity, GET /health."""
+    from fastapi import FastAPI
+
+    app = FastAPI(title="pear_b200 environment host")
+
+    @app.get("/health")
+    def health() -> dict:
+        return {"ok": True, "families": sorted(pool.servers)}
+
+    @app.get("/capacity")
+    def capacity() -> dict:
+        return {f: pool.capacity(f) for f in pool.servers}
+
+    @app.post("/rollout")
+    def rollout(body: dict) -> dict:
+        return pool.get(body["family"]).rollout(body.get("args", {}), body.get("actions", []))
+
+    return app
+
+
+def main(argv=None) -> int:
+    """``python -m pear_b200.sim.server --family synthetic=pear_b200.envs.synthetic.SyntheticEnv --port 8200``: an environment
+    host as a process of its own (the env role of ``launch/roles.py``): supervised simulator subprocesses behind a small HTTP
+    API. ``--check`` starts the pool, runs one empty rollout per family and exits."""
+    import argparse
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--family", action="append", default=[], help="name=import.path.EnvClass (repeatable)")
+    ap.add_argument("--processes", type=int, default=2)
+    ap.add_argument("--host", default="127.0.0.1")
+    ap.add_argument("--port", type=int, default=8200)
+    ap.add_argument("--check", action="store_true")
+    args, _ = ap.parse_known_args(argv)
+    families = dict(f.split("=", 1) for f in args.family) or {"synthetic": "pear_b200.envs.synthetic.SyntheticEnv"}
+    pool = ServerPool()
+    try:
+        for name, path in families.items():
+            pool.start(name, path, "stateless", num_processes=args.processes)
+        if args.check:
+            for name in families:
+                out = pool.get(name).rollout({}, [])
+                print(f"env host: family {name} answered with keys {sorted(out)}")
+            return 0
+        import uvicorn
+
+        uvicorn.run(http_app(pool), host=args.host, port=args.port, log_level="warning")
+        return 0
+    finally:
+        pool.close()
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -120,7 +120,9 @@ def build_stack(cfg, replicas: int = 1, device: str = "cpu", env_families: Optio
         families = env_families or {"synthetic": {"env_path": "pear_b200.envs.synthetic.SyntheticEnv", "num_processes": 2,
                                                   "env_kwargs": {"hidden": mcfg.hidden_size, "tokens_per_image": 4}}}
         acfg = AgentLoopConfig(token_budget=int(cfg.data.max_response_length), temperature=float(ro.temperature), top_p=float(ro.top_p),
-                               topk_heads=tcfg.topk_heads, max_model_len=int(ro.max_model_len), log_dir=os.environ.get("PEAR_LOG_DIR"))
+                               topk_heads=tcfg.topk_heads, max_model_len=int(ro.max_model_len), log_dir=os.environ.get("PEAR_LOG_DIR"),
+                               synthetic_turns=int(ro.multi_turn.synthetic_turns), turn_max_tokens=int(ro.multi_turn.turn_max_tokens),
+                               synthetic_reward=ro.multi_turn.synthetic_reward)
         manager = AgentLoopManager(servers, mcfg.hidden_size, families, acfg, queue, num_workers=int(ro.agent.num_workers))
     else:
         full = engine.full_state_dict(torch.float32)  # collective: every rank takes part

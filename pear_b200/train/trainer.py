@@ -161,6 +161,9 @@ class Trainer:
         self._uid = itertools.count()
         self.run_id = uuid.uuid4().hex[:6]
         self.history: list[dict] = []
+        # With several trainer ranks, rank 0 drives: it owns the replay buffer, the agent-loop manager and the weight sync,
+        # builds every data-parallel rank's micro-batches and broadcasts them; the other ranks only compute.
+        self.is_driver = engine.rank == 0
 
     # -- issuing prompt groups ----------------------------------------------------------------------------------------
     def _issue(self, g: PromptGroup) -> None:
@@ -209,32 +212,45 @@ class Trainer:
                 rows.append(trajectory_to_rows(t, a, hidden, self.cfg.topk_heads))
                 lengths.append(len(t["tokens"]))
         dp = self.engine.dp_size
-        mine = balanced_partition(lengths, dp)[self.engine.dp_rank]
-        mbs = [pack_rows(mb) for mb in micro_batches([rows[i] for i in mine], self.cfg.max_token_len_per_gpu)]
+        parts = [[pack_rows(mb) for mb in micro_batches([rows[i] for i in mine], self.cfg.max_token_len_per_gpu)]
+                 for mine in balanced_partition(lengths, dp)]  # one list of packed micro-batches per data-parallel rank
         total_loss_tokens = int(sum(float(r["loss_mask"].sum()) for r in rows))
         stats = {"data/reward_mean": float(np.mean(rewards_all)), "data/sessions": float(len(rows)), "data/tokens": float(sum(lengths)),
                  "data/response_tokens": float(total_loss_tokens), "data/max_len": float(max(lengths)),
                  # whole-context lengths of the trained sessions (prompt + every turn): upstream verl patch 0012
                  "ctx_total_length/mean": float(np.mean(lengths)), "ctx_total_length/max": float(max(lengths))}
-        return mbs, dict(stats, _total_loss_tokens=total_loss_tokens)
+        return parts, dict(stats, _total_loss_tokens=total_loss_tokens)
 
     def train_step(self) -> dict:
         t0 = time.time()
         cap = None if self.cfg.trainer_mode == "sync" else self.replay.max_inflight_sessions
-        groups = self.replay.sample(self.engine.policy_version, self.cfg.train_batch_size, refill=self._refill,
-                                    timeout_s=self.cfg.sample_timeout_s, progress=self._while_waiting)
+        groups, parts, stats = [], None, None
+        if self.is_driver:
+            groups = self.replay.sample(self.engine.policy_version, self.cfg.train_batch_size, refill=self._refill,
+                                        timeout_s=self.cfg.sample_timeout_s, progress=self._while_waiting)
+            parts, stats = self._build(groups)
         t_gen = time.time() - t0
-        mbs, stats = self._build(groups)
+        if self.engine.world > 1:
+            import torch.distributed as dist
+
+            box = [parts, stats]
+            dist.broadcast_object_list(box, src=dist.get_global_rank(self.engine.group, 0), group=self.engine.group)
+            parts, stats = box
+        mbs = parts[self.engine.dp_rank]
         total = stats.pop("_total_loss_tokens")
         t1 = time.time()
         metrics = self.engine.forward_backward_batch(mbs, total_loss_tokens=total) if mbs else {}
         metrics.update(self.engine.optimizer_step())
         t_train = time.time() - t1
         stale = [self.engine.policy_version - 1 - g.issued_version for g in groups]
-        self.replay.release(groups)
+        if self.is_driver:
+            self.replay.release(groups)
         self.step += 1
-        if self.weight_sync is not None and self.step % self.cfg.parameter_sync_step == 0:
-            metrics.update(self.weight_sync.sync(self.engine.full_state_dict(torch.float32), self.engine.policy_version))
+        if self.step % self.cfg.parameter_sync_step == 0 and (self.weight_sync is not None or self.engine.world > 1):
+            state = self.engine.full_state_dict(torch.float32)  # collective: every trainer rank takes part
+            if self.weight_sync is not None:
+                metrics.update(self.weight_sync.sync(state, self.engine.policy_version))
+            del state
         metrics.update(stats)
         metrics.update(self.replay.metrics)
         # model FLOPs utilisation of the trainer ranks against the device table (upstream verl patch 0016 adds its GPU there)
@@ -258,8 +274,10 @@ class Trainer:
         report = self.checkpoints.load(self.engine, self.dataset, self.replay, self.queue)
         if report is not None:
             self.step = report["step"]
-            if self.weight_sync is not None:  # replicas start from the restored policy, not from the base model
-                self.weight_sync.sync(self.engine.full_state_dict(torch.float32), self.engine.policy_version)
+            if self.weight_sync is not None or self.engine.world > 1:  # replicas start from the restored policy, not from the base model
+                state = self.engine.full_state_dict(torch.float32)
+                if self.weight_sync is not None:
+                    self.weight_sync.sync(state, self.engine.policy_version)
         return report
 
     def fit(self) -> list[dict]:
@@ -272,13 +290,16 @@ class Trainer:
                     self.checkpoints.save(self.step, self.engine, self.dataset, self.replay, self.queue)
                     m["timing/checkpoint_s"] = time.time() - t0
                 self.history.append(m)
-                self.log(self.step, m)
+                if self.is_driver:
+                    self.log(self.step, m)
         finally:
             self.cancel_background()
         return self.history
 
     def cancel_background(self) -> None:
         """Run end: groups still generating are cancelled so no worker outlives the run."""
+        if self.manager is None:
+            return
         for g in list(self.replay.groups.values()):
             if g.status in (GroupStatus.IN_FLIGHT, GroupStatus.QUEUED):
                 self.manager.cancel_group(g.uid)
