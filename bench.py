@@ -159,6 +159,8 @@ def build_rollout(args, rank: int, world: int, symm):
         tables.append(shared + own)
         conv = {li: torch.empty(3, cfg.gdn_conv_dim, device=dev).normal_(0.0, 0.5, generator=g) for li in cfg.gdn_layers}
         dec.assign(b, b, prefix + suffix, tables[b], int(torch.randint(0, full.vocab_size, (1,), generator=tok)), conv)
+    if not args.no_prefix_sharing:
+        dec.set_shared_prefixes([(list(range(B)), prefix)])  # what the engine derives from equal leading pages of the block tables
     return full, cfg, model, dec, tables, dict(B=B, T=T, pages=pages, per_seq=per_seq)
 
 
@@ -438,6 +440,7 @@ def main() -> None:
     ap.add_argument("--mk-prompt-len", type=int, default=4096)
     ap.add_argument("--no-megakernel", action="store_true")
     ap.add_argument("--ar-mode", default="auto", choices=["auto", "one", "two"], help="form of the fused all-reduce + add + RMSNorm (N > 1)")
+    ap.add_argument("--no-prefix-sharing", action="store_true", help="attention reads the shared prefix pages once per sequence instead of once per group")
     ap.add_argument("--no-graph", action="store_true", help="launch every step eagerly (kernel-by-kernel profiling); the headline uses graph replay")
     ap.add_argument("--small", action="store_true", help="4-layer model of the 27B layer shape (smoke runs only; not the headline)")
     ap.add_argument("--trainer-step", action="store_true", help="component timing: trainer engine step on one GPU (prints its own JSON line)")

@@ -11,6 +11,13 @@
 // in tensor memory, eight softmax warps (two per TMEM lane quarter) keep running maxima and sums with the lazy rescale,
 // P goes back to shared memory as bf16. Row (g, t) sees keys 0 .. ctx + t. The epilogue divides by the row sum,
 // multiplies by sigmoid(gate) read from the projection output and writes bf16 [row][Hq * 256].
+//
+// Shared prefixes (the samples of one prompt group share their prompt's KV pages; a 6k-token prefix of an 8k context is
+// 3/4 of all page reads): with an item table, a CTA can serve SEVERAL sequences at once over a key range whose pages
+// they share - their query rows stack in the M dimension (5 sequences x 24 rows fill the 128 lanes that one sequence
+// leaves mostly idle), so the shared pages cross L2 -> shared memory once per group instead of once per sequence. Such
+// items, and the per-sequence items over the rest of the context, write un-normalised partial outputs with their running
+// maximum and sum; a small kernel merges a row's partials, applies the gate and writes bf16.
 // Every wait is bounded; no cluster multicast.
 #include "common.cuh"
 
@@ -74,10 +81,20 @@ __device__ __forceinline__ bool pa_warp_wait(uint64_t* bar, uint32_t parity, int
   return __all_sync(0xffffffffu, ok);
 }
 
+// An item of the work table: `nseq` sequences of the batch (seq[0 .. nseq), at most 16; their pages agree on the item's
+// key range), keys [key_begin, key_end) (key_begin a multiple of 128; key_end < 0: up to every sequence's own context end,
+// causal inside the step's rows), partial slot `slot`; the item also marks slots clear_from .. clear_to - 1 of its rows empty.
+constexpr int kPaItemSeqs = 16;
+struct PaItem {
+  int nseq, key_begin, key_end, slot, clear_from, clear_to, pad1, pad2;
+  int seq[kPaItemSeqs];
+};
+
 __global__ void __launch_bounds__(kPaThreads, 1)
 paged_attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const __nv_bfloat16* __restrict__ q,
                      const int* __restrict__ block_table, int max_blocks, const int* __restrict__ ctx, int T, int Hq, int Hkv, float scale,
-                     const float* __restrict__ gate_src, int gate_ld, int gated, __nv_bfloat16* __restrict__ out, int* status) {
+                     const float* __restrict__ gate_src, int gate_ld, int gated, __nv_bfloat16* __restrict__ out, int* status,
+                     const PaItem* __restrict__ items, float* __restrict__ part_o, float* __restrict__ part_ml, int rows_total) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   if ((uint32_t)(smem - smem_raw) > kPaAlignSlack) {
@@ -86,12 +103,19 @@ paged_attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
   }
   PaBars* bars = (PaBars*)(smem + kPaBarOff);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int b = blockIdx.x, kvh = blockIdx.y;
-  const int c = ctx[b];
-  if (c < 0) return;
-  const int group = Hq / Hkv, R = group * T;
-  const int kv_end = c + T;  // keys 0 .. c + T - 1 exist
-  const int ntiles = (kv_end + kPaKT - 1) / kPaKT;
+  const int kvh = blockIdx.y;
+  PaItem it;
+  if (items) it = items[blockIdx.x];
+  else { it.nseq = 1; it.key_begin = 0; it.key_end = -1; it.slot = 0; it.clear_from = it.clear_to = 0; it.seq[0] = blockIdx.x; }
+  if (it.nseq <= 0) return;
+  const int b = it.seq[0];
+  const int group = Hq / Hkv, RS = group * T, R = it.nseq * RS;  // rows per sequence, rows of the item
+  int c_max = -1;
+  for (int s2 = 0; s2 < it.nseq; ++s2) c_max = max(c_max, ctx[it.seq[s2]]);
+  if (c_max < 0) return;
+  const int kv_end = it.key_end >= 0 ? it.key_end : c_max + T;  // keys key_begin .. kv_end - 1 are visited
+  const int jt0 = it.key_begin / kPaKT;
+  const int ntiles = max(0, (kv_end + kPaKT - 1) / kPaKT - jt0);
   const int* table = block_table + (size_t)b * max_blocks;
 
   // zero Q, K, V tiles (rows beyond R and pages beyond the context must hold finite values), then stage the query rows
@@ -99,8 +123,8 @@ paged_attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
   __syncthreads();
   for (int i = threadIdx.x; i < R * 32; i += kPaThreads) {
     const int r = i >> 5, ch = i & 31;  // 32 chunks of 16 bytes per row
-    const int g = r / T, t = r % T;
-    const uint4 v = *(const uint4*)(q + ((size_t)(b * T + t) * Hq + kvh * group + g) * kPaHd + ch * 8);
+    const int sq = r / RS, g = (r % RS) / T, t = r % T;
+    const uint4 v = *(const uint4*)(q + ((size_t)(it.seq[sq] * T + t) * Hq + kvh * group + g) * kPaHd + ch * 8);
     *(uint4*)(smem + kPaQOff + (ch >> 3) * kPaPanel + r * 128 + (((ch & 7) ^ (r & 7)) << 4)) = v;
   }
   fence_proxy_async();
@@ -135,10 +159,10 @@ paged_attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
       if (j > 0 && lane == 0) ok = pa_wait(empty, (j - 1) & 1, status);
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (!ok) break;
-      const int npages = min(8, (kv_end - j * kPaKT + 15) >> 4);
+      const int npages = min(8, (kv_end - (jt0 + j) * kPaKT + 15) >> 4);
       if (lane == 0) mbar_expect_tx(full, (uint32_t)npages * 4u * 2048u);
       __syncwarp();
-      if (pg < npages) tma_load_2d(dst + p * kPaPanel + pg * 2048, map, kvh * kPaHd + p * 64, table[j * 8 + pg] * 16, full);
+      if (pg < npages) tma_load_2d(dst + p * kPaPanel + pg * 2048, map, kvh * kPaHd + p * 64, table[(jt0 + j) * 8 + pg] * 16, full);
     }
   } else if (warp == 9) {
     // ---------------------------------------------------------------------------------------- MMA issuer
@@ -184,9 +208,12 @@ paged_attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
     const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
     const uint32_t s_base = lane_base + kPaTmemS + half * 64, o_cols = lane_base + kPaTmemO + half * 128;
     const float sl2 = scale * 1.4426950408889634f;
-    const bool valid = row < R;
-    const int g = valid ? row / T : 0, t = valid ? row % T : 0;
-    const int last_key = valid ? c + t : -1;
+    const int sq = row < R ? row / RS : 0;
+    const int bs = it.seq[sq];  // this row's sequence
+    const int c = ctx[bs];
+    const bool valid = row < R && c >= 0;
+    const int g = valid ? (row % RS) / T : 0, t = valid ? row % T : 0;
+    const int last_key = valid ? min(kv_end - 1, c + t) : -1;
     float m_ref = -INFINITY, l_run = 0.f;
     uint8_t* p_row = smem + kPaPOff + half * kPaPanel + row * 128;
     float* xch = (float*)(smem + kPaXchOff);
@@ -195,7 +222,7 @@ paged_attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
       ok = pa_warp_wait(&bars->s_full[j & 1], (j >> 1) & 1, lane, status);
       if (!ok) break;
       tcgen05_fence_after();
-      const int k0 = j * kPaKT + half * 64;
+      const int k0 = (jt0 + j) * kPaKT + half * 64;
       const uint32_t s_cols = s_base + (j & 1) * kPaKT;
       uint32_t ra[32], rb[32];
       tmem_ld_32x32b_x32(s_cols, ra);
@@ -270,11 +297,43 @@ paged_attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
     xl[half * 128 + row] = l_run;
     asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
     l_run += xl[(half ^ 1) * 128 + row];
-    if (ok && ntiles > 0) {
+    if (items) {
+      // partial result of this item: un-normalised O (fp32), the reference maximum in log2 units and the row sum.
+      // (The TMEM loads are warp-wide instructions: every lane runs them, the stores are per valid row.)
+      const bool have = ok && ntiles > 0;  // uniform over the warp
+      const int h = kvh * group + g;
+      const size_t prow = (size_t)(bs * T + t) * Hq + h;
+      if (have) tcgen05_fence_after();
+      float* po = part_o + ((size_t)it.slot * rows_total * Hq + prow) * kPaHd + half * 128;
+#pragma unroll 1
+      for (int cc = 0; cc < 4; ++cc) {
+        uint32_t r[32];
+        if (have) {
+          tmem_ld_32x32b_x32(o_cols + cc * 32, r);
+          tcgen05_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = 0u;
+        }
+        if (valid) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) *(uint4*)(po + cc * 32 + i) = make_uint4(r[i], r[i + 1], r[i + 2], r[i + 3]);
+        }
+      }
+      if (valid && half == 0) {
+        float* pm = part_ml + ((size_t)it.slot * rows_total * Hq + prow) * 2;
+        pm[0] = (have && l_run > 0.f) ? m_ref * sl2 : -INFINITY;
+        pm[1] = have ? l_run : 0.f;
+        for (int e = it.clear_from; e < it.clear_to; ++e) {
+          float* pe = part_ml + ((size_t)e * rows_total * Hq + prow) * 2;
+          pe[0] = -INFINITY; pe[1] = 0.f;
+        }
+      }
+    } else if (!items && ok && ntiles > 0) {
       tcgen05_fence_after();
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
       const int h = kvh * group + g;
-      const size_t grow_ = (size_t)(b * T + t);
+      const size_t grow_ = (size_t)(bs * T + t);
       __nv_bfloat16* dst = out + grow_ * Hq * kPaHd + (size_t)h * kPaHd + half * 128;
       const float* gsrc = gate_src + grow_ * gate_ld + (size_t)h * 2 * kPaHd + kPaHd + half * 128;
 #pragma unroll 1
@@ -312,6 +371,41 @@ paged_attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
   }
 }
 
+// Merge a row's partial results: out = (sum_p 2^(m_p - m) O_p) / (sum_p 2^(m_p - m) l_p) * sigmoid(gate), bf16.
+// Grid (rows, Hq), 64 threads x 4 columns. Rows of empty batch slots (ctx < 0) are written as zeros.
+__global__ void __launch_bounds__(64) paged_attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, int nparts,
+                                                                int rows_total, int T, int Hq, const int* __restrict__ ctx,
+                                                                const float* __restrict__ gate_src, int gate_ld, int gated,
+                                                                __nv_bfloat16* __restrict__ out) {
+  const int row = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+  const size_t prow = (size_t)row * Hq + h;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  float l = 0.f;
+  if (ctx[row / T] >= 0) {
+    float m = -INFINITY;
+    for (int p = 0; p < nparts; ++p) m = fmaxf(m, part_ml[((size_t)p * rows_total * Hq + prow) * 2]);
+    for (int p = 0; p < nparts; ++p) {
+      const float mp = part_ml[((size_t)p * rows_total * Hq + prow) * 2], lp = part_ml[((size_t)p * rows_total * Hq + prow) * 2 + 1];
+      if (!(lp > 0.f) || mp == -INFINITY) continue;
+      const float w = pa_ex2(mp - m);
+      const float4 o = *(const float4*)(part_o + ((size_t)p * rows_total * Hq + prow) * kPaHd + tid * 4);
+      acc.x += w * o.x; acc.y += w * o.y; acc.z += w * o.z; acc.w += w * o.w;
+      l += w * lp;
+    }
+  }
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+  float o[4] = {acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv};
+  if (gated) {
+    const float4 g = *(const float4*)(gate_src + (size_t)row * gate_ld + (size_t)h * 2 * kPaHd + kPaHd + tid * 4);
+    o[0] *= 1.f / (1.f + __expf(-g.x)); o[1] *= 1.f / (1.f + __expf(-g.y));
+    o[2] *= 1.f / (1.f + __expf(-g.z)); o[3] *= 1.f / (1.f + __expf(-g.w));
+  }
+  __nv_bfloat162 a0 = __floats2bfloat162_rn(o[0], o[1]), a1 = __floats2bfloat162_rn(o[2], o[3]);
+  uint2 v;
+  v.x = *(uint32_t*)&a0; v.y = *(uint32_t*)&a1;
+  *(uint2*)(out + (size_t)row * Hq * kPaHd + (size_t)h * kPaHd + tid * 4) = v;
+}
+
 static PFN_cuTensorMapEncodeTiled_v12000 pa_get_encode() {
   static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
   if (!fn) {
@@ -342,12 +436,18 @@ static int pa_make_map(CUtensorMap* map, const void* base, long long rows, int c
 // block_table int32 [B, max_blocks]; ctx int32 [B] = tokens cached before the step (< 0: empty slot); gate_src fp32 rows of
 // the q projection output ([Hq x (q | gate)] per row, leading dimension gate_ld) when `gated`. out bf16 [B * T, Hq * 256].
 // Needs group * T <= 128. `status` is a device int that a bounded wait sets on expiry.
+// With an item table (`items` = device array of `n_items` 24-int records {sequences, key begin, key end or -1, partial slot,
+// first slot to clear, end of the slots to clear, 0, 0, sequence indices x 16}; every active row must be covered by items whose key ranges partition its context):
+// the items write partial results into part_o [nparts, B * T, Hq, 256] / part_ml [nparts, B * T, Hq, 2] (fp32) and a second
+// kernel merges them. A group item needs sequences * (Hq / Hkv) * T <= 128 rows. `items` null: one CTA per sequence.
 PEAR_API int pear_paged_attn_tc_hd256(const void* q, const void* kc, const void* vc, long long num_pages, const int* block_table, int max_blocks,
                                       const int* ctx, int B, int T, int Hq, int Hkv, float scale, const float* gate_src, int gate_ld, int gated,
-                                      void* out, int* status, void* stream) {
+                                      void* out, int* status, const int* items, int n_items, int nparts, float* part_o, float* part_ml,
+                                      void* stream) {
   using namespace pear;
   if (B <= 0) return 0;
   if (Hkv <= 0 || Hq % Hkv || (Hq / Hkv) * T > 128 || T < 1) return (int)cudaErrorInvalidValue;
+  if (items && (n_items <= 0 || nparts <= 0 || !part_o || !part_ml)) return (int)cudaErrorInvalidValue;
   if (((uintptr_t)q % 16) || ((uintptr_t)kc % 16) || ((uintptr_t)vc % 16) || ((uintptr_t)out % 16) || (gated && (gate_ld % 4))) return (int)cudaErrorInvalidValue;
   CUtensorMap mk, mv;
   int r = pa_make_map(&mk, kc, num_pages * 16, Hkv * kPaHd);
@@ -360,9 +460,14 @@ PEAR_API int pear_paged_attn_tc_hd256(const void* q, const void* kc, const void*
     PEAR_CUDA_CHECK(cudaFuncSetAttribute(paged_attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured = true;
   }
-  paged_attn_tc_kernel<<<dim3(B, Hkv), kPaThreads, smem, (cudaStream_t)stream>>>(mk, mv, (const __nv_bfloat16*)q, block_table, max_blocks, ctx, T, Hq,
-                                                                                 Hkv, scale, (const float*)gate_src, gate_ld, gated,
-                                                                                 (__nv_bfloat16*)out, status);
+  paged_attn_tc_kernel<<<dim3(items ? n_items : B, Hkv), kPaThreads, smem, (cudaStream_t)stream>>>(
+      mk, mv, (const __nv_bfloat16*)q, block_table, max_blocks, ctx, T, Hq, Hkv, scale, (const float*)gate_src, gate_ld, gated, (__nv_bfloat16*)out,
+      status, (const PaItem*)items, part_o, part_ml, B * T);
   PEAR_LAUNCH_CHECK();
+  if (items) {
+    paged_attn_combine_kernel<<<dim3(B * T, Hq), 64, 0, (cudaStream_t)stream>>>(part_o, part_ml, nparts, B * T, T, Hq, ctx, (const float*)gate_src,
+                                                                               gate_ld, gated, (__nv_bfloat16*)out);
+    PEAR_LAUNCH_CHECK();
+  }
   return 0;
 }

@@ -108,17 +108,29 @@ def attn_prep(qkv: torch.Tensor, qn_w, kn_w, inv_freq: torch.Tensor, rot: int, c
     _lib.count_launch()
 
 
+PA_ITEM_INTS, PA_ITEM_SEQS = 24, 16  # layout of one work item of the tensor-core paged attention (csrc/paged_attn_tc.cu: PaItem)
+
+
+def tc_attention_ok(d: int, hq: int, hkv: int, t: int) -> bool:
+    return d == 256 and (hq // hkv) * t <= 128
+
+
 def paged_attention(q, kc, vc, block_table, ctx, batch: int, t: int, hq: int, hkv: int, d: int, scale: float, gate_src, gated: bool, out,
-                    tensor_core: Optional[bool] = None) -> None:
+                    tensor_core: Optional[bool] = None, items: Optional[torch.Tensor] = None, nparts: int = 0, part_o=None, part_ml=None) -> None:
     """Verify / decode attention over the paged cache (row (b, t) sees keys 0 .. ctx[b] + t), sigmoid gate fused.
-    Head dimension 256 with ``group * t <= 128`` runs on the tcgen05 kernel, other shapes on the SIMT kernel."""
-    use_tc = (d == 256 and (hq // hkv) * t <= 128) if tensor_core is None else tensor_core
+    Head dimension 256 with ``group * t <= 128`` runs on the tcgen05 kernel, other shapes on the SIMT kernel. ``items``
+    (int32 [n, 24]): the work table of the tensor-core kernel (sequences that share pages stacked in one CTA); the partial
+    results go through ``part_o`` [nparts, batch * t, hq, 256] and ``part_ml`` [nparts, batch * t, hq, 2]."""
+    use_tc = tc_attention_ok(d, hq, hkv, t) if tensor_core is None else tensor_core
     gate_ld = gate_src.stride(0) if gated else 0
     if use_tc:
         _lib.check(_lib.lib().pear_paged_attn_tc_hd256(_lib.ptr(q), _lib.ptr(kc), _lib.ptr(vc), _ll(kc.shape[0]), _lib.ptr(block_table),
                                                        block_table.stride(0), _lib.ptr(ctx), batch, t, hq, hkv, _f(scale),
                                                        _lib.ptr(gate_src) if gated else _lib.ptr(None), gate_ld, 1 if gated else 0, _lib.ptr(out),
-                                                       _lib.ptr(status_word(q.device)), _lib.stream()), "paged_attn_tc")
+                                                       _lib.ptr(status_word(q.device)), _lib.ptr(items), items.shape[0] if items is not None else 0,
+                                                       nparts, _lib.ptr(part_o), _lib.ptr(part_ml), _lib.stream()), "paged_attn_tc")
+        if items is not None:
+            _lib.count_launch()
     else:
         _lib.check(_lib.lib().pear_ds_paged_attn_simt(_lib.ptr(q), _lib.ptr(kc), _lib.ptr(vc), _lib.ptr(block_table), block_table.stride(0),
                                                       _lib.ptr(ctx), batch * t, t, hq, hkv, d, _f(scale), _lib.ptr(gate_src) if gated else _lib.ptr(None),

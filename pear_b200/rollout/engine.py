@@ -116,7 +116,8 @@ class RolloutEngine:
         self.paused = False
         self.policy_version = 0
         self.step_count = 0
-        self.gen = torch.Generator(device="cpu").manual_seed(cfg.seed)
+        # sampling noise is drawn where the logits live: on a GPU the fused sampler / verifier run on the device
+        self.gen = torch.Generator(device=self.device if self.device.type == "cuda" else "cpu").manual_seed(cfg.seed)
         self._ids = itertools.count()
         self.metrics = {"prompt_tokens": 0, "generation_tokens": 0, "preemptions": 0, "aborted": 0, "spec_drafted": 0,
                         "spec_accepted": 0, "steps": 0}
@@ -448,6 +449,30 @@ class RolloutEngine:
                 self.runner.conv_state[li][req.seq.slot].copy_(rows)
         self._fast_free.append(b)
 
+    def _shared_prefix_groups(self, reqs: list[Request]) -> list:
+        """Sequences whose block tables start with the same pages (samples of one prompt, turns of one session that hit
+        the prefix cache): (batch slots, shared tokens) per group, for the attention kernel that reads shared pages once."""
+        buckets: dict[int, list[Request]] = {}
+        for r in reqs:
+            if r.block_table:
+                buckets.setdefault(r.block_table[0], []).append(r)
+        groups = []
+        bs = self.cfg.block_size
+        for members in buckets.values():
+            if len(members) < 2:
+                continue
+            first = members[0].block_table
+            common = min(len(m.block_table) for m in members)
+            for m in members[1:]:
+                n = 0
+                while n < common and m.block_table[n] == first[n]:
+                    n += 1
+                common = n
+            tokens = min(common * bs, min(m.computed for m in members))
+            if tokens >= 256:
+                groups.append(([self._fast_slot[id(m)] for m in members], tokens))
+        return groups
+
     def _fast_step(self, reqs: list[Request]) -> list[Request]:
         if not reqs:
             return []
@@ -483,6 +508,10 @@ class RolloutEngine:
             active.append(req)
         if not active:
             return []
+        members = tuple(sorted((self._fast_slot[id(r)], r.block_table[0] if r.block_table else -1) for r in active))
+        if members != getattr(self, "_fast_members", None):  # batch membership changed: regroup the sequences that share pages
+            self._fast_members = members
+            fast.set_shared_prefixes(self._shared_prefix_groups(active))
         fast.step()
         res = fast.results()
         fast.check()
@@ -519,9 +548,8 @@ class RolloutEngine:
         bad = S.count_nonfinite(logits)
         if bool((bad > 0).any()):
             raise S.NonFiniteLogits(self.step_count, torch.nonzero(bad).flatten().tolist(), [req.request_id])
-        logits = logits.cpu()
         if drafts:
-            out = S.verify_greedy_drafts(logits[None], torch.tensor([drafts]), p.temperature, p.topk_logprobs, self.gen)
+            out = S.verify_greedy_drafts(logits[None], torch.tensor([drafts], device=logits.device), p.temperature, p.topk_logprobs, self.gen)
             acc = int(out.accepted[0])
             new = [int(t) for t in out.tokens[0, : acc + 1]]
             lps = [float(v) for v in out.logprobs[0, : acc + 1]]

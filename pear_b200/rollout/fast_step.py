@@ -172,6 +172,19 @@ class FastDecoder:
             self.recs_ptrs = K._ptr_array([self.recs_t.data_ptr()])
             self.keys_ptrs = K._ptr_array([self.keys_t.data_ptr()])
             self.ar_ctr = self.sync_ctr = None
+        # work table of the tensor-core paged attention: per sequence one item over the keys it does not share, per group
+        # of sequences with a common prefix a few items over the shared keys (set_shared_prefixes)
+        self.pa_items = None
+        if cfg.attention_layers or self.mtp:
+            hq, hkv = cfg.num_attention_heads, cfg.num_kv_heads
+            if tensor_core_attention is not False and K.tc_attention_ok(cfg.head_dim, hq, hkv, T):
+                self.pa_splits = 8  # most items a shared prefix is cut into
+                self.pa_nparts = 1 + self.pa_splits
+                self.pa_group = max(1, min(K.PA_ITEM_SEQS, 128 // ((hq // hkv) * T)))
+                self.pa_items = torch.zeros(B + (B // 2 + 1) * self.pa_splits, K.PA_ITEM_INTS, **i32)
+                self.pa_part_o = torch.zeros(self.pa_nparts, M, hq, cfg.head_dim, **f32)
+                self.pa_part_ml = torch.zeros(self.pa_nparts, M, hq, 2, **f32)
+                self.set_shared_prefixes([])
         # pinned result record
         self._host = torch.zeros(B * (2 * T + 2), dtype=torch.int32).pin_memory()
         self._dev_rec = torch.zeros(B * (2 * T + 2), **i32)
@@ -264,6 +277,41 @@ class FastDecoder:
         for li in self.cfg.gdn_layers:
             self.conv_rec[li][slot, 0, :3] = conv_state[li].float() if conv_state is not None else 0.0
 
+    def set_shared_prefixes(self, groups: list, tiles_per_item: int = 8) -> None:
+        """``groups``: (batch slots, tokens) — sequences whose first ``tokens`` tokens live in the SAME pages (the samples of
+        one prompt; a prefix-cache hit). Their query rows are stacked in one CTA over the shared keys, so those pages are
+        read once per group instead of once per sequence; every sequence keeps an item of its own for the rest of its
+        context. Shared lengths are cut to multiples of 128 keys and must not exceed any member's context."""
+        if self.pa_items is None:
+            return
+        self.graph_sync()
+        rows = []
+        shared_of = {}
+        for members, tokens in groups:
+            tiles = int(tokens) // 128
+            if tiles < 2 or len(members) < 2 or self.pa_group < 2:
+                continue
+            nsplit = min(self.pa_splits, (tiles + tiles_per_item - 1) // tiles_per_item)
+            for i in range(0, len(members), self.pa_group):
+                sub = list(members[i:i + self.pa_group])
+                if len(sub) < 2:
+                    continue
+                for m in sub:
+                    shared_of[m] = (tiles * 128, nsplit)
+                for sp in range(nsplit):
+                    lo, hi = tiles * sp // nsplit, tiles * (sp + 1) // nsplit
+                    rows.append([len(sub), lo * 128, hi * 128, 1 + sp, 0, 0, 0, 0] + sub + [0] * (K.PA_ITEM_SEQS - len(sub)))
+        own = []
+        for b in range(self.B):
+            begin, nsplit = shared_of.get(b, (0, 0))
+            own.append([1, begin, -1, 0, 1 + nsplit, self.pa_nparts, 0, 0, b] + [0] * (K.PA_ITEM_SEQS - 1))
+        table = own + rows  # the per-sequence items first: they are the longest
+        if len(table) > self.pa_items.shape[0]:
+            raise ValueError("more attention work items than the table holds")
+        host = torch.zeros(self.pa_items.shape, dtype=torch.int32)
+        host[: len(table)] = torch.tensor(table, dtype=torch.int32)
+        self.pa_items.copy_(host)
+
     def set_block_table(self, b: int, block_table: list[int]) -> None:
         n = len(block_table)
         if n > self.block_table.shape[1]:
@@ -341,8 +389,12 @@ class FastDecoder:
         K.stream_gemm(self.h[:rows], lw.w_in, self.proj[:rows], 1, 0)
         K.attn_prep(self.proj, lw.qn, lw.kn, self.inv_freq, cfg.rotary_dim, ctx, self.rope_off, self.block_table, rows, t, lw.hq, lw.hkv, lw.d,
                     lw.gated, cfg.rms_eps, self.q, kc, vc)
-        K.paged_attention(self.q, kc, vc, self.block_table, ctx, batch, t, lw.hq, lw.hkv, lw.d, lw.d ** -0.5, self.proj, lw.gated, self.mix_out,
-                          self.tc_attn)
+        if self.pa_items is not None:
+            K.paged_attention(self.q, kc, vc, self.block_table, ctx, batch, t, lw.hq, lw.hkv, lw.d, lw.d ** -0.5, self.proj, lw.gated, self.mix_out,
+                              True, self.pa_items, self.pa_nparts, self.pa_part_o, self.pa_part_ml)
+        else:
+            K.paged_attention(self.q, kc, vc, self.block_table, ctx, batch, t, lw.hq, lw.hkv, lw.d, lw.d ** -0.5, self.proj, lw.gated, self.mix_out,
+                              self.tc_attn)
         return self._gemm(self.mix_out.view(-1)[: self.M * lw.hq * lw.d].view(self.M, lw.hq * lw.d), lw.w_out, rows)
 
     def _layer(self, li, lw, rows, batch, t, ctx, kc, vc, next_norm, residual, bcast_last=False):

@@ -53,6 +53,7 @@ class HostTier:
         self.pinned: dict[int, int] = {}  # device block -> outstanding stores reading it
         self.stream = torch.cuda.Stream() if (torch.cuda.is_available() and kv_caches and kv_caches[0].is_cuda) else None
         self.hit_watermark: dict[str, int] = {}
+        self._stage: dict = {}  # cache tensor index -> (device staging, pinned staging) of the batched store path
         self.stores = self.loads = self.evicted = 0
         self.release_block: Optional[Callable[[int], None]] = None
 
@@ -70,6 +71,8 @@ class HostTier:
         return [(session,) + w for w in work]
 
     def run_store(self, work: list[tuple]) -> int:
+        if self.stream is not None and len(work) > 1:
+            return self._run_store_batched(work)
         done = 0
         for session, pos, blk, h, st in work:
             try:
@@ -87,6 +90,57 @@ class HostTier:
             finally:
                 self._unpin(blk)
         return done
+
+    def _run_store_batched(self, work: list[tuple]) -> int:
+        """GPU path of a store of several blocks: per cache tensor ONE gather kernel packs the blocks into a device staging
+        buffer (``kv_blocks_copy_kernel``) and ONE copy moves it to pinned host memory, instead of one copy per block and
+        tensor; the host then files the rows into their tier slots."""
+        from ..ops import rollout_ops
+
+        plan = []
+        for session, pos, blk, h, st in work:
+            if h in self.entries or any(p[3] == h for p in plan):
+                self._unpin(blk)
+                continue
+            slot = self._host_slot()
+            if slot is None:
+                self._unpin(blk)
+                continue
+            plan.append((session, pos, blk, h, st, slot))
+        if not plan:
+            return 0
+        n = len(plan)
+        dev = self.kv_caches[0].device
+        ids = torch.tensor([p[2] for p in plan], dtype=torch.int32, device=dev)
+        self.stream.wait_stream(torch.cuda.current_stream())
+        staged = []
+        with torch.cuda.stream(self.stream):
+            for ci, (cache, host) in enumerate(zip(self.kv_caches, self.kv_host)):
+                shape = tuple(cache.shape[1:])
+                if ci not in self._stage or self._stage[ci][0].shape[0] < n:  # persistent staging per cache tensor, grown on demand
+                    cap = max(n, 64)
+                    self._stage[ci] = (torch.empty((cap,) + shape, dtype=cache.dtype, device=dev),
+                                       torch.empty((cap,) + shape, dtype=cache.dtype, pin_memory=True))
+                sd, sh = self._stage[ci]
+                rollout_ops.kv_blocks_copy(cache, sd, ids, to_staging=True)
+                sh[:n].copy_(sd[:n], non_blocking=True)
+                staged.append((host, sh))
+            for i, (_, _, _, _, st, slot) in enumerate(plan):
+                if st is not None:
+                    for cache, host in zip(self.state_caches, self.state_host):
+                        host[slot].copy_(cache[st], non_blocking=True)
+        self.stream.synchronize()
+        torch.cuda.current_stream().wait_stream(self.stream)  # the blocks may be reused right after
+        for host, sh in staged:
+            for i, p in enumerate(plan):
+                host[p[5]].copy_(sh[i])
+        for session, pos, blk, h, st, slot in plan:
+            self.entries[h] = HostEntry(slot, st is not None, session=session, position=pos)
+            if st is not None and session is not None:
+                self._demote_superseded(session, pos)
+            self.stores += 1
+            self._unpin(blk)
+        return n
 
     def offer(self, h: bytes, blk: int, state_slot: Optional[int]) -> None:
         """Eviction hook of the block manager: keep the block's contents on the host before it is reused."""

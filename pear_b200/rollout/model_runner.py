@@ -230,11 +230,26 @@ class ModelRunner:
         pos = torch.cat([r.positions.to(self.device) if r.positions is not None
                          else torch.arange(r.start, r.start + r.tokens.shape[0], device=self.device).expand(3, -1) for r in rows], dim=1)
         cos, sin = model.rope(pos)
-        x = model.model.embed_tokens(tokens).float()
-        for i, r in enumerate(rows):
-            if r.embeds is not None:
-                s, e = bounds[i], bounds[i + 1]
-                x[s:e] = torch.where(r.embeds_mask.to(self.device)[:, None], r.embeds.to(self.device).float(), x[s:e])
+        table = model.model.embed_tokens.weight
+        if self.use_kernels and table.dtype == torch.bfloat16:
+            # one kernel: embedding lookup with the vision-placeholder rows merged in (upstream `_shard_embed_kernel`)
+            from ..ops import rollout_ops
+
+            emb = msk = None
+            if any(r.embeds is not None for r in rows):
+                emb = torch.zeros(tokens.shape[0], cfg.hidden_size, device=self.device)
+                msk = torch.zeros(tokens.shape[0], dtype=torch.bool, device=self.device)
+                for i, r in enumerate(rows):
+                    if r.embeds is not None:
+                        s, e = bounds[i], bounds[i + 1]
+                        emb[s:e], msk[s:e] = r.embeds.to(self.device).float(), r.embeds_mask.to(self.device)
+            x = rollout_ops.embed_merge(tokens, table, emb, msk)
+        else:
+            x = model.model.embed_tokens(tokens).float()
+            for i, r in enumerate(rows):
+                if r.embeds is not None:
+                    s, e = bounds[i], bounds[i + 1]
+                    x[s:e] = torch.where(r.embeds_mask.to(self.device)[:, None], r.embeds.to(self.device).float(), x[s:e])
         layers = list(model.model.layers)
         if not hybrid.tensor_parallel_active():
             for li, layer in enumerate(layers):

@@ -348,3 +348,45 @@ def _run_fast_decoder_case(K, n_draft, graph):
     for li in cfg.gdn_layers:
         assert (rs[li][4] - caches[0].state[li]).abs().max() < 3e-2 * max(1.0, float(caches[0].state[li].abs().max()))
         assert (conv[li] - caches[0].conv[li]).abs().max() < 0.05
+
+
+def test_paged_attention_shared_prefix_items(K):
+    """Sequences whose first 256 tokens live in the same pages: the item form (stacked rows over the shared keys, partial
+    results merged) against the one-CTA-per-sequence form and the SIMT statement."""
+    batch, t, hq, hkv, d = 5, 4, 12, 2, 256
+    ctx_list = [300, 257, 410, 130, 290]  # sequence 3 shares nothing; the others share 256 tokens
+    g = torch.Generator(device="cuda").manual_seed(31)
+    pages = 200
+    kc = torch.randn(pages, 16, hkv, d, device="cuda", generator=g).to(torch.bfloat16)
+    vc = torch.randn(pages, 16, hkv, d, device="cuda", generator=g).to(torch.bfloat16)
+    table = torch.zeros(batch, 32, dtype=torch.int32, device="cuda")
+    shared = torch.arange(1, 17, dtype=torch.int32)
+    nxt = 20
+    for b in range(batch):
+        own = torch.arange(nxt, nxt + 32, dtype=torch.int32)
+        nxt += 32
+        if b != 3:
+            own[:16] = shared
+        table[b] = own.cuda()
+    ctx = torch.tensor(ctx_list, dtype=torch.int32, device="cuda")
+    q = (torch.randn(batch * t, hq, d, device="cuda", generator=g)).to(torch.bfloat16)
+    gate = torch.randn(batch * t, 2 * hq * d + 2 * hkv * d, device="cuda", generator=g)
+    outs = []
+    nparts, splits = 3, 2
+    rows = [[1, 256 if b != 3 else 0, -1, 0, 1 + (splits if b != 3 else 0), nparts, 0, 0, b] + [0] * 15 for b in range(batch)]
+    for sp in range(splits):
+        rows.append([4, sp * 128, (sp + 1) * 128, 1 + sp, 0, 0, 0, 0, 0, 1, 2, 4] + [0] * 12)
+    rows.append([0] * 24)  # an empty item
+    items = torch.tensor(rows, dtype=torch.int32, device="cuda")
+    part_o = torch.full((nparts, batch * t, hq, d), float("nan"), device="cuda")
+    part_ml = torch.full((nparts, batch * t, hq, 2), float("nan"), device="cuda")
+    for mode in ("items", "direct", "simt"):
+        out = torch.zeros(batch * t, hq * d, dtype=torch.bfloat16, device="cuda")
+        if mode == "items":
+            K.paged_attention(q, kc, vc, table, ctx, batch, t, hq, hkv, d, d ** -0.5, gate, True, out, True, items, nparts, part_o, part_ml)
+        else:
+            K.paged_attention(q, kc, vc, table, ctx, batch, t, hq, hkv, d, d ** -0.5, gate, True, out, mode == "direct")
+        outs.append(out.float())
+    torch.cuda.synchronize()
+    K.check_status()
+    assert (outs[0] - outs[2]).abs().max() < 0.03 and (outs[1] - outs[2]).abs().max() < 0.03
