@@ -20,6 +20,7 @@ megakernel, the configuration upstream publishes 921 tok/s for on one GB300 (REA
 from __future__ import annotations
 
 import argparse
+import dataclasses
 import json
 import math
 import os
@@ -122,8 +123,12 @@ def build_rollout(args, rank: int, world: int, symm):
     from pear_b200.rollout.fast_step import FastDecoder
 
     full = HybridConfig.small_gpu() if args.small else HybridConfig.qwen3_8_27b()
-    cfg = tp_config(full, world) if world > 1 else full
-    B, T = args.seqs_per_gpu * world, 1 + args.drafts
+    shards = max(world, args.emulate_tp)
+    cfg = tp_config(full, shards) if shards > 1 else full
+    if args.emulate_tp > 1:  # one rank's share of a tensor-parallel step, without the exchange: for kernel-by-kernel profiling
+        full = dataclasses.replace(full, vocab_size=full.vocab_size // args.emulate_tp)
+        cfg = dataclasses.replace(cfg, vocab_size=full.vocab_size)
+    B, T = args.seqs_per_gpu * shards, 1 + args.drafts
     prefix, suffix, bs = args.prefix_len, args.suffix_len, 16
     assert prefix % bs == 0 and suffix % bs == 0
     total_steps = 2 * args.steps + max(3, args.warmup) + 8
@@ -261,7 +266,8 @@ def run_rollout(args, rank, local_rank, world, dist, symm) -> dict:
     bound = max(t_hbm, t_flop, t_link)
     value = tokens / (ms / 1e3)
     return {
-        "metric": "rollout decode tokens/s", "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": warmup,
+        "metric": "rollout decode tokens/s" if args.emulate_tp <= 1 else f"NOT A BENCHMARK: one rank's share of a tp{args.emulate_tp} step without the exchange",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": warmup,
         "ms_per_step": round(step_ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16 (weights, activations, KV), fp32 accumulate / residual / recurrent state", "data": "synthetic",
         "config": {
@@ -441,6 +447,8 @@ def main() -> None:
     ap.add_argument("--no-megakernel", action="store_true")
     ap.add_argument("--ar-mode", default="auto", choices=["auto", "one", "two"], help="form of the fused all-reduce + add + RMSNorm (N > 1)")
     ap.add_argument("--no-prefix-sharing", action="store_true", help="attention reads the shared prefix pages once per sequence instead of once per group")
+    ap.add_argument("--emulate-tp", type=int, default=0, help="profiling aid (one GPU): run ONE rank's share of a tensor-parallel step of this size, "
+                    "without the inter-GPU exchange; not a benchmark of anything")
     ap.add_argument("--no-graph", action="store_true", help="launch every step eagerly (kernel-by-kernel profiling); the headline uses graph replay")
     ap.add_argument("--small", action="store_true", help="4-layer model of the 27B layer shape (smoke runs only; not the headline)")
     ap.add_argument("--trainer-step", action="store_true", help="component timing: trainer engine step on one GPU (prints its own JSON line)")

@@ -51,6 +51,7 @@ class SymmWorld:
         self.flags.tensor.zero_()
         self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
         self.epochs = [0] * SLOTS
+        self._dev_counters: dict = {}
         self._ag_bufs: dict = {}
         self.num_sms = torch.cuda.get_device_properties(self.device).multi_processor_count
         torch.cuda.synchronize(self.device)
@@ -63,6 +64,14 @@ class SymmWorld:
         buf = SymmBuffer(t, [int(p) for p in h.buffer_ptrs])
         buf.handle = h
         return buf
+
+    def device_counter(self, slot: int) -> torch.Tensor:
+        """The device-resident epoch of a flag slot (kernels that must replay inside a CUDA graph read and advance it
+        themselves). One counter per slot for the whole ``SymmWorld``: every user of the slot continues the same epoch
+        sequence, so flags left by an earlier user can never satisfy a later user's wait."""
+        if slot not in self._dev_counters:
+            self._dev_counters[slot] = torch.zeros(1, dtype=torch.int32, device=self.device)
+        return self._dev_counters[slot]
 
     def check(self) -> None:
         code = int(self.status[0].item())

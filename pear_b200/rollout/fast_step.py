@@ -155,9 +155,9 @@ class FastDecoder:
             self.ar_ws = s.alloc((2, M, H), torch.bfloat16)
             self.recs = s.alloc((2 * rec_elems * K.rec_bytes(),), torch.uint8)
             self.keys = s.alloc((2 * key_elems,), torch.int64)
-            self.ar_ctr = torch.zeros(1, **i32)
+            self.ar_ctr = s.device_counter(SLOT_STEP_AR)  # shared by every decoder on this SymmWorld: one epoch sequence per slot
             self.ar_ticket = torch.zeros(1, **i32)
-            self.sync_ctr = torch.zeros(1, **i32)
+            self.sync_ctr = s.device_counter(SLOT_STEP_SYNC)
             self.recs_ptrs, self.keys_ptrs = self.recs.c_ptrs, self.keys.c_ptrs
             self.recs_t, self.keys_t = self.recs.tensor, self.keys.tensor
             self.recs_t.zero_()
