@@ -721,13 +721,52 @@ __global__ void ds_symm_barrier_kernel(DsPeers flags, int rank, int world, int s
 // (*ctr + 1) & 1 of its workspace; the kernel releases that epoch to the peers, waits for theirs, sums all partials in
 // rank order in fp32 straight from peer memory, adds the residual and normalises. The last CTA to finish stores the new
 // epoch. (Upstream ar_norm.cu:61-208 at two ranks.)
-__global__ void __launch_bounds__(256) ds_ar_add_rmsnorm_kernel(DsPeers partials, DsPeers flags, int rank, int world, int slot, uint32_t* ctr,
+// Sum of every rank's 8 bf16 partial values at one position, in rank order, fp32. All peers' loads are issued before
+// the first one is consumed (one NVLink round trip per position instead of one per rank): the loop bounds are compile-time
+// constants, the ranks beyond `world` are predicated off.
+__device__ __forceinline__ void ds_sum_partials(const DsPeers& partials, int world, size_t off, float (&acc)[8]) {
+  uint4 v[kDsMaxRanks];
+#pragma unroll
+  for (int r = 0; r < kDsMaxRanks; ++r) {
+    if (r < world) {
+      const __nv_bfloat16* src = (const __nv_bfloat16*)partials.p[r] + off;
+      asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v[r].x), "=r"(v[r].y), "=r"(v[r].z), "=r"(v[r].w) : "l"(src) : "memory");
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+#pragma unroll
+  for (int r = 0; r < kDsMaxRanks; ++r) {
+    if (r < world) {
+      const __nv_bfloat162* h2 = (const __nv_bfloat162*)&v[r];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(h2[j]);
+        acc[2 * j] += f.x; acc[2 * j + 1] += f.y;
+      }
+    }
+  }
+}
+
+// block-wide sum of one float per thread (up to 32 warps), result to every thread
+__device__ __forceinline__ float ds_block_sum(float v, float* red) {
+  v = warp_sum(v);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float tot = 0.f;
+  const int nw = (blockDim.x + 31) >> 5;
+  for (int k = 0; k < nw; ++k) tot += red[k];
+  return tot;
+}
+
+__global__ void __launch_bounds__(1024) ds_ar_add_rmsnorm_kernel(DsPeers partials, DsPeers flags, int rank, int world, int slot, uint32_t* ctr,
                                                                 uint32_t* ticket, float* __restrict__ residual, int mode,
                                                                 const float* __restrict__ weight, __nv_bfloat16* __restrict__ out, int T, int H,
                                                                 size_t buf_elems, float eps, uint32_t budget, int* status) {
-  __shared__ float red[8];
+  __shared__ float red[32];
   __shared__ int ok_flag;
-  const int tid = threadIdx.x;
+  const int tid = threadIdx.x, nt = blockDim.x;
   const uint32_t epoch = *ctr + 1u;
   if (blockIdx.x == 0 && tid < world) {
     __threadfence_system();
@@ -748,21 +787,9 @@ __global__ void __launch_bounds__(256) ds_ar_add_rmsnorm_kernel(DsPeers partials
     const size_t boff = (size_t)(epoch & 1u) * buf_elems;
     for (int t = blockIdx.x; t < T; t += gridDim.x) {
       float ssq = 0.f;
-      for (int i = tid * 8; i < H; i += 2048) {
+      for (int i = tid * 8; i < H; i += nt * 8) {
         float acc[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-        for (int r = 0; r < world; ++r) {
-          const __nv_bfloat16* src = (const __nv_bfloat16*)partials.p[r] + boff + (size_t)t * H + i;
-          uint4 v;
-          asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(src) : "memory");
-          const __nv_bfloat162* h2 = (const __nv_bfloat162*)&v;
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float2 f = __bfloat1622float2(h2[j]);
-            acc[2 * j] += f.x; acc[2 * j + 1] += f.y;
-          }
-        }
+        ds_sum_partials(partials, world, boff + (size_t)t * H + i, acc);
         float* res = residual + (size_t)t * H + i;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
@@ -771,14 +798,8 @@ __global__ void __launch_bounds__(256) ds_ar_add_rmsnorm_kernel(DsPeers partials
           ssq += acc[j] * acc[j];
         }
       }
-      ssq = warp_sum(ssq);
-      __syncthreads();
-      if ((tid & 31) == 0) red[tid >> 5] = ssq;
-      __syncthreads();
-      float tot = 0.f;
-      for (int k = 0; k < 8; ++k) tot += red[k];
-      const float rstd = rsqrtf(tot / (float)H + eps);
-      for (int i = tid * 8; i < H; i += 2048) {
+      const float rstd = rsqrtf(ds_block_sum(ssq, red) / (float)H + eps);
+      for (int i = tid * 8; i < H; i += nt * 8) {
         const float* res = residual + (size_t)t * H + i;
         __nv_bfloat16* o = out + (size_t)t * H + i;
 #pragma unroll
@@ -801,13 +822,13 @@ __global__ void __launch_bounds__(256) ds_ar_add_rmsnorm_kernel(DsPeers partials
 // rank to finish releases a second flag to every peer and waits for theirs, so the kernel ends only when every rank's rows
 // have landed here. `out` (and `residual` when broadcast) are symmetric buffers. (Upstream's four-rank form: rollout/hopper/
 // csrc/ar_norm.cu:138-227, with the multicast store replaced by unicast peer stores.)
-__global__ void __launch_bounds__(256) ds_ar2_add_rmsnorm_kernel(DsPeers partials, DsPeers flags, DsPeers outs, DsPeers residuals, int rank, int world,
+__global__ void __launch_bounds__(1024) ds_ar2_add_rmsnorm_kernel(DsPeers partials, DsPeers flags, DsPeers outs, DsPeers residuals, int rank, int world,
                                                                  int slot, uint32_t* ctr, uint32_t* ticket, int mode, int bcast_residual,
-                                                                 const float* __restrict__ weight, int T, int H, size_t buf_elems, float eps,
+                                                                 const float* __restrict__ weight, int T, int H, size_t buf_elems, int fixed_buf, float eps,
                                                                  uint32_t budget, int* status) {
-  __shared__ float red[8];
+  __shared__ float red[32];
   __shared__ int ok_flag;
-  const int tid = threadIdx.x;
+  const int tid = threadIdx.x, nt = blockDim.x;
   const uint32_t epoch = *ctr + 1u;
   if (blockIdx.x == 0 && tid < world) {
     __threadfence_system();
@@ -826,24 +847,13 @@ __global__ void __launch_bounds__(256) ds_ar2_add_rmsnorm_kernel(DsPeers partial
   __syncthreads();
   float* residual = (float*)residuals.p[rank];
   if (ok_flag) {
-    const size_t boff = (size_t)(epoch & 1u) * buf_elems;
+    // fixed_buf >= 0: the partial rows were written straight into that buffer of the workspace by the producing GEMM
+    const size_t boff = (size_t)(fixed_buf >= 0 ? (uint32_t)fixed_buf : (epoch & 1u)) * buf_elems;
     for (int t = rank + world * (int)blockIdx.x; t < T; t += world * (int)gridDim.x) {
       float ssq = 0.f;
-      for (int i = tid * 8; i < H; i += 2048) {
+      for (int i = tid * 8; i < H; i += nt * 8) {
         float acc[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-        for (int r = 0; r < world; ++r) {
-          const __nv_bfloat16* src = (const __nv_bfloat16*)partials.p[r] + boff + (size_t)t * H + i;
-          uint4 v;
-          asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(src) : "memory");
-          const __nv_bfloat162* h2 = (const __nv_bfloat162*)&v;
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float2 f = __bfloat1622float2(h2[j]);
-            acc[2 * j] += f.x; acc[2 * j + 1] += f.y;
-          }
-        }
+        ds_sum_partials(partials, world, boff + (size_t)t * H + i, acc);
         float* res = residual + (size_t)t * H + i;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
@@ -852,14 +862,8 @@ __global__ void __launch_bounds__(256) ds_ar2_add_rmsnorm_kernel(DsPeers partial
           ssq += acc[j] * acc[j];
         }
       }
-      ssq = warp_sum(ssq);
-      __syncthreads();
-      if ((tid & 31) == 0) red[tid >> 5] = ssq;
-      __syncthreads();
-      float tot = 0.f;
-      for (int k = 0; k < 8; ++k) tot += red[k];
-      const float rstd = rsqrtf(tot / (float)H + eps);
-      for (int i = tid * 8; i < H; i += 2048) {
+      const float rstd = rsqrtf(ds_block_sum(ssq, red) / (float)H + eps);
+      for (int i = tid * 8; i < H; i += nt * 8) {
         const float* res = residual + (size_t)t * H + i;
         float v[8];
 #pragma unroll
@@ -884,7 +888,6 @@ __global__ void __launch_bounds__(256) ds_ar2_add_rmsnorm_kernel(DsPeers partial
   }
   __threadfence_system();
   __syncthreads();
-  if (atomicAdd_block((unsigned*)&ok_flag, 0u) == 0u) { /* a failed wait was already reported */ }
   __shared__ int last;
   if (tid == 0) {
     __threadfence();
@@ -1088,7 +1091,8 @@ PEAR_API int pear_ds_ar_add_rmsnorm(const void* const* partials, const void* con
                                     float eps, unsigned budget, int* status, int num_ctas, void* stream) {
   if (world < 1 || world > kDsMaxRanks || (H % 8) != 0 || T <= 0) return (int)cudaErrorInvalidValue;
   const int grid = T < num_ctas ? T : num_ctas;
-  ds_ar_add_rmsnorm_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(ds_ptrs(partials, world), ds_ptrs(flags, world), rank, world, slot, ctr, ticket,
+  const int threads = ((H / 8 + 31) / 32 * 32) < 1024 ? ((H / 8 + 31) / 32 * 32) : 1024;  // one 16-byte position per thread when the row fits
+  ds_ar_add_rmsnorm_kernel<<<grid, threads, 0, (cudaStream_t)stream>>>(ds_ptrs(partials, world), ds_ptrs(flags, world), rank, world, slot, ctr, ticket,
                                                                    residual, mode, weight, (__nv_bfloat16*)out_bf16, T, H, buf_elems, eps, budget, status);
   PEAR_LAUNCH_CHECK();
   return 0;
@@ -1098,14 +1102,15 @@ PEAR_API int pear_ds_ar_add_rmsnorm(const void* const* partials, const void* con
 // slots `slot` and `slot + 1`.
 PEAR_API int pear_ds_ar2_add_rmsnorm(const void* const* partials, const void* const* flags, const void* const* outs, const void* const* residuals,
                                      int rank, int world, int slot, unsigned* ctr, unsigned* ticket, int mode, int bcast_residual, const float* weight,
-                                     int T, int H, size_t buf_elems, float eps, unsigned budget, int* status, int num_ctas, void* stream) {
+                                     int T, int H, size_t buf_elems, int fixed_buf, float eps, unsigned budget, int* status, int num_ctas, void* stream) {
   if (world < 1 || world > kDsMaxRanks || (H % 8) != 0 || T <= 0) return (int)cudaErrorInvalidValue;
   const int mine = (T - rank + world - 1) / world;  // rows this rank owns
   int grid = mine < num_ctas ? mine : num_ctas;
   if (grid < 1) grid = 1;
-  ds_ar2_add_rmsnorm_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(ds_ptrs(partials, world), ds_ptrs(flags, world), ds_ptrs(outs, world),
+  const int threads = ((H / 8 + 31) / 32 * 32) < 1024 ? ((H / 8 + 31) / 32 * 32) : 1024;
+  ds_ar2_add_rmsnorm_kernel<<<grid, threads, 0, (cudaStream_t)stream>>>(ds_ptrs(partials, world), ds_ptrs(flags, world), ds_ptrs(outs, world),
                                                                     ds_ptrs(residuals, world), rank, world, slot, ctr, ticket, mode, bcast_residual, weight,
-                                                                    T, H, buf_elems, eps, budget, status);
+                                                                    T, H, buf_elems, fixed_buf, eps, budget, status);
   PEAR_LAUNCH_CHECK();
   return 0;
 }

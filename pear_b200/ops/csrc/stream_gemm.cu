@@ -254,7 +254,19 @@ PEAR_API int pear_stream_gemm_bf16(const void* x, const void* w, void* out, int 
   if ((ldx % 8) || (ldw % 8) || ((uintptr_t)x % 16) || ((uintptr_t)w % 16) || nsplit < 1 || epi < 0 || epi > 2) return (int)cudaErrorInvalidValue;
   if (epi != 0 && nsplit != 1) return (int)cudaErrorInvalidValue;
   if (nsplit > (K + kSgBK - 1) / kSgBK) return (int)cudaErrorInvalidValue;
-  const int bt = M <= 32 ? 32 : (M <= 64 ? 64 : (M <= 128 ? 128 : 256));
+  // token block: the whole step when it is small; for larger steps the block size that fills the SMs best (work items =
+  // weight tiles x token blocks x K splits, executed in rounds of num_sms), the larger block on a near tie
+  int bt = M <= 32 ? 32 : (M <= 64 ? 64 : 128);
+  if (M > 128) {
+    const int tiles_n = (N + kSgBM - 1) / kSgBM;
+    double best = -1.0;
+    for (int cand = 256; cand >= 64; cand >>= 1) {
+      const long long items = (long long)tiles_n * ((M + cand - 1) / cand) * nsplit;
+      const long long rounds = (items + num_sms - 1) / num_sms;
+      const double eff = (double)items / (double)(rounds * num_sms) * (cand == 64 ? 0.9 : 1.0);  // 64-token blocks reuse a weight tile less
+      if (eff > best + 0.05) { best = eff; bt = cand; }
+    }
+  }
   CUtensorMap mw, mx;
   const int w_rows = epi == 2 ? up_row0 + N : N;
   int r = sg_make_map(&mw, w, w_rows, K, ldw, kSgBM);

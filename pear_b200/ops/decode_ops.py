@@ -41,12 +41,22 @@ def check_status(device=None) -> None:
         raise RuntimeError(f"a bounded device-side wait of the rollout step gave up (status {code})")
 
 
-def pick_splits(m: int, n: int, k: int, sms: int = 148) -> int:
-    """K splits of the streaming GEMM so that about one work item per SM exists when the weight has few 128-row tiles."""
+def pick_splits(m: int, n: int, k: int, sms: int = 148, max_splits: int = 8) -> int:
+    """K splits of the streaming GEMM: work items (weight tiles x token blocks x splits) run in rounds of one per SM, so the
+    split count that fills its last round best wins (40 weight tiles: 7 splits = 280 items = 0.95 of two rounds, against 0.81
+    of one round with 3); fewer splits on a tie (every split is one more fp32 plane for the consumer to add)."""
     bt = 32 if m <= 32 else 64 if m <= 64 else 128 if m <= 128 else 256
     items = ((n + 127) // 128) * ((m + bt - 1) // bt)
     kblocks = (k + 63) // 64
-    return max(1, min(sms // max(1, items), max(1, kblocks // 4)))
+    if items >= sms:
+        return 1
+    best, best_eff = 1, 0.0
+    for ns in range(1, max(1, min(max_splits, kblocks // 4)) + 1):
+        total = items * ns
+        eff = total / (((total + sms - 1) // sms) * sms)
+        if eff > best_eff + 0.02:
+            best, best_eff = ns, eff
+    return best
 
 
 def stream_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, nsplit: int = 1, epi: int = 0, up_row0: int = 0, n: Optional[int] = None) -> torch.Tensor:
@@ -211,9 +221,9 @@ def ar_add_rmsnorm(partial_ptrs, flag_ptrs, rank: int, world: int, slot: int, ct
 
 
 def ar2_add_rmsnorm(partial_ptrs, flag_ptrs, out_ptrs, residual_ptrs, rank: int, world: int, slot: int, ctr, ticket, mode: int, bcast_residual: bool,
-                    weight, rows: int, h: int, buf_elems: int, eps: float, budget: int, status, num_ctas: int) -> None:
+                    weight, rows: int, h: int, buf_elems: int, eps: float, budget: int, status, num_ctas: int, fixed_buf: int = -1) -> None:
     """Two-shot all-reduce + add + RMSNorm over symmetric ``out`` / ``residual`` buffers (row t is reduced by rank t % world)."""
     _lib.check(_lib.lib().pear_ds_ar2_add_rmsnorm(partial_ptrs, flag_ptrs, out_ptrs, residual_ptrs, rank, world, slot, _lib.ptr(ctr), _lib.ptr(ticket), mode,
-                                                  1 if bcast_residual else 0, _lib.ptr(weight), rows, h, _sz(buf_elems), _f(eps), _u(budget),
+                                                  1 if bcast_residual else 0, _lib.ptr(weight), rows, h, _sz(buf_elems), fixed_buf, _f(eps), _u(budget),
                                                   _lib.ptr(status), num_ctas, _lib.stream()), "ds_ar2_add_rmsnorm")
     _lib.count_launch()

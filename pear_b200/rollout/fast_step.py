@@ -152,7 +152,7 @@ class FastDecoder:
             self.h_sel = torch.zeros(B, H, **b16)
         if self.world > 1:
             s = symm
-            self.ar_ws = s.alloc((2, M, H), torch.bfloat16)
+            self.ar_ws = s.alloc((3, M, H), torch.bfloat16)  # two buffers by epoch parity + one the GEMMs write straight into
             self.recs = s.alloc((2 * rec_elems * K.rec_bytes(),), torch.uint8)
             self.keys = s.alloc((2 * key_elems,), torch.int64)
             self.ar_ctr = s.device_counter(SLOT_STEP_AR)  # shared by every decoder on this SymmWorld: one epoch sequence per slot
@@ -357,6 +357,10 @@ class FastDecoder:
         """Row-parallel / column GEMM of the step's rows. Returns (tensor, nsplit)."""
         if epi == 0 and out is None:
             ns = min(self.max_split, K.pick_splits(rows, w.shape[0], w.shape[1], self.sms))
+            if self.world > 1 and ns == 1 and self._two_shot(rows):
+                # bf16 partial rows straight into the reduction's staging buffer: no separate staging kernel
+                K.stream_gemm(x[:rows], w, self.ar_ws.tensor[2, :rows], 1, 1)
+                return None, -1
             K.stream_gemm(x[:rows], w, self.parts[:, :rows], ns, 0)
             return self.parts, ns
         K.stream_gemm(x[:rows], w, out[:rows], 1, epi, up_row0, n)
@@ -374,11 +378,13 @@ class FastDecoder:
             K.add_rmsnorm(parts, ns, residual, weight, out, eps, mode, True, rows)
             return
         buf = self.ar_ws.tensor.shape[1] * self.ar_ws.tensor.shape[2]
-        K.reduce_parts_bf16(parts, ns, self.ar_ws.tensor, rows, self.H, buf, self.ar_ctr)
+        if ns >= 0:
+            K.reduce_parts_bf16(parts, ns, self.ar_ws.tensor, rows, self.H, buf, self.ar_ctr)
         if self._two_shot(rows):
             res_sym = self.x_sym if residual is self.x_res else self.r_sym
             K.ar2_add_rmsnorm(self.ar_ws.c_ptrs, self.symm.flags.c_ptrs, self.h_sym.c_ptrs, res_sym.c_ptrs, self.rank, self.world, SLOT_STEP_AR,
-                              self.ar_ctr, self.ar_ticket, mode, bcast, weight, rows, self.H, buf, eps, 1 << 22, self.status, 2 * self.sms)
+                              self.ar_ctr, self.ar_ticket, mode, bcast, weight, rows, self.H, buf, eps, 1 << 22, self.status, 2 * self.sms,
+                              fixed_buf=2 if ns < 0 else -1)
             return
         K.ar_add_rmsnorm(self.ar_ws.c_ptrs, self.symm.flags.c_ptrs, self.rank, self.world, SLOT_STEP_AR, self.ar_ctr, self.ar_ticket, residual, mode,
                          weight, out, rows, self.H, buf, eps, 1 << 22, self.status, 2 * self.sms)
