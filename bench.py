@@ -58,6 +58,231 @@ def reference_arm() -> None:
     print(json.dumps({"impl": "reference", "unavailable": why}))
 
 
+def reference_kernels_arm(args) -> None:
+    """``--impl reference --kernels``: the sm_100 kernels the reference itself ships for its Blackwell rollout backend
+    (``pear/models/qwen3_5/rollout/blackwell/csrc``: weight-streaming GEMM, tcgen05 verify attention, fused sampler, output
+    gate), JIT-built unmodified from ``baseline/_ref`` by the reference's own loader and timed on one GPU at the 27B shapes,
+    next to this repository's kernel for the same op on the same operands. Its peer-memory ops (fused all-reduce, logits
+    gather, draft argmax exchange) are not run: their device-side polls have no limit. CUDA events, L2 flushed between
+    iterations. Prints one JSON line."""
+    here = os.path.dirname(os.path.abspath(__file__))
+    ref = os.path.join(here, "baseline", "_ref")
+    out = {"impl": "reference", "mode": "kernels"}
+    if not os.path.isdir(os.path.join(ref, "pear")):
+        out["unavailable"] = "baseline/_ref is missing"
+        print(json.dumps(out))
+        return
+    sys.path.insert(0, ref)
+    import torch
+
+    try:
+        from pear.models.qwen3_5.rollout.blackwell.extension import BlackwellExtension
+
+        t0 = time.time()
+        try:
+            BlackwellExtension.load()
+        except RuntimeError as e:
+            # the installed package carries the .cu sources but not the host-only cuBLASLt wrappers (*.cpp), so the loader's
+            # last step (fake registration of `lt_mm` for traced graphs) fails AFTER the kernels were built and loaded; the
+            # ops timed here do not depend on it
+            if not hasattr(torch.ops.pear_rollout_blackwell, "sg_partials"):
+                raise
+            out["loader_note"] = f"register_fakes failed after the build ({str(e)[:120]}); the CUDA ops are loaded"
+        out["build_s"] = round(time.time() - t0, 1)
+    except Exception as e:  # noqa: BLE001
+        out["unavailable"] = f"the reference's extension did not build / load here: {type(e).__name__}: {str(e)[-600:]}"
+        print(json.dumps(out))
+        return
+    ref_ops = torch.ops.pear_rollout_blackwell
+    from pear_b200.ops import decode_ops as K
+
+    torch.cuda.set_device(0)
+    g = torch.Generator(device="cuda").manual_seed(0)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+
+    def timed(fn, iters=10, warmup=3) -> float:
+        """One launch at a time on an idle GPU with L2 flushed: includes the host's launch path (microseconds)."""
+        for _ in range(warmup):
+            fn()
+        total = 0.0
+        for _ in range(iters):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            total += e0.elapsed_time(e1)
+        return total / iters * 1e3  # microseconds
+
+    def timed_stream(fns, reps=4, iters=5) -> float:
+        """The launches of ``fns`` (one per operand copy, together larger than L2) captured back to back in a CUDA graph and
+        replayed: device time per launch as inside a decode step, no host launch path (microseconds)."""
+        for fn in fns:
+            fn()
+        torch.cuda.synchronize()
+        side = torch.cuda.Stream()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            for fn in fns:
+                fn()
+            side.synchronize()
+            with torch.cuda.graph(graph, stream=side):
+                for _ in range(reps):
+                    for fn in fns:
+                        fn()
+        torch.cuda.synchronize()
+        graph.replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(iters):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / (iters * reps * len(fns)) * 1e3
+
+    def bf(*shape, scale=0.05):
+        return (torch.randn(*shape, device="cuda", generator=g) * scale).to(torch.bfloat16)
+
+    rows = []
+
+    class guarded:  # one failing op must not lose the others' numbers
+        def __init__(self, what):
+            self.what = what
+
+        def __enter__(self):
+            return self
+
+        def __exit__(self, et, ev, tb):
+            if et is not None:
+                rows.append({"op": self.what, "error": f"{et.__name__}: {str(ev)[:300]}"})
+                torch.cuda.synchronize()
+            return True
+
+    M = 128
+    x5120 = bf(M, 5120, scale=0.5)
+    for name, n, k, splits in (("o_proj 5120x6144", 5120, 6144, 3), ("down_proj 5120x17408", 5120, 17408, 3), ("in_proj 16384x5120", 16384, 5120, 1)):
+      with guarded(f"stream GEMM {name}"):
+        copies = (300 << 20) // (n * k * 2) + 2  # weight copies cycled through: together well past L2
+        x, ws = bf(M, k, scale=0.5), [bf(n, k) for _ in range(copies)]
+        w = ws[0]
+        mine = torch.zeros(8, M, n, device="cuda")
+        ns = 1 if splits == 1 else K.pick_splits(M, n, k)  # the step runs its column-parallel GEMMs unsplit
+        t_ref = timed(lambda: ref_ops.sg_partials(x, w, splits))
+        t_own = timed(lambda: K.stream_gemm(x, w, mine, ns, 0))
+        err = float((mine[:ns].sum(0) - ref_ops.sg_partials(x, w, splits).sum(0)).abs().max())
+        row = {"op": f"stream GEMM fp32 partials, {M} tokens, {name}", "reference_us": round(t_ref, 1), "own_us": round(t_own, 1),
+               "reference_splits": splits, "own_splits": ns, "max_abs_diff": err}
+        with guarded(f"stream GEMM {name}, graph replay"):
+            s_ref = timed_stream([(lambda w_=w_: ref_ops.sg_partials(x, w_, splits)) for w_ in ws])
+            s_own = timed_stream([(lambda w_=w_: K.stream_gemm(x, w_, mine, ns, 0)) for w_ in ws])
+            s_own3 = timed_stream([(lambda w_=w_: K.stream_gemm(x, w_, mine, splits, 0)) for w_ in ws])
+            row.update({"replay_reference_us": round(s_ref, 1), "replay_own_us": round(s_own, 1), "replay_own_us_reference_splits": round(s_own3, 1),
+                        "replay_weight_gbs_reference": round(n * k * 2 / s_ref / 1e3, 1), "replay_weight_gbs_own": round(n * k * 2 / s_own / 1e3, 1)})
+        rows.append(row)
+        del ws
+    f = 17408
+    with guarded("stream GEMM + SwiGLU"):
+      w_gus = [bf(2 * f, 5120) for _ in range(3)]
+      w_gu = w_gus[0]
+      act = torch.zeros(M, f, dtype=torch.bfloat16, device="cuda")
+      t_ref = timed(lambda: ref_ops.sg_swiglu(x5120, w_gu))
+      t_own = timed(lambda: K.stream_gemm(x5120, w_gu, act, 1, 2, f, f))
+      row = {"op": f"stream GEMM + SwiGLU, {M} tokens, 2 x 17408 x 5120 (row layouts differ: timing only)", "reference_us": round(t_ref, 1),
+             "own_us": round(t_own, 1)}
+      with guarded("stream GEMM + SwiGLU, graph replay"):
+          s_ref = timed_stream([(lambda w_=w_: ref_ops.sg_swiglu(x5120, w_)) for w_ in w_gus])
+          s_own = timed_stream([(lambda w_=w_: K.stream_gemm(x5120, w_, act, 1, 2, f, f)) for w_ in w_gus])
+          row.update({"replay_reference_us": round(s_ref, 1), "replay_own_us": round(s_own, 1),
+                      "replay_weight_gbs_reference": round(2 * f * 5120 * 2 / s_ref / 1e3, 1), "replay_weight_gbs_own": round(2 * f * 5120 * 2 / s_own / 1e3, 1)})
+      rows.append(row)
+      del w_gus
+    with guarded("output gate"):
+      # output gate
+      xa = bf(M, 24 * 256, scale=1.0)
+      gate = bf(M, 24 * 256, scale=1.0)
+      t_ref = timed(lambda: ref_ops.output_gate(xa, gate))
+      rows.append({"op": "output gate x * sigmoid(g), 128 x 6144 (here: fused into the attention epilogue, no kernel of its own)", "reference_us": round(t_ref, 1),
+                   "own_us": 0.0})
+    with guarded("sampler"):
+      # fused sampler
+      R, V = 128, 248320
+      logits = torch.randn(R, V, device="cuda", generator=g) * 2
+      q = torch.empty(R, V, device="cuda").exponential_(generator=g)
+      temp = torch.ones(R, device="cuda")
+      t_ref = timed(lambda: ref_ops.fused_sample(logits, q, temp, 32, 32))  # 32 chunks per row: the reference's own launch shape
+      i32 = dict(dtype=torch.int32, device="cuda")
+      B, T = 32, 4
+      tok_in, ctx, step_ctr = torch.zeros(B * T, **i32), torch.zeros(B, **i32), torch.zeros(1, **i32)
+      recs = torch.zeros(B * T * 2 * K.rec_bytes(), dtype=torch.uint8, device="cuda")
+      ptrs = K._ptr_array([recs.data_ptr()])
+      outs = [torch.zeros(B, T, **i32), torch.zeros(B, T, device="cuda")] + [torch.zeros(B, **i32) for _ in range(3)] + [torch.zeros(B * T, **i32), torch.zeros(T, B, **i32)]
+      ncommit, parity = torch.zeros(B, **i32), torch.zeros(B, **i32)
+
+      def own_sampler():
+          ctx.zero_()
+          K.verify_chunks(logits, V, 0, 1.0, tok_in, ctx, B, T, 2, 1, step_ctr, ptrs, 0, 1, None, 0)
+          K.verify_finish(recs, 0, None, 1, 2, B, T, 1, step_ctr, tok_in, ctx, ncommit, parity, *outs)
+
+      t_own = timed(own_sampler)
+      rows.append({"op": f"sampler over {R} rows x {V} (reference: temperature sampling + top-32 log-probs from a caller-made noise tensor; "
+                         "here: rejection sampling of greedy drafts with in-kernel Philox, no top-32)", "reference_us": round(t_ref, 1), "own_us": round(t_own, 1)})
+    with guarded("verify attention"):
+      # verify attention: 32 requests x 4 rows, 24 q / 4 kv heads, 8192-token context with a 6144-token shared prefix
+      n, T, Hq, Hkv, D, ctx_len, prefix = 32, 4, 24, 4, 256, 8192, 6144
+      pages64 = prefix // 64 + n * ((ctx_len - prefix + T) // 64 + 1) + 1
+      kv = bf(pages64, Hkv, 64, 2 * D, scale=1.0)
+      table64 = torch.zeros(n, (ctx_len + T) // 64 + 1, **i32)
+      shared = torch.arange(1, 1 + prefix // 64, dtype=torch.int32)
+      per = (ctx_len - prefix + T) // 64 + 1
+      for b in range(n):
+          own = torch.arange(1 + prefix // 64 + b * per, 1 + prefix // 64 + (b + 1) * per, dtype=torch.int32)
+          table64[b, : prefix // 64 + per] = torch.cat([shared, own]).cuda()
+      qv, kn, vn = bf(n * T, Hq, D, scale=1.0), bf(n * T, Hkv, D, scale=1.0), bf(n * T, Hkv, D, scale=1.0)
+      pos = torch.arange(ctx_len, ctx_len + T)
+      slot = torch.stack([table64[b, (pos // 64)].cpu().long() * 64 + pos % 64 for b in range(n)]).reshape(-1).cuda()
+      seq_lens = torch.full((n,), ctx_len + T, **i32)
+      ctas = 148
+      part_o = torch.zeros((ctas + n * Hkv) * 48 * D, device="cuda")
+      part_ml = torch.zeros((ctas + n * Hkv) * 48 * 2, device="cuda")
+      o_ref = torch.zeros(n * T, Hq, D, dtype=torch.bfloat16, device="cuda")
+      t_ref = timed(lambda: ref_ops.verify_attention(qv, kn, vn, slot, kv, table64, seq_lens, o_ref, part_o, part_ml, n, T, D ** -0.5, ctas))
+      # the same keys and values in this repository's layout: 16-token pages [page, 16, Hkv, 256], K and V separate
+      pages16 = pages64 * 4
+      kc = kv[..., :D].permute(0, 2, 1, 3).reshape(pages64, 4, 16, Hkv, D).reshape(pages16, 16, Hkv, D).contiguous()
+      vc = kv[..., D:].permute(0, 2, 1, 3).reshape(pages64, 4, 16, Hkv, D).reshape(pages16, 16, Hkv, D).contiguous()
+      table16 = (table64.long()[:, :, None] * 4 + torch.arange(4, device="cuda")).reshape(n, -1).int().contiguous()
+      ctxv = torch.full((n,), ctx_len, **i32)
+      o_own = torch.zeros(n * T, Hq * D, dtype=torch.bfloat16, device="cuda")
+      gate_src = torch.zeros(n * T, 2 * Hq * D, device="cuda")
+      splits = 6
+      items = [[1, prefix, -1, 0, 1 + splits, 1 + 8, 0, 0, b] + [0] * 15 for b in range(n)]
+      tiles = prefix // 128
+      for i in range(0, n, 5):
+          sub = list(range(i, min(n, i + 5)))
+          for sp in range(splits):
+              items.append([len(sub), tiles * sp // splits * 128, tiles * (sp + 1) // splits * 128, 1 + sp, 0, 0, 0, 0] + sub + [0] * (16 - len(sub)))
+      items_t = torch.tensor(items, **i32)
+      po, pml = torch.zeros(9, n * T, Hq, D, device="cuda"), torch.zeros(9, n * T, Hq, 2, device="cuda")
+      t_own_items = timed(lambda: K.paged_attention(qv, kc, vc, table16, ctxv, n, T, Hq, Hkv, D, D ** -0.5, gate_src, False, o_own, True, items_t, 9, po, pml))
+      err_items = float((o_own.view(n * T, Hq, D).float() - o_ref.float()).abs().max())
+      t_own_direct = timed(lambda: K.paged_attention(qv, kc, vc, table16, ctxv, n, T, Hq, Hkv, D, D ** -0.5, gate_src, False, o_own, True))
+      row = {"op": f"paged verify attention, {n} requests x {T} rows, {Hq} q / {Hkv} kv heads, context {ctx_len} ({prefix} shared); reference pages of 64 "
+                         "tokens, here 16 (the reference also writes the step's K / V into the cache inside the kernel)", "reference_us": round(t_ref, 1),
+                   "own_us": round(t_own_items, 1), "own_us_without_prefix_sharing": round(t_own_direct, 1), "max_abs_diff": err_items}
+      with guarded("verify attention, graph replay"):  # one launch reads 290 MB of pages: larger than L2 by itself
+          row["replay_reference_us"] = round(timed_stream([lambda: ref_ops.verify_attention(qv, kn, vn, slot, kv, table64, seq_lens, o_ref, part_o, part_ml, n, T, D ** -0.5, ctas)]), 1)
+          row["replay_own_us"] = round(timed_stream([lambda: K.paged_attention(qv, kc, vc, table16, ctxv, n, T, Hq, Hkv, D, D ** -0.5, gate_src, False, o_own, True, items_t, 9, po, pml)]), 1)
+      rows.append(row)
+    K.check_status()
+    out["kernels"] = rows
+    out["note"] = ("x_us: CUDA events around single launches on an idle GPU, L2 flushed (256 MB write) before each, host launch path included; "
+                   "replay_x_us: device time per launch of a replayed CUDA graph cycling operand copies larger than L2; microseconds")
+    print(json.dumps(out))
+
+
 class ClockSampler:
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -438,6 +663,7 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="pear_b200")
+    ap.add_argument("--kernels", action="store_true", help="with --impl reference: time the reference's own sm_100 rollout kernels beside ours")
     ap.add_argument("--seqs-per-gpu", type=int, default=32)
     ap.add_argument("--prefix-len", type=int, default=6144)
     ap.add_argument("--suffix-len", type=int, default=2048)
@@ -461,7 +687,10 @@ def main() -> None:
     ap.add_argument("--breakdown", type=int, default=0)
     args = ap.parse_args()
     if args.impl == "reference":
-        reference_arm()
+        if args.kernels:
+            reference_kernels_arm(args)
+        else:
+            reference_arm()
         return
     if args.trainer_step or args.gdn_scan:
         print(json.dumps(run_trainer_step(args) if args.trainer_step else run_gdn_scan(args)))

@@ -12,6 +12,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define PEAR_API extern "C" __attribute__((visibility("default")))
 
@@ -320,5 +321,56 @@ template <>
 __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 template <>
 __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+
+// ------------------------------------------------------------------------------------------------ dependent launches
+// A kernel launched through launch_dependent() may start while the kernel before it in the stream is still running
+// (programmatic dependent launch): its blocks become resident as the earlier kernel's blocks retire, run whatever does
+// not depend on earlier kernels (barrier and TMEM set-up, loads of weights), and call grid_dependency_wait() before the
+// first access to memory that an earlier kernel writes or reads. grid_dependency_wait() returns once every kernel
+// before this one in the stream has completed and its writes are visible; without the launch attribute it returns at
+// once. grid_dependency_trigger() lets the NEXT kernel's blocks be scheduled as soon as every block of this grid has
+// called it or exited; that kernel still waits for this one's completion in its own grid_dependency_wait().
+// (The upstream GEMM launches the same way: pear/models/qwen3_5/rollout/blackwell/csrc/stream_gemm.cu:3-4.)
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+#ifdef __CUDACC__
+inline bool dependent_launch_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("PEAR_DEPENDENT_LAUNCH");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
+// Launch `kernel` as a programmatic dependent of the work before it in `stream`. Every kernel launched this way calls
+// grid_dependency_wait() before it touches anything but constants (weights, its own parameters).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(bool dependent, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = dependent && dependent_launch_enabled() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(static_cast<Args&&>(args))...);
+}
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  return launch_kernel(true, kernel, grid, block, smem, stream, static_cast<Args&&>(args)...);
+}
+// An ordinary launch (the kernel starts after everything before it in the stream has completed) of a kernel that calls
+// grid_dependency_trigger(): the kernel AFTER it, if launched as a dependent, may still start early. The step's small
+// kernels are launched this way: as dependents they measured slower (a chain of row-norm kernels: 6.5 us per launch
+// against 5.2 us), while the GEMM after each of them gains from filling its weight ring during their run.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_ordinary(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  return launch_kernel(false, kernel, grid, block, smem, stream, static_cast<Args&&>(args)...);
+}
+#endif
 
 }  // namespace pear

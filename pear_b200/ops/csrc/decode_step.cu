@@ -70,6 +70,8 @@ __global__ void ds_accept_uniform_kernel(float* out, int rows, uint32_t seed, ui
 __global__ void __launch_bounds__(256) ds_add_rmsnorm_kernel(const float* __restrict__ parts, int nsplit, long long split_stride, int ldp,
                                                              float* __restrict__ residual, int mode, const float* __restrict__ w,
                                                              __nv_bfloat16* __restrict__ out, int H, float eps, int one_plus) {
+  grid_dependency_trigger();
+  grid_dependency_wait();
   __shared__ float red[8];
   const int row = blockIdx.x, tid = threadIdx.x;
   float* res = residual + (size_t)row * H;
@@ -106,6 +108,8 @@ __global__ void __launch_bounds__(256) ds_add_rmsnorm_kernel(const float* __rest
 __global__ void __launch_bounds__(256) ds_reduce_parts_bf16_kernel(const float* __restrict__ parts, int nsplit, long long split_stride, int ldp,
                                                                    __nv_bfloat16* __restrict__ out, size_t buf_elems,
                                                                    const uint32_t* __restrict__ epoch_ctr, int H) {
+  grid_dependency_trigger();
+  grid_dependency_wait();
   const int row = blockIdx.x;
   __nv_bfloat16* o = out + (epoch_ctr ? (size_t)((*epoch_ctr + 1u) & 1u) * buf_elems : 0) + (size_t)row * H;
   for (int i = threadIdx.x * 4; i < H; i += 1024) {
@@ -133,6 +137,8 @@ __global__ void __launch_bounds__(256) ds_attn_prep_kernel(const float* __restri
                                                            const int* __restrict__ block_table, int max_blocks, int T, int Hq, int Hkv, int gated,
                                                            float eps, __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ kc,
                                                            __nv_bfloat16* __restrict__ vc) {
+  grid_dependency_trigger();
+  grid_dependency_wait();
   __shared__ float cs[64], sn[64];
   __shared__ float head[8][D];
   const int row = blockIdx.x, b = row / T, t = row % T;
@@ -276,7 +282,10 @@ __global__ void __launch_bounds__(kGdnThreads) ds_gdn_verify_kernel(const __grid
   uint64_t* bar = (uint64_t*)(rown + RM * 2);
   const int hv = blockIdx.x, b = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int row = tid >> 1, half = tid & 1;  // state row of this thread and which columns of it: chunks 4 * half .. + 3 of every box
-  if (ctx[b] < 0) return;
+  if (ctx[b] < 0) {
+    grid_dependency_wait();  // every block waits before it leaves: the grid must not complete ahead of the kernels before it
+    return;
+  }
   const int slot = slots[b], par = parity[b] & 1, nc = min(ncommit[b], Tmax);
   const int rep = Hv / Hk, hk = hv / rep;
   const int C = 2 * Hk * D + Hv * D;
@@ -294,6 +303,10 @@ __global__ void __launch_bounds__(kGdnThreads) ds_gdn_verify_kernel(const __grid
     mbar_expect_tx(bar, D * D * 4);
     for (int p = 0; p < 4; ++p) tma_load_2d(Ssm + p * 16384, &map_s, p * 32, srow0, bar);
   }
+  // Up to here the kernel read only what no kernel of this step writes before it (the sequence's slot, context and parity,
+  // this layer's state): the state streams in while the projection GEMM ahead in the stream drains.
+  grid_dependency_trigger();
+  grid_dependency_wait();
 
   // ---- (2) inputs of all rows: conv + SiLU on channel `row` of q, k, v (both threads of a pair compute it, one publishes)
   const float4 wq = *(const float4*)(conv_w + (size_t)ch_q * 4), wk = *(const float4*)(conv_w + (size_t)ch_k * 4),
@@ -472,6 +485,8 @@ __global__ void __launch_bounds__(256) ds_verify_chunks_kernel(const float* __re
                                                                const int* __restrict__ tok_in, const int* __restrict__ ctx, int T, int chunks,
                                                                uint32_t seed, const uint32_t* __restrict__ step_ctr, DsPeers recs, int rank, int world,
                                                                const uint32_t* __restrict__ epoch_ctr, size_t rec_buf_elems) {
+  grid_dependency_trigger();
+  grid_dependency_wait();
   __shared__ float red[8 * 5];
   __shared__ int redi[8 * 2];
   const int chunk = blockIdx.x, row = blockIdx.y, b = row / T, t = row % T, tid = threadIdx.x;
@@ -551,6 +566,8 @@ __global__ void ds_verify_finish_kernel(const DsRec* __restrict__ recs, size_t r
                                         int* __restrict__ ctx, int* __restrict__ ncommit, int* __restrict__ parity, int* __restrict__ out_tok,
                                         float* __restrict__ out_lp, int* __restrict__ n_accept, int* __restrict__ nonfinite,
                                         int* __restrict__ sel_row, int* __restrict__ mtp_tok, int* __restrict__ mtp_ctx, int B) {
+  grid_dependency_trigger();
+  grid_dependency_wait();
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   const uint32_t step = *step_ctr;
   if (b < B && ctx[b] >= 0) {
@@ -604,6 +621,8 @@ __global__ void ds_verify_finish_kernel(const DsRec* __restrict__ recs, size_t r
 
 // the step counter moves in a launch of its own: every CTA of the finish kernel has read it by then
 __global__ void ds_bump_kernel(uint32_t* ctr) {
+  grid_dependency_trigger();
+  grid_dependency_wait();
   if (threadIdx.x == 0 && blockIdx.x == 0) *ctr += 1u;
 }
 
@@ -614,6 +633,8 @@ __global__ void __launch_bounds__(256) ds_mtp_input_kernel(const int* __restrict
                                                            const float* __restrict__ hidden, const int* __restrict__ sel,
                                                            const float* __restrict__ we, const float* __restrict__ wh, int H, float eps,
                                                            __nv_bfloat16* __restrict__ out) {
+  grid_dependency_trigger();
+  grid_dependency_wait();
   __shared__ float red[16];
   const int row = blockIdx.x, tid = threadIdx.x;
   const int id = min(max(tokens[row], 0), V - 1);
@@ -639,6 +660,8 @@ __global__ void __launch_bounds__(256) ds_mtp_input_kernel(const int* __restrict
 
 // rows of fp32 [*, H] gathered through `sel` (the drafter's hidden state of the accepted row)
 __global__ void ds_gather_rows_kernel(const float* __restrict__ src, const int* __restrict__ sel, float* __restrict__ dst, int H) {
+  grid_dependency_trigger();
+  grid_dependency_wait();
   const int row = blockIdx.x;
   const float4* s = (const float4*)(src + (size_t)sel[row] * H);
   float4* d = (float4*)(dst + (size_t)row * H);
@@ -650,6 +673,8 @@ __global__ void ds_gather_rows_kernel(const float* __restrict__ src, const int* 
 // ~token id, so ties go to the lower id) stored into every rank's buffer, then a per-row maximum over ranks x chunks.
 __global__ void __launch_bounds__(256) ds_argmax_chunks_kernel(const float* __restrict__ logits, int ld, int Vs, int v0, int chunks, DsPeers keys,
                                                                int rank, int world, const uint32_t* __restrict__ epoch_ctr, size_t buf_elems) {
+  grid_dependency_trigger();
+  grid_dependency_wait();
   __shared__ unsigned long long red[8];
   const int chunk = blockIdx.x, row = blockIdx.y, tid = threadIdx.x;
   const int per = (Vs + chunks - 1) / chunks, lo = chunk * per, hi = min(Vs, lo + per);
@@ -680,6 +705,8 @@ __global__ void __launch_bounds__(256) ds_argmax_chunks_kernel(const float* __re
 __global__ void ds_argmax_finish_kernel(const unsigned long long* __restrict__ keys, size_t buf_elems, const uint32_t* __restrict__ epoch_ctr,
                                         int world, int chunks, int rows, int* __restrict__ dst, int dst_stride, int dst_off,
                                         int* __restrict__ tok_out) {
+  grid_dependency_trigger();
+  grid_dependency_wait();
   const int row = blockIdx.x * blockDim.x + threadIdx.x;
   if (row >= rows) return;
   const unsigned long long* base = keys + (epoch_ctr ? (size_t)((*epoch_ctr) & 1u) * buf_elems : 0);
@@ -699,6 +726,8 @@ __global__ void ds_argmax_finish_kernel(const unsigned long long* __restrict__ k
 // *ctr + 1 is released to every peer, every peer's flag is awaited with a bounded poll, then the counter takes the
 // new value. One CTA. Buffers exchanged under this barrier alternate by the epoch's parity.
 __global__ void ds_symm_barrier_kernel(DsPeers flags, int rank, int world, int slot, uint32_t* ctr, uint32_t budget, int* status) {
+  grid_dependency_trigger();
+  grid_dependency_wait();
   const int r = threadIdx.x;
   const uint32_t e = *ctr + 1u;
   if (r < world) {
@@ -764,6 +793,8 @@ __global__ void __launch_bounds__(1024) ds_ar_add_rmsnorm_kernel(DsPeers partial
                                                                 uint32_t* ticket, float* __restrict__ residual, int mode,
                                                                 const float* __restrict__ weight, __nv_bfloat16* __restrict__ out, int T, int H,
                                                                 size_t buf_elems, float eps, uint32_t budget, int* status) {
+  grid_dependency_trigger();
+  grid_dependency_wait();
   __shared__ float red[32];
   __shared__ int ok_flag;
   const int tid = threadIdx.x, nt = blockDim.x;
@@ -826,6 +857,8 @@ __global__ void __launch_bounds__(1024) ds_ar2_add_rmsnorm_kernel(DsPeers partia
                                                                  int slot, uint32_t* ctr, uint32_t* ticket, int mode, int bcast_residual,
                                                                  const float* __restrict__ weight, int T, int H, size_t buf_elems, int fixed_buf, float eps,
                                                                  uint32_t budget, int* status) {
+  grid_dependency_trigger();
+  grid_dependency_wait();
   __shared__ float red[32];
   __shared__ int ok_flag;
   const int tid = threadIdx.x, nt = blockDim.x;
@@ -935,8 +968,8 @@ PEAR_API int pear_ds_add_rmsnorm(const float* parts, int nsplit, long long split
                                  void* out_bf16, int rows, int H, float eps, int one_plus, void* stream) {
   if (H % 4 || (nsplit > 0 && ldp % 4)) return (int)cudaErrorInvalidValue;
   if (rows <= 0) return 0;
-  ds_add_rmsnorm_kernel<<<rows, 256, 0, (cudaStream_t)stream>>>(parts, nsplit, split_stride, ldp, residual, mode, w, (__nv_bfloat16*)out_bf16, H, eps,
-                                                                one_plus);
+  PEAR_CUDA_CHECK(launch_ordinary(ds_add_rmsnorm_kernel, dim3(rows), dim3(256), 0, (cudaStream_t)stream, parts, nsplit, split_stride, ldp, residual, mode, w, (__nv_bfloat16*)out_bf16, H, eps,
+                                                                one_plus));
   PEAR_LAUNCH_CHECK();
   return 0;
 }
@@ -945,7 +978,7 @@ PEAR_API int pear_ds_reduce_parts_bf16(const float* parts, int nsplit, long long
                                        const unsigned* epoch_ctr, int rows, int H, void* stream) {
   if (H % 4 || ldp % 4) return (int)cudaErrorInvalidValue;
   if (rows <= 0) return 0;
-  ds_reduce_parts_bf16_kernel<<<rows, 256, 0, (cudaStream_t)stream>>>(parts, nsplit, split_stride, ldp, (__nv_bfloat16*)out_bf16, buf_elems, epoch_ctr, H);
+  PEAR_CUDA_CHECK(launch_ordinary(ds_reduce_parts_bf16_kernel, dim3(rows), dim3(256), 0, (cudaStream_t)stream, parts, nsplit, split_stride, ldp, (__nv_bfloat16*)out_bf16, buf_elems, epoch_ctr, H));
   PEAR_LAUNCH_CHECK();
   return 0;
 }
@@ -956,8 +989,8 @@ PEAR_API int pear_ds_attn_prep(const float* qkv, int ld, const float* qn_w, cons
   if (rot > 128 || rot > D || (rot & 1)) return (int)cudaErrorInvalidValue;
   cudaStream_t s = (cudaStream_t)stream;
 #define PEAR_PREP(DD)                                                                                                                       \
-  ds_attn_prep_kernel<DD><<<rows, 256, 0, s>>>(qkv, ld, qn_w, kn_w, inv_freq, rot, ctx, rope_off, block_table, max_blocks, T, Hq, Hkv, gated, eps, \
-                                               (__nv_bfloat16*)q_out, (__nv_bfloat16*)kc, (__nv_bfloat16*)vc)
+  PEAR_CUDA_CHECK(launch_ordinary(ds_attn_prep_kernel<DD>, dim3(rows), dim3(256), 0, s, qkv, ld, qn_w, kn_w, inv_freq, rot, ctx, rope_off, block_table, \
+                                   max_blocks, T, Hq, Hkv, gated, eps, (__nv_bfloat16*)q_out, (__nv_bfloat16*)kc, (__nv_bfloat16*)vc))
   if (D == 256) PEAR_PREP(256);
   else if (D == 128) PEAR_PREP(128);
   else if (D == 64) PEAR_PREP(64);
@@ -1014,8 +1047,8 @@ PEAR_API int pear_ds_gdn_verify(const float* proj, int ld, const float* conv_w, 
     PEAR_CUDA_CHECK(cudaFuncSetAttribute(ds_gdn_verify_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured = true;
   }
-  ds_gdn_verify_kernel<<<dim3(Hv, B), kGdnThreads, smem, (cudaStream_t)stream>>>(map_s, proj, ld, conv_w, A_log, dt_bias, norm_w, state, conv_rec, ab_rec, slots, ctx,
-                                                                         parity, ncommit, T, Tmax, Hk, Hv, l2_eps, rms_eps, (__nv_bfloat16*)out, status);
+  PEAR_CUDA_CHECK(launch_dependent(ds_gdn_verify_kernel, dim3(dim3(Hv, B)), dim3(kGdnThreads), smem, (cudaStream_t)stream, map_s, proj, ld, conv_w, A_log, dt_bias, norm_w, state, conv_rec, ab_rec, slots, ctx,
+                                                                         parity, ncommit, T, Tmax, Hk, Hv, l2_eps, rms_eps, (__nv_bfloat16*)out, status));
   PEAR_LAUNCH_CHECK();
   return 0;
 }
@@ -1028,8 +1061,8 @@ PEAR_API int pear_ds_verify_chunks(const float* logits, int ld, int Vs, int v0, 
                                    int chunks, unsigned seed, const unsigned* step_ctr, const void* const* recs, int rank, int world,
                                    const unsigned* epoch_ctr, size_t rec_buf_elems, void* stream) {
   if (temperature <= 0.f || chunks < 1 || world < 1 || world > kDsMaxRanks) return (int)cudaErrorInvalidValue;
-  ds_verify_chunks_kernel<<<dim3(chunks, B * T), 256, 0, (cudaStream_t)stream>>>(logits, ld, Vs, v0, 1.f / temperature, tok_in, ctx, T, chunks, seed,
-                                                                                 step_ctr, ds_ptrs(recs, world), rank, world, epoch_ctr, rec_buf_elems);
+  PEAR_CUDA_CHECK(launch_ordinary(ds_verify_chunks_kernel, dim3(dim3(chunks, B * T)), dim3(256), 0, (cudaStream_t)stream, logits, ld, Vs, v0, 1.f / temperature, tok_in, ctx, T, chunks, seed,
+                                                                                 step_ctr, ds_ptrs(recs, world), rank, world, epoch_ctr, rec_buf_elems));
   PEAR_LAUNCH_CHECK();
   return 0;
 }
@@ -1038,10 +1071,10 @@ PEAR_API int pear_ds_verify_finish(const void* my_recs, size_t rec_buf_elems, co
                                    unsigned seed, unsigned* step_ctr, int* tok_in, int* ctx, int* ncommit, int* parity, int* out_tok, float* out_lp,
                                    int* n_accept, int* nonfinite, int* sel_row, int* mtp_tok, int* mtp_ctx, void* stream) {
   cudaStream_t s = (cudaStream_t)stream;
-  ds_verify_finish_kernel<<<(B + 31) / 32, 32, 0, s>>>((const DsRec*)my_recs, rec_buf_elems, epoch_ctr, world, chunks, B * T, T, seed, step_ctr, tok_in,
-                                                       ctx, ncommit, parity, out_tok, out_lp, n_accept, nonfinite, sel_row, mtp_tok, mtp_ctx, B);
+  PEAR_CUDA_CHECK(launch_ordinary(ds_verify_finish_kernel, dim3((B + 31) / 32), dim3(32), 0, s, (const DsRec*)my_recs, rec_buf_elems, epoch_ctr, world, chunks, B * T, T, seed, step_ctr, tok_in,
+                                                       ctx, ncommit, parity, out_tok, out_lp, n_accept, nonfinite, sel_row, mtp_tok, mtp_ctx, B));
   PEAR_LAUNCH_CHECK();
-  ds_bump_kernel<<<1, 32, 0, s>>>(step_ctr);
+  PEAR_CUDA_CHECK(launch_ordinary(ds_bump_kernel, dim3(1), dim3(32), 0, s, step_ctr));
   PEAR_LAUNCH_CHECK();
   return 0;
 }
@@ -1049,14 +1082,14 @@ PEAR_API int pear_ds_verify_finish(const void* my_recs, size_t rec_buf_elems, co
 PEAR_API int pear_ds_mtp_input(const int* tokens, const void* table, int V, const float* hidden, const int* sel, const float* we, const float* wh,
                                int rows, int H, float eps, void* out, void* stream) {
   if (rows <= 0) return 0;
-  ds_mtp_input_kernel<<<rows, 256, 0, (cudaStream_t)stream>>>(tokens, (const __nv_bfloat16*)table, V, hidden, sel, we, wh, H, eps, (__nv_bfloat16*)out);
+  PEAR_CUDA_CHECK(launch_ordinary(ds_mtp_input_kernel, dim3(rows), dim3(256), 0, (cudaStream_t)stream, tokens, (const __nv_bfloat16*)table, V, hidden, sel, we, wh, H, eps, (__nv_bfloat16*)out));
   PEAR_LAUNCH_CHECK();
   return 0;
 }
 
 PEAR_API int pear_ds_gather_rows(const float* src, const int* sel, float* dst, int rows, int H, void* stream) {
   if (H % 4) return (int)cudaErrorInvalidValue;
-  ds_gather_rows_kernel<<<rows, 256, 0, (cudaStream_t)stream>>>(src, sel, dst, H);
+  PEAR_CUDA_CHECK(launch_ordinary(ds_gather_rows_kernel, dim3(rows), dim3(256), 0, (cudaStream_t)stream, src, sel, dst, H));
   PEAR_LAUNCH_CHECK();
   return 0;
 }
@@ -1064,23 +1097,23 @@ PEAR_API int pear_ds_gather_rows(const float* src, const int* sel, float* dst, i
 PEAR_API int pear_ds_argmax_chunks(const float* logits, int ld, int Vs, int v0, int rows, int chunks, const void* const* keys, int rank, int world,
                                    const unsigned* epoch_ctr, size_t buf_elems, void* stream) {
   if (chunks < 1 || world < 1 || world > kDsMaxRanks) return (int)cudaErrorInvalidValue;
-  ds_argmax_chunks_kernel<<<dim3(chunks, rows), 256, 0, (cudaStream_t)stream>>>(logits, ld, Vs, v0, chunks, ds_ptrs(keys, world), rank, world, epoch_ctr,
-                                                                                buf_elems);
+  PEAR_CUDA_CHECK(launch_ordinary(ds_argmax_chunks_kernel, dim3(dim3(chunks, rows)), dim3(256), 0, (cudaStream_t)stream, logits, ld, Vs, v0, chunks, ds_ptrs(keys, world), rank, world, epoch_ctr,
+                                                                                buf_elems));
   PEAR_LAUNCH_CHECK();
   return 0;
 }
 
 PEAR_API int pear_ds_argmax_finish(const void* my_keys, size_t buf_elems, const unsigned* epoch_ctr, int world, int chunks, int rows, int* dst,
                                    int dst_stride, int dst_off, int* tok_out, void* stream) {
-  ds_argmax_finish_kernel<<<(rows + 127) / 128, 128, 0, (cudaStream_t)stream>>>((const unsigned long long*)my_keys, buf_elems, epoch_ctr, world, chunks,
-                                                                                rows, dst, dst_stride, dst_off, tok_out);
+  PEAR_CUDA_CHECK(launch_ordinary(ds_argmax_finish_kernel, dim3((rows + 127) / 128), dim3(128), 0, (cudaStream_t)stream, (const unsigned long long*)my_keys, buf_elems, epoch_ctr, world, chunks,
+                                                                                rows, dst, dst_stride, dst_off, tok_out));
   PEAR_LAUNCH_CHECK();
   return 0;
 }
 
 PEAR_API int pear_ds_symm_barrier(const void* const* flags, int rank, int world, int slot, unsigned* ctr, unsigned budget, int* status, void* stream) {
   if (world < 1 || world > kDsMaxRanks) return (int)cudaErrorInvalidValue;
-  ds_symm_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(ds_ptrs(flags, world), rank, world, slot, ctr, budget, status);
+  PEAR_CUDA_CHECK(launch_ordinary(ds_symm_barrier_kernel, dim3(1), dim3(32), 0, (cudaStream_t)stream, ds_ptrs(flags, world), rank, world, slot, ctr, budget, status));
   PEAR_LAUNCH_CHECK();
   return 0;
 }
@@ -1092,8 +1125,8 @@ PEAR_API int pear_ds_ar_add_rmsnorm(const void* const* partials, const void* con
   if (world < 1 || world > kDsMaxRanks || (H % 8) != 0 || T <= 0) return (int)cudaErrorInvalidValue;
   const int grid = T < num_ctas ? T : num_ctas;
   const int threads = ((H / 8 + 31) / 32 * 32) < 1024 ? ((H / 8 + 31) / 32 * 32) : 1024;  // one 16-byte position per thread when the row fits
-  ds_ar_add_rmsnorm_kernel<<<grid, threads, 0, (cudaStream_t)stream>>>(ds_ptrs(partials, world), ds_ptrs(flags, world), rank, world, slot, ctr, ticket,
-                                                                   residual, mode, weight, (__nv_bfloat16*)out_bf16, T, H, buf_elems, eps, budget, status);
+  PEAR_CUDA_CHECK(launch_ordinary(ds_ar_add_rmsnorm_kernel, dim3(grid), dim3(threads), 0, (cudaStream_t)stream, ds_ptrs(partials, world), ds_ptrs(flags, world), rank, world, slot, ctr, ticket,
+                                                                   residual, mode, weight, (__nv_bfloat16*)out_bf16, T, H, buf_elems, eps, budget, status));
   PEAR_LAUNCH_CHECK();
   return 0;
 }
@@ -1108,9 +1141,9 @@ PEAR_API int pear_ds_ar2_add_rmsnorm(const void* const* partials, const void* co
   int grid = mine < num_ctas ? mine : num_ctas;
   if (grid < 1) grid = 1;
   const int threads = ((H / 8 + 31) / 32 * 32) < 1024 ? ((H / 8 + 31) / 32 * 32) : 1024;
-  ds_ar2_add_rmsnorm_kernel<<<grid, threads, 0, (cudaStream_t)stream>>>(ds_ptrs(partials, world), ds_ptrs(flags, world), ds_ptrs(outs, world),
+  PEAR_CUDA_CHECK(launch_ordinary(ds_ar2_add_rmsnorm_kernel, dim3(grid), dim3(threads), 0, (cudaStream_t)stream, ds_ptrs(partials, world), ds_ptrs(flags, world), ds_ptrs(outs, world),
                                                                     ds_ptrs(residuals, world), rank, world, slot, ctr, ticket, mode, bcast_residual, weight,
-                                                                    T, H, buf_elems, fixed_buf, eps, budget, status);
+                                                                    T, H, buf_elems, fixed_buf, eps, budget, status));
   PEAR_LAUNCH_CHECK();
   return 0;
 }

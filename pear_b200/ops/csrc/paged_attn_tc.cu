@@ -97,10 +97,16 @@ paged_attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
                      const PaItem* __restrict__ items, float* __restrict__ part_o, float* __restrict__ part_ml, int rows_total) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  grid_dependency_trigger();
   if ((uint32_t)(smem - smem_raw) > kPaAlignSlack) {
+    grid_dependency_wait();
     if (threadIdx.x == 0) set_status(status, PEAR_ERR_SMEM_ALIGN);
     return;
   }
+  // zero Q, K, V tiles (rows beyond R and pages beyond the context must hold finite values) while the kernel ahead in the
+  // stream drains; every global access follows the wait
+  for (uint32_t i = threadIdx.x; i < (12 * kPaPanel) / 16; i += kPaThreads) ((uint4*)smem)[i] = make_uint4(0u, 0u, 0u, 0u);
+  grid_dependency_wait();
   PaBars* bars = (PaBars*)(smem + kPaBarOff);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kvh = blockIdx.y;
@@ -118,9 +124,7 @@ paged_attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
   const int ntiles = max(0, (kv_end + kPaKT - 1) / kPaKT - jt0);
   const int* table = block_table + (size_t)b * max_blocks;
 
-  // zero Q, K, V tiles (rows beyond R and pages beyond the context must hold finite values), then stage the query rows
-  for (uint32_t i = threadIdx.x; i < (12 * kPaPanel) / 16; i += kPaThreads) ((uint4*)smem)[i] = make_uint4(0u, 0u, 0u, 0u);
-  __syncthreads();
+  __syncthreads();  // the tiles are zero: stage the query rows
   for (int i = threadIdx.x; i < R * 32; i += kPaThreads) {
     const int r = i >> 5, ch = i & 31;  // 32 chunks of 16 bytes per row
     const int sq = r / RS, g = (r % RS) / T, t = r % T;
@@ -377,6 +381,8 @@ __global__ void __launch_bounds__(64) paged_attn_combine_kernel(const float* __r
                                                                 int rows_total, int T, int Hq, const int* __restrict__ ctx,
                                                                 const float* __restrict__ gate_src, int gate_ld, int gated,
                                                                 __nv_bfloat16* __restrict__ out) {
+  grid_dependency_trigger();
+  grid_dependency_wait();
   const int row = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
   const size_t prow = (size_t)row * Hq + h;
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -460,14 +466,12 @@ PEAR_API int pear_paged_attn_tc_hd256(const void* q, const void* kc, const void*
     PEAR_CUDA_CHECK(cudaFuncSetAttribute(paged_attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured = true;
   }
-  paged_attn_tc_kernel<<<dim3(items ? n_items : B, Hkv), kPaThreads, smem, (cudaStream_t)stream>>>(
-      mk, mv, (const __nv_bfloat16*)q, block_table, max_blocks, ctx, T, Hq, Hkv, scale, (const float*)gate_src, gate_ld, gated, (__nv_bfloat16*)out,
-      status, (const PaItem*)items, part_o, part_ml, B * T);
-  PEAR_LAUNCH_CHECK();
+  PEAR_CUDA_CHECK(launch_dependent(paged_attn_tc_kernel, dim3(items ? n_items : B, Hkv), dim3(kPaThreads), smem, (cudaStream_t)stream, mk, mv,
+                                   (const __nv_bfloat16*)q, block_table, max_blocks, ctx, T, Hq, Hkv, scale, (const float*)gate_src, gate_ld, gated,
+                                   (__nv_bfloat16*)out, status, (const PaItem*)items, part_o, part_ml, B * T));
   if (items) {
-    paged_attn_combine_kernel<<<dim3(B * T, Hq), 64, 0, (cudaStream_t)stream>>>(part_o, part_ml, nparts, B * T, T, Hq, ctx, (const float*)gate_src,
-                                                                               gate_ld, gated, (__nv_bfloat16*)out);
-    PEAR_LAUNCH_CHECK();
+    PEAR_CUDA_CHECK(launch_ordinary(paged_attn_combine_kernel, dim3(B * T, Hq), dim3(64), 0, (cudaStream_t)stream, part_o, part_ml, nparts, B * T, T, Hq,
+                                     ctx, (const float*)gate_src, gate_ld, gated, (__nv_bfloat16*)out));
   }
   return 0;
 }

@@ -19,20 +19,28 @@ namespace pear {
 constexpr int kSgBM = 128, kSgBK = 64;
 constexpr int kSgThreads = 192;
 
-template <int BT>
+// Ring depth: as many [weights | tokens] stages as 224 KB hold. The weight bytes a CTA keeps in flight set its share of the
+// HBM bandwidth (the loaded latency is microseconds). A separate, shallow ring for the token panels (they come from L2) was
+// measured and is slower: 46 us against 36 us on 16480 x 5120 at 128 tokens, because the token loads queue behind the
+// weight loads in the same TMA unit and see the same latency.
+template <int BT, int EPI>
 struct SgCfg {
-  static constexpr int kStageBytes = kSgBM * kSgBK * 2 + BT * kSgBK * 2;
-  static constexpr int kStages = BT >= 256 ? 4 : (BT >= 128 ? 6 : (BT >= 64 ? 8 : 10));
+  static constexpr int kDual = EPI == 2 ? 2 : 1;
+  static constexpr int kStageBytes = kDual * kSgBM * kSgBK * 2 + BT * kSgBK * 2;
+  static constexpr int kStagesRaw = (224 * 1024) / kStageBytes;
+  static constexpr int kStages = kStagesRaw > 12 ? 12 : kStagesRaw;
+  static constexpr int kSmem = kStages * kStageBytes + 1024;
 };
 
 struct SgSmem {
-  uint64_t full[10], empty[10];
+  uint64_t full[12], empty[12];
   uint64_t tmem_full[2], tmem_empty[2];
   uint32_t tmem_base;
 };
 
 // EPI 0: fp32 planes out[split][m][n]; EPI 1: bf16 out[m][n] (one split); EPI 2: SwiGLU — the item multiplies TWO weight
 // tiles (gate rows n0.. and up rows up_row0 + n0..) into two accumulators and writes silu(gate) * up as bf16.
+// Launched as a programmatic dependent: see the producer.
 template <int BT, int EPI>
 __global__ void __launch_bounds__(kSgThreads, 1)
 stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, void* __restrict__ out,
@@ -41,7 +49,7 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   constexpr int kDual = EPI == 2 ? 2 : 1;
   constexpr uint32_t kABytes = kSgBM * kSgBK * 2, kXBytes = BT * kSgBK * 2;
   constexpr uint32_t kStageBytes = kDual * kABytes + kXBytes;
-  constexpr int kStages = EPI == 2 ? (BT >= 256 ? 3 : (BT >= 128 ? 4 : 5)) : SgCfg<BT>::kStages;
+  constexpr int kStages = SgCfg<BT, EPI>::kStages;
   constexpr int kAccBufs = (kDual * 2 * BT <= 512) ? 2 : 1;
   constexpr uint32_t kTmemCols = kDual * kAccBufs * BT < 32 ? 32 : kDual * kAccBufs * BT;
   uint8_t* tiles = smem;
@@ -73,22 +81,40 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   tcgen05_fence_after();
   const uint32_t tmem_base = sm->tmem_base;
 
+  grid_dependency_trigger();  // the next kernel's blocks may take the SMs this grid's blocks leave
   if (warp == 0) {
     if (lane == 0) {
       prefetch_tensormap(&map_w);
       prefetch_tensormap(&map_x);
-      int st = 0, ph = 0;
+      // The weight halves of the first ring round go out BEFORE the wait for the kernels ahead in the stream (weights are
+      // constants of the step): they stream in while the previous kernel drains. The token halves, which that kernel may
+      // still be writing, follow the wait.
+      int pre = 0;
+      for (int it = blockIdx.x; it < nitems && pre < kStages; it += gridDim.x) {
+        int n0, m0, s, kb0, kb1;
+        item(it, n0, m0, s, kb0, kb1);
+        for (int kb = kb0; kb < kb1 && pre < kStages; ++kb, ++pre) {
+          uint8_t* a = tiles + pre * kStageBytes;
+          mbar_expect_tx(&sm->full[pre], kStageBytes);
+          tma_load_2d(a, &map_w, kb * kSgBK, n0, &sm->full[pre]);
+          if (kDual == 2) tma_load_2d(a + kABytes, &map_w, kb * kSgBK, up_row0 + n0, &sm->full[pre]);
+        }
+      }
+      grid_dependency_wait();
+      int st = 0, ph = 0, cnt = 0;
       bool ok = true;
       for (int it = blockIdx.x; it < nitems && ok; it += gridDim.x) {
         int n0, m0, s, kb0, kb1;
         item(it, n0, m0, s, kb0, kb1);
-        for (int kb = kb0; kb < kb1; ++kb) {
-          ok = mbar_wait_bounded(&sm->empty[st], ph ^ 1, status);
-          if (!ok) break;
+        for (int kb = kb0; kb < kb1; ++kb, ++cnt) {
           uint8_t* a = tiles + st * kStageBytes;
-          mbar_expect_tx(&sm->full[st], kStageBytes);
-          tma_load_2d(a, &map_w, kb * kSgBK, n0, &sm->full[st]);
-          if (kDual == 2) tma_load_2d(a + kABytes, &map_w, kb * kSgBK, up_row0 + n0, &sm->full[st]);
+          if (cnt >= pre) {
+            ok = mbar_wait_bounded(&sm->empty[st], ph ^ 1, status);
+            if (!ok) break;
+            mbar_expect_tx(&sm->full[st], kStageBytes);
+            tma_load_2d(a, &map_w, kb * kSgBK, n0, &sm->full[st]);
+            if (kDual == 2) tma_load_2d(a + kABytes, &map_w, kb * kSgBK, up_row0 + n0, &sm->full[st]);
+          }
           tma_load_2d(a + kDual * kABytes, &map_x, kb * kSgBK, m0, &sm->full[st]);
           if (++st == kStages) { st = 0; ph ^= 1; }
         }
@@ -99,6 +125,7 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       constexpr uint32_t idesc = umma_idesc_f16(kSgBM, BT, 1);
       int st = 0, ph = 0, n_it = 0;
       bool ok = true;
+      grid_dependency_wait();  // the bounded waits below count from the completion of the kernel ahead, however long it runs
       for (int it = blockIdx.x; it < nitems && ok; it += gridDim.x, ++n_it) {
         int n0, m0, s, kb0, kb1;
         item(it, n0, m0, s, kb0, kb1);
@@ -133,6 +160,7 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     const int q = warp & 3;
     int n_it = 0;
     bool ok = true;
+    grid_dependency_wait();  // `out` may still be read by a kernel ahead in the stream
     for (int it = blockIdx.x; it < nitems; it += gridDim.x, ++n_it) {
       int n0, m0, s, kb0, kb1;
       item(it, n0, m0, s, kb0, kb1);
@@ -213,9 +241,7 @@ static int sg_make_map(CUtensorMap* map, const void* base, int rows, int cols, i
 template <int BT, int EPI>
 static int sg_launch(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int M, int N, int K, int ldo, long long split_stride, int nsplit,
                      int up_row0, int* status, int num_sms, cudaStream_t stream) {
-  constexpr int kDual = EPI == 2 ? 2 : 1;
-  constexpr int kStages = EPI == 2 ? (BT >= 256 ? 3 : (BT >= 128 ? 4 : 5)) : SgCfg<BT>::kStages;
-  constexpr int smem = kStages * (kDual * kSgBM * kSgBK * 2 + BT * kSgBK * 2) + 1024;
+  constexpr int smem = SgCfg<BT, EPI>::kSmem;
   static bool configured = false;
   if (!configured) {
     PEAR_CUDA_CHECK(cudaFuncSetAttribute(stream_gemm_kernel<BT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -223,8 +249,8 @@ static int sg_launch(const CUtensorMap& mw, const CUtensorMap& mx, void* out, in
   }
   const int nitems = ((N + kSgBM - 1) / kSgBM) * nsplit * ((M + BT - 1) / BT);
   const int grid = nitems < num_sms ? nitems : num_sms;
-  stream_gemm_kernel<BT, EPI><<<grid, kSgThreads, smem, stream>>>(mw, mx, out, M, N, K, ldo, split_stride, nsplit, up_row0, status);
-  PEAR_LAUNCH_CHECK();
+  PEAR_CUDA_CHECK(launch_dependent(stream_gemm_kernel<BT, EPI>, dim3(grid), dim3(kSgThreads), smem, stream, mw, mx, out, M, N, K, ldo, split_stride, nsplit,
+                                   up_row0, status));
   return 0;
 }
 

@@ -42,21 +42,14 @@ def check_status(device=None) -> None:
 
 
 def pick_splits(m: int, n: int, k: int, sms: int = 148, max_splits: int = 8) -> int:
-    """K splits of the streaming GEMM: work items (weight tiles x token blocks x splits) run in rounds of one per SM, so the
-    split count that fills its last round best wins (40 weight tiles: 7 splits = 280 items = 0.95 of two rounds, against 0.81
-    of one round with 3); fewer splits on a tie (every split is one more fp32 plane for the consumer to add)."""
+    """K splits of the streaming GEMM. Work items (weight tiles x token blocks x splits) run one per SM at a time, so the
+    split count is the largest that still fits ONE round of the SMs: measured in a replayed graph at 128 tokens on
+    5120 x 17408, 3 splits (120 items) take 37.5 us, 4 splits (160 items: a second round for 12 of them) 52.9 us, 7 splits
+    (280 items, two nearly full rounds) 38.4 us; every split is also one more fp32 plane for the consumer to add."""
     bt = 32 if m <= 32 else 64 if m <= 64 else 128 if m <= 128 else 256
     items = ((n + 127) // 128) * ((m + bt - 1) // bt)
     kblocks = (k + 63) // 64
-    if items >= sms:
-        return 1
-    best, best_eff = 1, 0.0
-    for ns in range(1, max(1, min(max_splits, kblocks // 4)) + 1):
-        total = items * ns
-        eff = total / (((total + sms - 1) // sms) * sms)
-        if eff > best_eff + 0.02:
-            best, best_eff = ns, eff
-    return best
+    return max(1, min(max_splits, sms // max(items, 1), kblocks // 4))
 
 
 def stream_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, nsplit: int = 1, epi: int = 0, up_row0: int = 0, n: Optional[int] = None) -> torch.Tensor:
