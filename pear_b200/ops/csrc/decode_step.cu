@@ -242,223 +242,477 @@ __global__ void __launch_bounds__(256) ds_paged_attn_simt_kernel(const __nv_bflo
 // [Hv][128][128], one slot) and a two-copy record of that block: conv_rec [slot][2][3 + Tmax][C] = the three conv inputs
 // before the block followed by the block's conv inputs, ab_rec [slot][2][Tmax][2 * Hv] = its (a, b) rows. A step reads copy
 // `parity[b]`, replays the first ncommit[b] rows of the old block into the state (those were accepted), stores the state,
-// then runs this step's T rows on a private copy to produce their outputs and writes the new block into the other copy.
-// Nothing of the rejected rows ever reaches the stored state. CTA per (value head, sequence), thread = one state row.
-// T = 0 only replays (flush before a snapshot or when the sequence leaves the batch).
+// then runs this step's T rows to produce their outputs and writes the new block into the other copy. Nothing of the
+// rejected rows ever reaches the stored state. T = 0 only replays (flush before a snapshot or when the sequence leaves
+// the batch). (Upstream: rollout/blackwell/csrc/gdn_verify.cu:643 verify, :737 prep — effective vectors, 3xTF32.)
+//
+// The rows' recurrence  S <- g_t S;  u_t = beta_t (v_t - S k_t);  S <- S + u_t k_t^T;  o_t = S q_t  is independent per
+// state row i and linear in the start state S0, so with G_t = g_0 .. g_t
+//     a_t[i] = G_t (S0 k_t)[i] + sum_{tau < t}  (G_t / G_tau) u_tau[i] (k_tau . k_t),      u_t[i] = beta_t (v_t[i] - a_t[i])
+//     o_t[i] = G_t (S0 q_t)[i] + sum_{tau <= t} (G_t / G_tau) u_tau[i] (k_tau . q_t)
+//     S_nc   = G_{nc-1} S0 + sum_{tau < nc} (G_{nc-1} / G_tau) u_tau k_tau^T                (the state that is stored)
+// Two kernels. ds_gdn_prep_kernel (a CTA per key head and one per value head, per sequence) runs the conv + SiLU + L2 norm
+// front end of every row once per KEY head (three value heads share it), the gates, the k.k / k.q table, writes the new
+// record, and leaves the vectors already laid out as tensor-core operands. ds_gdn_state_kernel (CTA per value head and sequence, two per SM)
+// makes the two passes over the 64 KB state as tcgen05 products: P = S0 [k_0..k_7 | q_0..q_7] (M = 128 state rows, N = 16
+// vectors, K = 128) and the rank-nc update D = U' K^T (M = 128, N = 128, K = 8); between them each of 128 threads walks
+// its row's <= 8 steps on scalars. kind::tf32 with every fp32 operand split into a tf32 head and a remainder (x = hi + lo;
+// hi.hi + hi.lo + lo.hi products, fp32 accumulation): the state keeps fp32 accuracy (2e-7 of its scale per step against
+// float64). The state arrives as four TMA boxes [128 rows x 32 columns] with the 128-byte swizzle, which IS the K-major
+// operand layout; its remainder lives in tensor memory (the A operand of the lo.hi product); the vectors are one 32-row
+// K-major swizzled tile, U' and K^T 128 x 8 K-major tiles without swizzle. (An MN-major view of the vector tile as the
+// update's B operand gave wrong products with 32-bit elements: K^T is stored explicitly instead.)
 constexpr int kGdnD = 128;
 constexpr int kGdnRows = 8;    // most rows one CTA walks: replayed (<= Tmax) + new (<= Tmax), Tmax <= 4
-// Structure of the kernel: (1) the state head [128][128] fp32 starts moving into shared memory as four TMA boxes of
-// 128 rows x 32 columns with the 128-byte swizzle (threads walking their own rows hit different bank groups: no
-// conflicts, no padding, four copies per head instead of one per row); (2) meanwhile every input of every row (replayed
-// and new) is loaded, run through the conv + SiLU, and the L2 norms, the gates and k.q of ALL rows are reduced with two
-// block barriers in total; (3) TWO threads share a state row (each keeps 64 of its 128 columns in registers: 16 warps per
-// SM instead of 8 to cover the shared-memory latency of the k / q reads) and walk the rows without any barrier:
-//        a = S_t . k,  c = S_t . q   (one pass over the registers, one shuffle to add the pair's halves)
-//        u = (v_t - decay * a) * beta,   o_t = decay * c + u * (k . q),   S_t <- decay * S_t + u * k
-//     (algebraically the recurrence S <- S decay; u = (v - S k) beta; S <- S + u k^T; o = S q). The decay is carried as a
-//     running scalar (stored state = scale * registers), so the update is one FMA per element; the scalar is folded in
-//     before it can underflow;
-// (4) after the last replayed row the state goes back by TMA while the new rows continue on the registers;
-// (5) the gated RMSNorm of the new rows' outputs is one more reduction for all of them.
 constexpr int kGdnThreads = 256;
-__global__ void __launch_bounds__(kGdnThreads) ds_gdn_verify_kernel(const __grid_constant__ CUtensorMap map_s, const float* __restrict__ proj, int ld,
-                                                                    const float* __restrict__ conv_w, const float* __restrict__ A_log,
-                                                                    const float* __restrict__ dt_bias, const float* __restrict__ norm_w,
-                                                                    float* __restrict__ state, float* __restrict__ conv_rec,
-                                                                    float* __restrict__ ab_rec, const int* __restrict__ slots,
-                                                                    const int* __restrict__ ctx, const int* __restrict__ parity,
-                                                                    const int* __restrict__ ncommit, int T, int Tmax, int Hk, int Hv, float l2_eps,
-                                                                    float rms_eps, __nv_bfloat16* __restrict__ out, int* status) {
+// what the prep kernel leaves per (sequence, key head) and per (sequence, value head), in the state kernel's smem layout
+constexpr uint32_t kGdnXBytes = 16384;   // vectors: 4 panels of [32 rows][128 bytes]: rows 0-7 k, 8-15 q, 16-31 remainders
+constexpr uint32_t kGdnKtBytes = 8192;   // K^T head | remainder: [16 groups of 8 rows j][2 K chunks][8 rows][16 bytes] each
+constexpr uint32_t kGdnGramBytes = 512;  // kk [8][8], kq [8][8] (no decays)
+constexpr uint32_t kGdnKeyBlock = kGdnXBytes + kGdnKtBytes + kGdnGramBytes;
+constexpr uint32_t kGdnValBlock = 4096 + 64;  // v [8][128] fp32 (conv outputs), decay [8], beta [8]
+// shared memory of the state kernel
+constexpr uint32_t kGdnS = 0;                             // state: 4 boxes of [128 rows][128 bytes], swizzled; head part in place
+constexpr uint32_t kGdnKey = 65536;                       // the key block as the prep kernel wrote it
+constexpr uint32_t kGdnVal = kGdnKey + kGdnKeyBlock;      // the value block; v rows turn into the rows' outputs
+constexpr uint32_t kGdnU = kGdnVal + kGdnValBlock + 64;   // U' head | remainder, same layout as K^T (1024-byte aligned not needed)
+constexpr uint32_t kGdnRed = kGdnU + 8192;                // [8][8 warps] sum o^2
+constexpr uint32_t kGdnTab = kGdnRed + 256;               // gcum [8], urat [8], wkk [8][8], wkq [8][8]
+constexpr uint32_t kGdnBar = kGdnTab + 1024;
+constexpr uint32_t kGdnSmem = kGdnBar + 64 + 1024;        // + alignment slack
+constexpr uint32_t kGdnTmemCols = 256;                    // [0, 128): the state's remainder; [128, 256): P (32 columns), then D
+static_assert(kGdnU % 16 == 0 && kGdnVal % 16 == 0 && kGdnKeyBlock % 16 == 0 && kGdnValBlock % 16 == 0, "bulk copy alignment");
+
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// A operand in tensor memory: lanes = the 128 rows, one 32-bit column per K element
+__device__ __forceinline__ void umma_tf32_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void gdn_tmem_st_x32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+      "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+      "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void gdn_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// x = hi + lo with hi a tf32 value (10 mantissa bits, rounded to nearest) and lo the exact remainder
+__device__ __forceinline__ void tf32_split(float x, float& hi, float& lo) {
+  hi = __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xffffe000u);
+  lo = x - hi;
+}
+__device__ __forceinline__ void tf32_split4(const float4& v, float4& h, float4& l) {
+  tf32_split(v.x, h.x, l.x); tf32_split(v.y, h.y, l.y); tf32_split(v.z, h.z, l.z); tf32_split(v.w, h.w, l.w);
+}
+
+// CTAs (x, sequence b) of 128 threads. x < Hk: key head x — thread c runs channel c of q and of k through the conv, then the
+// norms, the table and the operand images. x >= Hk: value head x - Hk — thread c runs channel c of v; the gates.
+// The heavier key-head CTAs have the lower block indices and start first.
+constexpr int kGdnPrepThreads = 128;
+__global__ void __launch_bounds__(kGdnPrepThreads, 4) ds_gdn_prep_kernel(const float* __restrict__ proj, int ld, const float* __restrict__ conv_w,
+                                                                         const float* __restrict__ A_log, const float* __restrict__ dt_bias,
+                                                                         float* __restrict__ conv_rec, float* __restrict__ ab_rec,
+                                                                         const int* __restrict__ slots, const int* __restrict__ ctx,
+                                                                         const int* __restrict__ parity, const int* __restrict__ ncommit, int T, int Tmax,
+                                                                         int Hk, int Hv, float l2_eps, uint8_t* __restrict__ key_blocks,
+                                                                         uint8_t* __restrict__ val_blocks) {
+  constexpr int D = kGdnD, RM = kGdnRows;
+  __shared__ __align__(16) float qk[2][RM][D];  // normalised q, k
+  __shared__ float red[2][RM][4];
+  __shared__ float nrm[2][RM];
+  grid_dependency_trigger();
+  grid_dependency_wait();
+  const int b = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (ctx[b] < 0) return;
+  const int slot = slots[b], par = parity[b] & 1, nc = min(ncommit[b], Tmax);
+  const int C = 2 * Hk * D + Hv * D;
+  const size_t rec_rows = 3 + Tmax;
+  const float* rin = conv_rec + ((size_t)slot * 2 + par) * rec_rows * C;
+  float* rout = conv_rec + ((size_t)slot * 2 + (par ^ 1)) * rec_rows * C;
+  const int total = min(nc + T, RM);
+
+  // the raw inputs of a channel: the window and every row; stores the new block's record ([the three conv inputs before it |
+  // its own conv inputs] = inputs nc .. nc + 2 + T) as the values arrive
+  auto load_channel = [&](int ch, float (&in)[3 + RM]) {
+#pragma unroll
+    for (int j = 0; j < 3 + RM; ++j) {
+      const int r = j - 3;
+      float a = 0.f;
+      if (j < 3 + total) {
+        a = r < nc ? rin[(size_t)j * C + ch] : proj[(size_t)(b * T + (r - nc)) * ld + ch];
+        if (j >= nc) rout[(size_t)(j - nc) * C + ch] = a;
+      }
+      in[j] = a;
+    }
+  };
+  auto conv_silu = [&](int ch, const float (&in)[3 + RM], float (&y)[RM]) {
+    const float4 w = *(const float4*)(conv_w + (size_t)ch * 4);
+#pragma unroll
+    for (int r = 0; r < RM; ++r) {
+      const float c = in[r] * w.x + in[r + 1] * w.y + in[r + 2] * w.z + in[r + 3] * w.w;
+      y[r] = c / (1.f + __expf(-c));
+    }
+  };
+
+  if ((int)blockIdx.x >= Hk) {  // ---- a value head: conv outputs of v, the gates
+    const int hv = blockIdx.x - Hk;
+    const int ch = 2 * Hk * D + hv * D + tid;
+    float gate_a = 0.f, gate_b = 0.f;
+    if (tid < total) {
+      if (tid < nc) {
+        const float* abin = ab_rec + ((size_t)slot * 2 + par) * Tmax * 2 * Hv;
+        gate_a = abin[(size_t)tid * 2 * Hv + hv]; gate_b = abin[(size_t)tid * 2 * Hv + Hv + hv];
+      } else {
+        const float* x = proj + (size_t)(b * T + (tid - nc)) * ld;
+        gate_b = x[C + Hv * D + hv]; gate_a = x[C + Hv * D + Hv + hv];
+      }
+    }
+    float in[3 + RM], y[RM];
+    load_channel(ch, in);
+    conv_silu(ch, in, y);
+    float* vb = (float*)(val_blocks + ((size_t)b * Hv + hv) * kGdnValBlock);
+#pragma unroll
+    for (int r = 0; r < RM; ++r) vb[r * D + tid] = y[r];
+    if (tid < RM) {
+      float decay = 1.f, beta = 0.f;
+      if (tid < total) {
+        if (tid >= nc) {
+          float* about = ab_rec + ((size_t)slot * 2 + (par ^ 1)) * Tmax * 2 * Hv;
+          about[(size_t)(tid - nc) * 2 * Hv + hv] = gate_a; about[(size_t)(tid - nc) * 2 * Hv + Hv + hv] = gate_b;
+        }
+        const float ax = gate_a + dt_bias[hv];
+        const float sp = ax > 20.f ? ax : log1pf(__expf(ax));
+        decay = __expf(-__expf(A_log[hv]) * sp);
+        beta = 1.f / (1.f + __expf(-gate_b));
+      }
+      vb[RM * D + tid] = decay;
+      vb[RM * D + RM + tid] = beta;
+    }
+    return;
+  }
+
+  // ---- a key head
+  const int hk = blockIdx.x;
+  uint8_t* kb = key_blocks + ((size_t)b * Hk + hk) * kGdnKeyBlock;
+  {
+    const int ch_q = hk * D + tid, ch_k = Hk * D + hk * D + tid;
+    float inq[3 + RM], ink[3 + RM], yq[RM], yk[RM];
+    load_channel(ch_q, inq);
+    load_channel(ch_k, ink);
+    conv_silu(ch_q, inq, yq);
+    conv_silu(ch_k, ink, yk);
+#pragma unroll
+    for (int r = 0; r < RM; ++r) {
+      const float sq = warp_sum(yq[r] * yq[r]), sk = warp_sum(yk[r] * yk[r]);
+      if (lane == 0) { red[0][r][warp] = sq; red[1][r][warp] = sk; }
+    }
+    __syncthreads();
+    if (tid < 2 * RM) {
+      const int wh = tid >> 3, r = tid & 7;
+      const float s = red[wh][r][0] + red[wh][r][1] + red[wh][r][2] + red[wh][r][3];
+      nrm[wh][r] = wh == 0 ? rsqrtf(s + l2_eps) * rsqrtf((float)D) : rsqrtf(s + l2_eps);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < RM; ++r) {
+      qk[0][r][tid] = r < total ? yq[r] * nrm[0][r] : 0.f;
+      qk[1][r][tid] = r < total ? yk[r] * nrm[1][r] : 0.f;
+    }
+  }
+  __syncthreads();
+  // the table (no decays: those belong to the value head)
+  float* gram = (float*)(kb + kGdnXBytes + kGdnKtBytes);
+  for (int e = warp; e < 2 * RM * RM; e += kGdnPrepThreads / 32) {
+    const int tau = (e & 63) >> 3, t = e & 7;
+    const bool isq = e >= 64;
+    const bool valid = tau < total && t < total && (isq ? (tau <= t && t >= nc) : (tau < t));  // the same in the whole warp
+    float d = 0.f;
+    if (valid) {
+      const float4 a = ((const float4*)qk[1][tau])[lane];
+      const float4 c = ((const float4*)qk[isq ? 0 : 1][t])[lane];
+      d = warp_sum(a.x * c.x + a.y * c.y + a.z * c.z + a.w * c.w);
+    }
+    if (lane == 0) gram[e] = d;
+  }
+  // the vectors as the K-major operand tile (heads in rows 0-15, remainders in rows 16-31)
+  for (int task = tid; task < 16 * 32; task += kGdnPrepThreads) {
+    const int n = task >> 5, c = task & 31;  // vector n (0-7: k of row n, 8-15: q of row n - 8), 16-byte chunk c of its 32
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (n < RM) v = ((const float4*)qk[1][n])[c];
+    else if (n - RM >= nc) v = ((const float4*)qk[0][n - RM])[c];
+    float4 h, l;
+    tf32_split4(v, h, l);
+    uint8_t* dst = kb + (c >> 3) * 4096 + n * 128 + (((c & 7) ^ (n & 7)) << 4);
+    *(float4*)dst = h;
+    *(float4*)(dst + 2048) = l;  // rows 16 + n
+  }
+  // K^T of the committed rows: thread j, four rows tau at a time -> one 16-byte chunk of the head and of the remainder
+#pragma unroll
+  for (int kc = 0; kc < 2; ++kc) {
+    const int j = tid;
+    float4 v = make_float4(qk[1][4 * kc][j], qk[1][4 * kc + 1][j], qk[1][4 * kc + 2][j], qk[1][4 * kc + 3][j]);
+    if (4 * kc >= nc) v.x = 0.f;
+    if (4 * kc + 1 >= nc) v.y = 0.f;
+    if (4 * kc + 2 >= nc) v.z = 0.f;
+    if (4 * kc + 3 >= nc) v.w = 0.f;
+    float4 h, l;
+    tf32_split4(v, h, l);
+    uint8_t* kt = kb + kGdnXBytes + (j >> 3) * 256 + kc * 128 + (j & 7) * 16;
+    *(float4*)kt = h;
+    *(float4*)(kt + 4096) = l;
+  }
+}
+
+// CTA (value head hv, sequence b), 256 threads, two CTAs per SM.
+__global__ void __launch_bounds__(kGdnThreads, 2) ds_gdn_state_kernel(const __grid_constant__ CUtensorMap map_s, const float* __restrict__ proj, int ld,
+                                                                      const float* __restrict__ norm_w, const int* __restrict__ slots,
+                                                                      const int* __restrict__ ctx, const int* __restrict__ ncommit, int T, int Tmax, int Hk,
+                                                                      int Hv, float rms_eps, const uint8_t* __restrict__ key_blocks,
+                                                                      const uint8_t* __restrict__ val_blocks, __nv_bfloat16* __restrict__ out, int* status) {
   constexpr int D = kGdnD, RM = kGdnRows, NW = kGdnThreads / 32;
   extern __shared__ __align__(1024) uint8_t gdn_smem_raw[];
-  uint8_t* gdn_smem = (uint8_t*)(((uintptr_t)gdn_smem_raw + 1023) & ~(uintptr_t)1023);
-  uint8_t* Ssm = gdn_smem;                                    // 4 boxes of [128 rows][128 bytes], swizzled
-  float* qs = (float*)(gdn_smem + D * D * 4);                 // [RM][128]
-  float* ks = qs + RM * D;                                    // [RM][128]
-  float* cvs = ks + RM * D;                                   // [RM][128]: conv outputs of the v channel, later the row outputs
-  float* red = cvs + RM * D;                                  // [RM][NW][4]: sum q^2, sum k^2, sum q k | sum o^2
-  float* rowc = red + RM * NW * 4;                            // [RM][4]: decay, beta, k.q, -
-  float* rown = rowc + RM * 4;                                // [RM][2]: normalisers of q and k
-  uint64_t* bar = (uint64_t*)(rown + RM * 2);
+  uint8_t* sm = (uint8_t*)(((uintptr_t)gdn_smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* Ssm = sm + kGdnS;
+  uint8_t* Xsm = sm + kGdnKey;
+  uint8_t* Ktsm = Xsm + kGdnXBytes;
+  const float* gram = (const float*)(Ktsm + kGdnKtBytes);
+  float* cvs = (float*)(sm + kGdnVal);      // [8][128]: v, then the rows' outputs
+  const float* dec = cvs + RM * D;          // [8] decays, [8] betas
+  uint8_t* Usm = sm + kGdnU;
+  float* red = (float*)(sm + kGdnRed);
+  float* gcum = (float*)(sm + kGdnTab);     // [RM]: g_0 .. g_t
+  float* urat = gcum + RM;                  // [RM]: g_{tau+1} .. g_{nc-1}
+  float* wkk = urat + RM;                   // [RM][RM]: (G_t / G_tau) k_tau . k_t, tau < t
+  float* wkq = wkk + RM * RM;               // [RM][RM]: (G_t / G_tau) k_tau . q_t, tau <= t, t >= nc
+  uint64_t* bar = (uint64_t*)(sm + kGdnBar);  // [0]: state loaded; [1]: MMAs done (two phases); [2]: the prep kernel's blocks loaded
+  uint32_t* tmem_slot = (uint32_t*)(bar + 3);
   const int hv = blockIdx.x, b = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int row = tid >> 1, half = tid & 1;  // state row of this thread and which columns of it: chunks 4 * half .. + 3 of every box
+  const int qd = warp & 3, hh = warp >> 2;  // row 32 qd + lane (the TMEM lanes this warp may touch), columns 64 hh .. + 63
+  const int srow = qd * 32 + lane;
   if (ctx[b] < 0) {
     grid_dependency_wait();  // every block waits before it leaves: the grid must not complete ahead of the kernels before it
     return;
   }
-  const int slot = slots[b], par = parity[b] & 1, nc = min(ncommit[b], Tmax);
-  const int rep = Hv / Hk, hk = hv / rep;
-  const int C = 2 * Hk * D + Hv * D;
-  const int ch_q = hk * D + row, ch_k = Hk * D + hk * D + row, ch_v = 2 * Hk * D + hv * D + row;
-  const size_t rec_rows = 3 + Tmax;
-  const float* rin = conv_rec + ((size_t)slot * 2 + par) * rec_rows * C;
-  float* rout = conv_rec + ((size_t)slot * 2 + (par ^ 1)) * rec_rows * C;
-  const float* abin = ab_rec + ((size_t)slot * 2 + par) * Tmax * 2 * Hv;
-  float* about = ab_rec + ((size_t)slot * 2 + (par ^ 1)) * Tmax * 2 * Hv;
+  const int slot = slots[b], nc = min(ncommit[b], Tmax);
+  const int hk = hv / (Hv / Hk);
   const int total = min(nc + T, RM);
   const int srow0 = (slot * Hv + hv) * D;  // first row of this head in the [slots * Hv * 128, 128] view of the state
   if (tid == 0) {
-    mbar_init(bar, 1);
+    mbar_init(&bar[0], 1);
+    mbar_init(&bar[1], 1);
+    mbar_init(&bar[2], 1);
     mbar_fence_init();
-    mbar_expect_tx(bar, D * D * 4);
-    for (int p = 0; p < 4; ++p) tma_load_2d(Ssm + p * 16384, &map_s, p * 32, srow0, bar);
+    mbar_expect_tx(&bar[0], D * D * 4);
+    for (int p = 0; p < 4; ++p) tma_load_2d(Ssm + p * 16384, &map_s, p * 32, srow0, &bar[0]);
   }
-  // Up to here the kernel read only what no kernel of this step writes before it (the sequence's slot, context and parity,
-  // this layer's state): the state streams in while the projection GEMM ahead in the stream drains.
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kGdnTmemCols);
+    tmem_relinquish();
+  }
+  // Up to here the kernel read only what no kernel of this step writes before it (the sequence's slot and context, this
+  // layer's state): the state streams in while the kernels ahead in the stream (projection GEMM, prep) run.
   grid_dependency_trigger();
   grid_dependency_wait();
+  if (tid == 0) {
+    mbar_expect_tx(&bar[2], kGdnKeyBlock + kGdnValBlock);
+    bulk_load_1d(Xsm, key_blocks + ((size_t)b * Hk + hk) * kGdnKeyBlock, kGdnKeyBlock, &bar[2]);
+    bulk_load_1d(cvs, val_blocks + ((size_t)b * Hv + hv) * kGdnValBlock, kGdnValBlock, &bar[2]);
+  }
+  // the output gate of the new rows and the norm weight: the kernel's only other global loads, issued before any wait
+  const int row = tid >> 1, half = tid & 1;  // the output norm: a pair of threads per channel (one publishes)
+  float zz[4] = {0.f, 0.f, 0.f, 0.f};
+  {
+    const int C = 2 * Hk * D + Hv * D;
+#pragma unroll
+    for (int t = 0; t < 4; ++t)
+      if (t < T && half == 0) zz[t] = proj[(size_t)(b * T + t) * ld + C + hv * D + row];
+  }
+  const float nw = norm_w[row];
+  __syncthreads();  // the mbarriers' initialisation and the TMEM address are visible to every thread
+  const uint32_t tmem = *tmem_slot;
+  bool ok = mbar_wait_bounded(&bar[2], 0, status);
 
-  // ---- (2) inputs of all rows: conv + SiLU on channel `row` of q, k, v (both threads of a pair compute it, one publishes)
-  const float4 wq = *(const float4*)(conv_w + (size_t)ch_q * 4), wk = *(const float4*)(conv_w + (size_t)ch_k * 4),
-               wv = *(const float4*)(conv_w + (size_t)ch_v * 4);
-  float iq[3 + RM], ik[3 + RM], iv[3 + RM];  // the window followed by the rows' raw conv inputs
-#pragma unroll
-  for (int j = 0; j < 3 + RM; ++j) {
-    const int r = j - 3;  // row index, < 0: window
-    float a = 0.f, c = 0.f, e = 0.f;
-    if (j < 3 + total) {
-      if (r < nc) {
-        a = rin[(size_t)j * C + ch_q]; c = rin[(size_t)j * C + ch_k]; e = rin[(size_t)j * C + ch_v];
-      } else {
-        const float* x = proj + (size_t)(b * T + (r - nc)) * ld;
-        a = x[ch_q]; c = x[ch_k]; e = x[ch_v];
-      }
-    }
-    iq[j] = a; ik[j] = c; iv[j] = e;
+  // ---- (1) the table with the decays between the two rows folded in
+  if (ok && tid < 2 * RM * RM) {
+    const int tau = (tid & 63) >> 3, t = tid & 7;
+    float d = gram[tid];
+    for (int s = tau + 1; s <= t; ++s) d *= dec[s];
+    (tid >= 64 ? wkq : wkk)[tau * RM + t] = d;
+  } else if (ok && tid < 2 * RM * RM + RM) {
+    const int r = tid - 2 * RM * RM;
+    float g = 1.f, u = 1.f;
+    for (int s = 0; s <= r && s < total; ++s) g *= dec[s];
+    for (int s = r + 1; s < nc; ++s) u *= dec[s];
+    gcum[r] = g;
+    urat[r] = r < nc ? u : 0.f;
   }
-  const float mine = half == 0 ? 1.f : 0.f;  // a pair holds the same channel: only one of the two enters the sums
-#pragma unroll
-  for (int r = 0; r < RM; ++r) {
-    float cq = iq[r] * wq.x + iq[r + 1] * wq.y + iq[r + 2] * wq.z + iq[r + 3] * wq.w;
-    float ck = ik[r] * wk.x + ik[r + 1] * wk.y + ik[r + 2] * wk.z + ik[r + 3] * wk.w;
-    float cv = iv[r] * wv.x + iv[r + 1] * wv.y + iv[r + 2] * wv.z + iv[r + 3] * wv.w;
-    cq = cq / (1.f + __expf(-cq)); ck = ck / (1.f + __expf(-ck)); cv = cv / (1.f + __expf(-cv));
-    if (half == 0) cvs[r * D + row] = cv;
-    iq[r] = cq; ik[r] = ck;  // raw input r is not read again: row r is its last user (rows use inputs r .. r + 3)
-    const float sq = warp_sum(cq * cq * mine), sk = warp_sum(ck * ck * mine), skq = warp_sum(cq * ck * mine);
-    if (lane == 0 && r < total) { red[(r * NW + warp) * 4] = sq; red[(r * NW + warp) * 4 + 1] = sk; red[(r * NW + warp) * 4 + 2] = skq; }
-  }
-  __syncthreads();
-  if (tid < total) {  // one thread per row finishes the row's scalars
-    const int r = tid;
-    float sq = 0.f, sk = 0.f, skq = 0.f;
-    for (int w8 = 0; w8 < NW; ++w8) { sq += red[(r * NW + w8) * 4]; sk += red[(r * NW + w8) * 4 + 1]; skq += red[(r * NW + w8) * 4 + 2]; }
-    const float nq = rsqrtf(sq + l2_eps) * rsqrtf((float)D), nk = rsqrtf(sk + l2_eps);
-    float av, bv;
-    if (r < nc) { av = abin[(size_t)r * 2 * Hv + hv]; bv = abin[(size_t)r * 2 * Hv + Hv + hv]; }
-    else {
-      const float* x = proj + (size_t)(b * T + (r - nc)) * ld;
-      bv = x[C + Hv * D + hv]; av = x[C + Hv * D + Hv + hv];
-      about[(size_t)(r - nc) * 2 * Hv + hv] = av; about[(size_t)(r - nc) * 2 * Hv + Hv + hv] = bv;
-    }
-    const float ax = av + dt_bias[hv];
-    const float sp = ax > 20.f ? ax : log1pf(__expf(ax));
-    rowc[r * 4] = __expf(-__expf(A_log[hv]) * sp);
-    rowc[r * 4 + 1] = 1.f / (1.f + __expf(-bv));
-    rowc[r * 4 + 2] = skq * nq * nk;
-    rown[r * 2] = nq;
-    rown[r * 2 + 1] = nk;
-  }
-  __syncthreads();
-  if (half == 0) {
-#pragma unroll
-    for (int r = 0; r < RM; ++r)
-      if (r < total) { qs[r * D + row] = iq[r] * rown[r * 2]; ks[r * D + row] = ik[r] * rown[r * 2 + 1]; }
-  }
-  __syncthreads();
 
-  // ---- (3) half a state row in registers, rows without barriers
-  // (the barriers above also made the mbarrier's initialisation visible to every waiter)
-  bool ok = mbar_wait_bounded(bar, 0, nullptr);
-  if (!ok) set_status(status, PEAR_ERR_MBAR_TIMEOUT);
+  // ---- (2) the state: head part in place (the A operand in shared memory), remainder into tensor memory
+  if (ok) ok = mbar_wait_bounded(&bar[0], 0, status);
   ok = __syncthreads_and(ok ? 1 : 0) != 0;
-  if (!ok) return;  // the whole CTA leaves together
-  // register block (p, i), p = 0..3 boxes, i = 0..3: columns p * 32 + (4 * half + i) * 4 .. + 3; in shared memory the 16-byte
-  // chunk c = 4 * half + i of row `row` in box p sits at slot c ^ (row % 8) of the row's 128-byte line
-  float S[D / 2];
-  uint8_t* Srow = Ssm + row * 128;
-  const int sx = row & 7, c0 = 4 * half;
-#pragma unroll
-  for (int j = 0; j < 16; ++j) {
-    const float4 v = *(const float4*)(Srow + (j >> 2) * 16384 + (((c0 + (j & 3)) ^ sx) << 4));
-    S[4 * j] = v.x; S[4 * j + 1] = v.y; S[4 * j + 2] = v.z; S[4 * j + 3] = v.w;
+  if (!ok) {  // the whole CTA leaves together
+    if (warp == 1) tmem_dealloc(tmem, kGdnTmemCols);
+    return;
   }
-  float scale = 1.f;  // true state = scale * S
+  const uint32_t lane_base = tmem + ((uint32_t)(qd * 32) << 16);
+  const int sx = srow & 7;
 #pragma unroll 1
-  for (int r = 0; r < total; ++r) {
-    const float4* k4 = (const float4*)(ks + r * D) + c0;
-    const float4* q4 = (const float4*)(qs + r * D) + c0;
-    const float decay = rowc[r * 4], beta = rowc[r * 4 + 1], kq = rowc[r * 4 + 2];
-    float4 a4 = make_float4(0.f, 0.f, 0.f, 0.f), c4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int pp = 0; pp < 2; ++pp) {
+    const int p = 2 * hh + pp;
+    uint8_t* base = Ssm + p * 16384 + srow * 128;
+    uint32_t lo[32];
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      const float4 kk = k4[(j >> 2) * 8 + (j & 3)], qq = q4[(j >> 2) * 8 + (j & 3)];
-      a4.x += S[4 * j] * kk.x; a4.y += S[4 * j + 1] * kk.y; a4.z += S[4 * j + 2] * kk.z; a4.w += S[4 * j + 3] * kk.w;
-      c4.x += S[4 * j] * qq.x; c4.y += S[4 * j + 1] * qq.y; c4.z += S[4 * j + 2] * qq.z; c4.w += S[4 * j + 3] * qq.w;
+    for (int c = 0; c < 8; ++c) {
+      float4* ptr = (float4*)(base + ((c ^ sx) << 4));
+      float4 h, l;
+      tf32_split4(*ptr, h, l);
+      *ptr = h;
+      lo[4 * c] = __float_as_uint(l.x); lo[4 * c + 1] = __float_as_uint(l.y); lo[4 * c + 2] = __float_as_uint(l.z); lo[4 * c + 3] = __float_as_uint(l.w);
     }
-    float a = (a4.x + a4.y) + (a4.z + a4.w), c = (c4.x + c4.y) + (c4.z + c4.w);
-    a += __shfl_xor_sync(0xffffffffu, a, 1);
-    c += __shfl_xor_sync(0xffffffffu, c, 1);
-    a *= scale; c *= scale;
-    const float uu = (cvs[r * D + row] - decay * a) * beta;
-    __syncwarp();  // both threads of the pair have read the row's v before it is replaced by the output
-    if (half == 0) cvs[r * D + row] = decay * c + uu * kq;  // the row's output
-    scale *= decay;
-    if (scale < 1e-12f) {  // the same decision in the whole CTA (the decay is a per-head scalar)
+    gdn_tmem_st_x32(lane_base + p * 32, lo);
+  }
+  gdn_wait_st();
+  fence_proxy_async();
+  tcgen05_fence_before();
+  __syncthreads();
+  if (tid == 0) {
+    tcgen05_fence_after();
+    constexpr uint32_t idesc_p = umma_idesc_f16(128, 32, 2), idesc_l = umma_idesc_f16(128, 16, 2);
+    const uint32_t s_addr = smem_u32(Ssm), x_addr = smem_u32(Xsm);
 #pragma unroll
-      for (int j = 0; j < D / 2; ++j) S[j] *= scale;
-      scale = 1.f;
-    }
-    const float us = uu / scale;
+    for (int kk = 0; kk < 16; ++kk)  // hi . [vector heads | vector remainders]: 32 columns
+      umma_tf32(tmem + 128, umma_desc_sw128(s_addr + (kk >> 2) * 16384) + (uint64_t)((kk & 3) * 2),
+                umma_desc_sw128(x_addr + (kk >> 2) * 4096) + (uint64_t)((kk & 3) * 2), idesc_p, kk != 0 ? 1u : 0u);
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      const float4 kk = k4[(j >> 2) * 8 + (j & 3)];
-      S[4 * j] += us * kk.x; S[4 * j + 1] += us * kk.y; S[4 * j + 2] += us * kk.z; S[4 * j + 3] += us * kk.w;
-    }
-    if (r == nc - 1) {  // the state at the start of the new block: the only state write of the step
+    for (int kk = 0; kk < 16; ++kk)  // lo . vector heads, onto the first 16 columns
+      umma_tf32_ts(tmem + 128, tmem + kk * 8, umma_desc_sw128(x_addr + (kk >> 2) * 4096) + (uint64_t)((kk & 3) * 2), idesc_l, 1u);
+    tcgen05_commit(&bar[1]);
+  }
+  ok = mbar_wait_bounded(&bar[1], 0, status);
+  ok = __syncthreads_and(ok ? 1 : 0) != 0;
+  if (!ok) {
+    if (warp == 1) tmem_dealloc(tmem, kGdnTmemCols);
+    return;
+  }
+  tcgen05_fence_after();
+
+  // ---- (3) a thread per state row walks the rows on scalars
+  if (hh == 0) {
+    uint32_t pr[32];
+    tmem_ld_32x32b_x32(lane_base + 128, pr);
+    tcgen05_wait_ld();
+    float u[RM];
 #pragma unroll
-      for (int j = 0; j < 16; ++j)
-        *(float4*)(Srow + (j >> 2) * 16384 + (((c0 + (j & 3)) ^ sx) << 4)) =
-            make_float4(S[4 * j] * scale, S[4 * j + 1] * scale, S[4 * j + 2] * scale, S[4 * j + 3] * scale);
-      fence_proxy_async();
-      __syncthreads();  // nc is the same for the whole CTA: every thread passes here in the same row
-      if (tid == 0) {
-        for (int p = 0; p < 4; ++p)
-          asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(&map_s), "r"(p * 32), "r"(srow0),
-                       "r"(smem_u32(Ssm + p * 16384))
-                       : "memory");
-        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    for (int t = 0; t < RM; ++t) {
+      u[t] = 0.f;
+      if (t < total) {
+        float a = gcum[t] * (__uint_as_float(pr[t]) + __uint_as_float(pr[16 + t]));
+#pragma unroll
+        for (int tau = 0; tau < t; ++tau) a += u[tau] * wkk[tau * RM + t];
+        u[t] = dec[RM + t] * (cvs[t * D + srow] - a);
+        if (t >= nc) {
+          float o = gcum[t] * (__uint_as_float(pr[8 + t]) + __uint_as_float(pr[24 + t]));
+#pragma unroll
+          for (int tau = 0; tau <= t; ++tau) o += u[tau] * wkq[tau * RM + t];
+          cvs[t * D + srow] = o;  // the row's output
+        }
       }
     }
+    float4 h0, h1, l0, l1;
+    tf32_split4(make_float4(u[0] * urat[0], u[1] * urat[1], u[2] * urat[2], u[3] * urat[3]), h0, l0);
+    tf32_split4(make_float4(u[4] * urat[4], u[5] * urat[5], u[6] * urat[6], u[7] * urat[7]), h1, l1);
+    uint8_t* ub = Usm + (srow >> 3) * 256 + (srow & 7) * 16;
+    *(float4*)ub = h0; *(float4*)(ub + 128) = h1;
+    *(float4*)(ub + 4096) = l0; *(float4*)(ub + 4096 + 128) = l1;
+    fence_proxy_async();
   }
-  // ---- (5) gated RMSNorm of the new rows' outputs, the new block's record
+  tcgen05_fence_before();
   __syncthreads();
+  if (nc > 0) {  // the same in the whole CTA
+    if (tid == 0) {
+      tcgen05_fence_after();
+      constexpr uint32_t idesc_u = umma_idesc_f16(128, 128, 2);
+      const uint64_t ua = umma_desc_interleaved(smem_u32(Usm), 128, 256), ul = umma_desc_interleaved(smem_u32(Usm + 4096), 128, 256);
+      const uint64_t kh = umma_desc_interleaved(smem_u32(Ktsm), 128, 256), kl = umma_desc_interleaved(smem_u32(Ktsm + 4096), 128, 256);
+      umma_tf32(tmem + 128, ua, kh, idesc_u, 0u);
+      umma_tf32(tmem + 128, ul, kh, idesc_u, 1u);
+      umma_tf32(tmem + 128, ua, kl, idesc_u, 1u);
+      tcgen05_commit(&bar[1]);
+    }
+    ok = mbar_wait_bounded(&bar[1], 1, status);
+    ok = __syncthreads_and(ok ? 1 : 0) != 0;
+    if (!ok) {
+      if (warp == 1) tmem_dealloc(tmem, kGdnTmemCols);
+      return;
+    }
+    tcgen05_fence_after();
+    // the stored state: G (hi + lo) + D, written over the head part and sent back by TMA (the only state write of the step)
+    const float G = gcum[nc - 1];
+#pragma unroll 1
+    for (int pp = 0; pp < 2; ++pp) {
+      const int p = 2 * hh + pp;
+      uint8_t* base = Ssm + p * 16384 + srow * 128;
+      uint32_t dd[32], lo[32];
+      tmem_ld_32x32b_x32(lane_base + 128 + p * 32, dd);
+      tmem_ld_32x32b_x32(lane_base + p * 32, lo);
+      tcgen05_wait_ld();
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        float4* ptr = (float4*)(base + ((c ^ sx) << 4));
+        float4 v = *ptr;
+        v.x = G * (v.x + __uint_as_float(lo[4 * c])) + __uint_as_float(dd[4 * c]);
+        v.y = G * (v.y + __uint_as_float(lo[4 * c + 1])) + __uint_as_float(dd[4 * c + 1]);
+        v.z = G * (v.z + __uint_as_float(lo[4 * c + 2])) + __uint_as_float(dd[4 * c + 2]);
+        v.w = G * (v.w + __uint_as_float(lo[4 * c + 3])) + __uint_as_float(dd[4 * c + 3]);
+        *ptr = v;
+      }
+    }
+    fence_proxy_async();
+    tcgen05_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+      for (int p = 0; p < 4; ++p)
+        asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(&map_s), "r"(p * 32), "r"(srow0),
+                     "r"(smem_u32(Ssm + p * 16384))
+                     : "memory");
+      asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    }
+  }
+  if (warp == 1) {  // every tensor-memory access of the CTA lies before the last barrier passed
+    tcgen05_fence_after();
+    tmem_dealloc(tmem, kGdnTmemCols);
+  }
+
+  // ---- (4) gated RMSNorm of the new rows' outputs
+  const float mine = half == 0 ? 1.f : 0.f;  // a pair holds the same channel: only one of the two enters the sums
   for (int r = nc; r < total; ++r) {
     const float o = cvs[r * D + row] * mine;
     const float so = warp_sum(o * o);
-    if (lane == 0) red[(r * NW + warp) * 4 + 3] = so;
+    if (lane == 0) red[r * NW + warp] = so;
   }
   __syncthreads();
   if (half == 0) {
     for (int r = nc; r < total; ++r) {
       const int t = r - nc;
       float so = 0.f;
-      for (int w8 = 0; w8 < NW; ++w8) so += red[(r * NW + w8) * 4 + 3];
-      const float zz = proj[(size_t)(b * T + t) * ld + C + hv * D + row];
+      for (int w8 = 0; w8 < NW; ++w8) so += red[r * NW + w8];
+      const float z = t == 0 ? zz[0] : (t == 1 ? zz[1] : (t == 2 ? zz[2] : zz[3]));
       out[(size_t)(b * T + t) * Hv * D + hv * D + row] =
-          __float2bfloat16_rn(cvs[r * D + row] * rsqrtf(so / (float)D + rms_eps) * norm_w[row] * (zz / (1.f + __expf(-zz))));
-    }
-    // record of the new block: [the three conv inputs before it | its own conv inputs], read back from where they came
-    for (int j = 0; j < 3 + T; ++j) {
-      const int src = nc + j;  // index into [old window | old rows] followed by the new rows
-      float a, c, e;
-      if (src < 3 + nc) { a = rin[(size_t)src * C + ch_q]; c = rin[(size_t)src * C + ch_k]; e = rin[(size_t)src * C + ch_v]; }
-      else {
-        const float* x = proj + (size_t)(b * T + (src - 3 - nc)) * ld;
-        a = x[ch_q]; c = x[ch_k]; e = x[ch_v];
-      }
-      rout[(size_t)j * C + ch_v] = e;
-      if (hv % rep == 0) { rout[(size_t)j * C + ch_q] = a; rout[(size_t)j * C + ch_k] = c; }
+          __float2bfloat16_rn(cvs[r * D + row] * rsqrtf(so / (float)D + rms_eps) * nw * (z / (1.f + __expf(-z))));
     }
   }
   // the stores read shared memory asynchronously: they must have finished reading before the CTA's memory goes away
@@ -1018,12 +1272,18 @@ PEAR_API int pear_ds_paged_attn_simt(const void* q, const void* kc, const void* 
   return 0;
 }
 
+// Bytes of scratch pear_ds_gdn_verify needs for a batch of B sequences (the prep kernel's blocks).
+PEAR_API long long pear_ds_gdn_scratch_bytes(int B, int Hk, int Hv) {
+  return (long long)B * Hk * pear::kGdnKeyBlock + (long long)B * Hv * pear::kGdnValBlock;
+}
+
 PEAR_API int pear_ds_gdn_verify(const float* proj, int ld, const float* conv_w, const float* A_log, const float* dt_bias, const float* norm_w,
                                 float* state, int num_slots, float* conv_rec, float* ab_rec, const int* slots, const int* ctx, const int* parity,
-                                const int* ncommit, int B, int T, int Tmax, int Hk, int Hv, float l2_eps, float rms_eps, void* out, int* status,
-                                void* stream) {
-  if (Hv % Hk || T > Tmax || B <= 0 || 2 * Tmax > kGdnRows || num_slots <= 0 || ((uintptr_t)state % 16)) return (int)cudaErrorInvalidValue;
-  constexpr int smem = kGdnD * kGdnD * 4 + 3 * kGdnRows * kGdnD * 4 + kGdnRows * (kGdnThreads / 32) * 16 + kGdnRows * 24 + 16 + 1024;
+                                const int* ncommit, int B, int T, int Tmax, int Hk, int Hv, float l2_eps, float rms_eps, void* out, void* scratch,
+                                int* status, void* stream) {
+  if (Hv % Hk || Hv / Hk > 8 || T > Tmax || Tmax > 4 || B <= 0 || 2 * Tmax > kGdnRows || num_slots <= 0 || ((uintptr_t)state % 16) || ((uintptr_t)scratch % 16))
+    return (int)cudaErrorInvalidValue;
+  constexpr int smem = (int)kGdnSmem;
   static PFN_cuTensorMapEncodeTiled_v12000 enc = nullptr;
   if (!enc) {
     cudaDriverEntryPointQueryResult q;
@@ -1044,12 +1304,16 @@ PEAR_API int pear_ds_gdn_verify(const float* proj, int ld, const float* conv_w, 
   }
   static bool configured = false;
   if (!configured) {
-    PEAR_CUDA_CHECK(cudaFuncSetAttribute(ds_gdn_verify_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    PEAR_CUDA_CHECK(cudaFuncSetAttribute(ds_gdn_state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured = true;
   }
-  PEAR_CUDA_CHECK(launch_dependent(ds_gdn_verify_kernel, dim3(dim3(Hv, B)), dim3(kGdnThreads), smem, (cudaStream_t)stream, map_s, proj, ld, conv_w, A_log, dt_bias, norm_w, state, conv_rec, ab_rec, slots, ctx,
-                                                                         parity, ncommit, T, Tmax, Hk, Hv, l2_eps, rms_eps, (__nv_bfloat16*)out, status));
-  PEAR_LAUNCH_CHECK();
+  uint8_t* key_blocks = (uint8_t*)scratch;
+  uint8_t* val_blocks = key_blocks + (size_t)B * Hk * kGdnKeyBlock;
+  cudaStream_t s = (cudaStream_t)stream;
+  PEAR_CUDA_CHECK(launch_ordinary(ds_gdn_prep_kernel, dim3(Hk + Hv, B), dim3(kGdnPrepThreads), 0, s, proj, ld, conv_w, A_log, dt_bias, conv_rec, ab_rec, slots, ctx,
+                                  parity, ncommit, T, Tmax, Hk, Hv, l2_eps, key_blocks, val_blocks));
+  PEAR_CUDA_CHECK(launch_dependent(ds_gdn_state_kernel, dim3(Hv, B), dim3(kGdnThreads), smem, s, map_s, proj, ld, norm_w, slots, ctx, ncommit, T, Tmax, Hk,
+                                   Hv, rms_eps, (const uint8_t*)key_blocks, (const uint8_t*)val_blocks, (__nv_bfloat16*)out, status));
   return 0;
 }
 

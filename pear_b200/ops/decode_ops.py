@@ -141,13 +141,31 @@ def paged_attention(q, kc, vc, block_table, ctx, batch: int, t: int, hq: int, hk
     _lib.count_launch()
 
 
+_gdn_scratch: dict = {}
+
+
+def gdn_scratch(device, batch: int, hk: int, hv: int) -> torch.Tensor:
+    """Scratch of the GDN verify pair of kernels (what the front-end kernel hands to the state kernel), one per device,
+    grown on demand (never while a graph is being captured: size it with the largest batch first)."""
+    fn = _lib.lib().pear_ds_gdn_scratch_bytes
+    fn.restype = ctypes.c_longlong
+    need = int(fn(batch, hk, hv))
+    buf = _gdn_scratch.get(device)
+    if buf is None or buf.numel() < need:
+        assert not torch.cuda.is_current_stream_capturing(), "the GDN scratch cannot grow inside a graph capture"
+        buf = torch.empty(need, dtype=torch.uint8, device=device)
+        _gdn_scratch[device] = buf
+    return buf
+
+
 def gdn_verify(proj, conv_w, a_log, dt_bias, norm_w, state, conv_rec, ab_rec, slots, ctx, parity, ncommit, batch: int, t: int, tmax: int, hk: int,
                hv: int, l2_eps: float, rms_eps: float, out) -> None:
+    scratch = gdn_scratch(state.device, batch, hk, hv)
     _lib.check(_lib.lib().pear_ds_gdn_verify(_lib.ptr(proj), proj.stride(0) if proj is not None else 0, _lib.ptr(conv_w), _lib.ptr(a_log),
                                              _lib.ptr(dt_bias), _lib.ptr(norm_w), _lib.ptr(state), state.shape[0], _lib.ptr(conv_rec), _lib.ptr(ab_rec), _lib.ptr(slots),
                                              _lib.ptr(ctx), _lib.ptr(parity), _lib.ptr(ncommit), batch, t, tmax, hk, hv, _f(l2_eps), _f(rms_eps),
-                                             _lib.ptr(out), _lib.ptr(status_word(state.device)), _lib.stream()), "ds_gdn_verify")
-    _lib.count_launch()
+                                             _lib.ptr(out), _lib.ptr(scratch), _lib.ptr(status_word(state.device)), _lib.stream()), "ds_gdn_verify")
+    _lib.count_launch(2)
 
 
 def rec_bytes() -> int:
