@@ -24,8 +24,23 @@ FLAGS = [
 ]
 
 
+STAMP = HERE / "_pear_kernels.src"  # digest of the sources the library was built from (checked by the loader)
+
+
+def source_digest() -> str:
+    """One digest over every source and header: the loader refuses a library built from other sources (a C entry point
+    whose argument list changed would otherwise be called with shifted arguments)."""
+    import hashlib
+
+    h = hashlib.sha256()
+    for p in sorted([*CSRC.glob("*.cu"), *CSRC.glob("*.cuh"), *CSRC.glob("*.h")]):
+        h.update(p.name.encode())
+        h.update(p.read_bytes())
+    return h.hexdigest()
+
+
 def _newest_header() -> float:
-    return max((p.stat().st_mtime for p in CSRC.glob("*.cuh")), default=0.0)
+    return max((p.stat().st_mtime for p in [*CSRC.glob("*.cuh"), *CSRC.glob("*.h")]), default=0.0)
 
 
 def build(verbose: bool = False, ptxas_info: bool = False) -> Path:
@@ -61,6 +76,7 @@ def build(verbose: bool = False, ptxas_info: bool = False) -> Path:
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}{r.stderr}")
+    STAMP.write_text(source_digest())
     return LIB
 
 

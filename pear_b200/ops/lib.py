@@ -32,6 +32,11 @@ def lib() -> ctypes.CDLL:
             else:
                 raise KernelLibraryMissing(
                     f"{LIB_PATH} is missing: run `python -m pear_b200.ops.build` (nvcc cross-compiles without a GPU)")
+        from .build import STAMP, source_digest
+
+        if not STAMP.exists() or STAMP.read_text().strip() != source_digest():
+            raise KernelLibraryMissing(
+                f"{LIB_PATH} was built from other sources than those in csrc/: run `python -m pear_b200.ops.build`")
         _LIB = ctypes.CDLL(str(LIB_PATH))
     return _LIB
 
