@@ -8,8 +8,9 @@
 // (Upstream: rollout/blackwell/csrc/stream_gemm.cu:105-316 — weights as A, tokens as N, split-K partials.)
 // Warp roles as in the training GEMM: warp 0 TMA producer, warp 1 MMA issuer, warps 2-5 epilogue over the four TMEM
 // lane quarters; two accumulators so that the epilogue of one item overlaps the main loop of the next.
-// The epilogue writes Y un-transposed: a thread holds one output feature and 32 tokens, so for each token the 32 lanes
-// of a warp store 32 consecutive features (coalesced). No cluster multicast; every wait is bounded.
+// The epilogue writes Y un-transposed: a thread holds one output feature and 32 tokens; a warp stages its 32 features x 32
+// tokens in shared memory and sends the box with one TMA store (scalar global stores, 128 per thread, took 4.7 us per
+// 128 x 128 tile, the largest fixed cost of a 20-40 us launch). No cluster multicast; every wait is bounded.
 #include "common.cuh"
 
 #include <cudaTypedefs.h>
@@ -27,9 +28,12 @@ template <int BT, int EPI>
 struct SgCfg {
   static constexpr int kDual = EPI == 2 ? 2 : 1;
   static constexpr int kStageBytes = kDual * kSgBM * kSgBK * 2 + BT * kSgBK * 2;
-  static constexpr int kStagesRaw = (224 * 1024) / kStageBytes;
+  // the epilogue's staging: per epilogue warp two boxes of 32 tokens x 32 features (fp32 or bf16) that TMA stores read
+  static constexpr int kBoxBytes = 32 * 32 * (EPI == 0 ? 4 : 2);
+  static constexpr int kStagingBytes = 4 * 2 * kBoxBytes;
+  static constexpr int kStagesRaw = (224 * 1024 - kStagingBytes) / kStageBytes;
   static constexpr int kStages = kStagesRaw > 12 ? 12 : kStagesRaw;
-  static constexpr int kSmem = kStages * kStageBytes + 1024;
+  static constexpr int kSmem = kStages * kStageBytes + kStagingBytes + 1024;
 };
 
 struct SgSmem {
@@ -43,8 +47,8 @@ struct SgSmem {
 // Launched as a programmatic dependent: see the producer.
 template <int BT, int EPI>
 __global__ void __launch_bounds__(kSgThreads, 1)
-stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, void* __restrict__ out,
-                   int M, int N, int K, int ldo, long long split_stride, int nsplit, int up_row0, int* status) {
+stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_o,
+                   int M, int N, int K, int nsplit, int up_row0, int* status) {
   extern __shared__ __align__(1024) uint8_t smem[];
   constexpr int kDual = EPI == 2 ? 2 : 1;
   constexpr uint32_t kABytes = kSgBM * kSgBK * 2, kXBytes = BT * kSgBK * 2;
@@ -53,7 +57,8 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   constexpr int kAccBufs = (kDual * 2 * BT <= 512) ? 2 : 1;
   constexpr uint32_t kTmemCols = kDual * kAccBufs * BT < 32 ? 32 : kDual * kAccBufs * BT;
   uint8_t* tiles = smem;
-  SgSmem* sm = (SgSmem*)(smem + kStages * kStageBytes);
+  uint8_t* staging = smem + kStages * kStageBytes;
+  SgSmem* sm = (SgSmem*)(staging + SgCfg<BT, EPI>::kStagingBytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_n = (N + kSgBM - 1) / kSgBM, tblocks = (M + BT - 1) / BT;
   const int nitems = tiles_n * nsplit * tblocks;
@@ -158,8 +163,11 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     }
   } else {
     const int q = warp & 3;
-    int n_it = 0;
+    int n_it = 0, box = 0;
     bool ok = true;
+    constexpr int kBoxBytes = SgCfg<BT, EPI>::kBoxBytes;
+    uint8_t* my_boxes = staging + (warp - 2) * 2 * kBoxBytes;
+    prefetch_tensormap(&map_o);
     grid_dependency_wait();  // `out` may still be read by a kernel ahead in the stream
     for (int it = blockIdx.x; it < nitems; it += gridDim.x, ++n_it) {
       int n0, m0, s, kb0, kb1;
@@ -170,7 +178,6 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       ok = __all_sync(0xffffffffu, ok);  // the warp leaves together: the arrive below is per warp
       if (!ok) break;
       tcgen05_fence_after();
-      const int n = n0 + q * 32 + lane;
       const uint32_t acc = tmem_base + ((uint32_t)(q * 32) << 16) + ab * kDual * BT;
 #pragma unroll 1
       for (int c0 = 0; c0 < BT; c0 += 32) {
@@ -188,24 +195,33 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         } else {
           tcgen05_wait_ld();
         }
-        if (n < N && kb1 > kb0) {
+        if (n0 + q * 32 < N && m0 + c0 < M && kb1 > kb0) {  // the same in the whole warp; the store clips the box at N and M
+          uint8_t* dst = my_boxes + (box & 1) * kBoxBytes;
+          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");  // the store before the last one has read its box
+          __syncwarp();
           if (EPI == 0) {
-            float* dst = (float*)out + (size_t)s * split_stride + (size_t)(m0 + c0) * ldo + n;
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (m0 + c0 + j < M) dst[(size_t)j * ldo] = __uint_as_float(r[j]);
+            for (int j = 0; j < 32; ++j) *(uint32_t*)(dst + j * 128 + lane * 4) = r[j];
           } else {
-            __nv_bfloat16* dst = (__nv_bfloat16*)out + (size_t)(m0 + c0) * ldo + n;
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (m0 + c0 + j < M) dst[(size_t)j * ldo] = __float2bfloat16_rn(__uint_as_float(r[j]));
+            for (int j = 0; j < 32; ++j) *(__nv_bfloat16*)(dst + j * 64 + lane * 2) = __float2bfloat16_rn(__uint_as_float(r[j]));
           }
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) {
+            asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3}], [%4];" ::"l"(&map_o), "r"(n0 + q * 32),
+                         "r"(m0 + c0), "r"(s), "r"(smem_u32(dst))
+                         : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
+          ++box;
         }
       }
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&sm->tmem_empty[ab]);
     }
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // every store of this warp has been performed
   }
   tcgen05_fence_before();
   __syncthreads();
@@ -238,8 +254,22 @@ static int sg_make_map(CUtensorMap* map, const void* base, int rows, int cols, i
   return r == CUDA_SUCCESS ? 0 : 1000 + (int)r;
 }
 
+// The output as [nsplit planes][M rows][N features] (fp32 planes or one bf16 matrix): boxes of 32 features x 32 rows.
+static int sg_make_out_map(CUtensorMap* map, void* base, int M, int N, int ldo, long long split_stride, int nsplit, bool fp32) {
+  auto enc = sg_get_encode();
+  if (!enc) return (int)cudaErrorNotSupported;
+  const cuuint64_t es = fp32 ? 4 : 2;
+  cuuint64_t dims[3] = {(cuuint64_t)N, (cuuint64_t)M, (cuuint64_t)nsplit};
+  cuuint64_t strides[2] = {(cuuint64_t)ldo * es, (cuuint64_t)(nsplit > 1 ? split_stride : (long long)M * ldo) * es};
+  cuuint32_t box[3] = {32u, 32u, 1u};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(map, fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, base, dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : 1000 + (int)r;
+}
+
 template <int BT, int EPI>
-static int sg_launch(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int M, int N, int K, int ldo, long long split_stride, int nsplit,
+static int sg_launch(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mo, int M, int N, int K, int nsplit,
                      int up_row0, int* status, int num_sms, cudaStream_t stream) {
   constexpr int smem = SgCfg<BT, EPI>::kSmem;
   static bool configured = false;
@@ -249,25 +279,26 @@ static int sg_launch(const CUtensorMap& mw, const CUtensorMap& mx, void* out, in
   }
   const int nitems = ((N + kSgBM - 1) / kSgBM) * nsplit * ((M + BT - 1) / BT);
   const int grid = nitems < num_sms ? nitems : num_sms;
-  PEAR_CUDA_CHECK(launch_dependent(stream_gemm_kernel<BT, EPI>, dim3(grid), dim3(kSgThreads), smem, stream, mw, mx, out, M, N, K, ldo, split_stride, nsplit,
-                                   up_row0, status));
+  PEAR_CUDA_CHECK(launch_dependent(stream_gemm_kernel<BT, EPI>, dim3(grid), dim3(kSgThreads), smem, stream, mw, mx, mo, M, N, K, nsplit, up_row0,
+                                   status));
   return 0;
 }
 
 template <int EPI>
-static int sg_dispatch(int bt, const CUtensorMap& mw, const CUtensorMap& mx, void* out, int M, int N, int K, int ldo, long long split_stride,
-                       int nsplit, int up_row0, int* status, int num_sms, cudaStream_t s) {
+static int sg_dispatch(int bt, const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mo, int M, int N, int K, int nsplit, int up_row0,
+                       int* status, int num_sms, cudaStream_t s) {
   switch (bt) {
-    case 32: return sg_launch<32, EPI>(mw, mx, out, M, N, K, ldo, split_stride, nsplit, up_row0, status, num_sms, s);
-    case 64: return sg_launch<64, EPI>(mw, mx, out, M, N, K, ldo, split_stride, nsplit, up_row0, status, num_sms, s);
-    case 128: return sg_launch<128, EPI>(mw, mx, out, M, N, K, ldo, split_stride, nsplit, up_row0, status, num_sms, s);
-    default: return sg_launch<256, EPI>(mw, mx, out, M, N, K, ldo, split_stride, nsplit, up_row0, status, num_sms, s);
+    case 32: return sg_launch<32, EPI>(mw, mx, mo, M, N, K, nsplit, up_row0, status, num_sms, s);
+    case 64: return sg_launch<64, EPI>(mw, mx, mo, M, N, K, nsplit, up_row0, status, num_sms, s);
+    case 128: return sg_launch<128, EPI>(mw, mx, mo, M, N, K, nsplit, up_row0, status, num_sms, s);
+    default: return sg_launch<256, EPI>(mw, mx, mo, M, N, K, nsplit, up_row0, status, num_sms, s);
   }
 }
 
 }  // namespace pear
 
-// Y = X W^T for a step of M token rows. x [M, K] bf16 (ldx), w [N, K] bf16 (ldw); both 16-byte aligned, ldx / ldw multiples of 8.
+// Y = X W^T for a step of M token rows. x [M, K] bf16 (ldx), w [N, K] bf16 (ldw); both 16-byte aligned, ldx / ldw multiples of 8;
+// out 16-byte aligned, ldo a multiple of 4 (fp32) or 8 (bf16).
 //   epi 0: out fp32, `nsplit` planes of [M, ldo] that are `split_stride` elements apart (the consumer adds the planes);
 //   epi 1: out bf16 [M, ldo] (nsplit must be 1);
 //   epi 2: w holds [gate rows | up rows] with the up rows starting at row `up_row0`; N = number of gate rows; out bf16
@@ -278,6 +309,8 @@ PEAR_API int pear_stream_gemm_bf16(const void* x, const void* w, void* out, int 
   using namespace pear;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((ldx % 8) || (ldw % 8) || ((uintptr_t)x % 16) || ((uintptr_t)w % 16) || nsplit < 1 || epi < 0 || epi > 2) return (int)cudaErrorInvalidValue;
+  // the output goes out by TMA stores: 16-byte aligned base, row and plane strides multiples of 16 bytes
+  if (((uintptr_t)out % 16) || (ldo % (epi == 0 ? 4 : 8)) || (nsplit > 1 && (split_stride % 4))) return (int)cudaErrorInvalidValue;
   if (epi != 0 && nsplit != 1) return (int)cudaErrorInvalidValue;
   if (nsplit > (K + kSgBK - 1) / kSgBK) return (int)cudaErrorInvalidValue;
   // token block: the whole step when it is small; for larger steps the block size that fills the SMs best (work items =
@@ -299,8 +332,11 @@ PEAR_API int pear_stream_gemm_bf16(const void* x, const void* w, void* out, int 
   if (r) return r;
   r = sg_make_map(&mx, x, M, K, ldx, bt);
   if (r) return r;
+  CUtensorMap mo;
+  r = sg_make_out_map(&mo, out, M, N, ldo, split_stride, nsplit, epi == 0);
+  if (r) return r;
   cudaStream_t s = (cudaStream_t)stream;
-  if (epi == 0) return sg_dispatch<0>(bt, mw, mx, out, M, N, K, ldo, split_stride, nsplit, up_row0, status, num_sms, s);
-  if (epi == 1) return sg_dispatch<1>(bt, mw, mx, out, M, N, K, ldo, split_stride, nsplit, up_row0, status, num_sms, s);
-  return sg_dispatch<2>(bt, mw, mx, out, M, N, K, ldo, split_stride, nsplit, up_row0, status, num_sms, s);
+  if (epi == 0) return sg_dispatch<0>(bt, mw, mx, mo, M, N, K, nsplit, up_row0, status, num_sms, s);
+  if (epi == 1) return sg_dispatch<1>(bt, mw, mx, mo, M, N, K, nsplit, up_row0, status, num_sms, s);
+  return sg_dispatch<2>(bt, mw, mx, mo, M, N, K, nsplit, up_row0, status, num_sms, s);
 }
