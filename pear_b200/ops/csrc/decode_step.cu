@@ -75,15 +75,48 @@ __global__ void __launch_bounds__(256) ds_add_rmsnorm_kernel(const float* __rest
   __shared__ float red[8];
   const int row = blockIdx.x, tid = threadIdx.x;
   float* res = residual + (size_t)row * H;
+  // a row of up to 8192 elements stays in registers between the two passes (8 x 4 per thread); every load of the kernel
+  // (residual, planes, norm weight) is issued before the first use
+  constexpr int kMaxIt = 8;
+  float4 v[kMaxIt], g[kMaxIt];
+  const bool in_regs = H <= kMaxIt * 1024;
   float ssq = 0.f;
-  for (int i = tid * 4; i < H; i += 1024) {
-    float4 v = mode == 0 ? *(const float4*)(res + i) : make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int s = 0; s < nsplit; ++s) {
-      const float4 p = *(const float4*)(parts + (size_t)s * split_stride + (size_t)row * ldp + i);
-      v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
+  if (in_regs) {
+#pragma unroll
+    for (int k = 0; k < kMaxIt; ++k) {
+      const int i = tid * 4 + k * 1024;
+      v[k] = (i < H && mode == 0) ? *(const float4*)(res + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+      g[k] = i < H ? *(const float4*)(w + i) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    if (nsplit > 0 || mode == 1) *(float4*)(res + i) = v;
-    ssq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    for (int s = 0; s < nsplit; ++s) {
+      const float* ps = parts + (size_t)s * split_stride + (size_t)row * ldp;
+#pragma unroll
+      for (int k = 0; k < kMaxIt; ++k) {
+        const int i = tid * 4 + k * 1024;
+        if (i < H) {
+          const float4 p = *(const float4*)(ps + i);
+          v[k].x += p.x; v[k].y += p.y; v[k].z += p.z; v[k].w += p.w;
+        }
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < kMaxIt; ++k) {
+      const int i = tid * 4 + k * 1024;
+      if (i < H) {
+        if (nsplit > 0 || mode == 1) *(float4*)(res + i) = v[k];
+        ssq += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+      }
+    }
+  } else {
+    for (int i = tid * 4; i < H; i += 1024) {
+      float4 t = mode == 0 ? *(const float4*)(res + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int s = 0; s < nsplit; ++s) {
+        const float4 p = *(const float4*)(parts + (size_t)s * split_stride + (size_t)row * ldp + i);
+        t.x += p.x; t.y += p.y; t.z += p.z; t.w += p.w;
+      }
+      if (nsplit > 0 || mode == 1) *(float4*)(res + i) = t;
+      ssq += t.x * t.x + t.y * t.y + t.z * t.z + t.w * t.w;
+    }
   }
   ssq = warp_sum(ssq);
   if ((tid & 31) == 0) red[tid >> 5] = ssq;
@@ -91,15 +124,22 @@ __global__ void __launch_bounds__(256) ds_add_rmsnorm_kernel(const float* __rest
   float tot = 0.f;
   for (int k = 0; k < 8; ++k) tot += red[k];
   const float rstd = rsqrtf(tot / (float)H + eps);
-  for (int i = tid * 4; i < H; i += 1024) {
-    const float4 v = *(const float4*)(res + i);
-    const float4 g = *(const float4*)(w + i);
-    const float a = one_plus ? 1.f : 0.f;
-    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x * rstd * (a + g.x), v.y * rstd * (a + g.y));
-    __nv_bfloat162 hi = __floats2bfloat162_rn(v.z * rstd * (a + g.z), v.w * rstd * (a + g.w));
+  const float a = one_plus ? 1.f : 0.f;
+  auto emit = [&](int i, const float4& x, const float4& gg) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(x.x * rstd * (a + gg.x), x.y * rstd * (a + gg.y));
+    __nv_bfloat162 hi = __floats2bfloat162_rn(x.z * rstd * (a + gg.z), x.w * rstd * (a + gg.w));
     uint2 pk;
     pk.x = *(uint32_t*)&lo; pk.y = *(uint32_t*)&hi;
     *(uint2*)(out + (size_t)row * H + i) = pk;
+  };
+  if (in_regs) {
+#pragma unroll
+    for (int k = 0; k < kMaxIt; ++k) {
+      const int i = tid * 4 + k * 1024;
+      if (i < H) emit(i, v[k], g[k]);
+    }
+  } else {
+    for (int i = tid * 4; i < H; i += 1024) emit(i, *(const float4*)(res + i), *(const float4*)(w + i));
   }
 }
 
