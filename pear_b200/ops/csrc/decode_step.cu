@@ -392,12 +392,16 @@ __global__ void __launch_bounds__(kGdnPrepThreads, 4) ds_gdn_prep_kernel(const f
     for (int j = 0; j < 3 + RM; ++j) {
       const int r = j - 3;
       float a = 0.f;
-      if (j < 3 + total) {
-        a = r < nc ? rin[(size_t)j * C + ch] : proj[(size_t)(b * T + (r - nc)) * ld + ch];
-        if (j >= nc) rout[(size_t)(j - nc) * C + ch] = a;
-      }
+      if (j < 3 + total) a = r < nc ? rin[(size_t)j * C + ch] : proj[(size_t)(b * T + (r - nc)) * ld + ch];
       in[j] = a;
     }
+  };
+  // (a loop of its own: a store between two loads would order them, the record being one array, and the 11 loads of a
+  // channel would become 11 round trips to memory)
+  auto store_record = [&](int ch, const float (&in)[3 + RM]) {
+#pragma unroll
+    for (int j = 0; j < 3 + RM; ++j)
+      if (j < 3 + total && j >= nc) rout[(size_t)(j - nc) * C + ch] = in[j];
   };
   auto conv_silu = [&](int ch, const float (&in)[3 + RM], float (&y)[RM]) {
     const float4 w = *(const float4*)(conv_w + (size_t)ch * 4);
@@ -423,6 +427,7 @@ __global__ void __launch_bounds__(kGdnPrepThreads, 4) ds_gdn_prep_kernel(const f
     }
     float in[3 + RM], y[RM];
     load_channel(ch, in);
+    store_record(ch, in);
     conv_silu(ch, in, y);
     float* vb = (float*)(val_blocks + ((size_t)b * Hv + hv) * kGdnValBlock);
 #pragma unroll
@@ -453,6 +458,8 @@ __global__ void __launch_bounds__(kGdnPrepThreads, 4) ds_gdn_prep_kernel(const f
     float inq[3 + RM], ink[3 + RM], yq[RM], yk[RM];
     load_channel(ch_q, inq);
     load_channel(ch_k, ink);
+    store_record(ch_q, inq);
+    store_record(ch_k, ink);
     conv_silu(ch_q, inq, yq);
     conv_silu(ch_k, ink, yk);
 #pragma unroll
