@@ -29,6 +29,7 @@ from typing import Optional
 
 import torch
 
+from ..utils import nvtx
 from ..models.hybrid import HybridForCausalLM
 from . import sampler as S
 from .block_manager import NULL_BLOCK, BlockManager
@@ -295,6 +296,10 @@ class RolloutEngine:
     # -- one step -----------------------------------------------------------------------------------------------------
     def step(self) -> list[Request]:
         """Schedule and run one step; returns the requests that finished in it."""
+        with nvtx.annotate("rollout/engine_step"):
+            return self._step()
+
+    def _step(self) -> list[Request]:
         if self.paused:
             return []
         cfg = self.cfg

@@ -29,6 +29,7 @@ from ..models.hybrid import HybridForCausalLM
 from ..ops import decode_ops as K
 from ..ops import lib as _lib
 from ..ops import rollout_ops
+from ..utils import nvtx
 
 SLOT_STEP_AR, SLOT_STEP_SYNC = 8, 10  # flag slots of the SymmWorld signal region used by the step (the two-shot reduction also uses 9)
 
@@ -483,6 +484,10 @@ class FastDecoder:
 
     def step(self) -> None:
         """Launch one step on the current stream (graph replay after two eager warm-up steps)."""
+        with nvtx.annotate("rollout/decode_step"):
+            self._step()
+
+    def _step(self) -> None:
         if not self.use_graph:
             self._launch_step()
         elif self.graph is not None:

@@ -26,6 +26,7 @@ from typing import Callable, Optional
 import numpy as np
 import torch
 
+from ..utils import nvtx
 from . import grpo
 from .engine import PackedBatch, TrainEngine
 from .replay_buffer import GroupStatus, PromptGroup, ReplayBuffer
@@ -239,8 +240,10 @@ class Trainer:
         mbs = parts[self.engine.dp_rank]
         total = stats.pop("_total_loss_tokens")
         t1 = time.time()
-        metrics = self.engine.forward_backward_batch(mbs, total_loss_tokens=total) if mbs else {}
-        metrics.update(self.engine.optimizer_step())
+        with nvtx.annotate("trainer/forward_backward"):
+            metrics = self.engine.forward_backward_batch(mbs, total_loss_tokens=total) if mbs else {}
+        with nvtx.annotate("trainer/optimizer_step"):
+            metrics.update(self.engine.optimizer_step())
         t_train = time.time() - t1
         stale = [self.engine.policy_version - 1 - g.issued_version for g in groups]
         if self.is_driver:
@@ -249,7 +252,8 @@ class Trainer:
         if self.step % self.cfg.parameter_sync_step == 0 and (self.weight_sync is not None or self.engine.world > 1):
             state = self.engine.full_state_dict(torch.float32)  # collective: every trainer rank takes part
             if self.weight_sync is not None:
-                metrics.update(self.weight_sync.sync(state, self.engine.policy_version))
+                with nvtx.annotate("trainer/weight_sync"):
+                    metrics.update(self.weight_sync.sync(state, self.engine.policy_version))
             del state
         metrics.update(stats)
         metrics.update(self.replay.metrics)

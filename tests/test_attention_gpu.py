@@ -55,6 +55,15 @@ def test_operands_sliced_from_a_fused_projection():
     _case([257, 640], [257, 640], hq=6, hkv=1, fused=True)
 
 
+def test_one_sequence_of_8192_tokens():
+    """The length of the profile (64 key tiles per query tile: many lazy rescales, the tile loop's phase bits wrap)."""
+    _case([8192], [8192], hq=6, hkv=1)
+
+
+def test_four_packed_sequences_of_8192_tokens():
+    _case([8192] * 4, [8192] * 4, hq=6, hkv=1, seed=3)
+
+
 def test_model_attention_without_gradients_runs_the_kernel():
     from pear_b200.ops import kernels as K
     from pear_b200.ops import lib as kl

@@ -104,6 +104,30 @@ def test_generate_runs_and_is_deterministic():
     assert all(0 <= t < model.config.vocab_size for t in a.tokens)
 
 
+def test_run_to_run_divergence_of_the_logits_is_bounded():
+    """The split-K partial sums of a GEMV are added with fp32 atomics, so the order of the additions differs between runs;
+    the effect on the verify rows' logits stays at the level of fp32 rounding (the sampled tokens above may still differ
+    once two candidates are closer than that)."""
+    import torch
+    from pear_b200.deploy.engine import MegakernelEngine, ModuleWeights
+
+    model, drafter = build_models(seed=2)
+    eng = MegakernelEngine(model.config, drafter.config, ModuleWeights(model, drafter, "cuda"), max_len=512, n_draft=3,
+                           temperature=1.0, seed=11)
+    prompt = list(range(5, 40))
+    runs = []
+    for _ in range(3):
+        eng.start(prompt)
+        eng.prefill()
+        eng.decode_step()
+        torch.cuda.synchronize()
+        eng.check_status()
+        runs.append(eng.logits[:1].float().clone())  # the row after the prompt's last token: its inputs are the same in every run
+    scale = float(runs[0].abs().max())
+    for other in runs[1:]:
+        assert float((other - runs[0]).abs().max()) <= 1e-4 * scale, (float((other - runs[0]).abs().max()), scale)
+
+
 def test_deploy_server_completes_through_the_engine():
     """The one-session server in front of the megakernel engine: a completion returns the requested number of tokens and
     the counters of its metrics text move."""
