@@ -32,7 +32,10 @@ __device__ __forceinline__ uint4 philox4x32_10(uint4 ctr, uint2 key) {
   }
   return ctr;
 }
-__device__ __forceinline__ float u01(uint32_t x) { return ((float)(x >> 8) + 0.5f) * (1.0f / 16777216.0f); }
+// 23 random bits + 1/2: every value is exact in fp32 and lies strictly inside (0, 1). (With 24 bits the largest one,
+// 2^24 - 1/2, rounds to 2^24: a uniform of exactly 1 makes the exponential-race key infinite, and at 248 320 draws per row
+// that happened in about 1.5 percent of the rows: found by the goodness-of-fit test.)
+__device__ __forceinline__ float u01(uint32_t x) { return ((float)(x >> 9) + 0.5f) * (1.0f / 8388608.0f); }
 __device__ __forceinline__ float gumbel(uint32_t x) { return -__logf(-__logf(u01(x))); }
 
 // merge (max, sum of exp relative to max)
