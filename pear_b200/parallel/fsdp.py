@@ -22,9 +22,25 @@ import torch.nn as nn
 from . import collectives as C
 
 
+_COMM_STREAMS: dict = {}
+
+
+def comm_stream(device) -> "torch.cuda.Stream":
+    """The side stream (one per device) on which prefetched all-gathers and gradient reduce-scatters run."""
+    key = torch.device(device)
+    if key not in _COMM_STREAMS:
+        _COMM_STREAMS[key] = torch.cuda.Stream(key)
+    return _COMM_STREAMS[key]
+
+
 class FlatUnit:
+    overlap = True  # multi-rank CUDA runs: gathers are prefetched and gradients reduced on the side stream
+
     def __init__(self, name: str, params: list[tuple[str, nn.Parameter]], shard_group=None, replicate_group=None,
-                 compute_dtype: torch.dtype = torch.bfloat16, device=None, average: bool = False):
+                 compute_dtype: torch.dtype = torch.bfloat16, device=None, average: bool = False, src_rank: Optional[int] = None):
+        """``src_rank``: only that rank of the shard group holds real parameters (the others built the model on the meta
+        device); the unit's fp32 flat buffer is broadcast from it and every rank keeps its own shard (upstream:
+        3rdparty/verl/patches/0031 — meta-device ranks receive the weights by broadcast)."""
         self.name = name
         self.average = average  # False: gradients are SUMMED over ranks (the loss is already normalised globally)
         self.names = [n for n, _ in params]
@@ -33,18 +49,21 @@ class FlatUnit:
         self.world = dist.get_world_size(shard_group) if shard_group is not None else 1
         self.rank = dist.get_rank(shard_group) if shard_group is not None else 0
         self.compute_dtype = compute_dtype
-        self.shapes = [tuple(p.shape) for p in self.params]
-        self.numels = [p.numel() for p in self.params]
+        self.shapes = [tuple(getattr(p, "_full_shape", p.shape)) for p in self.params]  # (meta-built ranks: see ShardedModel)
+        self.numels = [int(torch.Size(s).numel()) for s in self.shapes]
         total = sum(self.numels)
         align = 8 * self.world  # 16-byte aligned bf16 shards
         self.padded = (total + align - 1) // align * align
         self.shard_numel = self.padded // self.world
         device = device or self.params[0].device
         flat = torch.zeros(self.padded, dtype=torch.float32, device=device)
-        o = 0
-        for p, n in zip(self.params, self.numels):
-            flat[o : o + n] = p.detach().reshape(-1).float().to(device)
-            o += n
+        if src_rank is None or self.rank == src_rank:
+            o = 0
+            for p, n in zip(self.params, self.numels):
+                flat[o : o + n] = p.detach().reshape(-1).float().to(device)
+                o += n
+        if src_rank is not None and self.world > 1:
+            dist.broadcast(flat, dist.get_global_rank(shard_group, src_rank), group=shard_group)
         # the optimizer's parameter: this rank's fp32 master shard
         self.shard = nn.Parameter(flat[self.rank * self.shard_numel : (self.rank + 1) * self.shard_numel].clone())
         self.full: Optional[torch.Tensor] = None
@@ -52,17 +71,44 @@ class FlatUnit:
         for p in self.params:
             p.data = self._empty
         self.gathered = False
+        self._pending = None  # (full buffer, ready event) of a prefetched gather
+        self._grad_pending = False
+
+    def _overlapped(self) -> bool:
+        return FlatUnit.overlap and self.world > 1 and self.shard.is_cuda
 
     # -- parameter lifetime -----------------------------------------------------------------------------------------
+    def prefetch(self) -> None:
+        """Start this unit's all-gather on the side stream (the layer before it is still computing); ``gather`` picks the
+        result up. Without overlap (one rank, CPU) it does nothing and ``gather`` runs the collective itself."""
+        if self.gathered or self._pending is not None or not self._overlapped():
+            return
+        cur, side = torch.cuda.current_stream(self.shard.device), comm_stream(self.shard.device)
+        side.wait_stream(cur)  # the shard as the optimizer (or a load) on the compute stream left it
+        with torch.cuda.stream(side):
+            local = self.shard.detach().to(self.compute_dtype)
+            full = torch.empty(self.padded, dtype=self.compute_dtype, device=local.device)
+            dist.all_gather_into_tensor(full, local.contiguous(), group=self.group)
+            ready = torch.cuda.Event()
+            ready.record(side)
+        self._pending = (full, ready)
+
     def gather(self, stream=None) -> None:
         if self.gathered:
             return
-        local = self.shard.detach().to(self.compute_dtype)
-        if self.world > 1:
-            full = torch.empty(self.padded, dtype=self.compute_dtype, device=local.device)
-            dist.all_gather_into_tensor(full, local.contiguous(), group=self.group)
+        if self._pending is not None:
+            full, ready = self._pending
+            self._pending = None
+            cur = torch.cuda.current_stream(full.device)
+            cur.wait_event(ready)
+            full.record_stream(cur)  # allocated on the side stream, used (and freed) on the compute stream
         else:
-            full = local if local.data_ptr() != self.shard.data_ptr() else local.clone()
+            local = self.shard.detach().to(self.compute_dtype)
+            if self.world > 1:
+                full = torch.empty(self.padded, dtype=self.compute_dtype, device=local.device)
+                dist.all_gather_into_tensor(full, local.contiguous(), group=self.group)
+            else:
+                full = local if local.data_ptr() != self.shard.data_ptr() else local.clone()
         self.full = full
         o = 0
         for p, n, shp in zip(self.params, self.numels, self.shapes):
@@ -88,20 +134,38 @@ class FlatUnit:
                 flat[o : o + n] = p.grad.reshape(-1).float()
                 p.grad = None
             o += n
-        if self.world > 1:
-            piece = C.reduce_scatter_sum(flat, self.group)
-            if average:
-                piece = piece / self.world
+        def finish(flat):
+            if self.world > 1:
+                piece = C.reduce_scatter_sum(flat, self.group)
+                if average:
+                    piece = piece / self.world
+            else:
+                piece = flat
+            if self.shard.grad is None:
+                self.shard.grad = piece.clone()
+            else:
+                self.shard.grad.add_(piece)
+            if last_micro_batch and self.replicate_group is not None and dist.get_world_size(self.replicate_group) > 1:
+                dist.all_reduce(self.shard.grad, group=self.replicate_group)
+                if average:
+                    self.shard.grad.div_(dist.get_world_size(self.replicate_group))
+
+        if self._overlapped():
+            # the reduce-scatter (and the accumulation into the shard's gradient) runs on the side stream under the backward
+            # of the next layer; `wait_grads` joins it before anything on the compute stream reads the gradient
+            cur, side = torch.cuda.current_stream(flat.device), comm_stream(flat.device)
+            side.wait_stream(cur)
+            with torch.cuda.stream(side):
+                finish(flat)
+            flat.record_stream(side)
+            self._grad_pending = True
         else:
-            piece = flat
-        if self.shard.grad is None:
-            self.shard.grad = piece.clone()
-        else:
-            self.shard.grad.add_(piece)
-        if last_micro_batch and self.replicate_group is not None and dist.get_world_size(self.replicate_group) > 1:
-            dist.all_reduce(self.shard.grad, group=self.replicate_group)
-            if average:
-                self.shard.grad.div_(dist.get_world_size(self.replicate_group))
+            finish(flat)
+
+    def wait_grads(self) -> None:
+        if self._grad_pending:
+            torch.cuda.current_stream(self.shard.device).wait_stream(comm_stream(self.shard.device))
+            self._grad_pending = False
 
     # -- full state (checkpoint export, weight sync) ------------------------------------------------------------------
     def full_state(self, dtype=torch.float32) -> dict[str, torch.Tensor]:
@@ -131,8 +195,21 @@ class ShardedModel:
     """The model's parameters as flat sharded units: one per decoder layer, fp32 units for ``fp32_modules``, one root."""
 
     def __init__(self, model: nn.Module, shard_group=None, replicate_group=None, compute_dtype=torch.bfloat16,
-                 fp32_modules: Iterable[str] = (), device=None):
+                 fp32_modules: Iterable[str] = (), device=None, src_rank: Optional[int] = None):
+        """``src_rank``: the one rank whose ``model`` holds real weights (see :class:`FlatUnit`); the units are built in the
+        same order on every rank, one broadcast each, so no rank but the source ever holds more than one unit in full."""
         self.model = model
+        # a rank that built the model on the meta device: every parameter becomes an empty real tensor that remembers its
+        # shape (a meta tensor cannot be given storage later)
+        swapped: dict[int, nn.Parameter] = {}  # a parameter shared by two modules stays shared
+        for mod in model.modules():
+            for pname, p in list(mod._parameters.items()):
+                if p is not None and p.is_meta:
+                    if id(p) not in swapped:
+                        real = nn.Parameter(torch.empty(0, dtype=p.dtype, device=device), requires_grad=p.requires_grad)
+                        real._full_shape = tuple(p.shape)
+                        swapped[id(p)] = real
+                    mod._parameters[pname] = swapped[id(p)]
         self.units: dict[str, FlatUnit] = {}
         taken: set[int] = set()
         named = dict(model.named_parameters())
@@ -143,7 +220,7 @@ class ShardedModel:
             if not items:
                 return
             taken.update(id(p) for _, p in items)
-            self.units[name] = FlatUnit(name, items, shard_group, replicate_group, dtype, device)
+            self.units[name] = FlatUnit(name, items, shard_group, replicate_group, dtype, device, src_rank=src_rank)
 
         for pat in fp32_modules:
             make(f"fp32:{pat}", [(n, p) for n, p in named.items() if pat in n], torch.float32)
@@ -174,6 +251,11 @@ class ShardedModel:
         for name, u in self.units.items():
             if not name.startswith("layer"):
                 u.reduce_grads(last_micro_batch)
+
+    def wait_grads(self) -> None:
+        """Join the side stream: every unit's reduced gradient is complete for the compute stream."""
+        for u in self.units.values():
+            u.wait_grads()
 
     def full_state_dict(self, dtype=torch.float32) -> dict[str, torch.Tensor]:
         out: dict[str, torch.Tensor] = {}

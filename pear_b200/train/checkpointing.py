@@ -1,5 +1,8 @@
 """Layer runner: gradient checkpointing, FSDP gather/reduce-scatter and activation offload in one autograd node.
 
+On multi-rank CUDA runs the next layer's all-gather is started on a side stream when a layer begins (forward: layer i + 1,
+backward: layer i - 1) and a layer's gradient reduce-scatter runs on that stream under the backward of the layer before it.
+
 Forward of a layer: all-gather its parameter unit, run it without building a graph, stash its input (optionally to
 pinned host memory on a side stream), free the gathered parameters. Backward: gather again, bring the input back
 (prefetching the next layer's input while this one recomputes), recompute with a graph, backpropagate, reduce-scatter
@@ -30,11 +33,17 @@ class LayerRunner:
     def unit(self, i: int):
         return self.sharded.layer_units[i] if self.sharded is not None else None
 
+    def prefetch(self, i: int) -> None:
+        """Start the all-gather of layer ``i``'s parameters while the current layer computes."""
+        if self.sharded is not None and 0 <= i < len(self.sharded.layer_units):
+            self.sharded.layer_units[i].prefetch()
+
     def __call__(self, i: int, layer, r: torch.Tensor, meta) -> torch.Tensor:
         if not torch.is_grad_enabled() or not self.checkpoint:
             u = self.unit(i)
             if u is not None:
                 u.gather()
+                self.prefetch(i + 1)
             out = layer(r, meta)
             if u is not None and not torch.is_grad_enabled():
                 u.release()
@@ -50,6 +59,7 @@ class _CheckpointedLayer(torch.autograd.Function):
         u = runner.unit(i)
         if u is not None:
             u.gather()
+            runner.prefetch(i + 1)
         ctx.attn_box = [] if runner.retain_attention else None
         with torch.no_grad():
             if ctx.attn_box is not None:
@@ -76,6 +86,7 @@ class _CheckpointedLayer(torch.autograd.Function):
         u = runner.unit(i)
         if u is not None:
             u.gather()
+            runner.prefetch(i - 1)
         if ctx.handle is not None:
             r = runner.offload.fetch(ctx.handle)
             runner.offload.prefetch(i - 1)

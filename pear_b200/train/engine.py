@@ -117,6 +117,9 @@ class EngineConfig:
     # the TF32 tensor cores instead of SIMT fp32; the head's logits do not (split-bf16 GEMM, close to fp32)
     tf32_matmul: bool = True
     fused_adamw: bool = True  # on a GPU: one kernel pass per parameter tensor instead of torch's AdamW statements
+    # multi-rank runs: only rank 0 builds (or loads) real weights, the other ranks build the model on the meta device and
+    # receive their shards unit by unit (no rank but 0 ever holds the whole model; rank 0 holds it on the host only)
+    sharded_construction: bool = True
 
     @classmethod
     def from_config(cls, cfg) -> "EngineConfig":
@@ -166,25 +169,36 @@ class TrainEngine:
         if kernels is not None:
             kernels.check_config(cfg)
 
-        # ---- build: every rank builds the same seeded model, or takes the given weights (rank 0's in a real run)
-        model = HybridForCausalLM(model_cfg, with_mtp=with_mtp)
-        if state_dict is not None:
-            model.load_state_dict(state_dict, strict=False)
+        # ---- build: one rank builds the seeded model (or takes the given weights) on the host, the others on the meta device
+        self.src_rank = 0 if (self.world > 1 and cfg.sharded_construction) else None
+        on_meta = self.src_rank is not None and self.rank != self.src_rank
+        if on_meta:
+            with torch.device("meta"):
+                model = HybridForCausalLM(model_cfg, with_mtp=with_mtp)
         else:
-            model.init_weights(seed)
+            model = HybridForCausalLM(model_cfg, with_mtp=with_mtp)
+            if state_dict is not None:
+                model.load_state_dict(state_dict, strict=False)
+            else:
+                model.init_weights(seed)
         if kernels is not None:  # the install order the GPU backend relies on
             kernels.install(model, fp32_residual=True, use_fused_kernels=True, fused_kernels_backend=None)
             kernels.check_model(model, use_remove_padding=True, use_fused_kernels=True, fused_kernels_backend=None)
             if cfg.use_gpu_backend:
                 kernels.install_gpu_backend(model)
             kernels.install_checkpointing(model)
-        model.to(self.device)
+        if self.src_rank is None:
+            model.to(self.device)  # (with a source rank the parameters go to the device unit by unit while they are sharded)
         dtype = {"bf16": torch.bfloat16, "fp32": torch.float32, "fp16": torch.float16}[cfg.param_dtype]
         if self.device.type == "cpu" and dtype != torch.float32:
             dtype = torch.float32  # CPU plumbing runs in fp32
         self.model = model
         self.sharded = ShardedModel(model, world_group if self.world > 1 else None, replicate_group, dtype, cfg.fp32_modules,
-                                    self.device)
+                                    self.device, src_rank=self.src_rank)
+        for mod in model.modules():  # buffers (none hold weights) follow the parameters' device
+            for bname, buf in list(mod._buffers.items()):
+                if buf is not None and buf.device != self.device:
+                    mod._buffers[bname] = torch.zeros_like(buf, device=self.device) if buf.is_meta else buf.to(self.device)
         self.offload = CheckpointInputOffload(True) if cfg.enable_activation_offload else None
         self.runner = LayerRunner(self.sharded, self.offload, cfg.enable_gradient_checkpointing,
                                   retain_attention=cfg.gradient_checkpointing_retain_attention,
@@ -260,6 +274,7 @@ class TrainEngine:
                     self.offload.clear()
             self.sharded.reduce_static_grads(True)
             self.sharded.release_static()
+            self.sharded.wait_grads()
             return agg
 
         def before_rerun():
