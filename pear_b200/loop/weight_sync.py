@@ -14,8 +14,10 @@ Transports:
 * ``InProcessTransport``: trainer and replicas in one process (tests, the single-node synchronous recipe);
 * ``BroadcastTransport``: a ``torch.distributed`` group of {trainer rank 0} + {replica ranks}; bucket payloads are
   flattened into one buffer per bucket and broadcast (NCCL on GPUs, gloo on CPU); the group may be rebuilt every sync.
-The NVSwitch transport (P2P reads of the trainer's staging buffer fused with bf16 -> NVFP4 requantisation on the
-receiver) lives in ``pear_b200/parallel/symm.py`` and plugs in through the same interface.
+* ``SymmTransport``: trainer rank and replica ranks of one node share symmetric memory (``parallel/symm.py``); the
+  sender stages a bucket once, every replica rank pulls ONLY the blocks of its own tensor-parallel shard out of it with
+  peer loads over NVSwitch (the sender's egress is one model, not one model per receiver), and a receiver that serves in
+  NVFP4 quantises while it pulls (``bcast_quant_nvfp4_kernel``).
 """
 
 from __future__ import annotations
@@ -97,12 +99,102 @@ class BroadcastTransport:
         return out, info["version"], info["last"]
 
 
-def receive_all(transport: BroadcastTransport, server) -> int:
+class SymmTransport:
+    """NVSwitch transport over a :class:`pear_b200.parallel.symm.SymmWorld` whose group holds the sending trainer rank and
+    the replica ranks. Per bucket: the sender copies the (already cast) tensors into its symmetric staging buffer and
+    publishes a manifest; after a device barrier every receiver pulls the blocks ``shard_pieces`` names for its
+    tensor-parallel rank straight out of the sender's buffer (own kernel, 16-byte peer loads); a second barrier hands the
+    buffer back. With ``nvfp4`` the 2-D weights whose inner size is a multiple of 256 arrive as ``(packed, scale)`` in the
+    decode megakernel's stage layout, quantised during the pull; everything else stays in the rollout dtype.
+    (Upstream broadcasts whole buckets with NCCL and casts on the receiver: pear/rollout/checkpoint_engine.py:15-43.)"""
+
+    def __init__(self, symm, src: int, model_cfg=None, tp_rank: int = 0, tp_world: int = 1, bucket_megabytes: int = 512, nvfp4: bool = False):
+        self.symm, self.src = symm, src
+        self.model_cfg, self.tp_rank, self.tp_world, self.nvfp4 = model_cfg, tp_rank, tp_world, nvfp4
+        self.capacity = (bucket_megabytes << 20) + (1 << 20)  # offsets are rounded up to 256 bytes per tensor
+        self.staging = symm.alloc((self.capacity,), torch.uint8)
+        self.bytes_pulled = 0
+
+    # -- sender -------------------------------------------------------------------------------------------------------
+    def send(self, bucket: list[tuple[str, torch.Tensor]], version: int, last: bool) -> None:
+        manifest, off = [], 0
+        for name, t in bucket:
+            nbytes = t.numel() * t.element_size()
+            if off + nbytes > self.capacity:
+                raise ValueError(f"bucket of {off + nbytes} bytes exceeds the staging buffer ({self.capacity}); lower bucket_megabytes")
+            self.staging.tensor[off:off + nbytes].copy_(t.detach().contiguous().view(-1).view(torch.uint8), non_blocking=True)
+            manifest.append((name, tuple(t.shape), t.dtype, off))
+            off = (off + nbytes + 255) // 256 * 256
+        obj = [{"manifest": manifest, "version": version, "last": last}]
+        dist.broadcast_object_list(obj, src=dist.get_global_rank(self.symm.group, self.src), group=self.symm.group)
+        self.symm.device_barrier()  # the bucket is complete in the sender's buffer
+        self.symm.device_barrier()  # every receiver has pulled what it needs: the buffer may be overwritten
+
+    # -- receivers ----------------------------------------------------------------------------------------------------
+    def receive(self) -> tuple[dict, int, bool]:
+        import ctypes
+
+        from ..ops import lib as _lib
+        from ..parallel.tensor_parallel import shard_pieces, shard_shape
+
+        obj = [None]
+        dist.broadcast_object_list(obj, src=dist.get_global_rank(self.symm.group, self.src), group=self.symm.group)
+        info = obj[0]
+        self.symm.device_barrier()
+        base = self.staging.ptrs[self.src]
+        out: dict = {}
+        for name, shape, dtype, off in info["manifest"]:
+            es = torch.empty(0, dtype=dtype).element_size()
+            pieces = shard_pieces(name, shape, self.model_cfg, self.tp_rank, self.tp_world) if self.model_cfg is not None and self.tp_world > 1 \
+                else [(0, int(shape[0]) if shape else 1, 0, int(torch.Size(shape[1:]).numel()) if len(shape) > 1 else 1)]
+            full_cols = int(torch.Size(shape[1:]).numel()) if len(shape) > 1 else 1
+            local_shape = shard_shape(shape, pieces)
+            if (self.nvfp4 and len(shape) == 2 and dtype == torch.bfloat16 and len(pieces) == 1 and pieces[0][3] == full_cols
+                    and full_cols % 256 == 0):  # whole rows (a row cut or a replicated matrix): contiguous in the sender's buffer
+                r0, r, c0, c = pieces[0]
+                out[name] = self._pull_nvfp4(base + off + r0 * full_cols * es, r, c)
+                self.bytes_pulled += r * c * es
+                continue
+            dst = torch.empty(local_shape, dtype=dtype, device=self.symm.device)
+            dst_rows = dst.view(dst.shape[0], -1) if dst.dim() >= 1 and dst.numel() else dst.view(1, -1)
+            row = 0
+            for r0, r, c0, c in pieces:
+                _lib.check(_lib.lib().pear_pull_block(ctypes.c_void_p(base + off + (r0 * full_cols + c0) * es), ctypes.c_longlong(full_cols * es),
+                                                      ctypes.c_void_p(dst_rows.data_ptr() + row * dst_rows.shape[1] * es),
+                                                      ctypes.c_longlong(dst_rows.shape[1] * es), r, ctypes.c_longlong(c * es), _lib.stream()),
+                           "pull_block")
+                _lib.count_launch()
+                row += r
+                self.bytes_pulled += r * c * es
+            out[name] = dst
+        self.symm.device_barrier()
+        return out, info["version"], info["last"]
+
+    def _pull_nvfp4(self, src_ptr: int, rows: int, k: int):
+        import ctypes
+        import math
+
+        from ..ops import lib as _lib
+
+        lib, dev = _lib.lib(), self.symm.device
+        # the tensor scale needs the block's maximum first: one pass of peer loads for it, one for the quantisation
+        amax = torch.zeros(1, dtype=torch.int32, device=dev)
+        _lib.check(lib.pear_amax_bf16(ctypes.c_void_p(src_ptr), ctypes.c_size_t(rows * k), _lib.ptr(amax), _lib.stream()), "amax_bf16")
+        a = float(amax.view(torch.float32).item())
+        gs = 1.0 if (a <= 0.0 or not math.isfinite(a)) else 2.0 ** math.floor(math.log2(448.0 * 6.0 / a))
+        packed = torch.zeros((rows + 127) // 128, k // 256, 18432, dtype=torch.uint8, device=dev)
+        _lib.check(lib.pear_bcast_quant_nvfp4(ctypes.c_void_p(src_ptr), rows, k, k, ctypes.c_float(gs), _lib.ptr(packed), _lib.stream()),
+                   "bcast_quant_nvfp4")
+        _lib.count_launch(2)
+        return packed, gs
+
+
+def receive_all(transport, server) -> int:
     """Replica side of a broadcast sync: collect buckets until the last one, then load."""
     state: dict[str, torch.Tensor] = {}
     while True:
         part, version, last = transport.receive()
-        state.update({k: v.clone() for k, v in part.items()})
+        state.update({k: (v.clone() if torch.is_tensor(v) else v) for k, v in part.items()})
         if last:
             server.update_weights(state, version)
             return version

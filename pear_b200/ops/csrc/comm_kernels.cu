@@ -266,6 +266,26 @@ __global__ void argmax_finish_kernel(const unsigned long long* __restrict__ my_x
 
 using namespace pear;
 
+// ------------------------------------------------------------------------------------------------ strided block pull
+// Copy a [rows, row_bytes] block out of a peer's (or the local) memory into local memory, both sides strided: the weight-sync
+// receiver takes only its own tensor-parallel shard of each tensor out of the sender's staging buffer (a column-parallel
+// matrix is a row range, a row-parallel one a column range). 16-byte loads when both sides allow it. One CTA per group of rows.
+__global__ void __launch_bounds__(256) pull_block_kernel(const uint8_t* __restrict__ src, long long src_ld, uint8_t* __restrict__ dst, long long dst_ld,
+                                                         int rows, long long row_bytes, int vec) {
+  constexpr long long kChunk = 32768;  // bytes of a row one CTA copies
+  const long long c0 = (long long)blockIdx.y * kChunk;
+  const long long c1 = c0 + kChunk < row_bytes ? c0 + kChunk : row_bytes;
+  for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+    const uint8_t* s = src + (long long)r * src_ld;
+    uint8_t* d = dst + (long long)r * dst_ld;
+    if (vec) {
+      for (long long i = (c0 >> 4) + threadIdx.x; i < (c1 >> 4); i += blockDim.x) ((uint4*)d)[i] = ((const uint4*)s)[i];
+    } else {
+      for (long long i = c0 + threadIdx.x; i < c1; i += blockDim.x) d[i] = s[i];
+    }
+  }
+}
+
 static PeerPtrs to_ptrs(const void* const* host_ptrs, int world) {
   PeerPtrs p;
   for (int i = 0; i < kMaxRanks; ++i) p.p[i] = i < world ? const_cast<void*>(host_ptrs[i]) : nullptr;
@@ -335,6 +355,19 @@ PEAR_API int pear_argmax_shard(const float* logits, int rows, int Vs, int ld, in
 
 PEAR_API int pear_argmax_finish(const void* my_xbuf, int rows, int world, int* token, float* value, void* stream) {
   argmax_finish_kernel<<<(rows + 127) / 128, 128, 0, (cudaStream_t)stream>>>((const unsigned long long*)my_xbuf, rows, world, token, value);
+  PEAR_LAUNCH_CHECK();
+  return 0;
+}
+
+// src: a device pointer into a peer's symmetric buffer (or local memory); strides and sizes in bytes.
+PEAR_API int pear_pull_block(const void* src, long long src_ld, void* dst, long long dst_ld, int rows, long long row_bytes, void* stream) {
+  if (rows <= 0 || row_bytes <= 0) return 0;
+  const int vec = ((uintptr_t)src % 16 == 0) && ((uintptr_t)dst % 16 == 0) && (src_ld % 16 == 0) && (dst_ld % 16 == 0) && (row_bytes % 16 == 0);
+  const long long chunks = (row_bytes + 32767) / 32768;
+  if (chunks > 65535) return (int)cudaErrorInvalidValue;  // a single row of more than 2 GB: cut it on the caller's side
+  const long long want = 1184 / chunks > 0 ? 1184 / chunks : 1;
+  const dim3 grid((unsigned)(rows < want ? rows : want), (unsigned)chunks);
+  pull_block_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const uint8_t*)src, src_ld, (uint8_t*)dst, dst_ld, rows, row_bytes, vec);
   PEAR_LAUNCH_CHECK();
   return 0;
 }

@@ -89,6 +89,8 @@ def add_rmsnorm(parts: Optional[torch.Tensor], nsplit: int, residual: torch.Tens
     """residual (+)= sum of the first ``nsplit`` planes of ``parts`` [S, M, ld]; ``out`` bf16 = RMSNorm(residual)."""
     rows = residual.shape[0] if rows is None else rows
     h = residual.shape[1]
+    _lib.expect(torch.float32, False, parts=parts, residual=residual, weight=weight)
+    _lib.expect(torch.bfloat16, False, out=out)
     ss, ldp = (parts.stride(0), parts.stride(1)) if parts is not None else (0, 0)
     _lib.check(_lib.lib().pear_ds_add_rmsnorm(_lib.ptr(parts), nsplit, _ll(ss), ldp, _lib.ptr(residual), mode, _lib.ptr(weight), _lib.ptr(out), rows, h,
                                               _f(eps), 1 if one_plus else 0, _lib.stream()), "ds_add_rmsnorm")
@@ -105,6 +107,10 @@ def reduce_parts_bf16(parts: torch.Tensor, nsplit: int, out: torch.Tensor, rows:
 
 def attn_prep(qkv: torch.Tensor, qn_w, kn_w, inv_freq: torch.Tensor, rot: int, ctx, rope_off, block_table, rows: int, t: int, hq: int, hkv: int, d: int,
               gated: bool, eps: float, q_out, kc, vc) -> None:
+    _lib.expect(torch.float32, False, qkv=qkv, qn_w=qn_w, kn_w=kn_w)
+    _lib.expect(torch.float64, inv_freq=inv_freq)
+    _lib.expect(torch.bfloat16, False, q_out=q_out, kc=kc, vc=vc)
+    _lib.expect(torch.int32, False, ctx=ctx, rope_off=rope_off, block_table=block_table)
     _lib.check(_lib.lib().pear_ds_attn_prep(_lib.ptr(qkv), qkv.stride(0), _lib.ptr(qn_w), _lib.ptr(kn_w), _lib.ptr(inv_freq), rot, _lib.ptr(ctx),
                                             _lib.ptr(rope_off), _lib.ptr(block_table), block_table.stride(0), rows, t, hq, hkv, d, 1 if gated else 0,
                                             _f(eps), _lib.ptr(q_out), _lib.ptr(kc), _lib.ptr(vc), _lib.stream()), "ds_attn_prep")
@@ -161,6 +167,10 @@ def gdn_scratch(device, batch: int, hk: int, hv: int) -> torch.Tensor:
 def gdn_verify(proj, conv_w, a_log, dt_bias, norm_w, state, conv_rec, ab_rec, slots, ctx, parity, ncommit, batch: int, t: int, tmax: int, hk: int,
                hv: int, l2_eps: float, rms_eps: float, out) -> None:
     scratch = gdn_scratch(state.device, batch, hk, hv)
+    _lib.expect(torch.float32, False, proj=proj)
+    _lib.expect(torch.float32, conv_w=conv_w, a_log=a_log, dt_bias=dt_bias, norm_w=norm_w, state=state, conv_rec=conv_rec, ab_rec=ab_rec)
+    _lib.expect(torch.int32, slots=slots, ctx=ctx, parity=parity, ncommit=ncommit)
+    _lib.expect(torch.bfloat16, out=out)
     _lib.check(_lib.lib().pear_ds_gdn_verify(_lib.ptr(proj), proj.stride(0) if proj is not None else 0, _lib.ptr(conv_w), _lib.ptr(a_log),
                                              _lib.ptr(dt_bias), _lib.ptr(norm_w), _lib.ptr(state), state.shape[0], _lib.ptr(conv_rec), _lib.ptr(ab_rec), _lib.ptr(slots),
                                              _lib.ptr(ctx), _lib.ptr(parity), _lib.ptr(ncommit), batch, t, tmax, hk, hv, _f(l2_eps), _f(rms_eps),
@@ -178,6 +188,8 @@ def _ptr_array(ptrs):
 
 def verify_chunks(logits, vs: int, v0: int, temperature: float, tok_in, ctx, batch: int, t: int, chunks: int, seed: int, step_ctr, recs_ptrs,
                   rank: int, world: int, epoch_ctr, rec_buf_elems: int) -> None:
+    _lib.expect(torch.float32, False, logits=logits)
+    _lib.expect(torch.int32, False, tok_in=tok_in, ctx=ctx)
     _lib.check(_lib.lib().pear_ds_verify_chunks(_lib.ptr(logits), logits.stride(0), vs, v0, _f(temperature), _lib.ptr(tok_in), _lib.ptr(ctx), batch, t,
                                                 chunks, _u(seed), _lib.ptr(step_ctr), recs_ptrs, rank, world, _lib.ptr(epoch_ctr), _sz(rec_buf_elems),
                                                 _lib.stream()), "ds_verify_chunks")
@@ -194,6 +206,9 @@ def verify_finish(my_recs, rec_buf_elems: int, epoch_ctr, world: int, chunks: in
 
 
 def mtp_input(tokens, table, hidden, sel, we, wh, rows: int, h: int, eps: float, out) -> None:
+    _lib.expect(torch.bfloat16, table=table, out=out)
+    _lib.expect(torch.float32, False, hidden=hidden, we=we, wh=wh)
+    _lib.expect(torch.int32, False, tokens=tokens, sel=sel)
     _lib.check(_lib.lib().pear_ds_mtp_input(_lib.ptr(tokens), _lib.ptr(table), table.shape[0], _lib.ptr(hidden), _lib.ptr(sel), _lib.ptr(we), _lib.ptr(wh),
                                             rows, h, _f(eps), _lib.ptr(out), _lib.stream()), "ds_mtp_input")
     _lib.count_launch()
@@ -207,6 +222,7 @@ def gather_rows(src: torch.Tensor, sel: torch.Tensor, dst: torch.Tensor, rows: i
 
 
 def argmax_chunks(logits, vs: int, v0: int, rows: int, chunks: int, keys_ptrs, rank: int, world: int, epoch_ctr, buf_elems: int) -> None:
+    _lib.expect(torch.float32, False, logits=logits)
     _lib.check(_lib.lib().pear_ds_argmax_chunks(_lib.ptr(logits), logits.stride(0), vs, v0, rows, chunks, keys_ptrs, rank, world, _lib.ptr(epoch_ctr),
                                                 _sz(buf_elems), _lib.stream()), "ds_argmax_chunks")
     _lib.count_launch()

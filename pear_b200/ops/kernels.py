@@ -13,7 +13,7 @@ import torch
 import torch.nn.functional as F
 
 from . import reference as ref
-from .lib import check, count_launch, lib, ptr, stream
+from .lib import check, count_launch, lib, on_device, ptr, stream
 
 DT_F32, DT_BF16 = 0, 1
 
@@ -36,6 +36,7 @@ class _RMSNorm(torch.autograd.Function):
     def forward(ctx, x, weight, eps, one_plus, residual):
         shape = x.shape
         dim = shape[-1]
+        on_device(x)
         xc = x.contiguous()
         if xc.dtype not in (torch.float32, torch.bfloat16):
             xc = xc.float()

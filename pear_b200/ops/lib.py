@@ -50,6 +50,18 @@ def check(code: int, what: str = "kernel launch") -> None:
         raise RuntimeError(f"{what} failed with CUDA error {code}")
 
 
+def expect(dtype: torch.dtype, _contiguous: bool = True, **tensors) -> None:
+    """The kernels take raw pointers: a tensor of another element type (or a strided view where the kernel takes no stride)
+    would be read past its end. Raise instead (``None`` entries are optional arguments)."""
+    for name, t in tensors.items():
+        if t is None:
+            continue
+        if t.dtype != dtype:
+            raise TypeError(f"{name}: the kernel reads {dtype}, got {t.dtype}")
+        if _contiguous and not t.is_contiguous():
+            raise ValueError(f"{name}: the kernel needs a contiguous tensor")
+
+
 def ptr(t) -> ctypes.c_void_p:
     if t is None:
         return ctypes.c_void_p(0)
@@ -59,7 +71,16 @@ def ptr(t) -> ctypes.c_void_p:
 
 
 def stream() -> ctypes.c_void_p:
+    """The current stream of the calling thread's current device: the kernels launch there, so a thread that works on another
+    GPU than device 0 must have called ``torch.cuda.set_device`` (see :func:`on_device`)."""
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def on_device(t: torch.Tensor) -> None:
+    """Raise when ``t`` lives on another GPU than the calling thread's current device (host threads start on device 0)."""
+    if t.is_cuda and t.device.index != torch.cuda.current_device():
+        raise RuntimeError(f"tensor on cuda:{t.device.index} but this thread's current device is cuda:{torch.cuda.current_device()}: "
+                           "call torch.cuda.set_device in the thread before launching kernels")
 
 
 LAUNCH_COUNT = 0  # launches of this library's kernels issued through the python bindings (bench.py reports it)

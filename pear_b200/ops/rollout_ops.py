@@ -54,6 +54,8 @@ def verify_greedy(logits: torch.Tensor, drafts: torch.Tensor, temperature: float
 def gdn_decode(x, z, a, b, conv_w, A_log, dt_bias, norm_w, conv_state, state, slots, hk: int, hv: int, l2_eps=1e-6, rms_eps=1e-6):
     """One decode token per sequence; updates ``conv_state`` [slots, 3, C] and ``state`` [slots, Hv, 128, 128] in place."""
     batch = x.shape[0]
+    _lib.on_device(x)
+    _lib.expect(torch.float32, x=x, z=z, a=a, b=b, conv_w=conv_w, A_log=A_log, dt_bias=dt_bias, norm_w=norm_w, conv_state=conv_state, state=state)
     out = torch.empty(batch, hv * 128, dtype=torch.float32, device=x.device)
     _lib.check(_lib.lib().pear_gdn_decode(_lib.ptr(x), _lib.ptr(z), _lib.ptr(a), _lib.ptr(b), _lib.ptr(conv_w), _lib.ptr(A_log), _lib.ptr(dt_bias),
                                           _lib.ptr(norm_w), _lib.ptr(conv_state), _lib.ptr(state), _lib.ptr(slots.int()), _lib.ptr(out), batch, hk, hv,
@@ -66,6 +68,9 @@ def paged_attention(q, k_cache, v_cache, block_table, ctx_len, scale: float, nsp
     """q [rows, Hq, D] fp32; caches [blocks, 16, Hkv, D] bf16; block_table [rows, max_blocks] int32; ctx_len [rows] int32."""
     rows, hq, d = q.shape
     hkv = k_cache.shape[2]
+    q = q.contiguous()
+    _lib.expect(torch.float32, q=q)
+    _lib.expect(torch.bfloat16, k_cache=k_cache, v_cache=v_cache)
     if nsplit <= 0:
         nsplit = max(1, min(32, (2 * 148) // max(1, rows * hkv)))
     dev = q.device
@@ -81,6 +86,8 @@ def paged_attention(q, k_cache, v_cache, block_table, ctx_len, scale: float, nsp
 
 def embed_merge(ids: torch.Tensor, table: torch.Tensor, embeds: Optional[torch.Tensor] = None, mask: Optional[torch.Tensor] = None):
     t, (v, h) = ids.shape[0], table.shape
+    _lib.on_device(table)
+    _lib.expect(torch.bfloat16, table=table)
     out = torch.empty(t, h, dtype=torch.float32, device=ids.device)
     m = mask.to(torch.uint8).contiguous() if mask is not None else None
     _lib.check(_lib.lib().pear_embed_merge(_lib.ptr(ids.int().contiguous()), _lib.ptr(table), _lib.ptr(embeds.float().contiguous() if embeds is not None else None),

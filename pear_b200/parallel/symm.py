@@ -38,13 +38,15 @@ class SymmBuffer:
 
 
 class SymmWorld:
-    def __init__(self, group=None, device: Optional[torch.device] = None):
+    def __init__(self, group=None, device: Optional[torch.device] = None, reductions: bool = True):
+        """``reductions=False``: a world that only allocates, signals and pulls (the weight-sync group of one trainer rank and
+        the replica ranks, e.g. 1 + 4) may have any size up to 8; the reduction kernels need a power of two."""
         import torch.distributed._symmetric_memory as symm_mem
 
         self._symm = symm_mem
         self.group = group if group is not None else dist.group.WORLD
         self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
-        if self.world > 8 or self.world & (self.world - 1):
+        if self.world > 8 or (reductions and self.world & (self.world - 1)):
             raise ValueError(f"world size {self.world}: the NVSwitch kernels take a power of two up to 8")
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         self.flags = self.alloc((SLOTS * 8,), torch.int32)

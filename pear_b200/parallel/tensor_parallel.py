@@ -44,41 +44,60 @@ def tp_config(cfg: HybridConfig, world: int) -> HybridConfig:
                                intermediate_size=cfg.intermediate_size // world)
 
 
-def _rows(t: torch.Tensor, rank: int, world: int) -> torch.Tensor:
-    n = t.shape[0] // world
-    return t[rank * n:(rank + 1) * n]
-
-
-def _cols(t: torch.Tensor, rank: int, world: int) -> torch.Tensor:
-    n = t.shape[1] // world
-    return t[:, rank * n:(rank + 1) * n]
-
-
-def _sections(t: torch.Tensor, sizes: list[int], rank: int, world: int) -> torch.Tensor:
-    """Row-shard a tensor whose rows are consecutive sections (q | k | v): each section is cut separately."""
-    out, o = [], 0
-    for s in sizes:
-        out.append(_rows(t[o:o + s], rank, world))
-        o += s
-    return torch.cat(out, dim=0)
+def shard_pieces(name: str, shape: tuple, cfg: HybridConfig, rank: int, world: int) -> list[tuple[int, int, int, int]]:
+    """Which blocks of a full tensor one tensor-parallel rank holds, in the order they are stacked along dim 0 of its shard:
+    ``(row0, rows, col0, cols)`` of the tensor seen as a matrix ``[shape[0], prod(shape[1:])]``. Replicated tensors are one
+    block. The weight-sync receiver pulls exactly these blocks; ``shard_state`` cuts them out of a full state dict."""
+    rows = int(shape[0]) if len(shape) else 1
+    cols = 1
+    for d in shape[1:]:
+        cols *= int(d)
+    if world == 1:
+        return [(0, rows, 0, cols)]
+    kd, vd = cfg.gdn_key_dim, cfg.gdn_value_dim
+    _, kv_share = kv_heads_per_rank(cfg, world)
+    leaf = name.rsplit(".", 2)[-2] if name.endswith(".weight") else name.rsplit(".", 1)[-1]
+    if leaf in ("k_proj", "v_proj") and kv_share > 1:
+        head = rank // kv_share              # replicated KV head: every rank of the group takes the same rows
+        return [(head * cfg.head_dim, cfg.head_dim, 0, cols)]
+    if leaf in ("q_proj", "k_proj", "v_proj", "gate_proj", "up_proj", "in_proj_z", "in_proj_b", "in_proj_a", "A_log", "dt_bias"):
+        n = rows // world                    # q_proj rows are per head [q | gate]: head-major, so a plain row cut
+        return [(rank * n, n, 0, cols)]
+    if leaf in ("o_proj", "out_proj", "down_proj"):
+        n = cols // world
+        return [(0, rows, rank * n, n)]
+    if leaf in ("in_proj_qkv", "conv1d"):    # rows are consecutive sections (q | k | v): each section is cut separately
+        out, o = [], 0
+        for sec in (kd, kd, vd):
+            n = sec // world
+            out.append((o + rank * n, n, 0, cols))
+            o += sec
+        return out
+    return [(0, rows, 0, cols)]
 
 
 def shard_state(state: dict[str, torch.Tensor], cfg: HybridConfig, rank: int, world: int) -> dict[str, torch.Tensor]:
-    kd, vd = cfg.gdn_key_dim, cfg.gdn_value_dim
-    _, kv_share = kv_heads_per_rank(cfg, world)
     out: dict[str, torch.Tensor] = {}
     for name, t in state.items():
-        leaf = name.rsplit(".", 2)[-2] if name.endswith(".weight") else name.rsplit(".", 1)[-1]
-        if leaf in ("k_proj", "v_proj") and kv_share > 1:
-            head = rank // kv_share              # replicated KV head: every rank of the group takes the same rows
-            t = t[head * cfg.head_dim:(head + 1) * cfg.head_dim]
-        elif leaf in ("q_proj", "k_proj", "v_proj", "gate_proj", "up_proj", "in_proj_z", "in_proj_b", "in_proj_a"):
-            t = _rows(t, rank, world)          # q_proj rows are per head [q | gate]: head-major, so a plain row cut
-        elif leaf in ("o_proj", "out_proj", "down_proj"):
-            t = _cols(t, rank, world)
-        elif leaf in ("in_proj_qkv", "conv1d"):
-            t = _sections(t, [kd, kd, vd], rank, world)
-        elif leaf in ("A_log", "dt_bias"):
-            t = _rows(t, rank, world)
-        out[name] = t.contiguous()
+        pieces = shard_pieces(name, tuple(t.shape), cfg, rank, world)
+        m = t.reshape(t.shape[0], -1) if t.dim() >= 1 else t.reshape(1, 1)
+        cut = torch.cat([m[r0:r0 + r, c0:c0 + c] for r0, r, c0, c in pieces], dim=0) if len(pieces) > 1 else \
+            m[pieces[0][0]:pieces[0][0] + pieces[0][1], pieces[0][2]:pieces[0][2] + pieces[0][3]]
+        out[name] = cut.reshape(shard_shape(tuple(t.shape), pieces)).contiguous()
     return out
+
+
+def shard_shape(shape: tuple, pieces: list[tuple[int, int, int, int]]) -> tuple:
+    """Shape of the shard that ``pieces`` of a tensor of ``shape`` stack up to."""
+    if not shape:
+        return ()
+    rows = sum(p[1] for p in pieces)
+    if len(shape) == 1:
+        return (rows,)
+    full_cols = 1
+    for d in shape[1:]:
+        full_cols *= int(d)
+    if pieces[0][3] == full_cols:
+        return (rows, *shape[1:])
+    assert len(shape) == 2, "a column cut of a tensor with more than two dimensions"
+    return (rows, pieces[0][3])

@@ -488,6 +488,7 @@ class FastDecoder:
             self._step()
 
     def _step(self) -> None:
+        _lib.on_device(self.h)  # a thread on another current device would launch the step's kernels on the wrong GPU
         if not self.use_graph:
             self._launch_step()
         elif self.graph is not None:

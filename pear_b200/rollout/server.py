@@ -46,6 +46,12 @@ class RolloutServer:
                 f.set_result(r)
 
     def _loop(self) -> None:
+        # A new host thread starts on device 0: the kernel library launches on the thread's CURRENT device and stream, so a
+        # replica on another GPU must select it here (torch's own ops switch devices per tensor and would hide the mistake:
+        # the library's kernels would run on GPU 0 against the other GPU's memory).
+        dev = next(self.engine.model.parameters()).device
+        if dev.type == "cuda":
+            torch.cuda.set_device(dev)
         while not self.stop_flag:
             try:
                 with self.lock:
@@ -203,11 +209,18 @@ def load_rollout_model(path: str, dtype: torch.dtype = torch.bfloat16, device: s
         model = HybridForCausalLM(cfg, with_mtp=False)
         model_io.load_model_dir(path, model)
     if device != "cpu":
-        model = model.to(device)
-        for name, p in model.named_parameters():
-            if p.dim() >= 2 and "conv1d" not in name:
-                p.data = p.data.to(dtype)
+        to_rollout_dtypes(model.to(device), dtype)
     return model.eval()
+
+
+def to_rollout_dtypes(model, dtype: torch.dtype = torch.bfloat16):
+    """The element types the rollout kernels read: matrices (embedding, projections, head) in ``dtype``; norm weights, the
+    short conv, ``A_log`` and ``dt_bias`` stay fp32 (a model cast as a whole with ``.to(bfloat16)`` is refused by the kernel
+    wrappers)."""
+    for name, p in model.named_parameters():
+        if p.dim() >= 2 and "conv1d" not in name:
+            p.data = p.data.to(dtype)
+    return model
 
 
 def main(argv=None) -> int:

@@ -102,6 +102,79 @@ def main() -> int:
     if rank == 0:
         print("PASS pull_quantize_nvfp4", flush=True)
 
+    # ---- weight sync over NVSwitch: rank 0 stages buckets, every other rank pulls only its tensor-parallel shard
+    from pear_b200.loop.weight_sync import SymmTransport, SyncConfig, WeightSync
+    from pear_b200.models import hybrid as _hy
+    from pear_b200.models.config import HybridConfig as _HC
+    from pear_b200.parallel.tensor_parallel import shard_state as _shard_state
+
+    wcfg = _HC(vocab_size=1024, hidden_size=512, num_layers=4, num_attention_heads=4, num_kv_heads=2, head_dim=256, gdn_qk_heads=2,
+               gdn_v_heads=4, gdn_head_dim=128, intermediate_size=1024, num_mtp_layers=0)
+    full_state = {k: v.cuda() for k, v in _hy.HybridForCausalLM(wcfg, with_mtp=False).init_weights(3).state_dict().items()}
+    scfg = SyncConfig(bucket_megabytes=4, rollout_dtype=torch.bfloat16, fp32_modules=("norm",))
+    for tp_world, nvfp4_mode in ((1, False), (2, False), (1, True)):
+        tp_rank = 1 if tp_world == 2 else 0  # every receiver plays the same tensor-parallel rank: the check is per receiver
+        tr = SymmTransport(sw, 0, wcfg, tp_rank=tp_rank, tp_world=tp_world, bucket_megabytes=4, nvfp4=nvfp4_mode)
+        if rank == 0:
+            stats = WeightSync(scfg, tr).sync(full_state, version=7)
+            assert stats["weight_sync/buckets"] >= 2
+        else:
+            got, last = {}, False
+            while not last:
+                part, version, last = tr.receive()
+                got.update(part)
+            torch.cuda.synchronize()
+            assert version == 7
+            from pear_b200.loop.weight_sync import cast_for_rollout
+
+            want = _shard_state({k: cast_for_rollout(k, v, scfg) for k, v in full_state.items()}, wcfg, tp_rank, tp_world)
+            assert set(got) == set(want)
+            quantised = 0
+            for k, v in want.items():
+                if isinstance(got[k], tuple):  # NVFP4 on receipt: equal to the torch quantiser on the bf16 weights
+                    packed, gs = got[k]
+                    ref_packed, ref_gs = nvfp4.quantize_packed(v.float())
+                    assert gs == ref_gs and torch.equal(packed.cpu(), ref_packed.cpu()), k
+                    quantised += 1
+                else:
+                    assert got[k].dtype == v.dtype and torch.equal(got[k], v), k
+            assert (quantised > 0) == nvfp4_mode
+            whole = sum(v.numel() * cast_for_rollout(k, v, scfg).element_size() for k, v in full_state.items())
+            if tp_world == 2:  # a shard's worth of bytes crossed NVLink, not the model
+                assert tr.bytes_pulled < 0.7 * whole, (tr.bytes_pulled, whole)
+        sw.device_barrier()
+        sw.check()
+    if rank == 0:
+        print("PASS weight_sync_symm", flush=True)
+
+    # ---- the same transport in front of a real replica: WeightSync on the trainer rank, receive_all + RolloutServer on the others
+    from pear_b200.loop.weight_sync import receive_all
+    from pear_b200.rollout.engine import EngineConfig as _EC, SamplingParams as _SP
+    from pear_b200.rollout.server import build_server, to_rollout_dtypes
+
+    tr = SymmTransport(sw, 0, wcfg, bucket_megabytes=4)
+    new_state = {k: (v * 0.5 if v.dim() >= 2 else v) for k, v in full_state.items()}
+    if rank == 0:
+        WeightSync(scfg, tr).sync(new_state, version=8)
+    else:
+        rm = _hy.HybridForCausalLM(wcfg, with_mtp=False)
+        rm.load_state_dict({k: v.cpu() for k, v in full_state.items()})
+        srv = build_server(to_rollout_dtypes(rm.cuda()), _EC(num_blocks=64, max_num_seqs=2), device="cuda", name=f"replica-{rank}")
+        try:
+            before = srv.generate(list(range(1, 12)), _SP(max_tokens=3, temperature=0.0)).output
+            assert receive_all(tr, srv) == 8 and srv.engine.policy_version == 8
+            got_state = srv.engine.model.state_dict()
+            for k, v in new_state.items():
+                assert torch.equal(got_state[k].float(), cast_for_rollout(k, v, scfg).float().to(got_state[k].dtype).float()), k
+            after = srv.generate(list(range(1, 12)), _SP(max_tokens=3, temperature=0.0)).output
+            assert len(before) == 3 and len(after) == 3
+        finally:
+            srv.close()
+    sw.device_barrier()
+    sw.check()
+    if rank == 0:
+        print("PASS weight_sync_server", flush=True)
+
     # ---- vocab-parallel logits all-gather by P2P stores
     Tl, Vs = 8, 4096
     shards = torch.randn(world, Tl, Vs, device="cuda", generator=g)

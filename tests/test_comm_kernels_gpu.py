@@ -22,7 +22,7 @@ def test_fused_collective_kernels_two_ranks():
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=540)
     out = r.stdout + r.stderr
     assert r.returncode == 0, out[-4000:]
-    for name in ("all_reduce_add_rmsnorm", "ag_gemm", "gemm_rs", "pull_quantize_nvfp4", "all_gather_logits", "sharded_argmax", "gemm_a2a", "a2a_gemm", "reduce_scatter_adamw", "tp_rollout_fused"):
+    for name in ("all_reduce_add_rmsnorm", "ag_gemm", "gemm_rs", "pull_quantize_nvfp4", "weight_sync_symm", "weight_sync_server", "all_gather_logits", "sharded_argmax", "gemm_a2a", "a2a_gemm", "reduce_scatter_adamw", "tp_rollout_fused"):
         assert f"PASS {name}" in out, out[-4000:]
 
 
