@@ -4,6 +4,10 @@
 // other accumulator with tcgen05.ld and write C, so the epilogue of tile i overlaps the main loop of tile i+1.
 // (The building block of the fused paths; upstream calls cuBLAS/cuBLASLt here: pear/models/qwen3_5/trainer/operands.py:204,
 // rollout/blackwell/csrc/gemm_lt.cpp.) No cluster multicast anywhere: operands come through plain per-CTA TMA loads.
+// Operand forms: each operand is either K-major (a row-major [rows, K] matrix: the forward's X and W) or MN-major (a
+// row-major [K, rows] matrix, the reduction running over its ROWS: what the backward products dX = dY W and dW = dY^T X
+// read). A K-major tile is [rows][64 k] (128-byte rows); an MN-major tile is one panel of [64 k][64 rows] per 64 output
+// rows (the same 128-byte-swizzled TMA box, the tensor core told through its descriptors to read it transposed).
 #include "common.cuh"
 
 #include <cudaTypedefs.h>
@@ -19,7 +23,19 @@ struct GemmSmem {
   uint32_t tmem_base;
 };
 
-template <int BN, bool OUT_BF16>
+// MN-major operand tile with the 128-byte swizzle: rows of 128 bytes along MN (64 bf16), 8 K rows per 1024-byte atom;
+// `lbo` = bytes between 64-element MN groups, 8-row K groups are 1024 bytes apart.
+__device__ __forceinline__ uint64_t gemm_desc_mn_sw128(uint32_t smem_addr, uint32_t lbo) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)(lbo >> 4) << 16;
+  d |= (uint64_t)(1024u >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+template <int BN, bool OUT_BF16, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, void* __restrict__ c,
                  int M, int N, int K, int ldc, int* status) {
@@ -69,8 +85,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           if (!ok) break;
           uint8_t* a = tiles + st * kStageBytes;
           mbar_expect_tx(&sm->full[st], kStageBytes);
-          tma_load_2d(a, &map_a, kb * kBK, m0, &sm->full[st]);
-          tma_load_2d(a + kABytes, &map_b, kb * kBK, n0, &sm->full[st]);
+          if (A_MN) {
+#pragma unroll
+            for (int p = 0; p < kBM / 64; ++p) tma_load_2d(a + p * 8192, &map_a, m0 + p * 64, kb * kBK, &sm->full[st]);
+          } else {
+            tma_load_2d(a, &map_a, kb * kBK, m0, &sm->full[st]);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int p = 0; p < BN / 64; ++p) tma_load_2d(a + kABytes + p * 8192, &map_b, n0 + p * 64, kb * kBK, &sm->full[st]);
+          } else {
+            tma_load_2d(a + kABytes, &map_b, kb * kBK, n0, &sm->full[st]);
+          }
           if (++st == kStages) { st = 0; ph ^= 1; }
         }
       }
@@ -78,7 +104,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   } else if (warp == 1) {
     // ------------------------------------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_f16(kBM, BN, 1);
+      constexpr uint32_t idesc = umma_idesc_f16(kBM, BN, 1) | (A_MN ? (1u << 15) : 0u) | (B_MN ? (1u << 16) : 0u);
       int st = 0, ph = 0, it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++it) {
@@ -92,10 +118,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           if (!ok) break;
           tcgen05_fence_after();
           const uint32_t a_addr = smem_u32(tiles + st * kStageBytes);
-          const uint64_t da = umma_desc_sw128(a_addr), db = umma_desc_sw128(a_addr + kABytes);
 #pragma unroll
-          for (int k = 0; k < kBK / 16; ++k)
-            umma_f16(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) != 0 ? 1u : 0u);
+          for (int k = 0; k < kBK / 16; ++k) {
+            // a K step of 16: 32 bytes along a K-major row, 16 rows (2048 bytes) down an MN-major panel
+            const uint64_t da = A_MN ? gemm_desc_mn_sw128(a_addr + k * 2048, 8192) : umma_desc_sw128(a_addr) + (uint64_t)(k * 2);
+            const uint64_t db = B_MN ? gemm_desc_mn_sw128(a_addr + kABytes + k * 2048, 8192) : umma_desc_sw128(a_addr + kABytes) + (uint64_t)(k * 2);
+            umma_f16(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
           tcgen05_commit(&sm->empty[st]);  // the stage is free once these MMAs have read it
           if (++st == kStages) { st = 0; ph ^= 1; }
         }
@@ -193,18 +222,32 @@ static int make_map_bf16(CUtensorMap* map, const void* base, int rows, int cols,
   return r == CUDA_SUCCESS ? 0 : 1000 + (int)r;
 }
 
-template <int BN, bool OUT_BF16>
+// The same matrix read MN-major: a row-major [k_rows, mn_cols] matrix, box = [64 k rows, 64 mn columns].
+static int make_map_bf16_mn(CUtensorMap* map, const void* base, int k_rows, int mn_cols, int ld) {
+  auto enc = get_encode();
+  if (!enc) return (int)cudaErrorNotSupported;
+  cuuint64_t dims[2] = {(cuuint64_t)mn_cols, (cuuint64_t)k_rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {64u, (cuuint32_t)kBK};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : 1000 + (int)r;
+}
+
+template <int BN, bool OUT_BF16, bool A_MN, bool B_MN>
 static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, void* c, int M, int N, int K, int ldc, int* status,
                        int num_sms, cudaStream_t stream) {
   constexpr int smem = kStages * (kBM * kBK * 2 + BN * kBK * 2) + 1024;
   static bool configured = false;
   if (!configured) {
-    PEAR_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_kernel<BN, OUT_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    PEAR_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_kernel<BN, OUT_BF16, A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured = true;
   }
   const int ntiles = ((M + kBM - 1) / kBM) * ((N + BN - 1) / BN);
   const int grid = ntiles < num_sms ? ntiles : num_sms;
-  gemm_bf16_kernel<BN, OUT_BF16><<<grid, kGemmThreads, smem, stream>>>(ma, mb, c, M, N, K, ldc, status);
+  gemm_bf16_kernel<BN, OUT_BF16, A_MN, B_MN><<<grid, kGemmThreads, smem, stream>>>(ma, mb, c, M, N, K, ldc, status);
   PEAR_LAUNCH_CHECK();
   return 0;
 }
@@ -226,8 +269,32 @@ PEAR_API int pear_gemm_bf16_nt(const void* a, const void* b, void* c, int M, int
   r = make_map_bf16(&mb, b, N, K, ldb, wide ? 256 : 128);
   if (r) return r;
   cudaStream_t s = (cudaStream_t)stream;
-  if (wide) return out_bf16 ? launch_gemm<256, true>(ma, mb, c, M, N, K, ldc, status, num_sms, s)
-                            : launch_gemm<256, false>(ma, mb, c, M, N, K, ldc, status, num_sms, s);
-  return out_bf16 ? launch_gemm<128, true>(ma, mb, c, M, N, K, ldc, status, num_sms, s)
-                  : launch_gemm<128, false>(ma, mb, c, M, N, K, ldc, status, num_sms, s);
+  if (wide) return out_bf16 ? launch_gemm<256, true, false, false>(ma, mb, c, M, N, K, ldc, status, num_sms, s)
+                            : launch_gemm<256, false, false, false>(ma, mb, c, M, N, K, ldc, status, num_sms, s);
+  return out_bf16 ? launch_gemm<128, true, false, false>(ma, mb, c, M, N, K, ldc, status, num_sms, s)
+                  : launch_gemm<128, false, false, false>(ma, mb, c, M, N, K, ldc, status, num_sms, s);
+}
+
+// The backward products of a linear layer Y = X W^T on the same kernel (upstream leaves them to cuBLAS):
+//   a_mn = 0, b_mn = 1:  C[M,N] = A[M,K] * B[K,N]      (dX = dY W: a = dY [M, K], b = W stored row-major [K, N])
+//   a_mn = 1, b_mn = 1:  C[M,N] = A[K,M]^T * B[K,N]    (dW = dY^T X: a = dY stored [K, M], b = X stored [K, N])
+// lda / ldb are the row strides of the matrices as stored. Same alignment rules as pear_gemm_bf16_nt.
+PEAR_API int pear_gemm_bf16_form(const void* a, const void* b, void* c, int M, int N, int K, int lda, int ldb, int ldc, int a_mn, int b_mn,
+                                 int out_bf16, int* status, int num_sms, void* stream) {
+  using namespace pear;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda % 8) || (ldb % 8) || ((uintptr_t)a % 16) || ((uintptr_t)b % 16) || !b_mn) return (int)cudaErrorInvalidValue;
+  const bool wide = N > 128;
+  CUtensorMap ma, mb;
+  int r = a_mn ? make_map_bf16_mn(&ma, a, K, M, lda) : make_map_bf16(&ma, a, M, K, lda, kBM);
+  if (r) return r;
+  r = make_map_bf16_mn(&mb, b, K, N, ldb);
+  if (r) return r;
+  cudaStream_t s = (cudaStream_t)stream;
+#define PEAR_FORM(BN_, OUT_)                                                                                              \
+  (a_mn ? launch_gemm<BN_, OUT_, true, true>(ma, mb, c, M, N, K, ldc, status, num_sms, s)                                 \
+        : launch_gemm<BN_, OUT_, false, true>(ma, mb, c, M, N, K, ldc, status, num_sms, s))
+  if (wide) return out_bf16 ? PEAR_FORM(256, true) : PEAR_FORM(256, false);
+  return out_bf16 ? PEAR_FORM(128, true) : PEAR_FORM(128, false);
+#undef PEAR_FORM
 }

@@ -1,8 +1,8 @@
 """bf16 GEMM bindings: ``C = A @ B^T`` on the tcgen05/TMEM/TMA kernel (``csrc/gemm_tcgen05.cu``).
 
 ``linear_bf16`` is the forward of every bf16 linear layer of the trainer model; its backward (dX = dY @ W,
-dW = dY^T @ X) is a plain library GEMM (cuBLAS through torch), which needs the MN-major operand forms the kernel does
-not take.
+dW = dY^T @ X) runs on the same kernel's MN-major operand forms (``gemm_nn``, ``gemm_tn``): no library GEMM in a linear
+layer's forward or backward.
 """
 
 from __future__ import annotations
@@ -40,6 +40,44 @@ def gemm_nt(a: torch.Tensor, b: torch.Tensor, out_dtype=torch.float32, out: torc
     status, sms = _dev_state(a.device)
     check(lib().pear_gemm_bf16_nt(ptr(a), ptr(b), ptr(c), m, n, k, a.stride(0), b.stride(0), c.stride(0),
                                   1 if c.dtype == torch.bfloat16 else 0, ptr(status), sms, stream()), "gemm_bf16_nt")
+    count_launch()
+    return c
+
+
+def _aligned(t: torch.Tensor) -> torch.Tensor:
+    return t if (t.stride(1) == 1 and t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0) else t.contiguous()
+
+
+def gemm_nn(a: torch.Tensor, b: torch.Tensor, out_dtype=torch.float32) -> torch.Tensor:
+    """``a`` [M, K] @ ``b`` [K, N], both row-major bf16 (``b`` is read MN-major: no transpose is materialised). The input
+    gradient of a linear layer: dX = dY @ W."""
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.shape[1] == b.shape[0]
+    a, b = _aligned(a), _aligned(b)
+    m, k = a.shape
+    n = b.shape[1]
+    if k % 8 or n % 8:
+        return (a.float() @ b.float()).to(out_dtype)
+    c = torch.empty(m, n, dtype=out_dtype, device=a.device)
+    status, sms = _dev_state(a.device)
+    check(lib().pear_gemm_bf16_form(ptr(a), ptr(b), ptr(c), m, n, k, a.stride(0), b.stride(0), c.stride(0), 0, 1,
+                                    1 if c.dtype == torch.bfloat16 else 0, ptr(status), sms, stream()), "gemm_bf16_nn")
+    count_launch()
+    return c
+
+
+def gemm_tn(a: torch.Tensor, b: torch.Tensor, out_dtype=torch.float32) -> torch.Tensor:
+    """``a`` [K, M]^T @ ``b`` [K, N], both row-major bf16 and both read MN-major. The weight gradient of a linear layer:
+    dW = dY^T @ X (the reduction runs over the tokens)."""
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.shape[0] == b.shape[0]
+    a, b = _aligned(a), _aligned(b)
+    k, m = a.shape
+    n = b.shape[1]
+    if m % 8 or n % 8:
+        return (a.float().t() @ b.float()).to(out_dtype)
+    c = torch.empty(m, n, dtype=out_dtype, device=a.device)
+    status, sms = _dev_state(a.device)
+    check(lib().pear_gemm_bf16_form(ptr(a), ptr(b), ptr(c), m, n, k, a.stride(0), b.stride(0), c.stride(0), 1, 1,
+                                    1 if c.dtype == torch.bfloat16 else 0, ptr(status), sms, stream()), "gemm_bf16_tn")
     count_launch()
     return c
 
@@ -88,10 +126,12 @@ class _LinearBF16(torch.autograd.Function):
         x2, weight = ctx.saved_tensors
         dy2 = dy.reshape(-1, dy.shape[-1]).to(torch.bfloat16)
         dx = dw = None
+        # both products on the own kernel's MN-major operand forms (fp32 accumulation and fp32 results: the weight gradient
+        # is accumulated over micro-batches in fp32)
         if ctx.needs_input_grad[0]:
-            dx = (dy2 @ weight).to(ctx.in_dtype).view(ctx.shape)
+            dx = gemm_nn(dy2, weight, torch.float32).to(ctx.in_dtype).view(ctx.shape)
         if ctx.needs_input_grad[1]:
-            dw = (dy2.t() @ x2).to(weight.dtype)
+            dw = gemm_tn(dy2, x2, torch.float32).to(weight.dtype)
         return dx, dw, None
 
 

@@ -87,14 +87,44 @@ def test_gemm_tcgen05(m, n, k, out_dtype):
     assert err <= tol, f"max err {err} tol {tol}"
 
 
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (304, 520, 200), (4096, 5120, 5120), (80, 104, 136), (1024, 128, 776)])
+def test_gemm_backward_forms(m, n, k):
+    """The MN-major operand forms against the fp32 statement: C = A[M,K] B[K,N] (dX = dY W) and C = A[K,M]^T B[K,N] (dW = dY^T X),
+    ragged M, N and K (the reduction's tail rows come from the TMA's zero fill)."""
+    from pear_b200.ops import gemm, lib as kl
+
+    torch.manual_seed(5)
+    a = (torch.randn(m, k, device="cuda") * 0.5).bfloat16()
+    b = (torch.randn(k, n, device="cuda") * 0.5).bfloat16()
+    before = kl.LAUNCH_COUNT
+    c = gemm.gemm_nn(a, b)
+    at = a.t().contiguous()  # stored [K, M]
+    c2 = gemm.gemm_tn(at, b)
+    torch.cuda.synchronize()
+    assert gemm.gemm_status() == 0 and kl.LAUNCH_COUNT == before + 2  # the kernel ran both, not the fallback
+    refc = a.float() @ b.float()
+    tol = 2e-5 * refc.abs().max().item() + 1e-4
+    assert (c - refc).abs().max().item() <= tol
+    assert (c2 - refc).abs().max().item() <= tol
+    # operands that are column slices of wider matrices (row stride != width)
+    wide = (torch.randn(k, n + 64, device="cuda") * 0.5).bfloat16()
+    c3 = gemm.gemm_nn(a, wide[:, 32:32 + n] if n % 8 == 0 and 32 * 2 % 16 == 0 else wide[:, :n])
+    ref3 = a.float() @ (wide[:, 32:32 + n] if n % 8 == 0 else wide[:, :n]).float()
+    assert (c3 - ref3).abs().max().item() <= 2e-5 * ref3.abs().max().item() + 1e-4
+
+
 def test_linear_bf16_autograd():
     from pear_b200.ops import gemm
 
     torch.manual_seed(4)
     x = torch.randn(200, 512, device="cuda", requires_grad=True)
     w = (torch.randn(768, 512, device="cuda") * 0.05).bfloat16().requires_grad_(True)
+    from pear_b200.ops import lib as kl
+
+    before = kl.LAUNCH_COUNT
     y = gemm.linear_bf16(x, w)
     y.square().sum().backward()
+    assert kl.LAUNCH_COUNT == before + 3  # forward, input gradient and weight gradient: three launches of the own kernel
     xr = x.detach().clone().requires_grad_(True)
     wr = w.detach().float().requires_grad_(True)
     yr = xr.bfloat16().float() @ wr.t()
