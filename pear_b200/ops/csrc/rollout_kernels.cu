@@ -454,6 +454,65 @@ PEAR_API int pear_paged_attention(const float* q, const void* kc, const void* vc
   return 0;
 }
 
+// ------------------------------------------------------------------------------------------------ exact-max top-p
+// Nucleus mask of one row per CTA: softmax of logits * inv_temp shifted by the row's EXACT maximum, then bisection on the
+// probability threshold (the smallest kept probability): `iters` passes over the row, no sort, tokens tied with the pivot
+// all kept; tokens outside the nucleus are set to -inf in place. The row (1 MB at 248 320 tokens) stays in L2 between
+// the passes. (Upstream: pear/rollout/top_p.py:11-268 — vLLM's pivot search with the shift changed to the exact maximum.)
+constexpr int kTopPThreads = 1024;
+__device__ __forceinline__ float topp_block_sum(float v, float* red) {
+  v = warp_sum(v);
+  __syncthreads();  // `red` of the previous reduction has been read
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float t = 0.f;
+#pragma unroll
+  for (int i = 0; i < kTopPThreads / 32; ++i) t += red[i];
+  return t;
+}
+__global__ void __launch_bounds__(kTopPThreads) top_p_mask_kernel(float* __restrict__ logits, long long ld, int V, float inv_temp,
+                                                                  const float* __restrict__ top_p, int iters) {
+  __shared__ float red[kTopPThreads / 32];
+  float* x = logits + (long long)blockIdx.x * ld;
+  const float p = top_p[blockIdx.x];
+  if (!(p < 1.f)) return;  // the whole CTA
+  float m = -INFINITY;
+  for (int i = threadIdx.x; i < V; i += kTopPThreads) m = fmaxf(m, x[i]);
+  m = warp_max(m);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+  __syncthreads();
+  m = red[0];
+#pragma unroll
+  for (int i = 1; i < kTopPThreads / 32; ++i) m = fmaxf(m, red[i]);
+  float s = 0.f;
+  for (int i = threadIdx.x; i < V; i += kTopPThreads) s += __expf((x[i] - m) * inv_temp);
+  s = topp_block_sum(s, red);
+  const float inv_s = 1.f / s;
+  float lo = 0.f, hi = inv_s;  // the largest probability is exp(0) / s
+  for (int it = 0; it < iters; ++it) {
+    const float mid = 0.5f * (lo + hi);
+    float mass = 0.f;
+    for (int i = threadIdx.x; i < V; i += kTopPThreads) {
+      const float q = __expf((x[i] - m) * inv_temp) * inv_s;
+      mass += q >= mid ? q : 0.f;
+    }
+    mass = topp_block_sum(mass, red);
+    if (mass >= p) lo = mid;  // the threshold can still rise
+    else hi = mid;
+  }
+  for (int i = threadIdx.x; i < V; i += kTopPThreads)
+    if (!(__expf((x[i] - m) * inv_temp) * inv_s >= lo)) x[i] = -INFINITY;
+}
+
+// logits fp32 [rows, ld] (modified in place), top_p fp32 [rows]; rows with top_p >= 1 are left alone.
+PEAR_API int pear_top_p_mask(float* logits, long long ld, int rows, int V, float temperature, const float* top_p, int iters, void* stream) {
+  if (rows <= 0) return 0;
+  if (V <= 0 || temperature <= 0.f || iters < 1) return (int)cudaErrorInvalidValue;
+  top_p_mask_kernel<<<rows, kTopPThreads, 0, (cudaStream_t)stream>>>(logits, ld, V, 1.f / temperature, top_p, iters);
+  PEAR_LAUNCH_CHECK();
+  return 0;
+}
+
 PEAR_API int pear_embed_merge(const int* ids, const void* table, const float* embeds, const unsigned char* mask, float* out, int T, int H, int V,
                               void* stream) {
   embed_merge_kernel<<<T, 256, 0, (cudaStream_t)stream>>>(ids, (const __nv_bfloat16*)table, embeds, mask, out, H, V);

@@ -84,6 +84,21 @@ def paged_attention(q, k_cache, v_cache, block_table, ctx_len, scale: float, nsp
     return out
 
 
+def top_p_mask_(logits: torch.Tensor, top_p: torch.Tensor, temperature: float = 1.0, iters: int = 18) -> torch.Tensor:
+    """In place: every token outside the row's nucleus (smallest set of tokens of softmax(logits / temperature) whose mass
+    reaches ``top_p[row]``; ties with the pivot are kept) becomes -inf. ``logits`` fp32 [rows, V] with unit inner stride."""
+    _lib.on_device(logits)
+    _lib.expect(torch.float32, False, logits=logits)
+    _lib.expect(torch.float32, top_p=top_p)
+    assert logits.dim() == 2 and logits.stride(1) == 1 and top_p.numel() == logits.shape[0]
+    import ctypes
+
+    _lib.check(_lib.lib().pear_top_p_mask(_lib.ptr(logits), ctypes.c_longlong(logits.stride(0)), logits.shape[0], logits.shape[1], _f(temperature),
+                                          _lib.ptr(top_p), iters, _lib.stream()), "top_p_mask")
+    _lib.count_launch(1)
+    return logits
+
+
 def embed_merge(ids: torch.Tensor, table: torch.Tensor, embeds: Optional[torch.Tensor] = None, mask: Optional[torch.Tensor] = None):
     t, (v, h) = ids.shape[0], table.shape
     _lib.on_device(table)

@@ -100,10 +100,11 @@ def _scalar(x) -> Optional[float]:
 
 
 def _fused_sample_cuda(logits, temperature, top_p, top_k, topk_logprobs, generator, noise) -> Optional[SampleOutput]:
-    """Temperature-only rows on a GPU go through the fused CUDA sampler (two launches instead of a dozen torch ops over
-    the vocabulary); anything else (greedy, top-k / top-p, per-row temperatures) takes the general path."""
-    t, tp = _scalar(temperature), _scalar(top_p)
-    if t is None or t <= 0 or tp is None or tp < 1.0 or (top_k and top_k > 0) or topk_logprobs > 32:
+    """Temperature (and top-p) rows on a GPU go through the exact-max top-p kernel and the fused CUDA sampler (two or three
+    launches instead of dozens of torch ops over the vocabulary); anything else (greedy, top-k, per-row temperatures) takes
+    the general path."""
+    t = _scalar(temperature)
+    if t is None or t <= 0 or (top_k and top_k > 0) or topk_logprobs > 32:
         return None
     from ..ops import rollout_ops
 
@@ -113,6 +114,14 @@ def _fused_sample_cuda(logits, temperature, top_p, top_k, topk_logprobs, generat
     x = logits.float()
     if x.stride(1) != 1:
         x = x.contiguous()
+    tp = _scalar(top_p)
+    if tp is None or tp < 1.0:  # nucleus rows: the exact-max top-p kernel masks a private copy, the sampler then renormalises
+        if x.data_ptr() == logits.data_ptr():
+            x = x.clone()
+        tpt = top_p.to(x.device, torch.float32).reshape(-1).contiguous() if torch.is_tensor(top_p) else torch.full((n,), float(tp), device=x.device)
+        if tpt.numel() == 1 and n > 1:
+            tpt = tpt.expand(n).contiguous()
+        rollout_ops.top_p_mask_(x, tpt, t)
     k = max(1, topk_logprobs)
     tok, lp, tid, tlp, rank, nf = rollout_ops.fused_sample(x, t, noise.contiguous(), k)
     return SampleOutput(tok, lp, tid if topk_logprobs > 0 else None, tlp if topk_logprobs > 0 else None, rank, nf)

@@ -140,9 +140,13 @@ def test_rollout_sampler_uses_the_fused_kernel_on_gpu(ops):
     want = sampler.sample(logits.cpu(), 0.8, 1.0, -1, topk_logprobs=8, noise=noise.cpu())
     assert torch.equal(out.tokens.cpu(), want.tokens) and torch.allclose(out.logprobs.cpu(), want.logprobs, atol=1e-3)
     assert torch.equal(out.topk_ids.cpu(), want.topk_ids) and torch.equal(out.ranks.cpu(), want.ranks)
-    # top-p rows take the general path
+    # top-p rows: the nucleus kernel, then the fused sampler
     before = kl.LAUNCH_COUNT
     sampler.sample(logits, 0.8, 0.9, -1, noise=noise)
+    assert kl.LAUNCH_COUNT == before + 3
+    # top-k rows take the general path
+    before = kl.LAUNCH_COUNT
+    sampler.sample(logits, 0.8, 1.0, 5, noise=noise)
     assert kl.LAUNCH_COUNT == before
 
 
@@ -194,3 +198,58 @@ def test_rollout_engine_decodes_through_the_kernels(ops):
         outs[use] = ([r.output for r in reqs], kl.LAUNCH_COUNT - before)
     assert outs[True][0] == outs[False][0]
     assert outs[True][1] > outs[False][1] + 50  # the decode steps launched the attention and GDN kernels
+
+
+def test_exact_max_top_p_kernel(ops):
+    """The nucleus kernel against the definition (sort by probability, keep the shortest prefix whose mass reaches p) and
+    against the bisection statement of rollout/sampler.py, on rows with a dominant token, a flat tail and ties."""
+    import torch
+    from pear_b200.rollout import sampler as S
+
+    torch.manual_seed(0)
+    rows, V, temp = 6, 248320, 0.8
+    logits = torch.randn(rows, V, device="cuda") * 2.0
+    logits[0, 123] = 40.0                      # one token holds (almost) everything: the nucleus is that token
+    logits[1] = 0.0                            # a flat row: every token is tied with the pivot and kept
+    logits[2, :4] = torch.tensor([9.0, 9.0, 9.0, 1.0], device="cuda")  # ties at the pivot
+    top_p = torch.tensor([0.9, 0.5, 0.6, 0.95, 1.0, 0.2], device="cuda")
+    x = logits.clone()
+    ops.top_p_mask_(x, top_p, temp)
+    torch.cuda.synchronize()
+    kept = torch.isfinite(x)
+    assert torch.equal(x[kept], logits[kept])                      # kept tokens are untouched
+    assert kept[4].all()                                           # top_p = 1: the row is left alone
+    assert kept[0].sum() == 1 and kept[0, 123] and kept[1].all()
+    p = torch.softmax(logits.double() / temp, -1)
+    for r in range(rows):
+        if float(top_p[r]) >= 1.0:
+            continue
+        mass = float(p[r][kept[r]].sum())
+        assert mass >= float(top_p[r]) - 1e-6, (r, mass)
+        # minimal up to ties and the bisection's resolution: dropping every token at the smallest kept probability (and the
+        # ones within 2^-18 of the largest probability of it) falls below p
+        pivot = float(p[r][kept[r]].min())
+        res = float(p[r].max()) * 2.0 ** -17
+        assert float(p[r][p[r] > pivot + res].sum()) < float(top_p[r]) + 1e-6, r
+        assert not (p[r][~kept[r]] > pivot + res).any()              # nothing above the pivot was dropped
+    want = S.top_p_mask_exact_max(logits / temp, top_p)
+    differ = (want != kept)
+    # the two bisections add in different orders: they may part on tokens within the last bisection step of the pivot only
+    assert int(differ.sum()) <= 8, int(differ.sum())
+
+
+def test_sampler_with_top_p_runs_the_kernels(ops):
+    import torch
+    from pear_b200.ops import lib as kl
+    from pear_b200.rollout import sampler as S
+
+    torch.manual_seed(1)
+    logits = torch.randn(4, 4096, device="cuda") * 3
+    before = kl.LAUNCH_COUNT
+    out = S.sample(logits, 0.7, 0.3, generator=torch.Generator(device="cuda").manual_seed(5))
+    assert kl.LAUNCH_COUNT > before  # top-p kernel + fused sampler, not the torch statements
+    keep = S.top_p_mask_exact_max(logits / 0.7, torch.full((4,), 0.3, device="cuda"))
+    assert all(bool(keep[i, int(out.tokens[i])]) for i in range(4))  # every sampled token lies inside its row's nucleus
+    lp = torch.log_softmax((logits / 0.7).masked_fill(~keep, float("-inf")), -1)
+    got = out.logprobs.reshape(-1)
+    assert all(abs(float(got[i]) - float(lp[i, int(out.tokens[i])])) < 2e-3 for i in range(4))
