@@ -671,7 +671,7 @@ def main() -> None:
     ap.add_argument("--mk-steps", type=int, default=128)
     ap.add_argument("--mk-prompt-len", type=int, default=4096)
     ap.add_argument("--no-megakernel", action="store_true")
-    ap.add_argument("--ar-mode", default="auto", choices=["auto", "one", "two"], help="form of the fused all-reduce + add + RMSNorm (N > 1)")
+    ap.add_argument("--ar-mode", default="auto", choices=["auto", "one", "two", "nvls"], help="form of the fused all-reduce + add + RMSNorm (N > 1)")
     ap.add_argument("--no-prefix-sharing", action="store_true", help="attention reads the shared prefix pages once per sequence instead of once per group")
     ap.add_argument("--emulate-tp", type=int, default=0, help="profiling aid (one GPU): run ONE rank's share of a tensor-parallel step of this size, "
                     "without the inter-GPU exchange; not a benchmark of anything")

@@ -1157,10 +1157,34 @@ __global__ void __launch_bounds__(1024) ds_ar_add_rmsnorm_kernel(DsPeers partial
 // rank to finish releases a second flag to every peer and waits for theirs, so the kernel ends only when every rank's rows
 // have landed here. `out` (and `residual` when broadcast) are symmetric buffers. (Upstream's four-rank form: rollout/hopper/
 // csrc/ar_norm.cu:138-227, with the multicast store replaced by unicast peer stores.)
+// With multicast addresses of the three symmetric buffers (NVLS: the same offset of every rank's buffer behind one address)
+// the owner of a row gets the sum of all ranks' partial rows from ONE `multimem.ld_reduce` per 16 bytes (the switch adds,
+// fp32 accumulation, bf16 result) instead of one peer load per rank, and sends the normalised row (and the residual) to all
+// ranks with ONE `multimem.st` instead of one peer store per rank. Null addresses: plain peer loads and stores.
+__device__ __forceinline__ void ds_mc_sum_bf16x8(const __nv_bfloat16* mc, float (&acc)[8]) {
+  uint32_t r0, r1, r2, r3;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "l"(mc)
+               : "memory");
+  const uint32_t r[4] = {r0, r1, r2, r3};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 f = __bfloat1622float2(*(const __nv_bfloat162*)&r[j]);
+    acc[2 * j] = f.x; acc[2 * j + 1] = f.y;
+  }
+}
+__device__ __forceinline__ void ds_mc_store16(void* mc, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "f"(__uint_as_float(a)), "f"(__uint_as_float(b)),
+               "f"(__uint_as_float(c)), "f"(__uint_as_float(d))
+               : "memory");
+}
+
 __global__ void __launch_bounds__(1024) ds_ar2_add_rmsnorm_kernel(DsPeers partials, DsPeers flags, DsPeers outs, DsPeers residuals, int rank, int world,
                                                                  int slot, uint32_t* ctr, uint32_t* ticket, int mode, int bcast_residual,
                                                                  const float* __restrict__ weight, int T, int H, size_t buf_elems, int fixed_buf, float eps,
-                                                                 uint32_t budget, int* status) {
+                                                                 uint32_t budget, int* status, const __nv_bfloat16* mc_partials, __nv_bfloat16* mc_outs,
+                                                                 float* mc_residuals) {
   grid_dependency_trigger();
   grid_dependency_wait();
   __shared__ float red[32];
@@ -1190,7 +1214,8 @@ __global__ void __launch_bounds__(1024) ds_ar2_add_rmsnorm_kernel(DsPeers partia
       float ssq = 0.f;
       for (int i = tid * 8; i < H; i += nt * 8) {
         float acc[8];
-        ds_sum_partials(partials, world, boff + (size_t)t * H + i, acc);
+        if (mc_partials) ds_mc_sum_bf16x8(mc_partials + boff + (size_t)t * H + i, acc);
+        else ds_sum_partials(partials, world, boff + (size_t)t * H + i, acc);
         float* res = residual + (size_t)t * H + i;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
@@ -1211,13 +1236,22 @@ __global__ void __launch_bounds__(1024) ds_ar2_add_rmsnorm_kernel(DsPeers partia
         __nv_bfloat162 p2 = __floats2bfloat162_rn(v[4] * rstd * (1.f + weight[i + 4]), v[5] * rstd * (1.f + weight[i + 5]));
         __nv_bfloat162 p3 = __floats2bfloat162_rn(v[6] * rstd * (1.f + weight[i + 6]), v[7] * rstd * (1.f + weight[i + 7]));
         pk.x = *(uint32_t*)&p0; pk.y = *(uint32_t*)&p1; pk.z = *(uint32_t*)&p2; pk.w = *(uint32_t*)&p3;
-        for (int p = 0; p < world; ++p) {
-          const int peer = (rank + p) % world;
-          *(uint4*)((__nv_bfloat16*)outs.p[peer] + (size_t)t * H + i) = pk;
-          if (bcast_residual && peer != rank) {
-            float4* rd = (float4*)((float*)residuals.p[peer] + (size_t)t * H + i);
-            rd[0] = make_float4(v[0], v[1], v[2], v[3]);
-            rd[1] = make_float4(v[4], v[5], v[6], v[7]);
+        if (mc_outs) {
+          ds_mc_store16(mc_outs + (size_t)t * H + i, pk.x, pk.y, pk.z, pk.w);
+          if (bcast_residual) {  // (also rewrites this rank's own copy with the value it already holds)
+            float* rd = mc_residuals + (size_t)t * H + i;
+            ds_mc_store16(rd, __float_as_uint(v[0]), __float_as_uint(v[1]), __float_as_uint(v[2]), __float_as_uint(v[3]));
+            ds_mc_store16(rd + 4, __float_as_uint(v[4]), __float_as_uint(v[5]), __float_as_uint(v[6]), __float_as_uint(v[7]));
+          }
+        } else {
+          for (int p = 0; p < world; ++p) {
+            const int peer = (rank + p) % world;
+            *(uint4*)((__nv_bfloat16*)outs.p[peer] + (size_t)t * H + i) = pk;
+            if (bcast_residual && peer != rank) {
+              float4* rd = (float4*)((float*)residuals.p[peer] + (size_t)t * H + i);
+              rd[0] = make_float4(v[0], v[1], v[2], v[3]);
+              rd[1] = make_float4(v[4], v[5], v[6], v[7]);
+            }
           }
         }
       }
@@ -1449,15 +1483,18 @@ PEAR_API int pear_ds_ar_add_rmsnorm(const void* const* partials, const void* con
 // slots `slot` and `slot + 1`.
 PEAR_API int pear_ds_ar2_add_rmsnorm(const void* const* partials, const void* const* flags, const void* const* outs, const void* const* residuals,
                                      int rank, int world, int slot, unsigned* ctr, unsigned* ticket, int mode, int bcast_residual, const float* weight,
-                                     int T, int H, size_t buf_elems, int fixed_buf, float eps, unsigned budget, int* status, int num_ctas, void* stream) {
+                                     int T, int H, size_t buf_elems, int fixed_buf, float eps, unsigned budget, int* status, int num_ctas,
+                                     const void* mc_partials, void* mc_outs, void* mc_residuals, void* stream) {
   if (world < 1 || world > kDsMaxRanks || (H % 8) != 0 || T <= 0) return (int)cudaErrorInvalidValue;
+  if ((mc_partials != nullptr) != (mc_outs != nullptr) || (mc_outs && bcast_residual && !mc_residuals)) return (int)cudaErrorInvalidValue;
   const int mine = (T - rank + world - 1) / world;  // rows this rank owns
   int grid = mine < num_ctas ? mine : num_ctas;
   if (grid < 1) grid = 1;
   const int threads = ((H / 8 + 31) / 32 * 32) < 1024 ? ((H / 8 + 31) / 32 * 32) : 1024;
   PEAR_CUDA_CHECK(launch_ordinary(ds_ar2_add_rmsnorm_kernel, dim3(grid), dim3(threads), 0, (cudaStream_t)stream, ds_ptrs(partials, world), ds_ptrs(flags, world), ds_ptrs(outs, world),
                                                                     ds_ptrs(residuals, world), rank, world, slot, ctr, ticket, mode, bcast_residual, weight,
-                                                                    T, H, buf_elems, fixed_buf, eps, budget, status));
+                                                                    T, H, buf_elems, fixed_buf, eps, budget, status, (const __nv_bfloat16*)mc_partials,
+                                                                    (__nv_bfloat16*)mc_outs, (float*)mc_residuals));
   PEAR_LAUNCH_CHECK();
   return 0;
 }

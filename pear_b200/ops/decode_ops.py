@@ -248,9 +248,12 @@ def ar_add_rmsnorm(partial_ptrs, flag_ptrs, rank: int, world: int, slot: int, ct
 
 
 def ar2_add_rmsnorm(partial_ptrs, flag_ptrs, out_ptrs, residual_ptrs, rank: int, world: int, slot: int, ctr, ticket, mode: int, bcast_residual: bool,
-                    weight, rows: int, h: int, buf_elems: int, eps: float, budget: int, status, num_ctas: int, fixed_buf: int = -1) -> None:
-    """Two-shot all-reduce + add + RMSNorm over symmetric ``out`` / ``residual`` buffers (row t is reduced by rank t % world)."""
+                    weight, rows: int, h: int, buf_elems: int, eps: float, budget: int, status, num_ctas: int, fixed_buf: int = -1,
+                    mc_partials: int = 0, mc_outs: int = 0, mc_residuals: int = 0) -> None:
+    """Two-shot all-reduce + add + RMSNorm over symmetric ``out`` / ``residual`` buffers (row t is reduced by rank t % world).
+    ``mc_*``: multicast (NVLS) addresses of the same buffers; when given the sum and the broadcast go through the switch."""
     _lib.check(_lib.lib().pear_ds_ar2_add_rmsnorm(partial_ptrs, flag_ptrs, out_ptrs, residual_ptrs, rank, world, slot, _lib.ptr(ctr), _lib.ptr(ticket), mode,
                                                   1 if bcast_residual else 0, _lib.ptr(weight), rows, h, _sz(buf_elems), fixed_buf, _f(eps), _u(budget),
-                                                  _lib.ptr(status), num_ctas, _lib.stream()), "ds_ar2_add_rmsnorm")
+                                                  _lib.ptr(status), num_ctas, ctypes.c_void_p(mc_partials), ctypes.c_void_p(mc_outs),
+                                                  ctypes.c_void_p(mc_residuals), _lib.stream()), "ds_ar2_add_rmsnorm")
     _lib.count_launch()

@@ -65,6 +65,12 @@ class SymmWorld:
         h = self._symm.rendezvous(t, self.group.group_name)
         buf = SymmBuffer(t, [int(p) for p in h.buffer_ptrs])
         buf.handle = h
+        # the NVLS multicast address of the buffer (0 when the platform gives none): `multimem` loads from it return the sum over
+        # all ranks' buffers, stores to it land in all of them
+        try:
+            buf.mc_ptr = int(getattr(h, "multicast_ptr", 0) or 0)
+        except Exception:  # noqa: BLE001
+            buf.mc_ptr = 0
         return buf
 
     def device_counter(self, slot: int) -> torch.Tensor:

@@ -74,7 +74,9 @@ class FastDecoder:
         self.temperature, self.seed = float(temperature), int(seed) & 0xFFFFFFFF
         self.use_graph, self.graph, self._warm = use_graph, None, 0
         self.tc_attn = tensor_core_attention
-        self.ar_mode = ar_mode  # "one": one-shot pull, "two": two-shot (reduce-scatter + all-gather), "auto": by rows and ranks
+        # "one": one-shot pull, "two": two-shot (reduce-scatter + all-gather) over peer loads / stores, "nvls": the two-shot form
+        # with the sum and the broadcast done by the switch (multimem), "auto": by rows and ranks
+        self.ar_mode = ar_mode
         if cfg.gdn_head_dim != 128 and cfg.gdn_layers:
             raise ValueError("the GDN verify kernel is built for head dimension 128")
         if model.mtp is None and n_draft > 0:
@@ -154,6 +156,8 @@ class FastDecoder:
         if self.world > 1:
             s = symm
             self.ar_ws = s.alloc((3, M, H), torch.bfloat16)  # two buffers by epoch parity + one the GEMMs write straight into
+            if self.ar_mode == "nvls" and not self.nvls_available():
+                raise RuntimeError("ar_mode 'nvls': the symmetric buffers have no multicast address on this platform")
             self.recs = s.alloc((2 * rec_elems * K.rec_bytes(),), torch.uint8)
             self.keys = s.alloc((2 * key_elems,), torch.int64)
             self.ar_ctr = s.device_counter(SLOT_STEP_AR)  # shared by every decoder on this SymmWorld: one epoch sequence per slot
@@ -369,8 +373,13 @@ class FastDecoder:
 
     def _two_shot(self, rows: int) -> bool:
         if self.ar_mode != "auto":
-            return self.ar_mode == "two"
+            return self.ar_mode in ("two", "nvls")
         return rows * (self.world - 1) >= 256  # rows every rank would pull in the one-shot form
+
+    def nvls_available(self) -> bool:
+        """Multicast addresses exist for every buffer the switch-side reduction touches."""
+        bufs = [self.ar_ws, self.h_sym, self.x_sym] + ([self.r_sym] if getattr(self, "r_sym", None) is not None else [])
+        return self.world > 1 and all(getattr(b, "mc_ptr", 0) for b in bufs)
 
     def _reduce_norm(self, parts, ns, residual, weight, out, rows, eps, mode=0, bcast=False):
         """residual (+)= sum over splits and ranks of the partial rows; out = RMSNorm(residual). Under the two-shot form a
@@ -383,9 +392,10 @@ class FastDecoder:
             K.reduce_parts_bf16(parts, ns, self.ar_ws.tensor, rows, self.H, buf, self.ar_ctr)
         if self._two_shot(rows):
             res_sym = self.x_sym if residual is self.x_res else self.r_sym
+            mc = (self.ar_ws.mc_ptr, self.h_sym.mc_ptr, res_sym.mc_ptr) if self.ar_mode == "nvls" else (0, 0, 0)
             K.ar2_add_rmsnorm(self.ar_ws.c_ptrs, self.symm.flags.c_ptrs, self.h_sym.c_ptrs, res_sym.c_ptrs, self.rank, self.world, SLOT_STEP_AR,
                               self.ar_ctr, self.ar_ticket, mode, bcast, weight, rows, self.H, buf, eps, 1 << 22, self.status, 2 * self.sms,
-                              fixed_buf=2 if ns < 0 else -1)
+                              fixed_buf=2 if ns < 0 else -1, mc_partials=mc[0], mc_outs=mc[1], mc_residuals=mc[2])
             return
         K.ar_add_rmsnorm(self.ar_ws.c_ptrs, self.symm.flags.c_ptrs, self.rank, self.world, SLOT_STEP_AR, self.ar_ctr, self.ar_ticket, residual, mode,
                          weight, out, rows, self.H, buf, eps, 1 << 22, self.status, 2 * self.sms)

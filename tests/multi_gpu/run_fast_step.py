@@ -76,7 +76,12 @@ def main() -> int:
     B, n_draft, pages = 3, 3, 64
     Vs = cfg.vocab_size // world
     tp = None
-    for ar_mode in ("one", "two"):  # one-shot pull and two-shot (reduce-scatter + all-gather) forms of the fused reduction
+    modes = ["one", "two"]  # one-shot pull and two-shot (reduce-scatter + all-gather) forms of the fused reduction
+    if getattr(sw.alloc((64,), torch.float32), "mc_ptr", 0) and os.environ.get("PEAR_TEST_NVLS", "1") != "0":
+        modes.append("nvls")  # the two-shot form with the sum and the broadcast done by the switch (multimem)
+    elif rank == 0:
+        print("note: no multicast address on this platform: the nvls reduction is not exercised", flush=True)
+    for ar_mode in modes:
         one = build(cfg, state, 0, 1, None, B, n_draft, pages, seed=5)
         tp = build(cfg, state, rank, world, sw, B, n_draft, pages, seed=5, ar_mode=ar_mode)
         steps, T = 6, 1 + n_draft
