@@ -77,6 +77,7 @@ class FastDecoder:
         # "one": one-shot pull, "two": two-shot (reduce-scatter + all-gather) over peer loads / stores, "nvls": the two-shot form
         # with the sum and the broadcast done by the switch (multimem), "auto": by rows and ranks
         self.ar_mode = ar_mode
+        self.nvls_auto = False
         if cfg.gdn_head_dim != 128 and cfg.gdn_layers:
             raise ValueError("the GDN verify kernel is built for head dimension 128")
         if model.mtp is None and n_draft > 0:
@@ -158,6 +159,9 @@ class FastDecoder:
             self.ar_ws = s.alloc((3, M, H), torch.bfloat16)  # two buffers by epoch parity + one the GEMMs write straight into
             if self.ar_mode == "nvls" and not self.nvls_available():
                 raise RuntimeError("ar_mode 'nvls': the symmetric buffers have no multicast address on this platform")
+            # measured at 128 rows per step: switch-side sum and broadcast 24.7 ms against 25.1 ms per step at 8 ranks, no
+            # difference at 4, slightly behind at 2 (the two flag exchanges of a reduction, not its bytes, are most of its cost)
+            self.nvls_auto = self.ar_mode == "auto" and self.world >= 8 and self.nvls_available()
             self.recs = s.alloc((2 * rec_elems * K.rec_bytes(),), torch.uint8)
             self.keys = s.alloc((2 * key_elems,), torch.int64)
             self.ar_ctr = s.device_counter(SLOT_STEP_AR)  # shared by every decoder on this SymmWorld: one epoch sequence per slot
@@ -392,7 +396,7 @@ class FastDecoder:
             K.reduce_parts_bf16(parts, ns, self.ar_ws.tensor, rows, self.H, buf, self.ar_ctr)
         if self._two_shot(rows):
             res_sym = self.x_sym if residual is self.x_res else self.r_sym
-            mc = (self.ar_ws.mc_ptr, self.h_sym.mc_ptr, res_sym.mc_ptr) if self.ar_mode == "nvls" else (0, 0, 0)
+            mc = (self.ar_ws.mc_ptr, self.h_sym.mc_ptr, res_sym.mc_ptr) if (self.ar_mode == "nvls" or self.nvls_auto) else (0, 0, 0)
             K.ar2_add_rmsnorm(self.ar_ws.c_ptrs, self.symm.flags.c_ptrs, self.h_sym.c_ptrs, res_sym.c_ptrs, self.rank, self.world, SLOT_STEP_AR,
                               self.ar_ctr, self.ar_ticket, mode, bcast, weight, rows, self.H, buf, eps, 1 << 22, self.status, 2 * self.sms,
                               fixed_buf=2 if ns < 0 else -1, mc_partials=mc[0], mc_outs=mc[1], mc_residuals=mc[2])
