@@ -394,8 +394,10 @@ def build_rollout(args, rank: int, world: int, symm):
     return full, cfg, model, dec, tables, dict(B=B, T=T, pages=pages, per_seq=per_seq)
 
 
-def rollout_bytes(full, cfg, world: int, B: int, T: int, ctx: int, prefix: int, drafts: int) -> dict:
-    """Algorithmic traffic and work of one step on one rank."""
+def rollout_bytes(full, cfg, world: int, B: int, T: int, ctx: int, prefix: int, drafts: int, reduction: str = "one") -> dict:
+    """Algorithmic traffic and work of one step on one rank. ``reduction``: the form of the fused all-reduce, which sets the
+    bytes that enter a GPU over NVLink per reduced row of H bf16 values: one-shot pull (W - 1) rows, two-shot
+    2 (W - 1) / W (its share of the partial rows in, everyone else's results in), switch-side (nvls) 1 / W + (W - 1) / W."""
     h, V = full.hidden_size, full.vocab_size
     n_attn, n_gdn = len(cfg.attention_layers), len(cfg.gdn_layers)
     attn_w = h * (2 * cfg.q_size + 2 * cfg.kv_size) + cfg.q_size * h
@@ -415,7 +417,8 @@ def rollout_bytes(full, cfg, world: int, B: int, T: int, ctx: int, prefix: int, 
     n_ar = 2 * (n_attn + n_gdn) + 3 + 2 * (drafts - 1)  # reductions over M rows (main + first drafter pass) ...
     nvlink = 0.0
     if world > 1:
-        nvlink = (world - 1) * h * 2.0 * (M * (2 * (n_attn + n_gdn) + 3) + B * 3 * (drafts - 1))
+        per_row = {"one": float(world - 1), "two": 2.0 * (world - 1) / world, "nvls": 1.0}[reduction]
+        nvlink = per_row * h * 2.0 * (M * (2 * (n_attn + n_gdn) + 3) + B * 3 * (drafts - 1))
     return dict(weight_bytes=weights, kv_bytes=float(kv), state_bytes=float(state), flops=flops, nvlink_in_bytes=nvlink, reductions=n_ar)
 
 
@@ -485,7 +488,8 @@ def run_rollout(args, rank, local_rank, world, dist, symm) -> dict:
     hbm, tf = peaks.get("hbm_gbs", 6650.0), peaks.get("bf16_tflops_sustained", 1400.0)
     src = "measured" if peaks else "fallback"
     step_ms = ms / args.steps
-    acct = rollout_bytes(full, cfg, world, B, T, ctx_mid, args.prefix_len, args.drafts)
+    reduction = "one" if (world == 1 or not dec._two_shot(B * T)) else ("nvls" if (dec.ar_mode == "nvls" or dec.nvls_auto) else "two")
+    acct = rollout_bytes(full, cfg, world, B, T, ctx_mid, args.prefix_len, args.drafts, reduction)
     hbm_bytes = acct["weight_bytes"] + acct["kv_bytes"] + acct["state_bytes"]
     t_hbm, t_flop, t_link = hbm_bytes / (hbm * 1e9), acct["flops"] / (tf * 1e12), acct["nvlink_in_bytes"] / 770e9
     bound = max(t_hbm, t_flop, t_link)
@@ -501,6 +505,7 @@ def run_rollout(args, rank, local_rank, world, dist, symm) -> dict:
             "global_batch": B, "seq_len": args.prefix_len + args.suffix_len, "parallelism": f"tp{world}",
             "sequences_per_gpu": args.seqs_per_gpu, "shared_prefix": args.prefix_len, "unique_suffix": args.suffix_len,
             "mean_context": ctx_mid, "draft_tokens": args.drafts, "kv_block": 16, "temperature": 1.0,
+            "reduction": {"one": "one-shot pull", "two": "two-shot (peer loads / stores)", "nvls": "two-shot through the switch (multimem)"}[reduction] if world > 1 else "none",
             "accepted_per_step": round(tokens / max(1, args.steps * B) - 1.0, 4),
             "l2": "inputs larger than L2: every step streams %.1f GB of weights + %.1f GB of KV pages and recurrent state per GPU"
                   % (acct["weight_bytes"] / 1e9, (acct["kv_bytes"] + acct["state_bytes"]) / 1e9),
