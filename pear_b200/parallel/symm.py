@@ -224,8 +224,10 @@ class SymmWorld:
     # -- vocab-parallel logits all-gather -----------------------------------------------------------------------------
     def all_gather_logits(self, shard: torch.Tensor, full: SymmBuffer) -> torch.Tensor:
         """Write this rank's fp32 logits shard [T, V / world] into every rank's ``full`` [T, V]; returns the local full
-        buffer once every rank's shard has landed in it."""
+        buffer once every rank's shard has landed in it. Reuse contract: the call starts with a device barrier, so a rank that
+        is still reading the previous call's ``full`` (its sampler) is never overwritten by a faster peer's next call."""
         t, vs = shard.shape
+        self.device_barrier()
         _lib.check(_lib.lib().pear_logits_allgather(_lib.ptr(shard.contiguous()), full.c_ptrs, self.rank, self.world, t, vs,
                                                      full.tensor.stride(0), _lib.stream()), "logits_allgather")
         _lib.LAUNCH_COUNT += 1
@@ -240,9 +242,11 @@ class SymmWorld:
 
     def sharded_argmax(self, logits_shard: torch.Tensor, xbuf: SymmBuffer) -> tuple[torch.Tensor, torch.Tensor]:
         """Global (token, value) of the row-wise maximum over the vocabulary, each rank holding columns
-        ``[rank * Vs, (rank + 1) * Vs)``; ties go to the lower token id."""
+        ``[rank * Vs, (rank + 1) * Vs)``; ties go to the lower token id. Starts with a device barrier (same reuse contract as
+        :meth:`all_gather_logits`: ``xbuf`` of the previous call may still be read by a slower peer's ``argmax_finish``)."""
         rows, vs = logits_shard.shape
         lib = _lib.lib()
+        self.device_barrier()
         _lib.check(lib.pear_argmax_shard(_lib.ptr(logits_shard), rows, vs, logits_shard.stride(0), self.rank * vs, xbuf.c_ptrs, self.rank,
                                          self.world, _lib.stream()), "argmax_shard")
         e = self.next_epoch(SLOT_ARGMAX)
