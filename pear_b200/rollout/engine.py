@@ -388,6 +388,8 @@ class RolloutEngine:
             row = rows[i]
             if not is_dec:
                 # prefill chunk: rows are committed; the final chunk's last row yields the first sampled token
+                if self.spec > 0:
+                    self._fill_drafter_kv(req, row, x_all[bounds[i] : bounds[i + 1]])
                 if row.need_logits:
                     req.computed += n - 1
                     self._sample_rows(req, logits[lo : lo + 1], resid[lo : lo + 1], [], row)
@@ -586,6 +588,18 @@ class RolloutEngine:
                 self._finish(req, FinishReason.LENGTH)
                 return
         req.drafts = self._draft(req, row, resid, acc, new) if self.spec > 0 else []
+
+    def _fill_drafter_kv(self, req: Request, row: StepRow, x_rows: torch.Tensor) -> None:
+        """The drafter's KV of a prefill chunk: position p of the prompt pairs the main model's residual at p with the
+        embedding of prompt token p + 1, so every chunk row whose next token is part of the prompt goes through one MTP pass
+        (the row of the last prompt token is done by ``_draft`` once its successor has been sampled). Without this the
+        drafter would attend over an empty cache for the whole prompt and propose from the generated tokens alone."""
+        toks = req.tokens
+        m = min(x_rows.shape[0], len(toks) - 1 - row.start)
+        if m <= 0:
+            return
+        nxt = torch.tensor(toks[row.start + 1 : row.start + 1 + m], dtype=torch.long)
+        self.runner.mtp_forward(StepRow(req.seq, nxt, row.start, req.block_table, 0), nxt, x_rows[:m])
 
     def _draft(self, req: Request, row: StepRow, resid: torch.Tensor, acc: int, new: list[int]) -> list[int]:
         """MTP drafts for the next step: first a pass over the rows committed in this step (it fills the drafter's KV

@@ -113,6 +113,34 @@ def test_mtp_speculative_decoding_is_lossless_for_greedy(model):
     assert r.spec_drafted > 0
 
 
+def test_prefill_fills_the_drafter_kv_cache(model):
+    """Every prompt position but the last gets its drafter KV during prefill (the last one when its successor is sampled): the
+    pages of the drafter's layer hold the same keys as a dense MTP pass over the whole prompt."""
+    eng = RolloutEngine(model, EngineConfig(num_blocks=64, block_size=16, num_speculative_tokens=3, max_num_batched_tokens=24))
+    p = list(range(20, 61))  # 41 tokens: two prefill chunks of 24 and 17 rows
+    req = eng.add_request(p, SamplingParams(max_tokens=2, temperature=0.0))
+    while req.finish is None and len(req.output) < 1:
+        eng.step()
+    table = req.block_table
+    mk = eng.runner.mtp_k[0]
+    got = torch.stack([mk[table[i // 16], i % 16] for i in range(len(p))]).float()
+    assert (got.abs().sum(dim=(1, 2)) > 0).all()  # no prompt position was left empty
+    # dense oracle: the MTP layer's keys over the prompt with the sampled token as the last successor
+    from pear_b200.rollout.model_runner import linear_fp32  # noqa: F401  (the same projection helpers as the runner)
+    m, mtp = model, model.mtp
+    toks = torch.tensor(p + req.output[:1])
+    hidden = m(toks[:-1], torch.arange(len(p)), [0, len(p)])
+    x = torch.cat([mtp.pre_fc_norm_embedding(m.model.embed_tokens(toks[1:]).float()), mtp.pre_fc_norm_hidden(hidden)], dim=-1)
+    r = torch.nn.functional.linear(x, mtp.fc.weight.float())
+    attn = mtp.layers[0].self_attn
+    h = mtp.layers[0].input_layernorm(r)
+    cos, sin = m.rope(torch.arange(len(p)))
+    k = attn.k_norm(torch.nn.functional.linear(h, attn.k_proj.weight.float()).view(len(p), -1, m.config.head_dim))
+    from pear_b200.ops import reference as ref
+    k = ref.apply_rope(k, cos, sin)
+    assert torch.allclose(got, k.to(got.dtype).float(), atol=2e-2, rtol=2e-2)
+
+
 def test_lookup_keeps_matched_chain_blocks_out_of_eviction():
     """A prefix whose head sits on the device (oldest LRU entry) and whose tail sits in the host tier: promoting the tail
     needs a device block while the free list is empty, and must not evict (and overwrite) the matched head."""
