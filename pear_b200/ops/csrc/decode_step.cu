@@ -865,6 +865,185 @@ __global__ void __launch_bounds__(256) ds_verify_chunks_kernel(const float* __re
 // (the drafter fills tok_in[b][1..]), ctx += accepted + 1, ncommit = accepted + 1, parity ^= 1, sel_row[b] = the row
 // whose hidden state feeds the drafter, mtp_tok [B][T] = the token after each row (drafter input of its first pass),
 // mtp_ctx [T][B] = the context length of drafter pass k (pass 0 runs over the step's rows, pass k >= 1 over one new row).
+// ------------------------------------------------------------------------------------------------ top-k log-probs
+// The 32 largest scaled logits of every row with their token ids (what score centering reads from the sampler), over a
+// vocabulary that may be sharded: a CTA per (row, chunk of the local shard) selects its chunk's top 32 and stores the list to
+// every rank like the sampler's records; after the flag barrier one CTA per row merges ranks x chunks lists and turns them
+// into log-probs with the row's log-sum-exp from the sampler's own records. Selection: a histogram of (chunk max - z) in
+// 2048 bins of 1/32 finds the bin where the count reaches 32, the elements up to that bin are collected (at most 1024: when
+// more than that lie within 1/32 of the 32nd value the surplus of that bin is cut in arrival order) and sorted in shared
+// memory. (Upstream: rollout/blackwell/csrc/sampler.cu — top-32 log-probs beside the sampled token.)
+constexpr int kTopK = 32, kTopBins = 2048, kTopCand = 1024;
+struct DsTop {
+  float z[kTopK];
+  int id[kTopK];
+};
+__device__ __forceinline__ unsigned long long ds_top_key(float z, int id) {
+  const uint32_t b = __float_as_uint(z);
+  const uint32_t u = (b & 0x80000000u) ? ~b : (b | 0x80000000u);  // order-preserving
+  return ((unsigned long long)u << 32) | (uint32_t)(0x7fffffff - id);  // equal values: the lower id first
+}
+__device__ __forceinline__ void ds_top_unkey(unsigned long long k, float& z, int& id) {
+  const uint32_t u = (uint32_t)(k >> 32);
+  z = __uint_as_float((u & 0x80000000u) ? (u & 0x7fffffffu) : ~u);
+  id = 0x7fffffff - (int)(uint32_t)k;
+}
+// descending bitonic sort of n (a power of two, <= 1024) keys in shared memory by 256 threads
+__device__ __forceinline__ void ds_sort_desc(unsigned long long* a, int n) {
+  for (int k = 2; k <= n; k <<= 1) {
+    for (int j = k >> 1; j > 0; j >>= 1) {
+      for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const int l = i ^ j;
+        if (l > i) {
+          const unsigned long long x = a[i], y = a[l];
+          const bool up = (i & k) != 0;  // ascending block of the bitonic network
+          if (up ? (x > y) : (x < y)) { a[i] = y; a[l] = x; }
+        }
+      }
+      __syncthreads();
+    }
+  }
+}
+__global__ void __launch_bounds__(256) ds_topk_chunks_kernel(const float* __restrict__ logits, int ld, int Vs, int v0, float inv_temp,
+                                                             const int* __restrict__ ctx, int T, int chunks, DsPeers tops, int rank, int world,
+                                                             const uint32_t* __restrict__ epoch_ctr, size_t buf_elems) {
+  grid_dependency_trigger();
+  grid_dependency_wait();
+  __shared__ int hist[kTopBins];
+  __shared__ unsigned long long cand[kTopCand];
+  __shared__ int part[256];
+  __shared__ float red[8];
+  __shared__ int s_bin, s_count;
+  const int chunk = blockIdx.x, row = blockIdx.y, b = row / T, tid = threadIdx.x;
+  if (ctx[b] < 0) return;
+  const int per = (((Vs + chunks - 1) / chunks) + 3) & ~3;
+  const int lo = chunk * per, hi = min(Vs, lo + per);
+  const float* x = logits + (size_t)row * ld;
+  float m = -FLT_MAX;
+  for (int i = lo + tid; i < hi; i += 256) {
+    const float z = x[i] * inv_temp;
+    if (z == z) m = fmaxf(m, z);
+  }
+  m = warp_max(m);
+  if ((tid & 31) == 0) red[tid >> 5] = m;
+  for (int i = tid; i < kTopBins; i += 256) hist[i] = 0;
+  if (tid == 0) { s_count = 0; s_bin = kTopBins - 1; }
+  __syncthreads();
+  float cmax = -FLT_MAX;
+  for (int k = 0; k < 8; ++k) cmax = fmaxf(cmax, red[k]);
+  auto bin_of = [&](float z) {  // (a NaN or infinite distance lands in the last bin)
+    const float d = (cmax - z) * 32.f;
+    return d < (float)(kTopBins - 1) ? max(0, (int)d) : kTopBins - 1;
+  };
+  for (int i = lo + tid; i < hi; i += 256) {
+    const float z = x[i] * inv_temp;
+    if (z == z) atomicAdd(&hist[bin_of(z)], 1);
+  }
+  __syncthreads();
+  int local = 0;
+#pragma unroll
+  for (int k = 0; k < kTopBins / 256; ++k) local += hist[tid * (kTopBins / 256) + k];
+  part[tid] = local;
+  __syncthreads();
+  for (int o = 1; o < 256; o <<= 1) {  // inclusive scan
+    const int v = tid >= o ? part[tid - o] : 0;
+    __syncthreads();
+    part[tid] += v;
+    __syncthreads();
+  }
+  const int need = min(kTopK, part[255]);
+  const int excl = part[tid] - local;
+  if (need > 0 && excl < need && part[tid] >= need) {  // exactly one thread
+    int c = excl;
+    for (int k = 0; k < kTopBins / 256; ++k) {
+      c += hist[tid * (kTopBins / 256) + k];
+      if (c >= need) { s_bin = tid * (kTopBins / 256) + k; break; }
+    }
+  }
+  __syncthreads();
+  const int tb = s_bin;
+  // first everything strictly above the threshold bin (fewer than 32 elements), then the threshold bin itself up to the cap
+  for (int pass = 0; pass < 2; ++pass) {
+    for (int i = lo + tid; i < hi; i += 256) {
+      const float z = x[i] * inv_temp;
+      if (!(z == z)) continue;
+      const int bn = bin_of(z);
+      if (pass == 0 ? bn < tb : bn == tb) {
+        const int pos = atomicAdd(&s_count, 1);
+        if (pos < kTopCand) cand[pos] = ds_top_key(z, v0 + i);
+      }
+    }
+    __syncthreads();
+  }
+  const int n = min(s_count, kTopCand);
+  int n2 = 64;
+  while (n2 < n) n2 <<= 1;
+  for (int i = n + tid; i < n2; i += 256) cand[i] = 0ull;  // below every real key
+  __syncthreads();
+  ds_sort_desc(cand, n2);
+  if (tid < kTopK) {
+    float z = -INFINITY;
+    int id = -1;
+    if (tid < n) ds_top_unkey(cand[tid], z, id);
+    const size_t buf = epoch_ctr ? (size_t)((*epoch_ctr + 1u) & 1u) * buf_elems : 0;
+    const size_t idx = buf + ((size_t)rank * gridDim.y + row) * chunks + chunk;
+    for (int p = 0; p < world; ++p) {
+      DsTop* dst = (DsTop*)tops.p[(rank + p) % world] + idx;
+      dst->z[tid] = z;
+      dst->id[tid] = id;
+    }
+    if (world > 1) __threadfence_system();
+  }
+}
+
+// One CTA per row: merge world x chunks sorted lists, log-probs against the row's log-sum-exp (from the sampler's records).
+__global__ void __launch_bounds__(256) ds_topk_finish_kernel(const DsTop* __restrict__ tops, size_t top_buf_elems, const DsRec* __restrict__ recs,
+                                                             size_t rec_buf_elems, const uint32_t* __restrict__ epoch_ctr, int world, int chunks,
+                                                             int rows, const int* __restrict__ ctx, int T, int* __restrict__ out_id,
+                                                             float* __restrict__ out_lp) {
+  grid_dependency_trigger();
+  grid_dependency_wait();
+  __shared__ unsigned long long keys[kTopCand];
+  __shared__ float s_lse;
+  const int row = blockIdx.x, tid = threadIdx.x;
+  if (ctx[row / T] < 0) return;
+  // (launched after the flag barrier, which has advanced the epoch: the lists and records of this step sit in buffer epoch & 1;
+  // the chunk kernels, launched before it, wrote buffer (epoch + 1) & 1 of the value they saw)
+  const size_t tbuf = epoch_ctr ? (size_t)((*epoch_ctr) & 1u) * top_buf_elems : 0;
+  const size_t rbuf = epoch_ctr ? (size_t)((*epoch_ctr) & 1u) * rec_buf_elems : 0;
+  const int lists = world * chunks, total = lists * kTopK;
+  int n2 = 64;
+  while (n2 < total) n2 <<= 1;
+  for (int i = tid; i < n2; i += 256) {
+    unsigned long long k = 0ull;
+    if (i < total) {
+      const int l = i / kTopK, e = i % kTopK, r = l / chunks, c = l % chunks;
+      const DsTop* t = tops + tbuf + ((size_t)r * rows + row) * chunks + c;
+      if (t->id[e] >= 0) k = ds_top_key(t->z[e], t->id[e]);
+    }
+    keys[i] = k;
+  }
+  if (tid == 0) {
+    float gm = -FLT_MAX;
+    for (int l = 0; l < lists; ++l) gm = fmaxf(gm, recs[rbuf + ((size_t)(l / chunks) * rows + row) * chunks + (l % chunks)].max);
+    float sum = 0.f;
+    for (int l = 0; l < lists; ++l) {
+      const DsRec& r = recs[rbuf + ((size_t)(l / chunks) * rows + row) * chunks + (l % chunks)];
+      sum += r.sumexp * __expf(r.max - gm);
+    }
+    s_lse = gm + __logf(sum);
+  }
+  __syncthreads();
+  ds_sort_desc(keys, n2);
+  if (tid < kTopK) {
+    float z = -INFINITY;
+    int id = -1;
+    if (keys[tid] != 0ull) ds_top_unkey(keys[tid], z, id);
+    out_id[(size_t)row * kTopK + tid] = id;
+    out_lp[(size_t)row * kTopK + tid] = id >= 0 ? z - s_lse : -INFINITY;
+  }
+}
+
 __global__ void ds_verify_finish_kernel(const DsRec* __restrict__ recs, size_t rec_buf_elems, const uint32_t* __restrict__ epoch_ctr, int world,
                                         int chunks, int rows_total, int T, uint32_t seed, uint32_t* __restrict__ step_ctr, int* __restrict__ tok_in,
                                         int* __restrict__ ctx, int* __restrict__ ncommit, int* __restrict__ parity, int* __restrict__ out_tok,
@@ -1398,6 +1577,26 @@ PEAR_API int pear_ds_gdn_verify(const float* proj, int ld, const float* conv_w, 
                                   parity, ncommit, T, Tmax, Hk, Hv, l2_eps, key_blocks, val_blocks));
   PEAR_CUDA_CHECK(launch_dependent(ds_gdn_state_kernel, dim3(Hv, B), dim3(kGdnThreads), smem, s, map_s, proj, ld, norm_w, slots, ctx, ncommit, T, Tmax, Hk,
                                    Hv, rms_eps, (const uint8_t*)key_blocks, (const uint8_t*)val_blocks, (__nv_bfloat16*)out, status));
+  return 0;
+}
+
+PEAR_API int pear_ds_top_bytes() { return (int)sizeof(DsTop); }
+
+// tops: host array of `world` device pointers (each rank's list buffer: 2 x world x rows x chunks lists); null for one rank
+// together with a single local buffer in slot 0.
+PEAR_API int pear_ds_topk_chunks(const float* logits, int ld, int Vs, int v0, float temperature, const int* ctx, int B, int T, int chunks,
+                                 const void* const* tops, int rank, int world, const unsigned* epoch_ctr, size_t buf_elems, void* stream) {
+  if (temperature <= 0.f || chunks < 1 || world < 1 || world > kDsMaxRanks) return (int)cudaErrorInvalidValue;
+  PEAR_CUDA_CHECK(launch_ordinary(ds_topk_chunks_kernel, dim3(chunks, B * T), dim3(256), 0, (cudaStream_t)stream, logits, ld, Vs, v0, 1.f / temperature, ctx,
+                                  T, chunks, ds_ptrs(tops, world), rank, world, epoch_ctr, buf_elems));
+  return 0;
+}
+
+PEAR_API int pear_ds_topk_finish(const void* my_tops, size_t top_buf_elems, const void* my_recs, size_t rec_buf_elems, const unsigned* epoch_ctr,
+                                 int world, int chunks, int B, int T, const int* ctx, int* out_id, float* out_lp, void* stream) {
+  if (world * chunks * kTopK > kTopCand) return (int)cudaErrorInvalidValue;
+  PEAR_CUDA_CHECK(launch_ordinary(ds_topk_finish_kernel, dim3(B * T), dim3(256), 0, (cudaStream_t)stream, (const DsTop*)my_tops, top_buf_elems,
+                                  (const DsRec*)my_recs, rec_buf_elems, epoch_ctr, world, chunks, B * T, ctx, T, out_id, out_lp));
   return 0;
 }
 

@@ -205,6 +205,35 @@ def verify_finish(my_recs, rec_buf_elems: int, epoch_ctr, world: int, chunks: in
     _lib.count_launch(2)
 
 
+TOPK = 32  # log-probs per row the top-k kernels produce
+
+
+def top_bytes() -> int:
+    return int(_lib.lib().pear_ds_top_bytes())
+
+
+def topk_chunks(logits, vs: int, v0: int, temperature: float, ctx, batch: int, t: int, chunks: int, tops_ptrs, rank: int, world: int, epoch_ctr,
+                buf_elems: int) -> None:
+    """Per (row, chunk of this rank's vocabulary shard): the 32 largest scaled logits with their token ids, stored to every
+    rank's list buffer (same slots and epochs as the sampler's records)."""
+    _lib.expect(torch.float32, False, logits=logits)
+    _lib.expect(torch.int32, False, ctx=ctx)
+    _lib.check(_lib.lib().pear_ds_topk_chunks(_lib.ptr(logits), logits.stride(0), vs, v0, _f(temperature), _lib.ptr(ctx), batch, t, chunks, tops_ptrs,
+                                              rank, world, _lib.ptr(epoch_ctr), _sz(buf_elems), _lib.stream()), "ds_topk_chunks")
+    _lib.count_launch()
+
+
+def topk_finish(my_tops, top_buf_elems: int, my_recs, rec_buf_elems: int, epoch_ctr, world: int, chunks: int, batch: int, t: int, ctx, out_id,
+                out_lp) -> None:
+    """Merge the lists of all ranks and chunks into ``out_id`` int32 / ``out_lp`` fp32 [rows, 32] (log-probs of the step's
+    temperature-scaled distribution, descending; -1 / -inf padding)."""
+    _lib.expect(torch.int32, out_id=out_id, ctx=ctx)
+    _lib.expect(torch.float32, out_lp=out_lp)
+    _lib.check(_lib.lib().pear_ds_topk_finish(_lib.ptr(my_tops), _sz(top_buf_elems), _lib.ptr(my_recs), _sz(rec_buf_elems), _lib.ptr(epoch_ctr), world,
+                                              chunks, batch, t, _lib.ptr(ctx), _lib.ptr(out_id), _lib.ptr(out_lp), _lib.stream()), "ds_topk_finish")
+    _lib.count_launch()
+
+
 def mtp_input(tokens, table, hidden, sel, we, wh, rows: int, h: int, eps: float, out) -> None:
     _lib.expect(torch.bfloat16, table=table, out=out)
     _lib.expect(torch.float32, False, hidden=hidden, we=we, wh=wh)

@@ -415,8 +415,8 @@ class RolloutEngine:
         self.symm = symm
 
     def _fast_candidates(self):
-        """Decode-phase requests when ALL of them can take the fast step (one temperature > 0, plain sampling, no top-k
-        log-probs); None when the step has to stay on the packed runner."""
+        """Decode-phase requests when ALL of them can take the fast step (one temperature > 0, plain sampling, at most 32 top
+        log-probs per token); None when the step has to stay on the packed runner."""
         from ..models import hybrid
 
         if not self._fast_ok or (hybrid.tensor_parallel_active() and self.symm is None):
@@ -425,21 +425,21 @@ class RolloutEngine:
         if not reqs:
             return []
         p0 = reqs[0].params
-        if p0.temperature <= 0.0 or any(r.params.temperature != p0.temperature or r.params.top_p < 1.0 or r.params.top_k > 0 or r.params.topk_logprobs > 0
+        if p0.temperature <= 0.0 or any(r.params.temperature != p0.temperature or r.params.top_p < 1.0 or r.params.top_k > 0 or r.params.topk_logprobs > 32
                                         for r in reqs):
             for r in list(self.running):
                 self._fast_release(r)
             return None
         return reqs
 
-    def _fast_init(self, temperature: float) -> None:
+    def _fast_init(self, temperature: float, topk: bool = False) -> None:
         from .fast_step import FastDecoder
 
         cfg, rn = self.cfg, self.runner
         width = cfg.max_blocks_per_seq or cfg.num_blocks
         self.fast = FastDecoder(self.model, rn.k_cache, rn.v_cache, rn.rec_state, rn.mtp_k if rn.has_mtp else [], rn.mtp_v if rn.has_mtp else [],
                                 num_slots=2 * cfg.max_num_seqs + 64, max_batch=cfg.max_num_seqs, n_draft=self.spec, max_blocks_per_seq=width,
-                                temperature=temperature, seed=cfg.seed, symm=self.symm)
+                                temperature=temperature, seed=cfg.seed, symm=self.symm, topk_logprobs=topk)
         self._fast_free = list(range(cfg.max_num_seqs - 1, -1, -1))
 
     def _fast_release(self, req: Request, commit: Optional[int] = None) -> None:
@@ -484,8 +484,14 @@ class RolloutEngine:
         if not reqs:
             return []
         temp = reqs[0].params.temperature
+        want_topk = any(r.params.topk_logprobs > 0 for r in reqs)
+        if self.fast is not None and want_topk and not self.fast.topk:
+            # the decoder was built without the top log-prob kernels (they are part of its captured graph): rebuild it with them
+            for r in list(self.running):
+                self._fast_release(r)
+            self.fast = None
         if self.fast is None:
-            self._fast_init(temp)
+            self._fast_init(temp, topk=want_topk)
         elif self.fast.temperature != temp:
             self.fast.set_temperature(temp)
         fast, T = self.fast, 1 + self.spec
@@ -538,6 +544,9 @@ class RolloutEngine:
                 t = int(res.tokens[b, j])
                 req.output.append(t)
                 req.logprobs.append(float(res.logprobs[b, j]))
+                if p.topk_logprobs > 0:
+                    req.topk_ids.append(res.topk_ids[b, j, : p.topk_logprobs].tolist())
+                    req.topk_logprobs.append(res.topk_logprobs[b, j, : p.topk_logprobs].tolist())
                 self.metrics["generation_tokens"] += 1
                 reason = FinishReason.STOP if t in p.stop_token_ids else (FinishReason.LENGTH if len(req.output) >= p.max_tokens else None)
                 if reason is not None:

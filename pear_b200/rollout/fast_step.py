@@ -40,6 +40,8 @@ class StepResult:
     accepted: torch.Tensor  # [B] int32
     logprobs: torch.Tensor  # [B, T] fp32
     nonfinite: torch.Tensor  # [B] int32
+    topk_ids: Optional[torch.Tensor] = None  # [B, T, 32] int32 when the decoder was built with ``topk_logprobs``
+    topk_logprobs: Optional[torch.Tensor] = None  # [B, T, 32] fp32, descending
 
 
 def _bf16(t: torch.Tensor) -> torch.Tensor:
@@ -61,7 +63,8 @@ class FastDecoder:
 
     def __init__(self, model: HybridForCausalLM, k_cache: dict, v_cache: dict, rec_state: dict, mtp_k: list, mtp_v: list, num_slots: int,
                  max_batch: int, n_draft: int, max_blocks_per_seq: int, temperature: float = 1.0, seed: int = 0, symm=None,
-                 share_weights: bool = True, use_graph: bool = True, tensor_core_attention: Optional[bool] = None, ar_mode: str = "auto"):
+                 share_weights: bool = True, use_graph: bool = True, tensor_core_attention: Optional[bool] = None, ar_mode: str = "auto",
+                 topk_logprobs: bool = False):
         cfg = model.config
         self.model, self.cfg = model, cfg
         dev = next(model.parameters()).device
@@ -78,6 +81,7 @@ class FastDecoder:
         # with the sum and the broadcast done by the switch (multimem), "auto": by rows and ranks
         self.ar_mode = ar_mode
         self.nvls_auto = False
+        self.topk = bool(topk_logprobs)  # every step also produces the 32 largest log-probs of every row (what score centering reads)
         if cfg.gdn_head_dim != 128 and cfg.gdn_layers:
             raise ValueError("the GDN verify kernel is built for head dimension 128")
         if model.mtp is None and n_draft > 0:
@@ -143,6 +147,13 @@ class FastDecoder:
         rec_elems = self.world * M * self.chunks
         key_elems = self.world * B * self.achunks
         self.rec_buf_elems, self.key_buf_elems = rec_elems, key_elems
+        if self.topk:
+            if self.world * self.chunks * K.TOPK > 1024:
+                self.chunks = max(1, 1024 // (self.world * K.TOPK))  # the merge sorts world x chunks lists of 32 in one CTA
+                rec_elems = self.world * M * self.chunks
+                self.rec_buf_elems = rec_elems
+            self.top_ids = torch.zeros(M, K.TOPK, **i32)
+            self.top_lp = torch.zeros(M, K.TOPK, **f32)
         if self.mtp:
             self.xcat = torch.zeros(M, 2 * H, **b16)
             if self.world > 1:
@@ -171,6 +182,10 @@ class FastDecoder:
             self.recs_t, self.keys_t = self.recs.tensor, self.keys.tensor
             self.recs_t.zero_()
             self.keys_t.zero_()
+            if self.topk:
+                self.tops = s.alloc((2 * rec_elems * K.top_bytes(),), torch.uint8)
+                self.tops_ptrs, self.tops_t = self.tops.c_ptrs, self.tops.tensor
+                self.tops_t.zero_()
             torch.cuda.synchronize(dev)
             import torch.distributed as dist
 
@@ -181,6 +196,9 @@ class FastDecoder:
             self.recs_ptrs = K._ptr_array([self.recs_t.data_ptr()])
             self.keys_ptrs = K._ptr_array([self.keys_t.data_ptr()])
             self.ar_ctr = self.sync_ctr = None
+            if self.topk:
+                self.tops_t = torch.zeros(rec_elems * K.top_bytes(), dtype=torch.uint8, device=dev)
+                self.tops_ptrs = K._ptr_array([self.tops_t.data_ptr()])
         # work table of the tensor-core paged attention: per sequence one item over the keys it does not share, per group
         # of sequences with a common prefix a few items over the shared keys (set_shared_prefixes)
         self.pa_items = None
@@ -196,6 +214,9 @@ class FastDecoder:
                 self.set_shared_prefixes([])
         # pinned result record
         self._host = torch.zeros(B * (2 * T + 2), dtype=torch.int32).pin_memory()
+        if self.topk:
+            self._host_top_ids = torch.zeros(M, K.TOPK, dtype=torch.int32).pin_memory()
+            self._host_top_lp = torch.zeros(M, K.TOPK, dtype=torch.float32).pin_memory()
         self._dev_rec = torch.zeros(B * (2 * T + 2), **i32)
         self.steps = 0
         self.debug_logits = None  # tests: a [M, Vs] tensor that receives the verify rows' logits before the drafter reuses the buffer
@@ -453,7 +474,13 @@ class FastDecoder:
         K.stream_gemm(self.h, self.lm_head, self.logits, 1, 0)
         K.verify_chunks(self.logits, self.Vs, self.v0, self.temperature, self.tok_in, self.ctx, B, T, self.chunks, self.seed, self.step_ctr,
                         self.recs_ptrs, self.rank, self.world, self.sync_ctr, self.rec_buf_elems)
+        if self.topk:
+            K.topk_chunks(self.logits, self.Vs, self.v0, self.temperature, self.ctx, B, T, self.chunks, self.tops_ptrs, self.rank, self.world,
+                          self.sync_ctr, self.rec_buf_elems)
         self._sync()
+        if self.topk:  # (before verify_finish: it advances the contexts, inactive slots are told by ctx < 0 either way)
+            K.topk_finish(self.tops_t, self.rec_buf_elems, self.recs_t, self.rec_buf_elems, self.sync_ctr, self.world, self.chunks, B, T, self.ctx,
+                          self.top_ids, self.top_lp)
         K.verify_finish(self.recs_t, self.rec_buf_elems, self.sync_ctr, self.world, self.chunks, B, T, self.seed, self.step_ctr, self.tok_in, self.ctx,
                         self.ncommit, self.parity, self.out_tok, self.out_lp, self.n_accept, self.nonfinite, self.sel_row, self.mtp_tok, self.mtp_ctx)
         if self.debug_logits is not None:
@@ -523,10 +550,17 @@ class FastDecoder:
         """Copy the last step's result record to pinned host memory and wait for it."""
         B, T = self.B, self.T
         self._host.copy_(self._dev_rec, non_blocking=True)
+        if self.topk:
+            self._host_top_ids.copy_(self.top_ids, non_blocking=True)
+            self._host_top_lp.copy_(self.top_lp, non_blocking=True)
         torch.cuda.current_stream().synchronize()
         h = self._host
-        return StepResult(h[: B * T].view(B, T).clone(), h[B * T: B * T + B].clone(), h[B * T + 2 * B:].view(torch.float32).view(B, T).clone(),
-                          h[B * T + B: B * T + 2 * B].clone())
+        res = StepResult(h[: B * T].view(B, T).clone(), h[B * T: B * T + B].clone(), h[B * T + 2 * B:].view(torch.float32).view(B, T).clone(),
+                         h[B * T + B: B * T + 2 * B].clone())
+        if self.topk:
+            res.topk_ids = self._host_top_ids.view(B, T, K.TOPK).clone()
+            res.topk_logprobs = self._host_top_lp.view(B, T, K.TOPK).clone()
+        return res
 
     def check(self) -> None:
         K.check_status(self.dev)

@@ -78,3 +78,38 @@ def test_engine_fast_step_against_oracle(spec):
     reqs3 = eng.generate([follow[1]], SamplingParams(max_tokens=10, temperature=temp, stop_token_ids=(stop_tok,)), sessions=["s1"])
     assert reqs3[0].finish in (FinishReason.STOP, FinishReason.LENGTH)
     assert eng.stats()["num_running"] == 0 and not eng._fast_slot
+
+
+def test_fast_path_returns_top_logprobs():
+    """Requests that ask for top log-probs (what the training recipe's score centering reads) stay on the batched step; the
+    lists agree with the top of log_softmax of the oracle's logits at every generated position."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    from pear_b200.ops import api
+    from pear_b200.rollout.engine import EngineConfig, RolloutEngine, SamplingParams
+
+    cfg, oracle, model = _models()
+    eng = RolloutEngine(model, EngineConfig(num_blocks=128, max_num_seqs=4, num_speculative_tokens=3, seed=3), device="cuda")
+    prompts = [list(range(5, 30)), list(range(40, 52))]
+    temp, k = 0.9, 5
+    outs = eng.generate(prompts, SamplingParams(max_tokens=6, temperature=temp, topk_logprobs=k))
+    assert eng.fast is not None and eng.fast.topk and eng.fast.steps > 0  # the batched step ran and produced the lists
+    prev, api.FORCE_REFERENCE = api.FORCE_REFERENCE, True
+    try:
+        for p, r in zip(prompts, outs):
+            assert len(r.topk_ids) == len(r.output) == 6 and all(len(x) == k for x in r.topk_ids)
+            with torch.no_grad():
+                ids = torch.tensor(p + r.output, device="cuda")
+                lp = torch.log_softmax(oracle.logits(oracle(ids)[len(p) - 1:-1]) / temp, -1)
+            for j in range(6):
+                row = lp[j]
+                got_lp = torch.tensor(r.topk_logprobs[j], device="cuda")
+                got_id = torch.tensor(r.topk_ids[j], device="cuda")
+                assert (got_lp[:-1] >= got_lp[1:]).all() and len(set(r.topk_ids[j])) == k
+                # bf16 activations in the step against the fp32 oracle: values to a bf16-level bound, and every listed token is
+                # within that bound of the oracle's k-th value
+                assert torch.allclose(got_lp, row[got_id], atol=0.15), (j, got_lp, row[got_id])
+                assert float(row[got_id].min()) >= float(row.topk(k).values[-1]) - 0.3
+                assert abs(r.logprobs[j] - float(row[r.output[j]])) < 0.15
+    finally:
+        api.FORCE_REFERENCE = prev

@@ -393,3 +393,63 @@ def test_paged_attention_shared_prefix_items(K):
     torch.cuda.synchronize()
     K.check_status()
     assert (outs[0] - outs[2]).abs().max() < 0.03 and (outs[1] - outs[2]).abs().max() < 0.03
+
+
+def test_topk_logprob_kernels(K):
+    """The 32 largest log-probs per row over two emulated vocabulary shards (two chunk launches into one list buffer) against
+    torch.topk of log_softmax; a row with fewer than 32 finite tokens, a flat row (ties at the threshold) and an empty slot."""
+    import ctypes
+
+    from pear_b200.ops import lib as _lib
+
+    B, T, V, world, chunks, temp = 4, 2, 8192, 2, 2, 0.7
+    g = torch.Generator(device="cuda").manual_seed(31)
+    logits = torch.randn(B * T, V, device="cuda", generator=g) * 3
+    logits[2, 40:] = float("-inf")            # 40 finite tokens
+    logits[3] = 1.5                            # flat: every token ties
+    i32 = dict(dtype=torch.int32, device="cuda")
+    ctx = torch.tensor([10, 20, -1, 40], **i32)  # the third sequence's slot is empty
+    tok_in = torch.zeros(B * T, **i32)
+    step_ctr = torch.zeros(1, **i32)
+    Vs = V // world
+    rows = B * T
+    recs = torch.zeros(world * rows * chunks * K.rec_bytes(), dtype=torch.uint8, device="cuda")
+    tops = torch.zeros(world * rows * chunks * K.top_bytes(), dtype=torch.uint8, device="cuda")
+    for r in range(world):
+        shard = logits[:, r * Vs:(r + 1) * Vs].contiguous()
+        _lib.check(_lib.lib().pear_ds_verify_chunks(_lib.ptr(shard), shard.stride(0), Vs, r * Vs, ctypes.c_float(temp), _lib.ptr(tok_in), _lib.ptr(ctx), B, T,
+                                                    chunks, ctypes.c_uint(1), _lib.ptr(step_ctr), K._ptr_array([recs.data_ptr()] * 2), r, 1,
+                                                    _lib.ptr(None), ctypes.c_size_t(0), _lib.stream()), "chunks")
+        _lib.check(_lib.lib().pear_ds_topk_chunks(_lib.ptr(shard), shard.stride(0), Vs, r * Vs, ctypes.c_float(temp), _lib.ptr(ctx), B, T, chunks,
+                                                  K._ptr_array([tops.data_ptr()] * 2), r, 1, _lib.ptr(None), ctypes.c_size_t(0), _lib.stream()), "topk")
+    out_id = torch.full((rows, 32), -7, **i32)
+    out_lp = torch.zeros(rows, 32, device="cuda")
+    K.topk_finish(tops, 0, recs, 0, None, world, chunks, B, T, ctx, out_id, out_lp)
+    torch.cuda.synchronize()
+    lp = torch.log_softmax(logits.float() / temp, -1)
+    for row in range(rows):
+        if int(ctx[row // T]) < 0:
+            assert (out_id[row] == -7).all()  # untouched
+            continue
+        want_lp, want_id = lp[row].topk(32)
+        if row == 3:  # all equal: any 32 distinct tokens, each at log(1 / V)
+            assert len(set(out_id[row].tolist())) == 32 and (out_id[row] >= 0).all()
+            assert torch.allclose(out_lp[row], want_lp, atol=1e-4)
+            continue
+        n = 32 if row != 2 else 32  # row 2 has 40 finite tokens: still 32 results
+        assert torch.equal(out_id[row, :n].long(), want_id[:n]), row
+        assert torch.allclose(out_lp[row, :n], want_lp[:n], atol=2e-4), row
+    # fewer than 32 finite tokens in the whole row: the rest are tokens at -inf (as torch.topk would list them)
+    logits[0, 5:] = float("-inf")
+    for r in range(world):
+        shard = logits[:, r * Vs:(r + 1) * Vs].contiguous()
+        _lib.check(_lib.lib().pear_ds_verify_chunks(_lib.ptr(shard), shard.stride(0), Vs, r * Vs, ctypes.c_float(temp), _lib.ptr(tok_in), _lib.ptr(ctx), B, T,
+                                                    chunks, ctypes.c_uint(1), _lib.ptr(step_ctr), K._ptr_array([recs.data_ptr()] * 2), r, 1,
+                                                    _lib.ptr(None), ctypes.c_size_t(0), _lib.stream()), "chunks")
+        _lib.check(_lib.lib().pear_ds_topk_chunks(_lib.ptr(shard), shard.stride(0), Vs, r * Vs, ctypes.c_float(temp), _lib.ptr(ctx), B, T, chunks,
+                                                  K._ptr_array([tops.data_ptr()] * 2), r, 1, _lib.ptr(None), ctypes.c_size_t(0), _lib.stream()), "topk")
+    K.topk_finish(tops, 0, recs, 0, None, world, chunks, B, T, ctx, out_id, out_lp)
+    torch.cuda.synchronize()
+    K.check_status()
+    assert out_id[0, :5].tolist() == torch.log_softmax(logits[0] / temp, -1).topk(5).indices.tolist()
+    assert torch.isinf(out_lp[0, 5:]).all() and len(set(out_id[0].tolist())) == 32 and (out_id[0] >= 0).all()
