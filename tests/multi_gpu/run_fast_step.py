@@ -19,7 +19,7 @@ from pear_b200.parallel.tensor_parallel import shard_state, tp_config  # noqa: E
 from pear_b200.rollout.fast_step import FastDecoder  # noqa: E402
 
 
-def build(cfg, full_state, rank, world, symm, B, n_draft, pages, seed, ar_mode="auto"):
+def build(cfg, full_state, rank, world, symm, B, n_draft, pages, seed, ar_mode="auto", topk=False):
     local = tp_config(cfg, world) if world > 1 else cfg
     model = HybridForCausalLM(local)
     model.load_state_dict(shard_state(full_state, cfg, rank, world) if world > 1 else full_state, strict=True)
@@ -49,7 +49,7 @@ def build(cfg, full_state, rank, world, symm, B, n_draft, pages, seed, ar_mode="
     for li in cfg.gdn_layers:
         full_rs = torch.randn(B, hv, 128, 128, device="cuda", generator=g) * 0.05
         rs[li] = full_rs[:, rank * (hv // world):(rank + 1) * (hv // world)].contiguous() if world > 1 else full_rs
-    dec = FastDecoder(model, kc, vc, rs, mk, mv, num_slots=B, max_batch=B, n_draft=n_draft, max_blocks_per_seq=16, temperature=0.8, seed=77, symm=symm, ar_mode=ar_mode)
+    dec = FastDecoder(model, kc, vc, rs, mk, mv, num_slots=B, max_batch=B, n_draft=n_draft, max_blocks_per_seq=16, temperature=0.8, seed=77, symm=symm, ar_mode=ar_mode, topk_logprobs=topk)
     dec.debug_logits = torch.zeros_like(dec.logits)
     kd, vd = cfg.gdn_key_dim, cfg.gdn_value_dim
     for b in range(B):
@@ -82,8 +82,9 @@ def main() -> int:
     elif rank == 0:
         print("note: no multicast address on this platform: the nvls reduction is not exercised", flush=True)
     for ar_mode in modes:
-        one = build(cfg, state, 0, 1, None, B, n_draft, pages, seed=5)
-        tp = build(cfg, state, rank, world, sw, B, n_draft, pages, seed=5, ar_mode=ar_mode)
+        topk = ar_mode == modes[-1]  # the last pass also produces the top-32 log-prob lists (sharded select + merge over ranks)
+        one = build(cfg, state, 0, 1, None, B, n_draft, pages, seed=5, topk=topk)
+        tp = build(cfg, state, rank, world, sw, B, n_draft, pages, seed=5, ar_mode=ar_mode, topk=topk)
         steps, T = 6, 1 + n_draft
         same_hist = torch.ones(B, dtype=torch.bool)  # sequences whose committed tokens agree so far
         compared = 0
@@ -105,6 +106,12 @@ def main() -> int:
                     err, scale = float((got[b * T + t] - want[b * T + t]).abs().max()), float(want[b * T + t].abs().max())
                     assert err < 0.05 * max(1.0, scale), (ar_mode, step, b, t, err, scale)
                     compared += 1
+                    if topk:  # the sharded lists against the single-rank ones: same log-probs up to the staging's rounding, and
+                        # the same leading token unless the two best are closer than that
+                        a_lp, b_lp = r1.topk_logprobs[b, t], r2.topk_logprobs[b, t]
+                        assert torch.allclose(a_lp, b_lp, atol=0.05), (step, b, t, a_lp[:4], b_lp[:4])
+                        assert int(r1.topk_ids[b, t, 0]) == int(r2.topk_ids[b, t, 0]) or float(a_lp[0] - a_lp[1]) < 0.05
+                        assert len(set(r2.topk_ids[b, t].tolist())) == 32
             toks = r2.tokens.cuda()
             gathered = [torch.zeros_like(toks) for _ in range(world)]
             dist.all_gather(gathered, toks)
