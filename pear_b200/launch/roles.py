@@ -13,7 +13,8 @@ import os
 from dataclasses import dataclass, field
 
 
-ROLLOUT_PORT, ENV_PORT = 8100, 8200  # replica i serves on ROLLOUT_PORT + i, environment host j on ENV_PORT + j
+ROLLOUT_PORT, ENV_PORT, SYNC_PORT = 8100, 8200, 29650  # replica i serves on ROLLOUT_PORT + i, environment host j on ENV_PORT + j;
+# the weight-sync world {trainer rank 0} + {replicas} meets on SYNC_PORT
 
 
 @dataclass
@@ -35,9 +36,13 @@ def plan_node(n_gpus: int, trainer_gpus: int, rollout_tp: int, recipe: str, over
     if trainer_gpus > n_gpus or (n_gpus - trainer_gpus) % max(1, rollout_tp):
         raise ValueError(f"{n_gpus} GPUs cannot hold {trainer_gpus} trainer GPUs plus rollout replicas of {rollout_tp}")
     replicas = (n_gpus - trainer_gpus) // max(1, rollout_tp)
+    urls = ",".join(f"http://127.0.0.1:{ROLLOUT_PORT + i}" for i in range(replicas))
+    remote = [f"actor_rollout_ref.rollout.checkpoint_engine.replica_urls=[{urls}]",
+              f"actor_rollout_ref.rollout.checkpoint_engine.sync_master=127.0.0.1:{SYNC_PORT}"] if replicas else []
     return [
-        RolePlan("trainer", trainer_gpus, 1, 0, "pear_b200.train.main", [recipe] + overrides),
-        RolePlan("rollout", replicas, rollout_tp, trainer_gpus, "pear_b200.rollout.server", overrides),
+        RolePlan("trainer", trainer_gpus, 1, 0, "pear_b200.train.main", [recipe] + overrides + remote),
+        RolePlan("rollout", replicas, rollout_tp, trainer_gpus, "pear_b200.rollout.server",
+                 overrides + ["--sync-world", str(replicas + 1), "--sync-master", f"127.0.0.1:{SYNC_PORT}"]),
         RolePlan("env", env_hosts, 0, 0, "pear_b200.sim.server", []),
         RolePlan("monitor", 1, 0, 0, "pear_b200.monitor.progress_panel",
                  overrides + [a for i in range(replicas) for a in ("--replica", f"replica-{i}=http://127.0.0.1:{ROLLOUT_PORT + i}/metrics")]),
@@ -67,7 +72,7 @@ def command(plan: RolePlan, index: int, master_port: int = 29500) -> tuple[list[
     else:
         cmd = ["python", "-m", plan.module] + plan.args
         if plan.role == "rollout":
-            cmd += ["--port", str(ROLLOUT_PORT + index), "--name", f"replica-{index}"]
+            cmd += ["--port", str(ROLLOUT_PORT + index), "--name", f"replica-{index}", "--sync-rank", str(index + 1)]
         elif plan.role == "env":
             cmd += ["--port", str(ENV_PORT + index)]
     return cmd, env

@@ -72,26 +72,87 @@ class InProcessTransport:
                 s._pending = {}
 
 
+class StandaloneGroup:
+    """A process group of its own world, beside whatever ``torch.distributed`` world the process already belongs to: the
+    trainer's rank 0 (member of the training world) and the rollout replicas (each possibly the member of a tensor-parallel
+    world) meet here for weight syncs only. Rank 0 of this group hosts the rendezvous store at ``master`` (``host:port``).
+    Backends: ``gloo`` (host tensors) and ``nccl`` (tensors on ``device``). (Upstream names such a group per sync in its
+    checkpoint engine: pear/rollout/checkpoint_engine.py:15-43.)"""
+
+    def __init__(self, master: str, rank: int, world: int, backend: str = "gloo", device="cpu", timeout_s: float = 1800.0):
+        from datetime import timedelta
+
+        host, port = master.rsplit(":", 1)
+        self.rank, self.world, self.backend, self.device = rank, world, backend, torch.device(device)
+        timeout = timedelta(seconds=timeout_s)
+        self.store = dist.TCPStore(host, int(port), world, is_master=(rank == 0), timeout=timeout)
+        store = dist.PrefixStore("weight_sync", self.store)
+        if backend == "nccl":
+            torch.cuda.set_device(self.device)
+            self.pg = dist.ProcessGroupNCCL(store, rank, world, timeout)
+        elif backend == "gloo":
+            self.pg = dist.ProcessGroupGloo(store, rank, world, timeout)
+        else:
+            raise ValueError(f"unknown backend {backend!r}")
+
+    def broadcast(self, t: torch.Tensor, src: int) -> None:
+        opts = dist.BroadcastOptions()
+        opts.rootRank, opts.rootTensor = src, 0
+        self.pg.broadcast([t], opts).wait()
+        if t.is_cuda:
+            torch.cuda.current_stream(t.device).synchronize()
+
+    def broadcast_object(self, obj, src: int):
+        """Pickled through two broadcasts (length, then bytes); returns the object on every rank."""
+        import pickle
+
+        dev = self.device if self.backend == "nccl" else torch.device("cpu")
+        if self.rank == src:
+            payload = torch.frombuffer(bytearray(pickle.dumps(obj)), dtype=torch.uint8).to(dev)
+            n = torch.tensor([payload.numel()], dtype=torch.int64, device=dev)
+        else:
+            n = torch.zeros(1, dtype=torch.int64, device=dev)
+        self.broadcast(n, src)
+        if self.rank != src:
+            payload = torch.empty(int(n.item()), dtype=torch.uint8, device=dev)
+        self.broadcast(payload, src)
+        return obj if self.rank == src else pickle.loads(payload.cpu().numpy().tobytes())
+
+    def close(self) -> None:
+        self.pg = None
+        self.store = None
+
+
 class BroadcastTransport:
-    """Rank ``src`` of ``group`` owns the weights; every other rank calls ``receive`` with the same manifest."""
+    """Rank ``src`` of ``group`` owns the weights; every other rank calls ``receive`` with the same manifest. ``group`` is a
+    ``torch.distributed`` group (None: the default world) or a :class:`StandaloneGroup`."""
 
     def __init__(self, group=None, src: int = 0, device="cpu"):
         self.group, self.src, self.device = group, src, torch.device(device)
 
+    def _object(self, obj):
+        if isinstance(self.group, StandaloneGroup):
+            return self.group.broadcast_object(obj, self.src)
+        box = [obj]
+        dist.broadcast_object_list(box, src=self.src, group=self.group)
+        return box[0]
+
+    def _tensor(self, t: torch.Tensor) -> None:
+        if isinstance(self.group, StandaloneGroup):
+            self.group.broadcast(t, self.src)
+        else:
+            dist.broadcast(t, src=self.src, group=self.group)
+
     def send(self, bucket: list[tuple[str, torch.Tensor]], version: int, last: bool) -> None:
         manifest = [(n, tuple(t.shape), t.dtype, t.numel() * t.element_size()) for n, t in bucket]
-        obj = [{"manifest": manifest, "version": version, "last": last}]
-        dist.broadcast_object_list(obj, src=self.src, group=self.group)
-        flat = torch.cat([t.detach().contiguous().view(-1).view(torch.uint8).to(self.device) for _, t in bucket])
-        dist.broadcast(flat, src=self.src, group=self.group)
+        self._object({"manifest": manifest, "version": version, "last": last})
+        self._tensor(torch.cat([t.detach().contiguous().view(-1).view(torch.uint8).to(self.device) for _, t in bucket]))
 
     def receive(self) -> tuple[dict[str, torch.Tensor], int, bool]:
-        obj = [None]
-        dist.broadcast_object_list(obj, src=self.src, group=self.group)
-        info = obj[0]
+        info = self._object(None)
         total = sum(m[3] for m in info["manifest"])
         flat = torch.empty(total, dtype=torch.uint8, device=self.device)
-        dist.broadcast(flat, src=self.src, group=self.group)
+        self._tensor(flat)
         out, off = {}, 0
         for name, shape, dtype, nbytes in info["manifest"]:
             out[name] = flat[off:off + nbytes].view(dtype).reshape(shape)
@@ -217,6 +278,8 @@ class WeightSync:
             self.transport.send(b, version, last=(i == len(bl) - 1))
             sent += sum(t.numel() * t.element_size() for _, t in b)
         for s in self.servers:
+            if hasattr(s, "wait_version"):  # a replica in another process loads on a thread of its own
+                s.wait_version(version)
             s.resume()
         self.last_seconds, self.bytes_sent = time.time() - t0, sent
         return {"weight_sync/seconds": self.last_seconds, "weight_sync/bytes": float(sent), "weight_sync/buckets": float(len(bl)),

@@ -35,6 +35,8 @@ class RolloutServer:
         self.stop_flag = False
         self.idle_sleep_s = idle_sleep_s
         self.error: Optional[BaseException] = None
+        self.sync_error: Optional[BaseException] = None  # set by the weight-sync receiver thread of a replica process
+        self.weight_loads = 0
         self.thread = threading.Thread(target=self._loop, daemon=True, name=f"{name}-scheduler")
         self.thread.start()
 
@@ -127,6 +129,7 @@ class RolloutServer:
             cast[name] = t if (keep32 or not t.is_floating_point()) else t.to(self.rollout_dtype)
         with self.lock:
             self.engine.update_weights(cast, version)
+            self.weight_loads += 1
 
     # -- observability ------------------------------------------------------------------------------------------------
     def stats(self) -> dict:
@@ -160,7 +163,8 @@ class RolloutServer:
 
         @app.get("/health")
         def health() -> dict:
-            return {"ok": self.error is None, "paused": self.engine.paused}
+            return {"ok": self.error is None, "paused": self.engine.paused, "policy_version": self.engine.policy_version,
+                    "weight_loads": self.weight_loads}
 
         @app.post("/v1/completions")
         def completions(body: dict) -> dict:
@@ -169,19 +173,30 @@ class RolloutServer:
                 if tokenizer is None:
                     return {"error": "text prompts need a tokenizer"}
                 prompt = tokenizer.encode(body["prompt"])
+            from .remote import decode_embeds
+
             params = SamplingParams(max_tokens=int(body.get("max_tokens", 64)), temperature=float(body.get("temperature", 1.0)),
-                                    top_p=float(body.get("top_p", 1.0)), topk_logprobs=int(body.get("logprobs", 0) or 0))
-            req = self.generate(list(prompt), params, session=body.get("session"))
-            out = {"id": req.request_id, "choices": [{"token_ids": req.output, "logprobs": req.logprobs,
-                                                      "finish_reason": req.finish.value if req.finish else None}],
+                                    top_p=float(body.get("top_p", 1.0)), topk_logprobs=int(body.get("logprobs", 0) or 0),
+                                    stop_token_ids=tuple(int(t) for t in body.get("stop_token_ids", ())))
+            embeds, mask = decode_embeds(body)  # vision placeholder rows of a multi-modal prompt (bf16, base64)
+            req = self.generate(list(prompt), params, session=body.get("session"), embeds=embeds, embeds_mask=mask,
+                                max_resubmits=int(body.get("max_resubmits", 1000)))
+            out = {"id": req.request_id, "policy_version": req.policy_version, "cached_prefix": getattr(req, "cached_prefix", 0),
+                   "choices": [{"token_ids": req.output, "logprobs": req.logprobs, "topk_ids": req.topk_ids, "topk_logprobs": req.topk_logprobs,
+                                "finish_reason": req.finish.value if req.finish else None}],
                    "usage": {"prompt_tokens": len(req.prompt), "completion_tokens": len(req.output)}}
             if tokenizer is not None:
                 out["choices"][0]["text"] = tokenizer.decode(req.output)
             return out
 
         @app.post("/pause")
-        def pause() -> dict:
-            return {"aborted": self.pause(abort=True)}
+        def pause(body: Optional[dict] = None) -> dict:
+            return {"aborted": self.pause(abort=bool((body or {}).get("abort", True)))}
+
+        @app.post("/release_cached_memory")
+        def release() -> dict:
+            self.release_cached_memory()
+            return {"ok": True}
 
         @app.post("/resume")
         def resume() -> dict:
@@ -223,6 +238,42 @@ def to_rollout_dtypes(model, dtype: torch.dtype = torch.bfloat16):
     return model
 
 
+def start_weight_receiver(server: RolloutServer, rank: int, world: int, master: str, src: int = 0, backend: str = "auto", device: str = "cpu"):
+    """Join the weight-sync process group ({sending trainer rank} + {replica ranks}) and load every sync the sender starts, on
+    a thread of its own: each ``WeightSync.sync`` on the trainer side arrives here as buckets until the last one, then the
+    replica loads them, bumps its policy version and clears its KV tiers. Returns the thread."""
+    import threading
+
+    import torch.distributed as dist
+
+    from ..loop.weight_sync import BroadcastTransport, StandaloneGroup, SymmTransport, receive_all
+
+    if backend == "auto":
+        backend = "nccl" if device != "cpu" else "gloo"
+    if backend == "nvswitch":  # symmetric memory rendezvous goes through the default world: this process has no other
+        from ..parallel.symm import SymmWorld
+
+        dist.init_process_group("nccl", init_method=f"tcp://{master}", rank=rank, world_size=world)
+        transport = SymmTransport(SymmWorld(reductions=False), src, server.engine.model.config)
+    else:  # a world of its own, beside a tensor-parallel world the replica may be part of
+        transport = BroadcastTransport(StandaloneGroup(master, rank, world, backend, device), src, device)
+
+    def loop():
+        if device != "cpu":
+            torch.cuda.set_device(next(server.engine.model.parameters()).device)  # a new thread starts on device 0
+        while not server.stop_flag:
+            try:
+                receive_all(transport, server)
+            except Exception as e:  # noqa: BLE001 - the group went away (the trainer exited): stop listening, keep serving
+                if not server.stop_flag:
+                    server.sync_error = e
+                return
+
+    t = threading.Thread(target=loop, daemon=True, name=f"{server.name}-weight-sync")
+    t.start()
+    return t
+
+
 def main(argv=None) -> int:
     """``python -m pear_b200.rollout.server --model preset:tiny --port 8100``: one rollout replica as a process of its own
     (the rollout role of ``launch/roles.py``): builds the model and the engine on this process's GPU (CPU without one) and
@@ -239,6 +290,12 @@ def main(argv=None) -> int:
     ap.add_argument("--max-num-seqs", type=int, default=64)
     ap.add_argument("--speculative-tokens", type=int, default=0)
     ap.add_argument("--check", action="store_true", help="build the replica, answer one request and exit (no HTTP server)")
+    ap.add_argument("--sync-rank", type=int, default=-1, help="this replica's rank in the weight-sync process group (-1: no group)")
+    ap.add_argument("--sync-world", type=int, default=0, help="size of the weight-sync group: the sending trainer rank + the replica ranks")
+    ap.add_argument("--sync-master", default="127.0.0.1:29650", help="host:port of the weight-sync group's rendezvous")
+    ap.add_argument("--sync-src", type=int, default=0, help="rank of the sender in the weight-sync group")
+    ap.add_argument("--sync-backend", default="auto", choices=["auto", "gloo", "nccl", "nvswitch"],
+                    help="nvswitch: pull this replica's shard out of the sender's symmetric staging buffer; gloo / nccl: broadcast")
     args, overrides = ap.parse_known_args(argv)
     kv = dict(o.split("=", 1) for o in overrides if "=" in o and not o.startswith("-"))
     path = args.model or kv.get("actor_rollout_ref.model.path", "preset:tiny")
@@ -247,6 +304,8 @@ def main(argv=None) -> int:
     model = load_rollout_model(path, device=device)
     server = build_server(model, EngineConfig(num_blocks=args.num_blocks, max_num_seqs=max_seqs, num_speculative_tokens=args.speculative_tokens),
                           device=device, name=args.name)
+    if args.sync_rank >= 0:
+        start_weight_receiver(server, args.sync_rank, args.sync_world, args.sync_master, args.sync_src, args.sync_backend, device)
     try:
         if args.check:
             r = server.generate(list(range(1, 20)), SamplingParams(max_tokens=4, temperature=1.0))

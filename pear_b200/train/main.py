@@ -26,7 +26,7 @@ from ..loop.agent_loop import AgentLoopConfig
 from ..loop.dataset import EpisodeDataset
 from ..loop.manager import AgentLoopManager
 from ..loop.transfer_queue import TransferQueue
-from ..loop.weight_sync import InProcessTransport, SyncConfig, WeightSync
+from ..loop.weight_sync import BroadcastTransport, InProcessTransport, StandaloneGroup, SyncConfig, WeightSync
 from ..models.config import HybridConfig
 from ..models.hybrid import HybridForCausalLM
 from ..models import io as model_io
@@ -107,9 +107,21 @@ def build_stack(cfg, replicas: int = 1, device: str = "cpu", env_families: Optio
     ro = cfg.actor_rollout_ref.rollout
     servers, manager = [], None
     tcfg = TrainerConfig.from_config(cfg)
+    ce = ro.checkpoint_engine
+    urls = [str(u) for u in (ce.get("replica_urls", None) or [])]
+    transport = None
     if rank == 0:
         full = engine.full_state_dict(torch.float32)
-        for i in range(replicas):
+        if urls:  # replicas are processes of their own: requests over HTTP, weights through a world shared with them only
+            from ..rollout.remote import RemoteReplica
+
+            backend = "gloo" if device == "cpu" or str(ce.backend) == "gloo" else "nccl"
+            group = StandaloneGroup(str(ce.sync_master), 0, 1 + len(urls), backend, device)
+            transport = BroadcastTransport(group, 0, device if backend == "nccl" else "cpu")
+            servers = [RemoteReplica(u, name=f"replica-{i}") for i, u in enumerate(urls)]
+            for s in servers:
+                s.wait_ready(float(ce.get("ready_timeout_s", 600)))
+        for i in range(0 if urls else replicas):
             rm = HybridForCausalLM(mcfg, with_mtp=bool(cfg.actor_rollout_ref.model.mtp.enable_rollout))
             rm.load_state_dict(full, strict=False)
             rc = RolloutConfig(num_blocks=int(ro.get("num_blocks", 2048)), block_size=int(ro.block_size), max_num_seqs=int(ro.max_num_seqs),
@@ -132,9 +144,10 @@ def build_stack(cfg, replicas: int = 1, device: str = "cpu", env_families: Optio
     files = cfg.data.train_files
     dataset = EpisodeDataset(files if files is not None else {"family": "synthetic", "args": {"task": ["reach"], "seed": list(range(64))}},
                              seed=int(cfg.trainer.seed))
-    ce = ro.checkpoint_engine
     sync = WeightSync(SyncConfig(int(ce.update_weights_bucket_megabytes), getattr(torch, str(ro.dtype)), tuple(ro.fp32_modules)),
-                      InProcessTransport(servers), servers) if rank == 0 else None
+                      transport or InProcessTransport(servers), servers) if rank == 0 else None
+    if sync is not None and urls:  # replica processes built their own weights: start them from the trainer's policy
+        sync.sync(full, engine.policy_version)
     ckpt = CheckpointManager(str(cfg.run_dir), rank, engine.world, cfg.trainer.max_actor_ckpt_to_keep,
                              barrier=(lambda: dist.barrier(world_group)) if engine.world > 1 else None)
     trainer = Trainer(tcfg, engine, dataset, manager, replay, queue, sync, ckpt, MetricsLog(str(cfg.run_dir), tuple(cfg.trainer.logger)))
