@@ -19,28 +19,56 @@ def main(argv=None) -> int:
     ap.add_argument("--trainer-gpus", type=int, default=4)
     ap.add_argument("--rollout-tp", type=int, default=2)
     ap.add_argument("--dry-run", action="store_true")
+    ap.add_argument("--master-port", type=int, default=29500, help="rendezvous of the trainer ranks (replica i of several GPUs uses the next ports)")
+    ap.add_argument("--rollout-port", type=int, default=8100)
+    ap.add_argument("--env-port", type=int, default=8200)
+    ap.add_argument("--sync-port", type=int, default=29650, help="rendezvous of the weight-sync world")
     args, overrides = ap.parse_known_args(argv)
-    plans = plan_node(args.gpus, args.trainer_gpus, args.rollout_tp, args.recipe, overrides)
+    plans = plan_node(args.gpus, args.trainer_gpus, args.rollout_tp, args.recipe, overrides, rollout_port=args.rollout_port,
+                      env_port=args.env_port, sync_port=args.sync_port)
     if args.dry_run:
         out = []
         for p in plans:
             for i in range(1 if p.role == "trainer" else p.processes):
-                cmd, env = command(p, i)
+                cmd, env = command(p, i, args.master_port)
                 out.append({"role": p.role, "index": i, "cmd": cmd, "env": env})
         print(json.dumps(out, indent=1))
         return 0
     raise_fd_limit()
+    import signal
     import subprocess
+    import time
+
+    def on_signal(signum, frame):  # a terminated launcher takes its roles with it (the finally below)
+        raise SystemExit(128 + signum)
+
+    signal.signal(signal.SIGTERM, on_signal)
+    signal.signal(signal.SIGINT, on_signal)
     procs = []
     try:
         for p in plans:
             for i in range(1 if p.role == "trainer" else p.processes):
-                cmd, env = command(p, i)
-                procs.append(subprocess.Popen(cmd, env={**os.environ, **env}))
+                cmd, env = command(p, i, args.master_port)
+                # a session per role: the role's own children (torch.distributed.run workers, environment processes) form one
+                # process group with it, which is what gets signalled at the end
+                procs.append(subprocess.Popen(cmd, env={**os.environ, **env}, start_new_session=True))
         return procs[0].wait()  # the trainer's exit ends the run
     finally:
-        for pr in procs[1:]:
-            pr.terminate()
+        for pr in procs:
+            if pr.poll() is None:
+                try:
+                    os.killpg(pr.pid, signal.SIGTERM)
+                except ProcessLookupError:
+                    pass
+        deadline = time.time() + 20
+        for pr in procs:
+            try:
+                pr.wait(timeout=max(0.1, deadline - time.time()))
+            except subprocess.TimeoutExpired:
+                try:
+                    os.killpg(pr.pid, signal.SIGKILL)
+                except ProcessLookupError:
+                    pass
 
 
 if __name__ == "__main__":

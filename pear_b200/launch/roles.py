@@ -25,27 +25,30 @@ class RolePlan:
     gpu_offset: int = 0
     module: str = ""
     args: list[str] = field(default_factory=list)
+    port: int = 0  # process i of the role listens on port + i
 
     def gpu_ids(self, index: int) -> list[int]:
         lo = self.gpu_offset + index * self.gpus_per_process
         return list(range(lo, lo + self.gpus_per_process))
 
 
-def plan_node(n_gpus: int, trainer_gpus: int, rollout_tp: int, recipe: str, overrides: list[str], env_hosts: int = 1) -> list[RolePlan]:
+def plan_node(n_gpus: int, trainer_gpus: int, rollout_tp: int, recipe: str, overrides: list[str], env_hosts: int = 1,
+              rollout_port: int = ROLLOUT_PORT, env_port: int = ENV_PORT, sync_port: int = SYNC_PORT) -> list[RolePlan]:
     """Split one node: the first ``trainer_gpus`` GPUs train, the rest serve rollouts in groups of ``rollout_tp``."""
     if trainer_gpus > n_gpus or (n_gpus - trainer_gpus) % max(1, rollout_tp):
         raise ValueError(f"{n_gpus} GPUs cannot hold {trainer_gpus} trainer GPUs plus rollout replicas of {rollout_tp}")
     replicas = (n_gpus - trainer_gpus) // max(1, rollout_tp)
-    urls = ",".join(f"http://127.0.0.1:{ROLLOUT_PORT + i}" for i in range(replicas))
+    urls = ",".join(f"http://127.0.0.1:{rollout_port + i}" for i in range(replicas))
     remote = [f"actor_rollout_ref.rollout.checkpoint_engine.replica_urls=[{urls}]",
-              f"actor_rollout_ref.rollout.checkpoint_engine.sync_master=127.0.0.1:{SYNC_PORT}"] if replicas else []
+              f"actor_rollout_ref.rollout.checkpoint_engine.sync_master=127.0.0.1:{sync_port}",
+              f"actor_rollout_ref.rollout.tensor_model_parallel_size={max(1, rollout_tp)}"] if replicas else []
     return [
         RolePlan("trainer", trainer_gpus, 1, 0, "pear_b200.train.main", [recipe] + overrides + remote),
         RolePlan("rollout", replicas, rollout_tp, trainer_gpus, "pear_b200.rollout.server",
-                 overrides + ["--sync-world", str(replicas + 1), "--sync-master", f"127.0.0.1:{SYNC_PORT}"]),
-        RolePlan("env", env_hosts, 0, 0, "pear_b200.sim.server", []),
+                 overrides + ["--sync-world", str(replicas * max(1, rollout_tp) + 1), "--sync-master", f"127.0.0.1:{sync_port}"], rollout_port),
+        RolePlan("env", env_hosts, 0, 0, "pear_b200.sim.server", [], env_port),
         RolePlan("monitor", 1, 0, 0, "pear_b200.monitor.progress_panel",
-                 overrides + [a for i in range(replicas) for a in ("--replica", f"replica-{i}=http://127.0.0.1:{ROLLOUT_PORT + i}/metrics")]),
+                 overrides + [a for i in range(replicas) for a in ("--replica", f"replica-{i}=http://127.0.0.1:{rollout_port + i}/metrics")]),
     ]
 
 
@@ -72,9 +75,13 @@ def command(plan: RolePlan, index: int, master_port: int = 29500) -> tuple[list[
     else:
         cmd = ["python", "-m", plan.module] + plan.args
         if plan.role == "rollout":
-            cmd += ["--port", str(ROLLOUT_PORT + index), "--name", f"replica-{index}", "--sync-rank", str(index + 1)]
+            tp = max(1, plan.gpus_per_process)
+            if tp > 1:  # the replica's ranks are a world of their own: rank 0 serves, the others follow in lock-step
+                cmd = ["python", "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={tp}", "--master-addr", "127.0.0.1",
+                       "--master-port", str(master_port + 1 + index), "-m", plan.module] + plan.args
+            cmd += ["--port", str(plan.port + index), "--name", f"replica-{index}", "--sync-rank", str(1 + index * tp)]
         elif plan.role == "env":
-            cmd += ["--port", str(ENV_PORT + index)]
+            cmd += ["--port", str(plan.port + index)]
     return cmd, env
 
 

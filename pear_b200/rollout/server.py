@@ -297,23 +297,45 @@ def main(argv=None) -> int:
     ap.add_argument("--sync-backend", default="auto", choices=["auto", "gloo", "nccl", "nvswitch"],
                     help="nvswitch: pull this replica's shard out of the sender's symmetric staging buffer; gloo / nccl: broadcast")
     args, overrides = ap.parse_known_args(argv)
+    from ..utils.process import die_with_parent, dump_stacks_on_signal
+
+    die_with_parent()
+    dump_stacks_on_signal()
     kv = dict(o.split("=", 1) for o in overrides if "=" in o and not o.startswith("-"))
     path = args.model or kv.get("actor_rollout_ref.model.path", "preset:tiny")
     max_seqs = int(kv.get("actor_rollout_ref.rollout.max_num_seqs", args.max_num_seqs))
+    import os
+
     device = "cuda" if torch.cuda.is_available() else "cpu"
-    model = load_rollout_model(path, device=device)
-    server = build_server(model, EngineConfig(num_blocks=args.num_blocks, max_num_seqs=max_seqs, num_speculative_tokens=args.speculative_tokens),
-                          device=device, name=args.name)
-    if args.sync_rank >= 0:
-        start_weight_receiver(server, args.sync_rank, args.sync_world, args.sync_master, args.sync_src, args.sync_backend, device)
+    ecfg = EngineConfig(num_blocks=args.num_blocks, max_num_seqs=max_seqs, num_speculative_tokens=args.speculative_tokens)
+    tp_rank, tp_world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    if tp_world > 1:  # one rank of a tensor-parallel replica (started under torch.distributed.run): lock-step with its peers
+        import torch.distributed as dist
+
+        from .lockstep import build_tp_replica
+
+        dist.init_process_group("nccl" if device == "cuda" else "gloo")
+        server = build_tp_replica(path, ecfg, name=args.name)
+        device = str(server.engine.device)
+        if args.sync_backend == "nvswitch":
+            raise SystemExit("--sync-backend nvswitch needs the default process group, which a tensor-parallel replica uses for its own ranks: use nccl")
+    else:
+        model = load_rollout_model(path, device=device)
+        server = build_server(model, ecfg, device=device, name=args.name)
+    if args.sync_rank >= 0:  # a tensor-parallel replica's ranks are consecutive in the weight-sync world
+        start_weight_receiver(server, args.sync_rank + tp_rank, args.sync_world, args.sync_master, args.sync_src, args.sync_backend, device)
     try:
+        if tp_world > 1 and tp_rank != 0:  # followers mirror the leader until its stop message
+            server.thread.join()
+            return 0 if server.error is None else 1
         if args.check:
             r = server.generate(list(range(1, 20)), SamplingParams(max_tokens=4, temperature=1.0))
             print(f"{args.name}: {len(r.output)} tokens on {device}, finish {r.finish.value}")
             return 0
         import uvicorn
 
-        uvicorn.run(server.http_app(), host=args.host, port=args.port, log_level="warning")
+        # a request that can no longer finish (a peer rank is gone) must not keep a terminated replica alive
+        uvicorn.run(server.http_app(), host=args.host, port=args.port, log_level="warning", timeout_graceful_shutdown=3)
         return 0
     finally:
         server.close()

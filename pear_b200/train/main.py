@@ -116,7 +116,8 @@ def build_stack(cfg, replicas: int = 1, device: str = "cpu", env_families: Optio
             from ..rollout.remote import RemoteReplica
 
             backend = "gloo" if device == "cpu" or str(ce.backend) == "gloo" else "nccl"
-            group = StandaloneGroup(str(ce.sync_master), 0, 1 + len(urls), backend, device)
+            # every rank of a tensor-parallel replica receives for itself: the world is this rank plus all of theirs
+            group = StandaloneGroup(str(ce.sync_master), 0, 1 + len(urls) * max(1, int(ro.tensor_model_parallel_size)), backend, device)
             transport = BroadcastTransport(group, 0, device if backend == "nccl" else "cpu")
             servers = [RemoteReplica(u, name=f"replica-{i}") for i, u in enumerate(urls)]
             for s in servers:
@@ -164,6 +165,9 @@ def build_stack(cfg, replicas: int = 1, device: str = "cpu", env_families: Optio
 
 def main(argv: Optional[list[str]] = None) -> int:
     argv = list(sys.argv[1:] if argv is None else argv)
+    from ..utils.process import dump_stacks_on_signal
+
+    dump_stacks_on_signal()
     recipe = argv.pop(0) if argv and "=" not in argv[0] else "training"
     cfg = RunConfig(compose(recipe, argv)).prepare()
     world_group = None

@@ -28,9 +28,19 @@ def die_with_parent(sig: int = signal.SIGTERM) -> None:
         pass
 
 
+def dump_stacks_on_signal(sig: int = signal.SIGUSR1) -> None:
+    """``kill -USR1 <pid>`` prints every thread's Python stack to stderr: the first question about a role process that
+    stopped making progress is where it waits."""
+    import faulthandler
+
+    try:
+        faulthandler.register(sig, all_threads=True, chain=False)
+    except (AttributeError, ValueError, OSError):  # not on this platform / not on the main thread
+        pass
+
+
 def _child(target, args, kwargs):
     die_with_parent()
-    os.setsid() if False else None
     target(*args, **kwargs)
 
 

@@ -42,8 +42,43 @@ def test_node_plan_and_commands():
     assert by["trainer"].processes == 4 and by["rollout"].processes == 2 and by["rollout"].gpu_ids(1) == [6, 7]
     cmd, env = command(by["trainer"], 0, master_port=1234)
     assert "--nproc-per-node=4" in cmd and "127.0.0.1" in cmd and env["CUDA_VISIBLE_DEVICES"] == "0,1,2,3"
-    cmd, env = command(by["rollout"], 0)
-    assert cmd[:3] == ["python", "-m", "pear_b200.rollout.server"] and env["CUDA_VISIBLE_DEVICES"] == "4,5"
+    # a replica of two GPUs is a world of two ranks under torch.distributed.run; its ranks are consecutive in the weight-sync
+    # world (rank 0 = the sending trainer rank), whose size and rendezvous the trainer gets as config keys
+    cmd, env = command(by["rollout"], 1)
+    assert cmd[:3] == ["python", "-m", "torch.distributed.run"] and "--nproc-per-node=2" in cmd and env["CUDA_VISIBLE_DEVICES"] == "6,7"
+    assert cmd[cmd.index("-m", 3) + 1] == "pear_b200.rollout.server" and cmd[cmd.index("--sync-rank") + 1] == "3" and cmd[cmd.index("--sync-world") + 1] == "5"
+    assert any(a.startswith("actor_rollout_ref.rollout.checkpoint_engine.replica_urls=[http://127.0.0.1:8100,http://127.0.0.1:8101]") for a in by["trainer"].args)
+    single = {p.role: p for p in plan_node(8, 4, 1, "training", [])}["rollout"]
+    cmd, env = command(single, 2)
+    assert cmd[:3] == ["python", "-m", "pear_b200.rollout.server"] and env["CUDA_VISIBLE_DEVICES"] == "6" and cmd[cmd.index("--sync-rank") + 1] == "3"
     assert gpu_process_env([3])["NCCL_LAUNCH_ORDER_IMPLICIT"] == "1"
     with pytest.raises(ValueError):
         plan_node(8, 5, 2, "training", [])
+
+
+@pytest.mark.timeout(600)
+def test_roles_recipe_runs_as_processes(tmp_path):
+    """The recipe that starts every role as a process (two trainer ranks, one replica of two lock-step ranks, environment
+    host, monitor) trains one step on CPU; the launcher leaves no role behind when the trainer exits."""
+    import json
+    import os
+    import socket
+    import subprocess
+
+    def free_port() -> int:
+        with socket.socket() as s:
+            s.bind(("127.0.0.1", 0))
+            return s.getsockname()[1]
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    run = str(tmp_path / "run")
+    env = dict(os.environ, PYTHONPATH=root, RUN=run, STEPS="1", PORT=str(free_port()), ROLLOUT_PORT=str(free_port()), ENV_PORT=str(free_port()),
+               SYNC_PORT=str(free_port()), OMP_NUM_THREADS="2")
+    proc = subprocess.run(["bash", os.path.join(root, "examples", "tiny_roles_cpu.sh")], cwd=root, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
+                          text=True, timeout=500, start_new_session=True)
+    assert proc.returncode == 0, proc.stdout[-4000:]
+    with open(os.path.join(run, "metrics.jsonl")) as f:
+        rows = [json.loads(line) for line in f]
+    assert len(rows) == 1 and rows[0]["weight_sync/bytes"] > 0 and rows[0]["actor/grad_norm"] > 0
+    left = subprocess.run(["ps", "-eo", "pid,args"], stdout=subprocess.PIPE, text=True).stdout
+    assert not [line for line in left.splitlines() if run in line], "a role outlived the launcher"

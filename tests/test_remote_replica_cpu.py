@@ -99,7 +99,7 @@ def test_training_entry_drives_a_replica_process(tmp_path):
                  "trainer.total_training_steps=1", "trainer.save_freq=0", "transfer_queue.num_data_storage_units=4", "actor_rollout_ref.actor.optim.lr=1e-3",
                  "actor_rollout_ref.actor.ppo_max_token_len_per_gpu=4096", "trainer.logger=[file]",
                  f"actor_rollout_ref.rollout.checkpoint_engine.replica_urls=[http://127.0.0.1:{http_port}]",
-                 f"actor_rollout_ref.rollout.checkpoint_engine.sync_master=127.0.0.1:{sync_port}"]
+                 f"actor_rollout_ref.rollout.checkpoint_engine.sync_master=127.0.0.1:{sync_port}", "actor_rollout_ref.rollout.tensor_model_parallel_size=1"]
     close = None
     try:
         trainer, close = build_stack(RunConfig(compose("training", overrides)).prepare())
@@ -117,3 +117,41 @@ def test_training_entry_drives_a_replica_process(tmp_path):
             proc.kill()
             out, _ = proc.communicate()
     assert "Traceback" not in (out or ""), out[-3000:]
+
+
+@pytest.mark.timeout(600)
+def test_tensor_parallel_replica_runs_in_lock_step_behind_one_endpoint():
+    """Two gloo ranks form one replica: rank 0 serves HTTP and broadcasts the control events, both ranks step together; each
+    rank receives the weight sync itself and keeps its shard. Tokens equal the unsharded model's before and after a sync."""
+    http_port, sync_port, tp_port = _free_port(), _free_port(), _free_port()
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, PYTHONPATH=root, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="2")
+    proc = subprocess.Popen([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+                             "--master-port", str(tp_port), "-m", "pear_b200.rollout.server", "--model", "preset:tiny", "--port", str(http_port),
+                             "--num-blocks", "128", "--max-num-seqs", "4", "--sync-rank", "1", "--sync-world", "3",
+                             "--sync-master", f"127.0.0.1:{sync_port}", "--sync-backend", "gloo"],
+                            env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    try:
+        group = StandaloneGroup(f"127.0.0.1:{sync_port}", 0, 3, "gloo")
+        replica = RemoteReplica(f"http://127.0.0.1:{http_port}")
+        replica.wait_ready(180)
+        model = load_rollout_model("preset:tiny", device="cpu")
+        prompts = [list(range(3, 40)), list(range(50, 61))]
+        p = SamplingParams(max_tokens=6, temperature=0.0)
+        import concurrent.futures as cf
+        with cf.ThreadPoolExecutor(2) as pool:  # two requests in flight: the leader batches them, the follower must too
+            outs = list(pool.map(lambda pr: replica.generate(pr, p), prompts))
+        assert [o.output for o in outs] == [_greedy(model, pr, 6) for pr in prompts]
+        new_state = {k: ((v * 0.5).to(torch.bfloat16).float() if v.dim() >= 2 else v.clone()) for k, v in model.state_dict().items()}
+        WeightSync(SyncConfig(bucket_megabytes=1, rollout_dtype=torch.bfloat16), BroadcastTransport(group, 0, "cpu"), [replica]).sync(new_state, version=5)
+        model.load_state_dict(new_state)
+        r2 = replica.generate(prompts[0], p)
+        assert r2.policy_version == 5 and r2.output == _greedy(model, prompts[0], 6)
+    finally:
+        proc.terminate()
+        try:
+            out, _ = proc.communicate(timeout=30)
+        except subprocess.TimeoutExpired:
+            proc.kill()
+            out, _ = proc.communicate()
+    assert "Traceback" not in (out or "") or "SignalException" in out, out[-3000:]
