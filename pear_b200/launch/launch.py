@@ -51,7 +51,11 @@ def main(argv=None) -> int:
                 cmd, env = command(p, i, args.master_port)
                 # a session per role: the role's own children (torch.distributed.run workers, environment processes) form one
                 # process group with it, which is what gets signalled at the end
-                procs.append(subprocess.Popen(cmd, env={**os.environ, **env}, start_new_session=True))
+                # the role's GPU set is the plan's; every other variable of `gpu_process_env` is a default the caller may override
+                merged = {**env, **os.environ}
+                if "CUDA_VISIBLE_DEVICES" in env:
+                    merged["CUDA_VISIBLE_DEVICES"] = env["CUDA_VISIBLE_DEVICES"]
+                procs.append(subprocess.Popen(cmd, env=merged, start_new_session=True))
         return procs[0].wait()  # the trainer's exit ends the run
     finally:
         for pr in procs:

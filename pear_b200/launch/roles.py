@@ -42,10 +42,17 @@ def plan_node(n_gpus: int, trainer_gpus: int, rollout_tp: int, recipe: str, over
     remote = [f"actor_rollout_ref.rollout.checkpoint_engine.replica_urls=[{urls}]",
               f"actor_rollout_ref.rollout.checkpoint_engine.sync_master=127.0.0.1:{sync_port}",
               f"actor_rollout_ref.rollout.tensor_model_parallel_size={max(1, rollout_tp)}"] if replicas else []
+    # both sides of the weight-sync world must name one backend: NCCL when both are on GPUs (each side's default), gloo when
+    # the trainer has no GPU or the recipe asks for it
+    force_gloo = trainer_gpus == 0 or "actor_rollout_ref.rollout.checkpoint_engine.backend=gloo" in overrides
+    if force_gloo and replicas:
+        remote.append("actor_rollout_ref.rollout.checkpoint_engine.backend=gloo")
     return [
-        RolePlan("trainer", trainer_gpus, 1, 0, "pear_b200.train.main", [recipe] + overrides + remote),
+        # trainer_gpus = 0: one trainer process without a GPU (plumbing runs: a CPU trainer beside GPU replicas)
+        RolePlan("trainer", max(1, trainer_gpus), 1 if trainer_gpus else 0, 0, "pear_b200.train.main", [recipe] + overrides + remote),
         RolePlan("rollout", replicas, rollout_tp, trainer_gpus, "pear_b200.rollout.server",
-                 overrides + ["--sync-world", str(replicas * max(1, rollout_tp) + 1), "--sync-master", f"127.0.0.1:{sync_port}"], rollout_port),
+                 overrides + ["--sync-world", str(replicas * max(1, rollout_tp) + 1), "--sync-master", f"127.0.0.1:{sync_port}"]
+                 + (["--sync-backend", "gloo"] if force_gloo else []), rollout_port),
         RolePlan("env", env_hosts, 0, 0, "pear_b200.sim.server", [], env_port),
         RolePlan("monitor", 1, 0, 0, "pear_b200.monitor.progress_panel",
                  overrides + [a for i in range(replicas) for a in ("--replica", f"replica-{i}=http://127.0.0.1:{rollout_port + i}/metrics")]),
@@ -71,7 +78,7 @@ def command(plan: RolePlan, index: int, master_port: int = 29500) -> tuple[list[
     if plan.role == "trainer":
         cmd = ["python", "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={plan.processes}", "--master-addr", "127.0.0.1",
                "--master-port", str(master_port), "-m", plan.module] + plan.args
-        env = gpu_process_env(list(range(plan.gpu_offset, plan.gpu_offset + plan.processes)))
+        env = gpu_process_env(list(range(plan.gpu_offset, plan.gpu_offset + plan.processes)) if plan.gpus_per_process else [])
     else:
         cmd = ["python", "-m", plan.module] + plan.args
         if plan.role == "rollout":

@@ -126,6 +126,15 @@ class HybridConfig:
         )
 
     @classmethod
+    def tiny_gpu(cls) -> "HybridConfig":
+        """The plumbing configuration with the head sizes the rollout kernels are built for (attention 256, GDN 128): a CPU
+        trainer can step it and a GPU replica runs it through the batched step, also sharded over two ranks."""
+        return cls(
+            vocab_size=4096, hidden_size=512, num_layers=4, num_attention_heads=4, num_kv_heads=2, head_dim=256,
+            gdn_qk_heads=2, gdn_v_heads=4, gdn_head_dim=128, intermediate_size=1024, num_mtp_layers=1,
+        )
+
+    @classmethod
     def small_gpu(cls) -> "HybridConfig":
         """A few layers of the 27B per-layer shape: kernels see their production tile sizes, memory stays small."""
         return cls(num_layers=4, vocab_size=32768)

@@ -256,7 +256,7 @@ def start_weight_receiver(server: RolloutServer, rank: int, world: int, master: 
         dist.init_process_group("nccl", init_method=f"tcp://{master}", rank=rank, world_size=world)
         transport = SymmTransport(SymmWorld(reductions=False), src, server.engine.model.config)
     else:  # a world of its own, beside a tensor-parallel world the replica may be part of
-        transport = BroadcastTransport(StandaloneGroup(master, rank, world, backend, device), src, device)
+        transport = BroadcastTransport(StandaloneGroup(master, rank, world, backend, device), src, device if backend == "nccl" else "cpu")
 
     def loop():
         if device != "cpu":
@@ -326,19 +326,40 @@ def main(argv=None) -> int:
         start_weight_receiver(server, args.sync_rank + tp_rank, args.sync_world, args.sync_master, args.sync_src, args.sync_backend, device)
     try:
         if tp_world > 1 and tp_rank != 0:  # followers mirror the leader until its stop message
-            server.thread.join()
+            import signal
+
+            # the launcher signals every rank; a follower leaves only through the leader's stop message, between steps, so that
+            # no rank ever waits on a peer that is gone
+            signal.signal(signal.SIGTERM, lambda *_: None)
+            while server.thread.is_alive():
+                server.thread.join(0.5)
             return 0 if server.error is None else 1
         if args.check:
             r = server.generate(list(range(1, 20)), SamplingParams(max_tokens=4, temperature=1.0))
             print(f"{args.name}: {len(r.output)} tokens on {device}, finish {r.finish.value}")
             return 0
+        import signal
+
         import uvicorn
 
+        # uvicorn shuts down on SIGTERM / SIGINT and then raises the signal again under the handler it found: with the default
+        # handler the process would end inside `run`, before a tensor-parallel leader has told its followers to stop
+        signal.signal(signal.SIGTERM, lambda *_: None)
+        signal.signal(signal.SIGINT, lambda *_: None)
         # a request that can no longer finish (a peer rank is gone) must not keep a terminated replica alive
         uvicorn.run(server.http_app(), host=args.host, port=args.port, log_level="warning", timeout_graceful_shutdown=3)
         return 0
     finally:
         server.close()
+        eng = server.engine
+        print(f"{args.name} rank {tp_rank}: steps={eng.metrics['steps']} fast_steps={eng.fast.steps if eng.fast is not None else 0} "
+              f"policy_version={eng.policy_version} weight_loads={server.weight_loads}", flush=True)
+        if tp_world > 1:
+            import torch.distributed as dist
+
+            if device != "cpu":
+                torch.cuda.synchronize()
+            dist.destroy_process_group()
 
 
 if __name__ == "__main__":

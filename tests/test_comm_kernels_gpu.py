@@ -55,3 +55,4 @@ def test_trainer_overlap_two_ranks():
     out = r.stdout + r.stderr
     assert r.returncode == 0, out[-4000:]
     assert "PASS fsdp_overlap" in out, out[-4000:]
+
