@@ -72,10 +72,20 @@ def _model_config(path: str) -> HybridConfig:
 
 
 class MetricsLog:
-    def __init__(self, run_dir: str, backends=("console", "file")):
+    """Per-step metrics to the backends ``trainer.logger`` lists: ``file`` (``metrics.jsonl`` + a one-line-per-step
+    ``train.log``), ``console``, ``wandb`` (one ``wandb.log(..., commit=True)`` per trainer step, so a step's metrics appear
+    as one row whatever logged them: 3rdparty/verl/patches/0014; the package is imported only when the backend is listed)."""
+
+    def __init__(self, run_dir: str, backends=("console", "file"), project: str = "pear_b200", name: Optional[str] = None):
         self.path = os.path.join(run_dir, "metrics.jsonl")
         self.train_log = os.path.join(run_dir, "train.log")
         self.backends = backends
+        self.wandb = None
+        if "wandb" in backends:
+            import wandb  # fails loudly when the backend is asked for and the package is absent
+
+            self.wandb = wandb
+            wandb.init(project=project, name=name or os.path.basename(os.path.normpath(run_dir)), dir=run_dir, resume="allow")
 
     def __call__(self, step: int, m: dict) -> None:
         rec = {"step": step, "time": time.time(), **{k: (float(v) if isinstance(v, (int, float)) else v) for k, v in m.items()}}
@@ -84,6 +94,8 @@ class MetricsLog:
                 f.write(json.dumps(rec) + "\n")
             with open(self.train_log, "a") as f:
                 f.write(f"step:{step} - " + " - ".join(f"{k}:{v:.6g}" for k, v in sorted(m.items()) if isinstance(v, (int, float))) + "\n")
+        if self.wandb is not None:
+            self.wandb.log({k: v for k, v in rec.items() if isinstance(v, (int, float)) and k != "step"}, step=step, commit=True)
         if "console" in self.backends:
             keys = ("data/reward_mean", "actor/pg_loss", "actor/grad_norm", "timing/step_s", "train/staleness_mean")
             log.info("step %d | %s", step, " | ".join(f"{k.split('/')[-1]} {m[k]:.4g}" for k in keys if k in m))

@@ -113,3 +113,24 @@ def test_checkpoint_retention_prunes_before_writing(tmp_path):
         cm.save(step, FakeEngine())
         assert len(cm.steps_on_disk()) <= 2
     assert cm.steps_on_disk() == [3, 4] and cm.latest() == 4
+
+
+def test_metrics_log_commits_one_wandb_row_per_step(tmp_path, monkeypatch):
+    import json
+    import sys
+    import types
+
+    from pear_b200.train.main import MetricsLog
+
+    calls = {"init": [], "log": []}
+    fake = types.ModuleType("wandb")
+    fake.init = lambda **kw: calls["init"].append(kw)
+    fake.log = lambda data, step=None, commit=None: calls["log"].append((dict(data), step, commit))
+    monkeypatch.setitem(sys.modules, "wandb", fake)
+    log = MetricsLog(str(tmp_path), ("file", "wandb"))
+    log(1, {"actor/pg_loss": 0.5, "note": "text"})
+    log(2, {"actor/pg_loss": 0.25})
+    assert calls["init"][0]["dir"] == str(tmp_path) and len(calls["log"]) == 2
+    assert calls["log"][0][1:] == (1, True) and calls["log"][0][0]["actor/pg_loss"] == 0.5 and "note" not in calls["log"][0][0]
+    with open(tmp_path / "metrics.jsonl") as f:
+        assert [json.loads(line)["step"] for line in f] == [1, 2]
