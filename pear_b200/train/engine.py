@@ -101,6 +101,10 @@ class EngineConfig:
     param_dtype: str = "bf16"
     fp32_modules: list = field(default_factory=list)
     ulysses_sequence_parallel_size: int = 1
+    # ranks per sharding group: -1 (or the world size) shards over the whole world (FSDP); a divisor S of the world size
+    # gives world / S replicas of an S-way sharded model (HSDP): reduce-scatter inside a shard group, all-reduce of the
+    # shard gradients across replicas on the last micro-batch
+    fsdp_size: int = -1
     enable_gradient_checkpointing: bool = True
     gradient_checkpointing_retain_attention: bool = False
     enable_activation_offload: bool = False
@@ -132,7 +136,7 @@ class EngineConfig:
             weight_decay=float(actor.optim.get("weight_decay", 0.01)), clip_grad=float(actor.get("clip_grad", 1.0)),
             lr_warmup_steps=int(actor.optim.get("lr_warmup_steps", 0)), param_dtype=fs.mixed_precision.get("param_dtype", "bf16"),
             fp32_modules=list(fs.mixed_precision.get("fp32_modules", [])),
-            ulysses_sequence_parallel_size=int(fs.ulysses_sequence_parallel_size),
+            ulysses_sequence_parallel_size=int(fs.ulysses_sequence_parallel_size), fsdp_size=int(fs.get("fsdp_size", -1)),
             enable_gradient_checkpointing=bool(model.enable_gradient_checkpointing),
             enable_activation_offload=bool(model.get("enable_activation_offload", False)),
             gradient_checkpointing_retain_attention=bool(model.get("gradient_checkpointing_retain_attention", False)),
@@ -165,13 +169,31 @@ class TrainEngine:
                 if d == self.dp_rank:
                     self.sp_group = g
         self.sp = SequenceParallel(self.sp_group) if sp > 1 else None
+        # ---- sharding groups. `group` / `world` / `rank` stay the whole job's (data distribution, checkpoints, the driver rank);
+        # the sharder and the gradient norm work inside `shard_group`
+        self.shard_group, self.shard_world, self.shard_rank = world_group, self.world, self.rank
+        S = cfg.fsdp_size
+        if replicate_group is None and self.world > 1 and 0 < S < self.world:
+            if self.world % S or S % sp:
+                raise ValueError(f"fsdp_size {S} must divide the world size {self.world} and be a multiple of the sequence-parallel size {sp}")
+            ranks = [dist.get_global_rank(world_group, r) for r in range(self.world)]
+            for i in range(self.world // S):  # every rank creates every group (collective calls), in the same order
+                g = dist.new_group(ranks[i * S:(i + 1) * S])
+                if i == self.rank // S:
+                    self.shard_group = g
+            for j in range(S):
+                g = dist.new_group(ranks[j::S])
+                if j == self.rank % S:
+                    replicate_group = g
+            self.shard_world, self.shard_rank = S, self.rank % S
+        self.replicate_group = replicate_group
         self.kernels = kernels
         if kernels is not None:
             kernels.check_config(cfg)
 
         # ---- build: one rank builds the seeded model (or takes the given weights) on the host, the others on the meta device
-        self.src_rank = 0 if (self.world > 1 and cfg.sharded_construction) else None
-        on_meta = self.src_rank is not None and self.rank != self.src_rank
+        self.src_rank = 0 if (self.shard_world > 1 and cfg.sharded_construction) else None  # (rank 0 of every shard group)
+        on_meta = self.src_rank is not None and self.shard_rank != self.src_rank
         if on_meta:
             with torch.device("meta"):
                 model = HybridForCausalLM(model_cfg, with_mtp=with_mtp)
@@ -193,7 +215,7 @@ class TrainEngine:
         if self.device.type == "cpu" and dtype != torch.float32:
             dtype = torch.float32  # CPU plumbing runs in fp32
         self.model = model
-        self.sharded = ShardedModel(model, world_group if self.world > 1 else None, replicate_group, dtype, cfg.fp32_modules,
+        self.sharded = ShardedModel(model, self.shard_group if self.shard_world > 1 else None, replicate_group, dtype, cfg.fp32_modules,
                                     self.device, src_rank=self.src_rank)
         for mod in model.modules():  # buffers (none hold weights) follow the parameters' device
             for bname, buf in list(mod._buffers.items()):
@@ -300,8 +322,8 @@ class TrainEngine:
         for p in self.sharded.parameters():
             if p.grad is not None:
                 sq = sq + p.grad.float().pow(2).sum()
-        if self.world > 1:
-            dist.all_reduce(sq, group=self.group)
+        if self.shard_world > 1:  # (replicas of a shard hold the same gradient after the cross-replica all-reduce)
+            dist.all_reduce(sq, group=self.shard_group)
         return sq.sqrt()
 
     def optimizer_step(self) -> dict:
@@ -334,11 +356,13 @@ class TrainEngine:
 
     def train_state(self) -> dict:
         return {"shards": self.sharded.shard_state(), "optimizer": self.optimizer.state_dict(), "step": self.step_count,
-                "policy_version": self.policy_version, "world_size": self.world}
+                "policy_version": self.policy_version, "world_size": self.world, "shard_world_size": self.shard_world}
 
     def load_train_state(self, st: dict) -> None:
         if st["world_size"] != self.world:
             raise ValueError(f"checkpoint was written by world size {st['world_size']}, this run has {self.world}")
+        if st.get("shard_world_size", st["world_size"]) != self.shard_world:
+            raise ValueError(f"checkpoint was sharded over {st.get('shard_world_size')} ranks, this run shards over {self.shard_world}")
         self.sharded.load_shard_state(st["shards"])
         self.optimizer.load_state_dict(st["optimizer"])
         self.step_count, self.policy_version = st["step"], st["policy_version"]

@@ -101,3 +101,48 @@ def test_two_rank_fsdp_and_sequence_parallel_match_single_process(tmp_path, sp):
     assert abs(got["norm"] - want_norm) < 2e-4 * max(1.0, want_norm)
     for k, v in want.items():
         assert torch.allclose(got["state"][k], v, atol=5e-5, rtol=2e-4), k
+
+
+def _hsdp_rank_fn(rank, world, out_dir, sp):
+    cfg = HybridConfig.tiny()
+    ecfg = _ecfg(sp)
+    ecfg.fsdp_size = 2
+    import torch.distributed as dist
+
+    eng = TrainEngine(cfg, ecfg, world_group=dist.group.WORLD, seed=5)
+    assert eng.shard_world == 2 and eng.shard_rank == rank % 2 and dist.get_world_size(eng.replicate_group) == 2
+    assert eng.world == 4 and eng.dp_size == 4 // sp and eng.dp_rank == rank // sp
+    all_batches = _hsdp_batches(cfg)
+    per = len(all_batches) // eng.dp_size
+    eng.forward_backward_batch(all_batches[eng.dp_rank * per:(eng.dp_rank + 1) * per])
+    m = eng.optimizer_step()
+    state = eng.full_state_dict()
+    torch.save({"state": state, "norm": m["actor/grad_norm"]}, os.path.join(out_dir, f"out{rank}.pt"))
+    # the checkpoint's shard files: the offline merger rebuilds the tensors from the first replica's shards
+    from pear_b200.train.checkpoint import CheckpointManager
+
+    CheckpointManager(os.path.join(out_dir, "run"), rank, world, barrier=dist.barrier).save(1, eng)
+
+
+def _hsdp_batches(cfg):
+    return [make_batch(cfg, 0), make_batch(cfg, 1, lens=(40, 33, 21)), make_batch(cfg, 2, lens=(64,)), make_batch(cfg, 3, lens=(30, 50))]
+
+
+@pytest.mark.parametrize("sp", [1, 2])
+def test_hsdp_two_replicas_of_two_shards_match_single_process(tmp_path, sp):
+    """world 4 with ``fsdp_size`` 2: two replicas of a 2-way sharded model. sp=1: four data-parallel ranks, one micro-batch each;
+    sp=2: each replica is one sequence-parallel pair with two micro-batches. Gradients are reduce-scattered inside a shard
+    group and all-reduced across the replicas on the last micro-batch; every rank ends with the single-process step's weights."""
+    cfg = HybridConfig.tiny()
+    ecfg = _ecfg()
+    want, want_norm = reference_step(cfg, ecfg, _hsdp_batches(cfg), seed=5)
+    run_ranks(_hsdp_rank_fn, 4, tmp_path, str(tmp_path), sp)
+    for rank in range(4):
+        got = torch.load(os.path.join(str(tmp_path), f"out{rank}.pt"))
+        assert abs(got["norm"] - want_norm) < 2e-4 * max(1.0, want_norm), (rank, got["norm"], want_norm)
+        for k, v in want.items():
+            assert torch.allclose(got["state"][k], v, atol=5e-5, rtol=2e-4), (rank, k)
+    from pear_b200.utils.model_merger import merge_shards
+
+    merged = merge_shards(os.path.join(str(tmp_path), "run", "ckpt", "global_step_1", "actor"))
+    assert all(torch.equal(merged[k], got["state"][k]) for k in want)
