@@ -76,7 +76,10 @@ class CheckpointManager:
         actor = os.path.join(d, "actor")
         os.makedirs(actor, exist_ok=True)
         st = engine.train_state()
-        torch.save(st, os.path.join(actor, f"model_world_size_{self.world}_rank_{self.rank}.pt"))
+        # HSDP: the first replica (the ranks below the shard group size) writes; the other replicas hold copies of its shards
+        # (upstream: 3rdparty/verl/patches/0021)
+        if self.rank < int(getattr(engine, "shard_world", self.world)):
+            torch.save(st, os.path.join(actor, f"model_world_size_{self.world}_rank_{self.rank}.pt"))
         if self.rank == 0:
             torch.save({"step": step, "policy_version": st["policy_version"], "world_size": self.world,
                         "rng": torch.get_rng_state(), **(extra or {})}, os.path.join(actor, "extra_state.pt"))
@@ -97,7 +100,7 @@ class CheckpointManager:
             return None
         d = self.step_dir(step)
         actor = os.path.join(d, "actor")
-        mine = os.path.join(actor, f"model_world_size_{self.world}_rank_{self.rank}.pt")
+        mine = os.path.join(actor, f"model_world_size_{self.world}_rank_{self.rank % int(getattr(engine, 'shard_world', self.world))}.pt")
         if not os.path.exists(mine):
             sizes = sorted({int(m.group(1)) for f in os.listdir(actor) if (m := re.match(r"model_world_size_(\d+)_rank_", f))})
             raise ValueError(f"checkpoint {d} was written by world size {sizes}, this run has world size {self.world}")

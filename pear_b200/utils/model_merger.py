@@ -20,11 +20,11 @@ def merge_shards(actor_dir: str) -> dict[str, torch.Tensor]:
     if not files:
         raise FileNotFoundError(f"no shard files in {actor_dir}")
     world = int(re.match(r"model_world_size_(\d+)_", files[0]).group(1))
-    if len(files) != world:
-        raise ValueError(f"{actor_dir}: {len(files)} shard files for world size {world}")
     first = torch.load(os.path.join(actor_dir, f"model_world_size_{world}_rank_0.pt"), map_location="cpu", weights_only=False)
-    # HSDP: ranks [0, S) are the first replica's S shards, the other replicas hold copies
+    # HSDP: only the first replica (ranks [0, S)) writes shard files, the other replicas hold copies
     sharded_over = int(first.get("shard_world_size", world))
+    if len(files) != sharded_over:
+        raise ValueError(f"{actor_dir}: {len(files)} shard files for world size {world} sharded over {sharded_over} ranks")
     shards = [first["shards"]] + [torch.load(os.path.join(actor_dir, f"model_world_size_{world}_rank_{r}.pt"), map_location="cpu", weights_only=False)["shards"]
                                   for r in range(1, sharded_over)]
     out: dict[str, torch.Tensor] = {}

@@ -121,7 +121,15 @@ def _hsdp_rank_fn(rank, world, out_dir, sp):
     # the checkpoint's shard files: the offline merger rebuilds the tensors from the first replica's shards
     from pear_b200.train.checkpoint import CheckpointManager
 
-    CheckpointManager(os.path.join(out_dir, "run"), rank, world, barrier=dist.barrier).save(1, eng)
+    mgr = CheckpointManager(os.path.join(out_dir, "run"), rank, world, barrier=dist.barrier)
+    mgr.save(1, eng)
+    # every rank of every replica restores from the first replica's files
+    with torch.no_grad():
+        for p in eng.sharded.parameters():
+            p.zero_()
+    assert mgr.load(eng)["step"] == 1
+    again = eng.full_state_dict()
+    assert all(torch.equal(again[k], state[k]) for k in state)
 
 
 def _hsdp_batches(cfg):
@@ -144,5 +152,7 @@ def test_hsdp_two_replicas_of_two_shards_match_single_process(tmp_path, sp):
             assert torch.allclose(got["state"][k], v, atol=5e-5, rtol=2e-4), (rank, k)
     from pear_b200.utils.model_merger import merge_shards
 
-    merged = merge_shards(os.path.join(str(tmp_path), "run", "ckpt", "global_step_1", "actor"))
+    actor = os.path.join(str(tmp_path), "run", "ckpt", "global_step_1", "actor")
+    assert sorted(f for f in os.listdir(actor) if f.startswith("model_")) == ["model_world_size_4_rank_0.pt", "model_world_size_4_rank_1.pt"]
+    merged = merge_shards(actor)
     assert all(torch.equal(merged[k], got["state"][k]) for k in want)
