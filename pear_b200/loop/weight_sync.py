@@ -118,6 +118,14 @@ class StandaloneGroup:
         self.broadcast(payload, src)
         return obj if self.rank == src else pickle.loads(payload.cpu().numpy().tobytes())
 
+    def heartbeat(self, timeout_s: float = 30.0):
+        """A :class:`pear_b200.parallel.heartbeat.Heartbeat` of this world over its rendezvous store: replica ranks beat from a
+        thread of their own, the sender checks before every sync, so a replica that died is named on the host instead of being
+        waited for inside a broadcast."""
+        from ..parallel.heartbeat import Heartbeat
+
+        return Heartbeat(self.store, self.rank, self.world, timeout_s, prefix="weight_sync_hb")
+
     def close(self) -> None:
         self.pg = None
         self.store = None
@@ -262,13 +270,17 @@ def receive_all(transport, server) -> int:
 
 
 class WeightSync:
-    def __init__(self, cfg: SyncConfig, transport, servers: Optional[list] = None):
-        self.cfg, self.transport, self.servers = cfg, transport, servers or []
+    def __init__(self, cfg: SyncConfig, transport, servers: Optional[list] = None, heartbeat=None):
+        """``heartbeat``: checked before anything of a sync starts (``PeerLost`` names the replica ranks that are gone)."""
+        self.cfg, self.transport, self.servers, self.heartbeat = cfg, transport, servers or [], heartbeat
         self.last_seconds = 0.0
         self.bytes_sent = 0
 
     def sync(self, state: dict[str, torch.Tensor], version: int) -> dict:
         t0 = time.time()
+        if self.heartbeat is not None:
+            self.heartbeat.beat(version)
+            self.heartbeat.check()
         aborted = sum(s.pause(abort=True) for s in self.servers)
         for s in self.servers:
             s.release_cached_memory()

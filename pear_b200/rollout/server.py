@@ -238,7 +238,8 @@ def to_rollout_dtypes(model, dtype: torch.dtype = torch.bfloat16):
     return model
 
 
-def start_weight_receiver(server: RolloutServer, rank: int, world: int, master: str, src: int = 0, backend: str = "auto", device: str = "cpu"):
+def start_weight_receiver(server: RolloutServer, rank: int, world: int, master: str, src: int = 0, backend: str = "auto", device: str = "cpu",
+                          heartbeat_s: float = 1.0):
     """Join the weight-sync process group ({sending trainer rank} + {replica ranks}) and load every sync the sender starts, on
     a thread of its own: each ``WeightSync.sync`` on the trainer side arrives here as buckets until the last one, then the
     replica loads them, bumps its policy version and clears its KV tiers. Returns the thread."""
@@ -256,7 +257,20 @@ def start_weight_receiver(server: RolloutServer, rank: int, world: int, master: 
         dist.init_process_group("nccl", init_method=f"tcp://{master}", rank=rank, world_size=world)
         transport = SymmTransport(SymmWorld(reductions=False), src, server.engine.model.config)
     else:  # a world of its own, beside a tensor-parallel world the replica may be part of
-        transport = BroadcastTransport(StandaloneGroup(master, rank, world, backend, device), src, device if backend == "nccl" else "cpu")
+        group = StandaloneGroup(master, rank, world, backend, device)
+        transport = BroadcastTransport(group, src, device if backend == "nccl" else "cpu")
+        hb = group.heartbeat()
+        server.leave_sync_world = lambda: hb.leave(server.weight_loads)  # a clean exit says so: the sender is told, not timed out
+
+        def beat():
+            while not server.stop_flag:
+                try:
+                    hb.beat(server.weight_loads)
+                except Exception:  # noqa: BLE001 - the sender (and its store) is gone
+                    return
+                time.sleep(heartbeat_s)
+
+        threading.Thread(target=beat, daemon=True, name=f"{server.name}-heartbeat").start()
 
     def loop():
         if device != "cpu":
@@ -350,6 +364,12 @@ def main(argv=None) -> int:
         uvicorn.run(server.http_app(), host=args.host, port=args.port, log_level="warning", timeout_graceful_shutdown=3)
         return 0
     finally:
+        leave = getattr(server, "leave_sync_world", None)
+        if leave is not None:
+            try:
+                leave()
+            except Exception:  # noqa: BLE001 - the sender's store is gone already
+                pass
         server.close()
         eng = server.engine
         print(f"{args.name} rank {tp_rank}: steps={eng.metrics['steps']} fast_steps={eng.fast.steps if eng.fast is not None else 0} "

@@ -121,7 +121,7 @@ def build_stack(cfg, replicas: int = 1, device: str = "cpu", env_families: Optio
     tcfg = TrainerConfig.from_config(cfg)
     ce = ro.checkpoint_engine
     urls = [str(u) for u in (ce.get("replica_urls", None) or [])]
-    transport = None
+    transport, heartbeat = None, None
     if rank == 0:
         full = engine.full_state_dict(torch.float32)
         if urls:  # replicas are processes of their own: requests over HTTP, weights through a world shared with them only
@@ -131,6 +131,7 @@ def build_stack(cfg, replicas: int = 1, device: str = "cpu", env_families: Optio
             # every rank of a tensor-parallel replica receives for itself: the world is this rank plus all of theirs
             group = StandaloneGroup(str(ce.sync_master), 0, 1 + len(urls) * max(1, int(ro.tensor_model_parallel_size)), backend, device)
             transport = BroadcastTransport(group, 0, device if backend == "nccl" else "cpu")
+            heartbeat = group.heartbeat(float(ce.get("heartbeat_timeout_s", 30.0)))
             servers = [RemoteReplica(u, name=f"replica-{i}") for i, u in enumerate(urls)]
             for s in servers:
                 s.wait_ready(float(ce.get("ready_timeout_s", 600)))
@@ -158,7 +159,7 @@ def build_stack(cfg, replicas: int = 1, device: str = "cpu", env_families: Optio
     dataset = EpisodeDataset(files if files is not None else {"family": "synthetic", "args": {"task": ["reach"], "seed": list(range(64))}},
                              seed=int(cfg.trainer.seed))
     sync = WeightSync(SyncConfig(int(ce.update_weights_bucket_megabytes), getattr(torch, str(ro.dtype)), tuple(ro.fp32_modules)),
-                      transport or InProcessTransport(servers), servers) if rank == 0 else None
+                      transport or InProcessTransport(servers), servers, heartbeat=heartbeat) if rank == 0 else None
     if sync is not None and urls:  # replica processes built their own weights: start them from the trainer's policy
         sync.sync(full, engine.policy_version)
     ckpt = CheckpointManager(str(cfg.run_dir), rank, engine.world, cfg.trainer.max_actor_ckpt_to_keep,

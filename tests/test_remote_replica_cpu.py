@@ -155,3 +155,49 @@ def test_tensor_parallel_replica_runs_in_lock_step_behind_one_endpoint():
             proc.kill()
             out, _ = proc.communicate()
     assert "Traceback" not in (out or "") or "SignalException" in out, out[-3000:]
+
+
+def _replica(http_port, sync_port, world=2):
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, PYTHONPATH=root, CUDA_VISIBLE_DEVICES="")
+    return subprocess.Popen([sys.executable, "-m", "pear_b200.rollout.server", "--model", "preset:tiny", "--port", str(http_port), "--num-blocks", "128",
+                             "--max-num-seqs", "4", "--sync-rank", "1", "--sync-world", str(world), "--sync-master", f"127.0.0.1:{sync_port}",
+                             "--sync-backend", "gloo"], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+
+
+@pytest.mark.timeout(300)
+@pytest.mark.parametrize("how", ["killed", "terminated"])
+def test_a_lost_replica_is_named_before_the_sync_starts(how):
+    """The replica's ranks beat into the weight-sync world's store; the sender checks before a sync. A replica that was killed
+    stops beating and is reported after the heartbeat timeout; one that was terminated says that it leaves. Neither is waited
+    for inside a broadcast."""
+    from pear_b200.parallel.heartbeat import PeerLost
+
+    http_port, sync_port = _free_port(), _free_port()
+    proc = _replica(http_port, sync_port)
+    try:
+        group = StandaloneGroup(f"127.0.0.1:{sync_port}", 0, 2, "gloo")
+        replica = RemoteReplica(f"http://127.0.0.1:{http_port}")
+        replica.wait_ready(120)
+        sync = WeightSync(SyncConfig(bucket_megabytes=1, rollout_dtype=torch.bfloat16), BroadcastTransport(group, 0, "cpu"), [replica],
+                          heartbeat=group.heartbeat(timeout_s=2.5))
+        state = load_rollout_model("preset:tiny", device="cpu").state_dict()
+        sync.sync(state, version=1)  # a live replica: the sync goes through
+        assert replica.policy_version() == 1
+        if how == "killed":
+            proc.kill()
+            proc.wait(30)
+            time.sleep(3.0)
+            with pytest.raises(PeerLost, match=r"ranks \[1\] lost: no heartbeat"):
+                sync.sync(state, version=2)
+        else:
+            proc.terminate()
+            proc.wait(60)
+            with pytest.raises(PeerLost, match=r"ranks \[1\] lost: left the job"):
+                sync.sync(state, version=2)
+        with pytest.raises(Exception):  # requests to it fail at once as well
+            replica.generate([1, 2, 3], SamplingParams(max_tokens=2))
+    finally:
+        if proc.poll() is None:
+            proc.kill()
+        proc.communicate()
