@@ -111,6 +111,20 @@ def build_stack(cfg, replicas: int = 1, device: str = "cpu", env_families: Optio
         m = HybridForCausalLM(mcfg, with_mtp=False)
         model_io.load_model_dir(mpath, m)
         init = m.state_dict()
+    if str(device).startswith("cuda"):  # sized on the host before anything is allocated: over capacity is said now, not by the allocator mid-step
+        try:
+            from .memory_plan import plan as memory_plan
+
+            world = dist.get_world_size(world_group) if world_group is not None else 1
+            shard = world if ecfg.fsdp_size in (-1, 0) or ecfg.fsdp_size >= world else ecfg.fsdp_size
+            capacity = torch.cuda.get_device_properties(device).total_memory
+            mp = memory_plan(mcfg, ecfg, int(cfg.actor_rollout_ref.actor.ppo_max_token_len_per_gpu) * ecfg.ulysses_sequence_parallel_size, shard,
+                             hbm_bytes=capacity, raise_if_over=False)
+            over = mp.total_device_bytes > 0.92 * capacity
+            if int(os.environ.get("RANK", "0")) == 0:
+                (log.warning if over else log.info)("trainer memory plan per GPU%s:\n%s", " (OVER the device's capacity)" if over else "", mp.table())
+        except Exception as e:  # noqa: BLE001 - a planning note never stops a run
+            log.warning("trainer memory plan skipped: %r", e)
     engine = TrainEngine(mcfg, ecfg, device=device, world_group=world_group, seed=int(cfg.trainer.seed), state_dict=init)
     rank = engine.rank
     if rank == 0:

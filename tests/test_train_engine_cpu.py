@@ -156,3 +156,20 @@ def test_hsdp_two_replicas_of_two_shards_match_single_process(tmp_path, sp):
     assert sorted(f for f in os.listdir(actor) if f.startswith("model_")) == ["model_world_size_4_rank_0.pt", "model_world_size_4_rank_1.pt"]
     merged = merge_shards(actor)
     assert all(torch.equal(merged[k], got["state"][k]) for k in want)
+
+
+def test_memory_plan_of_the_27b_recipe_fits_and_names_what_does_not():
+    from pear_b200.train.memory_plan import plan
+
+    cfg = HybridConfig.qwen3_8_27b()
+    ecfg = EngineConfig(ulysses_sequence_parallel_size=8, enable_gradient_checkpointing=True, enable_activation_offload=True, topk_log_probs=32)
+    p = plan(cfg, ecfg, tokens_per_micro_batch=8 * 16384, shard_world=8)  # 8 sequences of 16k tokens per micro-batch over SP 8
+    assert p.total_device_bytes < 0.92 * (180 << 30) and p.checkpoints_on_host and p.host_bytes > 0
+    assert p.master_bytes == 4 * cfg.num_parameters() // 8 and p.optimizer_bytes == 2 * p.master_bytes
+    streamed = plan(cfg, EngineConfig(ulysses_sequence_parallel_size=8, enable_activation_offload=True, streamed_adamw=True), 8 * 16384, 8)
+    assert streamed.total_device_bytes == p.total_device_bytes - p.optimizer_bytes - (p.head_bytes - streamed.head_bytes) and streamed.optimizer_on_host
+    with pytest.raises(MemoryError, match="shard over more ranks"):  # one GPU cannot hold the 27B model's optimizer state
+        plan(cfg, ecfg, 8 * 16384, shard_world=1)
+    with pytest.raises(MemoryError):  # nor can eight hold every layer's intermediates of 16k-token sequences without checkpointing
+        plan(cfg, EngineConfig(ulysses_sequence_parallel_size=8, enable_gradient_checkpointing=False), 8 * 16384, 8)
+    assert "device total" in p.table()
