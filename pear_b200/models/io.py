@@ -15,7 +15,7 @@ import mmap
 import os
 import struct
 import warnings
-from typing import Iterable, Iterator, Optional
+from typing import Callable, Iterable, Iterator, Optional
 
 import torch
 
@@ -89,19 +89,35 @@ def load_safetensors(path: str) -> dict[str, torch.Tensor]:
         f.close()
 
 
-def iter_model_tensors(directory: str) -> Iterator[tuple[str, torch.Tensor]]:
-    """Stream (name, tensor) from a model directory, shard by shard (a 27B model never sits in host memory twice)."""
+def _model_files(directory: str) -> list[str]:
     index = os.path.join(directory, "model.safetensors.index.json")
     if os.path.exists(index):
         with open(index) as fh:
-            files = sorted(set(json.load(fh)["weight_map"].values()))
-    else:
-        files = ["model.safetensors"]
-    for fn in files:
+            return sorted(set(json.load(fh)["weight_map"].values()))
+    return ["model.safetensors"]
+
+
+def model_tensor_names(directory: str) -> list[str]:
+    """The tensor names of a model directory, from the files' headers only (no tensor is read)."""
+    names: list[str] = []
+    for fn in _model_files(directory):
+        f = SafetensorsFile(os.path.join(directory, fn))
+        try:
+            names += f.keys()
+        finally:
+            f.close()
+    return names
+
+
+def iter_model_tensors(directory: str, only: Optional[Callable[[str], bool]] = None) -> Iterator[tuple[str, torch.Tensor]]:
+    """Stream (name, tensor) from a model directory, shard by shard (a 27B model never sits in host memory twice); ``only``
+    selects by name before a tensor is read."""
+    for fn in _model_files(directory):
         f = SafetensorsFile(os.path.join(directory, fn))
         try:
             for k in f.keys():
-                yield k, f.get(k)
+                if only is None or only(k):
+                    yield k, f.get(k)
         finally:
             f.close()
 

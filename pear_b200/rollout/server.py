@@ -210,8 +210,14 @@ def build_server(model, cfg: Optional[EngineConfig] = None, device="cpu", **kw) 
     return RolloutServer(RolloutEngine(model, cfg or EngineConfig(), device), **kw)
 
 
-def load_rollout_model(path: str, dtype: torch.dtype = torch.bfloat16, device: str = "cpu", with_mtp: bool = True, seed: int = 0):
-    """``preset:<name>`` (random init of a ``HybridConfig`` preset) or a model directory in the Hugging Face layout."""
+def load_rollout_model(path: str, dtype: torch.dtype = torch.bfloat16, device: str = "cpu", with_mtp: bool = True, seed: int = 0,
+                       drafter_path: Optional[str] = None):
+    """``preset:<name>`` (random init of a ``HybridConfig`` preset) or a model directory in the Hugging Face layout.
+
+    The MTP drafter of a model directory: trained checkpoints are exported without it, so it comes from ``drafter_path`` (the
+    base model's directory; only its ``mtp.*`` tensors are read) and stays frozen across weight syncs; without
+    ``drafter_path`` the directory's own ``mtp.*`` tensors are used when it has them, else the model comes up without a
+    drafter (upstream: pear/rollout/server.py:22,32-35 loads the frozen drafter from files)."""
     from ..models import io as model_io
     from ..models.config import HybridConfig
     from ..models.hybrid import HybridForCausalLM
@@ -221,8 +227,28 @@ def load_rollout_model(path: str, dtype: torch.dtype = torch.bfloat16, device: s
         model = HybridForCausalLM(cfg, with_mtp=with_mtp and cfg.num_mtp_layers > 0).init_weights(seed)
     else:
         cfg = model_io.load_config(path)
-        model = HybridForCausalLM(cfg, with_mtp=False)
-        model_io.load_model_dir(path, model)
+        source = drafter_path or path
+        has_drafter = with_mtp and cfg.num_mtp_layers > 0 and any(model_io.from_hf_name(k).startswith("mtp.") for k in model_io.model_tensor_names(source))
+        if drafter_path and with_mtp and not has_drafter:
+            raise KeyError(f"{drafter_path} holds no mtp.* tensors")
+        model = HybridForCausalLM(cfg, with_mtp=has_drafter)
+        if has_drafter and drafter_path:
+            model_io.load_model_dir(path, model, allow_missing=("mtp.",))  # everything but the drafter, strictly
+            own = dict(model.state_dict())
+            seen = set()
+            with torch.no_grad():
+                for key, t in model_io.iter_model_tensors(drafter_path, only=lambda k: model_io.from_hf_name(k).startswith("mtp.")):
+                    name = model_io.from_hf_name(key)
+                    if name in own:
+                        if tuple(own[name].shape) != tuple(t.shape):
+                            raise ValueError(f"{drafter_path}: tensor {key} has shape {tuple(t.shape)}, the drafter expects {tuple(own[name].shape)}")
+                        own[name].copy_(t.to(own[name].dtype))
+                        seen.add(name)
+            lost = [k for k in own if k.startswith("mtp.") and k not in seen]
+            if lost:
+                raise KeyError(f"{drafter_path} lacks {len(lost)} drafter tensors (first: {lost[:4]})")
+        else:
+            model_io.load_model_dir(path, model, ignore_unexpected=("visual.",) if has_drafter else ("visual.", "mtp."))
     if device != "cpu":
         to_rollout_dtypes(model.to(device), dtype)
     return model.eval()
@@ -303,6 +329,7 @@ def main(argv=None) -> int:
     ap.add_argument("--num-blocks", type=int, default=2048)
     ap.add_argument("--max-num-seqs", type=int, default=64)
     ap.add_argument("--speculative-tokens", type=int, default=0)
+    ap.add_argument("--drafter", default=None, help="directory whose mtp.* tensors are the (frozen) drafter of a model directory without one")
     ap.add_argument("--check", action="store_true", help="build the replica, answer one request and exit (no HTTP server)")
     ap.add_argument("--sync-rank", type=int, default=-1, help="this replica's rank in the weight-sync process group (-1: no group)")
     ap.add_argument("--sync-world", type=int, default=0, help="size of the weight-sync group: the sending trainer rank + the replica ranks")
@@ -334,7 +361,7 @@ def main(argv=None) -> int:
         if args.sync_backend == "nvswitch":
             raise SystemExit("--sync-backend nvswitch needs the default process group, which a tensor-parallel replica uses for its own ranks: use nccl")
     else:
-        model = load_rollout_model(path, device=device)
+        model = load_rollout_model(path, device=device, drafter_path=args.drafter)
         server = build_server(model, ecfg, device=device, name=args.name)
     if args.sync_rank >= 0:  # a tensor-parallel replica's ranks are consecutive in the weight-sync world
         start_weight_receiver(server, args.sync_rank + tp_rank, args.sync_world, args.sync_master, args.sync_src, args.sync_backend, device)

@@ -150,8 +150,23 @@ def build_stack(cfg, replicas: int = 1, device: str = "cpu", env_families: Optio
             for s in servers:
                 s.wait_ready(float(ce.get("ready_timeout_s", 600)))
         for i in range(0 if urls else replicas):
-            rm = HybridForCausalLM(mcfg, with_mtp=bool(cfg.actor_rollout_ref.model.mtp.enable_rollout))
+            mtp_cfg = cfg.actor_rollout_ref.model.mtp
+            rm = HybridForCausalLM(mcfg, with_mtp=bool(mtp_cfg.enable_rollout))
             rm.load_state_dict(full, strict=False)
+            if rm.mtp is not None and not mpath.startswith("preset:"):
+                # the frozen drafter comes from files (the base model's directory unless `mtp.drafter_path` names another): the
+                # trainer's state has none, and a drafter left at its random init would propose nothing that is accepted
+                src = str(mtp_cfg.get("drafter_path", None) or mpath)
+                own, seen = dict(rm.state_dict()), set()
+                with torch.no_grad():
+                    for key, t in model_io.iter_model_tensors(src, only=lambda k: model_io.from_hf_name(k).startswith("mtp.")):
+                        name = model_io.from_hf_name(key)
+                        if name in own:
+                            own[name].copy_(t.to(own[name].dtype))
+                            seen.add(name)
+                lost = [k for k in own if k.startswith("mtp.") and k not in seen]
+                if lost:
+                    raise KeyError(f"{src} lacks {len(lost)} drafter tensors (first: {lost[:4]}): set actor_rollout_ref.model.mtp.drafter_path")
             rc = RolloutConfig(num_blocks=int(ro.get("num_blocks", 2048)), block_size=int(ro.block_size), max_num_seqs=int(ro.max_num_seqs),
                                max_num_batched_tokens=int(ro.max_num_batched_tokens), enable_prefix_caching=bool(ro.enable_prefix_caching),
                                num_speculative_tokens=int(cfg.actor_rollout_ref.model.mtp.num_speculative_tokens) if cfg.actor_rollout_ref.model.mtp.enable_rollout else 0,

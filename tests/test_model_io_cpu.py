@@ -61,3 +61,43 @@ def test_loading_a_directory_that_does_not_match_raises(tmp_path):
     assert "model.visual.patch_embed.weight" in model_io.load_safetensors(os.path.join(out2, "model.safetensors"))
     missing, unexpected = model_io.load_model_dir(out2, fresh)
     assert not missing and all(k.startswith(("mtp.", "visual.")) for k in unexpected)
+
+
+def test_replica_takes_its_frozen_drafter_from_the_base_model_directory(tmp_path):
+    """A trained checkpoint is exported without the drafter; the replica reads the base directory's ``mtp.*`` tensors for it,
+    the rest strictly from the trained directory, and a weight sync without drafter tensors leaves the drafter as loaded."""
+    import torch
+
+    from pear_b200.models import io as model_io
+    from pear_b200.models.config import HybridConfig
+    from pear_b200.models.hybrid import HybridForCausalLM
+    from pear_b200.rollout.engine import EngineConfig, SamplingParams
+    from pear_b200.rollout.server import build_server, load_rollout_model
+
+    cfg = HybridConfig.tiny()
+    base = HybridForCausalLM(cfg, with_mtp=True).init_weights(1)
+    trained = HybridForCausalLM(cfg, with_mtp=False).init_weights(2)
+    model_io.save_model_dir(str(tmp_path / "base"), cfg, base.state_dict(), dtype=torch.float32, drop_mtp=False)
+    model_io.save_model_dir(str(tmp_path / "trained"), cfg, trained.state_dict(), dtype=torch.float32)  # no drafter inside
+    assert any(n.startswith("mtp.") for n in map(model_io.from_hf_name, model_io.model_tensor_names(str(tmp_path / "base"))))
+    assert not any(n.startswith("mtp.") for n in map(model_io.from_hf_name, model_io.model_tensor_names(str(tmp_path / "trained"))))
+    m = load_rollout_model(str(tmp_path / "trained"), drafter_path=str(tmp_path / "base"))
+    got, want_body, want_mtp = m.state_dict(), trained.state_dict(), base.state_dict()
+    assert m.mtp is not None and all(torch.equal(got[k], want_body[k]) for k in want_body)
+    assert all(torch.equal(got[k], want_mtp[k]) for k in want_mtp if k.startswith("mtp."))
+    assert load_rollout_model(str(tmp_path / "trained")).mtp is None          # no drafter anywhere: none built
+    assert load_rollout_model(str(tmp_path / "base")).mtp is not None         # a directory that carries its own
+    with pytest.raises(KeyError, match="holds no mtp"):
+        load_rollout_model(str(tmp_path / "trained"), drafter_path=str(tmp_path / "trained"))
+    # speculative decoding runs with it, and a sync of the trainer's (drafter-less) state leaves it frozen
+    srv = build_server(m, EngineConfig(num_blocks=64, max_num_seqs=2, num_speculative_tokens=2))
+    try:
+        r = srv.generate(list(range(3, 20)), SamplingParams(max_tokens=6, temperature=0.0))
+        assert len(r.output) == 6 and srv.engine.metrics["spec_drafted"] > 0
+        srv.pause(abort=True)
+        srv.update_weights({k: v * 0.5 for k, v in trained.state_dict().items()}, version=1)
+        srv.resume()
+        after = srv.engine.model.state_dict()
+        assert all(torch.equal(after[k].float(), want_mtp[k]) for k in want_mtp if k.startswith("mtp."))
+    finally:
+        srv.close()
