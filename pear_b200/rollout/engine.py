@@ -93,6 +93,8 @@ class EngineConfig:
     enable_prefix_caching: bool = True
     num_speculative_tokens: int = 0
     host_blocks: int = 0  # capacity of the host-DRAM tier in blocks (0: disabled)
+    host_bytes: int = 0  # ... or in bytes (the tier holds as many blocks as fit); `host_blocks` wins when both are set
+    host_numa_node: Optional[int] = None  # report the tier's locality to this node after it was touched
     state_interval_blocks: int = 0  # extra recurrent-state snapshots every N blocks during prefill (0: turn ends only)
     seed: int = 0
     fast_decode: bool = True  # on a GPU: decode / verify rows go through the batched GPU-resident step (rollout/fast_step.py)
@@ -108,8 +110,12 @@ class RolloutEngine:
         self.host = None
         has_state = len(model.config.gdn_layers) > 0
         self.blocks = BlockManager(cfg.num_blocks, cfg.block_size, n_slots, cfg.enable_prefix_caching, needs_state=has_state)
-        if cfg.host_blocks > 0:
-            self.host = HostTier(cfg.host_blocks, self.runner.kv_tensors(), self.runner.state_tensors())
+        host_blocks = cfg.host_blocks
+        if host_blocks <= 0 and cfg.host_bytes > 0:
+            host_blocks = cfg.host_bytes // max(1, HostTier.bytes_per_block(self.runner.kv_tensors(), self.runner.state_tensors()))
+        if host_blocks > 0:
+            self.host = HostTier(host_blocks, self.runner.kv_tensors(), self.runner.state_tensors())
+            self.host_locality = self.host.prefault(cfg.host_numa_node)
             self.blocks.host_tier = self.host
         self.waiting: deque[Request] = deque()
         self.running: list[Request] = []

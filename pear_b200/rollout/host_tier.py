@@ -57,6 +57,28 @@ class HostTier:
         self.stores = self.loads = self.evicted = 0
         self.release_block: Optional[Callable[[int], None]] = None
 
+    @staticmethod
+    def bytes_per_block(kv_caches: list[torch.Tensor], state_caches: Optional[list[torch.Tensor]] = None) -> int:
+        """Host bytes one cached block takes: its KV pages of every layer plus one recurrent-state snapshot per state pool."""
+        return sum(c[0].numel() * c.element_size() for c in list(kv_caches) + list(state_caches or []))
+
+    def prefault(self, node: Optional[int] = None) -> Optional[float]:
+        """Touch every page of the tier now (the first touch decides the NUMA node of a page, and a tier that faults its pages
+        in under load stalls the stores) and report the fraction of it that sits on ``node`` (None: not asked / no answer).
+        Upstream's sidecar waits until its tier is fully pinned and >= 95 % local before the replica serves
+        (pear/rollout/lmcache.py:152-187)."""
+        from ..utils.process import numa_locality
+
+        local, total = 0.0, 0
+        for t in self.kv_host + self.state_host:
+            t.view(torch.uint8).reshape(-1)[::4096].zero_()
+            if node is not None:
+                nbytes = t.numel() * t.element_size()
+                frac = numa_locality(t.data_ptr(), nbytes, node)
+                if frac is not None:
+                    local, total = local + frac * nbytes, total + nbytes
+        return (local / total) if total else None
+
     # -- store --------------------------------------------------------------------------------------------------------
     def schedule_store(self, block_table: list[int], hashes: list[Optional[bytes]], state_slots: list[Optional[int]],
                        session: Optional[str] = None) -> list[tuple]:

@@ -329,6 +329,8 @@ def main(argv=None) -> int:
     ap.add_argument("--num-blocks", type=int, default=2048)
     ap.add_argument("--max-num-seqs", type=int, default=64)
     ap.add_argument("--speculative-tokens", type=int, default=0)
+    ap.add_argument("--host-gb", type=float, default=0.0, help="host-DRAM tier of the KV / state cache in GiB (also: actor_rollout_ref.rollout.lmcache.enable=true l1_size_gb=...)")
+    ap.add_argument("--numa", default="auto", help="NUMA node to run on and allocate the host tier from: auto (the GPU's node), none, or a number")
     ap.add_argument("--drafter", default=None, help="directory whose mtp.* tensors are the (frozen) drafter of a model directory without one")
     ap.add_argument("--check", action="store_true", help="build the replica, answer one request and exit (no HTTP server)")
     ap.add_argument("--sync-rank", type=int, default=-1, help="this replica's rank in the weight-sync process group (-1: no group)")
@@ -348,7 +350,21 @@ def main(argv=None) -> int:
     import os
 
     device = "cuda" if torch.cuda.is_available() else "cpu"
-    ecfg = EngineConfig(num_blocks=args.num_blocks, max_num_seqs=max_seqs, num_speculative_tokens=args.speculative_tokens)
+    host_gb = args.host_gb
+    if not host_gb and str(kv.get("actor_rollout_ref.rollout.lmcache.enable", "false")).lower() == "true":
+        host_gb = float(kv.get("actor_rollout_ref.rollout.lmcache.l1_size_gb", 700))
+    # bind to the GPU's NUMA node before anything large is allocated: the pinned host tier is touched by this process, and a
+    # tier on the far socket halves the copy bandwidth of every store and load
+    node = None
+    if args.numa != "none":
+        from ..utils.process import gpu_numa_node, set_numa_affinity, visible_gpu_index
+
+        local = int(os.environ.get("LOCAL_RANK", "0"))
+        node = int(args.numa) if args.numa != "auto" else (gpu_numa_node(visible_gpu_index(local)) if device == "cuda" else None)
+        if node is not None and not set_numa_affinity(node):
+            node = None
+    ecfg = EngineConfig(num_blocks=args.num_blocks, max_num_seqs=max_seqs, num_speculative_tokens=args.speculative_tokens,
+                        host_bytes=int(host_gb * (1 << 30)), host_numa_node=node)
     tp_rank, tp_world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     if tp_world > 1:  # one rank of a tensor-parallel replica (started under torch.distributed.run): lock-step with its peers
         import torch.distributed as dist

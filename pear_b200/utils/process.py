@@ -67,19 +67,77 @@ class WorkerProcess:
             self.proc.join(grace_s)
 
 
+_SYS_SET_MEMPOLICY, _SYS_MOVE_PAGES = 238, 279  # x86_64 system call numbers
+_MPOL_PREFERRED = 1
+
+
+def node_cpus(node: int) -> list[int]:
+    """CPUs of a NUMA node from sysfs (``0-7,16-23`` notation)."""
+    with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+        text = f.read().strip()
+    cpus: list[int] = []
+    for part in filter(None, text.split(",")):
+        lo, _, hi = part.partition("-")
+        cpus += list(range(int(lo), int(hi or lo) + 1))
+    return cpus
+
+
 def set_numa_affinity(node: int) -> bool:
-    """Bind this process's CPUs to a NUMA node through libnuma (loaded by its runtime name). False if unavailable."""
-    for name in ("libnuma.so.1", "libnuma.so"):
-        try:
-            numa = ctypes.CDLL(name)
-        except OSError:
-            continue
-        if numa.numa_available() < 0:
+    """Run this process on the CPUs of ``node`` and prefer its memory for what it allocates from now on (pinned host buffers
+    land on the node of the thread that first touches them). Plain system calls (``sched_setaffinity``, ``set_mempolicy``), so
+    no libnuma is needed (upstream binds its cache sidecar with ``numactl --cpunodebind --membind``:
+    pear/rollout/lmcache.py:21-221). False when the platform refuses or has no such node."""
+    import platform
+
+    try:
+        cpus = node_cpus(node)
+        if not cpus:
             return False
-        numa.numa_run_on_node(ctypes.c_int(node))
-        numa.numa_set_preferred(ctypes.c_int(node))
-        return True
-    return False
+        os.sched_setaffinity(0, cpus)
+        if platform.machine() != "x86_64":
+            return True  # CPU binding only: first touch then places the memory
+        libc = ctypes.CDLL(ctypes.util.find_library("c") or "libc.so.6", use_errno=True)
+        libc.syscall.restype = ctypes.c_long
+        words = node // 64 + 1
+        mask = (ctypes.c_ulong * words)()
+        mask[node // 64] = 1 << (node % 64)
+        rc = libc.syscall(ctypes.c_long(_SYS_SET_MEMPOLICY), ctypes.c_int(_MPOL_PREFERRED), ctypes.byref(mask), ctypes.c_ulong(64 * words + 1))
+        return rc == 0
+    except (OSError, ValueError):
+        return False
+
+
+def numa_locality(address: int, nbytes: int, node: int, samples: int = 512, page: int = 4096) -> Optional[float]:
+    """Fraction of (sampled) resident pages of ``[address, address + nbytes)`` that sit on ``node``, from the ``move_pages``
+    query form; None when the platform does not answer. Upstream waits until its host tier is >= 95 % local to the GPUs' node."""
+    import platform
+
+    if platform.machine() != "x86_64" or nbytes <= 0:
+        return None
+    try:
+        libc = ctypes.CDLL(ctypes.util.find_library("c") or "libc.so.6", use_errno=True)
+        libc.syscall.restype = ctypes.c_long
+        n_pages = max(1, nbytes // page)
+        count = min(samples, n_pages)
+        first = address - address % page
+        pages = (ctypes.c_void_p * count)(*[first + (i * n_pages // count) * page for i in range(count)])
+        status = (ctypes.c_int * count)()
+        rc = libc.syscall(ctypes.c_long(_SYS_MOVE_PAGES), ctypes.c_int(0), ctypes.c_ulong(count), pages, None, status, ctypes.c_int(0))
+        if rc != 0:
+            return None
+        resident = [s for s in status if s >= 0]
+        return (sum(s == node for s in resident) / len(resident)) if resident else None
+    except OSError:
+        return None
+
+
+def visible_gpu_index(local_index: int = 0) -> int:
+    """The machine-wide index of this process's ``local_index``-th GPU (``CUDA_VISIBLE_DEVICES`` renumbers them)."""
+    vis = [v for v in os.environ.get("CUDA_VISIBLE_DEVICES", "").split(",") if v.strip()]
+    try:
+        return int(vis[local_index]) if vis else local_index
+    except (ValueError, IndexError):
+        return local_index
 
 
 def gpu_numa_node(gpu_index: int) -> Optional[int]:

@@ -168,3 +168,40 @@ def test_lookup_keeps_matched_chain_blocks_out_of_eviction():
         assert float(kv[0][blk].mean()) == float(i + 1), "a chain block was overwritten by a promotion"
     assert hit.tokens in (4, 8)  # the head always; the tail as far as free blocks allowed
     mgr.release(y)
+
+
+def test_host_tier_sized_in_bytes_prefaulted_and_local_to_the_bound_node():
+    """``host_bytes`` holds as many blocks as fit; the tier is touched at construction; after binding the process to NUMA node 0
+    the tier's resident pages are reported on it (the platform may not answer: then no figure, never a wrong one)."""
+    import os
+
+    from pear_b200.rollout.host_tier import HostTier
+    from pear_b200.utils.process import node_cpus, numa_locality, set_numa_affinity, visible_gpu_index
+
+    before = os.sched_getaffinity(0)
+    try:
+        bound = os.path.exists("/sys/devices/system/node/node0/cpulist") and set_numa_affinity(0)
+        if bound:
+            assert os.sched_getaffinity(0) == set(node_cpus(0)) & before or os.sched_getaffinity(0) == set(node_cpus(0))
+        assert not set_numa_affinity(4095)  # no such node: refused, nothing changed
+        model = HybridForCausalLM(HybridConfig.tiny(), with_mtp=False).init_weights(0)
+        probe = RolloutEngine(model, EngineConfig(num_blocks=32, max_num_seqs=2))
+        per_block = HostTier.bytes_per_block(probe.runner.kv_tensors(), probe.runner.state_tensors())
+        assert per_block > 0
+        eng = RolloutEngine(model, EngineConfig(num_blocks=32, max_num_seqs=2, host_bytes=10 * per_block + per_block // 2, host_numa_node=0 if bound else None))
+        assert eng.host is not None and eng.host.capacity == 10
+        if bound and eng.host_locality is not None:
+            assert eng.host_locality >= 0.95
+        t = torch.ones(1 << 20)
+        frac = numa_locality(t.data_ptr(), t.numel() * 4, 0)
+        assert frac is None or 0.0 <= frac <= 1.0
+    finally:
+        os.sched_setaffinity(0, before)
+    os.environ["CUDA_VISIBLE_DEVICES"], saved = "5,2", os.environ.get("CUDA_VISIBLE_DEVICES")
+    try:
+        assert visible_gpu_index(0) == 5 and visible_gpu_index(1) == 2
+    finally:
+        if saved is None:
+            os.environ.pop("CUDA_VISIBLE_DEVICES")
+        else:
+            os.environ["CUDA_VISIBLE_DEVICES"] = saved
