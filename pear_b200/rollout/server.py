@@ -329,7 +329,7 @@ def main(argv=None) -> int:
     ap.add_argument("--num-blocks", type=int, default=2048)
     ap.add_argument("--max-num-seqs", type=int, default=64)
     ap.add_argument("--speculative-tokens", type=int, default=0)
-    ap.add_argument("--host-gb", type=float, default=0.0, help="host-DRAM tier of the KV / state cache in GiB (also: actor_rollout_ref.rollout.lmcache.enable=true l1_size_gb=...)")
+    ap.add_argument("--host-gb", type=float, default=0.0, help="host-DRAM tier of the KV / state cache in GiB (also: actor_rollout_ref.rollout.custom.lmcache.enable=true and .l1_size_gb=...)")
     ap.add_argument("--numa", default="auto", help="NUMA node to run on and allocate the host tier from: auto (the GPU's node), none, or a number")
     ap.add_argument("--drafter", default=None, help="directory whose mtp.* tensors are the (frozen) drafter of a model directory without one")
     ap.add_argument("--check", action="store_true", help="build the replica, answer one request and exit (no HTTP server)")
@@ -351,8 +351,8 @@ def main(argv=None) -> int:
 
     device = "cuda" if torch.cuda.is_available() else "cpu"
     host_gb = args.host_gb
-    if not host_gb and str(kv.get("actor_rollout_ref.rollout.lmcache.enable", "false")).lower() == "true":
-        host_gb = float(kv.get("actor_rollout_ref.rollout.lmcache.l1_size_gb", 700))
+    if not host_gb and str(kv.get("actor_rollout_ref.rollout.custom.lmcache.enable", "false")).lower() == "true":
+        host_gb = float(kv.get("actor_rollout_ref.rollout.custom.lmcache.l1_size_gb", 700))
     # bind to the GPU's NUMA node before anything large is allocated: the pinned host tier is touched by this process, and a
     # tier on the far socket halves the copy bandwidth of every store and load
     node = None

@@ -171,7 +171,7 @@ def build_stack(cfg, replicas: int = 1, device: str = "cpu", env_families: Optio
                                max_num_batched_tokens=int(ro.max_num_batched_tokens), enable_prefix_caching=bool(ro.enable_prefix_caching),
                                num_speculative_tokens=int(cfg.actor_rollout_ref.model.mtp.num_speculative_tokens) if cfg.actor_rollout_ref.model.mtp.enable_rollout else 0,
                                host_blocks=int(ro.get("host_blocks", 0)),
-                               host_bytes=int(float(ro.lmcache.l1_size_gb) * (1 << 30)) if bool(ro.lmcache.enable) else 0, seed=int(cfg.trainer.seed) + i)
+                               host_bytes=int(float(ro.custom.lmcache.l1_size_gb) * (1 << 30)) if bool(ro.custom.lmcache.enable) else 0, seed=int(cfg.trainer.seed) + i)
             servers.append(build_server(rm, rc, device, name=f"replica-{i}", fp32_modules=tuple(ro.fp32_modules)))
         families = env_families or {"synthetic": {"env_path": "pear_b200.envs.synthetic.SyntheticEnv", "num_processes": 2,
                                                   "env_kwargs": {"hidden": mcfg.hidden_size, "tokens_per_image": 4}}}
