@@ -20,6 +20,7 @@ def main(argv=None) -> int:
     ap.add_argument("--rollout-tp", type=int, default=2)
     ap.add_argument("--dry-run", action="store_true")
     ap.add_argument("--master-port", type=int, default=29500, help="rendezvous of the trainer ranks (replica i of several GPUs uses the next ports)")
+    ap.add_argument("--replica-master-port", type=int, default=0, help="rendezvous of the ranks of replica 0 (replica i: + i; default: master-port + 1)")
     ap.add_argument("--rollout-port", type=int, default=8100)
     ap.add_argument("--env-port", type=int, default=8200)
     ap.add_argument("--sync-port", type=int, default=29650, help="rendezvous of the weight-sync world")
@@ -30,7 +31,7 @@ def main(argv=None) -> int:
         out = []
         for p in plans:
             for i in range(1 if p.role == "trainer" else p.processes):
-                cmd, env = command(p, i, args.master_port)
+                cmd, env = command(p, i, args.master_port, args.replica_master_port)
                 out.append({"role": p.role, "index": i, "cmd": cmd, "env": env})
         print(json.dumps(out, indent=1))
         return 0
@@ -48,7 +49,7 @@ def main(argv=None) -> int:
     try:
         for p in plans:
             for i in range(1 if p.role == "trainer" else p.processes):
-                cmd, env = command(p, i, args.master_port)
+                cmd, env = command(p, i, args.master_port, args.replica_master_port)
                 # a session per role: the role's own children (torch.distributed.run workers, environment processes) form one
                 # process group with it, which is what gets signalled at the end
                 # the role's GPU set is the plan's; every other variable of `gpu_process_env` is a default the caller may override

@@ -73,7 +73,9 @@ def gpu_process_env(gpu_ids: list[int], threads: int = 8, cache_dir: str = "") -
     return env
 
 
-def command(plan: RolePlan, index: int, master_port: int = 29500) -> tuple[list[str], dict[str, str]]:
+def command(plan: RolePlan, index: int, master_port: int = 29500, replica_master_port: int = 0) -> tuple[list[str], dict[str, str]]:
+    """``replica_master_port``: rendezvous of replica 0's ranks when a replica has several (replica i: + i); default: the ports
+    after the trainer's."""
     env = gpu_process_env(plan.gpu_ids(index)) if plan.gpus_per_process else {}
     if plan.role == "trainer":
         cmd = ["python", "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={plan.processes}", "--master-addr", "127.0.0.1",
@@ -85,7 +87,7 @@ def command(plan: RolePlan, index: int, master_port: int = 29500) -> tuple[list[
             tp = max(1, plan.gpus_per_process)
             if tp > 1:  # the replica's ranks are a world of their own: rank 0 serves, the others follow in lock-step
                 cmd = ["python", "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={tp}", "--master-addr", "127.0.0.1",
-                       "--master-port", str(master_port + 1 + index), "-m", plan.module] + plan.args
+                       "--master-port", str((replica_master_port or master_port + 1) + index), "-m", plan.module] + plan.args
             cmd += ["--port", str(plan.port + index), "--name", f"replica-{index}", "--sync-rank", str(1 + index * tp)]
         elif plan.role == "env":
             cmd += ["--port", str(plan.port + index)]

@@ -82,9 +82,13 @@ class RemoteReplica:
         r.raise_for_status()
         return r.json()
 
-    def wait_ready(self, timeout_s: float = 300.0) -> None:
+    def wait_ready(self, timeout_s: float = 300.0, alive=None) -> None:
+        """Block until the replica answers ``/health``. ``alive``: a callable that tells whether the replica's process still
+        runs (a launcher's ``lambda: proc.poll() is None``): a replica that died while starting is reported at once."""
         t0 = time.time()
         while True:
+            if alive is not None and not alive():
+                raise RuntimeError(f"{self.name}: the replica process ended before it answered on {self.url}/health")
             try:
                 if self._session().get(self.url + "/health", timeout=5).json().get("ok"):
                     return

@@ -19,6 +19,21 @@ def free_port(host: str = "127.0.0.1") -> int:
         return s.getsockname()[1]
 
 
+def free_ports(n: int, host: str = "127.0.0.1") -> list[int]:
+    """``n`` DISTINCT free ports: all sockets stay open until every port is known (two calls of ``free_port`` in a row may be
+    handed the same port)."""
+    socks = []
+    try:
+        for _ in range(n):
+            s = socket.socket(socket.AF_INET, socket.SOCK_STREAM)
+            s.bind((host, 0))
+            socks.append(s)
+        return [s.getsockname()[1] for s in socks]
+    finally:
+        for s in socks:
+            s.close()
+
+
 def die_with_parent(sig: int = signal.SIGTERM) -> None:
     """Ask the kernel to signal this process when its parent exits (Linux prctl PR_SET_PDEATHSIG = 1)."""
     try:

@@ -62,18 +62,14 @@ def test_roles_recipe_runs_as_processes(tmp_path):
     host, monitor) trains one step on CPU; the launcher leaves no role behind when the trainer exits."""
     import json
     import os
-    import socket
     import subprocess
 
-    def free_port() -> int:
-        with socket.socket() as s:
-            s.bind(("127.0.0.1", 0))
-            return s.getsockname()[1]
+    from pear_b200.utils.process import free_ports
 
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     run = str(tmp_path / "run")
-    env = dict(os.environ, PYTHONPATH=root, RUN=run, STEPS="1", PORT=str(free_port()), ROLLOUT_PORT=str(free_port()), ENV_PORT=str(free_port()),
-               SYNC_PORT=str(free_port()), OMP_NUM_THREADS="2")
+    env = dict(os.environ, PYTHONPATH=root, RUN=run, STEPS="1", OMP_NUM_THREADS="2",
+               **dict(zip(("PORT", "ROLLOUT_PORT", "ENV_PORT", "SYNC_PORT", "REPLICA_PORT"), map(str, free_ports(5)))))
     proc = subprocess.run(["bash", os.path.join(root, "examples", "tiny_roles_cpu.sh")], cwd=root, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
                           text=True, timeout=500, start_new_session=True)
     assert proc.returncode == 0, proc.stdout[-4000:]

@@ -2,7 +2,6 @@
 through a process group it shares with the trainer side (gloo here; NCCL or the NVSwitch transport on GPUs)."""
 
 import os
-import socket
 import subprocess
 import sys
 import time
@@ -16,10 +15,7 @@ from pear_b200.rollout.remote import RemoteReplica, decode_embeds, encode_embeds
 from pear_b200.rollout.server import load_rollout_model
 
 
-def _free_port() -> int:
-    with socket.socket() as s:
-        s.bind(("127.0.0.1", 0))
-        return s.getsockname()[1]
+from pear_b200.utils.process import free_ports
 
 
 def _greedy(model, prompt, n):
@@ -42,7 +38,7 @@ def test_embeds_travel_as_bf16_rows():
 
 @pytest.mark.timeout(300)
 def test_replica_process_serves_requests_and_receives_weights():
-    http_port, sync_port = _free_port(), _free_port()
+    http_port, sync_port = free_ports(2)
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     env = dict(os.environ, PYTHONPATH=root, CUDA_VISIBLE_DEVICES="")
     proc = subprocess.Popen([sys.executable, "-m", "pear_b200.rollout.server", "--model", "preset:tiny", "--port", str(http_port), "--num-blocks", "128",
@@ -51,7 +47,7 @@ def test_replica_process_serves_requests_and_receives_weights():
     try:
         group = StandaloneGroup(f"127.0.0.1:{sync_port}", 0, 2, "gloo")  # the trainer side of the weight-sync world
         replica = RemoteReplica(f"http://127.0.0.1:{http_port}", name="replica-0")
-        replica.wait_ready(120)
+        replica.wait_ready(120, alive=lambda: proc.poll() is None)
         model = load_rollout_model("preset:tiny", device="cpu")  # the same seeded weights the replica process built
         prompt = list(range(3, 40))
         p = SamplingParams(max_tokens=6, temperature=0.0, topk_logprobs=3)
@@ -87,7 +83,7 @@ def test_training_entry_drives_a_replica_process(tmp_path):
     from pear_b200.config.loader import compose
     from pear_b200.train.main import RunConfig, build_stack
 
-    http_port, sync_port = _free_port(), _free_port()
+    http_port, sync_port = free_ports(2)
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     env = dict(os.environ, PYTHONPATH=root, CUDA_VISIBLE_DEVICES="")
     proc = subprocess.Popen([sys.executable, "-m", "pear_b200.rollout.server", "--model", "preset:tiny", "--port", str(http_port), "--num-blocks", "512",
@@ -123,7 +119,7 @@ def test_training_entry_drives_a_replica_process(tmp_path):
 def test_tensor_parallel_replica_runs_in_lock_step_behind_one_endpoint():
     """Two gloo ranks form one replica: rank 0 serves HTTP and broadcasts the control events, both ranks step together; each
     rank receives the weight sync itself and keeps its shard. Tokens equal the unsharded model's before and after a sync."""
-    http_port, sync_port, tp_port = _free_port(), _free_port(), _free_port()
+    http_port, sync_port, tp_port = free_ports(3)
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     env = dict(os.environ, PYTHONPATH=root, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="2")
     proc = subprocess.Popen([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
@@ -134,7 +130,7 @@ def test_tensor_parallel_replica_runs_in_lock_step_behind_one_endpoint():
     try:
         group = StandaloneGroup(f"127.0.0.1:{sync_port}", 0, 3, "gloo")
         replica = RemoteReplica(f"http://127.0.0.1:{http_port}")
-        replica.wait_ready(180)
+        replica.wait_ready(180, alive=lambda: proc.poll() is None)
         model = load_rollout_model("preset:tiny", device="cpu")
         prompts = [list(range(3, 40)), list(range(50, 61))]
         p = SamplingParams(max_tokens=6, temperature=0.0)
@@ -173,12 +169,12 @@ def test_a_lost_replica_is_named_before_the_sync_starts(how):
     for inside a broadcast."""
     from pear_b200.parallel.heartbeat import PeerLost
 
-    http_port, sync_port = _free_port(), _free_port()
+    http_port, sync_port = free_ports(2)
     proc = _replica(http_port, sync_port)
     try:
         group = StandaloneGroup(f"127.0.0.1:{sync_port}", 0, 2, "gloo")
         replica = RemoteReplica(f"http://127.0.0.1:{http_port}")
-        replica.wait_ready(120)
+        replica.wait_ready(120, alive=lambda: proc.poll() is None)
         sync = WeightSync(SyncConfig(bucket_megabytes=1, rollout_dtype=torch.bfloat16), BroadcastTransport(group, 0, "cpu"), [replica],
                           heartbeat=group.heartbeat(timeout_s=2.5))
         state = load_rollout_model("preset:tiny", device="cpu").state_dict()
