@@ -5,8 +5,11 @@ The order of upstream ``pear/trainer/main.py:12-32`` and ``runner.py:22-88``: co
 environment server pools and the agent-loop manager, ``fit``; on the way out (also on error) cancel in-flight prompt
 groups, stop the servers and close the queue.
 
-One process hosts one trainer rank. With ``WORLD_SIZE > 1`` (torchrun) the ranks form the FSDP / sequence-parallel
-group; rank 0 additionally hosts the rollout replicas and environment pools of the single-node recipes.
+One process hosts one trainer rank. With ``WORLD_SIZE > 1`` (torchrun) the ranks form the FSDP / HSDP / sequence-parallel
+groups; rank 0 drives the rollouts. With ``rollout.checkpoint_engine.replica_urls`` set (what ``launch/launch.py`` passes)
+the replicas are processes of their own on their own GPUs: rank 0 reaches them over HTTP (``rollout/remote.py``) and sends
+weights through a process group that holds only itself and the replica ranks (``weight_sync.StandaloneGroup``), checked by a
+heartbeat before every sync. Without it rank 0 hosts the replicas in-process (the single-process recipes and the tests).
 """
 
 from __future__ import annotations
