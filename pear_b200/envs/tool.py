@@ -29,6 +29,7 @@ def load_system_prompt() -> str:
 class Observation:
     text: str
     frames: list[np.ndarray] = field(default_factory=list)  # one [tokens, hidden] block per camera, in camera order
+    cameras: list[str] = field(default_factory=list)  # the cameras' names, in the same order: each picture is rendered under its label
     done: bool = False
     success: bool = False
     info: dict = field(default_factory=dict)
@@ -37,11 +38,9 @@ class Observation:
 def render_observation(result: dict) -> Observation:
     obs = result["observation"]
     lines = [json.dumps(obs["state"], sort_keys=True), obs.get("reminder", "")]
-    frames = []
-    for cam in sorted(obs.get("frames", {})):
-        lines.append(f"[{cam}]")
-        frames.append(np.asarray(obs["frames"][cam]))
-    return Observation("\n".join(lines), frames, bool(result.get("done")), bool(result.get("success")), dict(result.get("info", {})))
+    cameras = sorted(obs.get("frames", {}))
+    frames = [np.asarray(obs["frames"][cam]) for cam in cameras]
+    return Observation("\n".join(lines), frames, cameras, bool(result.get("done")), bool(result.get("success")), dict(result.get("info", {})))
 
 
 class EnvTool:

@@ -73,7 +73,7 @@ class AgentLoop:
         if first:
             ids += self.tok.render_turn("system", self.system_prompt)
         n_img_tokens = obs.frames[0].shape[0] if obs.frames else 0
-        turn = self.tok.render_turn("user", obs.text, images=len(obs.frames), image_tokens=n_img_tokens)
+        turn = self.tok.render_turn("user", obs.text, images=len(obs.frames), image_tokens=n_img_tokens, labels=obs.cameras or None)
         base = len(ep.tokens) + len(ids)
         # positions of the image pad runs inside the turn -> embedding blocks
         j, f = 0, 0

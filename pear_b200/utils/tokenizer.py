@@ -8,6 +8,7 @@ specials follow. A vocabulary larger than the tokenizer's is fine (the tail ids 
 from __future__ import annotations
 
 from dataclasses import dataclass
+from typing import Optional
 
 SPECIALS = ["<|pad|>", "<|im_start|>", "<|im_end|>", "<think>", "</think>", "<|vision_start|>", "<|vision_end|>",
             "<|image_pad|>", "<|mask|>", "<|eos|>"]
@@ -58,10 +59,14 @@ class ByteTokenizer:
         return "".join(parts)
 
     # -- chat template (the one the agent loop renders turn by turn) --------------------------------------------------
-    def render_turn(self, role: str, text: str, images: int = 0, image_tokens: int = 0) -> list[int]:
-        """``<|im_start|>role\\n`` text [vision blocks] ``<|im_end|>\\n``; an image is a run of pad ids between markers."""
+    def render_turn(self, role: str, text: str, images: int = 0, image_tokens: int = 0, labels: Optional[list[str]] = None) -> list[int]:
+        """``<|im_start|>role\\n`` text [vision blocks] ``<|im_end|>\\n``; an image is a run of pad ids between markers. With
+        ``labels`` (one per image) every image follows a line ``[label]`` of its own, so the model reads which camera a picture
+        is from right before it (upstream: pear/envs/tool.py:114-127)."""
         ids = [self.special_ids["<|im_start|>"]] + self.encode(role + "\n") + self.encode(text)
-        for _ in range(images):
+        for i in range(images):
+            if labels is not None:
+                ids += self.encode(f"\n[{labels[i]}]\n")
             ids += [self.special_ids["<|vision_start|>"]] + [self.image_pad_id] * image_tokens + [self.special_ids["<|vision_end|>"]]
         return ids + [self.special_ids["<|im_end|>"]] + self.encode("\n")
 

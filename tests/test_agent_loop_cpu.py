@@ -157,3 +157,26 @@ def test_manager_runs_groups_round_robin(pool):
         assert sorted(q.keys()) == ["gA/0", "gA/1", "gA/2", "gA/3", "gB/0", "gB/1"]
     finally:
         mgr.close()
+
+
+def test_first_turn_prompt_rendering_is_the_stored_text():
+    """The text a policy reads at the start of an episode, byte for byte: system prompt, the observation's state and reminder,
+    each camera's picture under its label, the assistant header. A change of the template shows up as a diff of the stored
+    rendering, not as a silent shift of what checkpoints were trained on."""
+    import os
+
+    import numpy as np
+
+    from pear_b200.envs.tool import load_system_prompt, render_observation
+
+    tok = ByteTokenizer()
+    res = {"observation": {"state": {"gripper": "open", "cube": [0.1, 0.2, 0.0], "step": 3}, "reminder": "Answer with one JSON action in a fenced json block.",
+                           "frames": {"wrist": np.zeros((2, 8)), "front": np.ones((2, 8))}}, "done": False}
+    obs = render_observation(res)
+    assert obs.cameras == ["front", "wrist"] and obs.frames[0].sum() == 16  # frames in the cameras' (sorted) order
+    ids = (tok.render_turn("system", load_system_prompt()) + tok.render_turn("user", obs.text, images=2, image_tokens=2, labels=obs.cameras)
+           + tok.generation_prompt())
+    with open(os.path.join(os.path.dirname(__file__), "golden", "first_turn_prompt.txt")) as f:
+        assert tok.decode(ids) == f.read()
+    text = tok.decode(ids)
+    assert text.index("[front]") < text.index("<|vision_start|>") < text.index("[wrist]") < text.rindex("<|vision_start|>")

@@ -173,3 +173,57 @@ def test_memory_plan_of_the_27b_recipe_fits_and_names_what_does_not():
     with pytest.raises(MemoryError):  # nor can eight hold every layer's intermediates of 16k-token sequences without checkpointing
         plan(cfg, EngineConfig(ulysses_sequence_parallel_size=8, enable_gradient_checkpointing=False), 8 * 16384, 8)
     assert "device total" in p.table()
+
+
+def test_engine_installs_the_family_kernels_in_order_and_runs_the_step_through_them():
+    """The hooks of a model family's training kernels are called in the order the GPU backend relies on: config check before
+    the model exists, install, model check, GPU backend (only when asked), checkpointing; the step runs inside ``run_checked``,
+    whose rerun path zeroes the gradients first."""
+    from pear_b200.models.kernels import TrainingKernels
+
+    calls = []
+
+    class Recording(TrainingKernels):
+        @classmethod
+        def check_config(cls, engine_config):
+            calls.append("check_config")
+
+        @classmethod
+        def install(cls, module, fp32_residual, use_fused_kernels, fused_kernels_backend):
+            calls.append(("install", fp32_residual, use_fused_kernels, type(module).__name__))
+
+        @classmethod
+        def check_model(cls, module, use_remove_padding, use_fused_kernels, fused_kernels_backend):
+            calls.append(("check_model", use_remove_padding))
+
+        @classmethod
+        def install_gpu_backend(cls, module):
+            calls.append("install_gpu_backend")
+
+        @classmethod
+        def install_checkpointing(cls, module):
+            calls.append("install_checkpointing")
+
+        @classmethod
+        def run_checked(cls, run, before_rerun):
+            calls.append("run_checked")
+            first = run()  # a run whose result is thrown away (as after an overflow), then the rerun
+            before_rerun()
+            calls.append("rerun")
+            return run()
+
+    cfg = HybridConfig.tiny()
+    ecfg = _ecfg()
+    batches = [make_batch(cfg, 0)]
+    want, want_norm = reference_step(cfg, ecfg, batches, seed=5)
+    eng = TrainEngine(cfg, ecfg, kernels=Recording, seed=5)
+    assert calls == ["check_config", ("install", True, True, "HybridForCausalLM"), ("check_model", True), "install_checkpointing"]
+    eng.forward_backward_batch(batches)
+    assert calls[-2:] == ["run_checked", "rerun"]
+    m = eng.optimizer_step()  # the thrown-away run's gradients were cleared: the step equals a single run's
+    assert abs(m["actor/grad_norm"] - want_norm) < 1e-4 * max(1.0, want_norm)
+    calls.clear()
+    ecfg2 = _ecfg()
+    ecfg2.use_gpu_backend = True
+    TrainEngine(cfg, ecfg2, kernels=Recording, seed=5)
+    assert calls.index("install_gpu_backend") == calls.index(("check_model", True)) + 1 and calls[-1] == "install_checkpointing"
