@@ -114,7 +114,9 @@ def main(argv=None) -> int:
     ecfg.update({"num_speculative_tokens": int(dict(cfg.speculative).get("num_speculative_tokens", 0))})
     kernels.configure_server(ecfg, int(cfg.engine.max_num_seqs), int(ecfg.get("max_num_batched_tokens", 8192)))
     engine = kernels.build_engine(str(cfg.model), cfg.draft, ecfg)
-    server = DeployServer(engine, name=str(cfg.server.served_model_name))
+    from ..utils.tokenizer import load_tokenizer
+
+    server = DeployServer(engine, tokenizer=load_tokenizer(str(cfg.model)), name=str(cfg.server.served_model_name))
     import uvicorn
     uvicorn.run(server.http_app(), host=str(cfg.server.host), port=int(cfg.server.port), log_level="warning")
     return 0

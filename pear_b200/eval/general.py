@@ -151,7 +151,7 @@ class BenchmarkRun:
     def params(self, max_tokens: int) -> SamplingParams:
         s = self.sampling
         return SamplingParams(max_tokens=max_tokens, temperature=float(s.get("temperature", 1.0)), top_p=float(s.get("top_p", 1.0)),
-                              top_k=int(s.get("top_k", 0)), stop_token_ids=(self.tok.eos_id,))
+                              top_k=int(s.get("top_k", 0)), stop_token_ids=(self.tok.eos_id,) + tuple(getattr(self.tok, "extra_stop_ids", ())))
 
     def sample(self, store: SampleStore, bench: dict, item: Item, repeat: int) -> None:
         prompt = self.tok.render_turn("user", item.prompt) + self.tok.generation_prompt()
@@ -330,7 +330,7 @@ def main(argv=None) -> int:
     import argparse
 
     from ..config.loader import compose
-    from ..utils.tokenizer import ByteTokenizer
+    from ..utils.tokenizer import load_tokenizer
 
     ap = argparse.ArgumentParser(description="general-capability evaluation")
     sub = ap.add_subparsers(dest="command", required=True)
@@ -338,6 +338,7 @@ def main(argv=None) -> int:
     r.add_argument("--replicas", default="", help="url,url,... of rollout replica processes")
     r.add_argument("--model", default="", help="model directory or preset:<name> for in-process replicas (when --replicas is empty)")
     r.add_argument("--num-replicas", type=int, default=1)
+    r.add_argument("--tokenizer", default="", help="directory with the model's tokenizer.json (default: --model; the byte tokenizer without one)")
     r.add_argument("--model-name", default="", help="the name the samples are kept under (default: --model or the first replica URL)")
     r.add_argument("--out", required=True)
     r.add_argument("--dataset-dir", required=True)
@@ -391,7 +392,7 @@ def main(argv=None) -> int:
             local.append(build_server(load_rollout_model(args.model, with_mtp=False), EngineConfig(), name=f"replica-{i}"))
         servers = local
     try:
-        BenchmarkRun(cfg, LeastInFlightRouter(servers), ByteTokenizer(), args.model_name or args.model or args.replicas.split(",")[0],
+        BenchmarkRun(cfg, LeastInFlightRouter(servers), load_tokenizer(args.tokenizer or args.model), args.model_name or args.model or args.replicas.split(",")[0],
                      args.out, args.dataset_dir, args.only, args.limit).run()
     finally:
         for s in servers:

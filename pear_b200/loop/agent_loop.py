@@ -139,7 +139,7 @@ class AgentLoop:
                         continue
                     embeds, mask = self._embeds(ep, hidden)
                     params = SamplingParams(max_tokens=left, temperature=cfg.temperature, top_p=cfg.top_p,
-                                            topk_logprobs=cfg.topk_heads, stop_token_ids=(self.tok.eos_id,))
+                                            topk_logprobs=cfg.topk_heads, stop_token_ids=(self.tok.eos_id,) + tuple(getattr(self.tok, "extra_stop_ids", ())))
                     t0 = time.time()
                     req = self.router.generate(list(ep.tokens), params, session=f"{ep.uid}/{ep.session}", embeds=embeds, embeds_mask=mask)
                     if req.finish == FinishReason.ABORTED:

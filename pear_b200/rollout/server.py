@@ -341,6 +341,7 @@ def main(argv=None) -> int:
                     help="nvswitch: pull this replica's shard out of the sender's symmetric staging buffer; gloo / nccl: broadcast")
     args, overrides = ap.parse_known_args(argv)
     from ..utils.process import die_with_parent, dump_stacks_on_signal
+    from ..utils.tokenizer import load_tokenizer
 
     die_with_parent()
     dump_stacks_on_signal()
@@ -404,7 +405,7 @@ def main(argv=None) -> int:
         signal.signal(signal.SIGTERM, lambda *_: None)
         signal.signal(signal.SIGINT, lambda *_: None)
         # a request that can no longer finish (a peer rank is gone) must not keep a terminated replica alive
-        uvicorn.run(server.http_app(), host=args.host, port=args.port, log_level="warning", timeout_graceful_shutdown=3)
+        uvicorn.run(server.http_app(load_tokenizer(path)), host=args.host, port=args.port, log_level="warning", timeout_graceful_shutdown=3)
         return 0
     finally:
         leave = getattr(server, "leave_sync_world", None)

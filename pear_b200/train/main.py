@@ -182,7 +182,10 @@ def build_stack(cfg, replicas: int = 1, device: str = "cpu", env_families: Optio
                                topk_heads=tcfg.topk_heads, max_model_len=int(ro.max_model_len), log_dir=os.environ.get("PEAR_LOG_DIR"),
                                synthetic_turns=int(ro.multi_turn.synthetic_turns), turn_max_tokens=int(ro.multi_turn.turn_max_tokens),
                                synthetic_reward=ro.multi_turn.synthetic_reward)
-        manager = AgentLoopManager(servers, mcfg.hidden_size, families, acfg, queue, num_workers=int(ro.agent.num_workers))
+        from ..utils.tokenizer import load_tokenizer
+
+        manager = AgentLoopManager(servers, mcfg.hidden_size, families, acfg, queue, num_workers=int(ro.agent.num_workers),
+                                   tokenizer=load_tokenizer(mpath))
     else:
         full = engine.full_state_dict(torch.float32)  # collective: every rank takes part
     sam = cfg.trainer.v1.sampler

@@ -101,3 +101,36 @@ def test_replica_takes_its_frozen_drafter_from_the_base_model_directory(tmp_path
         assert all(torch.equal(after[k].float(), want_mtp[k]) for k in want_mtp if k.startswith("mtp."))
     finally:
         srv.close()
+
+
+def test_model_directory_tokenizer_is_read_and_renders_the_chat_template(tmp_path):
+    """A directory with a ``tokenizer.json`` gets the reader over the ``tokenizers`` package (same interface as the byte
+    tokenizer); one without, or a preset, gets the byte tokenizer; a vocabulary without the chat specials is refused."""
+    from tokenizers import Tokenizer, models, pre_tokenizers
+
+    from pear_b200.utils.tokenizer import ByteTokenizer, HFTokenizer, load_tokenizer
+
+    words = ["user", "assistant", "system", "pick", "the", "cube", "front", "[", "]", "\n", "Ċ"]
+    vocab = {w: i for i, w in enumerate(words)}
+    vocab["[UNK]"] = len(vocab)
+    tk = Tokenizer(models.WordLevel(vocab, unk_token="[UNK]"))
+    tk.pre_tokenizer = pre_tokenizers.Sequence([pre_tokenizers.Split("\n", "isolated"), pre_tokenizers.WhitespaceSplit(), pre_tokenizers.Punctuation()])
+    tk.add_special_tokens(["<|endoftext|>", "<|im_start|>", "<|im_end|>", "<|vision_start|>", "<|vision_end|>", "<|image_pad|>"])
+    d = tmp_path / "model"
+    d.mkdir()
+    tk.save(str(d / "tokenizer.json"))
+    (d / "generation_config.json").write_text('{"eos_token_id": [%d, %d]}' % (tk.token_to_id("<|im_end|>"), tk.token_to_id("<|endoftext|>")))
+    tok = load_tokenizer(str(d))
+    assert isinstance(tok, HFTokenizer) and tok.eos_id == tk.token_to_id("<|im_end|>") and tok.extra_stop_ids == (tk.token_to_id("<|endoftext|>"),)
+    ids = tok.render_turn("user", "pick the cube", images=1, image_tokens=3, labels=["front"]) + tok.generation_prompt()
+    assert ids[0] == tok.special_ids["<|im_start|>"] and ids.count(tok.image_pad_id) == 3
+    text = tok.decode(ids)
+    assert text.startswith("<|im_start|>") and "pick the cube" in text and "<|vision_start|>" in text and "assistant" in text
+    assert "<|im_start|>" not in tok.decode(ids, skip_special=True)
+    assert tok.encode("pick the cube") == [vocab["pick"], vocab["the"], vocab["cube"]]
+    assert isinstance(load_tokenizer("preset:tiny"), ByteTokenizer) and isinstance(load_tokenizer(str(tmp_path)), ByteTokenizer)
+    bad = Tokenizer(models.WordLevel(vocab, unk_token="[UNK]"))
+    (tmp_path / "bad").mkdir()
+    bad.save(str(tmp_path / "bad" / "tokenizer.json"))
+    with pytest.raises(KeyError, match="im_start"):
+        load_tokenizer(str(tmp_path / "bad"))
