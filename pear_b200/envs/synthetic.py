@@ -23,8 +23,10 @@ class SyntheticEnv(BaseEnv):
     family = "synthetic"
 
     def __init__(self, cameras: tuple[str, ...] = ("front",), tokens_per_image: int = 16, hidden: int = 64,
-                 fail_after: int = -1, hang_after: int = -1):
-        self.cameras, self.tokens_per_image, self.hidden = tuple(cameras), tokens_per_image, hidden
+                 fail_after: int = -1, hang_after: int = -1, pixels: int = 0):
+        """``pixels`` > 0: the cameras deliver ``[pixels, pixels, 3]`` uint8 pictures (the agent loop's vision encoder turns them
+        into embedding rows) instead of finished embedding blocks; the picture changes only when the cursor moves."""
+        self.cameras, self.tokens_per_image, self.hidden, self.pixels = tuple(cameras), tokens_per_image, hidden, int(pixels)
         # host-side fault injection for the supervision tests: raise / sleep after this many steps
         self.fail_after, self.hang_after = fail_after, hang_after
         self.rng = np.random.default_rng(0)
@@ -37,7 +39,13 @@ class SyntheticEnv(BaseEnv):
                 "additionalProperties": False, "minProperties": 1}
 
     def _observe(self) -> dict:
-        frames = {cam: self.rng.standard_normal((self.tokens_per_image, self.hidden)).astype(np.float32) for cam in self.cameras}
+        if self.pixels:
+            frames = {}
+            for ci, cam in enumerate(self.cameras):  # a function of (task seed, camera, cursor): a scene that did not move looks the same
+                g = np.random.default_rng([self.target, ci, self.cursor])
+                frames[cam] = g.integers(0, 256, (self.pixels, self.pixels, 3), dtype=np.uint8)
+        else:
+            frames = {cam: self.rng.standard_normal((self.tokens_per_image, self.hidden)).astype(np.float32) for cam in self.cameras}
         state = {"task": self.task, "step": self.t, "cursor": self.cursor, "distance": self.target - self.cursor,
                  "horizon": self.horizon}
         return {"state": state, "frames": frames, "reminder": "Answer with one JSON action in a ```json block."}

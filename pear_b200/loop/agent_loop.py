@@ -53,8 +53,9 @@ class AgentLoopConfig:
 
 class AgentLoop:
     def __init__(self, router, pool: ServerPool, tokenizer: ByteTokenizer, cfg: AgentLoopConfig, schemas: dict[str, dict],
-                 queue=None, tracker=None):
-        self.router, self.pool, self.tok, self.cfg = router, pool, tokenizer, cfg
+                 queue=None, tracker=None, vision=None):
+        """``vision``: a ``loop.vision_encoder.VisionEncoder`` for environments whose cameras deliver pixels."""
+        self.router, self.pool, self.tok, self.cfg, self.vision = router, pool, tokenizer, cfg, vision
         self.schemas, self.queue, self.tracker = schemas, queue, tracker
         self.system_prompt = load_system_prompt()
 
@@ -72,6 +73,12 @@ class AgentLoop:
         ids: list[int] = []
         if first:
             ids += self.tok.render_turn("system", self.system_prompt)
+        if self.vision is not None:
+            obs.frames = self.vision.encode(obs.frames)
+        elif any(f.ndim != 2 for f in obs.frames):
+            raise ValueError("the environment delivers pixels: the agent loop needs a vision encoder (AgentLoopManager(vision=...))")
+        if len({f.shape[0] for f in obs.frames}) > 1:
+            raise ValueError(f"pictures of one observation must take the same number of tokens, got {[f.shape[0] for f in obs.frames]}")
         n_img_tokens = obs.frames[0].shape[0] if obs.frames else 0
         turn = self.tok.render_turn("user", obs.text, images=len(obs.frames), image_tokens=n_img_tokens, labels=obs.cameras or None)
         base = len(ep.tokens) + len(ids)

@@ -50,7 +50,7 @@ class Router:
 
 class AgentLoopManager:
     def __init__(self, servers: list, hidden_size: int, env_families: dict[str, dict], cfg: AgentLoopConfig, queue_=None,
-                 tracker=None, num_workers: int = 4, tokenizer: Optional[ByteTokenizer] = None):
+                 tracker=None, num_workers: int = 4, tokenizer: Optional[ByteTokenizer] = None, vision=None):
         """``env_families``: family -> {"env_path": dotted class path, "mode": "stateless"|"stateful", ...Server kwargs}."""
         self.pool = ServerPool()
         schemas = {}
@@ -62,7 +62,7 @@ class AgentLoopManager:
             module, _, name = env_path.rpartition(".")
             schemas[family] = getattr(__import__(module, fromlist=[name]), name).action_schema()
         self.router = Router(servers, hidden_size)
-        self.loop = AgentLoop(self.router, self.pool, tokenizer or ByteTokenizer(), cfg, schemas, queue_, tracker)
+        self.loop = AgentLoop(self.router, self.pool, tokenizer or ByteTokenizer(), cfg, schemas, queue_, tracker, vision=vision)
         self.jobs: "queue.Queue" = queue.Queue()
         self.cancelled: set[str] = set()
         self.errors: list[str] = []

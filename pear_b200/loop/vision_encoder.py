@@ -1,0 +1,70 @@
+"""Pictures of an observation -> the embedding rows that replace their image-pad tokens, on the agent-loop side.
+
+Environments hand over either finished embedding blocks (``[tokens, hidden]`` floats: the seeded synthetic family) or pixels
+(``[H, W, 3]`` uint8: a simulator's cameras). Pixels go through the vision tower here, once per distinct picture: a turn-based
+episode shows the same frame again whenever the scene did not change, and every sample of a prompt group starts from the same
+first frame, so encodings are kept in a small LRU keyed by the picture's bytes. The tower is shared by the agent-loop workers
+(one batched call per observation, under a lock) and runs without gradients: the trainer receives the rows as part of the
+trajectory, as it does for the synthetic family. (Upstream runs its tower inside the serving stack and again in the trainer:
+pear/models/qwen3_5/trainer/vision_tower.py:11-133.)
+"""
+
+from __future__ import annotations
+
+import hashlib
+import threading
+from collections import OrderedDict
+
+import numpy as np
+import torch
+
+
+class VisionEncoder:
+    def __init__(self, tower, device: str = "cpu", cache_entries: int = 512, pixel_dtype: torch.dtype = torch.float32):
+        self.tower = tower.to(device).eval()
+        self.device, self.pixel_dtype = torch.device(device), pixel_dtype
+        self.cache: "OrderedDict[bytes, np.ndarray]" = OrderedDict()
+        self.cache_entries = cache_entries
+        self.lock = threading.Lock()
+        self.encoded = self.hits = 0
+
+    @staticmethod
+    def is_pixels(frame: np.ndarray) -> bool:
+        return frame.ndim == 3 and frame.dtype == np.uint8
+
+    def _prepare(self, frame: np.ndarray) -> torch.Tensor:
+        """[H, W, C] uint8 -> [C, H, W] in [-1, 1]; ``pixel_dtype`` is the precision pixels are handed over in (the tower itself
+        computes in fp32)."""
+        x = torch.from_numpy(np.ascontiguousarray(frame)).to(self.device).permute(2, 0, 1).to(self.pixel_dtype)
+        return (x / 127.5 - 1.0).float()
+
+    def encode(self, frames: list[np.ndarray]) -> list[np.ndarray]:
+        out: list = [None] * len(frames)
+        todo: list[tuple[int, bytes]] = []
+        with self.lock:
+            for i, f in enumerate(frames):
+                if not self.is_pixels(f):
+                    out[i] = np.asarray(f, dtype=np.float32)
+                    continue
+                key = hashlib.blake2b(f.tobytes(), digest_size=16, person=str(f.shape).encode()[:16]).digest()
+                hit = self.cache.get(key)
+                if hit is not None:
+                    self.cache.move_to_end(key)
+                    out[i] = hit
+                    self.hits += 1
+                else:
+                    todo.append((i, key))
+            if todo:
+                first: dict[bytes, int] = {}
+                for i, key in todo:  # the same picture twice in one observation is encoded once
+                    first.setdefault(key, i)
+                with torch.no_grad():
+                    rows = self.tower([self._prepare(frames[i]) for i in first.values()])
+                for key, block in zip(first, rows):
+                    self.cache[key] = block.float().cpu().numpy()
+                    self.encoded += 1
+                while len(self.cache) > self.cache_entries:
+                    self.cache.popitem(last=False)
+                for i, key in todo:
+                    out[i] = self.cache[key]
+        return out

@@ -184,8 +184,17 @@ def build_stack(cfg, replicas: int = 1, device: str = "cpu", env_families: Optio
                                synthetic_reward=ro.multi_turn.synthetic_reward)
         from ..utils.tokenizer import load_tokenizer
 
+        vision = None
+        vcfg = cfg.actor_rollout_ref.model.get("vision", None)
+        if vcfg is not None and bool(vcfg.enable):
+            from ..loop.vision_encoder import VisionEncoder
+            from ..models.vision import VisionConfig, VisionTower
+
+            tower = VisionTower(getattr(VisionConfig, str(vcfg.preset))(out_hidden=mcfg.hidden_size)).init_weights(int(cfg.trainer.seed))
+            pixel_dtype = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[str(cfg.data.get("pixel_dtype", "fp32"))]
+            vision = VisionEncoder(tower, str(vcfg.device), pixel_dtype=pixel_dtype)
         manager = AgentLoopManager(servers, mcfg.hidden_size, families, acfg, queue, num_workers=int(ro.agent.num_workers),
-                                   tokenizer=load_tokenizer(mpath))
+                                   tokenizer=load_tokenizer(mpath), vision=vision)
     else:
         full = engine.full_state_dict(torch.float32)  # collective: every rank takes part
     sam = cfg.trainer.v1.sampler

@@ -180,3 +180,36 @@ def test_first_turn_prompt_rendering_is_the_stored_text():
         assert tok.decode(ids) == f.read()
     text = tok.decode(ids)
     assert text.index("[front]") < text.index("<|vision_start|>") < text.index("[wrist]") < text.rindex("<|vision_start|>")
+
+
+def test_pixel_cameras_go_through_the_vision_encoder(pool):
+    """An environment whose cameras deliver pixels: the agent loop encodes each distinct picture once with the vision tower
+    (the two cameras of a turn in one batched call, an unchanged scene from the cache) and the trajectory carries the rows at
+    the image-pad positions; without an encoder the loop refuses pixels by name."""
+    from pear_b200.loop.vision_encoder import VisionEncoder
+    from pear_b200.models.vision import VisionConfig, VisionTower
+
+    pool.start("synthetic", ENV, "stateless", num_processes=1, env_kwargs={"pixels": 16, "cameras": ("front", "wrist")})
+    tower = VisionTower(VisionConfig.tiny(out_hidden=8)).init_weights(1)
+    n_tok = tower.tokens_per_image(16, 16)
+    enc = VisionEncoder(tower)
+    tok = ByteTokenizer()
+    q = TransferQueue(4)
+    answers = ['```json\n{"move": 0}\n```', '```json\n{"move": 0}\n```', '```json\n{"submit": true}\n```']  # the scene never changes
+    router = ScriptedRouter(tok, answers)
+    loop = AgentLoop(router, pool, tok, AgentLoopConfig(token_budget=4000), {"synthetic": SyntheticEnv.action_schema()}, q, vision=enc)
+    ep = loop.run("gp", "0", "synthetic", {"seed": 3})
+    tr = q.get("gp/0")
+    assert ep.turns == 3 and len(tr["embeds"]) == 2 * ep.turns
+    for pos, block in tr["embeds"]:
+        assert block.shape == (n_tok, 8) and all(t == tok.image_pad_id for t in tr["tokens"][pos:pos + n_tok])
+    assert enc.encoded == 2 and enc.hits == 2 * (ep.turns - 1)  # two cameras encoded once, the later turns from the cache
+    # the rows are the tower's output for the environment's pictures
+    env = SyntheticEnv(pixels=16, cameras=("front", "wrist"))
+    frames = env.reset({"seed": 3})["frames"]
+    with torch.no_grad():
+        want = tower([torch.from_numpy(frames["front"]).permute(2, 0, 1).float() / 127.5 - 1.0])[0]
+    assert np.allclose(tr["embeds"][0][1], want.numpy().astype(np.float16), atol=2e-3)
+    bare = AgentLoop(ScriptedRouter(tok, answers), pool, tok, AgentLoopConfig(token_budget=4000, max_restarts=0), {"synthetic": SyntheticEnv.action_schema()})
+    with pytest.raises(ValueError, match="needs a vision encoder"):
+        bare.run("gq", "0", "synthetic", {"seed": 3})

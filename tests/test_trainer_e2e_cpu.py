@@ -104,3 +104,19 @@ def test_checkpoint_of_another_world_size_is_refused(tmp_path):
             other.load(trainer.engine)
     finally:
         close()
+
+
+@pytest.mark.timeout(600)
+def test_training_step_on_pixel_observations(tmp_path):
+    """Cameras that deliver pixels: the training entry builds the vision encoder, the rollouts carry its rows and a GRPO step
+    trains on them."""
+    fam = {"synthetic": {"env_path": "pear_b200.envs.synthetic.SyntheticEnv", "num_processes": 2, "env_kwargs": {"pixels": 16}}}
+    cfg = _cfg(str(tmp_path / "run"), ["actor_rollout_ref.model.vision.enable=true", "trainer.total_training_steps=1", "trainer.save_freq=0",
+                                        "actor_rollout_ref.rollout.multi_turn.synthetic_turns=1", "actor_rollout_ref.rollout.multi_turn.synthetic_reward=hash"])
+    trainer, close = build_stack(cfg, env_families=fam)
+    try:
+        hist = trainer.fit()
+        enc = trainer.manager.loop.vision
+        assert len(hist) == 1 and np.isfinite(hist[0]["actor/grad_norm"]) and enc is not None and enc.encoded >= 1 and enc.hits >= 1
+    finally:
+        close()
