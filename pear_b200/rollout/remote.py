@@ -103,7 +103,7 @@ class RemoteReplica:
                  timeout_s: Optional[float] = None, max_resubmits: int = 1000) -> RemoteRequest:
         p = params or SamplingParams()
         body = {"prompt_token_ids": list(map(int, prompt)), "max_tokens": p.max_tokens, "temperature": p.temperature, "top_p": p.top_p,
-                "logprobs": p.topk_logprobs, "stop_token_ids": list(p.stop_token_ids), "session": session, "max_resubmits": max_resubmits}
+                "top_k": p.top_k, "seed": p.seed, "logprobs": p.topk_logprobs, "stop_token_ids": list(p.stop_token_ids), "session": session, "max_resubmits": max_resubmits}
         body.update(encode_embeds(embeds, embeds_mask))
         out = self._post("/v1/completions", body, timeout_s)
         if "error" in out:

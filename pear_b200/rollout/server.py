@@ -176,7 +176,8 @@ class RolloutServer:
             from .remote import decode_embeds
 
             params = SamplingParams(max_tokens=int(body.get("max_tokens", 64)), temperature=float(body.get("temperature", 1.0)),
-                                    top_p=float(body.get("top_p", 1.0)), topk_logprobs=int(body.get("logprobs", 0) or 0),
+                                    top_p=float(body.get("top_p", 1.0)), top_k=int(body.get("top_k", -1) or -1),
+                                    seed=(int(body["seed"]) if body.get("seed") is not None else None), topk_logprobs=int(body.get("logprobs", 0) or 0),
                                     stop_token_ids=tuple(int(t) for t in body.get("stop_token_ids", ())))
             embeds, mask = decode_embeds(body)  # vision placeholder rows of a multi-modal prompt (bf16, base64)
             req = self.generate(list(prompt), params, session=body.get("session"), embeds=embeds, embeds_mask=mask,

@@ -54,6 +54,9 @@ def test_replica_process_serves_requests_and_receives_weights():
         r1 = replica.generate(prompt, p, session="s0")
         assert r1.finish == FinishReason.LENGTH and r1.output == _greedy(model, prompt, 6)
         assert len(r1.logprobs) == 6 and len(r1.topk_ids) == 6 and all(len(x) == 3 for x in r1.topk_ids) and r1.policy_version == 0
+        # every sampling parameter travels: top-k 1 at temperature 1 is the greedy sequence again
+        r_k1 = replica.generate(prompt, SamplingParams(max_tokens=6, temperature=1.0, top_k=1), session="s-k1")
+        assert r_k1.output == r1.output
         # a weight sync driven from this process: pause / resume over HTTP, buckets over the process group
         new_state = {k: ((v * 0.5).to(torch.bfloat16).float() if v.dim() >= 2 else v.clone()) for k, v in model.state_dict().items()}
         stats = WeightSync(SyncConfig(bucket_megabytes=1, rollout_dtype=torch.bfloat16), BroadcastTransport(group, 0, "cpu"), [replica]).sync(new_state, version=3)
