@@ -431,7 +431,7 @@ class RolloutEngine:
         if not reqs:
             return []
         p0 = reqs[0].params
-        if p0.temperature <= 0.0 or any(r.params.temperature != p0.temperature or r.params.top_p < 1.0 or r.params.top_k > 0 or r.params.topk_logprobs > 32
+        if p0.temperature <= 0.0 or any(r.params.temperature != p0.temperature or r.params.top_p < 1.0 or r.params.top_k > 0 or r.params.topk_logprobs > 32 or r.params.seed is not None
                                         for r in reqs):
             for r in list(self.running):
                 self._fast_release(r)
@@ -565,13 +565,24 @@ class RolloutEngine:
         return done
 
     # -- sampling / verification / drafting -----------------------------------------------------------------------------
+    def _generator(self, req: Request) -> torch.Generator:
+        """The engine's generator, or the request's own when it carries a seed: such a request draws the same tokens whatever
+        else is in the batch (it stays on the per-request sampling path; the batched step draws from one counter stream)."""
+        if req.params.seed is None:
+            return self.gen
+        g = getattr(req, "_gen", None)
+        if g is None:
+            g = torch.Generator(device=self.gen.device).manual_seed(int(req.params.seed))
+            req._gen = g
+        return g
+
     def _sample_rows(self, req: Request, logits: torch.Tensor, resid: torch.Tensor, drafts: list[int], row: StepRow) -> None:
         p = req.params
         bad = S.count_nonfinite(logits)
         if bool((bad > 0).any()):
             raise S.NonFiniteLogits(self.step_count, torch.nonzero(bad).flatten().tolist(), [req.request_id])
         if drafts:
-            out = S.verify_greedy_drafts(logits[None], torch.tensor([drafts], device=logits.device), p.temperature, p.topk_logprobs, self.gen)
+            out = S.verify_greedy_drafts(logits[None], torch.tensor([drafts], device=logits.device), p.temperature, p.topk_logprobs, self._generator(req))
             acc = int(out.accepted[0])
             new = [int(t) for t in out.tokens[0, : acc + 1]]
             lps = [float(v) for v in out.logprobs[0, : acc + 1]]
@@ -580,7 +591,7 @@ class RolloutEngine:
             req.spec_drafted += len(drafts)
             req.spec_accepted += acc
         else:
-            so = S.sample(logits[-1:], p.temperature, p.top_p, p.top_k, p.topk_logprobs, self.gen)
+            so = S.sample(logits[-1:], p.temperature, p.top_p, p.top_k, p.topk_logprobs, self._generator(req))
             acc, new, lps = 0, [int(so.tokens[0])], [float(so.logprobs[0])]
             tk_i = [so.topk_ids[0].tolist()] if so.topk_ids is not None else []
             tk_l = [so.topk_logprobs[0].tolist()] if so.topk_logprobs is not None else []

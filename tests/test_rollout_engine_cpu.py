@@ -205,3 +205,19 @@ def test_host_tier_sized_in_bytes_prefaulted_and_local_to_the_bound_node():
             os.environ.pop("CUDA_VISIBLE_DEVICES")
         else:
             os.environ["CUDA_VISIBLE_DEVICES"] = saved
+
+
+def test_a_seeded_request_draws_the_same_tokens_whatever_shares_its_batch():
+    model = HybridForCausalLM(HybridConfig.tiny(), with_mtp=False).init_weights(0)
+    p = SamplingParams(max_tokens=8, temperature=1.0, seed=1234)
+    prompt = list(range(5, 25))
+    alone = RolloutEngine(model, EngineConfig(num_blocks=64, max_num_seqs=4, seed=1)).generate([prompt], p)[0].output
+    eng = RolloutEngine(model, EngineConfig(num_blocks=64, max_num_seqs=4, seed=99))
+    a = eng.add_request(list(range(40, 70)), SamplingParams(max_tokens=8, temperature=1.0))
+    b = eng.add_request(prompt, p)
+    c = eng.add_request(list(range(3, 9)), SamplingParams(max_tokens=8, temperature=1.0, seed=7))
+    while eng.has_work():
+        eng.step()
+    assert b.output == alone and len(a.output) == 8 and len(c.output) == 8
+    other_seed = RolloutEngine(model, EngineConfig(num_blocks=64, max_num_seqs=4, seed=1)).generate([prompt], SamplingParams(max_tokens=8, temperature=1.0, seed=4321))[0].output
+    assert other_seed != alone
