@@ -35,7 +35,6 @@ class SyncConfig:
     bucket_megabytes: int = 512
     rollout_dtype: torch.dtype = torch.bfloat16
     fp32_modules: tuple = ()
-    rebuild_group: bool = True
 
 
 def cast_for_rollout(name: str, t: torch.Tensor, cfg: SyncConfig) -> torch.Tensor:

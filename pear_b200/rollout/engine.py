@@ -127,7 +127,8 @@ class RolloutEngine:
         self.gen = torch.Generator(device=self.device if self.device.type == "cuda" else "cpu").manual_seed(cfg.seed)
         self._ids = itertools.count()
         self.metrics = {"prompt_tokens": 0, "generation_tokens": 0, "preemptions": 0, "aborted": 0, "spec_drafted": 0,
-                        "spec_accepted": 0, "steps": 0}
+                        "spec_accepted": 0, "steps": 0, "request_seconds": 0.0, "requests_finished": 0,
+                        "first_token_seconds": 0.0, "first_tokens": 0}
         self.spec = cfg.num_speculative_tokens if model.mtp is not None else 0
         # the batched GPU-resident step for decode / verify rows (prefill chunks stay on the packed runner)
         self.fast = None
@@ -268,6 +269,9 @@ class RolloutEngine:
 
     def _finish(self, req: Request, reason: FinishReason) -> None:
         req.finish = reason
+        if reason != FinishReason.ABORTED:  # request latency from its arrival (queueing included), for the replica's metrics
+            self.metrics["request_seconds"] += time.time() - req.arrival
+            self.metrics["requests_finished"] += 1
         self._fast_release(req)
         if req.seq is not None:
             if reason != FinishReason.ABORTED:
@@ -600,6 +604,9 @@ class RolloutEngine:
             self.runner.commit(req.seq, committed)
         req.computed += committed if (drafts or row.tokens.shape[0] == 1) else 1
         req.seq.mtp_hidden = resid[acc]
+        if not req.output:  # time to the first token, from the request's arrival
+            self.metrics["first_token_seconds"] += time.time() - req.arrival
+            self.metrics["first_tokens"] += 1
         for j, t in enumerate(new):
             req.output.append(t)
             req.logprobs.append(lps[j])

@@ -72,7 +72,11 @@ def test_server_metrics_pause_resubmit_and_benchmark():
         router = LeastInFlightRouter([srv])
         scores = run_benchmark(router, tok, [Item("0", "2+2?", "4"), Item("1", "3+3?", "6")], n=2, max_tokens=8, workers=2)
         assert set(scores) == {"0", "1"} and all(len(v) == 2 for v in scores.values())
-        assert "pear_generation_tokens_total" in srv.metrics_text()
+        text = srv.metrics_text()
+        assert "pear_generation_tokens_total" in text
+        vals = {l.split("{")[0]: float(l.split()[-1]) for l in text.splitlines() if l and not l.startswith("#")}
+        assert vals["pear_requests_finished_total"] == 4 and vals["pear_first_tokens_total"] == 4  # 2 items x 2 samples
+        assert vals["pear_request_seconds_total"] >= vals["pear_first_token_seconds_total"] > 0
         # a paused replica rejects new requests as aborted; generate() resubmits after the resume
         srv.pause(abort=True)
         fut = srv.submit([1, 2, 3], SamplingParams(max_tokens=4))
