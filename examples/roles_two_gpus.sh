@@ -9,7 +9,7 @@ NCCL_NVLS_ENABLE=0 TORCH_SYMM_MEM_DISABLE_MULTICAST=1 PYTORCH_CUDA_ALLOC_CONF=ex
 python -m pear_b200.launch.launch training --gpus 2 --trainer-gpus 0 --rollout-tp 2 \
   --replica-master-port ${REPLICA_PORT:-0} --master-port ${PORT:-29531} --rollout-port ${ROLLOUT_PORT:-8131} --env-port ${ENV_PORT:-8231} --sync-port ${SYNC_PORT:-29631} \
   run_dir=$RUN actor_rollout_ref.model.path=preset:tiny_gpu trainer.total_training_steps=${STEPS:-1} trainer.save_freq=0 \
-  data.train_batch_size=2 actor_rollout_ref.rollout.n=4 data.max_prompt_length=128 data.max_response_length=32 \
+  data.train_batch_size=2 actor_rollout_ref.rollout.n=4 data.max_response_length=32 \
   actor_rollout_ref.rollout.multi_turn.synthetic_turns=1 actor_rollout_ref.rollout.multi_turn.synthetic_reward=hash \
   actor_rollout_ref.rollout.max_model_len=2048 actor_rollout_ref.rollout.max_num_seqs=16 \
   actor_rollout_ref.rollout.checkpoint_engine.backend=gloo actor_rollout_ref.actor.ppo_max_token_len_per_gpu=8192 \

@@ -8,7 +8,7 @@ RUN=${RUN:-runs/tiny_roles_cpu}
 CUDA_VISIBLE_DEVICES="" python -m pear_b200.launch.launch training --gpus 4 --trainer-gpus 2 --rollout-tp 2 \
   --replica-master-port ${REPLICA_PORT:-0} --master-port ${PORT:-29521} --rollout-port ${ROLLOUT_PORT:-8121} --env-port ${ENV_PORT:-8221} --sync-port ${SYNC_PORT:-29621} \
   run_dir=$RUN actor_rollout_ref.model.path=preset:tiny trainer.total_training_steps=${STEPS:-2} data.train_batch_size=4 \
-  actor_rollout_ref.rollout.n=4 data.max_prompt_length=128 data.max_response_length=48 \
+  actor_rollout_ref.rollout.n=4 data.max_response_length=48 \
   actor_rollout_ref.actor.fsdp_config.ulysses_sequence_parallel_size=2 \
   actor_rollout_ref.rollout.multi_turn.synthetic_turns=1 actor_rollout_ref.rollout.multi_turn.synthetic_reward=hash \
   actor_rollout_ref.rollout.max_model_len=2048 actor_rollout_ref.rollout.max_num_seqs=16 actor_rollout_ref.actor.ppo_max_token_len_per_gpu=8192 \

@@ -42,6 +42,7 @@ class AgentLoopConfig:
     top_p: float = 1.0
     topk_heads: int = 0              # rollout top-k head ids / log-probs kept for score centering
     max_model_len: int = 4096
+    max_prompt_length: int = 0       # an episode whose first-turn prompt is longer ends at once (budget end, no sampled token); 0: no limit
     log_dir: Optional[str] = None
     # synthetic benchmarks with a random-init policy: play `synthetic_turns` turns with a no-op action whatever the answer
     # says, at most `turn_max_tokens` sampled tokens per turn (0: the episode budget), and draw the reward ("hash": a seeded
@@ -133,6 +134,8 @@ class AgentLoop:
             self._append_user_turn(ep, obs, first=True)
             ep.prompt_len = len(ep.tokens)
             state = LoopState.GENERATING
+            if cfg.max_prompt_length > 0 and ep.prompt_len > cfg.max_prompt_length:  # (upstream filters such rows out of the dataset)
+                ep.end_reason, state = EndReason.BUDGET, LoopState.TERMINATED
             while state != LoopState.TERMINATED:
                 if state == LoopState.GENERATING:
                     left = min(cfg.token_budget - ep.response_tokens, cfg.max_model_len - len(ep.tokens))

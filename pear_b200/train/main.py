@@ -62,10 +62,49 @@ class RunConfig:
             ro.max_num_seqs = int(rs.seqs_per_session) * spr
             ro.agent.num_workers = max(1, (ro.max_num_seqs * self.replicas + int(rs.seqs_per_agent_worker) - 1) // int(rs.seqs_per_agent_worker))
             cfg.trainer.v1.sampler.max_inflight_sessions = self.replicas * spr
+        validate_config(cfg)
         for k, v in cfg.get("env_vars", {}).items():
             os.environ.setdefault(str(k), str(v))
         os.makedirs(cfg.run_dir, exist_ok=True)
         return cfg
+
+
+# Keys the recipes carry whose other values select algorithms or modes this framework does not implement: they are accepted at
+# the implemented value only, so a recipe edited to ask for something else fails at start instead of training something else.
+IMPLEMENTED_VALUES = {
+    "algorithm.adv_estimator": ("grpo",),
+    "algorithm.use_kl_in_reward": (False,),
+    "algorithm.rollout_correction.bypass_mode": (True,),
+    "algorithm.rollout_correction.loss_type": ("reinforce",),
+    "actor_rollout_ref.actor.use_kl_loss": (False,),
+    "actor_rollout_ref.actor.use_dynamic_bsz": (True,),
+    "actor_rollout_ref.actor.policy_loss.loss_mode": ("bypass_mode",),
+    "actor_rollout_ref.actor.strategy": ("fsdp2", "fsdp"),
+    "actor_rollout_ref.hybrid_engine": (False,),
+    "actor_rollout_ref.rollout.calculate_log_probs": (True,),
+    "actor_rollout_ref.rollout.enable_chunked_prefill": (True,),
+    "actor_rollout_ref.rollout.multi_turn.max_parallel_calls": (1,),
+    "trainer.val_before_train": (False,),
+    "trainer.test_freq": (-1, 0),
+    "trainer.v1.separate_async.num_warmup_batches": (0,),
+    "algorithm.filter_groups.max_num_gen_batches": (0,),
+}
+
+
+def validate_config(cfg) -> None:
+    """The role of upstream's ``validate_config`` call (pear/trainer/main.py:12-32): refuse what would be silently ignored."""
+    from ..config.loader import MISSING, ConfigError
+
+    bad = []
+    for key, allowed in IMPLEMENTED_VALUES.items():
+        v = cfg.get_path(key, MISSING)
+        if v != MISSING and v not in allowed:
+            bad.append(f"{key}={v!r} (implemented: {', '.join(map(repr, allowed))})")
+    mini, batch = cfg.get_path("actor_rollout_ref.actor.ppo_mini_batch_size", MISSING), cfg.get_path("data.train_batch_size", MISSING)
+    if MISSING not in (mini, batch) and int(mini) < int(batch):
+        bad.append(f"actor_rollout_ref.actor.ppo_mini_batch_size={mini} < data.train_batch_size={batch} (one optimizer step per training batch is implemented)")
+    if bad:
+        raise ConfigError("settings this framework does not implement:\n  " + "\n  ".join(bad))
 
 
 def _model_config(path: str) -> HybridConfig:
@@ -179,7 +218,7 @@ def build_stack(cfg, replicas: int = 1, device: str = "cpu", env_families: Optio
         families = env_families or {"synthetic": {"env_path": "pear_b200.envs.synthetic.SyntheticEnv", "num_processes": 2,
                                                   "env_kwargs": {"hidden": mcfg.hidden_size, "tokens_per_image": 4}}}
         acfg = AgentLoopConfig(token_budget=int(cfg.data.max_response_length), temperature=float(ro.temperature), top_p=float(ro.top_p),
-                               topk_heads=tcfg.topk_heads, max_model_len=int(ro.max_model_len), log_dir=os.environ.get("PEAR_LOG_DIR"),
+                               topk_heads=tcfg.topk_heads, max_model_len=int(ro.max_model_len), max_prompt_length=int(cfg.data.get("max_prompt_length", 0) or 0), log_dir=os.environ.get("PEAR_LOG_DIR"),
                                synthetic_turns=int(ro.multi_turn.synthetic_turns), turn_max_tokens=int(ro.multi_turn.turn_max_tokens),
                                synthetic_reward=ro.multi_turn.synthetic_reward)
         from ..utils.tokenizer import load_tokenizer

@@ -213,3 +213,12 @@ def test_pixel_cameras_go_through_the_vision_encoder(pool):
     bare = AgentLoop(ScriptedRouter(tok, answers), pool, tok, AgentLoopConfig(token_budget=4000, max_restarts=0), {"synthetic": SyntheticEnv.action_schema()})
     with pytest.raises(ValueError, match="needs a vision encoder"):
         bare.run("gq", "0", "synthetic", {"seed": 3})
+
+
+def test_prompt_longer_than_the_limit_ends_the_episode_before_any_request(pool):
+    pool.start("synthetic", ENV, "stateless", num_processes=1, env_kwargs={"hidden": 8, "tokens_per_image": 2})
+    loop, router = _loop(pool, ['```json\n{"submit": true}\n```'], token_budget=4000, max_prompt_length=64)  # the system prompt alone is longer
+    ep = loop.run("gl", "0", "synthetic", {"seed": 1})
+    assert ep.end_reason == EndReason.BUDGET and ep.response_tokens == 0 and not router.calls
+    loop2, router2 = _loop(pool, ['```json\n{"submit": true}\n```'], token_budget=4000, max_prompt_length=100000)
+    assert loop2.run("gm", "0", "synthetic", {"seed": 1}).response_tokens > 0 and router2.calls

@@ -134,3 +134,15 @@ def test_metrics_log_commits_one_wandb_row_per_step(tmp_path, monkeypatch):
     assert calls["log"][0][1:] == (1, True) and calls["log"][0][0]["actor/pg_loss"] == 0.5 and "note" not in calls["log"][0][0]
     with open(tmp_path / "metrics.jsonl") as f:
         assert [json.loads(line)["step"] for line in f] == [1, 2]
+
+
+def test_unimplemented_settings_are_refused_at_start(tmp_path):
+    from pear_b200.config.loader import ConfigError
+    from pear_b200.train.main import RunConfig
+
+    base = [f"run_dir={tmp_path}", "actor_rollout_ref.model.path=preset:tiny"]
+    RunConfig(compose("training", base)).prepare()  # the shipped recipe is all implemented values
+    with pytest.raises(ConfigError, match=r"adv_estimator='gae'.*\n.*use_kl_loss=True|use_kl_loss=True"):
+        RunConfig(compose("training", base + ["algorithm.adv_estimator=gae", "actor_rollout_ref.actor.use_kl_loss=true"])).prepare()
+    with pytest.raises(ConfigError, match="one optimizer step per training batch"):
+        RunConfig(compose("training", base + ["data.train_batch_size=64", "actor_rollout_ref.actor.ppo_mini_batch_size=16"])).prepare()
