@@ -212,6 +212,34 @@ def build_server(model, cfg: Optional[EngineConfig] = None, device="cpu", **kw) 
     return RolloutServer(RolloutEngine(model, cfg or EngineConfig(), device), **kw)
 
 
+def apply_rollout_kernels(kernels_path: Optional[str], cfg: EngineConfig, model=None, tensor_parallel_size: int = 1) -> EngineConfig:
+    """Run a model family's rollout hooks (``models/kernels.py: RolloutKernels``, named by ``rollout.kernels`` or exported in
+    ``PEAR_ROLLOUT_KERNELS``) over a replica's engine settings: ``configure_server`` checks and completes them (KV page size,
+    the batched-step switch, the batch limits), ``install_worker`` loads the kernel library before the model is used,
+    ``check_model`` refuses another architecture. Returns the engine config to build with. (Upstream calls the same three
+    hooks from its server and worker extension: pear/rollout/server.py:14-82, worker_extension.py:13-70.)"""
+    import dataclasses
+    import importlib
+
+    from ..models.kernels import RolloutKernels
+
+    if kernels_path:
+        module_path, _, name = str(kernels_path).rpartition(".")
+        kernels = getattr(importlib.import_module(module_path), name)
+    else:
+        kernels = RolloutKernels.from_env()
+    if kernels is None:
+        return cfg
+    settings = {"block_size": cfg.block_size, "fast_decode": cfg.fast_decode, "tensor_parallel_size": tensor_parallel_size,
+                "num_speculative_tokens": cfg.num_speculative_tokens}
+    kernels.configure_server(settings, cfg.max_num_seqs, cfg.max_num_batched_tokens)
+    kernels.install_worker(None)
+    if model is not None:
+        kernels.check_model(model, settings)
+    known = {f.name for f in dataclasses.fields(cfg)}
+    return dataclasses.replace(cfg, **{k: v for k, v in settings.items() if k in known})
+
+
 def load_rollout_model(path: str, dtype: torch.dtype = torch.bfloat16, device: str = "cpu", with_mtp: bool = True, seed: int = 0,
                        drafter_path: Optional[str] = None):
     """``preset:<name>`` (random init of a ``HybridConfig`` preset) or a model directory in the Hugging Face layout.
@@ -369,6 +397,7 @@ def main(argv=None) -> int:
     ecfg = EngineConfig(num_blocks=args.num_blocks, max_num_seqs=max_seqs, num_speculative_tokens=args.speculative_tokens,
                         host_bytes=int(host_gb * (1 << 30)), host_numa_node=node)
     tp_rank, tp_world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    ecfg = apply_rollout_kernels(kv.get("actor_rollout_ref.rollout.kernels"), ecfg, tensor_parallel_size=tp_world)
     if tp_world > 1:  # one rank of a tensor-parallel replica (started under torch.distributed.run): lock-step with its peers
         import torch.distributed as dist
 

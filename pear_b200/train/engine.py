@@ -187,6 +187,11 @@ class TrainEngine:
                     replicate_group = g
             self.shard_world, self.shard_rank = S, self.rank % S
         self.replicate_group = replicate_group
+        if kernels is None and cfg.kernels:  # the recipe names the family's training kernels by class path (`fsdp_config.kernels`)
+            import importlib
+
+            module_path, _, name = str(cfg.kernels).rpartition(".")
+            kernels = getattr(importlib.import_module(module_path), name)
         self.kernels = kernels
         if kernels is not None:
             kernels.check_config(cfg)

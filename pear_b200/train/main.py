@@ -34,7 +34,7 @@ from ..models.config import HybridConfig
 from ..models.hybrid import HybridForCausalLM
 from ..models import io as model_io
 from ..rollout.engine import EngineConfig as RolloutConfig
-from ..rollout.server import build_server
+from ..rollout.server import apply_rollout_kernels, build_server
 from ..utils.logging_utils import get_logger
 from .checkpoint import CheckpointManager
 from .engine import EngineConfig, TrainEngine
@@ -214,6 +214,7 @@ def build_stack(cfg, replicas: int = 1, device: str = "cpu", env_families: Optio
                                num_speculative_tokens=int(cfg.actor_rollout_ref.model.mtp.num_speculative_tokens) if cfg.actor_rollout_ref.model.mtp.enable_rollout else 0,
                                host_blocks=int(ro.get("host_blocks", 0)),
                                host_bytes=int(float(ro.custom.lmcache.l1_size_gb) * (1 << 30)) if bool(ro.custom.lmcache.enable) else 0, seed=int(cfg.trainer.seed) + i)
+            rc = apply_rollout_kernels(ro.get("kernels", None), rc, model=rm)  # the family's hooks check and complete the settings
             servers.append(build_server(rm, rc, device, name=f"replica-{i}", fp32_modules=tuple(ro.fp32_modules)))
         families = env_families or {"synthetic": {"env_path": "pear_b200.envs.synthetic.SyntheticEnv", "num_processes": 2,
                                                   "env_kwargs": {"hidden": mcfg.hidden_size, "tokens_per_image": 4}}}

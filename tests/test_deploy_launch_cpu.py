@@ -78,3 +78,31 @@ def test_roles_recipe_runs_as_processes(tmp_path):
     assert len(rows) == 1 and rows[0]["weight_sync/bytes"] > 0 and rows[0]["actor/grad_norm"] > 0
     left = subprocess.run(["ps", "-eo", "pid,args"], stdout=subprocess.PIPE, text=True).stdout
     assert not [line for line in left.splitlines() if run in line], "a role outlived the launcher"
+
+
+def test_rollout_kernel_hooks_check_and_complete_a_replicas_settings(monkeypatch):
+    """``rollout.kernels`` names a family's hooks: they refuse settings the kernels are not built for, complete the rest, and
+    refuse a model of another architecture; the class also reaches child processes through the environment."""
+    import torch.nn as nn
+
+    from pear_b200.models.config import HybridConfig
+    from pear_b200.models.hybrid import HybridForCausalLM
+    from pear_b200.models.kernels import RolloutKernels
+    from pear_b200.rollout.engine import EngineConfig
+    from pear_b200.rollout.server import apply_rollout_kernels
+
+    path = "pear_b200.models.qwen3_5.rollout_kernels.Qwen3_5RolloutKernels"
+    model = HybridForCausalLM(HybridConfig.tiny(), with_mtp=False)
+    cfg = apply_rollout_kernels(path, EngineConfig(max_num_seqs=8, fast_decode=False), model=model, tensor_parallel_size=2)
+    assert cfg.max_num_seqs == 8 and cfg.block_size == 16 and cfg.fast_decode is False  # an explicit choice is kept
+    with pytest.raises(ValueError, match="16-token blocks"):
+        apply_rollout_kernels(path, EngineConfig(block_size=32))
+    with pytest.raises(ValueError, match="power of two"):
+        apply_rollout_kernels(path, EngineConfig(), tensor_parallel_size=3)
+    with pytest.raises(TypeError, match="hybrid GDN"):
+        apply_rollout_kernels(path, EngineConfig(), model=nn.Linear(2, 2))
+    plain = EngineConfig(block_size=32)
+    assert apply_rollout_kernels(None, plain) is plain  # no hooks named: nothing checked
+    monkeypatch.setenv(RolloutKernels.ENV, path)
+    with pytest.raises(ValueError, match="16-token blocks"):
+        apply_rollout_kernels(None, plain)

@@ -227,3 +227,19 @@ def test_engine_installs_the_family_kernels_in_order_and_runs_the_step_through_t
     ecfg2.use_gpu_backend = True
     TrainEngine(cfg, ecfg2, kernels=Recording, seed=5)
     assert calls.index("install_gpu_backend") == calls.index(("check_model", True)) + 1 and calls[-1] == "install_checkpointing"
+
+
+def test_engine_resolves_the_family_kernels_the_recipe_names(tmp_path):
+    """``+qwen3_5=config`` names the family's training kernels by class path; the engine installs them (fp32 residual, fused head,
+    recompute that skips down_proj) and runs the step through their overflow check."""
+    from pear_b200.config.loader import compose
+    from pear_b200.models.qwen3_5.training_kernels import Qwen3_5TrainingKernels
+
+    cfg = compose("training", [f"run_dir={tmp_path}", "actor_rollout_ref.model.path=preset:tiny", "+qwen3_5=config"])
+    ecfg = EngineConfig.from_config(cfg)
+    assert ecfg.kernels.endswith("Qwen3_5TrainingKernels")
+    ecfg.param_dtype, ecfg.lr = "fp32", 1e-3
+    eng = TrainEngine(HybridConfig.tiny(), ecfg, seed=5)
+    assert eng.kernels is Qwen3_5TrainingKernels and eng.model.fp32_residual and eng.model.use_fused_head and eng.model.recompute_skips_down_proj
+    eng.forward_backward_batch([make_batch(HybridConfig.tiny(), 0, k=ecfg.topk_log_probs or 4)])
+    assert eng.optimizer_step()["actor/grad_norm"] > 0
