@@ -403,7 +403,12 @@ def main(argv=None) -> int:
 
         from .lockstep import build_tp_replica
 
-        dist.init_process_group("nccl" if device == "cuda" else "gloo")
+        if device == "cuda":  # the rank's GPU is chosen before the group exists and the group is bound to it
+            local = int(os.environ.get("LOCAL_RANK", "0"))
+            torch.cuda.set_device(local)
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        else:
+            dist.init_process_group("gloo")
         server = build_tp_replica(path, ecfg, name=args.name)
         device = str(server.engine.device)
         if args.sync_backend == "nvswitch":
