@@ -223,13 +223,15 @@ class GatedDeltaNet(nn.Module):
         cfg = self.cfg
         t = hidden.shape[0]
         mixed = linear_fp32(hidden, self.in_proj_qkv.weight)
+        sp_on = meta.sp is not None and meta.sp.size > 1
+        halo = meta.sp.start_conv_halo(mixed, cfg.conv_kernel) if sp_on else None  # in flight under the three projections below
         z = linear_fp32(hidden, self.in_proj_z.weight).view(t, cfg.gdn_v_heads, cfg.gdn_head_dim)
         b = linear_fp32(hidden, self.in_proj_b.weight)
         a = linear_fp32(hidden, self.in_proj_a.weight)
         g, beta = ops.gdn_gates(a, b, self.A_log, self.dt_bias)
         bounds = meta.local_bounds(t)
-        if meta.sp is not None and meta.sp.size > 1:
-            o = meta.sp.gdn(self, mixed, g, beta, meta, bounds)
+        if sp_on:
+            o = meta.sp.gdn(self, mixed, g, beta, meta, bounds, halo=halo)
         else:
             q, k, v, _ = self.front(mixed, bounds, None, need_conv_state=False)
             o = ops.gdn_scan_packed(q, k, v, g, beta, bounds)

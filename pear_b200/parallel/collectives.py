@@ -92,6 +92,42 @@ def all_gather_stack(x: torch.Tensor, group) -> torch.Tensor:
     return _AllGather.apply(x, group)
 
 
+_STARTED: list = []  # the work handle of the collective `_AllGatherStart.forward` just launched (taken by its caller at once)
+
+
+class _AllGatherStart(torch.autograd.Function):
+    """``_AllGather`` whose forward only launches the collective: the caller waits on the handle before it reads the result,
+    and whatever it computes in between overlaps the transfer (NCCL runs it on its own stream)."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        n = dist.get_world_size(group)
+        xc = x.contiguous()
+        out = torch.empty((n,) + tuple(xc.shape), dtype=xc.dtype, device=xc.device)  # (returned as it is: the collective fills it later)
+        _STARTED.append((dist.all_gather_into_tensor(out.view(-1), xc.reshape(-1), group=group, async_op=True), xc))  # xc stays alive until the wait
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        return reduce_scatter_sum(g.contiguous(), ctx.group).squeeze(0), None
+
+
+def all_gather_stack_start(x: torch.Tensor, group):
+    """Start a stacked all-gather; returns (result, wait). ``result`` may be read only after ``wait()``."""
+    if dist.get_world_size(group) == 1:
+        return x.unsqueeze(0), (lambda: None)
+    out = _AllGatherStart.apply(x, group)
+    work, keep = _STARTED.pop()
+
+    def wait() -> None:
+        work.wait()
+        keep.clear()
+
+    keep = [keep]
+    return out, wait
+
+
 class _AllToAll(torch.autograd.Function):
     """x [n, chunk...] -> y [n, chunk...] with y[j] = rank j's x[rank]; its own transpose in backward."""
 

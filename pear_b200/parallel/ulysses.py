@@ -65,13 +65,25 @@ class SequenceParallel:
     # -----------------------------------------------------------------------------------------------------------------
     # gated delta net: local scan with an incoming state chained across ranks
     # -----------------------------------------------------------------------------------------------------------------
-    def gdn(self, mixer, mixed: torch.Tensor, g: torch.Tensor, beta: torch.Tensor, meta, bounds: list[int]):
-        """``mixed`` [T_local, C] are this rank's conv inputs. Returns the scan output [T_local, Hv, V]."""
+    def start_conv_halo(self, mixed: torch.Tensor, conv_kernel: int):
+        """Launch the all-gather of every rank's last ``conv_kernel - 1`` conv-input rows as soon as they exist: the mixer's
+        z / b / a projections run while it is in flight (upstream overlaps the same exchange: trainer/gdn.py:570-584).
+        Returns what ``gdn(halo=...)`` takes."""
+        kw = conv_kernel - 1
+        return C.all_gather_stack_start(mixed[mixed.shape[0] - kw:].float(), self.group)
+
+    def gdn(self, mixer, mixed: torch.Tensor, g: torch.Tensor, beta: torch.Tensor, meta, bounds: list[int], halo=None):
+        """``mixed`` [T_local, C] are this rank's conv inputs. Returns the scan output [T_local, Hv, V]. ``halo``: the started
+        exchange of ``start_conv_halo`` (else it runs here, blocking)."""
         cfg = mixer.cfg
         t_local = mixed.shape[0]
         kw = cfg.conv_kernel - 1
         # ---- conv halo: the previous rank's last rows, unless this slice starts a sequence
-        tails = C.all_gather_stack(mixed[t_local - kw :].float(), self.group)  # [sp, kw, C]
+        if halo is not None:
+            tails, wait = halo
+            wait()
+        else:
+            tails = C.all_gather_stack(mixed[t_local - kw :].float(), self.group)  # [sp, kw, C]
         starts_sequence = meta.offset in meta.cu_seqlens
         if self.rank == 0 or starts_sequence:
             halo = torch.zeros_like(tails[0]) + 0.0 * tails[0]  # keeps the autograd edge so every rank's backward joins the collective
