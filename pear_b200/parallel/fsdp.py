@@ -127,13 +127,20 @@ class FlatUnit:
         """Flatten the unit's full gradients, reduce-scatter over the shard group into the master shard's ``.grad``
         (accumulating over micro-batches), and all-reduce over the replicate group on the last micro-batch."""
         average = self.average
-        flat = torch.zeros(self.padded, dtype=torch.float32, device=self.shard.device)
+        # one pass over the unit: every gradient is converted straight into its slice (no fp32 temporary, no memset of the whole
+        # buffer); only a parameter without a gradient and the alignment tail are zeroed
+        flat = torch.empty(self.padded, dtype=torch.float32, device=self.shard.device)
         o = 0
         for p, n in zip(self.params, self.numels):
             if p.grad is not None:
-                flat[o : o + n] = p.grad.reshape(-1).float()
+                flat[o : o + n].copy_(p.grad.reshape(-1))
                 p.grad = None
+            else:
+                flat[o : o + n].zero_()
             o += n
+        if o < self.padded:
+            flat[o:].zero_()
+
         def finish(flat):
             if self.world > 1:
                 piece = C.reduce_scatter_sum(flat, self.group)
