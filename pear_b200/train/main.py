@@ -100,9 +100,6 @@ def validate_config(cfg) -> None:
         v = cfg.get_path(key, MISSING)
         if v != MISSING and v not in allowed:
             bad.append(f"{key}={v!r} (implemented: {', '.join(map(repr, allowed))})")
-    mini, batch = cfg.get_path("actor_rollout_ref.actor.ppo_mini_batch_size", MISSING), cfg.get_path("data.train_batch_size", MISSING)
-    if MISSING not in (mini, batch) and int(mini) < int(batch):
-        bad.append(f"actor_rollout_ref.actor.ppo_mini_batch_size={mini} < data.train_batch_size={batch} (one optimizer step per training batch is implemented)")
     if bad:
         raise ConfigError("settings this framework does not implement:\n  " + "\n  ".join(bad))
 

@@ -36,6 +36,7 @@ from .replay_buffer import GroupStatus, PromptGroup, ReplayBuffer
 class TrainerConfig:
     total_training_steps: int = 1
     train_batch_size: int = 4            # prompt groups per step
+    ppo_mini_batch_size: int = 0         # prompt groups per optimizer step (0 or >= the batch: one update per step)
     n: int = 4                           # sessions per group
     trainer_mode: str = "separate_async"
     parameter_sync_step: int = 1
@@ -49,6 +50,7 @@ class TrainerConfig:
     def from_config(cls, cfg) -> "TrainerConfig":
         tr, v1 = cfg.trainer, cfg.trainer.v1
         return cls(total_training_steps=int(tr.total_training_steps), train_batch_size=int(cfg.data.train_batch_size),
+                   ppo_mini_batch_size=int(cfg.actor_rollout_ref.actor.get("ppo_mini_batch_size", 0) or 0),
                    n=int(cfg.actor_rollout_ref.rollout.n), trainer_mode=str(v1.trainer_mode),
                    parameter_sync_step=int(v1.separate_async.parameter_sync_step),
                    max_token_len_per_gpu=int(cfg.actor_rollout_ref.actor.ppo_max_token_len_per_gpu), save_freq=int(tr.save_freq),
@@ -225,25 +227,47 @@ class Trainer:
     def train_step(self) -> dict:
         t0 = time.time()
         cap = None if self.cfg.trainer_mode == "sync" else self.replay.max_inflight_sessions
-        groups, parts, stats = [], None, None
+        groups, chunks = [], None
         if self.is_driver:
             groups = self.replay.sample(self.engine.policy_version, self.cfg.train_batch_size, refill=self._refill,
                                         timeout_s=self.cfg.sample_timeout_s, progress=self._while_waiting)
-            parts, stats = self._build(groups)
+            # the batch is trained in mini-batches of `ppo_mini_batch_size` prompt groups, one optimizer step each (upstream's
+            # update loop); advantages are per group, so a group never straddles two updates
+            mini = self.cfg.ppo_mini_batch_size if 0 < self.cfg.ppo_mini_batch_size < len(groups) else len(groups)
+            chunks = [self._build(groups[i:i + mini]) for i in range(0, len(groups), mini)]
         t_gen = time.time() - t0
         if self.engine.world > 1:
             import torch.distributed as dist
 
-            box = [parts, stats]
+            box = [chunks]
             dist.broadcast_object_list(box, src=dist.get_global_rank(self.engine.group, 0), group=self.engine.group)
-            parts, stats = box
-        mbs = parts[self.engine.dp_rank]
-        total = stats.pop("_total_loss_tokens")
+            chunks = box[0]
         t1 = time.time()
-        with nvtx.annotate("trainer/forward_backward"):
-            metrics = self.engine.forward_backward_batch(mbs, total_loss_tokens=total) if mbs else {}
-        with nvtx.annotate("trainer/optimizer_step"):
-            metrics.update(self.engine.optimizer_step())
+        version = self.engine.policy_version
+        metrics, stats = {}, {}
+        for ci, (parts, cstats) in enumerate(chunks):
+            mbs = parts[self.engine.dp_rank]
+            total = cstats.pop("_total_loss_tokens")
+            with nvtx.annotate("trainer/forward_backward"):
+                m = self.engine.forward_backward_batch(mbs, total_loss_tokens=total) if mbs else {}
+            with nvtx.annotate("trainer/optimizer_step"):
+                m.update(self.engine.optimizer_step())
+            w = cstats["data/sessions"]
+            for k, v in m.items():  # update metrics: session-weighted means over the mini-batches
+                metrics[k] = metrics.get(k, 0.0) + float(v) * w
+            for k, v in cstats.items():
+                if k in ("data/sessions", "data/tokens", "data/response_tokens"):
+                    stats[k] = stats.get(k, 0.0) + v
+                elif k.endswith("/max") or k == "data/max_len":
+                    stats[k] = max(stats.get(k, 0.0), v)
+                else:
+                    stats[k] = stats.get(k, 0.0) + v * w
+        n_sessions = max(1.0, stats.get("data/sessions", 1.0))
+        metrics = {k: v / n_sessions for k, v in metrics.items()}
+        stats = {k: (v if k in ("data/sessions", "data/tokens", "data/response_tokens", "data/max_len") or k.endswith("/max") else v / n_sessions) for k, v in stats.items()}
+        metrics["actor/updates"] = float(len(chunks))
+        # one policy version per trained batch, however many updates it took (none when every update was skipped)
+        self.engine.policy_version = version + (1 if self.engine.policy_version > version else 0)
         t_train = time.time() - t1
         stale = [self.engine.policy_version - 1 - g.issued_version for g in groups]
         if self.is_driver:

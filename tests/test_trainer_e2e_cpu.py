@@ -120,3 +120,20 @@ def test_training_step_on_pixel_observations(tmp_path):
         assert len(hist) == 1 and np.isfinite(hist[0]["actor/grad_norm"]) and enc is not None and enc.encoded >= 1 and enc.hits >= 1
     finally:
         close()
+
+
+@pytest.mark.timeout(600)
+def test_batch_trained_in_mini_batches(tmp_path):
+    """``ppo_mini_batch_size`` below the batch: one optimizer step per mini-batch of prompt groups, one policy version (and one
+    weight sync) per batch."""
+    cfg = _cfg(str(tmp_path / "run"), ["data.train_batch_size=4", "actor_rollout_ref.actor.ppo_mini_batch_size=2", "trainer.total_training_steps=1",
+                                        "trainer.save_freq=0", "actor_rollout_ref.rollout.multi_turn.synthetic_turns=1",
+                                        "actor_rollout_ref.rollout.multi_turn.synthetic_reward=hash"])
+    trainer, close = build_stack(cfg)
+    try:
+        hist = trainer.fit()
+        assert hist[0]["actor/updates"] == 2.0 and trainer.engine.step_count == 2 and trainer.engine.policy_version == 1
+        assert hist[0]["data/sessions"] == 8.0 and hist[0]["train/policy_version"] == 1.0 and hist[0]["weight_sync/buckets"] >= 1
+        assert trainer.manager.router.servers[0].engine.policy_version == 1
+    finally:
+        close()
