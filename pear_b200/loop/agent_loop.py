@@ -30,7 +30,8 @@ from ..sim.server import ServerPool
 from ..utils.files import append_jsonl
 from ..utils.tokenizer import ByteTokenizer
 from .episode import EndReason, Episode, LoopState
-from .protocol import ParseError, parse_answer
+from .protocol import ParseError, parse_answer, validate_action
+from .tool_parser import get_parser
 
 
 @dataclass
@@ -47,6 +48,7 @@ class AgentLoopConfig:
     # synthetic benchmarks with a random-init policy: play `synthetic_turns` turns with a no-op action whatever the answer
     # says, at most `turn_max_tokens` sampled tokens per turn (0: the episode budget), and draw the reward ("hash": a seeded
     # hash of the sampled tokens mapped to {0, 1}; "bernoulli:p": a seeded coin per trajectory) instead of the env's success
+    tool_parser: str = "fenced_json"  # how an answer becomes the environment tool's call (`loop/tool_parser.py` registry)
     synthetic_turns: int = 0
     turn_max_tokens: int = 0
     synthetic_reward: Optional[str] = None
@@ -59,6 +61,7 @@ class AgentLoop:
         self.router, self.pool, self.tok, self.cfg, self.vision = router, pool, tokenizer, cfg, vision
         self.schemas, self.queue, self.tracker = schemas, queue, tracker
         self.system_prompt = load_system_prompt()
+        self.parse_calls = get_parser(cfg.tool_parser)
 
     # -- token bookkeeping --------------------------------------------------------------------------------------------
     def _append(self, ep: Episode, ids: list[int], mask: int, logprobs=None, topk_ids=None, topk_lps=None, version: int = 0) -> None:
@@ -166,7 +169,12 @@ class AgentLoop:
                         continue
                     answer = self.tok.decode([t for t in req.output if t != self.tok.eos_id])
                     try:
-                        action = parse_answer(answer, schema)
+                        calls = self.parse_calls(answer)
+                        if len(calls) != 1:  # one call to the environment per turn; none: the answer had no action
+                            parse_answer(answer, schema)  # (raises with the reason when the default format finds none either)
+                            raise ParseError(f"{len(calls)} tool calls in one answer")
+                        action = calls[0].arguments
+                        validate_action(action, schema)
                     except ParseError as e:
                         self._log_turn(ep, state, parse_error=str(e))
                         ep.end_reason, state = EndReason.PARSE, LoopState.TERMINATED

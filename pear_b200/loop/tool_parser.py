@@ -40,5 +40,6 @@ def fenced_json(text: str) -> list[ToolCall]:
         return []
 
 
-# the hybrid GDN + attention family answers in the same format
+# the hybrid GDN + attention family answers in the same format (`multi_turn.format` of the recipes names it)
 register("qwen3_5")(fenced_json)
+register("qwen3_8")(fenced_json)
