@@ -191,6 +191,34 @@ class RolloutServer:
                 out["choices"][0]["text"] = tokenizer.decode(req.output)
             return out
 
+        @app.post("/v1/chat/completions")
+        def chat(body: dict) -> dict:
+            """The OpenAI chat form for third-party clients (benchmark harnesses, agent CLIs): ``messages`` are rendered with the
+            tokenizer's chat template, the assistant header is opened, generation stops at the end-of-turn token."""
+            if tokenizer is None:
+                return {"error": "chat completions need a tokenizer"}
+            ids: list[int] = []
+            for m in body.get("messages", []):
+                content = m.get("content", "")
+                if isinstance(content, list):  # content parts: the text parts, in order
+                    content = "".join(part.get("text", "") for part in content if part.get("type", "text") == "text")
+                ids += tokenizer.render_turn(str(m.get("role", "user")), str(content))
+            ids += tokenizer.generation_prompt()
+            stops = (tokenizer.eos_id,) + tuple(getattr(tokenizer, "extra_stop_ids", ()))
+            params = SamplingParams(max_tokens=int(body.get("max_tokens") or body.get("max_completion_tokens") or 256),
+                                    temperature=float(body.get("temperature", 1.0)), top_p=float(body.get("top_p", 1.0)),
+                                    top_k=int(body.get("top_k", -1) or -1), seed=(int(body["seed"]) if body.get("seed") is not None else None),
+                                    stop_token_ids=stops)
+            choices, completion_tokens = [], 0
+            for i in range(int(body.get("n", 1))):
+                req = self.generate(ids, params, session=body.get("user"))
+                completion_tokens += len(req.output)
+                text = tokenizer.decode([t for t in req.output if t not in stops], skip_special=True)
+                choices.append({"index": i, "message": {"role": "assistant", "content": text},
+                                "finish_reason": "stop" if req.finish == FinishReason.STOP else (req.finish.value if req.finish else None)})
+            return {"id": f"chatcmpl-{req.request_id}", "object": "chat.completion", "model": body.get("model", self.name), "choices": choices,
+                    "usage": {"prompt_tokens": len(ids), "completion_tokens": completion_tokens}}
+
         @app.post("/pause")
         def pause(body: Optional[dict] = None) -> dict:
             return {"aborted": self.pause(abort=bool((body or {}).get("abort", True)))}

@@ -87,3 +87,25 @@ def test_server_metrics_pause_resubmit_and_benchmark():
         assert len(req.output) == 4 and req.policy_version == 7
     finally:
         srv.close()
+
+
+def test_chat_completions_endpoint_renders_the_template():
+    from fastapi.testclient import TestClient
+
+    cfg = HybridConfig.tiny()
+    srv = build_server(HybridForCausalLM(cfg, with_mtp=False).init_weights(0), EngineConfig(num_blocks=128, max_num_seqs=4))
+    try:
+        tok = ByteTokenizer()
+        client = TestClient(srv.http_app(tok))
+        body = {"model": "m", "messages": [{"role": "system", "content": "be brief"}, {"role": "user", "content": [{"type": "text", "text": "2+2?"}]}],
+                "max_tokens": 5, "temperature": 0.0, "n": 2}
+        out = client.post("/v1/chat/completions", json=body).json()
+        assert out["object"] == "chat.completion" and len(out["choices"]) == 2 and out["choices"][0]["message"]["role"] == "assistant"
+        want_prompt = tok.render_turn("system", "be brief") + tok.render_turn("user", "2+2?") + tok.generation_prompt()
+        assert out["usage"]["prompt_tokens"] == len(want_prompt) and 0 < out["usage"]["completion_tokens"] <= 10
+        direct = srv.generate(want_prompt, SamplingParams(max_tokens=5, temperature=0.0, stop_token_ids=(tok.eos_id,)))
+        assert out["choices"][0]["message"]["content"] == tok.decode([t for t in direct.output if t != tok.eos_id], skip_special=True)
+        assert out["choices"][0]["message"]["content"] == out["choices"][1]["message"]["content"]  # greedy twice
+        assert "error" in TestClient(srv.http_app()).post("/v1/chat/completions", json=body).json()
+    finally:
+        srv.close()
