@@ -80,5 +80,55 @@ def build(verbose: bool = False, ptxas_info: bool = False) -> Path:
     return LIB
 
 
+def resources() -> list[dict]:
+    """What the compiler made of every kernel, from ``-Xptxas -v`` (registers, spills, static shared memory, barriers): each
+    source is compiled once more into a scratch object; nothing of the build is touched and no GPU is needed."""
+    import re
+    import tempfile
+
+    rows: list[dict] = []
+
+    def run(src):
+        with tempfile.TemporaryDirectory() as d:
+            r = subprocess.run([NVCC, "-Xptxas", "-v", *FLAGS, "-c", str(src), "-o", os.path.join(d, "x.o")], capture_output=True, text=True)
+        return src, r
+
+    with ThreadPoolExecutor(max_workers=8) as pool:
+        for src, r in pool.map(run, sorted(CSRC.glob("*.cu"))):
+            if r.returncode != 0:
+                raise RuntimeError(f"nvcc failed on {src.name}:\n{r.stderr}")
+            name, spill = None, (0, 0, 0)
+            for line in r.stderr.splitlines():
+                m = re.search(r"Compiling entry function '(\S+)'", line)
+                if m:
+                    name = m.group(1)
+                    continue
+                m = re.search(r"(\d+) bytes stack frame, (\d+) bytes spill stores, (\d+) bytes spill loads", line)
+                if m:
+                    spill = tuple(int(x) for x in m.groups())
+                    continue
+                m = re.search(r"Used (\d+) registers(?:, used (\d+) barriers)?(?:, (\d+) bytes smem)?", line)
+                if m and name:
+                    rows.append({"file": src.name, "kernel": name, "registers": int(m.group(1)), "barriers": int(m.group(2) or 0),
+                                 "static_smem": int(m.group(3) or 0), "stack": spill[0], "spill_stores": spill[1], "spill_loads": spill[2]})
+                    name, spill = None, (0, 0, 0)
+    names = "\n".join(r["kernel"] for r in rows)
+    try:  # readable names when binutils is present
+        out = subprocess.run(["c++filt"], input=names, capture_output=True, text=True, check=True).stdout.splitlines()
+        for r, n in zip(rows, out):
+            r["kernel"] = re.sub(r"\(.*$", "", n).replace("pear::", "").replace("(anonymous namespace)::", "")
+    except (OSError, subprocess.CalledProcessError):
+        pass
+    return rows
+
+
 if __name__ == "__main__":
-    print(build(verbose="-v" in sys.argv, ptxas_info="--ptxas" in sys.argv))
+    if "--resources" in sys.argv:
+        table = resources()
+        print("| file | kernel | registers | spill stores / loads (B) | stack (B) | static smem (B) | barriers |\n| --- | --- | --- | --- | --- | --- | --- |")
+        for r in table:
+            print(f"| {r['file']} | `{r['kernel']}` | {r['registers']} | {r['spill_stores']} / {r['spill_loads']} | {r['stack']} | {r['static_smem']} | {r['barriers']} |")
+        spilled = [r for r in table if r["spill_stores"] or r["spill_loads"]]
+        print(f"\n{len(table)} kernels, {len(spilled)} with register spills, at most {max(r['registers'] for r in table)} registers per thread")
+    else:
+        print(build(verbose="-v" in sys.argv, ptxas_info="--ptxas" in sys.argv))
