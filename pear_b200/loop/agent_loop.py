@@ -77,6 +77,7 @@ class AgentLoop:
         ids: list[int] = []
         if first:
             ids += self.tok.render_turn("system", self.system_prompt)
+        pixels = [f if (f.ndim == 3 and f.dtype == np.uint8) else None for f in obs.frames]
         if self.vision is not None:
             obs.frames = self.vision.encode(obs.frames)
         elif any(f.ndim != 2 for f in obs.frames):
@@ -91,6 +92,8 @@ class AgentLoop:
         while j < len(turn) and f < len(obs.frames):
             if turn[j] == self.tok.image_pad_id:
                 ep.embeds.append((base + j, np.asarray(obs.frames[f], dtype=np.float32)))
+                if pixels[f] is not None:  # a trainer with the tower in its graph recomputes this block from the picture
+                    ep.images.append((base + j, pixels[f]))
                 j += n_img_tokens
                 f += 1
             else:
@@ -217,6 +220,7 @@ class AgentLoop:
                 "topk_ids": np.asarray(ep.topk_ids, dtype=np.int64).reshape(len(ep.tokens), -1),
                 "topk_logprobs": np.asarray(ep.topk_logprobs, dtype=np.float32).reshape(len(ep.tokens), -1),
                 "embeds": [(p, b.astype(np.float16)) for p, b in ep.embeds],
+                "images": list(ep.images),
                 "policy_versions": np.asarray(ep.policy_versions, dtype=np.int32),
                 "reward": reward, "prompt_len": ep.prompt_len,
             }, family=ep.family, end_reason=ep.end_reason.value if ep.end_reason else None, turns=ep.turns, restarts=ep.restarts)

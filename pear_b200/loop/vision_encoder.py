@@ -28,6 +28,18 @@ class VisionEncoder:
         self.lock = threading.Lock()
         self.encoded = self.hits = 0
 
+    def follow(self, state: dict, version: int = 0, prefix: str = "visual.") -> None:
+        """Take the tower's weights out of a trainer state (``WeightSync`` listener): encodings of the previous policy are dropped."""
+        own = dict(self.tower.state_dict())
+        mine = {k[len(prefix):]: v for k, v in state.items() if k.startswith(prefix) and k[len(prefix):] in own}
+        if not mine:
+            return
+        with self.lock:
+            with torch.no_grad():
+                for k, v in mine.items():
+                    own[k].copy_(v.to(own[k].dtype))
+            self.cache.clear()
+
     @staticmethod
     def is_pixels(frame: np.ndarray) -> bool:
         return frame.ndim == 3 and frame.dtype == np.uint8

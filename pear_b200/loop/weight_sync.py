@@ -269,9 +269,12 @@ def receive_all(transport, server) -> int:
 
 
 class WeightSync:
-    def __init__(self, cfg: SyncConfig, transport, servers: Optional[list] = None, heartbeat=None):
-        """``heartbeat``: checked before anything of a sync starts (``PeerLost`` names the replica ranks that are gone)."""
+    def __init__(self, cfg: SyncConfig, transport, servers: Optional[list] = None, heartbeat=None, listeners: Optional[list] = None):
+        """``heartbeat``: checked before anything of a sync starts (``PeerLost`` names the replica ranks that are gone).
+        ``listeners``: callables ``(state, version)`` of this process that also follow the policy (the agent loop's vision
+        encoder), called with the trainer's full-precision state while the replicas are paused."""
         self.cfg, self.transport, self.servers, self.heartbeat = cfg, transport, servers or [], heartbeat
+        self.listeners = listeners or []
         self.last_seconds = 0.0
         self.bytes_sent = 0
 
@@ -288,6 +291,8 @@ class WeightSync:
         for i, b in enumerate(bl):
             self.transport.send(b, version, last=(i == len(bl) - 1))
             sent += sum(t.numel() * t.element_size() for _, t in b)
+        for listen in self.listeners:
+            listen(state, version)
         for s in self.servers:
             if hasattr(s, "wait_version"):  # a replica in another process loads on a thread of its own
                 s.wait_version(version)

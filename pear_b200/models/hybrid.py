@@ -292,12 +292,19 @@ class MTPHead(nn.Module):
 
 
 class HybridForCausalLM(nn.Module):
-    def __init__(self, cfg: HybridConfig, with_mtp: bool = True):
+    def __init__(self, cfg: HybridConfig, with_mtp: bool = True, vision=None):
+        """``vision``: a ``models.vision.VisionConfig``: the model then owns a vision tower (``visual``) whose rows the trainer
+        computes from the trajectories' pictures with gradients (rollout replicas get finished rows and build without it)."""
         super().__init__()
         self.config = cfg
         self.model = Backbone(cfg)
         self.lm_head = nn.Linear(cfg.hidden_size, cfg.vocab_size, bias=False)
         self.mtp = MTPHead(cfg) if (with_mtp and cfg.num_mtp_layers > 0) else None
+        self.visual = None
+        if vision is not None:
+            from .vision import VisionTower
+
+            self.visual = VisionTower(vision)
         self.gradient_checkpointing = False
         self.activation_offload = None  # train.offload.CheckpointInputOffload when enabled
 
@@ -321,6 +328,8 @@ class HybridForCausalLM(nn.Module):
                     p.fill_(1.0)
                 else:
                     p.zero_()
+        if self.visual is not None:
+            self.visual.init_weights(seed)  # its own rule (LayerNorm weights are ones)
         return self
 
     def init_weights_device(self, seed: int = 0) -> "HybridForCausalLM":
@@ -343,6 +352,8 @@ class HybridForCausalLM(nn.Module):
                     p.fill_(1.0)
                 else:
                     p.zero_()
+        if self.visual is not None:
+            self.visual.init_weights(seed)
         return self
 
     def rope(self, position_ids: torch.Tensor):

@@ -48,6 +48,9 @@ class PackedBatch:
     head_log_probs: Optional[torch.Tensor] = None
     inputs_embeds: Optional[torch.Tensor] = None
     embeds_mask: Optional[torch.Tensor] = None
+    # pictures whose rows the trainer computes itself (a vision tower in the training graph): (position of the first row in the
+    # packed batch, uint8 [H, W, 3] picture); positions are global to the batch and survive padding and slicing unchanged
+    images: Optional[list] = None
 
     @property
     def num_tokens(self) -> int:
@@ -79,7 +82,8 @@ class PackedBatch:
             labels=ext(self.labels), loss_mask=ext(self.loss_mask), advantages=ext(self.advantages),
             sampler_log_probs=ext(self.sampler_log_probs), head_ids=ext(self.head_ids),
             head_log_probs=ext(self.head_log_probs, -math.log(max(1, self.head_ids.shape[1])) if self.head_ids is not None else 0),
-            inputs_embeds=ext(self.inputs_embeds), embeds_mask=ext(self.embeds_mask, False) if self.embeds_mask is not None else None)
+            inputs_embeds=ext(self.inputs_embeds), embeds_mask=ext(self.embeds_mask, False) if self.embeds_mask is not None else None,
+            images=self.images)
 
     def slice(self, lo: int, hi: int) -> "PackedBatch":
         def cut(t):
@@ -87,7 +91,7 @@ class PackedBatch:
         pos = self.position_ids[..., lo:hi]
         return PackedBatch(cut(self.input_ids), pos, self.cu_seqlens, cut(self.labels), cut(self.loss_mask), cut(self.advantages),
                            cut(self.sampler_log_probs), cut(self.head_ids), cut(self.head_log_probs), cut(self.inputs_embeds),
-                           cut(self.embeds_mask))
+                           cut(self.embeds_mask), self.images)
 
 
 @dataclass
@@ -152,7 +156,9 @@ class EngineConfig:
 class TrainEngine:
     def __init__(self, model_cfg: HybridConfig, cfg: EngineConfig, device="cpu", world_group=None, replicate_group=None,
                  kernels: Optional[type[TrainingKernels]] = None, seed: int = 0, state_dict: Optional[dict] = None,
-                 with_mtp: bool = False):
+                 with_mtp: bool = False, vision=None):
+        """``vision``: a ``VisionConfig``: the model gets a vision tower, kept in fp32 units of its own, and batches may carry
+        pictures (``PackedBatch.images``) whose rows are computed here, sharded over the sequence-parallel ranks."""
         self.model_cfg, self.cfg, self.device = model_cfg, cfg, torch.device(device)
         self.group = world_group
         self.world = dist.get_world_size(world_group) if world_group is not None else 1
@@ -201,9 +207,9 @@ class TrainEngine:
         on_meta = self.src_rank is not None and self.shard_rank != self.src_rank
         if on_meta:
             with torch.device("meta"):
-                model = HybridForCausalLM(model_cfg, with_mtp=with_mtp)
+                model = HybridForCausalLM(model_cfg, with_mtp=with_mtp, vision=vision)
         else:
-            model = HybridForCausalLM(model_cfg, with_mtp=with_mtp)
+            model = HybridForCausalLM(model_cfg, with_mtp=with_mtp, vision=vision)
             if state_dict is not None:
                 model.load_state_dict(state_dict, strict=False)
             else:
@@ -220,7 +226,8 @@ class TrainEngine:
         if self.device.type == "cpu" and dtype != torch.float32:
             dtype = torch.float32  # CPU plumbing runs in fp32
         self.model = model
-        self.sharded = ShardedModel(model, self.shard_group if self.shard_world > 1 else None, replicate_group, dtype, cfg.fp32_modules,
+        fp32_modules = list(cfg.fp32_modules) + (["visual."] if vision is not None and "visual." not in cfg.fp32_modules else [])
+        self.sharded = ShardedModel(model, self.shard_group if self.shard_world > 1 else None, replicate_group, dtype, fp32_modules,
                                     self.device, src_rank=self.src_rank)
         for mod in model.modules():  # buffers (none hold weights) follow the parameters' device
             for bname, buf in list(mod._buffers.items()):
@@ -258,8 +265,11 @@ class TrainEngine:
         t_local = t // self.sp_size
         lo = self.sp_rank * t_local
         loc = mb.slice(lo, lo + t_local) if self.sp_size > 1 else mb
-        hidden = self.model(loc.input_ids, loc.position_ids, mb.cu_seqlens, inputs_embeds=loc.inputs_embeds,
-                            embeds_mask=loc.embeds_mask, sp=self.sp, offset=lo)
+        inputs_embeds, embeds_mask = loc.inputs_embeds, loc.embeds_mask
+        if mb.images and self.model.visual is not None:
+            inputs_embeds, embeds_mask = self._image_rows(mb.images, lo, t_local, inputs_embeds, embeds_mask)
+        hidden = self.model(loc.input_ids, loc.position_ids, mb.cu_seqlens, inputs_embeds=inputs_embeds,
+                            embeds_mask=embeds_mask, sp=self.sp, offset=lo)
         ids = loc.labels[:, None].long()
         use_sc = cfg.loss.score_centering and loc.head_ids is not None
         if use_sc:
@@ -273,6 +283,31 @@ class TrainEngine:
             sampler_head_log_probs=loc.head_log_probs if use_sc else None, sampler_log_probs=loc.sampler_log_probs,
             entropy=ent, denominator=denom)
         return loss, metrics
+
+    def _image_rows(self, images: list, lo: int, t_local: int, inputs_embeds, embeds_mask):
+        """The vision tower's rows for a micro-batch's pictures, placed at their positions inside this rank's slice
+        ``[lo, lo + t_local)``. Every picture is encoded once, by the sequence-parallel rank it is dealt to (by patch count);
+        the rows are all-gathered with gradients (``parallel/vision_sp.py``), so the tower trains under the policy loss."""
+        from ..parallel.vision_sp import encode_sharded
+
+        dev = self.device
+        pics = [(torch.as_tensor(img).to(dev).permute(2, 0, 1).float() / 127.5 - 1.0) for _, img in images]
+        rows = encode_sharded(self.model.visual, pics, self.sp_group)
+        h = self.model_cfg.hidden_size
+        base = inputs_embeds.float() if inputs_embeds is not None else torch.zeros(t_local, h, device=dev)
+        mask = embeds_mask.clone() if embeds_mask is not None else torch.zeros(t_local, dtype=torch.bool, device=dev)
+        idx, parts = [], []
+        for (pos, _), block in zip(images, rows):
+            a, b = max(pos, lo), min(pos + block.shape[0], lo + t_local)
+            if a < b:
+                idx.append(torch.arange(a - lo, b - lo, device=dev))
+                parts.append(block[a - pos:b - pos])
+        keep = sum(r.sum() for r in rows) * 0.0  # every rank's graph reaches the gathered rows: the backward collectives stay matched
+        if idx:
+            where = torch.cat(idx)
+            base = base.index_copy(0, where, torch.cat(parts).to(base.dtype))
+            mask[where] = True
+        return base + keep, mask
 
     def forward_backward_batch(self, micro_batches: list[PackedBatch], total_loss_tokens: Optional[int] = None) -> dict:
         """Accumulate gradients over this DP rank's micro-batches. ``total_loss_tokens``: loss tokens of the GLOBAL

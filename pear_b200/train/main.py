@@ -164,7 +164,15 @@ def build_stack(cfg, replicas: int = 1, device: str = "cpu", env_families: Optio
                 (log.warning if over else log.info)("trainer memory plan per GPU%s:\n%s", " (OVER the device's capacity)" if over else "", mp.table())
         except Exception as e:  # noqa: BLE001 - a planning note never stops a run
             log.warning("trainer memory plan skipped: %r", e)
-    engine = TrainEngine(mcfg, ecfg, device=device, world_group=world_group, seed=int(cfg.trainer.seed), state_dict=init)
+    vcfg = cfg.actor_rollout_ref.model.get("vision", None)
+    vision_cfg = None
+    if vcfg is not None and bool(vcfg.enable):
+        from ..models.vision import VisionConfig
+
+        vision_cfg = getattr(VisionConfig, str(vcfg.preset))(out_hidden=mcfg.hidden_size)
+    train_vision = vision_cfg is not None and bool(vcfg.get("train", False))
+    engine = TrainEngine(mcfg, ecfg, device=device, world_group=world_group, seed=int(cfg.trainer.seed), state_dict=init,
+                         vision=vision_cfg if train_vision else None)
     rank = engine.rank
     if rank == 0:
         mcfg.save(os.path.join(str(cfg.run_dir), "model_config.json"))  # the offline merger reads it
@@ -222,12 +230,13 @@ def build_stack(cfg, replicas: int = 1, device: str = "cpu", env_families: Optio
         from ..utils.tokenizer import load_tokenizer
 
         vision = None
-        vcfg = cfg.actor_rollout_ref.model.get("vision", None)
-        if vcfg is not None and bool(vcfg.enable):
+        if vision_cfg is not None:
             from ..loop.vision_encoder import VisionEncoder
-            from ..models.vision import VisionConfig, VisionTower
+            from ..models.vision import VisionTower
 
-            tower = VisionTower(getattr(VisionConfig, str(vcfg.preset))(out_hidden=mcfg.hidden_size)).init_weights(int(cfg.trainer.seed))
+            tower = VisionTower(vision_cfg).init_weights(int(cfg.trainer.seed))
+            if train_vision:  # the agent loop's copy starts from (and then follows) the trainer's tower
+                tower.load_state_dict({k[len("visual."):]: v for k, v in full.items() if k.startswith("visual.")})
             pixel_dtype = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[str(cfg.data.get("pixel_dtype", "fp32"))]
             vision = VisionEncoder(tower, str(vcfg.device), pixel_dtype=pixel_dtype)
         manager = AgentLoopManager(servers, mcfg.hidden_size, families, acfg, queue, num_workers=int(ro.agent.num_workers),
@@ -241,7 +250,8 @@ def build_stack(cfg, replicas: int = 1, device: str = "cpu", env_families: Optio
     dataset = EpisodeDataset(files if files is not None else {"family": "synthetic", "args": {"task": ["reach"], "seed": list(range(64))}},
                              seed=int(cfg.trainer.seed))
     sync = WeightSync(SyncConfig(int(ce.update_weights_bucket_megabytes), getattr(torch, str(ro.dtype)), tuple(ro.fp32_modules)),
-                      transport or InProcessTransport(servers), servers, heartbeat=heartbeat) if rank == 0 else None
+                      transport or InProcessTransport(servers), servers, heartbeat=heartbeat,
+                      listeners=[manager.loop.vision.follow] if (manager is not None and manager.loop.vision is not None and train_vision) else None) if rank == 0 else None
     if sync is not None and urls:  # replica processes built their own weights: start them from the trainer's policy
         sync.sync(full, engine.policy_version)
     ckpt = CheckpointManager(str(cfg.run_dir), rank, engine.world, cfg.trainer.max_actor_ckpt_to_keep,

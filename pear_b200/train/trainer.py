@@ -58,8 +58,9 @@ class TrainerConfig:
                    topk_heads=int(cfg.actor_rollout_ref.rollout.get("topk_log_probs", 0)))
 
 
-def trajectory_to_rows(tr: dict, advantage: float, hidden: int, topk: int):
-    """One trajectory -> per-token training rows (inputs t, labels t+1)."""
+def trajectory_to_rows(tr: dict, advantage: float, hidden: int, topk: int, train_vision: bool = False):
+    """One trajectory -> per-token training rows (inputs t, labels t+1). ``train_vision``: blocks that came from pictures are
+    handed over as pictures (the trainer's tower computes their rows with gradients), the others as finished rows."""
     tokens = torch.from_numpy(np.asarray(tr["tokens"])).long()
     n = tokens.numel()
     mask = torch.from_numpy(np.asarray(tr["response_mask"])).float()
@@ -74,10 +75,15 @@ def trajectory_to_rows(tr: dict, advantage: float, hidden: int, topk: int):
         hlp = torch.from_numpy(np.asarray(tr["topk_logprobs"])).float().reshape(n, -1)[:, :topk]
         out["head_ids"] = torch.cat([ids[1:], ids[:1]]).int()
         out["head_log_probs"] = torch.cat([hlp[1:], hlp[:1]])
-    if tr.get("embeds"):
+    from_pixels = {int(p) for p, _ in tr.get("images", [])} if train_vision else set()
+    if from_pixels:
+        out["images"] = [(int(p), torch.from_numpy(np.ascontiguousarray(img))) for p, img in tr["images"]]
+    if tr.get("embeds") and any(int(p) not in from_pixels for p, _ in tr["embeds"]):
         e = torch.zeros(n, hidden)
         m = torch.zeros(n, dtype=torch.bool)
         for pos, block in tr["embeds"]:
+            if int(pos) in from_pixels:
+                continue
             b = torch.from_numpy(np.asarray(block, dtype=np.float32))
             e[pos:pos + b.shape[0]] = b
             m[pos:pos + b.shape[0]] = True
@@ -100,9 +106,10 @@ def pack_rows(rows: list[dict]) -> PackedBatch:
         h = next(r["inputs_embeds"].shape[1] for r in rows if "inputs_embeds" in r)
         emb = torch.cat([r.get("inputs_embeds", torch.zeros(r["input_ids"].numel(), h)) for r in rows])
         em = torch.cat([r.get("embeds_mask", torch.zeros(r["input_ids"].numel(), dtype=torch.bool)) for r in rows])
+    images = [(cu[i] + pos, img) for i, r in enumerate(rows) for pos, img in r.get("images", [])]
     return PackedBatch(cat("input_ids"), cat("position_ids"), cu, cat("labels"), cat("loss_mask"), cat("advantages"),
                        sampler_log_probs=cat("sampler_log_probs"), head_ids=cat("head_ids"), head_log_probs=cat("head_log_probs"),
-                       inputs_embeds=emb, embeds_mask=em)
+                       inputs_embeds=emb, embeds_mask=em, images=images or None)
 
 
 def balanced_partition(sizes: list[int], parts: int) -> list[list[int]]:
@@ -212,7 +219,7 @@ class Trainer:
             adv = grpo.group_advantages(rewards[None], self.cfg.norm_adv_by_std)[0]
             rewards_all += rewards.tolist()
             for t, a in zip(trs, adv.tolist()):
-                rows.append(trajectory_to_rows(t, a, hidden, self.cfg.topk_heads))
+                rows.append(trajectory_to_rows(t, a, hidden, self.cfg.topk_heads, train_vision=self.engine.model.visual is not None))
                 lengths.append(len(t["tokens"]))
         dp = self.engine.dp_size
         parts = [[pack_rows(mb) for mb in micro_batches([rows[i] for i in mine], self.cfg.max_token_len_per_gpu)]

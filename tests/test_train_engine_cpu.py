@@ -243,3 +243,47 @@ def test_engine_resolves_the_family_kernels_the_recipe_names(tmp_path):
     assert eng.kernels is Qwen3_5TrainingKernels and eng.model.fp32_residual and eng.model.use_fused_head and eng.model.recompute_skips_down_proj
     eng.forward_backward_batch([make_batch(HybridConfig.tiny(), 0, k=ecfg.topk_log_probs or 4)])
     assert eng.optimizer_step()["actor/grad_norm"] > 0
+
+
+def _vision_rank_fn(rank, world, out_dir, sp):
+    import torch.distributed as dist
+
+    from pear_b200.models.vision import VisionConfig
+
+    cfg = HybridConfig.tiny()
+    eng = TrainEngine(cfg, _ecfg(sp), world_group=dist.group.WORLD, seed=5, vision=VisionConfig.tiny(out_hidden=cfg.hidden_size))
+    eng.forward_backward_batch([_vision_batch(cfg)])
+    m = eng.optimizer_step()
+    state = eng.full_state_dict()
+    if rank == 0:
+        torch.save({"state": state, "norm": m["actor/grad_norm"]}, os.path.join(out_dir, "out.pt"))
+
+
+def _vision_batch(cfg):
+    from pear_b200.models.vision import VisionConfig, VisionTower
+
+    b = make_batch(cfg, 0)
+    g = torch.Generator().manual_seed(9)
+    n_tok = VisionTower(VisionConfig.tiny()).tokens_per_image(16, 16)
+    # three pictures: inside the first sequence, across the middle of the batch (the boundary of two sequence-parallel slices), near the end
+    b.images = [(pos, torch.randint(0, 256, (16, 16, 3), generator=g, dtype=torch.uint8)) for pos in (3, b.num_tokens // 2 - n_tok // 2, b.num_tokens - n_tok - 2)]
+    return b
+
+
+def test_pictures_are_encoded_once_over_the_sequence_parallel_ranks_and_train_the_tower(tmp_path):
+    """The trainer's own vision tower: a batch with pictures gives the same step on two sequence-parallel ranks (each picture
+    encoded by one rank, rows all-gathered with gradients, one picture's rows straddling the slice boundary) as on one."""
+    from pear_b200.models.vision import VisionConfig
+
+    cfg = HybridConfig.tiny()
+    eng = TrainEngine(cfg, _ecfg(), seed=5, vision=VisionConfig.tiny(out_hidden=cfg.hidden_size))
+    w0 = {k: v.clone() for k, v in eng.full_state_dict().items()}
+    eng.forward_backward_batch([_vision_batch(cfg)])
+    m = eng.optimizer_step()
+    want = eng.full_state_dict()
+    assert any(k.startswith("visual.") and not torch.equal(w0[k], want[k]) for k in want)  # the tower moved
+    run_ranks(_vision_rank_fn, 2, tmp_path, str(tmp_path), 2)
+    got = torch.load(os.path.join(str(tmp_path), "out.pt"))
+    assert abs(got["norm"] - m["actor/grad_norm"]) < 2e-4 * max(1.0, m["actor/grad_norm"])
+    for k, v in want.items():
+        assert torch.allclose(got["state"][k], v, atol=5e-5, rtol=2e-4), k

@@ -137,3 +137,29 @@ def test_batch_trained_in_mini_batches(tmp_path):
         assert trainer.manager.router.servers[0].engine.policy_version == 1
     finally:
         close()
+
+
+@pytest.mark.timeout(600)
+def test_vision_tower_trains_under_the_policy_loss_and_the_agent_loop_follows_it(tmp_path):
+    fam = {"synthetic": {"env_path": "pear_b200.envs.synthetic.SyntheticEnv", "num_processes": 2, "env_kwargs": {"pixels": 16}}}
+    cfg = _cfg(str(tmp_path / "run"), ["actor_rollout_ref.model.vision.enable=true", "actor_rollout_ref.model.vision.train=true",
+                                        "trainer.total_training_steps=1", "trainer.save_freq=1", "actor_rollout_ref.rollout.multi_turn.synthetic_turns=1",
+                                        "actor_rollout_ref.rollout.multi_turn.synthetic_reward=hash"])
+    trainer, close = build_stack(cfg, env_families=fam)
+    try:
+        before = {k: v.clone() for k, v in trainer.engine.full_state_dict().items() if k.startswith("visual.")}
+        enc = trainer.manager.loop.vision
+        assert before and all(torch.equal(enc.tower.state_dict()[k[len("visual."):]], v) for k, v in before.items())  # starts from the trainer's tower
+        hist = trainer.fit()
+        after = {k: v for k, v in trainer.engine.full_state_dict().items() if k.startswith("visual.")}
+        moved = [k for k in before if not torch.equal(before[k], after[k])]
+        assert len(hist) == 1 and np.isfinite(hist[0]["actor/grad_norm"]) and len(moved) >= len(before) // 2, moved
+        assert all(torch.allclose(enc.tower.state_dict()[k[len("visual."):]], v) for k, v in after.items()) and not enc.cache  # followed, old encodings dropped
+        # the tower is part of the checkpoint and of the exported model directory
+        from pear_b200.train.checkpoint import export_model
+
+        export_model(trainer.engine, str(tmp_path / "export"))
+        names = [model_io.from_hf_name(n) for n in model_io.model_tensor_names(str(tmp_path / "export"))]
+        assert any(n.startswith("visual.") for n in names)
+    finally:
+        close()
