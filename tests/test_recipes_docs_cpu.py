@@ -155,3 +155,13 @@ def test_every_kernel_launch_is_followed_by_an_error_check():
     for path in sorted(glob.glob(os.path.join(ROOT, "pear_b200", "ops", "csrc", "*.cu")) + glob.glob(os.path.join(ROOT, "pear_b200", "ops", "csrc", "*.cuh"))):
         unchecked += _unchecked_launches(open(path).read(), os.path.basename(path))
     assert not unchecked, "launches without an error check:\n" + "\n".join(unchecked)
+
+
+def test_installation_check_runs_without_a_gpu(capsys):
+    from pear_b200.utils import doctor
+
+    rc = doctor.main([])
+    out = capsys.readouterr().out
+    rows = {line.split()[0] + (" " + line.split()[1] if line.split()[1] not in ("ok", "missing", "n/a") else ""): line for line in out.splitlines() if line.strip() and not line.startswith("missing:")}
+    assert "GPUs" in rows and "no GPU" in rows["GPUs"] and "kernel library" in rows
+    assert rc == (1 if "missing:" in out else 0)
