@@ -26,6 +26,13 @@ class RolePlan:
     module: str = ""
     args: list[str] = field(default_factory=list)
     port: int = 0  # process i of the role listens on port + i
+    # several nodes: the address this node's servers bind, the job-wide index of this node's first process of the role, and the
+    # trainer's rendezvous (torch.distributed.run --nnodes / --node-rank / --master-addr)
+    host: str = "127.0.0.1"
+    index_offset: int = 0
+    nnodes: int = 1
+    node_rank: int = 0
+    master_addr: str = "127.0.0.1"
 
     def gpu_ids(self, index: int) -> list[int]:
         lo = self.gpu_offset + index * self.gpus_per_process
@@ -59,6 +66,42 @@ def plan_node(n_gpus: int, trainer_gpus: int, rollout_tp: int, recipe: str, over
     ]
 
 
+def plan_cluster(node_addrs: list[str], node_rank: int, gpus_per_node: int, trainer_nodes: int, rollout_tp: int, recipe: str,
+                 overrides: list[str], rollout_port: int = ROLLOUT_PORT, env_port: int = ENV_PORT, sync_port: int = SYNC_PORT) -> list[RolePlan]:
+    """The roles of ONE node of a job over several: the first ``trainer_nodes`` nodes train with all their GPUs (one
+    ``torch.distributed.run`` world over them, rendezvous on node 0), every other node serves rollouts in replicas of
+    ``rollout_tp`` GPUs. The trainer's rank 0 (node 0) reaches every replica by its node's address and is rank 0 of the
+    weight-sync world, whose rendezvous is on node 0 as well; node 0 also runs the environment host and the monitor. The same
+    command line runs on every node with its own ``node_rank`` (upstream: scripts/start_ray_node.sh:58-61 gives each node its
+    role through Ray resources)."""
+    n = len(node_addrs)
+    tp = max(1, rollout_tp)
+    if not 0 < trainer_nodes < n or gpus_per_node % tp or not 0 <= node_rank < n:
+        raise ValueError(f"{n} nodes of {gpus_per_node} GPUs: need 0 < trainer nodes ({trainer_nodes}) < nodes, replicas of {tp} GPUs that fill a node, "
+                         f"and a node rank ({node_rank}) below {n}")
+    per_node = gpus_per_node // tp
+    replicas = (n - trainer_nodes) * per_node
+    urls = [f"http://{node_addrs[trainer_nodes + r // per_node]}:{rollout_port + r % per_node}" for r in range(replicas)]
+    sync_master = f"{node_addrs[0]}:{sync_port}"
+    remote = [f"actor_rollout_ref.rollout.checkpoint_engine.replica_urls=[{','.join(urls)}]",
+              f"actor_rollout_ref.rollout.checkpoint_engine.sync_master={sync_master}", f"actor_rollout_ref.rollout.tensor_model_parallel_size={tp}"]
+    force_gloo = "actor_rollout_ref.rollout.checkpoint_engine.backend=gloo" in overrides
+    plans: list[RolePlan] = []
+    if node_rank < trainer_nodes:
+        plans.append(RolePlan("trainer", gpus_per_node, 1, 0, "pear_b200.train.main", [recipe] + overrides + remote, nnodes=trainer_nodes,
+                              node_rank=node_rank, master_addr=node_addrs[0]))
+        if node_rank == 0:
+            plans.append(RolePlan("env", 1, 0, 0, "pear_b200.sim.server", [], env_port, host=node_addrs[0]))
+            plans.append(RolePlan("monitor", 1, 0, 0, "pear_b200.monitor.progress_panel",
+                                  overrides + [a for i, u in enumerate(urls) for a in ("--replica", f"replica-{i}={u}/metrics")]))
+    else:
+        plans.append(RolePlan("rollout", per_node, tp, 0, "pear_b200.rollout.server",
+                              overrides + ["--sync-world", str(replicas * tp + 1), "--sync-master", sync_master, "--exit-with-trainer"]
+                              + (["--sync-backend", "gloo"] if force_gloo else []), rollout_port, host=node_addrs[node_rank],
+                              index_offset=(node_rank - trainer_nodes) * per_node))
+    return plans
+
+
 def gpu_process_env(gpu_ids: list[int], threads: int = 8, cache_dir: str = "") -> dict[str, str]:
     """Environment of one GPU process: visible devices, bounded host thread pools (many processes share a host),
     several NCCL communicators per GPU ordered by host issue order, build cache kept inside the tree."""
@@ -78,8 +121,8 @@ def command(plan: RolePlan, index: int, master_port: int = 29500, replica_master
     after the trainer's."""
     env = gpu_process_env(plan.gpu_ids(index)) if plan.gpus_per_process else {}
     if plan.role == "trainer":
-        cmd = ["python", "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={plan.processes}", "--master-addr", "127.0.0.1",
-               "--master-port", str(master_port), "-m", plan.module] + plan.args
+        cmd = ["python", "-m", "torch.distributed.run", f"--nnodes={plan.nnodes}", f"--nproc-per-node={plan.processes}", "--master-addr", plan.master_addr,
+               "--master-port", str(master_port)] + ([f"--node-rank={plan.node_rank}"] if plan.nnodes > 1 else []) + ["-m", plan.module] + plan.args
         env = gpu_process_env(list(range(plan.gpu_offset, plan.gpu_offset + plan.processes)) if plan.gpus_per_process else [])
     else:
         cmd = ["python", "-m", plan.module] + plan.args
@@ -88,9 +131,12 @@ def command(plan: RolePlan, index: int, master_port: int = 29500, replica_master
             if tp > 1:  # the replica's ranks are a world of their own: rank 0 serves, the others follow in lock-step
                 cmd = ["python", "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={tp}", "--master-addr", "127.0.0.1",
                        "--master-port", str((replica_master_port or master_port + 1) + index), "-m", plan.module] + plan.args
-            cmd += ["--port", str(plan.port + index), "--name", f"replica-{index}", "--sync-rank", str(1 + index * tp)]
+            job_index = plan.index_offset + index
+            cmd += ["--port", str(plan.port + index), "--name", f"replica-{job_index}", "--sync-rank", str(1 + job_index * tp)]
+            if plan.host != "127.0.0.1":
+                cmd += ["--host", plan.host]
         elif plan.role == "env":
-            cmd += ["--port", str(plan.port + index)]
+            cmd += ["--port", str(plan.port + index)] + (["--host", plan.host] if plan.host != "127.0.0.1" else [])
     return cmd, env
 
 

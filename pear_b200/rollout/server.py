@@ -323,7 +323,7 @@ def to_rollout_dtypes(model, dtype: torch.dtype = torch.bfloat16):
 
 
 def start_weight_receiver(server: RolloutServer, rank: int, world: int, master: str, src: int = 0, backend: str = "auto", device: str = "cpu",
-                          heartbeat_s: float = 1.0):
+                          heartbeat_s: float = 1.0, on_sender_gone=None):
     """Join the weight-sync process group ({sending trainer rank} + {replica ranks}) and load every sync the sender starts, on
     a thread of its own: each ``WeightSync.sync`` on the trainer side arrives here as buckets until the last one, then the
     replica loads them, bumps its policy version and clears its KV tiers. Returns the thread."""
@@ -365,6 +365,8 @@ def start_weight_receiver(server: RolloutServer, rank: int, world: int, master: 
             except Exception as e:  # noqa: BLE001 - the group went away (the trainer exited): stop listening, keep serving
                 if not server.stop_flag:
                     server.sync_error = e
+                    if on_sender_gone is not None:
+                        on_sender_gone()
                 return
 
     t = threading.Thread(target=loop, daemon=True, name=f"{server.name}-weight-sync")
@@ -395,6 +397,7 @@ def main(argv=None) -> int:
     ap.add_argument("--sync-world", type=int, default=0, help="size of the weight-sync group: the sending trainer rank + the replica ranks")
     ap.add_argument("--sync-master", default="127.0.0.1:29650", help="host:port of the weight-sync group's rendezvous")
     ap.add_argument("--sync-src", type=int, default=0, help="rank of the sender in the weight-sync group")
+    ap.add_argument("--exit-with-trainer", action="store_true", help="leave (orderly) when the weight-sync world's sender is gone")
     ap.add_argument("--sync-backend", default="auto", choices=["auto", "gloo", "nccl", "nvswitch"],
                     help="nvswitch: pull this replica's shard out of the sender's symmetric staging buffer; gloo / nccl: broadcast")
     args, overrides = ap.parse_known_args(argv)
@@ -445,7 +448,13 @@ def main(argv=None) -> int:
         model = load_rollout_model(path, device=device, drafter_path=args.drafter)
         server = build_server(model, ecfg, device=device, name=args.name)
     if args.sync_rank >= 0:  # a tensor-parallel replica's ranks are consecutive in the weight-sync world
-        start_weight_receiver(server, args.sync_rank + tp_rank, args.sync_world, args.sync_master, args.sync_src, args.sync_backend, device)
+        gone = None
+        if args.exit_with_trainer:  # a replica on a node of its own has nobody to stop it: it ends the way a launcher would end it
+            import signal
+
+            gone = lambda: os.kill(os.getpid(), signal.SIGTERM)  # noqa: E731
+        start_weight_receiver(server, args.sync_rank + tp_rank, args.sync_world, args.sync_master, args.sync_src, args.sync_backend, device,
+                              on_sender_gone=gone)
     try:
         if tp_world > 1 and tp_rank != 0:  # followers mirror the leader until its stop message
             import signal

@@ -106,3 +106,66 @@ def test_rollout_kernel_hooks_check_and_complete_a_replicas_settings(monkeypatch
     monkeypatch.setenv(RolloutKernels.ENV, path)
     with pytest.raises(ValueError, match="16-token blocks"):
         apply_rollout_kernels(None, plain)
+
+
+def test_cluster_plan_gives_every_node_its_roles():
+    from pear_b200.launch.roles import plan_cluster
+
+    addrs = ["10.0.0.1", "10.0.0.2", "10.0.0.3", "10.0.0.4"]
+    head = {p.role: p for p in plan_cluster(addrs, 0, 8, 2, 4, "training", ["run_dir=/r"])}
+    assert set(head) == {"trainer", "env", "monitor"} and head["trainer"].nnodes == 2 and head["trainer"].master_addr == "10.0.0.1"
+    cmd, env = command(head["trainer"], 0, master_port=1234)
+    assert "--nnodes=2" in cmd and "--node-rank=0" in cmd and "--nproc-per-node=8" in cmd and env["CUDA_VISIBLE_DEVICES"] == "0,1,2,3,4,5,6,7"
+    urls = next(a for a in head["trainer"].args if "replica_urls" in a)
+    assert urls.endswith("[http://10.0.0.3:8100,http://10.0.0.3:8101,http://10.0.0.4:8100,http://10.0.0.4:8101]")
+    assert "actor_rollout_ref.rollout.checkpoint_engine.sync_master=10.0.0.1:29650" in head["trainer"].args
+    second = {p.role: p for p in plan_cluster(addrs, 1, 8, 2, 4, "training", ["run_dir=/r"])}
+    assert set(second) == {"trainer"} and "--node-rank=1" in command(second["trainer"], 0)[0]
+    last = {p.role: p for p in plan_cluster(addrs, 3, 8, 2, 4, "training", ["run_dir=/r"])}
+    cmd, env = command(last["rollout"], 1)
+    assert set(last) == {"rollout"} and env["CUDA_VISIBLE_DEVICES"] == "4,5,6,7"
+    assert cmd[cmd.index("--name") + 1] == "replica-3" and cmd[cmd.index("--sync-rank") + 1] == "13" and cmd[cmd.index("--sync-world") + 1] == "17"
+    assert cmd[cmd.index("--host") + 1] == "10.0.0.4" and "--exit-with-trainer" in cmd
+    with pytest.raises(ValueError):
+        plan_cluster(addrs, 0, 8, 4, 4, "training", [])  # no node left for rollouts
+
+
+@pytest.mark.timeout(600)
+def test_two_nodes_on_loopback_addresses(tmp_path):
+    """The same command line on two "nodes" (127.0.0.1 trains with two ranks, 127.0.0.2 serves one replica of two lock-step
+    ranks): the trainer reaches the replica by the other node's address, trains a step, and the rollout node's launcher ends by
+    itself once the trainer's weight-sync world is gone."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    from pear_b200.utils.process import free_ports
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    run = str(tmp_path / "run")
+    master, replica_master, rollout, envp, sync = free_ports(5)
+    common = [sys.executable, "-m", "pear_b200.launch.launch", "training", "--node-addrs", "127.0.0.1,127.0.0.2", "--trainer-nodes", "1", "--gpus", "2",
+              "--rollout-tp", "2", "--master-port", str(master), "--replica-master-port", str(replica_master), "--rollout-port", str(rollout),
+              "--env-port", str(envp), "--sync-port", str(sync), f"run_dir={run}", "actor_rollout_ref.model.path=preset:tiny",
+              "trainer.total_training_steps=1", "trainer.save_freq=0", "data.train_batch_size=2", "actor_rollout_ref.rollout.n=4", "data.max_response_length=32",
+              "actor_rollout_ref.actor.fsdp_config.ulysses_sequence_parallel_size=2", "actor_rollout_ref.rollout.multi_turn.synthetic_turns=1",
+              "actor_rollout_ref.rollout.multi_turn.synthetic_reward=hash", "actor_rollout_ref.rollout.max_model_len=2048",
+              "actor_rollout_ref.rollout.max_num_seqs=8", "actor_rollout_ref.actor.ppo_max_token_len_per_gpu=8192", "trainer.logger=[file]"]
+    env = dict(os.environ, PYTHONPATH=root, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="2")
+    node1 = subprocess.Popen(common + ["--node-rank", "1"], cwd=root, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, start_new_session=True)
+    try:
+        node0 = subprocess.run(common + ["--node-rank", "0"], cwd=root, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=400,
+                               start_new_session=True)
+        assert node0.returncode == 0, node0.stdout[-4000:]
+        out1, _ = node1.communicate(timeout=90)  # ends by itself: its replicas saw the trainer's world go away
+    finally:
+        if node1.poll() is None:
+            import signal
+
+            os.killpg(node1.pid, signal.SIGTERM)
+            node1.communicate(timeout=30)
+    with open(os.path.join(run, "metrics.jsonl")) as f:
+        rows = [json.loads(line) for line in f]
+    assert len(rows) == 1 and rows[0]["weight_sync/bytes"] > 0 and rows[0]["actor/grad_norm"] > 0
+    assert "replica-0 rank 0:" in out1 and "replica-0 rank 1:" in out1 and "policy_version=1" in out1, out1[-3000:]

@@ -56,6 +56,8 @@ def test_recipe_overrides_compose_against_the_shipped_configs(script, tmp_path):
     if '"$N" = 1' in text:
         variants.append({"N": "1"})
     seen = 0
+    if "NODE_RANK" in text:
+        variants = [{"NODES": "10.0.0.1,10.0.0.2", "NODE_RANK": "0"}]
     for env in variants:
         for args in _record(script, tmp_path, {"RUN": str(tmp_path / "run"), **env}):
             assert args[-1] == "extra.key=1", "a recipe passes the caller's extra overrides on"
@@ -70,6 +72,16 @@ def test_recipe_overrides_compose_against_the_shipped_configs(script, tmp_path):
                 rest = args[args.index("pear_b200.launch.launch") + 1:]
                 assert launch_main([a for a in rest if a != "extra.key=1"] + ["--dry-run"]) == 0
                 flags = {rest[i]: rest[i + 1] for i in range(len(rest) - 1) if rest[i].startswith("--")}
+                if "--node-addrs" in flags:
+                    from pear_b200.launch.roles import plan_cluster
+
+                    plans = {p.role: p for p in plan_cluster(flags["--node-addrs"].split(","), int(flags["--node-rank"]), int(flags.get("--gpus", 8)),
+                                                             int(flags.get("--trainer-nodes", 1)), int(flags["--rollout-tp"]), rest[0],
+                                                             [a for a in rest[1:] if "=" in a and a != "extra.key=1"])}
+                    cfg = _compose_trainer(plans["trainer"].args)
+                    assert len(cfg.actor_rollout_ref.rollout.checkpoint_engine.replica_urls) == 2  # one rollout node of 8 GPUs in replicas of 4
+                    seen += 1
+                    continue
                 plans = {p.role: p for p in plan_node(int(flags.get("--gpus", 8)), int(flags["--trainer-gpus"]), int(flags["--rollout-tp"]), rest[0],
                                                       [a for a in rest[1:] if "=" in a and a != "extra.key=1"])}
                 cfg = _compose_trainer(plans["trainer"].args)
