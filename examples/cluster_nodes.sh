@@ -6,7 +6,7 @@
 #   NODES=10.0.0.1,10.0.0.2,10.0.0.3 NODE_RANK=0 TRAIN_NODES=1 TP=4 ./examples/cluster_nodes.sh     (add --dry-run to print this node's plan)
 set -e
 RUN=${RUN:-runs/cluster}
-python -m pear_b200.launch.launch training --node-addrs ${NODES:?comma-separated addresses of all nodes} --node-rank ${NODE_RANK:?this node's position} \
+python -m pear_b200.launch.launch training --node-addrs ${NODES:?comma-separated addresses of all nodes} --node-rank ${NODE_RANK:?position of this node in NODES} \
   --trainer-nodes ${TRAIN_NODES:-1} --gpus ${GPUS:-8} --rollout-tp ${TP:-4} \
   run_dir=$RUN actor_rollout_ref.model.path=${MODEL:-preset:qwen3_8_27b} trainer.v1.trainer_mode=separate_async \
   data.train_batch_size=64 actor_rollout_ref.rollout.n=8 data.max_response_length=3072 \
