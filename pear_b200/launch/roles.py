@@ -54,13 +54,15 @@ def plan_node(n_gpus: int, trainer_gpus: int, rollout_tp: int, recipe: str, over
     force_gloo = trainer_gpus == 0 or "actor_rollout_ref.rollout.checkpoint_engine.backend=gloo" in overrides
     if force_gloo and replicas:
         remote.append("actor_rollout_ref.rollout.checkpoint_engine.backend=gloo")
+    if env_hosts:  # the agent loop borrows environment processes from the env role's hosts
+        remote.append("actor_rollout_ref.rollout.agent.env_hosts=[" + ",".join(f"http://127.0.0.1:{env_port + i}" for i in range(env_hosts)) + "]")
     return [
         # trainer_gpus = 0: one trainer process without a GPU (plumbing runs: a CPU trainer beside GPU replicas)
         RolePlan("trainer", max(1, trainer_gpus), 1 if trainer_gpus else 0, 0, "pear_b200.train.main", [recipe] + overrides + remote),
         RolePlan("rollout", replicas, rollout_tp, trainer_gpus, "pear_b200.rollout.server",
                  overrides + ["--sync-world", str(replicas * max(1, rollout_tp) + 1), "--sync-master", f"127.0.0.1:{sync_port}"]
                  + (["--sync-backend", "gloo"] if force_gloo else []), rollout_port),
-        RolePlan("env", env_hosts, 0, 0, "pear_b200.sim.server", [], env_port),
+        RolePlan("env", env_hosts, 0, 0, "pear_b200.sim.server", overrides, env_port),
         RolePlan("monitor", 1, 0, 0, "pear_b200.monitor.progress_panel",
                  overrides + [a for i in range(replicas) for a in ("--replica", f"replica-{i}=http://127.0.0.1:{rollout_port + i}/metrics")]),
     ]
@@ -91,7 +93,8 @@ def plan_cluster(node_addrs: list[str], node_rank: int, gpus_per_node: int, trai
         plans.append(RolePlan("trainer", gpus_per_node, 1, 0, "pear_b200.train.main", [recipe] + overrides + remote, nnodes=trainer_nodes,
                               node_rank=node_rank, master_addr=node_addrs[0]))
         if node_rank == 0:
-            plans.append(RolePlan("env", 1, 0, 0, "pear_b200.sim.server", [], env_port, host=node_addrs[0]))
+            plans[0].args.append(f"actor_rollout_ref.rollout.agent.env_hosts=[http://{node_addrs[0]}:{env_port}]")
+            plans.append(RolePlan("env", 1, 0, 0, "pear_b200.sim.server", overrides, env_port, host=node_addrs[0]))
             plans.append(RolePlan("monitor", 1, 0, 0, "pear_b200.monitor.progress_panel",
                                   overrides + [a for i, u in enumerate(urls) for a in ("--replica", f"replica-{i}={u}/metrics")]))
     else:

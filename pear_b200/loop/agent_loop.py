@@ -217,8 +217,9 @@ class AgentLoop:
                 "tokens": np.asarray(ep.tokens, dtype=np.int64),
                 "response_mask": np.asarray(ep.response_mask, dtype=np.int8),
                 "rollout_logprobs": np.asarray(ep.logprobs, dtype=np.float32),
-                "topk_ids": np.asarray(ep.topk_ids, dtype=np.int64).reshape(len(ep.tokens), -1),
-                "topk_logprobs": np.asarray(ep.topk_logprobs, dtype=np.float32).reshape(len(ep.tokens), -1),
+                # (explicit width: an episode lost before its first turn has no tokens, and -1 cannot be inferred from nothing)
+                "topk_ids": np.asarray(ep.topk_ids, dtype=np.int64).reshape(len(ep.tokens), self.cfg.topk_heads),
+                "topk_logprobs": np.asarray(ep.topk_logprobs, dtype=np.float32).reshape(len(ep.tokens), self.cfg.topk_heads),
                 "embeds": [(p, b.astype(np.float16)) for p, b in ep.embeds],
                 "images": list(ep.images),
                 "policy_versions": np.asarray(ep.policy_versions, dtype=np.int32),

@@ -51,14 +51,20 @@ class Router:
 class AgentLoopManager:
     def __init__(self, servers: list, hidden_size: int, env_families: dict[str, dict], cfg: AgentLoopConfig, queue_=None,
                  tracker=None, num_workers: int = 4, tokenizer: Optional[ByteTokenizer] = None, vision=None):
-        """``env_families``: family -> {"env_path": dotted class path, "mode": "stateless"|"stateful", ...Server kwargs}."""
+        """``env_families``: family -> {"env_path": dotted class path, "mode": "stateless"|"stateful", ...Server kwargs}; with
+        ``"urls": [...]`` the family is served by environment hosts in other processes (``sim/server.py: main``) and only its
+        action schema is taken from the class here."""
         self.pool = ServerPool()
         schemas = {}
         for family, spec in env_families.items():
             spec = dict(spec)
             env_path = spec.pop("env_path")
             mode = spec.pop("mode", "stateless")
-            self.pool.start(family, env_path, mode, **spec)
+            urls = spec.pop("urls", None)
+            if urls:
+                self.pool.connect(family, list(urls))
+            else:
+                self.pool.start(family, env_path, mode, **spec)
             module, _, name = env_path.rpartition(".")
             schemas[family] = getattr(__import__(module, fromlist=[name]), name).action_schema()
         self.router = Router(servers, hidden_size)

@@ -13,6 +13,7 @@ All failure paths are host-side: nothing here touches a GPU.
 from __future__ import annotations
 
 import importlib
+import json
 import multiprocessing as mp
 import threading
 import time
@@ -204,16 +205,117 @@ class ServerPool:
             self.servers[family] = Server(env_path, mode, name=family, **kwargs)
         return self.servers[family]
 
+    def connect(self, family: str, urls: list[str], **kwargs) -> "RemoteServer":
+        """The family is served by environment hosts in other processes (``python -m pear_b200.sim.server``)."""
+        if family not in self.servers:
+            self.servers[family] = RemoteServer(family, urls, **kwargs)
+        return self.servers[family]
+
     def get(self, family: str) -> Server:
         return self.servers[family]
 
     def capacity(self, family: str) -> int:
-        return len(self.servers[family].slots)
+        srv = self.servers[family]
+        return srv.capacity() if isinstance(srv, RemoteServer) else len(srv.slots)
 
     def close(self) -> None:
         for s in self.servers.values():
             s.close()
         self.servers.clear()
+
+
+def encode_arrays(obj):
+    """JSON form of a rollout result: numpy arrays (camera frames, embedding blocks) become base64 with dtype and shape."""
+    import base64
+
+    import numpy as np
+
+    if isinstance(obj, np.ndarray):
+        return {"__ndarray__": base64.b64encode(np.ascontiguousarray(obj).tobytes()).decode(), "dtype": str(obj.dtype), "shape": list(obj.shape)}
+    if isinstance(obj, dict):
+        return {k: encode_arrays(v) for k, v in obj.items()}
+    if isinstance(obj, (list, tuple)):
+        return [encode_arrays(v) for v in obj]
+    if isinstance(obj, np.generic):
+        return obj.item()
+    return obj
+
+
+def decode_arrays(obj):
+    import base64
+
+    import numpy as np
+
+    if isinstance(obj, dict):
+        if "__ndarray__" in obj:
+            return np.frombuffer(base64.b64decode(obj["__ndarray__"]), dtype=np.dtype(obj["dtype"])).reshape(obj["shape"]).copy()
+        return {k: decode_arrays(v) for k, v in obj.items()}
+    if isinstance(obj, list):
+        return [decode_arrays(v) for v in obj]
+    return obj
+
+
+class RemoteServer:
+    """A family's environment hosts behind the interface episodes use on a local :class:`Server` (stateless families: every call
+    replays the action history, so any host can answer any call). A host that does not answer is skipped for a while and the
+    call goes to the next one; when none answers the episode is lost (the agent loop restarts it). Upstream's clients route
+    around dead server actors the same way (pear/sim/client.py:76-86)."""
+
+    mode = "stateless"
+
+    def __init__(self, family: str, urls: list[str], call_timeout_s: float = 60.0, retry_after_s: float = 10.0):
+        import itertools
+        import threading
+
+        import requests
+
+        self.name, self.urls, self.timeout, self.retry_after = family, [u.rstrip("/") for u in urls], call_timeout_s, retry_after_s
+        self._requests, self._local = requests, threading.local()
+        self._next = itertools.count()
+        self.down: dict[str, float] = {}
+        self.slots: list = []
+        self.failovers = 0
+
+    def _session(self):
+        s = getattr(self._local, "s", None)
+        if s is None:
+            s = self._local.s = self._requests.Session()
+        return s
+
+    def capacity(self) -> int:
+        total = 0
+        for u in self.urls:
+            try:
+                total += int(self._session().get(u + "/capacity", timeout=5).json().get(self.name, 0))
+            except Exception:  # noqa: BLE001 - a host that is down lends nothing
+                pass
+        return total
+
+    def rollout(self, args: dict, actions: list[dict]) -> dict:
+        import time
+
+        start = next(self._next)
+        order = [self.urls[(start + i) % len(self.urls)] for i in range(len(self.urls))]
+        now = time.time()
+        live = [u for u in order if self.down.get(u, 0.0) <= now] or order  # all marked down: try them anyway
+        last = None
+        for i, u in enumerate(live):
+            try:
+                r = self._session().post(u + "/rollout", json={"family": self.name, "args": args, "actions": actions}, timeout=self.timeout)
+                body = r.json()
+                if r.status_code == 200 and "lost" not in body:
+                    self.down.pop(u, None)
+                    return decode_arrays(body)
+                last = body.get("lost") or f"HTTP {r.status_code}"
+            except Exception as e:  # noqa: BLE001 - connection refused / reset / timed out: the host is gone or stuck
+                last = repr(e)
+                self.down[u] = time.time() + self.retry_after
+            if i + 1 < len(live):
+                self.failovers += 1
+        raise EpisodeLost(f"{self.name}: no environment host answered ({last})")
+
+    def close(self) -> None:
+        pass
 
 
 def http_app(pool: ServerPool):
@@ -233,7 +335,10 @@ def http_app(pool: ServerPool):
 
     @app.post("/rollout")
     def rollout(body: dict) -> dict:
-        return pool.get(body["family"]).rollout(body.get("args", {}), body.get("actions", []))
+        try:
+            return encode_arrays(pool.get(body["family"]).rollout(body.get("args", {}), body.get("actions", [])))
+        except EpisodeLost as e:  # the host's own processes were lost twice: the client tries another host
+            return {"lost": str(e)}
 
     return app
 
@@ -247,15 +352,27 @@ def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--family", action="append", default=[], help="name=import.path.EnvClass (repeatable)")
     ap.add_argument("--processes", type=int, default=2)
+    ap.add_argument("--env-kwargs", default="{}", help="JSON of the environment class's constructor arguments")
     ap.add_argument("--host", default="127.0.0.1")
     ap.add_argument("--port", type=int, default=8200)
     ap.add_argument("--check", action="store_true")
-    args, _ = ap.parse_known_args(argv)
+    args, rest = ap.parse_known_args(argv)
     families = dict(f.split("=", 1) for f in args.family) or {"synthetic": "pear_b200.envs.synthetic.SyntheticEnv"}
+    if args.env_kwargs == "{}" and not args.family:
+        # the launcher passes the recipe's overrides to every role: the default synthetic family draws its placeholder rows at the
+        # policy model's width, as the training entry's own environment processes do
+        kv = dict(o.split("=", 1) for o in rest if "=" in o and not o.startswith("-"))
+        path = kv.get("actor_rollout_ref.model.path")
+        if path:
+            from ..models import io as model_io
+            from ..models.config import HybridConfig
+
+            mcfg = getattr(HybridConfig, path.split(":", 1)[1])() if path.startswith("preset:") else model_io.load_config(path)
+            args.env_kwargs = json.dumps({"hidden": mcfg.hidden_size, "tokens_per_image": 4})
     pool = ServerPool()
     try:
         for name, path in families.items():
-            pool.start(name, path, "stateless", num_processes=args.processes)
+            pool.start(name, path, "stateless", num_processes=args.processes, env_kwargs=json.loads(args.env_kwargs))
         if args.check:
             for name in families:
                 out = pool.get(name).rollout({}, [])

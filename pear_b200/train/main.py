@@ -223,6 +223,10 @@ def build_stack(cfg, replicas: int = 1, device: str = "cpu", env_families: Optio
             servers.append(build_server(rm, rc, device, name=f"replica-{i}", fp32_modules=tuple(ro.fp32_modules)))
         families = env_families or {"synthetic": {"env_path": "pear_b200.envs.synthetic.SyntheticEnv", "num_processes": 2,
                                                   "env_kwargs": {"hidden": mcfg.hidden_size, "tokens_per_image": 4}}}
+        env_hosts = [str(u) for u in (ro.agent.get("env_hosts", None) or [])]
+        if env_hosts and env_families is None:  # environment hosts are processes of their own (the launcher's env role)
+            for spec in families.values():
+                spec["urls"] = env_hosts
         acfg = AgentLoopConfig(token_budget=int(cfg.data.max_response_length), temperature=float(ro.temperature), top_p=float(ro.top_p),
                                topk_heads=tcfg.topk_heads, max_model_len=int(ro.max_model_len), max_prompt_length=int(cfg.data.get("max_prompt_length", 0) or 0), log_dir=os.environ.get("PEAR_LOG_DIR"),
                                synthetic_turns=int(ro.multi_turn.synthetic_turns), turn_max_tokens=int(ro.multi_turn.turn_max_tokens),

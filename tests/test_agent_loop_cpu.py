@@ -222,3 +222,64 @@ def test_prompt_longer_than_the_limit_ends_the_episode_before_any_request(pool):
     assert ep.end_reason == EndReason.BUDGET and ep.response_tokens == 0 and not router.calls
     loop2, router2 = _loop(pool, ['```json\n{"submit": true}\n```'], token_budget=4000, max_prompt_length=100000)
     assert loop2.run("gm", "0", "synthetic", {"seed": 1}).response_tokens > 0 and router2.calls
+
+
+def test_episodes_on_remote_environment_hosts_with_failover(tmp_path):
+    """The environment role as processes: two hosts serve the synthetic family over HTTP; an episode runs through them (camera
+    blocks travel as encoded arrays), a host that dies is skipped, and when no host answers the episode is lost."""
+    import os
+    import subprocess
+    import sys
+    import time
+
+    import requests
+
+    from pear_b200.sim.server import RemoteServer, decode_arrays, encode_arrays
+    from pear_b200.utils.process import free_ports
+
+    x = {"a": np.arange(6, dtype=np.float32).reshape(2, 3), "b": [np.uint8(3), {"c": np.zeros((1, 2), dtype=np.uint8)}], "d": "s"}
+    y = decode_arrays(encode_arrays(x))
+    assert np.array_equal(y["a"], x["a"]) and y["a"].dtype == np.float32 and y["b"][0] == 3 and y["b"][1]["c"].dtype == np.uint8 and y["d"] == "s"
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    ports = free_ports(2)
+    hosts = [subprocess.Popen([sys.executable, "-m", "pear_b200.sim.server", "--port", str(p), "--processes", "1", "--env-kwargs", '{"hidden": 8, "tokens_per_image": 4}'],
+                              env=dict(os.environ, PYTHONPATH=root), stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL) for p in ports]
+    urls = [f"http://127.0.0.1:{p}" for p in ports]
+    try:
+        for u in urls:
+            t0 = time.time()
+            while True:
+                try:
+                    if requests.get(u + "/health", timeout=2).json()["ok"]:
+                        break
+                except Exception:  # noqa: BLE001
+                    assert time.time() - t0 < 60, "environment host did not start"
+                    time.sleep(0.2)
+        local = ServerPool()
+        try:
+            remote = local.connect("synthetic", urls, retry_after_s=60.0)
+            assert isinstance(remote, RemoteServer) and local.capacity("synthetic") == 2
+            env = SyntheticEnv(hidden=8, tokens_per_image=4)
+            d = env.reset({"seed": 0})["state"]["distance"]
+            moves = ['```json\n{"move": %d}\n```' % (1 if d > 0 else -1)] * abs(d) + ['```json\n{"submit": true}\n```']
+            q = TransferQueue(4)
+            loop, _ = _loop(local, moves, q, token_budget=4000)
+            ep = loop.run("gr", "0", "synthetic", {"seed": 0})
+            assert ep.end_reason == EndReason.ENV and ep.success and all(b.shape == (4, 8) for _, b in q.get("gr/0")["embeds"])
+            hosts[0].kill()
+            hosts[0].wait(30)
+            loop2, _ = _loop(local, moves, q, token_budget=4000)
+            ep2 = loop2.run("gs", "0", "synthetic", {"seed": 0})
+            assert ep2.success and remote.failovers >= 1 and urls[0] in remote.down  # the dead host is skipped from now on
+            hosts[1].kill()
+            hosts[1].wait(30)
+            loop3, _ = _loop(local, moves, q, token_budget=4000, max_restarts=1)
+            ep3 = loop3.run("gt", "0", "synthetic", {"seed": 0})
+            assert ep3.end_reason == EndReason.LOST and not ep3.success
+        finally:
+            local.close()
+    finally:
+        for h in hosts:
+            if h.poll() is None:
+                h.kill()
+            h.wait(30)
