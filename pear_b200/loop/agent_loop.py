@@ -28,6 +28,7 @@ from ..rollout.engine import FinishReason, SamplingParams
 from ..sim.env import EpisodeLost
 from ..sim.server import ServerPool
 from ..utils.files import append_jsonl
+from ..utils.logging_utils import event, get_logger
 from ..utils.tokenizer import ByteTokenizer
 from .episode import EndReason, Episode, LoopState
 from .protocol import ParseError, parse_answer, validate_action
@@ -41,6 +42,7 @@ class AgentLoopConfig:
     max_restarts: int = 2
     temperature: float = 1.0
     top_p: float = 1.0
+    top_k: int = -1
     topk_heads: int = 0              # rollout top-k head ids / log-probs kept for score centering
     max_model_len: int = 4096
     max_prompt_length: int = 0       # an episode whose first-turn prompt is longer ends at once (budget end, no sampled token); 0: no limit
@@ -52,6 +54,9 @@ class AgentLoopConfig:
     synthetic_turns: int = 0
     turn_max_tokens: int = 0
     synthetic_reward: Optional[str] = None
+
+
+_log = get_logger("pear_b200.agent_loop")
 
 
 class AgentLoop:
@@ -124,9 +129,12 @@ class AgentLoop:
                 break
             except EpisodeLost as e:
                 self._log_turn(ep, LoopState.TERMINATED, lost=str(e), attempt=attempt)
+                event(_log, "TRAJECTORY_RESTART", uid=ep.uid, session=ep.session, family=ep.family, attempt=attempt, reason=str(e)[:200])
                 if attempt == self.cfg.max_restarts:
                     ep.end_reason, ep.success = EndReason.LOST, False
         self._publish(ep)
+        event(_log, "EPISODE_END", uid=ep.uid, session=ep.session, family=ep.family, reason=ep.end_reason.value if ep.end_reason else None,
+              success=bool(ep.success), turns=ep.turns, tokens=len(ep.tokens), response_tokens=ep.response_tokens, restarts=ep.restarts)
         return ep
 
     def _run_once(self, ep: Episode) -> None:
@@ -154,7 +162,7 @@ class AgentLoop:
                         ep.end_reason, state = EndReason.BUDGET, LoopState.TERMINATED
                         continue
                     embeds, mask = self._embeds(ep, hidden)
-                    params = SamplingParams(max_tokens=left, temperature=cfg.temperature, top_p=cfg.top_p,
+                    params = SamplingParams(max_tokens=left, temperature=cfg.temperature, top_p=cfg.top_p, top_k=cfg.top_k,
                                             topk_logprobs=cfg.topk_heads, stop_token_ids=(self.tok.eos_id,) + tuple(getattr(self.tok, "extra_stop_ids", ())))
                     t0 = time.time()
                     req = self.router.generate(list(ep.tokens), params, session=f"{ep.uid}/{ep.session}", embeds=embeds, embeds_mask=mask)
@@ -180,6 +188,7 @@ class AgentLoop:
                         validate_action(action, schema)
                     except ParseError as e:
                         self._log_turn(ep, state, parse_error=str(e))
+                        event(_log, "PARSE_FAILURE", uid=ep.uid, session=ep.session, turn=ep.turns, error=str(e)[:200])
                         ep.end_reason, state = EndReason.PARSE, LoopState.TERMINATED
                         continue
                     state = LoopState.PROCESSING_TOOLS

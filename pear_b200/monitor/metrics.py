@@ -11,7 +11,9 @@ from dataclasses import dataclass, field
 from typing import Callable, Optional, Union
 
 COUNTERS = ("pear_prompt_tokens_total", "pear_generation_tokens_total", "pear_preemptions_total", "pear_aborted_total",
-            "pear_spec_drafted_total", "pear_spec_accepted_total")
+            "pear_spec_drafted_total", "pear_spec_accepted_total", "pear_prefix_cache_queries_total", "pear_prefix_cache_hits_total",
+            "pear_external_prefix_cache_hits_total", "pear_requests_finished_total", "pear_request_seconds_total", "pear_first_tokens_total",
+            "pear_first_token_seconds_total")
 GAUGES = ("pear_num_running", "pear_num_waiting", "pear_policy_version", "pear_free_blocks", "pear_cached_blocks")
 _LINE = re.compile(r"^([a-zA-Z_:][a-zA-Z0-9_:]*)(\{[^}]*\})?\s+([-+0-9.eE]+|NaN|[+-]?Inf)$")
 
@@ -82,5 +84,15 @@ class MetricsScraper:
         d, a = (sum(v.values.get(f"pear_spec_{x}_total", 0.0) for v in self.last.values()) for x in ("drafted", "accepted"))
         if d > 0:
             s["spec_accept_rate"] = a / d
+        # share of looked-up prompt tokens found in a cache over the last interval (device tier + host tier), as upstream's panel
+        # shows it (monitor/metrics.py:36-42), and the mean request latency / time to first token of that interval
+        q = s.get("pear_prefix_cache_queries_per_s", 0.0)
+        if q > 0:
+            s["cache_hit_rate"] = (s.get("pear_prefix_cache_hits_per_s", 0.0)) / q
+            s["external_cache_hit_rate"] = s.get("pear_external_prefix_cache_hits_per_s", 0.0) / q
+        for what, count in (("request_seconds", "requests_finished"), ("first_token_seconds", "first_tokens")):
+            n = s.get(f"pear_{count}_per_s", 0.0)
+            if n > 0:
+                s[f"mean_{what}"] = s.get(f"pear_{what}_per_s", 0.0) / n
         s["replicas_up"] = float(len(self.last) - len(self.errors))
         return s

@@ -21,7 +21,8 @@ import torch
 from .engine import EngineConfig, FinishReason, Request, RolloutEngine, SamplingParams
 
 PROM_COUNTERS = ("prompt_tokens", "generation_tokens", "preemptions", "aborted", "spec_drafted", "spec_accepted", "requests_finished",
-                 "request_seconds", "first_tokens", "first_token_seconds")  # (the *_seconds sums over their counts give mean latencies)
+                 "request_seconds", "first_tokens", "first_token_seconds",  # (the *_seconds sums over their counts give mean latencies)
+                 "prefix_cache_queries", "prefix_cache_hits", "external_prefix_cache_hits")  # tokens looked up / found on the device / found in the host tier
 PROM_GAUGES = ("num_running", "num_waiting", "policy_version", "free_blocks", "cached_blocks")
 
 

@@ -144,7 +144,7 @@ class EngineConfig:
             enable_gradient_checkpointing=bool(model.enable_gradient_checkpointing),
             enable_activation_offload=bool(model.get("enable_activation_offload", False)),
             gradient_checkpointing_retain_attention=bool(model.get("gradient_checkpointing_retain_attention", False)),
-            streamed_adamw=bool(fs.get("streamed_adamw", False) or fs.get("optimizer_offload", False)),
+            streamed_adamw=bool(fs.get("streamed_adamw", False) or fs.get("optimizer_offload", False) or fs.get("optimizer_offload_step", False)),
             temperature=float(rollout.temperature), topk_log_probs=int(rollout.get("topk_log_probs", 0)),
             loss=grpo.LossConfig(loss_agg_mode=actor.loss_agg_mode, score_centering=bool(rc.score_centering),
                                  rollout_is=rc.get("rollout_is"), rollout_is_threshold=rc.get("rollout_is_threshold", 2.0),

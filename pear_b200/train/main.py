@@ -119,6 +119,11 @@ class MetricsLog:
         self.path = os.path.join(run_dir, "metrics.jsonl")
         self.train_log = os.path.join(run_dir, "train.log")
         self.backends = backends
+        self.tensorboard = None
+        if "tensorboard" in backends:
+            from torch.utils.tensorboard import SummaryWriter  # fails loudly when the backend is asked for and the package is absent
+
+            self.tensorboard = SummaryWriter(log_dir=os.environ.get("TENSORBOARD_DIR") or os.path.join(run_dir, "tensorboard"))
         self.wandb = None
         if "wandb" in backends:
             import wandb  # fails loudly when the backend is asked for and the package is absent
@@ -133,6 +138,11 @@ class MetricsLog:
                 f.write(json.dumps(rec) + "\n")
             with open(self.train_log, "a") as f:
                 f.write(f"step:{step} - " + " - ".join(f"{k}:{v:.6g}" for k, v in sorted(m.items()) if isinstance(v, (int, float))) + "\n")
+        if self.tensorboard is not None:
+            for k, v in rec.items():
+                if isinstance(v, (int, float)) and k not in ("step", "time"):
+                    self.tensorboard.add_scalar(k, v, step)
+            self.tensorboard.flush()
         if self.wandb is not None:
             self.wandb.log({k: v for k, v in rec.items() if isinstance(v, (int, float)) and k != "step"}, step=step, commit=True)
         if "console" in self.backends:
@@ -227,7 +237,7 @@ def build_stack(cfg, replicas: int = 1, device: str = "cpu", env_families: Optio
         if env_hosts and env_families is None:  # environment hosts are processes of their own (the launcher's env role)
             for spec in families.values():
                 spec["urls"] = env_hosts
-        acfg = AgentLoopConfig(token_budget=int(cfg.data.max_response_length), temperature=float(ro.temperature), top_p=float(ro.top_p),
+        acfg = AgentLoopConfig(token_budget=int(cfg.data.max_response_length), temperature=float(ro.temperature), top_p=float(ro.top_p), top_k=int(ro.get("top_k", -1)),
                                topk_heads=tcfg.topk_heads, max_model_len=int(ro.max_model_len), max_prompt_length=int(cfg.data.get("max_prompt_length", 0) or 0), log_dir=os.environ.get("PEAR_LOG_DIR"),
                                synthetic_turns=int(ro.multi_turn.synthetic_turns), turn_max_tokens=int(ro.multi_turn.turn_max_tokens),
                                synthetic_reward=ro.multi_turn.synthetic_reward, tool_parser=str(ro.multi_turn.get("format", "fenced_json")))

@@ -283,3 +283,25 @@ def test_episodes_on_remote_environment_hosts_with_failover(tmp_path):
             if h.poll() is None:
                 h.kill()
             h.wait(30)
+
+
+def test_agent_loop_emits_the_structured_events(pool, caplog):
+    """One line per event, a name and a JSON object: what the monitor and operators grep for."""
+    import json
+    import logging
+
+    pool.start("synthetic", ENV, "stateless", num_processes=1, env_kwargs={"hidden": 8, "tokens_per_image": 2})
+    log = logging.getLogger("pear_b200.agent_loop")
+    log.propagate = True  # (the logger has a handler of its own; the test listens through the root)
+    try:
+        with caplog.at_level(logging.INFO, logger="pear_b200.agent_loop"):
+            loop, _ = _loop(pool, ["no json here"], token_budget=4000)
+            loop.run("ge", "0", "synthetic", {"seed": 1})
+    finally:
+        log.propagate = False
+    lines = [r.getMessage() for r in caplog.records]
+    fail = next(l for l in lines if l.startswith("PARSE_FAILURE "))
+    end = next(l for l in lines if l.startswith("EPISODE_END "))
+    assert json.loads(fail.split(" ", 1)[1])["uid"] == "ge"
+    e = json.loads(end.split(" ", 1)[1])
+    assert e["reason"] == "parse" and e["success"] is False and e["turns"] == 1 and e["tokens"] > 0

@@ -144,3 +144,17 @@ def test_unimplemented_settings_are_refused_at_start(tmp_path):
     RunConfig(compose("training", base)).prepare()  # the shipped recipe is all implemented values
     with pytest.raises(ConfigError, match=r"adv_estimator='gae'.*\n.*use_kl_loss=True|use_kl_loss=True"):
         RunConfig(compose("training", base + ["algorithm.adv_estimator=gae", "actor_rollout_ref.actor.use_kl_loss=true"])).prepare()
+
+
+def test_metrics_log_writes_tensorboard_events(tmp_path, monkeypatch):
+    import glob
+
+    monkeypatch.delenv("TENSORBOARD_DIR", raising=False)  # (a recipe's env_vars may have set it in this process: it would win)
+
+    from pear_b200.train.main import MetricsLog
+
+    log = MetricsLog(str(tmp_path), ("tensorboard",))
+    log(1, {"actor/pg_loss": 0.5})
+    log(2, {"actor/pg_loss": 0.25, "note": "text"})
+    files = glob.glob(str(tmp_path / "tensorboard" / "events.out.tfevents.*"))
+    assert files and sum(os.path.getsize(f) for f in files) > 0

@@ -109,3 +109,21 @@ def test_chat_completions_endpoint_renders_the_template():
         assert "error" in TestClient(srv.http_app()).post("/v1/chat/completions", json=body).json()
     finally:
         srv.close()
+
+
+def test_monitor_derives_cache_hit_rate_and_latencies_from_replica_counters():
+    def text(q, h, x, n, secs, gen):
+        vals = {"pear_prefix_cache_queries_total": q, "pear_prefix_cache_hits_total": h, "pear_external_prefix_cache_hits_total": x,
+                "pear_requests_finished_total": n, "pear_request_seconds_total": secs, "pear_generation_tokens_total": gen}
+        return "\n".join(f'{k}{{replica="r"}} {float(v)}' for k, v in vals.items()) + "\n"
+
+    feeds = iter([text(0, 0, 0, 0, 0.0, 0), text(1000, 600, 100, 10, 25.0, 500)])
+    sc = MetricsScraper({"r": "http://unused"})
+    sc._fetch = lambda src: next(feeds)
+    sc.scrape()
+    import time
+    time.sleep(0.05)
+    sc.scrape()
+    s = sc.summary()
+    assert abs(s["cache_hit_rate"] - 0.6) < 1e-9 and abs(s["external_cache_hit_rate"] - 0.1) < 1e-9 and abs(s["mean_request_seconds"] - 2.5) < 1e-9
+    assert s["pear_generation_tokens_per_s"] > 0
