@@ -410,8 +410,13 @@ def main(argv=None) -> int:
     kv = dict(o.split("=", 1) for o in overrides if "=" in o and not o.startswith("-"))
     path = args.model or kv.get("actor_rollout_ref.model.path", "preset:tiny")
     max_seqs = int(kv.get("actor_rollout_ref.rollout.max_num_seqs", args.max_num_seqs))
+    # modules that stay fp32 in the replica (checked before every sync): the recipe's list, or the exported variable
     import os
 
+    import yaml
+
+    fp32_modules = tuple(yaml.safe_load(kv.get("actor_rollout_ref.rollout.fp32_modules", "null")) or
+                         [m for m in os.environ.get("PEAR_ROLLOUT_FP32_MODULES", "").split(",") if m])
     device = "cuda" if torch.cuda.is_available() else "cpu"
     host_gb = args.host_gb
     if not host_gb and str(kv.get("actor_rollout_ref.rollout.custom.lmcache.enable", "false")).lower() == "true":
@@ -441,13 +446,13 @@ def main(argv=None) -> int:
             dist.init_process_group("nccl", device_id=torch.device("cuda", local))
         else:
             dist.init_process_group("gloo")
-        server = build_tp_replica(path, ecfg, name=args.name)
+        server = build_tp_replica(path, ecfg, name=args.name, fp32_modules=fp32_modules)
         device = str(server.engine.device)
         if args.sync_backend == "nvswitch":
             raise SystemExit("--sync-backend nvswitch needs the default process group, which a tensor-parallel replica uses for its own ranks: use nccl")
     else:
         model = load_rollout_model(path, device=device, drafter_path=args.drafter)
-        server = build_server(model, ecfg, device=device, name=args.name)
+        server = build_server(model, ecfg, device=device, name=args.name, fp32_modules=fp32_modules)
     if args.sync_rank >= 0:  # a tensor-parallel replica's ranks are consecutive in the weight-sync world
         gone = None
         if args.exit_with_trainer:  # a replica on a node of its own has nobody to stop it: it ends the way a launcher would end it
