@@ -211,12 +211,16 @@ class HybridConfig:
             kw["layer_types"] = list(t["layer_types"])
         return cls(**kw)
 
-    def save(self, path: str, hf: bool = True) -> None:
+    def save(self, path: str, hf: bool = True, dtype: str = "bfloat16") -> None:
         """``hf``: the Hugging Face layout (loadable by transformers-style tools); this framework's own flat field names are
-        added under "pear_b200" so nothing is lost in a round trip."""
+        added under "pear_b200" so nothing is lost in a round trip. ``dtype``: the element type of the tensors saved beside it
+        (transformers loads a checkpoint in the type its config names)."""
         d = self.to_hf_dict() if hf else self.to_dict()
         if hf:
             d["pear_b200"] = self.to_dict()
+            for section in (d, d.get("text_config", {})):
+                if "dtype" in section:
+                    section["dtype"] = dtype
         with open(path, "w") as f:
             json.dump(d, f, indent=1)
 

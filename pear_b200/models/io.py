@@ -178,7 +178,7 @@ def save_model_dir(directory: str, config: HybridConfig, state: dict[str, torch.
             weight_map.update({k: fn for k in sh})
         with open(os.path.join(directory, "model.safetensors.index.json"), "w") as fh:
             json.dump({"metadata": {"total_size": sum(t.numel() * t.element_size() for t in out.values())}, "weight_map": weight_map}, fh)
-    config.save(os.path.join(directory, "config.json"), hf=hf_names)
+    config.save(os.path.join(directory, "config.json"), hf=hf_names, dtype=str(dtype).replace("torch.", ""))
     return files
 
 
