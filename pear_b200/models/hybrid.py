@@ -302,9 +302,10 @@ class HybridForCausalLM(nn.Module):
         self.mtp = MTPHead(cfg) if (with_mtp and cfg.num_mtp_layers > 0) else None
         self.visual = None
         if vision is not None:
-            from .vision import VisionTower
+            from .vision import FamilyVisionConfig, FamilyVisionTower, VisionTower
 
-            self.visual = VisionTower(vision)
+            # the family's own tower (what its checkpoints carry under model.visual.*) or this framework's small ViT
+            self.visual = FamilyVisionTower(vision) if isinstance(vision, FamilyVisionConfig) else VisionTower(vision)
         self.gradient_checkpointing = False
         self.activation_offload = None  # train.offload.CheckpointInputOffload when enabled
 
@@ -403,6 +404,38 @@ class HybridForCausalLM(nn.Module):
         """Hidden states of the MTP layer predicting token t+2 from the backbone state at t and token t+1."""
         meta = self.make_meta(position_ids, cu_seqlens)
         return self.mtp(self.model.embed_tokens(next_ids).float(), prenorm_hidden, meta)
+
+
+def mrope_positions(input_ids: torch.Tensor, image_grids: list[tuple[int, int]], image_pad_id: int, merge: int = 2) -> torch.Tensor:
+    """(temporal, row, column) positions ``[3, T]`` of one sequence with pictures, as the family's checkpoints were trained: text
+    tokens advance all three together; the rows of a picture (a run of ``image_pad_id`` tokens, ``gh / merge x gw / merge`` of them
+    for a patch grid ``gh x gw``) share the temporal position where the picture starts and count rows and columns from it; the
+    text after a picture continues from the largest position the picture used plus one. The rollout and training paths of this
+    framework give pictures sequential positions instead (consistent with each other, not with a pretrained checkpoint's
+    pictures); this function is the checkpoint's rule, checked against ``transformers`` in ``tests/test_hf_parity_cpu.py``."""
+    ids = input_ids.tolist()
+    pos = torch.zeros(3, len(ids), dtype=torch.long)
+    nxt, i, k = 0, 0, 0
+    while i < len(ids):
+        if ids[i] == image_pad_id:
+            gh, gw = image_grids[k]
+            k += 1
+            rows, cols = gh // merge, gw // merge
+            n = rows * cols
+            if ids[i:i + n] != [image_pad_id] * n:
+                raise ValueError(f"picture {k - 1} needs {n} image-pad tokens at position {i}")
+            r = torch.arange(rows).repeat_interleave(cols)
+            c = torch.arange(cols).repeat(rows)
+            pos[0, i:i + n], pos[1, i:i + n], pos[2, i:i + n] = nxt, nxt + r, nxt + c
+            nxt += max(rows, cols)
+            i += n
+        else:
+            pos[:, i] = nxt
+            nxt += 1
+            i += 1
+    if k != len(image_grids):
+        raise ValueError(f"{len(image_grids)} pictures given, {k} found in the tokens")
+    return pos
 
 
 def _positions_from_cu(cu_seqlens, t: int, device) -> torch.Tensor:

@@ -214,5 +214,15 @@ def load_model_dir(directory: str, model: torch.nn.Module, strict: bool = True, 
     return missing, unexpected
 
 
+def load_vision_config(directory: str):
+    """The ``vision_config`` of a model directory's config.json as a ``FamilyVisionConfig`` (None: a text-only checkpoint)."""
+    from .vision import FamilyVisionConfig
+
+    with open(os.path.join(directory, "config.json")) as f:
+        d = json.load(f)
+    v = d.get("vision_config")
+    return FamilyVisionConfig.from_hf_dict(v) if isinstance(v, dict) else None
+
+
 def load_config(directory: str) -> HybridConfig:
     return HybridConfig.load(os.path.join(directory, "config.json"))

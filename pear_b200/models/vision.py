@@ -112,3 +112,198 @@ class VisionTower(nn.Module):
             for j, i in enumerate(idx):
                 out[i] = y[j]
         return out
+
+
+# ---------------------------------------------------------------------------------------------------------------------------
+# The family's own tower (the `model.visual.*` tensors of its checkpoints)
+# ---------------------------------------------------------------------------------------------------------------------------
+@dataclass
+class FamilyVisionConfig:
+    """Sizes of the family's vision tower as its checkpoints' ``vision_config`` names them."""
+
+    depth: int = 27
+    hidden_size: int = 1152
+    intermediate_size: int = 4304
+    num_heads: int = 16
+    in_channels: int = 3
+    patch_size: int = 16
+    temporal_patch_size: int = 2
+    spatial_merge_size: int = 2
+    num_position_embeddings: int = 2304
+    out_hidden_size: int = 3584
+    rope_theta: float = 10000.0
+
+    @classmethod
+    def from_hf_dict(cls, d: dict) -> "FamilyVisionConfig":
+        return cls(**{k: d[k] for k in cls.__dataclass_fields__ if k in d})
+
+    @classmethod
+    def tiny(cls, out_hidden: int = 256) -> "FamilyVisionConfig":
+        return cls(depth=2, hidden_size=64, intermediate_size=128, num_heads=4, patch_size=4, num_position_embeddings=64, out_hidden_size=out_hidden)
+
+    @property
+    def out_hidden(self) -> int:
+        return self.out_hidden_size
+
+
+class _FamilyAttention(nn.Module):
+    def __init__(self, cfg: FamilyVisionConfig):
+        super().__init__()
+        self.heads = cfg.num_heads
+        self.qkv = nn.Linear(cfg.hidden_size, 3 * cfg.hidden_size)
+        self.proj = nn.Linear(cfg.hidden_size, cfg.hidden_size)
+
+    def forward(self, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+        """x [images, tokens, width] of one size; cos / sin [tokens, head_dim]: rotate-half rotary over (row, column)."""
+        b, n, w = x.shape
+        q, k, v = self.qkv(x).view(b, n, 3, self.heads, w // self.heads).permute(2, 0, 3, 1, 4)
+
+        def rot(t):
+            half = t.shape[-1] // 2
+            return t * cos + torch.cat([-t[..., half:], t[..., :half]], dim=-1) * sin
+
+        a = F.scaled_dot_product_attention(rot(q.float()), rot(k.float()), v.float())
+        return self.proj(a.transpose(1, 2).reshape(b, n, w).to(x.dtype))
+
+
+class _FamilyMLP(nn.Module):
+    def __init__(self, cfg: FamilyVisionConfig):
+        super().__init__()
+        self.linear_fc1 = nn.Linear(cfg.hidden_size, cfg.intermediate_size)
+        self.linear_fc2 = nn.Linear(cfg.intermediate_size, cfg.hidden_size)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.linear_fc2(F.gelu(self.linear_fc1(x), approximate="tanh"))
+
+
+class _FamilyBlock(nn.Module):
+    def __init__(self, cfg: FamilyVisionConfig):
+        super().__init__()
+        self.norm1 = nn.LayerNorm(cfg.hidden_size, eps=1e-6)
+        self.norm2 = nn.LayerNorm(cfg.hidden_size, eps=1e-6)
+        self.attn = _FamilyAttention(cfg)
+        self.mlp = _FamilyMLP(cfg)
+
+    def forward(self, x, cos, sin):
+        x = x + self.attn(self.norm1(x), cos, sin)
+        return x + self.mlp(self.norm2(x))
+
+
+class _FamilyPatchEmbed(nn.Module):
+    def __init__(self, cfg: FamilyVisionConfig):
+        super().__init__()
+        k = (cfg.temporal_patch_size, cfg.patch_size, cfg.patch_size)
+        self.proj = nn.Conv3d(cfg.in_channels, cfg.hidden_size, kernel_size=k, stride=k, bias=True)  # (kept as a convolution for its tensor names)
+
+
+class _FamilyMerger(nn.Module):
+    def __init__(self, cfg: FamilyVisionConfig):
+        super().__init__()
+        wide = cfg.hidden_size * cfg.spatial_merge_size ** 2
+        self.norm = nn.LayerNorm(cfg.hidden_size, eps=1e-6)
+        self.linear_fc1 = nn.Linear(wide, wide)
+        self.linear_fc2 = nn.Linear(wide, cfg.out_hidden_size)
+
+
+class FamilyVisionTower(nn.Module):
+    """The vision tower of the model family's checkpoints (parameter names and arithmetic of ``model.visual.*``): a still picture
+    is two identical frames under a temporal patch of two; patches are embedded by the (3-D) patch projection, a learned position
+    table laid out on a square grid is interpolated bilinearly to the picture's patch grid and added; the blocks are pre-norm
+    LayerNorm / full attention inside the picture with a rotate-half rotary embedding over (row, column) / tanh-GELU MLP; the
+    merger normalises, concatenates every ``merge x merge`` window of patches and projects it to the language model's width.
+    Tokens are kept in window-major order (all patches of a window are consecutive), which is the order the merger consumes.
+    Same call interface as :class:`VisionTower`: ``tower(images)`` with ``[C, H, W]`` pictures gives one ``[tokens, out]`` block
+    each. Checked against ``transformers``' implementation in ``tests/test_hf_parity_cpu.py``."""
+
+    def __init__(self, cfg: FamilyVisionConfig):
+        super().__init__()
+        self.cfg = cfg
+        self.patch_embed = _FamilyPatchEmbed(cfg)
+        self.pos_embed = nn.Embedding(cfg.num_position_embeddings, cfg.hidden_size)
+        self.blocks = nn.ModuleList(_FamilyBlock(cfg) for _ in range(cfg.depth))
+        self.merger = _FamilyMerger(cfg)
+        self.side = int(cfg.num_position_embeddings ** 0.5)
+
+    def init_weights(self, seed: int = 0) -> "FamilyVisionTower":
+        g = torch.Generator().manual_seed(seed)
+        with torch.no_grad():
+            for name, p in self.named_parameters():
+                if p.dim() >= 2:
+                    p.copy_(torch.randn(p.shape, generator=g) * 0.02)
+                elif "norm" in name and name.endswith("weight"):
+                    p.fill_(1.0)
+                else:
+                    p.zero_()
+        return self
+
+    def tokens_per_image(self, height: int, width: int) -> int:
+        c = self.cfg
+        return (height // c.patch_size // c.spatial_merge_size) * (width // c.patch_size // c.spatial_merge_size)
+
+    def patches(self, img: torch.Tensor) -> tuple[torch.Tensor, int, int]:
+        """[C, H, W] -> window-major patch vectors [gh * gw, C * Tp * P * P] (the checkpoint processor's ``pixel_values`` rows)."""
+        c = self.cfg
+        ch, h, w = img.shape
+        p, m = c.patch_size, c.spatial_merge_size
+        gh, gw = h // p, w // p
+        if gh % m or gw % m or gh < m or gw < m:
+            raise ValueError(f"picture {h}x{w}: the patch grid {gh}x{gw} must be a multiple of {m}")
+        x = img[:, : gh * p, : gw * p].reshape(ch, gh // m, m, p, gw // m, m, p)
+        x = x.permute(1, 4, 2, 5, 0, 3, 6)  # block row, block column, row in block, column in block, channel, y, x
+        x = x.unsqueeze(5).expand(-1, -1, -1, -1, -1, c.temporal_patch_size, -1, -1)  # the still picture repeated over the temporal patch
+        return x.reshape(gh * gw, ch * c.temporal_patch_size * p * p), gh, gw
+
+    def _window_major(self, grid: torch.Tensor, gh: int, gw: int) -> torch.Tensor:
+        m = self.cfg.spatial_merge_size
+        return grid.reshape(gh // m, m, gw // m, m, -1).permute(0, 2, 1, 3, 4).reshape(gh * gw, -1)
+
+    def _positions(self, gh: int, gw: int, device) -> torch.Tensor:
+        """The position table interpolated bilinearly to a gh x gw grid, window-major: [gh * gw, width]."""
+        s = self.side
+        ys, xs = torch.linspace(0, s - 1, gh, device=device), torch.linspace(0, s - 1, gw, device=device)
+        y0, x0 = ys.long(), xs.long()
+        y1, x1 = (y0 + 1).clamp(max=s - 1), (x0 + 1).clamp(max=s - 1)
+        fy, fx = (ys - y0)[:, None], (xs - x0)[None, :]
+        table = self.pos_embed.weight
+
+        def at(yy, xx):
+            return table[(yy[:, None] * s + xx[None, :]).reshape(-1)].reshape(gh, gw, -1)
+
+        out = (at(y0, x0) * ((1 - fy) * (1 - fx))[..., None] + at(y0, x1) * ((1 - fy) * fx)[..., None]
+               + at(y1, x0) * (fy * (1 - fx))[..., None] + at(y1, x1) * (fy * fx)[..., None])
+        return self._window_major(out, gh, gw)
+
+    def _rotary(self, gh: int, gw: int, device) -> tuple[torch.Tensor, torch.Tensor]:
+        c = self.cfg
+        hd = c.hidden_size // c.num_heads
+        dim = hd // 2  # half of the head for rows, half for columns
+        inv = 1.0 / (c.rope_theta ** (torch.arange(0, dim, 2, dtype=torch.float32, device=device) / dim))
+        rows = torch.arange(gh, device=device, dtype=torch.float32)[:, None].expand(gh, gw)
+        cols = torch.arange(gw, device=device, dtype=torch.float32)[None, :].expand(gh, gw)
+        ang = torch.cat([rows[..., None] * inv, cols[..., None] * inv], dim=-1)  # [gh, gw, hd / 2]
+        ang = self._window_major(ang, gh, gw)
+        ang = torch.cat([ang, ang], dim=-1)  # [tokens, hd]
+        return ang.cos(), ang.sin()
+
+    def forward(self, images: list[torch.Tensor]) -> list[torch.Tensor]:
+        c = self.cfg
+        groups: dict[tuple[int, int], list[int]] = {}
+        vecs = []
+        for i, img in enumerate(images):
+            v, gh, gw = self.patches(img.float())
+            vecs.append(v)
+            groups.setdefault((gh, gw), []).append(i)
+        w = self.patch_embed.proj.weight.reshape(c.hidden_size, -1)
+        out: list[torch.Tensor] = [None] * len(images)  # type: ignore[list-item]
+        m2 = c.spatial_merge_size ** 2
+        for (gh, gw), idx in groups.items():
+            dev = vecs[idx[0]].device
+            x = F.linear(torch.stack([vecs[i] for i in idx]), w, self.patch_embed.proj.bias) + self._positions(gh, gw, dev)
+            cos, sin = self._rotary(gh, gw, dev)
+            for blk in self.blocks:
+                x = blk(x, cos, sin)
+            x = self.merger.norm(x).reshape(len(idx), gh * gw // m2, m2 * c.hidden_size)
+            y = self.merger.linear_fc2(F.gelu(self.merger.linear_fc1(x)))
+            for j, i in enumerate(idx):
+                out[i] = y[j]
+        return out

@@ -156,9 +156,25 @@ def build_stack(cfg, replicas: int = 1, device: str = "cpu", env_families: Optio
     ecfg = EngineConfig.from_config(cfg)
     init = None
     mpath = str(cfg.actor_rollout_ref.model.path)
+    vcfg = cfg.actor_rollout_ref.model.get("vision", None)
+    vision_cfg = None
+    if vcfg is not None and bool(vcfg.enable):
+        from ..models.vision import FamilyVisionConfig, VisionConfig
+
+        preset = str(vcfg.preset)
+        if preset == "checkpoint":  # the tower the model directory carries (model.visual.*, sizes from its vision_config)
+            vision_cfg = model_io.load_vision_config(mpath)
+            if vision_cfg is None:
+                raise ValueError(f"{mpath} has no vision_config: vision.preset=checkpoint needs a multi-modal model directory")
+        elif preset.startswith("family_"):
+            vision_cfg = getattr(FamilyVisionConfig, preset[len("family_"):])(out_hidden=mcfg.hidden_size)
+        else:
+            vision_cfg = getattr(VisionConfig, preset)(out_hidden=mcfg.hidden_size)
+    train_vision = vision_cfg is not None and bool(vcfg.get("train", False))
     if not mpath.startswith("preset:"):
-        m = HybridForCausalLM(mcfg, with_mtp=False)
-        model_io.load_model_dir(mpath, m)
+        from_dir = train_vision and str(vcfg.preset) == "checkpoint"  # the directory's tower trains on: its tensors are part of the start
+        m = HybridForCausalLM(mcfg, with_mtp=False, vision=vision_cfg if train_vision else None)
+        model_io.load_model_dir(mpath, m, allow_missing=() if (from_dir or not train_vision) else ("visual.",))
         init = m.state_dict()
     if str(device).startswith("cuda"):  # sized on the host before anything is allocated: over capacity is said now, not by the allocator mid-step
         try:
@@ -174,13 +190,6 @@ def build_stack(cfg, replicas: int = 1, device: str = "cpu", env_families: Optio
                 (log.warning if over else log.info)("trainer memory plan per GPU%s:\n%s", " (OVER the device's capacity)" if over else "", mp.table())
         except Exception as e:  # noqa: BLE001 - a planning note never stops a run
             log.warning("trainer memory plan skipped: %r", e)
-    vcfg = cfg.actor_rollout_ref.model.get("vision", None)
-    vision_cfg = None
-    if vcfg is not None and bool(vcfg.enable):
-        from ..models.vision import VisionConfig
-
-        vision_cfg = getattr(VisionConfig, str(vcfg.preset))(out_hidden=mcfg.hidden_size)
-    train_vision = vision_cfg is not None and bool(vcfg.get("train", False))
     engine = TrainEngine(mcfg, ecfg, device=device, world_group=world_group, seed=int(cfg.trainer.seed), state_dict=init,
                          vision=vision_cfg if train_vision else None)
     rank = engine.rank
@@ -246,9 +255,17 @@ def build_stack(cfg, replicas: int = 1, device: str = "cpu", env_families: Optio
         vision = None
         if vision_cfg is not None:
             from ..loop.vision_encoder import VisionEncoder
-            from ..models.vision import VisionTower
+            from ..models.vision import FamilyVisionConfig, FamilyVisionTower, VisionTower
 
-            tower = VisionTower(vision_cfg).init_weights(int(cfg.trainer.seed))
+            family = isinstance(vision_cfg, FamilyVisionConfig)
+            tower = (FamilyVisionTower if family else VisionTower)(vision_cfg).init_weights(int(cfg.trainer.seed))
+            if family and not mpath.startswith("preset:") and not train_vision:  # the checkpoint's own tower weights
+                own = dict(tower.state_dict())
+                with torch.no_grad():
+                    for key, t in model_io.iter_model_tensors(mpath, only=lambda k: model_io.from_hf_name(k).startswith("visual.")):
+                        name = model_io.from_hf_name(key)[len("visual."):]
+                        if name in own:
+                            own[name].copy_(t.to(own[name].dtype))
             if train_vision:  # the agent loop's copy starts from (and then follows) the trainer's tower
                 tower.load_state_dict({k[len("visual."):]: v for k, v in full.items() if k.startswith("visual.")})
             pixel_dtype = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[str(cfg.data.get("pixel_dtype", "fp32"))]

@@ -83,3 +83,132 @@ def test_rollout_engine_greedy_continuation_equals_generate(tmp_path):
         with torch.no_grad():
             want = hf.generate(torch.tensor([p]), max_new_tokens=10, do_sample=False, pad_token_id=0)[0, len(p):].tolist()
         assert r.output == want
+
+
+def test_family_vision_tower_equals_the_transformers_tower():
+    """The family's vision tower with transformers' weights: same rows for pictures of two sizes (position table interpolation,
+    row / column rotary, window-major patch order, merger), through the state dict as it is (same tensor names)."""
+    from transformers import Qwen3_5Config, Qwen3_5VisionModel
+
+    from pear_b200.models.vision import FamilyVisionConfig, FamilyVisionTower
+
+    v = Qwen3_5Config().vision_config
+    v.depth, v.hidden_size, v.intermediate_size, v.num_heads, v.out_hidden_size, v.num_position_embeddings, v.patch_size = 2, 64, 128, 4, 48, 64, 4
+    torch.manual_seed(0)
+    hf = Qwen3_5VisionModel(v).eval().float()
+    with torch.no_grad():
+        for p in hf.parameters():
+            p.copy_(torch.randn_like(p) * (0.05 if p.dim() > 1 else 0.3) + (1.0 if p.dim() == 1 else 0.0))
+    mine = FamilyVisionTower(FamilyVisionConfig.from_hf_dict(v.to_dict())).eval()
+    missing, unexpected = mine.load_state_dict(hf.state_dict(), strict=True)
+    assert not missing and not unexpected
+    g = torch.Generator().manual_seed(1)
+    pics = [torch.rand(3, 16, 24, generator=g) * 2 - 1, torch.rand(3, 32, 8, generator=g) * 2 - 1, torch.rand(3, 16, 24, generator=g) * 2 - 1]
+    with torch.no_grad():
+        got = mine(pics)
+        for img, rows in zip(pics, got):
+            vec, gh, gw = mine.patches(img)
+            want = hf(vec, grid_thw=torch.tensor([[1, gh, gw]])).pooler_output
+            assert rows.shape == want.shape == (mine.tokens_per_image(*img.shape[1:]), 48)
+            assert float((rows - want).abs().max()) < 2e-5 * max(1.0, float(want.abs().max()))
+
+
+def test_multimodal_checkpoint_with_a_picture_gives_the_same_logits(tmp_path):
+    """A transformers conditional-generation model (text + vision) written out under its state-dict names: everything loads
+    (``model.language_model.*`` into the decoder, ``model.visual.*`` into the family's tower, sizes from ``vision_config``), the
+    (temporal, row, column) positions of a prompt with pictures equal transformers', and so do the logits."""
+    import json
+
+    from transformers import Qwen3_5Config, Qwen3_5ForConditionalGeneration
+
+    from pear_b200.models.hybrid import mrope_positions
+
+    c = Qwen3_5Config()
+    t, v = c.text_config, c.vision_config
+    t.vocab_size, t.hidden_size, t.intermediate_size, t.num_hidden_layers, t.num_attention_heads, t.num_key_value_heads, t.head_dim = 512, 64, 128, 4, 4, 2, 32
+    t.linear_key_head_dim = t.linear_value_head_dim = 16
+    t.linear_num_key_heads, t.linear_num_value_heads = 2, 4
+    t.layer_types = ["linear_attention"] * 3 + ["full_attention"]
+    v.depth, v.hidden_size, v.intermediate_size, v.num_heads, v.out_hidden_size, v.num_position_embeddings, v.patch_size = 2, 64, 128, 4, 64, 64, 4
+    c.image_token_id, c.vision_start_token_id, c.vision_end_token_id, c.video_token_id = 500, 501, 502, 503
+    torch.manual_seed(0)
+    hf = Qwen3_5ForConditionalGeneration(c).eval().float()
+    d = tmp_path / "mm"
+    d.mkdir()
+    model_io.save_safetensors(str(d / "model.safetensors"), {k: p.contiguous() for k, p in hf.state_dict().items()})
+    (d / "config.json").write_text(json.dumps(c.to_dict(), default=str))
+    cfg, vcfg = model_io.load_config(str(d)), model_io.load_vision_config(str(d))
+    mine = HybridForCausalLM(cfg, with_mtp=False, vision=vcfg)
+    assert model_io.load_model_dir(str(d), mine, ignore_unexpected=()) == ([], [])
+    g = torch.Generator().manual_seed(1)
+    pics = [torch.rand(3, 16, 24, generator=g) * 2 - 1, torch.rand(3, 24, 8, generator=g) * 2 - 1]
+    grids, vecs = [], []
+    for img in pics:
+        vec, gh, gw = mine.visual.patches(img)
+        grids.append((gh, gw))
+        vecs.append(vec)
+    text = lambda n: torch.randint(0, 400, (n,), generator=g)  # noqa: E731
+    run = lambda k: torch.tensor([501] + [500] * (grids[k][0] * grids[k][1] // 4) + [502])  # noqa: E731
+    ids = torch.cat([text(7), run(0), text(5), run(1), text(9)])
+    mm = (ids == 500).int()[None]
+    thw = torch.tensor([[1, gh, gw] for gh, gw in grids])
+    with torch.no_grad():
+        want = hf(input_ids=ids[None], pixel_values=torch.cat(vecs), image_grid_thw=thw, mm_token_type_ids=mm).logits[0]
+        want_pos, _ = hf.model.get_rope_index(ids[None], mm, image_grid_thw=thw)
+        pos = mrope_positions(ids, grids, image_pad_id=500)
+        assert torch.equal(pos, want_pos[:, 0])
+        rows = torch.cat(mine.visual(pics))
+        mask = ids == 500
+        emb = torch.zeros(len(ids), cfg.hidden_size)
+        emb[mask] = rows
+        got = mine.logits(mine(ids, pos, [0, len(ids)], inputs_embeds=emb, embeds_mask=mask))
+    assert float((got - want).abs().max()) < 1e-5 * max(1.0, float(want.abs().max()))
+
+
+@pytest.mark.timeout(600)
+def test_training_entry_starts_from_a_multimodal_checkpoint_directory(tmp_path):
+    """``model.path`` = a conditional-generation checkpoint, ``vision.preset=checkpoint``: decoder and tower start from the
+    directory's tensors, the pixel environment's pictures go through that tower in the agent loop and in the trainer, a step
+    trains both."""
+    import json
+
+    import numpy as np
+    from transformers import Qwen3_5Config, Qwen3_5ForConditionalGeneration
+
+    from pear_b200.config.loader import compose
+    from pear_b200.train.main import RunConfig, build_stack
+
+    c = Qwen3_5Config()
+    t, v = c.text_config, c.vision_config
+    t.vocab_size, t.hidden_size, t.intermediate_size, t.num_hidden_layers, t.num_attention_heads, t.num_key_value_heads, t.head_dim = 512, 64, 128, 4, 4, 2, 32
+    t.linear_key_head_dim = t.linear_value_head_dim = 16
+    t.linear_num_key_heads, t.linear_num_value_heads = 2, 4
+    t.layer_types = ["linear_attention"] * 3 + ["full_attention"]
+    v.depth, v.hidden_size, v.intermediate_size, v.num_heads, v.out_hidden_size, v.num_position_embeddings, v.patch_size = 2, 64, 128, 4, 64, 64, 4
+    torch.manual_seed(0)
+    hf = Qwen3_5ForConditionalGeneration(c).eval().float()
+    d = tmp_path / "mm"
+    d.mkdir()
+    model_io.save_safetensors(str(d / "model.safetensors"), {k: p.contiguous() for k, p in hf.state_dict().items()})
+    (d / "config.json").write_text(json.dumps(c.to_dict(), default=str))
+    cfg = RunConfig(compose("training", [f"run_dir={tmp_path / 'run'}", f"actor_rollout_ref.model.path={d}", "data.train_batch_size=2", "actor_rollout_ref.rollout.n=2",
+                                         "data.max_response_length=16", "actor_rollout_ref.rollout.max_model_len=2048", "actor_rollout_ref.rollout.max_num_seqs=8",
+                                         "actor_rollout_ref.rollout.agent.num_workers=2", "actor_rollout_ref.rollout.topk_log_probs=4", "algorithm.filter_groups.enable=false",
+                                         "trainer.total_training_steps=1", "trainer.save_freq=0", "transfer_queue.num_data_storage_units=4",
+                                         "actor_rollout_ref.actor.optim.lr=1e-3", "actor_rollout_ref.actor.ppo_max_token_len_per_gpu=4096", "trainer.logger=[file]",
+                                         "actor_rollout_ref.model.vision.enable=true", "actor_rollout_ref.model.vision.preset=checkpoint",
+                                         "actor_rollout_ref.model.vision.train=true", "actor_rollout_ref.rollout.multi_turn.synthetic_turns=1",
+                                         "actor_rollout_ref.rollout.multi_turn.synthetic_reward=hash"])).prepare()
+    fam = {"synthetic": {"env_path": "pear_b200.envs.synthetic.SyntheticEnv", "num_processes": 1, "env_kwargs": {"pixels": 16}}}
+    trainer, close = build_stack(cfg, env_families=fam)
+    try:
+        start = trainer.engine.full_state_dict()
+        sd = hf.state_dict()
+        assert torch.equal(start["visual.blocks.0.attn.qkv.weight"], sd["model.visual.blocks.0.attn.qkv.weight"])
+        assert torch.equal(start["model.layers.3.self_attn.q_proj.weight"], sd["model.language_model.layers.3.self_attn.q_proj.weight"])
+        hist = trainer.fit()
+        after = trainer.engine.full_state_dict()
+        assert np.isfinite(hist[0]["actor/grad_norm"]) and hist[0]["actor/grad_norm"] > 0
+        assert not torch.equal(after["visual.blocks.0.attn.qkv.weight"], start["visual.blocks.0.attn.qkv.weight"])
+    finally:
+        close()
