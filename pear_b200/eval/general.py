@@ -31,6 +31,8 @@ from concurrent.futures import ThreadPoolExecutor
 from dataclasses import dataclass, field
 from typing import Callable, Optional
 
+import torch
+
 from ..rollout.engine import FinishReason, SamplingParams
 from ..utils.files import atomic_write
 from . import scorers
@@ -40,12 +42,14 @@ class LeastInFlightRouter:
     def __init__(self, servers: list):
         self.servers, self.inflight, self.lock = servers, [0] * len(servers), threading.Lock()
 
-    def generate(self, prompt: list[int], params: SamplingParams):
+    def generate(self, prompt: list[int], params: SamplingParams, embeds=None, embeds_mask=None):
         with self.lock:
             i = min(range(len(self.servers)), key=lambda j: self.inflight[j])
             self.inflight[i] += 1
         try:
-            return self.servers[i].generate(prompt, params)
+            if embeds is None:
+                return self.servers[i].generate(prompt, params)
+            return self.servers[i].generate(prompt, params, embeds=embeds, embeds_mask=embeds_mask)
         finally:
             with self.lock:
                 self.inflight[i] -= 1
@@ -139,13 +143,32 @@ class SampleStore:
         return out
 
 
+def load_picture(path: str, multiple: int, max_side: int = 1024):
+    """A picture file as uint8 ``[H, W, 3]`` whose sides are multiples of ``multiple`` (the tower's patch x merge) and at most
+    ``max_side``: scaled down keeping the aspect ratio when larger, then rounded to the nearest multiple (at least one window)."""
+    import numpy as np
+    from PIL import Image
+
+    img = Image.open(path).convert("RGB")
+    w, h = img.size
+    scale = min(1.0, max_side / max(w, h))
+    w2 = max(multiple, int(round(w * scale / multiple)) * multiple)
+    h2 = max(multiple, int(round(h * scale / multiple)) * multiple)
+    if (w2, h2) != (w, h):
+        img = img.resize((w2, h2), Image.BICUBIC)
+    return np.asarray(img, dtype=np.uint8)
+
+
 class BenchmarkRun:
     DONE = "ok"
 
     def __init__(self, config, router: LeastInFlightRouter, tokenizer, model_name: str, out_dir: str, dataset_dir: str,
-                 only: Optional[list[str]] = None, limit: Optional[int] = None):
+                 only: Optional[list[str]] = None, limit: Optional[int] = None, vision=None, hidden_size: int = 0):
+        """``vision``: a ``loop.vision_encoder.VisionEncoder`` for items that carry pictures (``"images": [file, ...]`` relative to
+        the dataset directory): the pictures follow the question in the user turn, their rows travel with the request."""
         self.config, self.router, self.tok, self.model_name = config, router, tokenizer, model_name
         self.out_dir, self.dataset_dir, self.only, self.limit = out_dir, dataset_dir, only, limit
+        self.vision, self.hidden_size = vision, hidden_size
         self.sampling = {k: config["sampling"][k] for k in sorted(config["sampling"])}
 
     def params(self, max_tokens: int) -> SamplingParams:
@@ -153,9 +176,30 @@ class BenchmarkRun:
         return SamplingParams(max_tokens=max_tokens, temperature=float(s.get("temperature", 1.0)), top_p=float(s.get("top_p", 1.0)),
                               top_k=int(s.get("top_k", 0)), stop_token_ids=(self.tok.eos_id,) + tuple(getattr(self.tok, "extra_stop_ids", ())))
 
+    def _prompt(self, item: Item):
+        """(token ids, picture rows [T, hidden] or None, their mask)."""
+        files = item.extra.get("images") or []
+        if not files:
+            return self.tok.render_turn("user", item.prompt) + self.tok.generation_prompt(), None, None
+        if self.vision is None:
+            raise ValueError(f"item {item.id} carries pictures: the run needs a vision tower (--vision)")
+        import torch
+
+        cfg = self.vision.tower.cfg
+        multiple = getattr(cfg, "patch_size", getattr(cfg, "patch", 1)) * getattr(cfg, "spatial_merge_size", getattr(cfg, "merge", 1))
+        blocks = self.vision.encode([load_picture(os.path.join(self.dataset_dir, f), multiple, int(self.config.get("image_max_side", 1024))) for f in files])
+        ids = self.tok.render_turn("user", item.prompt, images=len(blocks), image_tokens=[b.shape[0] for b in blocks]) + self.tok.generation_prompt()
+        mask = torch.tensor([t == self.tok.image_pad_id for t in ids])
+        rows = torch.from_numpy(__import__("numpy").concatenate(blocks, axis=0))
+        if int(mask.sum()) != rows.shape[0]:
+            raise ValueError(f"item {item.id}: {rows.shape[0]} picture rows for {int(mask.sum())} placeholder tokens")
+        embeds = torch.zeros(len(ids), rows.shape[1])
+        embeds[mask] = rows
+        return ids, embeds, mask
+
     def sample(self, store: SampleStore, bench: dict, item: Item, repeat: int) -> None:
-        prompt = self.tok.render_turn("user", item.prompt) + self.tok.generation_prompt()
-        req = self.router.generate(prompt, self.params(int(bench["max_tokens"])))
+        prompt, embeds, mask = self._prompt(item)
+        req = self.router.generate(prompt, self.params(int(bench["max_tokens"])), embeds=embeds, embeds_mask=mask)
         text = self.tok.decode([t for t in req.output if t != self.tok.eos_id], skip_special=True)
         finish = req.finish.value if isinstance(req.finish, FinishReason) else str(req.finish)
         score = scorers.KINDS[bench["kind"]](text, item.as_dict())
@@ -338,6 +382,7 @@ def main(argv=None) -> int:
     r.add_argument("--replicas", default="", help="url,url,... of rollout replica processes")
     r.add_argument("--model", default="", help="model directory or preset:<name> for in-process replicas (when --replicas is empty)")
     r.add_argument("--num-replicas", type=int, default=1)
+    r.add_argument("--vision", default="", help="vision tower for items with pictures: checkpoint (the --model directory's), family_tiny, tiny")
     r.add_argument("--tokenizer", default="", help="directory with the model's tokenizer.json (default: --model; the byte tokenizer without one)")
     r.add_argument("--model-name", default="", help="the name the samples are kept under (default: --model or the first replica URL)")
     r.add_argument("--out", required=True)
@@ -391,9 +436,29 @@ def main(argv=None) -> int:
         for i in range(args.num_replicas):
             local.append(build_server(load_rollout_model(args.model, with_mtp=False), EngineConfig(), name=f"replica-{i}"))
         servers = local
+    vision = None
+    if args.vision:
+        from ..loop.vision_encoder import VisionEncoder
+        from ..models import io as model_io
+        from ..models.vision import FamilyVisionConfig, FamilyVisionTower, VisionConfig, VisionTower
+
+        if args.vision == "checkpoint":
+            vcfg = model_io.load_vision_config(args.model)
+            if vcfg is None:
+                ap.error(f"{args.model} has no vision_config")
+            tower = FamilyVisionTower(vcfg)
+            own = dict(tower.state_dict())
+            for key, t in model_io.iter_model_tensors(args.model, only=lambda k: model_io.from_hf_name(k).startswith("visual.")):
+                own[model_io.from_hf_name(key)[len("visual."):]].copy_(t.to(torch.float32))
+        else:
+            hidden = model_io.load_config(args.model).hidden_size if args.model and not args.model.startswith("preset:") else 256
+            family = args.vision.startswith("family_")
+            vcfg = getattr(FamilyVisionConfig if family else VisionConfig, args.vision[len("family_"):] if family else args.vision)(out_hidden=hidden)
+            tower = (FamilyVisionTower if family else VisionTower)(vcfg).init_weights(0)
+        vision = VisionEncoder(tower)
     try:
         BenchmarkRun(cfg, LeastInFlightRouter(servers), load_tokenizer(args.tokenizer or args.model), args.model_name or args.model or args.replicas.split(",")[0],
-                     args.out, args.dataset_dir, args.only, args.limit).run()
+                     args.out, args.dataset_dir, args.only, args.limit, vision=vision).run()
     finally:
         for s in servers:
             s.close()

@@ -67,7 +67,8 @@ class ByteTokenizer:
         for i in range(images):
             if labels is not None:
                 ids += self.encode(f"\n[{labels[i]}]\n")
-            ids += [self.special_ids["<|vision_start|>"]] + [self.image_pad_id] * image_tokens + [self.special_ids["<|vision_end|>"]]
+            n = image_tokens[i] if isinstance(image_tokens, (list, tuple)) else image_tokens  # (pictures of different sizes: one count each)
+            ids += [self.special_ids["<|vision_start|>"]] + [self.image_pad_id] * n + [self.special_ids["<|vision_end|>"]]
         return ids + [self.special_ids["<|im_end|>"]] + self.encode("\n")
 
     def generation_prompt(self) -> list[int]:
@@ -124,7 +125,8 @@ class HFTokenizer:
         for i in range(images):
             if labels is not None:
                 ids += self.encode(f"\n[{labels[i]}]\n")
-            ids += [self.special_ids["<|vision_start|>"]] + [self.image_pad_id] * image_tokens + [self.special_ids["<|vision_end|>"]]
+            n = image_tokens[i] if isinstance(image_tokens, (list, tuple)) else image_tokens
+            ids += [self.special_ids["<|vision_start|>"]] + [self.image_pad_id] * n + [self.special_ids["<|vision_end|>"]]
         return ids + [self.special_ids["<|im_end|>"]] + self.encode("\n")
 
     def generation_prompt(self) -> list[int]:

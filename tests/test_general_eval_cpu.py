@@ -166,3 +166,52 @@ def test_router_process_balances_over_backends():
             await sb.close()
 
     asyncio.run(scenario())
+
+
+def test_items_with_pictures_travel_as_rows_at_their_placeholders(tmp_path):
+    """An image benchmark item: its picture files are read, resized to the tower's grid, encoded, and sent as rows at the
+    image-pad positions of a prompt in which they follow the question; two pictures of different sizes take their own counts."""
+    import numpy as np
+    import torch
+    from PIL import Image
+
+    from pear_b200.eval.general import load_picture
+    from pear_b200.loop.vision_encoder import VisionEncoder
+    from pear_b200.models.vision import FamilyVisionConfig, FamilyVisionTower
+
+    ds = tmp_path / "data"
+    (ds / "img").mkdir(parents=True)
+    rng = np.random.default_rng(0)
+    Image.fromarray(rng.integers(0, 256, (37, 50, 3), dtype=np.uint8)).save(ds / "img" / "a.png")   # rounds to 40 x 48
+    Image.fromarray(rng.integers(0, 256, (16, 16, 3), dtype=np.uint8)).save(ds / "img" / "b.png")
+    assert load_picture(str(ds / "img" / "a.png"), 8).shape == (40, 48, 3) and load_picture(str(ds / "img" / "a.png"), 8, max_side=25).shape == (16, 24, 3)
+    (ds / "v.jsonl").write_text(json.dumps({"id": "p1", "prompt": "which option?", "answer": "C", "num_options": 4, "images": ["img/a.png", "img/b.png"]}) + "\n")
+    cfg = compose("general", ["benchmarks={v: {file: v.jsonl, kind: multiple_choice, repeats: 1, max_tokens: 16}}", "concurrency=2"])
+    tower = FamilyVisionTower(FamilyVisionConfig.tiny(out_hidden=24)).init_weights(0)  # patch 4, merge 2: sides in multiples of 8
+    seen = {}
+
+    class Replica:
+        tok = ByteTokenizer()
+
+        def generate(self, prompt, params, embeds=None, embeds_mask=None):
+            seen.update(prompt=list(prompt), embeds=embeds, mask=embeds_mask)
+
+            class R:
+                output = Replica.tok.encode("ANSWER: C")
+                finish = FinishReason.STOP
+
+            return R()
+
+    rep = BenchmarkRun(cfg, LeastInFlightRouter([Replica()]), ByteTokenizer(), "m", str(tmp_path / "run"), str(ds), vision=VisionEncoder(tower)).run()
+    assert rep["v"]["mean"] == 1.0
+    tok = ByteTokenizer()
+    n_a, n_b = tower.tokens_per_image(40, 48), tower.tokens_per_image(16, 16)
+    pads = [i for i, t in enumerate(seen["prompt"]) if t == tok.image_pad_id]
+    assert len(pads) == n_a + n_b == 30 + 4 and seen["mask"].nonzero().flatten().tolist() == pads and seen["embeds"].shape == (len(seen["prompt"]), 24)
+    with torch.no_grad():
+        want = tower([torch.from_numpy(load_picture(str(ds / "img" / "b.png"), 8)).permute(2, 0, 1).float() / 127.5 - 1.0])[0]
+    assert torch.allclose(seen["embeds"][pads[n_a:]], want, atol=1e-5)
+    text = tok.decode(seen["prompt"])
+    assert text.index("which option?") < text.index("<|vision_start|>")
+    with pytest.raises(SystemExit, match="1 of 1 benchmarks failed"):  # pictures without a tower: the benchmark fails by name
+        BenchmarkRun(cfg, LeastInFlightRouter([Replica()]), ByteTokenizer(), "m", str(tmp_path / "run2"), str(ds)).run()
