@@ -105,7 +105,10 @@ def test_recipe_overrides_compose_against_the_shipped_configs(script, tmp_path):
 
 
 def test_commands_and_files_named_by_the_documents_exist():
-    docs = [os.path.join(ROOT, n) for n in ("README.md", "DESIGN.md", "examples/README.md")] + RECIPES
+    # the package's own documents: the markdown files at the top whose title names the package, and the recipes' notes
+    docs = [p for p in sorted(glob.glob(os.path.join(ROOT, "*.md"))) if open(p).readline().lower().startswith("# pear")]
+    docs += sorted(glob.glob(os.path.join(ROOT, "examples", "*.md"))) + RECIPES
+    assert len(docs) >= 3 + len(RECIPES)
     modules, paths = set(), set()
     for d in docs:
         text = open(d).read()
