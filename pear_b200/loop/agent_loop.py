@@ -50,6 +50,10 @@ class AgentLoopConfig:
     # synthetic benchmarks with a random-init policy: play `synthetic_turns` turns with a no-op action whatever the answer
     # says, at most `turn_max_tokens` sampled tokens per turn (0: the episode budget), and draw the reward ("hash": a seeded
     # hash of the sampled tokens mapped to {0, 1}; "bernoulli:p": a seeded coin per trajectory) instead of the env's success
+    # positions of picture rows: "sequential" (a row's position is its index) or "checkpoint" (the family's (temporal, row, column)
+    # rule its pretrained checkpoints expect: needs pictures as pixels, whose grid is known; such requests take the engine's
+    # per-request path)
+    picture_positions: str = "sequential"
     tool_parser: str = "fenced_json"  # how an answer becomes the environment tool's call (`loop/tool_parser.py` registry)
     synthetic_turns: int = 0
     turn_max_tokens: int = 0
@@ -83,6 +87,12 @@ class AgentLoop:
         if first:
             ids += self.tok.render_turn("system", self.system_prompt)
         pixels = [f if (f.ndim == 3 and f.dtype == np.uint8) else None for f in obs.frames]
+        if self.cfg.picture_positions == "checkpoint":
+            if self.vision is None or any(p is None for p in pixels):
+                raise ValueError("picture_positions=checkpoint needs cameras that deliver pixels and a vision encoder (the rows' grid must be known)")
+            c = self.vision.tower.cfg
+            cell = getattr(c, "patch_size", getattr(c, "patch", 1)) * getattr(c, "spatial_merge_size", getattr(c, "merge", 1))
+            ep.grids += [(p.shape[0] // cell, p.shape[1] // cell) for p in pixels]
         if self.vision is not None:
             obs.frames = self.vision.encode(obs.frames)
         elif any(f.ndim != 2 for f in obs.frames):
@@ -104,6 +114,14 @@ class AgentLoop:
             else:
                 j += 1
         self._append(ep, ids + turn + self.tok.generation_prompt(), 0)
+
+    def _positions(self, ep: Episode):
+        """[3, tokens] checkpoint positions of the episode so far (None under sequential positions or without pictures)."""
+        if self.cfg.picture_positions != "checkpoint" or not ep.grids:
+            return None
+        from ..models.hybrid import mrope_positions
+
+        return mrope_positions(torch.tensor(ep.tokens), ep.grids, self.tok.image_pad_id, merge=1)
 
     def _embeds(self, ep: Episode, hidden: int):
         if not ep.embeds:
@@ -165,7 +183,9 @@ class AgentLoop:
                     params = SamplingParams(max_tokens=left, temperature=cfg.temperature, top_p=cfg.top_p, top_k=cfg.top_k,
                                             topk_logprobs=cfg.topk_heads, stop_token_ids=(self.tok.eos_id,) + tuple(getattr(self.tok, "extra_stop_ids", ())))
                     t0 = time.time()
-                    req = self.router.generate(list(ep.tokens), params, session=f"{ep.uid}/{ep.session}", embeds=embeds, embeds_mask=mask)
+                    positions = self._positions(ep)
+                    extra = {} if positions is None else {"position_ids": positions}  # (routers without pictures never see the argument)
+                    req = self.router.generate(list(ep.tokens), params, session=f"{ep.uid}/{ep.session}", embeds=embeds, embeds_mask=mask, **extra)
                     if req.finish == FinishReason.ABORTED:
                         ep.end_reason, state = EndReason.ABORTED, LoopState.TERMINATED
                         continue
@@ -231,6 +251,7 @@ class AgentLoop:
                 "topk_logprobs": np.asarray(ep.topk_logprobs, dtype=np.float32).reshape(len(ep.tokens), self.cfg.topk_heads),
                 "embeds": [(p, b.astype(np.float16)) for p, b in ep.embeds],
                 "images": list(ep.images),
+                "position_ids": (lambda p: None if p is None else p.numpy().astype(np.int32))(self._positions(ep)),
                 "policy_versions": np.asarray(ep.policy_versions, dtype=np.int32),
                 "reward": reward, "prompt_len": ep.prompt_len,
             }, family=ep.family, end_reason=ep.end_reason.value if ep.end_reason else None, turns=ep.turns, restarts=ep.restarts)

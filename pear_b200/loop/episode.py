@@ -39,6 +39,7 @@ class Episode:
     topk_ids: list[list[int]] = field(default_factory=list)      # rollout top-k head ids (placeholders on masked tokens)
     topk_logprobs: list[list[float]] = field(default_factory=list)
     embeds: list = field(default_factory=list)                   # (position, [tokens, hidden] array) vision blocks
+    grids: list = field(default_factory=list)                    # (rows, columns) of every picture's block, in token order (checkpoint positions)
     images: list = field(default_factory=list)                   # (position, uint8 [H, W, 3] picture) of the blocks that came from pixels
     prompt_len: int = 0
     policy_versions: list[int] = field(default_factory=list)

@@ -35,10 +35,12 @@ class Router:
             self.inflight[i] += 1
             return i
 
-    def generate(self, prompt, params, session=None, embeds=None, embeds_mask=None):
+    def generate(self, prompt, params, session=None, embeds=None, embeds_mask=None, position_ids=None):
         i = self._pick(session)
         try:
-            return self.servers[i].generate(prompt, params, session=session, embeds=embeds, embeds_mask=embeds_mask)
+            if position_ids is None:
+                return self.servers[i].generate(prompt, params, session=session, embeds=embeds, embeds_mask=embeds_mask)
+            return self.servers[i].generate(prompt, params, session=session, embeds=embeds, embeds_mask=embeds_mask, position_ids=position_ids)
         finally:
             with self.lock:
                 self.inflight[i] -= 1

@@ -62,6 +62,9 @@ class Request:
     session: Optional[str] = None
     embeds: Optional[torch.Tensor] = None  # [len(prompt), H] placeholder rows (vision embeddings)
     embeds_mask: Optional[torch.Tensor] = None
+    # [3, len(prompt)] (temporal, row, column) positions of a prompt with pictures under the checkpoint's rule (None: every token's
+    # position is its index); generated tokens continue one after the largest position of the prompt
+    position_ids: Optional[torch.Tensor] = None
     arrival: float = field(default_factory=time.time)
     # -- runtime
     output: list[int] = field(default_factory=list)
@@ -142,8 +145,13 @@ class RolloutEngine:
 
     # -- public API ---------------------------------------------------------------------------------------------------
     def add_request(self, prompt: list[int], params: Optional[SamplingParams] = None, session: Optional[str] = None,
-                    request_id: Optional[str] = None, embeds=None, embeds_mask=None) -> Request:
+                    request_id: Optional[str] = None, embeds=None, embeds_mask=None, position_ids=None) -> Request:
         req = Request(request_id or f"req-{next(self._ids)}", list(prompt), params or SamplingParams(), session, embeds, embeds_mask)
+        if position_ids is not None:
+            position_ids = torch.as_tensor(position_ids, dtype=torch.long)
+            if tuple(position_ids.shape) != (3, len(prompt)):
+                raise ValueError(f"position_ids must be [3, {len(prompt)}], got {tuple(position_ids.shape)}")
+            req.position_ids = position_ids
         req.policy_version = self.policy_version
         if self.paused:  # the submission gate closes before the pause: the client resubmits later
             req.finish = FinishReason.ABORTED
@@ -339,7 +347,7 @@ class RolloutEngine:
             if req.seq is None or not self._ensure_blocks(req, req.computed + n) or budget < n:
                 continue
             toks = torch.tensor([req.tokens[-1]] + req.drafts, dtype=torch.long)
-            rows.append(StepRow(req.seq, toks, req.computed, req.block_table, n))
+            rows.append(StepRow(req.seq, toks, req.computed, req.block_table, n, positions=self._row_positions(req, req.computed, n)))
             plan.append((req, n, True))
             budget -= n
         # 2. prefill chunks: running requests still in prefill, then newly admitted ones
@@ -364,7 +372,7 @@ class RolloutEngine:
                 emb = torch.zeros(n_rows, req.embeds.shape[1])
                 msk = torch.zeros(n_rows, dtype=torch.bool)
                 emb[: e - s], msk[: e - s] = req.embeds[s:e], req.embeds_mask[s:e]
-            rows.append(StepRow(req.seq, toks, s, req.block_table, 1 if last_chunk else 0, emb, msk))
+            rows.append(StepRow(req.seq, toks, s, req.block_table, 1 if last_chunk else 0, emb, msk, positions=self._row_positions(req, s, n_rows)))
             plan.append((req, n_rows, False))
             budget -= n_rows
 
@@ -435,7 +443,7 @@ class RolloutEngine:
         if not reqs:
             return []
         p0 = reqs[0].params
-        if p0.temperature <= 0.0 or any(r.params.temperature != p0.temperature or r.params.top_p < 1.0 or r.params.top_k > 0 or r.params.topk_logprobs > 32 or r.params.seed is not None
+        if p0.temperature <= 0.0 or any(r.params.temperature != p0.temperature or r.params.top_p < 1.0 or r.params.top_k > 0 or r.params.topk_logprobs > 32 or r.params.seed is not None or r.position_ids is not None
                                         for r in reqs):
             for r in list(self.running):
                 self._fast_release(r)
@@ -569,6 +577,19 @@ class RolloutEngine:
         return done
 
     # -- sampling / verification / drafting -----------------------------------------------------------------------------
+    @staticmethod
+    def _row_positions(req: Request, start: int, n: int) -> Optional[torch.Tensor]:
+        """[3, n] positions of tokens ``start .. start + n`` of a request that carries its own prompt positions (else None: the
+        runner counts from ``start``): prompt tokens from the table, later tokens one after another past the prompt's largest."""
+        if req.position_ids is None:
+            return None
+        p = req.position_ids
+        n_prompt = p.shape[1]
+        after = int(p.max()) + 1 if n_prompt else 0
+        idx = torch.arange(start, start + n)
+        late = (after + (idx - n_prompt)).clamp(min=0).expand(3, -1)
+        return torch.where((idx < n_prompt)[None], p[:, idx.clamp(max=max(n_prompt - 1, 0))], late)
+
     def _generator(self, req: Request) -> torch.Generator:
         """The engine's generator, or the request's own when it carries a seed: such a request draws the same tokens whatever
         else is in the batch (it stays on the per-request sampling path; the batched step draws from one counter stream)."""
@@ -620,7 +641,8 @@ class RolloutEngine:
             if len(req.output) >= p.max_tokens:
                 self._finish(req, FinishReason.LENGTH)
                 return
-        req.drafts = self._draft(req, row, resid, acc, new) if self.spec > 0 else []
+        # (a request with its own positions does not draft: the drafter's passes count positions from the row's start)
+        req.drafts = self._draft(req, row, resid, acc, new) if (self.spec > 0 and req.position_ids is None) else []
 
     def _fill_drafter_kv(self, req: Request, row: StepRow, x_rows: torch.Tensor) -> None:
         """The drafter's KV of a prefill chunk: position p of the prompt pairs the main model's residual at p with the

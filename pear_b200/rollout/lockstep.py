@@ -76,9 +76,9 @@ class LockstepServer(RolloutServer):
         return fut
 
     def submit(self, prompt: list[int], params: Optional[SamplingParams] = None, session: Optional[str] = None,
-               embeds=None, embeds_mask=None) -> Future:
+               embeds=None, embeds_mask=None, position_ids=None) -> Future:
         cpu = lambda t: t.detach().cpu() if torch.is_tensor(t) else t  # noqa: E731 - events travel pickled
-        return self._enqueue("add", list(prompt), params, session, cpu(embeds), cpu(embeds_mask))
+        return self._enqueue("add", list(prompt), params, session, cpu(embeds), cpu(embeds_mask), cpu(position_ids))
 
     def pause(self, abort: bool = True) -> int:
         return int(self._enqueue("pause", bool(abort)).result(timeout=self.load_wait_s))
@@ -95,10 +95,10 @@ class LockstepServer(RolloutServer):
         kind, ticket = ev[0], ev[1]
         fut = self.tickets.pop(ticket, None) if self.channel.is_leader else None
         if kind == "add":
-            _, _, prompt, params, session, embeds, mask = ev
+            _, _, prompt, params, session, embeds, mask, position_ids = ev
             dev = self.engine.device
             req = self.engine.add_request(prompt, params, session, embeds=embeds.to(dev) if torch.is_tensor(embeds) else embeds,
-                                          embeds_mask=mask.to(dev) if torch.is_tensor(mask) else mask)
+                                          embeds_mask=mask.to(dev) if torch.is_tensor(mask) else mask, position_ids=position_ids)
             if fut is not None:
                 if req.finish is not None:  # rejected by a paused engine
                     fut.set_result(req)

@@ -100,11 +100,13 @@ class RemoteReplica:
 
     # -- the RolloutServer interface the router and WeightSync use ------------------------------------------------------
     def generate(self, prompt: list, params: Optional[SamplingParams] = None, session: Optional[str] = None, embeds=None, embeds_mask=None,
-                 timeout_s: Optional[float] = None, max_resubmits: int = 1000) -> RemoteRequest:
+                 timeout_s: Optional[float] = None, max_resubmits: int = 1000, position_ids=None) -> RemoteRequest:
         p = params or SamplingParams()
         body = {"prompt_token_ids": list(map(int, prompt)), "max_tokens": p.max_tokens, "temperature": p.temperature, "top_p": p.top_p,
                 "top_k": p.top_k, "seed": p.seed, "logprobs": p.topk_logprobs, "stop_token_ids": list(p.stop_token_ids), "session": session, "max_resubmits": max_resubmits}
         body.update(encode_embeds(embeds, embeds_mask))
+        if position_ids is not None:
+            body["position_ids"] = torch.as_tensor(position_ids).tolist()
         out = self._post("/v1/completions", body, timeout_s)
         if "error" in out:
             raise RuntimeError(f"{self.name}: {out['error']}")

@@ -75,12 +75,12 @@ class RolloutServer:
 
     # -- client API ---------------------------------------------------------------------------------------------------
     def submit(self, prompt: list[int], params: Optional[SamplingParams] = None, session: Optional[str] = None,
-               embeds=None, embeds_mask=None) -> Future:
+               embeds=None, embeds_mask=None, position_ids=None) -> Future:
         if self.error is not None:
             raise RuntimeError(f"{self.name}: scheduler stopped") from self.error
         fut: Future = Future()
         with self.lock:
-            req = self.engine.add_request(prompt, params, session, embeds=embeds, embeds_mask=embeds_mask)
+            req = self.engine.add_request(prompt, params, session, embeds=embeds, embeds_mask=embeds_mask, position_ids=position_ids)
             if req.finish is not None:  # rejected by a paused engine
                 fut.set_result(req)
             else:
@@ -88,10 +88,10 @@ class RolloutServer:
         return fut
 
     def generate(self, prompt: list[int], params: Optional[SamplingParams] = None, session: Optional[str] = None,
-                 embeds=None, embeds_mask=None, timeout_s: Optional[float] = None, max_resubmits: int = 1000) -> Request:
+                 embeds=None, embeds_mask=None, timeout_s: Optional[float] = None, max_resubmits: int = 1000, position_ids=None) -> Request:
         """Blocking generate that resubmits a request the engine aborted for a weight sync (keeping what it produced)."""
         for _ in range(max_resubmits):
-            req = self.submit(prompt, params, session, embeds, embeds_mask).result(timeout=timeout_s)
+            req = self.submit(prompt, params, session, embeds, embeds_mask, position_ids).result(timeout=timeout_s)
             if req.finish != FinishReason.ABORTED:
                 return req
             while self.engine.paused and not self.stop_flag:
@@ -183,7 +183,7 @@ class RolloutServer:
                                     stop_token_ids=tuple(int(t) for t in body.get("stop_token_ids", ())))
             embeds, mask = decode_embeds(body)  # vision placeholder rows of a multi-modal prompt (bf16, base64)
             req = self.generate(list(prompt), params, session=body.get("session"), embeds=embeds, embeds_mask=mask,
-                                max_resubmits=int(body.get("max_resubmits", 1000)))
+                                max_resubmits=int(body.get("max_resubmits", 1000)), position_ids=body.get("position_ids"))
             out = {"id": req.request_id, "policy_version": req.policy_version, "cached_prefix": getattr(req, "cached_prefix", 0),
                    "choices": [{"token_ids": req.output, "logprobs": req.logprobs, "topk_ids": req.topk_ids, "topk_logprobs": req.topk_logprobs,
                                 "finish_reason": req.finish.value if req.finish else None}],

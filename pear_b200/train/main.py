@@ -249,7 +249,8 @@ def build_stack(cfg, replicas: int = 1, device: str = "cpu", env_families: Optio
         acfg = AgentLoopConfig(token_budget=int(cfg.data.max_response_length), temperature=float(ro.temperature), top_p=float(ro.top_p), top_k=int(ro.get("top_k", -1)),
                                topk_heads=tcfg.topk_heads, max_model_len=int(ro.max_model_len), max_prompt_length=int(cfg.data.get("max_prompt_length", 0) or 0), log_dir=os.environ.get("PEAR_LOG_DIR"),
                                synthetic_turns=int(ro.multi_turn.synthetic_turns), turn_max_tokens=int(ro.multi_turn.turn_max_tokens),
-                               synthetic_reward=ro.multi_turn.synthetic_reward, tool_parser=str(ro.multi_turn.get("format", "fenced_json")))
+                               synthetic_reward=ro.multi_turn.synthetic_reward, tool_parser=str(ro.multi_turn.get("format", "fenced_json")),
+                               picture_positions=str(ro.get("picture_positions", "sequential")))
         from ..utils.tokenizer import load_tokenizer
 
         vision = None

@@ -68,7 +68,8 @@ def trajectory_to_rows(tr: dict, advantage: float, hidden: int, topk: int, train
     labels = torch.cat([tokens[1:], tokens[:1]])
     loss_mask = torch.cat([mask[1:], mask.new_zeros(1)])       # position t is trained iff token t+1 was sampled
     slp = torch.cat([lp[1:], lp.new_zeros(1)])
-    out = dict(input_ids=tokens, position_ids=torch.arange(n), labels=labels, loss_mask=loss_mask,
+    pos = tr.get("position_ids")  # [3, n] when the rollout used the checkpoint's picture positions
+    out = dict(input_ids=tokens, position_ids=torch.arange(n) if pos is None else torch.from_numpy(np.asarray(pos)).long(), labels=labels, loss_mask=loss_mask,
                advantages=torch.full((n,), float(advantage)) * loss_mask, sampler_log_probs=slp)
     if topk > 0:
         ids = torch.from_numpy(np.asarray(tr["topk_ids"])).reshape(n, -1)[:, :topk]
@@ -107,7 +108,12 @@ def pack_rows(rows: list[dict]) -> PackedBatch:
         emb = torch.cat([r.get("inputs_embeds", torch.zeros(r["input_ids"].numel(), h)) for r in rows])
         em = torch.cat([r.get("embeds_mask", torch.zeros(r["input_ids"].numel(), dtype=torch.bool)) for r in rows])
     images = [(cu[i] + pos, img) for i, r in enumerate(rows) for pos, img in r.get("images", [])]
-    return PackedBatch(cat("input_ids"), cat("position_ids"), cu, cat("labels"), cat("loss_mask"), cat("advantages"),
+    positions = [r["position_ids"] for r in rows]
+    if any(p.dim() == 2 for p in positions):  # some sequences carry (temporal, row, column) positions: all three axes for everyone
+        positions = torch.cat([p if p.dim() == 2 else p.expand(3, -1) for p in positions], dim=1)
+    else:
+        positions = torch.cat(positions)
+    return PackedBatch(cat("input_ids"), positions, cu, cat("labels"), cat("loss_mask"), cat("advantages"),
                        sampler_log_probs=cat("sampler_log_probs"), head_ids=cat("head_ids"), head_log_probs=cat("head_log_probs"),
                        inputs_embeds=emb, embeds_mask=em, images=images or None)
 

@@ -212,3 +212,56 @@ def test_training_entry_starts_from_a_multimodal_checkpoint_directory(tmp_path):
         assert not torch.equal(after["visual.blocks.0.attn.qkv.weight"], start["visual.blocks.0.attn.qkv.weight"])
     finally:
         close()
+
+
+def test_rollout_engine_with_pictures_and_checkpoint_positions_equals_generate(tmp_path):
+    """A prompt with a picture through the rollout engine (rows at the placeholders, the checkpoint's (t, h, w) positions, decode
+    positions continuing past the picture) gives transformers' greedy continuation of the same multi-modal input."""
+    import json
+
+    from transformers import Qwen3_5Config, Qwen3_5ForConditionalGeneration
+
+    from pear_b200.models.hybrid import mrope_positions
+    from pear_b200.rollout.engine import EngineConfig, RolloutEngine, SamplingParams
+
+    c = Qwen3_5Config()
+    t, v = c.text_config, c.vision_config
+    t.vocab_size, t.hidden_size, t.intermediate_size, t.num_hidden_layers, t.num_attention_heads, t.num_key_value_heads, t.head_dim = 512, 64, 128, 4, 4, 2, 32
+    t.linear_key_head_dim = t.linear_value_head_dim = 16
+    t.linear_num_key_heads, t.linear_num_value_heads = 2, 4
+    t.layer_types = ["linear_attention"] * 3 + ["full_attention"]
+    v.depth, v.hidden_size, v.intermediate_size, v.num_heads, v.out_hidden_size, v.num_position_embeddings, v.patch_size = 2, 64, 128, 4, 64, 64, 4
+    c.image_token_id, c.vision_start_token_id, c.vision_end_token_id, c.video_token_id = 500, 501, 502, 503
+    torch.manual_seed(3)
+    hf = Qwen3_5ForConditionalGeneration(c).eval().float()
+    with torch.no_grad():
+        for p in hf.parameters():
+            if p.dim() > 1:
+                p.mul_(3.0)
+    d = tmp_path / "mm"
+    d.mkdir()
+    model_io.save_safetensors(str(d / "model.safetensors"), {k: p.contiguous() for k, p in hf.state_dict().items()})
+    (d / "config.json").write_text(json.dumps(c.to_dict(), default=str))
+    cfg, vcfg = model_io.load_config(str(d)), model_io.load_vision_config(str(d))
+    mine = HybridForCausalLM(cfg, with_mtp=False, vision=vcfg)
+    model_io.load_model_dir(str(d), mine, ignore_unexpected=())
+    g = torch.Generator().manual_seed(1)
+    img = torch.rand(3, 16, 24, generator=g) * 2 - 1
+    vec, gh, gw = mine.visual.patches(img)
+    ids = torch.cat([torch.randint(0, 400, (6,), generator=g), torch.tensor([501] + [500] * (gh * gw // 4) + [502]), torch.randint(0, 400, (8,), generator=g)])
+    mask = ids == 500
+    with torch.no_grad():
+        emb = torch.zeros(len(ids), cfg.hidden_size)
+        emb[mask] = mine.visual([img])[0]
+        want = hf.generate(input_ids=ids[None], pixel_values=vec, image_grid_thw=torch.tensor([[1, gh, gw]]), mm_token_type_ids=mask.int()[None],
+                           max_new_tokens=8, do_sample=False, pad_token_id=0)[0, len(ids):].tolist()
+    eng = RolloutEngine(mine, EngineConfig(num_blocks=64, max_num_seqs=2, max_num_batched_tokens=16))  # (prefill in chunks: positions per chunk)
+    req = eng.add_request(ids.tolist(), SamplingParams(max_tokens=8, temperature=0.0), embeds=emb, embeds_mask=mask,
+                          position_ids=mrope_positions(ids, [(gh, gw)], image_pad_id=500))
+    while eng.has_work():
+        eng.step()
+    assert req.output == want
+    plain = eng.add_request(ids.tolist(), SamplingParams(max_tokens=8, temperature=0.0), embeds=emb, embeds_mask=mask)  # sequential positions: another model input
+    while eng.has_work():
+        eng.step()
+    assert len(plain.output) == 8

@@ -163,3 +163,37 @@ def test_vision_tower_trains_under_the_policy_loss_and_the_agent_loop_follows_it
         assert any(n.startswith("visual.") for n in names)
     finally:
         close()
+
+
+@pytest.mark.timeout(600)
+def test_checkpoint_picture_positions_in_rollout_and_training(tmp_path):
+    """``rollout.picture_positions=checkpoint``: the agent loop sends (temporal, row, column) positions with every request, the
+    engine runs such requests on its per-request path, trajectories carry the positions and the trainer trains on them."""
+    fam = {"synthetic": {"env_path": "pear_b200.envs.synthetic.SyntheticEnv", "num_processes": 2, "env_kwargs": {"pixels": 16, "cameras": ("front", "wrist")}}}
+    cfg = _cfg(str(tmp_path / "run"), ["actor_rollout_ref.model.vision.enable=true", "actor_rollout_ref.model.vision.preset=family_tiny",
+                                        "actor_rollout_ref.model.vision.train=true", "actor_rollout_ref.rollout.picture_positions=checkpoint",
+                                        "trainer.total_training_steps=1", "trainer.save_freq=0", "actor_rollout_ref.rollout.multi_turn.synthetic_turns=2",
+                                        "actor_rollout_ref.rollout.multi_turn.synthetic_reward=hash"])
+    trainer, close = build_stack(cfg, env_families=fam)
+    seen = []
+    try:
+        q = trainer.queue
+        put = q.put_trajectory
+
+        def spy(key, tr, **kw):
+            seen.append(tr)
+            return put(key, tr, **kw)
+
+        q.put_trajectory = spy
+        hist = trainer.fit()
+        assert len(hist) == 1 and np.isfinite(hist[0]["actor/grad_norm"]) and hist[0]["actor/grad_norm"] > 0
+        tr = seen[0]
+        pos = tr["position_ids"]
+        assert pos.shape == (3, len(tr["tokens"])) and len(tr["images"]) == 4  # two cameras, two turns
+        first = tr["images"][0][0]
+        n_tok = 4  # 16 x 16 pixels, patch 4, merge 2: a 2 x 2 block
+        assert pos[0, first:first + n_tok].tolist() == [pos[0, first]] * n_tok and pos[1, first:first + n_tok].tolist() == [pos[1, first] + d for d in (0, 0, 1, 1)]
+        assert pos[2, first:first + n_tok].tolist() == [pos[2, first] + d for d in (0, 1, 0, 1)]
+        assert int(pos.max()) < len(tr["tokens"]) - 1  # pictures used fewer positions than tokens
+    finally:
+        close()
