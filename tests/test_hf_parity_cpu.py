@@ -265,3 +265,30 @@ def test_rollout_engine_with_pictures_and_checkpoint_positions_equals_generate(t
     while eng.has_work():
         eng.step()
     assert len(plain.output) == 8
+
+
+def test_speculative_decoding_and_a_cached_second_turn_stay_equal_to_generate(tmp_path):
+    """Lossless by construction, checked against the outside implementation: with a (random) MTP drafter proposing three tokens a
+    step the greedy continuation is still transformers'; a second turn that resumes from the prefix cache (KV pages and the
+    recurrent-state snapshot of the first turn) continues as ``generate`` does on the whole conversation."""
+    from pear_b200.models.config import HybridConfig
+    from pear_b200.rollout.engine import EngineConfig, RolloutEngine, SamplingParams
+
+    hf = _hf_model(6)
+    hf.save_pretrained(str(tmp_path / "hf"), safe_serialization=True)
+    base = model_io.load_config(str(tmp_path / "hf"))
+    cfg = HybridConfig.from_dict({**base.to_dict(), "num_mtp_layers": 1})
+    mine = HybridForCausalLM(cfg, with_mtp=True).init_weights(11)  # the drafter keeps these random weights
+    model_io.load_model_dir(str(tmp_path / "hf"), mine, allow_missing=("mtp.",))
+    g = torch.Generator().manual_seed(8)
+    prompt = torch.randint(0, 512, (37,), generator=g).tolist()
+    eng = RolloutEngine(mine, EngineConfig(num_blocks=64, max_num_seqs=2, num_speculative_tokens=3))
+    first = eng.generate([prompt], SamplingParams(max_tokens=12, temperature=0.0), sessions=["s"])[0]
+    with torch.no_grad():
+        want1 = hf.generate(torch.tensor([prompt]), max_new_tokens=12, do_sample=False, pad_token_id=0)[0, len(prompt):].tolist()
+    assert first.output == want1 and eng.metrics["spec_drafted"] > 0
+    turn2 = prompt + first.output + torch.randint(0, 512, (9,), generator=g).tolist()
+    second = eng.generate([turn2], SamplingParams(max_tokens=10, temperature=0.0), sessions=["s"])[0]
+    with torch.no_grad():
+        want2 = hf.generate(torch.tensor([turn2]), max_new_tokens=10, do_sample=False, pad_token_id=0)[0, len(turn2):].tolist()
+    assert second.cached_prefix >= 16 and second.output == want2
