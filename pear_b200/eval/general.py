@@ -143,17 +143,33 @@ class SampleStore:
         return out
 
 
-def load_picture(path: str, multiple: int, max_side: int = 1024):
-    """A picture file as uint8 ``[H, W, 3]`` whose sides are multiples of ``multiple`` (the tower's patch x merge) and at most
-    ``max_side``: scaled down keeping the aspect ratio when larger, then rounded to the nearest multiple (at least one window)."""
+def picture_size(height: int, width: int, multiple: int, min_pixels: int, max_pixels: int) -> tuple[int, int]:
+    """The size a picture is resized to before the tower: both sides the nearest multiple of ``multiple`` (the tower's patch x
+    merge), then scaled (aspect kept, sides floored / ceiled to multiples) so that the area lies in [min_pixels, max_pixels]: the
+    rule of the family's image processor, checked against it in ``tests/test_hf_parity_cpu.py``."""
+    import math
+
+    h = max(multiple, round(height / multiple) * multiple)
+    w = max(multiple, round(width / multiple) * multiple)
+    if h * w > max_pixels:
+        beta = math.sqrt(height * width / max_pixels)
+        h = max(multiple, math.floor(height / beta / multiple) * multiple)
+        w = max(multiple, math.floor(width / beta / multiple) * multiple)
+    elif h * w < min_pixels:
+        beta = math.sqrt(min_pixels / (height * width))
+        h = math.ceil(height * beta / multiple) * multiple
+        w = math.ceil(width * beta / multiple) * multiple
+    return h, w
+
+
+def load_picture(path: str, multiple: int, max_pixels: int = 1 << 20, min_pixels: int = 0):
+    """A picture file as uint8 ``[H, W, 3]`` at :func:`picture_size` (bicubic)."""
     import numpy as np
     from PIL import Image
 
     img = Image.open(path).convert("RGB")
     w, h = img.size
-    scale = min(1.0, max_side / max(w, h))
-    w2 = max(multiple, int(round(w * scale / multiple)) * multiple)
-    h2 = max(multiple, int(round(h * scale / multiple)) * multiple)
+    h2, w2 = picture_size(h, w, multiple, min_pixels, max_pixels)
     if (w2, h2) != (w, h):
         img = img.resize((w2, h2), Image.BICUBIC)
     return np.asarray(img, dtype=np.uint8)
@@ -187,7 +203,7 @@ class BenchmarkRun:
 
         cfg = self.vision.tower.cfg
         multiple = getattr(cfg, "patch_size", getattr(cfg, "patch", 1)) * getattr(cfg, "spatial_merge_size", getattr(cfg, "merge", 1))
-        blocks = self.vision.encode([load_picture(os.path.join(self.dataset_dir, f), multiple, int(self.config.get("image_max_side", 1024))) for f in files])
+        blocks = self.vision.encode([load_picture(os.path.join(self.dataset_dir, f), multiple, int(self.config.get("image_max_pixels", 1 << 20)), int(self.config.get("image_min_pixels", 0))) for f in files])
         ids = self.tok.render_turn("user", item.prompt, images=len(blocks), image_tokens=[b.shape[0] for b in blocks]) + self.tok.generation_prompt()
         mask = torch.tensor([t == self.tok.image_pad_id for t in ids])
         rows = torch.from_numpy(__import__("numpy").concatenate(blocks, axis=0))

@@ -184,9 +184,9 @@ def test_items_with_pictures_travel_as_rows_at_their_placeholders(tmp_path):
     rng = np.random.default_rng(0)
     Image.fromarray(rng.integers(0, 256, (37, 50, 3), dtype=np.uint8)).save(ds / "img" / "a.png")   # rounds to 40 x 48
     Image.fromarray(rng.integers(0, 256, (16, 16, 3), dtype=np.uint8)).save(ds / "img" / "b.png")
-    assert load_picture(str(ds / "img" / "a.png"), 8).shape == (40, 48, 3) and load_picture(str(ds / "img" / "a.png"), 8, max_side=25).shape == (16, 24, 3)
+    assert load_picture(str(ds / "img" / "a.png"), 8).shape == (40, 48, 3) and load_picture(str(ds / "img" / "a.png"), 8, max_pixels=600).shape == (16, 24, 3)
     (ds / "v.jsonl").write_text(json.dumps({"id": "p1", "prompt": "which option?", "answer": "C", "num_options": 4, "images": ["img/a.png", "img/b.png"]}) + "\n")
-    cfg = compose("general", ["benchmarks={v: {file: v.jsonl, kind: multiple_choice, repeats: 1, max_tokens: 16}}", "concurrency=2"])
+    cfg = compose("general", ["benchmarks={v: {file: v.jsonl, kind: multiple_choice, repeats: 1, max_tokens: 16}}", "concurrency=2", "image_min_pixels=0"])
     tower = FamilyVisionTower(FamilyVisionConfig.tiny(out_hidden=24)).init_weights(0)  # patch 4, merge 2: sides in multiples of 8
     seen = {}
 

@@ -292,3 +292,25 @@ def test_speculative_decoding_and_a_cached_second_turn_stay_equal_to_generate(tm
     with torch.no_grad():
         want2 = hf.generate(torch.tensor([turn2]), max_new_tokens=10, do_sample=False, pad_token_id=0)[0, len(turn2):].tolist()
     assert second.cached_prefix >= 16 and second.output == want2
+
+
+def test_picture_patches_and_sizes_equal_the_family_image_processor():
+    """What reaches the tower: the window-major patch rows of a picture equal the family's image processor's ``pixel_values`` (same
+    normalisation, same order), and the resize rule picks the processor's sizes."""
+    import numpy as np
+    from transformers import Qwen2VLImageProcessor
+
+    from pear_b200.eval.general import picture_size
+    from pear_b200.models.vision import FamilyVisionConfig, FamilyVisionTower
+
+    tower = FamilyVisionTower(FamilyVisionConfig.tiny())  # patch 4, merge 2, temporal patch 2
+    rng = np.random.default_rng(0)
+    arr = rng.integers(0, 256, (16, 24, 3), dtype=np.uint8)
+    proc = Qwen2VLImageProcessor(patch_size=4, merge_size=2, temporal_patch_size=2, min_pixels=64, max_pixels=4096, image_mean=[0.5] * 3, image_std=[0.5] * 3, do_resize=False)
+    out = proc(images=[arr], return_tensors="pt")
+    vec, gh, gw = tower.patches(torch.from_numpy(arr).permute(2, 0, 1).float() / 127.5 - 1.0)
+    assert out["image_grid_thw"].tolist() == [[1, gh, gw]] and float((vec - out["pixel_values"]).abs().max()) < 1e-6
+    resizing = Qwen2VLImageProcessor(patch_size=4, merge_size=2, temporal_patch_size=2, min_pixels=256, max_pixels=2048, image_mean=[0.5] * 3, image_std=[0.5] * 3)
+    for h, w in ((37, 50), (9, 11), (100, 70), (16, 16), (64, 200)):
+        grid = resizing(images=[rng.integers(0, 256, (h, w, 3), dtype=np.uint8)], return_tensors="pt")["image_grid_thw"][0].tolist()
+        assert picture_size(h, w, 8, 256, 2048) == (grid[1] * 4, grid[2] * 4), (h, w, grid)
