@@ -35,6 +35,7 @@ import torch
 
 from ..rollout.engine import FinishReason, SamplingParams
 from ..utils.files import atomic_write
+from ..models.vision import picture_size  # noqa: F401  (re-exported: the rule lives beside the towers)
 from . import scorers
 
 
@@ -141,25 +142,6 @@ class SampleStore:
         for (i, _), rec in sorted(self.done.items()):
             out.setdefault(i, []).append(float(rec["score"]))
         return out
-
-
-def picture_size(height: int, width: int, multiple: int, min_pixels: int, max_pixels: int) -> tuple[int, int]:
-    """The size a picture is resized to before the tower: both sides the nearest multiple of ``multiple`` (the tower's patch x
-    merge), then scaled (aspect kept, sides floored / ceiled to multiples) so that the area lies in [min_pixels, max_pixels]: the
-    rule of the family's image processor, checked against it in ``tests/test_hf_parity_cpu.py``."""
-    import math
-
-    h = max(multiple, round(height / multiple) * multiple)
-    w = max(multiple, round(width / multiple) * multiple)
-    if h * w > max_pixels:
-        beta = math.sqrt(height * width / max_pixels)
-        h = max(multiple, math.floor(height / beta / multiple) * multiple)
-        w = max(multiple, math.floor(width / beta / multiple) * multiple)
-    elif h * w < min_pixels:
-        beta = math.sqrt(min_pixels / (height * width))
-        h = math.ceil(height * beta / multiple) * multiple
-        w = math.ceil(width * beta / multiple) * multiple
-    return h, w
 
 
 def load_picture(path: str, multiple: int, max_pixels: int = 1 << 20, min_pixels: int = 0):

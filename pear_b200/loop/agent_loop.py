@@ -90,9 +90,7 @@ class AgentLoop:
         if self.cfg.picture_positions == "checkpoint":
             if self.vision is None or any(p is None for p in pixels):
                 raise ValueError("picture_positions=checkpoint needs cameras that deliver pixels and a vision encoder (the rows' grid must be known)")
-            c = self.vision.tower.cfg
-            cell = getattr(c, "patch_size", getattr(c, "patch", 1)) * getattr(c, "spatial_merge_size", getattr(c, "merge", 1))
-            ep.grids += [(p.shape[0] // cell, p.shape[1] // cell) for p in pixels]
+            ep.grids += [self.vision.grid(p) for p in pixels]
         if self.vision is not None:
             obs.frames = self.vision.encode(obs.frames)
         elif any(f.ndim != 2 for f in obs.frames):

@@ -20,7 +20,13 @@ import torch
 
 
 class VisionEncoder:
-    def __init__(self, tower, device: str = "cpu", cache_entries: int = 512, pixel_dtype: torch.dtype = torch.float32):
+    def __init__(self, tower, device: str = "cpu", cache_entries: int = 512, pixel_dtype: torch.dtype = torch.float32,
+                 min_pixels: int = 0, max_pixels: int = 1 << 22):
+        """``min_pixels`` / ``max_pixels``: a camera picture whose sides are not multiples of the tower's patch x merge, or whose
+        area is out of bounds, is resized first (the family's image-processor rule, ``eval/general.py: picture_size``)."""
+        c = tower.cfg
+        self.cell = getattr(c, "patch_size", getattr(c, "patch", 1)) * getattr(c, "spatial_merge_size", getattr(c, "merge", 1))
+        self.min_pixels, self.max_pixels = min_pixels, max_pixels
         self.tower = tower.to(device).eval()
         self.device, self.pixel_dtype = torch.device(device), pixel_dtype
         self.cache: "OrderedDict[bytes, np.ndarray]" = OrderedDict()
@@ -40,6 +46,13 @@ class VisionEncoder:
                     own[k].copy_(v.to(own[k].dtype))
             self.cache.clear()
 
+    def grid(self, frame: np.ndarray) -> tuple[int, int]:
+        """(rows, columns) of the block a pixel frame is encoded to."""
+        from ..models.vision import picture_size
+
+        h, w = picture_size(frame.shape[0], frame.shape[1], self.cell, self.min_pixels, self.max_pixels)
+        return h // self.cell, w // self.cell
+
     @staticmethod
     def is_pixels(frame: np.ndarray) -> bool:
         return frame.ndim == 3 and frame.dtype == np.uint8
@@ -48,7 +61,13 @@ class VisionEncoder:
         """[H, W, C] uint8 -> [C, H, W] in [-1, 1]; ``pixel_dtype`` is the precision pixels are handed over in (the tower itself
         computes in fp32)."""
         x = torch.from_numpy(np.ascontiguousarray(frame)).to(self.device).permute(2, 0, 1).to(self.pixel_dtype)
-        return (x / 127.5 - 1.0).float()
+        x = (x / 127.5 - 1.0).float()
+        from ..models.vision import picture_size
+
+        h, w = picture_size(x.shape[1], x.shape[2], self.cell, self.min_pixels, self.max_pixels)
+        if (h, w) != tuple(x.shape[1:]):
+            x = torch.nn.functional.interpolate(x[None], size=(h, w), mode="bicubic", align_corners=False, antialias=True)[0].clamp(-1.0, 1.0)
+        return x
 
     def encode(self, frames: list[np.ndarray]) -> list[np.ndarray]:
         out: list = [None] * len(frames)
