@@ -24,8 +24,9 @@ class VisionEncoder:
                  min_pixels: int = 0, max_pixels: int = 1 << 22):
         """``min_pixels`` / ``max_pixels``: a camera picture whose sides are not multiples of the tower's patch x merge, or whose
         area is out of bounds, is resized first (the family's image-processor rule, ``eval/general.py: picture_size``)."""
-        c = tower.cfg
-        self.cell = getattr(c, "patch_size", getattr(c, "patch", 1)) * getattr(c, "spatial_merge_size", getattr(c, "merge", 1))
+        from ..models.vision import tower_cell
+
+        self.cell = tower_cell(tower.cfg)
         self.min_pixels, self.max_pixels = min_pixels, max_pixels
         self.tower = tower.to(device).eval()
         self.device, self.pixel_dtype = torch.device(device), pixel_dtype
@@ -60,14 +61,9 @@ class VisionEncoder:
     def _prepare(self, frame: np.ndarray) -> torch.Tensor:
         """[H, W, C] uint8 -> [C, H, W] in [-1, 1]; ``pixel_dtype`` is the precision pixels are handed over in (the tower itself
         computes in fp32)."""
-        x = torch.from_numpy(np.ascontiguousarray(frame)).to(self.device).permute(2, 0, 1).to(self.pixel_dtype)
-        x = (x / 127.5 - 1.0).float()
-        from ..models.vision import picture_size
+        from ..models.vision import prepare_picture
 
-        h, w = picture_size(x.shape[1], x.shape[2], self.cell, self.min_pixels, self.max_pixels)
-        if (h, w) != tuple(x.shape[1:]):
-            x = torch.nn.functional.interpolate(x[None], size=(h, w), mode="bicubic", align_corners=False, antialias=True)[0].clamp(-1.0, 1.0)
-        return x
+        return prepare_picture(np.ascontiguousarray(frame), self.cell, self.min_pixels, self.max_pixels, self.device, self.pixel_dtype)
 
     def encode(self, frames: list[np.ndarray]) -> list[np.ndarray]:
         out: list = [None] * len(frames)

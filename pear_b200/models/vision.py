@@ -37,6 +37,22 @@ def picture_size(height: int, width: int, multiple: int, min_pixels: int, max_pi
     return h, w
 
 
+def tower_cell(cfg) -> int:
+    """Pixels per side of one output row's window: patch x merge of either tower's config."""
+    return getattr(cfg, "patch_size", getattr(cfg, "patch", 1)) * getattr(cfg, "spatial_merge_size", getattr(cfg, "merge", 1))
+
+
+def prepare_picture(frame, cell: int, min_pixels: int = 0, max_pixels: int = 1 << 22, device="cpu", pixel_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """uint8 ``[H, W, C]`` (array or tensor) -> ``[C, H', W']`` in [-1, 1] at :func:`picture_size`: what both the agent loop's
+    encoder and the trainer feed a tower, so a picture gives the same rows on either side."""
+    x = torch.as_tensor(frame).to(device).permute(2, 0, 1).to(pixel_dtype)
+    x = (x / 127.5 - 1.0).float()
+    h, w = picture_size(x.shape[1], x.shape[2], cell, min_pixels, max_pixels)
+    if (h, w) != tuple(x.shape[1:]):
+        x = F.interpolate(x[None], size=(h, w), mode="bicubic", align_corners=False, antialias=True)[0].clamp(-1.0, 1.0)
+    return x
+
+
 @dataclass
 class VisionConfig:
     patch: int = 14

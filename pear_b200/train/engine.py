@@ -193,6 +193,7 @@ class TrainEngine:
                     replicate_group = g
             self.shard_world, self.shard_rank = S, self.rank % S
         self.replicate_group = replicate_group
+        self.vision_min_pixels, self.vision_max_pixels = 0, 1 << 22  # (the agent loop's encoder must be given the same bounds)
         if kernels is None and cfg.kernels:  # the recipe names the family's training kernels by class path (`fsdp_config.kernels`)
             import importlib
 
@@ -288,10 +289,12 @@ class TrainEngine:
         """The vision tower's rows for a micro-batch's pictures, placed at their positions inside this rank's slice
         ``[lo, lo + t_local)``. Every picture is encoded once, by the sequence-parallel rank it is dealt to (by patch count);
         the rows are all-gathered with gradients (``parallel/vision_sp.py``), so the tower trains under the policy loss."""
+        from ..models.vision import prepare_picture, tower_cell
         from ..parallel.vision_sp import encode_sharded
 
         dev = self.device
-        pics = [(torch.as_tensor(img).to(dev).permute(2, 0, 1).float() / 127.5 - 1.0) for _, img in images]
+        cell = tower_cell(self.model.visual.cfg)
+        pics = [prepare_picture(img, cell, self.vision_min_pixels, self.vision_max_pixels, dev) for _, img in images]  # as the agent loop's encoder does
         rows = encode_sharded(self.model.visual, pics, self.sp_group)
         h = self.model_cfg.hidden_size
         base = inputs_embeds.float() if inputs_embeds is not None else torch.zeros(t_local, h, device=dev)
