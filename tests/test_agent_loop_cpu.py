@@ -305,3 +305,19 @@ def test_agent_loop_emits_the_structured_events(pool, caplog):
     assert json.loads(fail.split(" ", 1)[1])["uid"] == "ge"
     e = json.loads(end.split(" ", 1)[1])
     assert e["reason"] == "parse" and e["success"] is False and e["turns"] == 1 and e["tokens"] > 0
+
+
+def test_answer_parsing_cases_of_the_family():
+    """The family's answer format, case by case: the call is the LAST fenced json block after the thinking; a block inside the
+    thinking is no answer; an invalid block gives its reason and no call; without a thinking marker the whole text counts."""
+    action = '{"x": 1.5}'
+    text = f'<think>```json\n{{"x": 0}}\n```</think>first ```json\n{{"x": 0.5}}\n``` then ```json\n{action}\n```'
+    assert extract_action(text) == {"x": 1.5}
+    calls = get_parser("qwen3_8")(text)
+    assert [(c.name, c.arguments) for c in calls] == [("env", {"x": 1.5})]
+    with pytest.raises(ParseError, match="no fenced json block"):
+        extract_action(f"<think>```json\n{action}\n```</think>no block here")
+    assert get_parser("qwen3_8")(f"<think>```json\n{action}\n```</think>no block here") == []
+    with pytest.raises(ParseError, match="invalid json"):
+        extract_action('</think>```json\n{"x": }\n```')
+    assert extract_action(f"plain ```json\n{action}\n```") == {"x": 1.5}
