@@ -45,7 +45,7 @@ def pass_rate_metrics(rewards: torch.Tensor, prefix: str = "filter_groups") -> d
     ok = (rewards > 0).float()
     solved = ok.sum(1)
     return {
-        f"{prefix}/avg@{n}": float(ok.mean()) if rewards.numel() else 0.0,
+        f"{prefix}/avg@n": float(ok.mean()) if rewards.numel() else 0.0,  # (the key says "n" literally, whatever the group size: dashboards keep one series)
         f"{prefix}/passrate/zero": float((solved == 0).float().mean()) if rewards.numel() else 0.0,
         f"{prefix}/passrate/one": float((solved == n).float().mean()) if rewards.numel() else 0.0,
     }

@@ -69,7 +69,7 @@ def test_replay_buffer_filter_staleness_and_caps():
     version[0] = 2
     got = rb.sample(2, 1, refill=refill, timeout_s=5)
     assert got[0].uid != "old" and rb.dropped_stale >= 1
-    assert "train/filter_groups/avg@2" in rb.metrics or any(k.startswith("train/filter_groups") for k in rb.metrics)
+    assert "train/filter_groups/avg@n" in rb.metrics and "train/filter_groups/passrate/zero" in rb.metrics
 
 
 def test_replay_buffer_restore_keeps_sealed_sessions():
@@ -158,3 +158,14 @@ def test_metrics_log_writes_tensorboard_events(tmp_path, monkeypatch):
     log(2, {"actor/pg_loss": 0.25, "note": "text"})
     files = glob.glob(str(tmp_path / "tensorboard" / "events.out.tfevents.*"))
     assert files and sum(os.path.getsize(f) for f in files) > 0
+
+
+def test_pass_rate_metrics_of_judged_groups():
+    """Groups with pass rates 1, 0 and three times 0.5: avg@n one half, a fifth of the groups unsolved, a fifth solved."""
+    import torch
+
+    from pear_b200.train import grpo
+
+    m = grpo.pass_rate_metrics(torch.tensor([[1.0, 1.0], [0.0, 0.0], [0.0, 1.0], [0.0, 1.0], [0.0, 1.0]]), "validation/filter_groups")
+    assert m["validation/filter_groups/avg@n"] == pytest.approx(0.5)
+    assert m["validation/filter_groups/passrate/zero"] == pytest.approx(1 / 5) and m["validation/filter_groups/passrate/one"] == pytest.approx(1 / 5)
