@@ -57,7 +57,12 @@ class SyntheticEnv(BaseEnv):
         self.target = int(self.rng.integers(0, 10))
         self.cursor = int(self.rng.integers(0, 10))
         self.t = 0
-        return self._observe()
+        first = self._observe()
+        # said once, in the system prompt of the episode: what the cameras show and what is to be done
+        first["environment"] = [f"{cam}: a synthetic camera; its picture changes only when the cursor moves" for cam in self.cameras] + [
+            "the episode ends by itself when you submit or when the horizon is reached"]
+        first["task"] = f"{self.task}: move the cursor until the distance is 0, then submit"
+        return first
 
     def step(self, action: dict) -> tuple[dict, bool, bool, dict]:
         self.t += 1

@@ -40,7 +40,24 @@ def render_observation(result: dict) -> Observation:
     lines = [json.dumps(obs["state"], sort_keys=True), obs.get("reminder", "")]
     cameras = sorted(obs.get("frames", {}))
     frames = [np.asarray(obs["frames"][cam]) for cam in cameras]
-    return Observation("\n".join(lines), frames, cameras, bool(result.get("done")), bool(result.get("success")), dict(result.get("info", {})))
+    info = dict(result.get("info", {}))
+    for key in ("environment", "task"):  # what the family says about itself once, for the system prompt of the episode
+        if key in obs:
+            info[key] = obs[key]
+    return Observation("\n".join(lines), frames, cameras, bool(result.get("done")), bool(result.get("success")), info)
+
+
+def episode_system_prompt(base: str, first: Observation) -> str:
+    """The system prompt of one episode: the general instructions, then what the environment family says about itself (one line
+    per camera or rule) and the task of this episode, as sections of their own (upstream's prompts end with ``## ENVIRONMENT`` and
+    ``## TASK``: tests/agent_loop/prompt_renderings/*.txt)."""
+    parts = [base.rstrip("\n")]
+    env_lines = first.info.get("environment")
+    if env_lines:
+        parts.append("## ENVIRONMENT\n\n" + "\n".join(f"- {line}" for line in env_lines))
+    if first.info.get("task"):
+        parts.append("## TASK\n\n" + str(first.info["task"]))
+    return "\n\n".join(parts) + "\n"
 
 
 class EnvTool:

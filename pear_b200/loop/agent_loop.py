@@ -23,7 +23,7 @@ from typing import Optional
 import numpy as np
 import torch
 
-from ..envs.tool import EnvTool, Observation, load_system_prompt
+from ..envs.tool import EnvTool, Observation, episode_system_prompt, load_system_prompt
 from ..rollout.engine import FinishReason, SamplingParams
 from ..sim.env import EpisodeLost
 from ..sim.server import ServerPool
@@ -85,7 +85,7 @@ class AgentLoop:
     def _append_user_turn(self, ep: Episode, obs: Observation, first: bool) -> None:
         ids: list[int] = []
         if first:
-            ids += self.tok.render_turn("system", self.system_prompt)
+            ids += self.tok.render_turn("system", episode_system_prompt(self.system_prompt, obs))
         pixels = [f if (f.ndim == 3 and f.dtype == np.uint8) else None for f in obs.frames]
         if self.cfg.picture_positions == "checkpoint":
             if self.vision is None or any(p is None for p in pixels):

@@ -167,18 +167,22 @@ def test_first_turn_prompt_rendering_is_the_stored_text():
 
     import numpy as np
 
-    from pear_b200.envs.tool import load_system_prompt, render_observation
+    from pear_b200.envs.tool import episode_system_prompt, load_system_prompt, render_observation
 
     tok = ByteTokenizer()
     res = {"observation": {"state": {"gripper": "open", "cube": [0.1, 0.2, 0.0], "step": 3}, "reminder": "Answer with one JSON action in a fenced json block.",
-                           "frames": {"wrist": np.zeros((2, 8)), "front": np.ones((2, 8))}}, "done": False}
+                           "frames": {"wrist": np.zeros((2, 8)), "front": np.ones((2, 8))},
+                           "environment": ["front: a fixed camera above the table", "wrist: a camera on the gripper"], "task": "put the cube in the bowl"},
+           "done": False}
     obs = render_observation(res)
     assert obs.cameras == ["front", "wrist"] and obs.frames[0].sum() == 16  # frames in the cameras' (sorted) order
-    ids = (tok.render_turn("system", load_system_prompt()) + tok.render_turn("user", obs.text, images=2, image_tokens=2, labels=obs.cameras)
+    assert episode_system_prompt("base\n", render_observation({"observation": {"state": {}}})) == "base\n"  # a family that says nothing adds nothing
+    ids = (tok.render_turn("system", episode_system_prompt(load_system_prompt(), obs)) + tok.render_turn("user", obs.text, images=2, image_tokens=2, labels=obs.cameras)
            + tok.generation_prompt())
     with open(os.path.join(os.path.dirname(__file__), "golden", "first_turn_prompt.txt")) as f:
         assert tok.decode(ids) == f.read()
     text = tok.decode(ids)
+    assert text.index("## ENVIRONMENT") < text.index("## TASK") < text.index("put the cube in the bowl") < text.index("<|im_start|>user")
     assert text.index("[front]") < text.index("<|vision_start|>") < text.index("[wrist]") < text.rindex("<|vision_start|>")
 
 
