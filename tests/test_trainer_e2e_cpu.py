@@ -143,6 +143,7 @@ def test_batch_trained_in_mini_batches(tmp_path):
 def test_vision_tower_trains_under_the_policy_loss_and_the_agent_loop_follows_it(tmp_path):
     fam = {"synthetic": {"env_path": "pear_b200.envs.synthetic.SyntheticEnv", "num_processes": 2, "env_kwargs": {"pixels": 16}}}
     cfg = _cfg(str(tmp_path / "run"), ["actor_rollout_ref.model.vision.enable=true", "actor_rollout_ref.model.vision.train=true",
+                                        "data.train_batch_size=3", "actor_rollout_ref.rollout.n=4",  # (a step of uniform-reward groups only would have no gradient)
                                         "trainer.total_training_steps=1", "trainer.save_freq=1", "actor_rollout_ref.rollout.multi_turn.synthetic_turns=1",
                                         "actor_rollout_ref.rollout.multi_turn.synthetic_reward=hash"])
     trainer, close = build_stack(cfg, env_families=fam)
@@ -172,6 +173,7 @@ def test_checkpoint_picture_positions_in_rollout_and_training(tmp_path):
     fam = {"synthetic": {"env_path": "pear_b200.envs.synthetic.SyntheticEnv", "num_processes": 2, "env_kwargs": {"pixels": 16, "cameras": ("front", "wrist")}}}
     cfg = _cfg(str(tmp_path / "run"), ["actor_rollout_ref.model.vision.enable=true", "actor_rollout_ref.model.vision.preset=family_tiny",
                                         "actor_rollout_ref.model.vision.train=true", "actor_rollout_ref.rollout.picture_positions=checkpoint",
+                                        "data.train_batch_size=3", "actor_rollout_ref.rollout.n=4",  # (a step of uniform-reward groups only would have no gradient)
                                         "trainer.total_training_steps=1", "trainer.save_freq=0", "actor_rollout_ref.rollout.multi_turn.synthetic_turns=2",
                                         "actor_rollout_ref.rollout.multi_turn.synthetic_reward=hash"])
     trainer, close = build_stack(cfg, env_families=fam)
@@ -189,7 +191,9 @@ def test_checkpoint_picture_positions_in_rollout_and_training(tmp_path):
         assert len(hist) == 1 and np.isfinite(hist[0]["actor/grad_norm"]) and hist[0]["actor/grad_norm"] > 0
         tr = seen[0]
         pos = tr["position_ids"]
-        assert pos.shape == (3, len(tr["tokens"])) and len(tr["images"]) == 4  # two cameras, two turns
+        tr = max(seen, key=lambda t: len(t["images"]))
+        pos = tr["position_ids"]
+        assert pos.shape == (3, len(tr["tokens"])) and len(tr["images"]) >= 4 and len(tr["images"]) % 2 == 0  # two cameras a turn
         first = tr["images"][0][0]
         n_tok = 4  # 16 x 16 pixels, patch 4, merge 2: a 2 x 2 block
         assert pos[0, first:first + n_tok].tolist() == [pos[0, first]] * n_tok and pos[1, first:first + n_tok].tolist() == [pos[1, first] + d for d in (0, 0, 1, 1)]
