@@ -148,7 +148,7 @@ def test_two_nodes_on_loopback_addresses(tmp_path):
     common = [sys.executable, "-m", "pear_b200.launch.launch", "training", "--node-addrs", "127.0.0.1,127.0.0.2", "--trainer-nodes", "1", "--gpus", "2",
               "--rollout-tp", "2", "--master-port", str(master), "--replica-master-port", str(replica_master), "--rollout-port", str(rollout),
               "--env-port", str(envp), "--sync-port", str(sync), f"run_dir={run}", "actor_rollout_ref.model.path=preset:tiny",
-              "trainer.total_training_steps=1", "trainer.save_freq=0", "data.train_batch_size=2", "actor_rollout_ref.rollout.n=4", "data.max_response_length=32",
+              "trainer.total_training_steps=1", "trainer.save_freq=0", "data.train_batch_size=3", "actor_rollout_ref.rollout.n=4", "data.max_response_length=32",
               "actor_rollout_ref.actor.fsdp_config.ulysses_sequence_parallel_size=2", "actor_rollout_ref.rollout.multi_turn.synthetic_turns=1",
               "actor_rollout_ref.rollout.multi_turn.synthetic_reward=hash", "actor_rollout_ref.rollout.max_model_len=2048",
               "actor_rollout_ref.rollout.max_num_seqs=8", "actor_rollout_ref.actor.ppo_max_token_len_per_gpu=8192", "trainer.logger=[file]"]

@@ -191,7 +191,7 @@ def test_training_entry_starts_from_a_multimodal_checkpoint_directory(tmp_path):
     d.mkdir()
     model_io.save_safetensors(str(d / "model.safetensors"), {k: p.contiguous() for k, p in hf.state_dict().items()})
     (d / "config.json").write_text(json.dumps(c.to_dict(), default=str))
-    cfg = RunConfig(compose("training", [f"run_dir={tmp_path / 'run'}", f"actor_rollout_ref.model.path={d}", "data.train_batch_size=2", "actor_rollout_ref.rollout.n=2",
+    cfg = RunConfig(compose("training", [f"run_dir={tmp_path / 'run'}", f"actor_rollout_ref.model.path={d}", "data.train_batch_size=3", "actor_rollout_ref.rollout.n=4",
                                          "data.max_response_length=16", "actor_rollout_ref.rollout.max_model_len=2048", "actor_rollout_ref.rollout.max_num_seqs=8",
                                          "actor_rollout_ref.rollout.agent.num_workers=2", "actor_rollout_ref.rollout.topk_log_probs=4", "algorithm.filter_groups.enable=false",
                                          "trainer.total_training_steps=1", "trainer.save_freq=0", "transfer_queue.num_data_storage_units=4",
