@@ -95,10 +95,8 @@ class AgentLoop:
             obs.frames = self.vision.encode(obs.frames)
         elif any(f.ndim != 2 for f in obs.frames):
             raise ValueError("the environment delivers pixels: the agent loop needs a vision encoder (AgentLoopManager(vision=...))")
-        if len({f.shape[0] for f in obs.frames}) > 1:
-            raise ValueError(f"pictures of one observation must take the same number of tokens, got {[f.shape[0] for f in obs.frames]}")
-        n_img_tokens = obs.frames[0].shape[0] if obs.frames else 0
-        turn = self.tok.render_turn("user", obs.text, images=len(obs.frames), image_tokens=n_img_tokens, labels=obs.cameras or None)
+        counts = [int(f.shape[0]) for f in obs.frames]  # cameras of different sizes give blocks of different lengths
+        turn = self.tok.render_turn("user", obs.text, images=len(obs.frames), image_tokens=counts, labels=obs.cameras or None)
         base = len(ep.tokens) + len(ids)
         # positions of the image pad runs inside the turn -> embedding blocks
         j, f = 0, 0
@@ -107,7 +105,7 @@ class AgentLoop:
                 ep.embeds.append((base + j, np.asarray(obs.frames[f], dtype=np.float32)))
                 if pixels[f] is not None:  # a trainer with the tower in its graph recomputes this block from the picture
                     ep.images.append((base + j, pixels[f]))
-                j += n_img_tokens
+                j += counts[f]
                 f += 1
             else:
                 j += 1

@@ -325,3 +325,24 @@ def test_answer_parsing_cases_of_the_family():
     with pytest.raises(ParseError, match="invalid json"):
         extract_action('</think>```json\n{"x": }\n```')
     assert extract_action(f"plain ```json\n{action}\n```") == {"x": 1.5}
+
+
+def test_cameras_of_different_sizes_take_their_own_block_lengths():
+    """One observation, two cameras with pictures of different sizes: each block sits at its own run of placeholders."""
+    from pear_b200.envs.tool import Observation
+    from pear_b200.loop.episode import Episode
+    from pear_b200.loop.vision_encoder import VisionEncoder
+    from pear_b200.models.vision import FamilyVisionConfig, FamilyVisionTower
+
+    tok = ByteTokenizer()
+    enc = VisionEncoder(FamilyVisionTower(FamilyVisionConfig.tiny(out_hidden=8)).init_weights(0))
+    loop = AgentLoop(None, None, tok, AgentLoopConfig(picture_positions="checkpoint"), {}, vision=enc)
+    rng = np.random.default_rng(0)
+    obs = Observation("state", [rng.integers(0, 256, (16, 24, 3), dtype=np.uint8), rng.integers(0, 256, (32, 8, 3), dtype=np.uint8)], ["front", "wrist"])
+    ep = Episode(uid="u", session="0", family="f", env_args={})
+    loop._append_user_turn(ep, obs, first=True)
+    (p0, b0), (p1, b1) = ep.embeds
+    assert b0.shape == (6, 8) and b1.shape == (4, 8) and ep.grids == [(2, 3), (4, 1)]
+    assert all(t == tok.image_pad_id for t in ep.tokens[p0:p0 + 6]) and all(t == tok.image_pad_id for t in ep.tokens[p1:p1 + 4]) and p1 > p0 + 6
+    pos = loop._positions(ep)
+    assert pos.shape == (3, len(ep.tokens)) and pos[1, p1:p1 + 4].tolist() == [int(pos[0, p1]) + d for d in range(4)]  # a 4 x 1 block: rows advance
