@@ -314,3 +314,46 @@ def test_picture_patches_and_sizes_equal_the_family_image_processor():
     for h, w in ((37, 50), (9, 11), (100, 70), (16, 16), (64, 200)):
         grid = resizing(images=[rng.integers(0, 256, (h, w, 3), dtype=np.uint8)], return_tensors="pt")["image_grid_thw"][0].tolist()
         assert picture_size(h, w, 8, 256, 2048) == (grid[1] * 4, grid[2] * 4), (h, w, grid)
+
+
+def _tp_rank_fn(rank, world, hf_dir, out_dir):
+    import torch.distributed as dist
+
+    from pear_b200.models import hybrid
+    from pear_b200.parallel.tensor_parallel import shard_state, tp_config
+    from pear_b200.rollout.engine import EngineConfig, RolloutEngine, SamplingParams
+
+    cfg = model_io.load_config(hf_dir)
+    full = HybridForCausalLM(cfg, with_mtp=False)
+    model_io.load_model_dir(hf_dir, full)
+    tp = HybridForCausalLM(tp_config(cfg, world), with_mtp=False)
+    tp.load_state_dict(shard_state(full.state_dict(), cfg, rank, world), strict=True)
+    hybrid.set_tensor_parallel_group(dist.group.WORLD)
+    try:
+        g = torch.Generator().manual_seed(5)
+        prompts = [torch.randint(0, 512, (n,), generator=g).tolist() for n in (19, 33)]
+        outs = RolloutEngine(tp, EngineConfig(num_blocks=64, max_num_seqs=4)).generate(prompts, SamplingParams(max_tokens=10, temperature=0.0))
+    finally:
+        hybrid.set_tensor_parallel_group(None)
+    if rank == 0:
+        torch.save({"prompts": prompts, "outputs": [r.output for r in outs]}, out_dir + "/tp.pt")
+
+
+def test_tensor_parallel_shards_of_a_transformers_checkpoint_generate_the_same(tmp_path):
+    """The sharding rules on the family's real tensor layouts (per-head [q | gate] rows of q_proj, the q | k | v sections of the
+    linear-attention projection and its convolution, vocabulary-parallel head): two ranks with half of every projection each
+    continue as transformers does with the whole model."""
+    import os
+    import sys
+
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from dist_utils import run_ranks
+
+    hf = _hf_model(4)
+    hf.save_pretrained(str(tmp_path / "hf"), safe_serialization=True)
+    run_ranks(_tp_rank_fn, 2, tmp_path, str(tmp_path / "hf"), str(tmp_path))
+    got = torch.load(str(tmp_path / "tp.pt"))
+    for p, out in zip(got["prompts"], got["outputs"]):
+        with torch.no_grad():
+            want = hf.generate(torch.tensor([p]), max_new_tokens=10, do_sample=False, pad_token_id=0)[0, len(p):].tolist()
+        assert out == want
