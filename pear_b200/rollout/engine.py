@@ -641,8 +641,7 @@ class RolloutEngine:
             if len(req.output) >= p.max_tokens:
                 self._finish(req, FinishReason.LENGTH)
                 return
-        # (a request with its own positions does not draft: the drafter's passes count positions from the row's start)
-        req.drafts = self._draft(req, row, resid, acc, new) if (self.spec > 0 and req.position_ids is None) else []
+        req.drafts = self._draft(req, row, resid, acc, new) if self.spec > 0 else []
 
     def _fill_drafter_kv(self, req: Request, row: StepRow, x_rows: torch.Tensor) -> None:
         """The drafter's KV of a prefill chunk: position p of the prompt pairs the main model's residual at p with the
@@ -654,7 +653,7 @@ class RolloutEngine:
         if m <= 0:
             return
         nxt = torch.tensor(toks[row.start + 1 : row.start + 1 + m], dtype=torch.long)
-        self.runner.mtp_forward(StepRow(req.seq, nxt, row.start, req.block_table, 0), nxt, x_rows[:m])
+        self.runner.mtp_forward(StepRow(req.seq, nxt, row.start, req.block_table, 0, positions=self._row_positions(req, row.start, m)), nxt, x_rows[:m])
 
     def _draft(self, req: Request, row: StepRow, resid: torch.Tensor, acc: int, new: list[int]) -> list[int]:
         """MTP drafts for the next step: first a pass over the rows committed in this step (it fills the drafter's KV
@@ -663,7 +662,7 @@ class RolloutEngine:
         n_commit = acc + 1
         first = req.computed - n_commit  # position of the first committed row
         nxt = torch.tensor(toks[first + 1 : first + 1 + n_commit], dtype=torch.long)
-        sub = StepRow(req.seq, nxt, first, req.block_table, 0)
+        sub = StepRow(req.seq, nxt, first, req.block_table, 0, positions=self._row_positions(req, first, n_commit))
         if not self._ensure_blocks(req, req.computed + self.spec + 1):
             return []
         logits, r = self.runner.mtp_forward(sub, nxt, resid[:n_commit] if resid.shape[0] >= n_commit else resid[-1:].expand(n_commit, -1))
@@ -671,7 +670,7 @@ class RolloutEngine:
         hidden = r[-1:]
         for j in range(1, self.spec):
             pos = req.computed + j - 1
-            sub = StepRow(req.seq, torch.tensor(drafts[-1:]), pos, req.block_table, 0)
+            sub = StepRow(req.seq, torch.tensor(drafts[-1:]), pos, req.block_table, 0, positions=self._row_positions(req, pos, 1))
             logits, hidden = self.runner.mtp_forward(sub, torch.tensor(drafts[-1:]), hidden)
             drafts.append(int(logits[-1].argmax()))
         return drafts

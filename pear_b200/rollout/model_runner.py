@@ -320,13 +320,14 @@ class ModelRunner:
     # -- MTP drafter ----------------------------------------------------------------------------------------------------
     @torch.no_grad()
     def mtp_forward(self, row: StepRow, next_tokens: torch.Tensor, residual: torch.Tensor):
-        """One MTP pass over rows at positions row.start.. combining ``residual[j]`` with ``embed(next_tokens[j])``;
-        writes the drafter's KV pages and returns (logits, the drafter's output residual)."""
+        """One MTP pass over rows at positions row.start.. (``row.positions`` when the request carries its own) combining
+        ``residual[j]`` with ``embed(next_tokens[j])``; writes the drafter's KV pages and returns (logits, the drafter's output
+        residual)."""
         model, mtp = self.model, self.model.mtp
         from ..models.hybrid import SeqMeta
 
         n = next_tokens.shape[0]
-        pos = torch.arange(row.start, row.start + n, device=self.device)
+        pos = row.positions.to(self.device) if row.positions is not None else torch.arange(row.start, row.start + n, device=self.device)
         cos, sin = model.rope(pos)
         x = torch.cat([mtp.pre_fc_norm_embedding(model.model.embed_tokens(next_tokens.to(self.device)).float()),
                        mtp.pre_fc_norm_hidden(residual)], dim=-1)

@@ -214,15 +214,14 @@ def test_training_entry_starts_from_a_multimodal_checkpoint_directory(tmp_path):
         close()
 
 
-def test_rollout_engine_with_pictures_and_checkpoint_positions_equals_generate(tmp_path):
-    """A prompt with a picture through the rollout engine (rows at the placeholders, the checkpoint's (t, h, w) positions, decode
-    positions continuing past the picture) gives transformers' greedy continuation of the same multi-modal input."""
+def _picture_case(tmp_path, with_mtp: bool = False):
+    """A small multi-modal transformers model saved as a checkpoint directory, this framework's model loaded from it, and one
+    prompt with a picture: (hf, mine, cfg, ids, mask, emb, vec, gh, gw)."""
     import json
 
     from transformers import Qwen3_5Config, Qwen3_5ForConditionalGeneration
 
-    from pear_b200.models.hybrid import mrope_positions
-    from pear_b200.rollout.engine import EngineConfig, RolloutEngine, SamplingParams
+    from pear_b200.models.config import HybridConfig
 
     c = Qwen3_5Config()
     t, v = c.text_config, c.vision_config
@@ -243,8 +242,13 @@ def test_rollout_engine_with_pictures_and_checkpoint_positions_equals_generate(t
     model_io.save_safetensors(str(d / "model.safetensors"), {k: p.contiguous() for k, p in hf.state_dict().items()})
     (d / "config.json").write_text(json.dumps(c.to_dict(), default=str))
     cfg, vcfg = model_io.load_config(str(d)), model_io.load_vision_config(str(d))
-    mine = HybridForCausalLM(cfg, with_mtp=False, vision=vcfg)
-    model_io.load_model_dir(str(d), mine, ignore_unexpected=())
+    if with_mtp:  # the checkpoint has no drafter: a random one proposes, the main model verifies
+        cfg = HybridConfig.from_dict({**cfg.to_dict(), "num_mtp_layers": 1})
+        mine = HybridForCausalLM(cfg, with_mtp=True, vision=vcfg).init_weights(11)
+        model_io.load_model_dir(str(d), mine, allow_missing=("mtp.",), ignore_unexpected=())
+    else:
+        mine = HybridForCausalLM(cfg, with_mtp=False, vision=vcfg)
+        model_io.load_model_dir(str(d), mine, ignore_unexpected=())
     g = torch.Generator().manual_seed(1)
     img = torch.rand(3, 16, 24, generator=g) * 2 - 1
     vec, gh, gw = mine.visual.patches(img)
@@ -253,6 +257,17 @@ def test_rollout_engine_with_pictures_and_checkpoint_positions_equals_generate(t
     with torch.no_grad():
         emb = torch.zeros(len(ids), cfg.hidden_size)
         emb[mask] = mine.visual([img])[0]
+    return hf, mine, cfg, ids, mask, emb, vec, gh, gw
+
+
+def test_rollout_engine_with_pictures_and_checkpoint_positions_equals_generate(tmp_path):
+    """A prompt with a picture through the rollout engine (rows at the placeholders, the checkpoint's (t, h, w) positions, decode
+    positions continuing past the picture) gives transformers' greedy continuation of the same multi-modal input."""
+    from pear_b200.models.hybrid import mrope_positions
+    from pear_b200.rollout.engine import EngineConfig, RolloutEngine, SamplingParams
+
+    hf, mine, cfg, ids, mask, emb, vec, gh, gw = _picture_case(tmp_path)
+    with torch.no_grad():
         want = hf.generate(input_ids=ids[None], pixel_values=vec, image_grid_thw=torch.tensor([[1, gh, gw]]), mm_token_type_ids=mask.int()[None],
                            max_new_tokens=8, do_sample=False, pad_token_id=0)[0, len(ids):].tolist()
     eng = RolloutEngine(mine, EngineConfig(num_blocks=64, max_num_seqs=2, max_num_batched_tokens=16))  # (prefill in chunks: positions per chunk)
@@ -265,6 +280,24 @@ def test_rollout_engine_with_pictures_and_checkpoint_positions_equals_generate(t
     while eng.has_work():
         eng.step()
     assert len(plain.output) == 8
+
+
+def test_speculative_decoding_of_a_picture_prompt_with_checkpoint_positions_equals_generate(tmp_path):
+    """The drafter runs at the request's own positions too: a picture prompt under the checkpoint's position rule, three drafts a
+    step from a (random) MTP module, still continues as transformers' ``generate`` does."""
+    from pear_b200.models.hybrid import mrope_positions
+    from pear_b200.rollout.engine import EngineConfig, RolloutEngine, SamplingParams
+
+    hf, mine, cfg, ids, mask, emb, vec, gh, gw = _picture_case(tmp_path, with_mtp=True)
+    with torch.no_grad():
+        want = hf.generate(input_ids=ids[None], pixel_values=vec, image_grid_thw=torch.tensor([[1, gh, gw]]), mm_token_type_ids=mask.int()[None],
+                           max_new_tokens=12, do_sample=False, pad_token_id=0)[0, len(ids):].tolist()
+    eng = RolloutEngine(mine, EngineConfig(num_blocks=64, max_num_seqs=2, max_num_batched_tokens=16, num_speculative_tokens=3))
+    req = eng.add_request(ids.tolist(), SamplingParams(max_tokens=12, temperature=0.0), embeds=emb, embeds_mask=mask,
+                          position_ids=mrope_positions(ids, [(gh, gw)], image_pad_id=500))
+    while eng.has_work():
+        eng.step()
+    assert req.output == want and eng.metrics["spec_drafted"] > 0
 
 
 def test_speculative_decoding_and_a_cached_second_turn_stay_equal_to_generate(tmp_path):
