@@ -152,8 +152,9 @@ class RolloutServer:
         self.thread.join(timeout=10)
 
     # -- HTTP ---------------------------------------------------------------------------------------------------------
-    def http_app(self, tokenizer=None):
-        """FastAPI application: POST /v1/completions (token ids or text), GET /metrics, POST /pause /resume."""
+    def http_app(self, tokenizer=None, vision=None, max_model_len: Optional[int] = None):
+        """FastAPI application: POST /v1/completions (token ids or text), /v1/chat/completions, the Messages routes of
+        ``messages_api.py`` (``vision``: the encoder of their image blocks), GET /metrics, POST /pause /resume."""
         from fastapi import FastAPI
         from fastapi.responses import PlainTextResponse
 
@@ -234,6 +235,9 @@ class RolloutServer:
             self.resume()
             return {"ok": True}
 
+        from . import messages_api
+
+        messages_api.register(app, self, tokenizer, vision, max_model_len)
         return app
 
 

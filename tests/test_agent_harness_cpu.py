@@ -1,0 +1,399 @@
+"""The agent harness (session service + upstream proxy) with the scripted agent as its agent process, against a scripted model
+server and against a real (tiny, CPU) rollout replica's Messages routes."""
+
+import asyncio
+import base64
+import io
+import json
+import os
+import sys
+import uuid
+
+import pytest
+
+aiohttp = pytest.importorskip("aiohttp")
+from aiohttp import web  # noqa: E402
+
+from pear_b200.deploy.harness.proxy import EngineMetrics, RequestAudit, UpstreamProxy  # noqa: E402
+from pear_b200.deploy.harness.service import SessionService  # noqa: E402
+
+AGENT = [sys.executable, "-m", "pear_b200.deploy.harness.scripted_agent"]
+ENV = {"PATH": os.environ.get("PATH", ""), "PYTHONPATH": os.path.dirname(os.path.dirname(os.path.abspath(__file__)))}
+
+
+def jpeg(color=(200, 30, 30), size=(32, 24)) -> str:
+    from PIL import Image
+
+    buf = io.BytesIO()
+    Image.new("RGB", size, color).save(buf, "JPEG")
+    return base64.b64encode(buf.getvalue()).decode()
+
+
+class ScriptedUpstream:
+    """A model server with the three Messages routes whose answers the test scripts."""
+
+    def __init__(self, limit=2000):
+        self.limit, self.seen, self.answers, self.delay_on, self.dropped = limit, [], [], None, 0
+
+    @staticmethod
+    def tokens(body) -> int:
+        n = len(str(body.get("system") or "")) // 4
+        for m in body.get("messages", []):
+            for b in UpstreamProxy.blocks(m.get("content")):
+                n += len(b.get("text", "")) // 4 if b.get("type") == "text" else 100
+        return n
+
+    async def start(self):
+        app = web.Application(client_max_size=1 << 28)
+        app.router.add_get("/v1/models", lambda r: web.json_response({"data": [{"id": "m", "max_model_len": self.limit}]}))
+        app.router.add_get("/health", lambda r: web.json_response({"ok": True}))
+        app.router.add_get("/metrics", lambda r: web.Response(text='# TYPE pear_num_running gauge\npear_num_running{replica="m"} 1.0\npear_other 3\n'))
+        app.router.add_post("/v1/messages/count_tokens", self.count)
+        app.router.add_post("/v1/messages", self.messages)
+        self.runner = web.AppRunner(app, handler_cancellation=True)
+        await self.runner.setup()
+        site = web.TCPSite(self.runner, "127.0.0.1", 0)
+        await site.start()
+        self.url = f"http://127.0.0.1:{self.runner.addresses[0][1]}"
+        return self
+
+    async def count(self, request):
+        return web.json_response({"input_tokens": self.tokens(await request.json())})
+
+    async def messages(self, request):
+        body = await request.json()
+        self.seen.append(body)
+        flat = json.dumps(body["messages"])
+        if self.delay_on and self.delay_on in flat:
+            try:
+                await asyncio.sleep(30)
+            except asyncio.CancelledError:
+                self.dropped += 1
+                raise
+        if self.answers:
+            text, stop = self.answers.pop(0)
+        elif "about to be replaced by your summary" in flat:
+            text, stop = "<summary>the robot moved the cup</summary>", "end_turn"
+        else:
+            text, stop = f"answer {len(self.seen)}", "end_turn"
+        usage = {"input_tokens": self.tokens(body) - 5, "cache_read_input_tokens": 5, "cache_creation_input_tokens": 0, "output_tokens": len(text) // 4 + 1}
+        msg = {"id": "msg_1", "type": "message", "role": "assistant", "content": [{"type": "text", "text": text}], "stop_reason": stop, "usage": usage}
+        if not body.get("stream"):
+            return web.json_response(msg)
+        from pear_b200.rollout.messages_api import MessagesFrontend
+
+        resp = web.StreamResponse(headers={"Content-Type": "text/event-stream"})
+        await resp.prepare(request)
+        for frame in MessagesFrontend.events(msg):
+            await resp.write(frame)
+        await resp.write_eof()
+        return resp
+
+
+class Harness:
+    def __init__(self, upstream_url, tmp_path, env=None, command=AGENT, **kw):
+        self.svc = SessionService(upstream_url, "m", command, audit_dir=str(tmp_path / "audit"), agent_env={**ENV, **(env or {})}, **kw)
+
+    async def __aenter__(self):
+        self.runner = web.AppRunner(self.svc.app(), handler_cancellation=True)
+        await self.runner.setup()
+        site = web.TCPSite(self.runner, "127.0.0.1", 0)
+        await site.start()
+        self.url = f"http://127.0.0.1:{self.runner.addresses[0][1]}"
+        self.http = aiohttp.ClientSession()
+        return self
+
+    async def __aexit__(self, *exc):
+        await self.http.close()
+        await self.runner.cleanup()
+
+    async def open(self, system="You drive a robot arm.", model="m"):
+        sid = str(uuid.uuid4())
+        async with self.http.post(self.url + "/sessions", json={"session_id": sid, "model": model, "system": system}) as r:
+            return sid, r.status
+
+    async def turn(self, sid, text, images=(), references=(), turn_id=None):
+        body = {"turn_id": turn_id or str(uuid.uuid4()), "text": text, "images": list(images), "reference_images": list(references)}
+        async with self.http.post(f"{self.url}/sessions/{sid}/turns", json=body) as r:
+            if r.status != 200:
+                return r.status, await r.text()
+            return 200, [json.loads(line) async for line in r.content if line.strip()]
+
+
+def _short_instruction(tmp_path) -> str:
+    """A deployment's own compaction instruction, short enough for the tests' small contexts."""
+    path = tmp_path / "summary.md"
+    path.write_text("CRITICAL: Respond with TEXT ONLY. The conversation is about to be replaced by your summary: <summary>...</summary>")
+    return str(path)
+
+
+def run(coro):
+    return asyncio.run(asyncio.wait_for(coro, 120))
+
+
+@pytest.mark.parametrize("stream", ["0", "1"])
+def test_a_turn_reaches_the_model_server_rewritten_sized_and_recorded(tmp_path, stream):
+    async def go():
+        up = await ScriptedUpstream().start()
+        async with Harness(up.url, tmp_path, env={"SCRIPTED_AGENT_STREAM": stream}, chat_template_kwargs={"enable_thinking": False}) as h:
+            async with h.http.get(h.url + "/health") as r:
+                health = await r.json()
+            assert health["status"] == "ok" and health["context_limit"] == 2000 and health["capabilities"]["reference_images"]
+            sid, status = await h.open()
+            assert status == 200
+            cam, ref = jpeg(), jpeg((10, 200, 10))
+            status, events = await h.turn(sid, "Pick up the cup.", images=[{"role": "wrist", "data": cam}], references=[{"data": ref}])
+            assert status == 200 and events[-1]["type"] == "result" and events[-1]["text"] == "answer 1" and not events[-1]["is_error"]
+            kinds = [e["type"] for e in events]
+            assert "text" in kinds and "usage" in kinds and kinds.index("text") < kinds.index("result")
+            usage = events[-1]["usage"]
+            assert usage["requests"] == 1 and usage["cached_tokens"] == 5 and usage["context_tokens"] == up.tokens(up.seen[0]) and usage["is_final"]
+            assert usage["engine"] == {"num_running": 1.0}  # (only the kept gauges of the model server's /metrics)
+            sent = up.seen[0]
+            assert sent["system"] == "You drive a robot arm." and sent["metadata"]["user_id"] == sid and sent["chat_template_kwargs"] == {"enable_thinking": False}
+            blocks = sent["messages"][0]["content"]
+            assert [b["type"] for b in blocks] == ["image", "text", "text", "image"]  # the task's picture, the text, the label, the camera
+            assert blocks[0]["source"]["data"] == ref and blocks[2]["text"] == "[wrist]" and blocks[3]["source"]["data"] == cam
+            assert sent["max_tokens"] == 2000 - up.tokens(sent) and bool(sent.get("stream")) == (stream == "1")
+            assert "temperature" not in sent  # sampling is the server's
+            # the second turn: the first turn's picture is put back into the history the agent sends
+            status, events = await h.turn(sid, "Now the plate.", images=[{"role": "wrist", "data": jpeg((1, 2, 3))}])
+            assert status == 200 and events[-1]["text"] == "answer 2"
+            second = up.seen[1]["messages"]
+            assert len(second) == 3 and second[0]["content"][3]["source"]["data"] == cam and second[1]["role"] == "assistant"
+            # the record: one line a request, pictures as digests
+            lines = [json.loads(x) for x in open(tmp_path / "audit" / f"{sid}.jsonl")]
+            assert [x["kind"] for x in lines] == ["main", "main"] and lines[0]["outcome"]["status"] == 200
+            assert cam not in json.dumps(lines) and "data_sha256" in json.dumps(lines[0]["upstream_request"])
+            placeholder = lines[0]["agent_request"]["messages"][0]["content"][2]["text"]
+            assert placeholder.startswith("[camera image ") and lines[0]["agent_request"]["system"] == "You are a scripted agent."
+            async with h.http.delete(f"{h.url}/sessions/{sid}") as r:
+                assert (await r.json())["closed"]
+            status, _ = await h.turn(sid, "again")
+            assert status == 410
+        await up.runner.cleanup()
+
+    run(go())
+
+
+def test_a_full_context_is_compacted_with_the_deployments_instruction_and_without_the_last_pictures(tmp_path):
+    async def go():
+        up = await ScriptedUpstream(limit=480).start()
+        async with Harness(up.url, tmp_path, summary_prompt=_short_instruction(tmp_path)) as h:
+            sid, _ = await h.open(system="S" * 40)
+            notes, results = [], []
+            for i in range(4):  # each turn adds about 130 tokens (a picture counts 100): the fourth finds no room
+                status, events = await h.turn(sid, f"step {i} " + "x" * 80, images=[{"role": "top", "data": jpeg((i, i, i))}])
+                assert status == 200
+                notes += [e for e in events if e["type"] == "note" and e.get("subtype") == "compact_boundary"]
+                results.append(events[-1])
+            assert len(notes) == 1 and all(not r["is_error"] for r in results) and results[-1]["usage"]["compactions"] == 1
+            summaries = [b for b in up.seen if "about to be replaced by your summary" in json.dumps(b["messages"])]
+            assert len(summaries) == 1
+            last = summaries[0]["messages"][-1]["content"]
+            assert [b["type"] for b in last] == ["text", "text"] and "CRITICAL" in last[1]["text"] and "Summarise the conversation so far" not in last[1]["text"]
+            assert any(b["type"] == "image" for m in summaries[0]["messages"][:-1] for b in m["content"] if isinstance(m["content"], list))  # earlier turns keep theirs
+            after = up.seen[-1]["messages"]  # the request after the compaction: the summary, then the turn with its picture
+            assert len(after) == 1 and "the robot moved the cup" in after[0]["content"][0]["text"] and after[0]["content"][-1]["type"] == "image"
+            kinds = [json.loads(x)["kind"] for x in open(tmp_path / "audit" / f"{sid}.jsonl")]
+            assert kinds.count("summary") == 1 and kinds[-1] == "main"
+            too_long = [json.loads(x) for x in open(tmp_path / "audit" / f"{sid}.jsonl") if json.loads(x)["outcome"].get("status") == 400]
+            assert len(too_long) == 1
+        await up.runner.cleanup()
+
+    run(go())
+
+
+def test_a_summary_without_its_closing_tag_is_asked_again_and_a_cut_answer_executes_nothing(tmp_path):
+    async def go():
+        up = await ScriptedUpstream(limit=360).start()
+        async with Harness(up.url, tmp_path, summary_prompt=_short_instruction(tmp_path)) as h:
+            sid, _ = await h.open()
+            for i in range(2):
+                await h.turn(sid, f"step {i} " + "x" * 80, images=[{"role": "top", "data": jpeg((i, i, i))}])
+            up.answers = [("<summary>cut off", "max_tokens")]  # the first summary: no closing tag
+            status, events = await h.turn(sid, "step 2 " + "x" * 80, images=[{"role": "top", "data": jpeg()}])
+            assert status == 200 and not events[-1]["is_error"] and events[-1]["usage"]["compactions"] == 1
+            kinds = [(json.loads(x)["kind"], json.loads(x)["outcome"].get("status")) for x in open(tmp_path / "audit" / f"{sid}.jsonl")]
+            assert ("summary", 500) in kinds and ("summary", 200) in kinds
+            up.answers = [("half an act", "max_tokens")]
+            status, events = await h.turn(sid, "go on")
+            assert events[-1]["is_error"] and events[-1]["stop"] == "refused" and "cut" in events[-1]["message"]
+        await up.runner.cleanup()
+
+    run(go())
+
+
+def test_requests_outside_a_turn_bad_input_and_used_ids_are_refused(tmp_path):
+    async def go():
+        up = await ScriptedUpstream().start()
+        async with Harness(up.url, tmp_path) as h:
+            sid, status = await h.open()
+            assert status == 200
+            async with h.http.post(f"{h.svc.proxy.url}/{sid}/v1/messages", json={"messages": [{"role": "user", "content": "hi"}], "max_tokens": 5}) as r:
+                assert r.status == 409 and r.headers["x-should-retry"] == "false"
+            assert not up.seen
+            async with h.http.post(f"{h.svc.proxy.url}/{sid}/v1/messages/count_tokens", json={"messages": [{"role": "user", "content": "x" * 40}]}) as r:
+                assert (await r.json())["input_tokens"] == 10 + len("You drive a robot arm.") // 4  # counted with the service's system prompt
+            async with h.http.post(h.url + "/sessions", json={"session_id": sid, "model": "m", "system": "s"}) as r:
+                assert r.status == 409
+            async with h.http.post(h.url + "/sessions", json={"session_id": "nope", "model": "m", "system": "s"}) as r:
+                assert r.status == 400
+            async with h.http.post(h.url + "/sessions", json={"session_id": str(uuid.uuid4()), "model": "other", "system": "s"}) as r:
+                assert r.status == 400
+            status, text = await h.turn(sid, "look", images=[{"role": "top", "data": base64.b64encode(b"not a jpeg").decode()}])
+            assert status == 400 and "JPEG" in text
+            status, _ = await h.turn(sid, "look", images=[{"role": "top", "data": jpeg()}, {"role": "top", "data": jpeg()}])
+            assert status == 400
+            status, _ = await h.turn(str(uuid.uuid4()), "look")
+            assert status == 410
+            sid2, status = await h.open()  # a newer session replaces the one that runs; the old id is spent
+            assert status == 200
+            async with h.http.post(h.url + "/sessions", json={"session_id": sid, "model": "m", "system": "s"}) as r:
+                assert r.status == 409
+        await up.runner.cleanup()
+
+    run(go())
+
+
+def test_an_interrupt_drops_the_request_in_flight_and_a_dead_agent_loses_the_session(tmp_path):
+    async def go():
+        up = await ScriptedUpstream().start()
+        up.delay_on = "slow one"
+        async with Harness(up.url, tmp_path) as h:
+            sid, _ = await h.open()
+            tid = str(uuid.uuid4())
+            task = asyncio.ensure_future(h.turn(sid, "slow one", turn_id=tid))
+            while not up.seen:
+                await asyncio.sleep(0.02)
+            status, text = await h.turn(sid, "second at once")
+            assert status == 409  # one turn at a time
+            async with h.http.post(f"{h.url}/sessions/{sid}/turns/{tid}/interrupt") as r:
+                assert (await r.json())["status"] == "stopped"
+            status, events = await task
+            assert events[-1]["stop"] == "interrupted" and up.dropped == 1
+            up.delay_on = None
+            status, events = await h.turn(sid, "fine again")  # the session goes on
+            assert status == 200 and not events[-1]["is_error"]
+        async with Harness(up.url, tmp_path, command=[sys.executable, "-c", "import sys; sys.stdin.readline()"]) as h:
+            sid, status = await h.open()
+            assert status == 200
+            status, events = await h.turn(sid, "anyone there")
+            assert events[-1]["stop"] == "lost" and events[-1]["is_error"]
+            status, _ = await h.turn(sid, "again")
+            assert status == 410
+        async with Harness(up.url, tmp_path, command=["/nonexistent/agent"]) as h:
+            _, status = await h.open()
+            assert status == 503
+        await up.runner.cleanup()
+
+    run(go())
+
+
+def test_audit_digests_and_metrics_parsing():
+    d = RequestAudit.digested({"a": [{"type": "base64", "media_type": "image/jpeg", "data": "QUJD"}], "b": "keep"})
+    assert d["b"] == "keep" and d["a"][0]["data_bytes"] == 4 and "data" not in d["a"][0] and len(d["a"][0]["data_sha256"]) == 64
+    m = EngineMetrics.parse('# TYPE x gauge\npear_num_running{replica="r"} 2.0\npear_cache_hit_rate 0.5\nbroken line x\n')
+    assert m == {"num_running": 2.0, "cache_hit_rate": 0.5}
+
+
+def _tiny_server(with_vision=False):
+    import torch
+
+    from pear_b200.models.config import HybridConfig
+    from pear_b200.models.hybrid import HybridForCausalLM
+    from pear_b200.rollout.engine import EngineConfig
+    from pear_b200.rollout.server import build_server
+    from pear_b200.utils.tokenizer import ByteTokenizer
+
+    cfg = HybridConfig.tiny()
+    model = HybridForCausalLM(cfg, with_mtp=False).init_weights(3)
+    srv = build_server(model, EngineConfig(num_blocks=64, block_size=16, max_num_seqs=4), name="tiny")
+    vision = None
+    if with_vision:
+        from pear_b200.loop.vision_encoder import VisionEncoder
+        from pear_b200.models.vision import VisionConfig, VisionTower
+
+        torch.manual_seed(0)
+        vision = VisionEncoder(VisionTower(VisionConfig.tiny(out_hidden=cfg.hidden_size)), "cpu")
+    return srv, ByteTokenizer(), vision
+
+
+def test_messages_routes_of_a_replica_count_answer_stream_and_refuse_what_does_not_fit():
+    from fastapi.testclient import TestClient
+
+    srv, tok, vision = _tiny_server(with_vision=True)
+    try:
+        client = TestClient(srv.http_app(tok, vision=vision))
+        assert client.get("/v1/models").json()["data"][0] == {"id": "tiny", "object": "model", "max_model_len": 1024}
+        body = {"model": "tiny", "system": "be brief", "messages": [{"role": "user", "content": "hello"}], "max_tokens": 6, "temperature": 0.0}
+        n = client.post("/v1/messages/count_tokens", json=body).json()["input_tokens"]
+        want = len(tok.render_turn("system", "be brief") + tok.render_turn("user", "hello") + tok.generation_prompt())
+        assert n == want
+        out = client.post("/v1/messages", json=body).json()
+        assert out["type"] == "message" and out["role"] == "assistant" and out["content"][0]["type"] == "text" and out["stop_reason"] in ("end_turn", "max_tokens")
+        u = out["usage"]
+        assert u["input_tokens"] + u["cache_read_input_tokens"] == n and 1 <= u["output_tokens"] <= 6
+        again = client.post("/v1/messages", json={**body, "metadata": {"user_id": "s1"}}).json()
+        assert again["content"] == out["content"]  # greedy: the same answer
+        streamed = client.post("/v1/messages", json={**body, "stream": True})
+        assert streamed.headers["content-type"].startswith("text/event-stream")
+        events = [json.loads(line[5:]) for line in streamed.text.splitlines() if line.startswith("data:")]
+        assert [e["type"] for e in events][0] == "message_start" and events[-1]["type"] == "message_stop"
+        text = "".join(e["delta"]["text"] for e in events if e["type"] == "content_block_delta")
+        assert text == out["content"][0]["text"]
+        # a picture: placeholders are counted, rows are computed by the encoder, and the answer differs from the text-only one's prompt
+        with_picture = {**body, "messages": [{"role": "user", "content": [{"type": "text", "text": "hello"},
+                                                                          {"type": "image", "source": {"type": "base64", "media_type": "image/jpeg", "data": jpeg(size=(28, 28))}}]}]}
+        gh, gw = vision.grid(__import__("numpy").zeros((28, 28, 3), dtype="uint8"))
+        assert client.post("/v1/messages/count_tokens", json=with_picture).json()["input_tokens"] == n + gh * gw + 2
+        assert client.post("/v1/messages", json=with_picture).json()["usage"]["output_tokens"] >= 1
+        long = {**body, "messages": [{"role": "user", "content": "x" * 2000}]}
+        r = client.post("/v1/messages", json=long)
+        assert r.status_code == 400 and "prompt is too long" in r.json()["error"]["message"]
+        no_vision = TestClient(srv.http_app(tok))
+        assert no_vision.post("/v1/messages", json=with_picture).status_code == 400
+    finally:
+        srv.close()
+
+
+def test_the_harness_in_front_of_a_real_replica(tmp_path):
+    """The whole chain on CPU: client -> session service -> scripted agent process -> proxy -> a tiny replica's Messages routes."""
+    import socket
+    import threading
+
+    import uvicorn
+
+    srv, tok, _ = _tiny_server()
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    server = uvicorn.Server(uvicorn.Config(srv.http_app(tok), host="127.0.0.1", port=port, log_level="warning"))
+    thread = threading.Thread(target=server.run, daemon=True)
+    thread.start()
+
+    async def go():
+        for _ in range(200):
+            if server.started:
+                break
+            await asyncio.sleep(0.05)
+        svc_kw = dict(require_summary_end=False)
+        h = Harness(f"http://127.0.0.1:{port}", tmp_path, env={"SCRIPTED_AGENT_MAX_TOKENS": "8"}, **svc_kw)
+        h.svc.model = "tiny"
+        async with h:
+            sid, status = await h.open(system="You answer in bytes.", model="tiny")
+            assert status == 200
+            for i in range(2):
+                status, events = await h.turn(sid, f"turn {i}: say something")
+                assert status == 200 and events[-1]["type"] == "result" and events[-1]["stop"] in ("end_turn", "refused")
+                assert events[-1]["usage"]["requests"] == 1 and events[-1]["usage"]["output_tokens"] >= 1
+            # (a random model's bytes do not survive decoding and re-encoding, so the second turn's prompt is not a token-exact
+            # continuation of the first and takes nothing from the prefix cache; a trained model's text does)
+            assert events[-1]["usage"]["context_limit"] == 1024 and events[-1]["usage"]["context_tokens"] > 60
+
+    try:
+        run(go())
+    finally:
+        server.should_exit = True
+        thread.join(timeout=10)
+        srv.close()
