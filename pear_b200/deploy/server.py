@@ -80,15 +80,35 @@ class DeployServer:
                 f'pear_deploy_generation_tokens_total{{model="{self.name}"}} {self.tokens_out}\n'
                 f'pear_deploy_busy_seconds_total{{model="{self.name}"}} {self.busy_s}\n')
 
+    def generate(self, ids: list[int], params, session=None, embeds=None, embeds_mask=None):
+        """The interface ``rollout/messages_api.py`` drives (a request object with ``output`` / ``finish`` / ``cached_prefix``): the
+        deploy engine decodes a fixed number of tokens, so the answer is cut at the first stop token here."""
+        from types import SimpleNamespace
+
+        from ..rollout.engine import FinishReason
+
+        if embeds is not None:
+            raise ValueError("the deploy engine takes text prompts")
+        toks = self.complete(list(ids), int(params.max_tokens), float(params.temperature), params.seed)["token_ids"]
+        cut = next((i for i, t in enumerate(toks) if t in params.stop_token_ids), None)
+        if cut is None:
+            return SimpleNamespace(output=toks, finish=FinishReason.LENGTH, cached_prefix=0)
+        return SimpleNamespace(output=toks[:cut + 1], finish=FinishReason.STOP, cached_prefix=0)
+
     def http_app(self):
         from fastapi import FastAPI
         from fastapi.responses import PlainTextResponse
 
-        app = FastAPI(title=f"pear_b200 deploy {self.name}")
+        from ..rollout import messages_api
 
-        @app.get("/v1/models")
-        def models() -> dict:
-            return {"data": [{"id": self.name, "object": "model"}]}
+        app = FastAPI(title=f"pear_b200 deploy {self.name}")
+        # GET /v1/models (with the context limit), POST /v1/messages and /v1/messages/count_tokens: what the agent harness
+        # (deploy/harness) asks of its model server
+        messages_api.register(app, self, self.tok, None, int(getattr(self.engine, "max_len", 0)) or None)
+
+        @app.get("/health")
+        def health() -> dict:
+            return {"ok": True}
 
         @app.get("/metrics", response_class=PlainTextResponse)
         def metrics() -> str:

@@ -54,8 +54,10 @@ class MessagesFrontend:
 
     def __init__(self, server, tokenizer, vision=None, max_model_len: Optional[int] = None):
         self.server, self.tokenizer, self.vision = server, tokenizer, vision
-        cfg = server.engine.cfg
-        self.max_model_len = int(max_model_len or cfg.num_blocks * cfg.block_size)
+        if max_model_len is None:  # what the paged cache holds of one sequence at most
+            cfg = server.engine.cfg
+            max_model_len = cfg.num_blocks * cfg.block_size
+        self.max_model_len = int(max_model_len)
 
     # -- prompt -----------------------------------------------------------------------------------------------------------
     def render(self, body: dict, with_rows: bool = True):

@@ -397,3 +397,36 @@ def test_the_harness_in_front_of_a_real_replica(tmp_path):
         server.should_exit = True
         thread.join(timeout=10)
         srv.close()
+
+
+def test_deploy_server_offers_the_messages_routes_over_its_one_session_engine():
+    """The deploy server (one checkpoint, one session at a time) is the model server the harness fronts in a deployment: the same
+    three routes over its engine's fixed-length decode, cut at the end-of-turn token. (A stand-in engine: the real one is a GPU
+    megakernel.)"""
+    from types import SimpleNamespace
+
+    from fastapi.testclient import TestClient
+
+    from pear_b200.deploy.server import DeployServer
+    from pear_b200.utils.tokenizer import ByteTokenizer
+
+    tok = ByteTokenizer()
+
+    class Engine:
+        max_len, temperature, seed = 256, 1.0, 0
+
+        def generate(self, prompt, max_new_tokens):
+            self.prompt = prompt.tolist()
+            text = tok.encode("ok then") + [tok.eos_id] + tok.encode("never read")
+            return SimpleNamespace(tokens=text[:max_new_tokens])
+
+    engine = Engine()
+    client = TestClient(DeployServer(engine, tok, name="served").http_app())
+    assert client.get("/v1/models").json()["data"][0] == {"id": "served", "object": "model", "max_model_len": 256} and client.get("/health").json()["ok"]
+    body = {"model": "served", "system": "s", "messages": [{"role": "user", "content": "go"}], "max_tokens": 32}
+    n = client.post("/v1/messages/count_tokens", json=body).json()["input_tokens"]
+    out = client.post("/v1/messages", json=body).json()
+    assert out["content"][0]["text"] == "ok then" and out["stop_reason"] == "end_turn" and out["usage"]["input_tokens"] == n == len(engine.prompt)
+    cut = client.post("/v1/messages", json={**body, "max_tokens": 3}).json()
+    assert cut["content"][0]["text"] == "ok " and cut["stop_reason"] == "max_tokens"
+    assert client.post("/v1/messages", json={**body, "messages": [{"role": "user", "content": "x" * 300}]}).status_code == 400
