@@ -33,7 +33,7 @@ class ScriptedUpstream:
     """A model server with the three Messages routes whose answers the test scripts."""
 
     def __init__(self, limit=2000):
-        self.limit, self.seen, self.answers, self.delay_on, self.dropped = limit, [], [], None, 0
+        self.limit, self.seen, self.answers, self.delay_on, self.dropped, self.answer_fn = limit, [], [], None, 0, None
 
     @staticmethod
     def tokens(body) -> int:
@@ -70,7 +70,9 @@ class ScriptedUpstream:
             except asyncio.CancelledError:
                 self.dropped += 1
                 raise
-        if self.answers:
+        if self.answer_fn is not None:
+            text, stop = self.answer_fn(body), "end_turn"
+        elif self.answers:
             text, stop = self.answers.pop(0)
         elif "about to be replaced by your summary" in flat:
             text, stop = "<summary>the robot moved the cup</summary>", "end_turn"
@@ -430,3 +432,152 @@ def test_deploy_server_offers_the_messages_routes_over_its_one_session_engine():
     cut = client.post("/v1/messages", json={**body, "max_tokens": 3}).json()
     assert cut["content"][0]["text"] == "ok " and cut["stop_reason"] == "max_tokens"
     assert client.post("/v1/messages", json={**body, "messages": [{"role": "user", "content": "x" * 300}]}).status_code == 400
+
+
+# -- the station: robot session in front of the harness ---------------------------------------------------------------------
+def _toward_target(body) -> str:
+    """A scripted policy: read the state out of the last turn's text and move toward (0.7, 0.6), at most 0.2 an axis."""
+    import re
+
+    text = " ".join(b.get("text", "") for b in UpstreamProxy.blocks(body["messages"][-1]["content"]) if b.get("type") == "text")
+    state = json.loads(re.findall(r"State: (\{.*?\})", text)[-1])
+    dx, dy = (max(-0.2, min(0.2, t - state[k])) for t, k in ((0.7, "x"), (0.6, "y")))
+    action = {"arm": {"dx": round(dx, 4), "dy": round(dy, 4), "dz": 0.0}, "gripper": {"opening": 0.5}}
+    return "The target is to the right.\n```json\n" + json.dumps(action) + "\n```"
+
+
+def test_action_parser_takes_only_a_whole_answer_that_ends_with_one_action_of_the_format():
+    from pear_b200.deploy.station.action_parser import parse_action
+    from pear_b200.deploy.station.robot import CARTESIAN
+
+    good = {"arm": {"dx": 0.1, "dy": 0, "dz": -0.05}, "gripper": {"opening": 1}}
+    fenced = lambda obj: "so:\n```json\n" + (obj if isinstance(obj, str) else json.dumps(obj)) + "\n```"  # noqa: E731
+    assert parse_action(fenced(good), CARTESIAN) == good
+    assert parse_action("```json\n{}\n```\nno, rather\n" + fenced(good), CARTESIAN) == good  # the last block counts
+    for bad in (fenced(good) + "\nand then some", "<think>hm</think>" + fenced(good), "no action here", fenced({"arm": good["arm"]}),
+                fenced({**good, "extra": {}}), fenced({"arm": {"dx": 0.1, "dy": 0}, "gripper": good["gripper"]}),
+                fenced({"arm": {"dx": True, "dy": 0, "dz": 0}, "gripper": good["gripper"]}), fenced({"arm": {"dx": 0.5, "dy": 0, "dz": 0}, "gripper": good["gripper"]}),
+                fenced('{"arm": {"dx": 0.1, "dx": 0.2, "dy": 0, "dz": 0}, "gripper": {"opening": 1}}'), fenced('{"arm": {"dx": NaN, "dy": 0, "dz": 0}, "gripper": {"opening": 1}}'),
+                fenced("{not json")):
+        with pytest.raises(ValueError):
+            parse_action(bad, CARTESIAN)
+
+
+def test_station_loop_executes_only_parsed_actions_records_turns_and_ends_requests_it_gives_up_on(tmp_path):
+    import threading
+    import time
+
+    from pear_b200.deploy.station.agent_loop import OperatorPaused, StationAgentLoop, system_prompt
+    from pear_b200.deploy.station.clients import ContextLimit, ModelClient, ModelOutput
+    from pear_b200.deploy.station.robot import CARTESIAN, SimulatedArm
+
+    class Scripted(ModelClient):
+        def __init__(self):
+            super().__init__("s")
+            self.script, self.inputs, self.cancelled, self.closed = [], [], 0, False
+
+        def infer(self, model_input, on_event, cancellation):
+            self.inputs.append(model_input)
+            item = self.script.pop(0)
+            if item == "hang":
+                while not cancellation.is_set():
+                    time.sleep(0.01)
+                raise InterruptedError("stopped")
+            if isinstance(item, Exception):
+                raise item
+            return ModelOutput(item, 0.01, {"output_tokens": 3})
+
+        def cancel(self):
+            self.cancelled += 1
+
+        def close(self):
+            self.closed = True
+
+    act = lambda dx, dy: "ok\n```json\n" + json.dumps({"arm": {"dx": dx, "dy": dy, "dz": 0.0}, "gripper": {"opening": 0.3}}) + "\n```"  # noqa: E731
+    arm, client, events = SimulatedArm(), Scripted(), []
+    loop = StationAgentLoop(arm, client, CARTESIAN, timeout_s=0.3, directory=str(tmp_path / "task"))
+    assert "```json" in system_prompt("put the cup away", CARTESIAN) and '"dx": <number>' in system_prompt("x", CARTESIAN)
+    on_event, never = (lambda kind, data: events.append((kind, data))), threading.Event()
+    client.script = [act(0.2, 0.2), "I would rather not say", act(0.2, 0.2), act(0.2, 0.2), "hang"]
+    r1 = loop.step(never, on_event)
+    assert r1.status == "completed" and arm.state()["x"] == 0.4 and arm.state()["opening"] == 0.3
+    r2 = loop.step(never, on_event)  # no action in the answer: nothing moves, the model is told next turn
+    assert r2.status == "rejected" and arm.moves == 1 and not loop.last_turn.dispatched
+    r3 = loop.step(never, on_event)
+    assert r3.status == "completed" and "was not sent to the robot" in client.inputs[2].text and "ended as rejected" in client.inputs[2].text
+    r4 = loop.step(never, on_event)  # x would be 0.8 + ... fine; y 0.8: still inside; one more would leave
+    assert r4.status == "completed" and "The last action completed." in client.inputs[3].text
+    t0 = time.time()
+    r5 = loop.step(never, on_event)  # the model hangs: the request is ended after the timeout, the turn fails, the session goes on
+    assert r5.status == "failed" and "did not answer within" in r5.detail and client.cancelled == 1 and time.time() - t0 < 5
+    client.script = [act(0.2, 0.2)]
+    arm.pos[:2] = (0.9, 0.9)
+    r6 = loop.step(never, on_event)  # 0.9 + 0.2: outside the workspace: the robot itself refuses a dispatched action
+    assert r6.status == "rejected" and loop.last_turn.dispatched and "workspace" in r6.detail
+    # the operator's stop ends the request in flight too
+    client.script = ["hang"]
+    stop = threading.Event()
+    threading.Timer(0.1, stop.set).start()
+    with pytest.raises(OperatorPaused):
+        loop.step(stop, on_event)
+    assert client.cancelled == 2 and loop.previous_result.status == "stopped"
+    # a conversation that cannot go on blocks the session for good
+    client.script = [ContextLimit("prompt is too long: 9 tokens > 8 maximum")]
+    with pytest.raises(ContextLimit):
+        loop.step(never, on_event)
+    with pytest.raises(ContextLimit):
+        loop.step(never, on_event)
+    assert len(client.inputs) == 8  # (the blocked step asked nobody)
+    records = [json.loads(x) for x in open(tmp_path / "task" / "turns.jsonl")]
+    assert [r["result"]["status"] for r in records] == ["completed", "rejected", "completed", "completed", "failed", "rejected", "stopped", "failed"]
+    assert records[0]["action"]["arm"]["dx"] == 0.2 and records[1]["action"] is None and records[0]["usage"] == {"output_tokens": 3}
+    assert len([f for f in os.listdir(tmp_path / "task") if f.endswith("_top.jpg")]) == 8
+    assert [k for k, _ in events[:6]] == ["phase", "observation", "phase", "model_output", "action", "phase"]
+    loop.close()
+    assert client.closed
+
+
+@pytest.mark.parametrize("kind", ["harness", "messages"])
+def test_a_simulated_arm_reaches_its_target_through_the_whole_deployment_chain(tmp_path, kind):
+    """station loop -> model client -> (session service -> agent process -> proxy ->) model server with a scripted policy."""
+    import threading
+
+    from pear_b200.deploy.station.agent_loop import StationAgentLoop, system_prompt
+    from pear_b200.deploy.station.clients import HarnessClient, MessagesClient
+    from pear_b200.deploy.station.robot import CARTESIAN, SimulatedArm
+
+    ready, stop, box = threading.Event(), threading.Event(), {}
+
+    async def serve():
+        up = await ScriptedUpstream(limit=3000).start()
+        up.answer_fn = _toward_target
+        async with Harness(up.url, tmp_path) as h:
+            box.update(up=up, upstream=up.url, service=h.url)
+            ready.set()
+            while not stop.is_set():
+                await asyncio.sleep(0.05)
+        await up.runner.cleanup()
+
+    thread = threading.Thread(target=lambda: asyncio.run(serve()), daemon=True)
+    thread.start()
+    assert ready.wait(30)
+    try:
+        arm = SimulatedArm()
+        prompt = system_prompt("Move the gripper over the green target.", CARTESIAN)
+        client = HarnessClient(box["service"], "m", prompt) if kind == "harness" else MessagesClient(box["upstream"], "m", prompt)
+        assert client.check()["status"] == "ok"
+        loop = StationAgentLoop(arm, client, CARTESIAN, timeout_s=60, directory=str(tmp_path / "task"), reference_images=(arm.observe().cameras["top"],))
+        never = threading.Event()
+        for _ in range(6):
+            if arm.distance() < 0.02:
+                break
+            assert loop.step(never, lambda k, d: None).status == "completed"
+        assert arm.distance() < 0.02 and arm.moves == 3  # 0.5 in x at 0.2 a turn
+        seen = box["up"].seen
+        assert seen[0]["system"] == prompt and seen[0]["messages"][0]["content"][0]["type"] == "image"  # the task's reference picture leads
+        assert sum(b["type"] == "image" for b in UpstreamProxy.blocks(seen[-1]["messages"][-1]["content"])) == 1  # the turn's camera
+        assert len(seen[-1]["messages"]) == 5  # the conversation so far: three user turns, two answers
+        loop.close()
+    finally:
+        stop.set()
+        thread.join(timeout=20)
