@@ -241,7 +241,9 @@ class UpstreamProxy:
     async def answer(self, request: web.Request, session: AgentSession, turn: Turn, kind: str, upstream_request: dict, outcome: dict) -> web.StreamResponse:
         counted = {k: upstream_request[k] for k in self.COUNTED_FIELDS if k in upstream_request}
         async with self.http.post(self.upstream + "/v1/messages/count_tokens", json=counted) as r:
-            r.raise_for_status()
+            if r.status != 200:  # the model server refuses the prompt itself (pictures without a vision encoder, a malformed block)
+                outcome.update(status=r.status, error="count_tokens refused")
+                return web.Response(status=r.status, body=await r.read(), content_type="application/json")
             prompt_tokens = int((await r.json())["input_tokens"])
         room = self.context_limit - prompt_tokens
         outcome.update(prompt_tokens=prompt_tokens)

@@ -436,24 +436,12 @@ def main(argv=None) -> int:
         servers = local
     vision = None
     if args.vision:
-        from ..loop.vision_encoder import VisionEncoder
-        from ..models import io as model_io
-        from ..models.vision import FamilyVisionConfig, FamilyVisionTower, VisionConfig, VisionTower
+        from ..loop.vision_encoder import build_vision_encoder
 
-        if args.vision == "checkpoint":
-            vcfg = model_io.load_vision_config(args.model)
-            if vcfg is None:
-                ap.error(f"{args.model} has no vision_config")
-            tower = FamilyVisionTower(vcfg)
-            own = dict(tower.state_dict())
-            for key, t in model_io.iter_model_tensors(args.model, only=lambda k: model_io.from_hf_name(k).startswith("visual.")):
-                own[model_io.from_hf_name(key)[len("visual."):]].copy_(t.to(torch.float32))
-        else:
-            hidden = model_io.load_config(args.model).hidden_size if args.model and not args.model.startswith("preset:") else 256
-            family = args.vision.startswith("family_")
-            vcfg = getattr(FamilyVisionConfig if family else VisionConfig, args.vision[len("family_"):] if family else args.vision)(out_hidden=hidden)
-            tower = (FamilyVisionTower if family else VisionTower)(vcfg).init_weights(0)
-        vision = VisionEncoder(tower)
+        try:
+            vision = build_vision_encoder(args.vision, args.model)
+        except ValueError as e:
+            ap.error(str(e))
     try:
         BenchmarkRun(cfg, LeastInFlightRouter(servers), load_tokenizer(args.tokenizer or args.model), args.model_name or args.model or args.replicas.split(",")[0],
                      args.out, args.dataset_dir, args.only, args.limit, vision=vision).run()

@@ -95,3 +95,28 @@ class VisionEncoder:
                 for i, key in todo:
                     out[i] = self.cache[key]
         return out
+
+
+def build_vision_encoder(preset: str, model_path: str = "", hidden: int = 0, device: str = "cpu") -> "VisionEncoder":
+    """The encoder a command-line option names: ``checkpoint`` (the family's tower with the model directory's sizes and
+    ``model.visual.*`` tensors), ``family_<preset>`` (that architecture, random) or a preset of the small plain ViT (``tiny``);
+    ``hidden`` is the decoder's width the rows are projected to (default: the model directory's)."""
+    from ..models import io as model_io
+    from ..models.vision import FamilyVisionConfig, FamilyVisionTower, VisionConfig, VisionTower
+
+    if preset == "checkpoint":
+        vcfg = model_io.load_vision_config(model_path)
+        if vcfg is None:
+            raise ValueError(f"{model_path} has no vision_config")
+        tower = FamilyVisionTower(vcfg)
+        own = dict(tower.state_dict())
+        with torch.no_grad():
+            for key, t in model_io.iter_model_tensors(model_path, only=lambda k: model_io.from_hf_name(k).startswith("visual.")):
+                own[model_io.from_hf_name(key)[len("visual."):]].copy_(t.to(torch.float32))
+    else:
+        if not hidden:
+            hidden = model_io.load_config(model_path).hidden_size if model_path and not model_path.startswith("preset:") else 256
+        family = preset.startswith("family_")
+        vcfg = getattr(FamilyVisionConfig if family else VisionConfig, preset[len("family_"):] if family else preset)(out_hidden=hidden)
+        tower = (FamilyVisionTower if family else VisionTower)(vcfg).init_weights(0)
+    return VisionEncoder(tower, device)

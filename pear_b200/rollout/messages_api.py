@@ -46,7 +46,7 @@ def picture_of(block: dict) -> np.ndarray:
     src = block.get("source") or {}
     if src.get("type") != "base64":
         raise ValueError("image blocks need a base64 source")
-    return np.asarray(Image.open(io.BytesIO(base64.b64decode(src["data"]))).convert("RGB"), dtype=np.uint8)
+    return np.array(Image.open(io.BytesIO(base64.b64decode(src["data"]))).convert("RGB"), dtype=np.uint8)  # (a writable copy)
 
 
 class MessagesFrontend:

@@ -397,6 +397,7 @@ def main(argv=None) -> int:
     ap.add_argument("--host-gb", type=float, default=0.0, help="host-DRAM tier of the KV / state cache in GiB (also: actor_rollout_ref.rollout.custom.lmcache.enable=true and .l1_size_gb=...)")
     ap.add_argument("--numa", default="auto", help="NUMA node to run on and allocate the host tier from: auto (the GPU's node), none, or a number")
     ap.add_argument("--drafter", default=None, help="directory whose mtp.* tensors are the (frozen) drafter of a model directory without one")
+    ap.add_argument("--vision", default="", help="vision encoder of the Messages routes' image blocks: checkpoint (the --model directory's tower), family_tiny, tiny")
     ap.add_argument("--check", action="store_true", help="build the replica, answer one request and exit (no HTTP server)")
     ap.add_argument("--sync-rank", type=int, default=-1, help="this replica's rank in the weight-sync process group (-1: no group)")
     ap.add_argument("--sync-world", type=int, default=0, help="size of the weight-sync group: the sending trainer rank + the replica ranks")
@@ -488,7 +489,12 @@ def main(argv=None) -> int:
         signal.signal(signal.SIGTERM, lambda *_: None)
         signal.signal(signal.SIGINT, lambda *_: None)
         # a request that can no longer finish (a peer rank is gone) must not keep a terminated replica alive
-        uvicorn.run(server.http_app(load_tokenizer(path)), host=args.host, port=args.port, log_level="warning", timeout_graceful_shutdown=3)
+        vision = None
+        if args.vision:
+            from ..loop.vision_encoder import build_vision_encoder
+
+            vision = build_vision_encoder(args.vision, path, hidden=server.engine.runner.cfg.hidden_size, device=str(device))
+        uvicorn.run(server.http_app(load_tokenizer(path), vision=vision), host=args.host, port=args.port, log_level="warning", timeout_graceful_shutdown=3)
         return 0
     finally:
         leave = getattr(server, "leave_sync_world", None)
