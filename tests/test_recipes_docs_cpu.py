@@ -60,8 +60,25 @@ def test_recipe_overrides_compose_against_the_shipped_configs(script, tmp_path):
         variants = [{"NODES": "10.0.0.1,10.0.0.2", "NODE_RANK": "0"}]
     for env in variants:
         for args in _record(script, tmp_path, {"RUN": str(tmp_path / "run"), **env}):
+            helpers = ("pear_b200.rollout.server", "pear_b200.deploy.station.cli")  # started beside the program that takes the overrides
+            if "-c" in args:
+                continue  # a readiness probe
+            if any(h in args for h in helpers):
+                module = next(h for h in helpers if h in args)
+                helptext = subprocess.run([sys.executable, "-m", module, "--help"], cwd=ROOT, capture_output=True, text=True, timeout=120).stdout
+                for a in args[args.index(module) + 1:]:
+                    if a.startswith("--"):
+                        assert a in helptext, f"{os.path.basename(script)} passes {a}, which {module} does not take"
+                continue
             assert args[-1] == "extra.key=1", "a recipe passes the caller's extra overrides on"
-            if "pear_b200.train.main" in args:
+            if "pear_b200.deploy.harness.service" in args:
+                from pear_b200.config.loader import compose
+
+                rest = args[args.index("pear_b200.deploy.harness.service") + 1:]
+                cfg = compose("agent_harness", [a for a in rest if a != "extra.key=1"])
+                assert str(cfg.audit_dir).startswith(str(tmp_path / "run"))
+                seen += 1
+            elif "pear_b200.train.main" in args:
                 cfg = _compose_trainer(args[args.index("pear_b200.train.main") + 1:])
                 assert str(cfg.run_dir) == str(tmp_path / "run")
                 seen += 1
