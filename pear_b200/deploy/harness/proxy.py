@@ -62,7 +62,9 @@ class RequestAudit:
 class EngineMetrics:
     """The model server's Prometheus text, read at most once an interval: what usage reports carry of the engine's state."""
 
-    KEPT = ("num_running", "num_waiting", "cache_hit_rate", "kv_blocks_used", "generation_tokens_total", "prompt_tokens_total")
+    # (the names of rollout/server.py's gauges and counters, without the ``pear_`` prefix)
+    KEPT = ("num_running", "num_waiting", "free_blocks", "cached_blocks", "generation_tokens_total", "prompt_tokens_total", "prefix_cache_queries_total",
+            "prefix_cache_hits_total", "spec_drafted_total", "spec_accepted_total", "deploy_generation_tokens_total", "deploy_busy_seconds_total")
 
     def __init__(self, http: aiohttp.ClientSession, url: str, interval_s: float):
         self.http, self.url, self.interval_s = http, url, interval_s

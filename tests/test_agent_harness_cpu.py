@@ -581,3 +581,33 @@ def test_a_simulated_arm_reaches_its_target_through_the_whole_deployment_chain(t
     finally:
         stop.set()
         thread.join(timeout=20)
+
+
+def test_messages_client_against_a_real_replica_says_when_an_answer_is_cut_and_when_the_context_is_full():
+    import threading
+
+    import numpy as np
+    from fastapi.testclient import TestClient
+
+    from pear_b200.deploy.station.clients import ContextLimit, MessagesClient, ModelInput
+
+    srv, tok, vision = _tiny_server(with_vision=True)
+    try:
+        http = TestClient(srv.http_app(tok, vision=vision))
+        client = MessagesClient("", "tiny", "You move an arm.", max_tokens=4, session=http)
+        assert client.check()["status"] == "ok" and client.check()["context_limit"] == 1024
+        assert MessagesClient("", "other", "s", session=http).check()["status"] == "offline"
+        frame = np.zeros((28, 28, 3), dtype=np.uint8)
+        never = threading.Event()
+        with pytest.raises(ValueError, match="cut"):  # a random model does not end its turn within four tokens
+            client.infer(ModelInput("Turn 1.", {"top": frame}, (frame,)), lambda k, d: None, never)
+        assert client.history == []  # a refused answer is not part of the conversation
+        with pytest.raises(ContextLimit, match="prompt is too long"):
+            client.infer(ModelInput("x" * 1200, {}, ()), lambda k, d: None, never)
+        stop = threading.Event()
+        stop.set()
+        with pytest.raises(InterruptedError):
+            client.infer(ModelInput("Turn 2.", {}, ()), lambda k, d: None, stop)
+        client.close()
+    finally:
+        srv.close()
