@@ -11,6 +11,7 @@ import threading
 
 from .agent_loop import StationAgentLoop, system_prompt
 from .clients import ContextLimit, HarnessClient, MessagesClient, SessionLost
+from .records import TaskRecords
 from .robot import CARTESIAN, SimulatedArm
 
 
@@ -31,11 +32,11 @@ def main(argv=None) -> int:
     if health.get("status") != "ok":
         raise SystemExit(f"the model is not available: {health}")
     loop = StationAgentLoop(arm, client, CARTESIAN, args.timeout_s, args.directory, reference_images=(arm.observe().cameras["top"],))
-    never = threading.Event()
+    never, records = threading.Event(), TaskRecords(args.directory)
     try:
         for i in range(args.steps):
             try:
-                result = loop.step(never, lambda kind, data: None)
+                result = loop.step(never, records.on_event)
             except (ContextLimit, SessionLost) as e:
                 print(json.dumps({"turn": i + 1, "blocked": str(e)}))
                 break

@@ -568,10 +568,19 @@ def test_a_simulated_arm_reaches_its_target_through_the_whole_deployment_chain(t
         assert client.check()["status"] == "ok"
         loop = StationAgentLoop(arm, client, CARTESIAN, timeout_s=60, directory=str(tmp_path / "task"), reference_images=(arm.observe().cameras["top"],))
         never = threading.Event()
+        from pear_b200.deploy.station.records import TaskRecords
+
+        records = TaskRecords(str(tmp_path / "task"))
         for _ in range(6):
             if arm.distance() < 0.02:
                 break
-            assert loop.step(never, lambda k, d: None).status == "completed"
+            assert loop.step(never, records.on_event).status == "completed"
+        events = [json.loads(x) for x in open(tmp_path / "task" / "events.jsonl")]
+        assert [e["type"] for e in events].count("action") == 3 and all("monotonic" in e for e in events)
+        usage = json.load(open(tmp_path / "task" / "context_usage.json"))
+        assert usage["turns"] == 3 and usage["output_tokens"] > 0 and len(usage["per_turn"]) == 3
+        if kind == "harness":  # the service reports the context against the model's limit
+            assert usage["context_limit"] == 3000 and 0 < usage["context_fraction"] < 1 and usage["compactions"] == 0
         assert arm.distance() < 0.02 and arm.moves == 3  # 0.5 in x at 0.2 a turn
         seen = box["up"].seen
         assert seen[0]["system"] == prompt and seen[0]["messages"][0]["content"][0]["type"] == "image"  # the task's reference picture leads
