@@ -1,4 +1,4 @@
-"""The Messages form of the model server: ``GET /v1/models``, ``POST /v1/messages`` (whole answers and event streams) and
+"""The Messages form of the model server: ``GET /v1/models``, ``POST /v1/messages`` (whole answers, and event streams whose text deltas go out as the engine produces tokens) and
 ``POST /v1/messages/count_tokens``, for agent CLIs that speak it.
 
 Upstream's agent harness sits between such a CLI and a serving stack that offers these three routes (the harness reads the
@@ -101,7 +101,8 @@ class MessagesFrontend:
     def count(self, body: dict) -> dict:
         return {"input_tokens": len(self.render(body, with_rows=False)[0])}
 
-    def run(self, body: dict):
+    def prepare(self, body: dict):
+        """(ids, embeds, mask, sampling parameters, stop ids, session) of a request; refuses a prompt that leaves no room."""
         tok = self.tokenizer
         ids, emb, mask = self.render(body)
         room = self.max_model_len - len(ids)
@@ -110,22 +111,86 @@ class MessagesFrontend:
         stops = (tok.eos_id,) + tuple(getattr(tok, "extra_stop_ids", ()))
         params = SamplingParams(max_tokens=min(int(body.get("max_tokens") or 256), room), temperature=float(body.get("temperature", 1.0)),
                                 top_p=float(body.get("top_p", 1.0)), top_k=int(body.get("top_k", -1) or -1), stop_token_ids=stops)
-        session = (body.get("metadata") or {}).get("user_id")
-        req = self.server.generate(ids, params, session=session, embeds=emb, embeds_mask=mask)
-        text = tok.decode([t for t in req.output if t not in stops], skip_special=True)
-        cached = int(getattr(req, "cached_prefix", 0))
-        usage = {"input_tokens": len(ids) - cached, "cache_read_input_tokens": cached, "cache_creation_input_tokens": 0, "output_tokens": len(req.output)}
+        return ids, emb, mask, params, stops, (body.get("metadata") or {}).get("user_id")
+
+    def message(self, body: dict, n_prompt: int, output: list, finish, cached: int, stops) -> dict:
+        text = self.tokenizer.decode([t for t in output if t not in stops], skip_special=True)
+        usage = {"input_tokens": n_prompt - cached, "cache_read_input_tokens": cached, "cache_creation_input_tokens": 0, "output_tokens": len(output)}
         return {"id": f"msg_{uuid.uuid4().hex[:24]}", "type": "message", "role": "assistant", "model": body.get("model", self.server.name),
-                "content": [{"type": "text", "text": text}], "stop_reason": END_TURN if req.finish == FinishReason.STOP else MAX_TOKENS,
+                "content": [{"type": "text", "text": text}], "stop_reason": END_TURN if finish == FinishReason.STOP else MAX_TOKENS,
                 "stop_sequence": None, "usage": usage}
+
+    def run(self, body: dict):
+        ids, emb, mask, params, stops, session = self.prepare(body)
+        req = self.server.generate(ids, params, session=session, embeds=emb, embeds_mask=mask)
+        return self.message(body, len(ids), req.output, req.finish, int(getattr(req, "cached_prefix", 0)), stops)
+
+    def can_stream(self) -> bool:
+        """Whether the server hands out the live request with its future (an in-process replica does; a lock-step leader
+        creates the request later, on every rank, and the deploy engine decodes a request whole)."""
+        return hasattr(self.server, "submit") and not hasattr(self.server, "channel") and hasattr(self.server, "futures")
+
+    def stream(self, prepared, body: dict, poll_s: float = 0.005) -> Iterator[bytes]:
+        """The answer as events while it is produced: the text decoded so far, minus what was sent, after every engine step
+        that added tokens (text that ends inside a multi-byte character waits for the rest). A request the engine aborts for a
+        weight sync goes on as a new request over the prompt plus what was produced."""
+        import time as _time
+
+        ids, emb, mask, params, stops, session = prepared
+        tok = self.tokenizer
+        produced: list[int] = []
+        sent, cached, finish, started = "", 0, None, False
+        head = self.message(body, len(ids), [], None, 0, stops)
+        while True:
+            left = params.max_tokens - len(produced)
+            prompt = ids + produced
+            e, m = emb, mask
+            if emb is not None and produced:  # the rows of the tokens produced so far are ordinary embeddings
+                e = torch.cat([emb, torch.zeros(len(produced), emb.shape[1])])
+                m = torch.cat([mask, torch.zeros(len(produced), dtype=torch.bool)])
+            import dataclasses
+
+            fut = self.server.submit(prompt, dataclasses.replace(params, max_tokens=left), session, e, m)
+            req = fut.request
+            while True:
+                done = fut.done()
+                out = produced + list(req.output)
+                if not started and (out or done):
+                    cached = int(getattr(req, "cached_prefix", 0))
+                    head["usage"].update(input_tokens=len(ids) - cached, cache_read_input_tokens=cached)
+                    yield self.frame("message_start", {"message": {**head, "content": [], "stop_reason": None}})
+                    yield self.frame("content_block_start", {"index": 0, "content_block": {"type": "text", "text": ""}})
+                    started = True
+                text = tok.decode([t for t in out if t not in stops], skip_special=True)
+                if not done and text.endswith("\ufffd"):
+                    text = text.rstrip("\ufffd")  # an unfinished character: wait for its remaining bytes
+                if len(text) > len(sent) and text.startswith(sent):
+                    yield self.frame("content_block_delta", {"index": 0, "delta": {"type": "text_delta", "text": text[len(sent):]}})
+                    sent = text
+                if done:
+                    break
+                _time.sleep(poll_s)
+            req = fut.result()
+            produced += list(req.output)
+            finish = req.finish
+            if finish != FinishReason.ABORTED or len(produced) >= params.max_tokens:
+                break
+            while self.server.engine.paused and not self.server.stop_flag:
+                _time.sleep(poll_s)
+        yield self.frame("content_block_stop", {"index": 0})
+        yield self.frame("message_delta", {"delta": {"stop_reason": END_TURN if finish == FinishReason.STOP else MAX_TOKENS, "stop_sequence": None},
+                                           "usage": {"output_tokens": len(produced)}})
+        yield self.frame("message_stop", {})
+
+    @staticmethod
+    def frame(kind: str, data: dict) -> bytes:
+        return f"event: {kind}\ndata: {json.dumps({'type': kind, **data})}\n\n".encode()
 
     @staticmethod
     def events(message: dict) -> Iterator[bytes]:
-        """The answer as the event stream of the Messages form: the engine answers requests whole, so the text arrives as one
-        delta between the opening and closing events a client's parser expects."""
-
-        def frame(kind: str, data: dict) -> bytes:
-            return f"event: {kind}\ndata: {json.dumps({'type': kind, **data})}\n\n".encode()
+        """A whole answer as the event stream of the Messages form (servers that cannot hand out a live request: the text
+        arrives as one delta between the opening and closing events a client's parser expects)."""
+        frame = MessagesFrontend.frame
 
         text = message["content"][0]["text"]
         head = {**message, "content": [], "stop_reason": None, "usage": {**message["usage"], "output_tokens": 0}}
@@ -165,6 +230,8 @@ def register(app, server, tokenizer, vision=None, max_model_len: Optional[int] =
     @app.post("/v1/messages")
     def messages(body: dict):
         try:
+            if body.get("stream") and front.can_stream():
+                return StreamingResponse(front.stream(front.prepare(body), body), media_type="text/event-stream")
             message = front.run(body)
         except (ValueError, OverflowError) as e:
             return JSONResponse(error_body("invalid_request_error", str(e)), status_code=400)

@@ -81,6 +81,7 @@ class RolloutServer:
         fut: Future = Future()
         with self.lock:
             req = self.engine.add_request(prompt, params, session, embeds=embeds, embeds_mask=embeds_mask, position_ids=position_ids)
+            fut.request = req  # (a streaming caller reads the tokens produced so far while the future is pending)
             if req.finish is not None:  # rejected by a paused engine
                 fut.set_result(req)
             else:

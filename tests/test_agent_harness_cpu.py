@@ -344,6 +344,15 @@ def test_messages_routes_of_a_replica_count_answer_stream_and_refuse_what_does_n
         assert [e["type"] for e in events][0] == "message_start" and events[-1]["type"] == "message_stop"
         text = "".join(e["delta"]["text"] for e in events if e["type"] == "content_block_delta")
         assert text == out["content"][0]["text"]
+        # tokens go out as the engine produces them: a longer answer arrives in several deltas that add up to the whole answer
+        longer = {**body, "max_tokens": 48}
+        whole = client.post("/v1/messages", json=longer).json()
+        events = [json.loads(line[5:]) for line in client.post("/v1/messages", json={**longer, "stream": True}).text.splitlines() if line.startswith("data:")]
+        deltas = [e["delta"]["text"] for e in events if e["type"] == "content_block_delta"]
+        assert len(deltas) > 1 and "".join(deltas) == whole["content"][0]["text"]
+        closing = next(e for e in events if e["type"] == "message_delta")
+        assert closing["delta"]["stop_reason"] == whole["stop_reason"] and closing["usage"]["output_tokens"] == whole["usage"]["output_tokens"]
+        assert events[0]["message"]["usage"]["input_tokens"] + events[0]["message"]["usage"]["cache_read_input_tokens"] == n
         # a picture: placeholders are counted, rows are computed by the encoder, and the answer differs from the text-only one's prompt
         with_picture = {**body, "messages": [{"role": "user", "content": [{"type": "text", "text": "hello"},
                                                                           {"type": "image", "source": {"type": "base64", "media_type": "image/jpeg", "data": jpeg(size=(28, 28))}}]}]}
